@@ -1,0 +1,350 @@
+// Python bindings (torch extension `triune_b200._C`). Thin argument checking + stream plumbing; all
+// device work is in the .cu translation units.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "elementwise/elementwise.cuh"
+#include "gemm/tc_gemm.cuh"
+#include "gla/gla.cuh"
+#include "quant/quant.cuh"
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline const __nv_bfloat16* bf(const Tensor& t) { return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr()); }
+inline __nv_bfloat16* bfm(Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+inline const __nv_bfloat16* bf_opt(const c10::optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<const __nv_bfloat16*>(t->data_ptr()) : nullptr;
+}
+
+void check_bf16_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+
+// C[b] = alpha * op(A[b]) * op(B[b])^T with the fused epilogue. a: [batch?, M, K] (or [batch?, K, M] when
+// a_mn_major), b: [batch?, N, K] (or [batch?, K, N] when b_mn_major). Inner dims must be contiguous.
+void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool b_mn_major, int64_t mode, int64_t flags,
+             double alpha, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& aux_in,
+             const c10::optional<Tensor>& aux_out, const c10::optional<Tensor>& row_scale,
+             const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& group_offsets,
+             const c10::optional<Tensor>& status) {
+  check_bf16_cuda(a, "a");
+  check_bf16_cuda(b, "b");
+  TORCH_CHECK(c.is_cuda(), "c must be CUDA");
+  TORCH_CHECK(a.stride(-1) == 1 && b.stride(-1) == 1 && c.stride(-1) == 1, "inner dims must be contiguous");
+  c10::cuda::CUDAGuard guard(a.device());
+  tb::GemmArgs g{};
+  g.A = bf(a);
+  g.B = bf(b);
+  g.C = c.data_ptr();
+  g.a_mn_major = a_mn_major;
+  g.b_mn_major = b_mn_major;
+  g.mode = (int)mode;
+  g.flags = (int)flags;
+  if (c.scalar_type() == at::kFloat) g.flags |= tb::GF_OUT_F32;
+  else TORCH_CHECK(c.scalar_type() == at::kBFloat16, "c must be bf16 or fp32");
+  g.alpha = (float)alpha;
+  const int ad = a.dim(), bd = b.dim(), cd = c.dim();
+  TORCH_CHECK(ad >= 2 && bd >= 2 && cd >= 2, "operands must be at least 2-D");
+  g.lda = a.stride(-2);
+  g.ldb = b.stride(-2);
+  g.ldc = c.stride(-2);
+  g.strideA = ad == 3 ? a.stride(0) : 0;
+  g.strideB = bd == 3 ? b.stride(0) : 0;
+  g.strideC = cd == 3 ? c.stride(0) : 0;
+  g.batch = cd == 3 ? (int)c.size(0) : 1;
+  g.M = (int)c.size(-2);
+  g.N = (int)c.size(-1);
+  if (mode == tb::GEMM_GROUPED_K) {
+    g.K = (int)a.size(-2);  // total rows being reduced over
+    TORCH_CHECK(a.size(-2) == b.size(-2), "grouped-K operands must share the row dimension");
+    TORCH_CHECK(a.size(-1) == g.M && b.size(-1) == g.N, "grouped-K: c[g] is [a.cols, b.cols]");
+  } else {
+    g.K = (int)(a_mn_major ? a.size(-2) : a.size(-1));
+    const int64_t kb = b_mn_major ? b.size(-2) : b.size(-1);
+    TORCH_CHECK(kb == g.K, "reduction dims differ: ", g.K, " vs ", kb);
+    const int64_t am = a_mn_major ? a.size(-1) : a.size(-2);
+    const int64_t bn = b_mn_major ? b.size(-1) : b.size(-2);
+    TORCH_CHECK(am == g.M, "a rows (", am, ") != c rows (", g.M, ")");
+    TORCH_CHECK(bn == g.N, "b rows (", bn, ") != c cols (", g.N, ")");
+  }
+  if (mode == tb::GEMM_GROUPED_M) {
+    TORCH_CHECK(bd == 3, "grouped-M: b must be [groups, N, K]");
+    g.batch = (int)b.size(0);
+    g.strideB = b.stride(0);
+  }
+  if (bias.has_value() && bias->defined()) {
+    check_bf16_cuda(*bias, "bias");
+    g.bias = bf(*bias);
+    g.bias_stride = bias->dim() == 2 ? bias->stride(0) : 0;
+  }
+  if (aux_in.has_value() && aux_in->defined()) {
+    check_bf16_cuda(*aux_in, "aux_in");
+    TORCH_CHECK(aux_in->stride(-2) == g.ldc, "aux_in must share c's layout");
+    g.aux_in = bf(*aux_in);
+  }
+  if (aux_out.has_value() && aux_out->defined()) {
+    check_bf16_cuda(*aux_out, "aux_out");
+    TORCH_CHECK(aux_out->stride(-2) == g.ldc, "aux_out must share c's layout");
+    g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out->data_ptr());
+  }
+  if (row_scale.has_value() && row_scale->defined()) {
+    TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous(), "row_scale must be fp32");
+    g.row_scale = row_scale->data_ptr<float>();
+  }
+  if (tile_group.has_value() && tile_group->defined()) {
+    TORCH_CHECK(tile_group->scalar_type() == at::kInt, "tile_group must be int32");
+    g.tile_group = tile_group->data_ptr<int>();
+  }
+  if (group_offsets.has_value() && group_offsets->defined()) {
+    TORCH_CHECK(group_offsets->scalar_type() == at::kInt, "group_offsets must be int32");
+    g.group_offsets = group_offsets->data_ptr<int>();
+  }
+  if (status.has_value() && status->defined()) {
+    TORCH_CHECK(status->scalar_type() == at::kInt, "status must be int32");
+    g.status = status->data_ptr<int>();
+  }
+  tb::launch_tc_gemm(g, cur_stream());
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& res, const Tensor& w, double eps) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous inputs required");
+  const int d = (int)x.size(-1);
+  TORCH_CHECK(d % 8 == 0 && d <= 2048, "rmsnorm kernel supports d % 8 == 0, d <= 2048");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = (int)(x.numel() / d);
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows}, x.options().dtype(at::kFloat));
+  Tensor sum_out;
+  const bool has_res = res.has_value() && res->defined();
+  if (has_res) {
+    TORCH_CHECK(res->is_contiguous() && res->sizes() == x.sizes(), "residual shape mismatch");
+    sum_out = torch::empty_like(x);
+  }
+  tb::launch_rmsnorm_fwd(bf(x), has_res ? bf(*res) : nullptr, bf(w), bfm(y), has_res ? bfm(sum_out) : nullptr,
+                         rstd.data_ptr<float>(), rows, d, (float)eps, cur_stream());
+  return {y, rstd, has_res ? sum_out : Tensor()};
+}
+
+std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd,
+                                const c10::optional<Tensor>& dres) {
+  check_bf16_cuda(x, "x");
+  const int d = (int)x.size(-1);
+  const int rows = (int)(x.numel() / d);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = torch::empty_like(x);
+  Tensor dw = torch::zeros({d}, x.options().dtype(at::kFloat));
+  Tensor dyc = dy.contiguous();
+  const bool has = dres.has_value() && dres->defined();
+  Tensor drc = has ? dres->contiguous() : Tensor();
+  tb::launch_rmsnorm_bwd(bf(x), bf(w), bf(dyc), rstd.data_ptr<float>(), has ? bf(drc) : nullptr, bfm(dx),
+                         dw.data_ptr<float>(), rows, d, cur_stream());
+  return {dx, dw};
+}
+
+// in: [tokens, ld] with q at col 0 and k at col k_off; returns [tokens, 2, H, D].
+Tensor qk_prep_fwd(const Tensor& in, int64_t k_off, const c10::optional<Tensor>& cs, const c10::optional<Tensor>& sn,
+                   int64_t T, int64_t H, int64_t D) {
+  check_bf16_cuda(in, "in");
+  TORCH_CHECK(in.dim() == 2 && in.stride(1) == 1, "in must be [tokens, ld]");
+  TORCH_CHECK(D == 64 || D == 128, "head_dim must be 64 or 128");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t tokens = in.size(0);
+  Tensor out = torch::empty({tokens, 2, H, D}, in.options());
+  const bool rope = cs.has_value() && cs->defined();
+  tb::launch_qk_prep_fwd(bf(in), in.stride(0), (int)k_off, bfm(out), rope ? cs->data_ptr<float>() : nullptr,
+                         rope ? sn->data_ptr<float>() : nullptr, tokens, (int)T, (int)H, (int)D, cur_stream());
+  return out;
+}
+
+void qk_prep_bwd(const Tensor& in, int64_t k_off, const Tensor& dout, Tensor& d_in, const c10::optional<Tensor>& cs,
+                 const c10::optional<Tensor>& sn, int64_t T, int64_t H, int64_t D) {
+  check_bf16_cuda(in, "in");
+  check_bf16_cuda(dout, "dout");
+  TORCH_CHECK(dout.is_contiguous(), "dout must be contiguous");
+  c10::cuda::CUDAGuard guard(in.device());
+  const bool rope = cs.has_value() && cs->defined();
+  tb::launch_qk_prep_bwd(bf(in), in.stride(0), (int)k_off, bf(dout), bfm(d_in), d_in.stride(0),
+                         rope ? cs->data_ptr<float>() : nullptr, rope ? sn->data_ptr<float>() : nullptr, in.size(0),
+                         (int)T, (int)H, (int)D, cur_stream());
+}
+
+Tensor ce_fwd_bwd(Tensor& logits, const Tensor& targets, int64_t ignore_index, double grad_scale) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [rows, V]");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous(), "targets must be int64");
+  TORCH_CHECK(logits.stride(0) % 8 == 0, "logits row stride must be a multiple of 8");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor loss = torch::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  tb::launch_ce_fwd_bwd(bfm(logits), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), loss.data_ptr<float>(),
+                        (int)logits.size(0), (int)logits.size(1), ignore_index, (float)grad_scale, cur_stream());
+  return loss;
+}
+
+Tensor gather_rows(const Tensor& src, const Tensor& row_src, const c10::optional<Tensor>& row_scale) {
+  check_bf16_cuda(src, "src");
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.size(1) % 8 == 0, "src must be [rows, width%8==0]");
+  TORCH_CHECK(row_src.scalar_type() == at::kInt, "row_src must be int32");
+  c10::cuda::CUDAGuard guard(src.device());
+  Tensor dst = torch::empty({row_src.size(0), src.size(1)}, src.options());
+  const bool has = row_scale.has_value() && row_scale->defined();
+  tb::launch_gather_rows(bfm(dst), bf(src), row_src.data_ptr<int>(), has ? row_scale->data_ptr<float>() : nullptr,
+                         (int)row_src.size(0), (int)src.size(1), cur_stream());
+  return dst;
+}
+
+Tensor combine_rows(const Tensor& src, const Tensor& pos, const c10::optional<Tensor>& w,
+                    const c10::optional<Tensor>& add, double add_scale) {
+  check_bf16_cuda(src, "src");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && pos.dim() == 2 && pos.is_contiguous(), "pos must be int32 [tokens,k]");
+  c10::cuda::CUDAGuard guard(src.device());
+  const int tokens = (int)pos.size(0), k = (int)pos.size(1), width = (int)src.size(1);
+  Tensor out = torch::empty({tokens, width}, src.options());
+  const bool hw = w.has_value() && w->defined();
+  const bool ha = add.has_value() && add->defined();
+  if (hw) TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous(), "w must be fp32 contiguous");
+  if (ha) TORCH_CHECK(add->is_contiguous(), "add must be contiguous");
+  tb::launch_combine_rows(bfm(out), bf(src), pos.data_ptr<int>(), hw ? w->data_ptr<float>() : nullptr,
+                          ha ? bf(*add) : nullptr, (float)add_scale, tokens, k, width, cur_stream());
+  return out;
+}
+
+Tensor row_dots(const Tensor& a, const Tensor& b, const Tensor& pos) {
+  check_bf16_cuda(a, "a");
+  check_bf16_cuda(b, "b");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && pos.is_contiguous(), "contiguous inputs required");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor dots = torch::empty({pos.size(0), pos.size(1)}, a.options().dtype(at::kFloat));
+  tb::launch_row_dots(dots.data_ptr<float>(), bf(a), bf(b), pos.data_ptr<int>(), (int)pos.size(0), (int)pos.size(1),
+                      (int)a.size(1), cur_stream());
+  return dots;
+}
+
+void adamw_flat(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, const c10::optional<Tensor>& param_bf16,
+                double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+                const c10::optional<Tensor>& grad_scale_ptr, double grad_scale) {
+  TORCH_CHECK(master.scalar_type() == at::kFloat && master.is_contiguous(), "master must be fp32 contiguous");
+  TORCH_CHECK(grad.is_contiguous() && grad.numel() == master.numel(), "grad shape mismatch");
+  c10::cuda::CUDAGuard guard(master.device());
+  const bool gf32 = grad.scalar_type() == at::kFloat;
+  TORCH_CHECK(gf32 || grad.scalar_type() == at::kBFloat16, "grad must be fp32 or bf16");
+  const float bc1 = 1.0f - (float)std::pow(beta1, (double)step);
+  const float bc2 = 1.0f - (float)std::pow(beta2, (double)step);
+  const bool hp = param_bf16.has_value() && param_bf16->defined();
+  const bool hs = grad_scale_ptr.has_value() && grad_scale_ptr->defined();
+  tb::launch_adamw_flat(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), gf32,
+                        hp ? reinterpret_cast<__nv_bfloat16*>(param_bf16->data_ptr()) : nullptr, master.numel(),
+                        (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, bc1, bc2,
+                        hs ? grad_scale_ptr->data_ptr<float>() : nullptr, (float)grad_scale, cur_stream());
+}
+
+void sumsq(const Tensor& x, Tensor& out) {
+  TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat, "sumsq: contiguous x, fp32 out");
+  c10::cuda::CUDAGuard guard(x.device());
+  tb::launch_sumsq(x.data_ptr(), x.scalar_type() == at::kFloat, x.numel(), out.data_ptr<float>(), cur_stream());
+}
+
+void muon_momentum(Tensor& mom, const Tensor& grad, Tensor& u_out, double beta, bool nesterov,
+                   const c10::optional<Tensor>& grad_scale_ptr) {
+  c10::cuda::CUDAGuard guard(mom.device());
+  const bool hs = grad_scale_ptr.has_value() && grad_scale_ptr->defined();
+  tb::launch_muon_momentum(mom.data_ptr<float>(), grad.data_ptr(), grad.scalar_type() == at::kFloat, bfm(u_out),
+                           mom.numel(), (float)beta, nesterov, hs ? grad_scale_ptr->data_ptr<float>() : nullptr,
+                           cur_stream());
+}
+
+void muon_apply(Tensor& master, const Tensor& o, const c10::optional<Tensor>& param_bf16, double lr, double wd,
+                double scale) {
+  c10::cuda::CUDAGuard guard(master.device());
+  const bool hp = param_bf16.has_value() && param_bf16->defined();
+  tb::launch_muon_apply(master.data_ptr<float>(), bf(o),
+                        hp ? reinterpret_cast<__nv_bfloat16*>(param_bf16->data_ptr()) : nullptr, master.numel(),
+                        (float)lr, (float)wd, (float)scale, cur_stream());
+}
+
+void axpby_bf16(Tensor& x, const Tensor& y, double a, double b) {
+  c10::cuda::CUDAGuard guard(x.device());
+  tb::launch_axpby_bf16(bfm(x), bf(y), (float)a, (float)b, x.numel(), cur_stream());
+}
+
+Tensor triangular_adamw(const Tensor& S, Tensor& m, Tensor& v, double beta1, double beta2, double eps, int64_t step,
+                        bool triu) {
+  TORCH_CHECK(S.scalar_type() == at::kFloat && S.is_contiguous() && S.dim() == 3 && S.size(1) == S.size(2),
+              "S must be fp32 [n, r, r]");
+  c10::cuda::CUDAGuard guard(S.device());
+  Tensor delta = torch::empty_like(S);
+  tb::launch_triangular_adamw(S.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), delta.data_ptr<float>(),
+                              (int)S.size(0), (int)S.size(1), (float)beta1, (float)beta2, (float)eps,
+                              1.0f - (float)std::pow(beta1, (double)step), 1.0f - (float)std::pow(beta2, (double)step),
+                              triu, cur_stream());
+  return delta;
+}
+
+void steer_update(Tensor& P, const Tensor& G, double momentum, double steer) {
+  c10::cuda::CUDAGuard guard(P.device());
+  tb::launch_steer_update(P.data_ptr<float>(), G.data_ptr<float>(), P.numel(), (float)momentum, (float)steer,
+                          cur_stream());
+}
+
+std::vector<Tensor> route_tiers(const Tensor& logits, double threshold) {
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.is_contiguous() && logits.size(-1) == 3, "logits [rows,3]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor tiers = torch::empty({logits.size(0)}, logits.options().dtype(at::kInt));
+  Tensor flag = torch::ones({1}, logits.options().dtype(at::kInt));
+  tb::launch_route_tiers(logits.data_ptr<float>(), tiers.data_ptr<int>(), flag.data_ptr<int>(), (int)logits.size(0),
+                         (float)threshold, cur_stream());
+  return {tiers, flag};
+}
+
+Tensor neuron_heatmap(const Tensor& act, int64_t num_bins) {
+  TORCH_CHECK(act.scalar_type() == at::kFloat && act.is_contiguous(), "act must be fp32 contiguous");
+  c10::cuda::CUDAGuard guard(act.device());
+  Tensor scratch = torch::empty({num_bins}, act.options());
+  Tensor rgba = torch::empty({num_bins}, act.options().dtype(at::kInt));
+  tb::launch_neuron_heatmap(act.data_ptr<float>(), act.numel(), (int)num_bins, scratch.data_ptr<float>(),
+                            reinterpret_cast<uint32_t*>(rgba.data_ptr<int>()), cur_stream());
+  return rgba;
+}
+
+Tensor tier_render(const Tensor& act, const Tensor& tiers) {
+  TORCH_CHECK(act.scalar_type() == at::kFloat && act.is_contiguous() && act.dim() == 2, "act must be fp32 [rows,w]");
+  c10::cuda::CUDAGuard guard(act.device());
+  Tensor rgba = torch::empty({act.size(0), act.size(1)}, act.options().dtype(at::kInt));
+  tb::launch_tier_render(act.data_ptr<float>(), tiers.data_ptr<int>(), reinterpret_cast<uint32_t*>(rgba.data_ptr<int>()),
+                         (int)act.size(0), (int)act.size(1), cur_stream());
+  return rgba;
+}
+
+}  // namespace
+
+void register_gla(pybind11::module& m);
+void register_quant(pybind11::module& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("tc_gemm", &tc_gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("qk_prep_fwd", &qk_prep_fwd);
+  m.def("qk_prep_bwd", &qk_prep_bwd);
+  m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("gather_rows", &gather_rows);
+  m.def("combine_rows", &combine_rows);
+  m.def("row_dots", &row_dots);
+  m.def("adamw_flat", &adamw_flat);
+  m.def("sumsq", &sumsq);
+  m.def("muon_momentum", &muon_momentum);
+  m.def("muon_apply", &muon_apply);
+  m.def("axpby_bf16", &axpby_bf16);
+  m.def("triangular_adamw", &triangular_adamw);
+  m.def("steer_update", &steer_update);
+  m.def("route_tiers", &route_tiers);
+  m.def("neuron_heatmap", &neuron_heatmap);
+  m.def("tier_render", &tier_render);
+  register_gla(m);
+  register_quant(m);
+}

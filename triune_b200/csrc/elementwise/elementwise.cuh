@@ -1,0 +1,71 @@
+// Launchers of the bandwidth-bound kernels (normalisation, feature map, loss, MoE data movement,
+// optimizer updates, quantisation helpers). All pointers are device pointers; all launches are
+// asynchronous on the given stream.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+// y = rmsnorm(x [+ res]) * w ; if res != null also writes sum_out = x + res. d % 8 == 0, d <= 2048.
+void launch_rmsnorm_fwd(const __nv_bfloat16* x, const __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y,
+                        __nv_bfloat16* sum_out, float* rstd, int rows, int d, float eps, cudaStream_t s);
+// dx = d(rmsnorm)/dx * dy [+ dres]; dw (fp32, pre-zeroed or accumulating) += sum_rows dy * xhat.
+void launch_rmsnorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy, const float* rstd,
+                        const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw, int rows, int d, cudaStream_t s);
+
+void launch_qk_prep_fwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, __nv_bfloat16* out, const float* cs,
+                        const float* sn, long long tokens, int T, int H, int D, cudaStream_t s);
+void launch_qk_prep_bwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, const __nv_bfloat16* dout,
+                        __nv_bfloat16* d_in, long long d_in_ld, const float* cs, const float* sn, long long tokens,
+                        int T, int H, int D, cudaStream_t s);
+
+// Row-wise cross entropy over bf16 logits [rows, V] (row stride ld). Writes per-row loss (0 for ignored
+// rows) and, when grad_scale != 0, overwrites the logits with grad_scale * (softmax - onehot).
+void launch_ce_fwd_bwd(__nv_bfloat16* logits, long long ld, const long long* targets, float* row_loss, int rows, int V,
+                       long long ignore_index, float grad_scale, cudaStream_t s);
+
+// dst[r] = scale[r] * src[row_src[r]] (zero row when row_src[r] < 0). Rows of `width` bf16 (width % 8 == 0).
+void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,
+                        int dst_rows, int width, cudaStream_t s);
+// out[t] = sum_j w[t,j] * src[pos[t,j]] (+ add_scale * add[t]); pos < 0 skips the term. w may be null (=1).
+void launch_combine_rows(__nv_bfloat16* out, const __nv_bfloat16* src, const int* pos, const float* w,
+                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, cudaStream_t s);
+// dots[t,j] = <a[t], b[pos[t,j]]> (0 when pos < 0).
+void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b, const int* pos, int tokens, int k,
+                     int width, cudaStream_t s);
+
+// Fused AdamW over a flat shard: fp32 master p, moments m, v; grads bf16 or fp32; writes bf16 copy.
+// grad_scale is read from device memory (clip coefficient) when grad_scale_ptr != null.
+void launch_adamw_flat(float* master, float* m, float* v, const void* grad, bool grad_is_f32, __nv_bfloat16* param_bf16,
+                       long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                       float bias_corr1, float bias_corr2, const float* grad_scale_ptr, float grad_scale,
+                       cudaStream_t s);
+// sum of squares of a flat buffer accumulated into out[0] (fp32 atomic per block).
+void launch_sumsq(const void* x, bool is_f32, long long n, float* out, cudaStream_t s);
+
+// Muon momentum: M = beta*M + G; U = nesterov ? G + beta*M : M (bf16 out for the polar iteration).
+void launch_muon_momentum(float* mom, const void* grad, bool grad_is_f32, __nv_bfloat16* u_out, long long n, float beta,
+                          bool nesterov, const float* grad_scale_ptr, cudaStream_t s);
+// W_master = W_master * (1 - lr*wd) - lr*scale*O ; also refresh bf16 copy.
+void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* param_bf16, long long n, float lr,
+                       float wd, float scale, cudaStream_t s);
+// X = a*X + Y (bf16, elementwise) used by the Newton-Schulz blend when not fused in a GEMM epilogue.
+void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s);
+
+// Batched triangular AdamW on [nmat, r1, r1] cores (fp32 state), optional upper-triangular mask.
+void launch_triangular_adamw(const float* S, float* m, float* v, float* delta, int nmat, int r1, float beta1,
+                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, cudaStream_t s);
+// P = momentum*P + steer*(G-P)
+void launch_steer_update(float* P, const float* G, long long n, float momentum, float steer, cudaStream_t s);
+
+// 3-way tier router: tiers[r] from logits[r,3]; all_reflex flag (int) set to 0 if any row is not tier 0.
+void launch_route_tiers(const float* logits, int* tiers, int* all_reflex, int rows, float threshold, cudaStream_t s);
+// |act| binned into num_bins, max-normalised, ABGR-packed colours.
+void launch_neuron_heatmap(const float* act, long long n, int num_bins, float* bin_scratch, uint32_t* rgba,
+                           cudaStream_t s);
+// act [rows,width] fp32 + tiers -> RGBA8 [rows,width].
+void launch_tier_render(const float* act, const int* tiers, uint32_t* rgba, int rows, int width, cudaStream_t s);
+
+}  // namespace tb

@@ -1,0 +1,509 @@
+// Cross-entropy with in-place gradient, MoE row movement (gather / weighted combine / row dots), flat
+// optimizer updates (AdamW, Muon momentum and apply, triangular AdamW core, steer update) and the
+// small routing / visualisation kernels of the native engine.
+//
+// Reference semantics: triune/kernels/fast_cross_entropy.py:20-220 (CE, in-place chunk gradient),
+// triune/model/moe.py:385-437 (capacity gather, weighted index_add), triune/kernels/fast_triangular.py:23-88,
+// csrc/kernels/muon.cu:26-99, csrc/kernels/centroid_steer.cu:48-114, csrc/kernels/router.cu:24-82,
+// csrc/engine/engine.cpp:314-414 of the reference project.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "../common/ptx.cuh"
+#include "elementwise.cuh"
+
+namespace tb {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+  t = warp_sum(t);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : -FLT_MAX;
+  t = warp_max(t);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+// One block per row. Pass 1: online max / sum-exp over 16-byte vectors; pass 2 (second read hits L2):
+// write grad_scale * (softmax - onehot) in place.
+constexpr int CE_THREADS = 256;
+__global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld,
+                                                                const long long* __restrict__ targets,
+                                                                float* __restrict__ row_loss, int V,
+                                                                long long ignore_index, float grad_scale) {
+  __shared__ float red[CE_THREADS / 32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lp = logits + row * ld;
+  const long long tgt = targets[row];
+  const int nvec = V >> 3;
+  uint4* lv = reinterpret_cast<uint4*>(lp);
+  if (tgt == ignore_index) {
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (grad_scale != 0.f) {
+      for (int v = threadIdx.x; v < nvec; v += CE_THREADS) lv[v] = make_uint4(0, 0, 0, 0);
+      for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) lp[i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  float mx = -FLT_MAX, sm = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    uint4 x = lv[v];
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(x2[j]);
+      f[2 * j] = t.x;
+      f[2 * j + 1] = t.y;
+    }
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > mx) {
+      sm *= __expf(mx - lm);
+      mx = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm += __expf(f[j] - mx);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) {
+    float f = __bfloat162float(lp[i]);
+    if (f > mx) {
+      sm *= __expf(mx - f);
+      mx = f;
+    }
+    sm += __expf(f - mx);
+  }
+  const float gmx = block_max<CE_THREADS>(mx, red);
+  sm *= __expf(mx - gmx);
+  const float gsm = block_sum<CE_THREADS>(sm, red);
+  const float lse = gmx + logf(gsm);
+  if (threadIdx.x == 0) row_loss[row] = lse - __bfloat162float(lp[tgt]);
+  if (grad_scale == 0.f) return;
+  __syncthreads();  // the target logit above is read before anyone overwrites it
+  const float inv = grad_scale / gsm;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    uint4 x = lv[v];
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(x2[j]);
+      f[2 * j] = __expf(t.x - gmx) * inv;
+      f[2 * j + 1] = __expf(t.y - gmx) * inv;
+    }
+    const long long base = (long long)v * 8;
+    if (tgt >= base && tgt < base + 8) f[tgt - base] -= grad_scale;
+    uint4 o;
+    o.x = pack_bf16x2(f[0], f[1]);
+    o.y = pack_bf16x2(f[2], f[3]);
+    o.z = pack_bf16x2(f[4], f[5]);
+    o.w = pack_bf16x2(f[6], f[7]);
+    lv[v] = o;
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) {
+    float f = __expf(__bfloat162float(lp[i]) - gmx) * inv;
+    if (i == tgt) f -= grad_scale;
+    lp[i] = __float2bfloat16(f);
+  }
+}
+
+// ---------------------------------------------------------------- MoE row movement
+__global__ void __launch_bounds__(256) gather_rows_kernel(__nv_bfloat16* __restrict__ dst,
+                                                          const __nv_bfloat16* __restrict__ src,
+                                                          const int* __restrict__ row_src,
+                                                          const float* __restrict__ row_scale, int dst_rows,
+                                                          int width) {
+  const int nvec = width >> 3;
+  const long long total = (long long)dst_rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / nvec), v = (int)(i % nvec);
+    const int s = row_src[r];
+    uint4 o = make_uint4(0, 0, 0, 0);
+    if (s >= 0) {
+      o = reinterpret_cast<const uint4*>(src + (long long)s * width)[v];
+      if (row_scale) {
+        const float sc = row_scale[r];
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(o2[j]);
+          o2[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+      }
+    }
+    reinterpret_cast<uint4*>(dst + (long long)r * width)[v] = o;
+  }
+}
+
+__global__ void __launch_bounds__(256) combine_rows_kernel(__nv_bfloat16* __restrict__ out,
+                                                           const __nv_bfloat16* __restrict__ src,
+                                                           const int* __restrict__ pos, const float* __restrict__ w,
+                                                           const __nv_bfloat16* __restrict__ add, float add_scale,
+                                                           int tokens, int k, int width) {
+  const int nvec = width >> 3;
+  const long long total = (long long)tokens * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / nvec), v = (int)(i % nvec);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (add) {
+      uint4 a = reinterpret_cast<const uint4*>(add + (long long)t * width)[v];
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(a2[j]);
+        acc[2 * j] = f.x * add_scale;
+        acc[2 * j + 1] = f.y * add_scale;
+      }
+    }
+    for (int j = 0; j < k; ++j) {
+      const int p = pos[(long long)t * k + j];
+      if (p < 0) continue;
+      const float wt = w ? w[(long long)t * k + j] : 1.f;
+      uint4 x = reinterpret_cast<const uint4*>(src + (long long)p * width)[v];
+      const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 f = __bfloat1622float2(x2[q]);
+        acc[2 * q] += wt * f.x;
+        acc[2 * q + 1] += wt * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + (long long)t * width)[v] = o;
+  }
+}
+
+// one warp per (token, slot)
+__global__ void __launch_bounds__(256) row_dots_kernel(float* __restrict__ dots, const __nv_bfloat16* __restrict__ a,
+                                                       const __nv_bfloat16* __restrict__ b,
+                                                       const int* __restrict__ pos, int tokens, int k, int width) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = width >> 3;
+  const long long total = (long long)tokens * k;
+  for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < total;
+       i += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const long long t = i / k;
+    const int p = pos[i];
+    float acc = 0.f;
+    if (p >= 0) {
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 x = reinterpret_cast<const uint4*>(a + t * width)[v];
+        uint4 y = reinterpret_cast<const uint4*>(b + (long long)p * width)[v];
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+        const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 f = __bfloat1622float2(x2[q]), g = __bfloat1622float2(y2[q]);
+          acc += f.x * g.x + f.y * g.y;
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) dots[i] = acc;
+  }
+}
+
+// ---------------------------------------------------------------- optimizer updates
+template <bool GRAD_F32>
+__global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ master, float* __restrict__ m,
+                                                         float* __restrict__ v, const void* __restrict__ grad,
+                                                         __nv_bfloat16* __restrict__ pb, long long n, float lr,
+                                                         float beta1, float beta2, float eps, float wd, float bc1,
+                                                         float bc2, const float* __restrict__ gsp, float gs) {
+  const float scale = gsp ? (*gsp) * gs : gs;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float g = GRAD_F32 ? reinterpret_cast<const float*>(grad)[i]
+                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i]);
+    g *= scale;
+    float mi = beta1 * m[i] + (1.f - beta1) * g;
+    float vi = beta2 * v[i] + (1.f - beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    float p = master[i];
+    p = p * (1.f - lr * wd) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    master[i] = p;
+    if (pb) pb[i] = __float2bfloat16(p);
+  }
+}
+
+template <bool IS_F32>
+__global__ void __launch_bounds__(256) sumsq_kernel(const void* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float red[8];
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float f = IS_F32 ? reinterpret_cast<const float*>(x)[i]
+                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    acc += f * f;
+  }
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+template <bool GRAD_F32>
+__global__ void __launch_bounds__(256) muon_momentum_kernel(float* __restrict__ mom, const void* __restrict__ grad,
+                                                            __nv_bfloat16* __restrict__ u, long long n, float beta,
+                                                            bool nesterov, const float* __restrict__ gsp) {
+  const float scale = gsp ? *gsp : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float g = GRAD_F32 ? reinterpret_cast<const float*>(grad)[i]
+                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i]);
+    g *= scale;
+    // lerp form of the reference: M <- beta*M + (1-beta)*G ; U = nesterov ? lerp(G, M, beta) : M
+    float mi = beta * mom[i] + (1.f - beta) * g;
+    mom[i] = mi;
+    float ui = nesterov ? (g * (1.f - beta) + mi * beta) : mi;
+    u[i] = __float2bfloat16(ui);
+  }
+}
+
+__global__ void __launch_bounds__(256) muon_apply_kernel(float* __restrict__ master,
+                                                         const __nv_bfloat16* __restrict__ o,
+                                                         __nv_bfloat16* __restrict__ pb, long long n, float lr, float wd,
+                                                         float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float p = master[i] * (1.f - lr * wd) - lr * scale * __bfloat162float(o[i]);
+    master[i] = p;
+    if (pb) pb[i] = __float2bfloat16(p);
+  }
+}
+
+__global__ void __launch_bounds__(256) axpby_bf16_kernel(__nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ y, float a, float b,
+                                                         long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = __float2bfloat16(a * __bfloat162float(x[i]) + b * __bfloat162float(y[i]));
+}
+
+__global__ void __launch_bounds__(256) triangular_adamw_kernel(const float* __restrict__ S, float* __restrict__ m,
+                                                               float* __restrict__ v, float* __restrict__ delta,
+                                                               long long total, int r1, float beta1, float beta2,
+                                                               float eps, float bc1, float bc2, bool triu) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int within = (int)(i % ((long long)r1 * r1));
+    const int row = within / r1, col = within % r1;
+    const bool keep = !triu || row <= col;
+    const float s = keep ? S[i] : 0.f;
+    float mi = beta1 * m[i] + (1.f - beta1) * s;
+    float vi = beta2 * v[i] + (1.f - beta2) * s * s;
+    m[i] = mi;
+    v[i] = vi;
+    delta[i] = keep ? (mi / bc1) / (sqrtf(vi / bc2) + eps) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(256) steer_update_kernel(float* __restrict__ P, const float* __restrict__ G,
+                                                           long long n, float momentum, float steer) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float p = P[i];
+    P[i] = momentum * p + steer * (G[i] - p);
+  }
+}
+
+// ---------------------------------------------------------------- routing tiers / rendering
+__global__ void __launch_bounds__(256) route_tiers_kernel(const float* __restrict__ logits, int* __restrict__ tiers,
+                                                          int* __restrict__ all_reflex, int rows, float threshold) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  bool not_reflex = false;
+  if (r < rows) {
+    const float a = logits[3 * r], b = logits[3 * r + 1], c = logits[3 * r + 2];
+    const float mx = fmaxf(a, fmaxf(b, c));
+    const float ea = __expf(a - mx), eb = __expf(b - mx), ec = __expf(c - mx);
+    const float inv = 1.f / (ea + eb + ec);
+    const int tier = (ea * inv >= threshold) ? 0 : (eb >= ec ? 1 : 2);
+    tiers[r] = tier;
+    not_reflex = tier != 0;
+  }
+  const unsigned any = __ballot_sync(0xffffffffu, not_reflex);
+  if ((threadIdx.x & 31) == 0 && any != 0u && all_reflex) atomicExch(all_reflex, 0);
+}
+
+__global__ void __launch_bounds__(256) heatmap_bins_kernel(const float* __restrict__ act, long long n, int num_bins,
+                                                           float* __restrict__ bins) {
+  __shared__ float red[8];
+  const int b = blockIdx.x;
+  const long long per = n / num_bins > 0 ? n / num_bins : 1;
+  const long long s = (long long)b * per;
+  long long e = (b == num_bins - 1) ? n : s + per;
+  if (e > n) e = n;
+  float acc = 0.f;
+  for (long long i = s + threadIdx.x; i < e; i += blockDim.x) acc += fabsf(act[i]);
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) bins[b] = e > s ? acc / (float)(e - s) : 0.f;
+}
+
+__global__ void __launch_bounds__(256) heatmap_colour_kernel(const float* __restrict__ bins, int num_bins,
+                                                             uint32_t* __restrict__ rgba) {
+  __shared__ float red[8];
+  float mx = 0.f;
+  for (int i = threadIdx.x; i < num_bins; i += blockDim.x) mx = fmaxf(mx, bins[i]);
+  mx = block_max<256>(mx, red);
+  mx = fmaxf(mx, 1e-12f);
+  for (int i = threadIdx.x; i < num_bins; i += blockDim.x) {
+    const float vn = bins[i] / mx;
+    const uint32_t r = (uint32_t)(fminf(1.f, 1.4f * vn) * 249.f);
+    const uint32_t g = (uint32_t)(vn * vn * 115.f);
+    const uint32_t b = (uint32_t)((1.f - 0.7f * vn) * 60.f);
+    rgba[i] = (255u << 24) | (b << 16) | (g << 8) | r;
+  }
+}
+
+__global__ void __launch_bounds__(256) tier_render_kernel(const float* __restrict__ act, const int* __restrict__ tiers,
+                                                          uint32_t* __restrict__ rgba, int rows, int width) {
+  const long long total = (long long)rows * width;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / width);
+    const int t = tiers[r];
+    const float cr = t == 0 ? 16.f : (t == 1 ? 245.f : 139.f);
+    const float cg = t == 0 ? 185.f : (t == 1 ? 158.f : 92.f);
+    const float cb = t == 0 ? 129.f : (t == 1 ? 11.f : 246.f);
+    const float inten = fminf(1.f, fabsf(act[i]));
+    const uint32_t R = (uint32_t)(cr * inten), G = (uint32_t)(cg * inten), B = (uint32_t)(cb * inten);
+    rgba[i] = (255u << 24) | (B << 16) | (G << 8) | R;
+  }
+}
+
+inline int flat_grid(long long n, int threads = 256) {
+  long long b = (n + threads - 1) / threads;
+  const long long cap = 148ll * 16;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+void launch_ce_fwd_bwd(__nv_bfloat16* logits, long long ld, const long long* targets, float* row_loss, int rows, int V,
+                       long long ignore_index, float grad_scale, cudaStream_t s) {
+  if (rows == 0) return;
+  ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, s>>>(logits, ld, targets, row_loss, V, ignore_index, grad_scale);
+}
+
+void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,
+                        int dst_rows, int width, cudaStream_t s) {
+  if (dst_rows == 0) return;
+  gather_rows_kernel<<<flat_grid((long long)dst_rows * (width >> 3)), 256, 0, s>>>(dst, src, row_src, row_scale,
+                                                                                    dst_rows, width);
+}
+
+void launch_combine_rows(__nv_bfloat16* out, const __nv_bfloat16* src, const int* pos, const float* w,
+                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, cudaStream_t s) {
+  if (tokens == 0) return;
+  combine_rows_kernel<<<flat_grid((long long)tokens * (width >> 3)), 256, 0, s>>>(out, src, pos, w, add, add_scale,
+                                                                                   tokens, k, width);
+}
+
+void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b, const int* pos, int tokens, int k,
+                     int width, cudaStream_t s) {
+  if (tokens == 0) return;
+  row_dots_kernel<<<flat_grid((long long)tokens * k * 32), 256, 0, s>>>(dots, a, b, pos, tokens, k, width);
+}
+
+void launch_adamw_flat(float* master, float* m, float* v, const void* grad, bool grad_is_f32, __nv_bfloat16* param_bf16,
+                       long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                       float bias_corr1, float bias_corr2, const float* grad_scale_ptr, float grad_scale,
+                       cudaStream_t s) {
+  if (n == 0) return;
+  if (grad_is_f32)
+    adamw_flat_kernel<true><<<flat_grid(n), 256, 0, s>>>(master, m, v, grad, param_bf16, n, lr, beta1, beta2, eps,
+                                                         weight_decay, bias_corr1, bias_corr2, grad_scale_ptr,
+                                                         grad_scale);
+  else
+    adamw_flat_kernel<false><<<flat_grid(n), 256, 0, s>>>(master, m, v, grad, param_bf16, n, lr, beta1, beta2, eps,
+                                                          weight_decay, bias_corr1, bias_corr2, grad_scale_ptr,
+                                                          grad_scale);
+}
+
+void launch_sumsq(const void* x, bool is_f32, long long n, float* out, cudaStream_t s) {
+  if (n == 0) return;
+  if (is_f32)
+    sumsq_kernel<true><<<flat_grid(n), 256, 0, s>>>(x, n, out);
+  else
+    sumsq_kernel<false><<<flat_grid(n), 256, 0, s>>>(x, n, out);
+}
+
+void launch_muon_momentum(float* mom, const void* grad, bool grad_is_f32, __nv_bfloat16* u_out, long long n, float beta,
+                          bool nesterov, const float* grad_scale_ptr, cudaStream_t s) {
+  if (n == 0) return;
+  if (grad_is_f32)
+    muon_momentum_kernel<true><<<flat_grid(n), 256, 0, s>>>(mom, grad, u_out, n, beta, nesterov, grad_scale_ptr);
+  else
+    muon_momentum_kernel<false><<<flat_grid(n), 256, 0, s>>>(mom, grad, u_out, n, beta, nesterov, grad_scale_ptr);
+}
+
+void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* param_bf16, long long n, float lr,
+                       float wd, float scale, cudaStream_t s) {
+  if (n == 0) return;
+  muon_apply_kernel<<<flat_grid(n), 256, 0, s>>>(master, o, param_bf16, n, lr, wd, scale);
+}
+
+void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s) {
+  if (n == 0) return;
+  axpby_bf16_kernel<<<flat_grid(n), 256, 0, s>>>(x, y, a, b, n);
+}
+
+void launch_triangular_adamw(const float* S, float* m, float* v, float* delta, int nmat, int r1, float beta1,
+                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, cudaStream_t s) {
+  const long long total = (long long)nmat * r1 * r1;
+  if (total == 0) return;
+  triangular_adamw_kernel<<<flat_grid(total), 256, 0, s>>>(S, m, v, delta, total, r1, beta1, beta2, eps, bias_corr1,
+                                                           bias_corr2, triu);
+}
+
+void launch_steer_update(float* P, const float* G, long long n, float momentum, float steer, cudaStream_t s) {
+  if (n == 0) return;
+  steer_update_kernel<<<flat_grid(n), 256, 0, s>>>(P, G, n, momentum, steer);
+}
+
+void launch_route_tiers(const float* logits, int* tiers, int* all_reflex, int rows, float threshold, cudaStream_t s) {
+  if (rows == 0) return;
+  route_tiers_kernel<<<(rows + 255) / 256, 256, 0, s>>>(logits, tiers, all_reflex, rows, threshold);
+}
+
+void launch_neuron_heatmap(const float* act, long long n, int num_bins, float* bin_scratch, uint32_t* rgba,
+                           cudaStream_t s) {
+  if (num_bins == 0) return;
+  heatmap_bins_kernel<<<num_bins, 256, 0, s>>>(act, n, num_bins, bin_scratch);
+  heatmap_colour_kernel<<<1, 256, 0, s>>>(bin_scratch, num_bins, rgba);
+}
+
+void launch_tier_render(const float* act, const int* tiers, uint32_t* rgba, int rows, int width, cudaStream_t s) {
+  if (rows == 0) return;
+  tier_render_kernel<<<flat_grid((long long)rows * width), 256, 0, s>>>(act, tiers, rgba, rows, width);
+}
+
+}  // namespace tb

@@ -1,0 +1,474 @@
+// bf16 GEMM on the 5th-generation tensor cores: C = alpha * A * B^T (+ epilogue).
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warp 0    TMA producer: cp.async.bulk.tensor tiles of A (128 x 64) and B (BN x 64) into a ring of
+//             128B-swizzled shared-memory stages, completion signalled on mbarriers;
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) reading the stages through
+//             shared-memory descriptors and accumulating into TMEM; tcgen05.commit releases a stage
+//             back to the producer and, after the last K step, publishes the accumulator;
+//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulator (lane == output row), apply bias / GELU /
+//             GELU' / row scale / accumulate, convert and store 16-byte vectors.
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
+// main loop of tile i+1. No cluster multicast is used; every CTA loads its own tiles.
+//
+// Replaces the reference's library GEMM call sites (torch.matmul / bmm / addmm in
+// triune/model/attention.py:537-572, triune/model/moe.py:385-437, triune/kernels/fast_muon.py:15-161).
+#include "tc_gemm.cuh"
+
+#include <cuda.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {64,128,256}
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct KParams {
+  int M, N, K;
+  int mode, flags, batch;
+  int num_m, num_n;
+  long long ldc, strideC;
+  int a_batched, b_batched;
+  float alpha;
+  void* C;
+  const __nv_bfloat16* bias;
+  long long bias_stride;
+  const __nv_bfloat16* aux_in;
+  __nv_bfloat16* aux_out;
+  const float* row_scale;
+  const int* tile_group;
+  const int* group_offsets;
+  int* status;
+  int total_tiles;
+};
+
+struct Tile {
+  int m0, n0, ba, bb, g, k_begin, k_iters;
+  bool valid;
+};
+
+__device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
+  Tile tl;
+  tl.valid = true;
+  if (p.mode == GEMM_GROUPED_M) {
+    int m_idx = t % p.num_m, n_idx = t / p.num_m;
+    int g = p.tile_group[m_idx];
+    tl.valid = g >= 0;
+    tl.g = g < 0 ? 0 : g;
+    tl.m0 = m_idx * BM;
+    tl.n0 = n_idx;  // scaled by BN by the caller
+    tl.ba = 0;
+    tl.bb = tl.g;
+    tl.k_begin = 0;
+    tl.k_iters = (p.K + BK - 1) / BK;
+  } else {
+    int per_b = p.num_m * p.num_n;
+    int b = t / per_b, r = t % per_b;
+    tl.m0 = (r % p.num_m) * BM;
+    tl.n0 = r / p.num_m;
+    tl.g = b;
+    if (p.mode == GEMM_GROUPED_K) {
+      tl.ba = 0;
+      tl.bb = 0;
+      int k0 = p.group_offsets[b], k1 = p.group_offsets[b + 1];
+      tl.k_begin = k0;
+      tl.k_iters = (k1 - k0 + BK - 1) / BK;
+    } else {
+      tl.ba = p.a_batched ? b : 0;
+      tl.bb = p.b_batched ? b : 0;
+      tl.k_begin = 0;
+      tl.k_iters = (p.K + BK - 1) / BK;
+    }
+  }
+  return tl;
+}
+
+__device__ __forceinline__ void report(const KParams& p, int code) {
+  if (p.status != nullptr) atomicCAS(p.status, 0, code);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint8_t* smemA = smem;
+  uint8_t* smemB = smem + STAGES * Cfg::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES] TMA -> MMA
+  uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;       // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        Tile tl = decode_tile(p, t);
+        if (!tl.valid) continue;
+        const int n0 = tl.n0 * BN;
+        for (int it = 0; it < tl.k_iters; ++it) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            report(p, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          const int k0 = tl.k_begin + it * BK;
+          uint8_t* a_dst = smemA + stage * Cfg::A_BYTES;
+          uint8_t* b_dst = smemB + stage * Cfg::B_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(a_dst + j * (BK * 128), &tmA, &full[stage], tl.m0 + 64 * j, k0, tl.ba);
+          } else {
+            tma_load_3d(a_dst, &tmA, &full[stage], k0, tl.m0, tl.ba);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * (BK * 128), &tmB, &full[stage], n0 + 64 * j, k0, tl.bb);
+          } else {
+            tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, tl.bb);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Give loads that are still in flight a bounded chance to land before the CTA retires.
+        int pending = issued < STAGES ? issued : STAGES;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) {
+            s = STAGES - 1;
+            ph ^= 1;
+          }
+          (void)mbar_wait(&full[s], ph);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        Tile tl = decode_tile(p, t);
+        if (!tl.valid) continue;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          report(p, ST_TIMEOUT_TMEM);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int it = 0; it < tl.k_iters; ++it) {
+          if (!mbar_wait(&full[stage], phase)) {
+            report(p, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smemA + stage * Cfg::A_BYTES);
+          const uint32_t b_addr = smem_u32(smemB + stage * Cfg::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(a_addr + k * 2048, BK * 128, 1024)
+                                        : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + k * 2048, BK * 128, 1024)
+                                        : make_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (it > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (tl.k_iters > 0)
+          umma_commit(&acc_full[acc]);
+        else
+          mbar_arrive(&acc_full[acc]);  // empty reduction: the epilogue substitutes zeros
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_base = (warp & 3) * 32;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = (p.flags & GF_OUT_F32) != 0;
+    const bool accumulate = (p.flags & GF_ACCUMULATE) != 0;
+    const bool do_gelu = (p.flags & GF_GELU) != 0;
+    const bool do_dgelu = (p.flags & GF_DGELU) != 0;
+    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+      Tile tl = decode_tile(p, t);
+      if (!tl.valid) continue;
+      bool ok = mbar_wait(&acc_full[acc], acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p, ST_TIMEOUT_TMEM);
+        break;
+      }
+      tc_fence_after_sync();
+      const int n0 = tl.n0 * BN;
+      const int gm = tl.m0 + lane_base + lane;
+      const bool row_ok = gm < p.M;
+      const long long c_off = (p.mode == GEMM_GROUPED_M ? 0ll : (long long)tl.g * p.strideC) + (long long)gm * p.ldc;
+      const __nv_bfloat16* bias = p.bias ? p.bias + (long long)tl.g * p.bias_stride : nullptr;
+      const float rs = (p.row_scale && row_ok) ? p.row_scale[gm] : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        if (tl.k_iters > 0) {
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + c + j * 8;
+            if (gn < p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j * 8 + i]) * p.alpha;
+              if (bias) {
+                uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
+                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float2 f = __bfloat1622float2(b2[i]);
+                  v[2 * i] += f.x;
+                  v[2 * i + 1] += f.y;
+                }
+              }
+              if (do_gelu) {
+                if (p.aux_out) {
+                  uint4 pre;
+                  pre.x = pack_bf16x2(v[0], v[1]);
+                  pre.y = pack_bf16x2(v[2], v[3]);
+                  pre.z = pack_bf16x2(v[4], v[5]);
+                  pre.w = pack_bf16x2(v[6], v[7]);
+                  *reinterpret_cast<uint4*>(p.aux_out + c_off + gn) = pre;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = gelu_tanh_f(v[i]);
+              }
+              if (do_dgelu) {
+                uint4 av = *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn);
+                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float2 f = __bfloat1622float2(a2[i]);
+                  v[2 * i] *= gelu_tanh_grad_f(f.x);
+                  v[2 * i + 1] *= gelu_tanh_grad_f(f.y);
+                }
+              }
+              if (p.row_scale) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] *= rs;
+              }
+              if (out_f32) {
+                float* cp = reinterpret_cast<float*>(p.C) + c_off + gn;
+                float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
+                float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
+                if (accumulate) {
+                  float4 e0 = *reinterpret_cast<float4*>(cp);
+                  float4 e1 = *reinterpret_cast<float4*>(cp + 4);
+                  o0.x += e0.x; o0.y += e0.y; o0.z += e0.z; o0.w += e0.w;
+                  o1.x += e1.x; o1.y += e1.y; o1.z += e1.z; o1.w += e1.w;
+                }
+                *reinterpret_cast<float4*>(cp) = o0;
+                *reinterpret_cast<float4*>(cp + 4) = o1;
+              } else {
+                __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + gn;
+                if (accumulate) {
+                  uint4 ev = *reinterpret_cast<const uint4*>(cp);
+                  const __nv_bfloat162* e2 = reinterpret_cast<const __nv_bfloat162*>(&ev);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    float2 f = __bfloat1622float2(e2[i]);
+                    v[2 * i] += f.x;
+                    v[2 * i + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(cp) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid, cudaStream_t stream) {
+  auto kern = tc_gemm_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm: cannot set shared memory size: ") + cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, kp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm launch failed: ") + cudaGetErrorString(e));
+}
+
+template <int BN>
+void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid,
+                    cudaStream_t s) {
+  if (!a_mn && !b_mn) launch_variant<BN, false, false>(tmA, tmB, kp, grid, s);
+  else if (!a_mn && b_mn) launch_variant<BN, false, true>(tmA, tmB, kp, grid, s);
+  else if (a_mn && !b_mn) launch_variant<BN, true, false>(tmA, tmB, kp, grid, s);
+  else launch_variant<BN, true, true>(tmA, tmB, kp, grid, s);
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return;
+  if (a.N % 8 != 0) throw std::runtime_error("tc_gemm: N must be a multiple of 8");
+  if (a.ldc % 8 != 0) throw std::runtime_error("tc_gemm: ldc must be a multiple of 8");
+  if (a.lda % 8 != 0 || a.ldb % 8 != 0) throw std::runtime_error("tc_gemm: lda/ldb must be multiples of 8");
+  if (a.mode != GEMM_GROUPED_K && a.K <= 0) throw std::runtime_error("tc_gemm: K must be positive");
+  if (a.mode == GEMM_GROUPED_M && a.tile_group == nullptr) throw std::runtime_error("tc_gemm: tile_group missing");
+  if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
+    throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
+
+  const int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : (a.N > 64 ? 128 : 64);
+  KParams kp;
+  kp.M = a.M; kp.N = a.N; kp.K = a.K;
+  kp.mode = a.mode; kp.flags = a.flags; kp.batch = a.batch < 1 ? 1 : a.batch;
+  kp.num_m = (a.M + BM - 1) / BM;
+  kp.num_n = (a.N + BN - 1) / BN;
+  kp.ldc = a.ldc; kp.strideC = a.strideC;
+  kp.a_batched = a.strideA != 0; kp.b_batched = a.strideB != 0;
+  kp.alpha = a.alpha;
+  kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
+  kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
+  kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.total_tiles = kp.num_m * kp.num_n * (a.mode == GEMM_GROUPED_M ? 1 : kp.batch);
+
+  // Tensor maps. dims are {contiguous, rows, batch}.
+  const uint64_t a_rows_total = (a.mode == GEMM_GROUPED_K) ? (uint64_t)a.K : 0;  // K = total rows for grouped-K
+  CUtensorMap tmA, tmB;
+  const uint64_t nbA = kp.a_batched ? (uint64_t)kp.batch : 1, nbB = (a.mode == GEMM_GROUPED_M || kp.b_batched) ? (uint64_t)kp.batch : 1;
+  const uint64_t sA = (kp.a_batched ? (uint64_t)a.strideA : (uint64_t)a.lda) * 2ull;
+  const uint64_t sB = ((a.mode == GEMM_GROUPED_M || kp.b_batched) ? (uint64_t)a.strideB : (uint64_t)a.ldb) * 2ull;
+  if (a.a_mn_major) {
+    const uint64_t krows = (a.mode == GEMM_GROUPED_K) ? a_rows_total : (uint64_t)a.K;
+    tmA = make_tmap_3d(a.A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.M, krows, nbA, (uint64_t)a.lda * 2ull, sA, 64, BK);
+  } else {
+    tmA = make_tmap_3d(a.A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.M, nbA, (uint64_t)a.lda * 2ull, sA, BK, BM);
+  }
+  if (a.b_mn_major) {
+    const uint64_t krows = (a.mode == GEMM_GROUPED_K) ? a_rows_total : (uint64_t)a.K;
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, krows, nbB, (uint64_t)a.ldb * 2ull, sB, 64, BK);
+  } else {
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull, sB, BK, (uint32_t)BN);
+  }
+  const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
+  if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
+  else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
+  else dispatch_major<64>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
+}
+
+}  // namespace tb

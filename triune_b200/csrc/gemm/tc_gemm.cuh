@@ -1,0 +1,50 @@
+// Interface of the bf16 tcgen05 GEMM family (dense / batched / grouped-by-rows / grouped-by-reduction).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+enum GemmMode : int {
+  GEMM_DENSE = 0,      // C[b] = A[b] * B[b]^T, b in [0, batch)
+  GEMM_GROUPED_M = 1,  // rows of A are grouped (padded to 128); tile_group[m_tile] selects B[g] and bias[g]
+  GEMM_GROUPED_K = 2,  // C[g] = sum over rows in [group_offsets[g], group_offsets[g+1]) (weight gradients)
+};
+
+enum GemmFlags : int {
+  GF_OUT_F32 = 1,     // C is fp32 (default bf16)
+  GF_ACCUMULATE = 2,  // C += result
+  GF_GELU = 4,        // C = gelu_tanh(result + bias); pre-activation optionally saved to aux_out
+  GF_DGELU = 8,       // C = result * gelu_tanh'(aux_in)
+};
+
+// Operand layouts. "K-major": the reduction index is contiguous (x[M,K] row-major, w[N,K] row-major).
+// "MN-major": the non-reduction index is contiguous (x stored [K,M] row-major). Both feed the tensor
+// core directly from 128B-swizzled shared memory; no transposes are materialised.
+struct GemmArgs {
+  const __nv_bfloat16* A;
+  const __nv_bfloat16* B;
+  void* C;
+  int M, N, K;
+  long long lda, ldb, ldc;             // leading dimensions in elements
+  long long strideA, strideB, strideC; // batch strides in elements (0 = shared)
+  int batch;
+  bool a_mn_major, b_mn_major;
+  int mode;
+  int flags;
+  float alpha;
+  const __nv_bfloat16* bias;  // [batch or groups][N] or null
+  long long bias_stride;
+  const __nv_bfloat16* aux_in;  // same layout as C (bf16), for GF_DGELU
+  __nv_bfloat16* aux_out;       // same layout as C (bf16), pre-activation for GF_GELU
+  const float* row_scale;       // [M] or null
+  const int* tile_group;        // GEMM_GROUPED_M: [ceil(M/128)], -1 marks an unused tile
+  const int* group_offsets;     // GEMM_GROUPED_K: [batch+1], multiples of 64
+  int* status;                  // optional device status word (see KernelStatus)
+};
+
+// Launches on `stream`. Throws std::runtime_error on invalid arguments.
+void launch_tc_gemm(const GemmArgs& args, cudaStream_t stream);
+
+}  // namespace tb
