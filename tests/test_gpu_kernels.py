@@ -1,0 +1,315 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 384), (1000, 1536, 384), (4096, 256, 1536), (130, 64, 72),
+                                   (512, 8, 384), (384, 32000, 128)])
+def test_gemm_kmajor(dev, M, N, K):
+    from triune_b200 import ops
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    c = ops.gemm(a, b)
+    ref = a.float() @ b.float().t()
+    assert _rel(c, ref) < 2e-2
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (1000, 384, 520), (384, 1536, 4096)])
+def test_gemm_mn_major(dev, a_mn, b_mn, M, N, K):
+    from triune_b200 import ops
+
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    c = ops.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn)
+    ref = a.float() @ b.float().t()
+    assert _rel(c, ref) < 2e-2
+
+
+def test_gemm_epilogues(dev):
+    from triune_b200 import ops
+
+    torch.manual_seed(2)
+    M, N, K = 512, 384, 256
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16) * 0.5
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    pre = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    h = ops.gemm(a, b, bias=bias, gelu=True, aux_out=pre)
+    ref_pre = a.float() @ b.float().t() + bias.float()
+    assert _rel(pre, ref_pre) < 2e-2
+    assert _rel(h, F.gelu(ref_pre, approximate="tanh")) < 2e-2
+    # derivative epilogue
+    g = ops.gemm(a, b, dgelu_aux=pre)
+    x = pre.float().requires_grad_(True)
+    F.gelu(x, approximate="tanh").sum().backward()
+    assert _rel(g, (a.float() @ b.float().t()) * x.grad) < 3e-2
+    # fp32 accumulate
+    c = torch.ones(M, N, device=dev, dtype=torch.float32)
+    ops.gemm(a, b, c, accumulate=True, alpha=0.5)
+    assert _rel(c, 1.0 + 0.5 * (a.float() @ b.float().t())) < 1e-2
+    # batched
+    A = torch.randn(5, 128, 192, device=dev, dtype=torch.bfloat16)
+    Bm = torch.randn(5, 256, 192, device=dev, dtype=torch.bfloat16)
+    C = ops.gemm(A, Bm)
+    assert _rel(C, torch.bmm(A.float(), Bm.float().transpose(1, 2))) < 2e-2
+    C2 = ops.gemm(A, A)
+    assert _rel(C2, torch.bmm(A.float(), A.float().transpose(1, 2))) < 2e-2
+
+
+def test_gemm_grouped(dev):
+    from triune_b200 import ops
+
+    torch.manual_seed(3)
+    E, d, H = 4, 128, 256
+    rows = [256, 0, 128, 384]
+    R = sum(rows) + 128  # one unused tile at the end
+    x = torch.randn(R, d, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(E, H, d, device=dev, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(E, H, device=dev, dtype=torch.bfloat16)
+    tg, offs = [], [0]
+    for e, r in enumerate(rows):
+        tg += [e] * (r // 128)
+        offs.append(offs[-1] + r)
+    tg.append(-1)
+    tile_group = torch.tensor(tg, device=dev, dtype=torch.int32)
+    group_offsets = torch.tensor(offs, device=dev, dtype=torch.int32)
+    y = torch.zeros(R, H, device=dev, dtype=torch.bfloat16)
+    ops.gemm(x, w, y, bias=bias, mode=ops.GEMM_GROUPED_M, tile_group=tile_group)
+    for e in range(E):
+        s, t = offs[e], offs[e + 1]
+        if t > s:
+            ref = x[s:t].float() @ w[e].float().t() + bias[e].float()
+            assert _rel(y[s:t], ref) < 2e-2
+    assert float(y[offs[-1]:].abs().max()) == 0.0
+    # grouped reduction (weight gradients): dW[e] = dy_e^T x_e
+    dy = torch.randn(R, H, device=dev, dtype=torch.bfloat16)
+    dw = ops.gemm(dy, x, a_mn=True, b_mn=True, mode=ops.GEMM_GROUPED_K, group_offsets=group_offsets, num_groups=E,
+                  out_dtype=torch.float32)
+    for e in range(E):
+        s, t = offs[e], offs[e + 1]
+        ref = dy[s:t].float().t() @ x[s:t].float()
+        assert float((dw[e] - ref).abs().max()) < 2e-2 * max(1.0, float(ref.abs().max()))
+
+
+# ------------------------------------------------------------------ row kernels
+@pytest.mark.parametrize("d", [384, 1536, 2048, 128])
+def test_rmsnorm(dev, d):
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(4)
+    x = torch.randn(777, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(777, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(d, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    y = ops.rmsnorm(x, w)
+    yr = ref.rmsnorm(x.detach().float(), w.detach().float())
+    assert _rel(y, yr) < 1e-2
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_(True)
+    wf = w.detach().float().requires_grad_(True)
+    ref.rmsnorm(xf, wf).backward(dy.float())
+    assert _rel(x.grad, xf.grad) < 2e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
+    # fused add + norm
+    x.grad = None
+    w.grad = None
+    y2, s2 = ops.add_rmsnorm(x, r, w)
+    (y2.float() * dy.float()).sum().backward()
+    xs = (x.detach().float() + r.detach().float()).to(torch.bfloat16).float().requires_grad_(True)
+    wf2 = w.detach().float().requires_grad_(True)
+    (ref.rmsnorm(xs, wf2) * dy.float()).sum().backward()
+    assert _rel(y2, ref.rmsnorm(xs.detach(), wf2.detach())) < 1e-2
+    assert _rel(x.grad, xs.grad) < 2e-2 and _rel(r.grad, xs.grad) < 2e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_qk_feature_map(dev, D):
+    from triune_b200 import ops, _ext
+
+    torch.manual_seed(5)
+    B, T, H = 2, 96, 3
+    qkvg = torch.randn(B * T, 4 * H * D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = ops.rope_tables(T, D, device=dev)
+    q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
+    w = torch.randn(B, T, H, D, device=dev)
+    (q.float() * w).sum().backward(retain_graph=True)
+    gq = qkvg.grad.clone()
+    _ext.set_reference_ops(True)
+    try:
+        x2 = qkvg.detach().float().requires_grad_(True)
+        q2, k2, _, _ = ops.qk_feature_map(x2, cos, sin, B, T, H, D)
+        (q2 * w).sum().backward()
+    finally:
+        _ext.set_reference_ops(False)
+    assert _rel(q, q2) < 2e-2 and _rel(k, k2) < 2e-2
+    assert _rel(gq[:, : H * D], x2.grad[:, : H * D]) < 3e-2
+
+
+def test_cross_entropy_fused(dev):
+    from triune_b200 import ops
+
+    torch.manual_seed(6)
+    N, d, V = 1000, 128, 4096
+    h = (torch.randn(N, d, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(V, d, device=dev) * 0.1).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn(V, device=dev) * 0.1).to(torch.bfloat16).requires_grad_(True)
+    t = torch.randint(0, V, (N,), device=dev)
+    t[::7] = -100
+    nv = int((t != -100).sum())
+    loss = ops.linear_cross_entropy(h, w, t, bias=b, n_valid=nv, chunk_rows=384)
+    (loss * 2.0).backward()
+    hf, wf, bf_ = (z.detach().float().requires_grad_(True) for z in (h, w, b))
+    lr = F.cross_entropy(F.linear(hf, wf, bf_), t, ignore_index=-100)
+    (lr * 2.0).backward()
+    assert abs(float(loss) - float(lr)) < 2e-2
+    assert _rel(h.grad, hf.grad) < 5e-2
+    assert _rel(w.grad, wf.grad) < 5e-2
+    assert _rel(b.grad, bf_.grad) < 5e-2
+
+
+def test_moe_experts(dev):
+    from triune_b200 import ops, _ext
+
+    torch.manual_seed(7)
+    N, d, H, E, k = 1500, 128, 256, 8, 2
+    x = (torch.randn(N, d, device=dev) * 0.5).to(torch.bfloat16)
+    w1 = (torch.randn(E, H, d, device=dev) * 0.05).to(torch.bfloat16)
+    b1 = (torch.randn(E, H, device=dev) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, d, H, device=dev) * 0.05).to(torch.bfloat16)
+    b2 = (torch.randn(E, d, device=dev) * 0.05).to(torch.bfloat16)
+    logits = torch.randn(N, E, device=dev)
+    idx, wts, _ = ops.moe_route(logits, torch.zeros(E, device=dev), k)
+    keep = torch.rand(N, k, device=dev) > 0.1
+    shared = torch.randn(N, d, device=dev).to(torch.bfloat16)
+    outs = []
+    for mode in (False, True):
+        _ext.set_reference_ops(mode)
+        try:
+            ps = [z.detach().clone().float().requires_grad_(True) if mode else z.detach().clone().requires_grad_(True)
+                  for z in (x, w1, b1, w2, b2, shared)]
+            wk = (wts * keep).detach().clone().requires_grad_(True)
+            o = ops.moe_experts(ps[0], idx, wk, keep, ps[1], ps[2], ps[3], ps[4], ps[5], 0.5)
+            (o.float() * torch.linspace(-1, 1, d, device=dev)).sum().backward()
+            outs.append((o, [p.grad for p in ps], wk.grad))
+        finally:
+            _ext.set_reference_ops(False)
+    (o1, g1, gw1), (o2, g2, gw2) = outs
+    assert _rel(o1, o2) < 3e-2
+    for a, b_ in zip(g1, g2):
+        assert _rel(a, b_) < 5e-2
+    assert _rel(gw1 * keep, gw2 * keep) < 5e-2
+
+
+def test_optimizer_kernels(dev):
+    from triune_b200 import _ext
+
+    e = _ext.ext()
+    torch.manual_seed(8)
+    n = 100_003
+    master = torch.randn(n, device=dev)
+    m = torch.zeros(n, device=dev)
+    v = torch.zeros(n, device=dev)
+    g = torch.randn(n, device=dev)
+    pb = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    p_ref = master.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([p_ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.05)
+    coef = torch.tensor([0.5], device=dev)
+    for step in (1, 2, 3):
+        e.adamw_flat(master, m, v, g, pb, 1e-2, 0.9, 0.95, 1e-8, 0.05, step, coef, 1.0)
+        p_ref.grad = g * 0.5
+        opt.step()
+    assert _rel(master, p_ref.detach()) < 1e-5
+    assert _rel(pb, master) < 1e-2
+    out = torch.zeros(1, device=dev)
+    e.sumsq(g, out)
+    assert abs(float(out) - float(g.pow(2).sum())) / float(g.pow(2).sum()) < 1e-4
+    S = torch.randn(6, 17, 17, device=dev)
+    mm, vv = torch.zeros_like(S), torch.zeros_like(S)
+    d = e.triangular_adamw(S, mm, vv, 0.9, 0.999, 1e-8, 1, True)
+    from triune_b200.ops import reference as ref
+
+    m2, v2 = torch.zeros_like(S), torch.zeros_like(S)
+    d2 = ref.triangular_adamw_core(S, m2, v2, 1, 1.0, 0.9, 0.999, 1e-8, True)
+    assert _rel(d, d2) < 1e-4 and float(d.tril(-1).abs().max()) == 0.0
+
+
+def test_newton_schulz_tensor_core(dev):
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(9)
+    for shape in ((5, 384, 384), (3, 128, 512), (2, 512, 128)):
+        G = torch.randn(*shape, device=dev)
+        X = ops.muon_ns(G.to(torch.bfloat16), steps=8).float()
+        k = min(shape[1], shape[2])
+        gram = X @ X.transpose(1, 2) if shape[1] <= shape[2] else X.transpose(1, 2) @ X
+        assert float((gram - torch.eye(k, device=dev)).abs().max()) < 0.08
+        Xr = ref.newton_schulz(G, steps=8)
+        assert _rel(X, Xr) < 0.1
+
+
+def test_small_native_kernels(dev):
+    from triune_b200 import ops, _ext
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(10)
+    lg = torch.randn(1000, 3, device=dev)
+    assert torch.equal(ops.route_tiers(lg, 0.5).cpu(), ref.route_tiers(lg.cpu(), 0.5))
+    act = torch.randn(4096, device=dev)
+    assert torch.equal(ops.neuron_heatmap(act, 64).cpu(), ref.neuron_heatmap(act.cpu(), 64))
+    a2 = torch.randn(16, 64, device=dev)
+    tiers = torch.randint(0, 3, (16,), device=dev)
+    got = ops.tier_colour_render(a2, tiers).cpu().int()
+    exp = ref.tier_colour_render(a2.cpu(), tiers.cpu()).int()
+    assert int((got - exp).abs().max()) <= 1
+
+
+def test_model_step_matches_reference_ops(dev):
+    """Whole-model loss and a few gradients: sm_100a kernels vs the PyTorch statements, same bf16 weights."""
+    from triune_b200 import _ext
+    from triune_b200.config import ModelConfig
+    from triune_b200.models import TriuneTransformer
+    from triune_b200.utils import place_model
+
+    torch.manual_seed(11)
+    cfg = ModelConfig(vocab_size=2048, hidden_dim=128, num_layers=5, num_heads=2, head_dim=64, num_experts=8, top_k=2,
+                      router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=256, dense_hidden=256)
+    model = place_model(TriuneTransformer.from_config(cfg), dev, torch.bfloat16)
+    ids = torch.randint(0, 2048, (2, 129), device=dev)
+    res = []
+    for mode in (False, True):
+        _ext.set_reference_ops(mode)
+        try:
+            model.zero_grad()
+            loss = model.forward_loss(ids[:, :-1], ids[:, 1:], 2, n_valid=256)
+            loss.backward()
+            res.append((float(loss), model.layers[0].attn.gla.qkvg_weight.grad.float().clone(),
+                        model.layers[4].ffn.w1.grad.float().clone()))
+        finally:
+            _ext.set_reference_ops(False)
+    assert abs(res[0][0] - res[1][0]) < 5e-2
+    assert _rel(res[0][1], res[1][1]) < 0.15
+    assert _rel(res[0][2], res[1][2]) < 0.15

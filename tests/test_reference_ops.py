@@ -1,0 +1,145 @@
+"""CPU oracles: chunked forms vs token recurrences, codecs, optimizer math."""
+
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from triune_b200.ops import reference as ref
+
+
+@pytest.mark.parametrize("T", [1, 17, 32, 70, 128])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_gla_chunk_matches_recurrence(T, with_state):
+    torch.manual_seed(T)
+    B, H, D = 2, 2, 16
+    q, k, v = (torch.randn(B, T, H, D, dtype=torch.float64) for _ in range(3))
+    g = F.logsigmoid(torch.randn(B, T, H, D, dtype=torch.float64) * 2)
+    s0 = torch.randn(B, H, D, D, dtype=torch.float64) if with_state else None
+    o1, s1 = ref.gla_recurrent(q, k, v, g, s0)
+    o2, s2 = ref.gla_chunk(q, k, v, g, s0, chunk_size=32)
+    assert (o1 - o2).abs().max() < 1e-9 and (s1 - s2).abs().max() < 1e-9
+
+
+def test_gla_extreme_decay_is_finite_and_exact():
+    torch.manual_seed(0)
+    B, T, H, D = 1, 96, 1, 8
+    q, k, v = (torch.randn(B, T, H, D, dtype=torch.float64) for _ in range(3))
+    g = torch.full((B, T, H, D), -20.0, dtype=torch.float64)
+    o1, _ = ref.gla_recurrent(q, k, v, g)
+    o2, _ = ref.gla_chunk(q, k, v, g)
+    assert torch.isfinite(o2).all() and (o1 - o2).abs().max() < 1e-9
+
+
+def test_gla_grads_flow():
+    torch.manual_seed(1)
+    B, T, H, D = 1, 40, 1, 8
+    q, k, v = (torch.randn(B, T, H, D, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    g = (-torch.rand(B, T, H, D, dtype=torch.float64)).requires_grad_(True)
+    o, s = ref.gla_chunk(q, k, v, g, chunk_size=16)
+    (o.sum() + s.sum()).backward()
+    o2, s2 = ref.gla_recurrent(q.detach().requires_grad_(True), k, v, g)
+    assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in (q, k, v, g))
+
+
+@pytest.mark.parametrize("beta_kind", [None, "head"])
+def test_gated_deltanet_chunk_matches_recurrence(beta_kind):
+    torch.manual_seed(2)
+    B, T, H, D = 2, 75, 2, 16
+    q, v = (torch.randn(B, T, H, D, dtype=torch.float64) for _ in range(2))
+    k = F.normalize(torch.randn(B, T, H, D, dtype=torch.float64), dim=-1)
+    g = F.logsigmoid(torch.randn(B, T, H, D, dtype=torch.float64) * 2)
+    beta = torch.rand(B, T, H, dtype=torch.float64) if beta_kind else None
+    s0 = torch.randn(B, H, D, D, dtype=torch.float64)
+    o1, s1 = ref.gated_deltanet_recurrent(q, k, v, g, beta, s0)
+    o2, s2 = ref.gated_deltanet_chunk(q, k, v, g, beta, s0, chunk_size=32)
+    assert (o1 - o2).abs().max() < 1e-8 and (s1 - s2).abs().max() < 1e-8
+
+
+def test_decode_step_matches_recurrence():
+    torch.manual_seed(3)
+    B, T, H, D = 2, 5, 2, 8
+    q, k, v = (torch.randn(B, T, H, D) for _ in range(3))
+    g = F.logsigmoid(torch.randn(B, T, H, D))
+    o, s = ref.gla_recurrent(q, k, v, g)
+    st = torch.zeros(B, H, D, D)
+    for t in range(T):
+        ot, st = ref.gla_decode_step(q[:, t], k[:, t], v[:, t], g[:, t], st)
+        assert (ot - o[:, t]).abs().max() < 1e-5
+    assert (st - s).abs().max() < 1e-5
+
+
+def test_linear_cross_entropy_matches_dense():
+    torch.manual_seed(4)
+    h = torch.randn(50, 16, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(37, 16, dtype=torch.float64, requires_grad=True)
+    t = torch.randint(0, 37, (50,))
+    t[::5] = -100
+    loss, nv = ref.linear_cross_entropy(h, w, t, chunk=16)
+    loss.backward()
+    h2, w2 = h.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    F.cross_entropy(F.linear(h2, w2), t, ignore_index=-100).backward()
+    assert (h.grad - h2.grad).abs().max() < 1e-6 and (w.grad - w2.grad).abs().max() < 1e-6
+
+
+def test_newton_schulz_semiorthogonal_and_input_untouched():
+    torch.manual_seed(5)
+    G = torch.randn(3, 24, 60)
+    G0 = G.clone()
+    X = ref.newton_schulz(G, steps=10)
+    assert torch.equal(G, G0)
+    assert (X @ X.transpose(1, 2) - torch.eye(24)).abs().max() < 1e-3
+    Xt = ref.newton_schulz(G.transpose(1, 2).contiguous(), steps=10)
+    assert (Xt.transpose(1, 2) - X).abs().max() < 1e-3
+
+
+def test_triangular_adamw_equals_dense_on_triangular_core():
+    torch.manual_seed(6)
+    S = torch.randn(2, 9, 9).triu()
+    m1, v1, m2, v2 = (torch.zeros_like(S) for _ in range(4))
+    d1 = ref.triangular_adamw_core(S, m1, v1, 1, 1.0, 0.9, 0.999, 1e-8, True)
+    d2 = ref.triangular_adamw_core(S, m2, v2, 1, 1.0, 0.9, 0.999, 1e-8, False)
+    assert (d1 - d2.triu()).abs().max() < 1e-6
+    assert d1.tril(-1).abs().max() == 0
+    noisy = S + 1e-4 * torch.randn(2, 9, 9).tril(-1)
+    d3 = ref.triangular_adamw_core(noisy, torch.zeros_like(S), torch.zeros_like(S), 1, 1.0, 0.9, 0.999, 1e-8, False)
+    assert d3.tril(-1).abs().max() > 0.5  # unconstrained Adam amplifies sub-diagonal noise to O(1) steps
+
+
+def test_nvfp4_codec_and_fwht():
+    torch.manual_seed(7)
+    x = torch.randn(8, 64)
+    assert (ref.fwht16(ref.fwht16(x)) - x).abs().max() < 1e-5
+    codes = torch.arange(16, dtype=torch.uint8)
+    vals = ref.e2m1_decode(codes)
+    assert torch.equal(ref.e2m1_encode(vals) & 7, codes & 7)
+    w = torch.randn(64, 128)
+    for sd in (torch.float8_e4m3fn, torch.bfloat16):
+        p, s, t = ref.nvfp4_quantize(w, sd)
+        assert p.shape == (64, 64) and s.shape == (64, 8)
+        wd = ref.nvfp4_dequantize(p, s, t, torch.float32)
+        assert F.cosine_similarity(w.flatten(), wd.flatten(), dim=0) > 0.95
+
+
+def test_fp8_block_quant_roundtrip():
+    torch.manual_seed(8)
+    x, w = torch.randn(50, 300), torch.randn(130, 300)
+    xq, xs = ref.fp8_block_quantize_act(x)
+    wq, ws = ref.fp8_block_quantize_weight(w)
+    y = ref.fp8_block_gemm(xq, xs, wq, ws, out_dtype=torch.float32)
+    assert F.cosine_similarity(y.flatten(), (x @ w.t()).flatten(), dim=0) > 0.995
+
+
+def test_route_tiers_and_heatmap():
+    lg = torch.tensor([[5.0, 0.0, 0.0], [0.0, 2.0, 1.0], [0.0, 1.0, 2.0]])
+    assert ref.route_tiers(lg, 0.5).tolist() == [0, 1, 2]
+    hm = ref.neuron_heatmap(torch.linspace(0, 1, 640), 64)
+    assert hm.shape == (64,) and int(hm[-1]) >> 24 == 255
+
+
+def test_moe_capacity_mask_priority():
+    idx = torch.tensor([[0], [0], [0], [1]])
+    w = torch.tensor([[0.2], [0.9], [0.5], [0.1]])
+    keep = ref.moe_capacity_mask(idx, w, 2, 2)
+    assert keep[:, 0].tolist() == [False, True, True, True]

@@ -1,0 +1,194 @@
+"""Sequence mixers: gated linear attention, Gated DeltaNet and softmax attention.
+
+Parity: ``VectorisedGLA`` / ``HybridAttention`` of the reference (``triune/model/attention.py:296-653``):
+bias-free q/k/v/g/out projections, q,k = normalize(elu+1) then RoPE, g = logsigmoid, O(1) recurrent
+cache ``(state, offset)``. Design differences: the four input projections are ONE parameter
+(``qkvg_weight`` [4*H*D, dim]) so the fused GEMM needs no concatenation, and it is split back into
+``{q,k,v,g}_proj.weight`` only when a state dict is written or read.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..config import GLA_HEAD_DIM, ROPE_BASE, ROPE_MAX_SEQ_LEN
+from .rotary import RotaryEmbedding
+
+
+def parse_cache(cache: Any) -> Tuple[Optional[torch.Tensor], int, str]:
+    """Accept the three cache formats of the reference: tuple (state, offset), dict, bare tensor."""
+    if isinstance(cache, dict):
+        return cache.get("state"), int(cache.get("offset", 0)), "dict"
+    if isinstance(cache, tuple):
+        return cache[0], int(cache[1]), "tuple"
+    if torch.is_tensor(cache):
+        return cache, 0, "tensor"
+    return None, 0, "none"
+
+
+def format_cache(state, cache, fmt: str, offset: int, seq_len: int):
+    if fmt == "dict":
+        return {"state": state, "offset": offset + seq_len}
+    if fmt == "tuple":
+        return (state, offset + seq_len)
+    if fmt == "tensor":
+        return state
+    return (state, offset + seq_len) if cache is not None else None
+
+
+class _ProjView:
+    """Read-only stand-in for ``nn.Linear`` exposing a slice of the fused projection weight."""
+
+    def __init__(self, owner: "VectorisedGLA", index: int):
+        self._owner, self._index = owner, index
+
+    @property
+    def weight(self) -> torch.Tensor:
+        hd = self._owner.hidden_dim
+        return self._owner.qkvg_weight[self._index * hd : (self._index + 1) * hd]
+
+    bias = None
+
+    def __call__(self, x):
+        return F.linear(x, self.weight)
+
+
+class VectorisedGLA(nn.Module):
+    """Multi-head GLA (or Gated DeltaNet when ``use_delta_rule``) with fused QKVG projection."""
+
+    _SPLIT = ("q_proj", "k_proj", "v_proj", "g_proj")
+
+    def __init__(self, dim: int, heads: int, head_dim: int = GLA_HEAD_DIM, use_delta_rule: bool = False,
+                 use_rope: bool = True, rope_base: float = ROPE_BASE, rope_max_seq_len: int = ROPE_MAX_SEQ_LEN,
+                 learn_beta: bool = False):
+        super().__init__()
+        self.dim, self.heads, self.head_dim = dim, heads, head_dim
+        self.hidden_dim = heads * head_dim
+        self.use_delta_rule = use_delta_rule
+        self.use_rope = use_rope
+        self.qkvg_weight = nn.Parameter(torch.empty(4 * self.hidden_dim, dim))
+        self.out_proj = nn.Linear(self.hidden_dim, dim, bias=False)
+        self.beta_proj = nn.Linear(dim, heads, bias=False) if (use_delta_rule and learn_beta) else None
+        nn.init.normal_(self.qkvg_weight, mean=0.0, std=0.02)
+        if use_rope:
+            self.rope = RotaryEmbedding(head_dim, max_seq_len=rope_max_seq_len, base=rope_base)
+        self._register_state_dict_hook(self._split_on_save)
+        self._register_load_state_dict_pre_hook(self._fuse_on_load)
+
+    # --- reference-compatible checkpoint keys -----------------------------------------------
+    @staticmethod
+    def _split_on_save(module, state_dict, prefix, local_metadata):
+        w = state_dict.pop(prefix + "qkvg_weight")
+        hd = module.hidden_dim
+        for i, name in enumerate(VectorisedGLA._SPLIT):
+            state_dict[f"{prefix}{name}.weight"] = w[i * hd : (i + 1) * hd]
+        return state_dict
+
+    def _fuse_on_load(self, state_dict, prefix, *args):
+        keys = [f"{prefix}{n}.weight" for n in self._SPLIT]
+        if all(k in state_dict for k in keys):
+            state_dict[prefix + "qkvg_weight"] = torch.cat([state_dict.pop(k) for k in keys], dim=0)
+
+    @property
+    def q_proj(self):
+        return _ProjView(self, 0)
+
+    @property
+    def k_proj(self):
+        return _ProjView(self, 1)
+
+    @property
+    def v_proj(self):
+        return _ProjView(self, 2)
+
+    @property
+    def g_proj(self):
+        return _ProjView(self, 3)
+
+    def forward(self, x: torch.Tensor, cache=None):
+        B, T, _ = x.shape
+        H, D = self.heads, self.head_dim
+        state, offset, fmt = parse_cache(cache)
+        qkvg = ops.linear(x.reshape(B * T, self.dim), self.qkvg_weight)
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self.rope(T, x.device, offset=offset)
+        q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
+        if self.use_delta_rule:
+            beta = torch.sigmoid(self.beta_proj(x)).view(B, T, H) if self.beta_proj is not None else None
+            out, new_state = ops.gated_deltanet(q, k, v, g, beta=beta, initial_state=state, gate_logits=True)
+        else:
+            out, new_state = ops.gla(q, k, v, g, initial_state=state, gate_logits=True)
+        out = out.reshape(B, T, self.hidden_dim).to(x.dtype)
+        y = ops.linear(out, self.out_proj.weight)
+        return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
+
+
+class SoftmaxAttention(nn.Module):
+    """Causal softmax attention with RoPE, GQA and a KV cache (library SDPA; not on a named hot path).
+
+    Reference: the ``use_sdpa`` branch of ``HybridAttention`` (``triune/model/attention.py:606-653``) and the
+    dense model's attention (``triune/universal.py:200-266``).
+    """
+
+    def __init__(self, dim: int, heads: int, head_dim: Optional[int] = None, num_kv_heads: Optional[int] = None,
+                 rope_base: float = ROPE_BASE, rope_max_seq_len: int = ROPE_MAX_SEQ_LEN):
+        super().__init__()
+        self.dim, self.heads = dim, heads
+        self.head_dim = head_dim or dim // heads
+        self.kv_heads = num_kv_heads or heads
+        self.q_proj = nn.Linear(dim, heads * self.head_dim, bias=False)
+        self.k_proj = nn.Linear(dim, self.kv_heads * self.head_dim, bias=False)
+        self.v_proj = nn.Linear(dim, self.kv_heads * self.head_dim, bias=False)
+        self.out_proj = nn.Linear(heads * self.head_dim, dim, bias=False)
+        self.rope = RotaryEmbedding(self.head_dim, max_seq_len=rope_max_seq_len, base=rope_base)
+
+    def forward(self, x, cache=None):
+        B, T, _ = x.shape
+        past, offset, fmt = parse_cache(cache)
+        q = ops.linear(x, self.q_proj.weight).view(B, T, self.heads, self.head_dim)
+        k = ops.linear(x, self.k_proj.weight).view(B, T, self.kv_heads, self.head_dim)
+        v = ops.linear(x, self.v_proj.weight).view(B, T, self.kv_heads, self.head_dim)
+        cos, sin = self.rope(T, x.device, offset=offset)
+        q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+        if past is not None:
+            k = torch.cat((past[0], k), dim=1)
+            v = torch.cat((past[1], v), dim=1)
+        new_state = (k, v) if cache is not None else None
+        kk, vv = k, v
+        if self.kv_heads != self.heads:
+            rep = self.heads // self.kv_heads
+            kk, vv = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        o = F.scaled_dot_product_attention(
+            q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=(past is None and T > 1)
+        )
+        o = o.transpose(1, 2).reshape(B, T, self.heads * self.head_dim)
+        return ops.linear(o, self.out_proj.weight), format_cache(new_state, cache, fmt, offset, T)
+
+
+class HybridAttention(nn.Module):
+    """Attention slot of a block: GLA by default, softmax attention when ``use_sdpa``."""
+
+    def __init__(self, dim: int, heads: int, use_fp4: bool = False, use_fp8: bool = False, use_delta_rule: bool = False,
+                 use_sdpa: bool = False, layer_idx: int = 0, reflex_exit_layer: Optional[int] = None,
+                 head_dim: Optional[int] = None, **kwargs):
+        super().__init__()
+        self.dim, self.heads = dim, heads
+        self.use_sdpa = use_sdpa
+        self.layer_idx = layer_idx
+        self.head_dim = head_dim or (dim // heads if heads > 0 and dim % heads == 0 else GLA_HEAD_DIM)
+        if use_sdpa:
+            self.sdpa = SoftmaxAttention(dim, heads, self.head_dim, **{k: v for k, v in kwargs.items() if k in ("num_kv_heads",)})
+            self.gla = None
+        else:
+            self.gla = VectorisedGLA(dim, heads, self.head_dim, use_delta_rule=use_delta_rule,
+                                     **{k: v for k, v in kwargs.items() if k in ("use_rope", "rope_base", "rope_max_seq_len", "learn_beta")})
+            self.sdpa = None
+
+    def forward(self, x, cache=None):
+        return (self.sdpa if self.use_sdpa else self.gla)(x, cache=cache)

@@ -1,0 +1,33 @@
+"""Rotary position tables with on-demand growth (reference: triune/model/rotary.py:13-63)."""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+class RotaryEmbedding(nn.Module):
+    """Caches cos/sin [max_len, head_dim] (half-split layout); the cache doubles when a longer range is asked."""
+
+    def __init__(self, head_dim: int, max_seq_len: int = 8192, base: float = 10000.0):
+        super().__init__()
+        self.head_dim = head_dim
+        self.base = base
+        self.max_seq_len = max_seq_len
+        self._cos = None
+        self._sin = None
+
+    def _build(self, length: int, device):
+        cos, sin = ops.rope_tables(length, self.head_dim, self.base, 0, device)
+        self._cos, self._sin = cos, sin
+
+    def forward(self, seq_len: int, device, offset: int = 0):
+        need = offset + seq_len
+        if self._cos is None or self._cos.device != torch.device(device) or self._cos.shape[0] < need:
+            length = max(self.max_seq_len, 1)
+            while length < need:
+                length *= 2
+            self._build(length, device)
+        return self._cos[offset:need], self._sin[offset:need]

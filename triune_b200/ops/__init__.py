@@ -1,0 +1,686 @@
+"""Operator API.
+
+Each op has one meaning and two executors: the sm_100a kernels of ``triune_b200._C`` for CUDA bf16
+tensors, and the PyTorch statements in :mod:`triune_b200.ops.reference` for CPU tensors (and as test
+oracles). There is no silent fall-back on a GPU: a CUDA tensor without the built extension raises.
+
+Parity: this is the role of the reference's ``triune/ops/__init__.py:1-84`` facade and
+``triune/kernels/__init__.py:10-68``; the autograd functions below replace
+``triune/kernels/fast_rmsnorm.py``, ``fast_rope.py``, ``fast_swiglu.py``, ``fast_cross_entropy.py``,
+``fast_gla.py`` and the expert GEMM path of ``triune/model/moe.py:385-437``.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .. import _ext
+from . import reference as ref
+
+GEMM_DENSE, GEMM_GROUPED_M, GEMM_GROUPED_K = 0, 1, 2
+GF_OUT_F32, GF_ACCUMULATE, GF_GELU, GF_DGELU = 1, 2, 4, 8
+
+# kernel launch accounting (used by bench.py's ``gpu_launches``)
+_LAUNCHES = {"count": 0}
+
+
+def launch_count() -> int:
+    return _LAUNCHES["count"]
+
+
+def reset_launch_count() -> None:
+    _LAUNCHES["count"] = 0
+
+
+def _tick(n: int = 1) -> None:
+    _LAUNCHES["count"] += n
+
+
+# ----------------------------------------------------------------------------
+# GEMM
+# ----------------------------------------------------------------------------
+def _tma_ok(t: torch.Tensor) -> bool:
+    return (
+        t.is_cuda
+        and t.dtype == torch.bfloat16
+        and t.stride(-1) == 1
+        and t.stride(-2) % 8 == 0
+        and t.data_ptr() % 16 == 0
+        and (t.dim() == 2 or (t.dim() == 3 and t.stride(0) % 8 == 0))
+    )
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    out: Optional[torch.Tensor] = None,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    gelu: bool = False,
+    aux_out: Optional[torch.Tensor] = None,
+    dgelu_aux: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    out_dtype: torch.dtype = torch.bfloat16,
+    row_scale: Optional[torch.Tensor] = None,
+    mode: int = GEMM_DENSE,
+    tile_group: Optional[torch.Tensor] = None,
+    group_offsets: Optional[torch.Tensor] = None,
+    num_groups: int = 0,
+) -> torch.Tensor:
+    """out = alpha * A @ B^T with a fused epilogue, on tcgen05 tensor cores.
+
+    ``a`` is [.., M, K] (``a_mn``: stored [.., K, M]); ``b`` is [.., N, K] (``b_mn``: stored [.., K, N]).
+    ``mode``: dense/batched, rows grouped by expert (``tile_group``), or reduction grouped by expert
+    (``group_offsets``; then ``a`` [R, M], ``b`` [R, N] and out is [G, M, N]).
+    """
+    assert _tma_ok(a) and _tma_ok(b), "gemm operands must be CUDA bf16 with 16-byte aligned rows"
+    if mode == GEMM_GROUPED_K:
+        M, N = a.shape[-1], b.shape[-1]
+        shape = (num_groups, M, N)
+    else:
+        M = a.shape[-1] if a_mn else a.shape[-2]
+        N = b.shape[-1] if b_mn else b.shape[-2]
+        batch = a.shape[0] if a.dim() == 3 else (b.shape[0] if (b.dim() == 3 and mode == GEMM_DENSE) else None)
+        shape = (M, N) if batch is None else (batch, M, N)
+    if out is None:
+        out = torch.empty(shape, device=a.device, dtype=out_dtype)
+    flags = (GF_ACCUMULATE if accumulate else 0) | (GF_GELU if gelu else 0) | (GF_DGELU if dgelu_aux is not None else 0)
+    _ext.ext().tc_gemm(
+        a, b, out, a_mn, b_mn, mode, flags, float(alpha), bias, dgelu_aux, aux_out, row_scale, tile_group,
+        group_offsets, None,
+    )
+    _tick()
+    return out
+
+
+def _accumulate_weight_grad(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
+    """dW = dy^T x. Accumulates into ``w.main_grad`` (fp32) when the parameter has one, else returns bf16."""
+    mg = getattr(w, "main_grad", None)
+    if mg is not None:
+        gemm(dy2, x2, mg, a_mn=True, b_mn=True, accumulate=True)
+        return None
+    return gemm(dy2, x2, a_mn=True, b_mn=True)
+
+
+def _accumulate_bias_grad(b: Optional[torch.Tensor], dy2: torch.Tensor):
+    if b is None:
+        return None
+    db = dy2.sum(0, dtype=torch.float32)
+    mg = getattr(b, "main_grad", None)
+    if mg is not None:
+        mg.add_(db)
+        return None
+    return db.to(b.dtype)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not _tma_ok(x2):
+            x2 = x2.contiguous()
+        y = gemm(x2, w, bias=bias)
+        ctx.save_for_backward(x2, w, bias if bias is not None else torch.empty(0))
+        ctx.has_bias = bias is not None
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, bias = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w.shape[0])
+        if not _tma_ok(dy2):
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = _accumulate_weight_grad(w, dy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _accumulate_bias_grad(bias, dy2)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w^T + bias."""
+    if _ext.use_kernels(x, w) and x.dtype == torch.bfloat16 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+        return _LinearFn.apply(x, w, bias)
+    return F.linear(x, w, bias)
+
+
+class _MLPFn(torch.autograd.Function):
+    """Linear -> GELU(tanh) -> Linear with the activation and its derivative fused into GEMM epilogues."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not _tma_ok(x2):
+            x2 = x2.contiguous()
+        M, Hd = x2.shape[0], w1.shape[0]
+        pre = torch.empty(M, Hd, device=x.device, dtype=x.dtype)
+        h = gemm(x2, w1, bias=b1, gelu=True, aux_out=pre)
+        y = gemm(h, w2, bias=b2)
+        ctx.save_for_backward(x2, w1, b1, w2, b2, pre, h)
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, b1, w2, b2, pre, h = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w2.shape[0])
+        if not _tma_ok(dy2):
+            dy2 = dy2.contiguous()
+        dpre = gemm(dy2, w2, b_mn=True, dgelu_aux=pre)
+        dw2 = _accumulate_weight_grad(w2, dy2, h)
+        db2 = _accumulate_bias_grad(b2, dy2)
+        dx = gemm(dpre, w1, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        dw1 = _accumulate_weight_grad(w1, dpre, x2)
+        db1 = _accumulate_bias_grad(b1, dpre)
+        return dx, dw1, db1, dw2, db2
+
+
+def mlp_gelu(x, w1, b1, w2, b2):
+    """Dense FFN: gelu_tanh(x w1^T + b1) w2^T + b2."""
+    if _ext.use_kernels(x, w1, w2) and x.dtype == torch.bfloat16 and b1 is not None and b2 is not None:
+        return _MLPFn.apply(x, w1, b1, w2, b2)
+    return F.linear(ref.gelu_tanh(F.linear(x, w1, b1)), w2, b2)
+
+
+def gelu_tanh(x):
+    return ref.gelu_tanh(x)
+
+
+def swiglu(gate, up):
+    return ref.swiglu(gate, up)
+
+
+# ----------------------------------------------------------------------------
+# RMSNorm
+# ----------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xc = x.contiguous()
+        y, rstd, _ = _ext.ext().rmsnorm_fwd(xc, None, w, eps)
+        _tick()
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = _ext.ext().rmsnorm_bwd(x, w, dy, rstd, None)
+        _tick()
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            mg.add_(dw)
+            dw = None
+        else:
+            dw = dw.to(w.dtype)
+        return dx, dw, None
+
+
+class _AddRMSNormFn(torch.autograd.Function):
+    """(y, s) = (rmsnorm(x + r), x + r); one pass over x and r."""
+
+    @staticmethod
+    def forward(ctx, x, r, w, eps):
+        y, rstd, s = _ext.ext().rmsnorm_fwd(x.contiguous(), r.contiguous(), w, eps)
+        _tick()
+        ctx.save_for_backward(s, w, rstd)
+        return y, s
+
+    @staticmethod
+    def backward(ctx, dy, ds):
+        s, w, rstd = ctx.saved_tensors
+        if dy is None:
+            dy = torch.zeros_like(s)
+        dx, dw = _ext.ext().rmsnorm_bwd(s, w, dy, rstd, ds)
+        _tick()
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            mg.add_(dw)
+            dw = None
+        else:
+            dw = dw.to(w.dtype)
+        return dx, dx, dw, None
+
+
+def _norm_kernel_ok(x, w):
+    return (
+        _ext.use_kernels(x, w)
+        and x.dtype == torch.bfloat16
+        and w.dtype == torch.bfloat16
+        and x.shape[-1] % 8 == 0
+        and x.shape[-1] <= 2048
+    )
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    if _norm_kernel_ok(x, w):
+        return _RMSNormFn.apply(x, w, eps)
+    return ref.rmsnorm(x, w, eps)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float = 1e-6):
+    """Returns (rmsnorm(x + residual), x + residual)."""
+    if _norm_kernel_ok(x, w) and residual.is_cuda:
+        return _AddRMSNormFn.apply(x, residual, w, eps)
+    return ref.add_rmsnorm(x, residual, w, eps)
+
+
+# ----------------------------------------------------------------------------
+# RoPE + GLA feature map
+# ----------------------------------------------------------------------------
+def rope_tables(seq_len, head_dim, base=10000.0, offset=0, device=None):
+    return ref.rope_tables(seq_len, head_dim, base, offset, device)
+
+
+def apply_rope(x, cos, sin):
+    return ref.apply_rope(x, cos, sin)
+
+
+class _QKPrepFn(torch.autograd.Function):
+    """qkvg [tokens, 4*H*D] -> (q~, k~) = rope(normalize(elu(.)+1)); reads the q and k column blocks in place."""
+
+    @staticmethod
+    def forward(ctx, qkvg, cos_half, sin_half, T, H, D):
+        out = _ext.ext().qk_prep_fwd(qkvg, H * D, cos_half, sin_half, T, H, D)
+        _tick()
+        ctx.save_for_backward(qkvg, cos_half if cos_half is not None else torch.empty(0),
+                              sin_half if sin_half is not None else torch.empty(0))
+        ctx.dims = (T, H, D, cos_half is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkvg, cs, sn = ctx.saved_tensors
+        T, H, D, has_rope = ctx.dims
+        d_in = torch.zeros_like(qkvg)
+        _ext.ext().qk_prep_bwd(qkvg, H * D, dout.contiguous(), d_in, cs if has_rope else None,
+                               sn if has_rope else None, T, H, D)
+        _tick()
+        return d_in, None, None, None, None, None
+
+
+def qk_feature_map(qkvg: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], B: int, T: int,
+                   H: int, D: int):
+    """From the fused projection output [B*T, 4*H*D] return (q~, k~, v, g_logits), each [B, T, H, D].
+
+    q~, k~ are feature-mapped, normalised and rotated; v and the raw gate logits are strided views of
+    the projection output (no copy). cos/sin are [T, D] tables (half-split convention).
+    """
+    HD = H * D
+    if _ext.use_kernels(qkvg) and qkvg.dtype == torch.bfloat16 and D in (64, 128):
+        ch = cos[:, : D // 2].float().contiguous() if cos is not None else None
+        sh = sin[:, : D // 2].float().contiguous() if sin is not None else None
+        qk = _QKPrepFn.apply(qkvg, ch, sh, T, H, D)  # [tokens, 2, H, D]
+        qk = qk.view(B, T, 2, H, D)
+        q, k = qk[:, :, 0], qk[:, :, 1]
+    else:
+        qr = qkvg[:, :HD].reshape(B, T, H, D)
+        kr = qkvg[:, HD : 2 * HD].reshape(B, T, H, D)
+        qf = F.normalize(F.elu(qr.float()) + 1.0, p=2.0, dim=-1, eps=1e-6)
+        kf = F.normalize(F.elu(kr.float()) + 1.0, p=2.0, dim=-1, eps=1e-6)
+        if cos is not None:
+            qf = ref.apply_rope(qf, cos.float(), sin.float())
+            kf = ref.apply_rope(kf, cos.float(), sin.float())
+        q, k = qf.to(qkvg.dtype), kf.to(qkvg.dtype)
+    v = qkvg[:, 2 * HD : 3 * HD].view(B, T, H, D)
+    g = qkvg[:, 3 * HD :].view(B, T, H, D)
+    return q, k, v, g
+
+
+# ----------------------------------------------------------------------------
+# GLA / Gated DeltaNet
+# ----------------------------------------------------------------------------
+def gla(q, k, v, g, initial_state=None, scale: float = 1.0, gate_logits: bool = False, chunk_size: int = 64):
+    """Gated linear attention over [B,T,H,D] tensors; returns (out [B,T,H,Dv], final_state [B,H,Dk,Dv] fp32).
+
+    ``g`` is the per-dimension log decay (<= 0), or the raw gate logits when ``gate_logits`` (then
+    log-sigmoid is applied in fp32 inside the op, avoiding a bf16 round trip of the decays).
+    """
+    from . import gla_cuda
+
+    if gla_cuda.supported(q, k, v, g, initial_state):
+        return gla_cuda.gla_chunk(q, k, v, g, initial_state, scale, gate_logits)
+    gl = F.logsigmoid(g.float()) if gate_logits else g
+    if q.shape[1] == 1 and initial_state is not None and not torch.is_grad_enabled():
+        o, s = ref.gla_decode_step(q[:, 0], k[:, 0], v[:, 0], gl[:, 0], initial_state, scale)
+        return o.unsqueeze(1), s
+    return ref.gla_chunk(q, k, v, gl, initial_state, scale, chunk_size)
+
+
+def gla_recurrent(q, k, v, g, initial_state=None, scale: float = 1.0):
+    return ref.gla_recurrent(q, k, v, g, initial_state, scale)
+
+
+def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0, gate_logits: bool = False,
+                   chunk_size: int = 64):
+    gl = F.logsigmoid(g.float()) if gate_logits else g
+    if q.shape[1] == 1 and initial_state is not None and not torch.is_grad_enabled():
+        o, s = ref.gated_deltanet_decode_step(
+            q[:, 0], k[:, 0], v[:, 0], gl[:, 0], initial_state, None if beta is None else beta[:, 0], scale
+        )
+        return o.unsqueeze(1), s
+    return ref.gated_deltanet_chunk(q, k, v, gl, beta, initial_state, scale, chunk_size)
+
+
+# ----------------------------------------------------------------------------
+# Cross entropy
+# ----------------------------------------------------------------------------
+def cross_entropy(logits, targets, ignore_index: int = -100):
+    return ref.cross_entropy(logits, targets, ignore_index)
+
+
+class _LinearCEFn(torch.autograd.Function):
+    """Head GEMM + cross entropy in row chunks; the [N,V] logits never exist in full.
+
+    For each chunk: logits = h W^T (+b) on tensor cores, one kernel turns them into the loss and, in
+    place, into d(logits); two more GEMMs fold that into dh and dW. Gradients are therefore complete
+    at the end of forward; backward only scales them by the incoming scalar.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, bias, targets, ignore_index, n_valid, chunk_rows):
+        d = h.shape[-1]
+        h2 = h.reshape(-1, d)
+        if not _tma_ok(h2):
+            h2 = h2.contiguous()
+        t = targets.reshape(-1).contiguous()
+        N, V = h2.shape[0], w.shape[0]
+        need_grad = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        inv = 1.0 / float(n_valid)
+        losses = torch.empty(N, device=h.device, dtype=torch.float32)
+        dh = torch.empty_like(h2) if need_grad else None
+        dw = torch.empty(V, d, device=h.device, dtype=torch.float32) if need_grad else None
+        db = torch.zeros(V, device=h.device, dtype=torch.float32) if (need_grad and bias is not None) else None
+        e = _ext.ext()
+        first = True
+        for s in range(0, N, chunk_rows):
+            hc = h2[s : s + chunk_rows]
+            logits = gemm(hc, w, bias=bias)
+            losses[s : s + chunk_rows] = e.ce_fwd_bwd(logits, t[s : s + chunk_rows], ignore_index,
+                                                      inv if need_grad else 0.0)
+            _tick()
+            if need_grad:
+                gemm(logits, w, dh[s : s + chunk_rows], b_mn=True)
+                gemm(logits, hc, dw, a_mn=True, b_mn=True, accumulate=not first)
+                if db is not None:
+                    db += logits.sum(0, dtype=torch.float32)
+                first = False
+        loss = losses.sum() * inv
+        if need_grad:
+            ctx.save_for_backward(dh, dw, db if db is not None else torch.empty(0), w,
+                                  bias if bias is not None else torch.empty(0))
+        ctx.in_shape = h.shape
+        ctx.has_bias = bias is not None
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw, db, w, bias = ctx.saved_tensors
+        dh_out = (dh * g.to(dh.dtype)).view(ctx.in_shape)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            mg.add_(dw * g)
+            dw_out = None
+        else:
+            dw_out = (dw * g).to(w.dtype)
+        db_out = None
+        if ctx.has_bias:
+            bmg = getattr(bias, "main_grad", None)
+            if bmg is not None:
+                bmg.add_(db * g)
+            else:
+                db_out = (db * g).to(bias.dtype)
+        return dh_out, dw_out, db_out, None, None, None, None
+
+
+def linear_cross_entropy(h, w, targets, bias=None, ignore_index: int = -100, n_valid: Optional[int] = None,
+                         chunk_rows: int = 8192):
+    """Mean CE of (h @ w^T + bias) against targets. ``n_valid`` (non-ignored count) avoids a host sync."""
+    if _ext.use_kernels(h, w) and h.dtype == torch.bfloat16 and w.shape[0] % 8 == 0:
+        if n_valid is None:
+            n_valid = max(1, int((targets != ignore_index).sum().item()))
+        return _LinearCEFn.apply(h, w, bias, targets, ignore_index, n_valid, chunk_rows)
+    loss, _ = ref.linear_cross_entropy(h, w, targets, bias, ignore_index)
+    return loss
+
+
+# ----------------------------------------------------------------------------
+# Mixture of experts
+# ----------------------------------------------------------------------------
+def moe_route(logits, expert_bias, top_k, temperature=1.0):
+    return ref.moe_route(logits, expert_bias, top_k, temperature)
+
+
+def moe_plan(idx: torch.Tensor, keep: Optional[torch.Tensor], num_experts: int, tile: int = 128):
+    """Device-side dispatch plan (no host sync).
+
+    idx [N,k] expert ids, keep [N,k] accepted mask (or None). Expert row ranges are padded to multiples of
+    ``tile`` inside a buffer of static size R = ceil_tile(N*k) + E*tile. Returns
+      pos [N,k] int32          row of each assignment in the expert-major buffer (-1 = dropped)
+      row_src [R] int32        source token of each buffer row (-1 = padding)
+      tile_group [R/tile] int32 expert of each row tile (-1 = unused)
+      group_offsets [E+1] int32 padded row offsets per expert
+      counts [E] int64         accepted assignments per expert
+    """
+    N, k = idx.shape
+    E = num_experts
+    dev = idx.device
+    flat_e = idx.reshape(-1)
+    if keep is not None:
+        flat_e = torch.where(keep.reshape(-1), flat_e, torch.full_like(flat_e, E))
+    order = torch.argsort(flat_e, stable=True)
+    counts_all = torch.bincount(flat_e, minlength=E + 1)
+    counts = counts_all[:E]
+    padded = (counts + tile - 1) // tile * tile
+    cum_p = torch.cumsum(padded, 0)
+    starts_p = cum_p - padded
+    starts = torch.cumsum(counts_all, 0) - counts_all
+    e_sorted = flat_e[order]
+    rank = torch.arange(N * k, device=dev) - starts[e_sorted]
+    valid = e_sorted < E
+    starts_p_ext = torch.cat((starts_p, starts_p.new_zeros(1)))
+    pos_sorted = torch.where(valid, starts_p_ext[e_sorted] + rank, torch.full_like(rank, -1))
+    pos = torch.empty(N * k, device=dev, dtype=torch.int64)
+    pos[order] = pos_sorted
+    R = ((N * k + tile - 1) // tile) * tile + E * tile
+    row_src = torch.full((R + 1,), -1, device=dev, dtype=torch.int64)
+    row_src[torch.where(valid, pos_sorted, torch.full_like(pos_sorted, R))] = order // k
+    row_src = row_src[:R]
+    tile_start = torch.arange(R // tile, device=dev) * tile
+    tg = torch.searchsorted(cum_p, tile_start, right=True)
+    tile_group = torch.where(tg < E, tg, torch.full_like(tg, -1))
+    group_offsets = torch.cat((cum_p.new_zeros(1), cum_p))
+    return (
+        pos.view(N, k).to(torch.int32),
+        row_src.to(torch.int32),
+        tile_group.to(torch.int32),
+        group_offsets.to(torch.int32),
+        counts,
+    )
+
+
+class _GatherRowsFn(torch.autograd.Function):
+    """xp[r] = x[row_src[r]] (zero rows for padding). Backward sums the k copies of each token."""
+
+    @staticmethod
+    def forward(ctx, x, row_src, pos):
+        ctx.save_for_backward(pos)
+        out = _ext.ext().gather_rows(x, row_src, None)
+        _tick()
+        return out
+
+    @staticmethod
+    def backward(ctx, dxp):
+        (pos,) = ctx.saved_tensors
+        dx = _ext.ext().combine_rows(dxp.contiguous(), pos, None, None, 0.0)
+        _tick()
+        return dx, None, None
+
+
+class _CombineRowsFn(torch.autograd.Function):
+    """out[t] = sum_j w[t,j] * yp[pos[t,j]] (+ add_scale * add[t])."""
+
+    @staticmethod
+    def forward(ctx, yp, pos, w, row_src, add, add_scale):
+        ctx.save_for_backward(yp, pos, w, row_src)
+        ctx.add_scale = add_scale
+        ctx.has_add = add is not None
+        out = _ext.ext().combine_rows(yp, pos, w, add, add_scale)
+        _tick()
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        yp, pos, w, row_src = ctx.saved_tensors
+        e = _ext.ext()
+        dout = dout.contiguous()
+        # per buffer row weight: w of the assignment that owns the row
+        R = row_src.shape[0]
+        row_w = torch.zeros(R + 1, device=dout.device, dtype=torch.float32)
+        p64 = pos.reshape(-1).long()
+        row_w[torch.where(p64 >= 0, p64, torch.full_like(p64, R))] = w.reshape(-1)
+        dyp = e.gather_rows(dout, row_src, row_w[:R].contiguous())
+        dw = e.row_dots(dout, yp, pos)
+        _tick(2)
+        dadd = dout * ctx.add_scale if ctx.has_add else None
+        return dyp, None, dw, None, dadd, None
+
+
+class _ExpertMLPFn(torch.autograd.Function):
+    """Grouped expert FFN on the expert-major buffer: gelu(xp W1[e]^T + b1[e]) W2[e]^T + b2[e]."""
+
+    @staticmethod
+    def forward(ctx, xp, w1, b1, w2, b2, tile_group, group_offsets):
+        R = xp.shape[0]
+        Hd = w1.shape[1]
+        # Row tiles past the last expert are never written and never read: the combine / gather kernels
+        # follow `pos`, and the grouped weight-gradient GEMMs stay inside group_offsets.
+        pre = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)
+        h = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)
+        yp = torch.empty(R, w2.shape[1], device=xp.device, dtype=xp.dtype)
+        gemm(xp, w1, h, bias=b1, gelu=True, aux_out=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(h, w2, yp, bias=b2, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        ctx.save_for_backward(xp, w1, b1, w2, b2, pre, h, tile_group, group_offsets)
+        return yp
+
+    @staticmethod
+    def backward(ctx, dyp):
+        xp, w1, b1, w2, b2, pre, h, tile_group, group_offsets = ctx.saved_tensors
+        dyp = dyp.contiguous()
+        E = w1.shape[0]
+        R = xp.shape[0]
+        dpre = torch.empty(R, w1.shape[1], device=xp.device, dtype=xp.dtype)
+        gemm(dyp, w2, dpre, b_mn=True, dgelu_aux=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        dxp = torch.empty_like(xp)
+        gemm(dpre, w1, dxp, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        ones = torch.ones(R, 8, device=xp.device, dtype=xp.dtype)
+
+        def wgrad(w, a, b):
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                gemm(a, b, mg, a_mn=True, b_mn=True, accumulate=True, mode=GEMM_GROUPED_K,
+                     group_offsets=group_offsets, num_groups=E)
+                return None
+            return gemm(a, b, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=group_offsets, num_groups=E)
+
+        def bgrad(bp, a):
+            s = gemm(ones, a, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=group_offsets, num_groups=E,
+                     out_dtype=torch.float32)[:, 0, :]
+            mg = getattr(bp, "main_grad", None)
+            if mg is not None:
+                mg.add_(s)
+                return None
+            return s.to(bp.dtype)
+
+        dw2 = wgrad(w2, dyp, h)
+        db2 = bgrad(b2, dyp)
+        dw1 = wgrad(w1, dpre, xp)
+        db1 = bgrad(b1, dpre)
+        return dxp, dw1, db1, dw2, db2, None, None
+
+
+def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_scale: float = 0.0):
+    """Sparse expert FFN. x2 [N,d]; idx/weights/keep [N,k]; stacked expert weights w1 [E,H,d], b1 [E,H],
+    w2 [E,d,H], b2 [E,d]. Returns sum_j w_j * expert_{idx_j}(x) (+ shared_scale * shared_out)."""
+    E = w1.shape[0]
+    if _ext.use_kernels(x2, w1, w2) and x2.dtype == torch.bfloat16:
+        pos, row_src, tile_group, group_offsets, _ = moe_plan(idx, keep, E)
+        xp = _GatherRowsFn.apply(x2.contiguous(), row_src, pos)
+        yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets)
+        wk = weights.float().contiguous()
+        return _CombineRowsFn.apply(yp, pos, wk, row_src, shared_out, float(shared_scale))
+    # reference path: loop over experts
+    N, d = x2.shape
+    out = torch.zeros(N, d, dtype=torch.float32, device=x2.device)
+    wz = weights.float() * (keep.float() if keep is not None else 1.0)
+    for e in range(E):
+        sel = idx == e
+        tok = sel.any(-1).nonzero(as_tuple=True)[0]
+        if tok.numel() == 0:
+            continue
+        we = (wz * sel)[tok].sum(-1, keepdim=True)
+        y = F.linear(ref.gelu_tanh(F.linear(x2[tok], w1[e], b1[e])), w2[e], b2[e])
+        out.index_add_(0, tok, y.float() * we)
+    if shared_out is not None:
+        out = out + shared_scale * shared_out.float()
+    return out.to(x2.dtype)
+
+
+# ----------------------------------------------------------------------------
+# Optimizer / misc ops re-exported for the public facade
+# ----------------------------------------------------------------------------
+def muon_ns(G, steps: int = 3, coeffs=(1.875, -1.25, 0.375)):
+    from . import optim_cuda
+
+    if optim_cuda.ns_supported(G):
+        return optim_cuda.newton_schulz(G, steps, coeffs)
+    return ref.newton_schulz(G, steps, coeffs)
+
+
+def triangular_steer_update(P, G, momentum: float, steer_scale: float):
+    if _ext.use_kernels(P, G) and P.dtype == torch.float32 and P.is_contiguous() and G.is_contiguous():
+        _ext.ext().steer_update(P, G, momentum, steer_scale)
+        _tick()
+        return P
+    return ref.steer_update(P, G, momentum, steer_scale)
+
+
+def route_tiers(logits, threshold: float = 0.5):
+    if _ext.use_kernels(logits) and logits.dtype == torch.float32:
+        tiers, _ = _ext.ext().route_tiers(logits.contiguous(), threshold)
+        _tick()
+        return tiers
+    return ref.route_tiers(logits, threshold)
+
+
+def neuron_heatmap(act, num_bins: int):
+    if _ext.use_kernels(act):
+        out = _ext.ext().neuron_heatmap(act.float().contiguous().flatten(), num_bins)
+        _tick(2)
+        return out.to(torch.int64) & 0xFFFFFFFF
+    return ref.neuron_heatmap(act, num_bins)
+
+
+def tier_colour_render(act, tiers):
+    if _ext.use_kernels(act):
+        out = _ext.ext().tier_render(act.float().contiguous(), tiers.to(torch.int32).contiguous())
+        _tick()
+        return out.view(torch.uint8).view(act.shape[0], act.shape[1], 4)
+    return ref.tier_colour_render(act, tiers)
+
+
+fwht16 = ref.fwht16
+newton_schulz_reference = ref.newton_schulz

@@ -1,0 +1,56 @@
+"""Data parallelism over the flat gradient arena.
+
+The reference only wraps the model in DDP (``triune/trainer/distributed.py:142-156``) and never reaches it from
+its trainer. Here gradients live in ONE fp32 buffer (``ParamArena.flat_grad``), so data parallelism is a single
+collective over that buffer followed by the tiered update:
+
+* ``mode="nccl"``  baseline: NCCL all-reduce (average) of the flat buffer, every rank applies the full update;
+* ``mode="fused"`` product path: one kernel per tier reads every peer's gradient shard over NVLink, averages,
+  applies the AdamW / Muon update to the shard it owns and writes the new bf16 parameters into every peer's
+  parameter buffer (reduce-scatter + update + all-gather in one launch; see ``parallel/fused_dp.py``).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class ShardedDataParallel:
+    def __init__(self, ctx, mode: str = "nccl"):
+        self.ctx = ctx
+        self.mode = mode
+        self.optimizer = None
+        self.comm_bytes = 0
+        self._fused = None
+
+    def attach(self, optimizer) -> None:
+        self.optimizer = optimizer
+        if not hasattr(optimizer, "arena"):
+            raise ValueError("ShardedDataParallel needs an arena-based optimizer (CentroidSteerOptimizer)")
+        if self.ctx.world_size > 1:
+            # identical initial parameters on every rank
+            dist.broadcast(optimizer.arena.flat_param, src=0)
+            optimizer.arena.sync_master_from_params()
+            for b in optimizer.model.buffers():
+                dist.broadcast(b, src=0)
+        if self.mode == "fused" and self.ctx.world_size > 1:
+            from .fused_dp import FusedDPUpdater
+
+            self._fused = FusedDPUpdater(self.ctx, optimizer)
+        inner = optimizer.step
+
+        def step(closure=None):
+            if self.ctx.world_size > 1:
+                optimizer.arena.fold_autograd_grads()
+                if self._fused is not None:
+                    return self._fused.step()
+                g = optimizer.arena.flat_grad
+                dist.all_reduce(g, op=dist.ReduceOp.SUM)
+                g.mul_(1.0 / self.ctx.world_size)
+                self.comm_bytes += g.numel() * 4
+            return inner(closure)
+
+        optimizer.step = step
