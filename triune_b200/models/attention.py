@@ -16,6 +16,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from ..ops import gla_cuda
 from ..config import GLA_HEAD_DIM, ROPE_BASE, ROPE_MAX_SEQ_LEN
 from .rotary import RotaryEmbedding
 
@@ -118,6 +119,10 @@ class VectorisedGLA(nn.Module):
         cos = sin = None
         if self.use_rope:
             cos, sin = self.rope(T, x.device, offset=offset)
+        if not self.use_delta_rule and gla_cuda.core_supported(qkvg, T, D):
+            out, new_state = gla_cuda.gla_attention_core(qkvg, cos, sin, state, B, T, H)
+            y = ops.linear(out.view(B, T, self.hidden_dim), self.out_proj.weight)
+            return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
         q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
         if self.use_delta_rule:
             beta = torch.sigmoid(self.beta_proj(x)).view(B, T, H) if self.beta_proj is not None else None

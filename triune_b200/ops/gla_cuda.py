@@ -1,27 +1,174 @@
-"""Dispatch to the sm_100a chunked GLA kernels (forward, backward, decode step)."""
+"""Dispatch to the sm_100a chunked GLA kernels (forward, backward, decode step).
+
+Two entry points:
+  * :func:`gla_chunk` for separate ``[B,T,H,64]`` tensors (the public ``ops.gla`` signature);
+  * :func:`gla_attention_core` for the model: it consumes the fused projection output ``qkvg [B*T, 4*H*64]``
+    directly (feature map + RoPE kernel, then the chunk kernels read v and the gate logits in place through
+    strided TMA maps) and its backward writes all four gradients into one ``d qkvg`` buffer.
+
+Reference: ``triune/kernels/fast_gla.py:692-778`` (``fast_chunk_gla``) and ``triune/model/attention.py:360-572``.
+"""
 
 from __future__ import annotations
+
+import os
+from typing import Optional
 
 import torch
 
 from .. import _ext
 
+_CHECK = os.environ.get("TRIUNE_CHECK_STATUS", "0") == "1"
+last_status = None  # device int32 status word of the most recent launch group (0 = ok)
+
+
+def _note(status):
+    global last_status
+    last_status = status
+    if _CHECK and int(status.item()) != 0:
+        raise RuntimeError(f"GLA kernel reported status {int(status.item())} (bounded wait expired)")
+
+
+def _tick(n):
+    from . import _tick as t
+
+    t(n)
+
 
 def supported(q, k, v, g, initial_state) -> bool:
-    """True when the CUDA kernels cover this call (bf16, head_dim 64, T a multiple of 64)."""
+    """True when the CUDA kernels cover this call (bf16, head_dim 64, T a multiple of 64 or T == 1)."""
     if not _ext.use_kernels(q, k, v, g):
         return False
-    if not hasattr(_ext.ext(), "gla_fwd"):
-        return False
     B, T, H, D = q.shape
-    return (
-        q.dtype == torch.bfloat16
-        and D == 64
-        and v.shape[-1] == 64
-        and T % 64 == 0
-        and T >= 64
-    )
+    if q.dtype != torch.bfloat16 or D != 64 or v.shape[-1] != 64:
+        return False
+    if T == 1:
+        return initial_state is not None and not torch.is_grad_enabled()
+    return T >= 64
+
+
+def _as_matrix(x: torch.Tensor) -> torch.Tensor:
+    """[B,T,H,64] -> a 2-D [B*T, ld] matrix view whose columns h*64.. hold head h (copying only if needed)."""
+    B, T, H, D = x.shape
+    if x.stride(3) == 1 and x.stride(2) == D and x.stride(0) == T * x.stride(1) and x.stride(1) % 8 == 0 \
+            and x.data_ptr() % 16 == 0:
+        return x.as_strided((B * T, H * D), (x.stride(1), 1))
+    return x.contiguous().view(B * T, H * D)
+
+
+class _GLAFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, init, gate_logits):
+        B, T, H, D = q.shape
+        e = _ext.ext()
+        qm, km, vm, gm = (_as_matrix(t.to(torch.bfloat16)) for t in (q, k, v, g))
+        out = torch.empty(B * T, H * D, device=q.device, dtype=torch.bfloat16)
+        states, decay, fin, status = e.gla_fwd(qm, 0, km, 0, vm, 0, gm, 0, out, 0, init, B, T, H, gate_logits)
+        _tick(3)
+        _note(status)
+        ctx.save_for_backward(qm, km, vm, gm, states, decay)
+        ctx.dims = (B, T, H, D, gate_logits, init is not None)
+        fin = fin.view(B, H, D, D)
+        ctx.mark_non_differentiable(fin)
+        return out.view(B, T, H, D), fin
+
+    @staticmethod
+    def backward(ctx, dout, dfin):
+        qm, km, vm, gm, states, decay = ctx.saved_tensors
+        B, T, H, D, gate_logits, has_init = ctx.dims
+        e = _ext.ext()
+        dom = _as_matrix(dout.to(torch.bfloat16))
+        dq, dk, dv, dg = (torch.empty(B * T, H * D, device=dom.device, dtype=torch.bfloat16) for _ in range(4))
+        status = e.gla_bwd(qm, 0, km, 0, vm, 0, gm, 0, dom, 0, states, decay, dq, 0, dk, 0, dv, 0, dg, 0, B, T, H,
+                           gate_logits)
+        _tick(4)
+        _note(status)
+        sh = (B, T, H, D)
+        return dq.view(sh), dk.view(sh), dv.view(sh), dg.view(sh), None, None
 
 
 def gla_chunk(q, k, v, g, initial_state, scale, gate_logits):
-    raise NotImplementedError
+    """Kernel path of ``ops.gla``. Ragged tails (T % 64) are finished by the reference op with state carry."""
+    from . import reference as ref
+
+    B, T, H, D = q.shape
+    if T == 1:
+        return decode_step(q, k, v, g, initial_state, gate_logits)
+    Tm = (T // 64) * 64
+    out, state = _GLAFn.apply(q[:, :Tm], k[:, :Tm], v[:, :Tm], g[:, :Tm], initial_state, gate_logits)
+    if Tm < T:
+        gl = torch.nn.functional.logsigmoid(g[:, Tm:].float()) if gate_logits else g[:, Tm:]
+        o2, state = ref.gla_chunk(q[:, Tm:], k[:, Tm:], v[:, Tm:], gl, state, 1.0)
+        out = torch.cat((out, o2.to(out.dtype)), dim=1)
+    if scale != 1.0:
+        out = out * scale
+    return out, state
+
+
+@torch.no_grad()
+def decode_step(q, k, v, g, state, gate_logits):
+    """O(1) decode: q,k,v,g [B,1,H,64]; state [B,H,64,64] fp32 (updated in place when fp32-contiguous)."""
+    B, T, H, D = q.shape
+    e = _ext.ext()
+    st = state if (state.dtype == torch.float32 and state.is_contiguous()) else state.float().contiguous()
+    qm, km, vm, gm = (_as_matrix(t.to(torch.bfloat16)) for t in (q, k, v, g))
+    out = torch.empty(B, H * D, device=q.device, dtype=torch.bfloat16)
+    e.gla_decode(qm, 0, km, 0, vm, 0, gm, 0, st, out, 0, B, H, gate_logits)
+    _tick(1)
+    return out.view(B, 1, H, D), st
+
+
+class _GLACoreFn(torch.autograd.Function):
+    """qkvg [B*T, 4*H*64] -> attention output [B*T, H*64] (feature map, RoPE and the chunk scan fused)."""
+
+    @staticmethod
+    def forward(ctx, qkvg, cos_half, sin_half, init, B, T, H):
+        D = 64
+        HD = H * D
+        e = _ext.ext()
+        qk = e.qk_prep_fwd(qkvg, HD, cos_half, sin_half, T, H, D).view(B * T, 2 * HD)
+        out = torch.empty(B * T, HD, device=qkvg.device, dtype=torch.bfloat16)
+        states, decay, fin, status = e.gla_fwd(qk, 0, qk, HD, qkvg, 2 * HD, qkvg, 3 * HD, out, 0, init, B, T, H, True)
+        _tick(4)
+        _note(status)
+        none = torch.empty(0, device=qkvg.device)
+        ctx.save_for_backward(qkvg, qk, states, decay, cos_half if cos_half is not None else none,
+                              sin_half if sin_half is not None else none)
+        ctx.dims = (B, T, H, cos_half is not None)
+        fin = fin.view(B, H, D, D)
+        ctx.mark_non_differentiable(fin)
+        return out, fin
+
+    @staticmethod
+    def backward(ctx, dout, dfin):
+        qkvg, qk, states, decay, cs, sn = ctx.saved_tensors
+        B, T, H, rope = ctx.dims
+        D = 64
+        HD = H * D
+        e = _ext.ext()
+        dout = dout.contiguous()
+        dqk = torch.empty_like(qk)
+        dqkvg = torch.empty_like(qkvg)
+        status = e.gla_bwd(qk, 0, qk, HD, qkvg, 2 * HD, qkvg, 3 * HD, dout, 0, states, decay, dqk, 0, dqk, HD, dqkvg,
+                           2 * HD, dqkvg, 3 * HD, B, T, H, True)
+        e.qk_prep_bwd(qkvg, HD, dqk.view(B * T, 2, H, D), dqkvg, cs if rope else None, sn if rope else None, T, H, D)
+        _tick(5)
+        _note(status)
+        return dqkvg, None, None, None, None, None, None
+
+
+def core_supported(qkvg: torch.Tensor, T: int, D: int) -> bool:
+    return (
+        _ext.use_kernels(qkvg)
+        and qkvg.dtype == torch.bfloat16
+        and D == 64
+        and T % 64 == 0
+        and T >= 64
+        and qkvg.is_contiguous()
+    )
+
+
+def gla_attention_core(qkvg, cos, sin, init, B, T, H):
+    ch = cos[:, :32].float().contiguous() if cos is not None else None
+    sh = sin[:, :32].float().contiguous() if sin is not None else None
+    return _GLACoreFn.apply(qkvg, ch, sh, init, B, T, H)
