@@ -324,6 +324,7 @@ Tensor tier_render(const Tensor& act, const Tensor& tiers) {
 
 void register_gla(pybind11::module& m);
 void register_quant(pybind11::module& m);
+void register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tc_gemm", &tc_gemm);
@@ -347,4 +348,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tier_render", &tier_render);
   register_gla(m);
   register_quant(m);
+  register_comm(m);
 }

@@ -372,7 +372,7 @@ def triangular_adamw_core(S, m, v, step: int, lr: float, beta1: float, beta2: fl
 
 def steer_update(P: torch.Tensor, G: torch.Tensor, momentum: float, steer_scale: float) -> torch.Tensor:
     """In place P = momentum * P + steer_scale * (G - P)."""
-    return P.mul_(momentum).add_(G - P, alpha=steer_scale)
+    return P.copy_(momentum * P + steer_scale * (G - P))
 
 
 # ----------------------------------------------------------------------------

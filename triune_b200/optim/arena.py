@@ -44,7 +44,10 @@ class ParamArena:
     ALIGN = 128  # elements; keeps every segment 256-byte aligned for TMA and vector access
 
     def __init__(self, named_params: Sequence[Tuple[str, torch.nn.Parameter]], tiers: Dict[int, str],
-                 mat_views: Optional[Dict[int, Tuple[int, int, int]]] = None, master_dtype=torch.float32):
+                 mat_views: Optional[Dict[int, Tuple[int, int, int]]] = None, master_dtype=torch.float32,
+                 storage_factory=None):
+        """``storage_factory(total_elems, param_dtype, device) -> (flat_param, flat_grad)`` lets a caller place the
+        two arenas in special memory (the symmetric NVLink heap for the fused data-parallel step)."""
         mat_views = mat_views or {}
         seen = set()
         uniq = []
@@ -107,8 +110,14 @@ class ParamArena:
         self.steer_range = (self.muon_range[1], off)
         self.total = off
 
-        self.flat_param = torch.zeros(self.total, device=self.device, dtype=self.dtype)
-        self.flat_grad = torch.zeros(self.total, device=self.device, dtype=torch.float32)
+        if storage_factory is not None:
+            self.flat_param, self.flat_grad = storage_factory(self.total, self.dtype, self.device)
+            assert self.flat_param.numel() == self.total and self.flat_grad.numel() == self.total
+            self.flat_param.zero_()
+            self.flat_grad.zero_()
+        else:
+            self.flat_param = torch.zeros(self.total, device=self.device, dtype=self.dtype)
+            self.flat_grad = torch.zeros(self.total, device=self.device, dtype=torch.float32)
         self.flat_master = None
         if self.dtype != torch.float32:
             self.flat_master = torch.zeros(self.total, device=self.device, dtype=master_dtype)

@@ -147,7 +147,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                  use_triangular_core=True, core_mask_mode: str = "full", param_roles=None, eps: float = 1e-8,
                  grad_clip: Optional[float] = None, nesterov: bool = True, aspect_safeguard: bool = True,
                  adaptive_subspace_refresh: bool = False, energy_threshold: float = 0.5, min_subspace_gap: int = 5,
-                 max_subspace_gap: int = 50):
+                 max_subspace_gap: int = 50, storage_factory=None, shard: Tuple[int, int] = (0, 1)):
         if core_mask_mode not in ("full", "triu"):
             raise ValueError(f"Unknown core_mask_mode={core_mask_mode!r}; expected 'full' or 'triu'")
         self._in_set_lr = False
@@ -155,7 +155,8 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         tiers, mat_views, steer_meta = classify_parameters(model, param_roles, use_muon, aspect_safeguard)
         self.tiers, self.steer_meta = tiers, steer_meta
         named = list(model.named_parameters())
-        self.arena = ParamArena(named, tiers, mat_views)
+        self.arena = ParamArena(named, tiers, mat_views, storage_factory=storage_factory)
+        self.shard = (int(shard[0]), int(shard[1]))  # (rank, world): which matrices / experts this rank updates
         group = _SyncedParamGroup(self, {"params": [s.param for s in self.arena.segments], "lr": lr, "betas": betas,
                                          "weight_decay": weight_decay})
         super().__init__([group], dict(lr=lr, betas=betas, weight_decay=weight_decay))
@@ -193,6 +194,35 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         self.non_expert_params = [s.param for s in a.segments if s.tier == "adamw"]
         self.muon_params = [s.param for s in a.segments if s.tier == "muon"]
         self.layer_groups = [s for s in a.segments if s.tier == "steer"]
+
+    # ------------------------------------------------------------------ ownership (sharded data parallel)
+    def _owned(self, count: int) -> Tuple[int, int]:
+        r, w = self.shard
+        return (count * r) // w, (count * (r + 1)) // w
+
+    def owned_adamw_range(self) -> Tuple[int, int]:
+        lo, hi = self.arena.adamw_range
+        r, w = self.shard
+        per = -(-((hi - lo) // w) // 128) * 128 if w > 1 else hi - lo
+        b = min(hi, lo + r * per)
+        e = hi if r == w - 1 else min(hi, lo + (r + 1) * per)
+        return b, e
+
+    def owned_matrix_ranges(self):
+        """Flat element ranges of the Muon matrices and experts this rank updates."""
+        out = []
+        for g in self.arena.muon_groups:
+            m, n = g.shape
+            k0, k1 = self._owned(g.count)
+            if k1 > k0:
+                out.append((g.offset + k0 * m * n, g.offset + k1 * m * n))
+        for seg in self.arena.segments:
+            if seg.tier == "steer":
+                K, m, n = seg.mat_shape
+                k0, k1 = self._owned(K)
+                if k1 > k0:
+                    out.append((seg.offset + k0 * m * n, seg.offset + k1 * m * n))
+        return out
 
     # ------------------------------------------------------------------ learning rates
     def set_lr(self, lr: float, expert_lr: Optional[float] = None, muon_lr: Optional[float] = None):
@@ -286,32 +316,35 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             return
         from .. import ops
 
-        grad = a.flat_grad[lo:hi]
         beta = self.muon_momentum
         kern = self._use_kernels()
-        if kern:
-            u = torch.empty(hi - lo, device=a.device, dtype=torch.bfloat16)
-            _ext.ext().muon_momentum(self.muon_mom, grad, u, beta, self.nesterov, self._clip_coef)
-            ops._tick()
-        else:
-            g = grad * self._clip_coef
-            self.muon_mom.lerp_(g, 1 - beta)
-            u = torch.lerp(g, self.muon_mom, beta) if self.nesterov else self.muon_mom.clone()
         for grp in a.muon_groups:
             m, n = grp.shape
-            s, e = grp.offset - lo, grp.offset - lo + grp.count * m * n
-            U = u[s:e].view(grp.count, m, n)
-            O = ops.muon_ns(U, steps=self.muon_ns_steps, coeffs=self.ns_coeffs)
-            scale = muon_update_scale(m, n, self.muon_rms_target)
-            master = a.master()[grp.offset : grp.offset + grp.count * m * n]
+            k0, k1 = self._owned(grp.count)
+            if k1 == k0:
+                continue
+            s, e = grp.offset + k0 * m * n, grp.offset + k1 * m * n
+            grad = a.flat_grad[s:e]
+            mom = self.muon_mom[s - lo : e - lo]
             if kern:
-                pb = a.flat_param[grp.offset : grp.offset + grp.count * m * n] if a.flat_master is not None else None
+                u = torch.empty(e - s, device=a.device, dtype=torch.bfloat16)
+                _ext.ext().muon_momentum(mom, grad, u, beta, self.nesterov, self._clip_coef)
+                ops._tick()
+            else:
+                g = grad * self._clip_coef
+                mom.lerp_(g, 1 - beta)
+                u = torch.lerp(g, mom, beta) if self.nesterov else mom.clone()
+            O = ops.muon_ns(u.view(k1 - k0, m, n), steps=self.muon_ns_steps, coeffs=self.ns_coeffs)
+            scale = muon_update_scale(m, n, self.muon_rms_target)
+            master = a.master()[s:e]
+            if kern:
+                pb = a.flat_param[s:e] if a.flat_master is not None else None
                 _ext.ext().muon_apply(master, O.reshape(-1).contiguous(), pb, self.muon_lr, self.muon_weight_decay, scale)
                 ops._tick()
             else:
                 master.mul_(1 - self.muon_lr * self.muon_weight_decay).add_(O.reshape(-1).float(), alpha=-self.muon_lr * scale)
                 if a.flat_master is not None:
-                    a.flat_param[grp.offset : grp.offset + grp.count * m * n].copy_(master)
+                    a.flat_param[s:e].copy_(master)
 
     # ---- Tier 2 --------------------------------------------------------------------------------
     def _centroid_inputs(self, seg: Segment) -> Optional[torch.Tensor]:
@@ -329,8 +362,12 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         for seg in a.segments:
             if seg.tier != "steer":
                 continue
-            K, m, n = seg.mat_shape
-            G = a.grad_view(seg).view(K, m, n) * self._clip_coef
+            K_all, m, n = seg.mat_shape
+            k0, k1 = self._owned(K_all)
+            if k1 == k0:
+                continue
+            K = k1 - k0
+            G = a.grad_view(seg).view(K_all, m, n)[k0:k1] * self._clip_coef
             r = max(1, min(self.rank, min(m, n) - 1))
             st = self.steer_state.get(seg.name)
             if not self.use_triangular_core:
@@ -341,7 +378,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                 st["m"].mul_(b1).add_(G, alpha=1 - b1)
                 st["v"].mul_(b2).addcmul_(G, G, value=1 - b2)
                 d = (st["m"] / (1 - b1 ** st["step"])) / ((st["v"] / (1 - b2 ** st["step"])).sqrt() + self.eps)
-                self._apply_steer_delta(seg, d)
+                self._apply_steer_delta(seg, d, k0, k1)
                 continue
             if st is None:
                 st = self.steer_state[seg.name] = {
@@ -385,6 +422,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                 st["v"][:, :, r].zero_()
                 st["v"][:, r, :].zero_()
                 c = self._centroid_inputs(seg)
+                c = c[k0:k1] if c is not None else None
                 if c is not None and c.shape == (K, n):
                     v_orth, vn = reorthogonalise(c, st["Q_R"][:, :, :r])
                     u = (G @ v_orth.unsqueeze(-1)).squeeze(-1)
@@ -417,14 +455,14 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                 if not triu:
                     delta[:, r, :r] = delta[:, r, :r] * mult
             dW = QL @ delta @ QR.transpose(1, 2)
-            self._apply_steer_delta(seg, dW)
+            self._apply_steer_delta(seg, dW, k0, k1)
 
-    def _apply_steer_delta(self, seg: Segment, dW: torch.Tensor):
+    def _apply_steer_delta(self, seg: Segment, dW: torch.Tensor, k0: int, k1: int):
         a = self.arena
-        master = a.master_view(seg)
-        master.mul_(1 - self.expert_lr * self.expert_wd).add_(dW.view(seg.shape).to(master.dtype), alpha=-self.expert_lr)
+        master = a.master_view(seg)[k0:k1]
+        master.mul_(1 - self.expert_lr * self.expert_wd).add_(dW.to(master.dtype), alpha=-self.expert_lr)
         if a.flat_master is not None:
-            a.param_view(seg).copy_(master)
+            a.param_view(seg)[k0:k1].copy_(master)
 
     # ------------------------------------------------------------------ state dict / telemetry
     def state_dict(self):
