@@ -105,7 +105,8 @@ def run_ours(args):
     cfg = get_model_config("bench-90m")
     model = place_model(TriuneTransformer.from_config(cfg), dev, torch.bfloat16)
     run_cfg = {"lr": 3e-4, "min_lr": 3e-5, "warmup_steps": 10, "total_steps": 100000, "depth_mode": "cortex",
-               "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": VOCAB, "ns_steps": 5}
+               "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": VOCAB, "ns_steps": 5,
+               "cuda_graph": (not args.no_graph) and ctx.world_size == 1}
     opt = CentroidSteerOptimizer(model, lr=3e-4, muon_ns_steps=5, grad_clip=1.0)
     dp = ShardedDataParallel(ctx, mode=args.dp_mode) if ctx.world_size > 1 else None
     trainer = Trainer(model, run_cfg, optimizer=opt, device=dev, dp=dp)
@@ -117,8 +118,7 @@ def run_ours(args):
 
     def dev_step(i):
         x, y = dev_batches[i % len(dev_batches)]
-        trainer._pending = (x, y, x.numel())
-        return trainer.engine.step_once()
+        return trainer.step_on_device(x, y, x.numel())
 
     for i in range(args.warmup):
         dev_step(i)
@@ -137,7 +137,7 @@ def run_ours(args):
     ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
     launches = ops.launch_count()
     clocks = sampler.stop() if ctx.rank == 0 else None
-    final_loss = float(last["loss"])
+    final_loss = float(last)
 
     # ---- end-to-end loop through the public API: pinned H2D each step + loss D2H each step ----
     for _ in range(2):
@@ -166,6 +166,7 @@ def run_ours(args):
                        "global_batch": BATCH * ctx.world_size, "seq_len": SEQ,
                        "parallelism": f"dp{ctx.world_size}" + (f" ({args.dp_mode})" if ctx.world_size > 1 else ""),
                        "optimizer": "CentroidSteer (Muon NS 5 iters + triangular core + AdamW)",
+                       "cuda_graph": not args.no_graph,
                        "l2": "per-step working set (GBs of activations) far exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms,
@@ -194,6 +195,10 @@ def run_reference(args):
         from triune.optim.centroid import CentroidSteerOptimizer as RefOpt
         import triune.model.moe as rmoe
         import triune.model.attention as ratt
+
+        # the named config: expert hidden 1536 = 4 * d, top-2 (module-level constants of the reference)
+        rmoe.EXPERT_HIDDEN_MULTIPLIER = 4
+        rmoe.TOP_K_EXPERTS = 2
     except Exception as e:  # pragma: no cover
         print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}))
         return
@@ -296,6 +301,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA-graph replay)")
     ap.add_argument("--dp-mode", default=os.environ.get("TRIUNE_DP_MODE", "nccl"), choices=["nccl", "fused"])
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
@@ -304,8 +310,14 @@ def main():
         return
     if args.impl == "reference":
         run_reference(args)
-    else:
+        return
+    try:
         run_ours(args)
+    except Exception as e:  # a failed graph capture must not cost the measurement: rerun eagerly in a fresh process
+        if args.no_graph or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise
+        print(f"[bench] graph path failed ({type(e).__name__}: {e}); re-running with --no-graph", file=sys.stderr, flush=True)
+        os.execv(sys.executable, [sys.executable] + sys.argv + ["--no-graph"])
 
 
 if __name__ == "__main__":

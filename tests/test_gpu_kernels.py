@@ -238,7 +238,7 @@ def test_optimizer_kernels(dev):
     opt = torch.optim.AdamW([p_ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.05)
     coef = torch.tensor([0.5], device=dev)
     for step in (1, 2, 3):
-        e.adamw_flat(master, m, v, g, pb, 1e-2, 0.9, 0.95, 1e-8, 0.05, step, coef, 1.0)
+        e.adamw_flat(master, m, v, g, pb, 1e-2, 0.9, 0.95, 1e-8, 0.05, step, coef, 1.0, None)
         p_ref.grad = g * 0.5
         opt.step()
     assert _rel(master, p_ref.detach()) < 1e-5
@@ -248,7 +248,7 @@ def test_optimizer_kernels(dev):
     assert abs(float(out) - float(g.pow(2).sum())) / float(g.pow(2).sum()) < 1e-4
     S = torch.randn(6, 17, 17, device=dev)
     mm, vv = torch.zeros_like(S), torch.zeros_like(S)
-    d = e.triangular_adamw(S, mm, vv, 0.9, 0.999, 1e-8, 1, True)
+    d = e.triangular_adamw(S, mm, vv, 0.9, 0.999, 1e-8, 1, True, None)
     from triune_b200.ops import reference as ref
 
     m2, v2 = torch.zeros_like(S), torch.zeros_like(S)

@@ -1,0 +1,167 @@
+"""Device-timed micro-benchmarks of the sm_100a kernels with roofline fractions.
+
+    python -m triune_b200.bench_kernels --case gemm --m 8192 --n 8192 --k 8192
+    python -m triune_b200.bench_kernels --case all
+
+Each case warms up, flushes L2 between timed iterations (writes a 256 MB buffer), times with CUDA events and
+reports achieved FLOP/s or bytes/s against the measured peaks in ``MEASURED_PEAKS.json`` at the repository
+root when present (copy bandwidth and cuBLAS bf16 throughput measured on this machine pool), otherwise against
+6.65 TB/s and 1.59 PFLOP/s. The same entry point, with ``--iters`` small, is what the ncu captures under
+``profiles/`` run.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable, Dict
+
+import torch
+
+
+def peaks() -> Dict[str, float]:
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.fill_(1)
+
+
+def timeit(fn: Callable, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def report(name, ms, flops=0.0, nbytes=0.0):
+    pk = peaks()
+    out = {"case": name, "ms": round(ms, 4)}
+    if flops:
+        tf = flops / ms / 1e9
+        out.update(tflops=round(tf, 1), frac_of_peak=round(tf / pk["tflops"], 3))
+    if nbytes:
+        gbs = nbytes / ms / 1e6
+        out.update(gbs=round(gbs, 1), frac_of_hbm=round(gbs / pk["hbm_gbs"], 3))
+    out["peaks"] = pk["src"]
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def case_gemm(a):
+    from . import ops
+
+    M, N, K = a.m, a.n, a.k
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: ops.gemm(A, B, C), a.iters, a.warmup)
+    report(f"tc_gemm {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=2.0 * (M * K + N * K + M * N))
+
+
+def case_wgrad(a):
+    from . import ops
+
+    M, N, K = a.m, a.n, a.k  # dW[M,N] += dY[K,M]^T X[K,N]
+    dY = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    X = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    dW = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    ms = timeit(lambda: ops.gemm(dY, X, dW, a_mn=True, b_mn=True, accumulate=True), a.iters, a.warmup)
+    report(f"tc_gemm wgrad split-K {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=2.0 * K * (M + N) + 4.0 * M * N)
+
+
+def case_gla(a):
+    from . import ops
+
+    B, T, H, D = a.batch, a.seq, a.heads, 64
+    q, k, v, g = (torch.randn(B, T, H, D, device="cuda").to(torch.bfloat16).requires_grad_(True) for _ in range(4))
+    out = None
+
+    def fwd():
+        nonlocal out
+        out, _ = ops.gla(q, k, v, g, gate_logits=True)
+
+    ms = timeit(fwd, a.iters, a.warmup)
+    report(f"gla fwd B{B} T{T} H{H}", ms, nbytes=2.0 * 5 * B * T * H * D)
+    do = torch.randn_like(out)
+
+    def fb():
+        o, _ = ops.gla(q, k, v, g, gate_logits=True)
+        o.backward(do)
+
+    ms2 = timeit(fb, a.iters, a.warmup)
+    report(f"gla fwd+bwd B{B} T{T} H{H}", ms2, nbytes=2.0 * 14 * B * T * H * D)
+
+
+def case_rmsnorm(a):
+    from . import ops
+
+    x = torch.randn(a.m, a.n, device="cuda").to(torch.bfloat16)
+    w = torch.ones(a.n, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: ops.rmsnorm(x, w), a.iters, a.warmup)
+    report(f"rmsnorm {a.m}x{a.n}", ms, nbytes=4.0 * a.m * a.n)
+
+
+def case_ce(a):
+    from . import _ext
+
+    lg = torch.randn(a.m, a.n, device="cuda").to(torch.bfloat16)
+    t = torch.randint(0, a.n, (a.m,), device="cuda")
+    ms = timeit(lambda: _ext.ext().ce_fwd_bwd(lg, t, -100, 1.0 / a.m), a.iters, a.warmup)
+    report(f"cross_entropy fwd+grad {a.m}x{a.n}", ms, nbytes=6.0 * a.m * a.n)
+
+
+CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=6)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    if a.case != "all":
+        CASES[a.case](a)
+        return
+    for (m, n, k) in ((8192, 8192, 8192), (32768, 1536, 384), (32768, 384, 1536), (32768, 32000, 384)):
+        a.m, a.n, a.k = m, n, k
+        case_gemm(a)
+    for (m, n, k) in ((1536, 384, 32768), (384, 384, 32768), (32000, 384, 8192)):
+        a.m, a.n, a.k = m, n, k
+        case_wgrad(a)
+    case_gla(a)
+    a.m, a.n = 32768, 384
+    case_rmsnorm(a)
+    a.m, a.n = 8192, 32000
+    case_ce(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -227,7 +227,7 @@ Tensor row_dots(const Tensor& a, const Tensor& b, const Tensor& pos) {
 
 void adamw_flat(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, const c10::optional<Tensor>& param_bf16,
                 double lr, double beta1, double beta2, double eps, double wd, int64_t step,
-                const c10::optional<Tensor>& grad_scale_ptr, double grad_scale) {
+                const c10::optional<Tensor>& grad_scale_ptr, double grad_scale, const c10::optional<Tensor>& hyper) {
   TORCH_CHECK(master.scalar_type() == at::kFloat && master.is_contiguous(), "master must be fp32 contiguous");
   TORCH_CHECK(grad.is_contiguous() && grad.numel() == master.numel(), "grad shape mismatch");
   c10::cuda::CUDAGuard guard(master.device());
@@ -240,7 +240,8 @@ void adamw_flat(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, const 
   tb::launch_adamw_flat(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), gf32,
                         hp ? reinterpret_cast<__nv_bfloat16*>(param_bf16->data_ptr()) : nullptr, master.numel(),
                         (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, bc1, bc2,
-                        hs ? grad_scale_ptr->data_ptr<float>() : nullptr, (float)grad_scale, cur_stream());
+                        hs ? grad_scale_ptr->data_ptr<float>() : nullptr, (float)grad_scale,
+                        hyper.has_value() && hyper->defined() ? hyper->data_ptr<float>() : nullptr, cur_stream());
 }
 
 void sumsq(const Tensor& x, Tensor& out) {
@@ -259,12 +260,13 @@ void muon_momentum(Tensor& mom, const Tensor& grad, Tensor& u_out, double beta, 
 }
 
 void muon_apply(Tensor& master, const Tensor& o, const c10::optional<Tensor>& param_bf16, double lr, double wd,
-                double scale) {
+                double scale, const c10::optional<Tensor>& hyper) {
   c10::cuda::CUDAGuard guard(master.device());
   const bool hp = param_bf16.has_value() && param_bf16->defined();
   tb::launch_muon_apply(master.data_ptr<float>(), bf(o),
                         hp ? reinterpret_cast<__nv_bfloat16*>(param_bf16->data_ptr()) : nullptr, master.numel(),
-                        (float)lr, (float)wd, (float)scale, cur_stream());
+                        (float)lr, (float)wd, (float)scale,
+                        hyper.has_value() && hyper->defined() ? hyper->data_ptr<float>() : nullptr, cur_stream());
 }
 
 void axpby_bf16(Tensor& x, const Tensor& y, double a, double b) {
@@ -273,7 +275,7 @@ void axpby_bf16(Tensor& x, const Tensor& y, double a, double b) {
 }
 
 Tensor triangular_adamw(const Tensor& S, Tensor& m, Tensor& v, double beta1, double beta2, double eps, int64_t step,
-                        bool triu) {
+                        bool triu, const c10::optional<Tensor>& hyper) {
   TORCH_CHECK(S.scalar_type() == at::kFloat && S.is_contiguous() && S.dim() == 3 && S.size(1) == S.size(2),
               "S must be fp32 [n, r, r]");
   c10::cuda::CUDAGuard guard(S.device());
@@ -281,7 +283,7 @@ Tensor triangular_adamw(const Tensor& S, Tensor& m, Tensor& v, double beta1, dou
   tb::launch_triangular_adamw(S.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), delta.data_ptr<float>(),
                               (int)S.size(0), (int)S.size(1), (float)beta1, (float)beta2, (float)eps,
                               1.0f - (float)std::pow(beta1, (double)step), 1.0f - (float)std::pow(beta2, (double)step),
-                              triu, cur_stream());
+                              triu, hyper.has_value() && hyper->defined() ? hyper->data_ptr<float>() : nullptr, cur_stream());
   return delta;
 }
 

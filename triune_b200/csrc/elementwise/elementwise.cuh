@@ -41,7 +41,10 @@ void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b
 void launch_adamw_flat(float* master, float* m, float* v, const void* grad, bool grad_is_f32, __nv_bfloat16* param_bf16,
                        long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
                        float bias_corr1, float bias_corr2, const float* grad_scale_ptr, float grad_scale,
-                       cudaStream_t s);
+                       const float* hyper, cudaStream_t s);
+// `hyper` (optional, device fp32[8]) overrides host scalars so a captured CUDA graph follows the schedule:
+//   [0] lr  [1] adam 1-beta1^t  [2] adam 1-beta2^t  [3] muon lr  [4] expert lr  [5] core 1-beta1^t  [6] core 1-beta2^t
+//   [7] 1 - expert_lr * expert_wd
 // sum of squares of a flat buffer accumulated into out[0] (fp32 atomic per block).
 void launch_sumsq(const void* x, bool is_f32, long long n, float* out, cudaStream_t s);
 
@@ -50,13 +53,14 @@ void launch_muon_momentum(float* mom, const void* grad, bool grad_is_f32, __nv_b
                           bool nesterov, const float* grad_scale_ptr, cudaStream_t s);
 // W_master = W_master * (1 - lr*wd) - lr*scale*O ; also refresh bf16 copy.
 void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* param_bf16, long long n, float lr,
-                       float wd, float scale, cudaStream_t s);
+                       float wd, float scale, const float* hyper, cudaStream_t s);
 // X = a*X + Y (bf16, elementwise) used by the Newton-Schulz blend when not fused in a GEMM epilogue.
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s);
 
 // Batched triangular AdamW on [nmat, r1, r1] cores (fp32 state), optional upper-triangular mask.
 void launch_triangular_adamw(const float* S, float* m, float* v, float* delta, int nmat, int r1, float beta1,
-                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, cudaStream_t s);
+                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, const float* hyper,
+                             cudaStream_t s);
 // P = momentum*P + steer*(G-P)
 void launch_steer_update(float* P, const float* G, long long n, float momentum, float steer, cudaStream_t s);
 

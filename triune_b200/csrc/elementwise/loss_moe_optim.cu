@@ -244,8 +244,14 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ mas
                                                          float* __restrict__ v, const void* __restrict__ grad,
                                                          __nv_bfloat16* __restrict__ pb, long long n, float lr,
                                                          float beta1, float beta2, float eps, float wd, float bc1,
-                                                         float bc2, const float* __restrict__ gsp, float gs) {
+                                                         float bc2, const float* __restrict__ gsp, float gs,
+                                                         const float* __restrict__ hyper) {
   const float scale = gsp ? (*gsp) * gs : gs;
+  if (hyper) {  // device-resident hyper-parameters (CUDA-graph replay): lr, bias corrections
+    lr = hyper[0];
+    bc1 = hyper[1];
+    bc2 = hyper[2];
+  }
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float g = GRAD_F32 ? reinterpret_cast<const float*>(grad)[i]
                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i]);
@@ -294,7 +300,8 @@ __global__ void __launch_bounds__(256) muon_momentum_kernel(float* __restrict__ 
 __global__ void __launch_bounds__(256) muon_apply_kernel(float* __restrict__ master,
                                                          const __nv_bfloat16* __restrict__ o,
                                                          __nv_bfloat16* __restrict__ pb, long long n, float lr, float wd,
-                                                         float scale) {
+                                                         float scale, const float* __restrict__ hyper) {
+  if (hyper) lr = hyper[3];
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float p = master[i] * (1.f - lr * wd) - lr * scale * __bfloat162float(o[i]);
     master[i] = p;
@@ -312,7 +319,12 @@ __global__ void __launch_bounds__(256) axpby_bf16_kernel(__nv_bfloat16* __restri
 __global__ void __launch_bounds__(256) triangular_adamw_kernel(const float* __restrict__ S, float* __restrict__ m,
                                                                float* __restrict__ v, float* __restrict__ delta,
                                                                long long total, int r1, float beta1, float beta2,
-                                                               float eps, float bc1, float bc2, bool triu) {
+                                                               float eps, float bc1, float bc2, bool triu,
+                                                               const float* __restrict__ hyper) {
+  if (hyper) {
+    bc1 = hyper[5];
+    bc2 = hyper[6];
+  }
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int within = (int)(i % ((long long)r1 * r1));
@@ -436,16 +448,16 @@ void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b
 void launch_adamw_flat(float* master, float* m, float* v, const void* grad, bool grad_is_f32, __nv_bfloat16* param_bf16,
                        long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
                        float bias_corr1, float bias_corr2, const float* grad_scale_ptr, float grad_scale,
-                       cudaStream_t s) {
+                       const float* hyper, cudaStream_t s) {
   if (n == 0) return;
   if (grad_is_f32)
     adamw_flat_kernel<true><<<flat_grid(n), 256, 0, s>>>(master, m, v, grad, param_bf16, n, lr, beta1, beta2, eps,
                                                          weight_decay, bias_corr1, bias_corr2, grad_scale_ptr,
-                                                         grad_scale);
+                                                         grad_scale, hyper);
   else
     adamw_flat_kernel<false><<<flat_grid(n), 256, 0, s>>>(master, m, v, grad, param_bf16, n, lr, beta1, beta2, eps,
                                                           weight_decay, bias_corr1, bias_corr2, grad_scale_ptr,
-                                                          grad_scale);
+                                                          grad_scale, hyper);
 }
 
 void launch_sumsq(const void* x, bool is_f32, long long n, float* out, cudaStream_t s) {
@@ -466,9 +478,9 @@ void launch_muon_momentum(float* mom, const void* grad, bool grad_is_f32, __nv_b
 }
 
 void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* param_bf16, long long n, float lr,
-                       float wd, float scale, cudaStream_t s) {
+                       float wd, float scale, const float* hyper, cudaStream_t s) {
   if (n == 0) return;
-  muon_apply_kernel<<<flat_grid(n), 256, 0, s>>>(master, o, param_bf16, n, lr, wd, scale);
+  muon_apply_kernel<<<flat_grid(n), 256, 0, s>>>(master, o, param_bf16, n, lr, wd, scale, hyper);
 }
 
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s) {
@@ -477,11 +489,12 @@ void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float 
 }
 
 void launch_triangular_adamw(const float* S, float* m, float* v, float* delta, int nmat, int r1, float beta1,
-                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, cudaStream_t s) {
+                             float beta2, float eps, float bias_corr1, float bias_corr2, bool triu, const float* hyper,
+                             cudaStream_t s) {
   const long long total = (long long)nmat * r1 * r1;
   if (total == 0) return;
   triangular_adamw_kernel<<<flat_grid(total), 256, 0, s>>>(S, m, v, delta, total, r1, beta1, beta2, eps, bias_corr1,
-                                                           bias_corr2, triu);
+                                                           bias_corr2, triu, hyper);
 }
 
 void launch_steer_update(float* P, const float* G, long long n, float momentum, float steer, cudaStream_t s) {

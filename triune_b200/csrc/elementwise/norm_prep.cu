@@ -185,51 +185,85 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
 }
 
 // ---------------------------------------------------------------- q/k feature map + RoPE
-// in: rows of width in_ld holding q at column 0 and k at column HD_total (both [H, D]); one warp per
-// (token, head, q-or-k). out: [tokens, 2, H, D] contiguous. cos/sin: [T, D/2] fp32, token t uses
-// position (t % T) (tokens are laid out [B, T]).
+// in: rows of width in_ld holding q at column 0 and k at column k_col_offset (both [H, D]). One vector = one
+// (token, head, q-or-k) row of D elements, handled by D/8 lanes with one 16-byte load each; the rotation
+// partner of element i (i + D/2) lives in lane ^ (D/16). out: [tokens, 2, H, D] contiguous. cos/sin: [T, D/2]
+// fp32, token t uses position (t % T) (tokens are laid out [B, T]).
+template <int D>
+struct PrepGeom {
+  static constexpr int LPV = D / 8;        // lanes per vector
+  static constexpr int VPW = 32 / LPV;     // vectors per warp
+};
+
+template <int LPV>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPV / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
 template <int D>
 __global__ void __launch_bounds__(256) qk_prep_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_ld,
                                                           int k_col_offset, __nv_bfloat16* __restrict__ out,
                                                           const float* __restrict__ cs, const float* __restrict__ sn,
                                                           long long tokens, int T, int H) {
-  constexpr int PAIRS = D / 64;  // pairs (i, i + D/2) handled per lane
-  const int lane = threadIdx.x & 31;
+  constexpr int LPV = PrepGeom<D>::LPV, VPW = PrepGeom<D>::VPW;
+  const int lane = threadIdx.x & 31, sub = lane % LPV, vin = lane / LPV;
   const long long total = tokens * 2 * H;
-  for (long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); idx < total;
-       idx += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const int h = idx % H;
-    const int which = (idx / H) % 2;
-    const long long tok = idx / (2 * H);
-    const __nv_bfloat16* src = in + tok * in_ld + (which ? k_col_offset : 0) + h * D;
-    float f0[PAIRS], f1[PAIRS];
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long base = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; base < total;
+       base += warps * VPW) {
+    const long long idx = base + vin;
+    const bool live = idx < total;
+    const long long cidx = live ? idx : total - 1;
+    const int h = cidx % H;
+    const int which = (cidx / H) % 2;
+    const long long tok = cidx / (2 * H);
+    float f[8];
+    load8(in + tok * in_ld + (which ? k_col_offset : 0) + h * D + sub * 8, f);
     float ss = 0.f;
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-      const int i = lane + p * 32;
-      float a = __bfloat162float(src[i]), b = __bfloat162float(src[i + D / 2]);
-      a = a > 0.f ? a + 1.f : __expf(a);
-      b = b > 0.f ? b + 1.f : __expf(b);
-      f0[p] = a;
-      f1[p] = b;
-      ss += a * a + b * b;
+    for (int i = 0; i < 8; ++i) {
+      f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);
+      ss += f[i] * f[i];
     }
-    ss = warp_sum(ss);
+    ss = group_sum<LPV>(ss);
     const float inv = 1.0f / fmaxf(sqrtf(ss), 1e-6f);
-    __nv_bfloat16* dst = out + ((tok * 2 + which) * H + h) * D;
+    float o[8];
+    const bool upper = sub >= LPV / 2;
     const int pos = (int)(tok % T);
+    const int ci = (sub % (LPV / 2)) * 8;
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-      const int i = lane + p * 32;
+    for (int i = 0; i < 8; ++i) {
+      const float mine = f[i] * inv;
+      const float other = __shfl_xor_sync(0xffffffffu, mine, LPV / 2);
       float c = 1.f, s = 0.f;
       if (cs) {
-        c = cs[(long long)pos * (D / 2) + i];
-        s = sn[(long long)pos * (D / 2) + i];
+        c = cs[(long long)pos * (D / 2) + ci + i];
+        s = sn[(long long)pos * (D / 2) + ci + i];
       }
-      const float a = f0[p] * inv, b = f1[p] * inv;
-      dst[i] = __float2bfloat16(a * c - b * s);
-      dst[i + D / 2] = __float2bfloat16(b * c + a * s);
+      o[i] = upper ? (mine * c + other * s) : (mine * c - other * s);
     }
+    if (live) store8(out + ((tok * 2 + which) * H + h) * D + sub * 8, o);
   }
 }
 
@@ -242,58 +276,57 @@ __global__ void __launch_bounds__(256) qk_prep_bwd_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ d_in, long long d_in_ld,
                                                           const float* __restrict__ cs, const float* __restrict__ sn,
                                                           long long tokens, int T, int H) {
-  constexpr int PAIRS = D / 64;
-  const int lane = threadIdx.x & 31;
+  constexpr int LPV = PrepGeom<D>::LPV, VPW = PrepGeom<D>::VPW;
+  const int lane = threadIdx.x & 31, sub = lane % LPV, vin = lane / LPV;
   const long long total = tokens * 2 * H;
-  for (long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); idx < total;
-       idx += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const int h = idx % H;
-    const int which = (idx / H) % 2;
-    const long long tok = idx / (2 * H);
-    const __nv_bfloat16* src = in + tok * in_ld + (which ? k_col_offset : 0) + h * D;
-    const __nv_bfloat16* g = dout + ((tok * 2 + which) * H + h) * D;
-    float raw0[PAIRS], raw1[PAIRS], f0[PAIRS], f1[PAIRS], dn0[PAIRS], dn1[PAIRS];
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long base = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; base < total;
+       base += warps * VPW) {
+    const long long idx = base + vin;
+    const bool live = idx < total;
+    const long long cidx = live ? idx : total - 1;
+    const int h = cidx % H;
+    const int which = (cidx / H) % 2;
+    const long long tok = cidx / (2 * H);
+    float raw[8], f[8], g[8], dn[8];
+    load8(in + tok * in_ld + (which ? k_col_offset : 0) + h * D + sub * 8, raw);
+    load8(dout + ((tok * 2 + which) * H + h) * D + sub * 8, g);
     float ss = 0.f;
+    const bool upper = sub >= LPV / 2;
     const int pos = (int)(tok % T);
+    const int ci = (sub % (LPV / 2)) * 8;
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-      const int i = lane + p * 32;
-      raw0[p] = __bfloat162float(src[i]);
-      raw1[p] = __bfloat162float(src[i + D / 2]);
-      f0[p] = raw0[p] > 0.f ? raw0[p] + 1.f : __expf(raw0[p]);
-      f1[p] = raw1[p] > 0.f ? raw1[p] + 1.f : __expf(raw1[p]);
-      ss += f0[p] * f0[p] + f1[p] * f1[p];
+    for (int i = 0; i < 8; ++i) {
+      f[i] = raw[i] > 0.f ? raw[i] + 1.f : __expf(raw[i]);
+      ss += f[i] * f[i];
+      const float other = __shfl_xor_sync(0xffffffffu, g[i], LPV / 2);
       float c = 1.f, s = 0.f;
       if (cs) {
-        c = cs[(long long)pos * (D / 2) + i];
-        s = sn[(long long)pos * (D / 2) + i];
+        c = cs[(long long)pos * (D / 2) + ci + i];
+        s = sn[(long long)pos * (D / 2) + ci + i];
       }
-      const float ga = __bfloat162float(g[i]), gb = __bfloat162float(g[i + D / 2]);
-      dn0[p] = ga * c + gb * s;   // transpose of the rotation
-      dn1[p] = gb * c - ga * s;
+      // transpose of the rotation: lower half gets g*c + g_partner*s, upper half g*c - g_partner*s
+      dn[i] = upper ? (g[i] * c - other * s) : (g[i] * c + other * s);
     }
-    ss = warp_sum(ss);
-    const float nrm = fmaxf(sqrtf(ss), 1e-6f);
-    const float inv = 1.0f / nrm;
+    ss = group_sum<LPV>(ss);
+    const float inv = 1.0f / fmaxf(sqrtf(ss), 1e-6f);
     float dot = 0.f;
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) dot += f0[p] * inv * dn0[p] + f1[p] * inv * dn1[p];
-    dot = warp_sum(dot);
-    __nv_bfloat16* dst = d_in + tok * d_in_ld + (which ? k_col_offset : 0) + h * D;
+    for (int i = 0; i < 8; ++i) dot += f[i] * inv * dn[i];
+    dot = group_sum<LPV>(dot);
+    float o[8];
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-      const int i = lane + p * 32;
-      const float df0 = (dn0[p] - f0[p] * inv * dot) * inv;
-      const float df1 = (dn1[p] - f1[p] * inv * dot) * inv;
-      dst[i] = __float2bfloat16(df0 * (raw0[p] > 0.f ? 1.f : f0[p]));
-      dst[i + D / 2] = __float2bfloat16(df1 * (raw1[p] > 0.f ? 1.f : f1[p]));
+    for (int i = 0; i < 8; ++i) {
+      const float df = (dn[i] - f[i] * inv * dot) * inv;
+      o[i] = df * (raw[i] > 0.f ? 1.f : f[i]);
     }
+    if (live) store8(d_in + tok * d_in_ld + (which ? k_col_offset : 0) + h * D + sub * 8, o);
   }
 }
 
 inline int row_grid(long long work_items, int per_block) {
   long long b = (work_items + per_block - 1) / per_block;
-  const long long cap = 148ll * 8;
+  const long long cap = 148ll * 16;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
@@ -312,8 +345,8 @@ void launch_rmsnorm_fwd(const __nv_bfloat16* x, const __nv_bfloat16* res, const 
 void launch_rmsnorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy, const float* rstd,
                         const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw, int rows, int d, cudaStream_t s) {
   if (rows == 0) return;
-  long long b = ((long long)rows + 8 * 16 - 1) / (8 * 16);  // >=16 rows per warp so the dw atomics amortise
-  const int grid = (int)(b < 1 ? 1 : (b > 148 * 4 ? 148 * 4 : b));
+  long long b = ((long long)rows + 8 * 4 - 1) / (8 * 4);  // >=4 rows per warp so the dw atomics amortise
+  const int grid = (int)(b < 1 ? 1 : (b > 148 * 8 ? 148 * 8 : b));
   if (dres)
     rmsnorm_bwd_kernel<true><<<grid, 256, d * sizeof(float), s>>>(x, w, dy, rstd, dres, dx, dw, rows, d);
   else
@@ -323,7 +356,7 @@ void launch_rmsnorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __
 void launch_qk_prep_fwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, __nv_bfloat16* out, const float* cs,
                         const float* sn, long long tokens, int T, int H, int D, cudaStream_t s) {
   if (tokens == 0) return;
-  const int grid = row_grid(tokens * 2 * H, 8);
+  const int grid = row_grid(tokens * 2 * H, 8 * (256 / D));
   if (D == 64)
     qk_prep_fwd_kernel<64><<<grid, 256, 0, s>>>(in, in_ld, k_col_offset, out, cs, sn, tokens, T, H);
   else
@@ -334,7 +367,7 @@ void launch_qk_prep_bwd(const __nv_bfloat16* in, long long in_ld, int k_col_offs
                         __nv_bfloat16* d_in, long long d_in_ld, const float* cs, const float* sn, long long tokens,
                         int T, int H, int D, cudaStream_t s) {
   if (tokens == 0) return;
-  const int grid = row_grid(tokens * 2 * H, 8);
+  const int grid = row_grid(tokens * 2 * H, 8 * (256 / D));
   if (D == 64)
     qk_prep_bwd_kernel<64><<<grid, 256, 0, s>>>(in, in_ld, k_col_offset, dout, d_in, d_in_ld, cs, sn, tokens, T, H);
   else

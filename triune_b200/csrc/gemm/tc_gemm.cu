@@ -58,6 +58,8 @@ struct KParams {
   const int* group_offsets;
   int* status;
   int total_tiles;
+  int splits;           // split-K factor (dense mode, fp32 accumulate only)
+  int iters_per_split;  // K iterations (of 64) handled by one split
 };
 
 struct Tile {
@@ -81,6 +83,12 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     tl.k_iters = (p.K + BK - 1) / BK;
   } else {
     int per_b = p.num_m * p.num_n;
+    int split = 0;
+    if (p.splits > 1) {
+      const int base = per_b * p.batch;
+      split = t / base;
+      t = t % base;
+    }
     int b = t / per_b, r = t % per_b;
     tl.m0 = (r % p.num_m) * BM;
     tl.n0 = r / p.num_m;
@@ -94,8 +102,15 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     } else {
       tl.ba = p.a_batched ? b : 0;
       tl.bb = p.b_batched ? b : 0;
-      tl.k_begin = 0;
-      tl.k_iters = (p.K + BK - 1) / BK;
+      const int total_iters = (p.K + BK - 1) / BK;
+      if (p.splits > 1) {
+        tl.k_begin = split * p.iters_per_split * BK;
+        const int left = total_iters - split * p.iters_per_split;
+        tl.k_iters = left < p.iters_per_split ? (left < 0 ? 0 : left) : p.iters_per_split;
+      } else {
+        tl.k_begin = 0;
+        tl.k_iters = total_iters;
+      }
     }
   }
   return tl;
@@ -338,6 +353,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 float* cp = reinterpret_cast<float*>(p.C) + c_off + gn;
                 float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
                 float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
+                if (p.splits > 1) {
+                  // split-K partials meet in memory: vector reduction, no read-modify-write race
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp), "f"(o0.x), "f"(o0.y),
+                               "f"(o0.z), "f"(o0.w)
+                               : "memory");
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + 4), "f"(o1.x), "f"(o1.y),
+                               "f"(o1.z), "f"(o1.w)
+                               : "memory");
+                } else {
                 if (accumulate) {
                   float4 e0 = *reinterpret_cast<float4*>(cp);
                   float4 e1 = *reinterpret_cast<float4*>(cp + 4);
@@ -346,6 +370,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
                 *reinterpret_cast<float4*>(cp) = o0;
                 *reinterpret_cast<float4*>(cp + 4) = o1;
+                }
               } else {
                 __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + gn;
                 if (accumulate) {
@@ -446,6 +471,25 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
   kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
   kp.total_tiles = kp.num_m * kp.num_n * (a.mode == GEMM_GROUPED_M ? 1 : kp.batch);
+  kp.splits = 1;
+  kp.iters_per_split = 0;
+  // Split-K: weight gradients reduce over tens of thousands of tokens into a handful of output tiles; spread the
+  // reduction over idle SMs. Only when the output is an fp32 accumulator (partials are added with red.add).
+  if (a.mode == GEMM_DENSE && (kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr &&
+      a.row_scale == nullptr && !(kp.flags & (GF_GELU | GF_DGELU))) {
+    const int total_iters = (a.K + BK - 1) / BK;
+    const int sms = sm_count();
+    if (kp.total_tiles * 2 <= sms && total_iters >= 16) {
+      int splits = sms / kp.total_tiles;
+      const int max_splits = total_iters / 8;
+      if (splits > max_splits) splits = max_splits;
+      if (splits > 1) {
+        kp.iters_per_split = (total_iters + splits - 1) / splits;
+        kp.splits = (total_iters + kp.iters_per_split - 1) / kp.iters_per_split;
+        kp.total_tiles *= kp.splits;
+      }
+    }
+  }
 
   // Tensor maps. dims are {contiguous, rows, batch}.
   const uint64_t a_rows_total = (a.mode == GEMM_GROUPED_K) ? (uint64_t)a.K : 0;  // K = total rows for grouped-K

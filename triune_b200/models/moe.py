@@ -206,12 +206,13 @@ class MoE_FFN(nn.Module):
     def _update_routing_stats(self, x2, idx, w, keep):
         E, N = self.num_experts, x2.shape[0]
         target = max(1.0, float(N * self.top_k / E))
-        requested = torch.bincount(idx.reshape(-1), minlength=E)
+        flat = idx.reshape(-1)
+        requested = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, torch.ones_like(flat))
         if keep is None:
             accepted = requested
             acc_mask = torch.ones_like(idx, dtype=torch.bool)
         else:
-            accepted = torch.bincount(idx.reshape(-1), weights=keep.reshape(-1).float(), minlength=E).long()
+            accepted = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, keep.reshape(-1).long())
             acc_mask = keep
         dropped = (requested - accepted).clamp_min(0)
         self._overflow_counter.add_(dropped.sum())

@@ -482,7 +482,7 @@ def moe_plan(idx: torch.Tensor, keep: Optional[torch.Tensor], num_experts: int, 
     if keep is not None:
         flat_e = torch.where(keep.reshape(-1), flat_e, torch.full_like(flat_e, E))
     order = torch.argsort(flat_e, stable=True)
-    counts_all = torch.bincount(flat_e, minlength=E + 1)
+    counts_all = torch.zeros(E + 1, device=dev, dtype=torch.int64).scatter_add_(0, flat_e, torch.ones_like(flat_e))
     counts = counts_all[:E]
     padded = (counts + tile - 1) // tile * tile
     cum_p = torch.cumsum(padded, 0)

@@ -542,7 +542,7 @@ def moe_capacity_mask(idx: torch.Tensor, w: torch.Tensor, num_experts: int, capa
         e_sorted = idx[order, j]
         order2 = torch.argsort(e_sorted, stable=True)
         e2 = e_sorted[order2]
-        counts = torch.bincount(e2, minlength=num_experts)
+        counts = torch.zeros(num_experts, device=idx.device, dtype=torch.int64).scatter_add_(0, e2, torch.ones_like(e2))
         starts = torch.cumsum(counts, 0) - counts
         rank = torch.arange(N, device=idx.device) - starts[e2]
         tok = order[order2]

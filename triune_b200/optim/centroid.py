@@ -187,6 +187,9 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         lo, hi = a.muon_range
         self.muon_mom = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
         self.steer_state: Dict[str, Dict] = {}
+        self.capturable = False  # device-resident hyper-parameters (CUDA-graph replay)
+        self.hyper = torch.zeros(8, device=dev, dtype=torch.float32)
+        self._hyper_host = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
         self._clip_coef = torch.ones(1, device=dev, dtype=torch.float32)
         self._sumsq = torch.zeros(1, device=dev, dtype=torch.float32)
         self.last_grad_norm = None
@@ -237,6 +240,58 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                 g["lr"] = lr
         finally:
             self._in_set_lr = False
+
+    # ------------------------------------------------------------------ CUDA-graph support
+    def _hyper_arg(self):
+        return self.hyper if self.capturable else None
+
+    def _subspace_step_next(self) -> int:
+        for st in self.steer_state.values():
+            if "subspace_step" in st:
+                return int(st["subspace_step"]) + 1
+        return 1
+
+    def write_hyper(self, step_count: Optional[int] = None) -> None:
+        """Publish the hyper-parameters of the NEXT step to the device (one small async copy)."""
+        t = (self.step_count + 1) if step_count is None else step_count
+        b1, b2 = self.betas
+        e1, e2 = self.expert_betas
+        ts = self._subspace_step_next()
+        h = self._hyper_host
+        h[0], h[1], h[2] = self.lr, 1 - b1**t, 1 - b2**t
+        h[3], h[4] = self.muon_lr, self.expert_lr
+        h[5], h[6] = 1 - e1**ts, 1 - e2**ts
+        h[7] = 1 - self.expert_lr * self.expert_wd
+        self.hyper.copy_(h, non_blocking=True)
+
+    def step_kind(self) -> str:
+        """What the NEXT step will do in the CentroidSteer tier: 'refresh' (new bases; needs host decisions),
+        'steer' (steering axis refresh) or 'plain'. Used to pick a captured graph or the eager path."""
+        nxt = self.step_count + 1
+        kind = "plain"
+        for seg in self.arena.segments:
+            if seg.tier != "steer" or not self.use_triangular_core:
+                continue
+            st = self.steer_state.get(seg.name)
+            if st is None or st["proj_step"] is None or self.adaptive_subspace_refresh:
+                return "refresh"
+            if nxt - st["proj_step"] >= self.update_gap:
+                return "refresh"
+            if st["last_steer_step"] is None or nxt - st["last_steer_step"] >= self.steer_update_gap:
+                kind = "steer"
+        return kind
+
+    def advance_counters(self, kind: str) -> None:
+        """Host-side bookkeeping for a step that ran as a graph replay."""
+        self.step_count += 1
+        for seg in self.arena.segments:
+            st = self.steer_state.get(seg.name)
+            if st is None or "subspace_step" not in st:
+                continue
+            st["step"] += 1
+            st["subspace_step"] += 1
+            if kind == "steer":
+                st["last_steer_step"] = self.step_count
 
     def zero_grad(self, set_to_none: bool = True):
         self.arena.zero_grad()
@@ -295,7 +350,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         if self._use_kernels():
             pb = a.flat_param[lo:hi] if a.flat_master is not None else None
             _ext.ext().adamw_flat(master, self.exp_avg, self.exp_avg_sq, grad, pb, self.lr, b1, b2, self.eps,
-                                  self.weight_decay, t, self._clip_coef, 1.0)
+                                  self.weight_decay, t, self._clip_coef, 1.0, self._hyper_arg())
             from .. import ops
             ops._tick()
             return
@@ -339,7 +394,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             master = a.master()[s:e]
             if kern:
                 pb = a.flat_param[s:e] if a.flat_master is not None else None
-                _ext.ext().muon_apply(master, O.reshape(-1).contiguous(), pb, self.muon_lr, self.muon_weight_decay, scale)
+                _ext.ext().muon_apply(master, O.reshape(-1).contiguous(), pb, self.muon_lr, self.muon_weight_decay, scale, self._hyper_arg())
                 ops._tick()
             else:
                 master.mul_(1 - self.muon_lr * self.muon_weight_decay).add_(O.reshape(-1).float(), alpha=-self.muon_lr * scale)
@@ -444,7 +499,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             st["subspace_step"] += 1
             triu = self.core_mask_mode == "triu"
             if self._use_kernels():
-                delta = _ext.ext().triangular_adamw(S.contiguous(), st["m"], st["v"], b1, b2, self.eps, st["subspace_step"], triu)
+                delta = _ext.ext().triangular_adamw(S.contiguous(), st["m"], st["v"], b1, b2, self.eps, st["subspace_step"], triu, self._hyper_arg())
                 from .. import ops
                 ops._tick()
             else:
@@ -460,7 +515,10 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
     def _apply_steer_delta(self, seg: Segment, dW: torch.Tensor, k0: int, k1: int):
         a = self.arena
         master = a.master_view(seg)[k0:k1]
-        master.mul_(1 - self.expert_lr * self.expert_wd).add_(dW.to(master.dtype), alpha=-self.expert_lr)
+        if self.capturable:
+            master.mul_(self.hyper[7]).sub_(dW.to(master.dtype) * self.hyper[4])
+        else:
+            master.mul_(1 - self.expert_lr * self.expert_wd).add_(dW.to(master.dtype), alpha=-self.expert_lr)
         if a.flat_master is not None:
             a.param_view(seg)[k0:k1].copy_(master)
 

@@ -58,6 +58,11 @@ class Trainer:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._h2d_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self.graph_engine = None
+        if self.config.get("cuda_graph") and self.device.type == "cuda":
+            from ..runtime.cuda_graph import CUDAGraphEngine
+
+            self.graph_engine = CUDAGraphEngine(self)
 
     # ---- protocol used by TrainingEngine ------------------------------------------------------
     def next_batch(self):
@@ -86,11 +91,18 @@ class Trainer:
             labels = labels.to(self.device, non_blocking=nb)
         if n_valid is None:
             n_valid = int(labels.numel())  # callers with ignored labels pass the exact count
-        self._pending = (input_ids, labels, n_valid)
-        out = self.engine.step_once()
-        loss = out["loss"]
+        loss = self.step_on_device(input_ids, labels, n_valid)
         self.d2h_bytes += 4
         return float(loss.item() if torch.is_tensor(loss) else loss)
+
+    def step_on_device(self, input_ids: torch.Tensor, labels: torch.Tensor, n_valid: Optional[int] = None):
+        """One optimizer step on device-resident tensors; returns the loss as a device tensor (no host sync)."""
+        if n_valid is None:
+            n_valid = int(labels.numel())
+        if self.graph_engine is not None:
+            return self.graph_engine.train_step(input_ids, labels, n_valid)
+        self._pending = (input_ids, labels, n_valid)
+        return self.engine.step_once()["loss"]
 
     def fit(self, total_steps: Optional[int] = None):
         self._install_signal_handlers()
