@@ -1,0 +1,40 @@
+"""Multi-GPU tests (need >= 2 B200): the fused NVLink data-parallel step against the NCCL baseline."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(nproc, env_extra):
+    env = dict(os.environ)
+    env.update(env_extra)
+    env.setdefault("NCCL_NVLS_ENABLE", "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "mp_fused_dp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    res = [json.loads(l[len("RESULT "):]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and len(res) == nproc, p.stdout[-3000:] + p.stderr[-3000:]
+    return res
+
+
+@pytest.mark.parametrize("multimem", ["0", "1"])
+def test_fused_dp_matches_nccl_baseline(multimem):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _launch(min(n, 2) if n < 4 else min(n, 4), {"TRIUNE_TEST_MULTIMEM": multimem})
+    for r in res:
+        assert r["status"] == 0
+        assert r["ranks_agree"]
+        assert r["max_param_diff"] <= 2e-2 * max(1.0, r["param_scale"])
+        assert r["metric_ok"]
+        assert r["timeout_status"] == 4 and r["context_alive"]
+        assert abs(r["loss_ref"][-1] - r["loss_fused"][-1]) < 0.1

@@ -30,6 +30,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int EPI_TILE = 32 * 128;  // one staged output tile: 32 rows x 128 bytes
 
 template <int BN>
 struct GemmCfg {
@@ -38,7 +39,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {64,128,256}
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 4096 /*epilogue staging*/ + 1024 /*alignment slack*/ + 256;
 };
 
 struct KParams {
@@ -122,7 +123,8 @@ __device__ __forceinline__ void report(const KParams& p, int code) {
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-    tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
+    tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const KParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -130,7 +132,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint8_t* smemA = smem;
   uint8_t* smemB = smem + STAGES * Cfg::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* smem_epi = smem + STAGES * Cfg::STAGE_BYTES;  // 4 warps x 2 staging tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + 8 * EPI_TILE);
   uint64_t* full = bars;                    // [STAGES] TMA -> MMA
   uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
   uint64_t* acc_full = bars + 2 * STAGES;   // [2] MMA -> epilogue
@@ -152,6 +155,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     mbar_fence_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -272,13 +276,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
+    // Each warp owns 32 accumulator rows. Per column chunk (128 bytes of output: 64 bf16 or 32 fp32) it reads the
+    // fp32 accumulator from TMEM, applies the epilogue, writes the rows into a private 128B-swizzled staging tile
+    // and one lane hands the tile to TMA (plain store, or reduce-add for accumulate / split-K): global writes are
+    // full 128-byte lines regardless of the row pitch, and ragged M/N edges are clipped by the tensor map.
     const int lane_base = (warp & 3) * 32;
+    uint8_t* my_stage = smem_epi + (warp & 3) * (2 * EPI_TILE);
+    int buf = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool out_f32 = (p.flags & GF_OUT_F32) != 0;
-    const bool accumulate = (p.flags & GF_ACCUMULATE) != 0;
+    const bool reduce_add = ((p.flags & GF_ACCUMULATE) != 0) || p.splits > 1;
     const bool do_gelu = (p.flags & GF_GELU) != 0;
     const bool do_dgelu = (p.flags & GF_DGELU) != 0;
+    const int CW = out_f32 ? 32 : 64;  // columns per staged chunk
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       Tile tl = decode_tile(p, t);
       if (!tl.valid) continue;
@@ -292,107 +303,121 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const int n0 = tl.n0 * BN;
       const int gm = tl.m0 + lane_base + lane;
       const bool row_ok = gm < p.M;
-      const long long c_off = (p.mode == GEMM_GROUPED_M ? 0ll : (long long)tl.g * p.strideC) + (long long)gm * p.ldc;
+      const int out_batch = (p.mode == GEMM_GROUPED_M) ? 0 : tl.g;
+      const long long c_off = (long long)out_batch * p.strideC + (long long)gm * p.ldc;
       const __nv_bfloat16* bias = p.bias ? p.bias + (long long)tl.g * p.bias_stride : nullptr;
       const float rs = (p.row_scale && row_ok) ? p.row_scale[gm] : 1.0f;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
+      for (int c = 0; c < BN; c += CW) {
+        if (n0 + c >= p.N) break;
+        float v[64];
         if (tl.k_iters > 0) {
+          uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c, r);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (!out_f32) {
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c + 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]) * p.alpha;
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 64; ++i) v[i] = 0.f;
         }
-        if (row_ok) {
+        const int ngroups = CW / 8;
+        if (bias) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < 8; ++j) {
             const int gn = n0 + c + j * 8;
-            if (gn < p.N) {
-              float v[8];
+            if (j < ngroups && gn < p.N) {
+              uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j * 8 + i]) * p.alpha;
-              if (bias) {
-                uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
-                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float2 f = __bfloat1622float2(b2[i]);
-                  v[2 * i] += f.x;
-                  v[2 * i + 1] += f.y;
-                }
-              }
-              if (do_gelu) {
-                if (p.aux_out) {
-                  uint4 pre;
-                  pre.x = pack_bf16x2(v[0], v[1]);
-                  pre.y = pack_bf16x2(v[2], v[3]);
-                  pre.z = pack_bf16x2(v[4], v[5]);
-                  pre.w = pack_bf16x2(v[6], v[7]);
-                  *reinterpret_cast<uint4*>(p.aux_out + c_off + gn) = pre;
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = gelu_tanh_f(v[i]);
-              }
-              if (do_dgelu) {
-                uint4 av = *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn);
-                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float2 f = __bfloat1622float2(a2[i]);
-                  v[2 * i] *= gelu_tanh_grad_f(f.x);
-                  v[2 * i + 1] *= gelu_tanh_grad_f(f.y);
-                }
-              }
-              if (p.row_scale) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] *= rs;
-              }
-              if (out_f32) {
-                float* cp = reinterpret_cast<float*>(p.C) + c_off + gn;
-                float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
-                float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
-                if (p.splits > 1) {
-                  // split-K partials meet in memory: vector reduction, no read-modify-write race
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp), "f"(o0.x), "f"(o0.y),
-                               "f"(o0.z), "f"(o0.w)
-                               : "memory");
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + 4), "f"(o1.x), "f"(o1.y),
-                               "f"(o1.z), "f"(o1.w)
-                               : "memory");
-                } else {
-                if (accumulate) {
-                  float4 e0 = *reinterpret_cast<float4*>(cp);
-                  float4 e1 = *reinterpret_cast<float4*>(cp + 4);
-                  o0.x += e0.x; o0.y += e0.y; o0.z += e0.z; o0.w += e0.w;
-                  o1.x += e1.x; o1.y += e1.y; o1.z += e1.z; o1.w += e1.w;
-                }
-                *reinterpret_cast<float4*>(cp) = o0;
-                *reinterpret_cast<float4*>(cp + 4) = o1;
-                }
-              } else {
-                __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + gn;
-                if (accumulate) {
-                  uint4 ev = *reinterpret_cast<const uint4*>(cp);
-                  const __nv_bfloat162* e2 = reinterpret_cast<const __nv_bfloat162*>(&ev);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    float2 f = __bfloat1622float2(e2[i]);
-                    v[2 * i] += f.x;
-                    v[2 * i + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[0], v[1]);
-                o.y = pack_bf16x2(v[2], v[3]);
-                o.z = pack_bf16x2(v[4], v[5]);
-                o.w = pack_bf16x2(v[6], v[7]);
-                *reinterpret_cast<uint4*>(cp) = o;
+              for (int i = 0; i < 4; ++i) {
+                float2 f = __bfloat1622float2(b2[i]);
+                v[j * 8 + 2 * i] += f.x;
+                v[j * 8 + 2 * i + 1] += f.y;
               }
             }
           }
         }
+        if (do_gelu) {
+          if (p.aux_out) {  // pre-activation goes out through the same staging path (always bf16, 64 columns)
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            uint8_t* st = my_stage + buf * EPI_TILE;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmAux, st, n0 + c, tl.m0 + lane_base, out_batch);
+              tma_store_commit();
+            }
+            buf ^= 1;
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh_f(v[i]);
+        }
+        if (do_dgelu && row_ok) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int gn = n0 + c + j * 8;
+            if (gn < p.N) {
+              uint4 av = *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn);
+              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float2 f = __bfloat1622float2(a2[i]);
+                v[j * 8 + 2 * i] *= gelu_tanh_grad_f(f.x);
+                v[j * 8 + 2 * i + 1] *= gelu_tanh_grad_f(f.y);
+              }
+            }
+          }
+        }
+        if (p.row_scale) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] *= rs;
+        }
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* st = my_stage + buf * EPI_TILE;
+        if (out_f32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+            o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+            o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+            o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (reduce_add)
+            tma_reduce_add_3d(&tmC, st, n0 + c, tl.m0 + lane_base, out_batch);
+          else
+            tma_store_3d(&tmC, st, n0 + c, tl.m0 + lane_base, out_batch);
+          tma_store_commit();
+        }
+        buf ^= 1;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -402,6 +427,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         acc_phase ^= 1;
       }
     }
+    if (lane == 0) tma_store_wait<0>();  // staged tiles must be fully written before the CTA retires
+    __syncwarp();
   }
 
   tc_fence_before_sync();
@@ -413,7 +440,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 template <int BN, bool A_MN, bool B_MN>
-void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid, cudaStream_t stream) {
+void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmAux,
+                    const KParams& kp, int grid, cudaStream_t stream) {
   auto kern = tc_gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -421,18 +449,18 @@ void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const KParam
     if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm: cannot set shared memory size: ") + cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, kp);
+  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmAux, kp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm launch failed: ") + cudaGetErrorString(e));
 }
 
 template <int BN>
-void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid,
-                    cudaStream_t s) {
-  if (!a_mn && !b_mn) launch_variant<BN, false, false>(tmA, tmB, kp, grid, s);
-  else if (!a_mn && b_mn) launch_variant<BN, false, true>(tmA, tmB, kp, grid, s);
-  else if (a_mn && !b_mn) launch_variant<BN, true, false>(tmA, tmB, kp, grid, s);
-  else launch_variant<BN, true, true>(tmA, tmB, kp, grid, s);
+void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                    const CUtensorMap& tmAux, const KParams& kp, int grid, cudaStream_t s) {
+  if (!a_mn && !b_mn) launch_variant<BN, false, false>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  else if (!a_mn && b_mn) launch_variant<BN, false, true>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  else if (a_mn && !b_mn) launch_variant<BN, true, false>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  else launch_variant<BN, true, true>(tmA, tmB, tmC, tmAux, kp, grid, s);
 }
 
 int sm_count() {
@@ -455,6 +483,9 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.lda % 8 != 0 || a.ldb % 8 != 0) throw std::runtime_error("tc_gemm: lda/ldb must be multiples of 8");
   if (a.mode != GEMM_GROUPED_K && a.K <= 0) throw std::runtime_error("tc_gemm: K must be positive");
   if (a.mode == GEMM_GROUPED_M && a.tile_group == nullptr) throw std::runtime_error("tc_gemm: tile_group missing");
+  if ((a.flags & GF_OUT_F32) && (a.flags & (GF_GELU | GF_DGELU)))
+    throw std::runtime_error("tc_gemm: activation epilogues write bf16 outputs");
+  if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0) throw std::runtime_error("tc_gemm: C must be 16-byte aligned");
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
 
@@ -509,10 +540,22 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   } else {
     tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull, sB, BK, (uint32_t)BN);
   }
+  // output maps: rows of 128 bytes (64 bf16 / 32 fp32) x 32 rows, one box per epilogue warp and column chunk
+  const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
+  const int c_elem = c_f32 ? 4 : 2;
+  const uint64_t c_batches = (a.mode == GEMM_GROUPED_M) ? 1 : (uint64_t)kp.batch;
+  const uint64_t c_bstride = (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
+  CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
+                                 (uint64_t)a.N, (uint64_t)a.M, c_batches, (uint64_t)a.ldc * c_elem, c_bstride,
+                                 c_f32 ? 32 : 64, 32);
+  CUtensorMap tmAux = tmC;
+  if (a.aux_out != nullptr)
+    tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.M, c_batches,
+                         (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 64, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
-  if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
-  else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
-  else dispatch_major<64>(a.a_mn_major, a.b_mn_major, tmA, tmB, kp, grid, stream);
+  if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else dispatch_major<64>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
 }
 
 }  // namespace tb

@@ -19,12 +19,18 @@ import torch.distributed as dist
 
 
 class ShardedDataParallel:
-    def __init__(self, ctx, mode: str = "nccl"):
+    def __init__(self, ctx, mode: str = "nccl", use_multimem=None):
         self.ctx = ctx
         self.mode = mode
         self.optimizer = None
         self.comm_bytes = 0
         self._fused = None
+        self.storage_factory = None
+        if mode == "fused" and ctx.world_size > 1:
+            from .fused_dp import SymmetricArenaStorage
+
+            # pass this to the optimizer (``storage_factory=dp.storage_factory``) so its arenas are peer-visible
+            self.storage_factory = SymmetricArenaStorage(ctx, use_multimem=use_multimem)
 
     def attach(self, optimizer) -> None:
         self.optimizer = optimizer
@@ -39,7 +45,7 @@ class ShardedDataParallel:
         if self.mode == "fused" and self.ctx.world_size > 1:
             from .fused_dp import FusedDPUpdater
 
-            self._fused = FusedDPUpdater(self.ctx, optimizer)
+            self._fused = FusedDPUpdater(self.ctx, optimizer, self.storage_factory)
         inner = optimizer.step
 
         def step(closure=None):

@@ -1,0 +1,109 @@
+"""Fused data-parallel optimizer step over NVLink (no NCCL on the path).
+
+Layout: the optimizer's parameter arena (bf16) and gradient arena (fp32) live in one symmetric buffer, so every
+rank can read every peer's gradients and write every peer's parameters from inside a kernel.
+
+One step =
+  1. ``dp_reduce_scatter``   each rank pulls, for the element ranges it owns (its AdamW shard, its Muon matrices,
+                             its experts), the gradients of all ranks (peer loads or one ``multimem.ld_reduce``),
+                             scales by 1/world, accumulates the grad-norm partial and publishes it to all peers;
+  2. ``dp_adamw_allgather``  waits for all partials, derives the global clip coefficient, applies AdamW to the
+                             owned shard and stores the new bf16 weights straight into every peer's arena;
+  3. Muon / CentroidSteer    run on the owned matrices only (Newton-Schulz on the tcgen05 GEMM), then
+     ``dp_broadcast_ranges`` pushes the updated bf16 ranges to all peers;
+  4. ``comm_barrier``        nobody starts the next forward before every owner's stores have landed.
+
+Ownership is whole-matrix for the matrix tiers (Newton-Schulz and the subspace projections need entire matrices)
+and flat for the AdamW tier. Reference baseline: DDP all-reduce + full update on every rank
+(``triune/trainer/distributed.py:142-156``).
+"""
+
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _ext, ops
+from .symm import SymmetricBuffer
+
+CH_PARAMS_DONE = 2
+
+
+class SymmetricArenaStorage:
+    """``storage_factory`` for :class:`ParamArena` that places both arenas in a :class:`SymmetricBuffer`."""
+
+    def __init__(self, ctx, use_multimem=None):
+        self.ctx = ctx
+        self.use_multimem = use_multimem
+        self.buffer = None
+        self.total = 0
+
+    def __call__(self, total: int, dtype: torch.dtype, device: torch.device):
+        assert dtype == torch.bfloat16, "the fused data-parallel step needs bf16 parameters"
+        w = self.ctx.world_size
+        self.total = total
+        self.buffer = SymmetricBuffer(
+            {"param": total * 2, "grad": total * 4, "norm": 2 * w * 4 + 64, "metric": 16 * w * 4},
+            device, use_multimem=self.use_multimem)
+        return self.buffer.view("param", torch.bfloat16, total), self.buffer.view("grad", torch.float32, total)
+
+
+class FusedDPUpdater:
+    def __init__(self, ctx, optimizer, storage: SymmetricArenaStorage, wait_limit_s: float = 20.0):
+        self.ctx, self.opt, self.buf = ctx, optimizer, storage.buffer
+        if self.buf is None:
+            raise RuntimeError("optimizer was not built with SymmetricArenaStorage as storage_factory")
+        a = optimizer.arena
+        if a.flat_master is None:
+            raise RuntimeError("fused data parallelism expects bf16 parameters with fp32 masters")
+        optimizer.shard = (ctx.rank, ctx.world_size)
+        dev = a.device
+        self.counter = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.status = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.norm_out = torch.zeros(1, device=dev, dtype=torch.float32)
+        b, e = optimizer.owned_adamw_range()
+        self.adamw_owned = (b, e)
+        self.matrix_ranges: List[Tuple[int, int]] = optimizer.owned_matrix_ranges()
+        flat: List[int] = [b, e] if e > b else []
+        for r in self.matrix_ranges:
+            flat += [r[0], r[1]]
+        self.owned_flat = flat
+        self.bcast_flat = [x for r in self.matrix_ranges for x in r]
+        self.comm_bytes = 0
+        self.steps = 0
+
+    def step(self):
+        opt, buf = self.opt, self.buf
+        a = opt.arena
+        e = _ext.ext()
+        rank, world, bufs, sigs, mc = buf.table()
+        ep = buf.next_epoch()
+        opt.step_count += 1
+        goff, noff, poff = buf.offset("grad"), buf.offset("norm"), buf.offset("param")
+        e.dp_reduce_scatter(rank, world, bufs, sigs, mc, goff, noff, self.owned_flat, ep, buf.use_multimem, self.counter,
+                            self.status)
+        lo, hi = a.adamw_range
+        b1, b2 = opt.betas
+        clip = float(opt.grad_clip) if opt.grad_clip else 0.0
+        ob, oe = self.adamw_owned
+        e.dp_adamw_allgather(rank, world, bufs, sigs, mc, goff, noff, poff, ob, oe, lo, a.master()[lo:hi], opt.exp_avg,
+                             opt.exp_avg_sq, opt.lr, b1, b2, opt.eps, opt.weight_decay, opt.step_count, clip,
+                             opt._clip_coef, self.norm_out, ep, buf.use_multimem, self.status)
+        ops._tick(2)
+        opt.last_grad_norm = self.norm_out
+        opt._step_muon()
+        opt._step_steer()
+        if self.bcast_flat:
+            e.dp_broadcast_ranges(rank, world, bufs, sigs, mc, poff, self.bcast_flat, buf.use_multimem)
+            ops._tick()
+        e.comm_barrier(rank, world, bufs, sigs, CH_PARAMS_DONE, ep, self.status)
+        ops._tick()
+        owned = sum(self.owned_flat[i + 1] - self.owned_flat[i] for i in range(0, len(self.owned_flat), 2))
+        self.comm_bytes += owned * 4 * (world - 1) + owned * 2 * (world - 1)
+        self.steps += 1
+
+    def check(self) -> int:
+        """Status word of the bounded waits (0 = every wait completed). Synchronises."""
+        return int(self.status.item())
