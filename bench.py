@@ -121,8 +121,15 @@ def run_ours(args):
         x, y = dev_batches[i % len(dev_batches)]
         return trainer.step_on_device(x, y, x.numel())
 
+    # W warm-up steps, plus (graph mode) enough extra untimed steps for every step kind to have been captured:
+    # the CentroidSteer tier refreshes its steering axis every 10th step and that kind has its own graph.
+    priming = 0
     for i in range(args.warmup):
         dev_step(i)
+    if run_cfg["cuda_graph"]:
+        while priming < 24 and (trainer.graph_engine.captures < 2 or opt.step_kind() != "plain"):
+            dev_step(args.warmup + priming)
+            priming += 1
     barrier_sync()
     sampler = ClockSampler(ctx.local_rank)
     if ctx.rank == 0:
@@ -167,7 +174,7 @@ def run_ours(args):
                        "global_batch": BATCH * ctx.world_size, "seq_len": SEQ,
                        "parallelism": f"dp{ctx.world_size}" + (f" ({args.dp_mode})" if ctx.world_size > 1 else ""),
                        "optimizer": "CentroidSteer (Muon NS 5 iters + triangular core + AdamW)",
-                       "cuda_graph": not args.no_graph,
+                       "cuda_graph": bool(run_cfg["cuda_graph"]), "graph_priming_steps": priming,
                        "l2": "per-step working set (GBs of activations) far exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms,

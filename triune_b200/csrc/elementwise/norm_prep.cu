@@ -22,10 +22,10 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// Each lane holds up to MAXV 8-element vectors of its row (d <= 32*8*MAXV).
-constexpr int MAXV = 8;
+// Each lane holds up to MAXV 8-element vectors of its row (d <= 32*8*MAXV); MAXV is a template parameter so
+// narrow models do not pay registers for wide ones.
 
-template <bool HAS_RES>
+template <bool HAS_RES, int MAXV>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ res,
                                                           const __nv_bfloat16* __restrict__ w,
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) [+ dres_in]; dw += sum_rows dy * xhat (fp32 atomics,
 // one atomic per column per block after an in-block reduction).
-template <bool HAS_DRES>
+template <bool HAS_DRES, int MAXV>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ w,
                                                           const __nv_bfloat16* __restrict__ dy,
@@ -330,27 +330,46 @@ inline int row_grid(long long work_items, int per_block) {
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
+
+template <int MAXV>
+void rmsnorm_fwd_dispatch(const __nv_bfloat16* x, const __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y,
+                          __nv_bfloat16* sum_out, float* rstd, int rows, int d, float eps, int grid, cudaStream_t s) {
+  if (res)
+    rmsnorm_fwd_kernel<true, MAXV><<<grid, 256, 0, s>>>(x, res, w, y, sum_out, rstd, rows, d, eps);
+  else
+    rmsnorm_fwd_kernel<false, MAXV><<<grid, 256, 0, s>>>(x, nullptr, w, y, nullptr, rstd, rows, d, eps);
+}
+
+template <int MAXV>
+void rmsnorm_bwd_dispatch(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy, const float* rstd,
+                          const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw, int rows, int d, int grid,
+                          cudaStream_t s) {
+  if (dres)
+    rmsnorm_bwd_kernel<true, MAXV><<<grid, 256, d * sizeof(float), s>>>(x, w, dy, rstd, dres, dx, dw, rows, d);
+  else
+    rmsnorm_bwd_kernel<false, MAXV><<<grid, 256, d * sizeof(float), s>>>(x, w, dy, rstd, nullptr, dx, dw, rows, d);
+}
+
 }  // namespace
 
 void launch_rmsnorm_fwd(const __nv_bfloat16* x, const __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y,
                         __nv_bfloat16* sum_out, float* rstd, int rows, int d, float eps, cudaStream_t s) {
   if (rows == 0) return;
   const int grid = row_grid(rows, 8);
-  if (res)
-    rmsnorm_fwd_kernel<true><<<grid, 256, 0, s>>>(x, res, w, y, sum_out, rstd, rows, d, eps);
-  else
-    rmsnorm_fwd_kernel<false><<<grid, 256, 0, s>>>(x, nullptr, w, y, nullptr, rstd, rows, d, eps);
+  if (d <= 512) rmsnorm_fwd_dispatch<2>(x, res, w, y, sum_out, rstd, rows, d, eps, grid, s);
+  else if (d <= 1024) rmsnorm_fwd_dispatch<4>(x, res, w, y, sum_out, rstd, rows, d, eps, grid, s);
+  else rmsnorm_fwd_dispatch<8>(x, res, w, y, sum_out, rstd, rows, d, eps, grid, s);
 }
 
 void launch_rmsnorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy, const float* rstd,
                         const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw, int rows, int d, cudaStream_t s) {
   if (rows == 0) return;
-  long long b = ((long long)rows + 8 * 4 - 1) / (8 * 4);  // >=4 rows per warp so the dw atomics amortise
-  const int grid = (int)(b < 1 ? 1 : (b > 148 * 8 ? 148 * 8 : b));
-  if (dres)
-    rmsnorm_bwd_kernel<true><<<grid, 256, d * sizeof(float), s>>>(x, w, dy, rstd, dres, dx, dw, rows, d);
-  else
-    rmsnorm_bwd_kernel<false><<<grid, 256, d * sizeof(float), s>>>(x, w, dy, rstd, nullptr, dx, dw, rows, d);
+  // few, fat blocks: every block ends with d global atomics into dw, so the block count bounds the contention
+  long long b = ((long long)rows + 8 * 8 - 1) / (8 * 8);
+  const int grid = (int)(b < 1 ? 1 : (b > 148 * 3 ? 148 * 3 : b));
+  if (d <= 512) rmsnorm_bwd_dispatch<2>(x, w, dy, rstd, dres, dx, dw, rows, d, grid, s);
+  else if (d <= 1024) rmsnorm_bwd_dispatch<4>(x, w, dy, rstd, dres, dx, dw, rows, d, grid, s);
+  else rmsnorm_bwd_dispatch<8>(x, w, dy, rstd, dres, dx, dw, rows, d, grid, s);
 }
 
 void launch_qk_prep_fwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, __nv_bfloat16* out, const float* cs,

@@ -37,8 +37,8 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {64,128,256}
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int TMEM_COLS = (BN == 192) ? 512 : 2 * BN;  // power of two >= 2 * BN
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 4096 /*epilogue staging*/ + 1024 /*alignment slack*/ + 256;
 };
 
@@ -489,7 +489,8 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
 
-  const int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : (a.N > 64 ? 128 : 64);
+  // widest tile that divides N: the tensor core is most efficient at N = 256, then 192 (e.g. N = 384), then 128
+  const int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : ((a.N >= 192 && a.N % 192 == 0) ? 192 : (a.N > 64 ? 128 : 64));
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
   kp.mode = a.mode; kp.flags = a.flags; kp.batch = a.batch < 1 ? 1 : a.batch;
@@ -554,6 +555,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
                          (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 64, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
   if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else if (BN == 192) dispatch_major<192>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
   else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
   else dispatch_major<64>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
 }

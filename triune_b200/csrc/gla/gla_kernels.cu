@@ -64,30 +64,31 @@ __device__ __forceinline__ uint64_t desc_mn(uint32_t tile_addr, int kstep) {
   return make_smem_desc(tile_addr + kstep * 2048, TILE, 1024);
 }
 
-// Fills bmat[t][d] (fp32, 64x64) with the inclusive cumulative log decay of the gate tile.
+// Fills bmat[t][d] (fp32, 64x64) with the inclusive cumulative log decay of the gate tile. Works for any block of
+// 64*P threads (P in {2,4}): P partial scans of 64/P tokens per column, then the earlier parts' totals are added.
 __device__ __forceinline__ void build_cumsum(const uint8_t* g_tile, float* bmat, bool logits) {
-  const int tid = threadIdx.x;
-#pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  for (int idx = tid; idx < 512; idx += nthr) {
+    const int row = idx >> 3, ch = idx & 7;
     float f[8];
     unpack8(*reinterpret_cast<const uint4*>(g_tile + sw_off(row, ch)), f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) bmat[row * D + ch * 8 + i] = log_decay(f[i], logits);
   }
   __syncthreads();
-  const int d = tid & 63, half = tid >> 6;
+  const int parts = nthr >> 6, len = C / parts;
+  const int d = tid & 63, part = tid >> 6;
   float acc = 0.f;
-#pragma unroll 8
-  for (int t = half * 32; t < half * 32 + 32; ++t) {
+  for (int t = part * len; t < part * len + len; ++t) {
     acc += bmat[t * D + d];
     bmat[t * D + d] = acc;
   }
   __syncthreads();
-  if (half == 1) {
-    const float base = bmat[31 * D + d];
-#pragma unroll 8
-    for (int t = 32; t < 64; ++t) bmat[t * D + d] += base;
+  float base = 0.f;
+  for (int pp = 0; pp < part; ++pp) base += bmat[(pp * len + len - 1) * D + d];
+  __syncthreads();
+  if (part > 0) {
+    for (int t = part * len; t < part * len + len; ++t) bmat[t * D + d] += base;
   }
   __syncthreads();
 }
@@ -148,9 +149,8 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_chunk_outer_kernel(const __gr
   ok = bars->failed == 0;
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+    for (int idx = tid; idx < 512; idx += blockDim.x) {
+      const int row = idx >> 3, ch = idx & 7;
       uint4* px = reinterpret_cast<uint4*>(sX + sw_off(row, ch));
       float f[8];
       unpack8(*px, f);
@@ -231,10 +231,8 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const float* __restrict__
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void build_score_operands(const uint8_t* sQ, const uint8_t* sK, uint8_t* sA, uint8_t* sKt,
                                                      const float* bmat) {
-  const int tid = threadIdx.x;
-#pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int idx = tid + it * GLA_THREADS, row = idx >> 3, ch = idx & 7;
+  for (int idx = threadIdx.x; idx < 512; idx += blockDim.x) {
+    const int row = idx >> 3, ch = idx & 7;
     const uint32_t off = sw_off(row, ch);
     float q[8], k[8], bt[8];
     unpack8(*reinterpret_cast<const uint4*>(sQ + off), q);
@@ -287,6 +285,26 @@ __device__ __forceinline__ void load_acc_row(uint32_t tmem, uint32_t col, int wa
     tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[half * 32 + i] = __uint_as_float(r[i]);
+  }
+}
+
+// 32-column variants for the 8-warp backward kernel: warp w works on TMEM lane quarter (w & 3) and on columns
+// [32*(w>>2), 32*(w>>2)+32) of every 64-column accumulator.
+__device__ __forceinline__ void load_acc_half(uint32_t tmem, uint32_t col, int quarter, float (&v)[32]) {
+  uint32_t r[32];
+  tmem_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + col, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void store_row_half(uint8_t* tile, int row, int half, const float (&v)[32], int limit) {
+#pragma unroll
+  for (int c4 = 0; c4 < 4; ++c4) {
+    const int ch = half * 4 + c4;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (ch * 8 + i <= limit) ? v[c4 * 8 + i] : 0.f;
+    *reinterpret_cast<uint4*>(tile + sw_off(row, ch)) = pack8(o);
   }
 }
 
@@ -437,7 +455,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
 constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
 constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * C * D * 4 + 1024 + 256;
 
-__global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
+__global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
     const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ CUtensorMap tmS,
@@ -496,14 +514,14 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
   if (!ok) bars->failed = ST_TIMEOUT_FULL;
   __syncthreads();
   ok = bars->failed == 0;
-  const int row = warp * 16 + (lane & 15);  // accumulator row owned by this thread when lane < 16
+  const int quarter = warp & 3, half = warp >> 2;  // TMEM lane quarter / 32-column half of this warp
+  const int row = quarter * 16 + (lane & 15);       // accumulator row owned by this thread when lane < 16
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
     build_score_operands(sQ, sK, sA, sKt, bmat);
     // K_end[s] = k_s e^{b_C - b_s}
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + it * GLA_THREADS, r = idx >> 3, ch = idx & 7;
+    for (int idx = tid; idx < 512; idx += blockDim.x) {
+      const int r = idx >> 3, ch = idx & 7;
       const uint32_t off = sw_off(r, ch);
       float k[8];
       unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
@@ -526,11 +544,11 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[64];
-      load_acc_row(tmem, 0, warp, v);
-      if (lane < 16) store_row_tile(sP, row, v, row);
-      load_acc_row(tmem, 64, warp, v);
-      if (lane < 16) store_row_tile(sdP, row, v, row);
+      float v[32];
+      load_acc_half(tmem, 0 + 32 * half, quarter, v);
+      if (lane < 16) store_row_half(sP, row, half, v, row);
+      load_acc_half(tmem, 64 + 32 * half, quarter, v);
+      if (lane < 16) store_row_half(sdP, row, half, v, row);
       fence_proxy_async_smem();
       tc_fence_before_sync();
     } else if (lane == 0) {
@@ -562,13 +580,14 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[64];
+      float v[32];
+      const int c0 = 32 * half;  // first column handled by this thread
       // dv
-      load_acc_row(tmem, 128, warp, v);
+      load_acc_half(tmem, 128 + c0, quarter, v);
       if (lane < 16) {
-        __nv_bfloat16* dst = dv + (long long)(row0 + row) * dv_ld + dvcol + h * D;
+        __nv_bfloat16* dst = dv + (long long)(row0 + row) * dv_ld + dvcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < 4; ++ch) {
           float o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = v[ch * 8 + i];
@@ -576,31 +595,31 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
         }
       }
       // dq
-      float acc[64];
-      load_acc_row(tmem, 192, warp, v);
+      float acc[32];
+      load_acc_half(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < 64; ++d) acc[d] = v[d] * __expf(bmat[row * D + d]);
+      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bmat[row * D + c0 + d]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        load_acc_row(tmem, 256 + 64 * j, warp, v);  // warp-collective: every lane executes the load
+        load_acc_half(tmem, 256 + 64 * j + c0, quarter, v);  // warp-collective: every lane executes the load
         if (j <= (row >> 4)) {
 #pragma unroll
-          for (int d = 0; d < 64; ++d) {
-            const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + d];
-            acc[d] += v[d] * __expf(bmat[row * D + d] - r);
+          for (int d = 0; d < 32; ++d) {
+            const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + c0 + d];
+            acc[d] += v[d] * __expf(bmat[row * D + c0 + d] - r);
           }
         }
       }
       if (lane < 16) {
-        __nv_bfloat16* dst = dq + (long long)(row0 + row) * dq_ld + dqcol + h * D;
+        __nv_bfloat16* dst = dq + (long long)(row0 + row) * dq_ld + dqcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < 4; ++ch) {
           float o[8], q[8];
-          unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, ch)), q);
+          unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, half * 4 + ch)), q);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             o[i] = acc[ch * 8 + i];
-            dmat[row * D + ch * 8 + i] = q[i] * o[i];
+            dmat[row * D + c0 + ch * 8 + i] = q[i] * o[i];
           }
           *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
         }
@@ -632,26 +651,27 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_bwd_main_kernel(
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[64], acc[64];
-      load_acc_row(tmem, 192, warp, v);
+      float v[32], acc[32];
+      const int c0 = 32 * half;
+      load_acc_half(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < 64; ++d) acc[d] = v[d] * __expf(bmat[63 * D + d] - bmat[row * D + d]);
-      load_acc_row(tmem, 256 + 64 * warp, warp, v);  // rows of sub-chunk j = warp live in accumulator j
+      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bmat[63 * D + c0 + d] - bmat[row * D + c0 + d]);
+      load_acc_half(tmem, 256 + 64 * quarter + c0, quarter, v);  // rows of sub-chunk j = quarter live in accumulator j
 #pragma unroll
-      for (int d = 0; d < 64; ++d) {
-        const float r = warp == 0 ? 0.f : bmat[(16 * warp - 1) * D + d];
-        acc[d] += v[d] * __expf(r - bmat[row * D + d]);
+      for (int d = 0; d < 32; ++d) {
+        const float r = quarter == 0 ? 0.f : bmat[(16 * quarter - 1) * D + c0 + d];
+        acc[d] += v[d] * __expf(r - bmat[row * D + c0 + d]);
       }
       if (lane < 16) {
-        __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D;
+        __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < 4; ++ch) {
           float o[8], k[8];
-          unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, ch)), k);
+          unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, half * 4 + ch)), k);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             o[i] = acc[ch * 8 + i];
-            dmat[row * D + ch * 8 + i] -= k[i] * o[i];
+            dmat[row * D + c0 + ch * 8 + i] -= k[i] * o[i];
           }
           *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
         }
@@ -829,7 +849,7 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
     cfg = true;
   }
   const int grid = d.B * d.H * (d.T / C);
-  gla_bwd_main_kernel<<<grid, GLA_THREADS, BWD_SMEM, s>>>(
+  gla_bwd_main_kernel<<<grid, 256, BWD_SMEM, s>>>(
       tq, tk, tv, tg, tdo, ts, tds, Q.col0, K.col0, V.col0, G.col0, dO.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dQ.ptr)), dQ.ld, dQ.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dK.ptr)), dK.ld, dK.col0,

@@ -329,7 +329,14 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         self.compute_clip()
         self._step_adamw()
         self._step_muon()
-        self._step_steer()
+        # the subspace projections are fp32 batched products; TF32 tensor cores keep ~1e-3 relative accuracy,
+        # the same order as the bf16 bases the reference uses on CUDA
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            self._step_steer()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
         return loss
 
     def step_parameters(self, params: Iterable[torch.nn.Parameter], is_global_step_end: bool = True):

@@ -40,6 +40,15 @@ def batched_qr(A: torch.Tensor, cond_threshold: float = 1e4, eps_shift: float = 
       degenerate column (norm < 1e-12), Cholesky failure, diag(L) ratio above ``cond_threshold``,
       ||Q^T Q - I||_F above ``orth_tol``.
     """
+    prev_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False  # the Gram / orthogonality checks need full fp32 products
+    try:
+        return _batched_qr_impl(A, cond_threshold, eps_shift, orth_tol, telemetry, return_info)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev_tf32
+
+
+def _batched_qr_impl(A, cond_threshold, eps_shift, orth_tol, telemetry, return_info):
     squeeze = A.dim() == 2
     X = (A.unsqueeze(0) if squeeze else A).float()
     K, d, r = X.shape

@@ -1,0 +1,324 @@
+"""Layer streaming: train or run models whose layers do not all fit on the GPU.
+
+Parity: ``LayerStreamingEngine`` / ``StreamingConfig`` / ``enable_layer_streaming``
+(``triune/runtime/streaming.py:153-1308``) and ``ParameterStager`` (``triune/runtime/staging.py:19-621``).
+Layers live in pinned host memory; the root (embedding, heads, norms, router) and ``resident_gpu_layers`` stay on
+the GPU. A streamed layer is staged host->device with ``cudaMemcpyAsync`` from pinned memory on a SIDE stream
+while the previous layer computes (prefetch of layer i+1 going forward, i-1 going backward), runs under
+activation checkpointing (only its input is kept), and is evicted afterwards. Gradients leave device->host on a
+third stream with their squared norm captured on the GPU; the optimizer then streams layer by layer: stage
+weights + gradients + optimizer state, update, write back.
+
+Design differences from the reference: instead of monkey-patching ``_forward_block`` and autograd hooks, each
+streamed layer is wrapped in ONE ``torch.autograd.Function`` that owns stage / compute / evict for both
+directions, so exception cleanup is a ``finally`` in one place; staging is per-layer flat buffers (one copy per
+layer per direction, not one per tensor).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+
+@dataclass
+class StreamingConfig:
+    enabled: bool = True
+    chunk_size: int = 1
+    pin_memory: Optional[bool] = None  # None: pin when CUDA is present
+    async_prefetch: bool = True
+    fp8_weights: bool = False
+    grad_clip: float = 1.0
+    instant_optimizer: bool = True
+    resident_gpu_layers: int = 0
+    activation_checkpointing: bool = True
+    forward_snapshots: bool = True
+
+
+class LayerStore:
+    """Flat host storage of one layer: parameters (model dtype), fp32 gradient, and views for each tensor."""
+
+    def __init__(self, layer: nn.Module, pin: bool):
+        self.layer = layer
+        self.params = [p for p in layer.parameters()]
+        self.numel = sum(p.numel() for p in self.params)
+        dtype = self.params[0].dtype if self.params else torch.float32
+        self.host = torch.empty(self.numel, dtype=dtype)
+        self.host_grad = torch.zeros(self.numel, dtype=torch.float32)
+        if pin:
+            self.host, self.host_grad = self.host.pin_memory(), self.host_grad.pin_memory()
+        off = 0
+        self.slices = []
+        for p in self.params:
+            n = p.numel()
+            self.host[off : off + n].copy_(p.data.reshape(-1))
+            p.data = self.host[off : off + n].view(p.shape)  # the host copy is the master
+            self.slices.append((off, n, p.shape))
+            off += n
+        self.device_buf: Optional[torch.Tensor] = None
+        self.ready: Optional[torch.cuda.Event] = None
+        self.grad_sumsq = None
+
+    def bind(self, buf: torch.Tensor):
+        for p, (off, n, shape) in zip(self.params, self.slices):
+            p.data = buf[off : off + n].view(shape)
+
+    def bind_host(self):
+        self.bind(self.host)
+
+
+class LayerStreamingEngine:
+    def __init__(self, model: nn.Module, device, config: Optional[StreamingConfig] = None, layers_attr: str = "layers"):
+        self.model = model
+        self.device = torch.device(device)
+        self.cfg = config or StreamingConfig()
+        self.cuda = self.device.type == "cuda"
+        self.layers: List[nn.Module] = list(getattr(model, layers_attr))
+        pin = self.cuda if self.cfg.pin_memory is None else (self.cfg.pin_memory and self.cuda)
+        self.resident = set(range(min(self.cfg.resident_gpu_layers, len(self.layers))))
+        self.stores: Dict[int, LayerStore] = {}
+        self.h2d_stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.d2h_stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.telemetry = {"h2d_bytes": 0, "d2h_bytes": 0, "h2d_copies": 0, "d2h_copies": 0, "peak_staged_layers": 0}
+        self._staged: Dict[int, int] = {}
+        self._attached = False
+        self._orig_forward: Dict[int, Any] = {}
+        self._pin = pin
+        self.opt_state: Dict[int, Dict[str, torch.Tensor]] = {}
+        self.step_count = 0
+
+    # ------------------------------------------------------------------ attach / detach
+    def attach(self):
+        if self._attached:
+            return self
+        layer_params = set()
+        for i, layer in enumerate(self.layers):
+            if i in self.resident:
+                layer.to(self.device)
+                continue
+            layer.to("cpu")
+            self.stores[i] = LayerStore(layer, self._pin)
+            layer_params.update(id(p) for p in layer.parameters())
+            self._wrap(i, layer)
+        # root: everything that is not a streamed layer
+        for p in self.model.parameters():
+            if id(p) not in layer_params and p.device != self.device:
+                p.data = p.data.to(self.device)
+        for b in self.model.buffers():
+            b.data = b.data.to(self.device)
+        self._attached = True
+        return self
+
+    def detach(self):
+        for i, layer in enumerate(self.layers):
+            if i in self._orig_forward:
+                layer.forward = self._orig_forward.pop(i)
+            if i in self.stores:
+                self.stores[i].bind_host()
+        self._attached = False
+
+    def _wrap(self, i: int, layer: nn.Module):
+        orig = layer.forward
+        self._orig_forward[i] = orig
+        engine = self
+
+        def forward(x, *args, **kwargs):
+            if torch.is_grad_enabled() and engine.cfg.activation_checkpointing and x.requires_grad:
+                out = _StreamedLayerFn.apply(engine, i, orig, args, kwargs, x)
+                return engine._unflatten(i, out)
+            engine.stage(i, prefetch=i + 1)
+            try:
+                return orig(x, *args, **kwargs)
+            finally:
+                engine.release(i)
+
+        layer.forward = forward
+
+    # outputs of a block are (x, logits_or_None, cache_or_None); only tensors pass through autograd
+    def _flatten(self, i, out):
+        if torch.is_tensor(out):
+            self._out_struct = None
+            return out
+        tensors = tuple(o for o in out if torch.is_tensor(o))
+        self._out_struct = [torch.is_tensor(o) for o in out]
+        self._out_consts = [None if torch.is_tensor(o) else o for o in out]
+        return tensors if len(tensors) > 1 else tensors[0]
+
+    def _unflatten(self, i, flat):
+        if getattr(self, "_out_struct", None) is None:
+            return flat
+        it = iter(flat if isinstance(flat, tuple) else (flat,))
+        return tuple(next(it) if is_t else c for is_t, c in zip(self._out_struct, self._out_consts))
+
+    # ------------------------------------------------------------------ staging
+    def _start_copy(self, i: int):
+        st = self.stores[i]
+        if st.device_buf is not None:
+            return
+        if not self.cuda:
+            st.device_buf = st.host
+            return
+        with torch.cuda.stream(self.h2d_stream):
+            st.device_buf = st.host.to(self.device, non_blocking=True)
+            st.ready = torch.cuda.Event()
+            st.ready.record(self.h2d_stream)
+        self.telemetry["h2d_bytes"] += st.host.numel() * st.host.element_size()
+        self.telemetry["h2d_copies"] += 1
+
+    def stage(self, i: int, prefetch: Optional[int] = None):
+        if i not in self.stores:
+            return
+        self._start_copy(i)
+        st = self.stores[i]
+        if self.cuda and st.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(st.ready)
+        st.bind(st.device_buf)
+        self._staged[i] = self._staged.get(i, 0) + 1
+        self.telemetry["peak_staged_layers"] = max(self.telemetry["peak_staged_layers"],
+                                                   sum(1 for s in self.stores.values() if s.device_buf is not None))
+        if self.cfg.async_prefetch and prefetch is not None and prefetch in self.stores:
+            self._start_copy(prefetch)
+
+    def release(self, i: int):
+        if i not in self.stores:
+            return
+        st = self.stores[i]
+        self._staged[i] = max(0, self._staged.get(i, 0) - 1)
+        if self._staged[i] == 0:
+            if self.cuda and st.device_buf is not None:
+                st.device_buf.record_stream(torch.cuda.current_stream(self.device))
+            st.bind_host()
+            st.device_buf = None
+            st.ready = None
+
+    def collect_grads(self, i: int):
+        """Move the gradients of layer i (on the device after its backward) into the pinned host buffer."""
+        st = self.stores[i]
+        flat = torch.zeros(st.numel, dtype=torch.float32, device=self.device)
+        for p, (off, n, _) in zip(st.params, st.slices):
+            if p.grad is not None:
+                flat[off : off + n] = p.grad.reshape(-1).float()
+                p.grad = None
+        sumsq = flat.double().pow(2).sum()
+        st.grad_sumsq = sumsq if st.grad_sumsq is None else st.grad_sumsq + sumsq
+        if self.cuda:
+            self.d2h_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.d2h_stream):
+                acc = flat if self._first_micro(i) else flat + st.host_grad.to(self.device, non_blocking=True)
+                st.host_grad.copy_(acc, non_blocking=True)
+                flat.record_stream(self.d2h_stream)
+        else:
+            st.host_grad.add_(flat) if not self._first_micro(i) else st.host_grad.copy_(flat)
+        st._has_grad = True
+        self.telemetry["d2h_bytes"] += st.numel * 4
+        self.telemetry["d2h_copies"] += 1
+
+    def _first_micro(self, i: int) -> bool:
+        return not getattr(self.stores[i], "_has_grad", False)
+
+    # ------------------------------------------------------------------ optimizer
+    @torch.no_grad()
+    def step_streaming_optimizer(self, optimizer=None, grad_clip: Optional[float] = None, lr: float = 1e-4,
+                                 betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.05):
+        """Global-norm clip (fp64) then: root/resident parameters through ``optimizer`` (if given), streamed layers
+        through a per-layer fused AdamW whose fp32 state lives in pinned host memory."""
+        clip = self.cfg.grad_clip if grad_clip is None else grad_clip
+        if self.cuda:
+            self.d2h_stream.synchronize()
+        total = torch.zeros((), dtype=torch.float64, device=self.device)
+        streamed = set()
+        for st in self.stores.values():
+            streamed.update(id(p) for p in st.params)
+            if st.grad_sumsq is not None:
+                total += st.grad_sumsq.to(self.device)
+        root = [p for p in self.model.parameters() if id(p) not in streamed and p.grad is not None]
+        for p in root:
+            total += p.grad.double().pow(2).sum()
+        norm = total.sqrt()
+        coef = torch.clamp(clip / (norm + 1e-6), max=1.0).float() if clip and clip > 0 else torch.ones((), device=self.device)
+        for p in root:
+            p.grad.mul_(coef.to(p.grad.dtype))
+        if optimizer is not None:
+            optimizer.step()
+            optimizer.zero_grad(set_to_none=True)
+        self.step_count += 1
+        t = self.step_count
+        b1, b2 = betas
+        for i, st in self.stores.items():
+            if not getattr(st, "_has_grad", False):
+                continue
+            if i not in self.opt_state:
+                mk = lambda: (torch.zeros(st.numel, dtype=torch.float32).pin_memory() if self._pin
+                              else torch.zeros(st.numel, dtype=torch.float32))
+                self.opt_state[i] = {"m": mk(), "v": mk(), "master": mk()}
+                self.opt_state[i]["master"].copy_(st.host.float())
+            os_ = self.opt_state[i]
+            dev = self.device
+            g = st.host_grad.to(dev, non_blocking=True) * coef
+            m, v, w = (os_[k].to(dev, non_blocking=True) for k in ("m", "v", "master"))
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            w.mul_(1 - lr * weight_decay).addcdiv_(m / (1 - b1**t), (v / (1 - b2**t)).sqrt() + eps, value=-lr)
+            os_["m"].copy_(m, non_blocking=True)
+            os_["v"].copy_(v, non_blocking=True)
+            os_["master"].copy_(w, non_blocking=True)
+            st.host.copy_(w.to(st.host.dtype), non_blocking=True)
+            st.host_grad.zero_()
+            st.grad_sumsq = None
+            st._has_grad = False
+            self.telemetry["h2d_bytes"] += st.numel * 16
+            self.telemetry["d2h_bytes"] += st.numel * 14
+        if self.cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        return float(norm)
+
+    def get_telemetry(self) -> Dict[str, int]:
+        return dict(self.telemetry)
+
+
+class _StreamedLayerFn(torch.autograd.Function):
+    """Checkpointed execution of one streamed layer: forward keeps only the input; backward re-stages the weights,
+    recomputes, back-propagates and ships the weight gradients to the host."""
+
+    @staticmethod
+    def forward(ctx, engine: LayerStreamingEngine, i: int, fn, args, kwargs, x):
+        ctx.engine, ctx.i, ctx.fn, ctx.args, ctx.kwargs = engine, i, fn, args, kwargs
+        ctx.save_for_backward(x)
+        engine.stage(i, prefetch=i + 1)
+        try:
+            with torch.no_grad():
+                out = fn(x, *args, **kwargs)
+        finally:
+            engine.release(i)
+        return engine._flatten(i, out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        engine, i = ctx.engine, ctx.i
+        (x,) = ctx.saved_tensors
+        engine.stage(i, prefetch=i - 1)
+        try:
+            xd = x.detach().requires_grad_(True)
+            with torch.enable_grad():
+                kw = dict(ctx.kwargs)
+                if "update_stats" in kw:
+                    kw["update_stats"] = False  # statistics were updated by the first pass
+                out = ctx.fn(xd, *ctx.args, **kw)
+            outs = [o for o in (out if isinstance(out, tuple) else (out,)) if torch.is_tensor(o)]
+            pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and o.requires_grad]
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+            engine.collect_grads(i)
+        finally:
+            engine.release(i)
+        return None, None, None, None, None, xd.grad
+
+
+def enable_layer_streaming(model: nn.Module, device, **kw) -> LayerStreamingEngine:
+    cfg = StreamingConfig(**{k: v for k, v in kw.items() if k in StreamingConfig.__dataclass_fields__})
+    eng = LayerStreamingEngine(model, device, cfg).attach()
+    model._streaming_engine = eng
+    return eng
