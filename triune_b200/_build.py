@@ -25,6 +25,7 @@ CSRC = PKG / "csrc"
 OBJ = CSRC / "_obj"
 EXT_SO = PKG / "_C.so"
 CORE_SO = PKG / "libtriune_core.so"
+NOALLOC_SO = PKG / "libtriune_noalloc.so"
 
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
@@ -75,7 +76,7 @@ def build_extension(force: bool = False, verbose: bool = False, ptxas_info: bool
     inc, defs, torch_lib = _torch_flags()
     OBJ.mkdir(parents=True, exist_ok=True)
     hdr_m = _newest_header_mtime()
-    sources = sorted(p for p in CSRC.rglob("*.cu") if "engine" not in p.parts) + sorted(
+    sources = sorted(p for p in CSRC.rglob("*.cu") if "engine" not in p.parts and p.name != "gla_noalloc.cu") + sorted(
         p for p in CSRC.rglob("*.cpp") if "engine" not in p.parts
     )
     jobs = []
@@ -144,9 +145,27 @@ def build_core(force: bool = False, verbose: bool = False) -> Path:
     return CORE_SO
 
 
+def build_noalloc(force: bool = False, verbose: bool = False) -> Path:
+    """Allocation-free C entry point over the GLA kernels (no torch dependency; loadable with ctypes)."""
+    cuda = _cuda_home()
+    nvcc = str(Path(cuda, "bin", "nvcc"))
+    srcs = [CSRC / "gla" / "gla_noalloc.cu", CSRC / "gla" / "gla_kernels.cu"]
+    deps = srcs + [CSRC / "gla" / "gla_noalloc.h", CSRC / "gla" / "gla.cuh", CSRC / "common" / "ptx.cuh",
+                   CSRC / "common" / "tma_desc.h"]
+    newest = max(p.stat().st_mtime for p in deps)
+    if not force and NOALLOC_SO.exists() and NOALLOC_SO.stat().st_mtime >= newest:
+        return NOALLOC_SO
+    cmd = ([nvcc, "-shared", "-o", str(NOALLOC_SO)] + [str(s) for s in srcs] + NVCC_ARCH
+           + ["-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "--use_fast_math", "-Xcompiler", "-fPIC",
+              f"-I{CSRC}", "-lcudart"])
+    _run(cmd, verbose)
+    return NOALLOC_SO
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_extension(force=force, verbose=verbose)
     build_core(force=force, verbose=verbose)
+    build_noalloc(force=force, verbose=verbose)
 
 
 if __name__ == "__main__":
