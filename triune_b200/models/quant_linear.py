@@ -1,0 +1,180 @@
+"""Quantised linear layers and model converters for the serving path.
+
+Parity: ``FP8Linear`` / ``convert_to_fp8`` (``triune/model/fp8.py:126-195``), ``FP4Linear`` /
+``convert_to_nvfp4`` (``triune/model/fp4.py:25-114``) and ``NVFP4Linear`` (``triune/kernels/fast_nvfp4.py:543-696``).
+
+Formats
+  * FP8: E4M3 weights with one fp32 scale per 128x128 block; activations are quantised per 1x128 row segment at
+    run time (the reference used a single per-tensor scale).
+  * NVFP4: packed E2M1 (two codes per byte) with one E4M3 scale per 16 elements and one fp32 per-tensor scale;
+    optional 16-point Hadamard rotation of the weight rows folded into the activation path. ``from_reference``
+    reads the reference's legacy layout (bf16 block scales, tensor scale 1).
+Sensitive layers (router, exit heads, final head, embeddings, small gates) are left in bf16 by the converters.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import reference as ref
+
+PROTECTED = ("router", "exit_head", "final_head", "lm_head", "embed")
+
+
+class FP8Linear(nn.Module):
+    """Linear with a bf16/fp32 master weight; the forward runs the block-scaled E4M3 GEMM."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, block: int = 128):
+        super().__init__()
+        self.in_features, self.out_features, self.block = in_features, out_features, block
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+        self._q = None  # (version, wq, ws)
+
+    @classmethod
+    def from_linear(cls, lin: nn.Linear, block: int = 128) -> "FP8Linear":
+        m = cls(lin.in_features, lin.out_features, lin.bias is not None, block)
+        m.weight = nn.Parameter(lin.weight.detach().clone(), requires_grad=lin.weight.requires_grad)
+        if lin.bias is not None:
+            m.bias = nn.Parameter(lin.bias.detach().clone(), requires_grad=lin.bias.requires_grad)
+        return m
+
+    def quantized(self):
+        v = self.weight._version
+        if self._q is None or self._q[0] != v or self._q[1].device != self.weight.device:
+            wq, ws = ref.fp8_block_quantize_weight(self.weight.detach(), self.block)
+            self._q = (v, wq, ws)
+        return self._q[1], self._q[2]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.training and torch.is_grad_enabled() and self.weight.requires_grad:
+            # straight-through: quantisation error enters the forward, gradients flow to the master weight
+            wq, ws = self.quantized()
+            w_dq = (wq.float() * ws.repeat_interleave(self.block, 0).repeat_interleave(self.block, 1)
+                    [: self.out_features, : self.in_features]).to(self.weight.dtype)
+            w = self.weight + (w_dq - self.weight).detach()
+            return F.linear(x, w, self.bias)
+        wq, ws = self.quantized()
+        x2 = x.reshape(-1, self.in_features)
+        y = ops.fp8_linear(x2, wq, ws, self.block, out_dtype=x.dtype)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y.view(*x.shape[:-1], self.out_features)
+
+
+class NVFP4Linear(nn.Module):
+    """Inference linear over packed NVFP4 weights (buffers only; ~4.5 bits per weight)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, hadamard: bool = False,
+                 scale_dtype=torch.float8_e4m3fn):
+        super().__init__()
+        assert in_features % 16 == 0, "NVFP4 needs in_features to be a multiple of 16"
+        self.in_features, self.out_features, self.hadamard = in_features, out_features, hadamard
+        self.register_buffer("packed_weight", torch.zeros(out_features, in_features // 2, dtype=torch.uint8))
+        self.register_buffer("block_scales", torch.zeros(out_features, in_features // 16, dtype=scale_dtype))
+        self.register_buffer("tensor_scale", torch.ones((), dtype=torch.float32))
+        self.bias = nn.Parameter(torch.zeros(out_features), requires_grad=False) if bias else None
+        self._dq = None
+
+    @classmethod
+    def empty_skeleton(cls, in_features, out_features, bias=False, hadamard=False, device=None):
+        m = cls(in_features, out_features, bias, hadamard)
+        return m.to(device) if device is not None else m
+
+    @classmethod
+    def from_linear(cls, lin: nn.Linear, hadamard: bool = False) -> "NVFP4Linear":
+        m = cls(lin.in_features, lin.out_features, lin.bias is not None, hadamard)
+        m.load_weight(lin.weight.detach())
+        if lin.bias is not None:
+            m.bias.data.copy_(lin.bias.detach())
+        return m.to(lin.weight.device)
+
+    @classmethod
+    def from_reference(cls, packed: torch.Tensor, scales_bf16: torch.Tensor, hadamard: bool = False) -> "NVFP4Linear":
+        """Adopt the reference's layout (E2M1 + bf16 scale per 16 elements)."""
+        out_f, half = packed.shape
+        m = cls(half * 2, out_f, False, hadamard, scale_dtype=torch.bfloat16)
+        m.packed_weight.copy_(packed)
+        m.block_scales.copy_(scales_bf16)
+        return m
+
+    @torch.no_grad()
+    def load_weight(self, w: torch.Tensor):
+        wf = w.float()
+        if self.hadamard:
+            wf = ref.fwht16(wf)  # rotate each group of 16 input features; the activation gets the same rotation
+        p, s, t = ref.nvfp4_quantize(wf, self.block_scales.dtype)
+        self.packed_weight = p.to(self.packed_weight.device)
+        self.block_scales = s.to(self.block_scales.device)
+        self.tensor_scale = t.to(self.tensor_scale.device)
+        self._dq = None
+
+    def dequantized(self, dtype=torch.bfloat16) -> torch.Tensor:
+        return ref.nvfp4_dequantize(self.packed_weight, self.block_scales, self.tensor_scale, dtype)
+
+    def bits_per_weight(self) -> float:
+        n = self.out_features * self.in_features
+        return 8.0 * (self.packed_weight.numel() + self.block_scales.numel() * self.block_scales.element_size()) / n
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, self.in_features)
+        if self.hadamard:
+            x2 = ref.fwht16(x2)
+        y = ops.nvfp4_linear(x2, self.packed_weight, self.block_scales, self.tensor_scale, out_dtype=x.dtype)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y.view(*x.shape[:-1], self.out_features)
+
+
+class FP4Linear(nn.Module):
+    """Training-time 4-bit linear: quantise-dequantise forward with a straight-through estimator, master-weight
+    backward (the reference used Transformer Engine when present, else this STE form)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x):
+        w = self.weight
+        if w.shape[1] % 16 == 0:
+            p, s, t = ref.nvfp4_quantize(w.detach().float())
+            w = w + (ref.nvfp4_dequantize(p, s, t, w.dtype) - w).detach()
+        return F.linear(x, w, self.bias)
+
+
+def _protected(name: str, mod: nn.Linear, extra: Iterable[str]) -> bool:
+    low = name.lower()
+    if any(k in low for k in tuple(PROTECTED) + tuple(extra)):
+        return True
+    return "gate" in low and mod.out_features * mod.in_features < 65536
+
+
+def _convert(model: nn.Module, make, protect: Iterable[str], min_features: int):
+    n = 0
+    for name, mod in list(model.named_modules()):
+        for child_name, child in list(mod.named_children()):
+            full = f"{name}.{child_name}" if name else child_name
+            if type(child) is nn.Linear and not _protected(full, child, protect) and child.in_features % 16 == 0 \
+                    and min(child.in_features, child.out_features) >= min_features:
+                setattr(mod, child_name, make(child))
+                n += 1
+    return n
+
+
+def convert_to_fp8(model: nn.Module, protect: Iterable[str] = (), min_features: int = 16) -> int:
+    """Replace eligible ``nn.Linear`` modules by :class:`FP8Linear`; returns the number converted."""
+    return _convert(model, FP8Linear.from_linear, protect, min_features)
+
+
+def convert_to_nvfp4(model: nn.Module, hadamard: bool = False, protect: Iterable[str] = (), min_features: int = 16) -> int:
+    """Replace eligible ``nn.Linear`` modules by packed :class:`NVFP4Linear`; returns the number converted."""
+    return _convert(model, lambda l: NVFP4Linear.from_linear(l, hadamard), protect, min_features)

@@ -684,3 +684,30 @@ def tier_colour_render(act, tiers):
 
 fwht16 = ref.fwht16
 newton_schulz_reference = ref.newton_schulz
+
+
+# ----------------------------------------------------------------------------
+# Quantised linears (serving path)
+# ----------------------------------------------------------------------------
+def fp8_linear(x2, wq, ws, block: int = 128, out_dtype=torch.bfloat16):
+    """y = x @ dequant(wq, ws)^T with activations quantised per 1x128 row segment (block-scaled E4M3)."""
+    from . import quant_cuda
+
+    if quant_cuda.fp8_supported(x2, wq):
+        return quant_cuda.fp8_block_linear(x2, wq, ws, block, out_dtype)
+    xq, xs = ref.fp8_block_quantize_act(x2, block)
+    return ref.fp8_block_gemm(xq, xs, wq, ws, block, out_dtype)
+
+
+def nvfp4_linear(x2, packed, scales, tscale, out_dtype=torch.bfloat16):
+    """y = x @ dequant(packed, scales, tscale)^T (W4A16: weights decoded on the fly, bf16 tensor-core GEMM)."""
+    from . import quant_cuda
+
+    if quant_cuda.nvfp4_supported(x2, packed):
+        return quant_cuda.nvfp4_linear(x2, packed, scales, tscale, out_dtype)
+    w = ref.nvfp4_dequantize(packed, scales, tscale, torch.float32)
+    return (x2.float() @ w.t()).to(out_dtype)
+
+
+nvfp4_quantize = ref.nvfp4_quantize
+nvfp4_dequantize = ref.nvfp4_dequantize
