@@ -1,0 +1,91 @@
+"""GPU numerics of the quantised serving kernels against the PyTorch fp32 oracles."""
+
+import pytest
+import torch
+
+from triune_b200 import ops
+from triune_b200.ops import quant_cuda, reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _need_cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+
+
+def test_fp8_act_quantiser_matches_oracle():
+    torch.manual_seed(0)
+    x = (torch.randn(300, 384, device="cuda") * 3).bfloat16()
+    q, s = quant_cuda.fp8_quantize_act(x)
+    q_ref, s_ref = ref.fp8_block_quantize_act(x)
+    assert torch.allclose(s, s_ref, rtol=1e-6, atol=0)
+    deq, deq_ref = q.float() * s.repeat_interleave(128, 1), q_ref.float() * s_ref.repeat_interleave(128, 1)
+    # one E4M3 ulp at most where the division rounds differently
+    assert (deq - deq_ref).abs().max() <= 0.07 * deq_ref.abs().max()
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 384), (1000, 1536, 384), (4096, 384, 1536), (130, 200, 272)])
+def test_fp8_block_gemm_matches_dequant_oracle(M, N, K):
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda") * 0.05
+    wq, ws = ref.fp8_block_quantize_weight(w)
+    xq, xs = quant_cuda.fp8_quantize_act(x)
+    y = quant_cuda.fp8_block_gemm(xq, xs, wq, ws).float()
+    want = ref.fp8_block_gemm(xq, xs, wq, ws, 128, torch.float32)
+    err = (y - want).abs().max() / want.abs().max()
+    assert err < 1e-2, err  # bf16 output rounding only: the operands are identical
+    full = x.float() @ w.t()
+    assert torch.nn.functional.cosine_similarity(y.flatten(), full.flatten(), dim=0) > 0.995
+
+
+@pytest.mark.parametrize("hadamard", [False, True])
+def test_nvfp4_quantise_and_dequant(hadamard):
+    torch.manual_seed(2)
+    w = torch.randn(192, 256, device="cuda") * 0.1
+    p, s, t = quant_cuda.nvfp4_quantize(w, hadamard)
+    wr = ref.fwht16(w) if hadamard else w
+    p_ref, s_ref, t_ref = ref.nvfp4_quantize(wr)
+    assert torch.allclose(t, t_ref, rtol=1e-6)
+    assert (s.view(torch.uint8) != s_ref.view(torch.uint8)).float().mean() < 0.01
+    assert (p != p_ref).float().mean() < 0.02
+    deq = quant_cuda.nvfp4_dequant(p, s, t).float()
+    assert torch.equal(deq, ref.nvfp4_dequantize(p, s, t, torch.bfloat16).float())
+    assert torch.nn.functional.cosine_similarity(deq.flatten(), wr.flatten(), dim=0) > 0.98
+    # bf16 block scales (the reference's legacy layout) decode through the same kernel
+    p2, s2, t2 = ref.nvfp4_quantize(wr, torch.bfloat16)
+    assert torch.equal(quant_cuda.nvfp4_dequant(p2, s2, t2).float(), ref.nvfp4_dequantize(p2, s2, t2, torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 64])
+def test_nvfp4_linear_paths(M):
+    torch.manual_seed(3)
+    w = torch.randn(512, 384, device="cuda") * 0.05
+    x = torch.randn(M, 384, device="cuda").bfloat16()
+    p, s, t = quant_cuda.nvfp4_quantize(w)
+    y = ops.nvfp4_linear(x, p, s, t).float()
+    want = x.float() @ ref.nvfp4_dequantize(p, s, t, torch.float32).t()
+    assert (y - want).abs().max() <= 2e-2 * want.abs().max()
+
+
+def test_fwht16_kernel():
+    x = torch.randn(64, 128, device="cuda").bfloat16()
+    y = quant_cuda.fwht16(x)
+    assert torch.allclose(y.float(), ref.fwht16(x.float()), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(quant_cuda.fwht16(y).float(), x.float(), atol=3e-2, rtol=3e-2)  # involution
+
+
+def test_quantised_modules_on_gpu():
+    from triune_b200.models.quant_linear import FP8Linear, NVFP4Linear
+
+    torch.manual_seed(4)
+    lin = torch.nn.Linear(384, 512, bias=True).cuda().bfloat16()
+    x = torch.randn(2, 40, 384, device="cuda").bfloat16()
+    want = lin(x).float()
+    for m in (FP8Linear.from_linear(lin).eval(), NVFP4Linear.from_linear(lin), NVFP4Linear.from_linear(lin, hadamard=True)):
+        with torch.no_grad():
+            y = m(x).float()
+        assert torch.nn.functional.cosine_similarity(y.flatten(), want.flatten(), dim=0) > 0.98, type(m).__name__

@@ -2,6 +2,7 @@
 
 import json
 import os
+import re
 import subprocess
 import sys
 
@@ -20,7 +21,10 @@ def _launch(nproc, env_extra):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
            "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "mp_fused_dp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
-    res = [json.loads(l[len("RESULT "):]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    # ranks share one pipe, so two RESULT records can land on one line: decode every occurrence separately
+    dec, res = json.JSONDecoder(), []
+    for m in re.finditer(r"RESULT (?=\{)", p.stdout):
+        res.append(dec.raw_decode(p.stdout, m.end())[0])
     assert p.returncode == 0 and len(res) == nproc, p.stdout[-3000:] + p.stderr[-3000:]
     return res
 

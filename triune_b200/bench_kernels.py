@@ -132,7 +132,36 @@ def case_ce(a):
     report(f"cross_entropy fwd+grad {a.m}x{a.n}", ms, nbytes=6.0 * a.m * a.n)
 
 
-CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
+def case_fp8(a):
+    from .ops import quant_cuda, reference as ref
+
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wq, ws = ref.fp8_block_quantize_weight(torch.randn(N, K, device="cuda") * 0.05)
+    xq, xs = quant_cuda.fp8_quantize_act(x)
+    ms = timeit(lambda: quant_cuda.fp8_block_gemm(xq, xs, wq, ws), a.iters, a.warmup)
+    report(f"fp8_block_gemm {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=1.0 * (M * K + N * K) + 2.0 * M * N)
+    ms = timeit(lambda: quant_cuda.fp8_quantize_act(x), a.iters, a.warmup)
+    report(f"fp8_quantize_act {M}x{K}", ms, nbytes=3.0 * M * K)
+
+
+def case_nvfp4(a):
+    from .ops import quant_cuda
+
+    N, K = a.n, a.k
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    p, s, t = quant_cuda.nvfp4_quantize(w)
+    x = torch.randn(1, K, device="cuda", dtype=torch.bfloat16)
+    e = quant_cuda._ext.ext()
+    ms = timeit(lambda: e.nvfp4_gemv(x, p, s, t), a.iters, a.warmup)
+    report(f"nvfp4_gemv M=1 {N}x{K}", ms, nbytes=N * K * 0.5625)
+    ms = timeit(lambda: quant_cuda.nvfp4_dequant(p, s, t), a.iters, a.warmup)
+    report(f"nvfp4_dequant {N}x{K}", ms, nbytes=N * K * 2.5625)
+    ms = timeit(lambda: quant_cuda.nvfp4_quantize(w), a.iters, a.warmup)
+    report(f"nvfp4_quantize {N}x{K}", ms, nbytes=N * K * 4.5625)
+
+
+CASES = {"fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():

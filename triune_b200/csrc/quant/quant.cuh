@@ -1,8 +1,26 @@
-// Launchers of the quantisation kernels (NVFP4 / FP8 block-scaled quantise, dequantise, GEMM).
+// Launchers of the quantisation kernels (NVFP4 / FP8 block-scaled quantise, dequantise, GEMM, GEMV).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace tb {
+
+// x bf16 [M,K] -> q E4M3 [M,K], scales fp32 [M, ceil(K/128)] (x ~= q * scale).
+void launch_fp8_quantize_act(const __nv_bfloat16* x, uint8_t* q, float* scales, int M, int K, cudaStream_t s);
+
+// C[M,N] bf16 = (xq * xs) @ (wq * ws)^T with xs per 1x128 segment and ws per 128x128 block. `status` (optional)
+// receives a non-zero code if a bounded wait inside the kernel expired.
+void launch_fp8_block_gemm(const uint8_t* xq, const float* xs, const uint8_t* wq, const float* ws, __nv_bfloat16* C,
+                           int M, int N, int K, int* status, cudaStream_t s);
+
+// NVFP4: two E2M1 codes per byte (low nibble first), one E4M3 scale per 16 elements, one fp32 tensor scale.
+void launch_nvfp4_quantize(const void* w, bool w_is_bf16, long long rows, long long K, bool hadamard, uint8_t* packed,
+                           uint8_t* scales_e4m3, float* tscale, unsigned int* amax_scratch, cudaStream_t s);
+void launch_nvfp4_dequant(const uint8_t* packed, const void* scales, bool scale_bf16, const float* tscale, long long rows,
+                          long long K, __nv_bfloat16* out, cudaStream_t s);
+void launch_nvfp4_gemv(const __nv_bfloat16* x, const uint8_t* packed, const void* scales, bool scale_bf16,
+                       const float* tscale, __nv_bfloat16* y, int M, int N, int K, cudaStream_t s);
+void launch_fwht16(const __nv_bfloat16* x, __nv_bfloat16* out, long long n, cudaStream_t s);
+
 }  // namespace tb

@@ -5,4 +5,97 @@
 
 #include "quant.cuh"
 
-void register_quant(pybind11::module& m) { (void)m; }
+namespace {
+
+void need(bool c, const char* msg) { TORCH_CHECK(c, msg); }
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
+const __nv_bfloat16* bf(const at::Tensor& t) { return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr()); }
+__nv_bfloat16* bfm(at::Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+
+std::vector<at::Tensor> fp8_quantize_act(const at::Tensor& x) {
+  need(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "fp8_quantize_act: bf16 [M,K] CUDA");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t M = x.size(0), K = x.size(1);
+  auto q = at::empty({M, K}, x.options().dtype(at::kFloat8_e4m3fn));
+  auto s = at::empty({M, (K + 127) / 128}, x.options().dtype(at::kFloat));
+  tb::launch_fp8_quantize_act(bf(x), (uint8_t*)q.data_ptr(), s.data_ptr<float>(), (int)M, (int)K, cur());
+  return {q, s};
+}
+
+at::Tensor fp8_block_gemm(const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq, const at::Tensor& ws) {
+  need(xq.is_cuda() && wq.is_cuda() && xq.dim() == 2 && wq.dim() == 2 && xq.is_contiguous() && wq.is_contiguous(), "fp8_block_gemm: contiguous 2-D CUDA operands");
+  need(xq.element_size() == 1 && wq.element_size() == 1, "fp8_block_gemm: E4M3 operands");
+  need(xs.scalar_type() == at::kFloat && ws.scalar_type() == at::kFloat && xs.is_contiguous() && ws.is_contiguous(), "fp8_block_gemm: fp32 scales");
+  const int64_t M = xq.size(0), K = xq.size(1), N = wq.size(0);
+  need(wq.size(1) == K, "fp8_block_gemm: K mismatch");
+  const int64_t KB = (K + 127) / 128;
+  need(xs.numel() == M * KB && ws.numel() == ((N + 127) / 128) * KB, "fp8_block_gemm: scale shapes");
+  c10::cuda::CUDAGuard g(xq.device());
+  auto out = at::empty({M, N}, xq.options().dtype(at::kBFloat16));
+  auto status = at::zeros({1}, xq.options().dtype(at::kInt));
+  tb::launch_fp8_block_gemm((const uint8_t*)xq.data_ptr(), xs.data_ptr<float>(), (const uint8_t*)wq.data_ptr(),
+                            ws.data_ptr<float>(), bfm(out), (int)M, (int)N, (int)K, status.data_ptr<int>(), cur());
+  return out;
+}
+
+std::vector<at::Tensor> nvfp4_quantize(const at::Tensor& w, bool hadamard) {
+  need(w.is_cuda() && w.dim() == 2 && w.is_contiguous(), "nvfp4_quantize: contiguous [N,K] CUDA");
+  need(w.scalar_type() == at::kBFloat16 || w.scalar_type() == at::kFloat, "nvfp4_quantize: bf16 or fp32");
+  need(w.size(1) % 16 == 0, "nvfp4_quantize: K % 16");
+  c10::cuda::CUDAGuard g(w.device());
+  const int64_t N = w.size(0), K = w.size(1);
+  auto packed = at::empty({N, K / 2}, w.options().dtype(at::kByte));
+  auto scales = at::empty({N, K / 16}, w.options().dtype(at::kFloat8_e4m3fn));
+  auto tscale = at::empty({}, w.options().dtype(at::kFloat));
+  auto scratch = at::empty({1}, w.options().dtype(at::kInt));
+  tb::launch_nvfp4_quantize(w.data_ptr(), w.scalar_type() == at::kBFloat16, N, K, hadamard, packed.data_ptr<uint8_t>(),
+                            (uint8_t*)scales.data_ptr(), tscale.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), cur());
+  return {packed, scales, tscale};
+}
+
+bool scale_is_bf16(const at::Tensor& scales) {
+  need(scales.scalar_type() == at::kBFloat16 || scales.element_size() == 1, "nvfp4: scales must be E4M3 or bf16");
+  return scales.scalar_type() == at::kBFloat16;
+}
+
+at::Tensor nvfp4_dequant(const at::Tensor& packed, const at::Tensor& scales, const at::Tensor& tscale) {
+  need(packed.is_cuda() && packed.dim() == 2 && packed.is_contiguous() && packed.scalar_type() == at::kByte, "nvfp4_dequant: packed uint8 [N,K/2]");
+  need(scales.is_contiguous() && scales.numel() * 8 == packed.numel(), "nvfp4_dequant: one scale per 16 elements");
+  need(tscale.is_cuda() && tscale.scalar_type() == at::kFloat && tscale.numel() == 1, "nvfp4_dequant: fp32 device tensor scale");
+  c10::cuda::CUDAGuard g(packed.device());
+  const int64_t N = packed.size(0), K = packed.size(1) * 2;
+  auto out = at::empty({N, K}, packed.options().dtype(at::kBFloat16));
+  tb::launch_nvfp4_dequant(packed.data_ptr<uint8_t>(), scales.data_ptr(), scale_is_bf16(scales), tscale.data_ptr<float>(), N, K, bfm(out), cur());
+  return out;
+}
+
+at::Tensor nvfp4_gemv(const at::Tensor& x, const at::Tensor& packed, const at::Tensor& scales, const at::Tensor& tscale) {
+  need(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "nvfp4_gemv: bf16 [M,K]");
+  need(packed.is_contiguous() && packed.scalar_type() == at::kByte && packed.size(1) * 2 == x.size(1), "nvfp4_gemv: K mismatch");
+  need(scales.is_contiguous() && scales.numel() * 8 == packed.numel(), "nvfp4_gemv: one scale per 16 elements");
+  need(tscale.is_cuda() && tscale.scalar_type() == at::kFloat && tscale.numel() == 1, "nvfp4_gemv: fp32 device tensor scale");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t M = x.size(0), K = x.size(1), N = packed.size(0);
+  auto y = at::empty({M, N}, x.options());
+  tb::launch_nvfp4_gemv(bf(x), packed.data_ptr<uint8_t>(), scales.data_ptr(), scale_is_bf16(scales), tscale.data_ptr<float>(), bfm(y), (int)M, (int)N, (int)K, cur());
+  return y;
+}
+
+at::Tensor fwht16(const at::Tensor& x) {
+  need(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.numel() % 16 == 0, "fwht16: contiguous bf16, numel % 16");
+  c10::cuda::CUDAGuard g(x.device());
+  auto out = at::empty_like(x);
+  tb::launch_fwht16(bf(x), bfm(out), x.numel(), cur());
+  return out;
+}
+
+}  // namespace
+
+void register_quant(pybind11::module& m) {
+  m.def("fp8_quantize_act", &fp8_quantize_act, "bf16 [M,K] -> (E4M3 [M,K], fp32 scales [M,K/128])");
+  m.def("fp8_block_gemm", &fp8_block_gemm, "block-scaled E4M3 GEMM (tcgen05 kind::f8f6f4), bf16 out");
+  m.def("nvfp4_quantize", &nvfp4_quantize, "[N,K] -> (packed E2M1, E4M3 block scales, fp32 tensor scale)");
+  m.def("nvfp4_dequant", &nvfp4_dequant, "packed NVFP4 -> bf16 [N,K]");
+  m.def("nvfp4_gemv", &nvfp4_gemv, "y = x @ W^T for M <= 8 straight from packed NVFP4 weights");
+  m.def("fwht16", &fwht16, "orthonormal 16-point Walsh-Hadamard transform over consecutive groups of 16");
+}

@@ -106,10 +106,12 @@ class NVFP4Linear(nn.Module):
 
     @torch.no_grad()
     def load_weight(self, w: torch.Tensor):
-        wf = w.float()
-        if self.hadamard:
-            wf = ref.fwht16(wf)  # rotate each group of 16 input features; the activation gets the same rotation
-        p, s, t = ref.nvfp4_quantize(wf, self.block_scales.dtype)
+        # the rotation of each group of 16 input features is folded into the quantiser; activations get the same one
+        if w.is_cuda and self.block_scales.dtype == torch.float8_e4m3fn:
+            p, s, t = ops.nvfp4_quantize(w, hadamard=self.hadamard)
+        else:
+            wf = ref.fwht16(w.float()) if self.hadamard else w.float()
+            p, s, t = ref.nvfp4_quantize(wf, self.block_scales.dtype)
         self.packed_weight = p.to(self.packed_weight.device)
         self.block_scales = s.to(self.block_scales.device)
         self.tensor_scale = t.to(self.tensor_scale.device)
@@ -125,7 +127,7 @@ class NVFP4Linear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, self.in_features)
         if self.hadamard:
-            x2 = ref.fwht16(x2)
+            x2 = ops.fwht16(x2)
         y = ops.nvfp4_linear(x2, self.packed_weight, self.block_scales, self.tensor_scale, out_dtype=x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)

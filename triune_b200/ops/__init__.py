@@ -709,5 +709,27 @@ def nvfp4_linear(x2, packed, scales, tscale, out_dtype=torch.bfloat16):
     return (x2.float() @ w.t()).to(out_dtype)
 
 
-nvfp4_quantize = ref.nvfp4_quantize
-nvfp4_dequantize = ref.nvfp4_dequantize
+def nvfp4_quantize(w, scale_dtype=torch.float8_e4m3fn, hadamard: bool = False):
+    """[N,K] -> (packed E2M1 [N,K/2], block scales [N,K/16], fp32 tensor scale); ``hadamard`` folds the 16-point
+    Walsh-Hadamard rotation of each group of 16 inputs into the quantiser."""
+    from . import quant_cuda
+
+    if scale_dtype == torch.float8_e4m3fn and _ext.use_kernels(w) and w.dtype in (torch.bfloat16, torch.float32):
+        return quant_cuda.nvfp4_quantize(w, hadamard)
+    return ref.nvfp4_quantize(ref.fwht16(w.float()) if hadamard else w, scale_dtype)
+
+
+def nvfp4_dequantize(packed, scales, tscale, dtype=torch.bfloat16):
+    from . import quant_cuda
+
+    if _ext.use_kernels(packed) and torch.is_tensor(tscale) and tscale.is_cuda:
+        return quant_cuda.nvfp4_dequant(packed, scales, tscale).to(dtype)
+    return ref.nvfp4_dequantize(packed, scales, tscale, dtype)
+
+
+def fwht16(x):
+    from . import quant_cuda
+
+    if _ext.use_kernels(x) and x.dtype == torch.bfloat16 and x.numel() % 16 == 0:
+        return quant_cuda.fwht16(x)
+    return ref.fwht16(x)

@@ -1,31 +1,64 @@
-"""Dispatch of the quantised GEMMs to the sm_100a kernels."""
+"""Dispatch of the quantised serving ops to the sm_100a kernels (``csrc/quant/quant_kernels.cu``)."""
 
 from __future__ import annotations
 
 import torch
 
 from .. import _ext
+from . import _tick
 
 
 def fp8_supported(x2, wq) -> bool:
-    return _ext.use_kernels(x2, wq) and hasattr(_ext.ext(), "fp8_block_gemm") and x2.dtype == torch.bfloat16 \
-        and x2.shape[1] % 128 == 0 and wq.shape[0] % 8 == 0
+    return _ext.use_kernels(x2, wq) and x2.dtype == torch.bfloat16 and x2.shape[1] % 16 == 0 and wq.shape[0] % 8 == 0
+
+
+def fp8_quantize_act(x2: torch.Tensor):
+    _tick()
+    return _ext.ext().fp8_quantize_act(x2.contiguous())
+
+
+def fp8_block_gemm(xq, xs, wq, ws):
+    _tick()
+    return _ext.ext().fp8_block_gemm(xq, xs.contiguous(), wq, ws.contiguous())
 
 
 def fp8_block_linear(x2, wq, ws, block, out_dtype):
-    e = _ext.ext()
-    xq, xs = e.fp8_quantize_act(x2.contiguous())
-    return e.fp8_block_gemm(xq, xs, wq, ws).to(out_dtype)
+    assert block == 128, "the tensor-core path uses 128-wide scale blocks"
+    xq, xs = fp8_quantize_act(x2)
+    y = fp8_block_gemm(xq, xs, wq, ws)
+    return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
 
 
 def nvfp4_supported(x2, packed) -> bool:
-    return _ext.use_kernels(x2, packed) and hasattr(_ext.ext(), "nvfp4_dequant") and x2.dtype == torch.bfloat16 \
-        and packed.shape[0] % 8 == 0
+    return _ext.use_kernels(x2, packed) and x2.dtype == torch.bfloat16 and packed.shape[0] % 8 == 0
+
+
+def nvfp4_quantize(w: torch.Tensor, hadamard: bool = False):
+    """[N,K] bf16/fp32 on the GPU -> (packed uint8 [N,K/2], E4M3 scales [N,K/16], fp32 tensor scale)."""
+    _tick(3)
+    return tuple(_ext.ext().nvfp4_quantize(w.contiguous(), bool(hadamard)))
+
+
+def nvfp4_dequant(packed, scales, tscale):
+    _tick()
+    return _ext.ext().nvfp4_dequant(packed, scales, tscale)
+
+
+def fwht16(x: torch.Tensor) -> torch.Tensor:
+    _tick()
+    return _ext.ext().fwht16(x.contiguous())
 
 
 def nvfp4_linear(x2, packed, scales, tscale, out_dtype):
+    """Decode (M <= 8): GEMV straight from the packed weights. Prefill: decode the weights to bf16 once per call
+    (4.5 -> 16 bits, a small fraction of the GEMM's traffic at large M) and run the tcgen05 GEMM."""
     from . import gemm
 
     e = _ext.ext()
-    w = e.nvfp4_dequant(packed, scales, tscale)  # bf16 [N, K], decoded by the dequant kernel
-    return gemm(x2.contiguous(), w).to(out_dtype)
+    x2 = x2.contiguous()
+    if x2.shape[0] <= 8:
+        _tick()
+        y = e.nvfp4_gemv(x2, packed, scales, tscale)
+    else:
+        y = gemm(x2, nvfp4_dequant(packed, scales, tscale))
+    return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
