@@ -106,7 +106,7 @@ def run_ours(args):
     model = place_model(TriuneTransformer.from_config(cfg), dev, torch.bfloat16)
     run_cfg = {"lr": 3e-4, "min_lr": 3e-5, "warmup_steps": 10, "total_steps": 100000, "depth_mode": "cortex",
                "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": VOCAB, "ns_steps": 5,
-               "cuda_graph": (not args.no_graph) and ctx.world_size == 1}
+               "cuda_graph": (not args.no_graph) and (ctx.world_size == 1 or args.dp_mode == "fused")}
     dp = ShardedDataParallel(ctx, mode=args.dp_mode) if ctx.world_size > 1 else None
     opt = CentroidSteerOptimizer(model, lr=3e-4, muon_ns_steps=5, grad_clip=1.0,
                                  storage_factory=dp.storage_factory if dp is not None else None)

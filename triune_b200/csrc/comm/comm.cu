@@ -95,10 +95,12 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
 
 // ---------------------------------------------------------------- phase 1: reduce-scatter + norm partial
 __global__ void __launch_bounds__(256) dp_reduce_scatter_kernel(PeerTable pt, long long grad_off, long long norm_off,
-                                                                RangeList ranges, uint32_t epoch, int use_multimem,
+                                                                RangeList ranges, uint32_t epoch,
+                                                                const uint32_t* __restrict__ epoch_dev, int use_multimem,
                                                                 unsigned int* block_counter, int* status) {
   __shared__ float red[8];
   __shared__ int last_block;
+  if (epoch_dev) epoch = *epoch_dev;  // device-resident epoch: the launch can be replayed from a CUDA graph
   // announce that this rank's gradients are final, then wait until every peer said the same
   if (blockIdx.x == 0) signal_all(pt, CH_GRADS_READY, epoch);
   const bool ok = cta_wait_all(pt, CH_GRADS_READY, epoch, status);
@@ -158,8 +160,16 @@ __global__ void __launch_bounds__(256) dp_adamw_allgather_kernel(PeerTable pt, l
                                                                  float* __restrict__ m, float* __restrict__ v, float lr,
                                                                  float beta1, float beta2, float eps, float wd, float bc1,
                                                                  float bc2, float max_norm, float* clip_out,
-                                                                 float* norm_out, uint32_t epoch, int use_multimem,
+                                                                 float* norm_out, uint32_t epoch,
+                                                                 const uint32_t* __restrict__ epoch_dev,
+                                                                 const float* __restrict__ hyper, int use_multimem,
                                                                  int* status) {
+  if (epoch_dev) epoch = *epoch_dev;
+  if (hyper) {  // [0] lr, [1] 1 - beta1^t, [2] 1 - beta2^t of this step, written by the host before the launch
+    lr = hyper[0];
+    bc1 = hyper[1];
+    bc2 = hyper[2];
+  }
   const bool ok = cta_wait_all(pt, CH_NORM_PARTIAL, epoch, status);
   if (!ok) return;
   const float* norm = reinterpret_cast<const float*>(pt.bufs[pt.rank] + norm_off);
@@ -230,7 +240,9 @@ __global__ void __launch_bounds__(256) dp_broadcast_ranges_kernel(PeerTable pt, 
   }
 }
 
-__global__ void __launch_bounds__(32) comm_barrier_kernel(PeerTable pt, int channel, uint32_t epoch, int* status) {
+__global__ void __launch_bounds__(32) comm_barrier_kernel(PeerTable pt, int channel, uint32_t epoch,
+                                                          const uint32_t* __restrict__ epoch_dev, int* status) {
+  if (epoch_dev) epoch = *epoch_dev;
   signal_all(pt, channel, epoch);
   (void)cta_wait_all(pt, channel, epoch, status);
 }
@@ -270,21 +282,21 @@ int comm_grid() { return 148 * 2; }
 }  // namespace
 
 void launch_dp_reduce_scatter(PeerTable pt, long long grad_off, long long norm_off, RangeList ranges, uint32_t epoch,
-                              bool use_multimem, unsigned int* block_counter, int* status, cudaStream_t s) {
+                              const uint32_t* epoch_dev, bool use_multimem, unsigned int* block_counter, int* status, cudaStream_t s) {
   if (pt.world > COMM_MAX_RANKS) throw std::runtime_error("too many ranks for the signal pad layout");
-  dp_reduce_scatter_kernel<<<comm_grid(), 256, 0, s>>>(pt, grad_off, norm_off, ranges, epoch, use_multimem ? 1 : 0,
-                                                       block_counter, status);
+  dp_reduce_scatter_kernel<<<comm_grid(), 256, 0, s>>>(pt, grad_off, norm_off, ranges, epoch, epoch_dev,
+                                                       use_multimem ? 1 : 0, block_counter, status);
   check("dp_reduce_scatter");
 }
 
 void launch_dp_adamw_allgather(PeerTable pt, long long grad_off, long long norm_off, long long param_off,
                                ElemRange owned, long long state_base, float* master, float* m, float* v, float lr,
                                float beta1, float beta2, float eps, float wd, float bc1, float bc2, float max_norm,
-                               float* clip_out, float* norm_out, uint32_t epoch, bool use_multimem, int* status,
-                               cudaStream_t s) {
+                               float* clip_out, float* norm_out, uint32_t epoch, const uint32_t* epoch_dev,
+                               const float* hyper, bool use_multimem, int* status, cudaStream_t s) {
   dp_adamw_allgather_kernel<<<comm_grid(), 256, 0, s>>>(pt, grad_off, norm_off, param_off, owned, state_base, master, m,
                                                         v, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm, clip_out,
-                                                        norm_out, epoch, use_multimem ? 1 : 0, status);
+                                                        norm_out, epoch, epoch_dev, hyper, use_multimem ? 1 : 0, status);
   check("dp_adamw_allgather");
 }
 
@@ -295,8 +307,9 @@ void launch_dp_broadcast_ranges(PeerTable pt, long long param_off, RangeList ran
   check("dp_broadcast_ranges");
 }
 
-void launch_comm_barrier(PeerTable pt, int channel, uint32_t epoch, int* status, cudaStream_t s) {
-  comm_barrier_kernel<<<1, 32, 0, s>>>(pt, channel, epoch, status);
+void launch_comm_barrier(PeerTable pt, int channel, uint32_t epoch, const uint32_t* epoch_dev, int* status,
+                         cudaStream_t s) {
+  comm_barrier_kernel<<<1, 32, 0, s>>>(pt, channel, epoch, epoch_dev, status);
   check("comm_barrier");
 }
 

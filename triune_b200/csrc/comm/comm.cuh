@@ -48,22 +48,23 @@ struct RangeList {
 // CH_NORM_PARTIAL. grad_off / norm_off are byte offsets of the gradient arena and of the fp32[world] norm array
 // inside the symmetric buffer.
 void launch_dp_reduce_scatter(PeerTable pt, long long grad_off, long long norm_off, RangeList ranges, uint32_t epoch,
-                              bool use_multimem, unsigned int* block_counter, int* status, cudaStream_t s);
+                              const uint32_t* epoch_dev, bool use_multimem, unsigned int* block_counter, int* status, cudaStream_t s);
 
 // Phase 2 for the AdamW tier: waits for all norm partials, derives the clip coefficient (written to clip_out),
 // applies AdamW to the owned range and stores the new bf16 parameters into EVERY rank's parameter arena.
 void launch_dp_adamw_allgather(PeerTable pt, long long grad_off, long long norm_off, long long param_off,
                                ElemRange owned, long long state_base, float* master, float* m, float* v, float lr,
                                float beta1, float beta2, float eps, float wd, float bc1, float bc2, float max_norm,
-                               float* clip_out, float* norm_out, uint32_t epoch, bool use_multimem, int* status,
-                               cudaStream_t s);
+                               float* clip_out, float* norm_out, uint32_t epoch, const uint32_t* epoch_dev,
+                               const float* hyper, bool use_multimem, int* status, cudaStream_t s);
 
 // Broadcast locally updated bf16 parameter ranges to every peer (plain peer stores or multimem.st).
 void launch_dp_broadcast_ranges(PeerTable pt, long long param_off, RangeList ranges, bool use_multimem,
                                 cudaStream_t s);
 
 // All ranks: raise `channel` on every peer, then wait until every peer raised it (bounded). One CTA.
-void launch_comm_barrier(PeerTable pt, int channel, uint32_t epoch, int* status, cudaStream_t s);
+void launch_comm_barrier(PeerTable pt, int channel, uint32_t epoch, const uint32_t* epoch_dev, int* status,
+                         cudaStream_t s);
 
 // Scalar metrics all-reduce (sum) piggy-backed on the signal protocol: each rank stores its `n` floats into slot
 // [rank] of every peer's metric array, barriers, and sums. out[n] on every rank.

@@ -71,26 +71,36 @@ class FusedDPUpdater:
             flat += [r[0], r[1]]
         self.owned_flat = flat
         self.bcast_flat = [x for r in self.matrix_ranges for x in r]
-        self.comm_bytes = 0
+        # The epoch of the three step channels lives on the device and is bumped by the step itself, so a captured
+        # step can be replayed; every rank runs the same sequence of steps, so the counters stay equal.
+        self.epoch_dev = torch.zeros(1, device=dev, dtype=torch.int32)
+        owned = sum(flat[i + 1] - flat[i] for i in range(0, len(flat), 2))
+        self.bytes_per_step = owned * 4 * (ctx.world_size - 1) + owned * 2 * (ctx.world_size - 1)
         self.steps = 0
+
+    @property
+    def comm_bytes(self) -> int:
+        return self.bytes_per_step * self.opt.step_count
 
     def step(self):
         opt, buf = self.opt, self.buf
         a = opt.arena
         e = _ext.ext()
         rank, world, bufs, sigs, mc = buf.table()
-        ep = buf.next_epoch()
+        ep = 0
+        self.epoch_dev.add_(1)
+        hyper = opt.hyper if getattr(opt, "capturable", False) else None
         opt.step_count += 1
         goff, noff, poff = buf.offset("grad"), buf.offset("norm"), buf.offset("param")
         e.dp_reduce_scatter(rank, world, bufs, sigs, mc, goff, noff, self.owned_flat, ep, buf.use_multimem, self.counter,
-                            self.status)
+                            self.status, self.epoch_dev)
         lo, hi = a.adamw_range
         b1, b2 = opt.betas
         clip = float(opt.grad_clip) if opt.grad_clip else 0.0
         ob, oe = self.adamw_owned
         e.dp_adamw_allgather(rank, world, bufs, sigs, mc, goff, noff, poff, ob, oe, lo, a.master()[lo:hi], opt.exp_avg,
                              opt.exp_avg_sq, opt.lr, b1, b2, opt.eps, opt.weight_decay, opt.step_count, clip,
-                             opt._clip_coef, self.norm_out, ep, buf.use_multimem, self.status)
+                             opt._clip_coef, self.norm_out, ep, buf.use_multimem, self.status, self.epoch_dev, hyper)
         ops._tick(2)
         opt.last_grad_norm = self.norm_out
         opt._step_muon()
@@ -98,10 +108,8 @@ class FusedDPUpdater:
         if self.bcast_flat:
             e.dp_broadcast_ranges(rank, world, bufs, sigs, mc, poff, self.bcast_flat, buf.use_multimem)
             ops._tick()
-        e.comm_barrier(rank, world, bufs, sigs, CH_PARAMS_DONE, ep, self.status)
+        e.comm_barrier(rank, world, bufs, sigs, CH_PARAMS_DONE, ep, self.status, self.epoch_dev)
         ops._tick()
-        owned = sum(self.owned_flat[i + 1] - self.owned_flat[i] for i in range(0, len(self.owned_flat), 2))
-        self.comm_bytes += owned * 4 * (world - 1) + owned * 2 * (world - 1)
         self.steps += 1
 
     def check(self) -> int:
