@@ -107,9 +107,20 @@ def run_ours(args):
     run_cfg = {"lr": 3e-4, "min_lr": 3e-5, "warmup_steps": 10, "total_steps": 100000, "depth_mode": "cortex",
                "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": VOCAB, "ns_steps": 5,
                "cuda_graph": (not args.no_graph) and (ctx.world_size == 1 or args.dp_mode == "fused")}
-    dp = ShardedDataParallel(ctx, mode=args.dp_mode) if ctx.world_size > 1 else None
-    opt = CentroidSteerOptimizer(model, lr=3e-4, muon_ns_steps=5, grad_clip=1.0,
-                                 storage_factory=dp.storage_factory if dp is not None else None)
+    dp, opt = None, None
+    if ctx.world_size > 1:
+        try:
+            dp = ShardedDataParallel(ctx, mode=args.dp_mode)
+            opt = CentroidSteerOptimizer(model, lr=3e-4, muon_ns_steps=5, grad_clip=1.0, storage_factory=dp.storage_factory)
+        except Exception as e:  # no peer-mapped memory on this box: fall back to the NCCL all-reduce path, eagerly
+            if args.dp_mode != "fused":
+                raise
+            print(f"[bench] fused NVLink DP unavailable ({type(e).__name__}: {e}); using --dp-mode nccl", file=sys.stderr, flush=True)
+            args.dp_mode, run_cfg["cuda_graph"] = "nccl", False
+            dp = ShardedDataParallel(ctx, mode="nccl")
+            opt = None
+    if opt is None:
+        opt = CentroidSteerOptimizer(model, lr=3e-4, muon_ns_steps=5, grad_clip=1.0)
     trainer = Trainer(model, run_cfg, optimizer=opt, device=dev, dp=dp)
     src = SyntheticTokenSource(VOCAB, BATCH, SEQ, seed=1234 + ctx.rank, pin=True, pool=4)
     tokens_per_step = BATCH * SEQ * ctx.world_size
@@ -310,7 +321,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA-graph replay)")
-    ap.add_argument("--dp-mode", default=os.environ.get("TRIUNE_DP_MODE", "nccl"), choices=["nccl", "fused"])
+    ap.add_argument("--dp-mode", default=os.environ.get("TRIUNE_DP_MODE", "fused"), choices=["nccl", "fused"])
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if not torch.cuda.is_available():

@@ -33,6 +33,10 @@ class CUDAGraphEngine:
         self.replays = 0
         self.captures = 0
         self.enabled = torch.cuda.is_available()
+        # Eager steps and captures share ONE side stream: autograd nodes that outlive a step (gradient accumulators
+        # kept alive by a retained graph) remember the stream they were created on, and a capture that has to wait
+        # for work on any other, uncaptured stream is invalid.
+        self.stream = torch.cuda.Stream() if self.enabled else None
 
     # ------------------------------------------------------------------ training
     def _body(self, x, y, n_valid):
@@ -75,7 +79,14 @@ class CUDAGraphEngine:
             if hasattr(opt, "capturable"):
                 opt.capturable = False
             tr._pending = (x, y, n_valid)
-            out = eng.step_once()
+            if self.stream is not None:
+                cur = torch.cuda.current_stream()
+                self.stream.wait_stream(cur)
+                with torch.cuda.stream(self.stream):
+                    out = eng.step_once()
+                cur.wait_stream(self.stream)
+            else:
+                out = eng.step_once()
             self.eager_steps += 1
             return out["loss"]
         key = (kind, tuple(x.shape), int(n_valid))
@@ -87,7 +98,7 @@ class CUDAGraphEngine:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(g, pool=self.pool):
+            with torch.cuda.graph(g, pool=self.pool, stream=self.stream):
                 loss = self._body(sx, sy, n_valid)
             if self.pool is None:
                 self.pool = g.pool()
