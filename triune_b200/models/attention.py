@@ -59,6 +59,14 @@ class _ProjView:
         return F.linear(x, self.weight)
 
 
+def _project(mod: nn.Module, x: torch.Tensor) -> torch.Tensor:
+    """Plain ``nn.Linear`` goes straight to the GEMM; wrapped / quantised replacements (LoRA, FP8, NVFP4) run their own
+    forward."""
+    if type(mod) is nn.Linear:
+        return ops.linear(x, mod.weight, mod.bias)
+    return mod(x)
+
+
 class VectorisedGLA(nn.Module):
     """Multi-head GLA (or Gated DeltaNet when ``use_delta_rule``) with fused QKVG projection."""
 
@@ -115,13 +123,15 @@ class VectorisedGLA(nn.Module):
         B, T, _ = x.shape
         H, D = self.heads, self.head_dim
         state, offset, fmt = parse_cache(cache)
-        qkvg = ops.linear(x.reshape(B * T, self.dim), self.qkvg_weight)
+        lora = getattr(self, "qkvg_lora", None)  # set by the fine-tuner (FusedProjectionLoRA)
+        x2 = x.reshape(B * T, self.dim)
+        qkvg = lora(x2) if lora is not None else ops.linear(x2, self.qkvg_weight)
         cos = sin = None
         if self.use_rope:
             cos, sin = self.rope(T, x.device, offset=offset)
         if not self.use_delta_rule and gla_cuda.core_supported(qkvg, T, D):
             out, new_state = gla_cuda.gla_attention_core(qkvg, cos, sin, state, B, T, H)
-            y = ops.linear(out.view(B, T, self.hidden_dim), self.out_proj.weight)
+            y = _project(self.out_proj, out.view(B, T, self.hidden_dim))
             return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
         q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
         if self.use_delta_rule:
@@ -130,7 +140,7 @@ class VectorisedGLA(nn.Module):
         else:
             out, new_state = ops.gla(q, k, v, g, initial_state=state, gate_logits=True)
         out = out.reshape(B, T, self.hidden_dim).to(x.dtype)
-        y = ops.linear(out, self.out_proj.weight)
+        y = _project(self.out_proj, out)
         return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
 
 
@@ -173,7 +183,7 @@ class SoftmaxAttention(nn.Module):
             q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=(past is None and T > 1)
         )
         o = o.transpose(1, 2).reshape(B, T, self.heads * self.head_dim)
-        return ops.linear(o, self.out_proj.weight), format_cache(new_state, cache, fmt, offset, T)
+        return _project(self.out_proj, o), format_cache(new_state, cache, fmt, offset, T)
 
 
 class HybridAttention(nn.Module):

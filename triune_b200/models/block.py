@@ -28,7 +28,9 @@ class DenseFFN(nn.Sequential):
         super().__init__(nn.Linear(dim, hidden), nn.GELU(approximate="tanh"), nn.Linear(hidden, dim))
 
     def forward(self, x):
-        return ops.mlp_gelu(x, self[0].weight, self[0].bias, self[2].weight, self[2].bias)
+        if type(self[0]) is nn.Linear and type(self[2]) is nn.Linear:
+            return ops.mlp_gelu(x, self[0].weight, self[0].bias, self[2].weight, self[2].bias)
+        return self[2](ops.gelu_tanh(self[0](x)))  # wrapped / quantised projections run their own forward
 
 
 class TransformerBlock(nn.Module):

@@ -733,3 +733,53 @@ def fwht16(x):
     if _ext.use_kernels(x) and x.dtype == torch.bfloat16 and x.numel() % 16 == 0:
         return quant_cuda.fwht16(x)
     return ref.fwht16(x)
+
+
+# ----------------------------------------------------------------------------
+# LoRA: frozen base GEMM with the rank-r update accumulated into its output
+# ----------------------------------------------------------------------------
+class _LoRALinearFn(torch.autograd.Function):
+    """y = x W^T + b + s * (x A^T) B^T with W, b frozen. The low-rank product is added to the base GEMM's output tile
+    by tile through the GEMM's reduce-add epilogue, so y is written once and updated in place (no separate add pass);
+    the backward never forms B A."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, A, B, scaling):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not _tma_ok(x2):
+            x2 = x2.contiguous()
+        y = gemm(x2, w, bias=bias)
+        t = gemm(x2, A)                                  # [M, r]
+        gemm(t, B, y, accumulate=True, alpha=float(scaling))
+        ctx.save_for_backward(x2, w, A, B, t)
+        ctx.scaling, ctx.in_shape = float(scaling), x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, A, B, t = ctx.saved_tensors
+        s = ctx.scaling
+        dy2 = dy.reshape(-1, w.shape[0])
+        if not _tma_ok(dy2):
+            dy2 = dy2.contiguous()
+        u = gemm(dy2, B, b_mn=True, alpha=s)             # [M, r] = s * dy B
+        dx = dA = dB = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True)
+            gemm(u, A, dx, b_mn=True, accumulate=True)
+            dx = dx.view(ctx.in_shape)
+        if ctx.needs_input_grad[3]:
+            dA = gemm(u, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(A.dtype)      # [r, K]
+        if ctx.needs_input_grad[4]:
+            dB = gemm(dy2, t, a_mn=True, b_mn=True, alpha=s, out_dtype=torch.float32).to(B.dtype)  # [N, r]
+        return dx, None, None, dA, dB, None
+
+
+def lora_linear(x, w, bias, A, B, scaling: float):
+    """LoRA linear over a frozen base weight. A: [r, in], B: [out, r]."""
+    r = A.shape[0]
+    if (_ext.use_kernels(x, w, A, B) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and A.dtype == torch.bfloat16
+            and r % 8 == 0 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and not w.requires_grad):
+        return _LoRALinearFn.apply(x, w, bias, A, B, scaling)
+    return F.linear(x, w, bias) + F.linear(F.linear(x, A), B) * scaling
