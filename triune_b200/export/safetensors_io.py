@@ -23,7 +23,7 @@ _RD = {v: k for k, v in _DT.items()}
 
 def _raw(t: torch.Tensor) -> bytes:
     t = t.detach().cpu().contiguous()
-    return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+    return t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 
 def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Dict[str, str]] = None) -> None:

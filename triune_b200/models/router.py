@@ -19,11 +19,12 @@ class GumbelSoftmaxRouter(nn.Module):
     def __init__(self, hidden_dim: int, target_depth_dist=(0.34, 0.33, 0.33), balance_coef: float | None = None):
         super().__init__()
         self.router_mlp = nn.Sequential(nn.Linear(hidden_dim, 256), nn.ReLU(), nn.Linear(256, 3))
-        t = torch.as_tensor(target_depth_dist, dtype=torch.float32)
-        if t.ndim != 1 or t.numel() != 3:
+        vals = [float(v) for v in (target_depth_dist.tolist() if torch.is_tensor(target_depth_dist) else target_depth_dist)]
+        if len(vals) != 3:
             raise ValueError(f"target_depth_dist must have 3 elements, got {target_depth_dist}")
-        if abs(float(t.sum()) - 1.0) > 1e-4:
-            raise ValueError(f"target_depth_dist must sum to 1.0, got {float(t.sum()):.4f}")
+        if abs(sum(vals) - 1.0) > 1e-4:
+            raise ValueError(f"target_depth_dist must sum to 1.0, got {sum(vals):.4f}")
+        t = torch.tensor(vals, dtype=torch.float32)  # validated on the host: construction also works on the meta device
         self.balance_coef = balance_coef
         self.register_buffer("target_dist", t)
         self.register_buffer("router_bias", torch.zeros(3, dtype=torch.float32))
