@@ -200,3 +200,16 @@ class PinnedStageRing:
             self.close()
         except Exception:
             pass
+
+
+def get_native_c_info() -> dict:
+    """Which native pieces are loaded: the C-ABI engine library and the CUDA extension."""
+    from .. import _ext
+
+    lib = None
+    try:
+        lib = load_library()
+    except Exception:
+        pass
+    return {"c_engine_loaded": lib is not None, "c_engine_path": str(getattr(lib, "_name", "")) if lib is not None else None,
+            "cuda_extension": _ext.ext_available(), "simd": "avx2+fma", "arch": "sm_100a"}
