@@ -1,0 +1,406 @@
+"""CPU tests of the framework components around the model core: zoo, exits, JEV, conversion, LoRA, tokenizers, data,
+export, staging, planning, session state, callbacks."""
+
+import json
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+from triune_b200.config import ModelConfig
+from triune_b200.models import TriuneTransformer
+
+CFG = dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4, top_k=2, router_prefix_layers=1,
+           reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=96, dense_hidden=80)
+
+
+def tiny():
+    torch.manual_seed(0)
+    return TriuneTransformer.from_config(ModelConfig(**CFG))
+
+
+class Tok:
+    def encode(self, s):
+        return [ord(c) % 256 for c in s]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(int(i)) for i in ids)
+
+
+# ------------------------------------------------------------------------------------------------ zoo / specs
+def test_model_specs_clamp_and_resolve(tmp_path):
+    from triune_b200.models.zoo import CANONICAL_MODEL_SPECS, get_model_spec, load_model, register_model
+
+    assert len(CANONICAL_MODEL_SPECS) == 11 and CANONICAL_MODEL_SPECS["triune-base"].compute_exact_params()[0] == 90_789_271
+    s = get_model_spec("triune-micro", num_layers=3, reflex_exit_layer=9, limbic_exit_layer=9)
+    assert s.num_layers == 4 and 0 < s.router_prefix_layers < s.reflex_exit_layer < s.limbic_exit_layer < s.num_layers
+    assert get_model_spec("triune-nano", precision="float8_e4m3").use_fp8
+    assert get_model_spec("triune-nano", hidden_dim=384).head_dim == 128  # 3 heads kept, head_dim follows hidden_dim
+    m = load_model("triune-nano", vocab_size=512)
+    assert sum(p.numel() for p in m.parameters()) == get_model_spec("triune-nano", vocab_size=512).compute_exact_params()[0]
+
+    @register_model("unit-test-arch")
+    class Toy(nn.Module):
+        def __init__(self, n=3):
+            super().__init__()
+            self.l = nn.Linear(n, n)
+
+    assert isinstance(load_model("unit-test-arch", n=5), Toy)
+    p = tmp_path / "m.pt"
+    torch.save({"model_state": m.state_dict(), "config": {}}, p)
+    m2 = load_model(str(p))
+    assert all(torch.equal(a, b) for a, b in zip(m.state_dict().values(), m2.state_dict().values()))
+    with pytest.raises(ValueError):
+        load_model("definitely-not-a-model")
+
+
+# ------------------------------------------------------------------------------------------------ JEV / exits
+def test_jev_objective_and_router():
+    from triune_b200.models.jev import JEVExitRouter, JEVLatentPredictor, JEVObjective
+
+    torch.manual_seed(0)
+    p = JEVLatentPredictor(32)
+    z, t = torch.randn(4, 7, 32), torch.randn(4, 7, 32)
+    for mode in ("euclidean", "geodesic", "stiefel"):
+        loss, parts = JEVObjective(stp_mode=mode)(p(z), t, return_dict=True)
+        assert torch.isfinite(loss) and set(parts) == {"l_sim", "l_stp", "l_cov", "total_loss"}
+    assert float(JEVObjective().compute_sim_loss(t, t)) < 1e-6 and float(JEVObjective().compute_stp_loss(t, t)) == 0.0
+    for metric in ("cosine", "euclidean", "geodesic", "stp_tube", "learned"):
+        r = JEVExitRouter(32, distance_metric=metric)(z, z)
+        assert r.should_exit.shape == (4, 7)
+        if metric != "learned":
+            assert bool(r.should_exit.all())  # identical latents are always confident
+    with pytest.raises(ValueError):
+        JEVExitRouter(32, distance_metric="manhattan")
+
+
+def test_early_exit_adapters_on_foreign_model():
+    from triune_b200.models.adapters import WeightTiedExitProjection, attach_early_exits
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(32, 32)
+
+        def forward(self, x):
+            return (x + torch.tanh(self.l(x)),)
+
+    class LM(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb, self.layers, self.lm_head = nn.Embedding(100, 32), nn.ModuleList(Blk() for _ in range(8)), nn.Linear(32, 100, bias=False)
+
+        def forward(self, ids):
+            x = self.emb(ids)
+            for l in self.layers:
+                x = l(x)[0]
+            return self.lm_head(x)
+
+    torch.manual_seed(0)
+    m = attach_early_exits(LM(), rank=8, use_jev=True)
+    assert m.reflex_layer_idx == 2 and m.limbic_layer_idx == 4
+    x = torch.randn(2, 5, 32)
+    head = m.reflex_head
+    assert isinstance(head, WeightTiedExitProjection) and len(head.adapter_parameters()) == 3
+    assert torch.allclose(head(x), m.lm_head(head.norm(x)), atol=1e-6)  # zero-initialised up-projection
+    out = m.generate_adaptive(torch.randint(0, 100, (1, 4)), max_new_tokens=5, use_jev=False)
+    assert sum(out["exit_counts"].values()) == len(out["generated_token_ids"]) <= 5
+    out = m.generate_adaptive(torch.randint(0, 100, (1, 4)), max_new_tokens=3, confidence_threshold=0.0)
+    assert out["exit_counts"]["reflex"] == 3 and out["flops_saved_pct"] > 50
+
+
+def test_low_rank_embedding_factorisation():
+    from triune_b200.models.manifold_embedding import UniversalAdaptiveEmbedding
+
+    torch.manual_seed(0)
+    W = torch.randn(300, 12) @ torch.randn(12, 40)
+    e = UniversalAdaptiveEmbedding.from_pretrained_weights(W, rank=12)
+    assert (e(torch.arange(300)) - W).abs().max() < 1e-3
+    h = torch.randn(3, 40)
+    assert torch.allclose(e.compute_logits(h), h @ e(torch.arange(300)).t(), atol=1e-3)
+    vals, idx = e.compute_logits(h, top_k=5)
+    assert idx.shape == (3, 5)
+
+
+def test_transmuter_weight_surgery_and_distillation():
+    transformers = pytest.importorskip("transformers")
+    from triune_b200.models.transmuter import (distill_native_triune_step, expand_gqa_weight, ollama_to_hf_candidate,
+                                                transfer_weights_to_native_triune, transmute_hf_to_triune)
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=6,
+                                   num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+    teacher = transformers.LlamaForCausalLM(cfg)
+    student, rep = transfer_weights_to_native_triune(teacher, num_experts=4, top_k=2)
+    assert rep["weights_transferred"] and rep["lm_head_untied"] and rep["student_layers"] == 6
+    hd = 128
+    k_t = teacher.model.layers[0].self_attn.k_proj.weight
+    assert torch.equal(student.layers[0].attn.gla.qkvg_weight[hd : 2 * hd], expand_gqa_weight(k_t, 4, 2))
+    assert torch.equal(student.token_embed.weight, teacher.model.embed_tokens.weight)
+    ids = torch.randint(0, 300, (2, 16))
+    opt = torch.optim.AdamW(student.parameters(), lr=1e-3)
+    a = distill_native_triune_step(student, teacher, ids, opt)
+    b = distill_native_triune_step(student, teacher, ids, opt)
+    assert b["loss"] < a["loss"]
+    m, meta = transmute_hf_to_triune(teacher, use_jev=False)
+    assert meta["transmute_mode"] == "early_exit" and hasattr(m, "generate_adaptive")
+    assert ollama_to_hf_candidate("ollama:gemma3:4b-instruct-q4_K_M") == "google/gemma-3-4b-it"
+    assert ollama_to_hf_candidate("org/repo") == "org/repo" and ollama_to_hf_candidate("nonexistent:1b") is None
+
+
+# ------------------------------------------------------------------------------------------------ LoRA / quantised modules
+DATA = [{"prompt": "hello ", "completion": "world!"}, {"instruction": "say hi", "output": "hi there"},
+        {"messages": [{"role": "user", "content": "a"}, {"role": "assistant", "content": "bcd"}]}, "plain text sample"] * 3
+
+
+def test_lora_finetune_save_load_merge(tmp_path):
+    from triune_b200.trainer.finetune import LoRAConfig, TriuneFineTuner, list_adapters, merge_adapter_checkpoint
+
+    m = tiny()
+    n_base = sum(p.numel() for p in m.parameters())
+    ft = TriuneFineTuner(m, LoRAConfig(rank=8, dropout=0.0), tokenizer=Tok())
+    assert all(not p.requires_grad for n, p in m.named_parameters() if "lora" not in n)
+    assert 0 < ft.count_trainable_parameters() < 0.2 * n_base
+    ex = ft.build_examples(DATA, max_seq_len=32)
+    assert any((y == -100).any() for _, y in ex)  # prompt tokens are masked
+    r = ft.fit(DATA, epochs=6, batch_size=4, lr=5e-3)
+    assert r["final_loss"] < r["first_loss"]
+    x = torch.randint(0, 256, (1, 9))
+    m.eval()
+    y_adapted = m(x, force_depth=2)[0]
+    d = ft.save_adapter(tmp_path / "ad")
+    cfg = json.loads((d / "adapter_config.json").read_text())
+    assert cfg["peft_type"] == "LORA" and cfg["r"] == 8 and (d / "adapter_model.safetensors").is_file()
+    assert list_adapters([str(tmp_path)])[0]["rank"] == 8
+    ft.detach_lora()
+    assert not any("lora" in k for k in m.state_dict())
+    y_base = m(x, force_depth=2)[0]
+    assert (y_base - y_adapted).abs().max() > 1e-4
+    merge_adapter_checkpoint(m, d)
+    assert torch.allclose(m(x, force_depth=2)[0], y_adapted, atol=1e-4)
+
+
+def test_qlora_and_quantised_converters():
+    from triune_b200.models.quant_linear import FP4Linear, NVFP4Linear, convert_to_fp8, convert_to_nvfp4
+    from triune_b200.trainer.finetune import LoRAConfig, TriuneFineTuner
+
+    m = tiny()
+    ft = TriuneFineTuner(m, LoRAConfig(rank=8, use_qlora=True, quantization="4-bit NVFP4", dropout=0.0), tokenizer=Tok())
+    assert sum(isinstance(getattr(a, "original_layer", None), NVFP4Linear) for a in ft.applied_adapters.values()) > 0
+    r = ft.fit(DATA, epochs=2, batch_size=4, lr=5e-3)
+    assert torch.isfinite(torch.tensor(r["final_loss"]))
+    m2 = tiny().eval()
+    x = torch.randint(0, 256, (2, 8))
+    want = m2(x, force_depth=2)[0]
+    assert convert_to_fp8(m2) > 0
+    assert torch.nn.functional.cosine_similarity(m2(x, force_depth=2)[0].flatten(), want.flatten(), dim=0) > 0.99
+    m3 = tiny().eval()
+    n = convert_to_nvfp4(m3, hadamard=True)
+    assert n > 0 and not any(isinstance(mod, NVFP4Linear) for name, mod in m3.named_modules() if "exit_head" in name or "router" in name)
+    assert torch.nn.functional.cosine_similarity(m3(x, force_depth=2)[0].flatten(), want.flatten(), dim=0) > 0.9
+    lin = FP4Linear(32, 16)
+    lin(torch.randn(3, 32)).sum().backward()
+    assert lin.weight.grad is not None and NVFP4Linear.from_linear(nn.Linear(64, 8)).bits_per_weight() == 4.5
+
+
+# ------------------------------------------------------------------------------------------------ tokenizers / data
+CORPUS = ["the quick brown fox jumps over the lazy dog. " * 6, "héllo wörld — naïve café 日本語 🙂 snake_case",
+          "def f(x):\n    return x + 123456\n" * 4] * 4
+
+
+def test_bpe_tokenizer_roundtrip_and_fast_parity(tmp_path):
+    from triune_b200.data.tokenizer import SPECIAL_TOKENS, load_tokenizer, train_bpe
+
+    tok = train_bpe(CORPUS, vocab_size=400)
+    assert len(SPECIAL_TOKENS) == 21 and tok.token_to_id("[PAD]") == 0
+    s = "<|user|>the quick café 🙂 12345 a_b\n<|eot_id|>"
+    ids = tok.encode(s)
+    assert ids.ids == list(ids) and tok.decode(ids, skip_special_tokens=False) == s and "<|user|>" not in tok.decode(ids)
+    tok.save(tmp_path / "t.json")
+    slow = load_tokenizer(tmp_path / "t.json", prefer_fast=False)
+    assert list(slow.encode(s)) == list(ids)
+    pytest.importorskip("tokenizers")
+    fast = load_tokenizer(tmp_path / "t.json")
+    for t in ("the quick café 12345", "def f(x):\n    return  x_1 + 99\n\n", "日本語 🙂 it's"):
+        assert fast.encode(t).ids == list(slow.encode(t)) and fast.decode(fast.encode(t).ids) == t
+    buf, out = bytearray(), ""
+    for i in tok.encode("café 🙂 ok"):
+        buf, piece = tok.decode_stream_step(buf, i)
+        out += piece
+        assert "�" not in piece  # never half a UTF-8 sequence
+    assert out == "café 🙂 ok"
+    assert tok.apply_chat_template([{"role": "user", "content": "hi"}]).endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+
+
+def test_token_stream_dataset_packing_and_holdout(tmp_path):
+    from triune_b200.data.dataset import TokenStreamDataset, build_dataloader
+    from triune_b200.data.tokenizer import train_bpe
+
+    tok = train_bpe(CORPUS, vocab_size=350)
+    ds = TokenStreamDataset(tok, seq_len=32, sep_token_id=tok.sep_token_id, texts=CORPUS, shuffle_buffer=8)
+    items = list(ds)
+    assert len(items) > 4 and all(x.shape == (32,) and torch.equal(x[1:], y[:-1]) for x, y in items)
+    p = tmp_path / "c.jsonl"
+    p.write_text("\n".join(json.dumps({"text": t}) for t in CORPUS))
+    from_file = list(TokenStreamDataset(tok, seq_len=32, sep_token_id=tok.sep_token_id, dataset_name=str(p), shuffle_buffer=1))
+    assert len(from_file) == len(items)
+    two = [len(list(TokenStreamDataset(tok, seq_len=32, sep_token_id=3, texts=CORPUS, rank=r, world_size=2))) for r in (0, 1)]
+    assert abs(two[0] - two[1]) <= 2 and sum(two) <= len(items) + 2  # ranks read disjoint documents
+    cfg = {"batch_size": 2, "seq_len": 32, "eval_batches": 2}
+    hold = list(build_dataloader(tok, cfg, tok.sep_token_id, is_holdout=True, texts=CORPUS))
+    assert len(hold) == 2 and hold[0][0].shape == (2, 32)
+
+
+def test_dynamic_tokenizer_is_lossless():
+    from triune_b200.data.dynamic_tokenizer import DynamicTokenizer
+    from triune_b200.data.tokenizer import train_bpe
+
+    dt = DynamicTokenizer(train_bpe(CORPUS, vocab_size=350))
+    s = "the quick brown fox jumps over the lazy dog. " * 8 + "def f(x):\n    return x\n"
+    o = dt.encode(s, return_chunks=True)
+    assert 2.2 <= o.compression_ratio <= 4.5 and dt.decode(o.input_ids) == s and dt.decode(dt.unpack_chunks(o.chunks)) == s
+    assert all(len(c) == dt.chunk_size for c in o.chunks) and max(o.input_ids) >= dt.dynamic_id_start
+    b = dt.encode_batch([s, "hello world"])
+    assert dt.decode_batch(b["input_ids"], b["attention_mask"]) == [s, "hello world"]
+    assert dt.learn_ngrams(CORPUS, max_new_rules=10) > 0
+    tab = dt.lookup_vector(8)
+    first = dt.dynamic_id_start
+    assert tab[0, 1 : 1 + min(8, int(tab[0, 0]))].tolist() == dt._expand_token(first)[:8]
+    fallback = DynamicTokenizer()
+    t = "héllo héllo héllo héllo wörld"
+    assert fallback.decode(fallback.encode(t).input_ids) == t
+
+
+# ------------------------------------------------------------------------------------------------ export
+def test_safetensors_io_and_hf_bundle(tmp_path):
+    from triune_b200.export import export_model, export_to_huggingface, load_file, load_from_huggingface, save_file
+
+    t = {"a": torch.randn(3, 5).bfloat16(), "b": torch.arange(7), "s": torch.tensor(3), "e": torch.empty(0, 3)}
+    save_file(t, str(tmp_path / "x.safetensors"), {"format": "pt"})
+    back = load_file(str(tmp_path / "x.safetensors"))
+    assert all(torch.equal(back[k], t[k]) for k in t)
+    st = pytest.importorskip("safetensors.torch")
+    assert all(torch.equal(v, t[k]) for k, v in st.load_file(str(tmp_path / "x.safetensors")).items())
+    m = tiny().eval()
+    d = export_to_huggingface(m, tmp_path / "hf")
+    assert {"config.json", "generation_config.json", "configuration_triune.py", "modeling_triune.py", "model.safetensors"} <= set(os.listdir(d))
+    keys = set(load_file(str(d / "model.safetensors")))
+    assert "transformer.layers.0.attn.gla.q_proj.weight" in keys and "transformer.layers.3.ffn.experts.0.0.weight" in keys
+    assert "transformer.final_head.weight" in keys and "transformer.token_embed.weight" in keys  # tied tensors stored twice
+    m2 = load_from_huggingface(d)
+    x = torch.randint(0, 256, (2, 12))
+    assert torch.equal(m(x, force_depth=2)[0], m2(x, force_depth=2)[0])
+    with pytest.raises(NotImplementedError):
+        export_model(m, tmp_path / "m.gguf", "gguf")
+    with pytest.raises(ValueError):
+        export_model(m, tmp_path / "l.safetensors", "lora")
+
+
+# ------------------------------------------------------------------------------------------------ runtime services
+@pytest.mark.parametrize("kw,min_cos", [({}, 0.99999), ({"use_fp8": True}, 0.995), ({"use_fp4": True}, 0.97)])
+def test_parameter_stager_roundtrip(kw, min_cos):
+    from triune_b200.runtime.staging import ParameterStager
+
+    torch.manual_seed(0)
+    ref_layer = nn.Sequential(nn.Linear(512, 256), nn.BatchNorm1d(256), nn.Linear(256, 64))
+    layer = nn.Sequential(nn.Linear(512, 256), nn.BatchNorm1d(256), nn.Linear(256, 64))
+    layer.load_state_dict(ref_layer.state_dict())
+    x = torch.randn(8, 512)
+    want = ref_layer(x)
+    st = ParameterStager("cpu", min_quant_numel=1000, **kw)
+    st.register_module(layer)
+    st.stage_layer(layer)
+    y = layer(x)
+    assert torch.nn.functional.cosine_similarity(y.flatten(), want.flatten(), dim=0) > min_cos
+    st.release_layer(layer, clear_snapshot=True)
+    s = st.get_memory_summary()
+    assert s["gpu_bytes"] == 0 and s["h2d_bytes_transferred"] == s["transfer_bytes_per_pass"]
+    assert (s["transfer_bytes_per_pass"] < 0.5 * s["cpu_master_bytes"]) == bool(kw)
+    assert torch.allclose(layer[1].running_mean, ref_layer[1].running_mean, atol=5e-2) and layer[1].running_mean.abs().sum() > 0  # written back
+    assert torch.equal(layer[0].weight, ref_layer[0].weight)  # masters untouched by compressed staging
+
+
+def test_memory_planner_and_resource_manager():
+    from triune_b200.config import get_model_config
+    from triune_b200.runtime.memory_planner import MemoryPlanner
+    from triune_b200.runtime.resource_manager import DynamicResourceManager, HardwareProfile, VRAMBudgetExceededError
+
+    small = MemoryPlanner.estimate_vram({**get_model_config("bench-90m").to_dict(), "batch_size": 16, "seq_len": 2048}, available_vram_gb=180)
+    assert small.fits and small.recommended_mode == "resident" and small.total_params == 99_663_531
+    big = MemoryPlanner.estimate_vram({**get_model_config("triune-70b").to_dict(), "batch_size": 16, "seq_len": 2048}, available_vram_gb=180)
+    assert not big.fits and big.recommended_mode in ("layer_streaming", "disk_streaming")
+    hf = MemoryPlanner.estimate_hf_model({"hidden_size": 4096, "num_hidden_layers": 32, "vocab_size": 128256, "intermediate_size": 14336,
+                                          "num_attention_heads": 32, "num_key_value_heads": 8}, available_vram_gb=180)
+    assert abs(hf["total_params"] - 8.03e9) < 0.05e9 and hf["fits"]
+    hw = HardwareProfile("B200", 180, 178, 2, (10, 0), True, True, False, 148, 8)
+    cfg = {**get_model_config("triune-7b").to_dict(), "batch_size": 16, "seq_len": 2048}
+    a = DynamicResourceManager.assess_feasibility(cfg, hardware=hw)
+    assert not a.is_feasible and a.suggested_batch_size * a.suggested_grad_accum >= 16
+    with pytest.raises(VRAMBudgetExceededError):
+        DynamicResourceManager.validate_and_allot(cfg, hardware=hw)
+    assert DynamicResourceManager.validate_and_allot(cfg, hardware=hw, force=True).forced_override
+    plan = DynamicResourceManager.validate_and_allot(cfg, hardware=hw, auto_fit=True)
+    assert plan.auto_fitted and plan.batch_size == a.suggested_batch_size
+
+
+def test_session_state_manager_lru_ttl_and_queue():
+    import time
+
+    from triune_b200.serve.srsm import ServingRequestQueue, SessionRecurrentStateManager
+
+    m = SessionRecurrentStateManager(max_active_sessions=2, session_ttl_seconds=0.3)
+    c = [(torch.randn(2, 3, 4, 4), 7), (None, 7), (torch.randn(2, 3, 4, 4), 7)]
+    m.update_session_cache("a", c, depth=2)
+    got, depth = m.get_session_cache("a", "cpu")
+    assert depth == 2 and torch.equal(got[0][0], c[0][0]) and got[1] == (None, 7) and got[2][1] == 7
+    got[0][0].zero_()  # a caller mutating its copy must not corrupt the parked state
+    assert torch.equal(m.get_session_cache("a", "cpu")[0][0][0], c[0][0])
+    m.update_session_cache("b", c)
+    m.update_session_cache("c", c)
+    assert m.get_session_cache("a", "cpu") is None and m.stats()["active_sessions"] == 2
+    time.sleep(0.35)
+    assert m.get_session_cache("c", "cpu") is None
+    q = ServingRequestQueue(1)
+    ev = q.register_request("r")
+    assert q.acquire(0.05) and not q.acquire(0.05) and q.cancel_request("r") and ev.is_set() and not q.cancel_request("zz")
+
+
+def test_callbacks_events_and_loggers(tmp_path):
+    from triune_b200.callbacks import Callback, CallbackList, EventEmitter, TelemetryCallback
+    from triune_b200.trainer.logger import JsonlLogger, NullLogger
+
+    class Count(Callback):
+        n = 0
+
+        def on_step_end(self, trainer, step, logs):
+            Count.n += 1
+
+    tel = TelemetryCallback()
+    cl = CallbackList([Count(), tel])
+    cl.on_train_begin(None)
+    cl.on_step_end(type("T", (), {"device": None})(), 3, {"loss": torch.tensor(1.5)})
+    assert Count.n == 1 and tel.history[0]["loss"] == 1.5 and tel.history[0]["step"] == 3
+    em, got = EventEmitter(), []
+    em.on("on_loss_update", got.append)
+    em.on("on_loss_update", lambda p: 1 / 0)  # a failing listener is isolated
+    em.emit_loss_update(1, 2.0)
+    assert got[0]["loss"] == 2.0 and "timestamp" in got[0]
+    lg = JsonlLogger(tmp_path / "run.jsonl", config={"lr": 1e-3})
+    lg.log({"loss": torch.tensor(0.5)}, step=4)
+    lg.finish()
+    lines = [json.loads(l) for l in (tmp_path / "run.jsonl").read_text().splitlines()]
+    assert lines[0]["config"]["lr"] == 1e-3 and lines[1] == {**lines[1], "step": 4, "loss": 0.5}
+    assert NullLogger().log({}, step=0) is None
+
+
+def test_sandbox_validation_and_limits():
+    from triune_b200.runtime.sandbox import PythonSandbox
+
+    sb = PythonSandbox(timeout=5)
+    ok = sb.execute_code("import math\nresult = math.sqrt(x) + 1\nprint('hi')", {"x": 16})
+    assert ok["success"] and ok["result"] == 5.0 and ok["stdout"] == "hi\n"
+    for bad in ("import os", "open('/etc/passwd')", "().__class__", "from subprocess import run", "eval('1')"):
+        assert not sb.execute_code(bad)["success"]
+    assert sb.execute_code("while True: pass")["timed_out"]
+    assert "ZeroDivisionError" in sb.execute_code("result = 1/0")["error"]

@@ -236,17 +236,19 @@ def load_model(model_name_or_path, **kwargs: Any) -> nn.Module:
         return build_model(build_config({**json.loads(path.read_text(encoding="utf-8")), **kwargs}))
     if path.is_file():
         ck = _load_state(path)
-        cfg = build_config({**(ck.get("config") or {}), **kwargs}) if isinstance(ck, dict) else build_config(kwargs)
+        saved = (ck.get("config") or {}) if isinstance(ck, dict) else {}
         sd = ck["model_state"] if isinstance(ck, dict) and "model_state" in ck else ck
         sd = {k.removeprefix("_orig_mod."): v for k, v in sd.items()}
-        try:
-            model = build_model(cfg)
-            model.load_state_dict(sd)
-        except Exception:  # config missing or stale: recover the architecture from the tensors themselves
-            from ..inference import load_checkpoint_model
+        if all(k in saved for k in ("hidden_dim", "num_layers", "num_heads")):
+            try:
+                model = build_model(build_config({**saved, **kwargs}))
+                model.load_state_dict(sd)
+                return model
+            except Exception:
+                pass  # stale or partial config: fall through and read the architecture off the tensors
+        from ..inference import load_checkpoint_model
 
-            model = load_checkpoint_model(str(path))[0]
-        return model
+        return load_checkpoint_model(str(path))[0]
     if name in MODEL_REGISTRY:
         return MODEL_REGISTRY[name](**kwargs)
     if name in CANONICAL_MODEL_SPECS or name in LEGACY_PRESET_ALIASES:
@@ -260,6 +262,8 @@ def load_model(model_name_or_path, **kwargs: Any) -> nn.Module:
     if name in ("default", "none", ""):
         return build_model(build_config(kwargs))
     try:
+        if not (path.is_dir() or "/" in str(model_name_or_path)):
+            raise FileNotFoundError("not a local directory and not an 'org/name' hub id")
         from transformers import AutoModelForCausalLM
 
         return AutoModelForCausalLM.from_pretrained(str(model_name_or_path), **kwargs)

@@ -101,7 +101,7 @@ class StagingBuffer:
         self.forward_snapshot = None
 
     def release_gpu(self, clear_snapshot: bool = False, keep_snapshot_on_param: bool = False) -> None:
-        if self.is_buffer and not self.read_only and not clear_snapshot and self.gpu_tensor is not None:
+        if self.is_buffer and not self.read_only and self.gpu_tensor is not None:
             self.wait()
             self.cpu_master.copy_(self.gpu_tensor.to(self.cpu_master.dtype))  # running statistics etc. must survive
         self.gpu_tensor, self.event = None, None
