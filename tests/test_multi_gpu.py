@@ -14,12 +14,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _launch(nproc, env_extra):
+def _launch(nproc, env_extra, worker="mp_fused_dp_worker.py", port="29613"):
     env = dict(os.environ)
     env.update(env_extra)
     env.setdefault("NCCL_NVLS_ENABLE", "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "mp_fused_dp_worker.py")]
+           "127.0.0.1", "--master-port", port, os.path.join(ROOT, "tests", worker)]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     # ranks share one pipe, so two RESULT records can land on one line: decode every occurrence separately
     dec, res = json.JSONDecoder(), []
@@ -42,3 +42,19 @@ def test_fused_dp_matches_nccl_baseline(multimem):
         assert r["metric_ok"]
         assert r["timeout_status"] == 4 and r["context_alive"]
         assert abs(r["loss_ref"][-1] - r["loss_fused"][-1]) < 0.1
+
+
+def test_tensor_parallel_fused_gemms():
+    """All-gather GEMM and GEMM reduce-scatter with the collective inside the kernel, against fp32 PyTorch and NCCL."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _launch(2, {}, worker="mp_tp_worker.py", port="29617")
+    for r in res:
+        for mode in ("fused", "nccl"):
+            assert r[f"{mode}_status"] == 0
+            assert r[f"{mode}_gather_ok"]
+            assert r[f"{mode}_ag_err"] < 2e-2 and r[f"{mode}_rs_err"] < 2e-2, r
+            assert r[f"{mode}_mod_fwd"] < 3e-2 and r[f"{mode}_mod_dx"] < 3e-2, r
+            assert r[f"{mode}_mod_dw1"] < 3e-2 and r[f"{mode}_mod_dw2"] < 3e-2, r
+        assert r["fused_status_after_bench"] == 0
