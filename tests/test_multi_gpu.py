@@ -58,3 +58,17 @@ def test_tensor_parallel_fused_gemms():
             assert r[f"{mode}_mod_fwd"] < 3e-2 and r[f"{mode}_mod_dx"] < 3e-2, r
             assert r[f"{mode}_mod_dw1"] < 3e-2 and r[f"{mode}_mod_dw2"] < 3e-2, r
         assert r["fused_status_after_bench"] == 0
+
+
+def test_expert_parallel_dispatch_combine():
+    """Expert parallelism over NVLink peer stores: forward, all gradients, and capacity overflow."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _launch(2, {}, worker="mp_ep_worker.py", port="29619")
+    for r in res:
+        assert r["fused_status"] == 0 and r["nccl_status"] == 0 and r["overflow_status"] == 0
+        assert r["fused_fwd"] < 3e-2 and r["nccl_fwd"] < 3e-2, r
+        for k in ("dx", "dwts", "dw1", "db1", "dw2", "db2"):
+            assert r[k] < 4e-2, (k, r)
+        assert r["overflow_finite"] and r["overflow_dropped"] > 0

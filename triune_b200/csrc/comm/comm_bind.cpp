@@ -136,25 +136,25 @@ void allgather_gemm(const Tensor& a_full, const Tensor& b, bool b_mn, Tensor& c,
   f.b_mn_major = b_mn; f.out_f32 = c.scalar_type() == at::kFloat; f.groups = 1;
   f.rank = (int)rank; f.world = (int)world; f.peer_bufs = reinterpret_cast<const uint64_t*>(bufs_dev);
   f.C = c.data_ptr(); f.ldc = c.stride(0); f.a_off = a_off; f.rows_per_src = (int)rows_per_src;
-  TORCH_CHECK(chunk_flags.numel() >= (f.M + 127) / 128, "chunk_flags too small");
+  TORCH_CHECK(chunk_flags.numel() >= 4 * ((f.M + 127) / 128), "chunk_flags too small (4 per 128 rows)");
   f.chunk_flags = reinterpret_cast<uint32_t*>(chunk_flags.data_ptr<int>()); f.epoch = (uint32_t)epoch;
   f.status = status_ptr(status);
   tb::launch_fused_gemm(f, cur_stream());
 }
 
-void gemm_scatter_rows(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& row_scale,
+void gemm_scatter_rows(const Tensor& a, const Tensor& b, bool b_mn, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& row_scale,
                        const Tensor& tile_group, const Tensor& row_dst, int64_t slots_per_rank, int64_t rank, int64_t world,
                        int64_t bufs_dev, int64_t out_off, int64_t out_ld, const c10::optional<Tensor>& status) {
   TORCH_CHECK(a.is_cuda() && a.dim() == 2 && a.scalar_type() == at::kBFloat16 && a.stride(1) == 1, "A: bf16 [M,K] row-major");
-  TORCH_CHECK(b.dim() == 3 && b.is_contiguous() && b.scalar_type() == at::kBFloat16, "B: contiguous bf16 [groups, N, K]");
+  TORCH_CHECK(b.dim() == 3 && b.is_contiguous() && b.scalar_type() == at::kBFloat16, "B: contiguous bf16 [groups, N, K] ([groups, K, N] when b_mn)");
   c10::cuda::CUDAGuard g(a.device());
   tb::FusedGemmArgs f{};
   f.mode = tb::FG_SCATTER_ROWS;
   f.A = bfp(a); f.B = bfp(b);
-  f.M = (int)a.size(0); f.K = (int)a.size(1); f.N = (int)b.size(1);
-  TORCH_CHECK(b.size(2) == f.K, "K mismatch");
+  f.M = (int)a.size(0); f.K = (int)a.size(1); f.N = (int)(b_mn ? b.size(2) : b.size(1));
+  TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == f.K, "K mismatch");
   f.lda = a.stride(0); f.ldb = b.stride(1); f.strideB = b.stride(0); f.groups = (int)b.size(0);
-  f.b_mn_major = false; f.out_f32 = false;
+  f.b_mn_major = b_mn; f.out_f32 = false;
   f.rank = (int)rank; f.world = (int)world; f.peer_bufs = reinterpret_cast<const uint64_t*>(bufs_dev);
   f.tile_group = tile_group.data_ptr<int>(); f.row_dst = row_dst.data_ptr<int>(); f.slots_per_rank = (int)slots_per_rank;
   f.out_off = out_off; f.out_ld = out_ld;
@@ -180,6 +180,14 @@ void ep_build_tiles(const Tensor& counts_all, int64_t experts_per_rank, int64_t 
   tb::launch_ep_build_tiles(counts_all.data_ptr<int>(), (int)experts_per_rank, (int)world, (int)cap, tile_group.data_ptr<int>(),
                             row_dst.data_ptr<int>(), cur_stream());
 }
+
+void ep_zero_invalid_rows(Tensor& buf, const Tensor& counts_all, int64_t experts_per_rank, int64_t world, int64_t cap) {
+  TORCH_CHECK(buf.is_cuda() && buf.dim() == 2 && buf.is_contiguous() && buf.scalar_type() == at::kBFloat16, "buf: contiguous bf16 [rows, d]");
+  TORCH_CHECK(buf.size(0) == experts_per_rank * world * cap, "buf rows must be experts_per_rank * world * cap");
+  c10::cuda::CUDAGuard g(buf.device());
+  tb::launch_ep_zero_invalid_rows(reinterpret_cast<__nv_bfloat16*>(buf.data_ptr()), (int)buf.size(1), counts_all.data_ptr<int>(),
+                                  (int)experts_per_rank, (int)world, (int)cap, cur_stream());
+}
 }  // namespace
 
 void register_comm(pybind11::module& m) {
@@ -202,6 +210,7 @@ void register_comm(pybind11::module& m) {
   m.def("allgather_gemm", &allgather_gemm, "GEMM over row-sharded A; remote shards are fetched by in-kernel copy warps");
   m.def("gemm_scatter_rows", &gemm_scatter_rows, "grouped expert GEMM storing each output row into its token owner's buffer");
   m.def("ep_dispatch", &ep_dispatch, "token rows -> expert-major buffers on the expert owners (peer stores)");
+  m.def("ep_zero_invalid_rows", &ep_zero_invalid_rows, "zero the rows of an expert-major buffer beyond each segment's count");
   m.def("ep_build_tiles", &ep_build_tiles, "tile list and row validity of the expert owner from the received counts");
   m.def("metric_allreduce", &metric_allreduce);
 }

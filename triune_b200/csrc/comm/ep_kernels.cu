@@ -60,7 +60,32 @@ __global__ void __launch_bounds__(256) ep_build_tiles_kernel(const int* __restri
   }
 }
 
+// Zero every row of the expert-major buffer that holds no token this step (position >= count of its segment), so
+// the weight-gradient GEMMs can run over whole expert ranges. One warp per row.
+__global__ void __launch_bounds__(256) ep_zero_invalid_rows_kernel(__nv_bfloat16* __restrict__ buf, int d,
+                                                                   const int* __restrict__ counts_all, int experts_per_rank,
+                                                                   int world, int cap) {
+  const long long total_rows = (long long)experts_per_rank * world * cap;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp; r < total_rows; r += nwarps) {
+    const int seg = (int)(r / cap), p = (int)(r % cap);
+    if (p < counts_all[(seg % world) * experts_per_rank + seg / world]) continue;
+    uint4* row = reinterpret_cast<uint4*>(buf + r * d);
+    for (int j = lane; j < d / 8; j += 32) row[j] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 }  // namespace
+
+void launch_ep_zero_invalid_rows(__nv_bfloat16* buf, int d, const int* counts_all, int experts_per_rank, int world, int cap,
+                                 cudaStream_t s) {
+  if (d % 8 != 0) throw std::runtime_error("ep_zero_invalid_rows: d must be a multiple of 8");
+  ep_zero_invalid_rows_kernel<<<148 * 8, 256, 0, s>>>(buf, d, counts_all, experts_per_rank, world, cap);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("ep_zero_invalid_rows launch failed: ") + cudaGetErrorString(e));
+}
 
 void launch_ep_dispatch(const __nv_bfloat16* x, int d, const int* idx, const int* pos, int n_assign, int top_k, int experts_per_rank,
                         int cap, int rank, int world, const uint64_t* peer_bufs, long long in_off, long long dst_off,

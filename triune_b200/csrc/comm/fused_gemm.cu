@@ -32,6 +32,7 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_TILE = 32 * 128;
 constexpr unsigned long long FLAG_WAIT_NS = 2000000000ull;
+constexpr int FETCH_PARTS = 4;  // a 128-row chunk is fetched as four 32-row parts, each with its own flag
 
 template <int BN>
 struct Cfg {
@@ -163,13 +164,15 @@ __global__ void __launch_bounds__(MODE == FG_ALL_GATHER ? 320 : 192, 1)
         if (MODE == FG_ALL_GATHER && (m0 / p.rows_per_src) != p.rank) {
           // rows of a remote shard: wait until the fetch warps of some CTA have landed this chunk locally
           const unsigned long long t0 = globaltimer_ns();
-          while ((int)(ld_acquire_gpu(p.chunk_flags + tl.m_idx) - p.epoch) < 0) {
-            if (globaltimer_ns() - t0 > FLAG_WAIT_NS) {
-              report(p, 5);
-              ok = false;
-              break;
+          for (int part = 0; part < FETCH_PARTS && ok; ++part) {
+            while ((int)(ld_acquire_gpu(p.chunk_flags + tl.m_idx * FETCH_PARTS + part) - p.epoch) < 0) {
+              if (globaltimer_ns() - t0 > FLAG_WAIT_NS) {
+                report(p, 5);
+                ok = false;
+                break;
+              }
+              __nanosleep(128);
             }
-            __nanosleep(128);
           }
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores of the fetch warps -> TMA reads
@@ -379,28 +382,31 @@ __global__ void __launch_bounds__(MODE == FG_ALL_GATHER ? 320 : 192, 1)
     // ---------------------------------------------------------------- fetch warps (6..9): remote shards -> local buffer
     const int ft = threadIdx.x - 192;                      // 0..127
     const long long row_bytes = (long long)p.K * 2;         // gathered A is [M, K] bf16, dense
-    const long long chunk_bytes = row_bytes * BM;
+    const long long part_bytes = row_bytes * (BM / FETCH_PARTS);
     uint8_t* local = reinterpret_cast<uint8_t*>(p.peer_bufs[p.rank]) + p.a_off;
-    for (int i = blockIdx.x; i < p.num_m; i += gridDim.x) {
-      const int chunk = (i + p.m_rotate) % p.num_m;        // same visiting order as the tiles
+    // Work item = a quarter of a 128-row chunk (32 rows), visited in the order in which the tiles need the chunks, so
+    // one chunk is pulled by four CTAs at once and the first remote chunks land early.
+    const int items = p.num_m * FETCH_PARTS;
+    for (int i = blockIdx.x; i < items; i += gridDim.x) {
+      const int chunk = (i / FETCH_PARTS + p.m_rotate) % p.num_m, part = i % FETCH_PARTS;
       const int src = (chunk * BM) / p.rows_per_src;
       if (src == p.rank) continue;
-      const uint8_t* remote = reinterpret_cast<const uint8_t*>(p.peer_bufs[src]) + p.a_off + (long long)chunk * chunk_bytes;
-      uint8_t* dst = local + (long long)chunk * chunk_bytes;
-      const long long n16 = chunk_bytes >> 4;
+      const long long off = ((long long)chunk * FETCH_PARTS + part) * part_bytes;
+      const uint8_t* remote = reinterpret_cast<const uint8_t*>(p.peer_bufs[src]) + p.a_off + off;
+      uint8_t* dst = local + off;
+      const long long n16 = part_bytes >> 4;
       long long j = ft;
-      for (; j + 3 * 128 < n16; j += 4 * 128) {  // four loads in flight per thread
-        const uint4 a = ld_peer_16B(remote + (j << 4)), b = ld_peer_16B(remote + ((j + 128) << 4));
-        const uint4 c = ld_peer_16B(remote + ((j + 256) << 4)), d = ld_peer_16B(remote + ((j + 384) << 4));
-        *reinterpret_cast<uint4*>(dst + (j << 4)) = a;
-        *reinterpret_cast<uint4*>(dst + ((j + 128) << 4)) = b;
-        *reinterpret_cast<uint4*>(dst + ((j + 256) << 4)) = c;
-        *reinterpret_cast<uint4*>(dst + ((j + 384) << 4)) = d;
+      for (; j + 7 * 128 < n16; j += 8 * 128) {  // eight 16-byte loads in flight per thread
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ld_peer_16B(remote + ((j + u * 128) << 4));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst + ((j + u * 128) << 4)) = v[u];
       }
       for (; j < n16; j += 128) *reinterpret_cast<uint4*>(dst + (j << 4)) = ld_peer_16B(remote + (j << 4));
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ft == 0) st_release_gpu(p.chunk_flags + chunk, p.epoch);
+      if (ft == 0) st_release_gpu(p.chunk_flags + chunk * FETCH_PARTS + part, p.epoch);
     }
   }
 

@@ -30,7 +30,7 @@ struct FusedGemmArgs {
   long long ldc;
   long long a_off;
   int rows_per_src;
-  uint32_t* chunk_flags;  // [M / 128] local flags, monotonically increasing epochs
+  uint32_t* chunk_flags;  // [4 * M / 128] local flags (one per 32-row part), monotonically increasing epochs
   uint32_t epoch;
   // scatter rows
   const int* tile_group;  // [ceil(M/128)] expert of each row tile, -1 = skip
@@ -62,5 +62,9 @@ void launch_ep_dispatch(const __nv_bfloat16* x, int d, const int* idx, const int
 // invalidates (row_dst = -1) the rows of every segment beyond its count.
 void launch_ep_build_tiles(const int* counts_all /* [world][experts_per_rank] */, int experts_per_rank, int world, int cap,
                            int* tile_group, int* row_dst, cudaStream_t s);
+
+// Zeroes the rows of an expert-major buffer [experts_per_rank][world][cap][d] beyond each segment's count.
+void launch_ep_zero_invalid_rows(__nv_bfloat16* buf, int d, const int* counts_all, int experts_per_rank, int world, int cap,
+                                 cudaStream_t s);
 
 }  // namespace tb

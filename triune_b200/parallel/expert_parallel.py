@@ -1,0 +1,232 @@
+"""Expert parallelism: experts are split over the group; tokens travel to their experts and back over NVLink.
+
+The reference keeps every expert on one device (``MoE_FFN``, ``triune/model/moe.py:64-73``) and has no all-to-all. Here
+``E`` experts are partitioned ``E / ep`` per rank and the two all-to-alls are done by kernels through peer memory:
+
+  dispatch   ``ep_dispatch``: every (token, choice) row is stored straight into the owner's expert-major input buffer
+             (segment = (local expert, source rank), fixed capacity per segment so no size exchange is needed for
+             addressing), together with the slot its result must return to and the per-expert counts;
+  experts    grouped GEMM-1 (+bias, GELU) over the valid 128-row tiles of the received segments;
+  combine    ``gemm_scatter_rows``: grouped GEMM-2 whose epilogue adds the bias and stores every output row into the
+             token owner's receive buffer; the owner then sums its k rows with the routing weights.
+
+The backward pass is the same machinery run in reverse (gradient rows are dispatched to the experts, the data-gradient
+GEMM scatters rows back), with expert weight gradients as local grouped-by-reduction GEMMs.
+``mode="nccl"`` does the two all-to-alls with ``all_to_all_single`` around the single-GPU expert kernels: the baseline.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import _ext, ops
+from ..ops import GEMM_GROUPED_K, GEMM_GROUPED_M, gemm
+from .symm import SymmetricBuffer
+
+CH_DISPATCH, CH_COMBINE = 3, 4
+
+
+class EPContext:
+    def __init__(self, num_experts: int, group=None, device=None, capacity_factor: float = 1.5, mode: str = "fused"):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        assert num_experts % self.world == 0, "experts must divide evenly over the expert-parallel group"
+        self.num_experts, self.experts_per_rank = num_experts, num_experts // self.world
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.capacity_factor, self.mode = capacity_factor, mode
+        self._bufs: Dict[Tuple, SymmetricBuffer] = {}
+        self._epochs: Dict[Tuple, int] = {}
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.comm_bytes = 0
+
+    def capacity(self, n_assign: int) -> int:
+        """Rows reserved per (expert, source rank) segment: capacity_factor x the mean load, rounded up to 128."""
+        return max(128, int(math.ceil(self.capacity_factor * n_assign / self.num_experts / 128.0)) * 128)
+
+    def workspace(self, n_assign: int, d: int) -> Tuple[SymmetricBuffer, int]:
+        cap = self.capacity(n_assign)
+        key = (n_assign, d, cap)
+        if key not in self._bufs:  # collective allocation: same sequence of shapes on every rank
+            rows = self.experts_per_rank * self.world * cap
+            self._bufs[key] = SymmetricBuffer({"xin": rows * d * 2, "dst": rows * 4, "cnt": self.world * self.experts_per_rank * 4,
+                                               "recv": n_assign * d * 2}, self.device, self.group, use_multimem=False)
+        return self._bufs[key], cap
+
+    def barrier(self, buf: SymmetricBuffer, channel: int) -> None:
+        k = (id(buf), channel)
+        self._epochs[k] = self._epochs.get(k, 0) + 1
+        _ext.ext().comm_barrier(buf.rank, buf.world, buf.bufs_dev, buf.signals_dev, channel, self._epochs[k], self.status)
+        ops._tick()
+
+    def check(self) -> int:
+        return int(self.status.item())
+
+
+def _positions(idx_flat: torch.Tensor, num_experts: int):
+    """Position of every assignment among this rank's assignments to the same expert (in assignment order), and the
+    per-expert counts. No host synchronisation."""
+    onehot = idx_flat.view(-1, 1) == torch.arange(num_experts, device=idx_flat.device, dtype=idx_flat.dtype).view(1, -1)
+    csum = onehot.to(torch.int32).cumsum(0, dtype=torch.int32)
+    pos = (csum.gather(1, idx_flat.clamp_min(0).long().view(-1, 1)).view(-1) - 1).to(torch.int32)
+    pos = torch.where(idx_flat >= 0, pos, torch.full_like(pos, -1))
+    return pos.contiguous(), csum[-1].contiguous()
+
+
+class _EPExpertsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, idx, wts, w1, b1, w2, b2, ep: EPContext):
+        e = _ext.ext()
+        T, d = x.shape
+        K = idx.shape[1]
+        A = T * K
+        El, W = ep.experts_per_rank, ep.world
+        buf, cap = ep.workspace(A, d)
+        rows = El * W * cap
+        idx_flat = idx.reshape(-1).to(torch.int32).contiguous()
+        pos, counts = _positions(idx_flat, ep.num_experts)
+        xin = buf.view("xin", torch.bfloat16, rows * d).view(rows, d)
+        row_dst = buf.view("dst", torch.int32, rows)
+        cnt_all = buf.view("cnt", torch.int32, W * El)
+        recv = buf.view("recv", torch.bfloat16, A * d).view(A, d)
+        e.ep_dispatch(x.contiguous(), idx_flat, pos, K, El, cap, buf.rank, W, buf.bufs_dev, buf.offset("xin"), buf.offset("dst"),
+                      buf.offset("cnt"), counts, A)
+        ep.barrier(buf, CH_DISPATCH)
+        tile_group = torch.empty(rows // 128, dtype=torch.int32, device=x.device)
+        e.ep_build_tiles(cnt_all, El, W, cap, tile_group, row_dst)
+        e.ep_zero_invalid_rows(xin, cnt_all, El, W, cap)
+        H = w1.shape[1]
+        pre = torch.zeros(rows, H, dtype=x.dtype, device=x.device)  # rows of skipped tiles must stay finite (they meet
+        h = torch.zeros(rows, H, dtype=x.dtype, device=x.device)    # zero rows in the weight-gradient GEMMs)
+        gemm(xin, w1, h, bias=b1, gelu=True, aux_out=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        e.gemm_scatter_rows(h, w2, False, b2, None, tile_group, row_dst, A, buf.rank, W, buf.bufs_dev, buf.offset("recv"), d, ep.status)
+        ops._tick(5)
+        ep.barrier(buf, CH_COMBINE)
+        keep = (pos >= 0) & (pos < cap)
+        slot = torch.where(keep, torch.arange(A, device=x.device, dtype=torch.int32), torch.full_like(pos, -1)).view(T, K).contiguous()
+        wk = wts.float().contiguous()
+        out = e.combine_rows(recv, slot, wk, None, 0.0)
+        ops._tick()
+        ctx.ep, ctx.cap, ctx.buf = ep, cap, buf
+        ctx.save_for_backward(xin.clone(), pre, h, tile_group, row_dst.clone(), cnt_all.clone(), idx_flat, pos, counts, slot, wk,
+                              recv.clone(), w1, b1, w2, b2)
+        ep.comm_bytes += 2 * A * d * 2
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (xin, pre, h, tile_group, row_dst, cnt_all, idx_flat, pos, counts, slot, wk, recv, w1, b1, w2, b2) = ctx.saved_tensors
+        ep, cap, buf = ctx.ep, ctx.cap, ctx.buf
+        e = _ext.ext()
+        dout = dout.contiguous()
+        T, d = dout.shape
+        K = slot.shape[1]
+        A = T * K
+        El, W = ep.experts_per_rank, ep.world
+        rows = El * W * cap
+        dw = e.row_dots(dout, recv, slot)  # d loss / d routing weight
+        src_tok = (torch.arange(A, device=dout.device, dtype=torch.int32) // K).contiguous()
+        drows = e.gather_rows(dout, src_tok, (wk.view(-1) * (slot.view(-1) >= 0)).contiguous())  # w[a] * dout[t(a)]
+        dyin = buf.view("xin", torch.bfloat16, rows * d).view(rows, d)  # the forward copy of this region was saved
+        live_dst = buf.view("dst", torch.int32, rows)
+        e.ep_dispatch(drows, idx_flat, pos, 1, El, cap, buf.rank, W, buf.bufs_dev, buf.offset("xin"), buf.offset("dst"),
+                      buf.offset("cnt"), counts, A)
+        ep.barrier(buf, CH_DISPATCH)
+        e.ep_zero_invalid_rows(dyin, cnt_all, El, W, cap)
+        live_dst.copy_(row_dst)  # same routing as the forward, including the rows invalidated there
+        H = w1.shape[1]
+        dpre = torch.zeros(rows, H, dtype=dout.dtype, device=dout.device)
+        gemm(dyin, w2, dpre, b_mn=True, dgelu_aux=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        offs = (torch.arange(El + 1, device=dout.device, dtype=torch.int32) * (W * cap)).contiguous()
+        ones = torch.ones(rows, 8, device=dout.device, dtype=dout.dtype)
+
+        def wgrad(w, a, b):
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                gemm(a, b, mg, a_mn=True, b_mn=True, accumulate=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El)
+                return None
+            return gemm(a, b, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El)
+
+        def bgrad(bp, a):
+            s = gemm(ones, a, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El, out_dtype=torch.float32)[:, 0, :]
+            mg = getattr(bp, "main_grad", None)
+            if mg is not None:
+                mg.add_(s)
+                return None
+            return s.to(bp.dtype)
+
+        dyin_c = dyin.clone()  # the region is reused below by nobody, but the wgrad reads must not race a later layer
+        dw2, db2 = wgrad(w2, dyin_c, h), bgrad(b2, dyin_c)
+        dw1, db1 = wgrad(w1, dpre, xin), bgrad(b1, dpre)
+        e.gemm_scatter_rows(dpre, w1, True, None, None, tile_group, live_dst, A, buf.rank, W, buf.bufs_dev, buf.offset("recv"), d, ep.status)
+        ops._tick(8)
+        ep.barrier(buf, CH_COMBINE)
+        recv2 = buf.view("recv", torch.bfloat16, A * d).view(A, d)
+        dx = e.combine_rows(recv2, slot, torch.ones_like(wk), None, 0.0)
+        ep.comm_bytes += 2 * A * d * 2
+        return dx, None, dw.to(wk.dtype), dw1, db1, dw2, db2, None
+
+
+def _experts_nccl(x, idx, wts, w1, b1, w2, b2, ep: EPContext):
+    """Baseline: tokens sorted by destination rank, ``all_to_all_single`` there and back, local expert kernels."""
+    T, d = x.shape
+    K = idx.shape[1]
+    El, W = ep.experts_per_rank, ep.world
+    flat = idx.reshape(-1)
+    dest = (flat // El).clamp(0, W - 1)
+    order = torch.argsort(dest, stable=True)
+    send_counts = torch.bincount(dest, minlength=W)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=ep.group)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()  # host sync: part of what the fused path avoids
+    xs = x[(order // K)]
+    es = (flat[order] % El).to(torch.int64)
+    xr = torch.empty(sum(rc), d, dtype=x.dtype, device=x.device)
+    er = torch.empty(sum(rc), dtype=torch.int64, device=x.device)
+    dist.all_to_all_single(xr, xs.contiguous(), rc, sc, group=ep.group)
+    dist.all_to_all_single(er, es.contiguous(), rc, sc, group=ep.group)
+    yr = ops.moe_experts(xr, er.view(-1, 1), torch.ones(er.numel(), 1, device=x.device), None, w1, b1, w2, b2)
+    ys = torch.empty(A := T * K, d, dtype=x.dtype, device=x.device)
+    dist.all_to_all_single(ys, yr.contiguous(), sc, rc, group=ep.group)
+    y = torch.empty_like(ys)
+    y[order] = ys
+    return (y.view(T, K, d).float() * wts.float().unsqueeze(-1)).sum(1).to(x.dtype)
+
+
+def ep_experts(x, idx, wts, w1, b1, w2, b2, ep: EPContext):
+    """x [T, d] local tokens; idx / wts [T, k] global expert ids and routing weights; w1 [E/ep, H, d] ... local experts."""
+    if ep.world == 1:
+        return ops.moe_experts(x, idx, wts, None, w1, b1, w2, b2)
+    if ep.mode == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
+        return _EPExpertsFn.apply(x, idx, wts, w1, b1, w2, b2, ep)
+    return _experts_nccl(x, idx, wts, w1, b1, w2, b2, ep)
+
+
+class ExpertParallelMoE(nn.Module):
+    """MoE FFN whose routed experts are partitioned over the expert-parallel group; the router is replicated."""
+
+    def __init__(self, dim: int, hidden: int, num_experts: int, top_k: int, ep: EPContext, dtype=torch.bfloat16):
+        super().__init__()
+        self.dim, self.hidden, self.num_experts, self.top_k, self.ep = dim, hidden, num_experts, top_k, ep
+        El = ep.experts_per_rank
+        dev = ep.device
+        self.router = nn.Linear(dim, num_experts, device=dev, dtype=dtype)
+        self.register_buffer("expert_bias", torch.zeros(num_experts, device=dev, dtype=torch.float32))
+        self.w1 = nn.Parameter(torch.empty(El, hidden, dim, device=dev, dtype=dtype))
+        self.b1 = nn.Parameter(torch.zeros(El, hidden, device=dev, dtype=dtype))
+        self.w2 = nn.Parameter(torch.empty(El, dim, hidden, device=dev, dtype=dtype))
+        self.b2 = nn.Parameter(torch.zeros(El, dim, device=dev, dtype=dtype))
+        nn.init.normal_(self.w1, std=0.02)
+        nn.init.normal_(self.w2, std=0.02)
+        nn.init.normal_(self.router.weight, std=0.02)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, self.dim)
+        logits = self.router(x2).float()
+        idx, w, _ = ops.ref.moe_route(logits, self.expert_bias, self.top_k)
+        return ep_experts(x2, idx, w.to(torch.float32), self.w1, self.b1, self.w2, self.b2, self.ep).view(shape)

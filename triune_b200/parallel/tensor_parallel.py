@@ -79,7 +79,7 @@ def _ag_gemm_fused(ctx: TPContext, x_shard: torch.Tensor, w: torch.Tensor, b_mn:
     gathered = buf.view(region, torch.bfloat16, M * K).view(M, K)
     gathered[ctx.rank * rows : (ctx.rank + 1) * rows].copy_(x_shard)
     ctx.barrier(buf, CH_AG)  # every rank's own slot is written (and, transitively, call n-1 finished everywhere)
-    flags = ctx._flags.setdefault(id(buf), torch.zeros(max(1, M // 128), dtype=torch.int32, device=ctx.device))
+    flags = ctx._flags.setdefault(id(buf), torch.zeros(max(4, M // 32), dtype=torch.int32, device=ctx.device))
     y = torch.empty(M, N, dtype=torch.bfloat16, device=ctx.device)
     _ext.ext().allgather_gemm(gathered, w, b_mn, y, buf.rank, buf.world, buf.bufs_dev, buf.offset(region), rows, flags, n, ctx.status)
     ops._tick()
