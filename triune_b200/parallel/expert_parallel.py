@@ -103,6 +103,9 @@ class _EPExpertsFn(torch.autograd.Function):
         pre = torch.zeros(rows, H, dtype=x.dtype, device=x.device)  # rows of skipped tiles must stay finite (they meet
         h = torch.zeros(rows, H, dtype=x.dtype, device=x.device)    # zero rows in the weight-gradient GEMMs)
         gemm(xin, w1, h, bias=b1, gelu=True, aux_out=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        # Copies for the backward pass are taken BEFORE this rank signals the combine barrier: once a peer has passed
+        # that barrier it may start its next dispatch and overwrite these regions.
+        xin_saved, dst_saved, cnt_saved = xin.clone(), row_dst.clone(), cnt_all.clone()
         e.gemm_scatter_rows(h, w2, False, b2, None, tile_group, row_dst, A, buf.rank, W, buf.bufs_dev, buf.offset("recv"), d, ep.status)
         ops._tick(5)
         ep.barrier(buf, CH_COMBINE)
@@ -112,7 +115,7 @@ class _EPExpertsFn(torch.autograd.Function):
         out = e.combine_rows(recv, slot, wk, None, 0.0)
         ops._tick()
         ctx.ep, ctx.cap, ctx.buf = ep, cap, buf
-        ctx.save_for_backward(xin.clone(), pre, h, tile_group, row_dst.clone(), cnt_all.clone(), idx_flat, pos, counts, slot, wk,
+        ctx.save_for_backward(xin_saved, pre, h, tile_group, dst_saved, cnt_saved, idx_flat, pos, counts, slot, wk,
                               recv.clone(), w1, b1, w2, b2)
         ep.comm_bytes += 2 * A * d * 2
         return out
