@@ -382,3 +382,40 @@ def test_gla_layer_matches_reference_ops(dev):
     assert _rel(res[0][0], res[1][0]) < 3e-2
     assert _rel(res[0][1], res[1][1]) < 6e-2
     assert _rel(res[0][2], res[1][2]) < 6e-2
+
+
+@pytest.mark.parametrize("N,E,K,cap", [(4096, 8, 2, 700), (1000, 64, 2, None), (2048, 8, 1, 200), (512, 16, 4, 100)])
+def test_moe_route_plan_matches_oracle(N, E, K, cap):
+    """One-sort routing / capacity / plan kernels against the PyTorch composition."""
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(N + E)
+    logits = torch.randn(N, E, device="cuda") * 2
+    bias = torch.randn(E, device="cuda") * 0.1
+    temp = torch.tensor(0.7, device="cuda")
+    lg = logits.clone().requires_grad_(True)
+    idx, w, keep, (pos, row_src, tile_group, offsets, accepted) = ops.moe_route_plan(lg, bias, K, temp, cap)
+    lr = logits.clone().requires_grad_(True)
+    idx_r, w_r, _ = ref.moe_route(lr, bias, K, temp)
+    assert torch.equal(idx, idx_r)
+    assert torch.allclose(w, w_r, atol=1e-5, rtol=1e-4)
+    keep_r = ref.moe_capacity_mask(idx_r, w_r.detach(), E, cap) if cap is not None else torch.ones_like(idx, dtype=torch.bool)
+    # fast-math exp can flip the order of two nearly equal weights at the capacity boundary
+    assert (keep != keep_r).float().mean() < 2e-3
+    g = torch.randn_like(w)
+    (w * g).sum().backward()
+    (w_r * g).sum().backward()
+    assert torch.allclose(lg.grad, lr.grad, atol=2e-5, rtol=1e-3)
+    # plan invariants
+    kept = keep.reshape(-1)
+    p = pos.reshape(-1).long()
+    assert bool((p[kept] >= 0).all()) and bool((p[~kept] == -1).all())
+    assert p[kept].unique().numel() == int(kept.sum())
+    tok = torch.arange(N, device="cuda").repeat_interleave(K)
+    assert torch.equal(row_src.long()[p[kept]], tok[kept])
+    assert int((row_src >= 0).sum()) == int(kept.sum())
+    assert torch.equal(tile_group.long()[p[kept] // 128], idx.reshape(-1)[kept])
+    cnt = torch.zeros(E, device="cuda", dtype=torch.int64).scatter_add_(0, idx.reshape(-1)[kept], torch.ones_like(p[kept]))
+    assert torch.equal(accepted, cnt)
+    padded = (cnt + 127) // 128 * 128
+    assert torch.equal(offsets.long(), torch.cat((padded.new_zeros(1), padded.cumsum(0))))

@@ -225,6 +225,53 @@ Tensor row_dots(const Tensor& a, const Tensor& b, const Tensor& pos) {
   return dots;
 }
 
+std::vector<Tensor> moe_route_topk(const Tensor& logits, const Tensor& bias, const c10::optional<Tensor>& temperature,
+                                   double temp_value, int64_t K) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kFloat, "logits: contiguous fp32 [N, E]");
+  TORCH_CHECK(bias.scalar_type() == at::kFloat && bias.is_contiguous() && bias.numel() == logits.size(1), "bias: fp32 [E]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t N = logits.size(0), E = logits.size(1);
+  Tensor idx = torch::empty({N, K}, logits.options().dtype(at::kLong));
+  Tensor w = torch::empty({N, K}, logits.options());
+  Tensor keys = torch::empty({N * K}, logits.options().dtype(at::kLong));
+  Tensor counts = torch::empty({E, K}, logits.options().dtype(at::kInt));
+  const bool ht = temperature.has_value() && temperature->defined();
+  if (ht) TORCH_CHECK(temperature->scalar_type() == at::kFloat && temperature->is_cuda(), "temperature: fp32 device scalar");
+  tb::launch_moe_route_topk(logits.data_ptr<float>(), bias.data_ptr<float>(), ht ? temperature->data_ptr<float>() : nullptr,
+                            (float)temp_value, (int)N, (int)E, (int)K, (long long*)idx.data_ptr<int64_t>(), w.data_ptr<float>(),
+                            (long long*)keys.data_ptr<int64_t>(), counts.data_ptr<int>(), cur_stream());
+  return {idx, w, keys, counts};
+}
+
+Tensor moe_route_bwd(const Tensor& logits, const c10::optional<Tensor>& temperature, double temp_value, const Tensor& idx,
+                     const Tensor& w, const Tensor& dw) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t N = logits.size(0), E = logits.size(1), K = idx.size(1);
+  Tensor dl = torch::empty_like(logits);
+  const bool ht = temperature.has_value() && temperature->defined();
+  tb::launch_moe_route_bwd(logits.data_ptr<float>(), ht ? temperature->data_ptr<float>() : nullptr, (float)temp_value,
+                           (const long long*)idx.data_ptr<int64_t>(), w.data_ptr<float>(), dw.contiguous().data_ptr<float>(), (int)N,
+                           (int)E, (int)K, dl.data_ptr<float>(), cur_stream());
+  return dl;
+}
+
+std::vector<Tensor> moe_plan_sorted(const Tensor& sorted_keys, const Tensor& order, const Tensor& counts, int64_t N, int64_t K,
+                                    int64_t cap) {
+  TORCH_CHECK(sorted_keys.scalar_type() == at::kLong && order.scalar_type() == at::kLong && counts.scalar_type() == at::kInt, "dtypes");
+  c10::cuda::CUDAGuard guard(sorted_keys.device());
+  const int64_t A = N * K, E = counts.size(0);
+  const int64_t R = (A + 127) / 128 * 128 + E * 128;
+  auto oi = sorted_keys.options().dtype(at::kInt);
+  Tensor pos = torch::empty({N, K}, oi), keep = torch::empty({N, K}, sorted_keys.options().dtype(at::kBool));
+  Tensor row_src = torch::empty({R}, oi), tile_group = torch::empty({R / 128}, oi), offsets = torch::empty({E + 1}, oi);
+  Tensor accepted = torch::empty({E}, sorted_keys.options());
+  tb::launch_moe_plan_sorted((const long long*)sorted_keys.data_ptr<int64_t>(), (const long long*)order.data_ptr<int64_t>(),
+                             counts.data_ptr<int>(), (int)A, (int)E, (int)K, (int)cap, (int)R, pos.data_ptr<int>(),
+                             (unsigned char*)keep.data_ptr<bool>(), row_src.data_ptr<int>(), tile_group.data_ptr<int>(),
+                             offsets.data_ptr<int>(), (long long*)accepted.data_ptr<int64_t>(), cur_stream());
+  return {pos, keep, row_src, tile_group, offsets, accepted};
+}
+
 void adamw_flat(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, const c10::optional<Tensor>& param_bf16,
                 double lr, double beta1, double beta2, double eps, double wd, int64_t step,
                 const c10::optional<Tensor>& grad_scale_ptr, double grad_scale, const c10::optional<Tensor>& hyper) {
@@ -338,6 +385,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gather_rows", &gather_rows);
   m.def("combine_rows", &combine_rows);
   m.def("row_dots", &row_dots);
+  m.def("moe_route_topk", &moe_route_topk);
+  m.def("moe_route_bwd", &moe_route_bwd);
+  m.def("moe_plan_sorted", &moe_plan_sorted);
   m.def("adamw_flat", &adamw_flat);
   m.def("sumsq", &sumsq);
   m.def("muon_momentum", &muon_momentum);

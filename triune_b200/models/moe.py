@@ -177,13 +177,25 @@ class MoE_FFN(nn.Module):
                     keep = ref.moe_capacity_mask(idx, w.detach(), self.num_experts, cap)
         return idx, w, keep
 
+    def _capacity(self, N: int) -> Optional[int]:
+        if not self.training:
+            return None
+        cap = max(1, min(int(math.ceil(N / self.num_experts * self.capacity_multiplier)), N))
+        return cap if cap < N else None
+
     def forward(self, x: torch.Tensor, update_stats: bool = True) -> torch.Tensor:
         B, T, D = x.shape
         x2 = x.reshape(B * T, D)
-        idx, w, keep = self.route(x2)
+        plan = None
+        logits = ops.linear(x2, self.router.weight, self.router.bias).float()
+        if ops.route_plan_supported(logits, self.top_k) and x2.dtype == torch.bfloat16:
+            # routing, capacity admission and the dispatch plan from one sort and three kernels
+            idx, w, keep, plan = ops.moe_route_plan(logits, self.expert_bias, self.top_k, self._temperature(), self._capacity(B * T))
+        else:
+            idx, w, keep = self.route(x2)
         shared_out = self.shared(x2) if self.shared is not None else None
         wk = w if keep is None else w * keep.to(w.dtype)
-        out = ops.moe_experts(x2, idx, wk, keep, self.w1, self.b1, self.w2, self.b2, shared_out, self.shared_scale)
+        out = ops.moe_experts(x2, idx, wk, keep, self.w1, self.b1, self.w2, self.b2, shared_out, self.shared_scale, plan=plan)
         if self.training and update_stats:
             with torch.no_grad():
                 self._update_routing_stats(x2.detach(), idx, w.detach(), keep)

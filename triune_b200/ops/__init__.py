@@ -464,6 +464,50 @@ def moe_route(logits, expert_bias, top_k, temperature=1.0):
     return ref.moe_route(logits, expert_bias, top_k, temperature)
 
 
+class _RouteTopKFn(torch.autograd.Function):
+    """Top-k routing in one kernel; differentiable in the mixing weights (probabilities recomputed in the backward)."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, temperature, top_k):
+        t_dev = temperature if torch.is_tensor(temperature) else None
+        t_val = 1.0 if t_dev is not None else float(temperature)
+        if t_dev is not None:
+            t_dev = t_dev.detach().reshape(1).float().contiguous()
+        idx, w, keys, counts = _ext.ext().moe_route_topk(logits, bias.float().contiguous(), t_dev, t_val, top_k)
+        _tick(2)
+        ctx.save_for_backward(logits, idx, w, t_dev if t_dev is not None else torch.empty(0))
+        ctx.t_val, ctx.has_t = t_val, t_dev is not None
+        ctx.mark_non_differentiable(idx, keys, counts)
+        return idx, w, keys, counts
+
+    @staticmethod
+    def backward(ctx, _didx, dw, _dkeys, _dcounts):
+        logits, idx, w, t_dev = ctx.saved_tensors
+        dl = _ext.ext().moe_route_bwd(logits, t_dev if ctx.has_t else None, ctx.t_val, idx, w, dw.float().contiguous())
+        _tick()
+        return dl, None, None, None
+
+
+def route_plan_supported(logits, top_k: int) -> bool:
+    return (_ext.use_kernels(logits) and logits.dtype == torch.float32 and logits.dim() == 2 and logits.shape[1] <= 64
+            and 1 <= top_k <= 4 and top_k <= logits.shape[1])
+
+
+def moe_route_plan(logits, expert_bias, top_k: int, temperature=1.0, capacity: Optional[int] = None):
+    """Routing + capacity admission + dispatch plan with ONE sort and three kernels, no host synchronisation.
+
+    Returns ``(idx [N,k] int64, w [N,k] fp32 (differentiable), keep [N,k] bool, plan)`` where ``plan`` is the tuple
+    :func:`moe_plan` returns. ``capacity`` (per (k-slot, expert), highest weight first, ties to the lower token index) may
+    be ``None`` for no limit."""
+    N, E = logits.shape
+    idx, w, keys, counts = _RouteTopKFn.apply(logits.contiguous(), expert_bias, temperature, top_k)
+    skeys, order = torch.sort(keys, stable=True)
+    cap = int(capacity) if capacity is not None and capacity < N else N
+    pos, keep, row_src, tile_group, offsets, accepted = _ext.ext().moe_plan_sorted(skeys, order, counts, N, top_k, cap)
+    _tick(3)
+    return idx, w, keep, (pos, row_src, tile_group, offsets, accepted)
+
+
 def moe_plan(idx: torch.Tensor, keep: Optional[torch.Tensor], num_experts: int, tile: int = 128):
     """Device-side dispatch plan (no host sync).
 
@@ -612,12 +656,12 @@ class _ExpertMLPFn(torch.autograd.Function):
         return dxp, dw1, db1, dw2, db2, None, None
 
 
-def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_scale: float = 0.0):
+def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_scale: float = 0.0, plan=None):
     """Sparse expert FFN. x2 [N,d]; idx/weights/keep [N,k]; stacked expert weights w1 [E,H,d], b1 [E,H],
     w2 [E,d,H], b2 [E,d]. Returns sum_j w_j * expert_{idx_j}(x) (+ shared_scale * shared_out)."""
     E = w1.shape[0]
     if _ext.use_kernels(x2, w1, w2) and x2.dtype == torch.bfloat16:
-        pos, row_src, tile_group, group_offsets, _ = moe_plan(idx, keep, E)
+        pos, row_src, tile_group, group_offsets, _ = plan if plan is not None else moe_plan(idx, keep, E)
         xp = _GatherRowsFn.apply(x2.contiguous(), row_src, pos)
         yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets)
         wk = weights.float().contiguous()
