@@ -387,6 +387,7 @@ def test_gla_layer_matches_reference_ops(dev):
 @pytest.mark.parametrize("N,E,K,cap", [(4096, 8, 2, 700), (1000, 64, 2, None), (2048, 8, 1, 200), (512, 16, 4, 100)])
 def test_moe_route_plan_matches_oracle(N, E, K, cap):
     """One-sort routing / capacity / plan kernels against the PyTorch composition."""
+    from triune_b200 import ops
     from triune_b200.ops import reference as ref
 
     torch.manual_seed(N + E)
