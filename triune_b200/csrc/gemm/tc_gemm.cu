@@ -1,12 +1,12 @@
 // bf16 GEMM on the 5th-generation tensor cores: C = alpha * A * B^T (+ epilogue).
 //
-// One persistent CTA per SM, 192 threads, three roles:
+// One persistent CTA per SM, 320 threads, three roles:
 //   warp 0    TMA producer: cp.async.bulk.tensor tiles of A (128 x 64) and B (BN x 64) into a ring of
 //             128B-swizzled shared-memory stages, completion signalled on mbarriers;
 //   warp 1    MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) reading the stages through
 //             shared-memory descriptors and accumulating into TMEM; tcgen05.commit releases a stage
 //             back to the producer and, after the last K step, publishes the accumulator;
-//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulator (lane == output row), apply bias / GELU /
+//   warps 2-9 epilogue: tcgen05.ld the fp32 accumulator (lane == output row), apply bias / GELU /
 //             GELU' / row scale / accumulate, convert and store 16-byte vectors.
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1. No cluster multicast is used; every CTA loads its own tiles.
@@ -29,7 +29,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr int EPI_TILE = 32 * 128;  // one staged output tile: 32 rows x 128 bytes
 
 template <int BN>
@@ -39,7 +39,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = (BN == 192) ? 512 : 2 * BN;  // power of two >= 2 * BN
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 4096 /*epilogue staging*/ + 1024 /*alignment slack*/ + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 4096 /*epilogue staging: 8 warps x 1 tile*/ + 1024 /*alignment slack*/ + 256;
 };
 
 struct KParams {
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint8_t* smemA = smem;
   uint8_t* smemB = smem + STAGES * Cfg::A_BYTES;
-  uint8_t* smem_epi = smem + STAGES * Cfg::STAGE_BYTES;  // 4 warps x 2 staging tiles
+  uint8_t* smem_epi = smem + STAGES * Cfg::STAGE_BYTES;  // 8 warps x 1 staging tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + 8 * EPI_TILE);
   uint64_t* full = bars;                    // [STAGES] TMA -> MMA
   uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], 8);
     }
     mbar_fence_init();
     prefetch_tmap(&tmA);
@@ -280,9 +280,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // fp32 accumulator from TMEM, applies the epilogue, writes the rows into a private 128B-swizzled staging tile
     // and one lane hands the tile to TMA (plain store, or reduce-add for accumulate / split-K): global writes are
     // full 128-byte lines regardless of the row pitch, and ragged M/N edges are clipped by the tensor map.
+    // Eight epilogue warps: a warp can only read the TMEM lanes of its quarter (warp % 4), so two warps share every
+    // quarter and take alternate column chunks. Short reductions (K = 384) make the epilogue the longer phase of a
+    // tile; halving it is worth more than a deeper load ring.
     const int lane_base = (warp & 3) * 32;
-    uint8_t* my_stage = smem_epi + (warp & 3) * (2 * EPI_TILE);
-    int buf = 0;
+    const int col_half = (warp - 2) >> 2;
+    uint8_t* my_stage = smem_epi + (warp - 2) * EPI_TILE;  // one staging tile per warp (a second one costs a load stage and measured slower)
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool out_f32 = (p.flags & GF_OUT_F32) != 0;
@@ -308,9 +311,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const __nv_bfloat16* bias = p.bias ? p.bias + (long long)tl.g * p.bias_stride : nullptr;
       const float rs = (p.row_scale && row_ok) ? p.row_scale[gm] : 1.0f;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += CW) {
+      for (int c = col_half * CW; c < BN; c += 2 * CW) {
         if (n0 + c >= p.N) break;
         float v[64];
+        // GELU' operand: issue the row loads first so their latency hides behind the TMEM reads
+        uint4 auxv[8];
+        if (do_dgelu && row_ok) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int gn = n0 + c + j * 8;
+            auxv[j] = gn < p.N ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn) : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         if (tl.k_iters > 0) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c, r);
@@ -346,9 +358,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         if (do_gelu) {
           if (p.aux_out) {  // pre-activation goes out through the same staging path (always bf16, 64 columns)
-            if (lane == 0) tma_store_wait_read<1>();
+            if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
-            uint8_t* st = my_stage + buf * EPI_TILE;
+            uint8_t* st = my_stage;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               uint4 o;
@@ -364,7 +376,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               tma_store_3d(&tmAux, st, n0 + c, tl.m0 + lane_base, out_batch);
               tma_store_commit();
             }
-            buf ^= 1;
           }
 #pragma unroll
           for (int i = 0; i < 64; ++i) v[i] = gelu_tanh_f(v[i]);
@@ -374,8 +385,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           for (int j = 0; j < 8; ++j) {
             const int gn = n0 + c + j * 8;
             if (gn < p.N) {
-              uint4 av = *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn);
-              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&auxv[j]);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 float2 f = __bfloat1622float2(a2[i]);
@@ -389,9 +399,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 64; ++i) v[i] *= rs;
         }
-        if (lane == 0) tma_store_wait_read<1>();
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
-        uint8_t* st = my_stage + buf * EPI_TILE;
+        uint8_t* st = my_stage;
         if (out_f32) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -417,7 +427,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             tma_store_3d(&tmC, st, n0 + c, tl.m0 + lane_base, out_batch);
           tma_store_commit();
         }
-        buf ^= 1;
       }
       tc_fence_before_sync();
       __syncwarp();
