@@ -1,0 +1,232 @@
+"""CPU tests of the training loop, checkpoints, schedule, generation, speculative decoding, dense models, layer
+streaming, and data parallelism over gloo (world size 2)."""
+
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from triune_b200.config import ModelConfig
+from triune_b200.models import TriuneTransformer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CFG = dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4, top_k=2, router_prefix_layers=1,
+           reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=96, dense_hidden=80)
+
+
+def tiny(seed=0):
+    torch.manual_seed(seed)
+    return TriuneTransformer.from_config(ModelConfig(**CFG))
+
+
+class Tok:
+    pad_token_id, sep_token_id, eos_token_id = None, None, None
+
+    def encode(self, s):
+        return [ord(c) % 256 for c in s]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(int(i) % 128 or 32) for i in ids)
+
+
+def _trainer(model, **cfg):
+    from triune_b200.data import SyntheticTokenSource
+    from triune_b200.optim import CentroidSteerOptimizer
+    from triune_b200.trainer import Trainer
+
+    run = {"lr": 3e-3, "min_lr": 3e-4, "warmup_steps": 2, "total_steps": 50, "depth_mode": "cortex", "grad_accum_steps": 1,
+           "grad_clip": 1.0, "vocab_size": 256, "batch_size": 4, "seq_len": 32}
+    run.update(cfg)
+    opt = CentroidSteerOptimizer(model, lr=run["lr"], grad_clip=1.0)
+    src = SyntheticTokenSource(256, run["batch_size"], run["seq_len"], seed=3, pool=1)  # one repeating batch: loss must fall
+    return Trainer(model, run, optimizer=opt, train_loader=src, device=torch.device("cpu"))
+
+
+@pytest.mark.parametrize("mode", ["cortex", "joint", "dynamic"])
+def test_training_modes_reduce_loss(mode):
+    tr = _trainer(tiny(), depth_mode=mode)
+    losses = [float(tr.engine.step_once()["loss"]) for _ in range(12)]
+    assert all(math.isfinite(l) for l in losses) and min(losses[-3:]) < losses[0]
+    assert tr.engine.step == 12
+
+
+def test_lr_schedule_warmup_cosine_and_cycles():
+    from triune_b200.trainer.scheduler import lr_schedule
+
+    cfg = {"lr": 1.0, "min_lr": 0.1, "warmup_steps": 10, "total_steps": 110}
+    assert lr_schedule(cfg, 0) < lr_schedule(cfg, 5) < lr_schedule(cfg, 10) <= 1.0
+    assert abs(lr_schedule(cfg, 10) - 1.0) < 0.11 and abs(lr_schedule(cfg, 109) - 0.1) < 0.02
+    mid = lr_schedule(cfg, 60)
+    assert 0.1 < mid < 1.0
+    assert all(0.1 - 1e-9 <= lr_schedule(cfg, s) <= 1.0 + 1e-9 for s in range(0, 400, 7))  # wraps into new cycles
+
+
+def test_checkpoint_roundtrip_resume_and_fingerprint(tmp_path):
+    from triune_b200.trainer import checkpoint as ckpt
+
+    tr = _trainer(tiny())
+    for _ in range(3):
+        tr.engine.step_once()
+    tr.config["checkpoint_dir"] = str(tmp_path)
+    path = tr.save_latest()
+    assert os.path.exists(path) and not [p for p in os.listdir(tmp_path) if p.endswith(".tmp")]  # atomic rename
+    ref_next = float(tr.engine.step_once()["loss"])
+    tr2 = _trainer(tiny(seed=1))
+    ck = tr2.resume(path)
+    assert tr2.engine.step == 3 and ck["step"] == 3
+    for a, b in zip(tr.model.state_dict().values(), tr2.model.state_dict().values()):
+        pass  # tr advanced one more step; compare the resumed run's next loss instead
+    assert abs(float(tr2.engine.step_once()["loss"]) - ref_next) < 5e-3  # same weights, optimizer state and batch
+    fp = ckpt.fingerprint({"hidden_dim": 64, "num_layers": 5, "lr": 1.0})
+    assert fp == ckpt.fingerprint({"hidden_dim": 64, "num_layers": 5, "lr": 2.0})  # optimisation settings are not semantics
+    assert fp != ckpt.fingerprint({"hidden_dim": 128, "num_layers": 5})
+    with pytest.raises(Exception):
+        ckpt.load_checkpoint(path, model=TriuneTransformer.from_config(ModelConfig(**{**CFG, "hidden_dim": 32, "num_heads": 1})),
+                             config={"hidden_dim": 32, "num_layers": 5})
+
+
+def test_generation_cache_penalties_and_stop():
+    from triune_b200.inference import _apply_penalties, generate_response, generate_tokens, infer_config_from_state_dict
+
+    m = tiny().eval()
+    ids = torch.randint(0, 256, (1, 11))
+    out, cache, tele = generate_tokens(m, ids, max_new_tokens=6, temperature=0.0, repetition_penalty=1.0, count_penalty=0.0,
+                                       prefill_chunk=4)
+    # greedy decoding with the recurrent cache equals re-running the whole prefix every step
+    seq = ids.clone()
+    for _ in range(6):
+        nxt = m(seq, force_depth=2)[0][0, -1].argmax().view(1, 1)
+        seq = torch.cat((seq, nxt), 1)
+    assert out == seq[0, 11:].tolist() and tele["new_tokens"] == 6 and cache is not None
+    lg = torch.tensor([2.0, -2.0, 1.0, 0.5])
+    pen = _apply_penalties(lg.clone(), torch.tensor([0, 0, 1]), 2.0, 0.5)
+    assert pen[0] == 2.0 / 2.0 - 0.5 and pen[1] == -4.0 and pen[2] == 1.0
+    seen = []
+    r = generate_response(m, Tok(), "hello", max_new_tokens=8, temperature=0.0, stream_callback=seen.append, stop=("zzzz",))
+    assert isinstance(r["text"], str) and len(r["tokens"]) <= 8 and "".join(seen).strip().startswith(r["text"][:3])
+    cfg = infer_config_from_state_dict(m.state_dict())
+    assert (cfg.hidden_dim, cfg.num_layers, cfg.num_experts, cfg.expert_hidden, cfg.dense_hidden) == (64, 5, 4, 96, 80)
+    assert (cfg.reflex_exit_layer, cfg.limbic_exit_layer) == (2, 3)
+
+
+def test_self_speculative_greedy_equals_autoregressive():
+    from triune_b200.models.speculative import SelfSpeculativeGenerator
+
+    m = tiny().eval()
+    gen = SelfSpeculativeGenerator(m, k_draft=3)
+    ids = torch.randint(0, 256, (1, 9))
+    a = gen.generate(ids, max_new_tokens=10, temperature=0.0)
+    b = gen.generate_autoregressive(ids, max_new_tokens=10)
+    assert torch.equal(a[:, : b.shape[1]], b[:, : a.shape[1]])
+    assert 0.0 <= gen.acceptance_rate <= 1.0 and gen.telemetry["proposed"] > 0
+
+
+@pytest.mark.parametrize("mixer,ffn", [("gla", "swiglu"), ("gated_deltanet", "swiglu"), ("sdpa", "gelu")])
+def test_universal_dense_models_train_and_cache(mixer, ffn):
+    from triune_b200.models.universal import TriuneUniversalEngine, UniversalDenseTransformer
+
+    torch.manual_seed(0)
+    cfg = ModelConfig(family="universal", vocab_size=128, hidden_dim=64, num_layers=2, num_heads=2, head_dim=32, mixer=mixer,
+                      ffn=ffn, dense_hidden=96, num_experts=1, top_k=1)
+    m = UniversalDenseTransformer.from_config(cfg)
+    eng = TriuneUniversalEngine(m, lr=5e-3)
+    x = torch.randint(0, 128, (2, 17))
+    losses = [eng.train_step(x) for _ in range(8)]
+    assert losses[-1] < losses[0]
+    m.eval()
+    full = m(x[:, :12])[0] if isinstance(m(x[:, :12]), tuple) else m(x[:, :12])
+    cache = m.init_cache(2)
+    lg1, cache = m(x[:, :7], cache=cache)
+    lg2, cache = m(x[:, 7:12], cache=cache)
+    assert torch.allclose(torch.cat((lg1, lg2), 1), full, atol=2e-4, rtol=1e-3)
+    out = eng.generate(x[:1, :5], max_new_tokens=4)
+    assert out.shape == (1, 9)
+
+
+def test_layer_streaming_matches_resident_training():
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming
+
+    a, b = tiny(), tiny()
+    x = torch.randint(0, 256, (2, 16))
+    y = torch.randint(0, 256, (2, 16))
+    eng = enable_layer_streaming(b, "cpu", config=StreamingConfig(resident_gpu_layers=1, pin_memory=False))
+    la = a.forward_loss(x, y, force_depth=2)
+    lb = b.forward_loss(x, y, force_depth=2)
+    la, lb = (la[0] if isinstance(la, tuple) else la), (lb[0] if isinstance(lb, tuple) else lb)
+    assert torch.allclose(la, lb, atol=1e-5)
+    la.backward()
+    lb.backward()
+    # streamed layers hand their gradients to the host store; resident ones keep .grad
+    tel = eng.get_telemetry()
+    assert tel["d2h_copies"] >= 1 and tel["d2h_bytes"] > 0
+    eng.step_streaming_optimizer(None, lr=1e-2)
+    lb2 = b.forward_loss(x, y, force_depth=2)
+    lb2 = lb2[0] if isinstance(lb2, tuple) else lb2
+    assert torch.isfinite(lb2) and float(lb2) != float(lb)  # streamed layers were updated
+    eng.detach()
+    out = b(x, force_depth=2)[0]
+    assert out.shape == (2, 16, 256)
+
+
+GLOO_WORKER = r'''
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from triune_b200.config import ModelConfig
+from triune_b200.models import TriuneTransformer
+from triune_b200.optim import CentroidSteerOptimizer
+from triune_b200.parallel import setup_distributed, all_reduce_dict
+from triune_b200.parallel.data_parallel import ShardedDataParallel
+from triune_b200.trainer import Trainer
+ctx = setup_distributed(backend="gloo")
+cfg = dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4, top_k=2, router_prefix_layers=1,
+           reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=96, dense_hidden=80)
+torch.manual_seed(100 + ctx.rank)           # different initial weights per rank: attach() must broadcast rank 0's
+model = TriuneTransformer.from_config(ModelConfig(**cfg))
+dp = ShardedDataParallel(ctx, mode="nccl")   # collective all-reduce path (gloo here)
+opt = CentroidSteerOptimizer(model, lr=3e-3, grad_clip=1.0)
+run = {"lr": 3e-3, "min_lr": 3e-4, "warmup_steps": 2, "total_steps": 50, "depth_mode": "cortex", "grad_accum_steps": 1,
+       "grad_clip": 1.0, "vocab_size": 256}
+tr = Trainer(model, run, optimizer=opt, device=torch.device("cpu"), dp=dp)
+g = torch.Generator().manual_seed(7)
+data = torch.randint(0, 256, (4, 33), generator=g)        # global batch of 4, two rows per rank
+mine = data[ctx.rank * 2:(ctx.rank + 1) * 2]
+losses = []
+for _ in range(6):
+    losses.append(tr.train_step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous()))
+avg = all_reduce_dict({"loss": losses[-1]}, ctx)
+chk = float(sum(p.double().sum() for p in model.parameters()))
+print("RESULT " + json.dumps({"rank": ctx.rank, "losses": losses, "avg": avg["loss"], "checksum": chk}), flush=True)
+dist.barrier(); dist.destroy_process_group()
+'''
+
+
+def test_gloo_data_parallel_matches_single_process_large_batch(tmp_path):
+    """Two gloo ranks with half the batch each follow the same loss curve as one process with the whole batch."""
+    import json
+
+    worker = tmp_path / "w.py"
+    worker.write_text(GLOO_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29731", str(worker), ROOT]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    import re
+
+    dec = json.JSONDecoder()  # two ranks share the pipe: records can land on one line
+    res = sorted((dec.raw_decode(p.stdout, m.end())[0] for m in re.finditer(r"RESULT (?=\{)", p.stdout)), key=lambda r: r["rank"])
+    assert p.returncode == 0 and len(res) == 2, p.stdout[-2000:] + p.stderr[-2000:]
+    assert abs(res[0]["checksum"] - res[1]["checksum"]) < 1e-6 * max(1.0, abs(res[0]["checksum"]))  # replicas stay identical
+    # single process, same initial weights as rank 0, whole batch
+    torch.manual_seed(100)
+    model = TriuneTransformer.from_config(ModelConfig(**CFG))
+    tr = _trainer(model)
+    g = torch.Generator().manual_seed(7)
+    data = torch.randint(0, 256, (4, 33), generator=g)
+    single = [tr.train_step(data[:, :-1].contiguous(), data[:, 1:].contiguous()) for _ in range(6)]
+    dp_mean = [(a + b) / 2 for a, b in zip(res[0]["losses"], res[1]["losses"])]
+    assert abs(dp_mean[0] - single[0]) < 2e-3                      # same weights, same data: same first loss
+    assert dp_mean[-1] < dp_mean[0] and abs(dp_mean[-1] - single[-1]) < 0.15  # same trajectory up to routing / capacity effects
+    assert abs(res[0]["avg"] - dp_mean[-1]) < 1e-5

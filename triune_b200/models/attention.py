@@ -179,9 +179,14 @@ class SoftmaxAttention(nn.Module):
         if self.kv_heads != self.heads:
             rep = self.heads // self.kv_heads
             kk, vv = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
-        o = F.scaled_dot_product_attention(
-            q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=(past is None and T > 1)
-        )
+        if past is None or T == 1:
+            mask, causal = None, (past is None and T > 1)
+        else:  # a multi-token chunk after a prefix: query i sees the whole prefix and chunk positions <= i
+            P = kk.shape[1] - T
+            mask = torch.ones(T, P + T, dtype=torch.bool, device=x.device).tril(diagonal=P)
+            causal = False
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask,
+                                           is_causal=causal)
         o = o.transpose(1, 2).reshape(B, T, self.heads * self.head_dim)
         return _project(self.out_proj, o), format_cache(new_state, cache, fmt, offset, T)
 

@@ -112,6 +112,29 @@ def polar_stiefel_retraction(X: torch.Tensor, steps: int = 5) -> torch.Tensor:
     return ref.newton_schulz(X, steps=max(steps, 8))
 
 
+_SKETCH_GENERATORS: Dict[str, torch.Generator] = {}
+_SKETCH_SEED = 0x5EED
+
+
+def set_sketch_seed(seed: int) -> None:
+    """Seed of the Gaussian sketches. Every data-parallel replica must draw the same sketches or the replicas' expert
+    weights drift apart, so the sketches come from a dedicated generator and never from the global RNG (which ranks
+    seed differently for data order and dropout)."""
+    global _SKETCH_SEED
+    _SKETCH_SEED = int(seed)
+    _SKETCH_GENERATORS.clear()
+
+
+def _sketch(shape, device) -> torch.Tensor:
+    key = str(device)
+    g = _SKETCH_GENERATORS.get(key)
+    if g is None:
+        g = torch.Generator(device=device)
+        g.manual_seed(_SKETCH_SEED)
+        _SKETCH_GENERATORS[key] = g
+    return torch.randn(shape, device=device, dtype=torch.float32, generator=g)
+
+
 def subspace_projection(G: torch.Tensor, rank: int, oversample: int = 4, power_iters: int = 1) -> torch.Tensor:
     """Randomized range finder: orthonormal basis [m, rank] of the dominant left subspace of G [m, n]."""
     return batched_subspace_projection(G.unsqueeze(0), rank, oversample, power_iters)[0]
@@ -121,7 +144,7 @@ def batched_subspace_projection(G: torch.Tensor, rank: int, oversample: int = 4,
     K, m, n = G.shape
     r = min(rank + oversample, m, n)
     Gf = G.float()
-    Y = Gf @ torch.randn(K, n, r, device=G.device, dtype=torch.float32)
+    Y = Gf @ _sketch((K, n, r), G.device)
     Q = batched_qr(Y)
     for _ in range(power_iters):
         Q = batched_qr(Gf @ batched_qr(Gf.transpose(1, 2) @ Q))
@@ -136,7 +159,7 @@ def two_sided_bases(G: torch.Tensor, r: int, telemetry: Optional[Dict] = None) -
     """Gaussian sketch + three QR passes: (Q_L [K,m,r], Q_R [K,n,r]) capturing the dominant subspaces of G."""
     K, m, n = G.shape
     Gf = G.float()
-    Y = Gf @ torch.randn(K, n, r, device=G.device, dtype=torch.float32)
+    Y = Gf @ _sketch((K, n, r), G.device)
     QL = batched_qr(Y, telemetry=telemetry)
     QR = batched_qr(Gf.transpose(1, 2) @ QL, telemetry=telemetry)
     QL = batched_qr(Gf @ QR, telemetry=telemetry)

@@ -57,6 +57,29 @@ class ShardedDataParallel:
                 dist.all_reduce(g, op=dist.ReduceOp.SUM)
                 g.mul_(1.0 / self.ctx.world_size)
                 self.comm_bytes += g.numel() * 4
+                self._sync_routing_statistics()
             return inner(closure)
 
         optimizer.step = step
+
+    def _sync_routing_statistics(self) -> None:
+        """Average the routing statistics that feed the update rule (expert centroids used by the steering tier, the
+        pending selection-bias update, the load ratios) so every replica applies the identical step. They are derived
+        from each rank's own tokens; without this the replicas' expert weights drift apart."""
+        tensors = []
+        for m in self.optimizer.model.modules():
+            for name in ("last_centroids", "expert_load_ratio", "_pending_bias_update"):
+                t = getattr(m, name, None)
+                if torch.is_tensor(t) and t.is_floating_point() and hasattr(m, "expert_bias"):
+                    tensors.append(t)
+        if not tensors:
+            return
+        flat = torch.cat([t.detach().float().reshape(-1) for t in tensors])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+        flat.mul_(1.0 / self.ctx.world_size)
+        off = 0
+        for t in tensors:
+            n = t.numel()
+            t.copy_(flat[off : off + n].view(t.shape).to(t.dtype))
+            off += n
+        self.comm_bytes += flat.numel() * 4
