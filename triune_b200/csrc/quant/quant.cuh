@@ -23,4 +23,10 @@ void launch_nvfp4_gemv(const __nv_bfloat16* x, const uint8_t* packed, const void
                        const float* tscale, __nv_bfloat16* y, int M, int N, int K, cudaStream_t s);
 void launch_fwht16(const __nv_bfloat16* x, __nv_bfloat16* out, long long n, cudaStream_t s);
 
+// GGML / GGUF block formats (F32, F16, BF16, Q4_0, Q4_1, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K) decoded on the device:
+// to bf16, or straight into NVFP4 (optional 16-point Hadamard rotation) without a bf16 copy of the tensor.
+void launch_ggml_dequant(const uint8_t* raw, int type, long long n, __nv_bfloat16* out, cudaStream_t s);
+void launch_ggml_to_nvfp4(const uint8_t* raw, int type, long long rows, long long K, bool hadamard, uint8_t* packed,
+                          uint8_t* scales_e4m3, float* tscale, unsigned int* amax_scratch, cudaStream_t s);
+
 }  // namespace tb

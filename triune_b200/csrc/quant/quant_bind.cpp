@@ -89,6 +89,26 @@ at::Tensor fwht16(const at::Tensor& x) {
   return out;
 }
 
+
+at::Tensor ggml_dequant(const at::Tensor& raw, int64_t type, int64_t numel) {
+  need(raw.is_cuda() && raw.scalar_type() == at::kByte && raw.is_contiguous(), "ggml_dequant: contiguous uint8 CUDA buffer");
+  c10::cuda::CUDAGuard g(raw.device());
+  auto out = at::empty({numel}, raw.options().dtype(at::kBFloat16));
+  tb::launch_ggml_dequant(raw.data_ptr<uint8_t>(), (int)type, numel, bfm(out), cur());
+  return out;
+}
+
+std::vector<at::Tensor> ggml_to_nvfp4(const at::Tensor& raw, int64_t type, int64_t rows, int64_t K, bool hadamard) {
+  need(raw.is_cuda() && raw.scalar_type() == at::kByte && raw.is_contiguous(), "ggml_to_nvfp4: contiguous uint8 CUDA buffer");
+  c10::cuda::CUDAGuard g(raw.device());
+  auto packed = at::empty({rows, K / 2}, raw.options());
+  auto scales = at::empty({rows, K / 16}, raw.options().dtype(at::kFloat8_e4m3fn));
+  auto tscale = at::empty({}, raw.options().dtype(at::kFloat));
+  auto scratch = at::empty({1}, raw.options().dtype(at::kInt));
+  tb::launch_ggml_to_nvfp4(raw.data_ptr<uint8_t>(), (int)type, rows, K, hadamard, packed.data_ptr<uint8_t>(),
+                           (uint8_t*)scales.data_ptr(), tscale.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), cur());
+  return {packed, scales, tscale};
+}
 }  // namespace
 
 void register_quant(pybind11::module& m) {
@@ -97,5 +117,7 @@ void register_quant(pybind11::module& m) {
   m.def("nvfp4_quantize", &nvfp4_quantize, "[N,K] -> (packed E2M1, E4M3 block scales, fp32 tensor scale)");
   m.def("nvfp4_dequant", &nvfp4_dequant, "packed NVFP4 -> bf16 [N,K]");
   m.def("nvfp4_gemv", &nvfp4_gemv, "y = x @ W^T for M <= 8 straight from packed NVFP4 weights");
+  m.def("ggml_dequant", &ggml_dequant, "GGML block formats -> bf16");
+  m.def("ggml_to_nvfp4", &ggml_to_nvfp4, "GGML block formats -> NVFP4 (packed, scales, tensor scale) without a bf16 copy");
   m.def("fwht16", &fwht16, "orthonormal 16-point Walsh-Hadamard transform over consecutive groups of 16");
 }

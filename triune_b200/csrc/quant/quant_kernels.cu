@@ -316,13 +316,147 @@ __device__ __forceinline__ void load16<float>(const float* src, float (&v)[16]) 
   }
 }
 
-// pass 1: global max of |x| (after the optional rotation), as the bit pattern of a non-negative float
+// ---------------------------------------------------------------------------------------------------------
+// GGML block formats (GGUF files): random-access decode of element i of a block.
+// ---------------------------------------------------------------------------------------------------------
+enum GgmlType : int { GGML_F32 = 0, GGML_F16 = 1, GGML_Q4_0 = 2, GGML_Q4_1 = 3, GGML_Q5_0 = 6, GGML_Q8_0 = 8, GGML_Q4_K = 12,
+                      GGML_Q5_K = 13, GGML_Q6_K = 14, GGML_BF16 = 30 };
+
+__host__ __device__ inline int ggml_block_elems(int t) {
+  return (t == GGML_Q4_K || t == GGML_Q5_K || t == GGML_Q6_K) ? 256 : ((t == GGML_F32 || t == GGML_F16 || t == GGML_BF16) ? 1 : 32);
+}
+__host__ __device__ inline int ggml_block_bytes(int t) {
+  switch (t) {
+    case GGML_F32: return 4;
+    case GGML_F16: case GGML_BF16: return 2;
+    case GGML_Q4_0: return 18;
+    case GGML_Q4_1: return 20;
+    case GGML_Q5_0: return 22;
+    case GGML_Q8_0: return 34;
+    case GGML_Q4_K: return 144;
+    case GGML_Q5_K: return 176;
+    case GGML_Q6_K: return 210;
+    default: return 0;
+  }
+}
+
+__device__ __forceinline__ float ld_half(const uint8_t* p) {  // blocks are only 2-byte aligned
+  const unsigned short h = (unsigned short)p[0] | ((unsigned short)p[1] << 8);
+  return __half2float(__ushort_as_half(h));
+}
+
+__device__ __forceinline__ void k4_scale_min(const uint8_t* q, int j, float& sc, float& mn) {
+  if (j < 4) {
+    sc = (float)(q[j] & 63);
+    mn = (float)(q[j + 4] & 63);
+  } else {
+    sc = (float)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+    mn = (float)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+  }
+}
+
+__device__ __forceinline__ float ggml_elem(const uint8_t* blk, int type, int i) {
+  switch (type) {
+    case GGML_F32: return *reinterpret_cast<const float*>(blk);
+    case GGML_F16: return ld_half(blk);
+    case GGML_BF16: return __uint_as_float(((unsigned int)blk[0] | ((unsigned int)blk[1] << 8)) << 16);
+    case GGML_Q4_0: {
+      const uint8_t* qs = blk + 2;
+      const int q = i < 16 ? (qs[i] & 0xF) : (qs[i - 16] >> 4);
+      return ld_half(blk) * (float)(q - 8);
+    }
+    case GGML_Q4_1: {
+      const uint8_t* qs = blk + 4;
+      const int q = i < 16 ? (qs[i] & 0xF) : (qs[i - 16] >> 4);
+      return ld_half(blk) * (float)q + ld_half(blk + 2);
+    }
+    case GGML_Q5_0: {
+      const unsigned int qh = (unsigned int)blk[2] | ((unsigned int)blk[3] << 8) | ((unsigned int)blk[4] << 16) | ((unsigned int)blk[5] << 24);
+      const uint8_t* qs = blk + 6;
+      const int lo = i < 16 ? (qs[i] & 0xF) : (qs[i - 16] >> 4);
+      return ld_half(blk) * (float)((lo | (((qh >> i) & 1u) << 4)) - 16);
+    }
+    case GGML_Q8_0: return ld_half(blk) * (float)reinterpret_cast<const int8_t*>(blk + 2)[i];
+    case GGML_Q4_K:
+    case GGML_Q5_K: {
+      const float d = ld_half(blk), dmin = ld_half(blk + 2);
+      const uint8_t* scales = blk + 4;
+      const int g = i >> 6, half = (i >> 5) & 1, l = i & 31;
+      float sc, mn;
+      k4_scale_min(scales, 2 * g + half, sc, mn);
+      int q;
+      if (type == GGML_Q4_K) {
+        const uint8_t b = blk[16 + 32 * g + l];
+        q = half ? (b >> 4) : (b & 0xF);
+      } else {
+        const uint8_t hb = blk[16 + l];
+        const uint8_t b = blk[48 + 32 * g + l];
+        q = (half ? (b >> 4) : (b & 0xF)) + (((hb >> (2 * g + half)) & 1) << 4);
+      }
+      return d * sc * (float)q - dmin * mn;
+    }
+    case GGML_Q6_K: {
+      const int n = i >> 7, r = i & 127, quarter = r >> 5, l = r & 31;
+      const uint8_t* ql = blk + 64 * n;
+      const uint8_t* qh = blk + 128 + 32 * n;
+      const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * n;
+      const float d = ld_half(blk + 208);
+      const uint8_t lo = (quarter & 1) ? ql[l + 32] : ql[l];
+      const int q = ((quarter < 2 ? (lo & 0xF) : (lo >> 4)) | (((qh[l] >> (2 * quarter)) & 3) << 4)) - 32;
+      return d * (float)sc[(l >> 4) + 2 * quarter] * (float)q;
+    }
+    default: return 0.f;
+  }
+}
+
+// Sources of 16 consecutive values for the NVFP4 quantiser: plain arrays or GGML blocks decoded on the fly.
 template <typename T>
-__global__ void nvfp4_amax_kernel(const T* __restrict__ w, long long nblocks, int hadamard, unsigned int* gmax_bits) {
+struct ArraySrc {
+  const T* p;
+  __device__ __forceinline__ void load(long long b, float (&v)[16]) const { load16<T>(p + b * 16, v); }
+};
+struct GgmlSrc {
+  const uint8_t* raw;
+  int type, elems, bytes;
+  __device__ __forceinline__ void load(long long b, float (&v)[16]) const {
+    const long long e0 = b * 16;
+    const uint8_t* blk = raw + (e0 / elems) * bytes;
+    const int i0 = (int)(e0 % elems);
+    if (elems == 1) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = ggml_elem(raw + (e0 + i) * bytes, type, 0);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = ggml_elem(blk, type, i0 + i);  // 16 divides 32 and 256: never crosses a block
+    }
+  }
+};
+
+__global__ void ggml_dequant_kernel(GgmlSrc src, long long n, __nv_bfloat16* __restrict__ out) {
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g * 8 < n; g += (long long)gridDim.x * blockDim.x) {
+    const long long e0 = g * 8;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const long long e = e0 + i;
+      v[i] = e < n ? ggml_elem(src.raw + (e / src.elems) * src.bytes, src.type, (int)(e % src.elems)) : 0.f;
+    }
+    if (e0 + 8 <= n) {
+      *reinterpret_cast<uint4*>(out + e0) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                                      pack_bf16x2(v[6], v[7]));
+    } else {
+      for (int i = 0; e0 + i < n; ++i) out[e0 + i] = __float2bfloat16(v[i]);
+    }
+  }
+}
+
+// pass 1: global max of |x| (after the optional rotation), as the bit pattern of a non-negative float
+template <typename Src>
+__global__ void nvfp4_amax_kernel(Src w, long long nblocks, int hadamard, unsigned int* gmax_bits) {
   float m = 0.f;
   for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (long long)gridDim.x * blockDim.x) {
     float v[16];
-    load16<T>(w + b * 16, v);
+    w.load(b, v);
     if (hadamard) fwht16_inplace(v);
 #pragma unroll
     for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
@@ -333,15 +467,15 @@ __global__ void nvfp4_amax_kernel(const T* __restrict__ w, long long nblocks, in
 }
 
 // pass 2: codes + block scales
-template <typename T>
-__global__ void nvfp4_quantize_kernel(const T* __restrict__ w, long long nblocks, int hadamard,
+template <typename Src>
+__global__ void nvfp4_quantize_kernel(Src w, long long nblocks, int hadamard,
                                       const unsigned int* __restrict__ gmax_bits, uint8_t* __restrict__ packed,
                                       uint8_t* __restrict__ scales, float* __restrict__ tscale_out) {
   const float tscale = fmaxf(__uint_as_float(*gmax_bits) / (6.0f * 448.0f), 1e-12f);
   if (blockIdx.x == 0 && threadIdx.x == 0) *tscale_out = tscale;
   for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (long long)gridDim.x * blockDim.x) {
     float v[16];
-    load16<T>(w + b * 16, v);
+    w.load(b, v);
     if (hadamard) fwht16_inplace(v);
     float amax = 0.f;
 #pragma unroll
@@ -501,13 +635,41 @@ void launch_nvfp4_quantize(const void* w, bool w_is_bf16, long long rows, long l
   cudaMemsetAsync(amax_scratch, 0, sizeof(unsigned int), s);
   const int g = grid_for(nblocks, 256);
   if (w_is_bf16) {
-    nvfp4_amax_kernel<__nv_bfloat16><<<g, 256, 0, s>>>((const __nv_bfloat16*)w, nblocks, hadamard, amax_scratch);
-    nvfp4_quantize_kernel<__nv_bfloat16><<<g, 256, 0, s>>>((const __nv_bfloat16*)w, nblocks, hadamard, amax_scratch, packed, scales_e4m3, tscale);
+    ArraySrc<__nv_bfloat16> src{(const __nv_bfloat16*)w};
+    nvfp4_amax_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch);
+    nvfp4_quantize_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch, packed, scales_e4m3, tscale);
   } else {
-    nvfp4_amax_kernel<float><<<g, 256, 0, s>>>((const float*)w, nblocks, hadamard, amax_scratch);
-    nvfp4_quantize_kernel<float><<<g, 256, 0, s>>>((const float*)w, nblocks, hadamard, amax_scratch, packed, scales_e4m3, tscale);
+    ArraySrc<float> src{(const float*)w};
+    nvfp4_amax_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch);
+    nvfp4_quantize_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch, packed, scales_e4m3, tscale);
   }
   check_launch("nvfp4_quantize");
+}
+
+static GgmlSrc make_ggml_src(const uint8_t* raw, int type, long long n) {
+  const int be = ggml_block_elems(type), bb = ggml_block_bytes(type);
+  if (bb == 0) throw std::runtime_error("ggml: unsupported tensor type " + std::to_string(type));
+  if (n % be != 0) throw std::runtime_error("ggml: element count is not a multiple of the block size");
+  return GgmlSrc{raw, type, be, bb};
+}
+
+void launch_ggml_dequant(const uint8_t* raw, int type, long long n, __nv_bfloat16* out, cudaStream_t s) {
+  if (n <= 0) return;
+  ggml_dequant_kernel<<<grid_for((n + 7) / 8, 256), 256, 0, s>>>(make_ggml_src(raw, type, n), n, out);
+  check_launch("ggml_dequant");
+}
+
+void launch_ggml_to_nvfp4(const uint8_t* raw, int type, long long rows, long long K, bool hadamard, uint8_t* packed,
+                          uint8_t* scales_e4m3, float* tscale, unsigned int* amax_scratch, cudaStream_t s) {
+  if (K % 16 != 0) throw std::runtime_error("ggml_to_nvfp4: K must be a multiple of 16");
+  const long long nblocks = rows * (K / 16);
+  if (nblocks <= 0) return;
+  GgmlSrc src = make_ggml_src(raw, type, rows * K);
+  cudaMemsetAsync(amax_scratch, 0, sizeof(unsigned int), s);
+  const int g = grid_for(nblocks, 256);
+  nvfp4_amax_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch);
+  nvfp4_quantize_kernel<<<g, 256, 0, s>>>(src, nblocks, (int)hadamard, amax_scratch, packed, scales_e4m3, tscale);
+  check_launch("ggml_to_nvfp4");
 }
 
 void launch_nvfp4_dequant(const uint8_t* packed, const void* scales, bool scale_bf16, const float* tscale, long long rows,
