@@ -374,7 +374,7 @@ __device__ __forceinline__ float ggml_elem(const uint8_t* blk, int type, int i) 
       const unsigned int qh = (unsigned int)blk[2] | ((unsigned int)blk[3] << 8) | ((unsigned int)blk[4] << 16) | ((unsigned int)blk[5] << 24);
       const uint8_t* qs = blk + 6;
       const int lo = i < 16 ? (qs[i] & 0xF) : (qs[i - 16] >> 4);
-      return ld_half(blk) * (float)((lo | (((qh >> i) & 1u) << 4)) - 16);
+      return ld_half(blk) * (float)((lo | (int)(((qh >> i) & 1u) << 4)) - 16);
     }
     case GGML_Q8_0: return ld_half(blk) * (float)reinterpret_cast<const int8_t*>(blk + 2)[i];
     case GGML_Q4_K:
