@@ -228,3 +228,100 @@ def _cut_at_stop(text: str, stop: Tuple[str, ...]) -> str:
             if i >= 0:
                 cut = min(cut, i)
     return text[:cut].strip()
+
+
+class GraphedGreedyDecoder:
+    """Greedy decoding with the whole per-token step (all layers, exit head, arg-max, state update) captured in ONE
+    CUDA graph and replayed once per token, with no host synchronisation until the requested tokens are done.
+
+    A decode step of a small model is a few hundred kernel launches of a few microseconds each: run eagerly it is bound
+    by launch latency and Python, not by the GPU. Everything that changes between steps lives in device memory: the
+    current token, the position (RoPE rows are gathered by a device index), the recurrent states (updated in place) and
+    the output buffer. On a CPU device the same step function runs eagerly, which is what the tests compare against.
+    """
+
+    def __init__(self, model, batch_size: int = 1, decode_depth: Optional[int] = 2, max_positions: int = 32768):
+        self.model, self.B, self.depth = model, batch_size, decode_depth
+        self.device = next(model.parameters()).device
+        self.max_positions = max_positions
+        self.graph = None
+        self.states: List[Optional[torch.Tensor]] = []
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.step_idx = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.token = torch.zeros(batch_size, 1, dtype=torch.long, device=self.device)
+        self.out: Optional[torch.Tensor] = None
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, prefill_chunk: int = 4096) -> torch.Tensor:
+        """Runs the prompt, loads the static state buffers, returns the first generated token [B, 1]."""
+        m = self.model
+        m.eval()
+        cache = m.init_cache(self.B)
+        logits = None
+        for s in range(0, input_ids.shape[1], prefill_chunk):
+            logits, cache = m(input_ids[:, s : s + prefill_chunk], force_depth=self.depth, cache=cache, last_token_only=True)
+        # make sure every rotary table covers the positions the graph will index
+        for mod in m.modules():
+            if hasattr(mod, "_build") and hasattr(mod, "head_dim") and hasattr(mod, "_cos"):
+                mod(1, self.device, offset=min(self.max_positions, max(mod.max_seq_len, input_ids.shape[1] + 1)) - 1)
+        new_states = [c[0] if isinstance(c, tuple) else None for c in cache]
+        if len(self.states) == len(new_states) and all((a is None) == (b is None) for a, b in zip(self.states, new_states)):
+            for a, b in zip(self.states, new_states):
+                if a is not None:
+                    a.copy_(b)
+        else:
+            self.states = [None if s is None else s.clone() for s in new_states]
+            self.graph = None
+        self.pos.fill_(input_ids.shape[1])
+        self.token.copy_(logits[:, -1].argmax(-1, keepdim=True))
+        return self.token.clone()
+
+    def _step(self):
+        cache = [(s, self.pos) if s is not None else (None, self.pos) for s in self.states]
+        logits, new_cache = self.model(self.token, force_depth=self.depth, cache=cache, last_token_only=True)
+        for s, c in zip(self.states, new_cache):
+            if s is not None and isinstance(c, tuple) and c[0] is not None:
+                s.copy_(c[0])
+        self.out.index_copy_(1, self.step_idx, self.token)
+        self.token.copy_(logits[:, -1].argmax(-1, keepdim=True))
+        self.pos.add_(1)
+        self.step_idx.add_(1)
+
+    @torch.no_grad()
+    def decode(self, max_new_tokens: int) -> torch.Tensor:
+        """-> [B, max_new_tokens] token ids (the first one is the token ``prefill`` returned)."""
+        if self.out is None or self.out.shape[1] < max_new_tokens:
+            self.out = torch.zeros(self.B, max_new_tokens, dtype=torch.long, device=self.device)
+            self.graph = None
+        self.step_idx.zero_()
+        if self.device.type != "cuda":
+            for _ in range(max_new_tokens):
+                self._step()
+            return self.out[:, :max_new_tokens].clone()
+        if self.graph is None:
+            # snapshot, warm up on a side stream (allocator and autotune effects must not land in the capture), restore
+            snap = ([None if s is None else s.clone() for s in self.states], self.pos.clone(), self.token.clone())
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step()
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step()
+            self.graph = g
+            for s, b in zip(self.states, snap[0]):
+                if s is not None:
+                    s.copy_(b)
+            self.pos.copy_(snap[1])
+            self.token.copy_(snap[2])
+            self.step_idx.zero_()
+        for _ in range(max_new_tokens):
+            self.graph.replay()
+        return self.out[:, :max_new_tokens].clone()
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        self.prefill(input_ids)
+        return torch.cat((input_ids, self.decode(max_new_tokens)), dim=1)

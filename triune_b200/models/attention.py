@@ -23,10 +23,13 @@ from .rotary import RotaryEmbedding
 
 def parse_cache(cache: Any) -> Tuple[Optional[torch.Tensor], int, str]:
     """Accept the three cache formats of the reference: tuple (state, offset), dict, bare tensor."""
+    def _off(o):  # a device tensor offset (position kept on the GPU for graph-replayed decoding) passes through
+        return o if torch.is_tensor(o) else int(o)
+
     if isinstance(cache, dict):
-        return cache.get("state"), int(cache.get("offset", 0)), "dict"
+        return cache.get("state"), _off(cache.get("offset", 0)), "dict"
     if isinstance(cache, tuple):
-        return cache[0], int(cache[1]), "tuple"
+        return cache[0], _off(cache[1]), "tuple"
     if torch.is_tensor(cache):
         return cache, 0, "tensor"
     return None, 0, "none"

@@ -23,7 +23,13 @@ class RotaryEmbedding(nn.Module):
         cos, sin = ops.rope_tables(length, self.head_dim, self.base, 0, device)
         self._cos, self._sin = cos, sin
 
-    def forward(self, seq_len: int, device, offset: int = 0):
+    def forward(self, seq_len: int, device, offset=0):
+        if torch.is_tensor(offset):
+            # position lives on the device (CUDA-graph decoding): gather rows; the caller sized the table beforehand
+            if self._cos is None or self._cos.device != torch.device(device):
+                self._build(max(self.max_seq_len, 1), device)
+            pos = offset.reshape(-1)[:1].long() + torch.arange(seq_len, device=offset.device)
+            return self._cos.index_select(0, pos), self._sin.index_select(0, pos)
         need = offset + seq_len
         if self._cos is None or self._cos.device != torch.device(device) or self._cos.shape[0] < need:
             length = max(self.max_seq_len, 1)
