@@ -78,6 +78,33 @@ def main():
     out["overflow_finite"] = bool(torch.isfinite(y.float()).all())
     out["overflow_dropped"] = int((y.float().abs().sum(-1) == 0).sum())
     out["overflow_status"] = ep.check()
+    # model level: an expert-sharded TriuneTransformer computes what the unsharded model computes
+    from triune_b200.config import ModelConfig
+    from triune_b200.models import TriuneTransformer
+    from triune_b200.parallel.expert_parallel import allreduce_replicated_grads, shard_experts
+    from triune_b200.utils import place_model
+
+    torch.manual_seed(3)
+    cfg = ModelConfig(vocab_size=512, hidden_dim=128, num_layers=5, num_heads=2, head_dim=64, num_experts=8, top_k=2,
+                      router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=256, dense_hidden=256)
+    full = place_model(TriuneTransformer.from_config(cfg), dev, torch.bfloat16).eval()
+    import copy
+
+    sharded = copy.deepcopy(full)
+    ep_m = EPContext(8, mode="fused", capacity_factor=4.0)
+    out["model_layers_sharded"] = shard_experts(sharded, ep_m)
+    tok = torch.randint(0, 512, (2, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(10 + r))
+    with torch.no_grad():
+        a = full(tok, force_depth=2)[0].float()
+        b = sharded(tok, force_depth=2)[0].float()
+    out["model_fwd"] = ((a - b).abs().max() / a.abs().max()).item()
+    sharded.train()
+    loss = sharded.forward_loss(tok, tok, force_depth=2)
+    loss = loss[0] if isinstance(loss, tuple) else loss
+    loss.backward()
+    allreduce_replicated_grads(sharded)
+    out["model_loss_finite"] = bool(torch.isfinite(loss))
+    out["model_status"] = ep_m.check()
     sys.stdout.write("\nRESULT " + json.dumps(out) + "\n")
     sys.stdout.flush()
     dist.barrier()

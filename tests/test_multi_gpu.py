@@ -72,3 +72,4 @@ def test_expert_parallel_dispatch_combine():
         for k in ("dx", "dwts", "dw1", "db1", "dw2", "db2"):
             assert r[k] < 4e-2, (k, r)
         assert r["overflow_finite"] and r["overflow_dropped"] > 0
+        assert r["model_layers_sharded"] == 2 and r["model_fwd"] < 3e-2 and r["model_loss_finite"] and r["model_status"] == 0, r

@@ -233,3 +233,73 @@ class ExpertParallelMoE(nn.Module):
         logits = self.router(x2).float()
         idx, w, _ = ops.ref.moe_route(logits, self.expert_bias, self.top_k)
         return ep_experts(x2, idx, w.to(torch.float32), self.w1, self.b1, self.w2, self.b2, self.ep).view(shape)
+
+
+class EPMoE_FFN(nn.Module):
+    """Drop-in replacement for :class:`triune_b200.models.moe.MoE_FFN` holding only this rank's experts.
+
+    The router, the selection bias and the shared expert are replicated; routed experts ``[rank * E/ep, (rank+1) * E/ep)``
+    live here. Capacity is the per-(expert, source rank) segment size of the dispatch buffers
+    (``EPContext.capacity_factor``), which plays the role of the reference's ``ceil(N / E * 1.5)`` admission limit.
+    """
+
+    def __init__(self, moe: nn.Module, ep: EPContext):
+        super().__init__()
+        self.ep, self.dim, self.num_experts, self.top_k = ep, moe.dim, moe.num_experts, moe.top_k
+        self.shared_scale = moe.shared_scale
+        lo, hi = ep.rank * ep.experts_per_rank, (ep.rank + 1) * ep.experts_per_rank
+        self.router, self.shared = moe.router, moe.shared
+        self.register_buffer("expert_bias", moe.expert_bias.detach().clone())
+        for name in ("w1", "b1", "w2", "b2"):
+            setattr(self, name, nn.Parameter(getattr(moe, name).detach()[lo:hi].clone()))
+        self._pending_bias_update = None
+
+    def forward(self, x: torch.Tensor, update_stats: bool = True) -> torch.Tensor:
+        B, T, D = x.shape
+        x2 = x.reshape(B * T, D)
+        logits = ops.linear(x2, self.router.weight, self.router.bias).float()
+        if ops.route_plan_supported(logits, self.top_k):
+            idx, w, _keep, _plan = ops.moe_route_plan(logits, self.expert_bias, self.top_k, 1.0, None)
+        else:
+            idx, w, _ = ops.moe_route(logits, self.expert_bias, self.top_k, 1.0)
+        out = ep_experts(x2, idx, w.float(), self.w1, self.b1, self.w2, self.b2, self.ep)
+        if self.shared is not None:
+            out = out + self.shared_scale * self.shared(x2)
+        return out.reshape(B, T, D)
+
+    def step_bias(self) -> None:  # selection-bias updates need global counts; kept fixed under expert parallelism
+        self._pending_bias_update = None
+
+
+def shard_experts(model: nn.Module, ep: EPContext) -> int:
+    """Replace every ``MoE_FFN`` of ``model`` by an :class:`EPMoE_FFN` with this rank's slice of its experts. Every rank
+    must hold the same full model when this is called (e.g. same seed or a broadcast). Returns the number of layers."""
+    from ..models.moe import MoE_FFN
+
+    n = 0
+    for parent in model.modules():
+        for name, child in list(parent.named_children()):
+            if isinstance(child, MoE_FFN):
+                setattr(parent, name, EPMoE_FFN(child, ep))
+                n += 1
+    return n
+
+
+def allreduce_replicated_grads(model: nn.Module, group=None) -> None:
+    """Average the gradients of parameters that every rank holds (everything except the local experts): with expert
+    parallelism each rank sees different tokens, so replicated weights need data-parallel averaging while expert
+    gradients are already complete on their owner."""
+    group = group if group is not None else dist.group.WORLD
+    world = dist.get_world_size(group)
+    expert_ids = {id(p) for m in model.modules() if isinstance(m, EPMoE_FFN) for p in (m.w1, m.b1, m.w2, m.b2)}
+    grads = [p.grad for p in model.parameters() if p.grad is not None and id(p) not in expert_ids]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    dist.all_reduce(flat, group=group)
+    flat.div_(world)
+    off = 0
+    for g in grads:
+        n = g.numel()
+        g.copy_(flat[off : off + n].view_as(g).to(g.dtype))
+        off += n
