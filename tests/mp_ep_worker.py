@@ -98,6 +98,12 @@ def main():
         a = full(tok, force_depth=2)[0].float()
         b = sharded(tok, force_depth=2)[0].float()
     out["model_fwd"] = ((a - b).abs().max() / a.abs().max()).item()
+    out["model_fwd_mean"] = ((a - b).abs().mean() / a.abs().mean()).item()
+    moe_full, moe_ep = full.layers[3].ffn, sharded.layers[3].ffn
+    xin = torch.randn(2, 128, 128, device=dev, generator=torch.Generator(device=dev).manual_seed(20 + r)).bfloat16()
+    with torch.no_grad():
+        ya, yb = moe_full(xin).float(), moe_ep(xin).float()
+    out["layer_fwd"] = ((ya - yb).abs().max() / ya.abs().max()).item()
     sharded.train()
     loss = sharded.forward_loss(tok, tok, force_depth=2)
     loss = loss[0] if isinstance(loss, tuple) else loss
