@@ -404,3 +404,100 @@ def test_sandbox_validation_and_limits():
         assert not sb.execute_code(bad)["success"]
     assert sb.execute_code("while True: pass")["timed_out"]
     assert "ZeroDivisionError" in sb.execute_code("result = 1/0")["error"]
+
+
+# ------------------------------------------------------------------------------------------------ DAG / plugins / agents / engines
+def test_dag_validation_execution_and_signed_plugins(tmp_path):
+    from triune_b200.execution.dag import DAGValidationError, execute_dag, node_catalog, parse_dag
+    from triune_b200.plugins.registry import PluginError, PluginRegistry, file_sha256, sign_manifest
+
+    over = {"vocab_size": 256, "hidden_dim": 64, "num_heads": 2, "head_dim": 32}
+    spec = {"nodes": [{"id": "m", "type": "load_model", "params": {"model": "triune-nano", "overrides": over}}, {"id": "i", "type": "model_info"},
+                      {"id": "t", "type": "text", "params": {"text": "hi"}}, {"id": "g", "type": "generate", "params": {"max_new_tokens": 3}},
+                      {"id": "p", "type": "python", "params": {"code": "result = value['parameters'] > 0"}}],
+            "edges": [{"from": "m.model", "to": "i.model"}, {"from": "m.model", "to": "g.model"}, {"from": "t.out", "to": "g.prompt"},
+                      {"from": "i.out", "to": "p.value"}]}
+    r = execute_dag(spec)
+    assert r["order"].index("m") < r["order"].index("g") and r["outputs"]["p.out"] is True and isinstance(r["outputs"]["g.text"], str)
+    for bad in ({"nodes": [{"id": "a", "type": "nope"}]}, {"nodes": [{"id": "a", "type": "concat_text"}]},
+                {"nodes": [{"id": "a", "type": "text"}, {"id": "b", "type": "model_info"}], "edges": [{"from": "a.out", "to": "b.model"}]},
+                {"nodes": [{"id": "a", "type": "python"}, {"id": "b", "type": "python"}],
+                 "edges": [{"from": "a.out", "to": "b.value"}, {"from": "b.out", "to": "a.value"}]}):
+        with pytest.raises(DAGValidationError):
+            parse_dag(bad)
+    assert any(n["type"] == "train_steps" for n in node_catalog())
+    (tmp_path / "p1").mkdir()
+    (tmp_path / "p1" / "main.py").write_text("def register(api):\n    @api.register_node('double', {'x': 'any'}, {'out': 'any'})\n"
+                                              "    def f(i, p, c):\n        return {'out': i['x'] * 2}\n")
+    sha = file_sha256(tmp_path / "p1" / "main.py")
+    key = "k" * 32
+    (tmp_path / "p1" / "plugin.json").write_text(json.dumps({"name": "p1", "version": "1", "entry": "main.py", "sha256": sha,
+                                                              "signature": sign_manifest("p1", "1", sha, key)}))
+    reg = PluginRegistry(key=key)
+    reg.discover(tmp_path)
+    assert reg.load("p1").nodes == ["p1.double"]
+    out = execute_dag({"nodes": [{"id": "c", "type": "constant", "params": {"value": 21}}, {"id": "d", "type": "p1.double"}],
+                       "edges": [{"from": "c.out", "to": "d.x"}]})
+    assert out["outputs"]["d.out"] == 42
+    wrong = PluginRegistry(key="z" * 32)
+    wrong.discover(tmp_path)
+    with pytest.raises(PluginError):
+        wrong.load("p1")
+    (tmp_path / "p1" / "main.py").write_text("def register(api):\n    pass\n# tampered\n")
+    fresh = PluginRegistry(key=key)
+    fresh.discover(tmp_path)
+    with pytest.raises(PluginError):
+        fresh.load("p1")
+
+
+def test_agent_tools_and_url_guard():
+    from triune_b200.agents import Agent, AgentMemory, MultiAgentOrchestrator, build_integrated_toolbelt, is_safe_public_url
+
+    urls = ("http://127.0.0.1/x", "http://10.0.0.5", "https://224.0.0.1", "https://239.1.1.1", "ftp://example.com", "http://[ff02::1]/",
+            "http://localhost:8000", "http://169.254.169.254/latest")
+    assert not any(is_safe_public_url(u, resolve=False) for u in urls) and is_safe_public_url("http://93.184.216.34/", resolve=False)
+    replies = iter(['<|tool_call|>{"tool": "python", "args": {"code": "result = 6*7"}}\n', "The answer is 42.", "ok"])
+    a = Agent(lambda p: next(replies), tools=build_integrated_toolbelt())
+    r = a.run("what is 6*7?")
+    assert r["text"] == "The answer is 42." and r["tool_calls"][0]["result"]["result"] == 42
+    assert MultiAgentOrchestrator({"a": a}).run("again")[0]["text"] == "ok"
+    mem = AgentMemory(max_items=2)
+    for k in "abc":
+        mem.set(k, k)
+    assert mem.get("a") is None and mem.get("c") == "c" and mem.delete("c") and not mem.delete("c")
+
+
+def test_parallel_engine_and_disk_streaming(tmp_path):
+    from triune_b200.runtime.disk_streaming import DiskNVFP4StreamingEngine, build_nvfp4_disk_cache, describe_cache
+    from triune_b200.runtime.model_scanner import scan_models
+    from triune_b200.runtime.parallel_engine import ParallelEngine
+
+    torch.manual_seed(0)
+    e = ParallelEngine(dim=64, heads=2, head_dim=32, num_experts=4, device="cpu")
+    x = torch.randn(3, 64, 64)
+    o, s = e.prefill_batched(x)
+    assert o.shape == (3, 64, 64) and s.shape == (3, 2, 32, 32) and e.forward(x).shape == x.shape
+    r = e.score_draft_chunks(torch.ones(2, 4, 8), torch.ones(2, 4, 8), 0.9)
+    assert r["contiguous_accepted"].tolist() == [4, 4] and float(r["acceptance_rate"]) == 1.0
+    assert e.benchmark_throughput(2, 64, iters=1, warmup=1)["tokens_per_s"] > 0
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.LlamaConfig(vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                                   num_key_value_heads=2, tie_word_embeddings=False)
+    m = transformers.LlamaForCausalLM(cfg).eval()
+    m.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    man = build_nvfp4_disk_cache(tmp_path / "hf", tmp_path / "cache", hadamard=False, device="cpu")
+    assert man["num_layers"] == 3 and man["compression"] > 2.5 and "mlp.up_proj" in man["quantized_modules"][0]
+    assert build_nvfp4_disk_cache(tmp_path / "hf", tmp_path / "cache", hadamard=False, device="cpu") == man  # reused, not rebuilt
+    eng = DiskNVFP4StreamingEngine(tmp_path / "cache", "cpu", dtype=torch.float32, prefetch=1, resident_budget_gb=0)
+    st = eng.layer_state(0)
+    w, ref_w = st["self_attn.q_proj.weight"], m.model.layers[0].self_attn.q_proj.weight
+    assert torch.nn.functional.cosine_similarity(w.flatten(), ref_w.flatten(), dim=0) > 0.99
+    assert torch.allclose(st["input_layernorm.weight"], m.model.layers[0].input_layernorm.weight, atol=1e-2)
+    for i in range(3):
+        eng.layer_state(i)
+    assert eng.telemetry["layers_loaded"] >= 3 and eng.telemetry["evictions"] >= 1
+    assert "model.embed_tokens.weight" in eng.root_state()
+    eng.close()
+    assert describe_cache(tmp_path / "cache")["num_layers"] == 3
+    counts = scan_models([str(tmp_path)])["counts"]
+    assert counts.get("hf_model") == 1 and counts.get("nvfp4_cache") == 1

@@ -1,0 +1,153 @@
+"""Agent harness (thin version of ``triune/agents/*.py``): personas, key/value memory, a tool registry with an
+outbound-URL guard, and a loop that lets a locally served model call tools.
+
+The model proposes tool calls as ``<|tool_call|>{"tool": name, "args": {...}}`` lines; results are fed back as
+``<|tool_return|>...``. The provider is the in-process engine (no remote keys); the orchestrator runs agents in turn.
+"""
+
+from __future__ import annotations
+
+import ipaddress
+import json
+import re
+import socket
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional
+from urllib.parse import urlparse
+
+
+@dataclass
+class Tool:
+    name: str
+    description: str
+    fn: Callable[..., Any]
+    parameters: Dict[str, str] = field(default_factory=dict)
+
+
+class ToolRegistry:
+    def __init__(self):
+        self.tools: Dict[str, Tool] = {}
+
+    def register(self, tool: Tool) -> None:
+        self.tools[tool.name] = tool
+
+    def call(self, name: str, **args) -> Any:
+        if name not in self.tools:
+            raise KeyError(f"unknown tool {name!r}")
+        return self.tools[name].fn(**args)
+
+    def describe(self) -> List[Dict[str, Any]]:
+        return [{"name": t.name, "description": t.description, "parameters": t.parameters} for t in self.tools.values()]
+
+
+_GROUP_NETS = (ipaddress.ip_network("224.0.0.0/4"), ipaddress.ip_network("ff00::/8"))  # group-addressed ranges
+
+
+def is_safe_public_url(url: str, resolve: bool = True) -> bool:
+    """Only http(s) URLs whose host resolves exclusively to public addresses: loopback, private, link-local, reserved,
+    unspecified and group-addressed targets are refused (server-side request forgery guard)."""
+    try:
+        u = urlparse(url)
+        if u.scheme not in ("http", "https") or not u.hostname:
+            return False
+        host = u.hostname
+        try:
+            addrs = [ipaddress.ip_address(host)]
+        except ValueError:
+            if not resolve:
+                return not host.endswith((".local", ".internal", ".localhost")) and host != "localhost"
+            addrs = [ipaddress.ip_address(ai[4][0]) for ai in socket.getaddrinfo(host, None)]
+        return bool(addrs) and all(a.is_global and not a.is_loopback and not a.is_private and not a.is_link_local
+                                   and not a.is_reserved and not a.is_unspecified and not any(a in n for n in _GROUP_NETS if n.version == a.version)
+                                   for a in addrs)
+    except (OSError, ValueError):
+        return False
+
+
+def build_integrated_toolbelt() -> ToolRegistry:
+    from ..runtime.sandbox import PythonSandbox
+
+    reg = ToolRegistry()
+    reg.register(Tool("python", "run Python in the restricted sandbox; set `result`", lambda code: PythonSandbox(5).execute_code(code), {"code": "str"}))
+    reg.register(Tool("clock", "current UTC time", lambda: time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())))
+    reg.register(Tool("check_url", "whether a URL is a safe public target", lambda url: is_safe_public_url(url, resolve=False), {"url": "str"}))
+    return reg
+
+
+@dataclass
+class Persona:
+    name: str = "assistant"
+    system_prompt: str = "You are a helpful assistant."
+    temperature: float = 0.7
+
+
+class AgentMemory:
+    def __init__(self, max_items: int = 256):
+        self.items: Dict[str, Any] = {}
+        self.max_items = max_items
+
+    def set(self, key: str, value: Any) -> None:
+        self.items[key] = value
+        while len(self.items) > self.max_items:
+            self.items.pop(next(iter(self.items)))
+
+    def get(self, key: str, default=None):
+        return self.items.get(key, default)
+
+    def delete(self, key: str) -> bool:
+        return self.items.pop(key, None) is not None
+
+    def clear(self) -> None:
+        self.items.clear()
+
+
+_CALL = re.compile(r"<\|tool_call\|>\s*(\{.*?\})\s*(?:$|\n)", re.S)
+
+
+class Agent:
+    def __init__(self, generate: Callable[[str], str], persona: Optional[Persona] = None, tools: Optional[ToolRegistry] = None,
+                 memory: Optional[AgentMemory] = None, max_tool_rounds: int = 3):
+        self.generate, self.persona = generate, persona or Persona()
+        self.tools, self.memory, self.max_tool_rounds = tools or ToolRegistry(), memory or AgentMemory(), max_tool_rounds
+        self.transcript: List[Dict[str, str]] = []
+
+    def _prompt(self, user: str) -> str:
+        tools = "\n".join(f"- {t['name']}: {t['description']}" for t in self.tools.describe())
+        hist = "".join(f"{m['role'].capitalize()}: {m['content']}\n" for m in self.transcript[-8:])
+        return f"System: {self.persona.system_prompt}\nTools:\n{tools}\n{hist}User: {user}\nAssistant:"
+
+    def run(self, user: str) -> Dict[str, Any]:
+        calls = []
+        prompt = self._prompt(user)
+        text = ""
+        for _ in range(self.max_tool_rounds + 1):
+            text = self.generate(prompt)
+            m = _CALL.search(text)
+            if not m:
+                break
+            try:
+                req = json.loads(m.group(1))
+                result = self.tools.call(req["tool"], **req.get("args", {}))
+            except Exception as e:
+                result = f"error: {type(e).__name__}: {e}"
+            calls.append({"request": m.group(1), "result": result})
+            prompt += f"{text}\n<|tool_return|>{json.dumps(result, default=str)}\nAssistant:"
+        self.transcript += [{"role": "user", "content": user}, {"role": "assistant", "content": text}]
+        return {"text": text, "tool_calls": calls, "persona": self.persona.name}
+
+
+class MultiAgentOrchestrator:
+    def __init__(self, agents: Dict[str, Agent]):
+        self.agents = agents
+
+    def run(self, task: str, order: Optional[List[str]] = None) -> List[Dict[str, Any]]:
+        out, msg = [], task
+        for name in order or list(self.agents):
+            r = self.agents[name].run(msg)
+            out.append({"agent": name, **r})
+            msg = f"{task}\n\nPrevious agent ({name}) said: {r['text']}"
+        return out
+
+
+__all__ = ["Tool", "ToolRegistry", "build_integrated_toolbelt", "is_safe_public_url", "Persona", "AgentMemory", "Agent", "MultiAgentOrchestrator"]
