@@ -132,6 +132,38 @@ def case_ce(a):
     report(f"cross_entropy fwd+grad {a.m}x{a.n}", ms, nbytes=6.0 * a.m * a.n)
 
 
+def case_mlp(a):
+    """Dense FFN forward + backward: the GELU-epilogue GEMM, the GELU'-epilogue data-gradient GEMM, two weight-gradient
+    GEMMs and the plain GEMMs, at the benchmark model's shapes (tokens x d -> hidden -> d)."""
+    from . import ops
+
+    M, d, H = a.m, a.k, a.n
+    x = torch.randn(M, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w1 = (torch.randn(H, d, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b1 = torch.zeros(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w2 = (torch.randn(d, H, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b2 = torch.zeros(d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(M, d, device="cuda", dtype=torch.bfloat16)
+
+    def fb():
+        for t in (x, w1, b1, w2, b2):
+            t.grad = None
+        ops.mlp_gelu(x, w1, b1, w2, b2).backward(g)
+
+    ms = timeit(fb, a.iters, a.warmup)
+    report(f"mlp_gelu fwd+bwd {M}x{d}x{H}", ms, flops=6.0 * 2.0 * M * d * H, nbytes=2.0 * M * (4 * d + 3 * H))
+
+
+def case_moe_route(a):
+    from . import ops
+
+    N, E = a.m, a.n
+    logits = torch.randn(N, E, device="cuda")
+    bias = torch.zeros(E, device="cuda")
+    ms = timeit(lambda: ops.moe_route_plan(logits, bias, 2, 1.0, int(N / E * 1.5)), a.iters, a.warmup)
+    report(f"moe_route_plan N={N} E={E} k=2 (route + sort + plan)", ms, nbytes=4.0 * N * E + 2 * N * (8 + 4 + 8 + 4 + 1))
+
+
 def case_fp8(a):
     from .ops import quant_cuda, reference as ref
 
@@ -161,7 +193,7 @@ def case_nvfp4(a):
     report(f"nvfp4_quantize {N}x{K}", ms, nbytes=N * K * 4.5625)
 
 
-CASES = {"fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
+CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():
