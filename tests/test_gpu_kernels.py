@@ -441,3 +441,37 @@ def test_graph_replayed_decoder_matches_eager_generation():
     assert got == again
     agree = sum(a == b for a, b in zip(got, want)) / 24
     assert agree >= 0.9, (got, want)  # bf16 arg-max ties between two nearly equal logits may flip a token
+
+
+def test_layer_streaming_on_gpu_matches_resident_model():
+    """Layers staged from pinned host memory on a side stream give the loss and the update of the resident model."""
+    from triune_b200.config import ModelConfig
+    from triune_b200.models import TriuneTransformer
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming
+    from triune_b200.utils import place_model
+
+    cfg = ModelConfig(vocab_size=512, hidden_dim=128, num_layers=6, num_heads=2, head_dim=64, num_experts=8, top_k=2,
+                      router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=4, expert_hidden=256, dense_hidden=256)
+    torch.manual_seed(0)
+    a = place_model(TriuneTransformer.from_config(cfg), torch.device("cuda"), torch.bfloat16)
+    torch.manual_seed(0)
+    b = TriuneTransformer.from_config(cfg).to(torch.bfloat16)
+    eng = enable_layer_streaming(b, "cuda", config=StreamingConfig(resident_gpu_layers=1))
+    x = torch.randint(0, 512, (4, 128), device="cuda")
+    y = torch.randint(0, 512, (4, 128), device="cuda")
+
+    def loss_of(m):
+        out = m.forward_loss(x, y, force_depth=2)
+        return out[0] if isinstance(out, tuple) else out
+
+    la, lb = loss_of(a), loss_of(b)
+    assert abs(float(la) - float(lb)) < 2e-2
+    lb.backward()
+    tel = eng.get_telemetry()
+    assert tel["h2d_copies"] >= 10 and tel["d2h_copies"] >= 5 and tel["peak_staged_layers"] <= 3  # each streamed layer: fwd + bwd
+    assert all(p.device.type == "cpu" for p in b.layers[3].parameters())  # evicted after use
+    norm = eng.step_streaming_optimizer(None, lr=1e-2)
+    assert norm > 0
+    lb2 = loss_of(b)
+    assert torch.isfinite(lb2) and abs(float(lb2) - float(lb)) > 1e-4
+    eng.detach()
