@@ -317,8 +317,8 @@ class _StreamedLayerFn(torch.autograd.Function):
         return None, None, None, None, None, xd.grad
 
 
-def enable_layer_streaming(model: nn.Module, device, **kw) -> LayerStreamingEngine:
-    cfg = StreamingConfig(**{k: v for k, v in kw.items() if k in StreamingConfig.__dataclass_fields__})
+def enable_layer_streaming(model: nn.Module, device, config: Optional[StreamingConfig] = None, **kw) -> LayerStreamingEngine:
+    cfg = config or StreamingConfig(**{k: v for k, v in kw.items() if k in StreamingConfig.__dataclass_fields__})
     eng = LayerStreamingEngine(model, device, cfg).attach()
     model._streaming_engine = eng
     return eng
