@@ -55,16 +55,20 @@ def test_gemm_epilogues(dev):
     a = torch.randn(M, K, device=dev, dtype=torch.bfloat16) * 0.5
     b = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.1
     bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
-    pre = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-    h = ops.gemm(a, b, bias=bias, gelu=True, aux_out=pre)
-    ref_pre = a.float() @ b.float().t() + bias.float()
-    assert _rel(pre, ref_pre) < 2e-2
-    assert _rel(h, F.gelu(ref_pre, approximate="tanh")) < 2e-2
-    # derivative epilogue
-    g = ops.gemm(a, b, dgelu_aux=pre)
-    x = pre.float().requires_grad_(True)
-    F.gelu(x, approximate="tanh").sum().backward()
-    assert _rel(g, (a.float() @ b.float().t()) * x.grad) < 3e-2
+    dact = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    h = ops.gemm(a, b, bias=bias, gelu=True, aux_out=dact)
+    ref_pre = (a.float() @ b.float().t() + bias.float()).requires_grad_(True)
+    ref_h = F.gelu(ref_pre, approximate="tanh")
+    ref_h.sum().backward()
+    assert _rel(h, ref_h.detach()) < 2e-2
+    assert _rel(dact, ref_pre.grad) < 2e-2  # the forward epilogue also emits GELU'(pre-activation)
+    h2 = ops.gemm(a, b, bias=bias, gelu=True)  # inference form: no derivative tile
+    assert torch.equal(h2, h)
+    # derivative epilogue: multiply by the saved rows
+    g = ops.gemm(a, b, dgelu_aux=dact)
+    assert _rel(g, (a.float() @ b.float().t()) * ref_pre.grad) < 3e-2
+    g2 = ops.gemm(a, b.t().contiguous(), b_mn=True, dgelu_aux=dact, alpha=0.5)
+    assert _rel(g2, 0.5 * (a.float() @ b.float().t()) * ref_pre.grad) < 3e-2
     # fp32 accumulate
     c = torch.ones(M, N, device=dev, dtype=torch.float32)
     ops.gemm(a, b, c, accumulate=True, alpha=0.5)

@@ -252,6 +252,45 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Packed fp32 pairs (Blackwell f32x2 arithmetic): one instruction per two values. A pair lives in a 64-bit register.
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t bf16x2_to_f2(uint32_t x) {
+  return pack_f2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {
+  float lo, hi;
+  unpack_f2(v, lo, hi);
+  return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ uint64_t tanh2(uint64_t u) {
+  float a, b, ta, tb;
+  unpack_f2(u, a, b);
+  asm("tanh.approx.f32 %0, %1;" : "=f"(ta) : "f"(a));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(tb) : "f"(b));
+  return pack_f2(ta, tb);
+}
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);

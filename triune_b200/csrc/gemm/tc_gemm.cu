@@ -6,8 +6,9 @@
 //   warp 1    MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) reading the stages through
 //             shared-memory descriptors and accumulating into TMEM; tcgen05.commit releases a stage
 //             back to the producer and, after the last K step, publishes the accumulator;
-//   warps 2-9 epilogue: tcgen05.ld the fp32 accumulator (lane == output row), apply bias / GELU /
-//             GELU' / row scale / accumulate, convert and store 16-byte vectors.
+//   warps 2-9 epilogue: tcgen05.ld the fp32 accumulator (lane == output row), apply the epilogue in packed
+//             f32x2 arithmetic (bias, GELU plus its derivative, multiply by saved rows, row scale), stage the
+//             converted rows in shared memory and hand them to TMA (store or reduce-add).
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1. No cluster multicast is used; every CTA loads its own tiles.
 //
@@ -17,6 +18,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -121,7 +123,14 @@ __device__ __forceinline__ void report(const KParams& p, int code) {
   if (p.status != nullptr) atomicCAS(p.status, 0, code);
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// Epilogue kinds (compile-time, so the plain stores do not carry the activation code's registers):
+//   EPI_PLAIN      alpha, bias, row scale, bf16 output (store or reduce-add)
+//   EPI_PLAIN_F32  the same with an fp32 output (weight-gradient accumulation, split-K)
+//   EPI_GELU       bias, tanh-GELU, bf16 output; optionally GELU'(pre-activation) as a second bf16 output
+//   EPI_MULAUX     output = alpha * acc * aux_in (the backward of EPI_GELU: aux_in holds GELU')
+enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3 };
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const KParams p) {
@@ -288,11 +297,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint8_t* my_stage = smem_epi + (warp - 2) * EPI_TILE;  // one staging tile per warp (a second one costs a load stage and measured slower)
     int acc = 0;
     uint32_t acc_phase = 0;
-    const bool out_f32 = (p.flags & GF_OUT_F32) != 0;
+    constexpr bool out_f32 = (EPI == EPI_PLAIN_F32);
+    constexpr int CW = out_f32 ? 32 : 64;  // columns per staged chunk (128 bytes)
+    constexpr int NP = CW / 2;             // packed fp32 pairs per lane and chunk
     const bool reduce_add = ((p.flags & GF_ACCUMULATE) != 0) || p.splits > 1;
-    const bool do_gelu = (p.flags & GF_GELU) != 0;
-    const bool do_dgelu = (p.flags & GF_DGELU) != 0;
-    const int CW = out_f32 ? 32 : 64;  // columns per staged chunk
+    const uint64_t alpha2 = pack_f2(p.alpha, p.alpha);
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       Tile tl = decode_tile(p, t);
       if (!tl.valid) continue;
@@ -309,114 +318,144 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const int out_batch = (p.mode == GEMM_GROUPED_M) ? 0 : tl.g;
       const long long c_off = (long long)out_batch * p.strideC + (long long)gm * p.ldc;
       const __nv_bfloat16* bias = p.bias ? p.bias + (long long)tl.g * p.bias_stride : nullptr;
-      const float rs = (p.row_scale && row_ok) ? p.row_scale[gm] : 1.0f;
 #pragma unroll 1
       for (int c = col_half * CW; c < BN; c += 2 * CW) {
         if (n0 + c >= p.N) break;
-        float v[64];
-        // GELU' operand: issue the row loads first so their latency hides behind the TMEM reads
+        uint64_t v[NP];
+        // Multiplier rows (the activation derivative saved by the forward pass): issue the loads first so their
+        // latency hides behind the TMEM reads.
         uint4 auxv[8];
-        if (do_dgelu && row_ok) {
+        if constexpr (EPI == EPI_MULAUX) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int gn = n0 + c + j * 8;
-            auxv[j] = gn < p.N ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn) : make_uint4(0u, 0u, 0u, 0u);
+            auxv[j] = (row_ok && gn < p.N) ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn)
+                                           : make_uint4(0u, 0u, 0u, 0u);
           }
         }
         if (tl.k_iters > 0) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c, r);
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c;
+          tmem_ld_32x32b_x32(taddr, r0);
+          if (!out_f32) tmem_ld_32x32b_x32(taddr + 32, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          for (int i = 0; i < 16; ++i) v[i] = pack_f2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
           if (!out_f32) {
-            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c + 32, r);
-            tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]) * p.alpha;
+            for (int i = 0; i < 16; ++i)
+              v[(NP - 16) + i] = pack_f2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = 0.f;
+          for (int i = 0; i < NP; ++i) v[i] = 0ull;
         }
-        const int ngroups = CW / 8;
+        // alpha and bias: one packed fma per pair
         if (bias) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int gn = n0 + c + j * 8;
-            if (j < ngroups && gn < p.N) {
-              uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
-              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float2 f = __bfloat1622float2(b2[i]);
-                v[j * 8 + 2 * i] += f.x;
-                v[j * 8 + 2 * i + 1] += f.y;
-              }
-            }
-          }
-        }
-        if (do_gelu) {
-          if (p.aux_out) {  // pre-activation goes out through the same staging path (always bf16, 64 columns)
-            if (lane == 0) tma_store_wait_read<0>();
-            __syncwarp();
-            uint8_t* st = my_stage;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              uint4 o;
-              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-              *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&tmAux, st, n0 + c, tl.m0 + lane_base, out_batch);
-              tma_store_commit();
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh_f(v[i]);
-        }
-        if (do_dgelu && row_ok) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < NP / 4; ++j) {
             const int gn = n0 + c + j * 8;
             if (gn < p.N) {
-              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&auxv[j]);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float2 f = __bfloat1622float2(a2[i]);
-                v[j * 8 + 2 * i] *= gelu_tanh_grad_f(f.x);
-                v[j * 8 + 2 * i + 1] *= gelu_tanh_grad_f(f.y);
-              }
+              const uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
+              v[j * 4 + 0] = fma2(v[j * 4 + 0], alpha2, bf16x2_to_f2(bv.x));
+              v[j * 4 + 1] = fma2(v[j * 4 + 1], alpha2, bf16x2_to_f2(bv.y));
+              v[j * 4 + 2] = fma2(v[j * 4 + 2], alpha2, bf16x2_to_f2(bv.z));
+              v[j * 4 + 3] = fma2(v[j * 4 + 3], alpha2, bf16x2_to_f2(bv.w));
             }
           }
-        }
-        if (p.row_scale) {
+        } else if (p.alpha != 1.0f) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] *= rs;
+          for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], alpha2);
         }
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
         uint8_t* st = my_stage;
-        if (out_f32) {
+        if constexpr (EPI == EPI_PLAIN_F32) {
+          if (p.row_scale) {
+            const float rs = row_ok ? p.row_scale[gm] : 1.0f;
+            const uint64_t rs2 = pack_f2(rs, rs);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<float4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-        } else {
+            for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], rs2);
+          }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            uint4 o;
-            o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-            o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-            o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-            o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+            float4 o;
+            unpack_f2(v[(j * 2) % NP], o.x, o.y);
+            unpack_f2(v[(j * 2 + 1) % NP], o.z, o.w);
+            *reinterpret_cast<float4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
           }
+        } else {
+          uint32_t q[32];  // the chunk as bf16 pairs
+          if constexpr (EPI == EPI_GELU) {
+            // gelu(x) = h + h t with h = x / 2, t = tanh(k0 (x + k1 x^3)); its derivative
+            // (1 + t) / 2 + h (1 - t^2) k0 (1 + 3 k1 x^2) reuses t and goes out as a second bf16 tile, so the
+            // backward GEMM's epilogue is a single multiply.
+            const uint64_t C0 = pack_f2(0.7978845608028654f, 0.7978845608028654f);
+            const uint64_t C1 = pack_f2(0.0356774081363001f, 0.0356774081363001f);
+            const uint64_t NC0 = pack_f2(-0.7978845608028654f, -0.7978845608028654f);
+            const uint64_t NC3 = pack_f2(-0.1070322244089003f, -0.1070322244089003f);
+            const uint64_t HALF = pack_f2(0.5f, 0.5f);
+            const uint64_t NEG1 = pack_f2(-1.0f, -1.0f);
+            if (p.aux_out) {
+              uint32_t dq[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const uint64_t x = v[i % NP];
+                const uint64_t x2 = mul2(x, x);
+                const uint64_t tt = tanh2(mul2(x, fma2(x2, C1, C0)));
+                const uint64_t h = mul2(x, HALF);
+                q[i] = f2_to_bf16x2(fma2(h, tt, h));
+                const uint64_t sgm = fma2(tt, HALF, HALF);
+                const uint64_t nq = fma2(tt, tt, NEG1);   // -(1 - t^2)
+                const uint64_t ndu = fma2(x2, NC3, NC0);  // -k0 (1 + 3 k1 x^2)
+                dq[i] = f2_to_bf16x2(fma2(mul2(h, nq), ndu, sgm));
+              }
+              if (lane == 0) tma_store_wait_read<0>();
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_uint4(dq[j * 4 + 0], dq[j * 4 + 1], dq[j * 4 + 2], dq[j * 4 + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&tmAux, st, n0 + c, tl.m0 + lane_base, out_batch);
+                tma_store_commit();
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const uint64_t x = v[i % NP];
+                const uint64_t tt = tanh2(mul2(x, fma2(mul2(x, x), C1, C0)));
+                const uint64_t h = mul2(x, HALF);
+                q[i] = f2_to_bf16x2(fma2(h, tt, h));
+              }
+            }
+          } else if constexpr (EPI == EPI_MULAUX) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              q[j * 4 + 0] = f2_to_bf16x2(mul2(v[(j * 4 + 0) % NP], bf16x2_to_f2(auxv[j].x)));
+              q[j * 4 + 1] = f2_to_bf16x2(mul2(v[(j * 4 + 1) % NP], bf16x2_to_f2(auxv[j].y)));
+              q[j * 4 + 2] = f2_to_bf16x2(mul2(v[(j * 4 + 2) % NP], bf16x2_to_f2(auxv[j].z)));
+              q[j * 4 + 3] = f2_to_bf16x2(mul2(v[(j * 4 + 3) % NP], bf16x2_to_f2(auxv[j].w)));
+            }
+          } else {
+            if (p.row_scale) {
+              const float rs = row_ok ? p.row_scale[gm] : 1.0f;
+              const uint64_t rs2 = pack_f2(rs, rs);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(mul2(v[i % NP], rs2));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(v[i % NP]);
+            }
+          }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(q[j * 4 + 0], q[j * 4 + 1], q[j * 4 + 2], q[j * 4 + 3]);
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -448,10 +487,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int EPI>
 void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmAux,
                     const KParams& kp, int grid, cudaStream_t stream) {
-  auto kern = tc_gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = tc_gemm_kernel<BN, A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES);
@@ -463,13 +502,25 @@ void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
   if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm launch failed: ") + cudaGetErrorString(e));
 }
 
+template <int BN, bool A_MN, bool B_MN>
+void dispatch_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                  const CUtensorMap& tmAux, const KParams& kp, int grid, cudaStream_t s) {
+  if (epi == EPI_PLAIN) return launch_variant<BN, A_MN, B_MN, EPI_PLAIN>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  if (epi == EPI_PLAIN_F32) return launch_variant<BN, A_MN, B_MN, EPI_PLAIN_F32>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  if constexpr (!A_MN) {  // the activation epilogues follow row-major activations
+    if (epi == EPI_GELU) return launch_variant<BN, A_MN, B_MN, EPI_GELU>(tmA, tmB, tmC, tmAux, kp, grid, s);
+    if (epi == EPI_MULAUX) return launch_variant<BN, A_MN, B_MN, EPI_MULAUX>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  }
+  throw std::runtime_error("tc_gemm: activation epilogues need a K-major A operand");
+}
+
 template <int BN>
-void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+void dispatch_major(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                     const CUtensorMap& tmAux, const KParams& kp, int grid, cudaStream_t s) {
-  if (!a_mn && !b_mn) launch_variant<BN, false, false>(tmA, tmB, tmC, tmAux, kp, grid, s);
-  else if (!a_mn && b_mn) launch_variant<BN, false, true>(tmA, tmB, tmC, tmAux, kp, grid, s);
-  else if (a_mn && !b_mn) launch_variant<BN, true, false>(tmA, tmB, tmC, tmAux, kp, grid, s);
-  else launch_variant<BN, true, true>(tmA, tmB, tmC, tmAux, kp, grid, s);
+  if (!a_mn && !b_mn) dispatch_epi<BN, false, false>(epi, tmA, tmB, tmC, tmAux, kp, grid, s);
+  else if (!a_mn && b_mn) dispatch_epi<BN, false, true>(epi, tmA, tmB, tmC, tmAux, kp, grid, s);
+  else if (a_mn && !b_mn) dispatch_epi<BN, true, false>(epi, tmA, tmB, tmC, tmAux, kp, grid, s);
+  else dispatch_epi<BN, true, true>(epi, tmA, tmB, tmC, tmAux, kp, grid, s);
 }
 
 int sm_count() {
@@ -494,12 +545,23 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.mode == GEMM_GROUPED_M && a.tile_group == nullptr) throw std::runtime_error("tc_gemm: tile_group missing");
   if ((a.flags & GF_OUT_F32) && (a.flags & (GF_GELU | GF_DGELU)))
     throw std::runtime_error("tc_gemm: activation epilogues write bf16 outputs");
+  if ((a.flags & (GF_GELU | GF_DGELU)) && a.row_scale != nullptr)
+    throw std::runtime_error("tc_gemm: activation epilogues take no row scale");
+  if ((a.flags & GF_GELU) && (a.flags & GF_DGELU)) throw std::runtime_error("tc_gemm: one activation epilogue at a time");
+  if ((a.flags & GF_DGELU) && a.aux_in == nullptr) throw std::runtime_error("tc_gemm: multiplier rows missing");
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0) throw std::runtime_error("tc_gemm: C must be 16-byte aligned");
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
 
   // widest tile that divides N: the tensor core is most efficient at N = 256, then 192 (e.g. N = 384), then 128
-  const int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : ((a.N >= 192 && a.N % 192 == 0) ? 192 : (a.N > 64 ? 128 : 64));
+  int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : ((a.N >= 192 && a.N % 192 == 0) ? 192 : (a.N > 64 ? 128 : 64));
+  {
+    static const int forced = [] {
+      const char* e = std::getenv("TRIUNE_GEMM_BN");  // experiments only: force the tile width
+      return e ? std::atoi(e) : 0;
+    }();
+    if (forced == 64 || forced == 128 || forced == 192 || forced == 256) BN = forced;
+  }
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
   kp.mode = a.mode; kp.flags = a.flags; kp.batch = a.batch < 1 ? 1 : a.batch;
@@ -563,10 +625,11 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
     tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.M, c_batches,
                          (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 64, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
-  if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
-  else if (BN == 192) dispatch_major<192>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
-  else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
-  else dispatch_major<64>(a.a_mn_major, a.b_mn_major, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  const int epi = (kp.flags & GF_GELU) ? EPI_GELU : ((kp.flags & GF_DGELU) ? EPI_MULAUX : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN));
+  if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else if (BN == 192) dispatch_major<192>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
+  else dispatch_major<64>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
 }
 
 }  // namespace tb

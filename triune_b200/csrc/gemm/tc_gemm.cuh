@@ -15,8 +15,8 @@ enum GemmMode : int {
 enum GemmFlags : int {
   GF_OUT_F32 = 1,     // C is fp32 (default bf16)
   GF_ACCUMULATE = 2,  // C += result
-  GF_GELU = 4,        // C = gelu_tanh(result + bias); pre-activation optionally saved to aux_out
-  GF_DGELU = 8,       // C = result * gelu_tanh'(aux_in)
+  GF_GELU = 4,        // C = gelu_tanh(result + bias); gelu_tanh'(result + bias) optionally saved to aux_out
+  GF_DGELU = 8,       // C = result * aux_in (aux_in = the derivative rows saved by GF_GELU)
 };
 
 // Operand layouts. "K-major": the reduction index is contiguous (x[M,K] row-major, w[N,K] row-major).
@@ -37,7 +37,7 @@ struct GemmArgs {
   const __nv_bfloat16* bias;  // [batch or groups][N] or null
   long long bias_stride;
   const __nv_bfloat16* aux_in;  // same layout as C (bf16), for GF_DGELU
-  __nv_bfloat16* aux_out;       // same layout as C (bf16), pre-activation for GF_GELU
+  __nv_bfloat16* aux_out;       // same layout as C (bf16), activation derivative from GF_GELU
   const float* row_scale;       // [M] or null
   const int* tile_group;        // GEMM_GROUPED_M: [ceil(M/128)], -1 marks an unused tile
   const int* group_offsets;     // GEMM_GROUPED_K: [batch+1], multiples of 64

@@ -79,6 +79,8 @@ def gemm(
     ``a`` is [.., M, K] (``a_mn``: stored [.., K, M]); ``b`` is [.., N, K] (``b_mn``: stored [.., K, N]).
     ``mode``: dense/batched, rows grouped by expert (``tile_group``), or reduction grouped by expert
     (``group_offsets``; then ``a`` [R, M], ``b`` [R, N] and out is [G, M, N]).
+    ``gelu`` applies tanh-GELU after the bias; ``aux_out`` (bf16, out's layout) then receives GELU'(pre-activation),
+    which a later call takes as ``dgelu_aux`` to form ``out = alpha * (A @ B^T) * dgelu_aux`` in its epilogue.
     """
     assert _tma_ok(a) and _tma_ok(b), "gemm operands must be CUDA bf16 with 16-byte aligned rows"
     if mode == GEMM_GROUPED_K:
@@ -166,20 +168,20 @@ class _MLPFn(torch.autograd.Function):
         if not _tma_ok(x2):
             x2 = x2.contiguous()
         M, Hd = x2.shape[0], w1.shape[0]
-        pre = torch.empty(M, Hd, device=x.device, dtype=x.dtype)
-        h = gemm(x2, w1, bias=b1, gelu=True, aux_out=pre)
+        dact = torch.empty(M, Hd, device=x.device, dtype=x.dtype)  # GELU'(x w1^T + b1), written by the same epilogue
+        h = gemm(x2, w1, bias=b1, gelu=True, aux_out=dact)
         y = gemm(h, w2, bias=b2)
-        ctx.save_for_backward(x2, w1, b1, w2, b2, pre, h)
+        ctx.save_for_backward(x2, w1, b1, w2, b2, dact, h)
         ctx.in_shape = x.shape
         return y.view(*x.shape[:-1], w2.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w1, b1, w2, b2, pre, h = ctx.saved_tensors
+        x2, w1, b1, w2, b2, dact, h = ctx.saved_tensors
         dy2 = dy.reshape(-1, w2.shape[0])
         if not _tma_ok(dy2):
             dy2 = dy2.contiguous()
-        dpre = gemm(dy2, w2, b_mn=True, dgelu_aux=pre)
+        dpre = gemm(dy2, w2, b_mn=True, dgelu_aux=dact)
         dw2 = _accumulate_weight_grad(w2, dy2, h)
         db2 = _accumulate_bias_grad(b2, dy2)
         dx = gemm(dpre, w1, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
@@ -612,22 +614,22 @@ class _ExpertMLPFn(torch.autograd.Function):
         Hd = w1.shape[1]
         # Row tiles past the last expert are never written and never read: the combine / gather kernels
         # follow `pos`, and the grouped weight-gradient GEMMs stay inside group_offsets.
-        pre = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)
+        dact = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)  # GELU' of the pre-activation
         h = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)
         yp = torch.empty(R, w2.shape[1], device=xp.device, dtype=xp.dtype)
-        gemm(xp, w1, h, bias=b1, gelu=True, aux_out=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(xp, w1, h, bias=b1, gelu=True, aux_out=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         gemm(h, w2, yp, bias=b2, mode=GEMM_GROUPED_M, tile_group=tile_group)
-        ctx.save_for_backward(xp, w1, b1, w2, b2, pre, h, tile_group, group_offsets)
+        ctx.save_for_backward(xp, w1, b1, w2, b2, dact, h, tile_group, group_offsets)
         return yp
 
     @staticmethod
     def backward(ctx, dyp):
-        xp, w1, b1, w2, b2, pre, h, tile_group, group_offsets = ctx.saved_tensors
+        xp, w1, b1, w2, b2, dact, h, tile_group, group_offsets = ctx.saved_tensors
         dyp = dyp.contiguous()
         E = w1.shape[0]
         R = xp.shape[0]
         dpre = torch.empty(R, w1.shape[1], device=xp.device, dtype=xp.dtype)
-        gemm(dyp, w2, dpre, b_mn=True, dgelu_aux=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(dyp, w2, dpre, b_mn=True, dgelu_aux=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         dxp = torch.empty_like(xp)
         gemm(dpre, w1, dxp, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group)
         ones = torch.ones(R, 8, device=xp.device, dtype=xp.dtype)

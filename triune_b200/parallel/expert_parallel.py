@@ -100,9 +100,9 @@ class _EPExpertsFn(torch.autograd.Function):
         e.ep_build_tiles(cnt_all, El, W, cap, tile_group, row_dst)
         e.ep_zero_invalid_rows(xin, cnt_all, El, W, cap)
         H = w1.shape[1]
-        pre = torch.zeros(rows, H, dtype=x.dtype, device=x.device)  # rows of skipped tiles must stay finite (they meet
+        dact = torch.zeros(rows, H, dtype=x.dtype, device=x.device)  # rows of skipped tiles must stay finite (they meet
         h = torch.zeros(rows, H, dtype=x.dtype, device=x.device)    # zero rows in the weight-gradient GEMMs)
-        gemm(xin, w1, h, bias=b1, gelu=True, aux_out=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(xin, w1, h, bias=b1, gelu=True, aux_out=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         # Copies for the backward pass are taken BEFORE this rank signals the combine barrier: once a peer has passed
         # that barrier it may start its next dispatch and overwrite these regions.
         xin_saved, dst_saved, cnt_saved = xin.clone(), row_dst.clone(), cnt_all.clone()
@@ -115,14 +115,14 @@ class _EPExpertsFn(torch.autograd.Function):
         out = e.combine_rows(recv, slot, wk, None, 0.0)
         ops._tick()
         ctx.ep, ctx.cap, ctx.buf = ep, cap, buf
-        ctx.save_for_backward(xin_saved, pre, h, tile_group, dst_saved, cnt_saved, idx_flat, pos, counts, slot, wk,
+        ctx.save_for_backward(xin_saved, dact, h, tile_group, dst_saved, cnt_saved, idx_flat, pos, counts, slot, wk,
                               recv.clone(), w1, b1, w2, b2)
         ep.comm_bytes += 2 * A * d * 2
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        (xin, pre, h, tile_group, row_dst, cnt_all, idx_flat, pos, counts, slot, wk, recv, w1, b1, w2, b2) = ctx.saved_tensors
+        (xin, dact, h, tile_group, row_dst, cnt_all, idx_flat, pos, counts, slot, wk, recv, w1, b1, w2, b2) = ctx.saved_tensors
         ep, cap, buf = ctx.ep, ctx.cap, ctx.buf
         e = _ext.ext()
         dout = dout.contiguous()
@@ -143,7 +143,7 @@ class _EPExpertsFn(torch.autograd.Function):
         live_dst.copy_(row_dst)  # same routing as the forward, including the rows invalidated there
         H = w1.shape[1]
         dpre = torch.zeros(rows, H, dtype=dout.dtype, device=dout.device)
-        gemm(dyin, w2, dpre, b_mn=True, dgelu_aux=pre, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(dyin, w2, dpre, b_mn=True, dgelu_aux=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         offs = (torch.arange(El + 1, device=dout.device, dtype=torch.int32) * (W * cap)).contiguous()
         ones = torch.ones(rows, 8, device=dout.device, dtype=dout.dtype)
 
