@@ -29,6 +29,21 @@ constexpr int C = 64;             // chunk length (tokens)
 constexpr int D = 64;             // head dim (keys and values)
 constexpr int TILE = C * 128;     // bytes of one 64x64 bf16 tile (128-byte rows)
 constexpr int GLA_THREADS = 128;
+// Row pitch (floats) of the fp32 scratch matrices in shared memory (cumulative log decay, gate-gradient terms).
+// Rows stay 16-byte aligned and consecutive rows start one 16-byte bank group apart, so float4 accesses with one
+// row per lane are conflict-free (a pitch of 64 puts every row on the same banks: 16-way conflicts).
+constexpr int BST = 68;
+constexpr int BMAT_BYTES = C * BST * 4;
+
+__device__ __forceinline__ void ld8(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void st8(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
 
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
@@ -73,22 +88,23 @@ __device__ __forceinline__ void build_cumsum(const uint8_t* g_tile, float* bmat,
     float f[8];
     unpack8(*reinterpret_cast<const uint4*>(g_tile + sw_off(row, ch)), f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) bmat[row * D + ch * 8 + i] = log_decay(f[i], logits);
+    for (int i = 0; i < 8; ++i) f[i] = log_decay(f[i], logits);
+    st8(bmat + row * BST + ch * 8, f);
   }
   __syncthreads();
   const int parts = nthr >> 6, len = C / parts;
   const int d = tid & 63, part = tid >> 6;
   float acc = 0.f;
   for (int t = part * len; t < part * len + len; ++t) {
-    acc += bmat[t * D + d];
-    bmat[t * D + d] = acc;
+    acc += bmat[t * BST + d];
+    bmat[t * BST + d] = acc;
   }
   __syncthreads();
   float base = 0.f;
-  for (int pp = 0; pp < part; ++pp) base += bmat[(pp * len + len - 1) * D + d];
+  for (int pp = 0; pp < part; ++pp) base += bmat[(pp * len + len - 1) * BST + d];
   __syncthreads();
   if (part > 0) {
-    for (int t = part * len; t < part * len + len; ++t) bmat[t * D + d] += base;
+    for (int t = part * len; t < part * len + len; ++t) bmat[t * BST + d] += base;
   }
   __syncthreads();
 }
@@ -117,7 +133,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_chunk_outer_kernel(const __gr
   uint8_t* sY = smem + TILE;
   uint8_t* sG = smem + 2 * TILE;
   float* bmat = reinterpret_cast<float*>(smem + 3 * TILE);
-  Bars* bars = reinterpret_cast<Bars*>(smem + 3 * TILE + C * D * 4);
+  Bars* bars = reinterpret_cast<Bars*>(smem + 3 * TILE + BMAT_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
@@ -152,14 +168,12 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_chunk_outer_kernel(const __gr
     for (int idx = tid; idx < 512; idx += blockDim.x) {
       const int row = idx >> 3, ch = idx & 7;
       uint4* px = reinterpret_cast<uint4*>(sX + sw_off(row, ch));
-      float f[8];
+      float f[8], bt[8], bl[8];
       unpack8(*px, f);
+      ld8(bmat + row * BST + ch * 8, bt);
+      ld8(bmat + 63 * BST + ch * 8, bl);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int dd = ch * 8 + i;
-        const float w = mode == 0 ? (bmat[63 * D + dd] - bmat[row * D + dd]) : bmat[row * D + dd];
-        f[i] *= __expf(w);
-      }
+      for (int i = 0; i < 8; ++i) f[i] *= __expf(mode == 0 ? (bl[i] - bt[i]) : bt[i]);
       *px = pack8(f);
     }
     fence_proxy_async_smem();
@@ -190,7 +204,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_chunk_outer_kernel(const __gr
                             __uint_as_float(r[i + 3]));
         }
       }
-      if (mode == 0 && out_decay != nullptr && tid < D) out_decay[(long long)blockIdx.x * D + tid] = __expf(bmat[63 * D + tid]);
+      if (mode == 0 && out_decay != nullptr && tid < D) out_decay[(long long)blockIdx.x * D + tid] = __expf(bmat[63 * BST + tid]);
     } else if (lane == 0) {
       bars->failed = ST_TIMEOUT_TMEM;
     }
@@ -238,29 +252,36 @@ __device__ __forceinline__ void build_score_operands(const uint8_t* sQ, const ui
     unpack8(*reinterpret_cast<const uint4*>(sQ + off), q);
     unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) bt[i] = bmat[row * D + ch * 8 + i];
+    ld8(bmat + row * BST + ch * 8, bt);
     const int jrow = row >> 4;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float o[8];
       if (j <= jrow) {
+        float r[8];
+        if (j == 0) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + ch * 8 + i];
-          o[i] = q[i] * __expf(bt[i] - r);
+          for (int i = 0; i < 8; ++i) r[i] = 0.f;
+        } else {
+          ld8(bmat + (16 * j - 1) * BST + ch * 8, r);
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = q[i] * __expf(bt[i] - r[i]);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = 0.f;
       }
       *reinterpret_cast<uint4*>(sA + j * TILE + off) = pack8(o);
     }
-    float o[8];
+    float o[8], r[8];
+    if (jrow == 0) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float r = jrow == 0 ? 0.f : bmat[(16 * jrow - 1) * D + ch * 8 + i];
-      o[i] = k[i] * __expf(r - bt[i]);
+      for (int i = 0; i < 8; ++i) r[i] = 0.f;
+    } else {
+      ld8(bmat + (16 * jrow - 1) * BST + ch * 8, r);
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = k[i] * __expf(r[i] - bt[i]);
     *reinterpret_cast<uint4*>(sKt + off) = pack8(o);
   }
 }
@@ -322,7 +343,7 @@ __device__ __forceinline__ void store_row_tile(uint8_t* tile, int row, const flo
 // ------------------------------------------------------------------------------------------------
 // Phase 3 forward: o = Q~(0) S_c + mask(P) V
 // ------------------------------------------------------------------------------------------------
-constexpr int FWD_SMEM = 5 * TILE + C * D * 4 + 4 * TILE + TILE + TILE + 1024 + 256;
+constexpr int FWD_SMEM = 5 * TILE + BMAT_BYTES + 4 * TILE + TILE + TILE + 1024 + 256;
 
 __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                   const __grid_constant__ CUtensorMap tmK,
@@ -344,7 +365,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
   uint8_t* sKt = smem + 9 * TILE;
   uint8_t* sP = smem + 10 * TILE;
   float* bmat = reinterpret_cast<float*>(smem + 11 * TILE);
-  Bars* bars = reinterpret_cast<Bars*>(smem + 11 * TILE + C * D * 4);
+  Bars* bars = reinterpret_cast<Bars*>(smem + 11 * TILE + BMAT_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
@@ -453,7 +474,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
 //   dg_t = sum_{tau >= t} (q dq - k dk)   (suffix over the whole sequence; chunk suffix added by dg_finalize)
 // ------------------------------------------------------------------------------------------------
 constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
-constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * C * D * 4 + 1024 + 256;
+constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * BMAT_BYTES + 1024 + 256;
 
 __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -479,8 +500,8 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
   uint8_t* sP = smem + 13 * TILE;
   uint8_t* sdP = smem + 14 * TILE;
   float* bmat = reinterpret_cast<float*>(smem + 15 * TILE);
-  float* dmat = bmat + C * D;
-  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * C * D * 4);
+  float* dmat = bmat + C * BST;
+  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * BMAT_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
@@ -523,10 +544,12 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     for (int idx = tid; idx < 512; idx += blockDim.x) {
       const int r = idx >> 3, ch = idx & 7;
       const uint32_t off = sw_off(r, ch);
-      float k[8];
+      float k[8], bl[8], bt[8];
       unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
+      ld8(bmat + 63 * BST + ch * 8, bl);
+      ld8(bmat + r * BST + ch * 8, bt);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) k[i] *= __expf(bmat[63 * D + ch * 8 + i] - bmat[r * D + ch * 8 + i]);
+      for (int i = 0; i < 8; ++i) k[i] *= __expf(bl[i] - bt[i]);
       *reinterpret_cast<uint4*>(sKe + off) = pack8(k);
     }
     fence_proxy_async_smem();
@@ -595,18 +618,27 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
         }
       }
       // dq
-      float acc[32];
+      float acc[32], bt[32];
+#pragma unroll
+      for (int d4 = 0; d4 < 8; ++d4) {
+        const float4 t4 = *reinterpret_cast<const float4*>(bmat + row * BST + c0 + 4 * d4);
+        bt[4 * d4] = t4.x; bt[4 * d4 + 1] = t4.y; bt[4 * d4 + 2] = t4.z; bt[4 * d4 + 3] = t4.w;
+      }
       load_acc_half(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bmat[row * D + c0 + d]);
+      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bt[d]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         load_acc_half(tmem, 256 + 64 * j + c0, quarter, v);  // warp-collective: every lane executes the load
         if (j <= (row >> 4)) {
 #pragma unroll
-          for (int d = 0; d < 32; ++d) {
-            const float r = j == 0 ? 0.f : bmat[(16 * j - 1) * D + c0 + d];
-            acc[d] += v[d] * __expf(bmat[row * D + c0 + d] - r);
+          for (int d4 = 0; d4 < 8; ++d4) {
+            float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j > 0) r4 = *reinterpret_cast<const float4*>(bmat + (16 * j - 1) * BST + c0 + 4 * d4);
+            acc[4 * d4] += v[4 * d4] * __expf(bt[4 * d4] - r4.x);
+            acc[4 * d4 + 1] += v[4 * d4 + 1] * __expf(bt[4 * d4 + 1] - r4.y);
+            acc[4 * d4 + 2] += v[4 * d4 + 2] * __expf(bt[4 * d4 + 2] - r4.z);
+            acc[4 * d4 + 3] += v[4 * d4 + 3] * __expf(bt[4 * d4 + 3] - r4.w);
           }
         }
       }
@@ -614,13 +646,14 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
         __nv_bfloat16* dst = dq + (long long)(row0 + row) * dq_ld + dqcol + h * D + c0;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          float o[8], q[8];
+          float o[8], q[8], qd[8];
           unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, half * 4 + ch)), q);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             o[i] = acc[ch * 8 + i];
-            dmat[row * D + c0 + ch * 8 + i] = q[i] * o[i];
+            qd[i] = q[i] * o[i];
           }
+          st8(dmat + row * BST + c0 + ch * 8, qd);
           *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
         }
       }
@@ -651,28 +684,45 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[32], acc[32];
+      float v[32], acc[32], bt[32];
       const int c0 = 32 * half;
+#pragma unroll
+      for (int d4 = 0; d4 < 8; ++d4) {
+        const float4 t4 = *reinterpret_cast<const float4*>(bmat + row * BST + c0 + 4 * d4);
+        bt[4 * d4] = t4.x; bt[4 * d4 + 1] = t4.y; bt[4 * d4 + 2] = t4.z; bt[4 * d4 + 3] = t4.w;
+      }
       load_acc_half(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bmat[63 * D + c0 + d] - bmat[row * D + c0 + d]);
+      for (int d4 = 0; d4 < 8; ++d4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(bmat + 63 * BST + c0 + 4 * d4);
+        acc[4 * d4] = v[4 * d4] * __expf(l4.x - bt[4 * d4]);
+        acc[4 * d4 + 1] = v[4 * d4 + 1] * __expf(l4.y - bt[4 * d4 + 1]);
+        acc[4 * d4 + 2] = v[4 * d4 + 2] * __expf(l4.z - bt[4 * d4 + 2]);
+        acc[4 * d4 + 3] = v[4 * d4 + 3] * __expf(l4.w - bt[4 * d4 + 3]);
+      }
       load_acc_half(tmem, 256 + 64 * quarter + c0, quarter, v);  // rows of sub-chunk j = quarter live in accumulator j
 #pragma unroll
-      for (int d = 0; d < 32; ++d) {
-        const float r = quarter == 0 ? 0.f : bmat[(16 * quarter - 1) * D + c0 + d];
-        acc[d] += v[d] * __expf(r - bmat[row * D + c0 + d]);
+      for (int d4 = 0; d4 < 8; ++d4) {
+        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (quarter > 0) r4 = *reinterpret_cast<const float4*>(bmat + (16 * quarter - 1) * BST + c0 + 4 * d4);
+        acc[4 * d4] += v[4 * d4] * __expf(r4.x - bt[4 * d4]);
+        acc[4 * d4 + 1] += v[4 * d4 + 1] * __expf(r4.y - bt[4 * d4 + 1]);
+        acc[4 * d4 + 2] += v[4 * d4 + 2] * __expf(r4.z - bt[4 * d4 + 2]);
+        acc[4 * d4 + 3] += v[4 * d4 + 3] * __expf(r4.w - bt[4 * d4 + 3]);
       }
       if (lane < 16) {
         __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D + c0;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          float o[8], k[8];
+          float o[8], k[8], qd[8];
           unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, half * 4 + ch)), k);
+          ld8(dmat + row * BST + c0 + ch * 8, qd);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             o[i] = acc[ch * 8 + i];
-            dmat[row * D + c0 + ch * 8 + i] -= k[i] * o[i];
+            qd[i] -= k[i] * o[i];
           }
+          st8(dmat + row * BST + c0 + ch * 8, qd);
           *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
         }
       }
@@ -682,15 +732,21 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     __syncthreads();
     ok = bars->failed == 0;
   }
-  if (ok && tid < D) {
-    // in-chunk suffix sum of (q dq - k dk) per key dimension
+  if (ok) {
+    // in-chunk suffix sum of (q dq - k dk) per key dimension: four 16-row parts in parallel, then the totals of the
+    // later parts (left in their first rows) are added on the way out
+    const int d = tid & 63, part = tid >> 6;
     float acc = 0.f;
-    float* dst = dgl_local + (long long)row0 * (H * D) + h * D + tid;
-    for (int t = C - 1; t >= 0; --t) {
-      acc += dmat[t * D + tid];
-      dst[(long long)t * (H * D)] = acc;
+    for (int t = 16 * part + 15; t >= 16 * part; --t) {
+      acc += dmat[t * BST + d];
+      dmat[t * BST + d] = acc;
     }
-    chunk_tot[(long long)blockIdx.x * D + tid] = acc;
+    __syncthreads();
+    float base = 0.f;
+    for (int pp = part + 1; pp < 4; ++pp) base += dmat[(16 * pp) * BST + d];
+    float* dst = dgl_local + (long long)row0 * (H * D) + h * D + d;
+    for (int t = 16 * part; t < 16 * part + 16; ++t) dst[(long long)t * (H * D)] = dmat[t * BST + d] + base;
+    if (part == 0) chunk_tot[(long long)blockIdx.x * D + d] = dmat[d] + base;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -794,7 +850,7 @@ void launch_gla_chunk_outer(int mode, GlaMat X, GlaMat Y, GlaMat G, float* out_k
   const int width = (int)X.ld;
   CUtensorMap tx = tile_map(X, rows, (int)X.ld), ty = tile_map(Y, rows, (int)Y.ld), tg = tile_map(G, rows, (int)G.ld);
   (void)width;
-  constexpr int SMEM = 3 * TILE + C * D * 4 + 1024 + 256;
+  constexpr int SMEM = 3 * TILE + BMAT_BYTES + 1024 + 256;
   static bool cfg = false;
   if (!cfg) {
     set_smem(gla_chunk_outer_kernel, SMEM);
