@@ -80,7 +80,7 @@ __device__ __forceinline__ uint64_t desc_mn(uint32_t tile_addr, int kstep) {
 }
 
 // Fills bmat[t][d] (fp32, 64x64) with the inclusive cumulative log decay of the gate tile. Works for any block of
-// 64*P threads (P in {2,4}): P partial scans of 64/P tokens per column, then the earlier parts' totals are added.
+// 64*P threads (P in {2,4,8}): P partial scans of 64/P tokens per column, then the earlier parts' totals are added.
 __device__ __forceinline__ void build_cumsum(const uint8_t* g_tile, float* bmat, bool logits) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   for (int idx = tid; idx < 512; idx += nthr) {
@@ -318,6 +318,36 @@ __device__ __forceinline__ void load_acc_half(uint32_t tmem, uint32_t col, int q
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// N-column slice (N = 16 or 32) of an accumulator row: TMEM lane quarter `quarter`, columns [col, col + N).
+template <int N>
+__device__ __forceinline__ void load_acc_cols(uint32_t tmem, uint32_t col, int quarter, float (&v)[N]) {
+  uint32_t r[N];
+  if constexpr (N == 32) tmem_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + col, r);
+  else tmem_ld_32x32b_x16(tmem + ((uint32_t)(quarter * 32) << 16) + col, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Writes columns [c0, c0 + N) of a row as bf16 into a swizzled tile; columns > limit are zeroed (causal mask).
+template <int N>
+__device__ __forceinline__ void store_row_cols(uint8_t* tile, int row, int c0, const float (&v)[N], int limit) {
+#pragma unroll
+  for (int c8 = 0; c8 < N / 8; ++c8) {
+    const int ch = c0 / 8 + c8;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (ch * 8 + i <= limit) ? v[c8 * 8 + i] : 0.f;
+    *reinterpret_cast<uint4*>(tile + sw_off(row, ch)) = pack8(o);
+  }
+}
+template <int N>
+__device__ __forceinline__ void ld_row(const float* p, float (&f)[N]) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const float4 t = *reinterpret_cast<const float4*>(p + 4 * i);
+    f[4 * i] = t.x; f[4 * i + 1] = t.y; f[4 * i + 2] = t.z; f[4 * i + 3] = t.w;
+  }
+}
 __device__ __forceinline__ void store_row_half(uint8_t* tile, int row, int half, const float (&v)[32], int limit) {
 #pragma unroll
   for (int c4 = 0; c4 < 4; ++c4) {
@@ -345,7 +375,9 @@ __device__ __forceinline__ void store_row_tile(uint8_t* tile, int row, const flo
 // ------------------------------------------------------------------------------------------------
 constexpr int FWD_SMEM = 5 * TILE + BMAT_BYTES + 4 * TILE + TILE + TILE + 1024 + 256;
 
-__global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_constant__ CUtensorMap tmQ,
+constexpr int FWD_THREADS = 256;
+
+__global__ void __launch_bounds__(FWD_THREADS) gla_fwd_out_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                   const __grid_constant__ CUtensorMap tmK,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const __grid_constant__ CUtensorMap tmG,
@@ -398,6 +430,9 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
   if (!ok) bars->failed = ST_TIMEOUT_FULL;
   __syncthreads();
   ok = bars->failed == 0;
+  // eight warps: TMEM lane quarter (warp & 3) x 32-column half (warp >> 2) of every 64-column accumulator
+  const int quarter = warp & 3, c0 = (warp >> 2) * 32;
+  const int row = quarter * 16 + (lane & 15);
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
     build_score_operands(sQ, sK, sA, sKt, bmat);
@@ -415,10 +450,9 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[64];
-      load_acc_row(tmem, 0, warp, v);
-      const int row = warp * 16 + (lane & 15);
-      if (lane < 16) store_row_tile(sP, row, v, row);
+      float v[32];
+      load_acc_cols<32>(tmem, c0, quarter, v);
+      if (lane < 16) store_row_cols<32>(sP, row, c0, v, row);
       fence_proxy_async_smem();
       tc_fence_before_sync();
     } else if (lane == 0) {
@@ -438,13 +472,12 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
       if (ok) {
         tc_fence_after_sync();
-        float v[64];
-        load_acc_row(tmem, 64, warp, v);
+        float v[32];
+        load_acc_cols<32>(tmem, 64 + c0, quarter, v);
         if (lane < 16) {
-          const int row = warp * 16 + lane;
-          __nv_bfloat16* dst = out + (long long)(row0 + row) * out_ld + ocol + h * D;
+          __nv_bfloat16* dst = out + (long long)(row0 + row) * out_ld + ocol + h * D + c0;
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
+          for (int ch = 0; ch < 4; ++ch) {
             float o[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = v[ch * 8 + i];
@@ -476,7 +509,9 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_fwd_out_kernel(const __grid_c
 constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
 constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * BMAT_BYTES + 1024 + 256;
 
-__global__ void __launch_bounds__(256) gla_bwd_main_kernel(
+constexpr int BWD_THREADS = 512;
+
+__global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
     const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ CUtensorMap tmS,
@@ -535,8 +570,9 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
   if (!ok) bars->failed = ST_TIMEOUT_FULL;
   __syncthreads();
   ok = bars->failed == 0;
-  const int quarter = warp & 3, half = warp >> 2;  // TMEM lane quarter / 32-column half of this warp
-  const int row = quarter * 16 + (lane & 15);       // accumulator row owned by this thread when lane < 16
+  constexpr int CPW = 64 / (BWD_THREADS / 128);      // accumulator columns per warp (16 warps: 16)
+  const int quarter = warp & 3, c0 = (warp >> 2) * CPW;  // TMEM lane quarter / first column of this warp
+  const int row = quarter * 16 + (lane & 15);        // accumulator row owned by this thread when lane < 16
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
     build_score_operands(sQ, sK, sA, sKt, bmat);
@@ -567,11 +603,11 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[32];
-      load_acc_half(tmem, 0 + 32 * half, quarter, v);
-      if (lane < 16) store_row_half(sP, row, half, v, row);
-      load_acc_half(tmem, 64 + 32 * half, quarter, v);
-      if (lane < 16) store_row_half(sdP, row, half, v, row);
+      float v[CPW];
+      load_acc_cols<CPW>(tmem, 0 + c0, quarter, v);
+      if (lane < 16) store_row_cols<CPW>(sP, row, c0, v, row);
+      load_acc_cols<CPW>(tmem, 64 + c0, quarter, v);
+      if (lane < 16) store_row_cols<CPW>(sdP, row, c0, v, row);
       fence_proxy_async_smem();
       tc_fence_before_sync();
     } else if (lane == 0) {
@@ -600,17 +636,19 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
         umma_bf16(tmem + 256 + 64 * j, desc_k(adP, j), desc_mn(aKt, j), id_km, 0u);
       umma_commit(&bars->mma[1]);
     }
+    // the row's cumulative log decay for this warp's columns: shared-memory reads overlap the MMAs
+    float bt[CPW];
+    ld_row<CPW>(bmat + row * BST + c0, bt);
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[32];
-      const int c0 = 32 * half;  // first column handled by this thread
+      float v[CPW];
       // dv
-      load_acc_half(tmem, 128 + c0, quarter, v);
+      load_acc_cols<CPW>(tmem, 128 + c0, quarter, v);
       if (lane < 16) {
         __nv_bfloat16* dst = dv + (long long)(row0 + row) * dv_ld + dvcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < CPW / 8; ++ch) {
           float o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = v[ch * 8 + i];
@@ -618,36 +656,31 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
         }
       }
       // dq
-      float acc[32], bt[32];
+      float acc[CPW];
+      load_acc_cols<CPW>(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d4 = 0; d4 < 8; ++d4) {
-        const float4 t4 = *reinterpret_cast<const float4*>(bmat + row * BST + c0 + 4 * d4);
-        bt[4 * d4] = t4.x; bt[4 * d4 + 1] = t4.y; bt[4 * d4 + 2] = t4.z; bt[4 * d4 + 3] = t4.w;
-      }
-      load_acc_half(tmem, 192 + c0, quarter, v);
-#pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = v[d] * __expf(bt[d]);
+      for (int d = 0; d < CPW; ++d) acc[d] = v[d] * __expf(bt[d]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        load_acc_half(tmem, 256 + 64 * j + c0, quarter, v);  // warp-collective: every lane executes the load
+        load_acc_cols<CPW>(tmem, 256 + 64 * j + c0, quarter, v);  // warp-collective: every lane executes the load
         if (j <= (row >> 4)) {
+          float r[CPW];
+          if (j == 0) {
 #pragma unroll
-          for (int d4 = 0; d4 < 8; ++d4) {
-            float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (j > 0) r4 = *reinterpret_cast<const float4*>(bmat + (16 * j - 1) * BST + c0 + 4 * d4);
-            acc[4 * d4] += v[4 * d4] * __expf(bt[4 * d4] - r4.x);
-            acc[4 * d4 + 1] += v[4 * d4 + 1] * __expf(bt[4 * d4 + 1] - r4.y);
-            acc[4 * d4 + 2] += v[4 * d4 + 2] * __expf(bt[4 * d4 + 2] - r4.z);
-            acc[4 * d4 + 3] += v[4 * d4 + 3] * __expf(bt[4 * d4 + 3] - r4.w);
+            for (int d = 0; d < CPW; ++d) r[d] = 0.f;
+          } else {
+            ld_row<CPW>(bmat + (16 * j - 1) * BST + c0, r);
           }
+#pragma unroll
+          for (int d = 0; d < CPW; ++d) acc[d] += v[d] * __expf(bt[d] - r[d]);
         }
       }
       if (lane < 16) {
         __nv_bfloat16* dst = dq + (long long)(row0 + row) * dq_ld + dqcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < CPW / 8; ++ch) {
           float o[8], q[8], qd[8];
-          unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, half * 4 + ch)), q);
+          unpack8(*reinterpret_cast<const uint4*>(sQ + sw_off(row, c0 / 8 + ch)), q);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             o[i] = acc[ch * 8 + i];
@@ -681,41 +714,31 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
       }
       umma_commit(&bars->mma[2]);
     }
+    float bt[CPW], bl[CPW], br[CPW];
+    ld_row<CPW>(bmat + row * BST + c0, bt);
+    ld_row<CPW>(bmat + 63 * BST + c0, bl);
+    if (quarter > 0) {
+      ld_row<CPW>(bmat + (16 * quarter - 1) * BST + c0, br);
+    } else {
+#pragma unroll
+      for (int d = 0; d < CPW; ++d) br[d] = 0.f;
+    }
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
     if (ok) {
       tc_fence_after_sync();
-      float v[32], acc[32], bt[32];
-      const int c0 = 32 * half;
+      float v[CPW], acc[CPW];
+      load_acc_cols<CPW>(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d4 = 0; d4 < 8; ++d4) {
-        const float4 t4 = *reinterpret_cast<const float4*>(bmat + row * BST + c0 + 4 * d4);
-        bt[4 * d4] = t4.x; bt[4 * d4 + 1] = t4.y; bt[4 * d4 + 2] = t4.z; bt[4 * d4 + 3] = t4.w;
-      }
-      load_acc_half(tmem, 192 + c0, quarter, v);
+      for (int d = 0; d < CPW; ++d) acc[d] = v[d] * __expf(bl[d] - bt[d]);
+      load_acc_cols<CPW>(tmem, 256 + 64 * quarter + c0, quarter, v);  // rows of sub-chunk j = quarter live in accumulator j
 #pragma unroll
-      for (int d4 = 0; d4 < 8; ++d4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(bmat + 63 * BST + c0 + 4 * d4);
-        acc[4 * d4] = v[4 * d4] * __expf(l4.x - bt[4 * d4]);
-        acc[4 * d4 + 1] = v[4 * d4 + 1] * __expf(l4.y - bt[4 * d4 + 1]);
-        acc[4 * d4 + 2] = v[4 * d4 + 2] * __expf(l4.z - bt[4 * d4 + 2]);
-        acc[4 * d4 + 3] = v[4 * d4 + 3] * __expf(l4.w - bt[4 * d4 + 3]);
-      }
-      load_acc_half(tmem, 256 + 64 * quarter + c0, quarter, v);  // rows of sub-chunk j = quarter live in accumulator j
-#pragma unroll
-      for (int d4 = 0; d4 < 8; ++d4) {
-        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (quarter > 0) r4 = *reinterpret_cast<const float4*>(bmat + (16 * quarter - 1) * BST + c0 + 4 * d4);
-        acc[4 * d4] += v[4 * d4] * __expf(r4.x - bt[4 * d4]);
-        acc[4 * d4 + 1] += v[4 * d4 + 1] * __expf(r4.y - bt[4 * d4 + 1]);
-        acc[4 * d4 + 2] += v[4 * d4 + 2] * __expf(r4.z - bt[4 * d4 + 2]);
-        acc[4 * d4 + 3] += v[4 * d4 + 3] * __expf(r4.w - bt[4 * d4 + 3]);
-      }
+      for (int d = 0; d < CPW; ++d) acc[d] += v[d] * __expf(br[d] - bt[d]);
       if (lane < 16) {
         __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D + c0;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < CPW / 8; ++ch) {
           float o[8], k[8], qd[8];
-          unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, half * 4 + ch)), k);
+          unpack8(*reinterpret_cast<const uint4*>(sK + sw_off(row, c0 / 8 + ch)), k);
           ld8(dmat + row * BST + c0 + ch * 8, qd);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -733,19 +756,20 @@ __global__ void __launch_bounds__(256) gla_bwd_main_kernel(
     ok = bars->failed == 0;
   }
   if (ok) {
-    // in-chunk suffix sum of (q dq - k dk) per key dimension: four 16-row parts in parallel, then the totals of the
+    // in-chunk suffix sum of (q dq - k dk) per key dimension: parts of PR rows in parallel, then the totals of the
     // later parts (left in their first rows) are added on the way out
+    constexpr int NPARTS = BWD_THREADS / 64, PR = C / NPARTS;
     const int d = tid & 63, part = tid >> 6;
     float acc = 0.f;
-    for (int t = 16 * part + 15; t >= 16 * part; --t) {
+    for (int t = PR * part + PR - 1; t >= PR * part; --t) {
       acc += dmat[t * BST + d];
       dmat[t * BST + d] = acc;
     }
     __syncthreads();
     float base = 0.f;
-    for (int pp = part + 1; pp < 4; ++pp) base += dmat[(16 * pp) * BST + d];
+    for (int pp = part + 1; pp < NPARTS; ++pp) base += dmat[(PR * pp) * BST + d];
     float* dst = dgl_local + (long long)row0 * (H * D) + h * D + d;
-    for (int t = 16 * part; t < 16 * part + 16; ++t) dst[(long long)t * (H * D)] = dmat[t * BST + d] + base;
+    for (int t = PR * part; t < PR * part + PR; ++t) dst[(long long)t * (H * D)] = dmat[t * BST + d] + base;
     if (part == 0) chunk_tot[(long long)blockIdx.x * D + d] = dmat[d] + base;
   }
   tc_fence_before_sync();
@@ -883,7 +907,7 @@ void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloa
     cfg = true;
   }
   const int grid = d.B * d.H * (d.T / C);
-  gla_fwd_out_kernel<<<grid, GLA_THREADS, FWD_SMEM, s>>>(tq, tk, tv, tg, ts, Q.col0, K.col0, V.col0, G.col0,
+  gla_fwd_out_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tq, tk, tv, tg, ts, Q.col0, K.col0, V.col0, G.col0,
                                                          reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(O.ptr)), O.ld,
                                                          O.col0, d.T, d.H, d.gate_logits ? 1 : 0, status);
   check_launch("gla_fwd_out");
@@ -905,7 +929,7 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
     cfg = true;
   }
   const int grid = d.B * d.H * (d.T / C);
-  gla_bwd_main_kernel<<<grid, 256, BWD_SMEM, s>>>(
+  gla_bwd_main_kernel<<<grid, BWD_THREADS, BWD_SMEM, s>>>(
       tq, tk, tv, tg, tdo, ts, tds, Q.col0, K.col0, V.col0, G.col0, dO.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dQ.ptr)), dQ.ld, dQ.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dK.ptr)), dK.ld, dK.col0,
