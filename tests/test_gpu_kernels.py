@@ -47,6 +47,22 @@ def test_gemm_mn_major(dev, a_mn, b_mn, M, N, K):
     assert _rel(c, ref) < 2e-2
 
 
+def test_colsum_matches_fp32(dev):
+    from triune_b200 import _ext
+
+    torch.manual_seed(5)
+    for (M, N) in ((4096, 384), (1000, 1536), (37, 8)):
+        x = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        ref = x.float().sum(0)
+        got = _ext.ext().colsum(x, None)
+        assert torch.allclose(got, ref, rtol=1e-4, atol=1e-2)
+        acc = torch.ones(N, device=dev, dtype=torch.float32)
+        _ext.ext().colsum(x, acc)
+        assert torch.allclose(acc, 1.0 + ref, rtol=1e-4, atol=1e-2)
+    wide = torch.randn(512, 768, device=dev, dtype=torch.bfloat16)[:, :384]  # row pitch larger than the width
+    assert torch.allclose(_ext.ext().colsum(wide, None), wide.float().sum(0), rtol=1e-4, atol=1e-2)
+
+
 def test_gemm_epilogues(dev):
     from triune_b200 import ops
 

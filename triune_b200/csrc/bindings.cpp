@@ -186,6 +186,24 @@ Tensor ce_fwd_bwd(Tensor& logits, const Tensor& targets, int64_t ignore_index, d
   return loss;
 }
 
+// Column sums of a bf16 [M, N] matrix in fp32: returns a new [N] tensor, or adds into `out` when given.
+Tensor colsum(const Tensor& x, const c10::optional<Tensor>& out) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 8 == 0 && x.stride(0) % 8 == 0,
+              "x must be [M, N] with N and the row pitch multiples of 8");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int M = (int)x.size(0), N = (int)x.size(1);
+  const bool acc = out.has_value() && out->defined();
+  if (acc)
+    TORCH_CHECK(out->scalar_type() == at::kFloat && out->is_contiguous() && out->numel() == N, "out must be fp32 [N]");
+  Tensor res = acc ? *out : torch::empty({N}, x.options().dtype(at::kFloat));
+  const int parts = tb::colsum_parts(M, N);
+  Tensor partial = torch::empty({parts, N}, x.options().dtype(at::kFloat));
+  tb::launch_colsum(bf(x), x.stride(0), M, N, partial.data_ptr<float>(), parts, res.data_ptr<float>(), acc, cur_stream());
+  return res;
+}
+
 Tensor gather_rows(const Tensor& src, const Tensor& row_src, const c10::optional<Tensor>& row_scale) {
   check_bf16_cuda(src, "src");
   TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.size(1) % 8 == 0, "src must be [rows, width%8==0]");
@@ -382,6 +400,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_prep_fwd", &qk_prep_fwd);
   m.def("qk_prep_bwd", &qk_prep_bwd);
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("colsum", &colsum);
   m.def("gather_rows", &gather_rows);
   m.def("combine_rows", &combine_rows);
   m.def("row_dots", &row_dots);

@@ -15,6 +15,11 @@ void launch_rmsnorm_fwd(const __nv_bfloat16* x, const __nv_bfloat16* res, const 
 void launch_rmsnorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy, const float* rstd,
                         const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw, int rows, int d, cudaStream_t s);
 
+// out[n] (+)= sum over rows of x[m, n] (bf16 in, fp32 out); `partial` holds colsum_parts(M, N) x N floats.
+int colsum_parts(int M, int N);
+void launch_colsum(const __nv_bfloat16* x, long long ld, int M, int N, float* partial, int parts, float* out,
+                   bool accumulate, cudaStream_t s);
+
 void launch_qk_prep_fwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, __nv_bfloat16* out, const float* cs,
                         const float* sn, long long tokens, int T, int H, int D, cudaStream_t s);
 void launch_qk_prep_bwd(const __nv_bfloat16* in, long long in_ld, int k_col_offset, const __nv_bfloat16* dout,

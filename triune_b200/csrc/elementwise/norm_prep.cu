@@ -393,4 +393,71 @@ void launch_qk_prep_bwd(const __nv_bfloat16* in, long long in_ld, int k_col_offs
     qk_prep_bwd_kernel<128><<<grid, 256, 0, s>>>(in, in_ld, k_col_offset, dout, d_in, d_in_ld, cs, sn, tokens, T, H);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Column sums of a bf16 matrix (bias gradients): out[n] (+)= sum_m x[m, n].
+// Phase 1: a block owns a 256-column slab and every gridDim.y-th group of 8 rows; a warp reads 512 contiguous bytes
+// of one row per step, a thread keeps 8 fp32 sums, the block's 8 warps are combined through shared memory and one
+// partial row is written per block. Phase 2 adds the partial rows in a fixed order, so results are reproducible.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M,
+                                                             int N, float* __restrict__ partial) {
+  __shared__ float red[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 256 + lane * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (col < N) {
+    for (int m = blockIdx.y * 8 + warp; m < M; m += gridDim.y * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(x + (long long)m * ld + col);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = acc[i];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+    partial[(long long)blockIdx.y * N + c] = s;
+  }
+}
+
+__global__ void colsum_finalize_kernel(const float* __restrict__ partial, int parts, int N, float* __restrict__ out,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[(long long)p * N + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+}  // namespace
+
+int colsum_parts(int M, int N) {
+  const int slabs = (N + 255) / 256;
+  int parts = (148 * 4 + slabs - 1) / slabs;
+  const int max_parts = (M + 63) / 64;  // at least 8 rows per warp
+  if (parts > max_parts) parts = max_parts;
+  return parts < 1 ? 1 : parts;
+}
+
+void launch_colsum(const __nv_bfloat16* x, long long ld, int M, int N, float* partial, int parts, float* out,
+                   bool accumulate, cudaStream_t s) {
+  dim3 grid((N + 255) / 256, parts);
+  colsum_partial_kernel<<<grid, 256, 0, s>>>(x, ld, M, N, partial);
+  colsum_finalize_kernel<<<(N + 255) / 256, 256, 0, s>>>(partial, parts, N, out, accumulate ? 1 : 0);
+}
+
 }  // namespace tb

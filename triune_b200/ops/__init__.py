@@ -114,12 +114,20 @@ def _accumulate_weight_grad(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor
 def _accumulate_bias_grad(b: Optional[torch.Tensor], dy2: torch.Tensor):
     if b is None:
         return None
-    db = dy2.sum(0, dtype=torch.float32)
     mg = getattr(b, "main_grad", None)
+    fast = _tma_ok(dy2) and dy2.dim() == 2 and dy2.shape[1] % 8 == 0 and _ext.use_kernels(dy2)
     if mg is not None:
-        mg.add_(db)
+        if fast and mg.dtype == torch.float32 and mg.is_contiguous():
+            _ext.ext().colsum(dy2, mg)  # column sums added into the fp32 gradient arena
+            _tick(2)
+        else:
+            mg.add_(dy2.sum(0, dtype=torch.float32))
         return None
-    return db.to(b.dtype)
+    if fast:
+        db = _ext.ext().colsum(dy2, None)
+        _tick(2)
+        return db.to(b.dtype)
+    return dy2.sum(0, dtype=torch.float32).to(b.dtype)
 
 
 class _LinearFn(torch.autograd.Function):
