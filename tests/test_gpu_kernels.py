@@ -63,6 +63,43 @@ def test_colsum_matches_fp32(dev):
     assert torch.allclose(_ext.ext().colsum(wide, None), wide.float().sum(0), rtol=1e-4, atol=1e-2)
 
 
+@pytest.mark.parametrize(
+    "M,N,K,a_mn,b_mn,mode",
+    [
+        (640, 384, 1024, False, False, "bias"),      # 256 x 384 pair tiles, odd number of 128-row tiles
+        (512, 768, 1088, False, True, "plain"),      # input-gradient layout, two column tiles
+        (384, 512, 2048, True, True, "accumulate"),  # weight-gradient layout, 256 x 256 pair tiles, split-K
+        (1536, 384, 4096, True, True, "accumulate"),
+        (256, 256, 1024, True, False, "plain"),
+    ],
+)
+def test_gemm_cta_pairs(dev, M, N, K, a_mn, b_mn, mode):
+    from triune_b200 import _ext, ops
+
+    torch.manual_seed(11)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16) * 0.25
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.25
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    ref = a.float() @ b.float().t()
+    before = _ext.ext().tc_gemm_pair_launches()
+    if mode == "accumulate":
+        c = torch.full((M, N), 2.0, device=dev, dtype=torch.float32)
+        ops.gemm(aa, bb, c, a_mn=a_mn, b_mn=b_mn, accumulate=True, alpha=0.5)
+        ref = 2.0 + 0.5 * ref
+        tol = 2e-3
+    elif mode == "bias":
+        bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+        c = ops.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, bias=bias)
+        ref = ref + bias.float()
+        tol = 1e-2
+    else:
+        c = ops.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn)
+        tol = 1e-2
+    assert _ext.ext().tc_gemm_pair_launches() == before + 1, "the CTA-pair kernel did not take this shape"
+    assert _rel(c, ref) < tol
+
+
 def test_gemm_epilogues(dev):
     from triune_b200 import ops
 

@@ -24,111 +24,11 @@
 
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
+#include "tc_gemm_impl.cuh"
 
 namespace tb {
 
 namespace {
-
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr int EPI_TILE = 32 * 128;  // one staged output tile: 32 rows x 128 bytes
-
-template <int BN>
-struct GemmCfg {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
-  static constexpr int TMEM_COLS = (BN == 192) ? 512 : 2 * BN;  // power of two >= 2 * BN
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 4096 /*epilogue staging: 8 warps x 1 tile*/ + 1024 /*alignment slack*/ + 256;
-};
-
-struct KParams {
-  int M, N, K;
-  int mode, flags, batch;
-  int num_m, num_n;
-  long long ldc, strideC;
-  int a_batched, b_batched;
-  float alpha;
-  void* C;
-  const __nv_bfloat16* bias;
-  long long bias_stride;
-  const __nv_bfloat16* aux_in;
-  __nv_bfloat16* aux_out;
-  const float* row_scale;
-  const int* tile_group;
-  const int* group_offsets;
-  int* status;
-  int total_tiles;
-  int splits;           // split-K factor (dense mode, fp32 accumulate only)
-  int iters_per_split;  // K iterations (of 64) handled by one split
-};
-
-struct Tile {
-  int m0, n0, ba, bb, g, k_begin, k_iters;
-  bool valid;
-};
-
-__device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
-  Tile tl;
-  tl.valid = true;
-  if (p.mode == GEMM_GROUPED_M) {
-    int m_idx = t % p.num_m, n_idx = t / p.num_m;
-    int g = p.tile_group[m_idx];
-    tl.valid = g >= 0;
-    tl.g = g < 0 ? 0 : g;
-    tl.m0 = m_idx * BM;
-    tl.n0 = n_idx;  // scaled by BN by the caller
-    tl.ba = 0;
-    tl.bb = tl.g;
-    tl.k_begin = 0;
-    tl.k_iters = (p.K + BK - 1) / BK;
-  } else {
-    int per_b = p.num_m * p.num_n;
-    int split = 0;
-    if (p.splits > 1) {
-      const int base = per_b * p.batch;
-      split = t / base;
-      t = t % base;
-    }
-    int b = t / per_b, r = t % per_b;
-    tl.m0 = (r % p.num_m) * BM;
-    tl.n0 = r / p.num_m;
-    tl.g = b;
-    if (p.mode == GEMM_GROUPED_K) {
-      tl.ba = 0;
-      tl.bb = 0;
-      int k0 = p.group_offsets[b], k1 = p.group_offsets[b + 1];
-      tl.k_begin = k0;
-      tl.k_iters = (k1 - k0 + BK - 1) / BK;
-    } else {
-      tl.ba = p.a_batched ? b : 0;
-      tl.bb = p.b_batched ? b : 0;
-      const int total_iters = (p.K + BK - 1) / BK;
-      if (p.splits > 1) {
-        tl.k_begin = split * p.iters_per_split * BK;
-        const int left = total_iters - split * p.iters_per_split;
-        tl.k_iters = left < p.iters_per_split ? (left < 0 ? 0 : left) : p.iters_per_split;
-      } else {
-        tl.k_begin = 0;
-        tl.k_iters = total_iters;
-      }
-    }
-  }
-  return tl;
-}
-
-__device__ __forceinline__ void report(const KParams& p, int code) {
-  if (p.status != nullptr) atomicCAS(p.status, 0, code);
-}
-
-// Epilogue kinds (compile-time, so the plain stores do not carry the activation code's registers):
-//   EPI_PLAIN      alpha, bias, row scale, bf16 output (store or reduce-add)
-//   EPI_PLAIN_F32  the same with an fp32 output (weight-gradient accumulation, split-K)
-//   EPI_GELU       bias, tanh-GELU, bf16 output; optionally GELU'(pre-activation) as a second bf16 output
-//   EPI_MULAUX     output = alpha * acc * aux_in (the backward of EPI_GELU: aux_in holds GELU')
-enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3 };
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -284,24 +184,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    // Each warp owns 32 accumulator rows. Per column chunk (128 bytes of output: 64 bf16 or 32 fp32) it reads the
-    // fp32 accumulator from TMEM, applies the epilogue, writes the rows into a private 128B-swizzled staging tile
-    // and one lane hands the tile to TMA (plain store, or reduce-add for accumulate / split-K): global writes are
-    // full 128-byte lines regardless of the row pitch, and ragged M/N edges are clipped by the tensor map.
-    // Eight epilogue warps: a warp can only read the TMEM lanes of its quarter (warp % 4), so two warps share every
-    // quarter and take alternate column chunks. Short reductions (K = 384) make the epilogue the longer phase of a
-    // tile; halving it is worth more than a deeper load ring.
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Short reductions (K = 384) make the epilogue the longer phase of a tile; eight warps halve it, which is worth
+    // more than a deeper load ring.
     const int lane_base = (warp & 3) * 32;
     const int col_half = (warp - 2) >> 2;
     uint8_t* my_stage = smem_epi + (warp - 2) * EPI_TILE;  // one staging tile per warp (a second one costs a load stage and measured slower)
     int acc = 0;
     uint32_t acc_phase = 0;
-    constexpr bool out_f32 = (EPI == EPI_PLAIN_F32);
-    constexpr int CW = out_f32 ? 32 : 64;  // columns per staged chunk (128 bytes)
-    constexpr int NP = CW / 2;             // packed fp32 pairs per lane and chunk
-    const bool reduce_add = ((p.flags & GF_ACCUMULATE) != 0) || p.splits > 1;
-    const uint64_t alpha2 = pack_f2(p.alpha, p.alpha);
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       Tile tl = decode_tile(p, t);
       if (!tl.valid) continue;
@@ -312,161 +202,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
-      const int n0 = tl.n0 * BN;
-      const int gm = tl.m0 + lane_base + lane;
-      const bool row_ok = gm < p.M;
-      const int out_batch = (p.mode == GEMM_GROUPED_M) ? 0 : tl.g;
-      const long long c_off = (long long)out_batch * p.strideC + (long long)gm * p.ldc;
-      const __nv_bfloat16* bias = p.bias ? p.bias + (long long)tl.g * p.bias_stride : nullptr;
-#pragma unroll 1
-      for (int c = col_half * CW; c < BN; c += 2 * CW) {
-        if (n0 + c >= p.N) break;
-        uint64_t v[NP];
-        // Multiplier rows (the activation derivative saved by the forward pass): issue the loads first so their
-        // latency hides behind the TMEM reads.
-        uint4 auxv[8];
-        if constexpr (EPI == EPI_MULAUX) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int gn = n0 + c + j * 8;
-            auxv[j] = (row_ok && gn < p.N) ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn)
-                                           : make_uint4(0u, 0u, 0u, 0u);
-          }
-        }
-        if (tl.k_iters > 0) {
-          uint32_t r0[32], r1[32];
-          const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + acc * BN + c;
-          tmem_ld_32x32b_x32(taddr, r0);
-          if (!out_f32) tmem_ld_32x32b_x32(taddr + 32, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = pack_f2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-          if (!out_f32) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              v[(NP - 16) + i] = pack_f2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < NP; ++i) v[i] = 0ull;
-        }
-        // alpha and bias: one packed fma per pair
-        if (bias) {
-#pragma unroll
-          for (int j = 0; j < NP / 4; ++j) {
-            const int gn = n0 + c + j * 8;
-            if (gn < p.N) {
-              const uint4 bv = *reinterpret_cast<const uint4*>(bias + gn);
-              v[j * 4 + 0] = fma2(v[j * 4 + 0], alpha2, bf16x2_to_f2(bv.x));
-              v[j * 4 + 1] = fma2(v[j * 4 + 1], alpha2, bf16x2_to_f2(bv.y));
-              v[j * 4 + 2] = fma2(v[j * 4 + 2], alpha2, bf16x2_to_f2(bv.z));
-              v[j * 4 + 3] = fma2(v[j * 4 + 3], alpha2, bf16x2_to_f2(bv.w));
-            }
-          }
-        } else if (p.alpha != 1.0f) {
-#pragma unroll
-          for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], alpha2);
-        }
-        uint8_t* st = my_stage;
-        if constexpr (EPI == EPI_PLAIN_F32) {
-          if (p.row_scale) {
-            const float rs = row_ok ? p.row_scale[gm] : 1.0f;
-            const uint64_t rs2 = pack_f2(rs, rs);
-#pragma unroll
-            for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], rs2);
-          }
-          if (lane == 0) tma_store_wait_read<0>();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 o;
-            unpack_f2(v[(j * 2) % NP], o.x, o.y);
-            unpack_f2(v[(j * 2 + 1) % NP], o.z, o.w);
-            *reinterpret_cast<float4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
-          }
-        } else {
-          uint32_t q[32];  // the chunk as bf16 pairs
-          if constexpr (EPI == EPI_GELU) {
-            // gelu(x) = h + h t with h = x / 2, t = tanh(k0 (x + k1 x^3)); its derivative
-            // (1 + t) / 2 + h (1 - t^2) k0 (1 + 3 k1 x^2) reuses t and goes out as a second bf16 tile, so the
-            // backward GEMM's epilogue is a single multiply.
-            const uint64_t C0 = pack_f2(0.7978845608028654f, 0.7978845608028654f);
-            const uint64_t C1 = pack_f2(0.0356774081363001f, 0.0356774081363001f);
-            const uint64_t NC0 = pack_f2(-0.7978845608028654f, -0.7978845608028654f);
-            const uint64_t NC3 = pack_f2(-0.1070322244089003f, -0.1070322244089003f);
-            const uint64_t HALF = pack_f2(0.5f, 0.5f);
-            const uint64_t NEG1 = pack_f2(-1.0f, -1.0f);
-            if (p.aux_out) {
-              uint32_t dq[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const uint64_t x = v[i % NP];
-                const uint64_t x2 = mul2(x, x);
-                const uint64_t tt = tanh2(mul2(x, fma2(x2, C1, C0)));
-                const uint64_t h = mul2(x, HALF);
-                q[i] = f2_to_bf16x2(fma2(h, tt, h));
-                const uint64_t sgm = fma2(tt, HALF, HALF);
-                const uint64_t nq = fma2(tt, tt, NEG1);   // -(1 - t^2)
-                const uint64_t ndu = fma2(x2, NC3, NC0);  // -k0 (1 + 3 k1 x^2)
-                dq[i] = f2_to_bf16x2(fma2(mul2(h, nq), ndu, sgm));
-              }
-              if (lane == 0) tma_store_wait_read<0>();
-              __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                    make_uint4(dq[j * 4 + 0], dq[j * 4 + 1], dq[j * 4 + 2], dq[j * 4 + 3]);
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                tma_store_3d(&tmAux, st, n0 + c, tl.m0 + lane_base, out_batch);
-                tma_store_commit();
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const uint64_t x = v[i % NP];
-                const uint64_t tt = tanh2(mul2(x, fma2(mul2(x, x), C1, C0)));
-                const uint64_t h = mul2(x, HALF);
-                q[i] = f2_to_bf16x2(fma2(h, tt, h));
-              }
-            }
-          } else if constexpr (EPI == EPI_MULAUX) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              q[j * 4 + 0] = f2_to_bf16x2(mul2(v[(j * 4 + 0) % NP], bf16x2_to_f2(auxv[j].x)));
-              q[j * 4 + 1] = f2_to_bf16x2(mul2(v[(j * 4 + 1) % NP], bf16x2_to_f2(auxv[j].y)));
-              q[j * 4 + 2] = f2_to_bf16x2(mul2(v[(j * 4 + 2) % NP], bf16x2_to_f2(auxv[j].z)));
-              q[j * 4 + 3] = f2_to_bf16x2(mul2(v[(j * 4 + 3) % NP], bf16x2_to_f2(auxv[j].w)));
-            }
-          } else {
-            if (p.row_scale) {
-              const float rs = row_ok ? p.row_scale[gm] : 1.0f;
-              const uint64_t rs2 = pack_f2(rs, rs);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(mul2(v[i % NP], rs2));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(v[i % NP]);
-            }
-          }
-          if (lane == 0) tma_store_wait_read<0>();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                make_uint4(q[j * 4 + 0], q[j * 4 + 1], q[j * 4 + 2], q[j * 4 + 3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (reduce_add)
-            tma_reduce_add_3d(&tmC, st, n0 + c, tl.m0 + lane_base, out_batch);
-          else
-            tma_store_3d(&tmC, st, n0 + c, tl.m0 + lane_base, out_batch);
-          tma_store_commit();
-        }
-      }
+      epilogue_tile<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * BN, BN, tl.n0 * BN, tl.m0, lane_base, col_half, lane,
+                         my_stage);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -552,6 +289,14 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0) throw std::runtime_error("tc_gemm: C must be 16-byte aligned");
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
+
+  {
+    static const bool pairs = [] {
+      const char* e = std::getenv("TRIUNE_GEMM_PAIR");  // "0" keeps every product on the one-CTA kernel
+      return !(e && e[0] == '0');
+    }();
+    if (pairs && launch_tc_gemm_pair(a, stream)) return;
+  }
 
   // widest tile that divides N: the tensor core is most efficient at N = 256, then 192 (e.g. N = 384), then 128
   int BN = (a.N >= 256 && a.N % 256 == 0) ? 256 : ((a.N >= 192 && a.N % 192 == 0) ? 192 : (a.N > 64 ? 128 : 64));

@@ -47,4 +47,9 @@ struct GemmArgs {
 // Launches on `stream`. Throws std::runtime_error on invalid arguments.
 void launch_tc_gemm(const GemmArgs& args, cudaStream_t stream);
 
+// CTA-pair (tcgen05 cta_group::2) variant for dense products with long reductions; returns false, launching
+// nothing, when the shape does not suit it. launch_tc_gemm tries it first.
+bool launch_tc_gemm_pair(const GemmArgs& args, cudaStream_t stream);
+long long tc_gemm_pair_launch_count();  // launches taken by the CTA-pair kernel so far in this process
+
 }  // namespace tb
