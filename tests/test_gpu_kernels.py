@@ -66,9 +66,9 @@ def test_colsum_matches_fp32(dev):
 @pytest.mark.parametrize(
     "M,N,K,a_mn,b_mn,mode",
     [
-        (640, 384, 1024, False, False, "bias"),      # 256 x 384 pair tiles, odd number of 128-row tiles
+        (1152, 384, 1024, False, False, "bias"),     # 256 x 384 pair tiles, odd number (9) of 128-row tiles
         (512, 768, 1088, False, True, "plain"),      # input-gradient layout, two column tiles
-        (384, 512, 2048, True, True, "accumulate"),  # weight-gradient layout, 256 x 256 pair tiles, split-K
+        (512, 512, 2048, True, True, "accumulate"),  # weight-gradient layout, 256 x 256 pair tiles, split-K
         (1536, 384, 4096, True, True, "accumulate"),
         (256, 256, 1024, True, False, "plain"),
     ],
@@ -98,6 +98,27 @@ def test_gemm_cta_pairs(dev, M, N, K, a_mn, b_mn, mode):
         tol = 1e-2
     assert _ext.ext().tc_gemm_pair_launches() == before + 1, "the CTA-pair kernel did not take this shape"
     assert _rel(c, ref) < tol
+
+
+def test_gemm_cta_pairs_grouped_k(dev):
+    """Per-expert weight gradients (reduction grouped by expert) on the CTA-pair kernel."""
+    from triune_b200 import _ext, ops
+
+    torch.manual_seed(12)
+    R, M, N = 4096, 256, 384
+    offs = torch.tensor([0, 1536, 4096], device=dev, dtype=torch.int32)
+    a = torch.randn(R, M, device=dev, dtype=torch.bfloat16) * 0.25
+    b = torch.randn(R, N, device=dev, dtype=torch.bfloat16) * 0.25
+    before = _ext.ext().tc_gemm_pair_launches()
+    out = ops.gemm(a, b, a_mn=True, b_mn=True, mode=ops.GEMM_GROUPED_K, group_offsets=offs, num_groups=2,
+                   out_dtype=torch.float32)
+    assert _ext.ext().tc_gemm_pair_launches() == before + 1
+    for g, (lo, hi) in enumerate(((0, 1536), (1536, 4096))):
+        ref = a[lo:hi].float().t() @ b[lo:hi].float()
+        assert _rel(out[g], ref) < 2e-3
+    acc = torch.ones(2, M, N, device=dev, dtype=torch.float32)
+    ops.gemm(a, b, acc, a_mn=True, b_mn=True, accumulate=True, mode=ops.GEMM_GROUPED_K, group_offsets=offs, num_groups=2)
+    assert _rel(acc[1], 1.0 + a[1536:].float().t() @ b[1536:].float()) < 2e-3
 
 
 def test_gemm_epilogues(dev):

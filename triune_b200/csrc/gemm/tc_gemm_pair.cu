@@ -45,14 +45,19 @@ __device__ __forceinline__ Tile decode_pair_tile(const KParams& p, int t, int nu
   Tile tl;
   tl.valid = true;
   const int per_split = num_mp * p.num_n;
-  const int split = t / per_split, r = t % per_split;
+  const int split = t / per_split, r = t % per_split;  // grouped-K: `split` is the group
   tl.m0 = (r % num_mp) * (2 * BM);
   tl.n0 = r / num_mp;
   tl.g = 0;
   tl.ba = 0;
   tl.bb = 0;
   const int total_iters = (p.K + BK - 1) / BK;
-  if (p.splits > 1) {
+  if (p.mode == GEMM_GROUPED_K) {
+    tl.g = split;
+    const int k0 = p.group_offsets[split], k1 = p.group_offsets[split + 1];
+    tl.k_begin = k0;
+    tl.k_iters = (k1 - k0 + BK - 1) / BK;
+  } else if (p.splits > 1) {
     tl.k_begin = split * p.iters_per_split * BK;
     const int left = total_iters - split * p.iters_per_split;
     tl.k_iters = left < p.iters_per_split ? (left < 0 ? 0 : left) : p.iters_per_split;
@@ -340,17 +345,26 @@ int pair_sm_count() {
 
 // Runs the product on CTA pairs when the shape suits them; returns false (nothing launched) otherwise.
 bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
-  if (a.mode != GEMM_DENSE || a.batch > 1 || a.strideA != 0 || a.strideB != 0) return false;
+  const bool grouped_k = a.mode == GEMM_GROUPED_K;
+  const int groups = grouped_k ? (a.batch < 1 ? 1 : a.batch) : 1;
+  if (grouped_k) {
+    if (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major) return false;
+  } else if (a.mode != GEMM_DENSE || a.batch > 1 || a.strideA != 0 || a.strideB != 0) {
+    return false;
+  }
   if (a.flags & (GF_GELU | GF_DGELU)) return false;
-  if (a.M < 2 * BM || a.K < 4 * BK) return false;
+  if (a.M < 2 * BM) return false;
+  const int num_m_tiles = (a.M + BM - 1) / BM;
+  if ((num_m_tiles & 1) && num_m_tiles < 9) return false;  // an odd tile leaves half a pair idle: too costly when few
+  const long long k_each = (long long)a.K / groups;       // grouped-K: K is the total over the groups
   int ncfg = 0;
-  if (a.N % 384 == 0 && a.K >= 1024) ncfg = 384;          // model-width outputs with a long reduction
-  else if (a.N % 256 == 0 && a.K >= 1024) ncfg = 256;     // short reductions are epilogue-bound: pairs gain nothing
+  if (a.N % 384 == 0 && k_each >= 1024) ncfg = 384;        // model-width outputs with a long reduction
+  else if (a.N % 256 == 0 && k_each >= 1024) ncfg = 256;   // short reductions are epilogue-bound: pairs gain nothing
   if (ncfg == 0) return false;
 
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
-  kp.mode = a.mode; kp.flags = a.flags; kp.batch = 1;
+  kp.mode = a.mode; kp.flags = a.flags; kp.batch = groups;
   kp.num_m = (a.M + BM - 1) / BM;
   kp.num_n = a.N / ncfg;
   kp.ldc = a.ldc; kp.strideC = a.strideC;
@@ -358,14 +372,14 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.alpha = a.alpha;
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
-  kp.tile_group = nullptr; kp.group_offsets = nullptr; kp.status = a.status;
+  kp.tile_group = nullptr; kp.group_offsets = a.group_offsets; kp.status = a.status;
   kp.splits = 1;
   kp.iters_per_split = 0;
   const int num_mp = (kp.num_m + 1) / 2;
-  int pair_tiles = num_mp * kp.num_n;
+  int pair_tiles = num_mp * kp.num_n * groups;
   const int max_clusters = pair_sm_count() / 2;
   // Split-K exactly as in the one-CTA kernel: only into an fp32 accumulator, when the tiles leave most SMs idle.
-  if ((kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr && a.row_scale == nullptr) {
+  if (!grouped_k && (kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr && a.row_scale == nullptr) {
     const int total_iters = (a.K + BK - 1) / BK;
     if (pair_tiles * 2 <= max_clusters && total_iters >= 16) {
       int splits = max_clusters / pair_tiles;
@@ -395,9 +409,10 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
                        (uint64_t)a.ldb * 2ull, BK, 64);
   const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
   const int c_elem = c_f32 ? 4 : 2;
+  const uint64_t c_bstride = (groups > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
   CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
-                                 (uint64_t)a.N, (uint64_t)a.M, 1, (uint64_t)a.ldc * c_elem,
-                                 (uint64_t)a.ldc * (uint64_t)a.M * c_elem, c_f32 ? 32 : 64, 32);
+                                 (uint64_t)a.N, (uint64_t)a.M, (uint64_t)groups, (uint64_t)a.ldc * c_elem, c_bstride,
+                                 c_f32 ? 32 : 64, 32);
   CUtensorMap tmAux = tmC;
   const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
   const int epi = c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN;
