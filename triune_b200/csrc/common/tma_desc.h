@@ -31,7 +31,7 @@ inline EncodeTiledFn get_encode_fn() {
 }
 
 // 3-D tiled map over a [d2][d1][d0] array (d0 contiguous). Strides in BYTES for d1 and d2 (multiples of
-// 16). Boxes are {b0, b1, 1}. 128-byte swizzle when b0 * elem_bytes == 128, none otherwise.
+// 16). Boxes are {b0, b1, 1}. 128-byte swizzle when b0 * elem_bytes == 128, 64-byte swizzle when it is 64, none otherwise.
 inline CUtensorMap make_tmap_3d(const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d0, uint64_t d1,
                                 uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
                                 uint32_t b1) {
@@ -44,7 +44,8 @@ inline CUtensorMap make_tmap_3d(const void* base, CUtensorMapDataType dt, int el
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUtensorMapSwizzle sw = (b0 * elem_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUtensorMapSwizzle sw = (b0 * elem_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (b0 * elem_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
   CUresult r = get_encode_fn()(&m, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int col_half = (warp - 2) >> 2;
     uint8_t* my_stage = smem_epi + (warp - 2) * EPI_TILE;  // one staging tile per warp (a second one costs a load stage and measured slower)
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, buf = 0;
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       Tile tl = decode_tile(p, t);
       if (!tl.valid) continue;
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       }
       tc_fence_after_sync();
       epilogue_tile<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * BN, BN, tl.n0 * BN, tl.m0, lane_base, col_half, lane,
-                         my_stage);
+                         my_stage, buf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -321,6 +321,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.total_tiles = kp.num_m * kp.num_n * (a.mode == GEMM_GROUPED_M ? 1 : kp.batch);
   kp.splits = 1;
   kp.iters_per_split = 0;
+  kp.group_m = raster_group_m(kp.num_m, kp.num_n, sm_count());
   // Split-K: weight gradients reduce over tens of thousands of tokens into a handful of output tiles; spread the
   // reduction over idle SMs. Only when the output is an fp32 accumulator (partials are added with red.add).
   if (a.mode == GEMM_DENSE && (kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr &&
@@ -357,18 +358,18 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   } else {
     tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull, sB, BK, (uint32_t)BN);
   }
-  // output maps: rows of 128 bytes (64 bf16 / 32 fp32) x 32 rows, one box per epilogue warp and column chunk
+  // output maps: rows of 64 bytes (32 bf16 / 16 fp32) x 32 rows, one box per epilogue warp and column chunk
   const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
   const int c_elem = c_f32 ? 4 : 2;
   const uint64_t c_batches = (a.mode == GEMM_GROUPED_M) ? 1 : (uint64_t)kp.batch;
   const uint64_t c_bstride = (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
   CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
                                  (uint64_t)a.N, (uint64_t)a.M, c_batches, (uint64_t)a.ldc * c_elem, c_bstride,
-                                 c_f32 ? 32 : 64, 32);
+                                 c_f32 ? 16 : 32, 32);
   CUtensorMap tmAux = tmC;
   if (a.aux_out != nullptr)
     tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.M, c_batches,
-                         (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 64, 32);
+                         (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 32, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
   const int epi = (kp.flags & GF_GELU) ? EPI_GELU : ((kp.flags & GF_DGELU) ? EPI_MULAUX : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN));
   if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);

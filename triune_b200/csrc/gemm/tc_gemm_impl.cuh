@@ -42,6 +42,7 @@ struct KParams {
   const int* group_offsets;
   int* status;
   int total_tiles;
+  int group_m;          // tile order: blocks of group_m row tiles x all column tiles (see raster)
   int splits;           // split-K factor (dense mode, fp32 accumulate only)
   int iters_per_split;  // K iterations (of 64) handled by one split
 };
@@ -51,11 +52,30 @@ struct Tile {
   bool valid;
 };
 
+// Tile order. The CTAs of one wave should share as many operand tiles as possible: the tiles are walked in blocks
+// of group_m row tiles x all num_n column tiles, row tile fastest inside a block, and group_m * num_n is about the
+// number of SMs. A block's A tiles are then read from DRAM once (every column tile of the block uses them while they
+// are in L2) instead of once per column tile, which matters as soon as A plus the output outgrow L2.
+__device__ __forceinline__ void raster(int r, int num_m, int num_n, int group_m, int& m_idx, int& n_idx) {
+  const int per_block = group_m * num_n;
+  const int blk = r / per_block, within = r % per_block;
+  const int m_first = blk * group_m;
+  const int gm = (num_m - m_first) < group_m ? (num_m - m_first) : group_m;
+  m_idx = m_first + within % gm;
+  n_idx = within / gm;
+}
+__host__ inline int raster_group_m(int num_m, int num_n, int ctas) {
+  int g = ctas / (num_n < 1 ? 1 : num_n);
+  if (g < 1) g = 1;
+  return g > num_m ? num_m : g;
+}
+
 __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
   Tile tl;
   tl.valid = true;
   if (p.mode == GEMM_GROUPED_M) {
-    int m_idx = t % p.num_m, n_idx = t / p.num_m;
+    int m_idx, n_idx;
+    raster(t, p.num_m, p.num_n, p.group_m, m_idx, n_idx);
     int g = p.tile_group[m_idx];
     tl.valid = g >= 0;
     tl.g = g < 0 ? 0 : g;
@@ -74,8 +94,10 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
       t = t % base;
     }
     int b = t / per_b, r = t % per_b;
-    tl.m0 = (r % p.num_m) * BM;
-    tl.n0 = r / p.num_m;
+    int m_idx, n_idx;
+    raster(r, p.num_m, p.num_n, p.group_m, m_idx, n_idx);
+    tl.m0 = m_idx * BM;
+    tl.n0 = n_idx;
     tl.g = b;
     if (p.mode == GEMM_GROUPED_K) {
       tl.ba = 0;
@@ -113,18 +135,33 @@ enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3 };
 
 // One accumulator tile (128 rows x n_cols fp32 in TMEM at tmem_acc) through the epilogue EPI and out to global
 // memory. Called by the eight epilogue warps of a CTA: a warp can only read the TMEM lanes of its quarter
-// (warp % 4), so two warps share every quarter and take alternate column chunks (col_half 0 / 1). Per chunk
-// (128 bytes of output: 64 bf16 or 32 fp32) a warp reads the accumulator, applies the epilogue in packed f32x2
-// arithmetic, writes the rows into its private 128B-swizzled staging tile and one lane hands the tile to TMA (plain
-// store, or reduce-add for accumulate / split-K): global writes are full 128-byte lines regardless of the row pitch,
-// and ragged M/N edges are clipped by the tensor map. m_base is the first output row of this CTA's 128 rows, n0 the
-// first output column of the tile.
+// (warp % 4), so two warps share every quarter and take alternate column chunks (col_half 0 / 1). Per chunk (64 bytes
+// of output per row: 32 bf16 or 16 fp32 columns) a warp reads the accumulator, applies the epilogue in packed f32x2
+// arithmetic, writes its 32 rows into one of its two 64B-swizzled staging buffers and one lane hands the buffer to TMA
+// (plain store, or reduce-add for accumulate / split-K). The buffers alternate, and a buffer is reused once the store
+// issued two chunks earlier has read it, so a warp never waits for the store it has just issued: with one buffer per
+// warp that wait (about a microsecond per chunk) made short reductions epilogue-bound. Ragged M/N edges are clipped
+// by the tensor map. m_base is the first output row of this CTA's 128 rows, n0 the first output column of the tile;
+// `buf` carries the buffer choice from tile to tile.
+constexpr int EPI_BUF = 32 * 64;  // one staging buffer: 32 rows x 64 bytes
+
+__device__ __forceinline__ uint8_t* epi_claim(uint8_t* my_stage, uint32_t& buf, int lane) {
+  if (lane == 0) tma_store_wait_read<1>();
+  __syncwarp();
+  uint8_t* st = my_stage + buf * EPI_BUF;
+  buf ^= 1u;
+  return st;
+}
+// 16-byte unit j of row `lane` in a 64B-swizzled buffer
+__device__ __forceinline__ uint32_t epi_off(int lane, int j) { return lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4); }
+
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, const CUtensorMap* tmC,
                                               const CUtensorMap* tmAux, uint32_t tmem_acc, int n_cols, int n0,
-                                              int m_base, int lane_base, int col_half, int lane, uint8_t* my_stage) {
+                                              int m_base, int lane_base, int col_half, int lane, uint8_t* my_stage,
+                                              uint32_t& buf) {
   constexpr bool out_f32 = (EPI == EPI_PLAIN_F32);
-  constexpr int CW = out_f32 ? 32 : 64;  // columns per staged chunk (128 bytes)
+  constexpr int CW = out_f32 ? 16 : 32;  // columns per staged chunk (64 bytes)
   constexpr int NP = CW / 2;             // packed fp32 pairs per lane and chunk
   const bool reduce_add = ((p.flags & GF_ACCUMULATE) != 0) || p.splits > 1;
   const uint64_t alpha2 = pack_f2(p.alpha, p.alpha);
@@ -138,28 +175,30 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
     if (n0 + c >= p.N) break;
     uint64_t v[NP];
     // Multiplier rows (the activation derivative saved by the forward pass): issue the loads first so their
-    // latency hides behind the TMEM reads.
-    uint4 auxv[8];
+    // latency hides behind the TMEM read.
+    uint4 auxv[4];
     if constexpr (EPI == EPI_MULAUX) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const int gn = n0 + c + j * 8;
         auxv[j] = (row_ok && gn < p.N) ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn)
                                        : make_uint4(0u, 0u, 0u, 0u);
       }
     }
     if (tl.k_iters > 0) {
-      uint32_t r0[32], r1[32];
       const uint32_t taddr = tmem_acc + ((uint32_t)lane_base << 16) + c;
-      tmem_ld_32x32b_x32(taddr, r0);
-      if (!out_f32) tmem_ld_32x32b_x32(taddr + 32, r1);
-      tmem_ld_wait();
+      if constexpr (out_f32) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = pack_f2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-      if (!out_f32) {
+        for (int i = 0; i < NP; ++i) v[i] = pack_f2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr, r);
+        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          v[(NP - 16) + i] = pack_f2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+        for (int i = 0; i < NP; ++i) v[i] = pack_f2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
       }
     } else {
 #pragma unroll
@@ -182,7 +221,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
 #pragma unroll
       for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], alpha2);
     }
-    uint8_t* st = my_stage;
+    uint8_t* st;
     if constexpr (EPI == EPI_PLAIN_F32) {
       if (p.row_scale) {
         const float rs = row_ok ? p.row_scale[gm] : 1.0f;
@@ -190,17 +229,16 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
 #pragma unroll
         for (int i = 0; i < NP; ++i) v[i] = mul2(v[i], rs2);
       }
-      if (lane == 0) tma_store_wait_read<0>();
-      __syncwarp();
+      st = epi_claim(my_stage, buf, lane);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         float4 o;
-        unpack_f2(v[(j * 2) % NP], o.x, o.y);
-        unpack_f2(v[(j * 2 + 1) % NP], o.z, o.w);
-        *reinterpret_cast<float4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+        unpack_f2(v[j * 2], o.x, o.y);
+        unpack_f2(v[j * 2 + 1], o.z, o.w);
+        *reinterpret_cast<float4*>(st + epi_off(lane, j)) = o;
       }
     } else {
-      uint32_t q[32];  // the chunk as bf16 pairs
+      uint32_t q[16];  // the chunk as bf16 pairs
       if constexpr (EPI == EPI_GELU) {
         // gelu(x) = h + h t with h = x / 2, t = tanh(k0 (x + k1 x^3)); its derivative
         // (1 + t) / 2 + h (1 - t^2) k0 (1 + 3 k1 x^2) reuses t and goes out as a second bf16 tile, so the
@@ -212,9 +250,9 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         const uint64_t HALF = pack_f2(0.5f, 0.5f);
         const uint64_t NEG1 = pack_f2(-1.0f, -1.0f);
         if (p.aux_out) {
-          uint32_t dq[32];
+          uint32_t dq[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const uint64_t x = v[i % NP];
             const uint64_t x2 = mul2(x, x);
             const uint64_t tt = tanh2(mul2(x, fma2(x2, C1, C0)));
@@ -225,21 +263,20 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
             const uint64_t ndu = fma2(x2, NC3, NC0);  // -k0 (1 + 3 k1 x^2)
             dq[i] = f2_to_bf16x2(fma2(mul2(h, nq), ndu, sgm));
           }
-          if (lane == 0) tma_store_wait_read<0>();
-          __syncwarp();
+          uint8_t* sd = epi_claim(my_stage, buf, lane);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(sd + epi_off(lane, j)) =
                 make_uint4(dq[j * 4 + 0], dq[j * 4 + 1], dq[j * 4 + 2], dq[j * 4 + 3]);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(tmAux, st, n0 + c, m_base + lane_base, out_batch);
+            tma_store_3d(tmAux, sd, n0 + c, m_base + lane_base, out_batch);
             tma_store_commit();
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const uint64_t x = v[i % NP];
             const uint64_t tt = tanh2(mul2(x, fma2(mul2(x, x), C1, C0)));
             const uint64_t h = mul2(x, HALF);
@@ -248,7 +285,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         }
       } else if constexpr (EPI == EPI_MULAUX) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           q[j * 4 + 0] = f2_to_bf16x2(mul2(v[(j * 4 + 0) % NP], bf16x2_to_f2(auxv[j].x)));
           q[j * 4 + 1] = f2_to_bf16x2(mul2(v[(j * 4 + 1) % NP], bf16x2_to_f2(auxv[j].y)));
           q[j * 4 + 2] = f2_to_bf16x2(mul2(v[(j * 4 + 2) % NP], bf16x2_to_f2(auxv[j].z)));
@@ -259,17 +296,16 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
           const float rs = row_ok ? p.row_scale[gm] : 1.0f;
           const uint64_t rs2 = pack_f2(rs, rs);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(mul2(v[i % NP], rs2));
+          for (int i = 0; i < 16; ++i) q[i] = f2_to_bf16x2(mul2(v[i % NP], rs2));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) q[i] = f2_to_bf16x2(v[i % NP]);
+          for (int i = 0; i < 16; ++i) q[i] = f2_to_bf16x2(v[i % NP]);
         }
       }
-      if (lane == 0) tma_store_wait_read<0>();
-      __syncwarp();
+      st = epi_claim(my_stage, buf, lane);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(st + epi_off(lane, j)) =
             make_uint4(q[j * 4 + 0], q[j * 4 + 1], q[j * 4 + 2], q[j * 4 + 3]);
     }
     fence_proxy_async_smem();

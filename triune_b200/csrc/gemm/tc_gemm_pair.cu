@@ -46,8 +46,10 @@ __device__ __forceinline__ Tile decode_pair_tile(const KParams& p, int t, int nu
   tl.valid = true;
   const int per_split = num_mp * p.num_n;
   const int split = t / per_split, r = t % per_split;  // grouped-K: `split` is the group
-  tl.m0 = (r % num_mp) * (2 * BM);
-  tl.n0 = r / num_mp;
+  int m_idx, n_idx;
+  raster(r, num_mp, p.num_n, p.group_m, m_idx, n_idx);
+  tl.m0 = m_idx * (2 * BM);
+  tl.n0 = n_idx;
   tl.g = 0;
   tl.ba = 0;
   tl.bb = 0;
@@ -241,7 +243,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int col_half = (warp - 2) >> 2;
     uint8_t* my_stage = smem_epi + (warp - 2) * EPI_TILE;
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, buf = 0;
     for (int t = cluster_id; t < pair_tiles; t += num_clusters) {
       const Tile tl = decode_pair_tile(p, t, num_mp);
       bool ok = mbar_wait(&acc_full[acc], acc_phase);
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       }
       tc_fence_after_sync();
       epilogue_tile<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * 256, NCFG, tl.n0 * NCFG, tl.m0 + (int)rank * BM,
-                         lane_base, col_half, lane, my_stage);
+                         lane_base, col_half, lane, my_stage, buf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -376,6 +378,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.splits = 1;
   kp.iters_per_split = 0;
   const int num_mp = (kp.num_m + 1) / 2;
+  kp.group_m = raster_group_m(num_mp, kp.num_n, pair_sm_count() / 2);
   int pair_tiles = num_mp * kp.num_n * groups;
   const int max_clusters = pair_sm_count() / 2;
   // Split-K exactly as in the one-CTA kernel: only into an fp32 accumulator, when the tiles leave most SMs idle.
@@ -412,7 +415,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   const uint64_t c_bstride = (groups > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
   CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
                                  (uint64_t)a.N, (uint64_t)a.M, (uint64_t)groups, (uint64_t)a.ldc * c_elem, c_bstride,
-                                 c_f32 ? 32 : 64, 32);
+                                 c_f32 ? 16 : 32, 32);
   CUtensorMap tmAux = tmC;
   const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
   const int epi = c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN;
