@@ -36,11 +36,12 @@ def _tick(n):
 
 
 def supported(q, k, v, g, initial_state) -> bool:
-    """True when the CUDA kernels cover this call (bf16, head_dim 64, T a multiple of 64 or T == 1)."""
+    """True when the CUDA kernels cover this call (bf16, head dims multiples of 64 up to 256, T >= 64 or T == 1)."""
     if not _ext.use_kernels(q, k, v, g):
         return False
     B, T, H, D = q.shape
-    if q.dtype != torch.bfloat16 or D != 64 or v.shape[-1] != 64:
+    Dv = v.shape[-1]
+    if q.dtype != torch.bfloat16 or D % 64 != 0 or Dv % 64 != 0 or D > 256 or Dv > 256:
         return False
     if T == 1:
         return initial_state is not None and not torch.is_grad_enabled()
@@ -92,6 +93,8 @@ def gla_chunk(q, k, v, g, initial_state, scale, gate_logits):
     from . import reference as ref
 
     B, T, H, D = q.shape
+    if D != 64 or v.shape[-1] != 64:
+        return _gla_wide_heads(q, k, v, g, initial_state, scale, gate_logits)
     if T == 1:
         return decode_step(q, k, v, g, initial_state, gate_logits)
     Tm = (T // 64) * 64
@@ -103,6 +106,34 @@ def gla_chunk(q, k, v, g, initial_state, scale, gate_logits):
     if scale != 1.0:
         out = out * scale
     return out, state
+
+
+def _gla_wide_heads(q, k, v, g, initial_state, scale, gate_logits):
+    """Heads wider than 64 on the 64-wide kernels.
+
+    The decay is diagonal over key dimensions, so the state rows of different key dimensions never mix:
+    S[d, :] only sees q_d, k_d, g_d. A head with dk = 64 a, dv = 64 c is therefore exactly the sum over the ``a``
+    key slices of ``a * c`` independent 64 x 64 heads (key slice i with value slice j), and the state is their block
+    matrix. The slices are laid out as extra heads; autograd sums the gradients of the repeated slices.
+    """
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    a, c = Dk // 64, Dv // 64
+
+    def keys(x):  # [B,T,H,Dk] -> [B,T,H*a*c,64], key slice i repeated for every value slice
+        return x.reshape(B, T, H, a, 1, 64).expand(B, T, H, a, c, 64).reshape(B, T, H * a * c, 64)
+
+    v4 = v.reshape(B, T, H, 1, c, 64).expand(B, T, H, a, c, 64).reshape(B, T, H * a * c, 64)
+    init4 = None
+    if initial_state is not None:
+        init4 = (initial_state.float().reshape(B, H, a, 64, c, 64).permute(0, 1, 2, 4, 3, 5)
+                 .reshape(B, H * a * c, 64, 64).contiguous())
+    o4, s4 = gla_chunk(keys(q), keys(k), v4, keys(g), init4, 1.0, gate_logits)
+    out = o4.reshape(B, T, H, a, c, 64).float().sum(3).reshape(B, T, H, Dv)
+    if scale != 1.0:
+        out = out * scale
+    state = s4.reshape(B, H, a, c, 64, 64).permute(0, 1, 2, 4, 3, 5).reshape(B, H, Dk, Dv)
+    return out.to(q.dtype), state
 
 
 @torch.no_grad()
