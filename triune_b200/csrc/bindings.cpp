@@ -395,6 +395,9 @@ void register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tc_gemm", &tc_gemm);
+  m.def("tc_gemm_debug_buffer", [](const c10::optional<Tensor>& t) {
+    tb::tc_gemm_set_debug_buffer(t.has_value() && t->defined() ? (long long*)t->data_ptr<int64_t>() : nullptr);
+  });
   m.def("tc_gemm_pair_launches", []() { return (int64_t)tb::tc_gemm_pair_launch_count(); });
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

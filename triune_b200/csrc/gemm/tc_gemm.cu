@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  const long long t_begin = (p.dbg != nullptr && threadIdx.x == 128) ? clock64() : 0;
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -195,8 +196,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       Tile tl = decode_tile(p, t);
       if (!tl.valid) continue;
+      const bool timed = p.dbg != nullptr && lane == 0 && warp == 2;
+      const long long tw0 = timed ? clock64() : 0;
       bool ok = mbar_wait(&acc_full[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
+      if (timed) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 5), (unsigned long long)(clock64() - tw0));  // wait for MMA
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 6), 1ull);                                    // tiles
+      }
       if (!ok) {
         if (lane == 0) report(p, ST_TIMEOUT_TMEM);
         break;
@@ -212,8 +219,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         acc_phase ^= 1;
       }
     }
+    const long long t_drain = (p.dbg != nullptr && threadIdx.x == 128) ? clock64() : 0;
     if (lane == 0) tma_store_wait<0>();  // staged tiles must be fully written before the CTA retires
     __syncwarp();
+    if (p.dbg != nullptr && threadIdx.x == 128) {
+      const long long now = clock64();
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 8), (unsigned long long)(now - t_begin));  // role lifetime
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 9), (unsigned long long)(now - t_drain));  // final drain
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 10), 1ull);
+    }
   }
 
   tc_fence_before_sync();
@@ -273,6 +287,9 @@ int sm_count() {
 
 }  // namespace
 
+static long long* g_gemm_dbg = nullptr;
+void tc_gemm_set_debug_buffer(long long* p) { g_gemm_dbg = p; }
+
 void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0) return;
   if (a.N % 8 != 0) throw std::runtime_error("tc_gemm: N must be a multiple of 8");
@@ -318,6 +335,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
   kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.dbg = g_gemm_dbg;
   kp.total_tiles = kp.num_m * kp.num_n * (a.mode == GEMM_GROUPED_M ? 1 : kp.batch);
   kp.splits = 1;
   kp.iters_per_split = 0;

@@ -41,6 +41,7 @@ struct KParams {
   const int* tile_group;
   const int* group_offsets;
   int* status;
+  long long* dbg;       // optional phase timers (clock ticks summed over one warp's chunks), null in normal runs
   int total_tiles;
   int group_m;          // tile order: blocks of group_m row tiles x all column tiles (see raster)
   int splits;           // split-K factor (dense mode, fp32 accumulate only)
@@ -173,6 +174,9 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
 #pragma unroll 1
   for (int c = col_half * CW; c < n_cols; c += 2 * CW) {
     if (n0 + c >= p.N) break;
+    const bool timed = p.dbg != nullptr && lane == 0 && lane_base == 0 && col_half == 0;
+    long long tk0 = 0, tk1 = 0, tk2 = 0, tk3 = 0;
+    if (timed) tk0 = clock64();
     uint64_t v[NP];
     // Multiplier rows (the activation derivative saved by the forward pass): issue the loads first so their
     // latency hides behind the TMEM read.
@@ -204,6 +208,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
 #pragma unroll
       for (int i = 0; i < NP; ++i) v[i] = 0ull;
     }
+    if (timed) tk1 = clock64();
     // alpha and bias: one packed fma per pair
     if (bias) {
 #pragma unroll
@@ -302,7 +307,9 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
           for (int i = 0; i < 16; ++i) q[i] = f2_to_bf16x2(v[i % NP]);
         }
       }
+      if (timed) tk2 = clock64();
       st = epi_claim(my_stage, buf, lane);
+      if (timed) tk3 = clock64();
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         *reinterpret_cast<uint4*>(st + epi_off(lane, j)) =
@@ -310,6 +317,14 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
     }
     fence_proxy_async_smem();
     __syncwarp();
+    if (timed) {
+      const long long tk4 = clock64();
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 0), (unsigned long long)(tk1 - tk0));  // TMEM read
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 1), (unsigned long long)(tk2 - tk1));  // arithmetic
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 2), (unsigned long long)(tk3 - tk2));  // buffer claim
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 3), (unsigned long long)(tk4 - tk3));  // staging writes + fence
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 4), 1ull);                              // chunks
+    }
     if (lane == 0) {
       if (reduce_add)
         tma_reduce_add_3d(tmC, st, n0 + c, m_base + lane_base, out_batch);
@@ -317,6 +332,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         tma_store_3d(tmC, st, n0 + c, m_base + lane_base, out_batch);
       tma_store_commit();
     }
+    if (timed) atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 7), (unsigned long long)(clock64() - tk0));  // whole chunk
   }
 }
 

@@ -19,6 +19,7 @@
 // an accumulator, in both CTAs at once. Loads carry no cluster multicast. Every wait is bounded.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -359,9 +360,13 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   const int num_m_tiles = (a.M + BM - 1) / BM;
   if ((num_m_tiles & 1) && num_m_tiles < 9) return false;  // an odd tile leaves half a pair idle: too costly when few
   const long long k_each = (long long)a.K / groups;       // grouped-K: K is the total over the groups
+  static const long long min_k = [] {
+    const char* e = std::getenv("TRIUNE_GEMM_PAIR_MIN_K");  // tuning knob: shortest reduction handed to CTA pairs
+    return e ? std::atoll(e) : 768ll;
+  }();
   int ncfg = 0;
-  if (a.N % 384 == 0 && k_each >= 1024) ncfg = 384;        // model-width outputs with a long reduction
-  else if (a.N % 256 == 0 && k_each >= 1024) ncfg = 256;   // short reductions are epilogue-bound: pairs gain nothing
+  if (a.N % 384 == 0 && k_each >= (min_k < 1024 ? 1024 : min_k)) ncfg = 384;  // single-buffered: long reductions only
+  else if (a.N % 256 == 0 && k_each >= min_k) ncfg = 256;
   if (ncfg == 0) return false;
 
   KParams kp;
@@ -375,6 +380,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
   kp.tile_group = nullptr; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.dbg = nullptr;
   kp.splits = 1;
   kp.iters_per_split = 0;
   const int num_mp = (kp.num_m + 1) / 2;
