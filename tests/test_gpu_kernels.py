@@ -153,6 +153,36 @@ def test_gla_wide_heads_match_recurrence(dev, Dk, Dv):
     assert _rel(o1, o1r) < 2e-2 and _rel(s1, s1r) < 2e-2
 
 
+def test_gemm_cta_pairs_grouped_rows(dev):
+    """Rows grouped by expert (groups padded to 256 rows) on the CTA-pair kernel: expert down-projection shape."""
+    from triune_b200 import _ext, ops
+
+    torch.manual_seed(13)
+    E, K, N = 3, 1536, 384
+    tiles = torch.tensor([0, 0, 0, 0, 2, 2, 1, 1, 1, 1, -1, -1], device=dev, dtype=torch.int32)  # per 128 rows
+    R = tiles.numel() * 128
+    a = torch.randn(R, K, device=dev, dtype=torch.bfloat16) * 0.25
+    w = torch.randn(E, N, K, device=dev, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(E, N, device=dev, dtype=torch.bfloat16)
+    out = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
+    before = _ext.ext().tc_gemm_pair_launches()
+    ops.gemm(a, w, out, bias=bias, mode=ops.GEMM_GROUPED_M, tile_group=tiles, paired_groups=True)
+    assert _ext.ext().tc_gemm_pair_launches() == before + 1
+    ref_out = torch.zeros(R, N, device=dev)
+    for t, g in enumerate(tiles.tolist()):
+        if g >= 0:
+            rows = slice(t * 128, t * 128 + 128)
+            ref_out[rows] = a[rows].float() @ w[g].float().t() + bias[g].float()
+    assert _rel(out, ref_out) < 1e-2
+    assert float(out[10 * 128:].abs().max()) == 0.0  # unused tiles are never written
+    # MN-major B (input-gradient layout): w as [E, K, N]
+    wt = w.transpose(1, 2).contiguous()
+    out2 = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
+    ops.gemm(a, wt, out2, b_mn=True, mode=ops.GEMM_GROUPED_M, tile_group=tiles, paired_groups=True)
+    assert _ext.ext().tc_gemm_pair_launches() == before + 2
+    assert _rel(out2, ref_out - torch.where((tiles >= 0).repeat_interleave(128)[:, None], bias[tiles.clamp_min(0).long()].float().repeat_interleave(128, 0), torch.zeros(1, device=dev))) < 1e-2
+
+
 def test_gemm_epilogues(dev):
     from triune_b200 import ops
 
@@ -528,8 +558,9 @@ def test_moe_route_plan_matches_oracle(N, E, K, cap):
     assert torch.equal(tile_group.long()[p[kept] // 128], idx.reshape(-1)[kept])
     cnt = torch.zeros(E, device="cuda", dtype=torch.int64).scatter_add_(0, idx.reshape(-1)[kept], torch.ones_like(p[kept]))
     assert torch.equal(accepted, cnt)
-    padded = (cnt + 127) // 128 * 128
+    padded = (cnt + 255) // 256 * 256  # whole pairs of 128-row tiles per expert
     assert torch.equal(offsets.long(), torch.cat((padded.new_zeros(1), padded.cumsum(0))))
+    assert torch.equal(tile_group[0::2], tile_group[1::2])
 
 
 def test_graph_replayed_decoder_matches_eager_generation():

@@ -278,7 +278,7 @@ std::vector<Tensor> moe_plan_sorted(const Tensor& sorted_keys, const Tensor& ord
   TORCH_CHECK(sorted_keys.scalar_type() == at::kLong && order.scalar_type() == at::kLong && counts.scalar_type() == at::kInt, "dtypes");
   c10::cuda::CUDAGuard guard(sorted_keys.device());
   const int64_t A = N * K, E = counts.size(0);
-  const int64_t R = (A + 127) / 128 * 128 + E * 128;
+  const int64_t R = (A + 255) / 256 * 256 + E * 256;  // every expert's rows are padded to a multiple of 256
   auto oi = sorted_keys.options().dtype(at::kInt);
   Tensor pos = torch::empty({N, K}, oi), keep = torch::empty({N, K}, sorted_keys.options().dtype(at::kBool));
   Tensor row_src = torch::empty({R}, oi), tile_group = torch::empty({R / 128}, oi), offsets = torch::empty({E + 1}, oi);

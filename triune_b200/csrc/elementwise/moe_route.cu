@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) moe_plan_sorted_kernel(const long long* _
         run += c;
         acc += c < cap ? c : cap;
       }
-      rows += (acc + 127) / 128 * 128;
+      rows += (acc + 255) / 256 * 256;  // whole pairs of 128-row tiles: the CTA-pair GEMM needs one expert per pair
       if (blockIdx.x == 0) accepted[e] = acc;
     }
     exp_pad_start[E] = rows;

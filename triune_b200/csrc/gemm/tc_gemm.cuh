@@ -17,6 +17,7 @@ enum GemmFlags : int {
   GF_ACCUMULATE = 2,  // C += result
   GF_GELU = 4,        // C = gelu_tanh(result + bias); gelu_tanh'(result + bias) optionally saved to aux_out
   GF_DGELU = 8,       // C = result * aux_in (aux_in = the derivative rows saved by GF_GELU)
+  GF_PAIRED_GROUPS = 16,  // GEMM_GROUPED_M: every group's rows are padded to 256, so tile_group[2i] == tile_group[2i+1]
 };
 
 // Operand layouts. "K-major": the reduction index is contiguous (x[M,K] row-major, w[N,K] row-major).

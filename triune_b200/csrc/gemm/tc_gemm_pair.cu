@@ -55,7 +55,14 @@ __device__ __forceinline__ Tile decode_pair_tile(const KParams& p, int t, int nu
   tl.ba = 0;
   tl.bb = 0;
   const int total_iters = (p.K + BK - 1) / BK;
-  if (p.mode == GEMM_GROUPED_K) {
+  if (p.mode == GEMM_GROUPED_M) {  // rows grouped by expert, groups padded to whole pairs: B and bias follow the group
+    const int g = p.tile_group[2 * m_idx];
+    tl.valid = g >= 0;
+    tl.g = g < 0 ? 0 : g;
+    tl.bb = tl.g;
+    tl.k_begin = 0;
+    tl.k_iters = total_iters;
+  } else if (p.mode == GEMM_GROUPED_K) {
     tl.g = split;
     const int k0 = p.group_offsets[split], k1 = p.group_offsets[split + 1];
     tl.k_begin = k0;
@@ -129,6 +136,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       for (int t = cluster_id; t < pair_tiles && ok; t += num_clusters) {
         const Tile tl = decode_pair_tile(p, t, num_mp);
+        if (!tl.valid) continue;
         const int n0 = tl.n0 * NCFG;
         const int m0 = tl.m0 + (int)rank * BM;
         for (int it = 0; it < tl.k_iters; ++it) {
@@ -153,9 +161,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             // this CTA's half of B: boxes 0,1 belong to the N = 256 MMA, box 2 (NCFG = 384) to the N = 128 MMA
             const int nb = (j < 2) ? (n0 + 128 * (int)rank + 64 * j) : (n0 + 256 + 64 * (int)rank);
             if (B_MN)
-              tma_load_3d_pair(b_dst + j * (BK * 128), &tmB, bar, nb, k0, 0);
+              tma_load_3d_pair(b_dst + j * (BK * 128), &tmB, bar, nb, k0, tl.bb);
             else
-              tma_load_3d_pair(b_dst + j * (64 * 128), &tmB, bar, k0, nb, 0);
+              tma_load_3d_pair(b_dst + j * (64 * 128), &tmB, bar, k0, nb, tl.bb);
           }
           ++issued;
           if (++stage == STAGES) {
@@ -190,6 +198,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       for (int t = cluster_id; t < pair_tiles && ok; t += num_clusters) {
         const Tile tl = decode_pair_tile(p, t, num_mp);
+        if (!tl.valid) continue;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
           report(p, ST_TIMEOUT_TMEM);
           break;
@@ -247,6 +256,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t acc_phase = 0, buf = 0;
     for (int t = cluster_id; t < pair_tiles; t += num_clusters) {
       const Tile tl = decode_pair_tile(p, t, num_mp);
+      if (!tl.valid) continue;
       bool ok = mbar_wait(&acc_full[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -349,9 +359,12 @@ int pair_sm_count() {
 // Runs the product on CTA pairs when the shape suits them; returns false (nothing launched) otherwise.
 bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   const bool grouped_k = a.mode == GEMM_GROUPED_K;
+  const bool grouped_m = a.mode == GEMM_GROUPED_M;
   const int groups = grouped_k ? (a.batch < 1 ? 1 : a.batch) : 1;
   if (grouped_k) {
     if (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major) return false;
+  } else if (grouped_m) {
+    if (!(a.flags & GF_PAIRED_GROUPS) || a.tile_group == nullptr || a.strideA != 0 || (a.M % (2 * BM)) != 0) return false;
   } else if (a.mode != GEMM_DENSE || a.batch > 1 || a.strideA != 0 || a.strideB != 0) {
     return false;
   }
@@ -379,7 +392,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.alpha = a.alpha;
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
-  kp.tile_group = nullptr; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
   kp.dbg = nullptr;
   kp.splits = 1;
   kp.iters_per_split = 0;
@@ -388,7 +401,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   int pair_tiles = num_mp * kp.num_n * groups;
   const int max_clusters = pair_sm_count() / 2;
   // Split-K exactly as in the one-CTA kernel: only into an fp32 accumulator, when the tiles leave most SMs idle.
-  if (!grouped_k && (kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr && a.row_scale == nullptr) {
+  if (!grouped_k && !grouped_m && (kp.flags & GF_OUT_F32) && (kp.flags & GF_ACCUMULATE) && a.bias == nullptr && a.row_scale == nullptr) {
     const int total_iters = (a.K + BK - 1) / BK;
     if (pair_tiles * 2 <= max_clusters && total_iters >= 16) {
       int splits = max_clusters / pair_tiles;
@@ -404,6 +417,8 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.total_tiles = pair_tiles;
 
   CUtensorMap tmA, tmB;
+  const uint64_t nbB = grouped_m ? (uint64_t)(a.batch < 1 ? 1 : a.batch) : 1;  // grouped-M: one B matrix per group
+  const uint64_t sB = (grouped_m ? (uint64_t)a.strideB : (uint64_t)a.ldb) * 2ull;
   if (a.a_mn_major)
     tmA = make_tmap_3d(a.A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.M, (uint64_t)a.K, 1, (uint64_t)a.lda * 2ull,
                        (uint64_t)a.lda * 2ull, 64, BK);
@@ -411,11 +426,11 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
     tmA = make_tmap_3d(a.A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.M, 1, (uint64_t)a.lda * 2ull,
                        (uint64_t)a.lda * 2ull, BK, BM);
   if (a.b_mn_major)
-    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.K, 1, (uint64_t)a.ldb * 2ull,
-                       (uint64_t)a.ldb * 2ull, 64, BK);
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.K, nbB, (uint64_t)a.ldb * 2ull,
+                       sB, 64, BK);
   else
-    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, 1, (uint64_t)a.ldb * 2ull,
-                       (uint64_t)a.ldb * 2ull, BK, 64);
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull,
+                       sB, BK, 64);
   const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
   const int c_elem = c_f32 ? 4 : 2;
   const uint64_t c_bstride = (groups > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;

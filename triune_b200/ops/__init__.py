@@ -22,7 +22,7 @@ from .. import _ext
 from . import reference as ref
 
 GEMM_DENSE, GEMM_GROUPED_M, GEMM_GROUPED_K = 0, 1, 2
-GF_OUT_F32, GF_ACCUMULATE, GF_GELU, GF_DGELU = 1, 2, 4, 8
+GF_OUT_F32, GF_ACCUMULATE, GF_GELU, GF_DGELU, GF_PAIRED_GROUPS = 1, 2, 4, 8, 16
 
 # kernel launch accounting (used by bench.py's ``gpu_launches``)
 _LAUNCHES = {"count": 0}
@@ -73,6 +73,7 @@ def gemm(
     tile_group: Optional[torch.Tensor] = None,
     group_offsets: Optional[torch.Tensor] = None,
     num_groups: int = 0,
+    paired_groups: bool = False,
 ) -> torch.Tensor:
     """out = alpha * A @ B^T with a fused epilogue, on tcgen05 tensor cores.
 
@@ -81,6 +82,8 @@ def gemm(
     (``group_offsets``; then ``a`` [R, M], ``b`` [R, N] and out is [G, M, N]).
     ``gelu`` applies tanh-GELU after the bias; ``aux_out`` (bf16, out's layout) then receives GELU'(pre-activation),
     which a later call takes as ``dgelu_aux`` to form ``out = alpha * (A @ B^T) * dgelu_aux`` in its epilogue.
+    ``paired_groups`` (rows grouped by expert only) promises that every expert's rows are padded to a multiple of 256,
+    which lets long reductions run on CTA pairs.
     """
     assert _tma_ok(a) and _tma_ok(b), "gemm operands must be CUDA bf16 with 16-byte aligned rows"
     if mode == GEMM_GROUPED_K:
@@ -94,6 +97,8 @@ def gemm(
     if out is None:
         out = torch.empty(shape, device=a.device, dtype=out_dtype)
     flags = (GF_ACCUMULATE if accumulate else 0) | (GF_GELU if gelu else 0) | (GF_DGELU if dgelu_aux is not None else 0)
+    if paired_groups and mode == GEMM_GROUPED_M:
+        flags |= GF_PAIRED_GROUPS
     _ext.ext().tc_gemm(
         a, b, out, a_mn, b_mn, mode, flags, float(alpha), bias, dgelu_aux, aux_out, row_scale, tile_group,
         group_offsets, None,
@@ -503,6 +508,13 @@ def route_plan_supported(logits, top_k: int) -> bool:
             and 1 <= top_k <= 4 and top_k <= logits.shape[1])
 
 
+class RoutePlan(tuple):
+    """The dispatch plan of :func:`moe_route_plan`: the 5-tuple of :func:`moe_plan` whose expert row ranges are padded
+    to multiples of 256 (``row_pad``), i.e. to whole pairs of 128-row tiles."""
+
+    row_pad = 256
+
+
 def moe_route_plan(logits, expert_bias, top_k: int, temperature=1.0, capacity: Optional[int] = None):
     """Routing + capacity admission + dispatch plan with ONE sort and three kernels, no host synchronisation.
 
@@ -515,7 +527,7 @@ def moe_route_plan(logits, expert_bias, top_k: int, temperature=1.0, capacity: O
     cap = int(capacity) if capacity is not None and capacity < N else N
     pos, keep, row_src, tile_group, offsets, accepted = _ext.ext().moe_plan_sorted(skeys, order, counts, N, top_k, cap)
     _tick(3)
-    return idx, w, keep, (pos, row_src, tile_group, offsets, accepted)
+    return idx, w, keep, RoutePlan((pos, row_src, tile_group, offsets, accepted))
 
 
 def moe_plan(idx: torch.Tensor, keep: Optional[torch.Tensor], num_experts: int, tile: int = 128):
@@ -617,8 +629,9 @@ class _ExpertMLPFn(torch.autograd.Function):
     """Grouped expert FFN on the expert-major buffer: gelu(xp W1[e]^T + b1[e]) W2[e]^T + b2[e]."""
 
     @staticmethod
-    def forward(ctx, xp, w1, b1, w2, b2, tile_group, group_offsets):
+    def forward(ctx, xp, w1, b1, w2, b2, tile_group, group_offsets, paired=False):
         R = xp.shape[0]
+        ctx.paired = bool(paired) and R % 256 == 0
         Hd = w1.shape[1]
         # Row tiles past the last expert are never written and never read: the combine / gather kernels
         # follow `pos`, and the grouped weight-gradient GEMMs stay inside group_offsets.
@@ -626,7 +639,7 @@ class _ExpertMLPFn(torch.autograd.Function):
         h = torch.empty(R, Hd, device=xp.device, dtype=xp.dtype)
         yp = torch.empty(R, w2.shape[1], device=xp.device, dtype=xp.dtype)
         gemm(xp, w1, h, bias=b1, gelu=True, aux_out=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
-        gemm(h, w2, yp, bias=b2, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(h, w2, yp, bias=b2, mode=GEMM_GROUPED_M, tile_group=tile_group, paired_groups=ctx.paired)
         ctx.save_for_backward(xp, w1, b1, w2, b2, dact, h, tile_group, group_offsets)
         return yp
 
@@ -639,7 +652,7 @@ class _ExpertMLPFn(torch.autograd.Function):
         dpre = torch.empty(R, w1.shape[1], device=xp.device, dtype=xp.dtype)
         gemm(dyp, w2, dpre, b_mn=True, dgelu_aux=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         dxp = torch.empty_like(xp)
-        gemm(dpre, w1, dxp, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        gemm(dpre, w1, dxp, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group, paired_groups=ctx.paired)
         ones = torch.ones(R, 8, device=xp.device, dtype=xp.dtype)
 
         def wgrad(w, a, b):
@@ -663,7 +676,7 @@ class _ExpertMLPFn(torch.autograd.Function):
         db2 = bgrad(b2, dyp)
         dw1 = wgrad(w1, dpre, xp)
         db1 = bgrad(b1, dpre)
-        return dxp, dw1, db1, dw2, db2, None, None
+        return dxp, dw1, db1, dw2, db2, None, None, None
 
 
 def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_scale: float = 0.0, plan=None):
@@ -673,7 +686,7 @@ def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_
     if _ext.use_kernels(x2, w1, w2) and x2.dtype == torch.bfloat16:
         pos, row_src, tile_group, group_offsets, _ = plan if plan is not None else moe_plan(idx, keep, E)
         xp = _GatherRowsFn.apply(x2.contiguous(), row_src, pos)
-        yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets)
+        yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets, getattr(plan, "row_pad", 128) == 256)
         wk = weights.float().contiguous()
         return _CombineRowsFn.apply(yp, pos, wk, row_src, shared_out, float(shared_scale))
     # reference path: loop over experts
