@@ -183,6 +183,37 @@ def test_gemm_cta_pairs_grouped_rows(dev):
     assert _rel(out2, ref_out - torch.where((tiles >= 0).repeat_interleave(128)[:, None], bias[tiles.clamp_min(0).long()].float().repeat_interleave(128, 0), torch.zeros(1, device=dev))) < 1e-2
 
 
+@pytest.mark.parametrize("D,T,beta_kind", [(64, 200, "none"), (64, 77, "head"), (128, 130, "row"), (128, 1, "head")])
+def test_gated_deltanet_recurrent_kernel(dev, D, T, beta_kind):
+    """The one-kernel Gated DeltaNet recurrence against the fp64 token loop (prefill, ragged lengths, decode)."""
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(31)
+    B, H = 2, 3
+    q = (torch.randn(B, T, H, D, device=dev) * 0.3).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device=dev), dim=-1).to(torch.bfloat16)
+    v = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16)
+    g = (-torch.rand(B, T, H, D, device=dev) * 0.3).to(torch.bfloat16)
+    beta = {"none": None, "head": torch.rand(B, T, H, device=dev), "row": torch.rand(B, T, H, D, device=dev)}[beta_kind]
+    s0 = torch.randn(B, H, D, D, device=dev) * 0.1
+    with torch.no_grad():
+        out, fin = ops.gated_deltanet(q, k, v, g, beta=beta, initial_state=s0, scale=0.5)
+        oref, fref = ref.gated_deltanet_recurrent(q.double(), k.double(), v.double(), g.double(),
+                                                  None if beta is None else beta.double(), s0.double(), 0.5)
+    assert out.dtype == torch.bfloat16 and fin.dtype == torch.float32
+    assert _rel(out, oref) < 2e-2
+    assert _rel(fin, fref) < 1e-3
+    # gate logits: log-sigmoid inside the kernel
+    x = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16)
+    with torch.no_grad():
+        o2, f2 = ops.gated_deltanet(q, k, v, x, beta=beta, initial_state=s0, gate_logits=True)
+        gl = torch.nn.functional.logsigmoid(x.double())
+        o2r, f2r = ref.gated_deltanet_recurrent(q.double(), k.double(), v.double(), gl,
+                                                None if beta is None else beta.double(), s0.double(), 1.0)
+    assert _rel(o2, o2r) < 2e-2 and _rel(f2, f2r) < 1e-3
+
+
 def test_gemm_epilogues(dev):
     from triune_b200 import ops
 

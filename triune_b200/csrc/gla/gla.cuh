@@ -44,5 +44,10 @@ void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaM
 // One decode step for B*H heads: state [BH,64,64] fp32 in place; q,k,v,g rows of 64 bf16; out bf16.
 void launch_gla_decode_step(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, float* state, GlaMat O, int B, int H,
                             bool gate_logits, cudaStream_t s);
+// Gated DeltaNet token recurrence over T tokens (T = 1: one decode step) for B*H heads of dimension D (64 or 128):
+// state [BH,D,D] fp32 in place; beta: null (1), fp32 [B*T,H] (beta_mode 1) or fp32 [B*T,H*D] (beta_mode 2).
+void launch_gdn_recurrent(const GlaMat& Q, const GlaMat& K, const GlaMat& V, const GlaMat& G, const float* beta,
+                          int beta_mode, float* state, const GlaMat& O, int B, int T, int H, int D, bool gate_logits,
+                          float scale, cudaStream_t s);
 
 }  // namespace tb

@@ -82,10 +82,31 @@ void gla_decode(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, co
   tb::launch_gla_decode_step(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), state.data_ptr<float>(), mat(out, ocol),
                              (int)B, (int)H, gate_logits, cur_stream());
 }
+
+// Gated DeltaNet recurrence (no gradient): q,k,v,g as [B*T, ld] matrices whose columns col0 + h*D.. hold head h.
+void gdn_recurrent(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol,
+                   const Tensor& g, int64_t gcol, const c10::optional<Tensor>& beta, Tensor& state, Tensor& out,
+                   int64_t ocol, int64_t B, int64_t T, int64_t H, int64_t D, bool gate_logits, double scale) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.is_contiguous() && state.numel() == B * H * D * D,
+              "state must be fp32 contiguous [B,H,D,D]");
+  const float* bp = nullptr;
+  int mode = 0;
+  if (beta.has_value() && beta->defined()) {
+    TORCH_CHECK(beta->scalar_type() == at::kFloat && beta->is_contiguous(), "beta must be fp32 contiguous");
+    if (beta->numel() == B * T * H) mode = 1;
+    else if (beta->numel() == B * T * H * D) mode = 2;
+    else TORCH_CHECK(false, "beta must be [B,T,H] or [B,T,H,D]");
+    bp = beta->data_ptr<float>();
+  }
+  tb::launch_gdn_recurrent(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), bp, mode, state.data_ptr<float>(),
+                           mat(out, ocol), (int)B, (int)T, (int)H, (int)D, gate_logits, (float)scale, cur_stream());
+}
 }  // namespace
 
 void register_gla(pybind11::module& m) {
   m.def("gla_fwd", &gla_fwd);
   m.def("gla_bwd", &gla_bwd);
   m.def("gla_decode", &gla_decode);
+  m.def("gdn_recurrent", &gdn_recurrent);
 }

@@ -381,6 +381,14 @@ def gla_recurrent(q, k, v, g, initial_state=None, scale: float = 1.0):
 
 def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0, gate_logits: bool = False,
                    chunk_size: int = 64):
+    """Gated DeltaNet over [B,T,H,D] tensors; returns (out, final_state [B,H,Dk,Dv]).
+
+    Without gradients (prefill, decode) CUDA bf16 inputs run the exact token recurrence in one kernel; with gradients
+    the differentiable chunked UT-transform form of :mod:`triune_b200.ops.reference` is used."""
+    from . import gla_cuda
+
+    if gla_cuda.gdn_supported(q, k, v, g, beta):
+        return gla_cuda.gdn_recurrent(q, k, v, g, beta, initial_state, scale, gate_logits)
     gl = F.logsigmoid(g.float()) if gate_logits else g
     if q.shape[1] == 1 and initial_state is not None and not torch.is_grad_enabled():
         o, s = ref.gated_deltanet_decode_step(

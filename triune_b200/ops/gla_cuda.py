@@ -149,6 +149,40 @@ def decode_step(q, k, v, g, state, gate_logits):
     return out.view(B, 1, H, D), st
 
 
+def gdn_supported(q, k, v, g, beta) -> bool:
+    """True when the recurrent Gated DeltaNet kernel covers this call: bf16, head dim 64 or 128 (keys = values), no
+    gradient wanted."""
+    if not _ext.use_kernels(q, k, v, g) or q.dtype != torch.bfloat16:
+        return False
+    D = q.shape[-1]
+    if D not in (64, 128) or v.shape[-1] != D:
+        return False
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta)):
+        return False
+    return True
+
+
+@torch.no_grad()
+def gdn_recurrent(q, k, v, g, beta, initial_state, scale, gate_logits):
+    """Exact Gated DeltaNet recurrence in one kernel per call (prefill of any length, or one decode step).
+
+    q,k,v,g [B,T,H,D]; beta None, [B,T,H] or [B,T,H,D]; returns (out [B,T,H,D] bf16, state [B,H,D,D] fp32).
+    Reference: the token loop of ``triune/kernels/fast_gla.py:781-836``.
+    """
+    B, T, H, D = q.shape
+    e = _ext.ext()
+    if initial_state is None:
+        st = torch.zeros(B, H, D, D, device=q.device, dtype=torch.float32)
+    else:
+        st = initial_state.float().contiguous().clone()
+    qm, km, vm, gm = (_as_matrix(t.to(torch.bfloat16)) for t in (q, k, v, g))
+    out = torch.empty(B * T, H * D, device=q.device, dtype=torch.bfloat16)
+    bt = None if beta is None else beta.float().contiguous()
+    e.gdn_recurrent(qm, 0, km, 0, vm, 0, gm, 0, bt, st, out, 0, B, T, H, D, gate_logits, float(scale))
+    _tick(1)
+    return out.view(B, T, H, D), st
+
+
 class _GLACoreFn(torch.autograd.Function):
     """qkvg [B*T, 4*H*64] -> attention output [B*T, H*64] (feature map, RoPE and the chunk scan fused)."""
 
