@@ -63,6 +63,13 @@ def main():
     dist.all_gather(allv, mine)
     out["ranks_agree"] = bool(all(float(v) == float(allv[0]) for v in allv))
     out["loss_ref"], out["loss_fused"] = l_ref, l_f
+    # the routing statistics behind the update rule (selection biases, centroids) are averaged over the ranks
+    stats = [getattr(m, n).detach().double().sum().reshape(1) for m in m_f.modules() if hasattr(m, "expert_bias")
+             for n in ("expert_bias", "last_centroids") if torch.is_tensor(getattr(m, n, None))]
+    sm = torch.cat(stats).sum().reshape(1) if stats else torch.zeros(1, device=ctx.device, dtype=torch.double)
+    alls = [torch.zeros_like(sm) for _ in range(ctx.world_size)]
+    dist.all_gather(alls, sm)
+    out["stats_agree"] = bool(all(abs(float(v) - float(alls[0])) <= 1e-9 * max(1.0, abs(float(alls[0]))) for v in alls))
     # metric all-reduce piggy-backed on the signal protocol
     buf = dp_f._fused.buf
     e = _ext.ext()

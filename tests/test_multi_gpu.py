@@ -38,6 +38,7 @@ def test_fused_dp_matches_nccl_baseline(multimem):
     for r in res:
         assert r["status"] == 0
         assert r["ranks_agree"]
+        assert r["stats_agree"], r
         assert r["max_param_diff"] <= 2e-2 * max(1.0, r["param_scale"])
         assert r["metric_ok"]
         assert r["timeout_status"] == 4 and r["context_alive"]

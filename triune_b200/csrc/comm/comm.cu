@@ -252,9 +252,11 @@ __global__ void __launch_bounds__(32) comm_wait_only_kernel(PeerTable pt, int ch
   (void)cta_wait_all(pt, channel, epoch, status, limit_ns);
 }
 
-__global__ void __launch_bounds__(64) metric_allreduce_kernel(PeerTable pt, long long metric_off,
-                                                              const float* __restrict__ local, float* __restrict__ out,
-                                                              int n, int channel, uint32_t epoch, int* status) {
+__global__ void __launch_bounds__(256) metric_allreduce_kernel(PeerTable pt, long long metric_off,
+                                                               const float* __restrict__ local, float* __restrict__ out,
+                                                               int n, int channel, uint32_t epoch,
+                                                               const uint32_t* __restrict__ epoch_dev, int* status) {
+  if (epoch_dev) epoch = *epoch_dev;  // device-resident epoch: the launch can be replayed from a CUDA graph
   // slot layout in each rank's buffer: [world][n]
   for (int i = threadIdx.x; i < n * pt.world; i += blockDim.x) {
     const int peer = i / n, j = i % n;
@@ -320,8 +322,8 @@ void launch_comm_wait_only(PeerTable pt, int channel, uint32_t epoch, unsigned l
 }
 
 void launch_metric_allreduce(PeerTable pt, long long metric_off, const float* local, float* out, int n, int channel,
-                             uint32_t epoch, int* status, cudaStream_t s) {
-  metric_allreduce_kernel<<<1, 64, 0, s>>>(pt, metric_off, local, out, n, channel, epoch, status);
+                             uint32_t epoch, const uint32_t* epoch_dev, int* status, cudaStream_t s) {
+  metric_allreduce_kernel<<<1, 256, 0, s>>>(pt, metric_off, local, out, n, channel, epoch, epoch_dev, status);
   check("metric_allreduce");
 }
 

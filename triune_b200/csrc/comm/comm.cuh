@@ -69,7 +69,7 @@ void launch_comm_barrier(PeerTable pt, int channel, uint32_t epoch, const uint32
 // Scalar metrics all-reduce (sum) piggy-backed on the signal protocol: each rank stores its `n` floats into slot
 // [rank] of every peer's metric array, barriers, and sums. out[n] on every rank.
 void launch_metric_allreduce(PeerTable pt, long long metric_off, const float* local, float* out, int n, int channel,
-                             uint32_t epoch, int* status, cudaStream_t s);
+                             uint32_t epoch, const uint32_t* epoch_dev, int* status, cudaStream_t s);
 
 // A wait that is expected to expire (used by failure-detection tests): waits on a channel nobody raises with a
 // short limit and reports ST_TIMEOUT_PEER through status; the context stays usable.

@@ -85,9 +85,14 @@ void comm_wait_only(int64_t rank, int64_t world, int64_t bufs, int64_t sigs, int
 }
 
 void metric_allreduce(int64_t rank, int64_t world, int64_t bufs, int64_t sigs, int64_t metric_off, const Tensor& local,
-                      Tensor& out, int64_t channel, int64_t epoch, const c10::optional<Tensor>& status) {
+                      Tensor& out, int64_t channel, int64_t epoch, const c10::optional<Tensor>& status,
+                      const c10::optional<Tensor>& epoch_dev) {
+  TORCH_CHECK(local.scalar_type() == at::kFloat && local.is_contiguous() && out.scalar_type() == at::kFloat &&
+                  out.is_contiguous() && out.numel() >= local.numel(),
+              "metric_allreduce: fp32 contiguous vectors");
+  const uint32_t* ed = epoch_ptr(epoch_dev);
   tb::launch_metric_allreduce(table(rank, world, bufs, sigs, 0), metric_off, local.data_ptr<float>(), out.data_ptr<float>(),
-                              (int)local.numel(), (int)channel, (uint32_t)epoch, status_ptr(status), cur_stream());
+                              (int)local.numel(), (int)channel, (uint32_t)epoch, ed, status_ptr(status), cur_stream());
 }
 
 // ---------------------------------------------------------------- GEMMs fused with collectives
@@ -212,5 +217,7 @@ void register_comm(pybind11::module& m) {
   m.def("ep_dispatch", &ep_dispatch, "token rows -> expert-major buffers on the expert owners (peer stores)");
   m.def("ep_zero_invalid_rows", &ep_zero_invalid_rows, "zero the rows of an expert-major buffer beyond each segment's count");
   m.def("ep_build_tiles", &ep_build_tiles, "tile list and row validity of the expert owner from the received counts");
-  m.def("metric_allreduce", &metric_allreduce);
+  m.def("metric_allreduce", &metric_allreduce, py::arg("rank"), py::arg("world"), py::arg("bufs"), py::arg("sigs"),
+        py::arg("metric_off"), py::arg("local"), py::arg("out"), py::arg("channel"), py::arg("epoch"),
+        py::arg("status") = py::none(), py::arg("epoch_dev") = py::none());
 }

@@ -29,6 +29,8 @@ from .. import _ext, ops
 from .symm import SymmetricBuffer
 
 CH_PARAMS_DONE = 2
+CH_STATS = 7
+STATS_MAX = 1 << 16  # floats of routing statistics the symmetric buffer has room for, per rank
 
 
 class SymmetricArenaStorage:
@@ -45,7 +47,8 @@ class SymmetricArenaStorage:
         w = self.ctx.world_size
         self.total = total
         self.buffer = SymmetricBuffer(
-            {"param": total * 2, "grad": total * 4, "norm": 2 * w * 4 + 64, "metric": 16 * w * 4},
+            {"param": total * 2, "grad": total * 4, "norm": 2 * w * 4 + 64, "metric": 16 * w * 4,
+             "stats": STATS_MAX * w * 4},
             device, use_multimem=self.use_multimem)
         return self.buffer.view("param", torch.bfloat16, total), self.buffer.view("grad", torch.float32, total)
 
@@ -82,6 +85,36 @@ class FusedDPUpdater:
     def comm_bytes(self) -> int:
         return self.bytes_per_step * self.opt.step_count
 
+    def _sync_routing_statistics(self, e, rank, world, bufs, sigs) -> None:
+        """Average the routing statistics that feed the update rule (expert centroids of the steering tier, pending
+        selection-bias updates, load ratios) over the ranks with one small peer-store all-reduce, so every replica
+        applies the step of the global batch. Same tensors as ``ShardedDataParallel._sync_routing_statistics``."""
+        model = getattr(self.opt, "model", None)
+        if model is None:
+            return
+        tensors = []
+        for m in model.modules():
+            if not hasattr(m, "expert_bias"):
+                continue
+            for name in ("last_centroids", "expert_load_ratio", "_pending_bias_update"):
+                t = getattr(m, name, None)
+                if torch.is_tensor(t) and t.is_floating_point() and t.is_cuda:
+                    tensors.append(t)
+        n = sum(t.numel() for t in tensors)
+        if n == 0 or n > STATS_MAX:
+            return
+        flat = torch.cat([t.detach().float().reshape(-1) for t in tensors])
+        red = torch.empty_like(flat)
+        e.metric_allreduce(rank, world, bufs, sigs, self.buf.offset("stats"), flat, red, CH_STATS, 0, self.status,
+                           self.epoch_dev)
+        ops._tick()
+        red.mul_(1.0 / world)
+        off = 0
+        for t in tensors:
+            k = t.numel()
+            t.copy_(red[off : off + k].view(t.shape).to(t.dtype))
+            off += k
+
     def step(self):
         opt, buf = self.opt, self.buf
         a = opt.arena
@@ -89,6 +122,8 @@ class FusedDPUpdater:
         rank, world, bufs, sigs, mc = buf.table()
         ep = 0
         self.epoch_dev.add_(1)
+        if world > 1:
+            self._sync_routing_statistics(e, rank, world, bufs, sigs)
         hyper = opt.hyper if getattr(opt, "capturable", False) else None
         opt.step_count += 1
         goff, noff, poff = buf.offset("grad"), buf.offset("norm"), buf.offset("param")
