@@ -230,3 +230,26 @@ def test_gloo_data_parallel_matches_single_process_large_batch(tmp_path):
     assert abs(dp_mean[0] - single[0]) < 2e-3                      # same weights, same data: same first loss
     assert dp_mean[-1] < dp_mean[0] and abs(dp_mean[-1] - single[-1]) < 0.15  # same trajectory up to routing / capacity effects
     assert abs(res[0]["avg"] - dp_mean[-1]) < 1e-5
+
+
+def test_layer_store_keeps_every_tensor_on_a_vector_boundary():
+    """The flat per-layer buffers pad every tensor to 64 elements, so a tensor packed behind an odd-sized one (a
+    3-element bias) still starts on a 16-byte boundary; the kernels read parameters in 16-byte vectors."""
+    import torch.nn as nn
+
+    from triune_b200.runtime.streaming import LayerStore
+
+    layer = nn.Sequential(nn.Linear(16, 3), nn.Linear(3, 24), nn.LayerNorm(24)).to(torch.bfloat16)
+    before = [p.detach().clone() for p in layer.parameters()]
+    st = LayerStore(layer, pin=False)
+    assert [off % 64 for off, _, _ in st.slices] == [0] * len(st.slices)
+    assert st.numel % 64 == 0 and st.host.numel() == st.numel and st.host_grad.numel() == st.numel
+    for p, q in zip(layer.parameters(), before):
+        assert torch.equal(p.detach(), q)
+        assert (p.data_ptr() - st.host.data_ptr()) % 16 == 0
+    dev = torch.zeros(st.numel, dtype=torch.bfloat16)
+    dev.copy_(st.host)
+    st.bind(dev)
+    for p, q in zip(layer.parameters(), before):
+        assert torch.equal(p.detach(), q) and (p.data_ptr() - dev.data_ptr()) % 16 == 0
+    st.bind_host()

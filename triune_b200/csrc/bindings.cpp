@@ -23,6 +23,8 @@ inline const __nv_bfloat16* bf_opt(const c10::optional<Tensor>& t) {
 void check_bf16_cuda(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  // every kernel reads and writes bf16 data in 16-byte vectors: a misaligned base would fault on the device
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, " must start on a 16-byte boundary");
 }
 
 // C[b] = alpha * op(A[b]) * op(B[b])^T with the fused epilogue. a: [batch?, M, K] (or [batch?, K, M] when
@@ -114,6 +116,8 @@ void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool 
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& res, const Tensor& w, double eps) {
   check_bf16_cuda(x, "x");
   TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous inputs required");
+  check_bf16_cuda(w, "w");
+  if (res.has_value() && res->defined()) check_bf16_cuda(*res, "residual");
   const int d = (int)x.size(-1);
   TORCH_CHECK(d % 8 == 0 && d <= 2048, "rmsnorm kernel supports d % 8 == 0, d <= 2048");
   c10::cuda::CUDAGuard guard(x.device());
@@ -134,6 +138,7 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& re
 std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd,
                                 const c10::optional<Tensor>& dres) {
   check_bf16_cuda(x, "x");
+  check_bf16_cuda(w, "w");
   const int d = (int)x.size(-1);
   const int rows = (int)(x.numel() / d);
   c10::cuda::CUDAGuard guard(x.device());

@@ -39,15 +39,24 @@ class StreamingConfig:
     forward_snapshots: bool = True
 
 
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
 class LayerStore:
     """Flat host storage of one layer: parameters (model dtype), fp32 gradient, and views for each tensor."""
+
+    ALIGN = 64  # elements
 
     def __init__(self, layer: nn.Module, pin: bool):
         self.layer = layer
         self.params = [p for p in layer.parameters()]
-        self.numel = sum(p.numel() for p in self.params)
+        # Every tensor starts on a 128-byte boundary of the flat buffers (ALIGN elements covers 2- and 4-byte types):
+        # the kernels read parameters in 16-byte vectors, and a tensor packed right behind a 3-element bias would
+        # otherwise start on an odd address.
+        self.numel = sum(_round_up(p.numel(), self.ALIGN) for p in self.params)
         dtype = self.params[0].dtype if self.params else torch.float32
-        self.host = torch.empty(self.numel, dtype=dtype)
+        self.host = torch.zeros(self.numel, dtype=dtype)
         self.host_grad = torch.zeros(self.numel, dtype=torch.float32)
         if pin:
             self.host, self.host_grad = self.host.pin_memory(), self.host_grad.pin_memory()
@@ -58,7 +67,7 @@ class LayerStore:
             self.host[off : off + n].copy_(p.data.reshape(-1))
             p.data = self.host[off : off + n].view(p.shape)  # the host copy is the master
             self.slices.append((off, n, p.shape))
-            off += n
+            off += _round_up(n, self.ALIGN)
         self.device_buf: Optional[torch.Tensor] = None
         self.ready: Optional[torch.cuda.Event] = None
         self.grad_sumsq = None
