@@ -69,12 +69,22 @@ class EPContext:
 
 def _positions(idx_flat: torch.Tensor, num_experts: int):
     """Position of every assignment among this rank's assignments to the same expert (in assignment order), and the
-    per-expert counts. No host synchronisation."""
-    onehot = idx_flat.view(-1, 1) == torch.arange(num_experts, device=idx_flat.device, dtype=idx_flat.dtype).view(1, -1)
-    csum = onehot.to(torch.int32).cumsum(0, dtype=torch.int32)
-    pos = (csum.gather(1, idx_flat.clamp_min(0).long().view(-1, 1)).view(-1) - 1).to(torch.int32)
-    pos = torch.where(idx_flat >= 0, pos, torch.full_like(pos, -1))
-    return pos.contiguous(), csum[-1].contiguous()
+    per-expert counts. No host synchronisation.
+
+    One stable sort by expert groups the assignments without disturbing their order inside a group; the position is
+    then the distance to the start of the group. (A one-hot cumulative sum over [assignments, experts] computes the
+    same thing but costs milliseconds per layer at 64 experts.)"""
+    E = num_experts
+    A = idx_flat.numel()
+    dev = idx_flat.device
+    key = torch.where(idx_flat >= 0, idx_flat, torch.full_like(idx_flat, E)).long()  # dropped assignments sort last
+    e_sorted, order = torch.sort(key, stable=True)
+    counts_all = torch.zeros(E + 1, device=dev, dtype=torch.int64).scatter_add_(0, key, torch.ones_like(key))
+    starts = torch.cumsum(counts_all, 0) - counts_all
+    rank_sorted = torch.arange(A, device=dev) - starts[e_sorted]
+    pos = torch.empty(A, device=dev, dtype=torch.int64)
+    pos[order] = torch.where(e_sorted < E, rank_sorted, torch.full_like(rank_sorted, -1))
+    return pos.to(torch.int32).contiguous(), counts_all[:E].to(torch.int32).contiguous()
 
 
 class _EPExpertsFn(torch.autograd.Function):
