@@ -214,6 +214,26 @@ def test_gated_deltanet_recurrent_kernel(dev, D, T, beta_kind):
     assert _rel(o2, o2r) < 2e-2 and _rel(f2, f2r) < 1e-3
 
 
+def test_subspace_tier_products_on_tensor_cores(dev):
+    """S = Q_L^T G Q_R and dW = Q_L delta Q_R^T with bf16 operands on the tcgen05 GEMM against the fp32 products, and
+    one optimizer step with the path on and off."""
+    from triune_b200.optim.centroid import CentroidSteerOptimizer as Opt
+
+    torch.manual_seed(41)
+    K, m, n, r1 = 3, 512, 384, 33
+    G = torch.randn(K, m, n, device=dev) * 0.02
+    QL = torch.linalg.qr(torch.randn(K, m, r1, device=dev))[0]
+    QR = torch.linalg.qr(torch.randn(K, n, r1, device=dev))[0]
+    QL16, QR16 = Opt._padded_bf16(QL), Opt._padded_bf16(QR)
+    assert QL16.shape[-1] == 40 and float(QL16[:, :, r1:].abs().max()) == 0.0
+    S = Opt._project_tc(G, QL16, QR16, r1)
+    S_ref = QL.transpose(1, 2) @ (G @ QR)
+    assert S.shape == S_ref.shape and _rel(S, S_ref) < 2e-2
+    delta = torch.randn(K, r1, r1, device=dev)
+    dW = Opt._reconstruct_tc(delta, QL16, QR16)
+    assert _rel(dW, QL @ delta @ QR.transpose(1, 2)) < 2e-2
+
+
 def test_gemm_epilogues(dev):
     from triune_b200 import ops
 

@@ -147,7 +147,8 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                  use_triangular_core=True, core_mask_mode: str = "full", param_roles=None, eps: float = 1e-8,
                  grad_clip: Optional[float] = None, nesterov: bool = True, aspect_safeguard: bool = True,
                  adaptive_subspace_refresh: bool = False, energy_threshold: float = 0.5, min_subspace_gap: int = 5,
-                 max_subspace_gap: int = 50, storage_factory=None, shard: Tuple[int, int] = (0, 1)):
+                 max_subspace_gap: int = 50, storage_factory=None, shard: Tuple[int, int] = (0, 1),
+                 tensor_core_subspace: bool = True):
         if core_mask_mode not in ("full", "triu"):
             raise ValueError(f"Unknown core_mask_mode={core_mask_mode!r}; expected 'full' or 'triu'")
         self._in_set_lr = False
@@ -187,6 +188,8 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         lo, hi = a.muon_range
         self.muon_mom = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
         self.steer_state: Dict[str, Dict] = {}
+        self.tensor_core_subspace = bool(tensor_core_subspace)
+        self._q16: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}  # bf16 copies of the bases (derived, not saved)
         self.capturable = False  # device-resident hyper-parameters (CUDA-graph replay)
         self.hyper = torch.zeros(8, device=dev, dtype=torch.float32)
         self._hyper_host = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
@@ -499,7 +502,17 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                     st["steer_applied"].zero_()
                 st["last_steer_step"] = self.step_count
             QL, QR = st["Q_L"], st["Q_R"]
-            S = QL.transpose(1, 2) @ (G @ QR)
+            tc = self._tensor_core_products(m, n)
+            if tc:
+                if seg.name not in self._q16:
+                    self._q16[seg.name] = (self._padded_bf16(QL), self._padded_bf16(QR))
+                elif refresh or need_steer:  # in place: a captured step keeps reading the same buffers
+                    self._q16[seg.name][0][:, :, : r + 1].copy_(QL)
+                    self._q16[seg.name][1][:, :, : r + 1].copy_(QR)
+                QL16, QR16 = self._q16[seg.name]
+                S = self._project_tc(G, QL16, QR16, r + 1)
+            else:
+                S = QL.transpose(1, 2) @ (G @ QR)
             if self.adaptive_subspace_refresh:
                 st["last_energy_ratio"] = S[:, :r, :r].pow(2).sum((-2, -1)) / G.pow(2).sum((-2, -1)).clamp_min(1e-12)
             st["step"] += 1
@@ -516,8 +529,45 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                 delta[:, :, r] = delta[:, :, r] * mult
                 if not triu:
                     delta[:, r, :r] = delta[:, r, :r] * mult
-            dW = QL @ delta @ QR.transpose(1, 2)
+            dW = self._reconstruct_tc(delta, QL16, QR16) if tc else QL @ delta @ QR.transpose(1, 2)
             self._apply_steer_delta(seg, dW, k0, k1)
+
+    # ------------------------------------------------------------------ subspace products on the tensor cores
+    # The two per-step products of the subspace tier, S = Q_L^T G Q_R and dW = Q_L delta Q_R^T, are skinny batched
+    # GEMMs (rank + 1 = 257 columns against thousands of rows). As fp32 library products they were a fifth of the
+    # step of the default preset; with bf16 operands and fp32 accumulation they run on the tcgen05 GEMM. The bases are
+    # kept as bf16 copies padded to a multiple of 8 columns (zero columns add nothing); they change only when the
+    # subspace is refreshed or the steering column is rewritten.
+    def _tensor_core_products(self, m: int, n: int) -> bool:
+        return bool(self._use_kernels() and self.tensor_core_subspace and m % 8 == 0 and n % 8 == 0 and m >= 128 and n >= 128)
+
+    @staticmethod
+    def _padded_bf16(Q: torch.Tensor) -> torch.Tensor:
+        K, d, r1 = Q.shape
+        r1p = (r1 + 7) // 8 * 8
+        out = torch.zeros(K, d, r1p, device=Q.device, dtype=torch.bfloat16)
+        out[:, :, :r1] = Q
+        return out
+
+    @staticmethod
+    def _project_tc(G: torch.Tensor, QL16: torch.Tensor, QR16: torch.Tensor, r1: int) -> torch.Tensor:
+        from .. import ops
+
+        G16 = G.to(torch.bfloat16)
+        GQ = ops.gemm(G16, QR16, b_mn=True)                                       # [K, m, r1p] = G Q_R
+        S = ops.gemm(QL16, GQ, a_mn=True, b_mn=True, out_dtype=torch.float32)     # [K, r1p, r1p] = Q_L^T (G Q_R)
+        return S[:, :r1, :r1].contiguous()
+
+    @staticmethod
+    def _reconstruct_tc(delta: torch.Tensor, QL16: torch.Tensor, QR16: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+
+        K, r1, _ = delta.shape
+        r1p = QL16.shape[-1]
+        d16 = torch.zeros(K, r1p, r1p, device=delta.device, dtype=torch.bfloat16)
+        d16[:, :r1, :r1] = delta
+        T = ops.gemm(QL16, d16, b_mn=True)                                        # [K, m, r1p] = Q_L delta
+        return ops.gemm(T, QR16, out_dtype=torch.float32)                          # [K, m, n] = (Q_L delta) Q_R^T
 
     def _apply_steer_delta(self, seg: Segment, dW: torch.Tensor, k0: int, k1: int):
         a = self.arena
@@ -556,6 +606,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             k: {kk: (vv.to(dev) if torch.is_tensor(vv) else vv) for kk, vv in v.items()} for k, v in sd["steer"].items()
         }
         self.qr_telemetry = sd.get("qr_telemetry", self.qr_telemetry)
+        self._q16.clear()  # derived from the bases just loaded
 
     def get_qr_telemetry(self) -> Dict:
         return self.qr_telemetry
