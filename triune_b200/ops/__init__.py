@@ -203,9 +203,20 @@ class _MLPFn(torch.autograd.Function):
         return dx, dw1, db1, dw2, db2
 
 
+def _wants_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
 def mlp_gelu(x, w1, b1, w2, b2):
     """Dense FFN: gelu_tanh(x w1^T + b1) w2^T + b2."""
     if _ext.use_kernels(x, w1, w2) and x.dtype == torch.bfloat16 and b1 is not None and b2 is not None:
+        if not _wants_grad(x, w1, b1, w2, b2):
+            # inference: the GELU epilogue skips the derivative tile (half the bytes written by the first GEMM)
+            K = x.shape[-1]
+            x2 = x.reshape(-1, K)
+            if not _tma_ok(x2):
+                x2 = x2.contiguous()
+            return gemm(gemm(x2, w1, bias=b1, gelu=True), w2, bias=b2).view(*x.shape[:-1], w2.shape[0])
         return _MLPFn.apply(x, w1, b1, w2, b2)
     return F.linear(ref.gelu_tanh(F.linear(x, w1, b1)), w2, b2)
 
@@ -694,7 +705,15 @@ def moe_experts(x2, idx, weights, keep, w1, b1, w2, b2, shared_out=None, shared_
     if _ext.use_kernels(x2, w1, w2) and x2.dtype == torch.bfloat16:
         pos, row_src, tile_group, group_offsets, _ = plan if plan is not None else moe_plan(idx, keep, E)
         xp = _GatherRowsFn.apply(x2.contiguous(), row_src, pos)
-        yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets, getattr(plan, "row_pad", 128) == 256)
+        paired = getattr(plan, "row_pad", 128) == 256
+        if not _wants_grad(xp, w1, b1, w2, b2):
+            R = xp.shape[0]
+            h = torch.empty(R, w1.shape[1], device=xp.device, dtype=xp.dtype)
+            yp = torch.empty(R, w2.shape[1], device=xp.device, dtype=xp.dtype)
+            gemm(xp, w1, h, bias=b1, gelu=True, mode=GEMM_GROUPED_M, tile_group=tile_group)
+            gemm(h, w2, yp, bias=b2, mode=GEMM_GROUPED_M, tile_group=tile_group, paired_groups=paired and R % 256 == 0)
+        else:
+            yp = _ExpertMLPFn.apply(xp, w1, b1, w2, b2, tile_group, group_offsets, paired)
         wk = weights.float().contiguous()
         return _CombineRowsFn.apply(yp, pos, wk, row_src, shared_out, float(shared_scale))
     # reference path: loop over experts
