@@ -41,6 +41,8 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
                          float* chunk_tot, GlaDims d, int* status, cudaStream_t s);
 void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaMat G, GlaMat dG, GlaDims d,
                             cudaStream_t s);
+// Developer aid: eight int64 counters (device memory) receiving the backward kernel's phase clocks; null disables.
+void gla_set_debug_buffer(long long* counters);
 // One decode step for B*H heads: state [BH,64,64] fp32 in place; q,k,v,g rows of 64 bf16; out bf16.
 void launch_gla_decode_step(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, float* state, GlaMat O, int B, int H,
                             bool gate_logits, cudaStream_t s);

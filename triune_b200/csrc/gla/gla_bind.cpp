@@ -108,5 +108,9 @@ void register_gla(pybind11::module& m) {
   m.def("gla_fwd", &gla_fwd);
   m.def("gla_bwd", &gla_bwd);
   m.def("gla_decode", &gla_decode);
+  m.def("gla_debug_buffer", [](const c10::optional<Tensor>& t) {
+    TORCH_CHECK(!t.has_value() || !t->defined() || (t->scalar_type() == at::kLong && t->numel() >= 8), "int64[8] expected");
+    tb::gla_set_debug_buffer(t.has_value() && t->defined() ? (long long*)t->data_ptr<int64_t>() : nullptr);
+  });
   m.def("gdn_recurrent", &gdn_recurrent);
 }

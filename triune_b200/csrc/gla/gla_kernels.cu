@@ -48,7 +48,8 @@ __device__ __forceinline__ void st8(float* p, const float (&f)[8]) {
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
 __device__ __forceinline__ float log_decay(float x, bool logits) {
-  float g = logits ? (fminf(x, 0.f) - log1pf(__expf(-fabsf(x)))) : fminf(x, 0.f);
+  // log(1 + e) with e in (0, 1]: the fast logarithm's absolute error (1e-7) is far below the bf16 spacing of the gate
+  float g = logits ? (fminf(x, 0.f) - __logf(1.0f + __expf(-fabsf(x)))) : fminf(x, 0.f);
   return fmaxf(g, GLA_MIN_LOG_DECAY);
 }
 
@@ -243,46 +244,81 @@ __global__ void __launch_bounds__(256) gla_scan_kernel(const float* __restrict__
 //   sQ -> sA[0..3]: Q~(j)[t] = q_t e^{b_t - r_j} for t >= 16 j (zero rows above), r_0 = 0, r_j = b[16j-1]
 //   sK -> sKt:      K~[s]    = k_s e^{r_j(s) - b_s}
 // ------------------------------------------------------------------------------------------------
+// Factor tables of a chunk. With r_0 = 0 and r_j = b[16j-1] (the cumulative log decay just before sub-chunk j) and
+// b_C = b[63]:
+//   ftab[i][j][d] = e^{r_i - r_j}  for j <= i (<= 1; zero elsewhere)      gl[i][d] = e^{b_C - r_i}  (<= 1)
+// Every exponential of the form e^{b_t - r_j} then costs one multiply on top of e^{b_t - r_i} (i = sub-chunk of t),
+// which a thread computes once per element: the special-function unit was a quarter of the backward kernel's time.
+constexpr int FTAB_FLOATS = 4 * 4 * D;
+constexpr int GL_FLOATS = 4 * D;
+
+__device__ __forceinline__ void build_factor_tables(const float* bmat, float* ftab, float* gl) {
+  for (int idx = threadIdx.x; idx < FTAB_FLOATS; idx += blockDim.x) {
+    const int i = idx >> 8, j = (idx >> 6) & 3, d = idx & 63;
+    float f = 0.f;
+    if (j <= i) {
+      const float ri = i == 0 ? 0.f : bmat[(16 * i - 1) * BST + d];
+      const float rj = j == 0 ? 0.f : bmat[(16 * j - 1) * BST + d];
+      f = j == i ? 1.f : __expf(ri - rj);
+    }
+    ftab[idx] = f;
+  }
+  if (gl != nullptr) {
+    for (int idx = threadIdx.x; idx < GL_FLOATS; idx += blockDim.x) {
+      const int i = idx >> 6, d = idx & 63;
+      const float ri = i == 0 ? 0.f : bmat[(16 * i - 1) * BST + d];
+      gl[idx] = __expf(bmat[63 * BST + d] - ri);
+    }
+  }
+  __syncthreads();
+}
+
 __device__ __forceinline__ void build_score_operands(const uint8_t* sQ, const uint8_t* sK, uint8_t* sA, uint8_t* sKt,
-                                                     const float* bmat) {
+                                                     uint8_t* sKe, const float* bmat, const float* ftab,
+                                                     const float* gl) {
   for (int idx = threadIdx.x; idx < 512; idx += blockDim.x) {
     const int row = idx >> 3, ch = idx & 7;
     const uint32_t off = sw_off(row, ch);
-    float q[8], k[8], bt[8];
+    float q[8], k[8], bt[8], rj[8];
     unpack8(*reinterpret_cast<const uint4*>(sQ + off), q);
     unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
-#pragma unroll
     ld8(bmat + row * BST + ch * 8, bt);
     const int jrow = row >> 4;
+    if (jrow == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) rj[i] = 0.f;
+    } else {
+      ld8(bmat + (16 * jrow - 1) * BST + ch * 8, rj);
+    }
+    float qe[8], o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qe[i] = q[i] * __expf(bt[i] - rj[i]);  // q_t e^{b_t - r_jrow}
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float o[8];
-      if (j <= jrow) {
-        float r[8];
-        if (j == 0) {
+      if (j < jrow) {
+        float f[8];
+        ld8(ftab + (jrow * 4 + j) * D + ch * 8, f);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) r[i] = 0.f;
-        } else {
-          ld8(bmat + (16 * j - 1) * BST + ch * 8, r);
-        }
+        for (int i = 0; i < 8; ++i) o[i] = qe[i] * f[i];
+      } else if (j == jrow) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = q[i] * __expf(bt[i] - r[i]);
+        for (int i = 0; i < 8; ++i) o[i] = qe[i];
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = 0.f;
       }
       *reinterpret_cast<uint4*>(sA + j * TILE + off) = pack8(o);
     }
-    float o[8], r[8];
-    if (jrow == 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) r[i] = 0.f;
-    } else {
-      ld8(bmat + (16 * jrow - 1) * BST + ch * 8, r);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = k[i] * __expf(r[i] - bt[i]);
+    for (int i = 0; i < 8; ++i) o[i] = k[i] * __expf(rj[i] - bt[i]);  // K~: k_s e^{r_j(s) - b_s}
     *reinterpret_cast<uint4*>(sKt + off) = pack8(o);
+    if (sKe != nullptr) {  // K_end[s] = k_s e^{b_C - b_s} = K~[s] e^{b_C - r_j(s)}
+      float g8[8];
+      ld8(gl + jrow * D + ch * 8, g8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] *= g8[i];
+      *reinterpret_cast<uint4*>(sKe + off) = pack8(o);
+    }
   }
 }
 
@@ -373,7 +409,7 @@ __device__ __forceinline__ void store_row_tile(uint8_t* tile, int row, const flo
 // ------------------------------------------------------------------------------------------------
 // Phase 3 forward: o = Q~(0) S_c + mask(P) V
 // ------------------------------------------------------------------------------------------------
-constexpr int FWD_SMEM = 5 * TILE + BMAT_BYTES + 4 * TILE + TILE + TILE + 1024 + 256;
+constexpr int FWD_SMEM = 5 * TILE + BMAT_BYTES + FTAB_FLOATS * 4 + 4 * TILE + TILE + TILE + 1024 + 256;
 
 constexpr int FWD_THREADS = 256;
 
@@ -397,7 +433,8 @@ __global__ void __launch_bounds__(FWD_THREADS) gla_fwd_out_kernel(const __grid_c
   uint8_t* sKt = smem + 9 * TILE;
   uint8_t* sP = smem + 10 * TILE;
   float* bmat = reinterpret_cast<float*>(smem + 11 * TILE);
-  Bars* bars = reinterpret_cast<Bars*>(smem + 11 * TILE + BMAT_BYTES);
+  float* ftab = bmat + C * BST;
+  Bars* bars = reinterpret_cast<Bars*>(smem + 11 * TILE + BMAT_BYTES + FTAB_FLOATS * 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
@@ -435,7 +472,8 @@ __global__ void __launch_bounds__(FWD_THREADS) gla_fwd_out_kernel(const __grid_c
   const int row = quarter * 16 + (lane & 15);
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
-    build_score_operands(sQ, sK, sA, sKt, bmat);
+    build_factor_tables(bmat, ftab, nullptr);
+    build_score_operands(sQ, sK, sA, sKt, nullptr, bmat, ftab, nullptr);
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
@@ -507,7 +545,7 @@ __global__ void __launch_bounds__(FWD_THREADS) gla_fwd_out_kernel(const __grid_c
 //   dg_t = sum_{tau >= t} (q dq - k dk)   (suffix over the whole sequence; chunk suffix added by dg_finalize)
 // ------------------------------------------------------------------------------------------------
 constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
-constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * BMAT_BYTES + 1024 + 256;
+constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * BMAT_BYTES + (FTAB_FLOATS + GL_FLOATS) * 4 + 1024 + 256;
 
 constexpr int BWD_THREADS = 512;
 
@@ -518,10 +556,20 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmdS, int qcol, int kcol, int vcol, int gcol, int docol,
     __nv_bfloat16* __restrict__ dq, long long dq_ld, int dqcol, __nv_bfloat16* __restrict__ dk, long long dk_ld,
     int dkcol, __nv_bfloat16* __restrict__ dv, long long dv_ld, int dvcol, float* __restrict__ dgl_local,
-    float* __restrict__ chunk_tot, int T, int H, int logits, int* status) {
+    float* __restrict__ chunk_tot, int T, int H, int logits, int* status, long long* dbg) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  // optional phase timers (developer aid): thread 0 adds the clocks spent up to each mark to dbg[i]
+  const bool timed = dbg != nullptr && threadIdx.x == 0;
+  long long tmark = timed ? clock64() : 0;
+  auto mark = [&](int i) {
+    if (timed) {
+      const long long now = clock64();
+      atomicAdd(reinterpret_cast<unsigned long long*>(dbg + i), (unsigned long long)(now - tmark));
+      tmark = now;
+    }
+  };
   uint8_t* sQ = smem;
   uint8_t* sK = smem + TILE;
   uint8_t* sV = smem + 2 * TILE;
@@ -536,7 +584,9 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
   uint8_t* sdP = smem + 14 * TILE;
   float* bmat = reinterpret_cast<float*>(smem + 15 * TILE);
   float* dmat = bmat + C * BST;
-  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * BMAT_BYTES);
+  float* ftab = dmat + C * BST;
+  float* gl = ftab + FTAB_FLOATS;
+  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * BMAT_BYTES + (FTAB_FLOATS + GL_FLOATS) * 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
@@ -556,6 +606,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_slot;
+  mark(0);  // barrier init + TMEM allocation
   if (tid == 0) {
     mbar_expect_tx(&bars->tma, 7 * TILE);
     tma_load_3d(sQ, &tmQ, &bars->tma, qcol + h * D, row0, 0);
@@ -569,27 +620,18 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
   bool ok = mbar_wait(&bars->tma, 0);
   if (!ok) bars->failed = ST_TIMEOUT_FULL;
   __syncthreads();
+  mark(1);  // input tiles
   ok = bars->failed == 0;
   constexpr int CPW = 64 / (BWD_THREADS / 128);      // accumulator columns per warp (16 warps: 16)
   const int quarter = warp & 3, c0 = (warp >> 2) * CPW;  // TMEM lane quarter / first column of this warp
   const int row = quarter * 16 + (lane & 15);        // accumulator row owned by this thread when lane < 16
   if (ok) {
     build_cumsum(sG, bmat, logits != 0);
-    build_score_operands(sQ, sK, sA, sKt, bmat);
-    // K_end[s] = k_s e^{b_C - b_s}
-    for (int idx = tid; idx < 512; idx += blockDim.x) {
-      const int r = idx >> 3, ch = idx & 7;
-      const uint32_t off = sw_off(r, ch);
-      float k[8], bl[8], bt[8];
-      unpack8(*reinterpret_cast<const uint4*>(sK + off), k);
-      ld8(bmat + 63 * BST + ch * 8, bl);
-      ld8(bmat + r * BST + ch * 8, bt);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) k[i] *= __expf(bl[i] - bt[i]);
-      *reinterpret_cast<uint4*>(sKe + off) = pack8(k);
-    }
+    build_factor_tables(bmat, ftab, gl);
+    build_score_operands(sQ, sK, sA, sKt, sKe, bmat, ftab, gl);  // also K_end[s] = k_s e^{b_C - b_s}
     fence_proxy_async_smem();
     __syncthreads();
+    mark(2);  // cumulative decay and operand tiles
     // ---- stage 1: P (cols 0..63) and dP = dO V^T (cols 64..127)
     if (tid == 0) {
       tc_fence_after_sync();
@@ -616,6 +658,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     __syncthreads();
     ok = bars->failed == 0;
   }
+  mark(3);  // stage 1
   if (ok) {
     // ---- stage 2: dv (128..191), R1 = dO S^T (192..255), T_j = dP_j K~_j (256+64j)
     if (tid == 0) {
@@ -636,9 +679,22 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
         umma_bf16(tmem + 256 + 64 * j, desc_k(adP, j), desc_mn(aKt, j), id_km, 0u);
       umma_commit(&bars->mma[1]);
     }
-    // the row's cumulative log decay for this warp's columns: shared-memory reads overlap the MMAs
-    float bt[CPW];
-    ld_row<CPW>(bmat + row * BST + c0, bt);
+    // e^{b_t - r_i} for this thread's row (i = its sub-chunk) and columns: the only exponentials of this stage; the
+    // shared-memory reads and the special-function work overlap the MMAs
+    const int jrow = row >> 4;
+    float e0[CPW];
+    {
+      float bt[CPW], rj[CPW];
+      ld_row<CPW>(bmat + row * BST + c0, bt);
+      if (jrow == 0) {
+#pragma unroll
+        for (int d = 0; d < CPW; ++d) rj[d] = 0.f;
+      } else {
+        ld_row<CPW>(bmat + (16 * jrow - 1) * BST + c0, rj);
+      }
+#pragma unroll
+      for (int d = 0; d < CPW; ++d) e0[d] = __expf(bt[d] - rj[d]);
+    }
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
     if (ok) {
       tc_fence_after_sync();
@@ -655,24 +711,24 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
           *reinterpret_cast<uint4*>(dst + ch * 8) = pack8(o);
         }
       }
-      // dq
+      // dq = e^{b_t} R1 + sum_{j <= i} e^{b_t - r_j} T_j, with e^{b_t - r_j} = e0 * ftab[i][j] (r_0 = 0 covers R1)
       float acc[CPW];
       load_acc_cols<CPW>(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < CPW; ++d) acc[d] = v[d] * __expf(bt[d]);
+      for (int d = 0; d < CPW; ++d) acc[d] = v[d];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         load_acc_cols<CPW>(tmem, 256 + 64 * j + c0, quarter, v);  // warp-collective: every lane executes the load
-        if (j <= (row >> 4)) {
-          float r[CPW];
+        if (j <= jrow) {
+          float f[CPW];
+          ld_row<CPW>(ftab + (jrow * 4 + j) * D + c0, f);
           if (j == 0) {
 #pragma unroll
-            for (int d = 0; d < CPW; ++d) r[d] = 0.f;
+            for (int d = 0; d < CPW; ++d) acc[d] = (acc[d] + v[d]) * (e0[d] * f[d]);
           } else {
-            ld_row<CPW>(bmat + (16 * j - 1) * BST + c0, r);
-          }
 #pragma unroll
-          for (int d = 0; d < CPW; ++d) acc[d] += v[d] * __expf(bt[d] - r[d]);
+            for (int d = 0; d < CPW; ++d) acc[d] += v[d] * (e0[d] * f[d]);
+          }
         }
       }
       if (lane < 16) {
@@ -697,6 +753,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     __syncthreads();
     ok = bars->failed == 0;
   }
+  mark(4);  // stage 2
   if (ok) {
     // ---- stage 3: R2 = V dS^T (192..255), U_j = dP^T Q~(j) (256+64j)
     if (tid == 0) {
@@ -714,14 +771,20 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
       }
       umma_commit(&bars->mma[2]);
     }
-    float bt[CPW], bl[CPW], br[CPW];
-    ld_row<CPW>(bmat + row * BST + c0, bt);
-    ld_row<CPW>(bmat + 63 * BST + c0, bl);
-    if (quarter > 0) {
-      ld_row<CPW>(bmat + (16 * quarter - 1) * BST + c0, br);
-    } else {
+    // dk = e^{b_C - b_s} R2 + e^{r_q - b_s} U_q with q the sub-chunk of s; e^{b_C - b_s} = e^{r_q - b_s} gl[q]
+    float x0[CPW], gq[CPW];
+    {
+      float bt[CPW], br[CPW];
+      ld_row<CPW>(bmat + row * BST + c0, bt);
+      if (quarter > 0) {
+        ld_row<CPW>(bmat + (16 * quarter - 1) * BST + c0, br);
+      } else {
 #pragma unroll
-      for (int d = 0; d < CPW; ++d) br[d] = 0.f;
+        for (int d = 0; d < CPW; ++d) br[d] = 0.f;
+      }
+#pragma unroll
+      for (int d = 0; d < CPW; ++d) x0[d] = __expf(br[d] - bt[d]);
+      ld_row<CPW>(gl + quarter * D + c0, gq);
     }
     ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
     if (ok) {
@@ -729,10 +792,10 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
       float v[CPW], acc[CPW];
       load_acc_cols<CPW>(tmem, 192 + c0, quarter, v);
 #pragma unroll
-      for (int d = 0; d < CPW; ++d) acc[d] = v[d] * __expf(bl[d] - bt[d]);
+      for (int d = 0; d < CPW; ++d) acc[d] = v[d] * gq[d];
       load_acc_cols<CPW>(tmem, 256 + 64 * quarter + c0, quarter, v);  // rows of sub-chunk j = quarter live in accumulator j
 #pragma unroll
-      for (int d = 0; d < CPW; ++d) acc[d] += v[d] * __expf(br[d] - bt[d]);
+      for (int d = 0; d < CPW; ++d) acc[d] = (acc[d] + v[d]) * x0[d];
       if (lane < 16) {
         __nv_bfloat16* dst = dk + (long long)(row0 + row) * dk_ld + dkcol + h * D + c0;
 #pragma unroll
@@ -755,6 +818,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     __syncthreads();
     ok = bars->failed == 0;
   }
+  mark(5);  // stage 3
   if (ok) {
     // in-chunk suffix sum of (q dq - k dk) per key dimension: parts of PR rows in parallel, then the totals of the
     // later parts (left in their first rows) are added on the way out
@@ -772,6 +836,8 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     for (int t = PR * part; t < PR * part + PR; ++t) dst[(long long)t * (H * D)] = dmat[t * BST + d] + base;
     if (part == 0) chunk_tot[(long long)blockIdx.x * D + d] = dmat[d] + base;
   }
+  mark(6);  // suffix sums
+  if (timed) atomicAdd(reinterpret_cast<unsigned long long*>(dbg + 7), 1ull);
   tc_fence_before_sync();
   __syncthreads();
   if (bars->failed != 0 && tid == 0 && status != nullptr) atomicCAS(status, 0, bars->failed);
@@ -913,6 +979,9 @@ void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloa
   check_launch("gla_fwd_out");
 }
 
+static long long* g_gla_dbg = nullptr;
+void gla_set_debug_buffer(long long* p) { g_gla_dbg = p; }
+
 void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, const __nv_bfloat16* states,
                          const __nv_bfloat16* dstates, GlaMat dQ, GlaMat dK, GlaMat dV, float* dgl_local,
                          float* chunk_tot, GlaDims d, int* status, cudaStream_t s) {
@@ -934,7 +1003,7 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dQ.ptr)), dQ.ld, dQ.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dK.ptr)), dK.ld, dK.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dV.ptr)), dV.ld, dV.col0, dgl_local, chunk_tot, d.T, d.H,
-      d.gate_logits ? 1 : 0, status);
+      d.gate_logits ? 1 : 0, status, g_gla_dbg);
   check_launch("gla_bwd_main");
 }
 
