@@ -542,10 +542,17 @@ __global__ void __launch_bounds__(FWD_THREADS) gla_fwd_out_kernel(const __grid_c
 //   dk = e^{b_C - b_s} (V dS_end^T) + e^{r_j(s) - b_s} (dP^T Q~(j(s)))
 //   dg_t = sum_{tau >= t} (q dq - k dk)   (suffix over the whole sequence; chunk suffix added by dg_finalize)
 // ------------------------------------------------------------------------------------------------
-constexpr int BWD_TILES = 7 + 4 + 4;  // Q K V G dO S dS | A0..3 | Kt Kend P dP
+constexpr int BWD_TILES = 2 * 7 + 4 + 4;  // 2 x (Q K V G dO S dS) | A0..3 | Kt Kend P dP
 constexpr int BWD_SMEM = BWD_TILES * TILE + 2 * BMAT_BYTES + (FTAB_FLOATS + GL_FLOATS) * 4 + 1024 + 256;
 
 constexpr int BWD_THREADS = 512;
+
+struct BwdBars {
+  uint64_t tma[2];  // input tiles of the two buffers
+  uint64_t mma[3];
+  uint32_t tmem_slot;
+  int failed;
+};
 
 __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -554,7 +561,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     const __grid_constant__ CUtensorMap tmdS, int qcol, int kcol, int vcol, int gcol, int docol,
     __nv_bfloat16* __restrict__ dq, long long dq_ld, int dqcol, __nv_bfloat16* __restrict__ dk, long long dk_ld,
     int dkcol, __nv_bfloat16* __restrict__ dv, long long dv_ld, int dvcol, float* __restrict__ dgl_local,
-    float* __restrict__ chunk_tot, int T, int H, int logits, int* status, long long* dbg) {
+    float* __restrict__ chunk_tot, int T, int H, int logits, int nchunks, int* status, long long* dbg) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -568,30 +575,23 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
       tmark = now;
     }
   };
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + TILE;
-  uint8_t* sV = smem + 2 * TILE;
-  uint8_t* sG = smem + 3 * TILE;
-  uint8_t* sdO = smem + 4 * TILE;
-  uint8_t* sS = smem + 5 * TILE;
-  uint8_t* sdS = smem + 6 * TILE;
-  uint8_t* sA = smem + 7 * TILE;  // 4 tiles
-  uint8_t* sKt = smem + 11 * TILE;
-  uint8_t* sKe = smem + 12 * TILE;
-  uint8_t* sP = smem + 13 * TILE;
-  uint8_t* sdP = smem + 14 * TILE;
-  float* bmat = reinterpret_cast<float*>(smem + 15 * TILE);
+  uint8_t* sIn = smem;              // 2 buffers x 7 input tiles (Q K V G dO S dS)
+  uint8_t* sA = smem + 14 * TILE;   // 4 tiles
+  uint8_t* sKt = smem + 18 * TILE;
+  uint8_t* sKe = smem + 19 * TILE;
+  uint8_t* sP = smem + 20 * TILE;
+  uint8_t* sdP = smem + 21 * TILE;
+  float* bmat = reinterpret_cast<float*>(smem + BWD_TILES * TILE);
   float* dmat = bmat + C * BST;
   float* ftab = dmat + C * BST;
   float* gl = ftab + FTAB_FLOATS;
-  Bars* bars = reinterpret_cast<Bars*>(smem + 15 * TILE + 2 * BMAT_BYTES + (FTAB_FLOATS + GL_FLOATS) * 4);
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + BWD_TILES * TILE + 2 * BMAT_BYTES + (FTAB_FLOATS + GL_FLOATS) * 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NT = T / C;
-  const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
-  const int row0 = b * T + chunk * C;
 
   if (tid == 0) {
-    mbar_init(&bars->tma, 1);
+    mbar_init(&bars->tma[0], 1);
+    mbar_init(&bars->tma[1], 1);
     for (int i = 0; i < 3; ++i) mbar_init(&bars->mma[i], 1);
     bars->failed = 0;
     mbar_fence_init();
@@ -605,17 +605,47 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_slot;
   mark(0);  // barrier init + TMEM allocation
-  if (tid == 0) {
-    mbar_expect_tx(&bars->tma, 7 * TILE);
-    tma_load_3d(sQ, &tmQ, &bars->tma, qcol + h * D, row0, 0);
-    tma_load_3d(sK, &tmK, &bars->tma, kcol + h * D, row0, 0);
-    tma_load_3d(sV, &tmV, &bars->tma, vcol + h * D, row0, 0);
-    tma_load_3d(sG, &tmG, &bars->tma, gcol + h * D, row0, 0);
-    tma_load_3d(sdO, &tmdO, &bars->tma, docol + h * D, row0, 0);
-    tma_load_3d(sS, &tmS, &bars->tma, 0, blockIdx.x * D, 0);
-    tma_load_3d(sdS, &tmdS, &bars->tma, 0, blockIdx.x * D, 0);
+  // The CTA is persistent: it walks the chunks blockIdx.x, blockIdx.x + gridDim.x, ... and loads the input tiles of
+  // the next chunk into the other buffer while it works on the current one, so neither the load latency nor the
+  // per-CTA set-up (TMEM allocation, barrier init, block scheduling) is paid per chunk.
+  auto issue_loads = [&](int cidx, int buf) {
+    const int ch_ = cidx % NT, bh_ = cidx / NT, h_ = bh_ % H, r0_ = (bh_ / H) * T + ch_ * C;
+    uint8_t* dst = sIn + buf * 7 * TILE;
+    uint64_t* bar = &bars->tma[buf];
+    mbar_expect_tx(bar, 7 * TILE);
+    tma_load_3d(dst, &tmQ, bar, qcol + h_ * D, r0_, 0);
+    tma_load_3d(dst + TILE, &tmK, bar, kcol + h_ * D, r0_, 0);
+    tma_load_3d(dst + 2 * TILE, &tmV, bar, vcol + h_ * D, r0_, 0);
+    tma_load_3d(dst + 3 * TILE, &tmG, bar, gcol + h_ * D, r0_, 0);
+    tma_load_3d(dst + 4 * TILE, &tmdO, bar, docol + h_ * D, r0_, 0);
+    tma_load_3d(dst + 5 * TILE, &tmS, bar, 0, cidx * D, 0);
+    tma_load_3d(dst + 6 * TILE, &tmdS, bar, 0, cidx * D, 0);
+  };
+  if (tid == 0 && (int)blockIdx.x < nchunks) issue_loads(blockIdx.x, 0);
+  int it = 0;
+  int pend_buf = -1;        // thread 0: buffer with a prefetch in flight (waited for, bounded, if the loop is left early)
+  uint32_t pend_par = 0;
+  for (int cidx = blockIdx.x; cidx < nchunks; cidx += gridDim.x, ++it) {
+  const int buf = it & 1;
+  const uint32_t par = (uint32_t)(it & 1);  // parity of the once-per-chunk MMA barriers
+  const int chunk = cidx % NT, bh = cidx / NT, h = bh % H, b = bh / H;
+  const int row0 = b * T + chunk * C;
+  uint8_t* sQ = sIn + buf * 7 * TILE;
+  uint8_t* sK = sQ + TILE;
+  uint8_t* sV = sQ + 2 * TILE;
+  uint8_t* sG = sQ + 3 * TILE;
+  uint8_t* sdO = sQ + 4 * TILE;
+  uint8_t* sS = sQ + 5 * TILE;
+  uint8_t* sdS = sQ + 6 * TILE;
+  if (tid == 0 && cidx + (int)gridDim.x < nchunks) {
+    fence_proxy_async_smem();  // the other buffer was last read through the generic proxy (previous chunk)
+    issue_loads(cidx + gridDim.x, buf ^ 1);
+    pend_buf = buf ^ 1;
+    pend_par = (uint32_t)(((it + 1) >> 1) & 1);
+  } else {
+    pend_buf = -1;
   }
-  bool ok = mbar_wait(&bars->tma, 0);
+  bool ok = mbar_wait(&bars->tma[buf], (uint32_t)((it >> 1) & 1));
   if (!ok) bars->failed = ST_TIMEOUT_FULL;
   __syncthreads();
   mark(1);  // input tiles
@@ -640,7 +670,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
       for (int k = 0; k < 4; ++k) umma_bf16(tmem + 64, desc_k(a, k), desc_k(bb, k), id, k > 0);
       umma_commit(&bars->mma[0]);
     }
-    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], 0));
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[0], par));
     if (ok) {
       tc_fence_after_sync();
       float v[CPW];
@@ -693,7 +723,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
 #pragma unroll
       for (int d = 0; d < CPW; ++d) e0[d] = __expf(bt[d] - rj[d]);
     }
-    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], 0));
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[1], par));
     if (ok) {
       tc_fence_after_sync();
       float v[CPW];
@@ -784,7 +814,7 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
       for (int d = 0; d < CPW; ++d) x0[d] = __expf(br[d] - bt[d]);
       ld_row<CPW>(gl + quarter * D + c0, gq);
     }
-    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], 0));
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars->mma[2], par));
     if (ok) {
       tc_fence_after_sync();
       float v[CPW], acc[CPW];
@@ -832,10 +862,18 @@ __global__ void __launch_bounds__(BWD_THREADS) gla_bwd_main_kernel(
     for (int pp = part + 1; pp < NPARTS; ++pp) base += dmat[(PR * pp) * BST + d];
     float* dst = dgl_local + (long long)row0 * (H * D) + h * D + d;
     for (int t = PR * part; t < PR * part + PR; ++t) dst[(long long)t * (H * D)] = dmat[t * BST + d] + base;
-    if (part == 0) chunk_tot[(long long)blockIdx.x * D + d] = dmat[d] + base;
+    if (part == 0) chunk_tot[(long long)cidx * D + d] = dmat[d] + base;
   }
   mark(6);  // suffix sums
   if (timed) atomicAdd(reinterpret_cast<unsigned long long*>(dbg + 7), 1ull);
+  // chunk boundary: every read of this chunk's tiles, scratch matrices and accumulators is done before the next
+  // chunk rewrites them
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (bars->failed != 0) break;
+  }  // chunk loop
+  if (bars->failed != 0 && tid == 0 && pend_buf >= 0) (void)mbar_wait(&bars->tma[pend_buf], pend_par);
   tc_fence_before_sync();
   __syncthreads();
   if (bars->failed != 0 && tid == 0 && status != nullptr) atomicCAS(status, 0, bars->failed);
@@ -995,13 +1033,21 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
     set_smem(gla_bwd_main_kernel, BWD_SMEM);
     cfg = true;
   }
-  const int grid = d.B * d.H * (d.T / C);
+  const int nchunks = d.B * d.H * (d.T / C);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int grid = nchunks < sms ? nchunks : sms;  // one persistent CTA per SM
   gla_bwd_main_kernel<<<grid, BWD_THREADS, BWD_SMEM, s>>>(
       tq, tk, tv, tg, tdo, ts, tds, Q.col0, K.col0, V.col0, G.col0, dO.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dQ.ptr)), dQ.ld, dQ.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dK.ptr)), dK.ld, dK.col0,
       reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dV.ptr)), dV.ld, dV.col0, dgl_local, chunk_tot, d.T, d.H,
-      d.gate_logits ? 1 : 0, status, g_gla_dbg);
+      d.gate_logits ? 1 : 0, nchunks, status, g_gla_dbg);
   check_launch("gla_bwd_main");
 }
 
