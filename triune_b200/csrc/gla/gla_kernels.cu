@@ -331,27 +331,6 @@ __device__ __forceinline__ void issue_score_mmas(uint32_t tmem, uint32_t p_col, 
   }
 }
 
-// Reads one 64-column fp32 accumulator row (lane i < 16 of warp w owns row 16w+i) into v[64].
-__device__ __forceinline__ void load_acc_row(uint32_t tmem, uint32_t col, int warp, float (&v)[64]) {
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t r[32];
-    tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + col + half * 32, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[half * 32 + i] = __uint_as_float(r[i]);
-  }
-}
-
-// 32-column variants for the 8-warp backward kernel: warp w works on TMEM lane quarter (w & 3) and on columns
-// [32*(w>>2), 32*(w>>2)+32) of every 64-column accumulator.
-__device__ __forceinline__ void load_acc_half(uint32_t tmem, uint32_t col, int quarter, float (&v)[32]) {
-  uint32_t r[32];
-  tmem_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + col, r);
-  tmem_ld_wait();
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 // N-column slice (N = 16 or 32) of an accumulator row: TMEM lane quarter `quarter`, columns [col, col + N).
 template <int N>
 __device__ __forceinline__ void load_acc_cols(uint32_t tmem, uint32_t col, int quarter, float (&v)[N]) {
@@ -382,28 +361,6 @@ __device__ __forceinline__ void ld_row(const float* p, float (&f)[N]) {
     f[4 * i] = t.x; f[4 * i + 1] = t.y; f[4 * i + 2] = t.z; f[4 * i + 3] = t.w;
   }
 }
-__device__ __forceinline__ void store_row_half(uint8_t* tile, int row, int half, const float (&v)[32], int limit) {
-#pragma unroll
-  for (int c4 = 0; c4 < 4; ++c4) {
-    const int ch = half * 4 + c4;
-    float o[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = (ch * 8 + i <= limit) ? v[c4 * 8 + i] : 0.f;
-    *reinterpret_cast<uint4*>(tile + sw_off(row, ch)) = pack8(o);
-  }
-}
-
-// Writes a row of 64 values as bf16 into a swizzled tile; entries with column > limit are zeroed (causal mask).
-__device__ __forceinline__ void store_row_tile(uint8_t* tile, int row, const float (&v)[64], int limit) {
-#pragma unroll
-  for (int ch = 0; ch < 8; ++ch) {
-    float o[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = (ch * 8 + i <= limit) ? v[ch * 8 + i] : 0.f;
-    *reinterpret_cast<uint4*>(tile + sw_off(row, ch)) = pack8(o);
-  }
-}
-
 // ------------------------------------------------------------------------------------------------
 // Phase 3 forward: o = Q~(0) S_c + mask(P) V
 // ------------------------------------------------------------------------------------------------
