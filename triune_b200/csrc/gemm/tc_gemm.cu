@@ -348,7 +348,12 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
     const int sms = sm_count();
     if (kp.total_tiles * 2 <= sms && total_iters >= 16) {
       int splits = sms / kp.total_tiles;
-      const int max_splits = total_iters / 8;
+      int max_splits = total_iters / 8;
+      static const int split_cap = [] {
+        const char* e = std::getenv("TRIUNE_GEMM_MAX_SPLITS");  // tuning knob: upper bound of the split-K factor
+        return e ? std::atoi(e) : 0;
+      }();
+      if (split_cap > 0 && max_splits > split_cap) max_splits = split_cap;
       if (splits > max_splits) splits = max_splits;
       if (splits > 1) {
         kp.iters_per_split = (total_iters + splits - 1) / splits;
