@@ -501,3 +501,21 @@ def test_parallel_engine_and_disk_streaming(tmp_path):
     assert describe_cache(tmp_path / "cache")["num_layers"] == 3
     counts = scan_models([str(tmp_path)])["counts"]
     assert counts.get("hf_model") == 1 and counts.get("nvfp4_cache") == 1
+
+
+def test_expert_parallel_positions_match_one_hot_cumsum():
+    """Position of an assignment inside its expert, from one stable sort, equals the cumulative one-hot count."""
+    import torch
+
+    from triune_b200.parallel.expert_parallel import _positions
+
+    torch.manual_seed(0)
+    E = 16
+    idx = torch.randint(-1, E, (5000,), dtype=torch.int32)  # -1 = dropped assignment
+    pos, counts = _positions(idx, E)
+    onehot = idx.view(-1, 1) == torch.arange(E, dtype=idx.dtype).view(1, -1)
+    csum = onehot.to(torch.int32).cumsum(0, dtype=torch.int32)
+    want = (csum.gather(1, idx.clamp_min(0).long().view(-1, 1)).view(-1) - 1).to(torch.int32)
+    want = torch.where(idx >= 0, want, torch.full_like(want, -1))
+    assert pos.dtype == torch.int32 and counts.dtype == torch.int32
+    assert torch.equal(pos, want) and torch.equal(counts, csum[-1])
