@@ -82,7 +82,9 @@ def classify_parameters(model: torch.nn.Module, param_roles: Optional[Dict] = No
     for mn, mod in model.named_modules():
         if isinstance(mod, (torch.nn.Embedding, torch.nn.EmbeddingBag)):
             embed_ptrs.add(mod.weight.data_ptr())
-        if isinstance(mod, MoE_FFN):
+        # the expert-sharded layer (parallel.expert_parallel.EPMoE_FFN) holds a slice of the same stacked weights
+        is_moe = isinstance(mod, MoE_FFN) or all(hasattr(mod, a) for a in ("w1", "b1", "w2", "b2", "router", "expert_bias"))
+        if is_moe:
             router_ids.update(id(p) for p in mod.router.parameters())
             for attr, role in (("w1", "input"), ("w2", "hidden")):
                 p = getattr(mod, attr)
