@@ -77,3 +77,22 @@ def test_expert_parallel_dispatch_combine():
         # so the whole-model check is on the mean error
         assert r["model_layers_sharded"] == 2 and r["layer_fwd"] < 3e-2 and r["model_fwd_mean"] < 2e-2, r
         assert r["model_loss_finite"] and r["model_status"] == 0, r
+
+
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_tensor_parallel_dense_model(mode):
+    """Two GPUs: the tensor-parallel dense model against the unsharded one in bf16 (library collectives, then the
+    GEMMs fused with their collectives)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _launch(2, {"TRIUNE_TP_DEVICE": "cuda", "TRIUNE_TP_MODE": mode}, worker="mp_tp_model_worker.py", port="29619")
+    for r in res:
+        for k, v in r.items():
+            if k == "rank":
+                continue
+            if k.endswith("_status"):
+                assert v == 0, (k, v)
+            elif k.endswith("_loss"):
+                assert v < 2e-2, (k, v)
+            else:
+                assert v < 8e-2, (k, v)  # bf16 activations end to end: a few percent on the largest gradient entry

@@ -253,3 +253,23 @@ def test_layer_store_keeps_every_tensor_on_a_vector_boundary():
     for p, q in zip(layer.parameters(), before):
         assert torch.equal(p.detach(), q) and (p.data_ptr() - dev.data_ptr()) % 16 == 0
     st.bind_host()
+
+
+def test_tensor_parallel_dense_model_matches_unsharded_on_gloo():
+    """Two gloo ranks: the tensor-parallel dense model (sequence-parallel rows, column / row parallel projections) gives
+    the loss and every gradient of the unsharded model, for GLA + SwiGLU and Gated DeltaNet + GELU blocks."""
+    import json
+    import re
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2", TRIUNE_TP_DEVICE="cpu")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29733", os.path.join(ROOT, "tests", "mp_tp_model_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    dec = json.JSONDecoder()
+    res = [dec.raw_decode(p.stdout, m.end())[0] for m in re.finditer(r"RESULT (?=\{)", p.stdout)]
+    assert p.returncode == 0 and len(res) == 2, p.stdout[-2000:] + p.stderr[-2000:]
+    for r in res:
+        for k, v in r.items():
+            if k == "rank" or k.endswith("_status"):
+                continue
+            assert v < 1e-4, (k, v)
