@@ -57,6 +57,30 @@ def test_gated_deltanet_chunk_matches_recurrence(beta_kind):
     assert (o1 - o2).abs().max() < 1e-8 and (s1 - s2).abs().max() < 1e-8
 
 
+@pytest.mark.parametrize("beta_kind,T", [(None, 128), ("head", 75), ("head", 200)])
+def test_gated_deltanet_parallel_form_matches_recurrence_with_gradients(beta_kind, T):
+    """The chunk-parallel WY form (the training path) against the token recurrence: outputs, final state and the
+    gradients of q, k, v, g, for whole and ragged numbers of chunks."""
+    torch.manual_seed(4)
+    B, H, D, Dv = 2, 2, 16, 24
+    q = torch.randn(B, T, H, D, dtype=torch.float64) * 0.5
+    k = F.normalize(torch.randn(B, T, H, D, dtype=torch.float64), dim=-1)
+    v = torch.randn(B, T, H, Dv, dtype=torch.float64)
+    g = F.logsigmoid(torch.randn(B, T, H, D, dtype=torch.float64) * 2)
+    beta = torch.rand(B, T, H, dtype=torch.float64) if beta_kind else None
+    s0 = torch.randn(B, H, D, Dv, dtype=torch.float64) * 0.1
+    a = [t.clone().requires_grad_(True) for t in (q, k, v, g)]
+    b = [t.clone().requires_grad_(True) for t in (q, k, v, g)]
+    o1, s1 = ref.gated_deltanet_recurrent(*a, beta, s0, 0.7)
+    o2, s2 = ref.gated_deltanet_chunk_parallel(*b, beta, s0, 0.7, chunk_size=64)
+    do, ds = torch.randn_like(o1), torch.randn_like(s1)
+    ((o1 * do).sum() + (s1 * ds).sum()).backward()
+    ((o2 * do).sum() + (s2 * ds).sum()).backward()
+    assert (o1 - o2).abs().max() < 1e-9 and (s1 - s2).abs().max() < 1e-9
+    for x, y in zip(a, b):
+        assert (x.grad - y.grad).abs().max() < 1e-8
+
+
 def test_decode_step_matches_recurrence():
     torch.manual_seed(3)
     B, T, H, D = 2, 5, 2, 8

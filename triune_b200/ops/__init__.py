@@ -395,7 +395,8 @@ def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0
     """Gated DeltaNet over [B,T,H,D] tensors; returns (out, final_state [B,H,Dk,Dv]).
 
     Without gradients (prefill, decode) CUDA bf16 inputs run the exact token recurrence in one kernel; with gradients
-    the differentiable chunked UT-transform form of :mod:`triune_b200.ops.reference` is used."""
+    the differentiable chunk-parallel WY form of :mod:`triune_b200.ops.reference` is used (one batched pass over all
+    chunks plus two small products per chunk for the state)."""
     from . import gla_cuda
 
     if gla_cuda.gdn_supported(q, k, v, g, beta):
@@ -406,7 +407,7 @@ def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0
             q[:, 0], k[:, 0], v[:, 0], gl[:, 0], initial_state, None if beta is None else beta[:, 0], scale
         )
         return o.unsqueeze(1), s
-    return ref.gated_deltanet_chunk(q, k, v, gl, beta, initial_state, scale, chunk_size)
+    return ref.gated_deltanet_chunk_parallel(q, k, v, gl, beta, initial_state, scale, chunk_size)
 
 
 # ----------------------------------------------------------------------------

@@ -270,6 +270,89 @@ def gated_deltanet_chunk(q, k, v, g, beta=None, initial_state=None, scale: float
     return out.to(q.dtype), S
 
 
+def _chunk_scores_factored(qc, kc, bq, bk, strict: bool):
+    """The decayed scores of :func:`_chunk_scores` with every 16 x 16 block written as a matrix product around the
+    block's first query row (the layout of the tcgen05 kernels): off-diagonal blocks as there, diagonal blocks as
+    (q e^{bq - ref}) (k e^{ref - bk})^T with exponents up to +80 on the key side. Exact while the decay inside a
+    16-token sub-chunk stays above e^-80 (log-sigmoid gates reach that only with logits below -5 on every step); no
+    [.., 16, 16, d] intermediates are built, so memory and time drop by the head dimension."""
+    C = qc.shape[-2]
+    SC = 16
+    n_sub = (C + SC - 1) // SC
+    rows = []
+    for i in range(n_sub):
+        t0, t1 = i * SC, min(C, (i + 1) * SC)
+        ref = bq[..., t0 : t0 + 1, :]
+        qs = qc[..., t0:t1, :] * torch.exp(torch.clamp(bq[..., t0:t1, :] - ref, max=0.0))
+        ks = kc[..., :t1, :] * torch.exp(torch.clamp(ref - bk[..., :t1, :], max=80.0))
+        blk = qs @ ks.transpose(-1, -2)                                    # [.., t1-t0, t1]
+        n = t1 - t0
+        mask = torch.ones(n, n, dtype=torch.bool, device=qc.device).tril(-1 if strict else 0)
+        diag = blk[..., t0:t1] * mask
+        pad = blk.new_zeros(*blk.shape[:-1], C - t1)
+        rows.append(torch.cat((blk[..., :t0], diag, pad), dim=-1))
+    return torch.cat(rows, dim=-2)
+
+
+def gated_deltanet_chunk_parallel(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0, chunk_size: int = 64):
+    """Chunk-parallel Gated DeltaNet in the WY form, differentiable; the training path of ``ops.gated_deltanet``.
+
+    Same algebra as :func:`gated_deltanet_chunk`, arranged so that everything except the state recurrence is ONE batched
+    operation over all chunks: with T = (I + L)^{-1} per chunk, U0 = T (beta V) and W = T (beta Kbar) the effective
+    values of chunk c are U_c = U0_c - W_c S_c, so the only sequential part is two small matrix products per chunk
+    (W_c S_c and K_end_c^T U_c); scores, the triangular solves and the outputs run batched. Exact while no 16-token
+    sub-chunk decays by more than e^-80 in total (see :func:`_chunk_scores_factored`). A per-row [B,T,H,dk] beta falls
+    back to the token recurrence.
+    """
+    if beta is not None and beta.ndim == 4:
+        return gated_deltanet_recurrent(q, k, v, g, beta, initial_state, scale)
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    C = chunk_size
+    dt = torch.float64 if q.dtype == torch.float64 else torch.float32
+    pad = (-T) % C
+    NT = (T + pad) // C
+
+    def prep(x, fill=0.0):  # [B,T,H,d] -> [B,H,NT,C,d], zero rows appended (no key, no value, no decay: a no-op)
+        x = x.to(dt).permute(0, 2, 1, 3)
+        if pad:
+            x = torch.cat((x, x.new_full((B, H, pad, x.shape[-1]), fill)), dim=2)
+        return x.reshape(B, H, NT, C, x.shape[-1])
+
+    qf, kf, vf = prep(q), prep(k), prep(v)
+    gf = torch.clamp(prep(g), max=0.0)
+    b = torch.cumsum(gf, dim=-2)
+    b_prev = b - gf
+    b_last = b[..., -1:, :]                                                 # [B,H,NT,1,dk]
+    L = _chunk_scores_factored(kf, kf, b_prev, b, strict=True)             # [B,H,NT,C,C]
+    kbar = kf * torch.exp(b_prev)
+    rhs_v, rhs_k = vf, kbar
+    if beta is not None:
+        bf = beta.to(dt).permute(0, 2, 1)
+        if pad:
+            bf = torch.cat((bf, bf.new_zeros(B, H, pad)), dim=2)
+        bf = bf.reshape(B, H, NT, C, 1)
+        L, rhs_v, rhs_k = L * bf, vf * bf, kbar * bf
+    eye = torch.eye(C, dtype=dt, device=q.device)
+    sol = torch.linalg.solve_triangular(eye + L, torch.cat((rhs_v, rhs_k), dim=-1), upper=False, unitriangular=True)
+    U0, W = sol[..., :dv], sol[..., dv:]                                    # [B,H,NT,C,dv], [B,H,NT,C,dk]
+    kend_t = (kf * torch.exp(b_last - b)).transpose(-1, -2)                 # [B,H,NT,dk,C]
+    decay = torch.exp(b_last).transpose(-1, -2)                             # [B,H,NT,dk,1]
+    S = initial_state.to(dt) if initial_state is not None else q.new_zeros(B, H, dk, dv, dtype=dt)
+    states, us = [], []
+    for c in range(NT):                                                     # the sequential part
+        states.append(S)
+        Uc = U0[:, :, c] - W[:, :, c] @ S
+        us.append(Uc)
+        S = S * decay[:, :, c] + kend_t[:, :, c] @ Uc
+    S_all = torch.stack(states, dim=2)                                      # state before each chunk
+    U = torch.stack(us, dim=2)
+    A = _chunk_scores_factored(qf, kf, b, b, strict=False)
+    o = (A @ U + (qf * torch.exp(b)) @ S_all) * scale
+    out = o.reshape(B, H, NT * C, dv)[:, :, :T].permute(0, 2, 1, 3)
+    return out.to(q.dtype), S
+
+
 def gated_deltanet_decode_step(q, k, v, g, state, beta=None, scale: float = 1.0):
     sf = state.float()
     kf = k.float()
