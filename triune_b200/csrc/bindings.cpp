@@ -401,7 +401,10 @@ void register_comm(pybind11::module& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tc_gemm", &tc_gemm);
   m.def("tc_gemm_debug_buffer", [](const c10::optional<Tensor>& t) {
-    tb::tc_gemm_set_debug_buffer(t.has_value() && t->defined() ? (long long*)t->data_ptr<int64_t>() : nullptr);
+    const bool on = t.has_value() && t->defined();
+    TORCH_CHECK(!on || (t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() && t->numel() >= 16),
+                "tc_gemm_debug_buffer: a contiguous CUDA int64 tensor with at least 16 entries, or None");
+    tb::tc_gemm_set_debug_buffer(on ? (long long*)t->data_ptr<int64_t>() : nullptr);
   });
   m.def("tc_gemm_pair_launches", []() { return (int64_t)tb::tc_gemm_pair_launch_count(); });
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

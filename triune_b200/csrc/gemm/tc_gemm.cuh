@@ -52,7 +52,7 @@ void launch_tc_gemm(const GemmArgs& args, cudaStream_t stream);
 // nothing, when the shape does not suit it. launch_tc_gemm tries it first.
 bool launch_tc_gemm_pair(const GemmArgs& args, cudaStream_t stream);
 long long tc_gemm_pair_launch_count();
-// Developer aid: eight int64 counters (device memory) that one epilogue warp per CTA adds its phase times to; null disables.
+// Developer aid: sixteen int64 counters (device memory) that one epilogue warp per CTA adds its phase times to; null disables.
 void tc_gemm_set_debug_buffer(long long* counters);  // launches taken by the CTA-pair kernel so far in this process
 
 }  // namespace tb
