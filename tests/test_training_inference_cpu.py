@@ -273,3 +273,23 @@ def test_tensor_parallel_dense_model_matches_unsharded_on_gloo():
             if k == "rank" or k.endswith("_status"):
                 continue
             assert v < 1e-4, (k, v)
+
+
+def test_context_parallel_gla_matches_whole_sequence_on_gloo():
+    """Three gloo ranks, one sequence segment each: the state hand-off reproduces outputs, final state and all input
+    gradients of the whole-sequence recurrence (fp64), with and without an autograd graph."""
+    import json
+    import re
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29735", os.path.join(ROOT, "tests", "mp_cp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    dec = json.JSONDecoder()
+    res = [dec.raw_decode(p.stdout, m.end())[0] for m in re.finditer(r"RESULT (?=\{)", p.stdout)]
+    assert p.returncode == 0 and len(res) == 3, p.stdout[-2000:] + p.stderr[-2000:]
+    assert any("state" in r for r in res)
+    for r in res:
+        for k, v in r.items():
+            if k != "rank":
+                assert v < 1e-9, (k, v)
