@@ -1,5 +1,6 @@
-"""Tensor-parallel training throughput of the dense model family: one rank per GPU, the whole world is one
-tensor-parallel group (sequence-parallel rows between blocks, heads and FFN width split over the ranks).
+"""Tensor-parallel training throughput of the dense model family: one rank per GPU; `--tp N` makes tensor-parallel
+groups of N consecutive ranks (default: the whole world) with data parallelism across them (sequence-parallel rows
+between blocks, heads and FFN width split over a group; one batch of `--batch` sequences per replica).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29560 \
         bench_tp.py --steps 5 --warmup 3
@@ -29,6 +30,7 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (smoke runs)")
     ap.add_argument("--mixer", default="", help="override the sequence mixer: gla or gated_deltanet")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (default: the whole world); the rest is data parallel")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"])
     a = ap.parse_args()
 
@@ -37,7 +39,7 @@ def main():
     from triune_b200.optim import CentroidSteerOptimizer
     from triune_b200.parallel import setup_distributed
     from triune_b200.parallel.tensor_parallel import TPContext
-    from triune_b200.parallel.tp_model import TensorParallelDense
+    from triune_b200.parallel.tp_model import TensorParallelDense, average_grads_over_replicas, make_tp_dp_groups
 
     ctx = setup_distributed()
     dev, rank, world = ctx.device, ctx.rank, ctx.world_size
@@ -57,7 +59,10 @@ def main():
     finally:
         torch.set_default_dtype(prev)
     full_params = full.num_parameters()
-    tp = TPContext(mode=a.tp_mode)
+    tp_size = a.tp if a.tp > 0 else world
+    tp_group, dp_group = make_tp_dp_groups(tp_size)
+    replicas, replica = world // tp_size, rank // tp_size
+    tp = TPContext(group=tp_group, mode=a.tp_mode)
     model = TensorParallelDense(full, tp)
     del full
     torch.cuda.empty_cache()
@@ -65,7 +70,9 @@ def main():
     opt = CentroidSteerOptimizer(model, lr=1e-4, grad_clip=1.0)
     build_s = time.time() - t0
 
-    host = torch.randint(0, cfg.vocab_size, (a.batch, a.seq + 1), generator=torch.Generator().manual_seed(1234)).pin_memory()
+    # one batch per replica; the ranks of a tensor-parallel group read the same one
+    host = torch.randint(0, cfg.vocab_size, (a.batch, a.seq + 1),
+                         generator=torch.Generator().manual_seed(1234 + replica)).pin_memory()
     n_valid = a.batch * a.seq
 
     def step():
@@ -73,6 +80,7 @@ def main():
         loss = model.forward_loss(ids[:, :-1], ids[:, 1:], n_valid=n_valid)
         loss.backward()
         model.allreduce_replicated_grads()
+        average_grads_over_replicas(model, dp_group)
         opt.step()
         opt.zero_grad()
         return loss
@@ -98,12 +106,12 @@ def main():
     if rank == 0:
         print(json.dumps({
             "metric": "tensor-parallel train tok/s (device-timed, max over ranks)",
-            "value": a.batch * a.seq / float(ms) * 1e3, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
+            "value": a.batch * a.seq * replicas / float(ms) * 1e3, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": float(ms), "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
             "data": "synthetic uniform-random token ids from pinned host memory, random-init weights",
             "config": {"model": a.model, "layers": cfg.num_layers, "hidden_dim": cfg.hidden_dim, "mixer": cfg.mixer,
-                       "params_total": full_params, "params_per_rank": local_params, "global_batch": a.batch,
-                       "seq_len": a.seq, "parallelism": f"tp{world}", "tp_mode": a.tp_mode, "cuda_graph": False},
+                       "params_total": full_params, "params_per_rank": local_params, "global_batch": a.batch * replicas,
+                       "seq_len": a.seq, "parallelism": f"tp{tp_size} x dp{replicas}", "tp_mode": a.tp_mode, "cuda_graph": False},
             "wait_status": int(status), "peak_mem_GB": round(float(mem), 1), "build_s": round(build_s, 1),
             "final_loss": float(total), "impl": "triune_b200",
         }), flush=True)

@@ -293,3 +293,22 @@ def test_context_parallel_gla_matches_whole_sequence_on_gloo():
         for k, v in r.items():
             if k != "rank":
                 assert v < 1e-9, (k, v)
+
+
+def test_tensor_parallel_times_data_parallel_on_gloo():
+    """Four gloo ranks as tensor parallel 2 x data parallel 2: after the tensor-parallel sum of the replicated
+    gradients and the average over replicas, every gradient equals that of the unsharded model on the whole batch."""
+    import json
+    import re
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", "29737", os.path.join(ROOT, "tests", "mp_tp_dp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    dec = json.JSONDecoder()
+    res = [dec.raw_decode(p.stdout, m.end())[0] for m in re.finditer(r"RESULT (?=\{)", p.stdout)]
+    assert p.returncode == 0 and len(res) == 4, p.stdout[-2000:] + p.stderr[-2000:]
+    for r in res:
+        for k, v in r.items():
+            if k != "rank":
+                assert v < 1e-4, (k, v)

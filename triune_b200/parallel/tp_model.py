@@ -216,5 +216,51 @@ class TensorParallelDense(nn.Module):
             off += n
 
 
+def make_tp_dp_groups(tp_size: int):
+    """Split the world into tensor-parallel groups of ``tp_size`` consecutive ranks and the data-parallel groups across
+    them (ranks with the same position inside their tensor-parallel group). Every rank must call this. Returns
+    ``(tp_group, dp_group)`` of the calling rank."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if world % tp_size != 0:
+        raise ValueError(f"world size {world} is not a multiple of the tensor-parallel size {tp_size}")
+    tp_group = dp_group = None
+    for start in range(0, world, tp_size):
+        ranks = list(range(start, start + tp_size))
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            tp_group = g
+    for pos in range(tp_size):
+        ranks = list(range(pos, world, tp_size))
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            dp_group = g
+    return tp_group, dp_group
+
+
+@torch.no_grad()
+def average_grads_over_replicas(model: nn.Module, dp_group) -> None:
+    """Data parallelism on top of tensor parallelism: average every gradient over the replicas that hold the same shard
+    (one flat all-reduce). Call after ``allreduce_replicated_grads``."""
+    n = dist.get_world_size(dp_group)
+    if n == 1:
+        return
+    grads = []
+    for p in model.parameters():
+        g = getattr(p, "main_grad", None)
+        g = g if g is not None else p.grad
+        if g is not None:
+            grads.append(g)
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    dist.all_reduce(flat, group=dp_group)
+    flat.div_(n)
+    off = 0
+    for g in grads:
+        k = g.numel()
+        g.copy_(flat[off : off + k].view_as(g).to(g.dtype))
+        off += k
+
+
 def tensor_parallelize(model: UniversalDenseTransformer, tp: TPContext) -> TensorParallelDense:
     return TensorParallelDense(model, tp)
