@@ -114,6 +114,36 @@ def case_gla(a):
     report(f"gla fwd+bwd B{B} T{T} H{H}", ms2, nbytes=2.0 * 14 * B * T * H * D)
 
 
+def case_gdn(a):
+    """Gated DeltaNet: the recurrence kernel (no gradient) and forward + backward of the chunk-parallel training form."""
+    from . import ops
+
+    B, T, H, D = a.batch, a.seq, a.heads, a.head_dim
+    q, k, v, g = (torch.randn(B, T, H, D, device="cuda").to(torch.bfloat16) for _ in range(4))
+    k = torch.nn.functional.normalize(k.float(), dim=-1).to(torch.bfloat16)
+    beta = torch.rand(B, T, H, device="cuda")
+
+    def infer():
+        with torch.no_grad():
+            ops.gated_deltanet(q, k, v, g, beta=beta, gate_logits=True)
+
+    ms = timeit(infer, a.iters, a.warmup)
+    report(f"gdn recurrent kernel B{B} T{T} H{H} D{D}", ms, nbytes=2.0 * 5 * B * T * H * D)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, g)]
+    do = torch.randn_like(q)
+
+    def train():
+        o, _ = ops.gated_deltanet(*leaves, beta=beta, gate_logits=True)
+        o.backward(do)
+        for t in leaves:
+            t.grad = None
+
+    torch.cuda.reset_peak_memory_stats()
+    ms2 = timeit(train, max(1, a.iters // 2), min(a.warmup, 2))
+    out = report(f"gdn chunk-parallel fwd+bwd B{B} T{T} H{H} D{D}", ms2)
+    print(json.dumps({"case": out["case"], "peak_mem_GB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
+
+
 def case_rmsnorm(a):
     from . import ops
 
@@ -193,7 +223,7 @@ def case_nvfp4(a):
     report(f"nvfp4_quantize {N}x{K}", ms, nbytes=N * K * 4.5625)
 
 
-CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "rmsnorm": case_rmsnorm, "ce": case_ce}
+CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():
@@ -205,6 +235,7 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=6)
+    ap.add_argument("--head-dim", type=int, default=64, help="head dimension of the gdn case (64 or 128)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
