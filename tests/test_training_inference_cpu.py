@@ -312,3 +312,36 @@ def test_tensor_parallel_times_data_parallel_on_gloo():
         for k, v in r.items():
             if k != "rank":
                 assert v < 1e-4, (k, v)
+
+
+def test_pipeline_schedule_properties():
+    """1F1B as data: every stage runs each micro-batch forward once and backward once, backward after forward and in
+    order; a stage never holds more than (stages - stage) micro-batches; the layer split covers every layer once."""
+    from triune_b200.parallel.pipeline import one_f_one_b, peak_live_micro_batches, split_layers
+
+    for stages in (1, 2, 3, 4, 8):
+        for micro in (1, 2, 4, 8, 16):
+            for s in range(stages):
+                steps = one_f_one_b(s, stages, micro)
+                assert [i for k, i in steps if k == "F"] == list(range(micro))
+                assert [i for k, i in steps if k == "B"] == list(range(micro))
+                for i in range(micro):
+                    assert steps.index(("F", i)) < steps.index(("B", i))
+                assert peak_live_micro_batches(s, stages, micro) == min(stages - s, micro)
+    assert split_layers(24, 4) == [(0, 6), (6, 12), (12, 18), (18, 24)]
+    assert split_layers(5, 3) == [(0, 2), (2, 4), (4, 5)]
+    b = split_layers(24, 4, weights=[1, 1, 1, 1.5])
+    assert b[0][0] == 0 and b[-1][1] == 24 and all(b[i][1] == b[i + 1][0] for i in range(3))
+    assert b[-1][1] - b[-1][0] < b[0][1] - b[0][0]
+    with pytest.raises(ValueError):
+        split_layers(2, 3)
+
+
+def test_pipeline_parallel_on_gloo():
+    """Three gloo ranks, five layers, four micro-batches: loss and every gradient of every stage equal those of the
+    whole model on the whole batch, two steps in a row, and the number of live micro-batches follows the schedule."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1", PP_MICRO="4")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29741", os.path.join(ROOT, "tests", "mp_pp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0 and "PP_OK 3 4" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]

@@ -22,6 +22,12 @@ _LAZY = {
     "shard_experts": "expert_parallel",
     "allreduce_replicated_grads": "expert_parallel",
     "cp_gla": "context_parallel",
+    "PipelineStage": "pipeline",
+    "PipelineEngine": "pipeline",
+    "pipeline_parallelize": "pipeline",
+    "make_pp_dp_groups": "pipeline",
+    "make_tp_dp_groups": "tp_model",
+    "average_grads_over_replicas": "tp_model",
 }
 
 __all__ = ["DistributedContext", "all_reduce_dict", "all_reduce_tensor", "cleanup_distributed", "max_over_ranks",
