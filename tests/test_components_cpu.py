@@ -519,3 +519,54 @@ def test_expert_parallel_positions_match_one_hot_cumsum():
     want = torch.where(idx >= 0, want, torch.full_like(want, -1))
     assert pos.dtype == torch.int32 and counts.dtype == torch.int32
     assert torch.equal(pos, want) and torch.equal(counts, csum[-1])
+
+
+def test_launcher_starts_reuses_and_stops_the_server(tmp_path):
+    """The launcher starts the API server as a child on a free port, recognises it as its own service on a second call
+    (no second child), moves away from a port held by a foreign program, and stops the child it started."""
+    import socket
+
+    from triune_b200 import desktop
+
+    pytest.importorskip("fastapi")
+    pytest.importorskip("uvicorn")
+    port = desktop.find_free_port(18700, attempts=200)
+    with desktop.start_session(port, startup_timeout=180.0, quiet=True) as first:
+        assert not first.reused and first.port == port and desktop.server_alive(port)
+        again = desktop.start_session(port, quiet=True)
+        assert again.reused and again.proc is None and again.port == port
+        again.stop()  # must not touch the server it did not start
+        assert desktop.server_alive(port)
+    assert first.proc.poll() is not None and not desktop.server_alive(port)
+
+    # a foreign listener on the wanted port: not our service, so the launcher would move on to another port
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        s.listen(1)
+        held = s.getsockname()[1]
+        assert desktop.port_in_use(held) and not desktop.server_alive(held, timeout=0.3)
+        assert desktop.find_free_port(held, attempts=50) != held
+    cmd = desktop.server_command(9001, model="bench-90m", static_dir="web", precision="bf16")
+    assert cmd[1:4] == ["-m", "triune_b200", "serve"] and "--static-dir" in cmd and "9001" in cmd
+
+
+def test_packaging_bundles(tmp_path):
+    """Every platform bundle is generated as plain files with an entry that runs the desktop command; the POSIX
+    launchers are executable and syntactically valid shell."""
+    import subprocess
+
+    from triune_b200.packaging import build_native_targets
+
+    res = build_native_targets("all", out_dir=tmp_path)
+    assert sorted(res) == ["linux", "macos", "windows"]
+    for name, rec in res.items():
+        entry = open(rec["entry"]).read()
+        assert "-m triune_b200 desktop" in entry, name
+    for name in ("linux", "macos"):
+        assert os.access(res[name]["entry"], os.X_OK)
+        assert subprocess.run(["bash", "-n", res[name]["entry"]]).returncode == 0
+    assert os.path.isfile(os.path.join(res["linux"]["bundle"], "triune-b200.desktop"))
+    assert os.path.isfile(os.path.join(res["macos"]["bundle"], "Contents", "Info.plist"))
+    assert build_native_targets("mac", out_dir=tmp_path / "again").keys() == {"macos"}
+    with pytest.raises(ValueError):
+        build_native_targets("amiga", out_dir=tmp_path)

@@ -337,6 +337,21 @@ def cmd_sandbox(a) -> int:
     return 0 if out["success"] else 1
 
 
+def cmd_desktop(a) -> int:
+    from .desktop import launch_desktop_app
+
+    launch_desktop_app(a.port, use_browser=not a.no_browser, host=a.host, model=a.model, static_dir=a.static_dir,
+                       precision=a.precision)
+    return 0
+
+
+def cmd_package(a) -> int:
+    from .packaging import build_native_targets
+
+    _print(build_native_targets(a.target, out_dir=Path(a.out) if a.out else None))
+    return 0
+
+
 # ---------------------------------------------------------------------------------------------------- parser
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="triune_b200", description="Triune on B200: training, serving and model tools")
@@ -510,6 +525,19 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--timeout", type=int, default=10)
     s.add_argument("--memory-mb", type=int, default=256)
     s.set_defaults(fn=cmd_sandbox)
+
+    s = sub.add_parser("desktop", help="start (or reuse) the local server and open its page in the browser")
+    model_args(s, default=None)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--static-dir", default=None)
+    s.add_argument("--no-browser", action="store_true", help="do not open a browser; print the address only")
+    s.set_defaults(fn=cmd_desktop)
+
+    s = sub.add_parser("package", help="generate launcher bundles (Linux AppDir, macOS .app, Windows .cmd)")
+    s.add_argument("--target", default="all", help="linux, macos, windows or all")
+    s.add_argument("--out", default=None, help="output directory (default: dist/ in the source tree)")
+    s.set_defaults(fn=cmd_package)
     return p
 
 
