@@ -66,3 +66,97 @@ def test_training_step_resources_and_sandbox(client):
     assert d["model"]["num_layers"] == 5
     snap = client.get("/v1/playground/neurons").json()
     assert "layer_bins" in snap
+
+
+def test_shell_routes(client, tmp_path):
+    """Product-shell endpoints: DAG execution and single nodes, node catalogue, plugins, system config, datasets,
+    checkpoints (save, export, delete, path confinement), optimizer hyper-parameters, tuning knobs, provider keys."""
+    cat = client.get("/v1/nodes/catalog").json()["nodes"]
+    assert {"constant", "concat_text", "generate"} <= {n["type"] for n in cat}
+    dag = {"nodes": [{"id": "a", "type": "text", "params": {"text": "foo"}}, {"id": "b", "type": "text", "params": {"text": "bar"}},
+                     {"id": "c", "type": "concat_text", "params": {"separator": "-"}}],
+           "edges": [{"from": "a.out", "to": "c.a"}, {"from": "b.out", "to": "c.b"}]}
+    out = client.post("/v1/dag/execute", json={"dag": dag}).json()
+    assert out["outputs"]["c.out"] == "foo-bar" and out["order"][-1] == "c"
+    bad = client.post("/v1/dag/execute", json={"dag": {"nodes": [{"id": "x", "type": "no_such_node"}]}})
+    assert bad.status_code == 422
+    one = client.post("/v1/dag/execute_node", json={"type": "concat_text", "params": {"separator": "+"}, "inputs": {"a": "1", "b": "2"}})
+    assert one.json()["outputs"] == {"out": "1+2"}
+
+    assert client.get("/v1/plugins").json() == {"plugins": []} or isinstance(client.get("/v1/plugins").json()["plugins"], list)
+    assert client.post("/v1/modules/scan_local", json={"directory": str(tmp_path / "none")}).status_code == 404
+    assert client.get("/v1/modules/search").json()["results"] == []
+
+    cfg = client.post("/v1/system/config", json={"plugin_dir": str(tmp_path)}).json()["config"]
+    assert cfg["plugin_dir"] == str(tmp_path)
+    assert client.post("/v1/system/config", json={"nope": 1}).status_code == 400
+
+    data = tmp_path / "corpus.txt"
+    data.write_text("hello world\n" * 10)
+    reg = client.post("/v1/datasets/local/register", json={"path": str(data), "name": "toy"}).json()
+    assert reg["files"] == 1 and reg["bytes"] == data.stat().st_size
+    assert client.post("/v1/datasets/select", json={"name": "toy"}).json()["train_config"]["dataset_path"] == str(data)
+    assert client.get("/v1/datasets").json()["selected"] == "toy"
+    assert client.post("/v1/datasets/select", json={"name": "other"}).status_code == 404
+
+    assert client.post("/v1/training/optimizer", json={"lr": 1e-3}).status_code == 409
+    assert client.post("/v1/checkpoints/export", json={"path": str(tmp_path / "m.safetensors")}).status_code == 409
+    client.post("/v1/models/load", json={"model": "triune-nano", "overrides": TINY})
+    client.post("/v1/training/step", json={"config": {"batch_size": 2, "seq_len": 32}})
+    ch = client.post("/v1/training/optimizer", json={"lr": 5e-4}).json()
+    assert ch["changed"] == {"lr": 5e-4}
+    exp = client.post("/v1/checkpoints/export", json={"path": str(tmp_path / "m.safetensors"), "format": "safetensors"}).json()
+    assert (tmp_path / "m.safetensors").stat().st_size > 1000 and exp["format"] == "safetensors"
+    ck = tmp_path / "ck"
+    client.post("/v1/checkpoints/save", json={"directory": str(ck), "name": "t1"})
+    assert (ck / "t1.pt").is_file()
+    assert client.post("/v1/checkpoints/delete", json={"directory": str(ck), "name": "../m.safetensors"}).status_code in (400, 404)
+    assert (tmp_path / "m.safetensors").is_file()
+    gone = client.post("/v1/checkpoints/delete", json={"directory": str(ck), "name": "t1.pt"}).json()
+    assert not (ck / "t1.pt").exists() and gone["checkpoints"] == []
+
+    knobs = client.post("/v1/hardware/tune", json={"knobs": {"TRIUNE_GEMM_PAIR_MIN_K": 1024}}).json()
+    assert knobs["tuning"]["TRIUNE_GEMM_PAIR_MIN_K"] == "1024"
+    client.post("/v1/hardware/tune", json={"knobs": {"TRIUNE_GEMM_PAIR_MIN_K": None}})
+    assert client.get("/v1/system/config").json()["tuning"]["TRIUNE_GEMM_PAIR_MIN_K"] is None
+    assert client.post("/v1/hardware/tune", json={"knobs": {"PATH": 1}}).status_code == 400
+    saved = client.post("/v1/byok/save", json={"provider": "Example", "api_key": "sk-1234567890"}).json()
+    assert saved["stored"] and "1234567" not in json.dumps(saved)
+    assert client.post("/v1/byok/test", json={"provider": "example"}).json()["configured"]
+    assert "gemm" in client.get("/v1/engine/benchmarks").json()["cases"]
+
+
+def test_agents_and_turbo_mode(client):
+    """Agent endpoints drive the loaded model; turbo mode answers greedy requests through the graph decoder's step
+    function (eager on CPU) with the same tokens as the sampling path at temperature 0."""
+    assert client.post("/v1/agents/run", json={"message": "hi"}).status_code == 409
+    torch.manual_seed(0)
+    client.post("/v1/models/load", json={"model": "triune-nano", "overrides": TINY})
+    p = client.post("/v1/agents/persona", json={"name": "terse", "system_prompt": "Answer briefly.", "temperature": 0.0}).json()
+    assert p["persona"]["name"] == "terse"
+    mem = client.post("/v1/agents/memory", json={"set": {"colour": "green"}}).json()
+    assert mem["items"] == {"colour": "green"}
+    run = client.post("/v1/agents/run", json={"message": "hello", "max_tokens": 4}).json()
+    assert run["persona"] == "terse" and isinstance(run["text"], str)
+    team = client.post("/v1/agents/orchestrate", json={"task": "say hi", "max_tokens": 3}).json()
+    assert [s["agent"] for s in team["steps"]] == ["planner", "worker"]
+    st = client.get("/v1/agents/state").json()
+    assert st["runs"] == 1 and st["memory_items"] == 1 and len(st["tools"]) > 0
+
+    # pure greedy decoding of the same prompt, token by token through the ordinary model call
+    from triune_b200.inference import generate_tokens
+    from triune_b200.serve import get_state
+
+    st = get_state()
+    ids = torch.tensor([st.tokenizer.encode("User: abc\nAssistant:")])
+    want, _, _ = generate_tokens(st.model, ids, 8, temperature=0.0, repetition_penalty=1.0, count_penalty=0.0)
+    body = {"prompt": "abc", "max_tokens": 8, "temperature": 0.0, "repetition_penalty": 1.0}
+    assert client.post("/v1/engine/turbo_mode", json={"enabled": True}).json()["turbo_mode"]
+    out = st.generate("abc", max_new_tokens=8, temperature=0.0, repetition_penalty=1.0)
+    assert out["telemetry"]["turbo"] and out["tokens"] == want
+    turbo = client.post("/v1/chat/completions", json=body).json()
+    assert turbo["usage"]["completion_tokens"] == len(want)
+    sampled = st.generate("abc", max_new_tokens=4, temperature=0.7)  # anything but pure greedy keeps the sampling path
+    assert "turbo" not in sampled["telemetry"]
+    client.post("/v1/engine/turbo_mode", json={"enabled": False})
+    assert "turbo" not in st.generate("abc", max_new_tokens=2, temperature=0.0, repetition_penalty=1.0)["telemetry"]

@@ -85,6 +85,8 @@ class EngineState:
         self.lock = threading.RLock()
         self.telemetry_listeners: List[Callable[[Dict[str, Any]], None]] = []
         self.sessions_meta: Dict[str, Dict[str, Any]] = {}
+        self.turbo_mode = False          # greedy requests without a session decode through the graph-replayed decoder
+        self._turbo_decoder = None       # (model object, depth) -> GraphedGreedyDecoder, rebuilt when either changes
 
     # ------------------------------------------------------------------ model lifecycle
     def load_model(self, spec: str, tokenizer_path: Optional[str] = None, precision: Optional[str] = None, **overrides) -> Dict[str, Any]:
@@ -130,6 +132,9 @@ class EngineState:
         from ..inference import DEFAULT_STOPS, generate_response
 
         model = self.require_model()
+        if (self.turbo_mode and temperature <= 0 and not session_id and stream_callback is None and not speculative
+                and repetition_penalty == 1.0):
+            return self._generate_turbo(model, prompt, max_new_tokens, decode_depth, stop, template)
         cache = None
         if session_id:
             hit = self.srsm.get_session_cache(session_id, self.device)
@@ -147,6 +152,32 @@ class EngineState:
             meta["last_active"] = time.time()
         out.pop("cache", None)
         return out
+
+    def _generate_turbo(self, model, prompt: str, max_new_tokens: int, decode_depth, stop, template: bool) -> Dict[str, Any]:
+        """Pure greedy decoding with the per-token step replayed from one CUDA graph (eager on CPU): no sampling, no
+        repetition penalty, no per-token callbacks, so the whole answer costs one host synchronisation."""
+        from ..inference import DEFAULT_STOPS, GraphedGreedyDecoder, _cut_at_stop
+
+        with self.lock:
+            key = (id(model), decode_depth)
+            if self._turbo_decoder is None or self._turbo_decoder[0] != key:
+                self._turbo_decoder = (key, GraphedGreedyDecoder(model, 1, decode_depth))
+            dec = self._turbo_decoder[1]
+            text_in = f"User: {prompt}\nAssistant:" if template else prompt
+            ids = torch.tensor([self.tokenizer.encode(text_in)], device=self.device, dtype=torch.long)
+            n = max(1, min(int(max_new_tokens), 8192))
+            t0 = time.perf_counter()
+            dec.prefill(ids)
+            t1 = time.perf_counter()
+            toks = dec.decode(n)[0].tolist()
+            t2 = time.perf_counter()
+        eos = getattr(self.tokenizer, "sep_token_id", getattr(self.tokenizer, "eos_token_id", None))
+        if eos is not None and eos in toks:
+            toks = toks[: toks.index(eos)]
+        text = self.tokenizer.decode(toks)
+        tele = {"turbo": True, "prompt_tokens": int(ids.shape[1]), "ttft_s": t1 - t0, "new_tokens": len(toks),
+                "decode_tok_s": n / max(1e-9, t2 - t1), "graph_replayed": self.device.type == "cuda"}
+        return {"text": _cut_at_stop(text, tuple(stop) if stop else DEFAULT_STOPS), "tokens": toks, "telemetry": tele}
 
     # ------------------------------------------------------------------ training
     def _ensure_trainer(self, cfg: Dict[str, Any]):

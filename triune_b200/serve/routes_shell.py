@@ -1,0 +1,413 @@
+"""Product-shell routes: thin HTTP fronts for components that live elsewhere in the package.
+
+Model discovery (``runtime/model_scanner.py``), the DAG executor and its node catalogue (``execution/dag.py``), plugins
+(``plugins/registry.py``), agents (``agents``), checkpoint housekeeping, dataset registration, kernel benchmarks and the
+in-process tuning knobs. None of these does GPU work of its own. Counterparts in the reference: the route decorators of
+``triune/api/routes.py:3239-8346`` outside the chat / training core (``/v1/models/scan``, ``/v1/system/*``, ``/v1/dag/*``,
+``/v1/nodes/catalog``, ``/v1/plugins*``, ``/v1/modules/*``, ``/v1/agents/*``, ``/v1/checkpoints/{delete,export}``,
+``/v1/datasets*``, ``/v1/engine/{benchmarks,turbo_mode}``, ``/v1/hardware/{tune,autotune}``, ``/v1/training/{optimizer,export}``,
+``/v1/byok/*``). Endpoints whose job is to reach the internet (module search / clone, provider proxying) answer with
+what can be known locally and say so.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import os
+import time
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+from fastapi import APIRouter, HTTPException
+
+from .engine_state import get_state
+
+shell_router = APIRouter()
+
+# Process-wide shell state: small, in memory, reset with the process.
+_SHELL: Dict[str, Any] = {
+    "config": {"default_checkpoint_dir": "checkpoints_full", "plugin_dir": "plugins", "turbo_mode": False},
+    "datasets": {}, "selected_dataset": None, "byok": {}, "registry": None, "agents": None,
+}
+
+# Environment switches that change which kernel variant a launch picks (read at launch time by the extension).
+TUNING_KNOBS = ("TRIUNE_GEMM_BN", "TRIUNE_GEMM_PAIR", "TRIUNE_GEMM_PAIR_MIN_K", "TRIUNE_GEMM_MAX_SPLITS")
+
+
+def _bad(e: Exception, code: int = 400):
+    return HTTPException(code, f"{type(e).__name__}: {e}")
+
+
+def _registry():
+    if _SHELL["registry"] is None:
+        from ..plugins.registry import PluginRegistry
+
+        _SHELL["registry"] = PluginRegistry()
+    return _SHELL["registry"]
+
+
+def _inside(directory: str, name: str) -> Path:
+    """``directory/name`` resolved, refused unless it stays inside ``directory``."""
+    root = Path(directory).resolve()
+    p = (root / name).resolve()
+    if root != p.parent and root not in p.parents:
+        raise ValueError("path escapes the directory")
+    return p
+
+
+# ---------------------------------------------------------------------------------------------------- discovery, config
+@shell_router.get("/v1/models/scan")
+@shell_router.get("/v1/system/scan")
+async def models_scan(roots: Optional[str] = None, max_depth: int = 4):
+    from ..runtime.model_scanner import scan_models
+
+    return await asyncio.to_thread(scan_models, roots.split(os.pathsep) if roots else None, max_depth)
+
+
+@shell_router.get("/v1/system/config")
+async def system_config_get():
+    return {"config": dict(_SHELL["config"]), "tuning": {k: os.environ.get(k) for k in TUNING_KNOBS}}
+
+
+@shell_router.post("/v1/system/config")
+async def system_config_set(body: Dict[str, Any]):
+    unknown = sorted(set(body) - set(_SHELL["config"]))
+    if unknown:
+        raise HTTPException(400, f"unknown configuration keys: {unknown}")
+    _SHELL["config"].update(body)
+    return {"config": dict(_SHELL["config"])}
+
+
+# ---------------------------------------------------------------------------------------------------- DAG, nodes, plugins
+@shell_router.get("/v1/nodes/catalog")
+async def nodes_catalog():
+    from ..execution.dag import node_catalog
+
+    return {"nodes": node_catalog()}
+
+
+@shell_router.post("/v1/dag/execute")
+async def dag_execute(body: Dict[str, Any]):
+    from ..execution.dag import DAGValidationError, execute_dag
+
+    spec = body.get("dag", body)
+    try:
+        out = await asyncio.to_thread(execute_dag, spec, {"state": get_state()})
+    except DAGValidationError as e:
+        raise _bad(e, 422)
+    except Exception as e:
+        raise _bad(e)
+    return _jsonable(out)
+
+
+@shell_router.post("/v1/dag/execute_node")
+async def dag_execute_node(body: Dict[str, Any]):
+    """One node on its own: ``{"type": ..., "params": {...}, "inputs": {port: value}}``; inputs become constant nodes."""
+    from ..execution.dag import execute_dag
+
+    try:
+        nodes = [{"id": "n", "type": body["type"], "params": body.get("params", {})}]
+        edges = []
+        for i, (port, value) in enumerate(sorted((body.get("inputs") or {}).items())):
+            nodes.append({"id": f"in{i}", "type": "constant", "params": {"value": value}})
+            edges.append({"from": f"in{i}.out", "to": f"n.{port}"})
+        out = await asyncio.to_thread(execute_dag, {"nodes": nodes, "edges": edges}, {"state": get_state()})
+    except Exception as e:
+        raise _bad(e)
+    mine = {k.split(".", 1)[1]: v for k, v in out["outputs"].items() if k.startswith("n.")}
+    return {"outputs": _jsonable(mine), "seconds": out["timings"].get("n")}
+
+
+@shell_router.get("/v1/plugins")
+@shell_router.get("/v1/modules/installed")
+async def plugins_list():
+    return {"plugins": _registry().list()}
+
+
+@shell_router.get("/v1/plugins/nodes")
+async def plugins_nodes():
+    return {"nodes": sorted(n for p in _registry().list() for n in p["nodes"])}
+
+
+@shell_router.post("/v1/modules/scan_local")
+async def modules_scan_local(body: Dict[str, Any]):
+    d = str(body.get("directory") or _SHELL["config"]["plugin_dir"])
+    if not Path(d).is_dir():
+        raise HTTPException(404, f"no such directory: {d}")
+    return {"found": [p.name for p in _registry().discover(d)], "plugins": _registry().list()}
+
+
+@shell_router.post("/v1/modules/activate")
+async def modules_activate(body: Dict[str, Any]):
+    from ..plugins.registry import PluginError
+
+    try:
+        info = _registry().load(str(body["name"]))
+    except (PluginError, KeyError) as e:
+        raise _bad(e, 403 if isinstance(e, PluginError) else 400)
+    return {"name": info.name, "loaded": info.loaded, "nodes": info.nodes}
+
+
+@shell_router.get("/v1/modules/search")
+@shell_router.get("/v1/modules/updates")
+async def modules_remote():
+    return {"results": [], "note": "remote module catalogues need network access, which this server does not use"}
+
+
+def _jsonable(x: Any, depth: int = 0) -> Any:
+    """Tensors and other rich values become short descriptions so that any DAG output can be returned as JSON."""
+    if depth > 6:
+        return repr(x)[:200]
+    if isinstance(x, (str, int, float, bool)) or x is None:
+        return x
+    if isinstance(x, dict):
+        return {str(k): _jsonable(v, depth + 1) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_jsonable(v, depth + 1) for v in x]
+    shape = getattr(x, "shape", None)
+    if shape is not None and hasattr(x, "dtype"):
+        return {"tensor": list(shape), "dtype": str(x.dtype)}
+    return repr(x)[:200]
+
+
+# ---------------------------------------------------------------------------------------------------- agents
+def _agents() -> Dict[str, Any]:
+    if _SHELL["agents"] is None:
+        from ..agents import AgentMemory, Persona, build_integrated_toolbelt
+
+        _SHELL["agents"] = {"memory": AgentMemory(), "persona": Persona(), "tools": build_integrated_toolbelt(), "runs": 0}
+    return _SHELL["agents"]
+
+
+def _agent(persona=None, max_tokens: int = 256):
+    from ..agents import Agent
+
+    a, st = _agents(), get_state()
+    pers = persona or a["persona"]
+
+    def generate(prompt: str) -> str:
+        return st.generate(prompt, max_new_tokens=max_tokens, temperature=pers.temperature, template=False)["text"]
+
+    return Agent(generate, pers, a["tools"], a["memory"])
+
+
+@shell_router.get("/v1/agents/state")
+async def agents_state():
+    a = _agents()
+    return {"persona": vars(a["persona"]), "tools": a["tools"].describe(), "memory_items": len(a["memory"].items), "runs": a["runs"]}
+
+
+@shell_router.get("/v1/agents/memory")
+async def agents_memory_get():
+    return {"items": _jsonable(_agents()["memory"].items)}
+
+
+@shell_router.post("/v1/agents/memory")
+async def agents_memory_set(body: Dict[str, Any]):
+    mem = _agents()["memory"]
+    if body.get("clear"):
+        mem.clear()
+    for k in body.get("delete", []):
+        mem.delete(str(k))
+    for k, v in (body.get("set") or {}).items():
+        mem.set(str(k), v)
+    return {"items": _jsonable(mem.items)}
+
+
+@shell_router.post("/v1/agents/persona")
+async def agents_persona(body: Dict[str, Any]):
+    from ..agents import Persona
+
+    cur = _agents()["persona"]
+    _agents()["persona"] = Persona(str(body.get("name", cur.name)), str(body.get("system_prompt", cur.system_prompt)),
+                                   float(body.get("temperature", cur.temperature)))
+    return {"persona": vars(_agents()["persona"])}
+
+
+@shell_router.post("/v1/agents/run")
+async def agents_run(body: Dict[str, Any]):
+    try:
+        get_state().require_model()
+        out = await asyncio.to_thread(_agent(max_tokens=int(body.get("max_tokens", 256))).run, str(body.get("message", "")))
+    except RuntimeError as e:
+        raise _bad(e, 409)
+    _agents()["runs"] += 1
+    return _jsonable(out)
+
+
+@shell_router.post("/v1/agents/orchestrate")
+async def agents_orchestrate(body: Dict[str, Any]):
+    """``{"task": ..., "agents": [{"name", "system_prompt"}...]}``: the agents answer in turn, each seeing the previous one."""
+    from ..agents import MultiAgentOrchestrator, Persona
+
+    specs = body.get("agents") or [{"name": "planner", "system_prompt": "Break the task into steps."},
+                                   {"name": "worker", "system_prompt": "Carry out the steps and answer."}]
+    try:
+        get_state().require_model()
+        team = {str(s["name"]): _agent(Persona(str(s["name"]), str(s.get("system_prompt", "")), float(s.get("temperature", 0.7))),
+                                       int(body.get("max_tokens", 256))) for s in specs}
+        out = await asyncio.to_thread(MultiAgentOrchestrator(team).run, str(body.get("task", "")))
+    except RuntimeError as e:
+        raise _bad(e, 409)
+    return {"steps": _jsonable(out)}
+
+
+# ---------------------------------------------------------------------------------------------------- checkpoints, export
+@shell_router.post("/v1/checkpoints/delete")
+async def checkpoints_delete(body: Dict[str, Any]):
+    d = str(body.get("directory") or _SHELL["config"]["default_checkpoint_dir"])
+    try:
+        p = _inside(d, str(body["name"]))
+    except (KeyError, ValueError) as e:
+        raise _bad(e)
+    if p.suffix != ".pt" or not p.is_file():
+        raise HTTPException(404, f"no checkpoint {p.name!r} in {d}")
+    p.unlink()
+    return {"deleted": str(p), "checkpoints": get_state().list_checkpoints(d)}
+
+
+@shell_router.post("/v1/checkpoints/export")
+@shell_router.post("/v1/training/export")
+async def checkpoints_export(body: Dict[str, Any]):
+    """Write the loaded model as ``format`` (safetensors, hf or pt) to ``path``."""
+    from ..export.exporter import export_model
+
+    try:
+        model = get_state().require_model()
+        out = await asyncio.to_thread(export_model, model, str(body["path"]), str(body.get("format", "safetensors")))
+    except RuntimeError as e:
+        raise _bad(e, 409)
+    except Exception as e:
+        raise _bad(e)
+    return {"path": str(out), "format": body.get("format", "safetensors")}
+
+
+@shell_router.post("/v1/training/optimizer")
+async def training_optimizer(body: Dict[str, Any]):
+    """Change hyper-parameters of the live optimizer (``lr``, ``weight_decay``) without rebuilding it."""
+    tr = get_state().trainer
+    if tr is None:
+        raise HTTPException(409, "no training run exists; POST /v1/training/start or /v1/training/step first")
+    changed = {}
+    for group in tr.optimizer.param_groups:
+        for key in ("lr", "weight_decay"):
+            if key in body and key in group:
+                group[key] = float(body[key])
+                changed[key] = float(body[key])
+    return {"changed": changed, "groups": len(tr.optimizer.param_groups)}
+
+
+# ---------------------------------------------------------------------------------------------------- datasets
+@shell_router.get("/v1/datasets")
+async def datasets_list():
+    return {"datasets": list(_SHELL["datasets"].values()), "selected": _SHELL["selected_dataset"]}
+
+
+@shell_router.post("/v1/datasets/local/register")
+async def datasets_register(body: Dict[str, Any]):
+    p = Path(str(body.get("path", "")))
+    if not p.exists():
+        raise HTTPException(404, f"no such file or directory: {p}")
+    files = [p] if p.is_file() else sorted(f for f in p.rglob("*") if f.suffix in (".jsonl", ".txt", ".parquet"))
+    if not files:
+        raise HTTPException(400, "no .jsonl, .txt or .parquet files there")
+    name = str(body.get("name") or p.stem)
+    _SHELL["datasets"][name] = {"name": name, "path": str(p), "files": len(files), "bytes": sum(f.stat().st_size for f in files),
+                                "registered": time.time()}
+    return _SHELL["datasets"][name]
+
+
+@shell_router.post("/v1/datasets/select")
+async def datasets_select(body: Dict[str, Any]):
+    name = str(body.get("name", ""))
+    if name not in _SHELL["datasets"]:
+        raise HTTPException(404, f"unknown dataset {name!r}")
+    _SHELL["selected_dataset"] = name
+    return {"selected": name, "train_config": {"dataset_path": _SHELL["datasets"][name]["path"]}}
+
+
+@shell_router.get("/v1/datasets/stream/status")
+async def datasets_stream_status():
+    return {"connected": False, "note": "streaming from remote hubs needs network access, which this server does not use"}
+
+
+# ---------------------------------------------------------------------------------------------------- engine, hardware
+@shell_router.post("/v1/engine/turbo_mode")
+async def engine_turbo(body: Dict[str, Any]):
+    """Turbo mode: greedy requests (temperature 0, repetition penalty 1, no session, no streaming) decode through the
+    graph-replayed decoder (pure arg-max: no repetition or count penalty); every other request keeps the sampling path."""
+    st = get_state()
+    st.turbo_mode = bool(body.get("enabled", True))
+    _SHELL["config"]["turbo_mode"] = st.turbo_mode
+    return {"turbo_mode": st.turbo_mode}
+
+
+@shell_router.get("/v1/engine/benchmarks")
+async def engine_benchmarks():
+    """What can be measured from here, and the peaks measurements are compared against."""
+    from .. import bench_kernels
+
+    return {"cases": sorted(bench_kernels.CASES), "peaks": bench_kernels.peaks(),
+            "how": "POST /v1/engine/benchmarks {\"case\": name, ...sizes} runs one case on the server's GPU"}
+
+
+@shell_router.post("/v1/engine/benchmarks")
+async def engine_benchmark_run(body: Dict[str, Any]):
+    import argparse
+
+    import torch
+
+    from .. import bench_kernels
+
+    case = str(body.get("case", ""))
+    if case not in bench_kernels.CASES:
+        raise HTTPException(404, f"unknown case {case!r}; one of {sorted(bench_kernels.CASES)}")
+    if not torch.cuda.is_available():
+        raise HTTPException(409, "kernel benchmarks need a CUDA device")
+    a = argparse.Namespace(m=8192, n=8192, k=8192, batch=16, seq=2048, heads=6, head_dim=64, iters=5, warmup=3)
+    for k, v in body.items():
+        if hasattr(a, k):
+            setattr(a, k, int(v))
+    import contextlib
+    import io
+    import json as _json
+
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        await asyncio.to_thread(bench_kernels.CASES[case], a)
+    return {"results": [_json.loads(l) for l in buf.getvalue().splitlines() if l.startswith("{")]}
+
+
+@shell_router.post("/v1/hardware/tune")
+@shell_router.post("/v1/hardware/autotune")
+async def hardware_tune(body: Dict[str, Any]):
+    """Set the in-process kernel-selection switches. This never touches clocks, power limits or any other device
+    setting: those belong to the machine's operator."""
+    changed = {}
+    for k, v in (body.get("knobs") or {}).items():
+        if k not in TUNING_KNOBS:
+            raise HTTPException(400, f"unknown knob {k!r}; one of {list(TUNING_KNOBS)}")
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = str(int(v))
+        changed[k] = os.environ.get(k)
+    return {"changed": changed, "tuning": {k: os.environ.get(k) for k in TUNING_KNOBS}}
+
+
+# ---------------------------------------------------------------------------------------------------- provider keys
+@shell_router.post("/v1/byok/save")
+async def byok_save(body: Dict[str, Any]):
+    """Keep a provider key in this process's memory (never written to disk, never echoed back)."""
+    provider, key = str(body.get("provider", "")).strip().lower(), str(body.get("api_key", ""))
+    if not provider or len(key) < 8:
+        raise HTTPException(400, "provider and an api_key of at least 8 characters are required")
+    _SHELL["byok"][provider] = key
+    return {"provider": provider, "stored": True, "hint": f"...{key[-4:]}"}
+
+
+@shell_router.post("/v1/byok/test")
+async def byok_test(body: Dict[str, Any]):
+    provider = str(body.get("provider", "")).strip().lower()
+    return {"provider": provider, "configured": provider in _SHELL["byok"], "reachable": None,
+            "note": "this server makes no outbound requests; only the presence of a key is reported"}

@@ -51,6 +51,9 @@ def create_app(static_dir: Optional[str] = None):
         return await call_next(request)
 
     app.include_router(router)
+    from .routes_shell import shell_router
+
+    app.include_router(shell_router)
     root = Path(static_dir) if static_dir else None
     if root is not None and root.is_dir() and (root / "index.html").is_file():
         from fastapi.staticfiles import StaticFiles
