@@ -345,3 +345,36 @@ def test_pipeline_parallel_on_gloo():
            "--master-port", "29741", os.path.join(ROOT, "tests", "mp_pp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0 and "PP_OK 3 4" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def test_rescue_checkpoint_stages():
+    """Continuation rescue: on learnable synthetic data the three stages lower the loss of every exit, the report
+    carries before / per-stage / after metrics, block packing keeps separators and drops the ragged tail."""
+    from triune_b200.config import ModelConfig
+    from triune_b200.models import TriuneTransformer
+    from triune_b200.trainer.rescue import cosine_lr, evaluate_all_depths, pack_blocks, rescue_checkpoint
+
+    blocks = pack_blocks([[1, 2, 3], [4, 5, 6, 7], [8]], seq_len=3, sep_id=0)
+    assert blocks.shape == (2, 4) and blocks[0].tolist() == [1, 2, 3, 0]
+    assert cosine_lr(0, 100, 10, 1.0, 0.1) == pytest.approx(0.1) and cosine_lr(99, 100, 10, 1.0, 0.1) < 0.11
+    assert cosine_lr(10, 100, 10, 1.0, 0.1) == pytest.approx(1.0)
+
+    torch.manual_seed(0)
+    V, T = 32, 24
+    cfg = ModelConfig(vocab_size=V, hidden_dim=32, num_layers=5, num_heads=2, head_dim=16, num_experts=2, reflex_exit_layer=2,
+                      limbic_exit_layer=3, router_prefix_layers=1)
+    model = TriuneTransformer.from_config(cfg)
+    start = torch.randint(0, V, (96, 1))
+    seq = [start]
+    for _ in range(T):
+        seq.append((seq[-1] * 5 + 3) % V)  # a fixed next-token rule: learnable by every exit
+    data = torch.cat(seq, dim=1)
+    train, val = data[:80], data[80:]
+    before = evaluate_all_depths(model, val)
+    rep = rescue_checkpoint(model, train, val, deepen_steps=30, align_steps=10, joint_steps=10, lr=3e-3, batch_size=8)
+    assert set(rep["stages"]) == {"deepen", "align", "joint"} and rep["tokens_trained"] == 50 * 8 * T
+    assert rep["before"]["cortex"]["loss"] == pytest.approx(before["cortex"]["loss"])
+    assert rep["after"]["cortex"]["loss"] < before["cortex"]["loss"] - 0.5
+    assert rep["stages"]["align"]["val"]["reflex"]["loss"] < rep["stages"]["deepen"]["val"]["reflex"]["loss"]
+    assert all(rep["improved"][n] > 0 for n in ("reflex", "limbic", "cortex"))
+    assert rep["config_update"]["depth_mode"] == "joint" and all(p.requires_grad for p in model.parameters())

@@ -337,6 +337,41 @@ def cmd_sandbox(a) -> int:
     return 0 if out["success"] else 1
 
 
+def cmd_rescue(a) -> int:
+    """Continuation training that makes loss monotone in exit depth again; writes the repaired checkpoint and a report."""
+    import torch
+
+    from .trainer import checkpoint as ckpt
+    from .trainer.rescue import load_documents, pack_blocks, rescue_checkpoint
+
+    st = _load_for_inference(a)
+    model, tok = st.model, st.tokenizer
+    if not hasattr(model, "exit_losses"):
+        print("rescue needs a model with early exits (the Triune transformer family)", file=sys.stderr)
+        return 2
+    sep = getattr(tok, "sep_token_id", None)
+    val_docs = load_documents(a.data, tok, a.val_docs + (0 if a.train_data else a.train_docs))
+    if a.train_data:
+        train_docs = load_documents(a.train_data, tok, a.train_docs)
+    else:  # one corpus: the first documents are held out, the rest train
+        val_docs, train_docs = val_docs[: a.val_docs], val_docs[a.val_docs:]
+    train, val = pack_blocks(train_docs, a.seq_len, sep), pack_blocks(val_docs, a.seq_len, sep)
+    if len(val) == 0 or len(train) < a.batch_size:
+        print(f"not enough data: {len(train)} training and {len(val)} validation blocks of {a.seq_len} tokens", file=sys.stderr)
+        return 2
+    model.float() if st.device.type == "cpu" else None
+    rep = rescue_checkpoint(model, train, val, a.deepen_steps, a.align_steps, a.joint_steps, a.lr, a.batch_size, a.accum,
+                            eval_every=a.eval_every, log=lambda m: print(f"[rescue] {m}", flush=True))
+    cfg = model.cfg.to_dict() if hasattr(getattr(model, "cfg", None), "to_dict") else {}
+    cfg.update(rep["config_update"])
+    ckpt.save_checkpoint(a.out, model=model, step=int(st.config.get("step", 0)), loss=rep["after"]["cortex"]["loss"], config=cfg)
+    if a.report:
+        Path(a.report).parent.mkdir(parents=True, exist_ok=True)
+        Path(a.report).write_text(json.dumps(rep, indent=2, default=str))
+    _print({"checkpoint": a.out, "before": rep["before"], "after": rep["after"], "monotone": rep["after"]["monotone"]})
+    return 0
+
+
 def cmd_desktop(a) -> int:
     from .desktop import launch_desktop_app
 
@@ -525,6 +560,24 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--timeout", type=int, default=10)
     s.add_argument("--memory-mb", type=int, default=256)
     s.set_defaults(fn=cmd_sandbox)
+
+    s = sub.add_parser("rescue", help="continuation training that repairs a starved deep exit (deepen, align, joint)")
+    model_args(s)
+    s.add_argument("--data", required=True, help=".jsonl (text field) or plain text; validation comes from here")
+    s.add_argument("--train-data", default=None, help="separate training corpus (default: the rest of --data)")
+    s.add_argument("--out", required=True, help="where to write the repaired checkpoint")
+    s.add_argument("--report", default=None, help="optional JSON report path")
+    s.add_argument("--train-docs", type=int, default=7500)
+    s.add_argument("--val-docs", type=int, default=500)
+    s.add_argument("--seq-len", type=int, default=512)
+    s.add_argument("--batch-size", type=int, default=8)
+    s.add_argument("--accum", type=int, default=1)
+    s.add_argument("--deepen-steps", type=int, default=3500)
+    s.add_argument("--align-steps", type=int, default=300)
+    s.add_argument("--joint-steps", type=int, default=500)
+    s.add_argument("--lr", type=float, default=1e-4)
+    s.add_argument("--eval-every", type=int, default=0)
+    s.set_defaults(fn=cmd_rescue)
 
     s = sub.add_parser("desktop", help="start (or reuse) the local server and open its page in the browser")
     model_args(s, default=None)
