@@ -570,3 +570,21 @@ def test_packaging_bundles(tmp_path):
     assert build_native_targets("mac", out_dir=tmp_path / "again").keys() == {"macos"}
     with pytest.raises(ValueError):
         build_native_targets("amiga", out_dir=tmp_path)
+
+
+def test_mqar_recall_separates_the_mixers():
+    """Analytic associative recall: every mixer answers the plain task; after a key is re-bound only the delta rule is
+    guaranteed to return the fresh value (additive mixers keep the stale one in superposition)."""
+    from triune_b200.evals import mqar
+
+    tokens, answers = mqar.make_task(4, 128, 6, overwrite=True, seed=3)
+    assert tokens.shape == (4, 128) and ((tokens[:, -1] >= mqar.KEYS[0]) & (tokens[:, -1] < mqar.KEYS[1])).all()
+    for b in range(4):  # the queried key occurs twice before the query and its LAST binding is the answer
+        pos = (tokens[b, :-1] == tokens[b, -1]).nonzero().flatten()
+        assert len(pos) == 2 and tokens[b, pos[-1] + 1] == answers[b] and tokens[b, pos[0] + 1] >= mqar.STALE[0]
+    res = {m: mqar.evaluate(m, 128, 6, dim=64, heads=2, batch=8, device="cpu", reps=1, warmup=0) for m in mqar.MIXERS}
+    assert all(r["recall"] == 1.0 for r in res.values()), res
+    assert res["gated_deltanet"]["overwrite_recall"] == 1.0
+    assert res["gla"]["overwrite_recall"] <= 1.0 and res["softmax"]["overwrite_recall"] < 1.0
+    with pytest.raises(ValueError):
+        mqar.make_task(1, 16, 12)
