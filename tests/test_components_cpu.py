@@ -588,3 +588,40 @@ def test_mqar_recall_separates_the_mixers():
     assert res["gla"]["overwrite_recall"] <= 1.0 and res["softmax"]["overwrite_recall"] < 1.0
     with pytest.raises(ValueError):
         mqar.make_task(1, 16, 12)
+
+
+def test_failure_detector_and_status_word():
+    """Heartbeat bookkeeping against a fake store and a fake clock: a rank is overdue only after its counter stood
+    still for longer than the timeout; a moving counter resets it; a never-seen rank counts from construction.
+    A non-zero status word of a fused kernel becomes CollectiveTimeout on the host."""
+    from triune_b200.parallel.elastic import CollectiveTimeout, FailureDetector, RankFailure, raise_on_status
+
+    class Store(dict):
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+        def get(self, k):
+            return str(self[k]).encode()
+
+    now = [0.0]
+    st = Store({"hb/1": 1, "hb/2": 1})
+    det = FailureDetector(st, [1, 2, 3], timeout=2.0, clock=lambda: now[0])
+    assert det.poll() == []
+    now[0] = 1.5
+    st["hb/1"] = 2                        # rank 1 keeps beating, rank 2 stands still, rank 3 never appeared
+    assert det.poll() == []               # nobody has been silent for more than 2 s yet
+    now[0] = 2.5
+    assert det.poll() == [2, 3]           # rank 2 last moved at t=0, rank 3 never did; rank 1 moved at t=1.5
+    now[0] = 3.6
+    assert det.poll() == [1, 2, 3]        # now rank 1 is overdue too ...
+    st["hb/1"] = 3
+    assert det.poll() == [2, 3]           # ... until its next beat
+    st["hb/2"] = 2                        # a late beat revives it
+    assert det.poll() == [3]
+    det.forget([3])
+    assert det.poll() == []
+    raise_on_status(0)
+    with pytest.raises(CollectiveTimeout) as e:
+        raise_on_status(0x30002, "test kernel")
+    assert e.value.status == 0x30002 and "test kernel" in str(e.value)
+    assert RankFailure([2, 1]).dead == [1, 2]

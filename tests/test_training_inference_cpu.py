@@ -378,3 +378,42 @@ def test_rescue_checkpoint_stages():
     assert rep["stages"]["align"]["val"]["reflex"]["loss"] < rep["stages"]["deepen"]["val"]["reflex"]["loss"]
     assert all(rep["improved"][n] > 0 for n in ("reflex", "limbic", "cortex"))
     assert rep["config_update"]["depth_mode"] == "joint" and all(p.requires_grad for p in model.parameters())
+
+
+@pytest.mark.parametrize("victim,mode", [(2, "between"), (0, "midstep")])
+def test_elastic_data_parallel_survives_a_lost_rank(tmp_path, victim, mode):
+    """Three gloo ranks; one leaves without notice (between steps, or when the others are already inside the step's
+    all-reduce; once the lowest rank, which also writes the checkpoints). The survivors detect it by heartbeat or by
+    the process group's timeout, re-form as two ranks, reload the last checkpoint, finish all steps and agree on the
+    weights. The store lives in this process, so it outlives every rank."""
+    import json
+    import re
+
+    from triune_b200.parallel.elastic import connect_store
+    from triune_b200.desktop import find_free_port
+
+    port = find_free_port(29800, attempts=100)
+    store = connect_store("127.0.0.1", port, is_master=True)  # noqa: F841  (kept alive for the workers)
+    env = dict(os.environ, OMP_NUM_THREADS="1", EL_PORT=str(port), EL_WORLD="3", EL_VICTIM=str(victim), EL_DIE_AT="5",
+               EL_MODE=mode, EL_CKPT=str(tmp_path / "ck.pt"), EL_STEPS="8")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_elastic_worker.py")], env=dict(env, EL_IDENT=str(i)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for i in range(3)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=240))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append(p.communicate())
+    assert procs[victim].returncode == 17
+    res = []
+    for i, (p, (so, se)) in enumerate(zip(procs, outs)):
+        if i == victim:
+            continue
+        assert p.returncode == 0, (i, so[-1500:], se[-1500:])
+        res.append(json.loads(re.search(r"RESULT (\{.*\})", so).group(1)))
+    survivors = sorted(set(range(3)) - {victim})
+    for r in res:
+        assert r["steps"] == 8 and r["world"] == 2 and r["members"] == survivors and r["generation"] == 1
+        assert r["failures"] == [[victim]]
+    assert res[0]["w"] == res[1]["w"] and any(abs(v) > 1e-3 for v in res[0]["w"])

@@ -22,6 +22,12 @@ _LAZY = {
     "shard_experts": "expert_parallel",
     "allreduce_replicated_grads": "expert_parallel",
     "cp_gla": "context_parallel",
+    "ElasticGroup": "elastic",
+    "run_elastic": "elastic",
+    "RankFailure": "elastic",
+    "CollectiveTimeout": "elastic",
+    "FailureDetector": "elastic",
+    "Heartbeat": "elastic",
     "PipelineStage": "pipeline",
     "PipelineEngine": "pipeline",
     "pipeline_parallelize": "pipeline",

@@ -66,6 +66,13 @@ class EPContext:
     def check(self) -> int:
         return int(self.status.item())
 
+    def raise_if_failed(self) -> None:
+        """Raise :class:`~triune_b200.parallel.elastic.CollectiveTimeout` when a bounded device-side wait ran out
+        (a peer did not arrive); the CUDA context stays usable. Synchronises."""
+        from .elastic import raise_on_status
+
+        raise_on_status(self.check(), "expert-parallel dispatch / combine")
+
 
 def _positions(idx_flat: torch.Tensor, num_experts: int):
     """Position of every assignment among this rank's assignments to the same expert (in assignment order), and the

@@ -150,3 +150,10 @@ class FusedDPUpdater:
     def check(self) -> int:
         """Status word of the bounded waits (0 = every wait completed). Synchronises."""
         return int(self.status.item())
+
+    def raise_if_failed(self) -> None:
+        """Raise :class:`~triune_b200.parallel.elastic.CollectiveTimeout` when a bounded device-side wait ran out
+        (a peer did not arrive); the CUDA context stays usable. Synchronises."""
+        from .elastic import raise_on_status
+
+        raise_on_status(self.check(), "fused data-parallel reduction")

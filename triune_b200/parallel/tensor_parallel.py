@@ -66,6 +66,13 @@ class TPContext:
     def check(self) -> int:
         return int(self.status.item())
 
+    def raise_if_failed(self) -> None:
+        """Raise :class:`~triune_b200.parallel.elastic.CollectiveTimeout` when a bounded device-side wait ran out
+        (a peer did not arrive); the CUDA context stays usable. Synchronises."""
+        from .elastic import raise_on_status
+
+        raise_on_status(self.check(), "fused tensor-parallel GEMM")
+
 
 # ---------------------------------------------------------------------------------------------------- primitives
 def _ag_gemm_fused(ctx: TPContext, x_shard: torch.Tensor, w: torch.Tensor, b_mn: bool) -> Tuple[torch.Tensor, torch.Tensor]:
