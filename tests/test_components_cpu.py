@@ -625,3 +625,71 @@ def test_failure_detector_and_status_word():
         raise_on_status(0x30002, "test kernel")
     assert e.value.status == 0x30002 and "test kernel" in str(e.value)
     assert RankFailure([2, 1]).dead == [1, 2]
+
+
+def test_dag_component_nodes(tmp_path):
+    """The component node library: a training graph (model -> optimizer -> batch -> step -> perplexity -> checkpoint
+    -> reload), operator nodes on random tensors, inspectors, a nested subgraph; every node type has typed ports."""
+    import torch
+
+    from triune_b200.execution.dag import NODE_TYPES, execute_dag
+
+    assert len(NODE_TYPES) >= 45
+    tiny = dict(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=2, head_dim=16, num_experts=2, reflex_exit_layer=2,
+                limbic_exit_layer=3, router_prefix_layers=1)
+    ck = str(tmp_path / "g.pt")
+    train = {"nodes": [
+        {"id": "m", "type": "load_model", "params": {"model": "triune-nano", "overrides": tiny}},
+        {"id": "opt", "type": "adamw_optimizer", "params": {"lr": 1e-2}},
+        {"id": "data", "type": "synthetic_tokens", "params": {"vocab_size": 64, "batch_size": 2, "seq_len": 16}},
+        {"id": "b", "type": "next_batch"}, {"id": "insp", "type": "token_batch_inspector"},
+        {"id": "step", "type": "training_step"}, {"id": "ppl", "type": "perplexity"},
+        {"id": "joint", "type": "joint_exit_loss"}, {"id": "acc", "type": "gradient_accumulator", "params": {"micro_batches": 2}},
+        {"id": "save", "type": "checkpoint_save", "params": {"path": ck, "step": 1}},
+    ], "edges": [
+        {"from": "m.model", "to": "opt.model"}, {"from": "data.loader", "to": "b.loader"}, {"from": "b.input_ids", "to": "insp.input_ids"},
+        {"from": "opt.model", "to": "step.model"}, {"from": "opt.optimizer", "to": "step.optimizer"},
+        {"from": "b.input_ids", "to": "step.input_ids"}, {"from": "b.labels", "to": "step.labels"},
+        {"from": "step.model", "to": "ppl.model"}, {"from": "b.input_ids", "to": "ppl.input_ids"}, {"from": "b.labels", "to": "ppl.labels"},
+        {"from": "step.model", "to": "joint.model"}, {"from": "b.input_ids", "to": "joint.input_ids"}, {"from": "b.labels", "to": "joint.labels"},
+        {"from": "step.model", "to": "acc.model"}, {"from": "data.loader", "to": "acc.loader"},
+        {"from": "acc.model", "to": "save.model"},
+    ]}
+    out = execute_dag(train)["outputs"]
+    assert out["insp.out"]["shape"] == [2, 16] and out["step.loss"] > 0 and out["ppl.out"]["ppl"] > 1
+    assert len(out["joint.parts"]) == 3 and out["acc.loss"] > 0 and os.path.isfile(ck)
+    re = execute_dag({"nodes": [{"id": "l", "type": "checkpoint_load", "params": {"path": ck}}, {"id": "i", "type": "model_info"}],
+                      "edges": [{"from": "l.model", "to": "i.model"}]})["outputs"]
+    assert re["i.out"]["layers"] == 5
+
+    def rnd(i, shape, scale=1.0):
+        return {"id": i, "type": "random_tensor", "params": {"shape": shape, "seed": len(i), "scale": scale}}
+
+    ops_graph = {"nodes": [rnd("q", [1, 32, 2, 16]), rnd("kk", [1, 32, 2, 16]), rnd("vvv", [1, 32, 2, 16]), rnd("gggg", [1, 32, 2, 16]),
+                           {"id": "gla", "type": "gla"}, {"id": "gdn", "type": "gated_deltanet"}, {"id": "rope", "type": "rope"},
+                           {"id": "norm", "type": "rmsnorm"}, {"id": "see", "type": "tensor_inspector"},
+                           rnd("lg", [8, 6]), {"id": "route", "type": "moe_route", "params": {"top_k": 2}},
+                           {"id": "z", "type": "router_z_loss"}, rnd("w", [32, 64], 0.1), {"id": "fp4", "type": "nvfp4_roundtrip"},
+                           {"id": "lr", "type": "cosine_lr", "params": {"step": 10, "total_steps": 100, "warmup_steps": 10, "lr": 1.0}},
+                           {"id": "hw", "type": "resource_manager"}, {"id": "vram", "type": "vram_profiler"}],
+                 "edges": [{"from": "q.x", "to": "rope.x"}, {"from": "rope.y", "to": "gla.q"}, {"from": "kk.x", "to": "gla.k"},
+                           {"from": "vvv.x", "to": "gla.v"}, {"from": "gggg.x", "to": "gla.g"},
+                           {"from": "q.x", "to": "gdn.q"}, {"from": "kk.x", "to": "gdn.k"}, {"from": "vvv.x", "to": "gdn.v"},
+                           {"from": "gggg.x", "to": "gdn.g"}, {"from": "gla.out", "to": "norm.x"}, {"from": "norm.y", "to": "see.x"},
+                           {"from": "lg.x", "to": "route.logits"}, {"from": "lg.x", "to": "z.logits"}, {"from": "w.x", "to": "fp4.w"}]}
+    o = execute_dag(ops_graph)["outputs"]
+    assert o["see.out"]["shape"] == [1, 32, 2, 16] and o["see.out"]["finite"] and abs(o["see.out"]["std"] - 1.0) < 0.2
+    assert list(o["gdn.state"].shape) == [1, 2, 16, 16] and list(o["route.indices"].shape) == [8, 2]
+    assert float(o["z.loss"]) > 0 and 0 < o["fp4.error"] < 0.2 and o["lr.lr"] == pytest.approx(1.0)
+    assert "available" in o["vram.out"] and isinstance(o["hw.out"], dict)
+
+    inner = {"nodes": [{"id": "input", "type": "constant"}, {"id": "py", "type": "python", "params": {"code": "result = value * 2"}}],
+             "edges": [{"from": "input.out", "to": "py.value"}]}
+    sub = execute_dag({"nodes": [{"id": "c", "type": "constant", "params": {"value": 21}},
+                                 {"id": "s", "type": "subgraph", "params": {"dag": inner, "output": "py.out"}}],
+                       "edges": [{"from": "c.out", "to": "s.value"}]})["outputs"]
+    assert sub["s.out"] == 42
+    for t in NODE_TYPES.values():
+        if "." in t.name:  # nodes that plugins of other tests registered
+            continue
+        assert all(isinstance(v, str) for v in list(t.inputs.values()) + list(t.outputs.values())) and t.description

@@ -227,3 +227,6 @@ def _python(i, p, c):
     if not r["success"]:
         raise RuntimeError(r["error"])
     return {"out": r["result"]}
+
+
+from . import nodes  # noqa: E402,F401  (registers the component nodes)

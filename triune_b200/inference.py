@@ -41,6 +41,8 @@ def infer_config_from_state_dict(sd: Dict[str, torch.Tensor]) -> ModelConfig:
     head_dim = 64 if hd_total % 64 == 0 and (hd_total // 64) * 64 == d and d <= 2048 else 128
     if hd_total % head_dim != 0:
         head_dim = 64
+    while hd_total % head_dim != 0 and head_dim > 1:  # narrow test models: the largest power of two that divides
+        head_dim //= 2
     reflex = exits[0] if exits else max(1, first_moe - 1)
     limbic = exits[1] if len(exits) > 1 else min(layers - 2, reflex + 1)
     return ModelConfig(vocab_size=V, hidden_dim=d, num_layers=layers, num_heads=hd_total // head_dim, head_dim=head_dim,
@@ -61,6 +63,8 @@ def load_checkpoint_model(path: str, device="cpu", dtype: Optional[torch.dtype] 
     sd = ck.get("model_state", ck.get("model", ck)) if isinstance(ck, dict) else ck
     sd = {k.replace("_orig_mod.", ""): v for k, v in sd.items()}
     cfg_dict = ck.get("config") if isinstance(ck, dict) else None
+    if isinstance(ck, dict) and ck.get("architecture") and not (cfg_dict and "hidden_dim" in cfg_dict):
+        cfg_dict = {**ck["architecture"], **(cfg_dict or {})}
     cfg = None
     if cfg_dict and all(k in cfg_dict for k in ("hidden_dim", "num_layers", "num_heads")):
         try:

@@ -135,6 +135,12 @@ class TriuneTransformer(nn.Module):
     @classmethod
     def from_config(cls, cfg: ModelConfig) -> "TriuneTransformer":
         cfg.validate()
+        model = cls._from_validated(cfg)
+        model.model_config = cfg  # plain attribute: checkpoints record the architecture from here
+        return model
+
+    @classmethod
+    def _from_validated(cls, cfg: ModelConfig) -> "TriuneTransformer":
         return cls(
             vocab_size=cfg.vocab_size, hidden_dim=cfg.hidden_dim, num_layers=cfg.num_layers, num_heads=cfg.num_heads,
             head_dim=cfg.head_dim, num_experts=cfg.num_experts, router_prefix_layers=cfg.router_prefix_layers,

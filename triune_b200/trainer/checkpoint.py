@@ -57,12 +57,14 @@ def _plain(v):
 def save_checkpoint(path: str, model, optimizer=None, step: int = 0, loss: float = 0.0, best_eval_loss: float = float("inf"),
                     config: Optional[Dict[str, Any]] = None, depth_usage_ema=None, wandb_run_id=None) -> str:
     config = dict(config or {})
+    arch = getattr(model, "model_config", None)  # the architecture travels with the weights, apart from the run config
+    arch = _plain(arch.to_dict()) if arch is not None and hasattr(arch, "to_dict") else None
     sd = {k.replace("_orig_mod.", ""): v.detach().cpu() for k, v in model.state_dict().items()}
     payload = {
         "step": int(step), "model_state": sd,
         "optimizer_state": _to_cpu(optimizer.state_dict()) if optimizer is not None else None,
         "loss": float(loss), "best_eval_loss": float(best_eval_loss), "config": _plain(config),
-        "schema_version": SCHEMA_VERSION, "fingerprint": fingerprint(config),
+        "schema_version": SCHEMA_VERSION, "fingerprint": fingerprint(config), "architecture": arch,
         "canonical_semantics": canonical_semantics(config),
         "depth_usage_ema": list(depth_usage_ema) if depth_usage_ema is not None else None,
         "wandb_run_id": wandb_run_id,
