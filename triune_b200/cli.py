@@ -372,6 +372,27 @@ def cmd_rescue(a) -> int:
     return 0
 
 
+def cmd_plugin(a) -> int:
+    from .plugins.registry import PluginError, PluginRegistry, create_plugin, write_manifest
+
+    try:
+        if a.action == "create":
+            _print({"created": str(create_plugin(a.dir, a.name, a.key))})
+        elif a.action == "sign":
+            _print(write_manifest(Path(a.dir) / a.name if a.name else a.dir, a.key))
+        else:  # list / verify
+            reg = PluginRegistry(a.key)
+            found = reg.discover(a.dir)
+            if a.action == "verify":
+                for info in found:
+                    reg.verify(info)
+            _print({"plugins": reg.list(), "verified": a.action == "verify"})
+    except PluginError as e:
+        print(f"plugin error: {e}", file=sys.stderr)
+        return 1
+    return 0
+
+
 def cmd_desktop(a) -> int:
     from .desktop import launch_desktop_app
 
@@ -578,6 +599,13 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--lr", type=float, default=1e-4)
     s.add_argument("--eval-every", type=int, default=0)
     s.set_defaults(fn=cmd_rescue)
+
+    s = sub.add_parser("plugin", help="scaffold, sign, list or verify DAG plugins")
+    s.add_argument("action", choices=["create", "sign", "list", "verify"])
+    s.add_argument("--dir", default="plugins", help="directory that holds the plugin directories")
+    s.add_argument("--name", default=None, help="plugin name (create / sign)")
+    s.add_argument("--key", default=None, help="signing key (default: TRIUNE_PLUGIN_KEY)")
+    s.set_defaults(fn=cmd_plugin)
 
     s = sub.add_parser("desktop", help="start (or reuse) the local server and open its page in the browser")
     model_args(s, default=None)

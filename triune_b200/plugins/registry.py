@@ -103,3 +103,47 @@ class PluginRegistry:
     def list(self) -> List[Dict[str, Any]]:
         return [{"name": p.name, "version": p.version, "path": str(p.path), "loaded": p.loaded, "nodes": p.nodes,
                  "signed": bool(p.signature)} for p in self.plugins.values()]
+
+
+_SCAFFOLD = '''"""Plugin {name}: registers DAG nodes. Edit, then re-sign the manifest (the digest covers this file)."""
+
+
+def register(api):
+    @api.register_node("echo", {{"value": "any"}}, {{"out": "any"}}, "returns its input unchanged")
+    def echo(inputs, params, context):
+        return {{"out": inputs.get("value")}}
+'''
+
+
+def write_manifest(plugin_dir, key: Optional[str] = None) -> Dict[str, Any]:
+    """(Re)compute the entry file's digest, sign when a key is given (or configured in ``TRIUNE_PLUGIN_KEY``) and write
+    ``plugin.json``. Run after every edit of the entry file. Same job as the reference's
+    ``scripts/sign_plugin_manifest.py``."""
+    d = Path(plugin_dir)
+    man_path = d / "plugin.json"
+    man = json.loads(man_path.read_text()) if man_path.is_file() else {"name": d.name, "version": "0.1.0", "entry": "plugin.py"}
+    entry = (d / man["entry"]).resolve()
+    if d.resolve() not in entry.parents or not entry.is_file():
+        raise PluginError(f"{man.get('name', d.name)}: entry file {man['entry']!r} is missing or outside the plugin directory")
+    man["sha256"] = file_sha256(entry)
+    key = key if key is not None else os.environ.get("TRIUNE_PLUGIN_KEY") or None
+    if key:
+        man["signature"] = sign_manifest(man["name"], str(man["version"]), man["sha256"], key)
+    else:
+        man.pop("signature", None)
+    man_path.write_text(json.dumps(man, indent=2) + "\n")
+    return man
+
+
+def create_plugin(directory, name: str, key: Optional[str] = None, version: str = "0.1.0") -> Path:
+    """Scaffold ``directory/name`` with an entry file that registers one node, and a (signed) manifest."""
+    if not name.replace("_", "").replace("-", "").isalnum():
+        raise PluginError("plugin names are letters, digits, '-' and '_'")
+    d = Path(directory) / name
+    if d.exists():
+        raise PluginError(f"{d} already exists")
+    d.mkdir(parents=True)
+    (d / "plugin.py").write_text(_SCAFFOLD.format(name=name))
+    (d / "plugin.json").write_text(json.dumps({"name": name, "version": version, "entry": "plugin.py"}))
+    write_manifest(d, key)
+    return d

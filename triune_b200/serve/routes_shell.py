@@ -148,6 +148,19 @@ async def modules_activate(body: Dict[str, Any]):
     return {"name": info.name, "loaded": info.loaded, "nodes": info.nodes}
 
 
+@shell_router.post("/v1/modules/create_plugin")
+async def modules_create_plugin(body: Dict[str, Any]):
+    from ..plugins.registry import PluginError, create_plugin
+
+    d = str(body.get("directory") or _SHELL["config"]["plugin_dir"])
+    try:
+        path = create_plugin(d, str(body.get("name", "")))
+    except PluginError as e:
+        raise _bad(e)
+    _registry().discover(d)
+    return {"created": str(path), "plugins": _registry().list()}
+
+
 @shell_router.get("/v1/modules/search")
 @shell_router.get("/v1/modules/updates")
 async def modules_remote():
