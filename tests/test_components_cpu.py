@@ -729,3 +729,42 @@ def test_plugin_scaffold_sign_load_and_tamper(tmp_path):
         other.verify(other.plugins["scaf"])
     assert cli(["plugin", "verify", "--dir", str(tmp_path), "--key", "secret"]) == 0
     assert cli(["plugin", "verify", "--dir", str(tmp_path), "--key", "nope"]) == 1
+
+
+def test_agent_memory_skills_and_providers(tmp_path):
+    """Lessons are recalled by similarity and survive a reload; skills are parsed from markdown headers and picked by
+    triggers; provider records hide their keys and refuse to send without an injected transport."""
+    from triune_b200.agents import AgentMemoryStore, ProviderManager, SkillLibrary
+
+    path = tmp_path / "mem" / "store.json"
+    mem = AgentMemoryStore(str(path))
+    mem.add_lesson("when the loss is NaN lower the learning rate and check the gate clamp", ["training"])
+    mem.add_lesson("prefill is faster with larger chunks on long prompts", ["serving"])
+    mem.add_lesson("tokenizer files must be saved next to the checkpoint")
+    mem.set_preference("tone", "brief")
+    assert mem.record_tool("http_get", ok=False) == {"calls": 1, "failures": 1}
+    top = mem.recall("my training loss became nan, what about the learning rate?", k=2)
+    assert top and "NaN" in top[0][1] and (len(top) == 1 or top[0][0] >= top[1][0])
+    assert mem.recall("completely unrelated zebra question") == []
+    again = AgentMemoryStore(str(path))
+    assert again.data["preferences"] == {"tone": "brief"} and len(again.data["lessons"]) == 3
+
+    (tmp_path / "skills").mkdir()
+    (tmp_path / "skills" / "ckpt.md").write_text("---\nname: checkpoint-care\ndescription: saving and resuming runs\n"
+                                                 "triggers: resume, save checkpoint\n---\nAlways save the tokenizer too.\n")
+    (tmp_path / "skills" / "plain.md").write_text("Write short answers.\n")
+    lib = SkillLibrary(str(tmp_path / "skills"))
+    assert set(lib.skills) == {"checkpoint-care", "plain"}
+    assert [s.name for s in lib.select("how do I resume my run?")] == ["checkpoint-care"]
+    assert "Always save the tokenizer" in lib.prompt_block("please save checkpoint now")
+    assert lib.select("zebra") == []
+
+    pm = ProviderManager()
+    pm.save("Example", "https://api.example.com/v1/", "m-1", "sk-abcdef123456")
+    assert pm.describe()[0]["key_hint"] == "...3456" and "abcdef" not in json.dumps(pm.describe())
+    with pytest.raises(ValueError):
+        pm.save("bad", "http://evil.example.com", "m", "k")
+    with pytest.raises(RuntimeError):
+        pm.chat("example", [{"role": "user", "content": "hi"}])
+    pm.transport = lambda p, msgs, opt: f"{p.model}:{msgs[-1]['content']}"
+    assert pm.chat("example", [{"role": "user", "content": "hi"}]) == "m-1:hi"

@@ -150,4 +150,7 @@ class MultiAgentOrchestrator:
         return out
 
 
-__all__ = ["Tool", "ToolRegistry", "build_integrated_toolbelt", "is_safe_public_url", "Persona", "AgentMemory", "Agent", "MultiAgentOrchestrator"]
+from .extras import AgentMemoryStore, Provider, ProviderManager, Skill, SkillLibrary  # noqa: E402
+
+__all__ = ["Tool", "ToolRegistry", "build_integrated_toolbelt", "is_safe_public_url", "Persona", "AgentMemory", "Agent", "MultiAgentOrchestrator",
+           "AgentMemoryStore", "SkillLibrary", "Skill", "ProviderManager", "Provider"]
