@@ -14,7 +14,25 @@ from triune_b200.ops import reference as ref  # noqa: E402
 from triune_b200.parallel.context_parallel import cp_gla  # noqa: E402
 
 
+def emulate_kernel_path():
+    """Make the CPU operators look like the CUDA kernels to cp_gla: the local pass returns a state WITHOUT a gradient
+    and the kernel-path branch (decay clamp, analytic state gradient) is taken."""
+    import triune_b200.parallel.context_parallel as cpm
+
+    orig = cpm.ops.gla
+
+    def detached_state(*a, **kw):
+        o, s = orig(*a, **kw)
+        return o, s.detach()
+
+    cpm.ops.gla = detached_state
+    cpm._kernel_path = lambda *a: True
+
+
 def main():
+    emulate = os.environ.get("CP_EMULATE_KERNEL_STATE") == "1"
+    if emulate:
+        emulate_kernel_path()
     dist.init_process_group("gloo")
     r, w = dist.get_rank(), dist.get_world_size()
     torch.manual_seed(11)  # the same full tensors on every rank
@@ -25,6 +43,8 @@ def main():
     k = torch.randn(B, T, H, dk, dtype=dt) * 0.5
     v = torch.randn(B, T, H, dv, dtype=dt)
     x = torch.nn.functional.logsigmoid(torch.randn(B, T, H, dk, dtype=dt) * 2)  # per-dimension log decays
+    if emulate:
+        x = x.clamp(min=-4.5)  # stay above the kernels' clamp so that the unclamped oracle applies
     s0 = torch.randn(B, H, dk, dv, dtype=dt) * 0.1
     do = torch.randn(B, T, H, dv, dtype=dt)
     full = [t.clone().requires_grad_(True) for t in (q, k, v, x)]

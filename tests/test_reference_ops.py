@@ -167,3 +167,26 @@ def test_moe_capacity_mask_priority():
     w = torch.tensor([[0.2], [0.9], [0.5], [0.1]])
     keep = ref.moe_capacity_mask(idx, w, 2, 2)
     assert keep[:, 0].tolist() == [False, True, True, True]
+
+
+def test_gla_final_state_gradient_matches_autograd():
+    """The analytic gradient of the final state (for kernels that return it without one) equals autograd through the
+    token recurrence, for keys, values, log decays and the initial state."""
+    from triune_b200 import ops
+
+    torch.manual_seed(0)
+    B, T, H, D = 2, 37, 2, 8
+    q, k, v = (torch.randn(B, T, H, D, dtype=torch.float64) for _ in range(3))
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, D, dtype=torch.float64))
+    s0 = torch.randn(B, H, D, D, dtype=torch.float64)
+    for use_s0 in (True, False):
+        a = [t.clone().requires_grad_(True) for t in (k, v, g, s0)]
+        _, sf = ref.gla_recurrent(q, a[0], a[1], a[2], a[3] if use_s0 else None, 1.0)
+        G = torch.randn_like(sf)
+        want = torch.autograd.grad((sf * G).sum(), a[:3] + ([a[3]] if use_s0 else []))
+        b = [t.clone().requires_grad_(True) for t in (k, v, g, s0)]
+        sf2 = ops.gla_final_state_with_grad(b[0], b[1], b[2], b[3] if use_s0 else None, sf.detach())
+        assert torch.equal(sf2, sf.detach())
+        got = torch.autograd.grad((sf2 * G).sum(), b[:3] + ([b[3]] if use_s0 else []))
+        for x, y in zip(want, got):
+            assert (x - y).abs().max() < 1e-10

@@ -275,13 +275,16 @@ def test_tensor_parallel_dense_model_matches_unsharded_on_gloo():
             assert v < 1e-4, (k, v)
 
 
-def test_context_parallel_gla_matches_whole_sequence_on_gloo():
+@pytest.mark.parametrize("kernel_like", [False, True])
+def test_context_parallel_gla_matches_whole_sequence_on_gloo(kernel_like):
     """Three gloo ranks, one sequence segment each: the state hand-off reproduces outputs, final state and all input
-    gradients of the whole-sequence recurrence (fp64), with and without an autograd graph."""
+    gradients of the whole-sequence recurrence (fp64), with and without an autograd graph. ``kernel_like`` makes the
+    local pass return its state without a gradient, as the CUDA kernels do, so the analytic state gradient carries the
+    dependence of later segments on earlier keys, values and decays."""
     import json
     import re
 
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2", CP_EMULATE_KERNEL_STATE="1" if kernel_like else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
            "--master-port", "29735", os.path.join(ROOT, "tests", "mp_cp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)

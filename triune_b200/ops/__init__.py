@@ -390,6 +390,51 @@ def gla_recurrent(q, k, v, g, initial_state=None, scale: float = 1.0):
     return ref.gla_recurrent(q, k, v, g, initial_state, scale)
 
 
+class _FinalStateGradFn(torch.autograd.Function):
+    """Attaches the gradient of a GLA final state to a state that was computed without one.
+
+    S_T = sum_t diag(e^{R_t}) k_t v_t^T + diag(e^{R_0'}) S_0 with R_t = sum_{s>t} g_s (the decay from token t to the end)
+    and R_0' = sum_s g_s. For an incoming gradient G = dL/dS_T:
+
+        dk_t = e^{R_t} * (G v_t)        dv_t = G^T (e^{R_t} * k_t)        dS_0 = diag(e^{R_0'}) G
+        dg_s = sum_{t<s} k_t * dk_t  +  e^{R_0'} * rowsum(S_0 * G)
+
+    which is two batched products and two cumulative sums over the sequence: small next to the attention itself.
+    """
+
+    @staticmethod
+    def forward(ctx, k, v, gl, s0, s_final):
+        ctx.save_for_backward(k, v, gl, s0 if s0 is not None else torch.empty(0, device=k.device))
+        ctx.has_s0 = s0 is not None
+        return s_final.detach().clone()
+
+    @staticmethod
+    def backward(ctx, G):
+        k, v, gl, s0 = ctx.saved_tensors
+        dt = torch.float64 if gl.dtype == torch.float64 else torch.float32
+        G, kf, vf = G.to(dt), k.to(dt), v.to(dt)
+        bcum = torch.cumsum(gl.to(dt), dim=1)                      # [B, T, H, Dk]
+        w = torch.exp(bcum[:, -1:] - bcum)                           # e^{R_t}
+        dk = w * torch.einsum("bhkv,bthv->bthk", G, vf)
+        dv = torch.einsum("bhkv,bthk->bthv", G, w * kf)
+        c = kf * dk
+        dg = torch.cumsum(c, dim=1) - c                              # exclusive prefix sum over t < s
+        ds0 = None
+        if ctx.has_s0:
+            tot = torch.exp(bcum[:, -1])                             # [B, H, Dk]
+            ds0 = (tot.unsqueeze(-1) * G).to(s0.dtype)
+            dg = dg + (tot * (s0.to(dt) * G).sum(-1)).unsqueeze(1)
+        return dk.to(k.dtype), dv.to(v.dtype), dg.to(gl.dtype), ds0, None
+
+
+def gla_final_state_with_grad(k, v, log_decay, initial_state, final_state):
+    """``final_state`` (as returned by the kernels, which carry no gradient for it) with its dependence on ``k``, ``v``,
+    the per-step log decay ``[B, T, H, Dk]`` (already clamped the way the kernel clamps it) and ``initial_state``
+    restored for autograd. Used where the state itself is trained through: context parallelism, truncated
+    back-propagation across segments."""
+    return _FinalStateGradFn.apply(k, v, log_decay, initial_state, final_state)
+
+
 def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0, gate_logits: bool = False,
                    chunk_size: int = 64):
     """Gated DeltaNet over [B,T,H,D] tensors; returns (out, final_state [B,H,Dk,Dv]).

@@ -11,9 +11,9 @@ so each rank runs the chunked kernels ONCE on its own tokens, the ranks exchange
 folds the states of the ranks before it, and the correction is one batched product. This is what makes long prompts
 (the 4 x 16384 prefill shape and beyond) splittable over GPUs without any all-to-all of activations.
 
-On CUDA the local pass uses the tcgen05 kernels, whose final state carries no gradient, so the GPU path serves
-prefill / inference; with CPU tensors (the PyTorch operators) the whole function is differentiable, the collectives
-included. The reference has no sequence parallelism (``triune/model/attention.py:360-572`` runs whole sequences).
+The whole function is differentiable, the collectives included. On CUDA the local pass uses the tcgen05 kernels, whose
+final state carries no gradient of its own; :func:`triune_b200.ops.gla_final_state_with_grad` restores it analytically, so
+gradients flow from later segments back into the keys, values and decays of earlier ones on that path too. The reference has no sequence parallelism (``triune/model/attention.py:360-572`` runs whole sequences).
 """
 
 from __future__ import annotations
@@ -41,6 +41,11 @@ def _gather(t: torch.Tensor, group) -> list:
     return out
 
 
+def _kernel_path(q, k, v, g) -> bool:
+    """Whether the local pass runs the CUDA kernels (which clamp the decay and return the state without a gradient)."""
+    return gla_cuda.supported(q, k, v, g, None)
+
+
 def cp_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, group=None, scale: float = 1.0,
            gate_logits: bool = False, initial_state: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Gated linear attention over a sequence split across ``group``.
@@ -56,8 +61,13 @@ def cp_gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, g
     out0, s_loc = ops.gla(q, k, v, g, initial_state=None, scale=1.0, gate_logits=gate_logits)
     gl = F.logsigmoid(g.to(dt)) if gate_logits else g.to(dt)
     gl = torch.clamp(gl, max=0.0)
-    if gla_cuda.supported(q, k, v, g, None):
+    kernel_path = _kernel_path(q, k, v, g)
+    if kernel_path:
         gl = torch.clamp(gl, min=GLA_MIN_LOG_DECAY)  # the kernels clamp the per-step log decay
+        if torch.is_grad_enabled() and (k.requires_grad or v.requires_grad or g.requires_grad):
+            # the kernels return the state without a gradient; its dependence on k, v and the decays is restored here
+            # (two batched products and two cumulative sums), so the hand-off to later segments can be trained through
+            s_loc = ops.gla_final_state_with_grad(k, v, gl, None, s_loc)
     bcum = torch.cumsum(gl, dim=1)                                   # [B, T, H, dk]
     d_tot = torch.exp(bcum[:, -1])                                   # [B, H, dk]: decay over the whole segment
     s_loc = s_loc.to(dt)
