@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (smoke runs)")
     ap.add_argument("--mixer", default="gla", help="sequence mixer: gla or gated_deltanet")
+    ap.add_argument("--family", default="dense", choices=["dense", "triune"],
+                    help="dense: UniversalDenseTransformer; triune: the multi-exit MoE model at full depth (tied embedding)")
     ap.add_argument("--pp", type=int, default=0, help="pipeline size (default: the whole world); the rest is data parallel")
     ap.add_argument("--head-weight", type=float, default=1.0,
                     help="relative cost of the last stage (> 1 gives it fewer blocks, because it also runs the vocabulary head)")
@@ -40,7 +42,8 @@ def main():
     from triune_b200.models.universal import UniversalDenseTransformer
     from triune_b200.optim import CentroidSteerOptimizer
     from triune_b200.parallel import setup_distributed
-    from triune_b200.parallel.pipeline import PipelineEngine, PipelineStage, make_pp_dp_groups, split_layers
+    from triune_b200.models import TriuneTransformer
+    from triune_b200.parallel.pipeline import PipelineEngine, PipelineStage, TriunePipelineStage, make_pp_dp_groups, split_layers
     from triune_b200.parallel.tp_model import average_grads_over_replicas
 
     ctx = setup_distributed()
@@ -49,7 +52,11 @@ def main():
     cfg = get_model_config(a.model).to_dict()
     if a.layers:
         cfg["num_layers"] = a.layers
-    cfg.update(mixer=a.mixer, tie_embeddings=False)
+    if a.family == "dense":
+        cfg.update(mixer=a.mixer, tie_embeddings=False)
+    elif a.layers:
+        reflex = max(2, a.layers // 4)
+        cfg.update(router_prefix_layers=1, reflex_exit_layer=reflex, limbic_exit_layer=max(reflex + 1, a.layers // 2))
     cfg = ModelConfig.from_dict(cfg)
     pp = a.pp if a.pp > 0 else world
     pp_group, dp_group = make_pp_dp_groups(pp)
@@ -63,11 +70,11 @@ def main():
     torch.set_default_dtype(torch.bfloat16 if cuda else torch.float32)
     try:
         with torch.device(dev):
-            full = UniversalDenseTransformer.from_config(cfg)
+            full = (UniversalDenseTransformer if a.family == "dense" else TriuneTransformer).from_config(cfg)
     finally:
         torch.set_default_dtype(prev)
     full_params = full.num_parameters()
-    stage = PipelineStage(full, stage_idx, pp, bounds)
+    stage = (PipelineStage if a.family == "dense" else TriunePipelineStage)(full, stage_idx, pp, bounds)
     del full
     if cuda:
         torch.cuda.empty_cache()
@@ -120,7 +127,7 @@ def main():
             "dtype": "bf16" if cuda else "fp32", "timer": "cuda events" if cuda else "wall clock (cpu)",
             "data": "synthetic uniform-random token ids, random-init weights",
             "config": {"model": a.model, "layers": cfg.num_layers, "stage_layers": bounds, "hidden_dim": cfg.hidden_dim,
-                       "mixer": cfg.mixer, "params_total": full_params, "params_rank0": local_params,
+                       "family": a.family, "mixer": cfg.mixer if a.family == "dense" else "gla", "params_total": full_params, "params_rank0": local_params,
                        "global_batch": a.batch * replicas, "micro_batches": a.micro, "seq_len": a.seq,
                        "parallelism": f"pp{pp} x dp{replicas}", "schedule": "1F1B", "ideal_bubble_fraction": round(bubble, 3),
                        "cuda_graph": False},

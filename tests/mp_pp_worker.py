@@ -18,13 +18,31 @@ def main():
     from triune_b200.models.universal import UniversalDenseTransformer
     from triune_b200.parallel.pipeline import PipelineEngine, PipelineStage, peak_live_micro_batches
 
-    cfg = ModelConfig(family="universal", vocab_size=96, hidden_dim=32, num_layers=5, num_heads=2, head_dim=16,
-                      mixer="gla", ffn="swiglu", tie_embeddings=False)
-    torch.manual_seed(0)
-    oracle = UniversalDenseTransformer.from_config(cfg).double()
-    torch.manual_seed(0)
-    full = UniversalDenseTransformer.from_config(cfg).double()
-    stage = PipelineStage(full, rank, world)
+    tol = 1e-9
+    if os.environ.get("PP_FAMILY", "dense") == "triune":
+        tol = 1e-6  # the expert router computes its logits in fp32 whatever the model's dtype
+        # the multi-exit MoE family: tied embedding / head across first and last stage, capacity wide enough that the
+        # micro-batches drop no token the whole batch would keep
+        from triune_b200.models import TriuneTransformer
+        from triune_b200.parallel.pipeline import TriunePipelineStage
+
+        cfg = ModelConfig(vocab_size=96, hidden_dim=32, num_layers=6, num_heads=2, head_dim=16, num_experts=4, top_k=2,
+                          reflex_exit_layer=2, limbic_exit_layer=3, router_prefix_layers=1, capacity_multiplier=8.0)
+        torch.manual_seed(0)
+        oracle = TriuneTransformer.from_config(cfg).double()
+        torch.manual_seed(0)
+        full = TriuneTransformer.from_config(cfg).double()
+        stage = TriunePipelineStage(full, rank, world, update_stats=False)
+        oracle_loss = lambda a, b: oracle.forward_loss(a, b, force_depth=2)  # noqa: E731
+    else:
+        cfg = ModelConfig(family="universal", vocab_size=96, hidden_dim=32, num_layers=5, num_heads=2, head_dim=16,
+                          mixer="gla", ffn="swiglu", tie_embeddings=False)
+        torch.manual_seed(0)
+        oracle = UniversalDenseTransformer.from_config(cfg).double()
+        torch.manual_seed(0)
+        full = UniversalDenseTransformer.from_config(cfg).double()
+        stage = PipelineStage(full, rank, world)
+        oracle_loss = oracle.forward_loss
     del full
     eng = PipelineEngine(stage, micro)
 
@@ -36,20 +54,23 @@ def main():
             p.grad = None
         loss = eng.train_step(x, y)
         oracle.zero_grad()
-        ref = oracle.forward_loss(x, y)
+        ref = oracle_loss(x, y)
         ref.backward()
-        assert abs(float(loss) - float(ref.detach())) < 1e-9, (rank, step, float(loss))
+        assert abs(float(loss) - float(ref.detach())) < 1e-6, (rank, step, float(loss), float(ref.detach()))
         want = dict(oracle.named_parameters())
         n = 0
         for name, p in stage.full_names():
+            if want[name].grad is None:  # early-exit heads take no gradient from the full-depth loss
+                assert p.grad is None or float(p.grad.abs().max()) == 0.0, name
+                continue
             assert p.grad is not None, name
             err = (p.grad - want[name].grad).abs().max().item()
-            assert err < 1e-9, (rank, name, err)
+            assert err < tol, (rank, name, err)
             n += 1
         assert n > 0
         assert eng.peak_live == peak_live_micro_batches(rank, world, micro), (eng.peak_live, rank)
     total = eng.clip_grad_norm(1e9)
-    ref_norm = torch.sqrt(sum(p.grad.pow(2).sum() for p in oracle.parameters()))
+    ref_norm = torch.sqrt(sum(p.grad.pow(2).sum() for p in oracle.parameters() if p.grad is not None))
     assert abs(float(total) - float(ref_norm)) < 1e-6 * max(1.0, float(ref_norm)), (float(total), float(ref_norm))
     dist.barrier()
     if rank == 0:

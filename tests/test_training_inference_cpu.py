@@ -340,10 +340,13 @@ def test_pipeline_schedule_properties():
         split_layers(2, 3)
 
 
-def test_pipeline_parallel_on_gloo():
-    """Three gloo ranks, five layers, four micro-batches: loss and every gradient of every stage equal those of the
-    whole model on the whole batch, two steps in a row, and the number of live micro-batches follows the schedule."""
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1", PP_MICRO="4")
+@pytest.mark.parametrize("family", ["dense", "triune"])
+def test_pipeline_parallel_on_gloo(family):
+    """Three gloo ranks, four micro-batches: loss and every gradient of every stage equal those of the whole model on
+    the whole batch, two steps in a row, and the number of live micro-batches follows the schedule. ``triune`` is the
+    multi-exit MoE family, whose tied embedding / head weight lives on the first and the last stage and has its two
+    gradients summed after every step."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1", PP_MICRO="4", PP_FAMILY=family)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
            "--master-port", "29741", os.path.join(ROOT, "tests", "mp_pp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)

@@ -29,6 +29,7 @@ _LAZY = {
     "FailureDetector": "elastic",
     "Heartbeat": "elastic",
     "PipelineStage": "pipeline",
+    "TriunePipelineStage": "pipeline",
     "PipelineEngine": "pipeline",
     "pipeline_parallelize": "pipeline",
     "make_pp_dp_groups": "pipeline",

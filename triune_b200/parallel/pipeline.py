@@ -1,7 +1,9 @@
-"""Pipeline parallelism for the dense model family: contiguous layer ranges per rank, one-forward-one-backward schedule.
+"""Pipeline parallelism for both model families: contiguous layer ranges per rank, one-forward-one-backward schedule.
 
-Rank ``s`` of the pipeline group keeps the blocks ``[lo_s, hi_s)`` of a :class:`UniversalDenseTransformer`; the first
-stage also keeps the token embedding, the last one the final norm and the vocabulary head (fused with the cross
+Rank ``s`` of the pipeline group keeps the blocks ``[lo_s, hi_s)`` of a :class:`UniversalDenseTransformer`
+(:class:`PipelineStage`) or of the multi-exit MoE ``TriuneTransformer`` trained at full depth
+(:class:`TriunePipelineStage`, whose tied embedding / head weight lives on both end stages with summed gradients); the
+first stage also keeps the token embedding, the last one the final norm and the vocabulary head (fused with the cross
 entropy). A step splits the batch into ``micro_batches`` equal micro-batches and runs the classic 1F1B order:
 
     stage s:  (S - s - 1) warm-up forwards | steady pairs of one forward and one backward | the same number of backwards
@@ -99,6 +101,7 @@ class PipelineStage(nn.Module):
         if stages > 1 and getattr(full.cfg, "tie_embeddings", False):
             raise ValueError("pipeline parallelism needs untied embeddings: the table and the head live on different ranks")
         self.cfg = full.cfg
+        self.hidden_dim = full.cfg.hidden_dim
         self.stage, self.stages = stage, stages
         self.bounds = bounds if bounds is not None else split_layers(len(full.layers), stages)
         lo, hi = self.bounds[stage]
@@ -135,6 +138,58 @@ class PipelineStage(nn.Module):
         return ops.linear_cross_entropy(self.norm(x), self.lm_head.weight, labels, n_valid=n_valid)
 
 
+class TriunePipelineStage(nn.Module):
+    """One pipeline rank's part of the multi-exit MoE :class:`TriuneTransformer`, trained at full depth.
+
+    The stage keeps the model object (its layer-running helpers, routing statistics and exit bookkeeping stay in one
+    place) but replaces every block outside ``[lo, hi)`` by an empty module, drops the token embedding on all but the
+    first stage and the final norm / head on all but the last, so only this stage's weights stay allocated. The loss is
+    the full-depth one (``force_depth=2``); early-exit heads that live on this stage's blocks keep their weights and
+    receive no gradient from this loss, exactly as in single-device full-depth training. The tied embedding / head
+    weight exists on the first and on the last stage; see ``tied_weight``.
+    """
+
+    def __init__(self, full: nn.Module, stage: int, stages: int, bounds: Optional[List[Tuple[int, int]]] = None,
+                 update_stats: bool = True):
+        super().__init__()
+        self.stage, self.stages = stage, stages
+        self.hidden_dim = full.hidden_dim
+        self.bounds = bounds if bounds is not None else split_layers(len(full.layers), stages)
+        lo, hi = self.bounds[stage]
+        self.layer_range = (lo, hi)
+        self.is_first, self.is_last = stage == 0, stage == stages - 1
+        self.update_stats = update_stats
+        tied = getattr(full, "final_head", None) is not None and full.final_head.weight is full.token_embed.weight
+        for i in range(len(full.layers)):
+            if not lo <= i < hi:
+                full.layers[i] = nn.Identity()
+        if not self.is_first and not (self.is_last and tied):
+            full.token_embed = None  # (a tied last stage keeps the module: same tensor as the head, same parameter name)
+        if not self.is_last:
+            full.final_norm, full.final_head = None, None
+        if not self.is_first and getattr(full, "router", None) is not None:
+            full.router = None  # the depth router reads the prefix layers, which live on the first stage
+        # The table and the head are one tensor in this family. On two different ranks they become two copies that
+        # start equal and stay equal because the engine sums their gradients after every step (both then take the
+        # same update, under the same parameter name and therefore the same optimizer tier).
+        self.tied_weight = full.token_embed.weight if tied and stages > 1 and (self.is_first or self.is_last) else None
+        self.model = full
+
+    def full_names(self):
+        for name, p in self.model.named_parameters():
+            yield name, p
+
+    def forward(self, x: torch.Tensor, labels: Optional[torch.Tensor] = None, n_valid: Optional[int] = None):
+        m = self.model
+        if self.is_first:
+            x = m.token_embed(x)
+        lo, hi = self.layer_range
+        x, _ = m._run_layers(x, lo, hi, update_stats=self.update_stats)
+        if not self.is_last:
+            return x
+        return ops.linear_cross_entropy(m.final_norm(x), m.final_head.weight, labels, bias=m.final_head.bias, n_valid=n_valid)
+
+
 class PipelineEngine:
     """Runs training steps of a :class:`PipelineStage` under the 1F1B schedule.
 
@@ -144,7 +199,7 @@ class PipelineEngine:
     mean loss over the whole batch.
     """
 
-    def __init__(self, stage_module: PipelineStage, micro_batches: int, group=None):
+    def __init__(self, stage_module: nn.Module, micro_batches: int, group=None):
         self.m = stage_module
         self.group = group if group is not None else dist.group.WORLD
         self.stages = dist.get_world_size(self.group)
@@ -155,7 +210,7 @@ class PipelineEngine:
         ranks = dist.get_process_group_ranks(self.group)
         self.prev_rank = ranks[self.stage - 1] if self.stage > 0 else None
         self.next_rank = ranks[self.stage + 1] if self.stage + 1 < self.stages else None
-        self.last_rank = ranks[-1]
+        self.first_rank, self.last_rank = ranks[0], ranks[-1]
         self.peak_live = 0
 
     # ------------------------------------------------------------------ point-to-point
@@ -190,7 +245,7 @@ class PipelineEngine:
         mb = B // M
         dev = next(m.parameters()).device
         dtype = next(m.parameters()).dtype
-        act_shape = (mb, T, m.cfg.hidden_dim)
+        act_shape = (mb, T, m.hidden_dim)
         ids = input_ids.to(dev).split(mb) if m.is_first else None
         tgt = labels.to(dev).split(mb) if m.is_last else None
         live = deque()  # (input activation or None, output) of forwards whose backward is still to come
@@ -238,10 +293,22 @@ class PipelineEngine:
             grad_in = backward(grad_out)
             if not m.is_first:
                 self._exchange(grad_in, self.prev_rank, None, None)
+        self._sum_tied_gradients()
         loss = loss_sum / M
         if self.stages > 1:
             dist.broadcast(loss, src=self.last_rank, group=self.group)
         return loss
+
+    def _sum_tied_gradients(self) -> None:
+        """First and last stage exchange the gradient of the tied embedding / head weight and add the other's."""
+        w = getattr(self.m, "tied_weight", None)
+        if w is None or self.stages == 1:
+            return
+        if w.grad is None:
+            w.grad = torch.zeros_like(w)
+        other = self.last_rank if self.stage == 0 else self.first_rank
+        got = self._exchange(w.grad, other, torch.empty_like(w.grad), other)
+        w.grad.add_(got)
 
     # ------------------------------------------------------------------ helpers around the optimizer
     @torch.no_grad()
@@ -251,8 +318,11 @@ class PipelineEngine:
         grads = [p.grad for p in self.m.parameters() if p.grad is not None]
         dev = next(self.m.parameters()).device
         sq = torch.zeros((), dtype=torch.float32, device=dev)
-        for g in grads:
-            sq += g.float().pow(2).sum()
+        tied = getattr(self.m, "tied_weight", None)
+        for p in self.m.parameters():
+            if p.grad is None or (p is tied and self.stage != 0):  # the tied weight counts once, on the first stage
+                continue
+            sq += p.grad.float().pow(2).sum()
         if self.stages > 1:
             dist.all_reduce(sq, group=self.group)
         norm = sq.sqrt()
@@ -273,5 +343,6 @@ def make_pp_dp_groups(pp_size: int):
 def pipeline_parallelize(full: nn.Module, micro_batches: int, group=None, bounds=None) -> PipelineEngine:
     """Keep this rank's stage of ``full`` and wrap it in an engine. Drop ``full`` afterwards to free the other stages."""
     group = group if group is not None else dist.group.WORLD
-    stage = PipelineStage(full, dist.get_rank(group), dist.get_world_size(group), bounds)
+    cls = TriunePipelineStage if hasattr(full, "exit_layers") else PipelineStage
+    stage = cls(full, dist.get_rank(group), dist.get_world_size(group), bounds)
     return PipelineEngine(stage, micro_batches, group)
