@@ -423,3 +423,41 @@ def test_elastic_data_parallel_survives_a_lost_rank(tmp_path, victim, mode):
         assert r["steps"] == 8 and r["world"] == 2 and r["members"] == survivors and r["generation"] == 1
         assert r["failures"] == [[victim]]
     assert res[0]["w"] == res[1]["w"] and any(abs(v) > 1e-3 for v in res[0]["w"])
+
+
+def test_elastic_training_command_survives_a_killed_rank(tmp_path):
+    """`triune_b200 train` under the elastic environment, three gloo ranks: one process is killed (by its exact handle)
+    once the first checkpoint exists; the others re-form as two ranks, reload that checkpoint and finish all steps."""
+    import json
+    import re
+    import time
+
+    from triune_b200.desktop import find_free_port
+    from triune_b200.parallel.elastic import connect_store
+
+    port = find_free_port(29900, attempts=100)
+    store = connect_store("127.0.0.1", port, is_master=True)  # noqa: F841
+    ck = tmp_path / "ck"
+    tiny = json.dumps(dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4, reflex_exit_layer=2,
+                           limbic_exit_layer=3, router_prefix_layers=1))
+    cmd = [sys.executable, "-m", "triune_b200", "train", "--model", "triune-nano", "--overrides", tiny, "--batch-size", "2",
+           "--seq-len", "32", "--steps", "60", "--log-every", "5", "--checkpoint-dir", str(ck)]
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=ROOT, TRIUNE_ELASTIC_STORE=f"127.0.0.1:{port}", TRIUNE_ELASTIC_WORLD="3",
+               TRIUNE_ELASTIC_HB_TIMEOUT="1.0", TRIUNE_ELASTIC_PG_TIMEOUT="6.0", TRIUNE_ELASTIC_CKPT_EVERY="2")
+    procs = [subprocess.Popen(cmd, env=dict(env, TRIUNE_ELASTIC_IDENT=str(i)), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+             for i in range(3)]
+    try:
+        end = time.time() + 180
+        while not (ck / "latest.pt").exists() and time.time() < end and all(p.poll() is None for p in procs):
+            time.sleep(0.05)
+        assert (ck / "latest.pt").exists(), "no checkpoint appeared"
+        procs[1].kill()  # this exact child, mid-run and without notice
+        outs = [p.communicate(timeout=300) for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert procs[0].returncode == 0 and procs[2].returncode == 0, (outs[0][1][-1500:], outs[2][1][-1500:])
+    rep = json.loads(outs[0][0][outs[0][0].rindex('{\n  "steps"'):])
+    assert rep["steps"] == 60 and rep["world"] == 2 and rep["members"] == [0, 2] and rep["failures"] == [[1]]
+    assert rep["generation"] == 1 and "world 2" in outs[0][0]

@@ -189,7 +189,73 @@ def cmd_models(a) -> int:
     return 0
 
 
+def _train_elastic(a) -> int:
+    """Data-parallel training that survives lost ranks. Selected by the environment the elastic launcher sets
+    (``TRIUNE_ELASTIC_STORE=host:port``, ``TRIUNE_ELASTIC_IDENT``, ``TRIUNE_ELASTIC_WORLD``). Gradients are reduced with
+    library collectives here: a fused NVLink group is built over a fixed set of peers and cannot lose a member."""
+    import torch
+
+    from .config import build_config
+    from .data import SyntheticTokenSource
+    from .models.zoo import load_model
+    from .optim import CentroidSteerOptimizer
+    from .parallel.data_parallel import ShardedDataParallel
+    from .parallel.dist import DistributedContext
+    from .parallel.elastic import ElasticGroup, run_elastic
+    from .trainer import Trainer
+    from .utils import place_model
+
+    host, _, port = os.environ["TRIUNE_ELASTIC_STORE"].rpartition(":")
+    ident, world = int(os.environ["TRIUNE_ELASTIC_IDENT"]), int(os.environ["TRIUNE_ELASTIC_WORLD"])
+    cuda = torch.cuda.is_available()
+    local = int(os.environ.get("LOCAL_RANK", ident))
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(dev)
+    backend = "nccl" if cuda else "gloo"
+    group = ElasticGroup(host or "127.0.0.1", int(port), ident, world, backend,
+                         hb_timeout=float(os.environ.get("TRIUNE_ELASTIC_HB_TIMEOUT", "3.0")),
+                         pg_timeout=float(os.environ.get("TRIUNE_ELASTIC_PG_TIMEOUT", "30.0")), device_id=dev if cuda else None)
+    over = json.loads(a.overrides) if a.overrides else {}
+    latest = os.path.join(a.checkpoint_dir, "latest.pt")
+    state: Dict[str, Any] = {}
+
+    def build() -> int:
+        """(Re)build everything that depends on the membership, then load the last checkpoint if there is one."""
+        state.pop("tr", None)
+        ctx = DistributedContext(True, group.rank, local, group.world, backend, dev)
+        torch.manual_seed(0)
+        model = place_model(load_model(a.model, **over), dev, _dtype(dev))
+        cfg = build_config({"batch_size": a.batch_size, "seq_len": a.seq_len, "lr": a.lr, "total_steps": a.steps, "depth_mode": a.depth_mode,
+                            "grad_accum_steps": a.grad_accum, "checkpoint_dir": a.checkpoint_dir, "vocab_size": int(model.vocab_size),
+                            "cuda_graph": False})
+        dp = ShardedDataParallel(ctx, mode="nccl") if group.world > 1 else None
+        opt = CentroidSteerOptimizer(model, lr=a.lr, grad_clip=1.0, storage_factory=dp.storage_factory if dp is not None else None)
+        loader = SyntheticTokenSource(int(model.vocab_size), cfg["batch_size"], cfg["seq_len"], seed=group.ident)
+        tr = Trainer(model, cfg, optimizer=opt, train_loader=loader, device=dev, dp=dp)
+        resume_from = latest if os.path.exists(latest) else (a.resume if a.resume and os.path.exists(a.resume) else None)
+        if resume_from:
+            tr.resume(resume_from)
+        state["tr"], state["cfg"] = tr, cfg
+        return int(tr.engine.step)
+
+    def step_fn(step, g):
+        out = state["tr"].engine.step_once()
+        if g.rank == 0 and state["tr"].engine.step % a.log_every == 0:
+            print(f"step {state['tr'].engine.step:6d}  loss {float(out['loss']):.4f}  world {g.world}", flush=True)
+        return float(out["loss"])
+
+    res = run_elastic(group, step_fn, lambda step: state["tr"].save_latest(), build, total_steps=a.steps,
+                      checkpoint_every=max(1, int(os.environ.get("TRIUNE_ELASTIC_CKPT_EVERY", "10"))))
+    if group.rank == 0:
+        _print({k: res[k] for k in ("steps", "world", "members", "generation", "failures")})
+    group.shutdown()
+    return 0
+
+
 def cmd_train(a) -> int:
+    if os.environ.get("TRIUNE_ELASTIC_STORE"):
+        return _train_elastic(a)
     import torch
 
     from .config import build_config

@@ -285,11 +285,45 @@ def run_elastic(group: ElasticGroup, step_fn: Callable[[int, ElasticGroup], floa
             "failures": list(group.failures), "losses": losses}
 
 
+def launch(n: int, command: Sequence[str], host: str = "127.0.0.1", port: int = 0) -> int:
+    """Host the store in this process and start ``n`` copies of ``command`` with the elastic environment set
+    (``TRIUNE_ELASTIC_STORE`` / ``_IDENT`` / ``_WORLD``, ``LOCAL_RANK``). Unlike a rendezvous launcher this one leaves the
+    other children alone when one of them dies. Returns 0 when at least one child finished with exit code 0."""
+    import os
+    import socket
+    import subprocess
+
+    if port == 0:
+        with socket.socket() as s:
+            s.bind((host, 0))
+            port = s.getsockname()[1]
+    store = connect_store(host, port, is_master=True)  # noqa: F841  (the store lives as long as this process)
+    procs = []
+    for i in range(n):
+        env = dict(os.environ, TRIUNE_ELASTIC_STORE=f"{host}:{port}", TRIUNE_ELASTIC_IDENT=str(i), TRIUNE_ELASTIC_WORLD=str(n),
+                   LOCAL_RANK=str(i))
+        procs.append(subprocess.Popen(list(command), env=env))
+    codes = [p.wait() for p in procs]
+    print(f"[elastic] children exited with {codes}", flush=True)
+    return 0 if any(c == 0 for c in codes) else 1
+
+
 if __name__ == "__main__":
     import argparse
+    import sys
 
-    ap = argparse.ArgumentParser(description="stand-alone key-value store for elastic jobs")
-    ap.add_argument("--serve-store", type=int, required=True, metavar="PORT")
+    ap = argparse.ArgumentParser(description="elastic jobs: a stand-alone store, or a launcher of N elastic ranks")
+    ap.add_argument("--serve-store", type=int, default=None, metavar="PORT", help="only host the key-value store")
+    ap.add_argument("--launch", type=int, default=None, metavar="N", help="start N ranks of the command after '--'")
     ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=0)
+    ap.add_argument("command", nargs=argparse.REMAINDER)
     a = ap.parse_args()
+    if a.launch:
+        cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
+        if not cmd:
+            ap.error("give the command to run after '--'")
+        sys.exit(launch(a.launch, cmd, a.host, a.port))
+    if a.serve_store is None:
+        ap.error("one of --serve-store PORT or --launch N -- command")
     serve_store(a.serve_store, a.host)
