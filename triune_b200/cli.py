@@ -438,6 +438,15 @@ def cmd_rescue(a) -> int:
     return 0
 
 
+def cmd_eval(a) -> int:
+    from .evals import mqar
+
+    argv = ["--seq", *[str(t) for t in a.seq], "--dim", str(a.dim), "--heads", str(a.heads), "--batch", str(a.batch)]
+    if a.device:
+        argv += ["--device", a.device]
+    return mqar.main(argv)
+
+
 def cmd_plugin(a) -> int:
     from .plugins.registry import PluginError, PluginRegistry, create_plugin, write_manifest
 
@@ -665,6 +674,15 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--lr", type=float, default=1e-4)
     s.add_argument("--eval-every", type=int, default=0)
     s.set_defaults(fn=cmd_rescue)
+
+    s = sub.add_parser("eval", help="task evaluations of the sequence mixers (associative recall)")
+    s.add_argument("task", choices=["mqar"])
+    s.add_argument("--seq", type=int, nargs="+", default=[256, 512, 1024, 2048])
+    s.add_argument("--dim", type=int, default=256)
+    s.add_argument("--heads", type=int, default=4)
+    s.add_argument("--batch", type=int, default=8)
+    s.add_argument("--device", default=None)
+    s.set_defaults(fn=cmd_eval)
 
     s = sub.add_parser("plugin", help="scaffold, sign, list or verify DAG plugins")
     s.add_argument("action", choices=["create", "sign", "list", "verify"])
