@@ -9,7 +9,7 @@ Categories (the reference groups its suite the same way, `scripts/run_all_benchm
     A  headline training step (bench.py, ours and the reference arm)         1 GPU
     B  serving: prefill 4 x 16384, decode, FP8 / NVFP4 (bench_serving.py)    1 GPU
     C  kernels one at a time (triune_b200.bench_kernels, all cases)          1 GPU
-    D  sequence mixers on associative recall (triune_b200.evals.mqar)        1 GPU (or CPU)
+    D  associative recall of the mixers, 100-step optimizer convergence       1 GPU (or CPU)
     E  multi-GPU: data parallel scaling, expert / tensor / pipeline parallel  2+ GPUs, skipped when there are fewer
     F  layer-streamed training from host memory (bench_streaming.py)         1 GPU
 
@@ -54,6 +54,8 @@ def plan(gpus: int, quick: bool) -> List[Tuple[str, int, int, List[str]]]:
         ("C", 1, 900, [PY, "-m", "triune_b200.bench_kernels", "--case", "gdn", "--batch", "4", "--seq", "8192", "--heads", "16",
                        "--head-dim", "128", "--iters", "4"]),
         ("D", 0, 900, [PY, "-m", "triune_b200.evals.mqar"]),
+        ("D", 0, 900, [PY, "-m", "triune_b200.evals.convergence", "--family", "dense"]),
+        ("D", 0, 900, [PY, "-m", "triune_b200.evals.convergence", "--family", "moe"]),
     ]
     for n in (2, 4, 8):
         p.append(("E", n, 900, torchrun(n, 29500 + n, "bench.py", "--gpus", str(n), "--steps", steps, "--warmup", warm)))
