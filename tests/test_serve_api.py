@@ -160,3 +160,13 @@ def test_agents_and_turbo_mode(client):
     assert "turbo" not in sampled["telemetry"]
     client.post("/v1/engine/turbo_mode", json={"enabled": False})
     assert "turbo" not in st.generate("abc", max_new_tokens=2, temperature=0.0, repetition_penalty=1.0)["telemetry"]
+
+
+def test_adapter_export_and_upgrade_guards(client, tmp_path):
+    """Adapter export re-writes saved LoRA weights; the upgrade endpoints refuse anything that is not a local model."""
+    torch.save({"layers.0.lora_A": torch.randn(4, 8), "layers.0.lora_B": torch.zeros(8, 4)}, tmp_path / "adapter_model.pt")
+    out = client.post("/v1/finetune/export", json={"adapter_path": str(tmp_path), "output_path": str(tmp_path / "a.safetensors")})
+    assert out.status_code == 200 and (tmp_path / "a.safetensors").stat().st_size > 100
+    assert client.post("/v1/finetune/export", json={"adapter_path": str(tmp_path / "missing")}).status_code == 404
+    assert client.post("/v1/models/upgrade_to_triune", json={"source": "org/some-remote-model"}).status_code == 404
+    assert client.post("/v1/models/distill", json={"source": str(tmp_path / "nothing-here")}).status_code == 404

@@ -6,7 +6,7 @@ in-process tuning knobs. None of these does GPU work of its own. Counterparts in
 ``triune/api/routes.py:3239-8346`` outside the chat / training core (``/v1/models/scan``, ``/v1/system/*``, ``/v1/dag/*``,
 ``/v1/nodes/catalog``, ``/v1/plugins*``, ``/v1/modules/*``, ``/v1/agents/*``, ``/v1/checkpoints/{delete,export}``,
 ``/v1/datasets*``, ``/v1/engine/{benchmarks,turbo_mode}``, ``/v1/hardware/{tune,autotune}``, ``/v1/training/{optimizer,export}``,
-``/v1/byok/*``). Endpoints whose job is to reach the internet (module search / clone, provider proxying) answer with
+``/v1/byok/*``, ``/v1/finetune/export``, ``/v1/models/{upgrade_to_triune,distill}``). Endpoints whose job is to reach the internet (module search / clone, provider proxying) answer with
 what can be known locally and say so.
 """
 
@@ -293,6 +293,54 @@ async def checkpoints_export(body: Dict[str, Any]):
     except Exception as e:
         raise _bad(e)
     return {"path": str(out), "format": body.get("format", "safetensors")}
+
+
+@shell_router.post("/v1/finetune/export")
+async def finetune_export(body: Dict[str, Any]):
+    """Re-write a saved adapter as one ``safetensors`` (or ``pt``) file."""
+    from ..trainer.finetune import export_adapter
+
+    try:
+        out = await asyncio.to_thread(export_adapter, str(body["adapter_path"]), body.get("output_path"), str(body.get("format", "safetensors")))
+    except (KeyError, FileNotFoundError) as e:
+        raise _bad(e, 404 if isinstance(e, FileNotFoundError) else 400)
+    return {"path": str(out)}
+
+
+@shell_router.post("/v1/models/upgrade_to_triune")
+@shell_router.post("/v1/models/distill")
+async def models_upgrade(body: Dict[str, Any]):
+    """Turn a local Hugging Face causal LM into a Triune model: ``mode="exits"`` attaches early exits to it,
+    ``mode="native"`` transfers its weights into a native multi-exit MoE student. Local files only."""
+    from ..models.transmuter import transfer_weights_to_native_triune, transmute_hf_to_triune
+
+    src = str(body.get("source", ""))
+    if not src or not Path(src).exists():
+        raise HTTPException(404, f"no local model at {src!r} (this server downloads nothing)")
+
+    def work():
+        import torch
+
+        if str(body.get("mode", "exits")) == "exits":
+            model, meta = transmute_hf_to_triune(src, reflex_ratio=float(body.get("reflex_ratio", 0.25)), rank=int(body.get("rank", 64)),
+                                                 use_jev=bool(body.get("use_jev", True)), device=get_state().device, local_files_only=True)
+        else:
+            from transformers import AutoModelForCausalLM
+
+            teacher = AutoModelForCausalLM.from_pretrained(src, local_files_only=True)
+            model, meta = transfer_weights_to_native_triune(teacher, num_experts=int(body.get("experts", 8)), top_k=int(body.get("top_k", 2)),
+                                                            target_layers=body.get("layers"), target_dim=body.get("dim"),
+                                                            reflex_ratio=float(body.get("reflex_ratio", 0.25)))
+        if body.get("output"):
+            Path(str(body["output"])).parent.mkdir(parents=True, exist_ok=True)
+            torch.save({"model_state": model.state_dict(), "config": {}, "transmute": meta}, str(body["output"]))
+            meta["saved_to"] = str(body["output"])
+        return meta
+
+    try:
+        return _jsonable(await asyncio.to_thread(work))
+    except Exception as e:
+        raise _bad(e)
 
 
 @shell_router.post("/v1/training/optimizer")
