@@ -124,6 +124,14 @@ def test_shell_routes(client, tmp_path):
     assert saved["stored"] and "1234567" not in json.dumps(saved)
     assert client.post("/v1/byok/test", json={"provider": "example"}).json()["configured"]
     assert "gemm" in client.get("/v1/engine/benchmarks").json()["cases"]
+    if not torch.cuda.is_available():  # the timed endpoints start child processes on a GPU; without one they say so
+        assert client.post("/v1/engine/benchmarks", json={"case": "gemm"}).status_code == 409
+        assert client.post("/v1/hardware/autotune", json={"m": 256, "n": 256, "k": 256}).status_code == 409
+        from triune_b200.serve.routes_shell import _kernel_bench
+
+        with pytest.raises(RuntimeError):  # the child runs, finds no GPU, exits non-zero: reported, not swallowed
+            _kernel_bench("gemm", {"m": 256, "n": 256, "k": 256, "iters": 1}, {"TRIUNE_GEMM_PAIR": 0}, timeout=300)
+    assert client.post("/v1/engine/benchmarks", json={"case": "nope"}).status_code == 404
 
 
 def test_agents_and_turbo_mode(client):

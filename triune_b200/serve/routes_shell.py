@@ -412,48 +412,109 @@ async def engine_benchmarks():
             "how": "POST /v1/engine/benchmarks {\"case\": name, ...sizes} runs one case on the server's GPU"}
 
 
-@shell_router.post("/v1/engine/benchmarks")
-async def engine_benchmark_run(body: Dict[str, Any]):
-    import argparse
+_BENCH_SIZES = ("m", "n", "k", "batch", "seq", "heads", "head_dim", "iters", "warmup")
 
+
+def _kernel_bench(case: str, sizes: Dict[str, Any], knobs: Optional[Dict[str, Any]] = None, timeout: float = 600.0) -> List[Dict[str, Any]]:
+    """One case of the kernel benchmark in a CHILD process (the kernel-selection switches are read once per process,
+    so a new setting needs a new process); returns the JSON records it printed."""
+    import json as _json
+    import subprocess
+    import sys
+
+    cmd = [sys.executable, "-m", "triune_b200.bench_kernels", "--case", case]
+    for k in _BENCH_SIZES:
+        if k in sizes:
+            cmd += ["--" + k.replace("_", "-"), str(int(sizes[k]))]
+    env = dict(os.environ)
+    root = str(Path(__file__).resolve().parents[2])
+    env["PYTHONPATH"] = root + (os.pathsep + env["PYTHONPATH"] if env.get("PYTHONPATH") else "")
+    for k, v in (knobs or {}).items():
+        if v is None:
+            env.pop(k, None)
+        else:
+            env[k] = str(int(v))
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    recs = []
+    for line in r.stdout.splitlines():
+        if line.startswith("{"):
+            try:
+                recs.append(_json.loads(line))
+            except ValueError:
+                pass
+    if r.returncode != 0 and not recs:
+        raise RuntimeError(f"benchmark exited with {r.returncode}: {r.stderr[-400:]}")
+    return recs
+
+
+def _need_cuda() -> None:
     import torch
 
+    if not torch.cuda.is_available():
+        raise HTTPException(409, "kernel benchmarks need a CUDA device")
+
+
+@shell_router.post("/v1/engine/benchmarks")
+async def engine_benchmark_run(body: Dict[str, Any]):
     from .. import bench_kernels
 
     case = str(body.get("case", ""))
     if case not in bench_kernels.CASES:
         raise HTTPException(404, f"unknown case {case!r}; one of {sorted(bench_kernels.CASES)}")
-    if not torch.cuda.is_available():
-        raise HTTPException(409, "kernel benchmarks need a CUDA device")
-    a = argparse.Namespace(m=8192, n=8192, k=8192, batch=16, seq=2048, heads=6, head_dim=64, iters=5, warmup=3)
-    for k, v in body.items():
-        if hasattr(a, k):
-            setattr(a, k, int(v))
-    import contextlib
-    import io
-    import json as _json
+    _need_cuda()
+    try:
+        return {"results": await asyncio.to_thread(_kernel_bench, case, body, body.get("knobs"))}
+    except Exception as e:
+        raise _bad(e, 500)
 
-    buf = io.StringIO()
-    with contextlib.redirect_stdout(buf):
-        await asyncio.to_thread(bench_kernels.CASES[case], a)
-    return {"results": [_json.loads(l) for l in buf.getvalue().splitlines() if l.startswith("{")]}
+
+def _check_knobs(knobs: Dict[str, Any]) -> None:
+    for k in knobs:
+        if k not in TUNING_KNOBS:
+            raise HTTPException(400, f"unknown knob {k!r}; one of {list(TUNING_KNOBS)}")
 
 
 @shell_router.post("/v1/hardware/tune")
-@shell_router.post("/v1/hardware/autotune")
 async def hardware_tune(body: Dict[str, Any]):
-    """Set the in-process kernel-selection switches. This never touches clocks, power limits or any other device
+    """Set kernel-selection switches in this server's environment. They are read once per process by the extension,
+    so they apply to processes started from now on (the benchmarks this server runs are such processes) and to this
+    process only if it has not launched a GEMM yet. This never touches clocks, power limits or any other device
     setting: those belong to the machine's operator."""
+    knobs = body.get("knobs") or {}
+    _check_knobs(knobs)
     changed = {}
-    for k, v in (body.get("knobs") or {}).items():
-        if k not in TUNING_KNOBS:
-            raise HTTPException(400, f"unknown knob {k!r}; one of {list(TUNING_KNOBS)}")
+    for k, v in knobs.items():
         if v is None:
             os.environ.pop(k, None)
         else:
             os.environ[k] = str(int(v))
         changed[k] = os.environ.get(k)
     return {"changed": changed, "tuning": {k: os.environ.get(k) for k in TUNING_KNOBS}}
+
+
+@shell_router.post("/v1/hardware/autotune")
+async def hardware_autotune(body: Dict[str, Any]):
+    """Time one GEMM shape under each candidate setting (one child process each) and report the fastest.
+    ``{"m", "n", "k", "candidates": [{knob: value}, ...], "apply": false}``; the default candidates toggle CTA pairs
+    and move their shortest reduction. ``apply`` stores the winner in this server's environment."""
+    _need_cuda()
+    cands = body.get("candidates") or [{}, {"TRIUNE_GEMM_PAIR": 0}, {"TRIUNE_GEMM_PAIR_MIN_K": 384}, {"TRIUNE_GEMM_PAIR_MIN_K": 1536}]
+    for c in cands:
+        _check_knobs(c)
+    sizes = {k: body[k] for k in ("m", "n", "k", "iters", "warmup") if k in body}
+    table = []
+    for c in cands:
+        try:
+            recs = await asyncio.to_thread(_kernel_bench, "gemm", sizes, c)
+            table.append({"knobs": c, "ms": min(r["ms"] for r in recs if "ms" in r), "tflops": max(r.get("tflops", 0.0) for r in recs)})
+        except Exception as e:
+            table.append({"knobs": c, "error": f"{type(e).__name__}: {e}"[:300]})
+    ok = [t for t in table if "ms" in t]
+    best = min(ok, key=lambda t: t["ms"]) if ok else None
+    if best and body.get("apply"):
+        for k, v in best["knobs"].items():
+            os.environ[k] = str(int(v))
+    return {"results": table, "best": best, "applied": bool(best and body.get("apply"))}
 
 
 # ---------------------------------------------------------------------------------------------------- provider keys
