@@ -18,7 +18,13 @@ def main():
     from triune_b200.models.universal import UniversalDenseTransformer
     from triune_b200.parallel.pipeline import PipelineEngine, PipelineStage, peak_live_micro_batches
 
-    tol = 1e-9
+    from triune_b200.parallel.pipeline import make_pp_dp_groups
+    from triune_b200.parallel.tp_model import average_grads_over_replicas
+
+    pp = int(os.environ.get("PP_SIZE", "0")) or world
+    pp_group, dp_group = make_pp_dp_groups(pp)
+    stage_idx, replica, replicas = rank % pp, rank // pp, world // pp
+    tol = 1e-9 if replicas == 1 else 1e-6  # the average over replicas travels as one flat fp32 buffer
     if os.environ.get("PP_FAMILY", "dense") == "triune":
         tol = 1e-6  # the expert router computes its logits in fp32 whatever the model's dtype
         # the multi-exit MoE family: tied embedding / head across first and last stage, capacity wide enough that the
@@ -32,7 +38,7 @@ def main():
         oracle = TriuneTransformer.from_config(cfg).double()
         torch.manual_seed(0)
         full = TriuneTransformer.from_config(cfg).double()
-        stage = TriunePipelineStage(full, rank, world, update_stats=False)
+        stage = TriunePipelineStage(full, stage_idx, pp, update_stats=False)
         oracle_loss = lambda a, b: oracle.forward_loss(a, b, force_depth=2)  # noqa: E731
     else:
         cfg = ModelConfig(family="universal", vocab_size=96, hidden_dim=32, num_layers=5, num_heads=2, head_dim=16,
@@ -41,20 +47,25 @@ def main():
         oracle = UniversalDenseTransformer.from_config(cfg).double()
         torch.manual_seed(0)
         full = UniversalDenseTransformer.from_config(cfg).double()
-        stage = PipelineStage(full, rank, world)
+        stage = PipelineStage(full, stage_idx, pp)
         oracle_loss = oracle.forward_loss
     del full
-    eng = PipelineEngine(stage, micro)
+    eng = PipelineEngine(stage, micro, pp_group)
 
     gen = torch.Generator().manual_seed(7)
-    ids = torch.randint(0, cfg.vocab_size, (8, 17), generator=gen)
-    x, y = ids[:, :-1], ids[:, 1:]
+    ids = torch.randint(0, cfg.vocab_size, (8 * replicas, 17), generator=gen)
+    x_all, y_all = ids[:, :-1], ids[:, 1:]                 # the oracle sees every replica's batch
+    x, y = x_all[8 * replica: 8 * replica + 8], y_all[8 * replica: 8 * replica + 8]
     for step in range(2):  # the second step checks that nothing of the first is left in flight
         for p in stage.parameters():
             p.grad = None
         loss = eng.train_step(x, y)
+        average_grads_over_replicas(stage, dp_group)
+        if replicas > 1:
+            dist.all_reduce(loss, group=dp_group)
+            loss = loss / replicas
         oracle.zero_grad()
-        ref = oracle_loss(x, y)
+        ref = oracle_loss(x_all, y_all)
         ref.backward()
         assert abs(float(loss) - float(ref.detach())) < 1e-6, (rank, step, float(loss), float(ref.detach()))
         want = dict(oracle.named_parameters())
@@ -68,13 +79,13 @@ def main():
             assert err < tol, (rank, name, err)
             n += 1
         assert n > 0
-        assert eng.peak_live == peak_live_micro_batches(rank, world, micro), (eng.peak_live, rank)
+        assert eng.peak_live == peak_live_micro_batches(stage_idx, pp, micro), (eng.peak_live, rank)
     total = eng.clip_grad_norm(1e9)
     ref_norm = torch.sqrt(sum(p.grad.pow(2).sum() for p in oracle.parameters() if p.grad is not None))
     assert abs(float(total) - float(ref_norm)) < 1e-6 * max(1.0, float(ref_norm)), (float(total), float(ref_norm))
     dist.barrier()
     if rank == 0:
-        print("PP_OK", world, micro)
+        print("PP_OK", world, micro, f"pp{pp}xdp{replicas}")
     dist.destroy_process_group()
 
 

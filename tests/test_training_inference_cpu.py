@@ -461,3 +461,13 @@ def test_elastic_training_command_survives_a_killed_rank(tmp_path):
     rep = json.loads(outs[0][0][outs[0][0].rindex('{\n  "steps"'):])
     assert rep["steps"] == 60 and rep["world"] == 2 and rep["members"] == [0, 2] and rep["failures"] == [[1]]
     assert rep["generation"] == 1 and "world 2" in outs[0][0]
+
+
+def test_pipeline_times_data_parallel_on_gloo():
+    """Four gloo ranks as two pipelines of two stages: each pipeline trains its own batch; after the average over the
+    replicas every stage's gradients equal those of the whole model on both batches together."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1", PP_MICRO="4", PP_FAMILY="dense", PP_SIZE="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", "29743", os.path.join(ROOT, "tests", "mp_pp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0 and "PP_OK 4 4 pp2xdp2" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
