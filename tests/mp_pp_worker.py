@@ -80,6 +80,13 @@ def main():
             n += 1
         assert n > 0
         assert eng.peak_live == peak_live_micro_batches(stage_idx, pp, micro), (eng.peak_live, rank)
+    with torch.no_grad():  # forward-only pass through the pipeline against the oracle in eval mode
+        oracle.eval()
+        want_eval = oracle_loss(x, y)
+        oracle.train()
+    got_eval = eng.eval_loss(x, y)
+    assert abs(float(got_eval) - float(want_eval)) < 1e-5, (rank, float(got_eval), float(want_eval))
+    assert stage.training
     total = eng.clip_grad_norm(1e9)
     ref_norm = torch.sqrt(sum(p.grad.pow(2).sum() for p in oracle.parameters() if p.grad is not None))
     assert abs(float(total) - float(ref_norm)) < 1e-6 * max(1.0, float(ref_norm)), (float(total), float(ref_norm))

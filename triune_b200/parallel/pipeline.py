@@ -299,6 +299,36 @@ class PipelineEngine:
             dist.broadcast(loss, src=self.last_rank, group=self.group)
         return loss
 
+    @torch.no_grad()
+    def eval_loss(self, input_ids: torch.Tensor, labels: torch.Tensor, n_valid: Optional[int] = None) -> torch.Tensor:
+        """Forward only (validation): the micro-batches stream through the stages one after another; returns the mean
+        loss on every rank. Nothing is kept between micro-batches, so memory is one micro-batch per stage."""
+        M, m = self.micro_batches, self.m
+        B, T = input_ids.shape
+        if B % M != 0:
+            raise ValueError(f"batch {B} is not a multiple of the number of micro-batches {M}")
+        mb = B // M
+        dev, dtype = next(m.parameters()).device, next(m.parameters()).dtype
+        ids = input_ids.to(dev).split(mb) if m.is_first else None
+        tgt = labels.to(dev).split(mb) if m.is_last else None
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        was = m.training
+        m.eval()
+        try:
+            for i in range(M):
+                x = ids[i] if m.is_first else self._exchange(None, None, self._buffer((mb, T, m.hidden_dim), dtype, dev), self.prev_rank)
+                out = m(x, labels=tgt[i] if m.is_last else None, n_valid=n_valid)
+                if m.is_last:
+                    total += out.float()
+                else:
+                    self._exchange(out, self.next_rank, None, None)
+        finally:
+            m.train(was)
+        total = total / M
+        if self.stages > 1:
+            dist.broadcast(total, src=self.last_rank, group=self.group)
+        return total
+
     def _sum_tied_gradients(self) -> None:
         """First and last stage exchange the gradient of the tied embedding / head weight and add the other's."""
         w = getattr(self.m, "tied_weight", None)
