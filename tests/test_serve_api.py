@@ -115,6 +115,21 @@ def test_shell_routes(client, tmp_path):
     gone = client.post("/v1/checkpoints/delete", json={"directory": str(ck), "name": "t1.pt"}).json()
     assert not (ck / "t1.pt").exists() and gone["checkpoints"] == []
 
+    import time as _time
+
+    for n in ("a1", "a2", "a3"):
+        client.post("/v1/checkpoints/save", json={"directory": str(ck), "name": n})
+        _time.sleep(0.02)
+        assert client.post("/v1/checkpoints/assign_project", json={"directory": str(ck), "name": f"{n}.pt", "project": "runA"}).status_code == 200
+    client.post("/v1/checkpoints/save", json={"directory": str(ck), "name": "loose"})
+    grouped = client.get("/v1/checkpoints/projects", params={"directory": str(ck)}).json()
+    assert [c["name"] for c in grouped["projects"]["runA"]] == ["a1.pt", "a2.pt", "a3.pt"]
+    assert [c["name"] for c in grouped["unassigned"]] == ["loose.pt"]
+    pruned = client.post("/v1/checkpoints/prune_project", json={"directory": str(ck), "project": "runA", "keep": 1}).json()
+    assert pruned["kept"] == ["a3.pt"] and sorted(pruned["deleted"]) == ["a1.pt", "a2.pt"] and (ck / "loose.pt").is_file()
+    assert client.post("/v1/checkpoints/assign_project", json={"directory": str(ck), "name": "../x.pt", "project": "p"}).status_code in (400, 404)
+    assert client.post("/v1/checkpoints/prune_project", json={"directory": str(ck), "project": "nope"}).status_code == 404
+
     knobs = client.post("/v1/hardware/tune", json={"knobs": {"TRIUNE_GEMM_PAIR_MIN_K": 1024}}).json()
     assert knobs["tuning"]["TRIUNE_GEMM_PAIR_MIN_K"] == "1024"
     client.post("/v1/hardware/tune", json={"knobs": {"TRIUNE_GEMM_PAIR_MIN_K": None}})

@@ -4,7 +4,7 @@ Model discovery (``runtime/model_scanner.py``), the DAG executor and its node ca
 (``plugins/registry.py``), agents (``agents``), checkpoint housekeeping, dataset registration, kernel benchmarks and the
 in-process tuning knobs. None of these does GPU work of its own. Counterparts in the reference: the route decorators of
 ``triune/api/routes.py:3239-8346`` outside the chat / training core (``/v1/models/scan``, ``/v1/system/*``, ``/v1/dag/*``,
-``/v1/nodes/catalog``, ``/v1/plugins*``, ``/v1/modules/*``, ``/v1/agents/*``, ``/v1/checkpoints/{delete,export}``,
+``/v1/nodes/catalog``, ``/v1/plugins*``, ``/v1/modules/*``, ``/v1/agents/*``, ``/v1/checkpoints/{delete,export,projects,assign_project,prune_project}``,
 ``/v1/datasets*``, ``/v1/engine/{benchmarks,turbo_mode}``, ``/v1/hardware/{tune,autotune}``, ``/v1/training/{optimizer,export}``,
 ``/v1/byok/*``, ``/v1/finetune/export``, ``/v1/models/{upgrade_to_triune,distill}``). Endpoints whose job is to reach the internet (module search / clone, provider proxying) answer with
 what can be known locally and say so.
@@ -277,6 +277,67 @@ async def checkpoints_delete(body: Dict[str, Any]):
         raise HTTPException(404, f"no checkpoint {p.name!r} in {d}")
     p.unlink()
     return {"deleted": str(p), "checkpoints": get_state().list_checkpoints(d)}
+
+
+def _projects(d: str) -> Dict[str, List[str]]:
+    import json as _json
+
+    f = Path(d) / "projects.json"
+    try:
+        return dict(_json.loads(f.read_text()).get("projects", {})) if f.is_file() else {}
+    except ValueError:
+        return {}
+
+
+def _save_projects(d: str, projects: Dict[str, List[str]]) -> None:
+    import json as _json
+
+    Path(d).mkdir(parents=True, exist_ok=True)
+    tmp = Path(d) / "projects.json.tmp"
+    tmp.write_text(_json.dumps({"projects": projects}, indent=2))
+    os.replace(tmp, Path(d) / "projects.json")
+
+
+@shell_router.get("/v1/checkpoints/projects")
+async def checkpoints_projects(directory: Optional[str] = None):
+    """Checkpoints grouped by project (a JSON side file in the checkpoint directory); unassigned ones come last."""
+    d = directory or _SHELL["config"]["default_checkpoint_dir"]
+    have = {c["name"]: c for c in get_state().list_checkpoints(d)}
+    projects = {p: [have[n] for n in names if n in have] for p, names in _projects(d).items()}
+    taken = {n for names in _projects(d).values() for n in names}
+    return {"projects": projects, "unassigned": [c for n, c in have.items() if n not in taken]}
+
+
+@shell_router.post("/v1/checkpoints/assign_project")
+async def checkpoints_assign(body: Dict[str, Any]):
+    d = str(body.get("directory") or _SHELL["config"]["default_checkpoint_dir"])
+    try:
+        name, project = _inside(d, str(body["name"])).name, str(body["project"]).strip()
+    except (KeyError, ValueError) as e:
+        raise _bad(e)
+    if not project or not (Path(d) / name).is_file():
+        raise HTTPException(404, f"no checkpoint {name!r} in {d}, or empty project name")
+    projects = {p: [n for n in names if n != name] for p, names in _projects(d).items()}
+    projects.setdefault(project, []).append(name)
+    _save_projects(d, {p: v for p, v in projects.items() if v})
+    return {"project": project, "checkpoints": projects[project]}
+
+
+@shell_router.post("/v1/checkpoints/prune_project")
+async def checkpoints_prune(body: Dict[str, Any]):
+    """Keep the ``keep`` newest checkpoints of a project and delete the rest of that project's files."""
+    d = str(body.get("directory") or _SHELL["config"]["default_checkpoint_dir"])
+    project, keep = str(body.get("project", "")), max(1, int(body.get("keep", 3)))
+    projects = _projects(d)
+    if project not in projects:
+        raise HTTPException(404, f"unknown project {project!r}")
+    files = sorted((p for p in (_inside(d, n) for n in projects[project]) if p.is_file() and p.suffix == ".pt"),
+                   key=lambda p: -p.stat().st_mtime)
+    for p in files[keep:]:
+        p.unlink()
+    projects[project] = [p.name for p in files[:keep]]
+    _save_projects(d, projects)
+    return {"project": project, "kept": projects[project], "deleted": [p.name for p in files[keep:]]}
 
 
 @shell_router.post("/v1/checkpoints/export")
