@@ -536,6 +536,36 @@ def test_gla_chunk_kernels(dev, B, T, H, with_state, gate_scale):
         assert _rel(a, b_) < 4e-2, name
 
 
+@pytest.mark.parametrize("T", [100, 200, 128])
+def test_gla_ragged_length_and_state_gradients(dev, T):
+    """Lengths that are not a multiple of the chunk, a loss on the final state and a trained initial state: every
+    gradient, including the part that reaches the first whole chunks through the state, against the fp32 oracle."""
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(21)
+    B, H, D = 2, 2, 64
+    q = F.normalize(torch.randn(B, T, H, D, device=dev).abs(), dim=-1).to(torch.bfloat16).requires_grad_(True)
+    k = F.normalize(torch.randn(B, T, H, D, device=dev).abs(), dim=-1).to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    gx = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    s0 = (torch.randn(B, H, D, D, device=dev) * 0.1).requires_grad_(True)
+    w = torch.randn(B, T, H, D, device=dev)
+    ws = torch.randn(B, H, D, D, device=dev) * 0.05
+    out, fin = ops.gla(q, k, v, gx, initial_state=s0, gate_logits=True)
+    ((out.float() * w).sum() + (fin.float() * ws).sum()).backward()
+    qf, kf, vf, gf = (t.detach().float().requires_grad_(True) for t in (q, k, v, gx))
+    s0f = s0.detach().clone().requires_grad_(True)
+    gl = torch.clamp(F.logsigmoid(gf), min=-5.0)
+    o_ref, fin_ref = ref.gla_chunk(qf, kf, vf, gl, s0f)
+    ((o_ref * w).sum() + (fin_ref * ws).sum()).backward()
+    assert _rel(out, o_ref) < 2e-2 and _rel(fin, fin_ref) < 2e-2
+    for a, b_, name in ((q.grad, qf.grad, "dq"), (k.grad, kf.grad, "dk"), (v.grad, vf.grad, "dv"),
+                        (gx.grad, gf.grad, "dg"), (s0.grad, s0f.grad, "ds0")):
+        assert a is not None, name
+        assert _rel(a, b_) < 4e-2, name
+
+
 def test_gla_decode_step_kernel(dev):
     from triune_b200 import ops
     from triune_b200.ops import reference as ref

@@ -53,6 +53,19 @@ def test_training_modes_reduce_loss(mode):
     assert tr.engine.step == 12
 
 
+def test_dynamic_mode_trains_the_depth_router():
+    """The router that picks the exit at inference must receive a gradient in the default depth mode."""
+    tr = _trainer(tiny(), depth_mode="dynamic")
+    batch = tr.next_batch()
+    loss, stats = tr.engine._micro_loss(batch[0], batch[1], None)
+    loss.backward()
+    router = tr.model.router.router_mlp
+    grads = [p.grad if p.grad is not None else getattr(p, "main_grad", None) for p in router.parameters()]
+    assert all(g is not None for g in grads)
+    assert sum(float(g.float().abs().sum()) for g in grads) > 0.0
+    assert "router_loss" in stats and math.isfinite(float(stats["router_loss"]))
+
+
 def test_lr_schedule_warmup_cosine_and_cycles():
     from triune_b200.trainer.scheduler import lr_schedule
 
@@ -471,3 +484,88 @@ def test_pipeline_times_data_parallel_on_gloo():
            "--master-port", "29743", os.path.join(ROOT, "tests", "mp_pp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0 and "PP_OK 4 4 pp2xdp2" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def _reference_checkpoint_module():
+    import sys
+
+    ref_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "triune")):
+        pytest.skip("reference not installed")
+    sys.path.insert(0, ref_dir)
+    try:
+        from triune.model.transformer import TriuneTransformer as RefModel
+        from triune.trainer import checkpoint as ref_ckpt
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"reference import failed: {e}")
+    finally:
+        sys.path.remove(ref_dir)
+    return RefModel, ref_ckpt
+
+
+def test_checkpoint_fingerprint_and_files_interoperate_with_the_reference(tmp_path):
+    """Schema-v2 contract: equal fingerprints for equal configs, and a file written by either project loads in the
+    other through that project's own ``load_checkpoint`` (weights-only and with the fingerprint gate active)."""
+    from types import SimpleNamespace
+
+    from triune_b200.trainer import checkpoint as ckpt
+
+    RefModel, ref_ckpt = _reference_checkpoint_module()
+    arch = dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4,
+                router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=3)
+    cfg = dict(arch, top_k=1, use_rope=True, shared_expert=True, target_depth_dist=(0.34, 0.33, 0.33), use_muon=True,
+               muon_lr=0.02, lr=3e-4)
+    assert ckpt.fingerprint(cfg) == ref_ckpt.compute_checkpoint_fingerprint(cfg)
+    assert ckpt.canonical_semantics(cfg) == ref_ckpt.extract_canonical_semantics(cfg)
+    assert ckpt.model_fingerprint(cfg) == ref_ckpt.compute_model_fingerprint(cfg)
+
+    torch.manual_seed(0)
+    ours = TriuneTransformer(**arch)
+    ref = RefModel(**arch)
+    x = torch.randint(0, 256, (2, 24))
+
+    # ours -> reference
+    p1 = ckpt.save_checkpoint(str(tmp_path / "ours.pt"), ours, None, step=7, loss=1.5, config=cfg)
+    ref_trainer = SimpleNamespace(model=ref, optimizer=None, config=dict(cfg))
+    got = ref_ckpt.load_checkpoint(ref_trainer, p1, load_optimizer=False)
+    assert got["step"] == 7
+    ours.eval(), ref.eval()
+    with torch.no_grad():
+        assert (ours(x, force_depth=2)[0] - ref(x, force_depth=2)[0]).abs().max() < 2e-3
+    with pytest.raises(ValueError):
+        ref_ckpt.load_checkpoint(SimpleNamespace(model=ref, optimizer=None, config=dict(cfg, hidden_dim=128)), p1,
+                                 load_optimizer=False)
+
+    # reference -> ours
+    torch.manual_seed(1)
+    ref2 = RefModel(**arch)
+    eng = SimpleNamespace(best_eval_loss=2.0, depth_usage_ema=None)
+    tr = SimpleNamespace(model=ref2, optimizer=None, config=dict(cfg, checkpoint_dir=str(tmp_path)), logger=None)
+    p2 = ref_ckpt.save_latest(tr, eng, 11, 0.9)
+    ours2 = TriuneTransformer(**arch)
+    ck = ckpt.load_checkpoint(str(p2), model=ours2, config=dict(cfg))
+    assert ck["step"] == 11
+    ours2.eval(), ref2.eval()
+    with torch.no_grad():
+        assert (ours2(x, force_depth=2)[0] - ref2(x, force_depth=2)[0]).abs().max() < 2e-3
+    with pytest.raises(ValueError, match="architecture.num_layers"):
+        ckpt.load_checkpoint(str(p2), model=None, config=dict(cfg, num_layers=6))
+    # an optimizer-only difference is tolerated when only the weights are loaded
+    ckpt.load_checkpoint(str(p2), model=None, config=dict(cfg, muon_lr=0.5))
+
+
+def test_checkpoint_loader_refuses_pickled_code(tmp_path):
+    """A file that needs the unrestricted unpickler is refused instead of executed."""
+    import pickle
+
+    from triune_b200.trainer import checkpoint as ckpt
+
+    class Boom:
+        def __reduce__(self):
+            return (os.system, ("true",))
+
+    path = tmp_path / "evil.pt"
+    torch.save({"model_state": {}, "payload": Boom()}, path)
+    with pytest.raises(Exception) as e:
+        ckpt.load_checkpoint(str(path))
+    assert isinstance(e.value, (pickle.UnpicklingError, RuntimeError))

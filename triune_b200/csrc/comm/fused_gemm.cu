@@ -22,6 +22,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "fused_gemm.cuh"
@@ -432,11 +433,10 @@ int sm_count() {
 template <int BN, bool B_MN, int MODE>
 void launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const FParams& p, cudaStream_t s) {
   auto kern = fused_gemm_kernel<BN, B_MN, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;  // the attribute is per device
+  if (configured.first_use()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
     if (e != cudaSuccess) throw std::runtime_error(std::string("fused_gemm: ") + cudaGetErrorString(e));
-    configured = true;
   }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   kern<<<grid, MODE == FG_ALL_GATHER ? 320 : 192, Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);

@@ -22,6 +22,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "tc_gemm_impl.cuh"
@@ -242,11 +243,10 @@ template <int BN, bool A_MN, bool B_MN, int EPI>
 void launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmAux,
                     const KParams& kp, int grid, cudaStream_t stream) {
   auto kern = tc_gemm_kernel<BN, A_MN, B_MN, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;  // the attribute is per device
+  if (configured.first_use()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES);
     if (e != cudaSuccess) throw std::runtime_error(std::string("tc_gemm: cannot set shared memory size: ") + cudaGetErrorString(e));
-    configured = true;
   }
   kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmAux, kp);
   cudaError_t e = cudaGetLastError();

@@ -23,6 +23,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "tc_gemm_impl.cuh"
@@ -298,12 +299,11 @@ void launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const C
                          const CUtensorMap& tmAux, const KParams& kp, int num_mp, int pair_tiles, int clusters,
                          cudaStream_t stream) {
   auto kern = tc_gemm_pair_kernel<NCFG, A_MN, B_MN, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;  // the attribute is per device
+  if (configured.first_use()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<NCFG>::SMEM_BYTES);
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("tc_gemm_pair: cannot set shared memory size: ") + cudaGetErrorString(e));
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);

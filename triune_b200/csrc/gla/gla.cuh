@@ -39,8 +39,10 @@ void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloa
 void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, const __nv_bfloat16* states,
                          const __nv_bfloat16* dstates, GlaMat dQ, GlaMat dK, GlaMat dV, float* dgl_local,
                          float* chunk_tot, GlaDims d, int* status, cudaStream_t s);
+// end_term (optional, fp32 [B*H, 64]): rowsum(dS_T * S_T), the gate gradient that reaches every token through a
+// differentiated final state.
 void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaMat G, GlaMat dG, GlaDims d,
-                            cudaStream_t s);
+                            cudaStream_t s, const float* end_term = nullptr);
 // Developer aid: eight int64 counters (device memory) receiving the backward kernel's phase clocks; null disables.
 void gla_set_debug_buffer(long long* counters);
 // One decode step for B*H heads: state [BH,64,64] fp32 in place; q,k,v,g rows of 64 bf16; out bf16.

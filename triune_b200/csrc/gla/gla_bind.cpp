@@ -48,14 +48,24 @@ std::vector<Tensor> gla_fwd(const Tensor& q, int64_t qcol, const Tensor& k, int6
   return {states, decay, fin, status};
 }
 
-// Backward: writes dq, dk, dv, dg into the given matrices.
-Tensor gla_bwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol, const Tensor& g,
+// Backward: writes dq, dk, dv, dg into the given matrices. With `dfin` (gradient of the final state, fp32
+// [BH,64,64]) and `fin` (the final state itself) the reverse scan starts from dfin instead of zero and the gate
+// gradient receives rowsum(dfin * fin). Returns (status, gradient of the initial state [BH,64,64] fp32).
+std::vector<Tensor> gla_bwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol, const Tensor& g,
                int64_t gcol, const Tensor& dout, int64_t docol, const Tensor& states, const Tensor& decay, Tensor& dq,
                int64_t dqcol, Tensor& dk, int64_t dkcol, Tensor& dv, int64_t dvcol, Tensor& dg, int64_t dgcol, int64_t B,
-               int64_t T, int64_t H, bool gate_logits) {
+               int64_t T, int64_t H, bool gate_logits, const c10::optional<Tensor>& dfin,
+               const c10::optional<Tensor>& fin) {
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t NT = T / 64, BH = B * H;
   auto f32 = q.options().dtype(at::kFloat);
+  Tensor dfinc, end_term;
+  Tensor dinit = torch::empty({BH, 64, 64}, f32);
+  if (dfin.has_value() && dfin->defined()) {
+    TORCH_CHECK(fin.has_value() && fin->defined(), "the final state is needed with its gradient");
+    dfinc = dfin->to(at::kFloat).reshape({BH, 64, 64}).contiguous();
+    end_term = (dfinc * fin->to(at::kFloat).reshape({BH, 64, 64})).sum(-1).contiguous();
+  }
   Tensor m = torch::empty({BH * NT, 64, 64}, f32);
   Tensor dstates = torch::empty({BH * NT, 64, 64}, q.options());
   Tensor dgl = torch::empty({B * T, H * 64}, f32);
@@ -65,14 +75,16 @@ Tensor gla_bwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, con
   auto s = cur_stream();
   tb::launch_gla_chunk_outer(1, mat(q, qcol), mat(dout, docol), mat(g, gcol), m.data_ptr<float>(), nullptr, d,
                              status.data_ptr<int>(), s);
-  tb::launch_gla_scan(m.data_ptr<float>(), decay.data_ptr<float>(), nullptr,
-                      reinterpret_cast<__nv_bfloat16*>(dstates.data_ptr()), nullptr, (int)BH, (int)NT, true, s);
+  tb::launch_gla_scan(m.data_ptr<float>(), decay.data_ptr<float>(), dfinc.defined() ? dfinc.data_ptr<float>() : nullptr,
+                      reinterpret_cast<__nv_bfloat16*>(dstates.data_ptr()), dinit.data_ptr<float>(), (int)BH, (int)NT,
+                      true, s);
   tb::launch_gla_bwd_main(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), mat(dout, docol),
                           reinterpret_cast<const __nv_bfloat16*>(states.data_ptr()),
                           reinterpret_cast<const __nv_bfloat16*>(dstates.data_ptr()), mat(dq, dqcol), mat(dk, dkcol),
                           mat(dv, dvcol), dgl.data_ptr<float>(), tot.data_ptr<float>(), d, status.data_ptr<int>(), s);
-  tb::launch_gla_dg_finalize(dgl.data_ptr<float>(), tot.data_ptr<float>(), mat(g, gcol), mat(dg, dgcol), d, s);
-  return status;
+  tb::launch_gla_dg_finalize(dgl.data_ptr<float>(), tot.data_ptr<float>(), mat(g, gcol), mat(dg, dgcol), d, s,
+                             end_term.defined() ? end_term.data_ptr<float>() : nullptr);
+  return {status, dinit};
 }
 
 void gla_decode(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v, int64_t vcol, const Tensor& g,

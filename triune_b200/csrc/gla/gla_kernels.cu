@@ -18,6 +18,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 
@@ -845,12 +846,14 @@ __global__ void __launch_bounds__(256) gla_dg_finalize_kernel(const float* __res
                                                               const float* __restrict__ chunk_tot,
                                                               const __nv_bfloat16* __restrict__ g, long long g_ld,
                                                               int gcol, __nv_bfloat16* __restrict__ dg, long long dg_ld,
-                                                              int dgcol, int T, int H, int logits) {
+                                                              int dgcol, int T, int H, int logits,
+                                                              const float* __restrict__ end_term) {
   __shared__ float carry[D];
   const int NT = T / C;
   const int chunk = blockIdx.x % NT, bh = blockIdx.x / NT, h = bh % H, b = bh / H;
   if (threadIdx.x < D) {
-    float acc = 0.f;
+    // end_term[bh][d] = sum_v dS_T[d][v] S_T[d][v]: the final state depends on every log decay of the sequence
+    float acc = end_term != nullptr ? end_term[(long long)bh * D + threadIdx.x] : 0.f;
     for (int c = chunk + 1; c < NT; ++c) acc += chunk_tot[((long long)bh * NT + c) * D + threadIdx.x];
     carry[threadIdx.x] = acc;
   }
@@ -934,11 +937,8 @@ void launch_gla_chunk_outer(int mode, GlaMat X, GlaMat Y, GlaMat G, float* out_k
   CUtensorMap tx = tile_map(X, rows, (int)X.ld), ty = tile_map(Y, rows, (int)Y.ld), tg = tile_map(G, rows, (int)G.ld);
   (void)width;
   constexpr int SMEM = 3 * TILE + BMAT_BYTES + 1024 + 256;
-  static bool cfg = false;
-  if (!cfg) {
-    set_smem(gla_chunk_outer_kernel, SMEM);
-    cfg = true;
-  }
+  static PerDeviceOnce cfg;  // the attribute is per device
+  if (cfg.first_use()) set_smem(gla_chunk_outer_kernel, SMEM);
   const int grid = d.B * d.H * (d.T / C);
   gla_chunk_outer_kernel<<<grid, GLA_THREADS, SMEM, s>>>(tx, ty, tg, X.col0, Y.col0, G.col0, mode, out_kv, out_decay, d.T,
                                                          d.H, d.gate_logits ? 1 : 0, status);
@@ -960,11 +960,8 @@ void launch_gla_fwd_out(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, const __nv_bfloa
               tg = tile_map(G, rows, (int)G.ld);
   GlaMat S{states, D, 0};
   CUtensorMap ts = tile_map(S, srows, D);
-  static bool cfg = false;
-  if (!cfg) {
-    set_smem(gla_fwd_out_kernel, FWD_SMEM);
-    cfg = true;
-  }
+  static PerDeviceOnce cfg;  // the attribute is per device
+  if (cfg.first_use()) set_smem(gla_fwd_out_kernel, FWD_SMEM);
   const int grid = d.B * d.H * (d.T / C);
   gla_fwd_out_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(tq, tk, tv, tg, ts, Q.col0, K.col0, V.col0, G.col0,
                                                          reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(O.ptr)), O.ld,
@@ -985,11 +982,8 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
               tg = tile_map(G, rows, (int)G.ld), tdo = tile_map(dO, rows, (int)dO.ld);
   GlaMat S{states, D, 0}, dS{dstates, D, 0};
   CUtensorMap ts = tile_map(S, srows, D), tds = tile_map(dS, srows, D);
-  static bool cfg = false;
-  if (!cfg) {
-    set_smem(gla_bwd_main_kernel, BWD_SMEM);
-    cfg = true;
-  }
+  static PerDeviceOnce cfg;  // the attribute is per device
+  if (cfg.first_use()) set_smem(gla_bwd_main_kernel, BWD_SMEM);
   const int nchunks = d.B * d.H * (d.T / C);
   static int sms = 0;
   if (sms == 0) {
@@ -1009,12 +1003,12 @@ void launch_gla_bwd_main(GlaMat Q, GlaMat K, GlaMat V, GlaMat G, GlaMat dO, cons
 }
 
 void launch_gla_dg_finalize(const float* dgl_local, const float* chunk_tot, GlaMat G, GlaMat dG, GlaDims d,
-                            cudaStream_t s) {
+                            cudaStream_t s, const float* end_term) {
   check_dims(d);
   const int grid = d.B * d.H * (d.T / C);
   gla_dg_finalize_kernel<<<grid, 256, 0, s>>>(dgl_local, chunk_tot, reinterpret_cast<const __nv_bfloat16*>(G.ptr), G.ld,
                                               G.col0, reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dG.ptr)), dG.ld,
-                                              dG.col0, d.T, d.H, d.gate_logits ? 1 : 0);
+                                              dG.col0, d.T, d.H, d.gate_logits ? 1 : 0, end_term);
   check_launch("gla_dg_finalize");
 }
 

@@ -16,6 +16,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "quant.cuh"
@@ -612,11 +613,10 @@ void launch_fp8_block_gemm(const uint8_t* xq, const float* xs, const uint8_t* wq
                                  (uint64_t)K * (uint64_t)M, QBK, QBM);
   CUtensorMap tmB = make_tmap_3d(wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K,
                                  (uint64_t)K * (uint64_t)N, QBK, QBN);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;  // the attribute is per device
+  if (configured.first_use()) {
     cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM);
     if (e != cudaSuccess) throw std::runtime_error(std::string("fp8_block_gemm: ") + cudaGetErrorString(e));
-    configured = true;
   }
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);

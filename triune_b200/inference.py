@@ -56,10 +56,9 @@ def load_checkpoint_model(path: str, device="cpu", dtype: Optional[torch.dtype] 
     from .models.transformer import TriuneTransformer
     from .utils import place_model
 
-    try:
-        ck = torch.load(path, map_location="cpu", weights_only=True)
-    except Exception:
-        ck = torch.load(path, map_location="cpu", weights_only=False)
+    from .trainer.checkpoint import safe_torch_load
+
+    ck = safe_torch_load(path)
     sd = ck.get("model_state", ck.get("model", ck)) if isinstance(ck, dict) else ck
     sd = {k.replace("_orig_mod.", ""): v for k, v in sd.items()}
     cfg_dict = ck.get("config") if isinstance(ck, dict) else None

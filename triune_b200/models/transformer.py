@@ -484,13 +484,30 @@ class TriuneTransformer(nn.Module):
         return self._head(xr, 0), self._head(xl, 1), self._head(xc, 2), route_logits
 
     def forward_loss(self, input_ids, labels, force_depth: int = 2, ignore_index: int = -100,
-                     n_valid: Optional[int] = None):
-        """Mean next-token CE at one exit through the fused head + CE op (labels already shifted)."""
+                     n_valid: Optional[int] = None, return_route: bool = False):
+        """Mean next-token CE at one exit through the fused head + CE op (labels already shifted).
+
+        With ``return_route`` the depth router is evaluated on the prefix output of the same pass and
+        ``(loss, route_logits, balance_loss)`` is returned; the route logits keep their graph, so a router loss
+        added by the caller trains the router and the prefix layers (the ``dynamic`` training mode)."""
         x = self.token_embed(input_ids)
-        h, _ = self._run_layers(x, 0, self.exit_layers[force_depth] + 1)
+        end = self.exit_layers[force_depth] + 1
+        route_logits = bal = None
+        if return_route:
+            P = min(self.router_prefix_layers, end)
+            xp, _ = self._run_layers(x, 0, P)
+            route_logits, _, choice, bal = self._route(xp, None, x.shape[0], x.device)
+            self.last_route_logits, self.last_depth_choice, self.last_balance_loss = (
+                route_logits.detach(), choice.detach(), bal)
+            h, _ = self._run_layers(xp, P, end)
+        else:
+            h, _ = self._run_layers(x, 0, end)
         norm, head = self._head_modules(force_depth)
-        return ops.linear_cross_entropy(norm(h), head.weight, labels, bias=head.bias, ignore_index=ignore_index,
+        loss = ops.linear_cross_entropy(norm(h), head.weight, labels, bias=head.bias, ignore_index=ignore_index,
                                         n_valid=n_valid)
+        if return_route:
+            return loss, route_logits, bal
+        return loss
 
     def exit_losses(self, input_ids, labels, ignore_index: int = -100, n_valid: Optional[int] = None,
                     update_stats: bool = True):

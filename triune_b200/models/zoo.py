@@ -219,10 +219,9 @@ def build_model_from_spec(spec: ModelSpec, device=None, dtype: Optional[torch.dt
 
 
 def _load_state(path: Path) -> Dict[str, Any]:
-    try:
-        return torch.load(path, map_location="cpu", weights_only=True)
-    except Exception:
-        return torch.load(path, map_location="cpu", weights_only=False)
+    from ..trainer.checkpoint import safe_torch_load
+
+    return safe_torch_load(path)
 
 
 def load_model(model_name_or_path, **kwargs: Any) -> nn.Module:

@@ -19,6 +19,7 @@ import torch
 from .. import _ext
 
 _CHECK = os.environ.get("TRIUNE_CHECK_STATUS", "0") == "1"
+GLA_MIN_LOG_DECAY = -5.0  # the kernels' lower clamp of the per-token log decay (csrc/gla/gla.cuh)
 last_status = None  # device int32 status word of the most recent launch group (0 = ok)
 
 
@@ -67,25 +68,30 @@ class _GLAFn(torch.autograd.Function):
         states, decay, fin, status = e.gla_fwd(qm, 0, km, 0, vm, 0, gm, 0, out, 0, init, B, T, H, gate_logits)
         _tick(3)
         _note(status)
-        ctx.save_for_backward(qm, km, vm, gm, states, decay)
+        ctx.save_for_backward(qm, km, vm, gm, states, decay, fin)
         ctx.dims = (B, T, H, D, gate_logits, init is not None)
-        fin = fin.view(B, H, D, D)
-        ctx.mark_non_differentiable(fin)
-        return out.view(B, T, H, D), fin
+        ctx.set_materialize_grads(False)
+        return out.view(B, T, H, D), fin.view(B, H, D, D)
 
     @staticmethod
     def backward(ctx, dout, dfin):
-        qm, km, vm, gm, states, decay = ctx.saved_tensors
+        # The final state is differentiable: its gradient seeds the reverse inter-chunk scan (it is the state
+        # gradient after the last chunk), adds rowsum(dS_T * S_T) to every token's gate gradient, and the scan's
+        # last value is the gradient of the initial state.
+        qm, km, vm, gm, states, decay, fin = ctx.saved_tensors
         B, T, H, D, gate_logits, has_init = ctx.dims
         e = _ext.ext()
+        if dout is None:
+            dout = torch.zeros(B, T, H, D, device=qm.device, dtype=torch.bfloat16)
         dom = _as_matrix(dout.to(torch.bfloat16))
         dq, dk, dv, dg = (torch.empty(B * T, H * D, device=dom.device, dtype=torch.bfloat16) for _ in range(4))
-        status = e.gla_bwd(qm, 0, km, 0, vm, 0, gm, 0, dom, 0, states, decay, dq, 0, dk, 0, dv, 0, dg, 0, B, T, H,
-                           gate_logits)
+        status, dinit = e.gla_bwd(qm, 0, km, 0, vm, 0, gm, 0, dom, 0, states, decay, dq, 0, dk, 0, dv, 0, dg, 0, B, T, H,
+                                  gate_logits, dfin, fin if dfin is not None else None)
         _tick(4)
         _note(status)
         sh = (B, T, H, D)
-        return dq.view(sh), dk.view(sh), dv.view(sh), dg.view(sh), None, None
+        dinit = dinit.view(B, H, D, D) if (has_init and ctx.needs_input_grad[4]) else None
+        return dq.view(sh), dk.view(sh), dv.view(sh), dg.view(sh), dinit, None
 
 
 def gla_chunk(q, k, v, g, initial_state, scale, gate_logits):
@@ -100,7 +106,10 @@ def gla_chunk(q, k, v, g, initial_state, scale, gate_logits):
     Tm = (T // 64) * 64
     out, state = _GLAFn.apply(q[:, :Tm], k[:, :Tm], v[:, :Tm], g[:, :Tm], initial_state, gate_logits)
     if Tm < T:
-        gl = torch.nn.functional.logsigmoid(g[:, Tm:].float()) if gate_logits else g[:, Tm:]
+        # ragged tail: the reference op continues from the kernels' final state (which carries its gradient back into
+        # the first Tm tokens) with the kernels' clamp of the per-token log decay
+        gl = torch.nn.functional.logsigmoid(g[:, Tm:].float()) if gate_logits else g[:, Tm:].float()
+        gl = gl.clamp(min=GLA_MIN_LOG_DECAY, max=0.0)
         o2, state = ref.gla_chunk(q[:, Tm:], k[:, Tm:], v[:, Tm:], gl, state, 1.0)
         out = torch.cat((out, o2.to(out.dtype)), dim=1)
     if scale != 1.0:
@@ -214,8 +223,8 @@ class _GLACoreFn(torch.autograd.Function):
         dout = dout.contiguous()
         dqk = torch.empty_like(qk)
         dqkvg = torch.empty_like(qkvg)
-        status = e.gla_bwd(qk, 0, qk, HD, qkvg, 2 * HD, qkvg, 3 * HD, dout, 0, states, decay, dqk, 0, dqk, HD, dqkvg,
-                           2 * HD, dqkvg, 3 * HD, B, T, H, True)
+        status, _ = e.gla_bwd(qk, 0, qk, HD, qkvg, 2 * HD, qkvg, 3 * HD, dout, 0, states, decay, dqk, 0, dqk, HD, dqkvg,
+                              2 * HD, dqkvg, 3 * HD, B, T, H, True, None, None)
         e.qk_prep_bwd(qkvg, HD, dqk.view(B * T, 2, H, D), dqkvg, cs if rope else None, sn if rope else None, T, H, D)
         _tick(5)
         _note(status)

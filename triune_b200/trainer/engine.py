@@ -7,7 +7,9 @@ Parity: ``TrainingEngine`` (``triune/trainer/engine.py:18-511``). ``step_once``:
                 (0.25,0.30,0.45)) + 0.2 * (KL_R + KL_L) toward the detached Cortex distribution + 0.5 * router
                 CE + 1e-3 * z-loss + 0.3 * balance,
   * ``dynamic`` router labels from a no-grad all-exits pass (batch-centred exit losses + depth cost + bias
-                toward the target usage), exploration schedule, 0.8/0.2 mix with a Cortex anchor,
+                toward the target usage), exploration schedule, 0.8/0.2 mix with a Cortex anchor, plus
+                0.5 * router CE + z-loss + balance on the route logits of the anchor pass (the reference's
+                dynamic branch, ``triune/trainer/engine.py:342-411``),
 then clip -> optimizer step -> MoE selection-bias update. The duck-typed ``trainer`` protocol is the
 reference's (``.model .optimizer .config .device .next_batch() .lr_schedule .set_optimizer_lr ...``).
 
@@ -121,9 +123,20 @@ class TrainingEngine:
                 continue
             ld = model.forward_loss(x[idx], y[idx], force_depth=d)
             total = total + ld * (idx.numel() / x.shape[0])
-        anchor = model.forward_loss(x, y, force_depth=2, n_valid=n_valid)
+        # The anchor pass also evaluates the depth router with its graph attached: the router (and the prefix layers
+        # under it) learn the exit labels here; at inference it is this router that picks the exit.
+        anchor, route_logits, balance = model.forward_loss(x, y, force_depth=2, n_valid=n_valid, return_route=True)
         loss = 0.8 * total + 0.2 * anchor
-        rl = model.last_route_logits
+        rl = route_logits.float()
+        if balance is None:
+            target = torch.as_tensor(self.config.get("target_depth_dist", (0.34, 0.33, 0.33)), device=rl.device,
+                                     dtype=torch.float32)
+            balance = (torch.softmax(rl, dim=-1).mean(dim=0) - target).pow(2).mean()
+        router_loss = F.cross_entropy(rl, labels)
+        z_loss = (torch.logsumexp(rl, dim=-1) ** 2).mean()
+        loss = (loss + 0.5 * router_loss + float(self.config.get("z_loss_coef", 1e-3)) * z_loss
+                + float(self.config.get("balance_coef", 0.3)) * balance)
+        stats.update(router_loss=router_loss.detach(), z_loss=z_loss.detach())
         with torch.no_grad():
             use = torch.bincount(labels, minlength=3).float().cpu() / max(1, labels.numel())
             d = float(self.config.get("usage_ema_decay", 0.98))

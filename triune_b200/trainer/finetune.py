@@ -176,7 +176,9 @@ def _load_tensors(path: Path) -> Dict[str, torch.Tensor]:
         from ..export.safetensors_io import load_file
 
         return load_file(str(path))
-    return torch.load(path, map_location="cpu")
+    from .checkpoint import safe_torch_load
+
+    return safe_torch_load(path)
 
 
 class TriuneFineTuner:
