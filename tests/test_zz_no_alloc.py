@@ -79,3 +79,58 @@ def test_noalloc_entry_rejects_oversized_and_bad_arguments():
     assert lib.triune_gla_forward_noalloc(*args, 64, 64 * 64, 1, 1, None, stream) == -2  # 4096 chunks > 512
     assert lib.triune_gla_forward_noalloc(*args, 1, 100, 1, 1, None, stream) == -1       # T not a multiple of 64
     torch.cuda.synchronize()
+
+
+def test_noalloc_entry_at_the_scratch_limit():
+    """Exactly 512 chunks (the whole built-in array) must work and agree with the regular entry; one chunk more is
+    refused with -2 before anything is launched."""
+    from triune_b200 import _ext
+
+    lib = _load()
+    dev = torch.device("cuda", 0)
+    e = _ext.ext()
+    B, T, H = 4, 4096, 2  # 4 * 2 * 64 = 512 chunks
+    torch.manual_seed(3)
+    q, k, v, g = (torch.randn(B * T, H * 64, device=dev).to(torch.bfloat16) for _ in range(4))
+    q, k = q.abs() * 0.2, k.abs() * 0.2
+    ref_out = torch.empty(B * T, H * 64, device=dev, dtype=torch.bfloat16)
+    _, _, ref_fin, ref_status = e.gla_fwd(q, 0, k, 0, v, 0, g, 0, ref_out, 0, None, B, T, H, True)
+    torch.cuda.synchronize()
+    assert int(ref_status.item()) == 0
+    rc, out, fin, status = _call(lib, q, k, v, g, None, B, T, H)
+    assert rc == 0 and status == 0
+    scale = float(ref_out.float().abs().max().clamp_min(1e-6))
+    assert float((out.float() - ref_out.float()).abs().max()) <= 2e-2 * scale
+    fscale = float(ref_fin.abs().max().clamp_min(1e-6))
+    assert float((fin - ref_fin.view_as(fin)).abs().max()) <= 2e-2 * fscale
+    # 513 chunks: B=513, T=64, H=1
+    x = torch.zeros(64, 64, device=dev, dtype=torch.bfloat16)
+    f1 = torch.zeros(1, 64, 64, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (x.data_ptr(),) * 4 + (x.data_ptr(), f1.data_ptr(), None)
+    assert lib.triune_gla_forward_noalloc(*args, 513, 64, 1, 1, None, stream) == -2
+    torch.cuda.synchronize()
+
+
+def test_noalloc_entry_on_a_second_device():
+    """The scratch address and the kernels' shared-memory attributes are per device: the first call on another GPU
+    of the same process has to set them up again."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    from triune_b200 import _ext
+
+    lib = _load()
+    e = _ext.ext()
+    B, T, H = 1, 128, 2
+    for ordinal in (0, 1):
+        dev = torch.device("cuda", ordinal)
+        with torch.cuda.device(dev):
+            torch.manual_seed(4 + ordinal)
+            q, k, v, g = (torch.randn(B * T, H * 64, device=dev).to(torch.bfloat16) for _ in range(4))
+            q, k = q.abs() * 0.2, k.abs() * 0.2
+            ref_out = torch.empty(B * T, H * 64, device=dev, dtype=torch.bfloat16)
+            _, _, ref_fin, _ = e.gla_fwd(q, 0, k, 0, v, 0, g, 0, ref_out, 0, None, B, T, H, True)
+            rc, out, fin, status = _call(lib, q, k, v, g, None, B, T, H)
+            assert rc == 0 and status == 0, ordinal
+            scale = float(ref_out.float().abs().max().clamp_min(1e-6))
+            assert float((out.float() - ref_out.float()).abs().max()) <= 2e-2 * scale, ordinal

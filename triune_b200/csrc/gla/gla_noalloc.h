@@ -12,8 +12,9 @@
  *   - head_dim is 64, T is a positive multiple of 64, tensors are bf16 [B*T, H*64] row-major, 16-byte aligned.
  *   - The scratch array (about 12.3 MB) is part of the library image: every GPU that loads the library holds it
  *     until the process exits.
- *   - The first call on a device resolves the device address of that array (cudaGetSymbolAddress) and sets the
- *     kernels' shared-memory attributes. Make that first call before starting any stream capture.
+ *   - The first call on EACH device resolves the device address of that array on that device
+ *     (cudaGetSymbolAddress, with the device current) and sets the kernels' shared-memory attributes there. Make
+ *     that first call before starting any stream capture.
  *   - All calls share the one array and it keeps the previous call's contents; the entry point clears the words
  *     that must start at zero itself. Two calls that overlap on the GPU (different streams, no ordering) race on
  *     the scratch and give wrong results: order them on one stream or with events.
@@ -33,7 +34,9 @@ extern "C" {
  * init_state may be NULL (zero initial state). gate_logits != 0: g holds raw gate logits (log-sigmoid applied
  * inside). Returns 0 on success, -1 bad argument, -2 problem larger than the built-in scratch, -3 CUDA error
  * (cudaGetLastError() has the detail). The work is enqueued on `stream`; read *status_out after synchronising:
- * 0 means every bounded wait inside the kernels completed. status_out may be NULL. */
+ * 0 means every bounded wait inside the kernels completed. status_out may be NULL; when given it should point to
+ * pinned (page-locked) host memory: the status word is copied with cudaMemcpyAsync, and a copy into pageable memory
+ * makes the runtime stage it and blocks the calling thread until the stream has drained. */
 int triune_gla_forward_noalloc(const void* q, const void* k, const void* v, const void* g, void* out, float* final_state,
                                const float* init_state, int B, int T, int H, int gate_logits, int* status_out,
                                cudaStream_t stream);
