@@ -3,8 +3,10 @@
 Contract: ``python bench.py --gpus N --steps K --warmup W`` (under torchrun for N > 1) prints ONE JSON line from
 rank 0. ``value`` is the whole-job tokens/s from a device-timed loop (CUDA events, max over ranks); ``e2e`` is
 the same metric through the public ``Trainer.train_step`` API including the pinned host->device copy of every
-batch and the device->host read of every loss. ``--impl reference`` runs the unmodified reference project
-(installed under ``baseline/_ref``) on the same config.
+batch and the device->host read of every loss. ``prefill`` is the serving half of the metric: tokens/s of a 4 x 16384 prefill through the public
+forward, as N independent replicas for N > 1. ``wait_status`` is the status word of the fused data-parallel kernels
+(0 = every bounded wait completed). ``--impl reference`` runs the unmodified reference project (installed under
+``baseline/_ref``) on the same config.
 """
 
 from __future__ import annotations
@@ -23,6 +25,22 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 BASELINE_TOK_S = 9560.0  # reference's published pre-training number (RTX 5070 Laptop, B=4, T=256)
 BATCH, SEQ, VOCAB = 16, 2048, 32000
+PREFILL_BATCH, PREFILL_SEQ = 4, 16384  # the serving half of the metric: prefill tok/s at T = 16K
+
+
+def timed_prefill(fn, iters: int = 5, warmup: int = 3) -> float:
+    """Milliseconds per call of ``fn`` (CUDA events on the current stream, after warm-up, synchronised on both sides).
+    The 4 x 16384 inputs and their activations are far larger than the 126 MB L2, so no explicit flush."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
 
 
 class ClockSampler:
@@ -104,7 +122,8 @@ def run_ours(args):
     torch.manual_seed(0)
     cfg = get_model_config("bench-90m")
     model = place_model(TriuneTransformer.from_config(cfg), dev, torch.bfloat16)
-    run_cfg = {"lr": 3e-4, "min_lr": 3e-5, "warmup_steps": 10, "total_steps": 100000, "depth_mode": "cortex",
+    # constant learning rate 3e-4, as the reference arm uses, so the two final losses are comparable
+    run_cfg = {"lr": 3e-4, "min_lr": 3e-4, "warmup_steps": 0, "total_steps": 100000, "depth_mode": "cortex",
                "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": VOCAB, "ns_steps": 5,
                "cuda_graph": (not args.no_graph) and (ctx.world_size == 1 or args.dp_mode == "fused")}
     dp, opt = None, None
@@ -173,6 +192,37 @@ def run_ours(args):
     h2d = (trainer.h2d_bytes - h0) // args.steps
     d2h = (trainer.d2h_bytes - d0) // args.steps
 
+    # ---- status word of the fused data-parallel kernels: a bounded wait that expired would have skipped a reduction
+    # (and shortened the step), so a non-zero word invalidates the run. One device->host read, outside the timed loops.
+    wait_status = 0
+    fused = getattr(dp, "_fused", None) if dp is not None else None
+    if fused is not None:
+        wait_status = int(fused.check())
+    wait_status = int(max_over_ranks(float(wait_status), dev))
+
+    # ---- prefill tok/s at T = 16K through the public forward (recurrent cache, last-token logits); N > 1 runs N
+    # independent replicas and reports the whole-job rate from the slowest rank ----
+    prefill = None
+    if not args.no_prefill:
+        del dev_batches
+        torch.cuda.empty_cache()
+        model.eval()
+        pg = torch.Generator(device=dev).manual_seed(99 + ctx.rank)
+        pids = torch.randint(0, VOCAB, (PREFILL_BATCH, PREFILL_SEQ), device=dev, generator=pg)
+
+        @torch.no_grad()
+        def prefill_once():
+            return model(pids, force_depth=2, cache=model.init_cache(PREFILL_BATCH), last_token_only=True)
+
+        ops.reset_launch_count()
+        prefill_once()
+        p_launches = ops.launch_count()
+        barrier_sync()
+        p_ms = max_over_ranks(timed_prefill(prefill_once), dev)
+        prefill = {"tok_s": PREFILL_BATCH * PREFILL_SEQ * ctx.world_size / (p_ms / 1e3), "ms": p_ms,
+                   "batch": PREFILL_BATCH, "seq": PREFILL_SEQ, "dtype": "bf16", "variant": "bf16",
+                   "layout": f"{ctx.world_size} independent replica(s)", "gpu_launches": p_launches}
+
     if ctx.rank == 0:
         value = tokens_per_step / (ms / 1e3)
         out = {
@@ -190,6 +240,7 @@ def run_ours(args):
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "prefill": prefill, "wait_status": wait_status,
             "final_loss": final_loss, "impl": "triune_b200",
         }
         print(json.dumps(out), flush=True)
@@ -297,6 +348,33 @@ def run_reference(args):
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": f"run failed: {type(e).__name__}: {e}"[:300]}))
         return
+    prefill = None
+    if not args.no_prefill:
+        try:  # the reference's own forward: recurrent cache, last-token logits, bf16 autocast as its scripts use
+            del dev_pool
+            opt.zero_grad(set_to_none=True)
+            torch.cuda.empty_cache()
+            model.eval()
+            pg = torch.Generator(device=dev).manual_seed(99 + rank)
+            pids = torch.randint(0, VOCAB, (PREFILL_BATCH, PREFILL_SEQ), device=dev, generator=pg)
+
+            @torch.no_grad()
+            def prefill_once():
+                cache = model.init_cache(PREFILL_BATCH)
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    return model(pids, force_depth=2, cache=cache, last_token_only=True)
+
+            barrier_sync()
+            p_ms = timed_prefill(prefill_once)
+            t = torch.tensor([p_ms], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            p_ms = float(t.item())
+            prefill = {"tok_s": PREFILL_BATCH * PREFILL_SEQ * world / (p_ms / 1e3), "ms": p_ms, "batch": PREFILL_BATCH,
+                       "seq": PREFILL_SEQ, "dtype": "bf16", "variant": "bf16",
+                       "layout": f"{world} independent replica(s)"}
+        except Exception as e:
+            prefill = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     if rank == 0:
         tps = BATCH * SEQ * world
         value = tps / (ms / 1e3)
@@ -309,7 +387,7 @@ def run_reference(args):
                        "has_fla": bool(getattr(ratt, "HAS_FLA", False))},
             "clocks": clocks, "e2e": {"value": tps / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms,
                                       "h2d_bytes_per_step": BATCH * SEQ * 16, "d2h_bytes_per_step": 4},
-            "final_loss": lv, "impl": "reference"}), flush=True)
+            "prefill": prefill, "final_loss": lv, "impl": "reference"}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -321,6 +399,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA-graph replay)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (T = 16K) measurement after the training loops")
     ap.add_argument("--dp-mode", default=os.environ.get("TRIUNE_DP_MODE", "fused"), choices=["nccl", "fused"])
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)

@@ -305,6 +305,84 @@ def test_gemm_grouped(dev):
 
 
 # ------------------------------------------------------------------ row kernels
+@pytest.mark.parametrize("M,K,H", [(512, 384, 256), (1000, 2048, 2816), (300, 1024, 96), (4096, 2048, 1408)])
+def test_swiglu_ffn_fused_in_gemm_epilogues(dev, M, K, H):
+    """SwiGLU inside the GEMM epilogues (forward: silu(gate) * up from the fused weight's accumulator halves;
+    backward: the derivative applied while d(hidden) leaves the tensor core) against fp32 PyTorch."""
+    from triune_b200 import ops
+
+    torch.manual_seed(31)
+    x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w13 = (torch.randn(2 * H, K, device=dev) / math.sqrt(K)).to(torch.bfloat16).requires_grad_(True)
+    w2 = (torch.randn(K, H, device=dev) / math.sqrt(H)).to(torch.bfloat16).requires_grad_(True)
+    y = ops.swiglu_mlp(x, w13, w2)
+    wgt = torch.randn(M, K, device=dev)
+    (y.float() * wgt).sum().backward()
+    xf, w13f, w2f = (t.detach().float().requires_grad_(True) for t in (x, w13, w2))
+    gu = xf @ w13f.t()
+    h = F.silu(gu[:, :H]) * gu[:, H:]
+    y_ref = h.to(torch.bfloat16).float() @ w2f.t()
+    (y_ref * wgt).sum().backward()
+    assert _rel(y, y_ref) < 2e-2
+    assert _rel(x.grad, xf.grad) < 3e-2
+    assert _rel(w13.grad, w13f.grad) < 3e-2
+    assert _rel(w2.grad, w2f.grad) < 3e-2
+    with torch.no_grad():  # inference: no pre-activations are written
+        y2 = ops.swiglu_mlp(x.detach(), w13.detach(), w2.detach())
+    assert _rel(y2, y_ref) < 2e-2
+
+
+def test_standalone_swiglu_rope_cross_entropy_embedding_kernels(dev):
+    from triune_b200 import ops
+    from triune_b200.ops import reference as ref
+
+    torch.manual_seed(32)
+    # SwiGLU on the two halves of one projection output
+    gu = torch.randn(777, 2 * 264, device=dev).to(torch.bfloat16).requires_grad_(True)
+    out = ops.swiglu(gu[:, :264], gu[:, 264:])
+    w = torch.randn_like(out, dtype=torch.float32)
+    (out.float() * w).sum().backward()
+    guf = gu.detach().float().requires_grad_(True)
+    o_ref = F.silu(guf[:, :264]) * guf[:, 264:]
+    (o_ref * w).sum().backward()
+    assert _rel(out, o_ref) < 1e-2 and _rel(gu.grad, guf.grad) < 2e-2
+    # RoPE
+    B, T, H, D = 2, 96, 3, 64
+    x = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16).requires_grad_(True)
+    cos, sin = ops.rope_tables(T, D, device=dev)
+    y = ops.apply_rope(x, cos, sin)
+    wy = torch.randn(B, T, H, D, device=dev)
+    (y.float() * wy).sum().backward()
+    xf = x.detach().float().requires_grad_(True)
+    y_ref = ref.apply_rope(xf, cos.float(), sin.float())
+    (y_ref * wy).sum().backward()
+    assert _rel(y, y_ref) < 1e-2 and _rel(x.grad, xf.grad) < 1e-2
+    # cross entropy with ignored rows
+    N, V = 513, 4096
+    logits = (torch.randn(N, V, device=dev) * 2).to(torch.bfloat16).requires_grad_(True)
+    tgt = torch.randint(0, V, (N,), device=dev)
+    tgt[::7] = -100
+    keep = logits.detach().clone()
+    loss = ops.cross_entropy(logits, tgt)
+    loss.backward()
+    assert torch.equal(logits.detach(), keep)  # the logits are left intact
+    lf = keep.float().requires_grad_(True)
+    l_ref = F.cross_entropy(lf, tgt, ignore_index=-100)
+    l_ref.backward()
+    assert abs(float(loss) - float(l_ref)) < 2e-3 * max(1.0, abs(float(l_ref)))
+    assert _rel(logits.grad, lf.grad) < 2e-2
+    # embedding gradient scattered into an fp32 arena view
+    Vv, d = 1000, 384
+    wgt = torch.randn(Vv, d, device=dev).to(torch.bfloat16).requires_grad_(True)
+    wgt.main_grad = torch.zeros(Vv, d, device=dev, dtype=torch.float32)
+    ids = torch.randint(0, Vv, (4, 333), device=dev)
+    e = ops.embedding(ids, wgt)
+    we = torch.randn(4, 333, d, device=dev).to(torch.bfloat16)
+    (e * we).sum().backward()
+    g_ref = torch.zeros(Vv, d, device=dev).index_add_(0, ids.reshape(-1), we.float().reshape(-1, d))
+    assert wgt.grad is None and torch.allclose(wgt.main_grad, g_ref, rtol=1e-5, atol=1e-4)
+
+
 @pytest.mark.parametrize("d", [384, 1536, 2048, 128])
 def test_rmsnorm(dev, d):
     from triune_b200 import ops

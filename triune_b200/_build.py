@@ -151,7 +151,7 @@ def build_noalloc(force: bool = False, verbose: bool = False) -> Path:
     nvcc = str(Path(cuda, "bin", "nvcc"))
     srcs = [CSRC / "gla" / "gla_noalloc.cu", CSRC / "gla" / "gla_kernels.cu"]
     deps = srcs + [CSRC / "gla" / "gla_noalloc.h", CSRC / "gla" / "gla.cuh", CSRC / "common" / "ptx.cuh",
-                   CSRC / "common" / "tma_desc.h", CSRC / "common" / "per_device.h"]
+                   CSRC / "common" / "tma_desc.h", CSRC / "common" / "per_device.h", CSRC / "gla" / "gla_tiles.cuh"]
     newest = max(p.stat().st_mtime for p in deps)
     if not force and NOALLOC_SO.exists() and NOALLOC_SO.stat().st_mtime >= newest:
         return NOALLOC_SO

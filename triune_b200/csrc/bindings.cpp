@@ -179,6 +179,138 @@ void qk_prep_bwd(const Tensor& in, int64_t k_off, const Tensor& dout, Tensor& d_
                          (int)T, (int)H, (int)D, cur_stream());
 }
 
+// Cross entropy that leaves the logits intact: returns (per-row loss, grad_scale * (softmax - onehot) as a new tensor).
+std::vector<Tensor> ce_loss_grad(const Tensor& logits, const Tensor& targets, int64_t ignore_index, double grad_scale) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "logits must be [rows, V] with 16-byte rows");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0),
+              "targets must be int64 [rows]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor loss = torch::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  Tensor grad;
+  __nv_bfloat16* gp = nullptr;
+  if (grad_scale != 0.0) {
+    grad = torch::empty_strided(logits.sizes(), logits.strides(), logits.options());
+    gp = reinterpret_cast<__nv_bfloat16*>(grad.data_ptr());
+  }
+  tb::launch_ce_fwd_bwd(const_cast<__nv_bfloat16*>(bf(logits)), logits.stride(0),
+                        reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), loss.data_ptr<float>(),
+                        (int)logits.size(0), (int)logits.size(1), ignore_index, (float)grad_scale, cur_stream(), gp);
+  return {loss, grad};
+}
+
+// SwiGLU over the fused gate/up weight inside the GEMM: h [M, H] = silu(x Wg^T) * (x Wu^T) with w13 = [Wg ; Wu]
+// ([2H, K]); gu (optional, [M, 2H]) receives both pre-activations for the backward pass.
+void tc_gemm_swiglu(const Tensor& x, const Tensor& w13, Tensor& h, const c10::optional<Tensor>& gu) {
+  check_bf16_cuda(x, "x");
+  check_bf16_cuda(w13, "w13");
+  check_bf16_cuda(h, "h");
+  TORCH_CHECK(x.dim() == 2 && w13.dim() == 2 && h.dim() == 2 && x.stride(1) == 1 && w13.stride(1) == 1 && h.stride(1) == 1,
+              "tc_gemm_swiglu: 2-D operands with contiguous rows");
+  const int64_t M = x.size(0), K = x.size(1), H = h.size(1);
+  TORCH_CHECK(w13.size(0) == 2 * H && w13.size(1) == K && h.size(0) == M, "tc_gemm_swiglu: shapes");
+  c10::cuda::CUDAGuard guard(x.device());
+  tb::GemmArgs g{};
+  g.A = bf(x); g.B = bf(w13); g.C = h.data_ptr();
+  g.M = (int)M; g.N = (int)H; g.K = (int)K;
+  g.lda = x.stride(0); g.ldb = w13.stride(0); g.ldc = h.stride(0);
+  g.batch = 1; g.mode = tb::GEMM_DENSE; g.flags = tb::GF_SWIGLU; g.alpha = 1.0f; g.n_split = (int)H;
+  if (gu.has_value() && gu->defined()) {
+    check_bf16_cuda(*gu, "gu");
+    TORCH_CHECK(gu->dim() == 2 && gu->is_contiguous() && gu->size(0) == M && gu->size(1) == 2 * H, "gu must be [M, 2H] contiguous");
+    g.aux_out = reinterpret_cast<__nv_bfloat16*>(gu->data_ptr());
+  }
+  tb::launch_tc_gemm(g, cur_stream());
+}
+
+// Backward of the SwiGLU epilogue inside the GEMM that forms d(hidden): dgu [M, 2H] = (d gate | d up) from
+// dh = dy op(w) ([M, H], never written) and the saved pre-activations gu [M, 2H]. w is [H, K] (K-major) or, with
+// w_mn_major, stored [K, H] (the FFN's down projection as it is stored).
+void tc_gemm_dswiglu(const Tensor& dy, const Tensor& w, bool w_mn_major, const Tensor& gu, Tensor& dgu) {
+  check_bf16_cuda(dy, "dy");
+  check_bf16_cuda(w, "w");
+  check_bf16_cuda(gu, "gu");
+  check_bf16_cuda(dgu, "dgu");
+  TORCH_CHECK(dy.dim() == 2 && w.dim() == 2 && dy.stride(1) == 1 && w.stride(1) == 1, "tc_gemm_dswiglu: 2-D operands");
+  const int64_t M = dy.size(0), K = dy.size(1);
+  const int64_t H = w_mn_major ? w.size(1) : w.size(0);
+  TORCH_CHECK((w_mn_major ? w.size(0) : w.size(1)) == K, "tc_gemm_dswiglu: reduction dims differ");
+  TORCH_CHECK(gu.is_contiguous() && dgu.is_contiguous() && gu.size(0) == M && gu.size(1) == 2 * H && dgu.sizes() == gu.sizes(),
+              "gu and dgu must be [M, 2H] contiguous");
+  c10::cuda::CUDAGuard guard(dy.device());
+  tb::GemmArgs g{};
+  g.A = bf(dy); g.B = bf(w); g.C = dgu.data_ptr();
+  g.M = (int)M; g.N = (int)H; g.K = (int)K;
+  g.lda = dy.stride(0); g.ldb = w.stride(0); g.ldc = dgu.stride(0);
+  g.b_mn_major = w_mn_major;
+  g.batch = 1; g.mode = tb::GEMM_DENSE; g.flags = tb::GF_DSWIGLU; g.alpha = 1.0f; g.n_split = (int)H;
+  g.aux_in = bf(gu);
+  tb::launch_tc_gemm(g, cur_stream());
+}
+
+struct RowMat {
+  const __nv_bfloat16* p;
+  long long ld;
+};
+RowMat rows_of(const Tensor& t, int64_t width, const char* name) {
+  check_bf16_cuda(t, name);
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1 && t.size(1) == width && t.stride(0) % 8 == 0, name,
+              ": [rows, width] with contiguous, 16-byte aligned rows expected");
+  return RowMat{bf(t), t.stride(0)};
+}
+
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+  const int64_t rows = gate.size(0), width = gate.size(1);
+  TORCH_CHECK(width % 8 == 0 && up.size(0) == rows, "swiglu: width must be a multiple of 8");
+  RowMat g = rows_of(gate, width, "gate"), u = rows_of(up, width, "up");
+  c10::cuda::CUDAGuard guard(gate.device());
+  Tensor out = torch::empty({rows, width}, gate.options());
+  tb::launch_swiglu_fwd(g.p, g.ld, u.p, u.ld, bfm(out), width, rows, (int)width, cur_stream());
+  return out;
+}
+
+std::vector<Tensor> swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dh) {
+  const int64_t rows = gate.size(0), width = gate.size(1);
+  TORCH_CHECK(width % 8 == 0, "swiglu: width must be a multiple of 8");
+  RowMat g = rows_of(gate, width, "gate"), u = rows_of(up, width, "up"), d = rows_of(dh, width, "dh");
+  c10::cuda::CUDAGuard guard(gate.device());
+  // the two gradients are the halves of one [rows, 2 * width] tensor, so a fused gate/up projection gets its
+  // output gradient without a concatenation
+  Tensor dgu = torch::empty({rows, 2 * width}, gate.options());
+  __nv_bfloat16* base = bfm(dgu);
+  tb::launch_swiglu_bwd(g.p, g.ld, u.p, u.ld, d.p, d.ld, base, 2 * width, base + width, 2 * width, rows, (int)width,
+                        cur_stream());
+  return {dgu.slice(1, 0, width), dgu.slice(1, width, 2 * width), dgu};
+}
+
+// x: [rows = B*T, H*D] bf16 (row pitch free); cos/sin: fp32 [T, D/2] contiguous.
+Tensor rope_apply(const Tensor& x, const Tensor& cs, const Tensor& sn, int64_t T, int64_t H, int64_t D, bool transpose) {
+  RowMat xm = rows_of(x, H * D, "x");
+  TORCH_CHECK(D % 16 == 0 && cs.scalar_type() == at::kFloat && sn.scalar_type() == at::kFloat && cs.is_contiguous() &&
+                  sn.is_contiguous() && cs.numel() == T * (D / 2) && sn.numel() == T * (D / 2),
+              "rope: cos/sin must be fp32 [T, D/2] and D a multiple of 16");
+  TORCH_CHECK(x.size(0) % T == 0, "rope: rows must be a multiple of T");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), H * D}, x.options());
+  tb::launch_rope(xm.p, xm.ld, bfm(y), H * D, cs.data_ptr<float>(), sn.data_ptr<float>(), x.size(0), (int)T, (int)H, (int)D,
+                  transpose, cur_stream());
+  return y;
+}
+
+// grad [V, d] fp32 += scatter of dy [tokens, d] bf16 by ids [tokens] int64.
+void embedding_bwd(const Tensor& dy, const Tensor& ids, Tensor& grad) {
+  check_bf16_cuda(dy, "dy");
+  TORCH_CHECK(dy.dim() == 2 && dy.stride(1) == 1 && dy.stride(0) % 4 == 0 && dy.size(1) % 4 == 0, "dy must be [tokens, d], d % 4 == 0");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.numel() == dy.size(0), "ids must be int64 [tokens]");
+  TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.dim() == 2 &&
+                  grad.size(1) == dy.size(1) && (reinterpret_cast<uintptr_t>(grad.data_ptr()) & 15) == 0,
+              "grad must be a contiguous, 16-byte aligned fp32 [V, d]");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(dy.data_ptr()) & 7) == 0, "dy must be 8-byte aligned");
+  c10::cuda::CUDAGuard guard(dy.device());
+  tb::launch_embedding_bwd(bf(dy), dy.stride(0), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                           grad.data_ptr<float>(), dy.size(0), (int)dy.size(1), grad.size(0), cur_stream());
+}
+
 Tensor ce_fwd_bwd(Tensor& logits, const Tensor& targets, int64_t ignore_index, double grad_scale) {
   check_bf16_cuda(logits, "logits");
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [rows, V]");
@@ -412,6 +544,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_prep_fwd", &qk_prep_fwd);
   m.def("qk_prep_bwd", &qk_prep_bwd);
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("ce_loss_grad", &ce_loss_grad);
+  m.def("tc_gemm_swiglu", &tc_gemm_swiglu);
+  m.def("tc_gemm_dswiglu", &tc_gemm_dswiglu);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope_apply", &rope_apply);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("colsum", &colsum);
   m.def("gather_rows", &gather_rows);
   m.def("combine_rows", &combine_rows);

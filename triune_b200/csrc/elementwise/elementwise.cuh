@@ -28,8 +28,24 @@ void launch_qk_prep_bwd(const __nv_bfloat16* in, long long in_ld, int k_col_offs
 
 // Row-wise cross entropy over bf16 logits [rows, V] (row stride ld). Writes per-row loss (0 for ignored
 // rows) and, when grad_scale != 0, overwrites the logits with grad_scale * (softmax - onehot).
+// With grad_dst (a [rows, V] bf16 buffer of the same row stride) the gradient goes there and the logits stay intact.
 void launch_ce_fwd_bwd(__nv_bfloat16* logits, long long ld, const long long* targets, float* row_loss, int rows, int V,
-                       long long ignore_index, float grad_scale, cudaStream_t s);
+                       long long ignore_index, float grad_scale, cudaStream_t s, __nv_bfloat16* grad_dst = nullptr);
+
+// out = silu(gate) * up over rows of `width` bf16 (width % 8 == 0); every operand has its own row pitch.
+void launch_swiglu_fwd(const __nv_bfloat16* gate, long long ld_g, const __nv_bfloat16* up, long long ld_u,
+                       __nv_bfloat16* out, long long ld_o, long long rows, int width, cudaStream_t s);
+// d(gate) = dh * up * silu'(gate), d(up) = dh * silu(gate).
+void launch_swiglu_bwd(const __nv_bfloat16* gate, long long ld_g, const __nv_bfloat16* up, long long ld_u,
+                       const __nv_bfloat16* dh, long long ld_d, __nv_bfloat16* dgate, long long ld_dg,
+                       __nv_bfloat16* dup, long long ld_du, long long rows, int width, cudaStream_t s);
+// Half-split rotary embedding of x [rows = B*T, H, D] with cos/sin [T, D/2] fp32; `transpose` applies the inverse
+// rotation (the gradient). D % 16 == 0.
+void launch_rope(const __nv_bfloat16* x, long long ld_x, __nv_bfloat16* y, long long ld_y, const float* cs,
+                 const float* sn, long long rows, int T, int H, int D, bool transpose, cudaStream_t s);
+// Embedding gradient: grad[ids[n], :] += dy[n, :] (fp32 [V, width], 16-byte aligned rows; width % 4 == 0).
+void launch_embedding_bwd(const __nv_bfloat16* dy, long long ld, const long long* ids, float* grad, long long tokens,
+                          int width, long long V, cudaStream_t s);
 
 // dst[r] = scale[r] * src[row_src[r]] (zero row when row_src[r] < 0). Rows of `width` bf16 (width % 8 == 0).
 void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,

@@ -56,18 +56,22 @@ constexpr int CE_THREADS = 256;
 __global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld,
                                                                 const long long* __restrict__ targets,
                                                                 float* __restrict__ row_loss, int V,
-                                                                long long ignore_index, float grad_scale) {
+                                                                long long ignore_index, float grad_scale,
+                                                                __nv_bfloat16* grad_dst) {
   __shared__ float red[CE_THREADS / 32];
   const long long row = blockIdx.x;
   __nv_bfloat16* lp = logits + row * ld;
+  // gradient destination: the logits themselves (in place) unless a separate [rows, V] buffer of the same pitch is given
+  __nv_bfloat16* gp = grad_dst != nullptr ? grad_dst + row * ld : lp;
+  uint4* gv = reinterpret_cast<uint4*>(gp);
   const long long tgt = targets[row];
   const int nvec = V >> 3;
   uint4* lv = reinterpret_cast<uint4*>(lp);
   if (tgt == ignore_index) {
     if (threadIdx.x == 0) row_loss[row] = 0.f;
     if (grad_scale != 0.f) {
-      for (int v = threadIdx.x; v < nvec; v += CE_THREADS) lv[v] = make_uint4(0, 0, 0, 0);
-      for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) lp[i] = __float2bfloat16(0.f);
+      for (int v = threadIdx.x; v < nvec; v += CE_THREADS) gv[v] = make_uint4(0, 0, 0, 0);
+      for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) gp[i] = __float2bfloat16(0.f);
     }
     return;
   }
@@ -125,12 +129,12 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* _
     o.y = pack_bf16x2(f[2], f[3]);
     o.z = pack_bf16x2(f[4], f[5]);
     o.w = pack_bf16x2(f[6], f[7]);
-    lv[v] = o;
+    gv[v] = o;
   }
   for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) {
     float f = __expf(__bfloat162float(lp[i]) - gmx) * inv;
     if (i == tgt) f -= grad_scale;
-    lp[i] = __float2bfloat16(f);
+    gp[i] = __float2bfloat16(f);
   }
 }
 
@@ -420,9 +424,9 @@ inline int flat_grid(long long n, int threads = 256) {
 }  // namespace
 
 void launch_ce_fwd_bwd(__nv_bfloat16* logits, long long ld, const long long* targets, float* row_loss, int rows, int V,
-                       long long ignore_index, float grad_scale, cudaStream_t s) {
+                       long long ignore_index, float grad_scale, cudaStream_t s, __nv_bfloat16* grad_dst) {
   if (rows == 0) return;
-  ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, s>>>(logits, ld, targets, row_loss, V, ignore_index, grad_scale);
+  ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, s>>>(logits, ld, targets, row_loss, V, ignore_index, grad_scale, grad_dst);
 }
 
 void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,

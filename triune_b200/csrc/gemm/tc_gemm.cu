@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const KParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int NOUT = (EPI == EPI_SWIGLU) ? BN / 2 : BN;  // output columns per tile (SwiGLU: gate | up side by side)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         Tile tl = decode_tile(p, t);
         if (!tl.valid) continue;
-        const int n0 = tl.n0 * BN;
+        const int n0 = tl.n0 * NOUT;
         for (int it = 0; it < tl.k_iters; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             report(p, ST_TIMEOUT_EMPTY);
@@ -105,7 +106,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           } else {
             tma_load_3d(a_dst, &tmA, &full[stage], k0, tl.m0, tl.ba);
           }
-          if (B_MN) {
+          if constexpr (EPI == EPI_SWIGLU) {
+            // gate rows [n0, n0 + BN/2) and up rows [n_split + n0, ...) of the fused weight, side by side in the tile
+            tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, tl.bb);
+            tma_load_3d(b_dst + (BN / 2) * 128, &tmB, &full[stage], k0, p.n_split + n0, tl.bb);
+          } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_3d(b_dst + j * (BK * 128), &tmB, &full[stage], n0 + 64 * j, k0, tl.bb);
@@ -210,8 +215,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
-      epilogue_tile<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * BN, BN, tl.n0 * BN, tl.m0, lane_base, col_half, lane,
-                         my_stage, buf);
+      run_epilogue<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * BN, BN, tl.n0 * NOUT, tl.m0, lane_base, col_half, lane,
+                        my_stage, buf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -261,6 +266,10 @@ void dispatch_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const
   if constexpr (!A_MN) {  // the activation epilogues follow row-major activations
     if (epi == EPI_GELU) return launch_variant<BN, A_MN, B_MN, EPI_GELU>(tmA, tmB, tmC, tmAux, kp, grid, s);
     if (epi == EPI_MULAUX) return launch_variant<BN, A_MN, B_MN, EPI_MULAUX>(tmA, tmB, tmC, tmAux, kp, grid, s);
+    if (epi == EPI_DSWIGLU) return launch_variant<BN, A_MN, B_MN, EPI_DSWIGLU>(tmA, tmB, tmC, tmAux, kp, grid, s);
+    if constexpr (!B_MN) {
+      if (epi == EPI_SWIGLU) return launch_variant<BN, A_MN, B_MN, EPI_SWIGLU>(tmA, tmB, tmC, tmAux, kp, grid, s);
+    }
   }
   throw std::runtime_error("tc_gemm: activation epilogues need a K-major A operand");
 }
@@ -306,6 +315,15 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0) throw std::runtime_error("tc_gemm: C must be 16-byte aligned");
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
+  const bool swiglu = (a.flags & GF_SWIGLU) != 0, dswiglu = (a.flags & GF_DSWIGLU) != 0;
+  if (swiglu || dswiglu) {
+    if (a.mode != GEMM_DENSE || a.batch > 1 || a.a_mn_major || (a.flags & (GF_OUT_F32 | GF_ACCUMULATE | GF_GELU | GF_DGELU)) ||
+        a.bias != nullptr || a.row_scale != nullptr || (swiglu && dswiglu))
+      throw std::runtime_error("tc_gemm: the SwiGLU epilogues take dense K-major activations, bf16 output, no bias");
+    if (a.n_split != a.N || a.N % 32 != 0) throw std::runtime_error("tc_gemm: SwiGLU needs N == n_split, a multiple of 32");
+    if (swiglu && a.b_mn_major) throw std::runtime_error("tc_gemm: the fused gate/up weight must be K-major");
+    if (dswiglu && a.aux_in == nullptr) throw std::runtime_error("tc_gemm: gate/up rows missing");
+  }
 
   {
     static const bool pairs = [] {
@@ -324,11 +342,15 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
     }();
     if (forced == 64 || forced == 128 || forced == 192 || forced == 256) BN = forced;
   }
+  // SwiGLU forward: a tile of BN accumulator columns yields BN / 2 output columns
+  if (swiglu) BN = (a.N % 128 == 0) ? 256 : ((a.N % 64 == 0) ? 128 : 64);
+  const int n_out = swiglu ? BN / 2 : BN;
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
   kp.mode = a.mode; kp.flags = a.flags; kp.batch = a.batch < 1 ? 1 : a.batch;
   kp.num_m = (a.M + BM - 1) / BM;
-  kp.num_n = (a.N + BN - 1) / BN;
+  kp.num_n = (a.N + n_out - 1) / n_out;
+  kp.n_split = a.n_split;
   kp.ldc = a.ldc; kp.strideC = a.strideC;
   kp.a_batched = a.strideA != 0; kp.b_batched = a.strideB != 0;
   kp.alpha = a.alpha;
@@ -379,22 +401,30 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
     const uint64_t krows = (a.mode == GEMM_GROUPED_K) ? a_rows_total : (uint64_t)a.K;
     tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, krows, nbB, (uint64_t)a.ldb * 2ull, sB, 64, BK);
   } else {
-    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull, sB, BK, (uint32_t)BN);
+    // SwiGLU forward: B is the fused [2 N, K] weight, fetched as two boxes of BN / 2 rows
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)(swiglu ? 2 * a.N : a.N), nbB,
+                       (uint64_t)a.ldb * 2ull, sB, BK, (uint32_t)n_out);
   }
   // output maps: rows of 64 bytes (32 bf16 / 16 fp32) x 32 rows, one box per epilogue warp and column chunk
   const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
   const int c_elem = c_f32 ? 4 : 2;
   const uint64_t c_batches = (a.mode == GEMM_GROUPED_M) ? 1 : (uint64_t)kp.batch;
   const uint64_t c_bstride = (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
+  const uint64_t c_cols = dswiglu ? 2ull * (uint64_t)a.N : (uint64_t)a.N;  // d(gate) | d(up)
   CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
-                                 (uint64_t)a.N, (uint64_t)a.M, c_batches, (uint64_t)a.ldc * c_elem, c_bstride,
+                                 c_cols, (uint64_t)a.M, c_batches, (uint64_t)a.ldc * c_elem, c_bstride,
                                  c_f32 ? 16 : 32, 32);
   CUtensorMap tmAux = tmC;
-  if (a.aux_out != nullptr)
+  if (swiglu && a.aux_out != nullptr)  // gate | up pre-activations, [M, 2 N] contiguous
+    tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2ull * (uint64_t)a.N, (uint64_t)a.M, 1,
+                         4ull * (uint64_t)a.N, 4ull * (uint64_t)a.N * (uint64_t)a.M, 32, 32);
+  else if (a.aux_out != nullptr)
     tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.M, c_batches,
                          (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 32, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
-  const int epi = (kp.flags & GF_GELU) ? EPI_GELU : ((kp.flags & GF_DGELU) ? EPI_MULAUX : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN));
+  const int epi = swiglu ? EPI_SWIGLU
+                  : (dswiglu ? EPI_DSWIGLU
+                     : ((kp.flags & GF_GELU) ? EPI_GELU : ((kp.flags & GF_DGELU) ? EPI_MULAUX : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN))));
   if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
   else if (BN == 192) dispatch_major<192>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);
   else if (BN == 128) dispatch_major<128>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);

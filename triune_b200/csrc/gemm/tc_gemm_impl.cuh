@@ -46,6 +46,7 @@ struct KParams {
   int group_m;          // tile order: blocks of group_m row tiles x all column tiles (see raster)
   int splits;           // split-K factor (dense mode, fp32 accumulate only)
   int iters_per_split;  // K iterations (of 64) handled by one split
+  int n_split;          // SwiGLU epilogues: column offset of the "up" half (= FFN hidden width)
 };
 
 struct Tile {
@@ -132,7 +133,11 @@ __device__ __forceinline__ void report(const KParams& p, int code) {
 //   EPI_PLAIN_F32  the same with an fp32 output (weight-gradient accumulation, split-K)
 //   EPI_GELU       bias, tanh-GELU, bf16 output; optionally GELU'(pre-activation) as a second bf16 output
 //   EPI_MULAUX     output = alpha * acc * aux_in (the backward of EPI_GELU: aux_in holds GELU')
-enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3 };
+//   EPI_SWIGLU     accumulator columns [0, n/2) hold gate, [n/2, n) hold up pre-activations of the SAME output columns
+//                  (the producer loads the two row blocks of the fused gate/up weight side by side); output =
+//                  silu(gate) * up, and optionally both pre-activations go out as bf16 (aux_out, [M, 2 * n_split])
+//   EPI_DSWIGLU    acc = d(hidden); reads gate/up from aux_in and writes d(gate), d(up) into C ([M, 2 * n_split])
+enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3, EPI_SWIGLU = 4, EPI_DSWIGLU = 5 };
 
 // One accumulator tile (128 rows x n_cols fp32 in TMEM at tmem_acc) through the epilogue EPI and out to global
 // memory. Called by the eight epilogue warps of a CTA: a warp can only read the TMEM lanes of its quarter
@@ -334,6 +339,121 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
     }
     if (timed) atomicAdd(reinterpret_cast<unsigned long long*>(p.dbg + 7), (unsigned long long)(clock64() - tk0));  // whole chunk
   }
+}
+
+// Stage one 32-row x 32-column bf16 chunk (16 packed pairs per lane) and hand it to TMA.
+__device__ __forceinline__ void epi_store_chunk(const CUtensorMap* tm, const uint32_t (&q)[16], int col, int row,
+                                                int batch, int lane, uint8_t* my_stage, uint32_t& buf) {
+  uint8_t* st = epi_claim(my_stage, buf, lane);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(st + epi_off(lane, j)) = make_uint4(q[j * 4 + 0], q[j * 4 + 1], q[j * 4 + 2], q[j * 4 + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_3d(tm, st, col, row, batch);
+    tma_store_commit();
+  }
+}
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+// SwiGLU forward epilogue: n_cols accumulator columns = [gate (n_cols/2) | up (n_cols/2)] of output columns
+// [n0, n0 + n_cols/2). Same warp roles and staging as epilogue_tile.
+__device__ __forceinline__ void epilogue_tile_swiglu(const KParams& p, const Tile& tl, const CUtensorMap* tmC,
+                                                     const CUtensorMap* tmAux, uint32_t tmem_acc, int n_cols, int n0,
+                                                     int m_base, int lane_base, int col_half, int lane,
+                                                     uint8_t* my_stage, uint32_t& buf) {
+  const int half = n_cols >> 1;
+#pragma unroll 1
+  for (int c = col_half * 32; c < half; c += 64) {
+    if (n0 + c >= p.N) break;
+    uint32_t rg[32], ru[32];
+    if (tl.k_iters > 0) {
+      const uint32_t taddr = tmem_acc + ((uint32_t)lane_base << 16) + c;
+      tmem_ld_32x32b_x32(taddr, rg);
+      tmem_ld_32x32b_x32(taddr + half, ru);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) rg[i] = ru[i] = 0u;
+    }
+    uint32_t q[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float g0 = __uint_as_float(rg[2 * i]), g1 = __uint_as_float(rg[2 * i + 1]);
+      const float u0 = __uint_as_float(ru[2 * i]), u1 = __uint_as_float(ru[2 * i + 1]);
+      q[i] = pack_bf16x2(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+    }
+    epi_store_chunk(tmC, q, n0 + c, m_base + lane_base, 0, lane, my_stage, buf);
+    if (p.aux_out) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__uint_as_float(rg[2 * i]), __uint_as_float(rg[2 * i + 1]));
+      epi_store_chunk(tmAux, q, n0 + c, m_base + lane_base, 0, lane, my_stage, buf);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__uint_as_float(ru[2 * i]), __uint_as_float(ru[2 * i + 1]));
+      epi_store_chunk(tmAux, q, p.n_split + n0 + c, m_base + lane_base, 0, lane, my_stage, buf);
+    }
+  }
+}
+
+// SwiGLU backward epilogue: acc = d(hidden) for output columns [n0, n0 + n_cols); with g, u read from aux_in
+// ([M, 2 * n_split], row pitch ldc) it writes d(gate) = dh * u * silu'(g) and d(up) = dh * silu(g) into C
+// ([M, 2 * n_split]) at columns n0.. and n_split + n0...
+__device__ __forceinline__ void epilogue_tile_dswiglu(const KParams& p, const Tile& tl, const CUtensorMap* tmC,
+                                                      uint32_t tmem_acc, int n_cols, int n0, int m_base, int lane_base,
+                                                      int col_half, int lane, uint8_t* my_stage, uint32_t& buf) {
+  const int gm = m_base + lane_base + lane;
+  const bool row_ok = gm < p.M;
+  const long long c_off = (long long)gm * p.ldc;
+#pragma unroll 1
+  for (int c = col_half * 32; c < n_cols; c += 64) {
+    if (n0 + c >= p.N) break;
+    uint4 gv[4], uv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + c + j * 8;
+      const bool ok = row_ok && gn < p.N;
+      gv[j] = ok ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + gn) : make_uint4(0u, 0u, 0u, 0u);
+      uv[j] = ok ? *reinterpret_cast<const uint4*>(p.aux_in + c_off + p.n_split + gn) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    uint32_t r[32];
+    if (tl.k_iters > 0) {
+      tmem_ld_32x32b_x32(tmem_acc + ((uint32_t)lane_base << 16) + c, r);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = 0u;
+    }
+    uint32_t qg[16], qu[16];
+    const uint32_t* gp = reinterpret_cast<const uint32_t*>(gv);
+    const uint32_t* up = reinterpret_cast<const uint32_t*>(uv);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float g0, g1, u0, u1;
+      unpack_f2(bf16x2_to_f2(gp[i]), g0, g1);
+      unpack_f2(bf16x2_to_f2(up[i]), u0, u1);
+      const float d0 = __uint_as_float(r[2 * i]) * p.alpha, d1 = __uint_as_float(r[2 * i + 1]) * p.alpha;
+      const float s0 = sigmoid_f(g0), s1 = sigmoid_f(g1);
+      qg[i] = pack_bf16x2(d0 * u0 * s0 * (1.0f + g0 * (1.0f - s0)), d1 * u1 * s1 * (1.0f + g1 * (1.0f - s1)));
+      qu[i] = pack_bf16x2(d0 * g0 * s0, d1 * g1 * s1);
+    }
+    epi_store_chunk(tmC, qg, n0 + c, m_base + lane_base, 0, lane, my_stage, buf);
+    epi_store_chunk(tmC, qu, p.n_split + n0 + c, m_base + lane_base, 0, lane, my_stage, buf);
+  }
+}
+
+// One call site for every epilogue kind.
+template <int EPI>
+__device__ __forceinline__ void run_epilogue(const KParams& p, const Tile& tl, const CUtensorMap* tmC,
+                                             const CUtensorMap* tmAux, uint32_t tmem_acc, int n_cols, int n0, int m_base,
+                                             int lane_base, int col_half, int lane, uint8_t* my_stage, uint32_t& buf) {
+  if constexpr (EPI == EPI_SWIGLU)
+    epilogue_tile_swiglu(p, tl, tmC, tmAux, tmem_acc, n_cols, n0, m_base, lane_base, col_half, lane, my_stage, buf);
+  else if constexpr (EPI == EPI_DSWIGLU)
+    epilogue_tile_dswiglu(p, tl, tmC, tmem_acc, n_cols, n0, m_base, lane_base, col_half, lane, my_stage, buf);
+  else
+    epilogue_tile<EPI>(p, tl, tmC, tmAux, tmem_acc, n_cols, n0, m_base, lane_base, col_half, lane, my_stage, buf);
 }
 
 }  // namespace

@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   using Cfg = PairCfg<NCFG>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NACC = Cfg::NACC;
+  constexpr int NOUT = (EPI == EPI_SWIGLU) ? NCFG / 2 : NCFG;  // output columns per pair tile
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int t = cluster_id; t < pair_tiles && ok; t += num_clusters) {
         const Tile tl = decode_pair_tile(p, t, num_mp);
         if (!tl.valid) continue;
-        const int n0 = tl.n0 * NCFG;
+        const int n0 = tl.n0 * NOUT;
         const int m0 = tl.m0 + (int)rank * BM;
         for (int it = 0; it < tl.k_iters; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
@@ -160,7 +161,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < Cfg::B_BOXES; ++j) {
             // this CTA's half of B: boxes 0,1 belong to the N = 256 MMA, box 2 (NCFG = 384) to the N = 128 MMA
-            const int nb = (j < 2) ? (n0 + 128 * (int)rank + 64 * j) : (n0 + 256 + 64 * (int)rank);
+            // SwiGLU forward: the even CTA holds the 128 gate rows, the odd CTA the 128 up rows of the same outputs
+            const int nb = (EPI == EPI_SWIGLU) ? ((rank == 0 ? n0 : p.n_split + n0) + 64 * j)
+                           : ((j < 2) ? (n0 + 128 * (int)rank + 64 * j) : (n0 + 256 + 64 * (int)rank));
             if (B_MN)
               tma_load_3d_pair(b_dst + j * (BK * 128), &tmB, bar, nb, k0, tl.bb);
             else
@@ -265,8 +268,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
-      epilogue_tile<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * 256, NCFG, tl.n0 * NCFG, tl.m0 + (int)rank * BM,
-                         lane_base, col_half, lane, my_stage, buf);
+      run_epilogue<EPI>(p, tl, &tmC, &tmAux, tmem_base + acc * 256, NCFG, tl.n0 * NOUT, tl.m0 + (int)rank * BM,
+                        lane_base, col_half, lane, my_stage, buf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -325,6 +328,15 @@ template <int NCFG, bool A_MN, bool B_MN>
 void dispatch_pair_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmAux, const KParams& kp, int num_mp, int pair_tiles, int clusters,
                        cudaStream_t s) {
+  if constexpr (NCFG == 256 && !A_MN) {
+    if (epi == EPI_DSWIGLU)
+      return launch_pair_variant<NCFG, A_MN, B_MN, EPI_DSWIGLU>(tmA, tmB, tmC, tmAux, kp, num_mp, pair_tiles, clusters, s);
+    if constexpr (!B_MN) {
+      if (epi == EPI_SWIGLU)
+        return launch_pair_variant<NCFG, A_MN, B_MN, EPI_SWIGLU>(tmA, tmB, tmC, tmAux, kp, num_mp, pair_tiles, clusters, s);
+    }
+  }
+  if (epi == EPI_SWIGLU || epi == EPI_DSWIGLU) throw std::runtime_error("tc_gemm_pair: unsupported SwiGLU variant");
   if (epi == EPI_PLAIN_F32)
     launch_pair_variant<NCFG, A_MN, B_MN, EPI_PLAIN_F32>(tmA, tmB, tmC, tmAux, kp, num_mp, pair_tiles, clusters, s);
   else
@@ -377,16 +389,24 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
     const char* e = std::getenv("TRIUNE_GEMM_PAIR_MIN_K");  // tuning knob: shortest reduction handed to CTA pairs
     return e ? std::atoll(e) : 768ll;
   }();
+  const bool swiglu = (a.flags & GF_SWIGLU) != 0, dswiglu = (a.flags & GF_DSWIGLU) != 0;
   int ncfg = 0;
-  if (a.N % 384 == 0 && k_each >= (min_k < 1024 ? 1024 : min_k)) ncfg = 384;  // single-buffered: long reductions only
+  if (swiglu) {
+    // 256 accumulator columns = 128 gate + 128 up columns of 128 outputs
+    if (a.N % 128 == 0 && k_each >= min_k && !a.a_mn_major && !a.b_mn_major) ncfg = 256;
+  } else if (dswiglu) {
+    if (a.N % 256 == 0 && k_each >= min_k && !a.a_mn_major) ncfg = 256;
+  } else if (a.N % 384 == 0 && k_each >= (min_k < 1024 ? 1024 : min_k)) ncfg = 384;  // single-buffered: long reductions only
   else if (a.N % 256 == 0 && k_each >= min_k) ncfg = 256;
   if (ncfg == 0) return false;
+  const int n_out = swiglu ? ncfg / 2 : ncfg;
 
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
   kp.mode = a.mode; kp.flags = a.flags; kp.batch = groups;
   kp.num_m = (a.M + BM - 1) / BM;
-  kp.num_n = a.N / ncfg;
+  kp.num_n = a.N / n_out;
+  kp.n_split = a.n_split;
   kp.ldc = a.ldc; kp.strideC = a.strideC;
   kp.a_batched = 0; kp.b_batched = 0;
   kp.alpha = a.alpha;
@@ -429,17 +449,20 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
     tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.K, nbB, (uint64_t)a.ldb * 2ull,
                        sB, 64, BK);
   else
-    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.N, nbB, (uint64_t)a.ldb * 2ull,
-                       sB, BK, 64);
+    tmB = make_tmap_3d(a.B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)(swiglu ? 2 * a.N : a.N), nbB,
+                       (uint64_t)a.ldb * 2ull, sB, BK, 64);
   const bool c_f32 = (kp.flags & GF_OUT_F32) != 0;
   const int c_elem = c_f32 ? 4 : 2;
   const uint64_t c_bstride = (groups > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * c_elem;
   CUtensorMap tmC = make_tmap_3d(a.C, c_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, c_elem,
-                                 (uint64_t)a.N, (uint64_t)a.M, (uint64_t)groups, (uint64_t)a.ldc * c_elem, c_bstride,
-                                 c_f32 ? 16 : 32, 32);
+                                 dswiglu ? 2ull * (uint64_t)a.N : (uint64_t)a.N, (uint64_t)a.M, (uint64_t)groups,
+                                 (uint64_t)a.ldc * c_elem, c_bstride, c_f32 ? 16 : 32, 32);
   CUtensorMap tmAux = tmC;
+  if (swiglu && a.aux_out != nullptr)  // gate | up pre-activations, [M, 2 N] contiguous
+    tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2ull * (uint64_t)a.N, (uint64_t)a.M, 1,
+                         4ull * (uint64_t)a.N, 4ull * (uint64_t)a.N * (uint64_t)a.M, 32, 32);
   const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
-  const int epi = c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN;
+  const int epi = swiglu ? EPI_SWIGLU : (dswiglu ? EPI_DSWIGLU : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN));
   if (ncfg == 256)
     dispatch_pair_major<256>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, num_mp, pair_tiles, clusters, stream);
   else

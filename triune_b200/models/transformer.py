@@ -289,7 +289,7 @@ class TriuneTransformer(nn.Module):
                     return self.token_embed(remapped)
                 if tok is not None:
                     return self.embed_compressed(input_ids, tok)
-        return self.token_embed(input_ids)
+        return ops.embedding(input_ids, self.token_embed.weight)
 
     # ------------------------------------------------------------------ layer execution
     def _forward_block(self, layer, x, return_exit, cache=None, update_stats=True, exit_decider=None,
@@ -469,7 +469,7 @@ class TriuneTransformer(nn.Module):
     def forward_hidden_all_exits(self, input_ids, update_stats=False):
         """Hidden states at the three exits (before the exit norms) plus router outputs."""
         B = input_ids.shape[0]
-        x = self.token_embed(input_ids)
+        x = ops.embedding(input_ids, self.token_embed.weight)
         P = self.router_prefix_layers
         x_prefix, _ = self._run_layers(x, 0, P, update_stats=update_stats)
         route_logits, _, choice, bal = self._route(x_prefix, None, B, x.device)
@@ -490,7 +490,7 @@ class TriuneTransformer(nn.Module):
         With ``return_route`` the depth router is evaluated on the prefix output of the same pass and
         ``(loss, route_logits, balance_loss)`` is returned; the route logits keep their graph, so a router loss
         added by the caller trains the router and the prefix layers (the ``dynamic`` training mode)."""
-        x = self.token_embed(input_ids)
+        x = ops.embedding(input_ids, self.token_embed.weight)
         end = self.exit_layers[force_depth] + 1
         route_logits = bal = None
         if return_route:

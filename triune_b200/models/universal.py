@@ -49,9 +49,7 @@ class SwiGLUFFN(nn.Module):
             sd[prefix + "down.weight"] = sd.pop(prefix + "down_proj.weight")
 
     def forward(self, x):
-        gu = ops.linear(x, self.gate_up)
-        h = ops.swiglu(gu[..., : self.hidden], gu[..., self.hidden:])
-        return ops.linear(h, self.down.weight)
+        return ops.swiglu_mlp(x, self.gate_up, self.down.weight)
 
 
 class UniversalBlock(nn.Module):
@@ -116,7 +114,7 @@ class UniversalDenseTransformer(nn.Module):
             l._use_gradient_checkpointing = flag
 
     def hidden_states(self, input_ids=None, cache=None, inputs_embeds=None):
-        x = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        x = inputs_embeds if inputs_embeds is not None else ops.embedding(input_ids, self.embed_tokens.weight)
         new_cache = list(cache) if cache is not None else None
         for i, layer in enumerate(self.layers):
             lc = None

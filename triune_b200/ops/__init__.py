@@ -225,8 +225,93 @@ def gelu_tanh(x):
     return ref.gelu_tanh(x)
 
 
+class _SwiGLUFn(torch.autograd.Function):
+    """silu(gate) * up for separate [.., width] tensors (either may be a column slice of a wider matrix)."""
+
+    @staticmethod
+    def forward(ctx, gate, up):
+        w = gate.shape[-1]
+        g2, u2 = gate.reshape(-1, w), up.reshape(-1, w)
+        ctx.save_for_backward(g2, u2)
+        ctx.shape = gate.shape
+        out = _ext.ext().swiglu_fwd(g2, u2)
+        _tick()
+        return out.view(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dh):
+        g2, u2 = ctx.saved_tensors
+        d2 = dh.reshape(-1, g2.shape[-1])
+        if not _rows_ok(d2):
+            d2 = d2.contiguous()
+        dg, du, _ = _ext.ext().swiglu_bwd(g2, u2, d2)
+        _tick()
+        return dg.view(ctx.shape), du.view(ctx.shape)
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    return (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
 def swiglu(gate, up):
+    """silu(gate) * up (``triune/kernels/fast_swiglu.py:19-45``)."""
+    if (_ext.use_kernels(gate, up) and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16
+            and gate.shape == up.shape and gate.shape[-1] % 8 == 0
+            and _rows_ok(gate.reshape(-1, gate.shape[-1])) and _rows_ok(up.reshape(-1, up.shape[-1]))):
+        return _SwiGLUFn.apply(gate, up)
     return ref.swiglu(gate, up)
+
+
+class _SwiGLUMLPFn(torch.autograd.Function):
+    """down( silu(x Wg^T) * (x Wu^T) ) with w13 = [Wg ; Wu] ([2H, d]) and w2 = [d, H].
+
+    Forward: ONE GEMM over the fused weight whose epilogue forms silu(gate) * up from the two halves of its accumulator
+    tile (the [M, 2H] pre-activations go out once, for the backward pass), then the down projection. Backward: the GEMM
+    that forms d(hidden) = dy w2 applies the SwiGLU derivative in its epilogue and writes d(gate | up) directly, which
+    feeds the input-gradient and weight-gradient GEMMs of the fused weight. No stand-alone elementwise pass remains."""
+
+    @staticmethod
+    def forward(ctx, x, w13, w2):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not _tma_ok(x2):
+            x2 = x2.contiguous()
+        M, H = x2.shape[0], w13.shape[0] // 2
+        train = _wants_grad(x, w13, w2)
+        h = torch.empty(M, H, device=x.device, dtype=x.dtype)
+        gu = torch.empty(M, 2 * H, device=x.device, dtype=x.dtype) if train else None
+        _ext.ext().tc_gemm_swiglu(x2, w13, h, gu)
+        _tick()
+        y = gemm(h, w2)
+        if train:
+            ctx.save_for_backward(x2, w13, w2, gu, h)
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w13, w2, gu, h = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w2.shape[0])
+        if not _tma_ok(dy2):
+            dy2 = dy2.contiguous()
+        dgu = torch.empty_like(gu)
+        _ext.ext().tc_gemm_dswiglu(dy2, w2, True, gu, dgu)   # d(hidden) = dy @ w2, w2 stored [d, H] = [K, N]
+        _tick()
+        dw2 = _accumulate_weight_grad(w2, dy2, h)
+        dx = gemm(dgu, w13, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        dw13 = _accumulate_weight_grad(w13, dgu, x2)
+        return dx, dw13, dw2
+
+
+def swiglu_mlp(x, w13, w2):
+    """SwiGLU feed-forward over a fused gate/up weight: ``down(silu(x Wg^T) * (x Wu^T))``."""
+    H = w13.shape[0] // 2
+    if (_ext.use_kernels(x, w13, w2) and x.dtype == torch.bfloat16 and H % 32 == 0 and w13.shape[1] % 8 == 0
+            and w2.shape[0] % 8 == 0 and w13.is_contiguous() and w2.is_contiguous()):
+        return _SwiGLUMLPFn.apply(x, w13, w2)
+    gu = F.linear(x, w13)
+    return F.linear(ref.swiglu(gu[..., :H], gu[..., H:]), w2)
 
 
 # ----------------------------------------------------------------------------
@@ -311,8 +396,79 @@ def rope_tables(seq_len, head_dim, base=10000.0, offset=0, device=None):
     return ref.rope_tables(seq_len, head_dim, base, offset, device)
 
 
+class _RoPEFn(torch.autograd.Function):
+    """Half-split rotation of [B, T, H, D] by [T, D/2] tables; the gradient is the inverse rotation."""
+
+    @staticmethod
+    def forward(ctx, x, cos_half, sin_half):
+        B, T, H, D = x.shape
+        x2 = x.reshape(B * T, H * D)
+        if not _rows_ok(x2):
+            x2 = x2.contiguous()
+        y = _ext.ext().rope_apply(x2, cos_half, sin_half, T, H, D, False)
+        _tick()
+        ctx.save_for_backward(cos_half, sin_half)
+        ctx.dims = (B, T, H, D)
+        return y.view(B, T, H, D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos_half, sin_half = ctx.saved_tensors
+        B, T, H, D = ctx.dims
+        d2 = dy.reshape(B * T, H * D)
+        if not _rows_ok(d2):
+            d2 = d2.contiguous()
+        dx = _ext.ext().rope_apply(d2, cos_half, sin_half, T, H, D, True)
+        _tick()
+        return dx.view(B, T, H, D), None, None
+
+
 def apply_rope(x, cos, sin):
+    """Rotary embedding of ``x [B, T, H, D]`` with ``cos/sin [T, D]`` tables in the half-split convention
+    (``triune/kernels/fast_rope.py:16-80``)."""
+    if (_ext.use_kernels(x) and x.dtype == torch.bfloat16 and x.dim() == 4 and x.shape[-1] % 16 == 0
+            and cos.shape[0] == x.shape[1] and cos.shape[-1] == x.shape[-1]):
+        D = x.shape[-1]
+        ch = cos[:, : D // 2].float().contiguous()
+        sh = sin[:, : D // 2].float().contiguous()
+        return _RoPEFn.apply(x, ch, sh)
     return ref.apply_rope(x, cos, sin)
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    """Row gather whose gradient is scattered straight into the fp32 gradient arena (``weight.main_grad``): no dense
+    [V, d] bf16 gradient, no sort, no second pass to fold it into the arena."""
+
+    @staticmethod
+    def forward(ctx, ids, weight):
+        flat = ids.reshape(-1).contiguous()
+        ctx.save_for_backward(flat, weight)
+        return F.embedding(ids, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        flat, weight = ctx.saved_tensors
+        d = weight.shape[1]
+        dy2 = dy.reshape(-1, d)
+        if dy2.dtype != torch.bfloat16 or dy2.stride(1) != 1 or dy2.stride(0) % 4 != 0:
+            dy2 = dy2.to(torch.bfloat16).contiguous()
+        mg = getattr(weight, "main_grad", None)
+        if mg is not None and mg.is_contiguous() and mg.dtype == torch.float32 and mg.data_ptr() % 16 == 0:
+            _ext.ext().embedding_bwd(dy2, flat, mg)
+            _tick()
+            return None, None
+        g = torch.zeros(weight.shape, device=weight.device, dtype=torch.float32)
+        _ext.ext().embedding_bwd(dy2, flat, g)
+        _tick()
+        return None, g.to(weight.dtype)
+
+
+def embedding(ids, weight):
+    """``weight[ids]``; on the kernel path the gradient is a scatter-add into the fp32 arena."""
+    if (_ext.use_kernels(weight) and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0
+            and ids.is_cuda and ids.dtype == torch.int64 and _wants_grad(weight)):
+        return _EmbeddingFn.apply(ids, weight)
+    return F.embedding(ids, weight)
 
 
 class _QKPrepFn(torch.autograd.Function):
@@ -458,7 +614,39 @@ def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0
 # ----------------------------------------------------------------------------
 # Cross entropy
 # ----------------------------------------------------------------------------
-def cross_entropy(logits, targets, ignore_index: int = -100):
+class _CrossEntropyFn(torch.autograd.Function):
+    """Mean cross entropy over bf16 logits: one kernel computes the per-row loss and (softmax - onehot) / n_valid into a
+    separate buffer (the logits stay intact); backward scales that buffer by the incoming scalar."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, ignore_index, n_valid):
+        V = logits.shape[-1]
+        l2 = logits.reshape(-1, V)
+        if not _rows_ok(l2):
+            l2 = l2.contiguous()
+        t = targets.reshape(-1).contiguous()
+        need = ctx.needs_input_grad[0]
+        inv = 1.0 / float(n_valid)
+        losses, grad = _ext.ext().ce_loss_grad(l2, t, ignore_index, inv if need else 0.0)
+        _tick()
+        if need:
+            ctx.save_for_backward(grad)
+        ctx.shape = logits.shape
+        return losses.sum() * inv
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return (grad * g.to(grad.dtype)).view(ctx.shape), None, None, None
+
+
+def cross_entropy(logits, targets, ignore_index: int = -100, n_valid: Optional[int] = None):
+    """Mean CE over the non-ignored rows (``triune/kernels/fast_cross_entropy.py:20-108``). ``n_valid`` (their count)
+    avoids a host synchronisation."""
+    if _ext.use_kernels(logits) and logits.dtype == torch.bfloat16 and logits.shape[-1] % 8 == 0 and targets.is_cuda:
+        if n_valid is None:
+            n_valid = max(1, int((targets != ignore_index).sum().item()))
+        return _CrossEntropyFn.apply(logits, targets.long(), ignore_index, n_valid)
     return ref.cross_entropy(logits, targets, ignore_index)
 
 

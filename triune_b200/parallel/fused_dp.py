@@ -54,7 +54,9 @@ class SymmetricArenaStorage:
 
 
 class FusedDPUpdater:
-    def __init__(self, ctx, optimizer, storage: SymmetricArenaStorage, wait_limit_s: float = 20.0):
+    def __init__(self, ctx, optimizer, storage: SymmetricArenaStorage):
+        # Every device-side wait of the step gives up after one second (``WAIT_LIMIT_NS`` in ``csrc/common/ptx.cuh``,
+        # a compile-time constant) and records why in ``self.status``; read it with :meth:`check`.
         self.ctx, self.opt, self.buf = ctx, optimizer, storage.buffer
         if self.buf is None:
             raise RuntimeError("optimizer was not built with SymmetricArenaStorage as storage_factory")
