@@ -54,4 +54,47 @@ void launch_gdn_recurrent(const GlaMat& Q, const GlaMat& K, const GlaMat& V, con
                           int beta_mode, float* state, const GlaMat& O, int B, int T, int H, int D, bool gate_logits,
                           float scale, cudaStream_t s);
 
+// ---- Gated DeltaNet, chunk-parallel training path (gdn_chunk_kernels.cu) ----
+struct GdnDims {
+  int B, T, H, D;    // T a multiple of 64, D = 64 or 128 (keys and values)
+  bool gate_logits;
+};
+// Per-chunk tensors produced by the forward pass and kept for the backward pass. nchunks = B * H * T / 64.
+struct GdnScratch {
+  __nv_bfloat16* U0;      // [nchunks, 64, D]   T (beta V)
+  __nv_bfloat16* W;       // [nchunks, 64, D]   T (beta Kbar)
+  __nv_bfloat16* Tm;      // [nchunks, 64, 64]  (I + L)^-1
+  __nv_bfloat16* Kend;    // [nchunks, 64, D]   k e^{b_C - b}
+  float* decay;           // [nchunks, D]       e^{b_C}
+  float* Lraw;            // [nchunks, 64, 64]  strict decayed key-key scores (null: not kept)
+  __nv_bfloat16* U;       // [nchunks, 64, D]   effective values
+  __nv_bfloat16* states;  // [nchunks, D, D]    state before each chunk
+  float* fin;             // [B * H, D, D]      state after the last token
+};
+struct GdnBwdScratch {
+  float* G1;              // [nchunks, 64, D]
+  float* H1;              // [nchunks, D, D]
+  __nv_bfloat16* dU;      // [nchunks, 64, D]
+  __nv_bfloat16* dSend;   // [nchunks, D, D]    gradient of the state after each chunk
+  float* dS0;             // [B * H, D, D]      gradient of the initial state
+  float* dq1;             // [nchunks, 64, D]
+  float* dkw1;            // [nchunks, 64, D]
+  float* dkr1;            // [nchunks, 64, D]
+  __nv_bfloat16* dW;      // [nchunks, 64, D]
+  __nv_bfloat16* dLraw;   // [nchunks, 64, 64]
+  float* dbeta;           // [B * T, H] (null without beta)
+  float* dgl_local;       // [B * T, H * D]     in-chunk part of the gate gradient
+  float* chunk_tot;       // [B * H * D / 64, T / 64, 64] chunk totals (the layout gla_dg_finalize reads with H * D / 64 heads)
+};
+// out = scale * GatedDeltaNet(q, k, v, g, beta); beta fp32 [B*T, H] or null; init fp32 [B*H, D, D] or null.
+void launch_gdn_chunk_fwd(const GlaMat& Q, const GlaMat& K, const GlaMat& V, const GlaMat& G, const float* beta,
+                          const float* init, const GlaMat& O, const GdnScratch& w, const GdnDims& d, float scale,
+                          int* status, cudaStream_t s);
+// Writes dq, dk, dv and fills dbeta, dS0, dgl_local, chunk_tot; the gate gradient is completed by
+// launch_gla_dg_finalize with H * D / 64 heads. dfin: gradient of the final state (fp32 [B*H, D, D]) or null.
+void launch_gdn_chunk_bwd(const GlaMat& Q, const GlaMat& K, const GlaMat& V, const GlaMat& G, const GlaMat& dO,
+                          const float* beta, const float* dfin, const GlaMat& dQ, const GlaMat& dK, const GlaMat& dV,
+                          const GdnScratch& w, const GdnBwdScratch& x, const GdnDims& d, float scale, int* status,
+                          cudaStream_t s);
+
 }  // namespace tb

@@ -114,6 +114,98 @@ void gdn_recurrent(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol,
   tb::launch_gdn_recurrent(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), bp, mode, state.data_ptr<float>(),
                            mat(out, ocol), (int)B, (int)T, (int)H, (int)D, gate_logits, (float)scale, cur_stream());
 }
+inline __nv_bfloat16* bfp(Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+
+// Chunk-parallel Gated DeltaNet forward. q, k, v, g: [B*T, ld] bf16 matrices with head h at columns col + h*D;
+// beta fp32 [B*T, H] or None; init fp32 [B*H, D, D] or None. Writes `out`; returns
+// [U0, W, Tm, Kend, decay, Lraw (empty when not kept), U, states, fin, status].
+std::vector<Tensor> gdn_chunk_fwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v,
+                                  int64_t vcol, const Tensor& g, int64_t gcol, const c10::optional<Tensor>& beta,
+                                  const c10::optional<Tensor>& init, Tensor& out, int64_t ocol, int64_t B, int64_t T,
+                                  int64_t H, int64_t D, bool gate_logits, double scale, bool keep_scores) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(T % 64 == 0 && (D == 64 || D == 128), "gdn_chunk_fwd: T % 64 == 0 and D in {64, 128}");
+  const int64_t NT = T / 64, BH = B * H, n = BH * NT;
+  auto bf = q.options();
+  auto f32 = q.options().dtype(at::kFloat);
+  Tensor U0 = torch::empty({n, 64, D}, bf), W = torch::empty({n, 64, D}, bf), Tm = torch::empty({n, 64, 64}, bf),
+         Kend = torch::empty({n, 64, D}, bf), decay = torch::empty({n, D}, f32), U = torch::empty({n, 64, D}, bf),
+         states = torch::empty({n, D, D}, bf), fin = torch::empty({BH, D, D}, f32);
+  Tensor Lraw = keep_scores ? torch::empty({n, 64, 64}, f32) : torch::empty({0}, f32);
+  Tensor status = torch::zeros({1}, q.options().dtype(at::kInt));
+  const float* bp = nullptr;
+  Tensor betac, initc;
+  if (beta.has_value() && beta->defined()) {
+    betac = beta->to(at::kFloat).contiguous();
+    TORCH_CHECK(betac.numel() == B * T * H, "beta must be [B*T, H]");
+    bp = betac.data_ptr<float>();
+  }
+  const float* ip = nullptr;
+  if (init.has_value() && init->defined()) {
+    initc = init->to(at::kFloat).contiguous();
+    TORCH_CHECK(initc.numel() == BH * D * D, "init must be [B*H, D, D]");
+    ip = initc.data_ptr<float>();
+  }
+  tb::GdnScratch w{bfp(U0), bfp(W), bfp(Tm), bfp(Kend), decay.data_ptr<float>(),
+                   keep_scores ? Lraw.data_ptr<float>() : nullptr, bfp(U), bfp(states), fin.data_ptr<float>()};
+  tb::GdnDims d{(int)B, (int)T, (int)H, (int)D, gate_logits};
+  tb::launch_gdn_chunk_fwd(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), bp, ip, mat(out, ocol), w, d,
+                           (float)scale, status.data_ptr<int>(), cur_stream());
+  return {U0, W, Tm, Kend, decay, Lraw, U, states, fin, status};
+}
+
+// Backward. `saved` is the list returned by gdn_chunk_fwd. Writes dq, dk, dv, dg into the given matrices; returns
+// [dbeta (fp32 [B*T, H], empty without beta), dS0 (fp32 [B*H, D, D]), status, then the per-chunk intermediates].
+std::vector<Tensor> gdn_chunk_bwd(const Tensor& q, int64_t qcol, const Tensor& k, int64_t kcol, const Tensor& v,
+                                  int64_t vcol, const Tensor& g, int64_t gcol, const Tensor& dout, int64_t docol,
+                                  const c10::optional<Tensor>& beta, const c10::optional<Tensor>& dfin,
+                                  std::vector<Tensor> saved, Tensor& dq, int64_t dqcol, Tensor& dk, int64_t dkcol,
+                                  Tensor& dv, int64_t dvcol, Tensor& dg, int64_t dgcol, int64_t B, int64_t T, int64_t H,
+                                  int64_t D, bool gate_logits, double scale) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(saved.size() >= 9, "gdn_chunk_bwd: the forward's saved tensors are missing");
+  const int64_t NT = T / 64, BH = B * H, n = BH * NT, NH = D / 64;
+  auto bf = q.options();
+  auto f32 = q.options().dtype(at::kFloat);
+  Tensor G1 = torch::empty({n, 64, D}, f32), H1 = torch::empty({n, D, D}, f32), dU = torch::empty({n, 64, D}, bf),
+         dSend = torch::empty({n, D, D}, bf), dS0 = torch::empty({BH, D, D}, f32), dq1 = torch::empty({n, 64, D}, f32),
+         dkw1 = torch::empty({n, 64, D}, f32), dkr1 = torch::empty({n, 64, D}, f32), dW = torch::empty({n, 64, D}, bf),
+         dLraw = torch::empty({n, 64, 64}, bf), dgl = torch::empty({B * T, H * D}, f32),
+         tot = torch::empty({BH * NH * NT, 64}, f32);
+  Tensor status = torch::zeros({1}, q.options().dtype(at::kInt));
+  const float* bp = nullptr;
+  Tensor betac, dfinc, dbeta = torch::empty({0}, f32);
+  if (beta.has_value() && beta->defined()) {
+    betac = beta->to(at::kFloat).contiguous();
+    bp = betac.data_ptr<float>();
+    dbeta = torch::empty({B * T, H}, f32);
+    TORCH_CHECK(saved[5].numel() == n * 64 * 64, "gdn_chunk_bwd: the key-key scores were not kept by the forward pass");
+  }
+  const float* dfp = nullptr;
+  if (dfin.has_value() && dfin->defined()) {
+    dfinc = dfin->to(at::kFloat).contiguous();
+    dfp = dfinc.data_ptr<float>();
+  }
+  tb::GdnScratch w{bfp(saved[0]), bfp(saved[1]), bfp(saved[2]), bfp(saved[3]), saved[4].data_ptr<float>(),
+                   saved[5].numel() > 0 ? saved[5].data_ptr<float>() : nullptr, bfp(saved[6]), bfp(saved[7]),
+                   saved[8].data_ptr<float>()};
+  tb::GdnBwdScratch x{G1.data_ptr<float>(), H1.data_ptr<float>(), bfp(dU), bfp(dSend), dS0.data_ptr<float>(),
+                      dq1.data_ptr<float>(), dkw1.data_ptr<float>(), dkr1.data_ptr<float>(), bfp(dW), bfp(dLraw),
+                      bp != nullptr ? dbeta.data_ptr<float>() : nullptr, dgl.data_ptr<float>(), tot.data_ptr<float>()};
+  tb::GdnDims d{(int)B, (int)T, (int)H, (int)D, gate_logits};
+  auto s = cur_stream();
+  tb::launch_gdn_chunk_bwd(mat(q, qcol), mat(k, kcol), mat(v, vcol), mat(g, gcol), mat(dout, docol), bp, dfp, mat(dq, dqcol),
+                           mat(dk, dkcol), mat(dv, dvcol), w, x, d, (float)scale, status.data_ptr<int>(), s);
+  // the suffix sums over the chunks and the derivative of the clamped log decay: the GLA finalize kernel with every
+  // 64-wide slice of a head counted as a head of its own
+  Tensor end_term;
+  if (dfp != nullptr) end_term = (dfinc.reshape({BH, D, D}) * saved[8].reshape({BH, D, D})).sum(-1).reshape({BH * NH, 64}).contiguous();
+  tb::GlaDims gd{(int)B, (int)T, (int)(H * NH), gate_logits};
+  tb::launch_gla_dg_finalize(dgl.data_ptr<float>(), tot.data_ptr<float>(), mat(g, gcol), mat(dg, dgcol), gd, s,
+                             end_term.defined() ? end_term.data_ptr<float>() : nullptr);
+  // the per-chunk intermediates follow for inspection (stage-by-stage comparison against the PyTorch oracle)
+  return {dbeta, dS0, status, G1, H1, dU, dSend, dq1, dkw1, dkr1, dW, dLraw, dgl, tot};
+}
 }  // namespace
 
 void register_gla(pybind11::module& m) {
@@ -125,4 +217,6 @@ void register_gla(pybind11::module& m) {
     tb::gla_set_debug_buffer(t.has_value() && t->defined() ? (long long*)t->data_ptr<int64_t>() : nullptr);
   });
   m.def("gdn_recurrent", &gdn_recurrent);
+  m.def("gdn_chunk_fwd", &gdn_chunk_fwd);
+  m.def("gdn_chunk_bwd", &gdn_chunk_bwd);
 }

@@ -596,12 +596,15 @@ def gated_deltanet(q, k, v, g, beta=None, initial_state=None, scale: float = 1.0
     """Gated DeltaNet over [B,T,H,D] tensors; returns (out, final_state [B,H,Dk,Dv]).
 
     Without gradients (prefill, decode) CUDA bf16 inputs run the exact token recurrence in one kernel; with gradients
-    the differentiable chunk-parallel WY form of :mod:`triune_b200.ops.reference` is used (one batched pass over all
-    chunks plus two small products per chunk for the state)."""
+    they run the chunk-parallel tcgen05 kernels (UT transform per chunk, sequential state pass, chunk outputs, and the
+    stage-wise backward of ``csrc/gla/gdn_chunk_kernels.cu``). Other inputs (CPU, fp32, a per-key-row beta) use the
+    differentiable PyTorch forms of :mod:`triune_b200.ops.reference`."""
     from . import gla_cuda
 
     if gla_cuda.gdn_supported(q, k, v, g, beta):
         return gla_cuda.gdn_recurrent(q, k, v, g, beta, initial_state, scale, gate_logits)
+    if gla_cuda.gdn_chunk_supported(q, k, v, g, beta) and q.shape[1] > 1:
+        return gla_cuda.gdn_chunk(q, k, v, g, beta, initial_state, scale, gate_logits)
     gl = F.logsigmoid(g.float()) if gate_logits else g
     if q.shape[1] == 1 and initial_state is not None and not torch.is_grad_enabled():
         o, s = ref.gated_deltanet_decode_step(

@@ -171,6 +171,77 @@ def gdn_supported(q, k, v, g, beta) -> bool:
     return True
 
 
+def gdn_chunk_supported(q, k, v, g, beta) -> bool:
+    """True when the chunk-parallel training kernels cover this call: bf16, head dim 64 or 128 (keys = values), beta
+    absent or one value per (token, head)."""
+    if not _ext.use_kernels(q, k, v, g) or q.dtype != torch.bfloat16:
+        return False
+    D = q.shape[-1]
+    if D not in (64, 128) or v.shape[-1] != D:
+        return False
+    return beta is None or beta.dim() == 3
+
+
+class _GDNChunkFn(torch.autograd.Function):
+    """Chunk-parallel Gated DeltaNet on the tcgen05 kernels (``csrc/gla/gdn_chunk_kernels.cu``): UT transform per
+    chunk, sequential state pass, chunk outputs; the backward pass mirrors it stage by stage (see
+    :mod:`triune_b200.ops.gdn_stages` for the algebra and the oracle of every stage)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, init, scale, gate_logits):
+        B, T, H, D = q.shape
+        e = _ext.ext()
+        pad = (-T) % 64
+        if pad:
+            # appended tokens with no key, no value and no decay leave the state and the real outputs untouched
+            zeros = q.new_zeros(B, pad, H, D)
+            q, k, v = (torch.cat((t, zeros), dim=1) for t in (q, k, v))
+            g = torch.cat((g, g.new_full((B, pad, H, D), 30.0 if gate_logits else 0.0)), dim=1)
+            if beta is not None:
+                beta = torch.cat((beta, beta.new_zeros(B, pad, H)), dim=1)
+        Tp = T + pad
+        qm, km, vm, gm = (_as_matrix(t.to(torch.bfloat16)) for t in (q, k, v, g))
+        out = torch.empty(B * Tp, H * D, device=q.device, dtype=torch.bfloat16)
+        bt = beta.float().reshape(B * Tp, H).contiguous() if beta is not None else None
+        ini = init.float().reshape(B * H, D, D).contiguous() if init is not None else None
+        need = any(ctx.needs_input_grad[:6])
+        res = e.gdn_chunk_fwd(qm, 0, km, 0, vm, 0, gm, 0, bt, ini, out, 0, B, Tp, H, D, bool(gate_logits), float(scale),
+                              need and bt is not None)
+        _tick(3)
+        _note(res[9])
+        if need:
+            ctx.save_for_backward(qm, km, vm, gm, bt if bt is not None else torch.empty(0, device=q.device), *res[:9])
+        ctx.dims = (B, T, Tp, H, D, float(scale), bool(gate_logits), beta is not None, init is not None,
+                    None if beta is None else beta.dtype)
+        ctx.set_materialize_grads(False)
+        return out.view(B, Tp, H, D)[:, :T], res[8].view(B, H, D, D)
+
+    @staticmethod
+    def backward(ctx, dout, dfin):
+        qm, km, vm, gm, bt, *saved = ctx.saved_tensors
+        B, T, Tp, H, D, scale, gate_logits, has_beta, has_init, beta_dtype = ctx.dims
+        e = _ext.ext()
+        dom = torch.zeros(B, Tp, H, D, device=qm.device, dtype=torch.bfloat16)
+        if dout is not None:
+            dom[:, :T] = dout
+        dom = dom.view(B * Tp, H * D)
+        dq, dk, dv, dg = (torch.empty(B * Tp, H * D, device=qm.device, dtype=torch.bfloat16) for _ in range(4))
+        dfl = dfin.float().reshape(B * H, D, D).contiguous() if dfin is not None else None
+        dbeta, ds0, status = e.gdn_chunk_bwd(qm, 0, km, 0, vm, 0, gm, 0, dom, 0, bt if has_beta else None, dfl, list(saved),
+                                             dq, 0, dk, 0, dv, 0, dg, 0, B, Tp, H, D, gate_logits, scale)[:3]
+        _tick(6)
+        _note(status)
+        sh = (B, Tp, H, D)
+        cut = lambda t: t.view(sh)[:, :T]
+        db = dbeta.view(B, Tp, H)[:, :T].to(beta_dtype) if has_beta else None
+        return cut(dq), cut(dk), cut(dv), cut(dg), db, ds0.view(B, H, D, D) if has_init else None, None, None
+
+
+def gdn_chunk(q, k, v, g, beta, initial_state, scale, gate_logits):
+    """Kernel path of ``ops.gated_deltanet`` under autograd; returns (out [B,T,H,D] bf16, final state fp32)."""
+    return _GDNChunkFn.apply(q, k, v, g, beta, initial_state, float(scale), bool(gate_logits))
+
+
 @torch.no_grad()
 def gdn_recurrent(q, k, v, g, beta, initial_state, scale, gate_logits):
     """Exact Gated DeltaNet recurrence in one kernel per call (prefill of any length, or one decode step).
