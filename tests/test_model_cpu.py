@@ -199,6 +199,9 @@ def test_batched_qr_fast_path_and_fallbacks():
            "overlapping_triggers": {k: 0 for k in ("degenerate_columns", "cholesky_non_positive_definite",
                                                     "condition_ratio_exceeded", "orthogonality_tolerance_exceeded")}}
     Q, info = batched_qr(A, telemetry=tel, return_info=True)
+    from triune_b200.optim.subspace import flush_qr_telemetry
+
+    flush_qr_telemetry(tel)  # counters accumulate on the device; the report folds them in
     assert info["fallback_mask"].tolist() == [False, True, True]
     assert sum(tel["primary_fallback_reasons"].values()) == 2 == tel["householder_fallbacks"]
     eye = torch.eye(16)
@@ -209,3 +212,179 @@ def test_batched_qr_fast_path_and_fallbacks():
     Ak = U @ torch.diag(torch.logspace(0, -2, 16)) @ V.t()
     Qk, infok = batched_qr(Ak.unsqueeze(0), return_info=True)
     assert not bool(infok["fallback_mask"].any()) and float(infok["orth_err"].max()) < 1e-5
+
+
+def _loss_backward(m, x):
+    m.forward_loss(x[:, :-1], x[:, 1:], 2).backward()
+
+
+def test_step_parameters_layer_by_layer_equals_one_full_step():
+    """Several ``step_parameters`` calls over disjoint parameter subsets (the layers, then the root modules) make the
+    same global step as ``step()``: same weights, same optimizer state, one step counted."""
+    from triune_b200.optim.subspace import set_sketch_seed
+
+    x = torch.randint(0, 256, (2, 25))
+    models, opts = [], []
+    for _ in range(2):
+        torch.manual_seed(9)
+        m = TriuneTransformer.from_config(tiny())
+        models.append(m)
+        opts.append(CentroidSteerOptimizer(m, lr=2e-3, rank=6))
+    for step in range(3):
+        for m in models:
+            _loss_backward(m, x)
+        set_sketch_seed(100 + step)  # both optimizers draw the same Gaussian sketches for their subspace refresh
+        opts[0].step()
+        opts[0].zero_grad()
+        set_sketch_seed(100 + step)
+        m1, o1 = models[1], opts[1]
+        layer_params = [list(l.parameters()) for l in m1.layers]
+        in_layers = {id(p) for ps in layer_params for p in ps}
+        root = [p for p in m1.parameters() if id(p) not in in_layers]
+        for ps in layer_params:
+            o1.step_parameters(ps, is_global_step_end=False)
+        o1.step_parameters(root, is_global_step_end=True)
+        o1.zero_grad()
+        assert o1.step_count == opts[0].step_count == step + 1
+        for (n, a), (_, b) in zip(models[0].named_parameters(), m1.named_parameters()):
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (step, n)
+    s0, s1 = opts[0].steer_state["layers.3.ffn.w1"], opts[1].steer_state["layers.3.ffn.w1"]
+    assert torch.allclose(s0["m"], s1["m"], atol=1e-6) and s0["subspace_step"] == s1["subspace_step"] == 3
+    assert torch.allclose(opts[0].exp_avg, opts[1].exp_avg, atol=1e-7)
+    # a subset leaves everything else untouched
+    before = {n: p.detach().clone() for n, p in m1.named_parameters()}
+    _loss_backward(m1, x)
+    o1.step_parameters(list(m1.layers[0].parameters()), is_global_step_end=True)
+    changed = {n for n, p in m1.named_parameters() if not torch.equal(p, before[n])}
+    assert changed and all(n.startswith("layers.0.") for n in changed)
+
+
+def test_single_sided_low_rank_path_with_basis_transport():
+    torch.manual_seed(10)
+    m = TriuneTransformer.from_config(tiny())
+    opt = CentroidSteerOptimizer(m, lr=3e-3, rank=8, update_gap=3, use_triangular_core=False)
+    x = torch.randint(0, 256, (4, 33))
+    losses = []
+    for _ in range(8):
+        loss = m.forward_loss(x[:, :-1], x[:, 1:], 2)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(float(loss))
+    assert losses[-1] < losses[0] - 0.2
+    st = opt.steer_state["layers.3.ffn.w1"]
+    assert st["mode"] == "galore" and st["step"] == 8 and st["proj_step"] > 1   # refreshed, moments kept (transported)
+    P = st["P"][:, :, : st["rank"]]
+    assert ((P.transpose(1, 2) @ P) - torch.eye(st["rank"])).abs().max() < 1e-3
+    K, m_, n_ = opt.arena.segments[-1].mat_shape
+    assert st["m"].numel() < K * m_ * n_ / 3  # the moments live in the projected space
+
+
+def test_8bit_adam_tier_tracks_the_fp32_tier():
+    x = torch.randint(0, 256, (4, 33))
+    finals, state_bytes = [], []
+    for eight in (False, True):
+        torch.manual_seed(11)
+        m = TriuneTransformer.from_config(tiny())
+        opt = CentroidSteerOptimizer(m, lr=3e-3, rank=8, use_8bit_adam=eight)
+        for _ in range(10):
+            loss = m.forward_loss(x[:, :-1], x[:, 1:], 2)
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+        finals.append(float(loss))
+        state_bytes.append(opt.get_telemetry()["tiers"]["adamw"]["state_bytes"])
+        if eight:
+            sd = opt.state_dict()
+            opt2 = CentroidSteerOptimizer(m, lr=3e-3, rank=8, use_8bit_adam=True)
+            opt2.load_state_dict(sd)
+            a, b = opt.moments8.load(0, 4096), opt2.moments8.load(0, 4096)
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    assert abs(finals[0] - finals[1]) < 0.15 and state_bytes[1] < 0.3 * state_bytes[0]
+    from triune_b200.optim.adam8bit import BlockwiseMoments
+
+    bm = BlockwiseMoments(1000, torch.device("cpu"))
+    mm, vv = torch.randn(1000) * 0.01, torch.rand(1000) ** 4 * 1e-3
+    bm.store(0, 1000, mm, vv)
+    m2, v2 = bm.load(0, 1000)
+    assert float((m2 - mm).abs().max()) < 0.02 * float(mm.abs().max())
+    assert float(((v2.sqrt() - vv.sqrt()).abs() / vv.sqrt().clamp_min(1e-4)).median()) < 0.02
+    bm.store(300, 420, mm[300:420] * 2, vv[300:420])   # a partial update re-encodes only the touched blocks
+    m3, _ = bm.load(0, 1000)
+    assert torch.allclose(m3[:256], m2[:256]) and float((m3[300:420] - 2 * mm[300:420]).abs().max()) < 0.05 * float(mm.abs().max())
+
+
+def test_rank_sensitivity_profile_and_reference_state_layout():
+    torch.manual_seed(12)
+    m = TriuneTransformer.from_config(tiny())
+    opt = CentroidSteerOptimizer(m, lr=2e-3, rank=8)
+    x = torch.randint(0, 256, (4, 33))
+    _loss_backward(m, x)
+    rep = opt.profile_rank_sensitivity(ranks=(2, 4, 8, 16))
+    e = [rep["ranks"][r]["energy_ratio"] for r in (2, 4, 8, 16)]
+    assert all(b >= a - 1e-4 for a, b in zip(e, e[1:])) and 0.0 < e[0] <= e[-1] <= 1.0 + 1e-4
+    assert rep["recommended_rank"] in (2, 4, 8, 16) and opt.get_qr_telemetry()["total_qr_calls"] == 0
+    for _ in range(3):
+        opt.step()
+        opt.zero_grad()
+        _loss_backward(m, x)
+    ref_sd = opt.reference_state_dict()
+    n_experts = sum(s.mat_shape[0] for s in opt.arena.segments if s.tier == "steer")
+    assert len(ref_sd["layer_groups"]) == n_experts and ref_sd["step_count"] == 3
+    g0 = ref_sd["layer_groups"][0]
+    assert g0["Q_L"].dim() == 2 and g0["state"]["momentum"].shape == (g0["Q_L"].shape[1],) * 2
+    assert set(ref_sd["base_optimizer"]["state"][0]) == {"step", "exp_avg", "exp_avg_sq"}
+    opt2 = CentroidSteerOptimizer(m, lr=2e-3, rank=8)
+    opt2.load_reference_state_dict(ref_sd)
+    assert torch.allclose(opt2.exp_avg, opt.exp_avg) and torch.allclose(opt2.muon_mom, opt.muon_mom)
+    a, b = opt.steer_state["layers.3.ffn.w1"], opt2.steer_state["layers.3.ffn.w1"]
+    assert torch.allclose(a["Q_L"], b["Q_L"]) and torch.allclose(a["v"], b["v"]) and a["subspace_step"] == b["subspace_step"]
+
+
+def test_qr_calls_only_on_refresh_steps_and_unrouted_experts_are_skipped():
+    """No QR on a step that reuses its bases, and an expert without gradient never reaches the QR (so it cannot
+    trigger the degenerate-column fall-back) -- ``tests/test_triangular_core_integrity.py:362-418`` of the reference."""
+    torch.manual_seed(13)
+    m = TriuneTransformer.from_config(tiny())
+    opt = CentroidSteerOptimizer(m, lr=1e-3, rank=4, update_gap=5)
+    x = torch.randint(0, 256, (2, 17))
+    calls = []
+    for _ in range(3):
+        _loss_backward(m, x)
+        for seg in opt.arena.segments:
+            if seg.tier == "steer":
+                seg.param.main_grad[0].zero_()   # expert 0 received no tokens
+        opt.step()
+        opt.zero_grad()
+        tel = opt.get_qr_telemetry()
+        calls.append(tel["total_qr_calls"])
+        assert tel["primary_fallback_reasons"]["degenerate_columns"] == 0
+    assert calls[0] > 0 and calls[1] == calls[0] and calls[2] == calls[0]
+
+
+def test_steered_bases_meet_the_orthogonality_and_subdiagonal_bars():
+    """fp32 bars of the reference (``tests/test_triangular_core_integrity.py:169-240``): the steering-augmented bases
+    are orthonormal to 5e-5 and the projected core is upper triangular to 1e-7 of ||G|| below the diagonal; rounded to
+    bf16 the bars are 5e-3 and 1e-4."""
+    from triune_b200.optim.subspace import reorthogonalise, two_sided_bases
+
+    torch.manual_seed(42)
+    mm, nn_, r = 384, 1024, 16
+    G16 = torch.randn(1, mm, nn_).to(torch.bfloat16)
+    G = G16.float()
+    QL, QR = two_sided_bases(G, r)
+    c = torch.randn(1, nn_)
+    v_orth, _ = reorthogonalise(c, QR)
+    u = (G @ v_orth.unsqueeze(-1)).squeeze(-1)
+    u_orth, _ = reorthogonalise(u, QL)
+    QLb, QRb = torch.cat((QL, u_orth.unsqueeze(-1)), -1)[0], torch.cat((QR, v_orth.unsqueeze(-1)), -1)[0]
+    eye = torch.eye(r + 1)
+    assert float((QLb.t() @ QLb - eye).norm()) < 5e-5 and float((QRb.t() @ QRb - eye).norm()) < 5e-5
+    S = QLb.t() @ G[0] @ QRb
+    low = torch.tril(torch.ones(r + 1, r + 1, dtype=torch.bool), diagonal=-1)
+    # Q_L = qr(G Q_R) makes Q_L^T G Q_R the triangular factor: nothing below the diagonal of the leading r x r block
+    assert float(S[:r, :r][low[:r, :r]].abs().max()) / float(G.norm()) < 1e-7
+    l16, r16 = QLb.to(torch.bfloat16).float(), QRb.to(torch.bfloat16).float()
+    assert float((l16.t() @ l16 - eye).norm()) < 5e-3 and float((r16.t() @ r16 - eye).norm()) < 5e-3
+    S16 = l16.t() @ G[0] @ r16
+    assert float(S16[:r, :r][low[:r, :r]].abs().max()) / float(G.norm()) < 1e-4

@@ -8,6 +8,7 @@ import sys
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 from triune_b200.config import ModelConfig
 from triune_b200.models import TriuneTransformer
@@ -123,6 +124,54 @@ def test_generation_cache_penalties_and_stop():
     cfg = infer_config_from_state_dict(m.state_dict())
     assert (cfg.hidden_dim, cfg.num_layers, cfg.num_experts, cfg.expert_hidden, cfg.dense_hidden) == (64, 5, 4, 96, 80)
     assert (cfg.reflex_exit_layer, cfg.limbic_exit_layer) == (2, 3)
+
+
+def test_self_speculative_sampling_follows_the_verifier_distribution():
+    """Leviathan rejection sampling is exact: the first emitted token of many sampled runs is distributed as the
+    verifier's softmax(logits / temperature) (Pearson chi-square with small bins pooled; the reference's bar,
+    ``tests/test_self_speculative_decoding.py:126-214``: p > 0.005)."""
+    from triune_b200.models.speculative import SelfSpeculativeGenerator
+
+    torch.manual_seed(77)
+    vocab, temperature, n_draws = 12, 0.7, 2000
+    model = TriuneTransformer(vocab_size=vocab, hidden_dim=32, num_layers=6, num_heads=2, head_dim=16, num_experts=2,
+                              router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=4).eval()
+    with torch.no_grad():  # make the exits disagree visibly, so that rejections actually occur
+        model.final_head.weight.mul_(4.0)
+        model.layers[2].exit_head.weight.mul_(4.0)
+    prompt = torch.tensor([[1, 3, 7, 2]])
+    with torch.no_grad():
+        logits = model(prompt, force_depth=2, last_token_only=True)[0]
+        p_exact = F.softmax(logits[0, -1].float() / temperature, dim=-1).double()
+        q_draft = F.softmax(model(prompt, force_depth=0, last_token_only=True)[0][0, -1].float() / temperature, dim=-1).double()
+    assert float((p_exact - q_draft).abs().sum()) > 0.05  # the two exits really differ
+    gen = SelfSpeculativeGenerator(model, k_draft=2)
+    rng = torch.Generator().manual_seed(2026)
+    counts = torch.zeros(vocab, dtype=torch.float64)
+    for _ in range(n_draws):
+        out = gen.generate(prompt, max_new_tokens=1, temperature=temperature, generator=rng)
+        counts[int(out[0, -1])] += 1.0
+    assert gen.telemetry["proposed"] > 0 and gen.telemetry["accepted"] < gen.telemetry["proposed"]  # some rejections
+    obs, exp = [], []
+    tail_o = tail_e = 0.0
+    for o_i, e_i in zip(counts.tolist(), (p_exact * n_draws).tolist()):
+        if e_i >= 5.0:
+            obs.append(o_i)
+            exp.append(e_i)
+        else:
+            tail_o, tail_e = tail_o + o_i, tail_e + e_i
+    if tail_e >= 5.0:
+        obs.append(tail_o)
+        exp.append(tail_e)
+    elif tail_e > 0.0 and obs:
+        obs[-1] += tail_o
+        exp[-1] += tail_e
+    df = len(obs) - 1
+    assert df >= 3
+    chi2 = sum((o - e) ** 2 / e for o, e in zip(obs, exp))
+    z = ((chi2 / df) ** (1.0 / 3.0) - (1.0 - 2.0 / (9.0 * df))) / math.sqrt(2.0 / (9.0 * df))  # Wilson-Hilferty
+    p_val = 0.5 * math.erfc(z / math.sqrt(2.0))
+    assert p_val > 0.005, f"sampled tokens diverge from the verifier distribution (chi2={chi2:.2f}, df={df}, p={p_val:.4g})"
 
 
 def test_self_speculative_greedy_equals_autoregressive():

@@ -144,6 +144,38 @@ def case_gdn(a):
     print(json.dumps({"case": out["case"], "peak_mem_GB": round(torch.cuda.max_memory_allocated() / 2**30, 2)}), flush=True)
 
 
+def case_swiglu(a):
+    """SwiGLU feed-forward, forward + backward: the activation inside the GEMM epilogues against the same three GEMMs
+    with stand-alone activation kernels between them (M tokens, K model width, N hidden width)."""
+    from . import _ext, ops
+
+    M, K, H = a.m, a.k, a.n
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w13 = (torch.randn(2 * H, K, device="cuda") * K ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    w2 = (torch.randn(K, H, device="cuda") * H ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+
+    def clear():
+        for t in (x, w13, w2):
+            t.grad = None
+
+    def fused():
+        ops.swiglu_mlp(x, w13, w2).backward(dy)
+        clear()
+
+    def unfused():
+        gu = ops.linear(x, w13)
+        ops.linear(ops.swiglu(gu[:, :H], gu[:, H:]), w2).backward(dy)
+        clear()
+
+    flops = 18.0 * M * K * H  # 3 products forward (2 M K H each ... gate, up, down) and twice that backward
+    ms = timeit(fused, a.iters, a.warmup)
+    report(f"swiglu ffn fwd+bwd, activation in GEMM epilogues M{M} K{K} H{H}", ms, flops=flops)
+    ms2 = timeit(unfused, a.iters, a.warmup)
+    report(f"swiglu ffn fwd+bwd, stand-alone activation kernels M{M} K{K} H{H}", ms2, flops=flops)
+    print(json.dumps({"case": "swiglu", "pair_kernel_launches": int(_ext.ext().tc_gemm_pair_launches())}), flush=True)
+
+
 def case_rmsnorm(a):
     from . import ops
 
@@ -223,7 +255,7 @@ def case_nvfp4(a):
     report(f"nvfp4_quantize {N}x{K}", ms, nbytes=N * K * 4.5625)
 
 
-CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "rmsnorm": case_rmsnorm, "ce": case_ce}
+CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():

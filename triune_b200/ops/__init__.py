@@ -278,7 +278,7 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         if not _tma_ok(x2):
             x2 = x2.contiguous()
         M, H = x2.shape[0], w13.shape[0] // 2
-        train = _wants_grad(x, w13, w2)
+        train = any(ctx.needs_input_grad)  # (grad mode is off inside forward: ask the context, not torch)
         h = torch.empty(M, H, device=x.device, dtype=x.dtype)
         gu = torch.empty(M, 2 * H, device=x.device, dtype=x.dtype) if train else None
         _ext.ext().tc_gemm_swiglu(x2, w13, h, gu)

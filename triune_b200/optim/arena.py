@@ -150,8 +150,8 @@ class ParamArena:
 
     # ------------------------------------------------------------------ gradient plumbing
     @torch.no_grad()
-    def fold_autograd_grads(self) -> None:
-        for seg in self.segments:
+    def fold_autograd_grads(self, only: Optional[Sequence[Segment]] = None) -> None:
+        for seg in (self.segments if only is None else only):
             g = seg.param.grad
             if g is not None:
                 seg.param.main_grad.add_(g.to(torch.float32))

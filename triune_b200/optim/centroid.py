@@ -34,7 +34,8 @@ import torch
 from .. import _ext, config as C
 from ..ops import reference as ref
 from .arena import MuonGroup, ParamArena, Segment
-from .subspace import batched_qr, new_qr_telemetry, reorthogonalise, two_sided_bases
+from .subspace import (batched_qr, batched_subspace_projection, flush_qr_telemetry, new_qr_telemetry, reorthogonalise,
+                       two_sided_bases)
 
 _HEAD_KEYS = ("embed", "wte", "wpe", "exit_head", "final_head", "lm_head", "classifier", "output_head", "token_table")
 
@@ -150,7 +151,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                  grad_clip: Optional[float] = None, nesterov: bool = True, aspect_safeguard: bool = True,
                  adaptive_subspace_refresh: bool = False, energy_threshold: float = 0.5, min_subspace_gap: int = 5,
                  max_subspace_gap: int = 50, storage_factory=None, shard: Tuple[int, int] = (0, 1),
-                 tensor_core_subspace: bool = True):
+                 tensor_core_subspace: bool = True, use_8bit_adam: bool = False):
         if core_mask_mode not in ("full", "triu"):
             raise ValueError(f"Unknown core_mask_mode={core_mask_mode!r}; expected 'full' or 'triu'")
         self._in_set_lr = False
@@ -185,8 +186,19 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         a = self.arena
         dev = a.device
         lo, hi = a.adamw_range
-        self.exp_avg = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
-        self.exp_avg_sq = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
+        # Tier-3 moments: fp32, or block-wise 8-bit (``use_8bit_adam``; the reference's optional AdamW8bit tier,
+        # ``triune/optim/centroid.py:10-16``) which cuts that tier's optimizer state from 8 to ~2 bytes per parameter.
+        self.use_8bit_adam = bool(use_8bit_adam)
+        if self.use_8bit_adam:
+            from .adam8bit import BlockwiseMoments
+
+            self.moments8 = BlockwiseMoments(hi - lo, dev)
+            self.exp_avg = self.exp_avg_sq = torch.zeros(0, device=dev, dtype=torch.float32)
+        else:
+            self.moments8 = None
+            self.exp_avg = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
+            self.exp_avg_sq = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
+        self._partial_open = False  # a global step made of several step_parameters calls is in progress
         lo, hi = a.muon_range
         self.muon_mom = torch.zeros(hi - lo, device=dev, dtype=torch.float32)
         self.steer_state: Dict[str, Dict] = {}
@@ -334,49 +346,128 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         self.compute_clip()
         self._step_adamw()
         self._step_muon()
+        self._step_steer_tf32()
+        return loss
+
+    def _step_steer_tf32(self, only=None):
         # the subspace projections are fp32 batched products; TF32 tensor cores keep ~1e-3 relative accuracy,
         # the same order as the bf16 bases the reference uses on CUDA
         prev = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = True
         try:
-            self._step_steer()
+            self._step_steer(only)
         finally:
             torch.backends.cuda.matmul.allow_tf32 = prev
-        return loss
 
-    def step_parameters(self, params: Iterable[torch.nn.Parameter], is_global_step_end: bool = True):
-        """Layer-wise stepping hook (used by layer streaming): here all tiers step together on the last call."""
+    def set_clip_coefficient(self, coef) -> None:
+        """Gradient scale applied by the next (partial) steps. Layer-wise stepping cannot know the global gradient norm
+        when the first layer is updated, so the caller computes it over all layers first and passes
+        ``min(1, clip / norm)`` here."""
+        if torch.is_tensor(coef):
+            self._clip_coef.copy_(coef.reshape(1).to(self._clip_coef))
+        else:
+            self._clip_coef.fill_(float(coef))
+
+    @torch.no_grad()
+    def step_parameters(self, params: Iterable[torch.nn.Parameter], is_global_step_end: bool = False):
+        """Update only ``params`` (one layer, or the root modules) with their tiers' rules; several calls make up one
+        global step, the last one passing ``is_global_step_end=True`` (``triune/optim/centroid.py:531`` of the
+        reference). All calls of one global step share the same step number (bias corrections, refresh schedule) and
+        the clip coefficient set by :meth:`set_clip_coefficient` (1 by default); every other parameter, and its
+        optimizer state, is left untouched, which is what lets layer streaming keep only one layer's state on the
+        device."""
+        if self.shard[1] != 1:
+            raise RuntimeError("step_parameters updates whole parameters: use it without optimizer-state sharding")
+        ids = {id(p) for p in params}
+        a = self.arena
+        segs = [s for s in a.segments if id(s.param) in ids]
+        if not self._partial_open:
+            self.step_count += 1
+            self._partial_open = True
+        a.fold_autograd_grads(segs)
+        if segs:
+            self._step_adamw([s for s in segs if s.tier == "adamw"])
+            self._step_muon({id(s.param) for s in segs if s.tier == "muon"})
+            steer = {s.name for s in segs if s.tier == "steer"}
+            if steer:
+                self._step_steer_tf32(steer)
         if is_global_step_end:
-            self.step()
+            self._partial_open = False
 
     # ---- Tier 3 --------------------------------------------------------------------------------
-    def _step_adamw(self):
+    def _step_adamw(self, only: Optional[List[Segment]] = None):
+        """AdamW over the whole Tier-3 range, or (``only``) over the element ranges of the given segments."""
         a = self.arena
         lo, hi = a.adamw_range
         if hi == lo:
             return
+        if only is None:
+            runs = [(lo, hi)]
+        else:
+            runs = []
+            for seg in sorted(only, key=lambda s_: s_.offset):
+                b, e = seg.offset, seg.offset + seg.numel
+                if runs and b - runs[-1][1] < 8:  # neighbours (the padding between segments is < 8 elements)
+                    runs[-1] = (runs[-1][0], e)
+                else:
+                    runs.append((b, e))
+        for b, e in runs:
+            self._adamw_range(b, e)
+
+    def _adamw_range(self, b: int, e: int):
+        a = self.arena
+        lo, _ = a.adamw_range
         b1, b2 = self.betas
         t = self.step_count
-        master = a.master()[lo:hi]
-        grad = a.flat_grad[lo:hi]
+        master = a.master()[b:e]
+        grad = a.flat_grad[b:e]
+        if self.moments8 is not None:
+            g = grad * self._clip_coef
+            m, v = self.moments8.load(b - lo, e - lo)
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            upd = (m / (1 - b1**t)) / ((v / (1 - b2**t)).sqrt() + self.eps)
+            master.mul_(1 - self.lr * self.weight_decay).add_(upd, alpha=-self.lr)
+            self.moments8.store(b - lo, e - lo, m, v)
+            if a.flat_master is not None:
+                a.flat_param[b:e].copy_(master)
+            return
+        ea, es = self.exp_avg[b - lo : e - lo], self.exp_avg_sq[b - lo : e - lo]
         if self._use_kernels():
-            pb = a.flat_param[lo:hi] if a.flat_master is not None else None
-            _ext.ext().adamw_flat(master, self.exp_avg, self.exp_avg_sq, grad, pb, self.lr, b1, b2, self.eps,
+            pb = a.flat_param[b:e] if a.flat_master is not None else None
+            _ext.ext().adamw_flat(master, ea, es, grad, pb, self.lr, b1, b2, self.eps,
                                   self.weight_decay, t, self._clip_coef, 1.0, self._hyper_arg())
             from .. import ops
             ops._tick()
             return
         g = grad * self._clip_coef
-        self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
-        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
-        mh = self.exp_avg / (1 - b1**t)
-        vh = self.exp_avg_sq / (1 - b2**t)
+        ea.mul_(b1).add_(g, alpha=1 - b1)
+        es.mul_(b2).addcmul_(g, g, value=1 - b2)
+        mh = ea / (1 - b1**t)
+        vh = es / (1 - b2**t)
         master.mul_(1 - self.lr * self.weight_decay).add_(mh / (vh.sqrt() + self.eps), alpha=-self.lr)
         if a.flat_master is not None:
-            a.flat_param[lo:hi].copy_(master)
+            a.flat_param[b:e].copy_(master)
 
     # ---- Tier 1 --------------------------------------------------------------------------------
-    def _step_muon(self):
+    def _muon_runs(self, grp: MuonGroup, only):
+        """Index ranges [k0, k1) of the group's matrix stack to update: the owned share, or (``only``: a set of
+        parameter ids) the runs of consecutive matrices that belong to the selected parameters."""
+        if only is None:
+            k0, k1 = self._owned(grp.count)
+            return [(k0, k1)] if k1 > k0 else []
+        runs, k = [], 0
+        for seg in grp.segments:
+            K = seg.mat_shape[0]
+            if id(seg.param) in only:
+                if runs and runs[-1][1] == k:
+                    runs[-1] = (runs[-1][0], k + K)
+                else:
+                    runs.append((k, k + K))
+            k += K
+        return runs
+
+    def _step_muon(self, only=None):
         a = self.arena
         lo, hi = a.muon_range
         if hi == lo:
@@ -385,11 +476,8 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
 
         beta = self.muon_momentum
         kern = self._use_kernels()
-        for grp in a.muon_groups:
+        for grp, (k0, k1) in ((g_, r_) for g_ in a.muon_groups for r_ in self._muon_runs(g_, only)):
             m, n = grp.shape
-            k0, k1 = self._owned(grp.count)
-            if k1 == k0:
-                continue
             s, e = grp.offset + k0 * m * n, grp.offset + k1 * m * n
             grad = a.flat_grad[s:e]
             mom = self.muon_mom[s - lo : e - lo]
@@ -423,11 +511,93 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             c = ref.gelu_tanh(torch.baddbmm(mod.b1.float().unsqueeze(1), c.unsqueeze(1), mod.w1.float().transpose(1, 2))).squeeze(1)
         return c
 
-    def _step_steer(self):
+    def _step_galore(self, seg: Segment, G: torch.Tensor, k0: int, k1: int):
+        """Single-sided low-rank path (``use_triangular_core=False``; ``triune/optim/centroid.py:984-1268``): one basis
+        P [dim, r] on the shorter side of the matrix, Adam moments in the projected space ([r+1, n] or [m, r+1]), a
+        refresh every ``update_gap`` steps from a randomized range finder with the moments TRANSPORTED into the new
+        basis through T = P_old^T P_new (first moment by T, second moment by T*T plus the energy that left the span
+        replaced by the mean variance), and the steering axis in slot r: the unit residual of the expert's router
+        centroid, applied on reconstruction with weight steer_scale * utilisation * residual norm."""
+        a = self.arena
+        b1, b2 = self.expert_betas
+        K, m, n = G.shape
+        left = m <= n
+        dim = m if left else n
+        r = max(1, min(self.rank, m, n))
+        st = self.steer_state.get(seg.name)
+        if st is None:
+            P0 = torch.empty(K, dim, r, device=a.device)
+            for i in range(K):
+                torch.nn.init.orthogonal_(P0[i])
+            st = self.steer_state[seg.name] = {
+                "mode": "galore", "side": "left" if left else "right", "P": torch.zeros(K, dim, r + 1, device=a.device),
+                "m": None, "v": None, "step": 0, "proj_step": self.step_count, "rank": r,
+                "last_c": torch.zeros(K, dim, device=a.device), "steer_w": torch.zeros(K, device=a.device),
+            }
+            st["P"][:, :, :r] = P0
+        if self.step_count - st["proj_step"] >= self.update_gap:
+            Gs = G if left else G.transpose(1, 2)
+            P_new = batched_subspace_projection(Gs.contiguous(), r)            # [K, dim, r]
+            if P_new.shape[-1] == r and st["m"] is not None:
+                T = st["P"][:, :, :r].transpose(1, 2) @ P_new                  # [K, r, r]
+                T2 = T * T
+                energy = T2.sum(dim=1).clamp(0.0, 1.0)                         # column sums: energy kept per new axis
+                M, V = st["m"], st["v"]
+                if left:
+                    Mr = T.transpose(1, 2) @ M[:, :r]
+                    Vr = T2.transpose(1, 2) @ V[:, :r] + (1.0 - energy).unsqueeze(-1) * V[:, :r].mean(dim=1, keepdim=True)
+                    st["m"], st["v"] = torch.cat((Mr, M[:, r:]), dim=1), torch.cat((Vr, V[:, r:]), dim=1)
+                else:
+                    Mr = M[:, :, :r] @ T
+                    Vr = V[:, :, :r] @ T2 + (1.0 - energy).unsqueeze(1) * V[:, :, :r].mean(dim=2, keepdim=True)
+                    st["m"], st["v"] = torch.cat((Mr, M[:, :, r:]), dim=2), torch.cat((Vr, V[:, :, r:]), dim=2)
+            else:
+                st["m"] = st["v"] = None
+                st["step"] = 0
+            st["P"][:, :, : P_new.shape[-1]] = P_new
+            st["proj_step"] = self.step_count
+        # steering axis
+        P = st["P"]
+        P[:, :, r].zero_()
+        st["steer_w"].zero_()
+        c = self._centroid_inputs(seg)
+        mod, role = self.steer_meta.get(id(seg.param), (None, "input"))
+        if c is not None and (left and role == "hidden" or not left and role == "input" or c.shape[-1] == dim):
+            c = c[k0:k1]
+            if c.shape == (K, dim):
+                cn = c.norm(dim=-1, keepdim=True)
+                c_hat = c / cn.clamp_min(1e-8)
+                res = c_hat - (P[:, :, :r] @ (P[:, :, :r].transpose(1, 2) @ c_hat.unsqueeze(-1))).squeeze(-1)
+                rn = res.norm(dim=-1)
+                ok = (cn.squeeze(-1) > 1e-8) & (rn > 1e-8)
+                c_orth = res / rn.clamp_min(1e-8).unsqueeze(-1)
+                flip = ((c_orth * st["last_c"]).sum(-1) < 0) & (st["last_c"].abs().sum(-1) > 0)  # sign continuity
+                c_orth = torch.where(flip.unsqueeze(-1), -c_orth, c_orth)
+                util = torch.ones(K, device=a.device)
+                if mod is not None and getattr(mod, "expert_load_ratio", None) is not None:
+                    util = (1.0 + (1.0 - mod.expert_load_ratio.float()[k0:k1])).clamp(0.3, 2.0)
+                P[:, :, r] = torch.where(ok.unsqueeze(-1), c_orth, torch.zeros_like(c_orth))
+                st["last_c"] = torch.where(ok.unsqueeze(-1), c_orth, torch.zeros_like(c_orth))
+                st["steer_w"] = torch.where(ok, self.steer_scale * util * rn.clamp(0.0, 1.0), torch.zeros_like(rn))
+        g_lr = P.transpose(1, 2) @ G if left else G @ P                        # [K, r+1, n] or [K, m, r+1]
+        st["step"] += 1
+        if st["m"] is None:
+            st["m"], st["v"] = g_lr.clone(), g_lr * g_lr
+        else:
+            st["m"].mul_(b1).add_(g_lr, alpha=1 - b1)
+            st["v"].mul_(b2).addcmul_(g_lr, g_lr, value=1 - b2)
+        t = st["step"]
+        d_lr = (st["m"] / (1 - b1**t)) / ((st["v"] / max(1 - b2**t, 1e-7)).sqrt() + self.eps)
+        P_rec = P.clone()
+        P_rec[:, :, r] = P_rec[:, :, r] * st["steer_w"].unsqueeze(-1)
+        dW = P_rec @ d_lr if left else d_lr @ P_rec.transpose(1, 2)
+        self._apply_steer_delta(seg, dW, k0, k1)
+
+    def _step_steer(self, only=None):
         a = self.arena
         b1, b2 = self.expert_betas
         for seg in a.segments:
-            if seg.tier != "steer":
+            if seg.tier != "steer" or (only is not None and seg.name not in only):
                 continue
             K_all, m, n = seg.mat_shape
             k0, k1 = self._owned(K_all)
@@ -438,14 +608,7 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
             r = max(1, min(self.rank, min(m, n) - 1))
             st = self.steer_state.get(seg.name)
             if not self.use_triangular_core:
-                # dense AdamW on the experts (ablation path)
-                if st is None:
-                    st = self.steer_state[seg.name] = {"m": torch.zeros_like(G), "v": torch.zeros_like(G), "step": 0}
-                st["step"] += 1
-                st["m"].mul_(b1).add_(G, alpha=1 - b1)
-                st["v"].mul_(b2).addcmul_(G, G, value=1 - b2)
-                d = (st["m"] / (1 - b1 ** st["step"])) / ((st["v"] / (1 - b2 ** st["step"])).sqrt() + self.eps)
-                self._apply_steer_delta(seg, d, k0, k1)
+                self._step_galore(seg, G, k0, k1)
                 continue
             if st is None:
                 st = self.steer_state[seg.name] = {
@@ -583,24 +746,168 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
 
     # ------------------------------------------------------------------ state dict / telemetry
     def state_dict(self):
+        flush_qr_telemetry(self.qr_telemetry)
         return {
             "step_count": self.step_count, "lr": self.lr, "muon_lr": self.muon_lr, "expert_lr": self.expert_lr,
-            "layout": [(s.name, s.tier, s.offset, s.numel) for s in self.arena.segments],
+            "steer_scale": float(self.steer_scale),
+            "layout": [[s.name, s.tier, s.offset, s.numel] for s in self.arena.segments],
             "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "muon_momentum": self.muon_mom,
+            "moments8": self.moments8.state_dict() if self.moments8 is not None else None,
             "master": self.arena.flat_master,
             "steer": {k: {kk: vv for kk, vv in v.items()} for k, v in self.steer_state.items()},
             "qr_telemetry": self.qr_telemetry,
         }
 
+    # ---- the reference's optimizer-state layout ------------------------------------------------------------------
+    def reference_state_dict(self) -> Dict:
+        """Optimizer state in the layout of the reference's ``CentroidSteerOptimizer.state_dict``
+        (``triune/optim/centroid.py:1286-1311``): ``base_optimizer`` / ``muon_optimizer`` as torch-optimizer state
+        dicts over per-parameter tensors, and one ``layer_groups`` entry per EXPERT matrix (the stacked expert weights
+        are unstacked: ``w1`` of all experts first, then ``w2``, per layer) carrying Q_L / Q_R, the core moments under
+        ``state`` (``momentum``, ``variance``, ``step``, ``subspace_step``) and the refresh bookkeeping. Tools written
+        against the reference's checkpoints can read it; :meth:`load_reference_state_dict` is the inverse."""
+        a = self.arena
+        lo_a, _ = a.adamw_range
+        lo_m, _ = a.muon_range
+        if self.moments8 is not None:
+            ea, es = self.moments8.load(0, self.moments8.numel)
+        else:
+            ea, es = self.exp_avg, self.exp_avg_sq
+        b1, b2 = self.betas
+        base_state, base_params = {}, []
+        for i, seg in enumerate(s_ for s_ in a.segments if s_.tier == "adamw"):
+            sl = slice(seg.offset - lo_a, seg.offset - lo_a + seg.numel)
+            base_state[i] = {"step": torch.tensor(float(self.step_count)), "exp_avg": ea[sl].view(seg.shape).clone(),
+                             "exp_avg_sq": es[sl].view(seg.shape).clone()}
+            base_params.append(i)
+        muon_state, muon_params = {}, []
+        for i, seg in enumerate(s_ for s_ in a.segments if s_.tier == "muon"):
+            sl = slice(seg.offset - lo_m, seg.offset - lo_m + seg.numel)
+            muon_state[i] = {"momentum_buffer": self.muon_mom[sl].view(seg.shape).clone()}
+            muon_params.append(i)
+        groups = []
+        for seg in a.segments:
+            if seg.tier != "steer":
+                continue
+            st = self.steer_state.get(seg.name)
+            K = seg.mat_shape[0]
+            for e in range(K):
+                if st is None or st.get("mode") == "galore" or "Q_L" not in st:
+                    P = None if st is None else st["P"][e]
+                    groups.append({"projection": None if P is None else P[:, :-1].clone(),
+                                   "projection_side": "left" if st is None else st["side"],
+                                   "proj_step": 0 if st is None else st["proj_step"], "Q_L": None, "Q_R": None,
+                                   "proj_basis": None if P is None else P.clone(), "last_c_orth": None,
+                                   "last_steer_step": None, "steer_applied": False, "last_energy_ratio": None,
+                                   "state": {} if st is None or st["m"] is None else
+                                   {"momentum": st["m"][e].clone(), "variance": st["v"][e].clone(), "step": st["step"]},
+                                   "segment": seg.name, "expert_idx": e})
+                    continue
+                ler = st.get("last_energy_ratio")
+                groups.append({
+                    "projection": st["Q_L"][e, :, :-1].clone(), "projection_side": "left", "proj_step": st["proj_step"],
+                    "Q_L": st["Q_L"][e].clone(), "Q_R": st["Q_R"][e].clone(), "proj_basis": None, "last_c_orth": None,
+                    "last_steer_step": st["last_steer_step"], "steer_applied": bool(st["steer_applied"][e]),
+                    "last_energy_ratio": None if ler is None else float(ler[e]),
+                    "state": {"momentum": st["m"][e].clone(), "variance": st["v"][e].clone(), "step": st["step"],
+                              "subspace_step": st["subspace_step"]},
+                    "segment": seg.name, "expert_idx": e})
+        return {
+            "base_optimizer": {"state": base_state, "param_groups": [{"lr": self.lr, "betas": (b1, b2), "eps": self.eps,
+                                                                      "weight_decay": self.weight_decay,
+                                                                      "params": base_params}]},
+            "muon_optimizer": {"state": muon_state, "param_groups": [{"lr": self.muon_lr, "momentum": self.muon_momentum,
+                                                                      "weight_decay": self.muon_weight_decay,
+                                                                      "ns_steps": self.muon_ns_steps, "params": muon_params}]},
+            "step_count": self.step_count, "expert_lr": float(self.expert_lr), "steer_scale": float(self.steer_scale),
+            "param_groups": [{"lr": self.lr, "betas": (b1, b2), "weight_decay": self.weight_decay}],
+            "_last_synced_lr": self.lr, "layer_groups": groups,
+        }
+
+    def load_reference_state_dict(self, sd: Dict) -> None:
+        """Inverse of :meth:`reference_state_dict` (same tier partition and expert order)."""
+        a = self.arena
+        dev = a.device
+        lo_a, _ = a.adamw_range
+        lo_m, _ = a.muon_range
+        ea = torch.zeros(a.adamw_range[1] - lo_a, device=dev)
+        es = torch.zeros_like(ea)
+        base = (sd.get("base_optimizer") or {}).get("state", {})
+        for i, seg in enumerate(s_ for s_ in a.segments if s_.tier == "adamw"):
+            ent = base.get(i, base.get(str(i)))
+            if ent is None:
+                continue
+            sl = slice(seg.offset - lo_a, seg.offset - lo_a + seg.numel)
+            ea[sl] = ent["exp_avg"].to(dev).float().reshape(-1)
+            es[sl] = ent["exp_avg_sq"].to(dev).float().reshape(-1)
+        if self.moments8 is not None:
+            self.moments8.store(0, self.moments8.numel, ea, es)
+        else:
+            self.exp_avg.copy_(ea)
+            self.exp_avg_sq.copy_(es)
+        muon = (sd.get("muon_optimizer") or {}).get("state", {})
+        for i, seg in enumerate(s_ for s_ in a.segments if s_.tier == "muon"):
+            ent = muon.get(i, muon.get(str(i)))
+            if ent is not None:
+                sl = slice(seg.offset - lo_m, seg.offset - lo_m + seg.numel)
+                self.muon_mom[sl] = ent["momentum_buffer"].to(dev).float().reshape(-1)
+        self.step_count = int(sd.get("step_count", 0))
+        if "expert_lr" in sd:
+            self.expert_lr = float(sd["expert_lr"])
+        if "steer_scale" in sd:
+            self.steer_scale = float(sd["steer_scale"])
+        groups = list(sd.get("layer_groups", []))
+        n_expected = sum(s_.mat_shape[0] for s_ in a.segments if s_.tier == "steer")
+        if len(groups) != n_expected:
+            raise ValueError(f"layer group count mismatch: saved {len(groups)}, current {n_expected}")
+        pos = 0
+        self.steer_state = {}
+        for seg in a.segments:
+            if seg.tier != "steer":
+                continue
+            K, m, n = seg.mat_shape
+            gs = groups[pos : pos + K]
+            pos += K
+            if any(g.get("Q_L") is None for g in gs):
+                continue  # no two-sided bases saved for this segment: it starts fresh
+            r1 = gs[0]["Q_L"].shape[-1]
+            stack = lambda key: torch.stack([g[key].to(dev).float() for g in gs])
+            sstack = lambda key: torch.stack([g["state"][key].to(dev).float() for g in gs])
+            ler = [g.get("last_energy_ratio") for g in gs]
+            self.steer_state[seg.name] = {
+                "Q_L": stack("Q_L"), "Q_R": stack("Q_R"), "m": sstack("momentum"), "v": sstack("variance"),
+                "step": int(gs[0]["state"].get("step", 0)), "subspace_step": int(gs[0]["state"].get("subspace_step", 0)),
+                "proj_step": gs[0].get("proj_step"), "last_steer_step": gs[0].get("last_steer_step"), "rank": r1 - 1,
+                "steer_applied": torch.tensor([bool(g.get("steer_applied", False)) for g in gs], device=dev),
+                "has_grad": torch.ones(K, dtype=torch.bool, device=dev),
+                "last_energy_ratio": None if any(x is None for x in ler) else torch.tensor(ler, device=dev),
+            }
+        self._q16.clear()
+
     def load_state_dict(self, sd):
         layout = [(s.name, s.tier, s.offset, s.numel) for s in self.arena.segments]
-        if [tuple(x) for x in sd["layout"]] != layout:
+        if [tuple(x) for x in sd["layout"]] != [tuple(x) for x in layout]:
             raise ValueError("optimizer state layout does not match this model/tier partition")
         self.step_count = int(sd["step_count"])
         self.lr, self.muon_lr, self.expert_lr = float(sd["lr"]), float(sd["muon_lr"]), float(sd["expert_lr"])
         dev = self.arena.device
-        self.exp_avg.copy_(sd["exp_avg"].to(dev))
-        self.exp_avg_sq.copy_(sd["exp_avg_sq"].to(dev))
+        if "steer_scale" in sd:
+            self.steer_scale = float(sd["steer_scale"])
+        if self.moments8 is not None and sd.get("moments8") is not None:
+            self.moments8.load_state_dict(sd["moments8"])
+        elif self.moments8 is not None:
+            self.moments8.store(0, self.moments8.numel, sd["exp_avg"].to(dev).float(), sd["exp_avg_sq"].to(dev).float())
+        elif sd.get("moments8") is not None:
+            from .adam8bit import BlockwiseMoments
+
+            tmp = BlockwiseMoments(self.exp_avg.numel(), dev)
+            tmp.load_state_dict(sd["moments8"])
+            m8, v8 = tmp.load(0, tmp.numel)
+            self.exp_avg.copy_(m8)
+            self.exp_avg_sq.copy_(v8)
+        else:
+            self.exp_avg.copy_(sd["exp_avg"].to(dev))
+            self.exp_avg_sq.copy_(sd["exp_avg_sq"].to(dev))
         self.muon_mom.copy_(sd["muon_momentum"].to(dev))
         if self.arena.flat_master is not None and sd.get("master") is not None:
             self.arena.flat_master.copy_(sd["master"].to(dev))
@@ -611,7 +918,59 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         self._q16.clear()  # derived from the bases just loaded
 
     def get_qr_telemetry(self) -> Dict:
-        return self.qr_telemetry
+        """Fast-path survivals against Householder fall-backs of every QR so far, with the reasons. The counters live on
+        the device between reports; this is the one place that reads them back."""
+        t = flush_qr_telemetry(self.qr_telemetry)
+        total, fb = t["total_qr_calls"], t["householder_fallbacks"]
+        return {
+            "total_qr_calls": total, "cholesky_fast_path_survivals": total - fb,
+            "cholesky_survival_rate_pct": round(100.0 * (total - fb) / max(1, total), 2),
+            "householder_fallbacks": fb, "householder_fallback_rate_pct": round(100.0 * fb / max(1, total), 2),
+            "primary_fallback_reasons": dict(t["primary_fallback_reasons"]),
+            "overlapping_triggers": dict(t["overlapping_triggers"]),
+        }
+
+    @torch.no_grad()
+    def profile_rank_sensitivity(self, ranks=(4, 8, 16, 32, 64, 128), max_segments: int = 8) -> Dict:
+        """How much of the current expert gradients a rank-r two-sided subspace captures: for each candidate rank the
+        energy ratio ||Q_L^T G Q_R||_F^2 / ||G||_F^2 and the relative reconstruction error, averaged over the experts
+        that received gradient, plus the smallest rank reaching 90 % energy (``recommended_rank``). Call it after a
+        backward pass (the gradients are read, nothing is updated) to choose ``rank``
+        (``triune/optim/centroid.py:1542-1609`` of the reference)."""
+        a = self.arena
+        a.fold_autograd_grads()
+        report: Dict = {"ranks": {}, "segments": []}
+        sums = {int(r): [0.0, 0.0, 0] for r in ranks}
+        scratch = new_qr_telemetry()  # the profiler's QR calls do not count as training telemetry
+        for seg in [s_ for s_ in a.segments if s_.tier == "steer"][:max_segments]:
+            K, m, n = seg.mat_shape
+            G = a.grad_view(seg).view(K, m, n).float()
+            nz = G.flatten(1).abs().amax(-1) > 0
+            if not bool(nz.any()):
+                continue
+            G = G[nz]
+            gn = G.pow(2).sum((-2, -1)).clamp_min(1e-30)
+            report["segments"].append(seg.name)
+            for r in sums:
+                rr = max(1, min(r, min(m, n) - 1))
+                QL, QR = two_sided_bases(G, rr, telemetry=scratch)
+                S = QL.transpose(1, 2) @ (G @ QR)
+                energy = S.pow(2).sum((-2, -1)) / gn
+                err = (G - QL @ S @ QR.transpose(1, 2)).pow(2).sum((-2, -1)).sqrt() / gn.sqrt()
+                sums[r][0] += float(energy.sum())
+                sums[r][1] += float(err.sum())
+                sums[r][2] += int(G.shape[0])
+        rec = None
+        for r in sorted(sums):
+            e, err, cnt = sums[r]
+            if cnt == 0:
+                continue
+            report["ranks"][r] = {"energy_ratio": e / cnt, "relative_error": err / cnt, "matrices": cnt}
+            if rec is None and e / cnt >= 0.9:
+                rec = r
+        report["recommended_rank"] = rec if rec is not None else (max(report["ranks"]) if report["ranks"] else None)
+        report["current_rank"] = self.rank
+        return report
 
     def get_telemetry(self) -> Dict:
         """Parameter and optimizer-state memory by tier (bytes)."""
@@ -620,7 +979,8 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         for tier in ("adamw", "muon", "steer"):
             n = sum(s.numel for s in a.segments if s.tier == tier)
             out["tiers"][tier] = {"params": n}
-        out["tiers"]["adamw"]["state_bytes"] = self.exp_avg.numel() * 8
+        out["tiers"]["adamw"]["state_bytes"] = (self.moments8.nbytes() if self.moments8 is not None
+                                                else self.exp_avg.numel() * 8)
         out["tiers"]["muon"]["state_bytes"] = self.muon_mom.numel() * 4
         sb = 0
         for st in self.steer_state.values():

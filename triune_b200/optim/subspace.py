@@ -30,6 +30,19 @@ def new_qr_telemetry() -> Dict:
     }
 
 
+def flush_qr_telemetry(telemetry: Dict) -> Dict:
+    """Fold the device-resident counters of :func:`batched_qr` into the dictionary (one device -> host read)."""
+    pend = telemetry.pop("_pending", None)
+    if pend is not None:
+        vals = [int(v) for v in pend.tolist()]
+        telemetry["householder_fallbacks"] += vals[0]
+        for i, name in enumerate(REASONS):
+            telemetry["primary_fallback_reasons"][name] += vals[1 + i]
+            telemetry["overlapping_triggers"][name] += vals[5 + i]
+    telemetry["cholesky_fast_path_survivals"] = telemetry["total_qr_calls"] - telemetry["householder_fallbacks"]
+    return telemetry
+
+
 def batched_qr(A: torch.Tensor, cond_threshold: float = 1e4, eps_shift: float = 1e-7, orth_tol: float = 1e-4,
                telemetry: Optional[Dict] = None, return_info: bool = False):
     """Orthonormal basis of the columns of each slice of A [K, d, r] (d >= r), fp32.
@@ -82,17 +95,26 @@ def _batched_qr_impl(A, cond_threshold, eps_shift, orth_tol, telemetry, return_i
         Q = Q.clone()
         Q[idx] = Qh
     if telemetry is not None:
+        # Counters accumulate in a device tensor (no host synchronisation on the training path); they are folded into
+        # the dictionary by flush_qr_telemetry at the reporting boundary
+        # (``triune/optim/centroid.py:1393-1455`` of the reference).
         telemetry["total_qr_calls"] += K
-        nfb = int(fallback.sum())
-        telemetry["householder_fallbacks"] += nfb
-        telemetry["cholesky_fast_path_survivals"] += K - nfb
         flags = (degen, chol_fail, cond_fail, orth_fail)
         taken = torch.zeros_like(fallback)
-        for name, f in zip(REASONS, flags):
-            telemetry["overlapping_triggers"][name] += int((f & fallback).sum())
+        rows = [fallback]
+        prims = []
+        for f in flags:
             prim = f & fallback & ~taken
-            telemetry["primary_fallback_reasons"][name] += int(prim.sum())
-            taken |= prim
+            prims.append(prim)
+            taken = taken | prim
+        rows += prims + [f & fallback for f in flags]
+        counts = torch.stack(rows, dim=0).sum(dim=-1, dtype=torch.long)
+        pend = telemetry.get("_pending")
+        if pend is None or pend.device != counts.device:
+            flush_qr_telemetry(telemetry)
+            telemetry["_pending"] = counts
+        else:
+            pend.add_(counts)
     Q = Q.squeeze(0) if squeeze else Q
     if return_info:
         return Q, {"fallback_mask": fallback, "orth_err": orth_err, "degenerate": degen, "cholesky": chol_fail,

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _ext, ops
+from ..profiling import nvtx_range
 from .symm import SymmetricBuffer
 
 CH_PARAMS_DONE = 2
@@ -129,6 +130,8 @@ class FusedDPUpdater:
         hyper = opt.hyper if getattr(opt, "capturable", False) else None
         opt.step_count += 1
         goff, noff, poff = buf.offset("grad"), buf.offset("norm"), buf.offset("param")
+        dp_range = nvtx_range("dp_reduce_scatter_update_allgather")
+        dp_range.__enter__()
         e.dp_reduce_scatter(rank, world, bufs, sigs, mc, goff, noff, self.owned_flat, ep, buf.use_multimem, self.counter,
                             self.status, self.epoch_dev)
         lo, hi = a.adamw_range
@@ -139,6 +142,7 @@ class FusedDPUpdater:
                              opt.exp_avg_sq, opt.lr, b1, b2, opt.eps, opt.weight_decay, opt.step_count, clip,
                              opt._clip_coef, self.norm_out, ep, buf.use_multimem, self.status, self.epoch_dev, hyper)
         ops._tick(2)
+        dp_range.__exit__(None, None, None)
         opt.last_grad_norm = self.norm_out
         opt._step_muon()
         opt._step_steer()

@@ -15,6 +15,40 @@ from typing import Callable, Dict, Optional
 import torch
 
 
+_NVTX = {"on": None}
+
+
+def nvtx_enabled() -> bool:
+    """NVTX ranges are emitted when ``TRIUNE_NVTX=1`` (read once) and CUDA is present."""
+    if _NVTX["on"] is None:
+        import os
+
+        _NVTX["on"] = os.environ.get("TRIUNE_NVTX", "0") == "1" and torch.cuda.is_available()
+    return _NVTX["on"]
+
+
+class nvtx_range:
+    """``with nvtx_range("forward"):`` marks a phase of the step (forward / backward / data-parallel reduction /
+    optimizer) for timeline tools. A no-op unless :func:`nvtx_enabled`; safe inside CUDA-graph capture (ranges are
+    host-side markers)."""
+
+    __slots__ = ("name", "live")
+
+    def __init__(self, name: str):
+        self.name, self.live = name, False
+
+    def __enter__(self):
+        if nvtx_enabled():
+            torch.cuda.nvtx.range_push(self.name)
+            self.live = True
+        return self
+
+    def __exit__(self, *exc):
+        if self.live:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def time_steps(step_fn: Callable[[], object], steps: int = 10, warmup: int = 3) -> Dict[str, float]:
     """CUDA-event timing of ``steps`` calls after ``warmup`` calls; synchronises on both sides."""
     for _ in range(warmup):

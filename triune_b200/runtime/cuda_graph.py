@@ -18,6 +18,7 @@ from typing import Any, Callable, Dict, Optional, Tuple
 import torch
 
 from .. import ops
+from ..profiling import nvtx_range
 
 
 class CUDAGraphEngine:
@@ -43,10 +44,13 @@ class CUDAGraphEngine:
         tr = self.trainer
         eng = tr.engine
         eng.model.train()
-        loss, _ = eng._micro_loss(x, y, n_valid)
-        loss.backward()
-        tr.optimizer.step()
-        tr.optimizer.zero_grad(set_to_none=True)
+        with nvtx_range("forward"):
+            loss, _ = eng._micro_loss(x, y, n_valid)
+        with nvtx_range("backward"):
+            loss.backward()
+        with nvtx_range("optimizer"):
+            tr.optimizer.step()
+            tr.optimizer.zero_grad(set_to_none=True)
         for m in eng._moe:
             m.step_bias()
         return loss.detach()

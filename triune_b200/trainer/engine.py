@@ -27,6 +27,7 @@ import torch
 import torch.nn.functional as F
 
 from ..models.moe import MoE_FFN
+from ..profiling import nvtx_range
 
 
 def _moe_layers(model):
@@ -162,9 +163,11 @@ class TrainingEngine:
             batch = tr.next_batch()
             x, y = batch[0], batch[1]
             n_valid = batch[2] if len(batch) > 2 else None
-            with tr.model_autocast() if hasattr(tr, "model_autocast") else torch.autocast("cpu", enabled=False):
-                loss, st = self._micro_loss(x, y, n_valid)
-            (loss / accum).backward()
+            with nvtx_range("forward"):
+                with tr.model_autocast() if hasattr(tr, "model_autocast") else torch.autocast("cpu", enabled=False):
+                    loss, st = self._micro_loss(x, y, n_valid)
+            with nvtx_range("backward"):
+                (loss / accum).backward()
             tot = loss.detach() if tot is None else tot + loss.detach()
             stats.update(st)
             tokens += x.numel()
@@ -176,8 +179,9 @@ class TrainingEngine:
                 self.optimizer.grad_clip = clip
             elif clip:
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), clip)
-            self.optimizer.step()
-            self.optimizer.zero_grad(set_to_none=True)
+            with nvtx_range("optimizer"):
+                self.optimizer.step()
+                self.optimizer.zero_grad(set_to_none=True)
         for m in self._moe:
             m.step_bias()
         self.step += 1
