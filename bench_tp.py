@@ -7,7 +7,9 @@ between blocks, heads and FFN width split over a group; one batch of `--batch` s
 
 Default model: the dense 1.5B-class configuration (d = 2048, 24 layers, 16 x 128 Gated DeltaNet heads, SwiGLU 5632),
 4 x 2048 tokens per step for the group. `--tp-mode fused` (default) runs the all-gather and the reduce-scatter inside
-the GEMM kernels over NVLink; `--tp-mode nccl` uses library collectives around plain GEMMs. The reference has no tensor
+the GEMM kernels over NVLink; `--tp-mode nccl` uses library collectives around plain GEMMs. With replicas, `--dp-mode
+fused` (default) averages gradients and updates through the NVLink data-parallel kernels over each replica group and
+`--dp-mode nccl` through one NCCL all-reduce. The reference has no tensor
 parallelism, so there is no reference arm. Prints one JSON line on rank 0 (device-timed, maximum over the ranks).
 """
 
@@ -32,6 +34,8 @@ def main():
     ap.add_argument("--mixer", default="", help="override the sequence mixer: gla or gated_deltanet")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (default: the whole world); the rest is data parallel")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"],
+                    help="replica averaging: the fused NVLink reduce-scatter + update + all-gather kernels, or one NCCL all-reduce")
     a = ap.parse_args()
 
     from triune_b200.config import ModelConfig, get_model_config
@@ -67,7 +71,16 @@ def main():
     del full
     torch.cuda.empty_cache()
     local_params = sum(p.numel() for p in model.parameters())
-    opt = CentroidSteerOptimizer(model, lr=1e-4, grad_clip=1.0)
+    # data parallelism across the replicas (ranks holding the same shard): the fused kernels own the optimizer step
+    dp = None
+    if replicas > 1:
+        from triune_b200.parallel.data_parallel import ShardedDataParallel
+
+        dp = ShardedDataParallel(ctx, mode=a.dp_mode, group=dp_group)
+        opt = CentroidSteerOptimizer(model, lr=1e-4, grad_clip=1.0, storage_factory=dp.storage_factory)
+        dp.attach(opt)
+    else:
+        opt = CentroidSteerOptimizer(model, lr=1e-4, grad_clip=1.0)
     build_s = time.time() - t0
 
     # one batch per replica; the ranks of a tensor-parallel group read the same one
@@ -80,8 +93,7 @@ def main():
         loss = model.forward_loss(ids[:, :-1], ids[:, 1:], n_valid=n_valid)
         loss.backward()
         model.allreduce_replicated_grads()
-        average_grads_over_replicas(model, dp_group)
-        opt.step()
+        opt.step()  # with replicas: gradient reduce-scatter + sharded update + parameter all-gather over the dp group
         opt.zero_grad()
         return loss
 
@@ -99,7 +111,8 @@ def main():
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     total = model.reduce_loss(loss)
-    status = torch.tensor([tp.check()], device=dev)
+    dp_status = int(dp._fused.check()) if (dp is not None and dp._fused is not None) else 0
+    status = torch.tensor([max(tp.check(), dp_status)], device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
     mem = torch.tensor([torch.cuda.max_memory_allocated() / 2**30], device=dev)
     dist.all_reduce(mem, op=dist.ReduceOp.MAX)
@@ -111,7 +124,8 @@ def main():
             "data": "synthetic uniform-random token ids from pinned host memory, random-init weights",
             "config": {"model": a.model, "layers": cfg.num_layers, "hidden_dim": cfg.hidden_dim, "mixer": cfg.mixer,
                        "params_total": full_params, "params_per_rank": local_params, "global_batch": a.batch * replicas,
-                       "seq_len": a.seq, "parallelism": f"tp{tp_size} x dp{replicas}", "tp_mode": a.tp_mode, "cuda_graph": False},
+                       "seq_len": a.seq, "parallelism": f"tp{tp_size} x dp{replicas}", "tp_mode": a.tp_mode,
+                       "dp_mode": a.dp_mode if replicas > 1 else "none", "cuda_graph": False},
             "wait_status": int(status), "peak_mem_GB": round(float(mem), 1), "build_s": round(build_s, 1),
             "final_loss": float(total), "impl": "triune_b200",
         }), flush=True)

@@ -96,3 +96,18 @@ def test_tensor_parallel_dense_model(mode):
                 assert v < 2e-2, (k, v)
             else:
                 assert v < 8e-2, (k, v)  # bf16 activations end to end: a few percent on the largest gradient entry
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_context_parallel_gla_on_gpus(nproc):
+    """Sequence split over the ranks with the state handed from rank to rank (NCCL), the local passes on the kernels:
+    equal to the whole-sequence kernel pass and to the fp32 oracle, gradients included."""
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    res = _launch(nproc, {}, worker="mp_cp_gpu_worker.py", port="29631")
+    for r in res:
+        assert r["out_vs_oracle"] < 2e-2 and r["out_vs_kernel"] < 2e-2 and r["out_nograd"] < 2e-2, r
+        for k in ("dq", "dk", "dv", "dg"):
+            assert r[k + "_vs_oracle"] < 5e-2, (k, r)
+        if "state_vs_oracle" in r:
+            assert r["state_vs_oracle"] < 2e-2, r

@@ -449,27 +449,33 @@ __device__ __forceinline__ void cp_async_wait() {
 
 template <int D>
 struct StateCfg {
-  static constexpr int XP = D + 8;                     // row pitch (bf16) of the operand tiles: conflict-free row reads
+  static constexpr int XP = D + 8;                     // row pitch (bf16) of the operand tiles
   static constexpr int X_BYTES = C * XP * 2;
   static constexpr int ADD_BYTES = C * DVS * 4;        // the [64, 32] addend slice (bf16 forward, fp32 reverse)
-  static constexpr int SP = DVS + 4;                   // row pitch (floats) of the state slice and of the product
-  static constexpr int SMEM = 2 * (2 * X_BYTES + ADD_BYTES) + D * SP * 4 + C * SP * 4 + 1024 + 256;
-  static constexpr int CPT = D * DVS / GDN_THREADS;    // state columns per thread in the update (16 or 8)
-  static constexpr int TPR = DVS / CPT;                // threads per state row
+  static constexpr int SP = DVS + 4;                   // row pitch (floats) of the state slice, the product and its partial
+  static constexpr int SMEM = 2 * (2 * X_BYTES + ADD_BYTES) + D * SP * 4 + 2 * C * SP * 4 + 1024 + 256;
+  // update ownership: thread = (group of 4 state rows, CC consecutive columns)
+  static constexpr int CC = D * DVS / GDN_THREADS / 4;  // 4 (D = 128) or 2 (D = 64)
+  static constexpr int TPR = DVS / CC;                  // threads per row group
 };
 
+// Register tiling. Both products are bound by shared-memory bandwidth unless a thread reuses what it loads: a thread
+// owns a 4 x 4 (product 1) or 4 x CC (product 2) block of outputs, so one 16-byte load of state (or product) values
+// and one load of operand values feed 16 multiply-adds. Product 1 splits its reduction over the key dimension between
+// the two halves of the block and adds the partial sums through shared memory.
 template <int D, bool REV>
 __global__ void __launch_bounds__(GDN_THREADS) gdn_state_kernel(
     const __nv_bfloat16* __restrict__ X1, const __nv_bfloat16* __restrict__ X2, const void* __restrict__ add1,
     const float* __restrict__ add2, const float* __restrict__ decay, const float* __restrict__ init,
     __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ states, float* __restrict__ fin, int NT) {
   using Cfg = StateCfg<D>;
-  constexpr int XP = Cfg::XP, SP = Cfg::SP, CPT = Cfg::CPT, TPR = Cfg::TPR;
+  constexpr int XP = Cfg::XP, SP = Cfg::SP, CC = Cfg::CC, TPR = Cfg::TPR;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = aligned_smem(smem_raw);
   uint8_t* stage[2] = {smem, smem + 2 * Cfg::X_BYTES + Cfg::ADD_BYTES};
   float* sS = reinterpret_cast<float*>(smem + 2 * (2 * Cfg::X_BYTES + Cfg::ADD_BYTES));
-  float* sP = sS + D * SP;
+  float* sP = sS + D * SP;      // product 1 (U or dU), fp32
+  float* sRed = sP + C * SP;    // partial sums of product 1 from the upper half of the block
   const int tid = threadIdx.x;
   const int slices = D / DVS, bh = blockIdx.x / slices, slice = blockIdx.x % slices;
   const int col0 = slice * DVS;
@@ -503,14 +509,17 @@ __global__ void __launch_bounds__(GDN_THREADS) gdn_state_kernel(
     cp_async_commit();
   };
 
-  // state slice in registers: thread (d, part) holds S[d][col0 + part * CPT .. + CPT)
-  const int sd = tid / TPR, spart = tid % TPR;
-  float S[CPT];
+  // state slice in registers: thread (row group sg, column group sc) holds S[4 sg .. 4 sg + 3][col0 + CC sc .. + CC)
+  const int sg = tid / TPR, sc = tid % TPR;
+  const int sd0 = sg * 4, scol = sc * CC;
+  float S[4][CC];
 #pragma unroll
-  for (int e = 0; e < CPT; ++e)
-    S[e] = init != nullptr ? init[((long long)bh * D + sd) * D + col0 + spart * CPT + e] : 0.f;
-  // product 1 ownership: row r, columns cg * 8 .. + 8
-  const int pr = tid >> 2, pcg = tid & 3;
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int e = 0; e < CC; ++e)
+      S[r][e] = init != nullptr ? init[((long long)bh * D + sd0 + r) * D + col0 + scol + e] : 0.f;
+  // product 1 ownership: reduction half kh, rows 4 pg .. 4 pg + 3, columns 4 pc .. 4 pc + 3
+  const int kh = tid >> 7, pg = (tid & 127) >> 3, pc = tid & 7;
 
   if (NT > 0) prefetch(0, 0);
   for (int i = 0; i < NT; ++i) {
@@ -518,26 +527,33 @@ __global__ void __launch_bounds__(GDN_THREADS) gdn_state_kernel(
     const int c = REV ? NT - 1 - i : i;
     const long long cidx = (long long)bh * NT + c;
     // state before this chunk goes out (bf16) and into shared memory (fp32) for the first product
-    {
-      __nv_bfloat16* so = states + (cidx * D + sd) * D + col0 + spart * CPT;
 #pragma unroll
-      for (int e8 = 0; e8 < CPT / 8; ++e8) store8_bf16(so + e8 * 8, S + e8 * 8);
-#pragma unroll
-      for (int e4 = 0; e4 < CPT / 4; ++e4)
-        *reinterpret_cast<float4*>(sS + sd * SP + spart * CPT + e4 * 4) =
-            make_float4(S[e4 * 4], S[e4 * 4 + 1], S[e4 * 4 + 2], S[e4 * 4 + 3]);
+    for (int r = 0; r < 4; ++r) {
+      __nv_bfloat16* so = states + (cidx * D + sd0 + r) * D + col0 + scol;
+      if (CC == 4) {
+        *reinterpret_cast<uint2*>(so) = make_uint2(pack_bf16x2(S[r][0], S[r][1]), pack_bf16x2(S[r][2 % CC], S[r][3 % CC]));
+        *reinterpret_cast<float4*>(sS + (sd0 + r) * SP + scol) = make_float4(S[r][0], S[r][1], S[r][2 % CC], S[r][3 % CC]);
+      } else {
+        *reinterpret_cast<uint32_t*>(so) = pack_bf16x2(S[r][0], S[r][1]);
+        *reinterpret_cast<float2*>(sS + (sd0 + r) * SP + scol) = make_float2(S[r][0], S[r][1]);
+      }
     }
     // addends of the update, fetched early
-    const float dec = decay[cidx * D + sd];
-    float a2[CPT];
+    float dec[4], a2[4][CC];
 #pragma unroll
-    for (int e = 0; e < CPT; ++e) a2[e] = 0.f;
-    if (REV) {
-      const float* ap = add2 + (cidx * D + sd) * D + col0 + spart * CPT;
+    for (int r = 0; r < 4; ++r) {
+      dec[r] = decay[cidx * D + sd0 + r];
 #pragma unroll
-      for (int e4 = 0; e4 < CPT / 4; ++e4) {
-        const float4 t = *reinterpret_cast<const float4*>(ap + e4 * 4);
-        a2[e4 * 4] = t.x; a2[e4 * 4 + 1] = t.y; a2[e4 * 4 + 2] = t.z; a2[e4 * 4 + 3] = t.w;
+      for (int e = 0; e < CC; ++e) a2[r][e] = 0.f;
+      if (REV) {
+        const float* ap = add2 + (cidx * D + sd0 + r) * D + col0 + scol;
+        if (CC == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(ap);
+          a2[r][0] = t.x; a2[r][1] = t.y; a2[r][2 % CC] = t.z; a2[r][3 % CC] = t.w;
+        } else {
+          const float2 t = *reinterpret_cast<const float2*>(ap);
+          a2[r][0] = t.x; a2[r][1] = t.y;
+        }
       }
     }
     cp_async_wait<0>();
@@ -546,60 +562,93 @@ __global__ void __launch_bounds__(GDN_THREADS) gdn_state_kernel(
     const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(stage[buf]);
     const __nv_bfloat16* x2 = reinterpret_cast<const __nv_bfloat16*>(stage[buf] + Cfg::X_BYTES);
     const uint8_t* ad = stage[buf] + 2 * Cfg::X_BYTES;
-    // ---- product 1: P[r][cols] = add1[r][cols] -/+ X1[r][:] S[:, cols]
-    {
-      float acc[8];
+    // ---- product 1: P[r][cols] = add1[r][cols] -/+ X1[r][:] S[:, cols]; each block half reduces half of the key dims
+    float acc[4][4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[r][e] = 0.f;
 #pragma unroll 2
-      for (int d8 = 0; d8 < D / 8; ++d8) {
-        float xw[8];
-        unpack8(*reinterpret_cast<const uint4*>(x1 + pr * XP + d8 * 8), xw);
+    for (int d8 = kh * (D / 16); d8 < (kh + 1) * (D / 16); ++d8) {
+      float xw[4][8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float* sp = sS + (d8 * 8 + e) * SP + pcg * 8;
-          const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
-          acc[0] += xw[e] * s0.x; acc[1] += xw[e] * s0.y; acc[2] += xw[e] * s0.z; acc[3] += xw[e] * s0.w;
-          acc[4] += xw[e] * s1.x; acc[5] += xw[e] * s1.y; acc[6] += xw[e] * s1.z; acc[7] += xw[e] * s1.w;
+      for (int r = 0; r < 4; ++r) unpack8(*reinterpret_cast<const uint4*>(x1 + (pg * 4 + r) * XP + d8 * 8), xw[r]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float4 s4 = *reinterpret_cast<const float4*>(sS + (d8 * 8 + e) * SP + pc * 4);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[r][0] += xw[r][e] * s4.x; acc[r][1] += xw[r][e] * s4.y;
+          acc[r][2] += xw[r][e] * s4.z; acc[r][3] += xw[r][e] * s4.w;
         }
       }
-      float base[8];
-      if (REV) {
-        ld8(reinterpret_cast<const float*>(ad) + pr * DVS + pcg * 8, base);
+    }
+    if (kh == 1) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = base[e] + acc[e];
-      } else {
-        unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(ad) + pr * DVS + pcg * 8), base);
+      for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float4*>(sRed + (pg * 4 + r) * SP + pc * 4) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    }
+    __syncthreads();
+    if (kh == 0) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = base[e] - acc[e];
+      for (int r = 0; r < 4; ++r) {
+        const int row = pg * 4 + r;
+        const float4 o = *reinterpret_cast<const float4*>(sRed + row * SP + pc * 4);
+        float v[4] = {acc[r][0] + o.x, acc[r][1] + o.y, acc[r][2] + o.z, acc[r][3] + o.w};
+        if (REV) {
+          const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ad) + row * DVS + pc * 4);
+          v[0] = b.x + v[0]; v[1] = b.y + v[1]; v[2] = b.z + v[2]; v[3] = b.w + v[3];
+        } else {
+          const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(ad) + row * DVS + pc * 4);
+          float b0, b1, b2, b3;
+          unpack_f2(bf16x2_to_f2(raw.x), b0, b1);
+          unpack_f2(bf16x2_to_f2(raw.y), b2, b3);
+          v[0] = b0 - v[0]; v[1] = b1 - v[1]; v[2] = b2 - v[2]; v[3] = b3 - v[3];
+        }
+        *reinterpret_cast<float4*>(sP + row * SP + pc * 4) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<uint2*>(out1 + (cidx * C + row) * D + col0 + pc * 4) =
+            make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
       }
-      st8(sP + pr * SP + pcg * 8, acc);
-      store8_bf16(out1 + (cidx * C + pr) * D + col0 + pcg * 8, acc);
     }
     __syncthreads();
     // ---- product 2: S[d][cols] = e^{b_C}[d] S + add2 +/- sum_t X2[t][d] P[t][cols]
     {
-      float acc[CPT];
+      float up[4][CC];
 #pragma unroll
-      for (int e = 0; e < CPT; ++e) acc[e] = 0.f;
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int e = 0; e < CC; ++e) up[r][e] = 0.f;
 #pragma unroll 4
       for (int t = 0; t < C; ++t) {
-        const float x = __bfloat162float(x2[t * XP + sd]);
-        const float* pp = sP + t * SP + spart * CPT;
-#pragma unroll
-        for (int e4 = 0; e4 < CPT / 4; ++e4) {
-          const float4 p = *reinterpret_cast<const float4*>(pp + e4 * 4);
-          acc[e4 * 4] += x * p.x; acc[e4 * 4 + 1] += x * p.y; acc[e4 * 4 + 2] += x * p.z; acc[e4 * 4 + 3] += x * p.w;
+        const uint2 xr = *reinterpret_cast<const uint2*>(x2 + t * XP + sd0);
+        float xv[4];
+        unpack_f2(bf16x2_to_f2(xr.x), xv[0], xv[1]);
+        unpack_f2(bf16x2_to_f2(xr.y), xv[2], xv[3]);
+        float pv[CC];
+        if (CC == 4) {
+          const float4 p = *reinterpret_cast<const float4*>(sP + t * SP + scol);
+          pv[0] = p.x; pv[1] = p.y; pv[2 % CC] = p.z; pv[3 % CC] = p.w;
+        } else {
+          const float2 p = *reinterpret_cast<const float2*>(sP + t * SP + scol);
+          pv[0] = p.x; pv[1] = p.y;
         }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int e = 0; e < CC; ++e) up[r][e] += xv[r] * pv[e];
       }
 #pragma unroll
-      for (int e = 0; e < CPT; ++e) S[e] = dec * S[e] + a2[e] + (REV ? -acc[e] : acc[e]);
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int e = 0; e < CC; ++e) S[r][e] = dec[r] * S[r][e] + a2[r][e] + (REV ? -up[r][e] : up[r][e]);
     }
     // the next iteration's barrier orders these reads of sP / stage[buf] against their next writes
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int e = 0; e < CPT; ++e) fin[((long long)bh * D + sd) * D + col0 + spart * CPT + e] = S[e];
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int e = 0; e < CC; ++e) fin[((long long)bh * D + sd0 + r) * D + col0 + scol + e] = S[r][e];
 }
 
 // ------------------------------------------------------------------------------------------------

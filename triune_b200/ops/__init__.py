@@ -687,7 +687,8 @@ class _LinearCEFn(torch.autograd.Function):
                 gemm(logits, w, dh[s : s + chunk_rows], b_mn=True)
                 gemm(logits, hc, dw, a_mn=True, b_mn=True, accumulate=not first)
                 if db is not None:
-                    db += logits.sum(0, dtype=torch.float32)
+                    e.colsum(logits, db)  # column sums added into the fp32 bias gradient (two-phase kernel)
+                    _tick(2)
                 first = False
         loss = losses.sum() * inv
         if need_grad:

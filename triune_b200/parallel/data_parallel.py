@@ -18,8 +18,22 @@ import torch
 import torch.distributed as dist
 
 
+class _GroupView:
+    """rank / world_size of a process sub-group behind the attribute names of ``DistributedContext``."""
+
+    def __init__(self, ctx, group):
+        self.group = group
+        self.rank, self.world_size = dist.get_rank(group), dist.get_world_size(group)
+        self.device, self.local_rank = ctx.device, getattr(ctx, "local_rank", 0)
+
+
 class ShardedDataParallel:
-    def __init__(self, ctx, mode: str = "nccl", use_multimem=None):
+    def __init__(self, ctx, mode: str = "nccl", use_multimem=None, group=None):
+        """``group``: the data-parallel process group when it is not the whole world (replicas of a tensor-parallel
+        or pipeline-parallel model: the ranks that hold the same shard)."""
+        self.group = group
+        if group is not None:
+            ctx = _GroupView(ctx, group)
         self.ctx = ctx
         self.mode = mode
         self.optimizer = None
@@ -30,7 +44,7 @@ class ShardedDataParallel:
             from .fused_dp import SymmetricArenaStorage
 
             # pass this to the optimizer (``storage_factory=dp.storage_factory``) so its arenas are peer-visible
-            self.storage_factory = SymmetricArenaStorage(ctx, use_multimem=use_multimem)
+            self.storage_factory = SymmetricArenaStorage(ctx, use_multimem=use_multimem, group=group)
 
     def attach(self, optimizer) -> None:
         self.optimizer = optimizer
@@ -38,10 +52,11 @@ class ShardedDataParallel:
             raise ValueError("ShardedDataParallel needs an arena-based optimizer (CentroidSteerOptimizer)")
         if self.ctx.world_size > 1:
             # identical initial parameters on every rank
-            dist.broadcast(optimizer.arena.flat_param, src=0)
+            src = 0 if self.group is None else dist.get_global_rank(self.group, 0)
+            dist.broadcast(optimizer.arena.flat_param, src=src, group=self.group)
             optimizer.arena.sync_master_from_params()
             for b in optimizer.model.buffers():
-                dist.broadcast(b, src=0)
+                dist.broadcast(b, src=src, group=self.group)
         if self.mode == "fused" and self.ctx.world_size > 1:
             from .fused_dp import FusedDPUpdater
 
@@ -54,7 +69,7 @@ class ShardedDataParallel:
                 if self._fused is not None:
                     return self._fused.step()
                 g = optimizer.arena.flat_grad
-                dist.all_reduce(g, op=dist.ReduceOp.SUM)
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)
                 g.mul_(1.0 / self.ctx.world_size)
                 self.comm_bytes += g.numel() * 4
                 self._sync_routing_statistics()
@@ -75,7 +90,7 @@ class ShardedDataParallel:
         if not tensors:
             return
         flat = torch.cat([t.detach().float().reshape(-1) for t in tensors])
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
         flat.mul_(1.0 / self.ctx.world_size)
         off = 0
         for t in tensors:

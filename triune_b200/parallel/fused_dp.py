@@ -37,8 +37,9 @@ STATS_MAX = 1 << 16  # floats of routing statistics the symmetric buffer has roo
 class SymmetricArenaStorage:
     """``storage_factory`` for :class:`ParamArena` that places both arenas in a :class:`SymmetricBuffer`."""
 
-    def __init__(self, ctx, use_multimem=None):
+    def __init__(self, ctx, use_multimem=None, group=None):
         self.ctx = ctx
+        self.group = group
         self.use_multimem = use_multimem
         self.buffer = None
         self.total = 0
@@ -50,7 +51,7 @@ class SymmetricArenaStorage:
         self.buffer = SymmetricBuffer(
             {"param": total * 2, "grad": total * 4, "norm": 2 * w * 4 + 64, "metric": 16 * w * 4,
              "stats": STATS_MAX * w * 4},
-            device, use_multimem=self.use_multimem)
+            device, group=self.group, use_multimem=self.use_multimem)
         return self.buffer.view("param", torch.bfloat16, total), self.buffer.view("grad", torch.float32, total)
 
 
