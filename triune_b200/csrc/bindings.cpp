@@ -33,7 +33,7 @@ void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool 
              double alpha, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& aux_in,
              const c10::optional<Tensor>& aux_out, const c10::optional<Tensor>& row_scale,
              const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& group_offsets,
-             const c10::optional<Tensor>& status) {
+             const c10::optional<Tensor>& status, double beta) {
   check_bf16_cuda(a, "a");
   check_bf16_cuda(b, "b");
   TORCH_CHECK(c.is_cuda(), "c must be CUDA");
@@ -50,6 +50,7 @@ void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool 
   if (c.scalar_type() == at::kFloat) g.flags |= tb::GF_OUT_F32;
   else TORCH_CHECK(c.scalar_type() == at::kBFloat16, "c must be bf16 or fp32");
   g.alpha = (float)alpha;
+  g.beta = (float)beta;
   const int ad = a.dim(), bd = b.dim(), cd = c.dim();
   TORCH_CHECK(ad >= 2 && bd >= 2 && cd >= 2, "operands must be at least 2-D");
   g.lda = a.stride(-2);
@@ -471,6 +472,18 @@ void muon_apply(Tensor& master, const Tensor& o, const c10::optional<Tensor>& pa
                         hyper.has_value() && hyper->defined() ? hyper->data_ptr<float>() : nullptr, cur_stream());
 }
 
+// X [batch, m, n] bf16 contiguous (m <= n) -> X / safe spectral bound, bf16 (see launch_ns_prepare)
+Tensor ns_prepare(const Tensor& x, double eps) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && x.size(2) % 8 == 0 && x.size(1) <= x.size(2),
+              "ns_prepare: contiguous [batch, m, n] with m <= n and n % 8 == 0");
+  TORCH_CHECK((x.size(1) + x.size(2)) * 4 <= 200 * 1024, "ns_prepare: m + n too large for one CTA's shared memory");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  tb::launch_ns_prepare(bf(x), bfm(y), (int)x.size(0), (int)x.size(1), (int)x.size(2), (float)eps, cur_stream());
+  return y;
+}
+
 void axpby_bf16(Tensor& x, const Tensor& y, double a, double b) {
   c10::cuda::CUDAGuard guard(x.device());
   tb::launch_axpby_bf16(bfm(x), bf(y), (float)a, (float)b, x.numel(), cur_stream());
@@ -563,6 +576,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_momentum", &muon_momentum);
   m.def("muon_apply", &muon_apply);
   m.def("axpby_bf16", &axpby_bf16);
+  m.def("ns_prepare", &ns_prepare);
   m.def("triangular_adamw", &triangular_adamw);
   m.def("steer_update", &steer_update);
   m.def("route_tiers", &route_tiers);

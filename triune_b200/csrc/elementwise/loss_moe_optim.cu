@@ -11,6 +11,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "../common/per_device.h"
 #include "../common/ptx.cuh"
 #include "elementwise.cuh"
 
@@ -320,6 +321,103 @@ __global__ void __launch_bounds__(256) axpby_bf16_kernel(__nv_bfloat16* __restri
     x[i] = __float2bfloat16(a * __bfloat162float(x[i]) + b * __bfloat162float(y[i]));
 }
 
+// Newton-Schulz set-up, one CTA per matrix X [m, n] (m <= n, bf16, rows contiguous): Frobenius norm, a four-step power
+// iteration for the largest singular value (v <- X^T X v from the constant start vector, the deterministic estimate of
+// triune/kernels/fast_muon.py:15-91), and Y = X / max(1.15 sigma, ||X||_F / sqrt(m), 0.7 ||X||_F) so that the quintic
+// iteration starts inside its basin. Replaces nine fp32 library products and three reductions per shape group.
+constexpr int NSP_THREADS = 256;
+__global__ void __launch_bounds__(NSP_THREADS) ns_prepare_kernel(const __nv_bfloat16* __restrict__ X,
+                                                                 __nv_bfloat16* __restrict__ Y, int m, int n, float eps) {
+  extern __shared__ float nsp_smem[];
+  float* v = nsp_smem;       // [n]
+  float* w = v + n;          // [m]
+  __shared__ float red[NSP_THREADS / 32];
+  const __nv_bfloat16* x = X + (long long)blockIdx.x * m * n;
+  __nv_bfloat16* y = Y + (long long)blockIdx.x * m * n;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nvec = n >> 3;
+  const long long total_vec = (long long)m * nvec;
+  float ss = 0.f;
+  for (long long i = tid; i < total_vec; i += NSP_THREADS) {
+    const uint4 u = reinterpret_cast<const uint4*>(x)[i];
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(p2[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  const float fro = fmaxf(sqrtf(block_sum<NSP_THREADS>(ss, red)), eps);
+  const float v0 = rsqrtf((float)n);
+  for (int c = tid; c < n; c += NSP_THREADS) v[c] = v0;
+  __syncthreads();
+  float sigma = 0.f;
+  for (int it = 0; it < 5; ++it) {
+    // w = X v: one warp per row
+    for (int r = warp; r < m; r += NSP_THREADS / 32) {
+      const uint4* row = reinterpret_cast<const uint4*>(x + (long long)r * n);
+      float acc = 0.f;
+      for (int c8 = lane; c8 < nvec; c8 += 32) {
+        const uint4 u = row[c8];
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const float* vp = v + c8 * 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(p2[j]);
+          acc += f.x * vp[2 * j] + f.y * vp[2 * j + 1];
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) w[r] = acc;
+    }
+    __syncthreads();
+    if (it == 4) {
+      float s2 = 0.f;
+      for (int r = tid; r < m; r += NSP_THREADS) s2 += w[r] * w[r];
+      sigma = sqrtf(block_sum<NSP_THREADS>(s2, red));
+      break;
+    }
+    // v = X^T w: a thread owns eight columns and walks the rows (coalesced across threads)
+    float n2 = 0.f;
+    for (int c8 = tid; c8 < nvec; c8 += NSP_THREADS) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int r = 0; r < m; ++r) {
+        const uint4 u = reinterpret_cast<const uint4*>(x + (long long)r * n)[c8];
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const float wr = w[r];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(p2[j]);
+          acc[2 * j] += f.x * wr;
+          acc[2 * j + 1] += f.y * wr;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) n2 += acc[j] * acc[j];
+      // v is only read in the X v phase, which ended at the barrier above: it can be overwritten here
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[c8 * 8 + j] = acc[j];
+    }
+    const float nrm = fmaxf(sqrtf(block_sum<NSP_THREADS>(n2, red)), eps);
+    const float inv = 1.f / nrm;
+    __syncthreads();
+    for (int c = tid; c < n; c += NSP_THREADS) v[c] *= inv;
+    __syncthreads();
+  }
+  const float safe = fmaxf(fmaxf(1.15f * sigma, fro * rsqrtf((float)m)), 0.7f * fro);
+  const float sc = 1.f / safe;
+  for (long long i = tid; i < total_vec; i += NSP_THREADS) {
+    uint4 u = reinterpret_cast<const uint4*>(x)[i];
+    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(p2[j]);
+      p2[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    reinterpret_cast<uint4*>(y)[i] = u;
+  }
+}
+
 __global__ void __launch_bounds__(256) triangular_adamw_kernel(const float* __restrict__ S, float* __restrict__ m,
                                                                float* __restrict__ v, float* __restrict__ delta,
                                                                long long total, int r1, float beta1, float beta2,
@@ -485,6 +583,14 @@ void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* par
                        float wd, float scale, const float* hyper, cudaStream_t s) {
   if (n == 0) return;
   muon_apply_kernel<<<flat_grid(n), 256, 0, s>>>(master, o, param_bf16, n, lr, wd, scale, hyper);
+}
+
+void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int m, int n, float eps, cudaStream_t s) {
+  if (batch <= 0) return;
+  const size_t smem = (size_t)(m + n) * sizeof(float);
+  static PerDeviceOnce once;
+  if (once.first_use()) cudaFuncSetAttribute(ns_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  ns_prepare_kernel<<<batch, NSP_THREADS, smem, s>>>(X, Y, m, n, eps);
 }
 
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s) {

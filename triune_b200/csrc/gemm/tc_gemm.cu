@@ -267,6 +267,7 @@ void dispatch_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const
     if (epi == EPI_GELU) return launch_variant<BN, A_MN, B_MN, EPI_GELU>(tmA, tmB, tmC, tmAux, kp, grid, s);
     if (epi == EPI_MULAUX) return launch_variant<BN, A_MN, B_MN, EPI_MULAUX>(tmA, tmB, tmC, tmAux, kp, grid, s);
     if (epi == EPI_DSWIGLU) return launch_variant<BN, A_MN, B_MN, EPI_DSWIGLU>(tmA, tmB, tmC, tmAux, kp, grid, s);
+    if (epi == EPI_ADDAUX) return launch_variant<BN, A_MN, B_MN, EPI_ADDAUX>(tmA, tmB, tmC, tmAux, kp, grid, s);
     if constexpr (!B_MN) {
       if (epi == EPI_SWIGLU) return launch_variant<BN, A_MN, B_MN, EPI_SWIGLU>(tmA, tmB, tmC, tmAux, kp, grid, s);
     }
@@ -315,6 +316,10 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0) throw std::runtime_error("tc_gemm: C must be 16-byte aligned");
   if (a.mode == GEMM_GROUPED_K && (a.group_offsets == nullptr || !a.a_mn_major || !a.b_mn_major))
     throw std::runtime_error("tc_gemm: grouped-K needs group_offsets and MN-major operands");
+  const bool addaux = (a.flags & GF_ADDAUX) != 0;
+  if (addaux && (a.aux_in == nullptr || a.a_mn_major || a.bias != nullptr || a.row_scale != nullptr ||
+                 (a.flags & (GF_OUT_F32 | GF_ACCUMULATE | GF_GELU | GF_DGELU | GF_SWIGLU | GF_DSWIGLU))))
+    throw std::runtime_error("tc_gemm: the add-rows epilogue takes K-major A, bf16 output, rows to add, nothing else");
   const bool swiglu = (a.flags & GF_SWIGLU) != 0, dswiglu = (a.flags & GF_DSWIGLU) != 0;
   if (swiglu || dswiglu) {
     if (a.mode != GEMM_DENSE || a.batch > 1 || a.a_mn_major || (a.flags & (GF_OUT_F32 | GF_ACCUMULATE | GF_GELU | GF_DGELU)) ||
@@ -351,6 +356,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.num_m = (a.M + BM - 1) / BM;
   kp.num_n = (a.N + n_out - 1) / n_out;
   kp.n_split = a.n_split;
+  kp.beta = a.beta;
   kp.ldc = a.ldc; kp.strideC = a.strideC;
   kp.a_batched = a.strideA != 0; kp.b_batched = a.strideB != 0;
   kp.alpha = a.alpha;
@@ -422,7 +428,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
     tmAux = make_tmap_3d(a.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.N, (uint64_t)a.M, c_batches,
                          (uint64_t)a.ldc * 2ull, (c_batches > 1 ? (uint64_t)a.strideC : (uint64_t)a.ldc * (uint64_t)a.M) * 2ull, 32, 32);
   const int grid = kp.total_tiles < sm_count() ? kp.total_tiles : sm_count();
-  const int epi = swiglu ? EPI_SWIGLU
+  const int epi = addaux ? EPI_ADDAUX : swiglu ? EPI_SWIGLU
                   : (dswiglu ? EPI_DSWIGLU
                      : ((kp.flags & GF_GELU) ? EPI_GELU : ((kp.flags & GF_DGELU) ? EPI_MULAUX : (c_f32 ? EPI_PLAIN_F32 : EPI_PLAIN))));
   if (BN == 256) dispatch_major<256>(a.a_mn_major, a.b_mn_major, epi, tmA, tmB, tmC, tmAux, kp, grid, stream);

@@ -20,6 +20,7 @@ enum GemmFlags : int {
   GF_PAIRED_GROUPS = 16,  // GEMM_GROUPED_M: every group's rows are padded to 256, so tile_group[2i] == tile_group[2i+1]
   // SwiGLU over a fused gate/up weight B = [gate rows (n_split) ; up rows (n_split)], dense mode, K-major operands:
   GF_SWIGLU = 32,   // C [M, N = n_split] = silu(A gate^T) * (A up^T); aux_out [M, 2 N] optionally receives both pre-activations
+  GF_ADDAUX = 128,  // C = alpha * A B^T + beta * aux_in (aux_in: bf16, C's layout; bf16 output, no bias)
   GF_DSWIGLU = 64,  // acc = A B^T [M, N = n_split] is d(hidden); aux_in [M, 2 N] holds gate | up; C [M, 2 N] = d(gate) | d(up)
 };
 
@@ -47,6 +48,7 @@ struct GemmArgs {
   const int* group_offsets;     // GEMM_GROUPED_K: [batch+1], multiples of 64
   int* status;                  // optional device status word (see KernelStatus)
   int n_split;                  // GF_SWIGLU / GF_DSWIGLU: FFN hidden width (N); 0 otherwise
+  float beta;                   // GF_ADDAUX: weight of aux_in
 };
 
 // Launches on `stream`. Throws std::runtime_error on invalid arguments.

@@ -47,6 +47,7 @@ struct KParams {
   int splits;           // split-K factor (dense mode, fp32 accumulate only)
   int iters_per_split;  // K iterations (of 64) handled by one split
   int n_split;          // SwiGLU epilogues: column offset of the "up" half (= FFN hidden width)
+  float beta;           // EPI_ADDAUX: weight of the added rows
 };
 
 struct Tile {
@@ -137,7 +138,9 @@ __device__ __forceinline__ void report(const KParams& p, int code) {
 //                  (the producer loads the two row blocks of the fused gate/up weight side by side); output =
 //                  silu(gate) * up, and optionally both pre-activations go out as bf16 (aux_out, [M, 2 * n_split])
 //   EPI_DSWIGLU    acc = d(hidden); reads gate/up from aux_in and writes d(gate), d(up) into C ([M, 2 * n_split])
-enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3, EPI_SWIGLU = 4, EPI_DSWIGLU = 5 };
+//   EPI_ADDAUX     output = alpha * acc + beta * aux_in (bf16 rows of C's layout): the blends of the Newton-Schulz
+//                  iteration (b A + c A A, a X + B X) without separate elementwise passes
+enum { EPI_PLAIN = 0, EPI_PLAIN_F32 = 1, EPI_GELU = 2, EPI_MULAUX = 3, EPI_SWIGLU = 4, EPI_DSWIGLU = 5, EPI_ADDAUX = 6 };
 
 // One accumulator tile (128 rows x n_cols fp32 in TMEM at tmem_acc) through the epilogue EPI and out to global
 // memory. Called by the eight epilogue warps of a CTA: a warp can only read the TMEM lanes of its quarter
@@ -186,7 +189,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
     // Multiplier rows (the activation derivative saved by the forward pass): issue the loads first so their
     // latency hides behind the TMEM read.
     uint4 auxv[4];
-    if constexpr (EPI == EPI_MULAUX) {
+    if constexpr (EPI == EPI_MULAUX || EPI == EPI_ADDAUX) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int gn = n0 + c + j * 8;
@@ -300,6 +303,15 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
           q[j * 4 + 1] = f2_to_bf16x2(mul2(v[(j * 4 + 1) % NP], bf16x2_to_f2(auxv[j].y)));
           q[j * 4 + 2] = f2_to_bf16x2(mul2(v[(j * 4 + 2) % NP], bf16x2_to_f2(auxv[j].z)));
           q[j * 4 + 3] = f2_to_bf16x2(mul2(v[(j * 4 + 3) % NP], bf16x2_to_f2(auxv[j].w)));
+        }
+      } else if constexpr (EPI == EPI_ADDAUX) {
+        const uint64_t beta2 = pack_f2(p.beta, p.beta);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q[j * 4 + 0] = f2_to_bf16x2(fma2(bf16x2_to_f2(auxv[j].x), beta2, v[(j * 4 + 0) % NP]));
+          q[j * 4 + 1] = f2_to_bf16x2(fma2(bf16x2_to_f2(auxv[j].y), beta2, v[(j * 4 + 1) % NP]));
+          q[j * 4 + 2] = f2_to_bf16x2(fma2(bf16x2_to_f2(auxv[j].z), beta2, v[(j * 4 + 2) % NP]));
+          q[j * 4 + 3] = f2_to_bf16x2(fma2(bf16x2_to_f2(auxv[j].w), beta2, v[(j * 4 + 3) % NP]));
         }
       } else {
         if (p.row_scale) {

@@ -380,7 +380,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   } else if (a.mode != GEMM_DENSE || a.batch > 1 || a.strideA != 0 || a.strideB != 0) {
     return false;
   }
-  if (a.flags & (GF_GELU | GF_DGELU)) return false;
+  if (a.flags & (GF_GELU | GF_DGELU | GF_ADDAUX)) return false;
   if (a.M < 2 * BM) return false;
   const int num_m_tiles = (a.M + BM - 1) / BM;
   if ((num_m_tiles & 1) && num_m_tiles < 9) return false;  // an odd tile leaves half a pair idle: too costly when few
@@ -407,6 +407,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.num_m = (a.M + BM - 1) / BM;
   kp.num_n = a.N / n_out;
   kp.n_split = a.n_split;
+  kp.beta = 0.f;
   kp.ldc = a.ldc; kp.strideC = a.strideC;
   kp.a_batched = 0; kp.b_batched = 0;
   kp.alpha = a.alpha;

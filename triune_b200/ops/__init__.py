@@ -22,7 +22,7 @@ from .. import _ext
 from . import reference as ref
 
 GEMM_DENSE, GEMM_GROUPED_M, GEMM_GROUPED_K = 0, 1, 2
-GF_OUT_F32, GF_ACCUMULATE, GF_GELU, GF_DGELU, GF_PAIRED_GROUPS = 1, 2, 4, 8, 16
+GF_OUT_F32, GF_ACCUMULATE, GF_GELU, GF_DGELU, GF_PAIRED_GROUPS, GF_ADDAUX = 1, 2, 4, 8, 16, 128
 
 # kernel launch accounting (used by bench.py's ``gpu_launches``)
 _LAUNCHES = {"count": 0}
@@ -74,6 +74,8 @@ def gemm(
     group_offsets: Optional[torch.Tensor] = None,
     num_groups: int = 0,
     paired_groups: bool = False,
+    add_aux: Optional[torch.Tensor] = None,
+    beta: float = 1.0,
 ) -> torch.Tensor:
     """out = alpha * A @ B^T with a fused epilogue, on tcgen05 tensor cores.
 
@@ -82,6 +84,7 @@ def gemm(
     (``group_offsets``; then ``a`` [R, M], ``b`` [R, N] and out is [G, M, N]).
     ``gelu`` applies tanh-GELU after the bias; ``aux_out`` (bf16, out's layout) then receives GELU'(pre-activation),
     which a later call takes as ``dgelu_aux`` to form ``out = alpha * (A @ B^T) * dgelu_aux`` in its epilogue.
+    ``add_aux`` (bf16, out's layout) forms ``out = alpha * A @ B^T + beta * add_aux`` in the epilogue.
     ``paired_groups`` (rows grouped by expert only) promises that every expert's rows are padded to a multiple of 256,
     which lets long reductions run on CTA pairs.
     """
@@ -99,9 +102,14 @@ def gemm(
     flags = (GF_ACCUMULATE if accumulate else 0) | (GF_GELU if gelu else 0) | (GF_DGELU if dgelu_aux is not None else 0)
     if paired_groups and mode == GEMM_GROUPED_M:
         flags |= GF_PAIRED_GROUPS
+    aux_in = dgelu_aux
+    if add_aux is not None:
+        assert dgelu_aux is None and not gelu and not accumulate and out_dtype == torch.bfloat16
+        flags |= GF_ADDAUX
+        aux_in = add_aux
     _ext.ext().tc_gemm(
-        a, b, out, a_mn, b_mn, mode, flags, float(alpha), bias, dgelu_aux, aux_out, row_scale, tile_group,
-        group_offsets, None,
+        a, b, out, a_mn, b_mn, mode, flags, float(alpha), bias, aux_in, aux_out, row_scale, tile_group,
+        group_offsets, None, float(beta),
     )
     _tick()
     return out

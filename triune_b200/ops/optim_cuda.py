@@ -22,9 +22,9 @@ def ns_supported(G: torch.Tensor) -> bool:
 def newton_schulz(G: torch.Tensor, steps: int = 3, coeffs=(1.875, -1.25, 0.375), eps: float = 1e-7) -> torch.Tensor:
     """Batched quintic Newton-Schulz polar iteration; every product runs on the tcgen05 GEMM.
 
-    Per iteration: A = X X^T; B = b A + c A A; X <- a X + B X (five launches: three GEMMs with the
-    blends folded into their accumulate epilogues, two scaled copies). The spectral-norm safeguard
-    of the reference (``triune/kernels/fast_muon.py:15-91``) is computed with a short power iteration.
+    Per iteration: A = X X^T; T = c A A + b A; X <- T X + a X: three GEMM launches, the two blends in the GEMMs'
+    add-rows epilogue. The spectral-norm safeguard of the reference (``triune/kernels/fast_muon.py:15-91``: Frobenius
+    norm and a four-step power iteration) and the scaling run in one set-up kernel with one CTA per matrix.
     """
     from . import gemm, _tick
 
@@ -34,25 +34,30 @@ def newton_schulz(G: torch.Tensor, steps: int = 3, coeffs=(1.875, -1.25, 0.375),
     transposed = X.shape[-2] > X.shape[-1]
     if transposed:
         X = X.transpose(-1, -2)
-    Xf = X.float()
-    m, n = Xf.shape[-2], Xf.shape[-1]
-    fro = Xf.flatten(-2).norm(dim=-1).clamp_min(eps)
-    vec = torch.full((Xf.shape[0], n, 1), 1.0 / math.sqrt(n), device=G.device, dtype=torch.float32)
-    for _ in range(4):
-        w = Xf @ vec
-        vec = Xf.transpose(-1, -2) @ w
-        vec = vec / vec.norm(dim=-2, keepdim=True).clamp_min(eps)
-    sigma = (Xf @ vec).norm(dim=-2).squeeze(-1)
-    safe = torch.maximum(torch.maximum(1.15 * sigma, fro / math.sqrt(m)), 0.7 * fro)
-    Xb = (Xf / safe[:, None, None]).to(torch.bfloat16).contiguous()
-    Xn = torch.empty_like(Xb)
+    m, n = X.shape[-2], X.shape[-1]
     e = _ext.ext()
+    if (m + n) * 4 <= 200 * 1024:
+        # Frobenius norm, power iteration and scaling in ONE kernel (one CTA per matrix)
+        Xb = e.ns_prepare(X.to(torch.bfloat16).contiguous(), float(eps))
+        _tick()
+    else:
+        Xf = X.float()
+        fro = Xf.flatten(-2).norm(dim=-1).clamp_min(eps)
+        vec = torch.full((Xf.shape[0], n, 1), 1.0 / math.sqrt(n), device=G.device, dtype=torch.float32)
+        for _ in range(4):
+            w = Xf @ vec
+            vec = Xf.transpose(-1, -2) @ w
+            vec = vec / vec.norm(dim=-2, keepdim=True).clamp_min(eps)
+        sigma = (Xf @ vec).norm(dim=-2).squeeze(-1)
+        safe = torch.maximum(torch.maximum(1.15 * sigma, fro / math.sqrt(m)), 0.7 * fro)
+        Xb = (Xf / safe[:, None, None]).to(torch.bfloat16).contiguous()
+    Xn = torch.empty_like(Xb)
+    A = torch.empty(Xb.shape[0], m, m, device=G.device, dtype=torch.bfloat16)
+    T = torch.empty_like(A)
     for _ in range(steps):
-        A = gemm(Xb, Xb)  # [B, m, m]
-        T = A * b
-        gemm(A, A, T, alpha=c, accumulate=True)  # T = b A + c A A   (A symmetric: A A^T = A A)
-        torch.mul(Xb, a, out=Xn)
-        gemm(T, Xb, Xn, b_mn=True, accumulate=True)  # Xn = a X + T X
+        gemm(Xb, Xb, A)                                   # A = X X^T
+        gemm(A, A, T, alpha=c, add_aux=A, beta=b)         # T = c A A + b A   (A symmetric: A A^T = A A)
+        gemm(T, Xb, Xn, b_mn=True, add_aux=Xb, beta=a)    # X <- T X + a X
         Xb, Xn = Xn, Xb
     out = Xb.transpose(-1, -2) if transposed else Xb
     out = out.to(G.dtype)
