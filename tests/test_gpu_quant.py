@@ -71,6 +71,65 @@ def test_nvfp4_linear_paths(M):
     assert (y - want).abs().max() <= 2e-2 * want.abs().max()
 
 
+@pytest.mark.parametrize("hadamard", [False, True])
+def test_nvfp4_activation_quantiser_matches_oracle(hadamard):
+    torch.manual_seed(5)
+    x = (torch.randn(200, 384, device="cuda") * 1.5).bfloat16()
+    p, sf = quant_cuda.nvfp4_quantize_act(x, hadamard)
+    p_ref, s_ref = ref.nvfp4_quantize_act(x, hadamard)
+    s = ref.nvfp4_unblock_scales(sf, 200, 384)
+    assert (s.view(torch.uint8) != s_ref.view(torch.uint8)).float().mean() < 0.01
+    assert (p != p_ref).float().mean() < 0.02
+    # the blocked layout: re-blocking the oracle's scales gives the kernel's buffer wherever the scales agree
+    same = (s.view(torch.uint8) == s_ref.view(torch.uint8)).all()
+    if same:
+        assert torch.equal(ref.nvfp4_block_scales(s_ref, 384), sf)
+    # weight scales through the layout kernel
+    w_s = ref.nvfp4_quantize(torch.randn(136, 384, device="cuda"))[1]
+    assert torch.equal(quant_cuda.nvfp4_block_scales(w_s, 384), ref.nvfp4_block_scales(w_s, 384))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (256, 384, 512), (200, 136, 384), (1000, 1536, 2048), (4096, 512, 1056)])
+def test_nvfp4_block_scaled_gemm_matches_decoded_product(M, N, K):
+    """E2M1 x E2M1 with both scale sets applied by the tensor core == the fp32 product of the decoded operands."""
+    torch.manual_seed(6)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda") * 0.05
+    wp, ws, wt = quant_cuda.nvfp4_quantize(w)
+    a_p, a_sf = quant_cuda.nvfp4_quantize_act(x, False)
+    y, status = quant_cuda._ext.ext().nvfp4_gemm(a_p, a_sf, wp, quant_cuda.nvfp4_block_scales(ws, K), float(wt))
+    assert int(status.item()) == 0
+    a = ref.nvfp4_dequantize(a_p, ref.nvfp4_unblock_scales(a_sf, M, K), 1.0, torch.float32)
+    want = a @ ref.nvfp4_dequantize(wp, ws, wt, torch.float32).t()
+    err = (y.float() - want).abs().max() / want.abs().max()
+    assert err < 1e-2, err  # bf16 output rounding only: the operands are identical and the products exact in fp32
+    full = x.float() @ w.t()
+    assert torch.nn.functional.cosine_similarity(y.float().flatten(), full.flatten(), dim=0) > 0.97
+
+
+def test_nvfp4_module_takes_the_block_scaled_path_for_prefill():
+    from triune_b200.models.quant_linear import NVFP4Linear
+
+    torch.manual_seed(7)
+    lin = torch.nn.Linear(512, 384, bias=True).cuda().bfloat16()
+    x = torch.randn(3, 50, 512, device="cuda").bfloat16()
+    want = lin(x).float()
+    for hadamard in (False, True):
+        m = NVFP4Linear.from_linear(lin, hadamard=hadamard)
+        assert m._w4a4_ready(x.reshape(-1, 512))
+        with torch.no_grad():
+            y = m(x).float()
+            oracle = ref.nvfp4_w4a4_linear(x.reshape(-1, 512), m.packed_weight, m.block_scales, m.tensor_scale, hadamard)
+        assert int(quant_cuda.last_gemm_status.item()) == 0
+        oracle = oracle.reshape(3, 50, 384) + lin.bias.float()
+        assert (y - oracle).abs().max() <= 3e-2 * oracle.abs().max()  # differs only where a scale or code rounds the other way
+        assert torch.nn.functional.cosine_similarity(y.flatten(), want.flatten(), dim=0) > 0.97
+        m.w4a4 = False
+        with torch.no_grad():
+            y16 = m(x).float()
+        assert torch.nn.functional.cosine_similarity(y16.flatten(), want.flatten(), dim=0) > 0.98
+
+
 def test_fwht16_kernel():
     x = torch.randn(64, 128, device="cuda").bfloat16()
     y = quant_cuda.fwht16(x)

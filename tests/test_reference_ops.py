@@ -146,6 +146,22 @@ def test_nvfp4_codec_and_fwht():
         assert F.cosine_similarity(w.flatten(), wd.flatten(), dim=0) > 0.95
 
 
+def test_nvfp4_w4a4_oracle_and_blocked_scale_layout():
+    torch.manual_seed(9)
+    x, w = torch.randn(200, 384), torch.randn(136, 384) * 0.05
+    p, s, t = ref.nvfp4_quantize(w)
+    for hadamard in (False, True):
+        pw, sw, tw = ref.nvfp4_quantize(ref.fwht16(w) if hadamard else w)
+        y = ref.nvfp4_w4a4_linear(x, pw, sw, tw, hadamard)
+        assert F.cosine_similarity(y.flatten(), (x @ w.t()).flatten(), dim=0) > 0.97
+    blocked = ref.nvfp4_block_scales(s, 384)
+    assert blocked.shape == (2, 8, 512)  # 136 rows -> 2 row blocks; K = 384 -> 2 stages of 256 -> 8 blocks of 64
+    assert torch.equal(ref.nvfp4_unblock_scales(blocked, 136, 384).view(torch.uint8), s.view(torch.uint8))
+    # row 101 (row block 0), k block 5 (k = 80..95): block 5 // 4 = 1, byte (101 % 32) * 16 + (101 // 32) * 4 + 5 % 4
+    assert blocked[0, 1, 5 * 16 + 3 * 4 + 1] == s.view(torch.uint8)[101, 5]
+    assert int(blocked[1, :, :].view(-1).count_nonzero()) <= 8 * 24  # rows 136.. and k blocks 6, 7 stay zero
+
+
 def test_fp8_block_quant_roundtrip():
     torch.manual_seed(8)
     x, w = torch.randn(50, 300), torch.randn(130, 300)

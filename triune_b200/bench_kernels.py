@@ -253,6 +253,19 @@ def case_nvfp4(a):
     report(f"nvfp4_dequant {N}x{K}", ms, nbytes=N * K * 2.5625)
     ms = timeit(lambda: quant_cuda.nvfp4_quantize(w), a.iters, a.warmup)
     report(f"nvfp4_quantize {N}x{K}", ms, nbytes=N * K * 4.5625)
+    # prefill: E2M1 x E2M1 with block scales on the tensor core, against decoding the weights in front of the bf16 GEMM
+    M = a.m
+    xm = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    sfb = quant_cuda.nvfp4_block_scales(s, K)
+    a_p, a_sf = quant_cuda.nvfp4_quantize_act(xm)
+    ms = timeit(lambda: e.nvfp4_gemm(a_p, a_sf, p, sfb, 1.0), a.iters, a.warmup)
+    report(f"nvfp4_gemm (block-scaled tcgen05) {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=0.5625 * (M * K + N * K) + 2.0 * M * N)
+    ms = timeit(lambda: quant_cuda.nvfp4_quantize_act(xm), a.iters, a.warmup)
+    report(f"nvfp4_quantize_act {M}x{K}", ms, nbytes=2.5625 * M * K)
+    ms = timeit(lambda: quant_cuda.nvfp4_w4a4_linear(xm, p, sfb, 1.0, False, torch.bfloat16), a.iters, a.warmup)
+    report(f"nvfp4 W4A4 linear (quantise + GEMM) {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
+    ms = timeit(lambda: quant_cuda.nvfp4_linear(xm, p, s, t, torch.bfloat16), a.iters, a.warmup)
+    report(f"nvfp4 W4A16 linear (decode + bf16 GEMM) {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
 
 
 CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}

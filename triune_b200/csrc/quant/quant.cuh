@@ -23,6 +23,18 @@ void launch_nvfp4_gemv(const __nv_bfloat16* x, const uint8_t* packed, const void
                        const float* tscale, __nv_bfloat16* y, int M, int N, int K, cudaStream_t s);
 void launch_fwht16(const __nv_bfloat16* x, __nv_bfloat16* out, long long n, cudaStream_t s);
 
+// Block-scaled NVFP4 GEMM (nvfp4_gemm.cu). Scales travel in a blocked layout: per 128 rows and 64 elements of K,
+// 512 bytes ordered (row % 32) * 16 + (row / 32) * 4 + (k / 16) % 4; blocks stored [row block][nvfp4_sf_kblocks(K)].
+int nvfp4_sf_kblocks(int K);
+// x bf16 [M, K] (row pitch ld) -> packed E2M1 [M, K / 2] + unsigned E4M3 block scales (blocked layout, buffer pre-zeroed).
+void launch_nvfp4_quantize_act(const __nv_bfloat16* x, long long ld, int M, int K, bool hadamard, uint8_t* packed,
+                               uint8_t* sf_blocked, cudaStream_t s);
+// Row-major E4M3 scales [R, K / 16] -> blocked layout (buffer pre-zeroed).
+void launch_nvfp4_block_scales(const uint8_t* scales, int R, int K, uint8_t* out, cudaStream_t s);
+// C[M, N] bf16 = alpha * (A .* SFA) (B .* SFB)^T on tcgen05 kind::mxf4nvf4 (K % 32 == 0, N % 8 == 0).
+void launch_nvfp4_gemm(const uint8_t* a_packed, const uint8_t* sfa, const uint8_t* b_packed, const uint8_t* sfb,
+                       __nv_bfloat16* C, int M, int N, int K, float alpha, int* status, cudaStream_t s);
+
 // GGML / GGUF block formats (F32, F16, BF16, Q4_0, Q4_1, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K) decoded on the device:
 // to bf16, or straight into NVFP4 (optional 16-point Hadamard rotation) without a bf16 copy of the tensor.
 void launch_ggml_dequant(const uint8_t* raw, int type, long long n, __nv_bfloat16* out, cudaStream_t s);

@@ -53,6 +53,50 @@ std::vector<at::Tensor> nvfp4_quantize(const at::Tensor& w, bool hadamard) {
   return {packed, scales, tscale};
 }
 
+// x bf16 [M, K] -> (packed E2M1 uint8 [M, K/2], block scales uint8 [ceil(M/128), sf_kblocks, 512] in the GEMM's layout)
+std::vector<at::Tensor> nvfp4_quantize_act(const at::Tensor& x, bool hadamard) {
+  need(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16, "nvfp4_quantize_act: bf16 [M,K] CUDA");
+  need(x.size(1) % 32 == 0 && x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+       "nvfp4_quantize_act: K % 32 == 0 and 16-byte aligned rows");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t M = x.size(0), K = x.size(1);
+  auto packed = at::empty({M, K / 2}, x.options().dtype(at::kByte));
+  auto sf = at::zeros({(M + 127) / 128, (int64_t)tb::nvfp4_sf_kblocks((int)K), 512}, x.options().dtype(at::kByte));
+  tb::launch_nvfp4_quantize_act(bf(x), x.stride(0), (int)M, (int)K, hadamard, packed.data_ptr<uint8_t>(), sf.data_ptr<uint8_t>(), cur());
+  return {packed, sf};
+}
+
+// E4M3 scales [R, K/16] (row-major, as the weight quantiser writes them) -> the GEMM's blocked layout
+at::Tensor nvfp4_block_scales(const at::Tensor& scales, int64_t K) {
+  need(scales.is_cuda() && scales.dim() == 2 && scales.is_contiguous() && scales.element_size() == 1 && scales.size(1) == K / 16,
+       "nvfp4_block_scales: contiguous E4M3 [R, K/16] CUDA");
+  c10::cuda::CUDAGuard g(scales.device());
+  const int64_t R = scales.size(0);
+  auto out = at::zeros({(R + 127) / 128, (int64_t)tb::nvfp4_sf_kblocks((int)K), 512}, scales.options().dtype(at::kByte));
+  tb::launch_nvfp4_block_scales((const uint8_t*)scales.data_ptr(), (int)R, (int)K, out.data_ptr<uint8_t>(), cur());
+  return out;
+}
+
+// y [M, N] bf16 = alpha * (a .* sfa) (b .* sfb)^T, both operands packed E2M1 with blocked unsigned-E4M3 scales
+std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha) {
+  need(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() &&
+           a.element_size() == 1 && b.element_size() == 1 && a.size(1) == b.size(1),
+       "nvfp4_gemm: contiguous packed [M, K/2] and [N, K/2]");
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1) * 2;
+  const int64_t kb = tb::nvfp4_sf_kblocks((int)K);
+  need(sfa.is_contiguous() && sfb.is_contiguous() && sfa.numel() == ((M + 127) / 128) * kb * 512 &&
+           sfb.numel() == ((N + 127) / 128) * kb * 512,
+       "nvfp4_gemm: scale tensors must be in the blocked layout of nvfp4_quantize_act / nvfp4_block_scales");
+  need((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0,
+       "nvfp4_gemm: operands must be 16-byte aligned");
+  c10::cuda::CUDAGuard g(a.device());
+  auto out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  auto status = at::zeros({1}, a.options().dtype(at::kInt));
+  tb::launch_nvfp4_gemm(a.data_ptr<uint8_t>(), sfa.data_ptr<uint8_t>(), b.data_ptr<uint8_t>(), sfb.data_ptr<uint8_t>(), bfm(out),
+                        (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), cur());
+  return {out, status};
+}
+
 bool scale_is_bf16(const at::Tensor& scales) {
   need(scales.scalar_type() == at::kBFloat16 || scales.element_size() == 1, "nvfp4: scales must be E4M3 or bf16");
   return scales.scalar_type() == at::kBFloat16;
@@ -116,6 +160,9 @@ void register_quant(pybind11::module& m) {
   m.def("fp8_block_gemm", &fp8_block_gemm, "block-scaled E4M3 GEMM (tcgen05 kind::f8f6f4), bf16 out");
   m.def("nvfp4_quantize", &nvfp4_quantize, "[N,K] -> (packed E2M1, E4M3 block scales, fp32 tensor scale)");
   m.def("nvfp4_dequant", &nvfp4_dequant, "packed NVFP4 -> bf16 [N,K]");
+  m.def("nvfp4_quantize_act", &nvfp4_quantize_act, "bf16 [M,K] -> (packed E2M1, blocked E4M3 scales) for the block-scaled GEMM");
+  m.def("nvfp4_block_scales", &nvfp4_block_scales, "row-major E4M3 scales -> the block-scaled GEMM's layout");
+  m.def("nvfp4_gemm", &nvfp4_gemm, "block-scaled E2M1 x E2M1 GEMM (tcgen05 kind::mxf4nvf4), bf16 out");
   m.def("nvfp4_gemv", &nvfp4_gemv, "y = x @ W^T for M <= 8 straight from packed NVFP4 weights");
   m.def("ggml_dequant", &ggml_dequant, "GGML block formats -> bf16");
   m.def("ggml_to_nvfp4", &ggml_to_nvfp4, "GGML block formats -> NVFP4 (packed, scales, tensor scale) without a bf16 copy");

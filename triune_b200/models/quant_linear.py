@@ -81,6 +81,9 @@ class NVFP4Linear(nn.Module):
         self.register_buffer("tensor_scale", torch.ones((), dtype=torch.float32))
         self.bias = nn.Parameter(torch.zeros(out_features), requires_grad=False) if bias else None
         self._dq = None
+        self.w4a4 = True          # prefer the block-scaled E2M1 x E2M1 tensor-core GEMM where it applies
+        self._sf_blocked = None   # block scales in the GEMM's layout (derived, not saved)
+        self._alpha = 1.0
 
     @classmethod
     def empty_skeleton(cls, in_features, out_features, bias=False, hadamard=False, device=None):
@@ -116,6 +119,7 @@ class NVFP4Linear(nn.Module):
         self.block_scales = s.to(self.block_scales.device)
         self.tensor_scale = t.to(self.tensor_scale.device)
         self._dq = None
+        self._sf_blocked = None
 
     def dequantized(self, dtype=torch.bfloat16) -> torch.Tensor:
         return ref.nvfp4_dequantize(self.packed_weight, self.block_scales, self.tensor_scale, dtype)
@@ -124,11 +128,28 @@ class NVFP4Linear(nn.Module):
         n = self.out_features * self.in_features
         return 8.0 * (self.packed_weight.numel() + self.block_scales.numel() * self.block_scales.element_size()) / n
 
+    def _w4a4_ready(self, x2: torch.Tensor) -> bool:
+        """Block-scaled tensor-core path (activations quantised to E2M1 on the fly, both scale sets applied by the
+        tensor core): CUDA bf16 activations, E4M3 block scales, more rows than the GEMV path serves."""
+        from ..ops import quant_cuda
+
+        return (self.w4a4 and quant_cuda.nvfp4_supported(x2, self.packed_weight) and x2.shape[0] > 8
+                and self.block_scales.dtype == torch.float8_e4m3fn and self.in_features % 32 == 0
+                and self.out_features % 8 == 0)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, self.in_features)
-        if self.hadamard:
-            x2 = ops.fwht16(x2)
-        y = ops.nvfp4_linear(x2, self.packed_weight, self.block_scales, self.tensor_scale, out_dtype=x.dtype)
+        if self._w4a4_ready(x2):
+            from ..ops import quant_cuda
+
+            if self._sf_blocked is None or self._sf_blocked.device != x2.device:
+                self._sf_blocked = quant_cuda.nvfp4_block_scales(self.block_scales, self.in_features)
+                self._alpha = float(self.tensor_scale)  # one host read, at the first call
+            y = quant_cuda.nvfp4_w4a4_linear(x2, self.packed_weight, self._sf_blocked, self._alpha, self.hadamard, x.dtype)
+        else:
+            if self.hadamard:
+                x2 = ops.fwht16(x2)
+            y = ops.nvfp4_linear(x2, self.packed_weight, self.block_scales, self.tensor_scale, out_dtype=x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
         return y.view(*x.shape[:-1], self.out_features)
@@ -177,6 +198,15 @@ def convert_to_fp8(model: nn.Module, protect: Iterable[str] = (), min_features: 
     return _convert(model, FP8Linear.from_linear, protect, min_features)
 
 
-def convert_to_nvfp4(model: nn.Module, hadamard: bool = False, protect: Iterable[str] = (), min_features: int = 16) -> int:
-    """Replace eligible ``nn.Linear`` modules by packed :class:`NVFP4Linear`; returns the number converted."""
-    return _convert(model, lambda l: NVFP4Linear.from_linear(l, hadamard), protect, min_features)
+def convert_to_nvfp4(model: nn.Module, hadamard: bool = False, protect: Iterable[str] = (), min_features: int = 16,
+                     w4a4: bool = True) -> int:
+    """Replace eligible ``nn.Linear`` modules by packed :class:`NVFP4Linear`; returns the number converted. ``w4a4``
+    (default) lets prefill-sized calls quantise their activations too and run on the block-scaled tensor-core GEMM;
+    ``w4a4=False`` keeps activations in bf16 (weights decoded in front of the bf16 GEMM)."""
+
+    def make(l):
+        m = NVFP4Linear.from_linear(l, hadamard)
+        m.w4a4 = bool(w4a4)
+        return m
+
+    return _convert(model, make, protect, min_features)

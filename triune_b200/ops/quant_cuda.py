@@ -62,3 +62,30 @@ def nvfp4_linear(x2, packed, scales, tscale, out_dtype):
     else:
         y = gemm(x2, nvfp4_dequant(packed, scales, tscale))
     return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
+
+
+def nvfp4_block_scales(scales: torch.Tensor, K: int) -> torch.Tensor:
+    """Row-major E4M3 block scales [N, K/16] -> the blocked layout the tensor-core GEMM loads."""
+    _tick()
+    return _ext.ext().nvfp4_block_scales(scales.contiguous().view(torch.uint8), int(K))
+
+
+def nvfp4_quantize_act(x2: torch.Tensor, hadamard: bool = False):
+    """bf16 [M, K] -> (packed E2M1 [M, K/2], blocked unsigned-E4M3 scales); optional folded 16-point Hadamard rotation."""
+    _tick()
+    return tuple(_ext.ext().nvfp4_quantize_act(x2, bool(hadamard)))
+
+
+last_gemm_status = None
+
+
+def nvfp4_w4a4_linear(x2, packed, sf_blocked, alpha: float, hadamard: bool, out_dtype):
+    """y = alpha * dequant(quant(x)) @ dequant(W)^T with both operands E2M1 and both scale sets applied by the tensor
+    core (``tcgen05.mma.kind::mxf4nvf4``); nothing is decoded to bf16."""
+    global last_gemm_status
+    e = _ext.ext()
+    x2 = x2 if (x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0) else x2.contiguous()
+    a_p, a_sf = e.nvfp4_quantize_act(x2, bool(hadamard))
+    y, last_gemm_status = e.nvfp4_gemm(a_p, a_sf, packed, sf_blocked, float(alpha))
+    _tick(2)
+    return y if out_dtype == torch.bfloat16 else y.to(out_dtype)

@@ -565,6 +565,49 @@ def nvfp4_dequantize(packed: torch.Tensor, scales: torch.Tensor, tscale, dtype=t
     return (vals * eff).to(dtype)
 
 
+def nvfp4_quantize_act(x: torch.Tensor, hadamard: bool = False):
+    """Activation side of the W4A4 GEMM: [M,K] -> (packed uint8 [M,K/2], E4M3 scales [M,K/16]) with the block scale
+    amax/6 rounded to E4M3 and no tensor scale (activations are O(1) after a normalisation layer)."""
+    M, K = x.shape
+    xf = (fwht16(x.float()) if hadamard else x.float()).reshape(M, K // 16, 16)
+    sc = (xf.abs().amax(-1) / 6.0).clamp(min=2.0**-9, max=448.0).to(torch.float8_e4m3fn)
+    codes = e2m1_encode(xf / sc.float().unsqueeze(-1)).reshape(M, K)
+    return (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous(), sc.contiguous()
+
+
+def nvfp4_sf_kblocks(K: int) -> int:
+    return -(-K // 256) * 4
+
+
+def nvfp4_block_scales(scales: torch.Tensor, K: int) -> torch.Tensor:
+    """Row-major one-byte scales [R, K/16] -> the tensor core's blocked layout [ceil(R/128), kblocks, 512] (uint8):
+    per 128 rows x 64 elements of K, byte (row % 32) * 16 + (row // 32) * 4 + (k // 16) % 4; missing rows / k are 0."""
+    R, kb16 = scales.shape
+    assert kb16 == K // 16
+    kb = nvfp4_sf_kblocks(K)
+    out = torch.zeros((-(-R // 128), kb, 512), dtype=torch.uint8, device=scales.device)
+    r = torch.arange(R, device=scales.device).unsqueeze(1).expand(R, kb16)
+    b = torch.arange(kb16, device=scales.device).unsqueeze(0).expand(R, kb16)
+    out[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] = scales.view(torch.uint8)
+    return out
+
+
+def nvfp4_unblock_scales(blocked: torch.Tensor, R: int, K: int) -> torch.Tensor:
+    """Inverse of :func:`nvfp4_block_scales`: -> E4M3 [R, K/16]."""
+    kb16 = K // 16
+    r = torch.arange(R, device=blocked.device).unsqueeze(1).expand(R, kb16)
+    b = torch.arange(kb16, device=blocked.device).unsqueeze(0).expand(R, kb16)
+    flat = blocked.reshape(-(-R // 128), nvfp4_sf_kblocks(K), 512)
+    return flat[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4].contiguous().view(torch.float8_e4m3fn)
+
+
+def nvfp4_w4a4_linear(x: torch.Tensor, packed, scales, tscale, hadamard: bool = False) -> torch.Tensor:
+    """fp32 oracle of the W4A4 linear: both operands decoded from their codes and scales, product in fp32."""
+    a_p, a_s = nvfp4_quantize_act(x, hadamard)
+    a = nvfp4_dequantize(a_p, a_s, 1.0, torch.float32)
+    return a @ nvfp4_dequantize(packed, scales, tscale, torch.float32).t()
+
+
 def fp8_block_quantize_weight(w: torch.Tensor, block: int = 128):
     """[N,K] -> (E4M3 [N,K], fp32 scales [ceil(N/128), ceil(K/128)]): one scale per 128x128 block."""
     N, K = w.shape
