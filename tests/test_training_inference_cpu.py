@@ -233,6 +233,136 @@ def test_layer_streaming_matches_resident_training():
     assert out.shape == (2, 16, 256)
 
 
+def test_streamed_layers_get_the_tiered_optimizer_with_resident_parity():
+    """Streamed layers stepped one at a time through ``step_parameters`` (state sets in host memory, one device arena
+    per layer signature) follow the same trajectory as the resident model under one CentroidSteerOptimizer
+    (tests/test_streaming_training_parity.py:75-472 of the reference)."""
+    from triune_b200.optim import CentroidSteerOptimizer
+    from triune_b200.optim.subspace import set_sketch_seed
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming
+
+    a, b = tiny(), tiny()
+    # enough tokens per expert that every expert gradient has full rank: a rank-deficient gradient leaves the trailing
+    # basis vectors to rounding noise, and the two sides would then carry their moments in different bases
+    kw = dict(lr=3e-3, muon_ns_steps=3, update_gap=2, steer_update_gap=2, rank=16)
+    opt_a = CentroidSteerOptimizer(a, grad_clip=0.5, **kw)
+    eng = enable_layer_streaming(b, "cpu", config=StreamingConfig(resident_gpu_layers=0, pin_memory=False, grad_clip=0.5))
+    streamed = {id(p) for st in eng.stores.values() for p in st.params}
+    opt_root = CentroidSteerOptimizer(b, grad_clip=None, only=lambda n, p: id(p) not in streamed, **kw)
+    pool = eng.enable_tiered_optimizer(**kw)
+    assert len(pool.groups) >= 1 and sum(len(g.layers) for g in pool.groups.values()) == len(eng.stores)
+    tiers = {s.tier for g in pool.groups.values() for s in g.opt.arena.segments}
+    assert "muon" in tiers and "adamw" in tiers
+    for step in range(3):
+        x = torch.randint(0, 256, (8, 64), generator=torch.Generator().manual_seed(step))
+        y = torch.randint(0, 256, (8, 64), generator=torch.Generator().manual_seed(100 + step))
+        la = a.forward_loss(x, y, force_depth=2)
+        lb = b.forward_loss(x, y, force_depth=2)
+        la, lb = (la[0] if isinstance(la, tuple) else la), (lb[0] if isinstance(lb, tuple) else lb)
+        assert torch.allclose(la, lb, atol=2e-4), (step, float(la), float(lb))
+        la.backward()
+        lb.backward()
+        # the resident model takes the same step in the same order (root, then layer by layer), so that the
+        # randomised range finder of the CentroidSteer tier draws the same sketches on both sides
+        set_sketch_seed(500 + step)
+        opt_a.arena.fold_autograd_grads()
+        opt_a.compute_clip()
+        layer_ids = [{id(p) for p in l.parameters()} for l in a.layers]
+        in_layers = set().union(*layer_ids)
+        opt_a.step_parameters([p for p in a.parameters() if id(p) not in in_layers])
+        for k, l in enumerate(a.layers):
+            opt_a.step_parameters(list(l.parameters()), is_global_step_end=(k == len(a.layers) - 1))
+        opt_a.zero_grad()
+        # root parameters: autograd grads folded into the root arena, clipped by the engine's global coefficient
+        set_sketch_seed(500 + step)
+        norm = eng.step_streaming_optimizer(_RootStep(opt_root, eng))
+        assert abs(norm - float(opt_a.last_grad_norm)) < 1e-3 * max(1.0, norm)
+    for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.allclose(pa, pb, atol=5e-4, rtol=1e-3), n
+    assert pool.state_bytes() > 0
+    sd = pool.state_dict()
+    pool.load_state_dict(sd)
+
+
+class _RootStep:
+    """Adapter: the engine scales ``p.grad`` of the root parameters by the global clip coefficient and then calls
+    ``step()`` / ``zero_grad()``; the arena optimizer folds those gradients and steps its subset."""
+
+    def __init__(self, opt, eng):
+        self.opt, self.eng = opt, eng
+
+    def step(self):
+        self.opt.set_clip_coefficient(1.0)
+        self.opt.step_parameters([s.param for s in self.opt.arena.segments], is_global_step_end=True)
+
+    def zero_grad(self, set_to_none=True):
+        self.opt.zero_grad()
+
+
+def test_streaming_engine_cleans_up_after_an_exception():
+    """A layer that raises on the host in forward or backward, and an optimizer that raises, leave no layer staged or
+    bound to a device buffer, and the next step works (tests/test_streaming_exception_cleanup.py:13-116)."""
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming
+
+    b = tiny()
+    eng = enable_layer_streaming(b, "cpu", config=StreamingConfig(resident_gpu_layers=0, pin_memory=False))
+    x = torch.randint(0, 256, (2, 16))
+    y = torch.randint(0, 256, (2, 16))
+    victim = b.layers[1]
+    armed = {"fwd": True}
+    orig_ffn = victim.ffn.forward
+
+    def raising(*a_, **k_):
+        if armed["fwd"]:
+            raise RuntimeError("injected forward failure")
+        return orig_ffn(*a_, **k_)
+
+    victim.ffn.forward = raising
+    try:
+        b.forward_loss(x, y, force_depth=2)
+        assert False, "the injected failure did not surface"
+    except RuntimeError as e:
+        assert "injected forward failure" in str(e)
+    assert all(v == 0 for v in eng._staged.values())
+    assert all(st.device_buf is None for st in eng.stores.values())
+    assert all(p.data_ptr() == st.host[off : off + 1].data_ptr() for st in eng.stores.values()
+               for p, (off, n, _) in zip(st.params, st.slices))
+    # the same layer fails during the recomputation of the backward pass
+    armed["fwd"] = False
+    loss = b.forward_loss(x, y, force_depth=2)
+    loss = loss[0] if isinstance(loss, tuple) else loss
+    armed["fwd"] = True
+    try:
+        loss.backward()
+        assert False
+    except RuntimeError as e:
+        assert "injected forward failure" in str(e)
+    assert all(v == 0 for v in eng._staged.values()) and all(st.device_buf is None for st in eng.stores.values())
+    armed["fwd"] = False
+    eng.cleanup()
+
+    class FaultyOptimizer:
+        def step(self):
+            raise RuntimeError("injected optimizer failure")
+
+        def zero_grad(self, set_to_none=True):
+            pass
+
+    loss = b.forward_loss(x, y, force_depth=2)
+    (loss[0] if isinstance(loss, tuple) else loss).backward()
+    try:
+        eng.step_streaming_optimizer(FaultyOptimizer())
+        assert False
+    except RuntimeError as e:
+        assert "injected optimizer failure" in str(e)
+    assert all(st.device_buf is None for st in eng.stores.values())
+    assert all(p.grad is None for st in eng.stores.values() for p in st.params)
+    # the engine is reusable
+    loss = b.forward_loss(x, y, force_depth=2)
+    (loss[0] if isinstance(loss, tuple) else loss).backward()
+    assert eng.step_streaming_optimizer(None, lr=1e-2) > 0
+
+
 GLOO_WORKER = r'''
 import os, sys, json, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])

@@ -151,14 +151,16 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
                  grad_clip: Optional[float] = None, nesterov: bool = True, aspect_safeguard: bool = True,
                  adaptive_subspace_refresh: bool = False, energy_threshold: float = 0.5, min_subspace_gap: int = 5,
                  max_subspace_gap: int = 50, storage_factory=None, shard: Tuple[int, int] = (0, 1),
-                 tensor_core_subspace: bool = True, use_8bit_adam: bool = False):
+                 tensor_core_subspace: bool = True, use_8bit_adam: bool = False, only=None):
         if core_mask_mode not in ("full", "triu"):
             raise ValueError(f"Unknown core_mask_mode={core_mask_mode!r}; expected 'full' or 'triu'")
         self._in_set_lr = False
         self.model = model
         tiers, mat_views, steer_meta = classify_parameters(model, param_roles, use_muon, aspect_safeguard)
         self.tiers, self.steer_meta = tiers, steer_meta
-        named = list(model.named_parameters())
+        # ``only(name, param) -> bool`` restricts the optimizer to a subset (the root modules of a streamed model,
+        # whose layers are updated one at a time elsewhere); tiers are still decided with the whole model in view.
+        named = [(n, p) for n, p in model.named_parameters() if only is None or only(n, p)]
         self.arena = ParamArena(named, tiers, mat_views, storage_factory=storage_factory)
         self.shard = (int(shard[0]), int(shard[1]))  # (rank, world): which matrices / experts this rank updates
         group = _SyncedParamGroup(self, {"params": [s.param for s in self.arena.segments], "lr": lr, "betas": betas,

@@ -99,6 +99,42 @@ class LayerStreamingEngine:
         self._pin = pin
         self.opt_state: Dict[int, Dict[str, torch.Tensor]] = {}
         self.step_count = 0
+        self.layer_optimizer = None  # StreamedLayerOptimizer: tiered updates of the streamed layers
+
+    def enable_tiered_optimizer(self, make_optimizer=None, state_dtype: torch.dtype = torch.float32, **optimizer_kwargs):
+        """Update streamed layers with the tiered optimizer (AdamW / Muon / CentroidSteer through
+        ``step_parameters``, one layer's state on the device at a time) instead of the built-in AdamW."""
+        from .streamed_optimizer import StreamedLayerOptimizer
+
+        if not self._attached:
+            self.attach()
+        self.layer_optimizer = StreamedLayerOptimizer(self, make_optimizer, state_dtype, **optimizer_kwargs)
+        return self.layer_optimizer
+
+    def drop_prefetched(self):
+        """Free device copies that were prefetched but are not in use (called when a layer raises: the prefetch of
+        its neighbour would otherwise stay on the device until that layer next runs)."""
+        for i, st in self.stores.items():
+            if self._staged.get(i, 0) == 0 and st.device_buf is not None:
+                if self.cuda:
+                    self.h2d_stream.synchronize()
+                st.bind_host()
+                st.device_buf = None
+                st.ready = None
+
+    def cleanup(self):
+        """Return every streamed layer to its host storage and drop staged device buffers and in-flight gradient
+        bookkeeping (after an exception in forward, backward or the optimizer pass the engine is reusable)."""
+        if self.cuda:
+            for s_ in (self.h2d_stream, self.d2h_stream):
+                s_.synchronize()
+        for i, st in self.stores.items():
+            st.bind_host()
+            st.device_buf = None
+            st.ready = None
+            self._staged[i] = 0
+            for p in st.params:
+                p.grad = None
 
     # ------------------------------------------------------------------ attach / detach
     def attach(self):
@@ -142,7 +178,11 @@ class LayerStreamingEngine:
             engine.stage(i, prefetch=i + 1)
             try:
                 return orig(x, *args, **kwargs)
-            finally:
+            except BaseException:
+                engine.release(i)
+                engine.drop_prefetched()
+                raise
+            else:
                 engine.release(i)
 
         layer.forward = forward
@@ -257,6 +297,34 @@ class LayerStreamingEngine:
         self.step_count += 1
         t = self.step_count
         b1, b2 = betas
+        try:
+            if self.layer_optimizer is not None:
+                self._step_layers_tiered(coef)
+            else:
+                self._step_layers_adamw(coef, t, lr, b1, b2, eps, weight_decay)
+        except Exception:
+            self.cleanup()
+            raise
+        if self.cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        return float(norm)
+
+    def _step_layers_tiered(self, coef):
+        pool = self.layer_optimizer
+        ids = sorted(i for i, st in self.stores.items() if getattr(st, "_has_grad", False))
+        last_of_group = {id(pool.group_of(i)): i for i in ids}
+        for i in ids:
+            st = self.stores[i]
+            g = st.host_grad.to(self.device, non_blocking=True)
+            self.telemetry["h2d_bytes"] += st.numel * 4
+            pool.step_layer(i, g, coef, is_global_step_end=(last_of_group[id(pool.group_of(i))] == i))
+            if self.cuda:
+                torch.cuda.current_stream(self.device).synchronize()  # host_grad / host are reused right away
+            st.host_grad.zero_()
+            st.grad_sumsq = None
+            st._has_grad = False
+
+    def _step_layers_adamw(self, coef, t, lr, b1, b2, eps, weight_decay):
         for i, st in self.stores.items():
             if not getattr(st, "_has_grad", False):
                 continue
@@ -281,9 +349,6 @@ class LayerStreamingEngine:
             st._has_grad = False
             self.telemetry["h2d_bytes"] += st.numel * 16
             self.telemetry["d2h_bytes"] += st.numel * 14
-        if self.cuda:
-            torch.cuda.current_stream(self.device).synchronize()
-        return float(norm)
 
     def get_telemetry(self) -> Dict[str, int]:
         return dict(self.telemetry)
@@ -301,8 +366,11 @@ class _StreamedLayerFn(torch.autograd.Function):
         try:
             with torch.no_grad():
                 out = fn(x, *args, **kwargs)
-        finally:
+        except BaseException:
             engine.release(i)
+            engine.drop_prefetched()
+            raise
+        engine.release(i)
         return engine._flatten(i, out)
 
     @staticmethod
@@ -321,8 +389,13 @@ class _StreamedLayerFn(torch.autograd.Function):
             pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and o.requires_grad]
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
             engine.collect_grads(i)
-        finally:
+        except BaseException:
             engine.release(i)
+            engine.drop_prefetched()
+            for p in engine.stores[i].params:
+                p.grad = None
+            raise
+        engine.release(i)
         return None, None, None, None, None, xd.grad
 
 
