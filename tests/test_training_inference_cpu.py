@@ -467,6 +467,30 @@ def test_tensor_parallel_dense_model_matches_unsharded_on_gloo():
             assert v < 1e-4, (k, v)
 
 
+def test_sharded_checkpoints_merge_to_the_canonical_single_file_on_gloo(tmp_path):
+    """Two gloo ranks save rank-local shards of a tensor-parallel dense model and of an expert-parallel MoE model;
+    ``python -m triune_b200 checkpoint merge`` assembles the canonical file (reference key layout), which loads
+    strictly into the unsharded model and reproduces its logits; each rank resumes from its own shard."""
+    import json
+    import re
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29751", os.path.join(ROOT, "tests", "mp_shard_ckpt_worker.py"), str(tmp_path)]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    dec = json.JSONDecoder()
+    res = [dec.raw_decode(p.stdout, m.end())[0] for m in re.finditer(r"RESULT (?=\{)", p.stdout)]
+    assert p.returncode == 0 and len(res) == 2, p.stdout[-2000:] + p.stderr[-3000:]
+    r0 = [r for r in res if r["rank"] == 0][0]
+    for key in ("tp_gla_swiglu", "tp_gated_deltanet_gelu"):
+        assert r0[key + "_merged_logits"] < 1e-5 and r0[key + "_step"] == 7, r0
+        for r in res:
+            assert r[key + "_resume"] == 0.0 and r[key + "_resume_step"] == 7, r
+    assert r0["ep_merged_logits"] < 1e-5 and r0["ep_keys_equal"] == 1 and r0["ep_has_per_expert_keys"] == 1, r0
+    assert sorted(f for f in os.listdir(tmp_path / "ep") if f.startswith("shard-")) == [
+        "shard-00000-of-00002.pt", "shard-00001-of-00002.pt"]
+
+
 @pytest.mark.parametrize("kernel_like", [False, True])
 def test_context_parallel_gla_matches_whole_sequence_on_gloo(kernel_like):
     """Three gloo ranks, one sequence segment each: the state hand-off reproduces outputs, final state and all input

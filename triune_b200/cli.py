@@ -162,6 +162,14 @@ def cmd_checkpoint(a) -> int:
                 for p in sorted(d.glob("*.pt"))] if d.is_dir() else []
         _print(rows)
         return 0
+    if a.action == "merge":
+        from .trainer.sharded_checkpoint import merge_shards
+
+        out = a.output if a.output != "exports/model.safetensors" else str(Path(a.dir) / "merged.pt")
+        payload = merge_shards(a.dir, out)
+        _print({"path": out, "tensors": len(payload["model_state"]), "shards": payload["merged_from"]["shards"],
+                "step": payload["step"]})
+        return 0
     return cmd_export(a)
 
 
@@ -568,7 +576,8 @@ def build_parser() -> argparse.ArgumentParser:
     for name in ("checkpoint", "export"):
         s = sub.add_parser(name, help="list checkpoints / export a model" if name == "checkpoint" else "export a model")
         if name == "checkpoint":
-            s.add_argument("action", choices=["list", "export"])
+            s.add_argument("action", choices=["list", "export", "merge"],
+                           help="merge: assemble the rank-local shard files of --dir into one canonical checkpoint (--output)")
             s.add_argument("--dir", default="checkpoints_full")
         s.add_argument("--model", default="checkpoints_full/latest.pt")
         s.add_argument("--output", default="exports/model.safetensors")

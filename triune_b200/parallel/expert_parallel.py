@@ -267,6 +267,9 @@ class EPMoE_FFN(nn.Module):
         lo, hi = ep.rank * ep.experts_per_rank, (ep.rank + 1) * ep.experts_per_rank
         self.router, self.shared = moe.router, moe.shared
         self.register_buffer("expert_bias", moe.expert_bias.detach().clone())
+        for name in ("expert_load_ratio", "last_centroids", "_global_step"):  # carried for checkpoints of the full layer
+            if hasattr(moe, name):
+                self.register_buffer(name, getattr(moe, name).detach().clone())
         for name in ("w1", "b1", "w2", "b2"):
             setattr(self, name, nn.Parameter(getattr(moe, name).detach()[lo:hi].clone()))
         self._pending_bias_update = None
@@ -283,6 +286,27 @@ class EPMoE_FFN(nn.Module):
         if self.shared is not None:
             out = out + self.shared_scale * self.shared(x2)
         return out.reshape(B, T, D)
+
+    # ------------------------------------------------------------------ rank-local checkpoints
+    def checkpoint_pieces(self, prefix: str):
+        """This rank's experts under the unsharded layer's per-expert keys (``experts.{e}.{0,2}.{weight,bias}``), as
+        views of the live parameters (``trainer/sharded_checkpoint.py``)."""
+        lo = self.ep.rank * self.ep.experts_per_rank
+        for e in range(self.ep.experts_per_rank):
+            yield (f"{prefix}experts.{lo + e}.0.weight", None, 0, 0, 0, self.w1[e])
+            yield (f"{prefix}experts.{lo + e}.0.bias", None, 0, 0, 0, self.b1[e])
+            yield (f"{prefix}experts.{lo + e}.2.weight", None, 0, 0, 0, self.w2[e])
+            yield (f"{prefix}experts.{lo + e}.2.bias", None, 0, 0, 0, self.b2[e])
+
+    def checkpoint_replicated(self, prefix: str):
+        out = {f"{prefix}{n}": getattr(self, n) for n in ("expert_bias", "expert_load_ratio", "last_centroids", "_global_step")
+               if hasattr(self, n)}
+        for k, v in self.router.state_dict().items():
+            out[f"{prefix}router.{k}"] = v
+        if self.shared is not None:
+            for k, v in self.shared.state_dict().items():
+                out[f"{prefix}shared.{k}"] = v
+        return out
 
     def step_bias(self) -> None:  # selection-bias updates need global counts; kept fixed under expert parallelism
         self._pending_bias_update = None

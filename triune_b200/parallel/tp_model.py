@@ -84,6 +84,39 @@ class TPBlock(nn.Module):
             self.down_bias = _own(mlp[2].bias.detach(), tp)  # replicated: added once, on the reduced rows
         self.input_norm, self.post_attn_norm = block.input_norm, block.post_attn_norm
 
+    # ------------------------------------------------------------------ rank-local checkpoints
+    def checkpoint_pieces(self, prefix: str):
+        """This rank's slices under the unsharded model's state-dict keys, as views of the live parameters:
+        ``(key, dim, start, stop, full, tensor)`` (``trainer/sharded_checkpoint.py``)."""
+        w, r = self.tp.world, self.tp.rank
+        Hl, D = self.heads_local, self.head_dim
+        H = Hl * w
+        hd = Hl * D
+        for j, name in enumerate(("q_proj", "k_proj", "v_proj", "g_proj")):
+            yield (f"{prefix}attn.{name}.weight", 0, r * hd, (r + 1) * hd, H * D, self.qkvg_weight[j * hd : (j + 1) * hd])
+        if self.has_beta:
+            yield (f"{prefix}attn.beta_proj.weight", 0, r * Hl, (r + 1) * Hl, H, self.qkvg_weight[4 * hd : 4 * hd + Hl])
+        yield (f"{prefix}attn.out_proj.weight", 1, r * hd, (r + 1) * hd, H * D, self.out_weight)
+        hl = self.hidden_local
+        s0, s1, hid = r * hl, (r + 1) * hl, hl * w
+        if self.swiglu:
+            yield (f"{prefix}mlp.gate_proj.weight", 0, s0, s1, hid, self.up_weight[:hl])
+            yield (f"{prefix}mlp.up_proj.weight", 0, s0, s1, hid, self.up_weight[hl:])
+            yield (f"{prefix}mlp.down_proj.weight", 1, s0, s1, hid, self.down_weight)
+        else:
+            yield (f"{prefix}mlp.0.weight", 0, s0, s1, hid, self.up_weight)
+            yield (f"{prefix}mlp.0.bias", 0, s0, s1, hid, self.up_bias)
+            yield (f"{prefix}mlp.2.weight", 1, s0, s1, hid, self.down_weight)
+
+    def checkpoint_replicated(self, prefix: str):
+        out = {}
+        for name in ("input_norm", "post_attn_norm"):
+            for k, v in getattr(self, name).state_dict().items():
+                out[f"{prefix}{name}.{k}"] = v
+        if not self.swiglu:
+            out[f"{prefix}mlp.2.bias"] = self.down_bias
+        return out
+
     def _mix(self, proj: torch.Tensor, B: int, T: int) -> torch.Tensor:
         """Linear-attention scan over whole sequences for this rank's heads. proj: [B*T, 4*Hl*D (+Hl)(+pad)]."""
         Hl, D = self.heads_local, self.head_dim
