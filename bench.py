@@ -348,6 +348,20 @@ def run_reference(args):
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": f"run failed: {type(e).__name__}: {e}"[:300]}))
         return
+    # The same step through the reference's own Trainer / TrainingEngine.step_once in cortex mode (its data prefetcher,
+    # its sub-batch slicing, its loss bookkeeping). The faster of the two loops is the reference's number.
+    engine_ms, engine_note = None, None
+    if args.ref_loop in ("engine", "both"):
+        try:
+            engine_ms = _reference_engine_loop(args, train_model, opt, pool, dev, rank, world)
+        except Exception as e:
+            engine_note = f"{type(e).__name__}: {e}"[:200]
+    loops = {"manual": ms, "engine": engine_ms}
+    ref_loop = "manual"
+    if engine_ms is not None and (args.ref_loop == "engine" or engine_ms < ms):
+        ref_loop = "engine"
+        ms = engine_ms
+        e2e_ms = min(e2e_ms, engine_ms) if args.ref_loop == "both" else engine_ms  # the engine loop is end to end by construction
     prefill = None
     if not args.no_prefill:
         try:  # the reference's own forward: recurrent cache, last-token logits, bf16 autocast as its scripts use
@@ -384,12 +398,45 @@ def run_reference(args):
             "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "config": {"model": f"reference TriuneTransformer ({nparams} params; 8L d384 6x64 heads E=8 top-2 hidden 1536)",
                        "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"dp{world} (DDP/NCCL)",
-                       "has_fla": bool(getattr(ratt, "HAS_FLA", False))},
+                       "has_fla": bool(getattr(ratt, "HAS_FLA", False)), "lr": "constant 3e-4", "ref_loop": ref_loop,
+                       "ref_loop_ms": loops, "ref_engine_note": engine_note},
             "clocks": clocks, "e2e": {"value": tps / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms,
                                       "h2d_bytes_per_step": BATCH * SEQ * 16, "d2h_bytes_per_step": 4},
             "prefill": prefill, "final_loss": lv, "impl": "reference"}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _reference_engine_loop(args, train_model, opt, pool, dev, rank, world):
+    """ms per step of ``TrainingEngine.step_once`` (the reference's public training step) over the same batches."""
+    import torch.distributed as dist
+    from triune.trainer.trainer import Trainer as RefTrainer
+
+    class _Tok:
+        def get_vocab_size(self):
+            return VOCAB
+
+        def token_to_id(self, t):
+            return {"[PAD]": 0, "[SEP]": 1}.get(t)
+
+    cfg = {"vocab_size": VOCAB, "grad_accum_steps": 1, "target_depth_dist": [0.2, 0.3, 0.5], "exploration": "none",
+           "exploration_steps": 0, "eval_batches": 1, "cuda_graph": False, "lr": 3e-4, "min_lr": 3e-4, "warmup_steps": 0,
+           "total_steps": 100000, "depth_mode": "cortex", "grad_clip": 1.0, "balance_coef": 0.3}
+    tr = RefTrainer(model=train_model, optimizer=opt, train_loader=list(pool), eval_loader=list(pool[:1]), tokenizer=_Tok(),
+                    config=cfg, device=dev)
+    for _ in range(args.warmup):
+        tr.engine.step_once(advance_step=True)
+    barrier_sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        tr.engine.step_once(advance_step=True)
+    e1.record()
+    barrier_sync()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 def main():
@@ -401,6 +448,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly (no CUDA-graph replay)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (T = 16K) measurement after the training loops")
     ap.add_argument("--dp-mode", default=os.environ.get("TRIUNE_DP_MODE", "fused"), choices=["nccl", "fused"])
+    ap.add_argument("--ref-loop", default="both", choices=["manual", "engine", "both"],
+                    help="reference arm: hand-written full-batch step, the reference's TrainingEngine.step_once, or both "
+                         "(the faster one is reported)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if not torch.cuda.is_available():

@@ -1,7 +1,15 @@
 #!/usr/bin/env python
-"""Serving benchmark of the 90.8M-class MoE-GLA model (one GPU): long-context prefill and greedy decode.
+"""Serving benchmark of the 90.8M-class MoE-GLA model: long-context prefill and greedy decode, on one GPU or on all GPUs
+of a node.
 
     python bench_serving.py [--impl ours|reference] [--batch 4] [--seq 16384] [--new-tokens 256] [--iters 5]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench_serving.py --layout replicas
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench_serving.py --layout ep
+
+Under a multi-process launch every rank serves its own ``batch x seq`` prompt batch. ``--layout replicas``: one full
+model per GPU, no communication. ``--layout ep``: the routed experts are sharded over all ranks (fused NVLink dispatch /
+combine kernels), everything else replicated. Times are device-timed per rank; the reported value is the whole-node
+aggregate, world x tokens / max-over-ranks time. Decode is measured on rank 0 of a one-GPU run only.
 
 Prefill: one forward over ``batch x seq`` uniform-random token ids into the recurrent cache, logits of the last
 position only; timed with CUDA events after warm-up iterations, L2 irrelevant (inputs and activations are far larger
@@ -50,11 +58,23 @@ def run_ours(a):
     from triune_b200.models.speculative import SelfSpeculativeGenerator
     from triune_b200.utils import place_model
 
-    dev = torch.device("cuda", 0)
-    ids = torch.randint(0, VOCAB, (a.batch, a.seq), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
+    rank, world, local = _dist_env()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    ep = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    ids = torch.randint(0, VOCAB, (a.batch, a.seq), device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
     for variant in a.variants.split(","):
         torch.manual_seed(0)
-        model = place_model(TriuneTransformer.from_config(get_model_config("bench-90m")), dev, torch.bfloat16).eval()
+        model = place_model(TriuneTransformer.from_config(get_model_config(a.model)), dev, torch.bfloat16).eval()
+        if world > 1 and a.layout == "ep":
+            from triune_b200.parallel.expert_parallel import EPContext, shard_experts
+
+            ep = EPContext(model.num_experts, device=dev, mode="fused")
+            shard_experts(model, ep)
         converted = 0
         if variant == "fp8":
             converted = convert_to_fp8(model)
@@ -68,10 +88,13 @@ def run_ours(a):
         ops.reset_launch_count()
         prefill()
         launches = ops.launch_count()
-        ms = timed(prefill, a.iters)
-        emit(metric="prefill tok/s", impl="triune_b200", variant=variant, value=a.batch * a.seq / ms * 1e3, unit="tok/s", ms=ms,
-             batch=a.batch, seq_len=a.seq, converted_linears=converted, gpu_launches=launches, dtype="bf16 activations")
-        if variant == "bf16" and a.new_tokens > 0:
+        ms = _max_over_ranks(timed(prefill, a.iters), dev, world)
+        status = int(ep.check()) if ep is not None else 0
+        if rank == 0:
+            emit(metric="prefill tok/s", impl="triune_b200", variant=variant, value=world * a.batch * a.seq / ms * 1e3, unit="tok/s",
+                 ms=ms, batch=a.batch, seq_len=a.seq, n_gpus=world, layout=(a.layout if world > 1 else "one GPU"), model=a.model,
+                 converted_linears=converted, gpu_launches=launches, dtype="bf16 activations", wait_status=status)
+        if variant == "bf16" and a.new_tokens > 0 and world == 1:
             from triune_b200.inference import GraphedGreedyDecoder
 
             prompt = ids[:1, :128]
@@ -92,6 +115,20 @@ def run_ours(a):
         torch.cuda.empty_cache()
 
 
+def _dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+
+
+def _max_over_ranks(ms: float, dev, world: int) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def run_reference(a):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "triune")):
@@ -109,7 +146,13 @@ def run_reference(a):
     except Exception as e:
         emit(impl="reference", unavailable=f"import failed: {type(e).__name__}: {e}"[:300])
         return
-    dev = torch.device("cuda", 0)
+    rank, world, local = _dist_env()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:  # independent replicas of the reference, one per GPU (it has no expert-parallel serving path)
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(0)
     model = RefModel(vocab_size=VOCAB, hidden_dim=384, num_layers=8, num_heads=6, head_dim=64, num_experts=8, router_prefix_layers=1,
                      reflex_exit_layer=2, limbic_exit_layer=5).to(device=dev, dtype=torch.bfloat16).eval()
@@ -125,10 +168,11 @@ def run_reference(a):
             return model(ids, force_depth=2, cache=cache, last_token_only=True)
 
     try:
-        ms = timed(prefill, a.iters)
-        emit(metric="prefill tok/s", impl="reference", variant="bf16", value=a.batch * a.seq / ms * 1e3, unit="tok/s", ms=ms,
-             batch=a.batch, seq_len=a.seq)
-        if a.new_tokens > 0:
+        ms = _max_over_ranks(timed(prefill, a.iters), dev, world)
+        if rank == 0:
+            emit(metric="prefill tok/s", impl="reference", variant="bf16", value=world * a.batch * a.seq / ms * 1e3, unit="tok/s",
+                 ms=ms, batch=a.batch, seq_len=a.seq, n_gpus=world, layout="replicas" if world > 1 else "one GPU")
+        if a.new_tokens > 0 and world == 1:
             prompt = ids[:1, :128]
 
             @torch.no_grad()
@@ -160,6 +204,8 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--k-draft", type=int, default=3)
     ap.add_argument("--variants", default="bf16,fp8,nvfp4")
+    ap.add_argument("--layout", default="replicas", choices=["replicas", "ep"], help="multi-GPU layout (under torchrun)")
+    ap.add_argument("--model", default="bench-90m", help="model preset of the native arm")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         emit(impl=a.impl, unavailable="no CUDA device")

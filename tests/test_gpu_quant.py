@@ -89,15 +89,16 @@ def test_nvfp4_activation_quantiser_matches_oracle(hadamard):
     assert torch.equal(quant_cuda.nvfp4_block_scales(w_s, 384), ref.nvfp4_block_scales(w_s, 384))
 
 
+@pytest.mark.parametrize("tile_n", [128, 256])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 256), (256, 384, 512), (200, 136, 384), (1000, 1536, 2048), (4096, 512, 1056)])
-def test_nvfp4_block_scaled_gemm_matches_decoded_product(M, N, K):
+def test_nvfp4_block_scaled_gemm_matches_decoded_product(M, N, K, tile_n):
     """E2M1 x E2M1 with both scale sets applied by the tensor core == the fp32 product of the decoded operands."""
     torch.manual_seed(6)
     x = torch.randn(M, K, device="cuda").bfloat16()
     w = torch.randn(N, K, device="cuda") * 0.05
     wp, ws, wt = quant_cuda.nvfp4_quantize(w)
     a_p, a_sf = quant_cuda.nvfp4_quantize_act(x, False)
-    y, status = quant_cuda._ext.ext().nvfp4_gemm(a_p, a_sf, wp, quant_cuda.nvfp4_block_scales(ws, K), float(wt))
+    y, status = quant_cuda._ext.ext().nvfp4_gemm(a_p, a_sf, wp, quant_cuda.nvfp4_block_scales(ws, K), float(wt), tile_n)
     assert int(status.item()) == 0
     a = ref.nvfp4_dequantize(a_p, ref.nvfp4_unblock_scales(a_sf, M, K), 1.0, torch.float32)
     want = a @ ref.nvfp4_dequantize(wp, ws, wt, torch.float32).t()
@@ -128,6 +129,60 @@ def test_nvfp4_module_takes_the_block_scaled_path_for_prefill():
         with torch.no_grad():
             y16 = m(x).float()
         assert torch.nn.functional.cosine_similarity(y16.flatten(), want.flatten(), dim=0) > 0.98
+
+
+def test_mxfp8_quantiser_matches_oracle():
+    torch.manual_seed(8)
+    x = (torch.randn(200, 384, device="cuda") * torch.logspace(-3, 2, 384, device="cuda")).bfloat16()
+    x[5] = 0
+    q, sf = quant_cuda.mxfp8_quantize(x)
+    q_ref, e_ref = ref.mxfp8_quantize(x)
+    e = ref.mxfp8_unblock_scales(sf, 200, 384)
+    assert torch.equal(e, e_ref)  # exponents are exact integer arithmetic
+    assert torch.equal(ref.mxfp8_block_scales(e_ref, 384), sf)
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    deq = ref.mxfp8_dequantize(q, e)
+    assert (deq - x.float()).abs().max() <= 0.0625 * x.float().abs().max()  # half an E4M3 ulp (3 mantissa bits)
+    assert torch.nn.functional.cosine_similarity(deq.flatten(), x.float().flatten(), dim=0) > 0.999
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (200, 136, 416), (1000, 1536, 2048), (4096, 512, 1056)])
+def test_mxfp8_block_scaled_gemm_matches_decoded_product(M, N, K, tile_n):
+    """E4M3 x E4M3 with 1x32 power-of-two scales applied by the tensor core == the fp32 product of the decoded operands."""
+    torch.manual_seed(9)
+    x = (torch.randn(M, K, device="cuda") * torch.logspace(-1, 1, K, device="cuda")).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    xq, x_sf = quant_cuda.mxfp8_quantize(x)
+    wq, w_sf = quant_cuda.mxfp8_quantize(w)
+    y = quant_cuda.mxfp8_gemm(xq, x_sf, wq, w_sf, 1.0, tile_n)
+    assert int(quant_cuda.last_gemm_status.item()) == 0
+    a = ref.mxfp8_dequantize(xq, ref.mxfp8_unblock_scales(x_sf, M, K))
+    b = ref.mxfp8_dequantize(wq, ref.mxfp8_unblock_scales(w_sf, N, K))
+    want = a @ b.t()
+    err = (y.float() - want).abs().max() / want.abs().max()
+    assert err < 1e-2, err  # bf16 output rounding only
+    full = x.float() @ w.float().t()
+    assert torch.nn.functional.cosine_similarity(y.float().flatten(), full.flatten(), dim=0) > 0.998
+
+
+def test_fp8_module_takes_the_block_scaled_path():
+    from triune_b200.models.quant_linear import FP8Linear
+
+    torch.manual_seed(10)
+    lin = torch.nn.Linear(512, 384, bias=True).cuda().bfloat16()
+    x = torch.randn(3, 50, 512, device="cuda").bfloat16()
+    want = lin(x).float()
+    m = FP8Linear.from_linear(lin).eval()
+    with torch.no_grad():
+        y_mx = m(x).float()
+        m.mx = False
+        y_blk = m(x).float()
+    oracle = ref.mxfp8_linear(x.reshape(-1, 512), lin.weight).reshape(3, 50, 384) + lin.bias.float()
+    assert (y_mx - oracle).abs().max() <= 2e-2 * oracle.abs().max()
+    cos = torch.nn.functional.cosine_similarity
+    assert cos(y_mx.flatten(), want.flatten(), dim=0) > 0.998
+    assert cos(y_mx.flatten(), want.flatten(), dim=0) >= cos(y_blk.flatten(), want.flatten(), dim=0) - 1e-3  # finer scales
 
 
 def test_fwht16_kernel():

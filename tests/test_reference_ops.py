@@ -162,6 +162,26 @@ def test_nvfp4_w4a4_oracle_and_blocked_scale_layout():
     assert int(blocked[1, :, :].view(-1).count_nonzero()) <= 8 * 24  # rows 136.. and k blocks 6, 7 stay zero
 
 
+def test_mxfp8_codec_and_oracle():
+    torch.manual_seed(10)
+    x = torch.randn(70, 96) * torch.logspace(-3, 3, 96)
+    x[3] = 0
+    q, e = ref.mxfp8_quantize(x)
+    assert q.dtype == torch.float8_e4m3fn and e.shape == (70, 3) and e.dtype == torch.uint8
+    assert float(q.float().abs().max()) <= 448.0
+    # the scale is the SMALLEST power of two that fits: the block maximum lands in (224, 448]
+    top = q.float().abs().reshape(70, 3, 32).amax(-1)
+    assert bool(((top > 224 - 16) | (top == 0)).all())
+    deq = ref.mxfp8_dequantize(q, e)
+    assert (deq - x).abs().max() <= 0.0625 * x.abs().max()
+    assert torch.equal(deq[3], torch.zeros(96))
+    blocked = ref.mxfp8_block_scales(e, 96)
+    assert blocked.shape == (1, 1, 512) and torch.equal(ref.mxfp8_unblock_scales(blocked, 70, 96), e)
+    w = torch.randn(40, 96) * 0.05
+    y = ref.mxfp8_linear(x, w)
+    assert F.cosine_similarity(y.flatten(), (x @ w.t()).flatten(), dim=0) > 0.998
+
+
 def test_fp8_block_quant_roundtrip():
     torch.manual_seed(8)
     x, w = torch.randn(50, 300), torch.randn(130, 300)

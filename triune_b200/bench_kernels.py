@@ -237,6 +237,21 @@ def case_fp8(a):
     report(f"fp8_block_gemm {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=1.0 * (M * K + N * K) + 2.0 * M * N)
     ms = timeit(lambda: quant_cuda.fp8_quantize_act(x), a.iters, a.warmup)
     report(f"fp8_quantize_act {M}x{K}", ms, nbytes=3.0 * M * K)
+    # MXFP8: 1x32 power-of-two scales applied by the tensor core (no promotion out of TMEM per K block)
+    w16 = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    wq8, wsf = quant_cuda.mxfp8_quantize(w16)
+    xq8, xsf = quant_cuda.mxfp8_quantize(x)
+    for tile in (128, 256):
+        ms = timeit(lambda: quant_cuda.mxfp8_gemm(xq8, xsf, wq8, wsf, 1.0, tile), a.iters, a.warmup)
+        report(f"mxfp8_gemm (block-scaled tcgen05, 128x{tile} tiles) {M}x{N}x{K}", ms, flops=2.0 * M * N * K,
+               nbytes=1.03 * (M * K + N * K) + 2.0 * M * N)
+    ms = timeit(lambda: quant_cuda.mxfp8_quantize(x), a.iters, a.warmup)
+    report(f"mxfp8_quantize {M}x{K}", ms, nbytes=3.03 * M * K)
+    ms = timeit(lambda: quant_cuda.mxfp8_linear(x, wq8, wsf, torch.bfloat16), a.iters, a.warmup)
+    report(f"mxfp8 linear (quantise + GEMM) {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
+    from .ops import gemm
+    ms = timeit(lambda: gemm(x, w16), a.iters, a.warmup)
+    report(f"bf16 tcgen05 GEMM {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
 
 
 def case_nvfp4(a):
@@ -258,8 +273,10 @@ def case_nvfp4(a):
     xm = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     sfb = quant_cuda.nvfp4_block_scales(s, K)
     a_p, a_sf = quant_cuda.nvfp4_quantize_act(xm)
-    ms = timeit(lambda: e.nvfp4_gemm(a_p, a_sf, p, sfb, 1.0), a.iters, a.warmup)
-    report(f"nvfp4_gemm (block-scaled tcgen05) {M}x{N}x{K}", ms, flops=2.0 * M * N * K, nbytes=0.5625 * (M * K + N * K) + 2.0 * M * N)
+    for tile in (128, 256):
+        ms = timeit(lambda: e.nvfp4_gemm(a_p, a_sf, p, sfb, 1.0, tile), a.iters, a.warmup)
+        report(f"nvfp4_gemm (block-scaled tcgen05, 128x{tile} tiles) {M}x{N}x{K}", ms, flops=2.0 * M * N * K,
+               nbytes=0.5625 * (M * K + N * K) + 2.0 * M * N)
     ms = timeit(lambda: quant_cuda.nvfp4_quantize_act(xm), a.iters, a.warmup)
     report(f"nvfp4_quantize_act {M}x{K}", ms, nbytes=2.5625 * M * K)
     ms = timeit(lambda: quant_cuda.nvfp4_w4a4_linear(xm, p, sfb, 1.0, False, torch.bfloat16), a.iters, a.warmup)

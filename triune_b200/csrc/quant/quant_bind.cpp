@@ -78,7 +78,8 @@ at::Tensor nvfp4_block_scales(const at::Tensor& scales, int64_t K) {
 }
 
 // y [M, N] bf16 = alpha * (a .* sfa) (b .* sfb)^T, both operands packed E2M1 with blocked unsigned-E4M3 scales
-std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha) {
+std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha,
+                                   int64_t tile_n) {
   need(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() &&
            a.element_size() == 1 && b.element_size() == 1 && a.size(1) == b.size(1),
        "nvfp4_gemm: contiguous packed [M, K/2] and [N, K/2]");
@@ -93,7 +94,41 @@ std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, c
   auto out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
   auto status = at::zeros({1}, a.options().dtype(at::kInt));
   tb::launch_nvfp4_gemm(a.data_ptr<uint8_t>(), sfa.data_ptr<uint8_t>(), b.data_ptr<uint8_t>(), sfb.data_ptr<uint8_t>(), bfm(out),
-                        (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), cur());
+                        (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), (int)tile_n, cur());
+  return {out, status};
+}
+
+// bf16 [R, K] -> (E4M3 [R, K], blocked power-of-two scales per 32 elements)
+std::vector<at::Tensor> mxfp8_quantize(const at::Tensor& x) {
+  need(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16, "mxfp8_quantize: bf16 [R,K] CUDA");
+  need(x.size(1) % 32 == 0 && x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+       "mxfp8_quantize: K % 32 == 0 and 16-byte aligned rows");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t R = x.size(0), K = x.size(1);
+  auto q = at::empty({R, K}, x.options().dtype(at::kFloat8_e4m3fn));
+  auto sf = at::zeros({(R + 127) / 128, (int64_t)tb::mxfp8_sf_kblocks((int)K), 512}, x.options().dtype(at::kByte));
+  tb::launch_mxfp8_quantize(bf(x), x.stride(0), (int)R, (int)K, (uint8_t*)q.data_ptr(), sf.data_ptr<uint8_t>(), cur());
+  return {q, sf};
+}
+
+// y [M, N] bf16 = alpha * (a .* sfa) (b .* sfb)^T, E4M3 operands with blocked power-of-two scales per 32 elements
+std::vector<at::Tensor> mxfp8_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha,
+                                   int64_t tile_n) {
+  need(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() &&
+           a.element_size() == 1 && b.element_size() == 1 && a.size(1) == b.size(1),
+       "mxfp8_gemm: contiguous E4M3 [M, K] and [N, K]");
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+  const int64_t kb = tb::mxfp8_sf_kblocks((int)K);
+  need(sfa.is_contiguous() && sfb.is_contiguous() && sfa.numel() == ((M + 127) / 128) * kb * 512 &&
+           sfb.numel() == ((N + 127) / 128) * kb * 512,
+       "mxfp8_gemm: scale tensors must be in the blocked layout of mxfp8_quantize");
+  need((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0,
+       "mxfp8_gemm: operands must be 16-byte aligned");
+  c10::cuda::CUDAGuard g(a.device());
+  auto out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  auto status = at::zeros({1}, a.options().dtype(at::kInt));
+  tb::launch_mxfp8_gemm((const uint8_t*)a.data_ptr(), sfa.data_ptr<uint8_t>(), (const uint8_t*)b.data_ptr(), sfb.data_ptr<uint8_t>(),
+                        bfm(out), (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), (int)tile_n, cur());
   return {out, status};
 }
 
@@ -163,6 +198,8 @@ void register_quant(pybind11::module& m) {
   m.def("nvfp4_quantize_act", &nvfp4_quantize_act, "bf16 [M,K] -> (packed E2M1, blocked E4M3 scales) for the block-scaled GEMM");
   m.def("nvfp4_block_scales", &nvfp4_block_scales, "row-major E4M3 scales -> the block-scaled GEMM's layout");
   m.def("nvfp4_gemm", &nvfp4_gemm, "block-scaled E2M1 x E2M1 GEMM (tcgen05 kind::mxf4nvf4), bf16 out");
+  m.def("mxfp8_quantize", &mxfp8_quantize, "bf16 [R,K] -> (E4M3, blocked power-of-two scales per 32 elements)");
+  m.def("mxfp8_gemm", &mxfp8_gemm, "block-scaled E4M3 x E4M3 GEMM (tcgen05 kind::mxf8f6f4.block_scale), bf16 out");
   m.def("nvfp4_gemv", &nvfp4_gemv, "y = x @ W^T for M <= 8 straight from packed NVFP4 weights");
   m.def("ggml_dequant", &ggml_dequant, "GGML block formats -> bf16");
   m.def("ggml_to_nvfp4", &ggml_to_nvfp4, "GGML block formats -> NVFP4 (packed, scales, tensor scale) without a bf16 copy");

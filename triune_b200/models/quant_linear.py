@@ -36,6 +36,17 @@ class FP8Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
         self._q = None  # (version, wq, ws)
+        self._mx = None  # (version, E4M3 weight, blocked power-of-two scales per 1x32) for the block-scaled tensor-core GEMM
+        self.mx = True   # inference on CUDA: MXFP8 (scales applied by the tensor core); False: fp32 128-block scales
+
+    def quantized_mx(self):
+        from ..ops import quant_cuda
+
+        v = self.weight._version
+        if self._mx is None or self._mx[0] != v or self._mx[1].device != self.weight.device:
+            wq, sf = quant_cuda.mxfp8_quantize(self.weight.detach().to(torch.bfloat16))
+            self._mx = (v, wq, sf)
+        return self._mx[1], self._mx[2]
 
     @classmethod
     def from_linear(cls, lin: nn.Linear, block: int = 128) -> "FP8Linear":
@@ -60,9 +71,15 @@ class FP8Linear(nn.Module):
                     [: self.out_features, : self.in_features]).to(self.weight.dtype)
             w = self.weight + (w_dq - self.weight).detach()
             return F.linear(x, w, self.bias)
-        wq, ws = self.quantized()
         x2 = x.reshape(-1, self.in_features)
-        y = ops.fp8_linear(x2, wq, ws, self.block, out_dtype=x.dtype)
+        from ..ops import quant_cuda
+
+        if self.mx and quant_cuda.mxfp8_supported(x2, self.in_features, self.out_features) and self.weight.is_cuda:
+            wq, sf = self.quantized_mx()
+            y = quant_cuda.mxfp8_linear(x2, wq, sf, x.dtype)
+        else:
+            wq, ws = self.quantized()
+            y = ops.fp8_linear(x2, wq, ws, self.block, out_dtype=x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
         return y.view(*x.shape[:-1], self.out_features)

@@ -86,6 +86,32 @@ def nvfp4_w4a4_linear(x2, packed, sf_blocked, alpha: float, hadamard: bool, out_
     e = _ext.ext()
     x2 = x2 if (x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0) else x2.contiguous()
     a_p, a_sf = e.nvfp4_quantize_act(x2, bool(hadamard))
-    y, last_gemm_status = e.nvfp4_gemm(a_p, a_sf, packed, sf_blocked, float(alpha))
+    y, last_gemm_status = e.nvfp4_gemm(a_p, a_sf, packed, sf_blocked, float(alpha), 0)
     _tick(2)
+    return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
+
+
+def mxfp8_supported(x2, K: int, N: int) -> bool:
+    return _ext.use_kernels(x2) and x2.dtype == torch.bfloat16 and K % 32 == 0 and N % 8 == 0
+
+
+def mxfp8_quantize(x2: torch.Tensor):
+    """bf16 [R, K] -> (E4M3 [R, K], blocked power-of-two scales per 32 elements) for the block-scaled FP8 GEMM."""
+    _tick()
+    x2 = x2 if (x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0) else x2.contiguous()
+    return tuple(_ext.ext().mxfp8_quantize(x2))
+
+
+def mxfp8_gemm(a, sfa, b, sfb, alpha: float = 1.0, tile_n: int = 0):
+    global last_gemm_status
+    _tick()
+    y, last_gemm_status = _ext.ext().mxfp8_gemm(a, sfa, b, sfb, float(alpha), int(tile_n))
+    return y
+
+
+def mxfp8_linear(x2, wq, w_sf, out_dtype):
+    """y = dequant(quant(x)) @ dequant(W)^T, both E4M3 with 1x32 power-of-two scales applied by the tensor core
+    (``tcgen05.mma.kind::mxf8f6f4.block_scale``): no promotion of partial sums out of TMEM per K block."""
+    xq, x_sf = mxfp8_quantize(x2)
+    y = mxfp8_gemm(xq, x_sf, wq, w_sf)
     return y if out_dtype == torch.bfloat16 else y.to(out_dtype)

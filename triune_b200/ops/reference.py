@@ -579,26 +579,71 @@ def nvfp4_sf_kblocks(K: int) -> int:
     return -(-K // 256) * 4
 
 
-def nvfp4_block_scales(scales: torch.Tensor, K: int) -> torch.Tensor:
-    """Row-major one-byte scales [R, K/16] -> the tensor core's blocked layout [ceil(R/128), kblocks, 512] (uint8):
-    per 128 rows x 64 elements of K, byte (row % 32) * 16 + (row // 32) * 4 + (k // 16) % 4; missing rows / k are 0."""
-    R, kb16 = scales.shape
-    assert kb16 == K // 16
-    kb = nvfp4_sf_kblocks(K)
-    out = torch.zeros((-(-R // 128), kb, 512), dtype=torch.uint8, device=scales.device)
-    r = torch.arange(R, device=scales.device).unsqueeze(1).expand(R, kb16)
-    b = torch.arange(kb16, device=scales.device).unsqueeze(0).expand(R, kb16)
-    out[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] = scales.view(torch.uint8)
+def mxfp8_sf_kblocks(K: int) -> int:
+    return -(-K // 128)
+
+
+def _block_scale_bytes(scales_u8: torch.Tensor, kblocks: int) -> torch.Tensor:
+    """Row-major one-byte scales [R, G] -> the tensor core's blocked layout [ceil(R/128), kblocks, 512] (uint8): per 128
+    rows x 4 scale groups, byte (row % 32) * 16 + (row // 32) * 4 + group % 4; missing rows / groups are 0."""
+    R, G = scales_u8.shape
+    out = torch.zeros((-(-R // 128), kblocks, 512), dtype=torch.uint8, device=scales_u8.device)
+    r = torch.arange(R, device=scales_u8.device).unsqueeze(1).expand(R, G)
+    b = torch.arange(G, device=scales_u8.device).unsqueeze(0).expand(R, G)
+    out[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] = scales_u8
     return out
+
+
+def _unblock_scale_bytes(blocked: torch.Tensor, R: int, G: int, kblocks: int) -> torch.Tensor:
+    r = torch.arange(R, device=blocked.device).unsqueeze(1).expand(R, G)
+    b = torch.arange(G, device=blocked.device).unsqueeze(0).expand(R, G)
+    flat = blocked.reshape(-(-R // 128), kblocks, 512)
+    return flat[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4].contiguous()
+
+
+def nvfp4_block_scales(scales: torch.Tensor, K: int) -> torch.Tensor:
+    """Row-major E4M3 scales [R, K/16] -> the blocked layout of the NVFP4 GEMM (blocks of 128 rows x 64 elements)."""
+    assert scales.shape[1] == K // 16
+    return _block_scale_bytes(scales.view(torch.uint8), nvfp4_sf_kblocks(K))
 
 
 def nvfp4_unblock_scales(blocked: torch.Tensor, R: int, K: int) -> torch.Tensor:
     """Inverse of :func:`nvfp4_block_scales`: -> E4M3 [R, K/16]."""
-    kb16 = K // 16
-    r = torch.arange(R, device=blocked.device).unsqueeze(1).expand(R, kb16)
-    b = torch.arange(kb16, device=blocked.device).unsqueeze(0).expand(R, kb16)
-    flat = blocked.reshape(-(-R // 128), nvfp4_sf_kblocks(K), 512)
-    return flat[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4].contiguous().view(torch.float8_e4m3fn)
+    return _unblock_scale_bytes(blocked, R, K // 16, nvfp4_sf_kblocks(K)).view(torch.float8_e4m3fn)
+
+
+def mxfp8_quantize(x: torch.Tensor):
+    """[R,K] -> (E4M3 [R,K], exponent bytes [R,K/32]): one power-of-two scale 2^(byte-127) per 32 elements, the smallest
+    that brings the block's largest magnitude under 448 (OCP microscaling MXFP8 with E4M3 elements)."""
+    R, K = x.shape
+    assert K % 32 == 0
+    xf = x.float().reshape(R, K // 32, 32)
+    amax = xf.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 448.0)), torch.full_like(amax, -127.0, dtype=torch.float64))
+    e = e.clamp(-127, 127)
+    q = (xf.double() * torch.exp2(-e).unsqueeze(-1)).float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(R, K)
+    return q.contiguous(), (e + 127).to(torch.uint8).contiguous()
+
+
+def mxfp8_dequantize(q: torch.Tensor, exps: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+    scale = torch.exp2(exps.double() - 127.0).repeat_interleave(32, dim=1)
+    return (q.double() * scale).to(dtype)
+
+
+def mxfp8_block_scales(exps: torch.Tensor, K: int) -> torch.Tensor:
+    assert exps.shape[1] == K // 32
+    return _block_scale_bytes(exps, mxfp8_sf_kblocks(K))
+
+
+def mxfp8_unblock_scales(blocked: torch.Tensor, R: int, K: int) -> torch.Tensor:
+    return _unblock_scale_bytes(blocked, R, K // 32, mxfp8_sf_kblocks(K))
+
+
+def mxfp8_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """fp32 oracle of the MXFP8 linear: both operands quantised per 1x32 block, product of the decoded values."""
+    xq, xe = mxfp8_quantize(x)
+    wq, we = mxfp8_quantize(w)
+    return mxfp8_dequantize(xq, xe) @ mxfp8_dequantize(wq, we).t()
 
 
 def nvfp4_w4a4_linear(x: torch.Tensor, packed, scales, tscale, hadamard: bool = False) -> torch.Tensor:
