@@ -39,6 +39,11 @@ def test_ten_training_steps_track_the_reference_loss_curve():
     ours = TriuneTransformer(**arch)
     ours.load_state_dict(ref.state_dict())
     ours = ours.to(device=dev, dtype=torch.bfloat16)
+    import triune.model.attention as ref_attention  # already imported through the model; still in sys.modules
+    from triune_b200.models.attention import set_gla_scale
+
+    # with flash-linear-attention installed the reference's CUDA path scales the queries by head_dim ** -0.5
+    set_gla_scale(ours, "fla" if getattr(ref_attention, "HAS_FLA", False) else "none")
     g = torch.Generator().manual_seed(5)
     batches = [torch.randint(0, 2048, (4, 257), generator=g).to(dev) for _ in range(3)]  # a small pool: the loss must fall
     opt_ref = torch.optim.AdamW(ref.parameters(), lr=2e-3, betas=(0.9, 0.95), weight_decay=0.0)

@@ -388,3 +388,25 @@ def test_steered_bases_meet_the_orthogonality_and_subdiagonal_bars():
     assert float((l16.t() @ l16 - eye).norm()) < 5e-3 and float((r16.t() @ r16 - eye).norm()) < 5e-3
     S16 = l16.t() @ G[0] @ r16
     assert float(S16[:r, :r][low[:r, :r]].abs().max()) / float(G.norm()) < 1e-4
+
+
+def test_gla_output_scale_option():
+    """``gla_scale="fla"`` multiplies every GLA mixer's output by head_dim ** -0.5 (and its gradients accordingly)."""
+    from triune_b200.models.attention import VectorisedGLA, set_gla_scale
+
+    torch.manual_seed(0)
+    m = VectorisedGLA(32, 2, 16)
+    x = torch.randn(2, 24, 32, requires_grad=True)
+    y0, _ = m(x)
+    g0 = torch.autograd.grad(y0.square().sum(), [x, m.out_proj.weight])
+    wrap = torch.nn.ModuleList([m])
+    assert set_gla_scale(wrap, "fla") == 1 and abs(m.out_scale - 0.25) < 1e-12
+    y1, _ = m(x)
+    g1 = torch.autograd.grad(y1.square().sum(), [x, m.out_proj.weight])
+    assert torch.allclose(y1, 0.25 * y0, atol=1e-6)
+    for a, b in zip(g1, g0):
+        assert torch.allclose(a, 0.0625 * b, atol=1e-6)
+    set_gla_scale(wrap, "none")
+    assert m.out_scale == 1.0
+    d = VectorisedGLA(32, 2, 16, use_delta_rule=True)
+    assert set_gla_scale(torch.nn.ModuleList([d]), "fla") == 0 and d.out_scale == 1.0  # the delta-rule path is never scaled

@@ -88,6 +88,7 @@ class ModelConfig:
     ffn: str = "gelu"  # dense FFN activation: "gelu" | "swiglu"
     num_kv_heads: Optional[int] = None  # sdpa mixer only (GQA)
     use_rope: bool = True
+    gla_scale: str = "none"  # "fla": GLA outputs times head_dim ** -0.5 (models trained by the reference with flash-linear-attention)
     rope_base: float = ROPE_BASE
     rope_max_seq_len: int = ROPE_MAX_SEQ_LEN
     capacity_multiplier: float = MOE_CAPACITY_MULTIPLIER

@@ -389,13 +389,14 @@ std::vector<Tensor> moe_route_topk(const Tensor& logits, const Tensor& bias, con
   const int64_t N = logits.size(0), E = logits.size(1);
   Tensor idx = torch::empty({N, K}, logits.options().dtype(at::kLong));
   Tensor w = torch::empty({N, K}, logits.options());
-  Tensor keys = torch::empty({N * K}, logits.options().dtype(at::kLong));
+  const bool keys32 = E <= 32;  // 31-bit sort keys: half the radix passes of the plan's one sort
+  Tensor keys = torch::empty({N * K}, logits.options().dtype(keys32 ? at::kInt : at::kLong));
   Tensor counts = torch::empty({E, K}, logits.options().dtype(at::kInt));
   const bool ht = temperature.has_value() && temperature->defined();
   if (ht) TORCH_CHECK(temperature->scalar_type() == at::kFloat && temperature->is_cuda(), "temperature: fp32 device scalar");
   tb::launch_moe_route_topk(logits.data_ptr<float>(), bias.data_ptr<float>(), ht ? temperature->data_ptr<float>() : nullptr,
                             (float)temp_value, (int)N, (int)E, (int)K, (long long*)idx.data_ptr<int64_t>(), w.data_ptr<float>(),
-                            (long long*)keys.data_ptr<int64_t>(), counts.data_ptr<int>(), cur_stream());
+                            keys.data_ptr(), keys32, counts.data_ptr<int>(), cur_stream());
   return {idx, w, keys, counts};
 }
 
@@ -413,15 +414,17 @@ Tensor moe_route_bwd(const Tensor& logits, const c10::optional<Tensor>& temperat
 
 std::vector<Tensor> moe_plan_sorted(const Tensor& sorted_keys, const Tensor& order, const Tensor& counts, int64_t N, int64_t K,
                                     int64_t cap) {
-  TORCH_CHECK(sorted_keys.scalar_type() == at::kLong && order.scalar_type() == at::kLong && counts.scalar_type() == at::kInt, "dtypes");
+  const bool keys32 = sorted_keys.scalar_type() == at::kInt;
+  TORCH_CHECK((keys32 || sorted_keys.scalar_type() == at::kLong) && order.scalar_type() == at::kLong && counts.scalar_type() == at::kInt,
+              "dtypes");
   c10::cuda::CUDAGuard guard(sorted_keys.device());
   const int64_t A = N * K, E = counts.size(0);
   const int64_t R = (A + 255) / 256 * 256 + E * 256;  // every expert's rows are padded to a multiple of 256
   auto oi = sorted_keys.options().dtype(at::kInt);
   Tensor pos = torch::empty({N, K}, oi), keep = torch::empty({N, K}, sorted_keys.options().dtype(at::kBool));
   Tensor row_src = torch::empty({R}, oi), tile_group = torch::empty({R / 128}, oi), offsets = torch::empty({E + 1}, oi);
-  Tensor accepted = torch::empty({E}, sorted_keys.options());
-  tb::launch_moe_plan_sorted((const long long*)sorted_keys.data_ptr<int64_t>(), (const long long*)order.data_ptr<int64_t>(),
+  Tensor accepted = torch::empty({E}, sorted_keys.options().dtype(at::kLong));
+  tb::launch_moe_plan_sorted(sorted_keys.data_ptr(), keys32, (const long long*)order.data_ptr<int64_t>(),
                              counts.data_ptr<int>(), (int)A, (int)E, (int)K, (int)cap, (int)R, pos.data_ptr<int>(),
                              (unsigned char*)keep.data_ptr<bool>(), row_src.data_ptr<int>(), tile_group.data_ptr<int>(),
                              offsets.data_ptr<int>(), (long long*)accepted.data_ptr<int64_t>(), cur_stream());

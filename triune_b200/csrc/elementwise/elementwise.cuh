@@ -99,10 +99,10 @@ void launch_tier_render(const float* act, const int* tiers, uint32_t* rgba, int 
 // MoE routing: top-k + mixing weights + sort keys + per-(expert, slot) counts; gradient of the weights; and the
 // dispatch plan from the sorted keys (see moe_route.cu).
 void launch_moe_route_topk(const float* logits, const float* bias, const float* temperature, float temp_value, int N, int E, int K,
-                           long long* idx, float* w, long long* keys, int* counts, cudaStream_t s);
+                           long long* idx, float* w, void* keys, bool keys32, int* counts, cudaStream_t s);
 void launch_moe_route_bwd(const float* logits, const float* temperature, float temp_value, const long long* idx, const float* w,
                           const float* dw, int N, int E, int K, float* dlogits, cudaStream_t s);
-void launch_moe_plan_sorted(const long long* sorted_keys, const long long* order, const int* counts, int A, int E, int K, int cap,
+void launch_moe_plan_sorted(const void* sorted_keys, bool keys32, const long long* order, const int* counts, int A, int E, int K, int cap,
                             int R, int* pos, unsigned char* keep, int* row_src, int* tile_group, int* group_offsets,
                             long long* accepted, cudaStream_t s);
 

@@ -24,10 +24,33 @@ namespace {
 
 constexpr int MAX_E = 64, MAX_K = 4;
 
+// Sort keys: ascending key order = expert, then slot, then DEScending weight (weights are positive, so bit order = value
+// order). Up to 32 experts the key fits 31 bits (5 + 2 + the top 24 bits of the weight: sign, exponent, 15 mantissa
+// bits), which halves the passes and the bytes of the radix sort; weights closer than 2^-15 relative then count as
+// ties and go to the lower token index like exact ties.
+template <typename KeyT>
+__device__ __forceinline__ KeyT make_route_key(int e, int j, float w) {
+  if constexpr (sizeof(KeyT) == 4)
+    return (KeyT)(((uint32_t)e << 26) | ((uint32_t)j << 24) | (0xFFFFFFu - (__float_as_uint(w) >> 8)));
+  else
+    return ((long long)e << 36) | ((long long)j << 32) | (long long)(0xFFFFFFFFu - __float_as_uint(w));
+}
+template <typename KeyT>
+__device__ __forceinline__ void split_route_key(KeyT key, int& e, int& j) {
+  if constexpr (sizeof(KeyT) == 4) {
+    e = (int)((uint32_t)key >> 26);
+    j = (int)(((uint32_t)key >> 24) & 3u);
+  } else {
+    e = (int)(key >> 36);
+    j = (int)((key >> 32) & 0xF);
+  }
+}
+
+template <typename KeyT>
 __global__ void __launch_bounds__(256) moe_route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                                              const float* __restrict__ temperature, float temp_value, int N, int E,
                                                              int K, long long* __restrict__ idx, float* __restrict__ w,
-                                                             long long* __restrict__ keys, int* __restrict__ counts /*[E][K]*/) {
+                                                             KeyT* __restrict__ keys, int* __restrict__ counts /*[E][K]*/) {
   __shared__ int hist[MAX_E * MAX_K];
   for (int i = threadIdx.x; i < E * K; i += blockDim.x) hist[i] = 0;
   __syncthreads();
@@ -68,8 +91,7 @@ __global__ void __launch_bounds__(256) moe_route_topk_kernel(const float* __rest
       const float wj = pw[j] * norm;
       idx[(long long)t * K + j] = sel[j];
       w[(long long)t * K + j] = wj;
-      // ascending key order = expert, then slot, then DEScending weight (weights are positive: bit order = value order)
-      keys[(long long)t * K + j] = ((long long)sel[j] << 36) | ((long long)j << 32) | (long long)(0xFFFFFFFFu - __float_as_uint(wj));
+      keys[(long long)t * K + j] = make_route_key<KeyT>(sel[j], j, wj);
       atomicAdd(&hist[sel[j] * K + j], 1);
     }
   }
@@ -116,7 +138,8 @@ __global__ void __launch_bounds__(256) moe_route_bwd_kernel(const float* __restr
 }
 
 // One thread per SORTED assignment.
-__global__ void __launch_bounds__(256) moe_plan_sorted_kernel(const long long* __restrict__ sorted_keys,
+template <typename KeyT>
+__global__ void __launch_bounds__(256) moe_plan_sorted_kernel(const KeyT* __restrict__ sorted_keys,
                                                               const long long* __restrict__ order, const int* __restrict__ counts,
                                                               int A, int E, int K, int cap, int R, int* __restrict__ pos,
                                                               unsigned char* __restrict__ keep, int* __restrict__ row_src,
@@ -145,8 +168,8 @@ __global__ void __launch_bounds__(256) moe_plan_sorted_kernel(const long long* _
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < A) {
-    const long long key = sorted_keys[i];
-    const int e = (int)(key >> 36), j = (int)((key >> 32) & 0xF);
+    int e, j;
+    split_route_key<KeyT>(sorted_keys[i], e, j);
     const int a = (int)order[i];
     const int rank = i - seg_start[e * K + j];
     const bool ok = rank < cap;
@@ -176,11 +199,17 @@ void check(const char* what) {
 }  // namespace
 
 void launch_moe_route_topk(const float* logits, const float* bias, const float* temperature, float temp_value, int N, int E, int K,
-                           long long* idx, float* w, long long* keys, int* counts, cudaStream_t s) {
+                           long long* idx, float* w, void* keys, bool keys32, int* counts, cudaStream_t s) {
   if (E > MAX_E || K > MAX_K || K > E) throw std::runtime_error("moe_route_topk: at most 64 experts and top-4");
   cudaMemsetAsync(counts, 0, sizeof(int) * E * K, s);
   if (N <= 0) return;
-  moe_route_topk_kernel<<<(N + 255) / 256, 256, 0, s>>>(logits, bias, temperature, temp_value, N, E, K, idx, w, keys, counts);
+  if (keys32) {
+    if (E > 32) throw std::runtime_error("moe_route_topk: 32-bit sort keys hold at most 32 experts");
+    moe_route_topk_kernel<int><<<(N + 255) / 256, 256, 0, s>>>(logits, bias, temperature, temp_value, N, E, K, idx, w, (int*)keys, counts);
+  } else {
+    moe_route_topk_kernel<long long><<<(N + 255) / 256, 256, 0, s>>>(logits, bias, temperature, temp_value, N, E, K, idx, w,
+                                                                    (long long*)keys, counts);
+  }
   check("moe_route_topk");
 }
 
@@ -191,13 +220,17 @@ void launch_moe_route_bwd(const float* logits, const float* temperature, float t
   check("moe_route_bwd");
 }
 
-void launch_moe_plan_sorted(const long long* sorted_keys, const long long* order, const int* counts, int A, int E, int K, int cap,
+void launch_moe_plan_sorted(const void* sorted_keys, bool keys32, const long long* order, const int* counts, int A, int E, int K, int cap,
                             int R, int* pos, unsigned char* keep, int* row_src, int* tile_group, int* group_offsets,
                             long long* accepted, cudaStream_t s) {
   if (E > MAX_E || K > MAX_K) throw std::runtime_error("moe_plan_sorted: at most 64 experts and top-4");
   cudaMemsetAsync(row_src, 0xFF, sizeof(int) * (size_t)R, s);  // -1 = padding row
-  moe_plan_sorted_kernel<<<(A + 255) / 256, 256, 0, s>>>(sorted_keys, order, counts, A, E, K, cap, R, pos, keep, row_src, tile_group,
-                                                         group_offsets, accepted);
+  if (keys32)
+    moe_plan_sorted_kernel<int><<<(A + 255) / 256, 256, 0, s>>>((const int*)sorted_keys, order, counts, A, E, K, cap, R, pos, keep, row_src,
+                                                                tile_group, group_offsets, accepted);
+  else
+    moe_plan_sorted_kernel<long long><<<(A + 255) / 256, 256, 0, s>>>((const long long*)sorted_keys, order, counts, A, E, K, cap, R, pos,
+                                                                      keep, row_src, tile_group, group_offsets, accepted);
   check("moe_plan_sorted");
 }
 

@@ -405,12 +405,12 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const __nv_bfloat16
       v[2 * j + 1] = f.y;
       amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
     }
-    // e = ceil(log2(amax / 448)), from the exponent field: amax / 448 = m * 2^ex with m in [1, 2)
+    // e = ceil(log2(amax / 448)) in integer arithmetic: amax = m * 2^ea with m in [1, 2) and 448 = 1.75 * 2^8, so
+    // amax <= 448 * 2^e  <=>  e >= ea - 8 + (m > 1.75)
     int e = -127;
     if (amax > 0.f) {
-      const float t = amax * (1.0f / 448.0f);
-      const uint32_t bits = __float_as_uint(t);
-      e = (int)((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) != 0 ? 1 : 0);
+      const uint32_t bits = __float_as_uint(amax);
+      e = (int)((bits >> 23) & 0xFF) - 127 - 8 + ((bits & 0x7FFFFF) > 0x600000 ? 1 : 0);
       e = e < -127 ? -127 : (e > 127 ? 127 : e);
     }
     const float inv = __uint_as_float((uint32_t)(127 - e) << 23);  // 2^-e (e in [-127, 127]: 2^127 ... 2^-127 denormal-safe below)

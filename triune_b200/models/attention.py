@@ -62,12 +62,34 @@ class _ProjView:
         return F.linear(x, self.weight)
 
 
-def _project(mod: nn.Module, x: torch.Tensor) -> torch.Tensor:
-    """Plain ``nn.Linear`` goes straight to the GEMM; wrapped / quantised replacements (LoRA, FP8, NVFP4) run their own
-    forward."""
+def _project(mod: nn.Module, x: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+    """Plain ``nn.Linear`` goes straight to the GEMM (``alpha`` rides in its epilogue); wrapped / quantised
+    replacements (LoRA, FP8, NVFP4) run their own forward."""
     if type(mod) is nn.Linear:
-        return ops.linear(x, mod.weight, mod.bias)
-    return mod(x)
+        return ops.linear(x, mod.weight, mod.bias, alpha)
+    return mod(x if alpha == 1.0 else x * alpha)
+
+
+def set_gla_scale(model: nn.Module, mode) -> int:
+    """Output scale of every (non-delta-rule) GLA mixer of ``model``: ``"none"`` / ``None`` = 1, ``"fla"`` =
+    head_dim ** -0.5, or a number. Returns the number of mixers set.
+
+    The reference multiplies nothing on its PyTorch path, but where the flash-linear-attention package is installed
+    its CUDA path calls ``chunk_gla(..., scale=None)`` (``triune/model/attention.py:536-566``), whose default is
+    head_dim ** -0.5 on the queries. A checkpoint trained there carries that factor in its weights, so the choice is
+    part of the model's configuration here (``ModelConfig.gla_scale``) instead of depending on what is installed.
+    GLA is linear in the queries, so the factor is applied to the mixer output, inside the output projection's GEMM."""
+    n = 0
+    for m in model.modules():
+        if isinstance(m, VectorisedGLA) and not m.use_delta_rule:
+            if mode in (None, "none", "", 1, 1.0):
+                m.out_scale = 1.0
+            elif mode == "fla":
+                m.out_scale = float(m.head_dim) ** -0.5
+            else:
+                m.out_scale = float(mode)
+            n += 1
+    return n
 
 
 class VectorisedGLA(nn.Module):
@@ -83,6 +105,7 @@ class VectorisedGLA(nn.Module):
         self.hidden_dim = heads * head_dim
         self.use_delta_rule = use_delta_rule
         self.use_rope = use_rope
+        self.out_scale = 1.0  # see set_gla_scale
         self.qkvg_weight = nn.Parameter(torch.empty(4 * self.hidden_dim, dim))
         self.out_proj = nn.Linear(self.hidden_dim, dim, bias=False)
         self.beta_proj = nn.Linear(dim, heads, bias=False) if (use_delta_rule and learn_beta) else None
@@ -134,7 +157,7 @@ class VectorisedGLA(nn.Module):
             cos, sin = self.rope(T, x.device, offset=offset)
         if not self.use_delta_rule and gla_cuda.core_supported(qkvg, T, D):
             out, new_state = gla_cuda.gla_attention_core(qkvg, cos, sin, state, B, T, H)
-            y = _project(self.out_proj, out.view(B, T, self.hidden_dim))
+            y = _project(self.out_proj, out.view(B, T, self.hidden_dim), self.out_scale)
             return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
         q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
         if self.use_delta_rule:
@@ -143,7 +166,7 @@ class VectorisedGLA(nn.Module):
         else:
             out, new_state = ops.gla(q, k, v, g, initial_state=state, gate_logits=True)
         out = out.reshape(B, T, self.hidden_dim).to(x.dtype)
-        y = _project(self.out_proj, out)
+        y = _project(self.out_proj, out, 1.0 if self.use_delta_rule else self.out_scale)
         return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
 
 

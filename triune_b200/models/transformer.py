@@ -137,6 +137,10 @@ class TriuneTransformer(nn.Module):
         cfg.validate()
         model = cls._from_validated(cfg)
         model.model_config = cfg  # plain attribute: checkpoints record the architecture from here
+        if getattr(cfg, "gla_scale", "none") not in (None, "none"):
+            from .attention import set_gla_scale
+
+            set_gla_scale(model, cfg.gla_scale)
         return model
 
     @classmethod

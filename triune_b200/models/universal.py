@@ -97,7 +97,12 @@ class UniversalDenseTransformer(nn.Module):
 
     @classmethod
     def from_config(cls, cfg: ModelConfig):
-        return cls(cfg)
+        model = cls(cfg)
+        if getattr(cfg, "gla_scale", "none") not in (None, "none"):
+            from .attention import set_gla_scale
+
+            set_gla_scale(model, cfg.gla_scale)
+        return model
 
     @staticmethod
     def _init(m):

@@ -115,13 +115,13 @@ def gemm(
     return out
 
 
-def _accumulate_weight_grad(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
-    """dW = dy^T x. Accumulates into ``w.main_grad`` (fp32) when the parameter has one, else returns bf16."""
+def _accumulate_weight_grad(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor, alpha: float = 1.0):
+    """dW = alpha * dy^T x. Accumulates into ``w.main_grad`` (fp32) when the parameter has one, else returns bf16."""
     mg = getattr(w, "main_grad", None)
     if mg is not None:
-        gemm(dy2, x2, mg, a_mn=True, b_mn=True, accumulate=True)
+        gemm(dy2, x2, mg, a_mn=True, b_mn=True, accumulate=True, alpha=alpha)
         return None
-    return gemm(dy2, x2, a_mn=True, b_mn=True)
+    return gemm(dy2, x2, a_mn=True, b_mn=True, alpha=alpha)
 
 
 def _accumulate_bias_grad(b: Optional[torch.Tensor], dy2: torch.Tensor):
@@ -145,15 +145,16 @@ def _accumulate_bias_grad(b: Optional[torch.Tensor], dy2: torch.Tensor):
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, alpha=1.0):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         if not _tma_ok(x2):
             x2 = x2.contiguous()
-        y = gemm(x2, w, bias=bias)
+        y = gemm(x2, w, bias=bias, alpha=alpha)  # alpha scales the product, not the bias
         ctx.save_for_backward(x2, w, bias if bias is not None else torch.empty(0))
         ctx.has_bias = bias is not None
         ctx.in_shape = x.shape
+        ctx.alpha = float(alpha)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -164,18 +165,21 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).view(ctx.in_shape)
+            dx = gemm(dy2, w, b_mn=True, alpha=ctx.alpha).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = _accumulate_weight_grad(w, dy2, x2)
+            dw = _accumulate_weight_grad(w, dy2, x2, ctx.alpha)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _accumulate_bias_grad(bias, dy2)
-        return dx, dw, db
+        return dx, dw, db, None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x @ w^T + bias."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, alpha: float = 1.0) -> torch.Tensor:
+    """y = alpha * x @ w^T + bias (the scale rides in the GEMM epilogues of the forward and both gradients)."""
     if _ext.use_kernels(x, w) and x.dtype == torch.bfloat16 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
-        return _LinearFn.apply(x, w, bias)
+        return _LinearFn.apply(x, w, bias, alpha)
+    if alpha != 1.0:
+        y = F.linear(x, w) * alpha
+        return y if bias is None else y + bias
     return F.linear(x, w, bias)
 
 

@@ -619,7 +619,9 @@ def mxfp8_quantize(x: torch.Tensor):
     assert K % 32 == 0
     xf = x.float().reshape(R, K // 32, 32)
     amax = xf.abs().amax(-1)
-    e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 448.0)), torch.full_like(amax, -127.0, dtype=torch.float64))
+    # e = ceil(log2(amax / 448)) without a logarithm: amax = m * 2^ex with m in [0.5, 1), 448 = 0.875 * 2^9
+    m, ex = torch.frexp(amax.float())
+    e = torch.where(amax > 0, (ex - 9 + (m > 0.875).to(ex.dtype)).double(), torch.full_like(amax, -127.0, dtype=torch.float64))
     e = e.clamp(-127, 127)
     q = (xf.double() * torch.exp2(-e).unsqueeze(-1)).float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(R, K)
     return q.contiguous(), (e + 127).to(torch.uint8).contiguous()
