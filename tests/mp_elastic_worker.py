@@ -19,10 +19,19 @@ def main():
     victim, die_at, mode = int(os.environ["EL_VICTIM"]), int(os.environ["EL_DIE_AT"]), os.environ["EL_MODE"]
     ckpt = os.environ["EL_CKPT"]
     total = int(os.environ.get("EL_STEPS", "8"))
-    group = ElasticGroup("127.0.0.1", port, ident, world, backend="gloo", hb_interval=0.1, hb_timeout=1.0, pg_timeout=4.0)
+    on_gpu = os.environ.get("EL_DEVICE", "cpu") == "cuda"
+    strict = os.environ.get("EL_STRICT", "1" if on_gpu else "0") == "1"
+    dev = torch.device("cpu")
+    if on_gpu:
+        # GPU form of the test: NCCL over plain peer transport (no NVLS), members meet on the store before every step,
+        # and a rank only ever leaves between two steps with its own work drained
+        torch.cuda.set_device(ident)
+        dev = torch.device("cuda", ident)
+    group = ElasticGroup("127.0.0.1", port, ident, world, backend="nccl" if on_gpu else "gloo", hb_interval=0.1, hb_timeout=1.0,
+                         pg_timeout=20.0 if on_gpu else 4.0, device_id=dev if on_gpu else None, strict_steps=strict)
     torch.manual_seed(0)
-    w = torch.zeros(4, dtype=torch.float64)
-    target = torch.tensor([1.0, -2.0, 0.5, 3.0], dtype=torch.float64)
+    w = torch.zeros(4, dtype=torch.float64, device=dev)
+    target = torch.tensor([1.0, -2.0, 0.5, 3.0], dtype=torch.float64, device=dev)
 
     def save(step):
         tmp = ckpt + ".tmp"
@@ -32,22 +41,29 @@ def main():
     def load():
         if not os.path.exists(ckpt):
             return 0
-        ck = torch.load(ckpt)
+        ck = torch.load(ckpt, map_location="cpu")
         w.copy_(ck["w"])
         return int(ck["step"])
 
     def step_fn(step, g):
-        if ident == victim and step == die_at and mode == "between":
+        if ident == victim and step == die_at and mode == "between" and not on_gpu:
             os._exit(17)  # gone between two steps, nothing in flight
         gen = torch.Generator().manual_seed(1000 * step + g.rank)  # data sharded by the CURRENT rank
-        x = torch.randn(16, 4, generator=gen, dtype=torch.float64)
+        x = torch.randn(16, 4, generator=gen, dtype=torch.float64).to(dev)
         err = x @ w - x @ target
         grad = x.t() @ err / len(x)
-        if ident == victim and step == die_at and mode == "midstep":
+        if ident == victim and step == die_at and mode == "midstep" and not on_gpu:
             os._exit(17)  # the others are already on their way into the all-reduce
         dist.all_reduce(grad)
         w.sub_(0.1 * grad / g.world)
-        return float((err ** 2).mean())
+        loss = float((err ** 2).mean())
+        if on_gpu and ident == victim and step + 1 == die_at:
+            # leave BEFORE the next step's meeting: this rank's step is complete and drained, it says so on the store,
+            # and the others learn of it on the host before they launch anything
+            torch.cuda.synchronize()
+            g.leave()
+            os._exit(17)
+        return loss
 
     out = run_elastic(group, step_fn, save, load, total_steps=total, checkpoint_every=2)
     out["ident"] = ident

@@ -111,3 +111,44 @@ def test_context_parallel_gla_on_gpus(nproc):
             assert r[k + "_vs_oracle"] < (8e-2 if k == "dg" else 5e-2), (k, r)  # dg: a difference of equal-sized terms
         if "state_vs_oracle" in r:
             assert r["state_vs_oracle"] < 2e-2, r
+
+
+def test_elastic_group_reforms_after_a_rank_leaves_between_steps(tmp_path):
+    """NCCL ranks on separate GPUs (NVLS off, plain peer transport). One rank finishes a step, drains its device, says on
+    the store that it is leaving and exits; the others meet on the store before every step, so they learn of it on the
+    host before launching anything, re-form as a smaller group, reload the last checkpoint and finish with equal weights.
+    No collective is ever launched with a missing peer and nothing is killed while work is in flight."""
+    from triune_b200.desktop import find_free_port
+    from triune_b200.parallel.elastic import connect_store
+
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = min(n, 3)
+    victim = world - 1
+    port = find_free_port(29850, attempts=100)
+    store = connect_store("127.0.0.1", port, is_master=True)  # noqa: F841  (outlives every rank)
+    env = dict(os.environ, OMP_NUM_THREADS="1", EL_PORT=str(port), EL_WORLD=str(world), EL_VICTIM=str(victim), EL_DIE_AT="5",
+               EL_MODE="between", EL_CKPT=str(tmp_path / "ck.pt"), EL_STEPS="8", EL_DEVICE="cuda", EL_STRICT="1",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_elastic_worker.py")], env=dict(env, EL_IDENT=str(i)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for i in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=300))
+        except subprocess.TimeoutExpired:
+            p.kill()  # this exact child only
+            outs.append(p.communicate())
+    assert procs[victim].returncode == 17, outs[victim][1][-1500:]
+    res = []
+    for i, (p, (so, se)) in enumerate(zip(procs, outs)):
+        if i == victim:
+            continue
+        assert p.returncode == 0, (i, so[-1500:], se[-1500:])
+        res.append(json.loads(re.search(r"RESULT (\{.*\})", so).group(1)))
+    survivors = list(range(world - 1))
+    for r in res:
+        assert r["steps"] == 8 and r["world"] == world - 1 and r["members"] == survivors and r["generation"] == 1
+        assert r["failures"] == [[victim]]
+    assert all(r["w"] == res[0]["w"] for r in res) and any(abs(v) > 1e-3 for v in res[0]["w"])

@@ -602,8 +602,8 @@ def test_rescue_checkpoint_stages():
     assert rep["config_update"]["depth_mode"] == "joint" and all(p.requires_grad for p in model.parameters())
 
 
-@pytest.mark.parametrize("victim,mode", [(2, "between"), (0, "midstep")])
-def test_elastic_data_parallel_survives_a_lost_rank(tmp_path, victim, mode):
+@pytest.mark.parametrize("victim,mode,strict", [(2, "between", "0"), (0, "midstep", "0"), (1, "between", "1")])
+def test_elastic_data_parallel_survives_a_lost_rank(tmp_path, victim, mode, strict):
     """Three gloo ranks; one leaves without notice (between steps, or when the others are already inside the step's
     all-reduce; once the lowest rank, which also writes the checkpoints). The survivors detect it by heartbeat or by
     the process group's timeout, re-form as two ranks, reload the last checkpoint, finish all steps and agree on the
@@ -617,7 +617,7 @@ def test_elastic_data_parallel_survives_a_lost_rank(tmp_path, victim, mode):
     port = find_free_port(29800, attempts=100)
     store = connect_store("127.0.0.1", port, is_master=True)  # noqa: F841  (kept alive for the workers)
     env = dict(os.environ, OMP_NUM_THREADS="1", EL_PORT=str(port), EL_WORLD="3", EL_VICTIM=str(victim), EL_DIE_AT="5",
-               EL_MODE=mode, EL_CKPT=str(tmp_path / "ck.pt"), EL_STEPS="8")
+               EL_MODE=mode, EL_CKPT=str(tmp_path / "ck.pt"), EL_STEPS="8", EL_STRICT=strict)  # strict: meet on the store before every step
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "mp_elastic_worker.py")], env=dict(env, EL_IDENT=str(i)),
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for i in range(3)]
     outs = []

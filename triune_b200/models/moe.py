@@ -198,7 +198,7 @@ class MoE_FFN(nn.Module):
         out = ops.moe_experts(x2, idx, wk, keep, self.w1, self.b1, self.w2, self.b2, shared_out, self.shared_scale, plan=plan)
         if self.training and update_stats:
             with torch.no_grad():
-                self._update_routing_stats(x2.detach(), idx, w.detach(), keep)
+                self._update_routing_stats(x2.detach(), idx, w.detach(), keep, plan)
         return out.reshape(B, T, D)
 
     def dense_forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -217,15 +217,21 @@ class MoE_FFN(nn.Module):
 
     # --- statistics (no gradient, no host sync) ---------------------------------------------
     @torch.no_grad()
-    def _update_routing_stats(self, x2, idx, w, keep):
+    def _update_routing_stats(self, x2, idx, w, keep, plan=None):
         E, N = self.num_experts, x2.shape[0]
         target = max(1.0, float(N * self.top_k / E))
         flat = idx.reshape(-1)
-        requested = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, torch.ones_like(flat))
-        if keep is None:
+        if plan is not None and getattr(plan, "slot_counts", None) is not None:
+            # the routing and plan kernels already counted: no atomics over N * k indices into E bins
+            requested = plan.slot_counts.sum(1, dtype=torch.int64)
+            accepted = plan[4] if keep is not None else requested
+            acc_mask = keep if keep is not None else torch.ones_like(idx, dtype=torch.bool)
+        elif keep is None:
+            requested = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, torch.ones_like(flat))
             accepted = requested
             acc_mask = torch.ones_like(idx, dtype=torch.bool)
         else:
+            requested = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, torch.ones_like(flat))
             accepted = torch.zeros(E, device=flat.device, dtype=torch.int64).scatter_add_(0, flat, keep.reshape(-1).long())
             acc_mask = keep
         dropped = (requested - accepted).clamp_min(0)
@@ -239,7 +245,7 @@ class MoE_FFN(nn.Module):
         # centroid EMA: mean of accepted tokens per expert
         mask = torch.zeros(N, E, dtype=x2.dtype, device=x2.device)
         mask.scatter_(1, idx, acc_mask.to(x2.dtype))
-        counts = mask.float().sum(0).unsqueeze(1)
+        counts = accepted.float().unsqueeze(1) if plan is not None else mask.float().sum(0).unsqueeze(1)
         if x2.is_cuda and x2.dtype == torch.bfloat16 and E % 8 == 0 and not ops._ext.reference_ops_enabled():
             sums = ops.gemm(mask, x2.contiguous(), a_mn=True, b_mn=True, out_dtype=torch.float32)
         else:

@@ -782,6 +782,7 @@ class RoutePlan(tuple):
     to multiples of 256 (``row_pad``), i.e. to whole pairs of 128-row tiles."""
 
     row_pad = 256
+    slot_counts = None  # [E, k] int32: assignments REQUESTED per (expert, k-slot), from the routing kernel
 
 
 def moe_route_plan(logits, expert_bias, top_k: int, temperature=1.0, capacity: Optional[int] = None):
@@ -796,7 +797,9 @@ def moe_route_plan(logits, expert_bias, top_k: int, temperature=1.0, capacity: O
     cap = int(capacity) if capacity is not None and capacity < N else N
     pos, keep, row_src, tile_group, offsets, accepted = _ext.ext().moe_plan_sorted(skeys, order, counts, N, top_k, cap)
     _tick(3)
-    return idx, w, keep, RoutePlan((pos, row_src, tile_group, offsets, accepted))
+    plan = RoutePlan((pos, row_src, tile_group, offsets, accepted))
+    plan.slot_counts = counts
+    return idx, w, keep, plan
 
 
 def moe_plan(idx: torch.Tensor, keep: Optional[torch.Tensor], num_experts: int, tile: int = 128):

@@ -153,7 +153,12 @@ class ElasticGroup:
     """
 
     def __init__(self, host: str, port: int, ident: int, world: int, backend: str = "gloo", hb_interval: float = 0.2,
-                 hb_timeout: float = 2.0, pg_timeout: float = 10.0, host_store: bool = False, device_id=None):
+                 hb_timeout: float = 2.0, pg_timeout: float = 10.0, host_store: bool = False, device_id=None,
+                 strict_steps: bool = False):
+        """``strict_steps``: before every step all members meet on the store (``step_rendezvous``), so that no rank
+        launches a collective, or a fused kernel that waits for a peer, while a member is missing. This is the mode
+        for GPUs: a kernel that waits for a rank that is gone only ends through a timeout."""
+        self.strict_steps = bool(strict_steps)
         self.host, self.port, self.ident, self.backend = host, int(port), int(ident), backend
         self.hb_timeout, self.pg_timeout, self.device_id = float(hb_timeout), float(pg_timeout), device_id
         self.store = connect_store(host, port, is_master=host_store)
@@ -197,10 +202,33 @@ class ElasticGroup:
 
     # ------------------------------------------------------------------ detection
     def guard(self) -> None:
-        """Call on the host before launching a step: raises :class:`RankFailure` if a peer is overdue."""
-        dead = self.detector.poll()
+        """Call on the host before launching a step: raises :class:`RankFailure` if a peer is overdue or has left."""
+        dead = sorted(set(self.detector.poll()) | set(self._left()))
         if dead:
-            raise RankFailure(dead, "heartbeat overdue")
+            raise RankFailure(dead, "heartbeat overdue or rank left")
+
+    def _left(self) -> List[int]:
+        return [m for m in self.members if m != self.ident and self.store.check([f"left/{m}"])]
+
+    def leave(self) -> None:
+        """Announce on the store that this rank is going (between two steps, with nothing of its own in flight) and stop
+        its heartbeat. The others see the announcement at their next :meth:`guard` / :meth:`step_rendezvous`."""
+        self.store.set(f"left/{self.ident}", "1")
+        self.heartbeat.stop()
+
+    def step_rendezvous(self, step: int, poll_s: float = 0.002) -> None:
+        """Host-side meeting before step ``step``: returns once every member has arrived; raises :class:`RankFailure`
+        as soon as a member is known to have left or its heartbeat is overdue. Nothing is launched before it returns."""
+        prefix = f"ready/{self.generation}/{step}"
+        self.store.set(f"{prefix}/{self.ident}", "1")
+        others = [m for m in self.members if m != self.ident]
+        while True:
+            gone = sorted(set(self._left()) | set(self.detector.poll()))
+            if gone:
+                raise RankFailure(gone, "member missing at the step rendezvous")
+            if all(self.store.check([f"{prefix}/{m}"]) for m in others):
+                return
+            time.sleep(poll_s)
 
     def diagnose(self, error: BaseException) -> RankFailure:
         """An error came out of a step: find out whether a peer died (waits up to about 1.5 heartbeat timeouts)."""
@@ -264,7 +292,10 @@ def run_elastic(group: ElasticGroup, step_fn: Callable[[int, ElasticGroup], floa
     step, reforms, losses = load_fn(), 0, []
     while step < total_steps:
         try:
-            group.guard()
+            if group.strict_steps:
+                group.step_rendezvous(step)
+            else:
+                group.guard()
             loss = step_fn(step, group)
             step += 1
             losses.append(float(loss))

@@ -119,7 +119,10 @@ class FusedDPUpdater:
             t.copy_(red[off : off + k].view(t.shape).to(t.dtype))
             off += k
 
-    def step(self):
+    def step(self, mark=None):
+        """One data-parallel optimizer step. ``mark(name)`` (optional) is called after each phase, on the launching
+        stream, so a benchmark can record CUDA events between the kernels."""
+        mark = mark or (lambda name: None)
         opt, buf = self.opt, self.buf
         a = opt.arena
         e = _ext.ext()
@@ -135,6 +138,7 @@ class FusedDPUpdater:
         dp_range.__enter__()
         e.dp_reduce_scatter(rank, world, bufs, sigs, mc, goff, noff, self.owned_flat, ep, buf.use_multimem, self.counter,
                             self.status, self.epoch_dev)
+        mark("reduce_scatter")
         lo, hi = a.adamw_range
         b1, b2 = opt.betas
         clip = float(opt.grad_clip) if opt.grad_clip else 0.0
@@ -144,14 +148,17 @@ class FusedDPUpdater:
                              opt._clip_coef, self.norm_out, ep, buf.use_multimem, self.status, self.epoch_dev, hyper)
         ops._tick(2)
         dp_range.__exit__(None, None, None)
+        mark("adamw_allgather")
         opt.last_grad_norm = self.norm_out
         opt._step_muon()
         opt._step_steer()
+        mark("matrix_tiers")
         if self.bcast_flat:
             e.dp_broadcast_ranges(rank, world, bufs, sigs, mc, poff, self.bcast_flat, buf.use_multimem)
             ops._tick()
         e.comm_barrier(rank, world, bufs, sigs, CH_PARAMS_DONE, ep, self.status, self.epoch_dev)
         ops._tick()
+        mark("broadcast_barrier")
         self.steps += 1
 
     def check(self) -> int:
