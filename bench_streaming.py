@@ -61,6 +61,10 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--resident-too", action="store_true", help="also time the same model fully resident on the GPU")
+    ap.add_argument("--optimizer", default="adamw", choices=["adamw", "tiered"],
+                    help="streamed layers: the engine's built-in AdamW, or the tiered optimizer (AdamW / Muon / CentroidSteer "
+                         "through step_parameters, one layer's state on the device at a time)")
+    ap.add_argument("--state-dtype", default="fp32", choices=["fp32", "bf16"], help="host format of the tiered optimizer's moments")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("bench_streaming.py needs a CUDA device")
@@ -74,13 +78,30 @@ def main():
     host = torch.randint(0, cfg.vocab_size, (a.batch, a.seq + 1), generator=torch.Generator().manual_seed(1)).pin_memory()
     eng = enable_layer_streaming(model, "cuda", config=StreamingConfig(resident_gpu_layers=a.resident_layers))
     last = {}
+    root_opt = None
+    if a.optimizer == "tiered":
+        from triune_b200.optim import CentroidSteerOptimizer
+
+        streamed = {id(p) for st in eng.stores.values() for p in st.params}
+        inner = CentroidSteerOptimizer(model, lr=1e-4, grad_clip=None, only=lambda n, p: id(p) not in streamed)
+        eng.enable_tiered_optimizer(lr=1e-4, state_dtype=torch.bfloat16 if a.state_dtype == "bf16" else torch.float32)
+
+        class _Root:  # the engine clips the root gradients itself, then calls step / zero_grad
+            def step(self):
+                inner.set_clip_coefficient(1.0)
+                inner.step_parameters([s_.param for s_ in inner.arena.segments], is_global_step_end=True)
+
+            def zero_grad(self, set_to_none=True):
+                inner.zero_grad()
+
+        root_opt = _Root()
 
     def step():
         ids = host.to("cuda", non_blocking=True)
         out = model.forward_loss(ids[:, :-1], ids[:, 1:], force_depth=2)
         loss = out[0] if isinstance(out, tuple) else out
         loss.backward()
-        eng.step_streaming_optimizer(None, lr=1e-4)
+        eng.step_streaming_optimizer(root_opt, lr=1e-4)
         last["loss"] = loss
 
     for _ in range(a.warmup):
@@ -94,7 +115,7 @@ def main():
            "s_per_step": round(sec, 4), "steps": a.steps, "warmup": a.warmup, "dtype": "bf16",
            "config": {"model": a.model if not a.shape else f"d{a.shape[0]}-L{a.shape[1]}-V{a.vocab}", "params": params,
                       "layers": cfg.num_layers, "hidden_dim": cfg.hidden_dim, "batch": a.batch, "seq_len": a.seq,
-                      "resident_layers": a.resident_layers},
+                      "resident_layers": a.resident_layers, "streamed_optimizer": a.optimizer, "state_dtype": a.state_dtype},
            "h2d_GB_per_step": round((tel.get("h2d_bytes", 0) - tel0.get("h2d_bytes", 0)) / a.steps / 2**30, 2),
            "peak_gpu_GB": round(torch.cuda.max_memory_allocated() / 2**30, 2), "build_s": round(build_s, 1),
            "final_loss": float(last["loss"]), "impl": "triune_b200"}

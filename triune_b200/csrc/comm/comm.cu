@@ -109,24 +109,50 @@ __global__ void __launch_bounds__(256) dp_reduce_scatter_kernel(PeerTable pt, lo
   float ss = 0.f;
   if (ok) {
     const float inv = 1.0f / (float)pt.world;
+    // A peer load takes a few microseconds to come back over NVLink; one 16-byte load per thread keeps about 1 MB in
+    // flight, a fraction of the link's bandwidth-delay product. Each thread therefore owns U strided vectors per pass
+    // and issues all of their loads (per peer) before the first add.
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
     for (int r = 0; r < ranges.count; ++r) {
       const long long b4 = ranges.r[r].begin >> 2, e4 = ranges.r[r].end >> 2;
-      for (long long i = b4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < e4;
-           i += (long long)gridDim.x * blockDim.x) {
-        float4 acc;
+      for (long long i0 = b4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < e4; i0 += stride * U) {
+        float4 acc[U];
         if (use_multimem) {
-          acc = multimem_ld_reduce_f4(reinterpret_cast<const float*>(pt.multicast + grad_off) + i * 4);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * stride;
+            acc[u] = i < e4 ? multimem_ld_reduce_f4(reinterpret_cast<const float*>(pt.multicast + grad_off) + i * 4)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         } else {
-          acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int p = 0; p < pt.world; ++p) {
             const int peer = (pt.rank + p) % pt.world;  // stagger so ranks do not all hit the same peer first
-            float4 v = ld_peer_f4(reinterpret_cast<const float*>(pt.bufs[peer] + grad_off) + i * 4);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            const float* src = reinterpret_cast<const float*>(pt.bufs[peer] + grad_off);
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const long long i = i0 + u * stride;
+              v[u] = i < e4 ? ld_peer_f4(src + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+            }
           }
         }
-        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-        reinterpret_cast<float4*>(local_grad)[i] = acc;
-        ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < e4) {
+            float4 a = acc[u];
+            a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+            reinterpret_cast<float4*>(local_grad)[i] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+          }
+        }
       }
     }
   }

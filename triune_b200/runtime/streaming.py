@@ -284,13 +284,28 @@ class LayerStreamingEngine:
             streamed.update(id(p) for p in st.params)
             if st.grad_sumsq is not None:
                 total += st.grad_sumsq.to(self.device)
-        root = [p for p in self.model.parameters() if id(p) not in streamed and p.grad is not None]
-        for p in root:
-            total += p.grad.double().pow(2).sum()
+        # root gradients: autograd's ``.grad``, or the fp32 arena view the kernels accumulate into (``main_grad``) when
+        # the root optimizer is arena-based; ``.grad`` leftovers are folded into the arena first
+        root_grads = []
+        seen = set()
+        for p in self.model.parameters():
+            if id(p) in streamed or id(p) in seen:
+                continue
+            seen.add(id(p))
+            mg = getattr(p, "main_grad", None)
+            if mg is not None:
+                if p.grad is not None:
+                    mg.add_(p.grad.to(mg.dtype))
+                    p.grad = None
+                root_grads.append(mg)
+            elif p.grad is not None:
+                root_grads.append(p.grad)
+        for g in root_grads:
+            total += g.double().pow(2).sum()
         norm = total.sqrt()
         coef = torch.clamp(clip / (norm + 1e-6), max=1.0).float() if clip and clip > 0 else torch.ones((), device=self.device)
-        for p in root:
-            p.grad.mul_(coef.to(p.grad.dtype))
+        for g in root_grads:
+            g.mul_(coef.to(g.dtype))
         if optimizer is not None:
             optimizer.step()
             optimizer.zero_grad(set_to_none=True)
