@@ -53,6 +53,8 @@ def main():
     m_f, o_f, dp_f = build(ctx, "fused", use_mm)
     l_f = run(m_f, o_f, ctx)
     out["status"] = dp_f._fused.check()
+    dist.barrier()  # every rank has finished its last step: no signal may be outstanding
+    out["signals_consumed"] = bool(all(dp_f._fused.audit().values()))
     out["multimem"] = bool(dp_f._fused.buf.use_multimem)
     pa, pb = o_ref.arena.flat_param.float(), o_f.arena.flat_param.float()
     out["max_param_diff"] = float((pa - pb).abs().max())

@@ -798,3 +798,44 @@ def test_layer_streaming_on_gpu_matches_resident_model():
     lb2 = loss_of(b)
     assert torch.isfinite(lb2) and abs(float(lb2) - float(lb)) > 1e-4
     eng.detach()
+
+
+def test_guard_bands_and_index_error_word():
+    """Outputs carved out of guard-banded buffers: ragged GEMM tiles, a ragged FP8 block GEMM and the row-movement
+    kernels leave the bands untouched; an index outside its table is skipped and recorded instead of being followed."""
+    from triune_b200 import ops
+    from triune_b200.utils.guards import check_guards, guarded_empty, index_error
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    torch.manual_seed(0)
+    dev = "cuda"
+    for M, N, K in ((130, 200, 72), (257, 136, 384), (64, 8, 64)):
+        a = torch.randn(M, K, device=dev).bfloat16()
+        b = torch.randn(N, K, device=dev).bfloat16()
+        out, whole = guarded_empty((M, N), torch.bfloat16, dev)
+        ops.gemm(a, b, out)
+        torch.cuda.synchronize()
+        check_guards(out, whole)
+        want = a.float() @ b.float().t()
+        assert (out.float() - want).abs().max() <= 2e-2 * want.abs().max()
+        outf, wholef = guarded_empty((M, N), torch.float32, dev)
+        outf.zero_()
+        ops.gemm(a, b, outf, accumulate=True, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        check_guards(outf, wholef)
+    e = ops._ext.ext()
+    assert index_error() is None
+    src = torch.randn(40, 64, device=dev).bfloat16()
+    rows = torch.tensor([3, -1, 39, 40, 1000, 0], device=dev, dtype=torch.int32)  # 40 and 1000 are outside the table
+    got = e.gather_rows(src, rows, None)
+    err = index_error()
+    assert err is not None and err["kernel"] == "gather_rows" and err["limit"] == 40 and err["index"] in (40, 1000)
+    assert torch.equal(got[0], src[3]) and torch.equal(got[2], src[39]) and float(got[1].abs().sum()) == 0.0
+    assert float(got[3].abs().sum()) == 0.0 and float(got[4].abs().sum()) == 0.0  # skipped, not followed
+    pos = torch.tensor([[0, 41], [5, -1]], device=dev, dtype=torch.int32)
+    comb = e.combine_rows(src, pos, None, None, 0.0)
+    err = index_error()
+    assert err is not None and err["kernel"] == "combine_rows" and err["index"] == 41
+    assert torch.allclose(comb[0].float(), src[0].float()) and torch.allclose(comb[1].float(), src[5].float())
+    assert index_error() is None  # cleared by the read

@@ -37,6 +37,7 @@ def test_fused_dp_matches_nccl_baseline(multimem):
     res = _launch(min(n, 2) if n < 4 else min(n, 4), {"TRIUNE_TEST_MULTIMEM": multimem})
     for r in res:
         assert r["status"] == 0
+        assert r["signals_consumed"]  # every channel's flags from every peer stand at the last epoch
         assert r["ranks_agree"]
         assert r["stats_agree"], r
         assert r["max_param_diff"] <= 2e-2 * max(1.0, r["param_scale"])

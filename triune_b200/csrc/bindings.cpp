@@ -350,7 +350,7 @@ Tensor gather_rows(const Tensor& src, const Tensor& row_src, const c10::optional
   Tensor dst = torch::empty({row_src.size(0), src.size(1)}, src.options());
   const bool has = row_scale.has_value() && row_scale->defined();
   tb::launch_gather_rows(bfm(dst), bf(src), row_src.data_ptr<int>(), has ? row_scale->data_ptr<float>() : nullptr,
-                         (int)row_src.size(0), (int)src.size(1), cur_stream());
+                         (int)row_src.size(0), (int)src.size(1), (int)src.size(0), cur_stream());
   return dst;
 }
 
@@ -366,8 +366,14 @@ Tensor combine_rows(const Tensor& src, const Tensor& pos, const c10::optional<Te
   if (hw) TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous(), "w must be fp32 contiguous");
   if (ha) TORCH_CHECK(add->is_contiguous(), "add must be contiguous");
   tb::launch_combine_rows(bfm(out), bf(src), pos.data_ptr<int>(), hw ? w->data_ptr<float>() : nullptr,
-                          ha ? bf(*add) : nullptr, (float)add_scale, tokens, k, width, cur_stream());
+                          ha ? bf(*add) : nullptr, (float)add_scale, tokens, k, width, (int)src.size(0), cur_stream());
   return out;
+}
+
+std::vector<int64_t> index_error_word(bool clear) {
+  int w[4];
+  tb::index_error_word(w, clear);
+  return {w[0], w[1], w[2], w[3]};
 }
 
 Tensor row_dots(const Tensor& a, const Tensor& b, const Tensor& pos) {
@@ -570,6 +576,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum);
   m.def("gather_rows", &gather_rows);
   m.def("combine_rows", &combine_rows);
+  m.def("index_error_word", &index_error_word, "first out-of-table index seen by the row-movement kernels: [kernel, row, index, limit]");
   m.def("row_dots", &row_dots);
   m.def("moe_route_topk", &moe_route_topk);
   m.def("moe_route_bwd", &moe_route_bwd);

@@ -49,10 +49,15 @@ void launch_embedding_bwd(const __nv_bfloat16* dy, long long ld, const long long
 
 // dst[r] = scale[r] * src[row_src[r]] (zero row when row_src[r] < 0). Rows of `width` bf16 (width % 8 == 0).
 void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,
-                        int dst_rows, int width, cudaStream_t s);
+                        int dst_rows, int width, int src_rows, cudaStream_t s);
 // out[t] = sum_j w[t,j] * src[pos[t,j]] (+ add_scale * add[t]); pos < 0 skips the term. w may be null (=1).
+// An index >= src_rows is skipped and recorded (see index_error_word), never followed.
 void launch_combine_rows(__nv_bfloat16* out, const __nv_bfloat16* src, const int* pos, const float* w,
-                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, cudaStream_t s);
+                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, int src_rows,
+                         cudaStream_t s);
+// {kernel id (1 gather_rows, 2 combine_rows; 0 = none), row, offending index, limit} of the first out-of-table index
+// seen since the last clear. Synchronises.
+void index_error_word(int out[4], bool clear);
 // dots[t,j] = <a[t], b[pos[t,j]]> (0 when pos < 0).
 void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b, const int* pos, int tokens, int k,
                      int width, cudaStream_t s);

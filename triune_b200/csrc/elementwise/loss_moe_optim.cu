@@ -139,12 +139,25 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* _
   }
 }
 
+// ---------------------------------------------------------------- index checks of the row-movement kernels
+// An index that leaves its table (a corrupted dispatch plan) is neither followed nor trapped on: the access is
+// skipped and the first offender is recorded here as {kernel id, row, index, limit}; the host reads it with
+// index_error_word() (a device-to-host copy, so only tests and debugging runs do).
+__device__ int g_index_error[4] = {0, 0, 0, 0};
+__device__ __forceinline__ void record_index_error(int kernel_id, int row, int index, int limit) {
+  if (atomicCAS(&g_index_error[0], 0, kernel_id) == 0) {
+    g_index_error[1] = row;
+    g_index_error[2] = index;
+    g_index_error[3] = limit;
+  }
+}
+
 // ---------------------------------------------------------------- MoE row movement
 __global__ void __launch_bounds__(256) gather_rows_kernel(__nv_bfloat16* __restrict__ dst,
                                                           const __nv_bfloat16* __restrict__ src,
                                                           const int* __restrict__ row_src,
                                                           const float* __restrict__ row_scale, int dst_rows,
-                                                          int width) {
+                                                          int width, int src_rows) {
   const int nvec = width >> 3;
   const long long total = (long long)dst_rows * nvec;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -152,7 +165,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(__nv_bfloat16* __restr
     const int r = (int)(i / nvec), v = (int)(i % nvec);
     const int s = row_src[r];
     uint4 o = make_uint4(0, 0, 0, 0);
-    if (s >= 0) {
+    if (s >= src_rows) {
+      if (v == 0) record_index_error(1, r, s, src_rows);
+    } else if (s >= 0) {
       o = reinterpret_cast<const uint4*>(src + (long long)s * width)[v];
       if (row_scale) {
         const float sc = row_scale[r];
@@ -172,7 +187,7 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(__nv_bfloat16* __rest
                                                            const __nv_bfloat16* __restrict__ src,
                                                            const int* __restrict__ pos, const float* __restrict__ w,
                                                            const __nv_bfloat16* __restrict__ add, float add_scale,
-                                                           int tokens, int k, int width) {
+                                                           int tokens, int k, int width, int src_rows) {
   const int nvec = width >> 3;
   const long long total = (long long)tokens * nvec;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -194,6 +209,10 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(__nv_bfloat16* __rest
     for (int j = 0; j < k; ++j) {
       const int p = pos[(long long)t * k + j];
       if (p < 0) continue;
+      if (p >= src_rows) {
+        if (v == 0) record_index_error(2, t, p, src_rows);
+        continue;
+      }
       const float wt = w ? w[(long long)t * k + j] : 1.f;
       uint4 x = reinterpret_cast<const uint4*>(src + (long long)p * width)[v];
       const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
@@ -528,17 +547,26 @@ void launch_ce_fwd_bwd(__nv_bfloat16* logits, long long ld, const long long* tar
 }
 
 void launch_gather_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, const int* row_src, const float* row_scale,
-                        int dst_rows, int width, cudaStream_t s) {
+                        int dst_rows, int width, int src_rows, cudaStream_t s) {
   if (dst_rows == 0) return;
   gather_rows_kernel<<<flat_grid((long long)dst_rows * (width >> 3)), 256, 0, s>>>(dst, src, row_src, row_scale,
-                                                                                    dst_rows, width);
+                                                                                    dst_rows, width, src_rows);
 }
 
 void launch_combine_rows(__nv_bfloat16* out, const __nv_bfloat16* src, const int* pos, const float* w,
-                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, cudaStream_t s) {
+                         const __nv_bfloat16* add, float add_scale, int tokens, int k, int width, int src_rows,
+                         cudaStream_t s) {
   if (tokens == 0) return;
   combine_rows_kernel<<<flat_grid((long long)tokens * (width >> 3)), 256, 0, s>>>(out, src, pos, w, add, add_scale,
-                                                                                   tokens, k, width);
+                                                                                   tokens, k, width, src_rows);
+}
+
+void index_error_word(int out[4], bool clear) {
+  cudaMemcpyFromSymbol(out, g_index_error, sizeof(int) * 4);
+  if (clear) {
+    const int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_index_error, zero, sizeof(zero));
+  }
 }
 
 void launch_row_dots(float* dots, const __nv_bfloat16* a, const __nv_bfloat16* b, const int* pos, int tokens, int k,

@@ -20,7 +20,7 @@ and flat for the AdamW tier. Reference baseline: DDP all-reduce + full update on
 
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 import torch.distributed as dist
@@ -160,6 +160,13 @@ class FusedDPUpdater:
         ops._tick()
         mark("broadcast_barrier")
         self.steps += 1
+
+    def audit(self) -> Dict[int, bool]:
+        """Every step channel's flags from every peer stand at the device-resident epoch: no signal is outstanding and no
+        rank is a step ahead or behind. Synchronises."""
+        ep = int(self.epoch_dev.item())
+        chans = {0: ep, 1: ep, CH_PARAMS_DONE: ep}
+        return self.buf.audit_signals(chans)
 
     def check(self) -> int:
         """Status word of the bounded waits (0 = every wait completed). Synchronises."""

@@ -67,3 +67,18 @@ class SymmetricBuffer:
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch
+
+    # ------------------------------------------------------------------ protocol audit
+    def signal_slots(self, max_ranks: int = 16) -> torch.Tensor:
+        """This rank's signal pad as int32 [channels, max_ranks] (slot = channel * max_ranks + source rank)."""
+        pad = self.handle.get_signal_pad(self.rank, dtype=torch.int32)
+        n = pad.numel() // max_ranks * max_ranks
+        return pad.reshape(-1)[:n].view(-1, max_ranks)
+
+    def audit_signals(self, expected: Dict[int, int], max_ranks: int = 16) -> Dict[int, bool]:
+        """After a run: for each channel, did EVERY peer's last signal arrive with the epoch the protocol ended on?
+        ``expected`` maps channel -> final epoch. A slot behind its epoch is a signal that was never sent (or a step one
+        rank skipped); a slot ahead of it is a rank that ran an extra step. Synchronises."""
+        torch.cuda.synchronize(self.tensor.device)
+        slots = self.signal_slots(max_ranks).cpu()
+        return {int(ch): bool((slots[int(ch), : self.world] == int(ep)).all()) for ch, ep in expected.items()}
