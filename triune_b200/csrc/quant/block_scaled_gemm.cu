@@ -334,40 +334,58 @@ __device__ __forceinline__ void fwht16_rot(float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
 }
 
+// One CTA pass covers ONE 512-byte scale block: 128 rows x 4 scale groups (64 elements of K). Thread pair (row, group)
+// = (item / 4, item % 4): four neighbouring threads read 128 contiguous bytes of a row and write 32 contiguous bytes of
+// codes; the block's scales are collected in shared memory in the blocked order and leave as one coalesced 512-byte
+// store (written byte by byte from the threads they would be 4-byte fragments of 32-byte sectors).
 __global__ void __launch_bounds__(256) nvfp4_quantize_act_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M,
                                                                  int K, int sf_kblocks, int hadamard,
                                                                  uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
-  const int kb16 = K >> 4;
-  const long long total = (long long)M * kb16;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / kb16), b = (int)(i % kb16);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ld + b * 16);
-    const uint4 u0 = src[0], u1 = src[1];
-    float v[16];
-    const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
-    const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
+  __shared__ __align__(16) uint8_t s_sf[512];
+  const int rb = blockIdx.x;
+  const int groups = K >> 4;          // scale groups per row
+  const int kblocks = (groups + 3) >> 2;
+  for (int kb = blockIdx.y; kb < kblocks; kb += gridDim.y) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f0 = __bfloat1622float2(p0[j]), f1 = __bfloat1622float2(p1[j]);
-      v[2 * j] = f0.x; v[2 * j + 1] = f0.y;
-      v[8 + 2 * j] = f1.x; v[8 + 2 * j + 1] = f1.y;
+    for (int h = 0; h < 2; ++h) {
+      const int item = threadIdx.x + h * 256;
+      const int ri = item >> 2, g = item & 3;
+      const int r = rb * 128 + ri, b = kb * 4 + g;
+      uint8_t scb = 0;
+      if (r < M && b < groups) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ld + b * 16);
+        const uint4 u0 = src[0], u1 = src[1];
+        float v[16];
+        const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
+        const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f0 = __bfloat1622float2(p0[j]), f1 = __bfloat1622float2(p1[j]);
+          v[2 * j] = f0.x; v[2 * j + 1] = f0.y;
+          v[8 + 2 * j] = f1.x; v[8 + 2 * j + 1] = f1.y;
+        }
+        if (hadamard) fwht16_rot(v);
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        // scale = amax / 6 rounded to E4M3 (at least the smallest subnormal, so a block of zeros keeps a finite scale)
+        const __nv_fp8_storage_t sc = __nv_cvt_float_to_fp8(fminf(fmaxf(amax * (1.0f / 6.0f), 0.001953125f), 448.0f), __NV_SATFINITE, __NV_E4M3);
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(sc, __NV_E4M3);
+        const float inv = 1.0f / __half2float(*reinterpret_cast<const __half*>(&hr));
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) lo |= e2m1_code_f(v[j] * inv) << (4 * j);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hi |= e2m1_code_f(v[8 + j] * inv) << (4 * j);
+        *reinterpret_cast<uint2*>(packed + (long long)r * (K >> 1) + b * 8) = make_uint2(lo, hi);
+        scb = (uint8_t)sc;
+      }
+      s_sf[(ri & 31) * 16 + (ri >> 5) * 4 + g] = scb;
     }
-    if (hadamard) fwht16_rot(v);
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    // scale = amax / 6 rounded to E4M3 (at least the smallest subnormal, so a block of zeros keeps a finite scale)
-    const __nv_fp8_storage_t sc = __nv_cvt_float_to_fp8(fminf(fmaxf(amax * (1.0f / 6.0f), 0.001953125f), 448.0f), __NV_SATFINITE, __NV_E4M3);
-    const __half_raw hr = __nv_cvt_fp8_to_halfraw(sc, __NV_E4M3);
-    const float inv = 1.0f / __half2float(*reinterpret_cast<const __half*>(&hr));
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) lo |= e2m1_code_f(v[j] * inv) << (4 * j);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) hi |= e2m1_code_f(v[8 + j] * inv) << (4 * j);
-    *reinterpret_cast<uint2*>(packed + (long long)r * (K >> 1) + b * 8) = make_uint2(lo, hi);
-    const int rb = r >> 7, ri = r & 127;
-    sf[((long long)rb * sf_kblocks + (b >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (b & 3)] = (uint8_t)sc;
+    __syncthreads();
+    if (threadIdx.x < 32)
+      reinterpret_cast<uint4*>(sf + ((long long)rb * sf_kblocks + kb) * 512)[threadIdx.x] = reinterpret_cast<const uint4*>(s_sf)[threadIdx.x];
+    __syncthreads();
   }
 }
 
@@ -388,47 +406,62 @@ __global__ void __launch_bounds__(256) nvfp4_block_scales_kernel(const uint8_t* 
 // power-of-two scale costs no relative precision against amax / 448.
 __global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int R, int K,
                                                              int sf_kblocks, uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
-  const int kb32 = K >> 5;
-  const long long total = (long long)R * kb32;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / kb32), b = (int)(i % kb32);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ld + b * 32);
-    uint4 u[4];
+  // same tiling as the NVFP4 quantiser: one pass = one 512-byte scale block = 128 rows x 4 groups of 32 elements
+  __shared__ __align__(16) uint8_t s_sf[512];
+  const int rb = blockIdx.x;
+  const int groups = K >> 5;
+  const int kblocks = (groups + 3) >> 2;
+  for (int kb = blockIdx.y; kb < kblocks; kb += gridDim.y) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) u[j] = src[j];
-    float v[32];
-    float amax = 0.f;
+    for (int h = 0; h < 2; ++h) {
+      const int item = threadIdx.x + h * 256;
+      const int ri = item >> 2, g = item & 3;
+      const int r = rb * 128 + ri, b = kb * 4 + g;
+      uint8_t scb = 0;
+      if (r < R && b < groups) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ld + b * 32);
+        uint4 u[4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float2 f = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(u)[j]);
-      v[2 * j] = f.x;
-      v[2 * j + 1] = f.y;
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        for (int j = 0; j < 4; ++j) u[j] = src[j];
+        float v[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 f = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(u)[j]);
+          v[2 * j] = f.x;
+          v[2 * j + 1] = f.y;
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+        // e = ceil(log2(amax / 448)) in integer arithmetic: amax = m * 2^ea with m in [1, 2) and 448 = 1.75 * 2^8, so
+        // amax <= 448 * 2^e  <=>  e >= ea - 8 + (m > 1.75)
+        int e = -127;
+        if (amax > 0.f) {
+          const uint32_t bits = __float_as_uint(amax);
+          e = (int)((bits >> 23) & 0xFF) - 127 - 8 + ((bits & 0x7FFFFF) > 0x600000 ? 1 : 0);
+          e = e < -127 ? -127 : (e > 127 ? 127 : e);
+        }
+        // 2^-e: the exponent field 127 - e is a normal number for e in [-127, 126]; e = 127 needs the denormal 2^-127
+        const float mul = e == 127 ? 5.877471754111438e-39f : __uint_as_float((uint32_t)(127 - e) << 23);
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t pk = 0;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            pk |= (uint32_t)__nv_cvt_float_to_fp8(v[4 * j + c] * mul, __NV_SATFINITE, __NV_E4M3) << (8 * c);
+          w[j] = pk;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(q + (long long)r * K + b * 32);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        scb = (uint8_t)(e + 127);
+      }
+      s_sf[(ri & 31) * 16 + (ri >> 5) * 4 + g] = scb;
     }
-    // e = ceil(log2(amax / 448)) in integer arithmetic: amax = m * 2^ea with m in [1, 2) and 448 = 1.75 * 2^8, so
-    // amax <= 448 * 2^e  <=>  e >= ea - 8 + (m > 1.75)
-    int e = -127;
-    if (amax > 0.f) {
-      const uint32_t bits = __float_as_uint(amax);
-      e = (int)((bits >> 23) & 0xFF) - 127 - 8 + ((bits & 0x7FFFFF) > 0x600000 ? 1 : 0);
-      e = e < -127 ? -127 : (e > 127 ? 127 : e);
-    }
-    const float inv = __uint_as_float((uint32_t)(127 - e) << 23);  // 2^-e (e in [-127, 127]: 2^127 ... 2^-127 denormal-safe below)
-    const float mul = e == 127 ? 5.877471754111438e-39f : (e == -127 ? 1.7014118346046923e38f : inv);
-    uint32_t w[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      uint32_t pk = 0;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        pk |= (uint32_t)__nv_cvt_float_to_fp8(v[4 * j + c] * mul, __NV_SATFINITE, __NV_E4M3) << (8 * c);
-      w[j] = pk;
-    }
-    uint4* dst = reinterpret_cast<uint4*>(q + (long long)r * K + b * 32);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    const int rb = r >> 7, ri = r & 127;
-    sf[((long long)rb * sf_kblocks + (b >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (b & 3)] = (uint8_t)(e + 127);
+    __syncthreads();
+    if (threadIdx.x < 32)
+      reinterpret_cast<uint4*>(sf + ((long long)rb * sf_kblocks + kb) * 512)[threadIdx.x] = reinterpret_cast<const uint4*>(s_sf)[threadIdx.x];
+    __syncthreads();
   }
 }
 
@@ -445,13 +478,19 @@ int sm_count_f() {
 
 }  // namespace
 
+// grid: one CTA row per 128 rows, and as many CTAs along K as fill the GPU a few times over (each loops over k blocks)
+static dim3 quant_grid(int rows, int kblocks) {
+  const int rbs = (rows + 127) / 128;
+  int ky = (148 * 8 + rbs - 1) / rbs;
+  ky = ky < 1 ? 1 : (ky > kblocks ? kblocks : ky);
+  return dim3((unsigned)rbs, (unsigned)ky, 1);
+}
+
 void launch_nvfp4_quantize_act(const __nv_bfloat16* x, long long ld, int M, int K, bool hadamard, uint8_t* packed,
                                uint8_t* sf_blocked, cudaStream_t s) {
   if (M <= 0) return;
-  const long long total = (long long)M * (K >> 4);
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148ll * 16) blocks = 148ll * 16;
-  nvfp4_quantize_act_kernel<<<(int)blocks, 256, 0, s>>>(x, ld, M, K, nvfp4_sf_kblocks(K), hadamard ? 1 : 0, packed, sf_blocked);
+  const int kblocks = ((K >> 4) + 3) / 4;
+  nvfp4_quantize_act_kernel<<<quant_grid(M, kblocks), 256, 0, s>>>(x, ld, M, K, nvfp4_sf_kblocks(K), hadamard ? 1 : 0, packed, sf_blocked);
 }
 
 void launch_nvfp4_block_scales(const uint8_t* scales, int R, int K, uint8_t* out, cudaStream_t s) {
@@ -525,10 +564,8 @@ void launch_nvfp4_gemm(const uint8_t* a_packed, const uint8_t* sfa, const uint8_
 void launch_mxfp8_quantize(const __nv_bfloat16* x, long long ld, int R, int K, uint8_t* q, uint8_t* sf_blocked, cudaStream_t s) {
   if (R <= 0) return;
   if (K % 32 != 0) throw std::runtime_error("mxfp8_quantize: K must be a multiple of 32");
-  const long long total = (long long)R * (K >> 5);
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148ll * 16) blocks = 148ll * 16;
-  mxfp8_quantize_kernel<<<(int)blocks, 256, 0, s>>>(x, ld, R, K, mxfp8_sf_kblocks(K), q, sf_blocked);
+  const int kblocks = ((K >> 5) + 3) / 4;
+  mxfp8_quantize_kernel<<<quant_grid(R, kblocks), 256, 0, s>>>(x, ld, R, K, mxfp8_sf_kblocks(K), q, sf_blocked);
 }
 
 void launch_mxfp8_gemm(const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, __nv_bfloat16* C, int M,
