@@ -267,9 +267,11 @@ class EPMoE_FFN(nn.Module):
         lo, hi = ep.rank * ep.experts_per_rank, (ep.rank + 1) * ep.experts_per_rank
         self.router, self.shared = moe.router, moe.shared
         self.register_buffer("expert_bias", moe.expert_bias.detach().clone())
-        for name in ("expert_load_ratio", "last_centroids", "_global_step"):  # carried for checkpoints of the full layer
-            if hasattr(moe, name):
-                self.register_buffer(name, getattr(moe, name).detach().clone())
+        # statistics of the full layer, carried only so that a merged checkpoint has every key of the unsharded layer;
+        # kept under other attribute names because the optimizer's steering tier reads `last_centroids` of the module
+        # that owns the experts, and these are neither sliced to the local experts nor updated here
+        self._carried = {name: getattr(moe, name).detach().clone() for name in ("expert_load_ratio", "last_centroids", "_global_step")
+                         if hasattr(moe, name)}
         for name in ("w1", "b1", "w2", "b2"):
             setattr(self, name, nn.Parameter(getattr(moe, name).detach()[lo:hi].clone()))
         self._pending_bias_update = None
@@ -299,8 +301,11 @@ class EPMoE_FFN(nn.Module):
             yield (f"{prefix}experts.{lo + e}.2.bias", None, 0, 0, 0, self.b2[e])
 
     def checkpoint_replicated(self, prefix: str):
-        out = {f"{prefix}{n}": getattr(self, n) for n in ("expert_bias", "expert_load_ratio", "last_centroids", "_global_step")
-               if hasattr(self, n)}
+        out = {f"{prefix}expert_bias": self.expert_bias}
+        for n, t in self._carried.items():
+            if t.device != self.expert_bias.device:
+                t = self._carried[n] = t.to(self.expert_bias.device)
+            out[f"{prefix}{n}"] = t
         for k, v in self.router.state_dict().items():
             out[f"{prefix}router.{k}"] = v
         if self.shared is not None:
