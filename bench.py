@@ -54,8 +54,33 @@ class ClockSampler:
         self.idx = gpu_index
         self.proc = None
         self.lines = []
+        self._nvml = None      # (module, handle) when the NVML binding is importable: 20 ms sampling from a thread
+        self._samples = []
+        self._stop = threading.Event()
+
+    def _nvml_loop(self):
+        nv, h = self._nvml
+        while not self._stop.is_set():
+            try:
+                self._samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                      int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))))
+            except Exception:
+                break
+            self._stop.wait(0.02)
 
     def start(self):
+        try:  # read-only NVML queries; a short timed region still gets several samples
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.idx)
+            self._max = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self._nvml = (nv, h)
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self._nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
@@ -70,6 +95,16 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self._nvml is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            sm = [c for c, _ in self._samples]
+            bits = 0
+            for _, r in self._samples:
+                bits |= r
+            names = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self._max), "sm_min_mhz": min(sm) if sm else None,
+                    "reasons": sorted(n for n, b in names if bits & b), "samples": len(sm), "source": "nvml, 20 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
         self.proc.terminate()
