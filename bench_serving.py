@@ -111,6 +111,30 @@ def run_ours(a):
                 dt = time.perf_counter() - t0
                 emit(metric=name + " tok/s", impl="triune_b200", value=(out.shape[1] - prompt.shape[1]) / dt, unit="tok/s",
                      new_tokens=int(out.shape[1] - prompt.shape[1]), acceptance_rate=round(gen.acceptance_rate, 3) if "spec" in name else None)
+            # the same scheme with a whole round (k drafts, one batched verification, commit) replayed as ONE CUDA graph
+            from triune_b200.inference import GraphedSpeculativeDecoder
+
+            def spec_run(tag):
+                dec = GraphedSpeculativeDecoder(model, k_draft=a.k_draft)
+                dec.generate(prompt, a.new_tokens)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                out = dec.generate(prompt, a.new_tokens)
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                emit(metric=f"decode (self-speculative, greedy, one CUDA graph per round{tag}) tok/s", impl="triune_b200",
+                     value=(out.shape[1] - prompt.shape[1]) / dt, unit="tok/s", new_tokens=int(out.shape[1] - prompt.shape[1]),
+                     acceptance_rate=round(dec.acceptance_rate, 3), k_draft=a.k_draft,
+                     matches_greedy=bool(torch.equal(out, graphed.generate(prompt, a.new_tokens))))
+
+            spec_run("")
+            # random-init exits never agree with the full depth; a short KL distillation of the exit heads toward the
+            # full-depth predictions (the model's own `distill_exit_heads`) gives the drafts something to agree on
+            calib = torch.randint(0, VOCAB, (32, 128), device=dev, generator=torch.Generator(device=dev).manual_seed(7))
+            calib[0] = prompt[0]
+            rep = model.distill_exit_heads(calib, steps=200, lr=3e-3, batch_size=8)
+            model.eval()
+            spec_run(f", exit heads distilled {rep['steps']} steps")
         del model
         torch.cuda.empty_cache()
 

@@ -772,3 +772,37 @@ def test_checkpoint_loader_refuses_pickled_code(tmp_path):
     with pytest.raises(Exception) as e:
         ckpt.load_checkpoint(str(path))
     assert isinstance(e.value, (pickle.UnpicklingError, RuntimeError))
+
+
+def test_graphed_speculative_decoder_equals_greedy_and_accepts_agreeing_drafts():
+    """The device-resident speculative round (drafts by the Reflex exit, one batched verification with per-token
+    recurrent states, acceptance count as a device index) reproduces plain full-depth greedy decoding token for token:
+    with random weights (drafts mostly rejected) and with a model whose early exit agrees with the full depth (every
+    draft accepted, k + 1 tokens per round)."""
+    from triune_b200.inference import GraphedGreedyDecoder, GraphedSpeculativeDecoder
+
+    m = tiny().eval()
+    prompt = torch.randint(0, 256, (1, 9), generator=torch.Generator().manual_seed(4))
+    want = GraphedGreedyDecoder(m, batch_size=1, decode_depth=2).generate(prompt, 24)
+    spec = GraphedSpeculativeDecoder(m, k_draft=3)
+    got = spec.generate(prompt, 24)
+    assert torch.equal(got, want)
+    low = spec.acceptance_rate
+    # make the layers after the Reflex exit the identity and give the Reflex exit the final head: drafts always agree
+    with torch.no_grad():
+        r = m.exit_layers[0]
+        for blk in m.layers[r + 1 :]:
+            blk.attn.gla.out_proj.weight.zero_()
+            for p in blk.ffn.parameters():
+                p.zero_()
+        ex = m.layers[r]
+        ex.exit_norm.load_state_dict(m.final_norm.state_dict())
+        ex.exit_head.weight.copy_(m.final_head.weight)
+        if ex.exit_head.bias is not None:
+            ex.exit_head.bias.zero_() if m.final_head.bias is None else ex.exit_head.bias.copy_(m.final_head.bias)
+    want2 = GraphedGreedyDecoder(m, batch_size=1, decode_depth=2).generate(prompt, 24)
+    spec2 = GraphedSpeculativeDecoder(m, k_draft=3)
+    got2 = spec2.generate(prompt, 24)
+    assert torch.equal(got2, want2)
+    assert spec2.acceptance_rate == 1.0 and spec2.acceptance_rate >= low
+    assert int(spec2.rounds.item()) <= 8  # 23 tokens at 4 per round, checked every 8 rounds

@@ -328,3 +328,167 @@ class GraphedGreedyDecoder:
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
         self.prefill(input_ids)
         return torch.cat((input_ids, self.decode(max_new_tokens)), dim=1)
+
+
+class GraphedSpeculativeDecoder:
+    """Greedy self-speculative decoding with one whole ROUND captured in a CUDA graph: the Reflex exit drafts ``k``
+    tokens (k single-token steps through the first layers), the full depth verifies all of them plus the current token in
+    ONE batched pass, and the longest agreeing prefix plus one corrected token are committed, all without a host
+    synchronisation. The output equals plain greedy decoding at full depth token for token.
+
+    Parity: ``SelfSpeculativeGenerator`` (``triune/model/speculative.py:45-280`` of the reference), which runs the same
+    scheme from Python with cloned caches. What differs here: the acceptance count stays on the device (an index into
+    the per-token states the mixers return, see ``VectorisedGLA.forward_token_states``), every candidate token of a round
+    is written to the output buffer and the write position advances by the accepted count, so a round has the same
+    launches whatever it accepts and can be replayed. Batch size 1, recurrent (GLA / Gated DeltaNet) mixers.
+    """
+
+    def __init__(self, model, k_draft: int = 3, max_positions: int = 32768):
+        self.model, self.k = model, int(k_draft)
+        self.device = next(model.parameters()).device
+        self.max_positions = max_positions
+        self.draft_depth = 0
+        self.n_draft_layers = model.exit_layers[0] + 1
+        self.n_layers = model.exit_layers[2] + 1
+        for blk in model.layers[: self.n_layers]:
+            if getattr(blk.attn, "gla", None) is None:
+                raise NotImplementedError("graphed speculative decoding covers the recurrent mixers")
+        dev = self.device
+        self.states: List[torch.Tensor] = []
+        self.draft_states: List[torch.Tensor] = []
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.draft_pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.token = torch.zeros(1, 1, dtype=torch.long, device=dev)
+        self.step_idx = torch.zeros(1, dtype=torch.long, device=dev)
+        self.cand = torch.zeros(1, self.k + 1, dtype=torch.long, device=dev)   # [current token, drafts]
+        self.accepted = torch.zeros(1, dtype=torch.long, device=dev)           # drafted tokens accepted, all rounds
+        self.rounds = torch.zeros(1, dtype=torch.long, device=dev)
+        self.out: Optional[torch.Tensor] = None
+        self.graph = None
+        self._ar = torch.arange(self.k + 1, device=dev)
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, prefill_chunk: int = 4096) -> torch.Tensor:
+        m = self.model
+        m.eval()
+        assert input_ids.shape[0] == 1, "speculative decoding runs one sequence"
+        cache = m.init_cache(1)
+        logits = None
+        for s in range(0, input_ids.shape[1], prefill_chunk):
+            logits, cache = m(input_ids[:, s : s + prefill_chunk], force_depth=2, cache=cache, last_token_only=True)
+        for mod in m.modules():
+            if hasattr(mod, "_build") and hasattr(mod, "head_dim") and hasattr(mod, "_cos"):
+                mod(1, self.device, offset=min(self.max_positions, max(mod.max_seq_len, input_ids.shape[1] + 1)) - 1)
+        new_states = [c[0] for c in cache[: self.n_layers]]
+        if len(self.states) == len(new_states):
+            for a, b in zip(self.states, new_states):
+                a.copy_(b)
+        else:
+            self.states = [s.clone() for s in new_states]
+            self.draft_states = [s.clone() for s in new_states[: self.n_draft_layers]]
+            self.graph = None
+        self.pos.fill_(input_ids.shape[1])
+        self.token.copy_(logits[:, -1].argmax(-1, keepdim=True))
+        self.accepted.zero_()
+        self.rounds.zero_()
+        return self.token.clone()
+
+    # ------------------------------------------------------------------ one round
+    def _draft(self):
+        m = self.model
+        for a, b in zip(self.draft_states, self.states):
+            a.copy_(b)
+        self.draft_pos.copy_(self.pos)
+        self.cand[:, 0:1].copy_(self.token)
+        for i in range(self.k):
+            cache = [(s, self.draft_pos) for s in self.draft_states] + [(None, self.draft_pos)] * (len(m.layers) - self.n_draft_layers)
+            logits, new_cache = m(self.cand[:, i : i + 1], force_depth=self.draft_depth, cache=cache, last_token_only=True)
+            for s, c in zip(self.draft_states, new_cache):
+                s.copy_(c[0])
+            self.cand[:, i + 1 : i + 2].copy_(logits[:, -1].argmax(-1, keepdim=True))
+            self.draft_pos.add_(1)
+
+    def _verify(self):
+        """All k + 1 candidate tokens through the full depth in one pass -> (greedy targets [1, k+1], per-layer states
+        after each token)."""
+        from . import ops
+
+        m = self.model
+        x = ops.embedding(self.cand, m.token_embed.weight)
+        per_layer = []
+        for i in range(self.n_layers):
+            blk = m.layers[i]
+            y, sts = blk.attn.gla.forward_token_states(blk.norm1(x), self.states[i], self.pos)
+            n2, x = blk.norm2.forward_add(y, x)
+            x = x + blk._ffn(n2, False)
+            per_layer.append(sts)
+        logits = m._head(x, 2, False)
+        return logits.argmax(-1), per_layer
+
+    def _round(self):
+        self._draft()
+        targets, per_layer = self._verify()                       # targets[:, i] follows cand[:, i]
+        k = self.k
+        agree = (self.cand[:, 1:] == targets[:, :k]).to(torch.long)
+        n = torch.cumprod(agree, dim=1).sum(dim=1)                # [1]: drafted tokens accepted
+        # every candidate output of the round goes to the buffer; only n + 1 of them are kept by the index advance
+        idx = (self.step_idx + self._ar).clamp_(max=self.out.shape[1] - 1)
+        self.out.index_copy_(1, idx, targets)
+        for s, sts in zip(self.states, per_layer):
+            s.copy_(sts.index_select(0, n).squeeze(0))             # state after the last accepted token
+        self.token.copy_(targets.gather(1, n.view(1, 1)))
+        self.pos.add_(n + 1)
+        self.step_idx.add_(n + 1)
+        self.accepted.add_(n)
+        self.rounds.add_(1)
+
+    # ------------------------------------------------------------------ decoding
+    @torch.no_grad()
+    def decode(self, max_new_tokens: int, rounds_per_check: int = 8) -> torch.Tensor:
+        """-> [1, max_new_tokens]; the first token is the one ``prefill`` returned."""
+        need = max_new_tokens + self.k + 2
+        if self.out is None or self.out.shape[1] < need:
+            self.out = torch.zeros(1, need, dtype=torch.long, device=self.device)
+            self.graph = None
+        self.step_idx.fill_(1)
+        self.out[:, 0:1].copy_(self.token)
+        cuda = self.device.type == "cuda"
+        if cuda and self.graph is None:
+            snap = ([s.clone() for s in self.states], self.pos.clone(), self.token.clone(), self.out.clone())
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._round()
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._round()
+            self.graph = g
+            for s, b in zip(self.states, snap[0]):
+                s.copy_(b)
+            self.pos.copy_(snap[1])
+            self.token.copy_(snap[2])
+            self.out.copy_(snap[3])
+            self.step_idx.fill_(1)
+            self.accepted.zero_()
+            self.rounds.zero_()
+        while True:
+            for _ in range(rounds_per_check):
+                if cuda:
+                    self.graph.replay()
+                else:
+                    self._round()
+            if int(self.step_idx.item()) >= max_new_tokens:  # one host read per `rounds_per_check` rounds
+                break
+        return self.out[:, :max_new_tokens].clone()
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        self.prefill(input_ids)
+        return torch.cat((input_ids, self.decode(max_new_tokens)), dim=1)
+
+    @property
+    def acceptance_rate(self) -> float:
+        r = int(self.rounds.item())
+        return float(self.accepted.item()) / max(1, r * self.k)

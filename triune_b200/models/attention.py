@@ -170,6 +170,37 @@ class VectorisedGLA(nn.Module):
         return y, format_cache(new_state if cache is not None else None, cache, fmt, offset, T)
 
 
+    def forward_token_states(self, x: torch.Tensor, state, offset):
+        """``x`` [B, T, dim] with T small -> (y [B, T, dim], states [T, B, H, D, D]): the mixer output of every token and
+        the recurrent state AFTER every token. Speculative verification runs all drafted tokens in one batched pass
+        (one projection GEMM in, one out) and then keeps the state of the last ACCEPTED token; a recurrent state cannot
+        be rolled back, so the per-token states are what replaces truncating a KV cache."""
+        B, T, _ = x.shape
+        H, D = self.heads, self.head_dim
+        x2 = x.reshape(B * T, self.dim)
+        qkvg = ops.linear(x2, self.qkvg_weight)
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self.rope(T, x.device, offset=offset)
+        q, k, v, g = ops.qk_feature_map(qkvg, cos, sin, B, T, H, D)
+        beta = None
+        if self.use_delta_rule and self.beta_proj is not None:
+            beta = torch.sigmoid(self.beta_proj(x)).view(B, T, H)
+        outs, states, s = [], [], state
+        for j in range(T):
+            sl = slice(j, j + 1)
+            if self.use_delta_rule:
+                o, s = ops.gated_deltanet(q[:, sl], k[:, sl], v[:, sl], g[:, sl], beta=None if beta is None else beta[:, sl],
+                                          initial_state=s, gate_logits=True)
+            else:
+                o, s = ops.gla(q[:, sl], k[:, sl], v[:, sl], g[:, sl], initial_state=s, gate_logits=True)
+            outs.append(o)
+            states.append(s)
+        out = torch.cat(outs, dim=1).reshape(B, T, self.hidden_dim).to(x.dtype)
+        y = _project(self.out_proj, out, 1.0 if self.use_delta_rule else self.out_scale)
+        return y, torch.stack(states)
+
+
 class SoftmaxAttention(nn.Module):
     """Causal softmax attention with RoPE, GQA and a KV cache (library SDPA; not on a named hot path).
 
