@@ -61,9 +61,15 @@ def plan(gpus: int, quick: bool) -> List[Tuple[str, int, int, List[str]]]:
         p.append(("E", n, 900, torchrun(n, 29500 + n, "bench.py", "--gpus", str(n), "--steps", steps, "--warmup", warm)))
     p += [
         ("E", 8, 1800, torchrun(8, 29540, "bench_ep.py", "--steps", "5", "--warmup", "3")),
+        ("E", 8, 900, torchrun(8, 29541, "bench_dp.py", "--params", "1.5e9", "--iters", "5")),
+        ("E", 8, 900, torchrun(8, 29542, "bench_dp.py", "--params", "1.5e9", "--iters", "5", "--mode", "nccl")),
+        ("E", 8, 1200, torchrun(8, 29543, "bench_serving.py", "--new-tokens", "0", "--layout", "replicas")),
+        ("E", 8, 1200, torchrun(8, 29544, "bench_serving.py", "--new-tokens", "0", "--layout", "ep")),
         ("E", 2, 1800, torchrun(2, 29560, "bench_tp.py", "--steps", "5", "--warmup", "3")),
         ("E", 2, 1800, torchrun(2, 29561, "bench_tp.py", "--steps", "5", "--warmup", "3", "--mixer", "gla")),
-        ("E", 8, 1800, torchrun(8, 29562, "bench_tp.py", "--tp", "2", "--steps", "5", "--warmup", "3", "--mixer", "gla")),
+        ("E", 8, 1800, torchrun(8, 29562, "bench_tp.py", "--tp", "2", "--batch", "4", "--seq", "8192", "--steps", "3", "--warmup", "2")),
+        ("E", 8, 1800, torchrun(8, 29563, "bench_tp.py", "--tp", "2", "--batch", "4", "--seq", "8192", "--steps", "3", "--warmup", "2",
+                                "--tp-mode", "nccl", "--dp-mode", "nccl")),
         ("E", 4, 1800, torchrun(4, 29570, "bench_pp.py", "--steps", "5", "--warmup", "3")),
         ("F", 1, 1800, [PY, os.path.join(ROOT, "bench_streaming.py")]),
         ("F", 1, 1800, [PY, os.path.join(ROOT, "bench_streaming.py"), "--shape", "1536", "13", "--vocab", "4096", "--batch", "2",
