@@ -185,6 +185,31 @@ def test_fp8_module_takes_the_block_scaled_path():
     assert cos(y_mx.flatten(), want.flatten(), dim=0) >= cos(y_blk.flatten(), want.flatten(), dim=0) - 1e-3  # finer scales
 
 
+def test_block_scaled_gemm_bias_and_gelu_epilogues():
+    """Bias and tanh-GELU inside the block-scaled GEMM epilogues == the same applied to the plain GEMM's output."""
+    from triune_b200.models.quant_linear import FP8Linear, NVFP4Linear
+
+    torch.manual_seed(11)
+    lin = torch.nn.Linear(512, 384, bias=True).cuda().bfloat16()
+    with torch.no_grad():
+        lin.bias.mul_(20.0)  # a bias large enough to matter
+    x = torch.randn(300, 512, device="cuda").bfloat16()
+    for mod in (FP8Linear.from_linear(lin).eval(), NVFP4Linear.from_linear(lin)):
+        with torch.no_grad():
+            plain = mod(x).float()
+            fused = mod(x, gelu=True).float()
+            mod_nobias = type(mod).from_linear(torch.nn.Linear(512, 384, bias=False).cuda().bfloat16())
+        want = torch.nn.functional.gelu(plain, approximate="tanh")
+        assert (fused - want).abs().max() <= 2e-2 * want.abs().max().clamp_min(1.0), type(mod).__name__
+        assert int(quant_cuda.last_gemm_status.item()) == 0
+        # the bias really is in: remove it and the outputs move by the bias
+        if isinstance(mod, FP8Linear):
+            mod_nobias.weight.data.copy_(lin.weight)
+            with torch.no_grad():
+                nb = mod_nobias.eval()(x).float()
+            assert (plain - nb - lin.bias.float()).abs().max() <= 3e-2 * plain.abs().max()
+
+
 def test_fwht16_kernel():
     x = torch.randn(64, 128, device="cuda").bfloat16()
     y = quant_cuda.fwht16(x)

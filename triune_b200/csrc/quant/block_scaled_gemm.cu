@@ -119,7 +119,7 @@ __device__ __forceinline__ void umma_mxfp8(uint32_t tmem_d, uint64_t adesc, uint
       : "memory");
 }
 
-template <int BN, bool FP8>
+template <int BN, bool FP8, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     block_scaled_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                              const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa,
@@ -288,8 +288,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
-      epilogue_tile<EPI_PLAIN>(p, tl, &tmC, &tmC, tmem_base + acc * BN, BN, n_idx * BN, tl.m0, lane_base, col_half, lane,
-                               my_stage, buf);
+      epilogue_tile<EPI>(p, tl, &tmC, &tmC, tmem_base + acc * BN, BN, n_idx * BN, tl.m0, lane_base, col_half, lane, my_stage, buf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -312,6 +311,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 // Activation quantiser: x bf16 [M, K] -> packed E2M1 [M, K / 2] and unsigned E4M3 block scales in the blocked layout
 // the GEMM loads. One thread per 16 elements; `hadamard` applies the 16-point Walsh-Hadamard rotation first (weights
 // quantised with the same rotation then see x H (W H)^T = x W^T).
+// Two floats -> one byte of E2M1 codes (round to nearest even, saturating), `lo` in the low nibble.
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+  uint32_t r;
+  asm("{\n\t"
+      ".reg .b8 t;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\t"
+      "cvt.u32.u8 %0, t;\n\t"
+      "}" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ uint32_t e2m1_code_f(float x) {
   // nearest representable magnitude of {0, .5, 1, 1.5, 2, 3, 4, 6}, ties to the even code
   const float a = fabsf(x);
@@ -374,9 +383,9 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_act_kernel(const __nv_bflo
         const float inv = 1.0f / __half2float(*reinterpret_cast<const __half*>(&hr));
         uint32_t lo = 0, hi = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) lo |= e2m1_code_f(v[j] * inv) << (4 * j);
+        for (int j = 0; j < 4; ++j) lo |= e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) hi |= e2m1_code_f(v[8 + j] * inv) << (4 * j);
+        for (int j = 0; j < 4; ++j) hi |= e2m1x2(v[8 + 2 * j] * inv, v[9 + 2 * j] * inv) << (8 * j);
         *reinterpret_cast<uint2*>(packed + (long long)r * (K >> 1) + b * 8) = make_uint2(lo, hi);
         scb = (uint8_t)sc;
       }
@@ -445,11 +454,9 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const __nv_bfloat16
         uint32_t w[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          uint32_t pk = 0;
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            pk |= (uint32_t)__nv_cvt_float_to_fp8(v[4 * j + c] * mul, __NV_SATFINITE, __NV_E4M3) << (8 * c);
-          w[j] = pk;
+          const uint32_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * mul, v[4 * j + 1] * mul), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t p1 = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * mul, v[4 * j + 3] * mul), __NV_SATFINITE, __NV_E4M3);
+          w[j] = p0 | (p1 << 16);
         }
         uint4* dst = reinterpret_cast<uint4*>(q + (long long)r * K + b * 32);
         dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -503,9 +510,9 @@ void launch_nvfp4_block_scales(const uint8_t* scales, int R, int K, uint8_t* out
 
 namespace {
 
-template <int BN, bool FP8>
+template <int BN, bool FP8, int EPI>
 void launch_block_scaled(const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, __nv_bfloat16* C, int M,
-                         int N, int K, float alpha, int* status, cudaStream_t s) {
+                         int N, int K, float alpha, const __nv_bfloat16* bias, int* status, cudaStream_t s) {
   using Cfg = BSCfg<BN, FP8>;
   const int row_bytes = FP8 ? K : K / 2;
   KParams kp{};
@@ -516,6 +523,7 @@ void launch_block_scaled(const uint8_t* a, const uint8_t* sfa, const uint8_t* b,
   kp.ldc = N; kp.strideC = 0;
   kp.alpha = alpha;
   kp.C = C;
+  kp.bias = bias;  // bf16 [N], added after alpha (before the activation)
   kp.status = status;
   kp.total_tiles = kp.num_m * kp.num_n;
   kp.splits = 1;
@@ -530,11 +538,11 @@ void launch_block_scaled(const uint8_t* a, const uint8_t* sfa, const uint8_t* b,
                                  (uint64_t)N * 2ull * (uint64_t)M, 32, 32);
   static PerDeviceOnce once;
   if (once.first_use()) {
-    cudaError_t e = cudaFuncSetAttribute(block_scaled_gemm_kernel<BN, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(block_scaled_gemm_kernel<BN, FP8, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) throw std::runtime_error(std::string("block_scaled_gemm: cannot set shared memory size: ") + cudaGetErrorString(e));
   }
   const int grid = kp.total_tiles < sm_count_f() ? kp.total_tiles : sm_count_f();
-  block_scaled_gemm_kernel<BN, FP8><<<grid, GEMM_THREADS, Cfg::SMEM, s>>>(tmA, tmB, tmC, sfa, sfb, kp, k_stages, sf_kblocks);
+  block_scaled_gemm_kernel<BN, FP8, EPI><<<grid, GEMM_THREADS, Cfg::SMEM, s>>>(tmA, tmB, tmC, sfa, sfb, kp, k_stages, sf_kblocks);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("block_scaled_gemm launch failed: ") + cudaGetErrorString(e));
 }
@@ -550,15 +558,27 @@ bool wide_tile(int M, int N, int K_bytes, int tile_n) {
 
 }  // namespace
 
+template <bool FP8>
+void dispatch_block_scaled(const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, __nv_bfloat16* C, int M,
+                           int N, int K, int k_bytes, float alpha, const __nv_bfloat16* bias, bool gelu, int* status, int tile_n,
+                           cudaStream_t s) {
+  const bool wide = wide_tile(M, N, k_bytes, tile_n);
+  if (gelu) {
+    if (wide) launch_block_scaled<256, FP8, EPI_GELU>(a, sfa, b, sfb, C, M, N, K, alpha, bias, status, s);
+    else launch_block_scaled<128, FP8, EPI_GELU>(a, sfa, b, sfb, C, M, N, K, alpha, bias, status, s);
+  } else {
+    if (wide) launch_block_scaled<256, FP8, EPI_PLAIN>(a, sfa, b, sfb, C, M, N, K, alpha, bias, status, s);
+    else launch_block_scaled<128, FP8, EPI_PLAIN>(a, sfa, b, sfb, C, M, N, K, alpha, bias, status, s);
+  }
+}
+
 void launch_nvfp4_gemm(const uint8_t* a_packed, const uint8_t* sfa, const uint8_t* b_packed, const uint8_t* sfb,
-                       __nv_bfloat16* C, int M, int N, int K, float alpha, int* status, int tile_n, cudaStream_t s) {
+                       __nv_bfloat16* C, int M, int N, int K, float alpha, const __nv_bfloat16* bias, bool gelu, int* status,
+                       int tile_n, cudaStream_t s) {
   if (M <= 0 || N <= 0) return;
   if (K % 32 != 0) throw std::runtime_error("nvfp4_gemm: K must be a multiple of 32 (16-byte rows of packed codes)");
   if (N % 8 != 0) throw std::runtime_error("nvfp4_gemm: N must be a multiple of 8");
-  if (wide_tile(M, N, K / 2, tile_n))
-    launch_block_scaled<256, false>(a_packed, sfa, b_packed, sfb, C, M, N, K, alpha, status, s);
-  else
-    launch_block_scaled<128, false>(a_packed, sfa, b_packed, sfb, C, M, N, K, alpha, status, s);
+  dispatch_block_scaled<false>(a_packed, sfa, b_packed, sfb, C, M, N, K, K / 2, alpha, bias, gelu, status, tile_n, s);
 }
 
 void launch_mxfp8_quantize(const __nv_bfloat16* x, long long ld, int R, int K, uint8_t* q, uint8_t* sf_blocked, cudaStream_t s) {
@@ -569,14 +589,11 @@ void launch_mxfp8_quantize(const __nv_bfloat16* x, long long ld, int R, int K, u
 }
 
 void launch_mxfp8_gemm(const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, __nv_bfloat16* C, int M,
-                       int N, int K, float alpha, int* status, int tile_n, cudaStream_t s) {
+                       int N, int K, float alpha, const __nv_bfloat16* bias, bool gelu, int* status, int tile_n, cudaStream_t s) {
   if (M <= 0 || N <= 0) return;
   if (K % 32 != 0) throw std::runtime_error("mxfp8_gemm: K must be a multiple of 32");
   if (N % 8 != 0) throw std::runtime_error("mxfp8_gemm: N must be a multiple of 8");
-  if (wide_tile(M, N, K, tile_n))
-    launch_block_scaled<256, true>(a, sfa, b, sfb, C, M, N, K, alpha, status, s);
-  else
-    launch_block_scaled<128, true>(a, sfa, b, sfb, C, M, N, K, alpha, status, s);
+  dispatch_block_scaled<true>(a, sfa, b, sfb, C, M, N, K, K, alpha, bias, gelu, status, tile_n, s);
 }
 
 }  // namespace tb

@@ -33,8 +33,10 @@ void launch_nvfp4_quantize_act(const __nv_bfloat16* x, long long ld, int M, int 
 void launch_nvfp4_block_scales(const uint8_t* scales, int R, int K, uint8_t* out, cudaStream_t s);
 // C[M, N] bf16 = alpha * (A .* SFA) (B .* SFB)^T on tcgen05 kind::mxf4nvf4 (K % 32 == 0, N % 8 == 0). tile_n: 0 = choose,
 // 128 = double-buffered 128 x 128 tiles, 256 = 128 x 256 tiles with one accumulator.
+// bias (bf16 [N], may be null) is added after alpha; gelu applies tanh-GELU after the bias.
 void launch_nvfp4_gemm(const uint8_t* a_packed, const uint8_t* sfa, const uint8_t* b_packed, const uint8_t* sfb,
-                       __nv_bfloat16* C, int M, int N, int K, float alpha, int* status, int tile_n, cudaStream_t s);
+                       __nv_bfloat16* C, int M, int N, int K, float alpha, const __nv_bfloat16* bias, bool gelu, int* status,
+                       int tile_n, cudaStream_t s);
 
 // MXFP8: E4M3 values with one power-of-two (UE8M0) scale per 32 elements of K, scales in the blocked layout of the
 // block-scaled GEMM (512 bytes per 128 rows x 128 elements of K; buffer pre-zeroed).
@@ -42,7 +44,7 @@ int mxfp8_sf_kblocks(int K);
 void launch_mxfp8_quantize(const __nv_bfloat16* x, long long ld, int R, int K, uint8_t* q, uint8_t* sf_blocked, cudaStream_t s);
 // C[M, N] bf16 = alpha * (A .* SFA) (B .* SFB)^T on tcgen05 kind::mxf8f6f4.block_scale (K % 32 == 0, N % 8 == 0).
 void launch_mxfp8_gemm(const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, __nv_bfloat16* C, int M,
-                       int N, int K, float alpha, int* status, int tile_n, cudaStream_t s);
+                       int N, int K, float alpha, const __nv_bfloat16* bias, bool gelu, int* status, int tile_n, cudaStream_t s);
 
 // GGML / GGUF block formats (F32, F16, BF16, Q4_0, Q4_1, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K) decoded on the device:
 // to bf16, or straight into NVFP4 (optional 16-point Hadamard rotation) without a bf16 copy of the tensor.

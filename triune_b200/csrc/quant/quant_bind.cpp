@@ -78,8 +78,16 @@ at::Tensor nvfp4_block_scales(const at::Tensor& scales, int64_t K) {
 }
 
 // y [M, N] bf16 = alpha * (a .* sfa) (b .* sfb)^T, both operands packed E2M1 with blocked unsigned-E4M3 scales
+const __nv_bfloat16* opt_bias(const c10::optional<at::Tensor>& bias, int64_t N) {
+  if (!bias.has_value() || !bias->defined()) return nullptr;
+  need(bias->is_cuda() && bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == N &&
+           (reinterpret_cast<uintptr_t>(bias->data_ptr()) & 15) == 0,
+       "block-scaled GEMM: bias must be a contiguous, 16-byte aligned bf16 [N] CUDA tensor");
+  return bf(*bias);
+}
+
 std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha,
-                                   int64_t tile_n) {
+                                   int64_t tile_n, const c10::optional<at::Tensor>& bias, bool gelu) {
   need(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() &&
            a.element_size() == 1 && b.element_size() == 1 && a.size(1) == b.size(1),
        "nvfp4_gemm: contiguous packed [M, K/2] and [N, K/2]");
@@ -94,7 +102,7 @@ std::vector<at::Tensor> nvfp4_gemm(const at::Tensor& a, const at::Tensor& sfa, c
   auto out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
   auto status = at::zeros({1}, a.options().dtype(at::kInt));
   tb::launch_nvfp4_gemm(a.data_ptr<uint8_t>(), sfa.data_ptr<uint8_t>(), b.data_ptr<uint8_t>(), sfb.data_ptr<uint8_t>(), bfm(out),
-                        (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), (int)tile_n, cur());
+                        (int)M, (int)N, (int)K, (float)alpha, opt_bias(bias, N), gelu, status.data_ptr<int>(), (int)tile_n, cur());
   return {out, status};
 }
 
@@ -113,7 +121,7 @@ std::vector<at::Tensor> mxfp8_quantize(const at::Tensor& x) {
 
 // y [M, N] bf16 = alpha * (a .* sfa) (b .* sfb)^T, E4M3 operands with blocked power-of-two scales per 32 elements
 std::vector<at::Tensor> mxfp8_gemm(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, double alpha,
-                                   int64_t tile_n) {
+                                   int64_t tile_n, const c10::optional<at::Tensor>& bias, bool gelu) {
   need(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() &&
            a.element_size() == 1 && b.element_size() == 1 && a.size(1) == b.size(1),
        "mxfp8_gemm: contiguous E4M3 [M, K] and [N, K]");
@@ -128,7 +136,7 @@ std::vector<at::Tensor> mxfp8_gemm(const at::Tensor& a, const at::Tensor& sfa, c
   auto out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
   auto status = at::zeros({1}, a.options().dtype(at::kInt));
   tb::launch_mxfp8_gemm((const uint8_t*)a.data_ptr(), sfa.data_ptr<uint8_t>(), (const uint8_t*)b.data_ptr(), sfb.data_ptr<uint8_t>(),
-                        bfm(out), (int)M, (int)N, (int)K, (float)alpha, status.data_ptr<int>(), (int)tile_n, cur());
+                        bfm(out), (int)M, (int)N, (int)K, (float)alpha, opt_bias(bias, N), gelu, status.data_ptr<int>(), (int)tile_n, cur());
   return {out, status};
 }
 
@@ -191,15 +199,19 @@ std::vector<at::Tensor> ggml_to_nvfp4(const at::Tensor& raw, int64_t type, int64
 }  // namespace
 
 void register_quant(pybind11::module& m) {
+  namespace py = pybind11;
   m.def("fp8_quantize_act", &fp8_quantize_act, "bf16 [M,K] -> (E4M3 [M,K], fp32 scales [M,K/128])");
   m.def("fp8_block_gemm", &fp8_block_gemm, "block-scaled E4M3 GEMM (tcgen05 kind::f8f6f4), bf16 out");
   m.def("nvfp4_quantize", &nvfp4_quantize, "[N,K] -> (packed E2M1, E4M3 block scales, fp32 tensor scale)");
   m.def("nvfp4_dequant", &nvfp4_dequant, "packed NVFP4 -> bf16 [N,K]");
   m.def("nvfp4_quantize_act", &nvfp4_quantize_act, "bf16 [M,K] -> (packed E2M1, blocked E4M3 scales) for the block-scaled GEMM");
   m.def("nvfp4_block_scales", &nvfp4_block_scales, "row-major E4M3 scales -> the block-scaled GEMM's layout");
-  m.def("nvfp4_gemm", &nvfp4_gemm, "block-scaled E2M1 x E2M1 GEMM (tcgen05 kind::mxf4nvf4), bf16 out");
+  m.def("nvfp4_gemm", &nvfp4_gemm, "block-scaled E2M1 x E2M1 GEMM (tcgen05 kind::mxf4nvf4), bf16 out", py::arg("a"), py::arg("sfa"),
+        py::arg("b"), py::arg("sfb"), py::arg("alpha"), py::arg("tile_n") = 0, py::arg("bias") = py::none(), py::arg("gelu") = false);
   m.def("mxfp8_quantize", &mxfp8_quantize, "bf16 [R,K] -> (E4M3, blocked power-of-two scales per 32 elements)");
-  m.def("mxfp8_gemm", &mxfp8_gemm, "block-scaled E4M3 x E4M3 GEMM (tcgen05 kind::mxf8f6f4.block_scale), bf16 out");
+  m.def("mxfp8_gemm", &mxfp8_gemm, "block-scaled E4M3 x E4M3 GEMM (tcgen05 kind::mxf8f6f4.block_scale), bf16 out", py::arg("a"),
+        py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("alpha"), py::arg("tile_n") = 0, py::arg("bias") = py::none(),
+        py::arg("gelu") = false);
   m.def("nvfp4_gemv", &nvfp4_gemv, "y = x @ W^T for M <= 8 straight from packed NVFP4 weights");
   m.def("ggml_dequant", &ggml_dequant, "GGML block formats -> bf16");
   m.def("ggml_to_nvfp4", &ggml_to_nvfp4, "GGML block formats -> NVFP4 (packed, scales, tensor scale) without a bf16 copy");

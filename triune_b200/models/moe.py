@@ -80,7 +80,9 @@ class _SharedExpert(nn.Sequential):
     def forward(self, x):
         if type(self[0]) is nn.Linear and type(self[2]) is nn.Linear:
             return ops.mlp_gelu(x, self[0].weight, self[0].bias, self[2].weight, self[2].bias)
-        return self[2](ops.gelu_tanh(self[0](x)))  # wrapped / quantised projections run their own forward
+        if getattr(self[0], "fused_gelu", False):  # quantised projections take the activation into their GEMM epilogue
+            return self[2](self[0](x, gelu=True))
+        return self[2](ops.gelu_tanh(self[0](x)))  # wrapped projections run their own forward
 
 
 class MoE_FFN(nn.Module):

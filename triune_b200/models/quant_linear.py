@@ -169,6 +169,8 @@ class NVFP4Linear(nn.Module):
             y = ops.nvfp4_linear(x2, self.packed_weight, self.block_scales, self.tensor_scale, out_dtype=x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
+        if gelu:
+            y = ops.gelu_tanh(y)
         return y.view(*x.shape[:-1], self.out_features)
 
 

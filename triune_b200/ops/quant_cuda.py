@@ -79,14 +79,22 @@ def nvfp4_quantize_act(x2: torch.Tensor, hadamard: bool = False):
 last_gemm_status = None
 
 
-def nvfp4_w4a4_linear(x2, packed, sf_blocked, alpha: float, hadamard: bool, out_dtype):
+def _bias16(bias):
+    """The GEMM epilogue adds a contiguous bf16 bias; anything else is converted once per call (tiny)."""
+    if bias is None:
+        return None
+    b = bias.detach()
+    return b if (b.dtype == torch.bfloat16 and b.is_contiguous() and b.data_ptr() % 16 == 0) else b.to(torch.bfloat16).contiguous().clone()
+
+
+def nvfp4_w4a4_linear(x2, packed, sf_blocked, alpha: float, hadamard: bool, out_dtype, bias=None, gelu: bool = False):
     """y = alpha * dequant(quant(x)) @ dequant(W)^T with both operands E2M1 and both scale sets applied by the tensor
     core (``tcgen05.mma.kind::mxf4nvf4``); nothing is decoded to bf16."""
     global last_gemm_status
     e = _ext.ext()
     x2 = x2 if (x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0) else x2.contiguous()
     a_p, a_sf = e.nvfp4_quantize_act(x2, bool(hadamard))
-    y, last_gemm_status = e.nvfp4_gemm(a_p, a_sf, packed, sf_blocked, float(alpha), 0)
+    y, last_gemm_status = e.nvfp4_gemm(a_p, a_sf, packed, sf_blocked, float(alpha), 0, _bias16(bias), bool(gelu))
     _tick(2)
     return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
 
@@ -102,16 +110,16 @@ def mxfp8_quantize(x2: torch.Tensor):
     return tuple(_ext.ext().mxfp8_quantize(x2))
 
 
-def mxfp8_gemm(a, sfa, b, sfb, alpha: float = 1.0, tile_n: int = 0):
+def mxfp8_gemm(a, sfa, b, sfb, alpha: float = 1.0, tile_n: int = 0, bias=None, gelu: bool = False):
     global last_gemm_status
     _tick()
-    y, last_gemm_status = _ext.ext().mxfp8_gemm(a, sfa, b, sfb, float(alpha), int(tile_n))
+    y, last_gemm_status = _ext.ext().mxfp8_gemm(a, sfa, b, sfb, float(alpha), int(tile_n), _bias16(bias), bool(gelu))
     return y
 
 
-def mxfp8_linear(x2, wq, w_sf, out_dtype):
+def mxfp8_linear(x2, wq, w_sf, out_dtype, bias=None, gelu: bool = False):
     """y = dequant(quant(x)) @ dequant(W)^T, both E4M3 with 1x32 power-of-two scales applied by the tensor core
     (``tcgen05.mma.kind::mxf8f6f4.block_scale``): no promotion of partial sums out of TMEM per K block."""
     xq, x_sf = mxfp8_quantize(x2)
-    y = mxfp8_gemm(xq, x_sf, wq, w_sf)
+    y = mxfp8_gemm(xq, x_sf, wq, w_sf, bias=bias, gelu=gelu)  # bias and tanh-GELU ride in the GEMM epilogue
     return y if out_dtype == torch.bfloat16 else y.to(out_dtype)
