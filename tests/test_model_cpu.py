@@ -410,3 +410,23 @@ def test_gla_output_scale_option():
     assert m.out_scale == 1.0
     d = VectorisedGLA(32, 2, 16, use_delta_rule=True)
     assert set_gla_scale(torch.nn.ModuleList([d]), "fla") == 0 and d.out_scale == 1.0  # the delta-rule path is never scaled
+
+
+def test_quantised_linears_take_gelu_flag_and_dense_ffn_uses_it():
+    import torch.nn.functional as F
+
+    from triune_b200.models.block import DenseFFN
+    from triune_b200.models.quant_linear import FP8Linear, NVFP4Linear, convert_to_fp8
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(64, 48)
+    x = torch.randn(5, 64)
+    for mod in (FP8Linear.from_linear(lin).eval(), NVFP4Linear.from_linear(lin)):
+        with torch.no_grad():
+            assert torch.allclose(mod(x, gelu=True), F.gelu(mod(x), approximate="tanh"), atol=1e-6)
+    ffn = DenseFFN(64, 128).eval()
+    with torch.no_grad():
+        want = ffn(x)
+        assert convert_to_fp8(ffn) == 2 and getattr(ffn[0], "fused_gelu", False)
+        got = ffn(x)
+    assert F.cosine_similarity(got.flatten(), want.flatten(), dim=0) > 0.99

@@ -63,25 +63,30 @@ class FP8Linear(nn.Module):
             self._q = (v, wq, ws)
         return self._q[1], self._q[2]
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    fused_gelu = True  # forward(x, gelu=True) applies tanh-GELU (in the GEMM epilogue on the block-scaled path)
+
+    def forward(self, x: torch.Tensor, gelu: bool = False) -> torch.Tensor:
         if self.training and torch.is_grad_enabled() and self.weight.requires_grad:
             # straight-through: quantisation error enters the forward, gradients flow to the master weight
             wq, ws = self.quantized()
             w_dq = (wq.float() * ws.repeat_interleave(self.block, 0).repeat_interleave(self.block, 1)
                     [: self.out_features, : self.in_features]).to(self.weight.dtype)
             w = self.weight + (w_dq - self.weight).detach()
-            return F.linear(x, w, self.bias)
+            y = F.linear(x, w, self.bias)
+            return ops.gelu_tanh(y) if gelu else y
         x2 = x.reshape(-1, self.in_features)
         from ..ops import quant_cuda
 
         if self.mx and quant_cuda.mxfp8_supported(x2, self.in_features, self.out_features) and self.weight.is_cuda:
             wq, sf = self.quantized_mx()
-            y = quant_cuda.mxfp8_linear(x2, wq, sf, x.dtype)
-        else:
-            wq, ws = self.quantized()
-            y = ops.fp8_linear(x2, wq, ws, self.block, out_dtype=x.dtype)
+            y = quant_cuda.mxfp8_linear(x2, wq, sf, x.dtype, bias=self.bias, gelu=gelu)  # bias / GELU in the epilogue
+            return y.view(*x.shape[:-1], self.out_features)
+        wq, ws = self.quantized()
+        y = ops.fp8_linear(x2, wq, ws, self.block, out_dtype=x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
+        if gelu:
+            y = ops.gelu_tanh(y)
         return y.view(*x.shape[:-1], self.out_features)
 
 
@@ -154,7 +159,9 @@ class NVFP4Linear(nn.Module):
                 and self.block_scales.dtype == torch.float8_e4m3fn and self.in_features % 32 == 0
                 and self.out_features % 8 == 0)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    fused_gelu = True  # forward(x, gelu=True) applies tanh-GELU (in the GEMM epilogue on the block-scaled path)
+
+    def forward(self, x: torch.Tensor, gelu: bool = False) -> torch.Tensor:
         x2 = x.reshape(-1, self.in_features)
         if self._w4a4_ready(x2):
             from ..ops import quant_cuda
@@ -162,7 +169,9 @@ class NVFP4Linear(nn.Module):
             if self._sf_blocked is None or self._sf_blocked.device != x2.device:
                 self._sf_blocked = quant_cuda.nvfp4_block_scales(self.block_scales, self.in_features)
                 self._alpha = float(self.tensor_scale)  # one host read, at the first call
-            y = quant_cuda.nvfp4_w4a4_linear(x2, self.packed_weight, self._sf_blocked, self._alpha, self.hadamard, x.dtype)
+            y = quant_cuda.nvfp4_w4a4_linear(x2, self.packed_weight, self._sf_blocked, self._alpha, self.hadamard, x.dtype,
+                                             bias=self.bias, gelu=gelu)
+            return y.view(*x.shape[:-1], self.out_features)
         else:
             if self.hadamard:
                 x2 = ops.fwht16(x2)
