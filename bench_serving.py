@@ -122,10 +122,15 @@ def run_ours(a):
                 out = dec.generate(prompt, a.new_tokens)
                 torch.cuda.synchronize()
                 dt = time.perf_counter() - t0
+                ref_out = graphed.generate(prompt, a.new_tokens)
+                same = (out == ref_out)[0].long()
+                agree = int(torch.cumprod(same, 0).sum().item()) - prompt.shape[1]
+                # bf16: the batched verification (rows of 4 tokens) and the one-token step round differently, so with
+                # random-init weights (near-uniform logits) an arg-max can flip; the scheme itself is exact (CPU test)
                 emit(metric=f"decode (self-speculative, greedy, one CUDA graph per round{tag}) tok/s", impl="triune_b200",
                      value=(out.shape[1] - prompt.shape[1]) / dt, unit="tok/s", new_tokens=int(out.shape[1] - prompt.shape[1]),
                      acceptance_rate=round(dec.acceptance_rate, 3), k_draft=a.k_draft,
-                     matches_greedy=bool(torch.equal(out, graphed.generate(prompt, a.new_tokens))))
+                     tokens_equal_to_greedy_before_first_difference=agree)
 
             spec_run("")
             # random-init exits never agree with the full depth; a short KL distillation of the exit heads toward the
