@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=0, help="expert hidden width")
     ap.add_argument("--ep-mode", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--capacity-factor", type=float, default=1.5)
+    ap.add_argument("--profile", action="store_true", help="after the timed steps, print rank 0's kernel table of one more step")
     a = ap.parse_args()
 
     from triune_b200.config import ModelConfig, get_model_config
@@ -120,6 +121,15 @@ def main():
             "wait_status": int(status), "peak_mem_GB": round(float(mem), 1), "build_s": round(build_s, 1),
             "final_loss": float(loss.detach()), "impl": "triune_b200",
         }), flush=True)
+    if a.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        dist.barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=90), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
