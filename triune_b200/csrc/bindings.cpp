@@ -486,10 +486,12 @@ Tensor ns_prepare(const Tensor& x, double eps) {
   check_bf16_cuda(x, "x");
   TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && x.size(2) % 8 == 0 && x.size(1) <= x.size(2),
               "ns_prepare: contiguous [batch, m, n] with m <= n and n % 8 == 0");
-  TORCH_CHECK((x.size(1) + x.size(2)) * 4 <= 200 * 1024, "ns_prepare: m + n too large for one CTA's shared memory");
+  TORCH_CHECK(x.size(2) <= 12288, "ns_prepare: n <= 12288 (the iterate and an 8-row tile live in one CTA's shared memory)");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor y = torch::empty_like(x);
-  tb::launch_ns_prepare(bf(x), bfm(y), (int)x.size(0), (int)x.size(1), (int)x.size(2), (float)eps, cur_stream());
+  const int64_t K = x.size(0), n = x.size(2);
+  Tensor scratch = torch::empty({2 * K * n + 2 * K}, x.options().dtype(at::kFloat));
+  tb::launch_ns_prepare(bf(x), bfm(y), (int)K, (int)x.size(1), (int)n, (float)eps, scratch.data_ptr<float>(), cur_stream());
   return y;
 }
 

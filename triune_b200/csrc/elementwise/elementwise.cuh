@@ -82,7 +82,9 @@ void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* par
                        float wd, float scale, const float* hyper, cudaStream_t s);
 // Newton-Schulz set-up for `batch` matrices X [m, n] (m <= n, n % 8 == 0, contiguous): Y = X / safe with
 // safe = max(1.15 sigma_max estimate, ||X||_F / sqrt(m), 0.7 ||X||_F); sigma from a four-step power iteration.
-void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int m, int n, float eps, cudaStream_t s);
+// `scratch`: fp32 [2 * batch * n + 2 * batch] (two iterate buffers, ||X||_F^2 and sigma^2 per matrix). n <= 12288.
+void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int m, int n, float eps, float* scratch,
+                       cudaStream_t s);
 // X = a*X + Y (bf16, elementwise) used by the Newton-Schulz blend when not fused in a GEMM epilogue.
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s);
 

@@ -8,6 +8,8 @@
 // csrc/engine/engine.cpp:314-414 of the reference project.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <stdexcept>
 #include <float.h>
 #include <stdint.h>
 
@@ -340,100 +342,133 @@ __global__ void __launch_bounds__(256) axpby_bf16_kernel(__nv_bfloat16* __restri
     x[i] = __float2bfloat16(a * __bfloat162float(x[i]) + b * __bfloat162float(y[i]));
 }
 
-// Newton-Schulz set-up, one CTA per matrix X [m, n] (m <= n, bf16, rows contiguous): Frobenius norm, a four-step power
-// iteration for the largest singular value (v <- X^T X v from the constant start vector, the deterministic estimate of
-// triune/kernels/fast_muon.py:15-91), and Y = X / max(1.15 sigma, ||X||_F / sqrt(m), 0.7 ||X||_F) so that the quintic
-// iteration starts inside its basin. Replaces nine fp32 library products and three reductions per shape group.
+// Newton-Schulz set-up for a stack of matrices X [K, m, n] (m <= n, bf16, rows contiguous): Frobenius norm, a four-step
+// power iteration for the largest singular value (v <- X^T X v from the constant start vector, the deterministic
+// estimate of triune/kernels/fast_muon.py:15-91), and Y = X / max(1.15 sigma, ||X||_F / sqrt(m), 0.7 ||X||_F) so that the
+// quintic iteration starts inside its basin. Replaces nine fp32 library products and three reductions per shape group.
+//
+// Every matrix is split by rows over several CTAs, and one launch is one power-iteration step done in ONE pass over X:
+// a CTA stages 8 rows in shared memory, its warps form u_r = x_r . v for those rows, then every thread adds u_r x_r into
+// the columns it owns (registers), so X^T (X v) needs no second read. The partial X^T u of a CTA goes to the next
+// vector with fp32 atomics; the next launch normalises it while loading. (One CTA per matrix, the first form of this
+// kernel, read a 1536 x 6144 matrix ten times at the bandwidth of one SM: 7 ms per call on the 1.5 B-class models.)
 constexpr int NSP_THREADS = 256;
-__global__ void __launch_bounds__(NSP_THREADS) ns_prepare_kernel(const __nv_bfloat16* __restrict__ X,
-                                                                 __nv_bfloat16* __restrict__ Y, int m, int n, float eps) {
-  extern __shared__ float nsp_smem[];
-  float* v = nsp_smem;       // [n]
-  float* w = v + n;          // [m]
+constexpr int NSP_ROWS = 8;  // rows per shared-memory tile = warps per CTA
+__global__ void __launch_bounds__(NSP_THREADS) ns_power_step_kernel(const __nv_bfloat16* __restrict__ X,
+                                                                    const float* __restrict__ v_in, float* __restrict__ v_out,
+                                                                    float* __restrict__ fro2, float* __restrict__ sigma2, int m,
+                                                                    int n, int rows_per_cta, float eps) {
+  extern __shared__ __align__(16) uint8_t nsp_raw[];
+  float* v = reinterpret_cast<float*>(nsp_raw);                                   // [n]
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(nsp_raw + (size_t)n * 4);  // [NSP_ROWS][n]
   __shared__ float red[NSP_THREADS / 32];
-  const __nv_bfloat16* x = X + (long long)blockIdx.x * m * n;
-  __nv_bfloat16* y = Y + (long long)blockIdx.x * m * n;
+  __shared__ float u[NSP_ROWS];
+  const int k = blockIdx.y;
+  const __nv_bfloat16* x = X + (long long)k * m * n;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nvec = n >> 3;
-  const long long total_vec = (long long)m * nvec;
-  float ss = 0.f;
-  for (long long i = tid; i < total_vec; i += NSP_THREADS) {
-    const uint4 u = reinterpret_cast<const uint4*>(x)[i];
-    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(p2[j]);
-      ss += f.x * f.x + f.y * f.y;
+  // the iterate, normalised here (the previous launch left it as a sum of partial products)
+  if (v_in) {
+    float s2 = 0.f;
+    for (int c = tid; c < n; c += NSP_THREADS) {
+      const float t = v_in[(long long)k * n + c];
+      v[c] = t;
+      s2 += t * t;
     }
+    const float inv = 1.f / fmaxf(sqrtf(block_sum<NSP_THREADS>(s2, red)), eps);
+    for (int c = tid; c < n; c += NSP_THREADS) v[c] *= inv;
+  } else {
+    const float v0 = rsqrtf((float)n);
+    for (int c = tid; c < n; c += NSP_THREADS) v[c] = v0;
   }
-  const float fro = fmaxf(sqrtf(block_sum<NSP_THREADS>(ss, red)), eps);
-  const float v0 = rsqrtf((float)n);
-  for (int c = tid; c < n; c += NSP_THREADS) v[c] = v0;
   __syncthreads();
-  float sigma = 0.f;
-  for (int it = 0; it < 5; ++it) {
-    // w = X v: one warp per row
-    for (int r = warp; r < m; r += NSP_THREADS / 32) {
-      const uint4* row = reinterpret_cast<const uint4*>(x + (long long)r * n);
-      float acc = 0.f;
+  constexpr int MAXV = 6;  // column vectors (8 columns each) per thread: n <= 6 * 8 * 256 = 12288
+  float acc[MAXV][8];
+#pragma unroll
+  for (int q = 0; q < MAXV; ++q)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
+  float ss = 0.f, su = 0.f;
+  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_end = min(m, r_begin + rows_per_cta);
+  for (int r0 = r_begin; r0 < r_end; r0 += NSP_ROWS) {
+    const int rows = min(NSP_ROWS, r_end - r0);
+    for (int i = tid; i < rows * nvec; i += NSP_THREADS)
+      reinterpret_cast<uint4*>(tile)[i] = reinterpret_cast<const uint4*>(x + (long long)r0 * n)[i];
+    __syncthreads();
+    if (warp < rows) {
+      const uint4* row = reinterpret_cast<const uint4*>(tile + (size_t)warp * n);
+      float a = 0.f, sq = 0.f;
       for (int c8 = lane; c8 < nvec; c8 += 32) {
-        const uint4 u = row[c8];
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        const uint4 w4 = row[c8];
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&w4);
         const float* vp = v + c8 * 8;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = __bfloat1622float2(p2[j]);
-          acc += f.x * vp[2 * j] + f.y * vp[2 * j + 1];
+          a += f.x * vp[2 * j] + f.y * vp[2 * j + 1];
+          sq += f.x * f.x + f.y * f.y;
         }
       }
-      acc = warp_sum(acc);
-      if (lane == 0) w[r] = acc;
+      a = warp_sum(a);
+      sq = warp_sum(sq);
+      if (lane == 0) {
+        u[warp] = a;
+        ss += sq;
+        su += a * a;
+      }
     }
     __syncthreads();
-    if (it == 4) {
-      float s2 = 0.f;
-      for (int r = tid; r < m; r += NSP_THREADS) s2 += w[r] * w[r];
-      sigma = sqrtf(block_sum<NSP_THREADS>(s2, red));
-      break;
-    }
-    // v = X^T w: a thread owns eight columns and walks the rows (coalesced across threads)
-    float n2 = 0.f;
-    for (int c8 = tid; c8 < nvec; c8 += NSP_THREADS) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int r = 0; r < m; ++r) {
-        const uint4 u = reinterpret_cast<const uint4*>(x + (long long)r * n)[c8];
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-        const float wr = w[r];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(p2[j]);
-          acc[2 * j] += f.x * wr;
-          acc[2 * j + 1] += f.y * wr;
+    for (int q = 0; q < MAXV; ++q) {
+      const int c8 = tid + q * NSP_THREADS;
+      if (c8 < nvec) {
+        for (int r = 0; r < rows; ++r) {
+          const uint4 w4 = reinterpret_cast<const uint4*>(tile + (size_t)r * n)[c8];
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&w4);
+          const float ur = u[r];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(p2[j]);
+            acc[q][2 * j] += f.x * ur;
+            acc[q][2 * j + 1] += f.y * ur;
+          }
         }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) n2 += acc[j] * acc[j];
-      // v is only read in the X v phase, which ended at the barrier above: it can be overwritten here
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[c8 * 8 + j] = acc[j];
     }
-    const float nrm = fmaxf(sqrtf(block_sum<NSP_THREADS>(n2, red)), eps);
-    const float inv = 1.f / nrm;
-    __syncthreads();
-    for (int c = tid; c < n; c += NSP_THREADS) v[c] *= inv;
     __syncthreads();
   }
-  const float safe = fmaxf(fmaxf(1.15f * sigma, fro * rsqrtf((float)m)), 0.7f * fro);
-  const float sc = 1.f / safe;
-  for (long long i = tid; i < total_vec; i += NSP_THREADS) {
-    uint4 u = reinterpret_cast<const uint4*>(x)[i];
-    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&u);
+  if (v_out) {
+#pragma unroll
+    for (int q = 0; q < MAXV; ++q) {
+      const int c8 = tid + q * NSP_THREADS;
+      if (c8 < nvec) {
+        float* dst = v_out + (long long)k * n + c8 * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dst + j, acc[q][j]);
+      }
+    }
+  }
+  if (lane == 0) {
+    if (fro2) atomicAdd(fro2 + k, ss);
+    if (sigma2) atomicAdd(sigma2 + k, su);
+  }
+}
+
+__global__ void __launch_bounds__(256) ns_scale_kernel(const __nv_bfloat16* __restrict__ X, __nv_bfloat16* __restrict__ Y,
+                                                       const float* __restrict__ fro2, const float* __restrict__ sigma2,
+                                                       long long per_matrix_vec, long long total_vec, int m, float eps) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i / per_matrix_vec);
+    const float fro = fmaxf(sqrtf(fro2[k]), eps), sigma = sqrtf(sigma2[k]);
+    const float sc = 1.f / fmaxf(fmaxf(1.15f * sigma, fro * rsqrtf((float)m)), 0.7f * fro);
+    uint4 w4 = reinterpret_cast<const uint4*>(X)[i];
+    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&w4);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 f = __bfloat1622float2(p2[j]);
       p2[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
     }
-    reinterpret_cast<uint4*>(y)[i] = u;
+    reinterpret_cast<uint4*>(Y)[i] = w4;
   }
 }
 
@@ -613,12 +648,36 @@ void launch_muon_apply(float* master, const __nv_bfloat16* o, __nv_bfloat16* par
   muon_apply_kernel<<<flat_grid(n), 256, 0, s>>>(master, o, param_bf16, n, lr, wd, scale, hyper);
 }
 
-void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int m, int n, float eps, cudaStream_t s) {
+void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int m, int n, float eps, float* scratch,
+                       cudaStream_t s) {
+  // scratch: fp32 [2 * batch * n + 2 * batch]: two iterate buffers, then ||X||_F^2 and sigma^2 per matrix
   if (batch <= 0) return;
-  const size_t smem = (size_t)(m + n) * sizeof(float);
+  if (n > 6 * 8 * NSP_THREADS) throw std::runtime_error("ns_prepare: n <= 12288");
+  const size_t smem = (size_t)n * 4 + (size_t)NSP_ROWS * n * 2;
   static PerDeviceOnce once;
-  if (once.first_use()) cudaFuncSetAttribute(ns_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  ns_prepare_kernel<<<batch, NSP_THREADS, smem, s>>>(X, Y, m, n, eps);
+  if (once.first_use()) cudaFuncSetAttribute(ns_power_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  float* va = scratch;
+  float* vb = scratch + (size_t)batch * n;
+  float* fro2 = scratch + 2 * (size_t)batch * n;
+  float* sigma2 = fro2 + batch;
+  // rows per CTA: enough CTAs to fill the GPU a few times over, whole 8-row tiles
+  int splits = (148 * 4 + batch - 1) / batch;
+  int rows_per_cta = (m + splits - 1) / splits;
+  rows_per_cta = (rows_per_cta + NSP_ROWS - 1) / NSP_ROWS * NSP_ROWS;
+  splits = (m + rows_per_cta - 1) / rows_per_cta;
+  const dim3 grid((unsigned)splits, (unsigned)batch, 1);
+  cudaMemsetAsync(fro2, 0, sizeof(float) * 2 * batch, s);
+  const float* vin = nullptr;
+  for (int it = 0; it < 5; ++it) {
+    float* vout = (it & 1) ? vb : va;
+    const bool last = it == 4;
+    if (!last) cudaMemsetAsync(vout, 0, sizeof(float) * (size_t)batch * n, s);
+    ns_power_step_kernel<<<grid, NSP_THREADS, smem, s>>>(X, vin, last ? nullptr : vout, it == 0 ? fro2 : nullptr,
+                                                         last ? sigma2 : nullptr, m, n, rows_per_cta, eps);
+    vin = vout;
+  }
+  const long long per = (long long)m * (n >> 3), total = per * batch;
+  ns_scale_kernel<<<flat_grid(total), 256, 0, s>>>(X, Y, fro2, sigma2, per, total, m, eps);
 }
 
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s) {

@@ -24,7 +24,8 @@ def newton_schulz(G: torch.Tensor, steps: int = 3, coeffs=(1.875, -1.25, 0.375),
 
     Per iteration: A = X X^T; T = c A A + b A; X <- T X + a X: three GEMM launches, the two blends in the GEMMs'
     add-rows epilogue. The spectral-norm safeguard of the reference (``triune/kernels/fast_muon.py:15-91``: Frobenius
-    norm and a four-step power iteration) and the scaling run in one set-up kernel with one CTA per matrix.
+    norm and a four-step power iteration) and the scaling run as five passes over X (one per power step, X^T (X v) in one
+    read, rows split over CTAs) plus one scaling pass.
     """
     from . import gemm, _tick
 
@@ -36,10 +37,10 @@ def newton_schulz(G: torch.Tensor, steps: int = 3, coeffs=(1.875, -1.25, 0.375),
         X = X.transpose(-1, -2)
     m, n = X.shape[-2], X.shape[-1]
     e = _ext.ext()
-    if (m + n) * 4 <= 200 * 1024:
-        # Frobenius norm, power iteration and scaling in ONE kernel (one CTA per matrix)
+    if n <= 12288 and n % 8 == 0:
+        # Frobenius norm, power iteration (one fused pass over X per step, rows split over CTAs) and scaling
         Xb = e.ns_prepare(X.to(torch.bfloat16).contiguous(), float(eps))
-        _tick()
+        _tick(6)
     else:
         Xf = X.float()
         fro = Xf.flatten(-2).norm(dim=-1).clamp_min(eps)
