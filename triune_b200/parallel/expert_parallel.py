@@ -117,9 +117,14 @@ class _EPExpertsFn(torch.autograd.Function):
         e.ep_build_tiles(cnt_all, El, W, cap, tile_group, row_dst)
         e.ep_zero_invalid_rows(xin, cnt_all, El, W, cap)
         H = w1.shape[1]
-        dact = torch.zeros(rows, H, dtype=x.dtype, device=x.device)  # rows of skipped tiles must stay finite (they meet
-        h = torch.zeros(rows, H, dtype=x.dtype, device=x.device)    # zero rows in the weight-gradient GEMMs)
+        # Rows without a token must hold finite values (they meet zero rows in the weight-gradient GEMMs, and 0 * NaN
+        # would poison them). The grouped GEMM writes every row of a tile it runs; only the rows past each segment's count
+        # are zeroed afterwards (about a third of the buffer at capacity factor 1.5) instead of filling all of it first.
+        dact = torch.empty(rows, H, dtype=x.dtype, device=x.device)
+        h = torch.empty(rows, H, dtype=x.dtype, device=x.device)
         gemm(xin, w1, h, bias=b1, gelu=True, aux_out=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        e.ep_zero_invalid_rows(h, cnt_all, El, W, cap)
+        e.ep_zero_invalid_rows(dact, cnt_all, El, W, cap)
         # Copies for the backward pass are taken BEFORE this rank signals the combine barrier: once a peer has passed
         # that barrier it may start its next dispatch and overwrite these regions.
         xin_saved, dst_saved, cnt_saved = xin.clone(), row_dst.clone(), cnt_all.clone()
@@ -159,8 +164,9 @@ class _EPExpertsFn(torch.autograd.Function):
         e.ep_zero_invalid_rows(dyin, cnt_all, El, W, cap)
         live_dst.copy_(row_dst)  # same routing as the forward, including the rows invalidated there
         H = w1.shape[1]
-        dpre = torch.zeros(rows, H, dtype=dout.dtype, device=dout.device)
+        dpre = torch.empty(rows, H, dtype=dout.dtype, device=dout.device)
         gemm(dyin, w2, dpre, b_mn=True, dgelu_aux=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
+        e.ep_zero_invalid_rows(dpre, cnt_all, El, W, cap)  # rows of skipped tiles (the others are 0 * finite already)
         offs = (torch.arange(El + 1, device=dout.device, dtype=torch.int32) * (W * cap)).contiguous()
         ones = torch.ones(rows, 8, device=dout.device, dtype=dout.dtype)
 
