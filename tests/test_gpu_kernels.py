@@ -602,8 +602,11 @@ def test_model_step_matches_reference_ops(dev):
                         model.layers[4].ffn.w1.grad.float().clone()))
         finally:
             _ext.set_reference_ops(False)
-    assert abs(res[0][0] - res[1][0]) < 5e-2
-    assert _rel(res[0][1], res[1][1]) < 0.15
+    assert abs(res[0][0] - res[1][0]) < 1e-2  # measured 6e-5 ... 6e-4 over three seeds
+    a, b = res[0][1], res[1][1]
+    assert _rel(a, b) < 8e-2                                                   # largest entry: measured 2.4e-2 ... 3.6e-2
+    assert float((a - b).norm() / b.norm()) < 6e-2                             # measured 2.1e-2 ... 3.0e-2
+    assert F.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.998       # measured 0.9996 ... 0.9998
     # expert gradients: a near-tied router logit may pick a different expert in the two runs, so compare direction
     assert F.cosine_similarity(res[0][2].flatten(), res[1][2].flatten(), dim=0) > 0.9
 

@@ -486,7 +486,7 @@ Tensor ns_prepare(const Tensor& x, double eps) {
   check_bf16_cuda(x, "x");
   TORCH_CHECK(x.dim() == 3 && x.is_contiguous() && x.size(2) % 8 == 0 && x.size(1) <= x.size(2),
               "ns_prepare: contiguous [batch, m, n] with m <= n and n % 8 == 0");
-  TORCH_CHECK(x.size(2) <= 12288, "ns_prepare: n <= 12288 (the iterate and an 8-row tile live in one CTA's shared memory)");
+  TORCH_CHECK(x.size(2) <= 11568, "ns_prepare: n <= 11568 (the iterate and an 8-row tile live in one CTA's shared memory)");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor y = torch::empty_like(x);
   const int64_t K = x.size(0), n = x.size(2);

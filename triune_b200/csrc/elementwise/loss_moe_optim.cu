@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <stdexcept>
+#include <string>
 #include <float.h>
 #include <stdint.h>
 
@@ -652,10 +653,15 @@ void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int 
                        cudaStream_t s) {
   // scratch: fp32 [2 * batch * n + 2 * batch]: two iterate buffers, then ||X||_F^2 and sigma^2 per matrix
   if (batch <= 0) return;
-  if (n > 6 * 8 * NSP_THREADS) throw std::runtime_error("ns_prepare: n <= 12288");
+  if (n > 6 * 8 * NSP_THREADS || (size_t)n * 20 > 226 * 1024) throw std::runtime_error("ns_prepare: n <= 11568");
   const size_t smem = (size_t)n * 4 + (size_t)NSP_ROWS * n * 2;
+  constexpr int kMaxDyn = 226 * 1024;  // the kernel also has a few static words; 227 KB is the limit for both together
+  if (smem > (size_t)kMaxDyn) throw std::runtime_error("ns_prepare: the iterate and an 8-row tile do not fit shared memory");
   static PerDeviceOnce once;
-  if (once.first_use()) cudaFuncSetAttribute(ns_power_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (once.first_use()) {
+    cudaError_t e = cudaFuncSetAttribute(ns_power_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDyn);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("ns_prepare: cannot set shared memory size: ") + cudaGetErrorString(e));
+  }
   float* va = scratch;
   float* vb = scratch + (size_t)batch * n;
   float* fro2 = scratch + 2 * (size_t)batch * n;
@@ -678,6 +684,8 @@ void launch_ns_prepare(const __nv_bfloat16* X, __nv_bfloat16* Y, int batch, int 
   }
   const long long per = (long long)m * (n >> 3), total = per * batch;
   ns_scale_kernel<<<flat_grid(total), 256, 0, s>>>(X, Y, fro2, sigma2, per, total, m, eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("ns_prepare launch failed: ") + cudaGetErrorString(e));
 }
 
 void launch_axpby_bf16(__nv_bfloat16* x, const __nv_bfloat16* y, float a, float b, long long n, cudaStream_t s) {

@@ -37,7 +37,7 @@ def newton_schulz(G: torch.Tensor, steps: int = 3, coeffs=(1.875, -1.25, 0.375),
         X = X.transpose(-1, -2)
     m, n = X.shape[-2], X.shape[-1]
     e = _ext.ext()
-    if n <= 12288 and n % 8 == 0:
+    if n <= 11568 and n % 8 == 0:
         # Frobenius norm, power iteration (one fused pass over X per step, rows split over CTAs) and scaling
         Xb = e.ns_prepare(X.to(torch.bfloat16).contiguous(), float(eps))
         _tick(6)
