@@ -806,3 +806,61 @@ def test_graphed_speculative_decoder_equals_greedy_and_accepts_agreeing_drafts()
     assert torch.equal(got2, want2)
     assert spec2.acceptance_rate == 1.0 and spec2.acceptance_rate >= low
     assert int(spec2.rounds.item()) <= 8  # 23 tokens at 4 per round, checked every 8 rounds
+
+
+def test_streaming_finds_the_layer_stack_of_foreign_models():
+    """Layer streaming locates the block stack of models it did not build: Hugging Face style nesting, or any longest
+    list of same-typed blocks; streamed layers of such a model still train."""
+    import torch.nn as nn
+
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming, find_layer_list
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(16, 16)
+
+        def forward(self, x):
+            return x + torch.tanh(self.lin(x))
+
+    class Inner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed_tokens = nn.Embedding(32, 16)
+            self.layers = nn.ModuleList([Block() for _ in range(4)])
+
+    class HFLike(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+            self.lm_head = nn.Linear(16, 32)
+
+        def forward(self, ids):
+            x = self.model.embed_tokens(ids)
+            for l in self.model.layers:
+                x = l(x)
+            return self.lm_head(x)
+
+    class Odd(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.stem = nn.ModuleList([nn.Linear(4, 4)])
+            self.tower = nn.ModuleList([Block() for _ in range(3)])
+
+    torch.manual_seed(0)
+    m = HFLike()
+    assert find_layer_list(m) is m.model.layers
+    assert find_layer_list(Odd()) is not None and len(find_layer_list(Odd())) == 3
+    try:
+        find_layer_list(m, "transformer.h")
+        assert False
+    except AttributeError:
+        pass
+    eng = enable_layer_streaming(m, "cpu", config=StreamingConfig(resident_gpu_layers=1, pin_memory=False))
+    assert len(eng.stores) == 3
+    ids = torch.randint(0, 32, (2, 6))
+    before = m.model.layers[2].lin.weight.detach().clone()
+    loss = torch.nn.functional.cross_entropy(m(ids).reshape(-1, 32), ids.reshape(-1))
+    loss.backward()
+    eng.step_streaming_optimizer(None, lr=1e-2)
+    assert not torch.equal(before, m.model.layers[2].lin.weight.detach())

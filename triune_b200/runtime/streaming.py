@@ -80,13 +80,48 @@ class LayerStore:
         self.bind(self.host)
 
 
+_LAYER_PATHS = ("layers", "model.layers", "model.decoder.layers", "transformer.h", "transformer.blocks", "gpt_neox.layers",
+                "decoder.layers", "encoder.layer", "h", "blocks")
+
+
+def find_layer_list(model: nn.Module, layers_attr: Optional[str] = None) -> nn.ModuleList:
+    """The stack of repeated blocks to stream: ``layers_attr`` (dotted path) when given, else the usual places of this
+    framework's models and of Hugging Face causal LMs, else the longest ``nn.ModuleList`` of same-typed modules
+    (``triune/runtime/streaming.py:153-260`` of the reference probes the same way)."""
+    def walk(path):
+        obj = model
+        for part in path.split("."):
+            obj = getattr(obj, part, None)
+            if obj is None:
+                return None
+        return obj if isinstance(obj, (nn.ModuleList, list, tuple)) and len(obj) > 0 else None
+
+    if layers_attr:
+        found = walk(layers_attr)
+        if found is None:
+            raise AttributeError(f"model has no layer list at '{layers_attr}'")
+        return found
+    for path in _LAYER_PATHS:
+        found = walk(path)
+        if found is not None:
+            return found
+    best = None
+    for m in model.modules():
+        if isinstance(m, nn.ModuleList) and len(m) > 1 and len({type(c) for c in m}) == 1:
+            if best is None or len(m) > len(best):
+                best = m
+    if best is None:
+        raise AttributeError("no stack of repeated layers found; pass layers_attr")
+    return best
+
+
 class LayerStreamingEngine:
-    def __init__(self, model: nn.Module, device, config: Optional[StreamingConfig] = None, layers_attr: str = "layers"):
+    def __init__(self, model: nn.Module, device, config: Optional[StreamingConfig] = None, layers_attr: Optional[str] = None):
         self.model = model
         self.device = torch.device(device)
         self.cfg = config or StreamingConfig()
         self.cuda = self.device.type == "cuda"
-        self.layers: List[nn.Module] = list(getattr(model, layers_attr))
+        self.layers: List[nn.Module] = list(find_layer_list(model, layers_attr))
         pin = self.cuda if self.cfg.pin_memory is None else (self.cfg.pin_memory and self.cuda)
         self.resident = set(range(min(self.cfg.resident_gpu_layers, len(self.layers))))
         self.stores: Dict[int, LayerStore] = {}
