@@ -65,6 +65,8 @@ def main():
                     help="streamed layers: the engine's built-in AdamW, or the tiered optimizer (AdamW / Muon / CentroidSteer "
                          "through step_parameters, one layer's state on the device at a time)")
     ap.add_argument("--state-dtype", default="fp32", choices=["fp32", "bf16"], help="host format of the tiered optimizer's moments")
+    ap.add_argument("--fp8-weights", action="store_true", help="stage the forward / backward weights as E4M3 + block scales")
+    ap.add_argument("--grad-dtype", default="fp32", choices=["fp32", "bf16"], help="format of the gradients between device and host")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("bench_streaming.py needs a CUDA device")
@@ -76,7 +78,8 @@ def main():
     params = sum(p.numel() for p in model.parameters())
     build_s = time.time() - t0
     host = torch.randint(0, cfg.vocab_size, (a.batch, a.seq + 1), generator=torch.Generator().manual_seed(1)).pin_memory()
-    eng = enable_layer_streaming(model, "cuda", config=StreamingConfig(resident_gpu_layers=a.resident_layers))
+    eng = enable_layer_streaming(model, "cuda", config=StreamingConfig(resident_gpu_layers=a.resident_layers, fp8_weights=a.fp8_weights,
+                                                                       grad_dtype=a.grad_dtype))
     last = {}
     root_opt = None
     if a.optimizer == "tiered":
@@ -115,7 +118,8 @@ def main():
            "s_per_step": round(sec, 4), "steps": a.steps, "warmup": a.warmup, "dtype": "bf16",
            "config": {"model": a.model if not a.shape else f"d{a.shape[0]}-L{a.shape[1]}-V{a.vocab}", "params": params,
                       "layers": cfg.num_layers, "hidden_dim": cfg.hidden_dim, "batch": a.batch, "seq_len": a.seq,
-                      "resident_layers": a.resident_layers, "streamed_optimizer": a.optimizer, "state_dtype": a.state_dtype},
+                      "resident_layers": a.resident_layers, "streamed_optimizer": a.optimizer, "state_dtype": a.state_dtype,
+                      "fp8_weights": a.fp8_weights, "grad_dtype": a.grad_dtype},
            "h2d_GB_per_step": round((tel.get("h2d_bytes", 0) - tel0.get("h2d_bytes", 0)) / a.steps / 2**30, 2),
            "peak_gpu_GB": round(torch.cuda.max_memory_allocated() / 2**30, 2), "build_s": round(build_s, 1),
            "final_loss": float(last["loss"]), "impl": "triune_b200"}

@@ -864,3 +864,39 @@ def test_streaming_finds_the_layer_stack_of_foreign_models():
     loss.backward()
     eng.step_streaming_optimizer(None, lr=1e-2)
     assert not torch.equal(before, m.model.layers[2].lin.weight.detach())
+
+
+def test_streaming_fp8_weight_staging_and_bf16_gradient_staging():
+    """``fp8_weights``: the forward / backward passes receive an E4M3 copy (one fp32 scale per 128 elements, 1-D tensors
+    beside it unquantised) and about half the bytes; ``grad_dtype="bf16"`` halves the gradient traffic. The master copy
+    keeps training: the loss of the streamed model stays close to the unquantised one and falls."""
+    from triune_b200.runtime.streaming import StreamingConfig, enable_layer_streaming
+
+    x = torch.randint(0, 256, (2, 16), generator=torch.Generator().manual_seed(0))
+    y = torch.randint(0, 256, (2, 16), generator=torch.Generator().manual_seed(1))
+
+    def run(cfg, steps=3):
+        m = tiny()
+        eng = enable_layer_streaming(m, "cpu", config=cfg)
+        losses = []
+        for _ in range(steps):
+            l = m.forward_loss(x, y, force_depth=2)
+            l = l[0] if isinstance(l, tuple) else l
+            l.backward()
+            eng.step_streaming_optimizer(None, lr=5e-3)
+            losses.append(float(l))
+        return losses, eng
+
+    base, e0 = run(StreamingConfig(resident_gpu_layers=0, pin_memory=False))
+    q, e1 = run(StreamingConfig(resident_gpu_layers=0, pin_memory=False, fp8_weights=True, grad_dtype="bf16"))
+    assert abs(q[0] - base[0]) < 5e-2 and q[-1] < q[0]          # FP8 weights perturb the loss a little; it still falls
+    t0, t1 = e0.get_telemetry(), e1.get_telemetry()
+    st = next(iter(e1.stores.values()))
+    assert st.host_q.dtype == torch.float8_e4m3fn and st.host_grad.dtype == torch.bfloat16
+    assert st.fp8_stage_bytes() < 0.3 * st.numel * 4            # fp32 test model: 1.03 bytes per weight against 4
+    assert t1["h2d_bytes"] < 0.75 * t0["h2d_bytes"]             # weights in: 2 x 1.03 instead of 2 x 4 bytes; gradient back in bf16
+    assert t1["d2h_bytes"] < 0.97 * t0["d2h_bytes"]             # gradient out in bf16, plus the refreshed FP8 copy
+    # norm weights and biases are staged exactly
+    for p, (off, n, shape) in zip(st.params, st.slices):
+        if p.dim() < 2:
+            assert torch.equal(st.expand_fp8("cpu")[off : off + n].view(shape), st.host[off : off + n].view(shape))

@@ -37,6 +37,7 @@ class StreamingConfig:
     resident_gpu_layers: int = 0
     activation_checkpointing: bool = True
     forward_snapshots: bool = True
+    grad_dtype: str = "fp32"  # "bf16": gradients leave the device (and return for the update) in bf16: half the traffic
 
 
 def _round_up(n: int, m: int) -> int:
@@ -48,7 +49,9 @@ class LayerStore:
 
     ALIGN = 64  # elements
 
-    def __init__(self, layer: nn.Module, pin: bool):
+    FP8_BLOCK = 128  # elements per scale of the FP8 staging copy
+
+    def __init__(self, layer: nn.Module, pin: bool, grad_dtype: torch.dtype = torch.float32, fp8: bool = False):
         self.layer = layer
         self.params = [p for p in layer.parameters()]
         # Every tensor starts on a 128-byte boundary of the flat buffers (ALIGN elements covers 2- and 4-byte types):
@@ -57,9 +60,10 @@ class LayerStore:
         self.numel = sum(_round_up(p.numel(), self.ALIGN) for p in self.params)
         dtype = self.params[0].dtype if self.params else torch.float32
         self.host = torch.zeros(self.numel, dtype=dtype)
-        self.host_grad = torch.zeros(self.numel, dtype=torch.float32)
+        self.host_grad = torch.zeros(self.numel, dtype=grad_dtype)
         if pin:
             self.host, self.host_grad = self.host.pin_memory(), self.host_grad.pin_memory()
+        self._pin = pin
         off = 0
         self.slices = []
         for p in self.params:
@@ -71,6 +75,52 @@ class LayerStore:
         self.device_buf: Optional[torch.Tensor] = None
         self.ready: Optional[torch.cuda.Event] = None
         self.grad_sumsq = None
+        # FP8 staging (``StreamingConfig.fp8_weights``): the forward and backward passes receive an E4M3 copy with one
+        # fp32 scale per 128 elements (1.03 bytes per weight over PCIe instead of 2) and expand it on the device; tensors
+        # with fewer than two dimensions (norm weights, biases) travel beside it unquantised. The master copy in
+        # ``host`` is what the optimizer updates; ``refresh_fp8`` re-derives the staging copy afterwards.
+        self.fp8 = bool(fp8)
+        self.host_q = self.host_scale = self.host_small = None
+        self.small_slices = [(off, n) for p, (off, n, _) in zip(self.params, self.slices) if p.dim() < 2]
+        if self.fp8:
+            self.refresh_fp8()
+
+    def refresh_fp8(self, source: Optional[torch.Tensor] = None) -> None:
+        """(Re)build the FP8 staging copy from ``source`` (a flat tensor in this store's layout, any device; default: the
+        host master)."""
+        B = self.FP8_BLOCK
+        src = self.host if source is None else source
+        padded = -(-self.numel // B) * B
+        w = torch.zeros(padded, dtype=torch.float32, device=src.device)
+        w[: self.numel] = src.float()
+        blocks = w.view(-1, B)
+        scale = (blocks.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
+        q = (blocks / scale[:, None]).to(torch.float8_e4m3fn).view(-1)
+        small = torch.cat([src[o : o + n] for o, n in self.small_slices]) if self.small_slices else src[:0]
+        if self.host_q is None:
+            mk = (lambda t: t.pin_memory()) if self._pin else (lambda t: t)
+            self.host_q = mk(torch.empty(padded, dtype=torch.float8_e4m3fn))
+            self.host_scale = mk(torch.empty(padded // B, dtype=torch.float32))
+            self.host_small = mk(torch.empty(small.numel(), dtype=self.host.dtype))
+        self.host_q.copy_(q, non_blocking=True)
+        self.host_scale.copy_(scale, non_blocking=True)
+        self.host_small.copy_(small.to(self.host.dtype), non_blocking=True)
+
+    def fp8_stage_bytes(self) -> int:
+        return self.host_q.numel() + self.host_scale.numel() * 4 + self.host_small.numel() * self.host_small.element_size()
+
+    def expand_fp8(self, device) -> torch.Tensor:
+        """Copy the FP8 staging set to ``device`` and expand it to this store's flat layout in the model dtype."""
+        nb = self.host_q.is_pinned()
+        q = self.host_q.to(device, non_blocking=nb)
+        sc = self.host_scale.to(device, non_blocking=nb)
+        small = self.host_small.to(device, non_blocking=nb)
+        buf = (q.float().view(-1, self.FP8_BLOCK) * sc[:, None]).view(-1)[: self.numel].to(self.host.dtype)
+        pos = 0
+        for o, n in self.small_slices:
+            buf[o : o + n] = small[pos : pos + n]
+            pos += n
+        return buf
 
     def bind(self, buf: torch.Tensor):
         for p, (off, n, shape) in zip(self.params, self.slices):
@@ -181,7 +231,8 @@ class LayerStreamingEngine:
                 layer.to(self.device)
                 continue
             layer.to("cpu")
-            self.stores[i] = LayerStore(layer, self._pin)
+            self.stores[i] = LayerStore(layer, self._pin, torch.bfloat16 if self.cfg.grad_dtype == "bf16" else torch.float32,
+                                        fp8=self.cfg.fp8_weights)
             layer_params.update(id(p) for p in layer.parameters())
             self._wrap(i, layer)
         # root: everything that is not a streamed layer
@@ -243,14 +294,17 @@ class LayerStreamingEngine:
         st = self.stores[i]
         if st.device_buf is not None:
             return
+        nbytes = st.fp8_stage_bytes() if st.fp8 else st.host.numel() * st.host.element_size()
         if not self.cuda:
-            st.device_buf = st.host
+            st.device_buf = st.expand_fp8(self.device) if st.fp8 else st.host
+            self.telemetry["h2d_bytes"] += nbytes
+            self.telemetry["h2d_copies"] += 1
             return
         with torch.cuda.stream(self.h2d_stream):
-            st.device_buf = st.host.to(self.device, non_blocking=True)
+            st.device_buf = st.expand_fp8(self.device) if st.fp8 else st.host.to(self.device, non_blocking=True)
             st.ready = torch.cuda.Event()
             st.ready.record(self.h2d_stream)
-        self.telemetry["h2d_bytes"] += st.host.numel() * st.host.element_size()
+        self.telemetry["h2d_bytes"] += nbytes
         self.telemetry["h2d_copies"] += 1
 
     def stage(self, i: int, prefetch: Optional[int] = None):
@@ -292,13 +346,14 @@ class LayerStreamingEngine:
         if self.cuda:
             self.d2h_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.d2h_stream):
-                acc = flat if self._first_micro(i) else flat + st.host_grad.to(self.device, non_blocking=True)
-                st.host_grad.copy_(acc, non_blocking=True)
+                acc = flat if self._first_micro(i) else flat + st.host_grad.to(self.device, non_blocking=True).float()
+                st.host_grad.copy_(acc.to(st.host_grad.dtype), non_blocking=True)
                 flat.record_stream(self.d2h_stream)
         else:
-            st.host_grad.add_(flat) if not self._first_micro(i) else st.host_grad.copy_(flat)
+            acc = flat if self._first_micro(i) else flat + st.host_grad.float()
+            st.host_grad.copy_(acc.to(st.host_grad.dtype))
         st._has_grad = True
-        self.telemetry["d2h_bytes"] += st.numel * 4
+        self.telemetry["d2h_bytes"] += st.numel * st.host_grad.element_size()
         self.telemetry["d2h_copies"] += 1
 
     def _first_micro(self, i: int) -> bool:
@@ -365,11 +420,14 @@ class LayerStreamingEngine:
         last_of_group = {id(pool.group_of(i)): i for i in ids}
         for i in ids:
             st = self.stores[i]
-            g = st.host_grad.to(self.device, non_blocking=True)
-            self.telemetry["h2d_bytes"] += st.numel * 4
+            g = st.host_grad.to(self.device, non_blocking=True).float()
+            self.telemetry["h2d_bytes"] += st.numel * st.host_grad.element_size()
             pool.step_layer(i, g, coef, is_global_step_end=(last_of_group[id(pool.group_of(i))] == i))
             if self.cuda:
                 torch.cuda.current_stream(self.device).synchronize()  # host_grad / host are reused right away
+            if st.fp8:
+                st.refresh_fp8()
+                self.telemetry["d2h_bytes"] += st.fp8_stage_bytes() if self.cuda else 0
             st.host_grad.zero_()
             st.grad_sumsq = None
             st._has_grad = False
@@ -385,7 +443,7 @@ class LayerStreamingEngine:
                 self.opt_state[i]["master"].copy_(st.host.float())
             os_ = self.opt_state[i]
             dev = self.device
-            g = st.host_grad.to(dev, non_blocking=True) * coef
+            g = st.host_grad.to(dev, non_blocking=True).float() * coef
             m, v, w = (os_[k].to(dev, non_blocking=True) for k in ("m", "v", "master"))
             m.mul_(b1).add_(g, alpha=1 - b1)
             v.mul_(b2).addcmul_(g, g, value=1 - b2)
@@ -393,11 +451,15 @@ class LayerStreamingEngine:
             os_["m"].copy_(m, non_blocking=True)
             os_["v"].copy_(v, non_blocking=True)
             os_["master"].copy_(w, non_blocking=True)
-            st.host.copy_(w.to(st.host.dtype), non_blocking=True)
+            wq = w.to(st.host.dtype)
+            st.host.copy_(wq, non_blocking=True)
+            if st.fp8:  # the staging copy follows the update: quantised on the device, written back beside the master
+                st.refresh_fp8(wq)
+                self.telemetry["d2h_bytes"] += st.fp8_stage_bytes()
             st.host_grad.zero_()
             st.grad_sumsq = None
             st._has_grad = False
-            self.telemetry["h2d_bytes"] += st.numel * 16
+            self.telemetry["h2d_bytes"] += st.numel * (12 + st.host_grad.element_size())
             self.telemetry["d2h_bytes"] += st.numel * 14
 
     def get_telemetry(self) -> Dict[str, int]:
