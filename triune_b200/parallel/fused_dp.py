@@ -38,9 +38,13 @@ class SymmetricArenaStorage:
     """``storage_factory`` for :class:`ParamArena` that places both arenas in a :class:`SymmetricBuffer`."""
 
     def __init__(self, ctx, use_multimem=None, group=None):
+        """``use_multimem``: ``None`` (default) = plain peer loads and stores. With four loads in flight per thread they
+        match the in-switch reduction at 8 ranks (0.57 against 0.58 ms for 96 M parameters) and beat it at 2 (0.34 against
+        0.64 ms), and a rank that dies while bound to a multicast object can fault its peers' GPUs; ``True`` asks for
+        ``multimem`` where the heap reports multicast support."""
         self.ctx = ctx
         self.group = group
-        self.use_multimem = use_multimem
+        self.use_multimem = False if use_multimem is None else bool(use_multimem)
         self.buffer = None
         self.total = 0
 
