@@ -37,7 +37,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--params", type=float, default=100e6)
     ap.add_argument("--mode", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--multimem", type=int, default=-1, help="-1: as the symmetric heap reports; 0 / 1 force peer loads / multimem")
+    ap.add_argument("--multimem", type=int, default=-1, help="-1 or 0: plain peer loads and stores (the default); 1: multimem through the switch where supported")
     ap.add_argument("--matrix-frac", type=float, default=0.0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
