@@ -785,3 +785,34 @@ def test_convergence_evaluation_all_optimizers_learn():
         r = cv.run(opt, "dense", steps=30, vocab=64, width=32, layers=2, batch=8, seq_len=32, lr=3e-3, device="cpu")
         assert abs(r["loss_start"] - math.log(64)) < 0.5 and r["loss_end"] < r["loss_start"] - 0.5, r
         assert r["loss_end"] > r["entropy_floor"] - 0.05 and r["ms_per_step"] > 0 and r["optimizer_state_bytes"] > 0
+
+
+def test_merge_shards_rejects_incomplete_and_mixed_sets(tmp_path):
+    """The merge tool refuses a directory with a missing rank, shard sets of two sizes, and slices that do not cover a
+    parameter exactly once."""
+    import pytest
+
+    from triune_b200.trainer.checkpoint import _atomic_save
+    from triune_b200.trainer.sharded_checkpoint import FORMAT, merge_shards, shard_path
+
+    def shard(rank, world, pieces, replicated=None):
+        _atomic_save({"format": FORMAT, "rank": rank, "world": world, "step": 1, "loss": 0.0, "pieces": pieces,
+                      "replicated": replicated or {}, "optimizer_state": None, "config": {}, "architecture": None},
+                     shard_path(str(tmp_path), rank, world))
+
+    w = torch.arange(24.0).view(6, 4)
+    shard(0, 2, [("w", 0, 0, 3, 6, w[:3].clone())], {"b": torch.ones(2)})
+    with pytest.raises(ValueError, match="expected shards"):
+        merge_shards(str(tmp_path))
+    shard(1, 2, [("w", 0, 3, 6, 6, w[3:].clone())])
+    merged = merge_shards(str(tmp_path), str(tmp_path / "m.pt"))
+    assert torch.equal(merged["model_state"]["w"], w) and torch.equal(merged["model_state"]["b"], torch.ones(2))
+    assert merged["merged_from"]["shards"] == 2 and (tmp_path / "m.pt").exists()
+    shard(1, 2, [("w", 0, 3, 5, 6, w[3:5].clone())])  # one row never written
+    with pytest.raises(ValueError, match="incomplete or overlapping"):
+        merge_shards(str(tmp_path))
+    shard(0, 3, [])
+    with pytest.raises(ValueError, match="different sizes"):
+        merge_shards(str(tmp_path))
+    with pytest.raises(FileNotFoundError):
+        merge_shards(str(tmp_path / "nothing"))
