@@ -386,7 +386,10 @@ def run_reference(args):
     # The same step through the reference's own Trainer / TrainingEngine.step_once in cortex mode (its data prefetcher,
     # its sub-batch slicing, its loss bookkeeping). The faster of the two loops is the reference's number.
     engine_ms, engine_note = None, None
-    if args.ref_loop in ("engine", "both"):
+    # With "both" the engine loop is only taken on one GPU: it is nine times slower than the hand-written loop there
+    # (eight 4096-token sub-batches per step), so it cannot be the faster one, and under DDP every sub-batch backward
+    # is one more gradient all-reduce.
+    if args.ref_loop == "engine" or (args.ref_loop == "both" and world == 1):
         try:
             engine_ms = _reference_engine_loop(args, train_model, opt, pool, dev, rank, world)
         except Exception as e:
