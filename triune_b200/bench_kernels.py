@@ -285,7 +285,55 @@ def case_nvfp4(a):
     report(f"nvfp4 W4A16 linear (decode + bf16 GEMM) {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
 
 
-CASES = {"mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
+def case_dp(a):
+    """The two data-parallel step kernels on a world of ONE rank (a loop-back peer table: the rank's own buffer is its
+    only peer), so their instruction and memory counters can be profiled without a second GPU waiting on a flag. The
+    NVLink figures come from ``bench_dp.py`` on 2 and 8 GPUs."""
+    import os
+
+    import torch.distributed as dist
+
+    from . import _ext
+    from .parallel.symm import SymmetricBuffer
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29591")
+    dev = torch.device("cuda", 0)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    n = (a.m * a.k) // 1024 * 1024  # parameters of the synthetic arena (default 8192 * 8192 = 67 M)
+    buf = SymmetricBuffer({"param": n * 2, "grad": n * 4, "norm": 2 * 4 + 64}, dev, use_multimem=False)
+    buf.view("grad", torch.float32, n).normal_()
+    master = torch.randn(n, device=dev) * 0.02
+    m1, v1 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    counter = torch.zeros(1, device=dev, dtype=torch.int32)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    clip, norm = torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+    e = _ext.ext()
+    rank, world, bufs, sigs, mc = buf.table()
+    goff, noff, poff = buf.offset("grad"), buf.offset("norm"), buf.offset("param")
+    state = {"ep": 0}
+
+    def rs():
+        state["ep"] += 1
+        e.dp_reduce_scatter(rank, world, bufs, sigs, mc, goff, noff, [0, n], state["ep"], False, counter, status, None)
+
+    def ag():
+        # the reduce-scatter of the same epoch publishes the norm partial this kernel waits for
+        rs()
+        e.dp_adamw_allgather(rank, world, bufs, sigs, mc, goff, noff, poff, 0, n, 0, master, m1, v1, 1e-4, 0.9, 0.95, 1e-8, 0.05,
+                             state["ep"], 1.0, clip, norm, state["ep"], False, status, None, None)
+
+    ms_rs = timeit(rs, a.iters, a.warmup)
+    report(f"dp_reduce_scatter, one rank, {n} parameters", ms_rs, nbytes=8.0 * n)
+    ms_both = timeit(ag, a.iters, a.warmup)
+    report(f"dp_adamw_allgather, one rank, {n} parameters (time of the pair minus the reduce-scatter)", max(ms_both - ms_rs, 1e-6),
+           nbytes=30.0 * n)
+    print(json.dumps({"case": "dp", "wait_status": int(status.item())}))
+    dist.destroy_process_group()
+
+
+CASES = {"dp": case_dp, "mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():
