@@ -333,7 +333,41 @@ def case_dp(a):
     dist.destroy_process_group()
 
 
-CASES = {"dp": case_dp, "mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
+def case_tp(a):
+    """The fused tensor-parallel GEMMs (all-gather -> GEMM with in-kernel fetch warps and chunk flags; GEMM ->
+    reduce-scatter with TMA reduce-add into the owner's buffer) on a world of ONE rank, for profiler counters: the
+    whole kernel runs (flags, bounded waits, the reduce-add epilogue), only the remote rows are missing. The NVLink
+    figures come from the 2- and 8-GPU runs of ``tests/mp_tp_worker.py`` and ``bench_tp.py``."""
+    import os
+
+    import torch.distributed as dist
+
+    from .parallel import tensor_parallel as tpm
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29592")
+    dev = torch.device("cuda", 0)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    ctx = tpm.TPContext(device=dev, mode="fused")
+    ctx.mode = "fused"  # a one-rank context falls back to plain GEMMs by default; here the fused kernels are the point
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    ms = timeit(lambda: tpm._ag_gemm_fused(ctx, x, w, False), a.iters, a.warmup)
+    report(f"all-gather GEMM (fused kernel, one rank) {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
+    ms = timeit(lambda: tpm._gemm_rs_fused(ctx, x, w, False), a.iters, a.warmup)
+    report(f"GEMM reduce-scatter (fused kernel, one rank, incl. zero fill, two signal rounds and the copy out) {M}x{N}x{K}", ms,
+           flops=2.0 * M * N * K)
+    from .ops import gemm
+
+    ms = timeit(lambda: gemm(x, w), a.iters, a.warmup)
+    report(f"plain tcgen05 GEMM {M}x{N}x{K}", ms, flops=2.0 * M * N * K)
+    print(json.dumps({"case": "tp", "wait_status": int(ctx.check())}))
+    dist.destroy_process_group()
+
+
+CASES = {"tp": case_tp, "dp": case_dp, "mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():
