@@ -816,3 +816,20 @@ def test_merge_shards_rejects_incomplete_and_mixed_sets(tmp_path):
         merge_shards(str(tmp_path))
     with pytest.raises(FileNotFoundError):
         merge_shards(str(tmp_path / "nothing"))
+
+
+def test_expert_parallel_reduction_runs_follow_the_received_counts():
+    """The run list of the bounded weight-gradient reductions: one run per (local expert, source rank) segment of the
+    expert-major buffer, as many 64-row blocks as hold rows, counts above the capacity clamped."""
+    from types import SimpleNamespace
+
+    from triune_b200.parallel.expert_parallel import EPContext
+
+    W, El, cap = 3, 2, 256
+    cnt_all = torch.tensor([[0, 65], [64, 300], [1, 128]], dtype=torch.int32).reshape(-1)  # [source rank, local expert]
+    runs, offs = EPContext.reduction_runs(SimpleNamespace(experts_per_rank=El, world=W), cnt_all, cap)
+    assert runs.dtype == torch.int32 and offs.dtype == torch.int32
+    assert offs.tolist() == [0, 3, 6]
+    # segment order is expert-major: (e0, r0), (e0, r1), (e0, r2), (e1, r0), ...
+    assert runs[:, 0].tolist() == [0, 256, 512, 768, 1024, 1280]
+    assert runs[:, 1].tolist() == [0, 1, 1, 2, 4, 2]

@@ -121,6 +121,44 @@ def test_gemm_cta_pairs_grouped_k(dev):
     assert _rel(acc[1], 1.0 + a[1536:].float().t() @ b[1536:].float()) < 2e-3
 
 
+@pytest.mark.parametrize("M,N,pair", [(256, 384, True), (256, 256, True), (128, 192, False), (8, 384, False)])
+def test_gemm_grouped_k_over_run_list(dev, M, N, pair):
+    """Reduction grouped by expert over a list of row runs (partly filled fixed-capacity segments): only the listed
+    64-row blocks are read, empty runs and an empty group included, on the CTA-pair and the one-CTA kernel."""
+    from triune_b200 import _ext, ops
+
+    torch.manual_seed(14)
+    cap, segs = 1024, 8  # eight segments of 1024 rows; groups of 3, 3, 0 and 2 runs
+    R = cap * segs
+    blocks = [5, 0, 16, 1, 7, 0, 0, 0]  # 64-row blocks that hold rows, per segment
+    runs = torch.tensor([[s * cap, n] for s, n in enumerate(blocks)], device=dev, dtype=torch.int32)
+    offs = torch.tensor([0, 3, 6, 6, 8], device=dev, dtype=torch.int32)
+    a = torch.randn(R, M, device=dev, dtype=torch.bfloat16) * 0.25
+    b = torch.randn(R, N, device=dev, dtype=torch.bfloat16) * 0.25
+    # poison every row outside the listed blocks: a kernel that reads them shows up as NaN
+    live = torch.zeros(R, dtype=torch.bool, device=dev)
+    for s, n in enumerate(blocks):
+        live[s * cap : s * cap + 64 * n] = True
+    a[~live] = float("nan")
+    b[~live] = float("nan")
+    before = _ext.ext().tc_gemm_pair_launches()
+    out = ops.gemm(a, b, a_mn=True, b_mn=True, mode=ops.GEMM_GROUPED_K, group_offsets=offs, num_groups=4,
+                   out_dtype=torch.float32, k_runs=runs)
+    assert (_ext.ext().tc_gemm_pair_launches() == before + 1) == pair
+    af, bf = torch.nan_to_num(a.float()), torch.nan_to_num(b.float())
+    for g, (r0, r1) in enumerate(((0, 3), (3, 6), (6, 6), (6, 8))):
+        ref = af[r0 * cap : r1 * cap].t() @ bf[r0 * cap : r1 * cap] if r1 > r0 else torch.zeros(M, N, device=dev)
+        assert torch.isfinite(out[g]).all()
+        assert float((out[g] - ref).abs().max()) < 2e-3 * max(1.0, float(ref.abs().max())), g
+    assert float(out[2].abs().max()) == 0.0 and float(out[3].abs().max()) == 0.0
+    acc = torch.ones(4, M, N, device=dev, dtype=torch.float32)
+    ops.gemm(a, b, acc, a_mn=True, b_mn=True, accumulate=True, mode=ops.GEMM_GROUPED_K, group_offsets=offs, num_groups=4,
+             k_runs=runs)
+    ref1 = 1.0 + af[3 * cap : 6 * cap].t() @ bf[3 * cap : 6 * cap]
+    assert float((acc[1] - ref1).abs().max()) < 2e-3 * float(ref1.abs().max())
+    assert float((acc[2] - 1.0).abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("Dk,Dv", [(128, 128), (128, 64), (64, 192)])
 def test_gla_wide_heads_match_recurrence(dev, Dk, Dv):
     """Heads wider than 64 run on the 64-wide kernels as sums of independent key / value slices."""

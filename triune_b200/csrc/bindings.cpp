@@ -33,7 +33,7 @@ void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool 
              double alpha, const c10::optional<Tensor>& bias, const c10::optional<Tensor>& aux_in,
              const c10::optional<Tensor>& aux_out, const c10::optional<Tensor>& row_scale,
              const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& group_offsets,
-             const c10::optional<Tensor>& status, double beta) {
+             const c10::optional<Tensor>& status, double beta, const c10::optional<Tensor>& k_runs) {
   check_bf16_cuda(a, "a");
   check_bf16_cuda(b, "b");
   TORCH_CHECK(c.is_cuda(), "c must be CUDA");
@@ -110,6 +110,13 @@ void tc_gemm(const Tensor& a, const Tensor& b, Tensor& c, bool a_mn_major, bool 
   if (status.has_value() && status->defined()) {
     TORCH_CHECK(status->scalar_type() == at::kInt, "status must be int32");
     g.status = status->data_ptr<int>();
+  }
+  if (k_runs.has_value() && k_runs->defined()) {
+    TORCH_CHECK(mode == tb::GEMM_GROUPED_K && g.group_offsets != nullptr, "k_runs belongs to the grouped-K mode");
+    TORCH_CHECK(k_runs->is_cuda() && k_runs->scalar_type() == at::kInt && k_runs->is_contiguous() && k_runs->dim() == 2 &&
+                    k_runs->size(1) == 2,
+                "k_runs must be a contiguous CUDA int32 tensor [runs, 2]");
+    g.k_runs = k_runs->data_ptr<int>();
   }
   tb::launch_tc_gemm(g, cur_stream());
 }

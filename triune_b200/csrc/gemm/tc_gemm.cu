@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         Tile tl = decode_tile(p, t);
         if (!tl.valid) continue;
         const int n0 = tl.n0 * NOUT;
+        int run = tl.k_begin, run_left = 0, run_pos = 0;  // run-list walk (grouped-K with k_runs)
         for (int it = 0; it < tl.k_iters; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             report(p, ST_TIMEOUT_EMPTY);
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             break;
           }
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          const int k0 = tl.k_begin + it * BK;
+          const int k0 = p.k_runs ? run_list_next(p.k_runs, run, tl.k_end, run_left, run_pos) : tl.k_begin + it * BK;
           uint8_t* a_dst = smemA + stage * Cfg::A_BYTES;
           uint8_t* b_dst = smemB + stage * Cfg::B_BYTES;
           if (A_MN) {
@@ -363,6 +364,7 @@ void launch_tc_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
   kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.k_runs = a.mode == GEMM_GROUPED_K ? a.k_runs : nullptr;
   kp.dbg = g_gemm_dbg;
   kp.total_tiles = kp.num_m * kp.num_n * (a.mode == GEMM_GROUPED_M ? 1 : kp.batch);
   kp.splits = 1;

@@ -46,6 +46,10 @@ struct GemmArgs {
   const float* row_scale;       // [M] or null
   const int* tile_group;        // GEMM_GROUPED_M: [ceil(M/128)], -1 marks an unused tile
   const int* group_offsets;     // GEMM_GROUPED_K: [batch+1], multiples of 64
+  // GEMM_GROUPED_K, optional: [runs][2] = (first row, number of 64-row blocks) of the row runs to reduce over. With it
+  // group_offsets[g] .. group_offsets[g+1] index RUNS instead of rows, so a group may skip rows that hold nothing
+  // (segments of a fixed-capacity buffer that are only partly filled). First rows must be multiples of 64.
+  const int* k_runs;
   int* status;                  // optional device status word (see KernelStatus)
   int n_split;                  // GF_SWIGLU / GF_DSWIGLU: FFN hidden width (N); 0 otherwise
   float beta;                   // GF_ADDAUX: weight of aux_in

@@ -40,6 +40,7 @@ struct KParams {
   const float* row_scale;
   const int* tile_group;
   const int* group_offsets;
+  const int* k_runs;    // grouped-K over a run list: (first row, 64-row blocks) pairs; group_offsets then index runs
   int* status;
   long long* dbg;       // optional phase timers (clock ticks summed over one warp's chunks), null in normal runs
   int total_tiles;
@@ -52,8 +53,32 @@ struct KParams {
 
 struct Tile {
   int m0, n0, ba, bb, g, k_begin, k_iters;
+  int k_end;  // run-list mode: k_begin .. k_end are the group's runs, k_iters the blocks in them
   bool valid;
 };
+
+// Grouped-K over a run list: 64-row blocks in runs [r0, r1) (a negative count reads as an empty run).
+__device__ __forceinline__ int run_list_blocks(const int* __restrict__ runs, int r0, int r1) {
+  int s = 0;
+  for (int r = r0; r < r1; ++r) {
+    const int n = runs[2 * r + 1];
+    s += n > 0 ? n : 0;
+  }
+  return s;
+}
+// The producer's walk over a group's runs: `run` starts at Tile::k_begin with left = 0; returns the first row of the
+// next block. Called exactly Tile::k_iters times, so a non-empty run is always ahead.
+__device__ __forceinline__ int run_list_next(const int* __restrict__ runs, int& run, int run_end, int& left, int& kpos) {
+  while (left <= 0 && run < run_end) {
+    kpos = runs[2 * run];
+    left = runs[2 * run + 1];
+    ++run;
+  }
+  const int k0 = kpos;
+  kpos += 64;
+  --left;
+  return k0;
+}
 
 // Tile order. The CTAs of one wave should share as many operand tiles as possible: the tiles are walked in blocks
 // of group_m row tiles x all num_n column tiles, row tile fastest inside a block, and group_m * num_n is about the
@@ -107,7 +132,8 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
       tl.bb = 0;
       int k0 = p.group_offsets[b], k1 = p.group_offsets[b + 1];
       tl.k_begin = k0;
-      tl.k_iters = (k1 - k0 + BK - 1) / BK;
+      tl.k_end = k1;
+      tl.k_iters = p.k_runs ? run_list_blocks(p.k_runs, k0, k1) : (k1 - k0 + BK - 1) / BK;
     } else {
       tl.ba = p.a_batched ? b : 0;
       tl.bb = p.b_batched ? b : 0;

@@ -67,7 +67,8 @@ __device__ __forceinline__ Tile decode_pair_tile(const KParams& p, int t, int nu
     tl.g = split;
     const int k0 = p.group_offsets[split], k1 = p.group_offsets[split + 1];
     tl.k_begin = k0;
-    tl.k_iters = (k1 - k0 + BK - 1) / BK;
+    tl.k_end = k1;
+    tl.k_iters = p.k_runs ? run_list_blocks(p.k_runs, k0, k1) : (k1 - k0 + BK - 1) / BK;
   } else if (p.splits > 1) {
     tl.k_begin = split * p.iters_per_split * BK;
     const int left = total_iters - split * p.iters_per_split;
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (!tl.valid) continue;
         const int n0 = tl.n0 * NOUT;
         const int m0 = tl.m0 + (int)rank * BM;
+        int run = tl.k_begin, run_left = 0, run_pos = 0;  // run-list walk (grouped-K with k_runs)
         for (int it = 0; it < tl.k_iters; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             report(p, ST_TIMEOUT_EMPTY);
@@ -149,7 +151,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           }
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
           const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
-          const int k0 = tl.k_begin + it * BK;
+          const int k0 = p.k_runs ? run_list_next(p.k_runs, run, tl.k_end, run_left, run_pos) : tl.k_begin + it * BK;
           uint8_t* a_dst = smemA + stage * Cfg::A_BYTES;
           uint8_t* b_dst = smemB + stage * Cfg::B_BYTES;
           if (A_MN) {
@@ -414,6 +416,7 @@ bool launch_tc_gemm_pair(const GemmArgs& a, cudaStream_t stream) {
   kp.C = a.C; kp.bias = a.bias; kp.bias_stride = a.bias_stride;
   kp.aux_in = a.aux_in; kp.aux_out = a.aux_out; kp.row_scale = a.row_scale;
   kp.tile_group = a.tile_group; kp.group_offsets = a.group_offsets; kp.status = a.status;
+  kp.k_runs = grouped_k ? a.k_runs : nullptr;
   kp.dbg = nullptr;
   kp.splits = 1;
   kp.iters_per_split = 0;

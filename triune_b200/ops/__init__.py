@@ -76,6 +76,7 @@ def gemm(
     paired_groups: bool = False,
     add_aux: Optional[torch.Tensor] = None,
     beta: float = 1.0,
+    k_runs: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """out = alpha * A @ B^T with a fused epilogue, on tcgen05 tensor cores.
 
@@ -87,6 +88,9 @@ def gemm(
     ``add_aux`` (bf16, out's layout) forms ``out = alpha * A @ B^T + beta * add_aux`` in the epilogue.
     ``paired_groups`` (rows grouped by expert only) promises that every expert's rows are padded to a multiple of 256,
     which lets long reductions run on CTA pairs.
+    ``k_runs`` (reduction grouped by expert only; int32 [runs, 2] = first row, number of 64-row blocks): the rows each
+    group reduces over as a list of runs, ``group_offsets`` then indexing runs instead of rows, so partly filled
+    segments of a fixed-capacity buffer cost only the blocks that hold rows.
     """
     assert _tma_ok(a) and _tma_ok(b), "gemm operands must be CUDA bf16 with 16-byte aligned rows"
     if mode == GEMM_GROUPED_K:
@@ -109,7 +113,7 @@ def gemm(
         aux_in = add_aux
     _ext.ext().tc_gemm(
         a, b, out, a_mn, b_mn, mode, flags, float(alpha), bias, aux_in, aux_out, row_scale, tile_group,
-        group_offsets, None, float(beta),
+        group_offsets, None, float(beta), k_runs,
     )
     _tick()
     return out

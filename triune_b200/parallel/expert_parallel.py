@@ -43,6 +43,22 @@ class EPContext:
         self._epochs: Dict[Tuple, int] = {}
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.comm_bytes = 0
+        # The weight- and bias-gradient GEMMs reduce only over the 64-row blocks of each (expert, source rank) segment
+        # that hold tokens (a run list built from the received counts on the device) instead of whole capacity ranges.
+        self.bounded_wgrad = True
+
+    def reduction_runs(self, cnt_all: torch.Tensor, cap: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(k_runs [El * W, 2] int32, run offsets [El + 1] int32) for ``ops.gemm(mode=GEMM_GROUPED_K, k_runs=...)``.
+
+        ``cnt_all`` [W, El] holds the rows each source rank sent to each local expert; segment ``el * W + src`` of the
+        expert-major buffer starts at row ``(el * W + src) * cap`` and holds ``min(count, cap)`` rows. No host read."""
+        El, W = self.experts_per_rank, self.world
+        cnt = cnt_all.view(W, El).t().reshape(-1).clamp(min=0, max=cap)
+        blocks = torch.div(cnt + 63, 64, rounding_mode="floor").to(torch.int32)
+        starts = torch.arange(El * W, device=cnt.device, dtype=torch.int32) * cap
+        runs = torch.stack((starts, blocks), dim=1).contiguous()
+        offs = (torch.arange(El + 1, device=cnt.device, dtype=torch.int32) * W).contiguous()
+        return runs, offs
 
     def capacity(self, n_assign: int) -> int:
         """Rows reserved per (expert, source rank) segment: capacity_factor x the mean load, rounded up to 128."""
@@ -167,18 +183,24 @@ class _EPExpertsFn(torch.autograd.Function):
         dpre = torch.empty(rows, H, dtype=dout.dtype, device=dout.device)
         gemm(dyin, w2, dpre, b_mn=True, dgelu_aux=dact, mode=GEMM_GROUPED_M, tile_group=tile_group)
         e.ep_zero_invalid_rows(dpre, cnt_all, El, W, cap)  # rows of skipped tiles (the others are 0 * finite already)
-        offs = (torch.arange(El + 1, device=dout.device, dtype=torch.int32) * (W * cap)).contiguous()
+        if ep.bounded_wgrad:
+            # rows past a segment's count are zero in every operand below, so whole 64-row blocks are safe to include
+            runs, offs = ep.reduction_runs(cnt_all, cap)
+        else:
+            runs, offs = None, (torch.arange(El + 1, device=dout.device, dtype=torch.int32) * (W * cap)).contiguous()
         ones = torch.ones(rows, 8, device=dout.device, dtype=dout.dtype)
 
         def wgrad(w, a, b):
             mg = getattr(w, "main_grad", None)
             if mg is not None:
-                gemm(a, b, mg, a_mn=True, b_mn=True, accumulate=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El)
+                gemm(a, b, mg, a_mn=True, b_mn=True, accumulate=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El,
+                     k_runs=runs)
                 return None
-            return gemm(a, b, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El)
+            return gemm(a, b, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El, k_runs=runs)
 
         def bgrad(bp, a):
-            s = gemm(ones, a, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El, out_dtype=torch.float32)[:, 0, :]
+            s = gemm(ones, a, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_offsets=offs, num_groups=El, out_dtype=torch.float32,
+                     k_runs=runs)[:, 0, :]
             mg = getattr(bp, "main_grad", None)
             if mg is not None:
                 mg.add_(s)
