@@ -193,3 +193,54 @@ def test_adapter_export_and_upgrade_guards(client, tmp_path):
     assert client.post("/v1/finetune/export", json={"adapter_path": str(tmp_path / "missing")}).status_code == 404
     assert client.post("/v1/models/upgrade_to_triune", json={"source": "org/some-remote-model"}).status_code == 404
     assert client.post("/v1/models/distill", json={"source": str(tmp_path / "nothing-here")}).status_code == 404
+
+
+def test_canvas_graphs_over_http(client, tmp_path):
+    """The Studio canvas format on the DAG endpoints: execution with node events on the telemetry channel, the run queue,
+    single nodes, the catalogue, and a graph compiled into the live engine's model and training settings."""
+    from triune_b200.serve.engine_state import get_state
+
+    cat = client.get("/v1/nodes/catalog").json()["studio_nodes"]
+    assert len(cat) == 49 and {"TriuneTransformer", "TrainingStep", "Subgraph"} <= {n["name"] for n in cat}
+    assert client.get("/v1/dag/queue").json() == {"active_run_id": None, "waiting": 0, "capacity": 1}
+    corpus = tmp_path / "c.txt"
+    corpus.write_text("a few words of text for the graph to read and tokenise\n")
+    cfg = {"hidden_dim": 64, "num_layers": 4, "num_heads": 1, "num_experts": 4, "vocab_size": 256}
+    g = {"run_id": "run-1", "nodes": [
+        {"id": "d", "type": "Data", "title": "LocalFileReader", "params": {"file_path": str(corpus)}},
+        {"id": "t", "type": "BPETokenizer"},
+        {"id": "m", "type": "Model", "title": "TriuneTransformer", "params": {**cfg, "use_node_config": True}},
+        {"id": "o", "type": "AdamWOptimizer", "params": {"lr": 2e-3, "weight_decay": 0.0}},
+        {"id": "s", "type": "TrainingStep", "params": {"grad_accum_steps": 2, "max_grad_norm": 0.5}},
+    ], "edges": [
+        {"source": "d", "target": "t", "source_port": "text_sample", "target_port": "text"},
+        {"source": "t", "target": "m", "source_port": "tokens", "target_port": "input_ids"},
+        {"source": "m", "target": "o", "source_port": "model_handle", "target_port": "model_handle"},
+        {"source": "m", "target": "s", "source_port": "model_handle", "target_port": "model_handle"},
+        {"source": "o", "target": "s", "source_port": "optimizer_handle", "target_port": "optimizer_handle"},
+        {"source": "t", "target": "s", "source_port": "tokens", "target_port": "tokens"},
+    ]}
+    events = []
+    get_state().telemetry_listeners.append(events.append)
+    out = client.post("/v1/dag/execute", json=g).json()
+    assert out["status"] == "success" and out["run_id"] == "run-1", out
+    assert out["results"]["s"]["output"]["ports"]["step_metrics"]["tokens"] > 0
+    dag_events = [e["data"] for e in events if e.get("type") == "dag_event"]
+    assert [e["event"] for e in dag_events].count("node_finished") == 5 and all(e["run_id"] == "run-1" for e in dag_events)
+    bad = client.post("/v1/dag/execute", json={"nodes": [{"id": "a", "type": "BPETokenizer"}], "edges": [{"source": "a", "target": "b"}]})
+    assert bad.status_code == 422
+    one = client.post("/v1/dag/execute_node", json={"type": "RouterZLoss", "params": {"coeff": 1.0}, "inputs": {}})
+    assert one.json()["status"] == "failed" and "router logits" in one.json()["error"]
+    one = client.post("/v1/dag/execute_node", json={"node": {"type": "Runtime", "title": "Runtime"}})
+    assert one.json()["status"] == "success"
+
+    rec = client.post("/v1/dag/compile_to_training", json=g).json()
+    assert rec["status"] == "compiled" and rec["applied"]["model_architecture"]["num_layers"] == 4
+    assert rec["applied"]["training"] == {"optimizer": "adamw", "lr": 2e-3, "weight_decay": 0.0, "grad_accum_steps": 2, "grad_clip": 0.5}
+    st = get_state()
+    assert st.model is not None and st.model.num_layers == 4 and st.pending_training_config["optimizer"] == "adamw"
+    step = client.post("/v1/training/step", json={"batch_size": 2, "seq_len": 16}).json()
+    assert step["step"] == 1 and step["loss"] > 0
+    assert type(st.trainer.optimizer).__name__ == "AdamW" and st.trainer.optimizer.param_groups[0]["lr"] > 0
+    same = client.post("/v1/model/compile_dag", json={**g, "apply_model": False}).json()
+    assert "model_architecture" not in same["applied"]

@@ -109,6 +109,13 @@ def validate_dag(dag: DAG) -> DAG:
 
 
 def execute_dag(spec_or_dag, context: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+    """Run a graph. Graphs saved by the Studio canvas (edges with ``source`` / ``target``, the canvas' node names) are
+    handed to ``execution/studio.py`` and answer in that format; everything else is this module's own format."""
+    if not isinstance(spec_or_dag, DAG):
+        from .studio import is_studio_graph, run_studio_graph
+
+        if is_studio_graph(spec_or_dag):
+            return run_studio_graph(spec_or_dag, context)
     dag = spec_or_dag if isinstance(spec_or_dag, DAG) else parse_dag(spec_or_dag)
     ctx = context if context is not None else {}
     values: Dict[Tuple[str, str], Any] = {}

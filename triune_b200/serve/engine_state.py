@@ -85,6 +85,7 @@ class EngineState:
         self.lock = threading.RLock()
         self.telemetry_listeners: List[Callable[[Dict[str, Any]], None]] = []
         self.sessions_meta: Dict[str, Dict[str, Any]] = {}
+        self.pending_training_config: Dict[str, Any] = {}  # settings compiled from a canvas graph, used by the next trainer
         self.turbo_mode = False          # greedy requests without a session decode through the graph-replayed decoder
         self._turbo_decoder = None       # (model object, depth) -> GraphedGreedyDecoder, rebuilt when either changes
 
@@ -189,8 +190,14 @@ class EngineState:
         if self.trainer is None:
             run = {"lr": 3e-4, "min_lr": 3e-5, "warmup_steps": 10, "total_steps": 100000, "depth_mode": "cortex",
                    "grad_accum_steps": 1, "grad_clip": 1.0, "vocab_size": int(model.vocab_size), "batch_size": 4, "seq_len": 256}
+            run.update(self.pending_training_config)
             run.update(cfg)
-            opt = CentroidSteerOptimizer(model, lr=run["lr"], grad_clip=run["grad_clip"])
+            if run.get("optimizer") or self.pending_training_config:
+                from ..optim import build_optimizer
+
+                opt = build_optimizer(model, {"optimizer": "centroid_steer", **run})
+            else:
+                opt = CentroidSteerOptimizer(model, lr=run["lr"], grad_clip=run["grad_clip"])
             src = SyntheticTokenSource(int(model.vocab_size), int(run["batch_size"]), int(run["seq_len"]), seed=0)
             self.trainer = Trainer(model, run, optimizer=opt, train_loader=src, device=self.device)
         else:

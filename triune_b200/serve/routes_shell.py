@@ -81,30 +81,129 @@ async def system_config_set(body: Dict[str, Any]):
 # ---------------------------------------------------------------------------------------------------- DAG, nodes, plugins
 @shell_router.get("/v1/nodes/catalog")
 async def nodes_catalog():
+    """``nodes``: this executor's own node types; ``studio_nodes``: the canvas catalogue (typed ports, default parameters)."""
     from ..execution.dag import node_catalog
+    from ..execution.studio import studio_catalog
 
-    return {"nodes": node_catalog()}
+    return {"nodes": node_catalog(), "studio_nodes": studio_catalog()}
+
+
+# One graph runs at a time against the shared model / training state; the others wait (``/v1/dag/queue`` shows both).
+_DAG_QUEUE: Dict[str, Any] = {"active_run_id": None, "waiting": 0, "lock": None}
+
+
+def _dag_lock() -> asyncio.Lock:
+    if _DAG_QUEUE["lock"] is None:
+        _DAG_QUEUE["lock"] = asyncio.Lock()
+    return _DAG_QUEUE["lock"]
+
+
+@shell_router.get("/v1/dag/queue")
+async def dag_queue():
+    return {"active_run_id": _DAG_QUEUE["active_run_id"], "waiting": _DAG_QUEUE["waiting"], "capacity": 1}
 
 
 @shell_router.post("/v1/dag/execute")
 async def dag_execute(body: Dict[str, Any]):
+    """Both graph formats: the canvas' (``nodes`` / ``edges`` with ``source`` and ``target``, optional ``run_id``; node
+    events go to the telemetry listeners as ``dag_event`` records) and this executor's own (``{"dag": ...}``)."""
+    import uuid
+
     from ..execution.dag import DAGValidationError, execute_dag
+    from ..execution.studio import StudioGraphError, is_studio_graph, run_studio_graph
 
     spec = body.get("dag", body)
+    state = get_state()
+    run_id = str(body.get("run_id") or uuid.uuid4().hex)[:80]
+    _DAG_QUEUE["waiting"] += 1
+    t_queue = time.perf_counter()
+    acquired = False
     try:
-        out = await asyncio.to_thread(execute_dag, spec, {"state": get_state()})
-    except DAGValidationError as e:
+        async with _dag_lock():
+            acquired = True
+            _DAG_QUEUE["waiting"] -= 1
+            _DAG_QUEUE["active_run_id"] = run_id
+            waited_ms = round((time.perf_counter() - t_queue) * 1000, 1)
+            try:
+                if is_studio_graph(spec):
+                    def emit(ev):
+                        state._broadcast({"type": "dag_event", "data": {**ev, "run_id": run_id}})
+
+                    ctx = {"state": state, "provider_keys": _SHELL["byok"]}
+                    out = await asyncio.to_thread(run_studio_graph, {"nodes": spec.get("nodes", []), "edges": spec.get("edges", [])}, ctx, emit)
+                    out.update(run_id=run_id, queue_wait_ms=waited_ms)
+                    return _jsonable(out)
+                out = await asyncio.to_thread(execute_dag, spec, {"state": state})
+            finally:
+                _DAG_QUEUE["active_run_id"] = None
+    except (DAGValidationError, StudioGraphError) as e:
         raise _bad(e, 422)
+    except HTTPException:
+        raise
     except Exception as e:
         raise _bad(e)
+    finally:
+        if not acquired:  # cancelled while waiting for its turn
+            _DAG_QUEUE["waiting"] = max(0, _DAG_QUEUE["waiting"] - 1)
     return _jsonable(out)
+
+
+@shell_router.post("/v1/dag/compile_to_training")
+@shell_router.post("/v1/model/compile_dag")
+async def dag_compile_to_training(body: Dict[str, Any]):
+    """Read a canvas graph as a training recipe and apply it: a model node rebuilds the active model when it names an
+    architecture (``apply_model`` false keeps the loaded one), the rest becomes the configuration of the next training run."""
+    from ..execution.studio import StudioGraphError, compile_to_training
+
+    try:
+        rec = compile_to_training({"nodes": body.get("nodes", []), "edges": body.get("edges", [])})
+    except StudioGraphError as e:
+        raise _bad(e, 422)
+    state = get_state()
+    applied: Dict[str, Any] = {}
+    arch = {k: v for k, v in rec["model"].items() if k != "preset"}
+    if (arch or rec["model"].get("preset")) and body.get("apply_model", True):
+        if state.train_status.get("running"):
+            raise HTTPException(409, "pause background training before changing the architecture")
+        if arch.get("hidden_dim") and arch.get("num_heads") and "head_dim" not in arch:
+            arch["head_dim"] = arch["hidden_dim"] // arch["num_heads"]
+        try:
+            if arch.get("num_layers"):
+                from ..execution.studio import shallow_exit_layout
+
+                arch = {**shallow_exit_layout(arch["num_layers"]), **arch}
+            applied["model_architecture"] = await asyncio.to_thread(state.load_model, rec["model"].get("preset", "default"),
+                                                                    None, rec["run"].get("precision"), **arch)
+        except Exception as e:
+            raise _bad(e)
+    run = {k: v for k, v in rec["run"].items() if k != "precision"}
+    if run:
+        _SHELL["config"].setdefault("training", {}).update(run)
+        state.pending_training_config = {**getattr(state, "pending_training_config", {}), **run}
+        state.trainer = None  # the next step or run builds its trainer from the new settings
+        applied["training"] = run
+    if rec["data"]:
+        _SHELL["selected_dataset"] = rec["data"].get("path") or rec["data"].get("source")
+        applied["data"] = rec["data"]
+    return {"status": "compiled", "applied": applied, "sections": rec["applied"]}
 
 
 @shell_router.post("/v1/dag/execute_node")
 async def dag_execute_node(body: Dict[str, Any]):
-    """One node on its own: ``{"type": ..., "params": {...}, "inputs": {port: value}}``; inputs become constant nodes."""
-    from ..execution.dag import execute_dag
+    """One node on its own. Canvas form: the node object itself (``type`` / ``title`` / ``params`` ...), optional
+    ``inputs``. Own form: ``{"type": ..., "params": {...}, "inputs": {port: value}}``; inputs become constant nodes."""
+    from ..execution.dag import NODE_TYPES, execute_dag
+    from ..execution.studio import resolve_kind, run_studio_node
 
+    node = body.get("node") if isinstance(body.get("node"), dict) else body
+    if node.get("type") not in NODE_TYPES and resolve_kind(node) is not None:
+        state = get_state()
+        try:
+            out = await asyncio.to_thread(run_studio_node, {k: v for k, v in node.items() if k != "inputs"}, body.get("inputs") or node.get("inputs"),
+                                          {"state": state, "provider_keys": _SHELL["byok"]})
+        except Exception as e:
+            raise _bad(e)
+        return _jsonable(out)
     try:
         nodes = [{"id": "n", "type": body["type"], "params": body.get("params", {})}]
         edges = []
