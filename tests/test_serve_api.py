@@ -244,3 +244,79 @@ def test_canvas_graphs_over_http(client, tmp_path):
     assert type(st.trainer.optimizer).__name__ == "AdamW" and st.trainer.optimizer.param_groups[0]["lr"] > 0
     same = client.post("/v1/model/compile_dag", json={**g, "apply_model": False}).json()
     assert "model_architecture" not in same["applied"]
+
+
+def test_module_lifecycle_dataset_stream_and_adapter_endpoints(client, tmp_path):
+    """Install (copy or local git clone) / pull / uninstall of modules inside the plugin directory, a local dataset made the
+    active stream, and a saved adapter attached to and detached from the live model. Remote sources are refused plainly."""
+    import subprocess
+
+    from triune_b200.plugins.registry import create_plugin
+    from triune_b200.serve.engine_state import get_state
+
+    plug_dir = tmp_path / "plugins"
+    client.post("/v1/system/config", json={"plugin_dir": str(plug_dir)})
+    src = create_plugin(tmp_path / "src", "echo_tools")
+    r = client.post("/v1/modules/install", json={"path": str(src)})
+    assert r.status_code == 200 and r.json()["status"] == "installed" and r.json()["plugins_found"] == ["echo_tools"], r.text
+    assert (plug_dir / "echo_tools" / "plugin.json").is_file()
+    assert client.post("/v1/modules/install", json={"path": str(src)}).status_code == 409
+    assert client.post("/v1/modules/install", json={"url": "https://github.com/x/y"}).status_code == 501
+    assert client.post("/v1/modules/install", json={"path": str(src), "name": "../escape"}).status_code == 403
+    # a local git repository is cloned, and pulled after a new commit
+    repo = tmp_path / "repo"
+    repo.mkdir()
+    git = ["git", "-C", str(repo), "-c", "user.email=a@b", "-c", "user.name=t"]
+    subprocess.run(["git", "init", "-q", str(repo)], check=True)
+    (repo / "README.md").write_text("one\n")
+    subprocess.run(git + ["add", "-A"], check=True)
+    subprocess.run(git + ["commit", "-qm", "one"], check=True)
+    r = client.post("/v1/modules/clone", json={"url": "file://" + str(repo), "name": "cloned"})
+    assert r.status_code == 200 and r.json()["is_git"], r.text
+    (repo / "README.md").write_text("two\n")
+    subprocess.run(git + ["commit", "-qam", "two"], check=True)
+    r = client.post("/v1/modules/pull", json={"id": "cloned"})
+    assert r.status_code == 200 and (plug_dir / "cloned" / "README.md").read_text() == "two\n", r.text
+    assert client.post("/v1/modules/pull", json={"id": "echo_tools"}).status_code == 404
+    assert client.post("/v1/modules/uninstall", json={"id": "cloned"}).json()["status"] == "uninstalled"
+    assert not (plug_dir / "cloned").exists()
+    assert client.post("/v1/modules/uninstall", json={"id": "cloned"}).status_code == 404
+
+    assert client.get("/v1/datasets/stream/status").json()["is_streaming"] is False
+    assert client.post("/v1/datasets/stream/connect", json={"dataset_name": "roneneldan/TinyStories"}).json()["status"] == "error"
+    corpus = tmp_path / "c.jsonl"
+    corpus.write_text(json.dumps({"text": "first document"}) + "\n" + json.dumps({"text": "second"}) + "\n")
+    r = client.post("/v1/datasets/stream/connect", json={"dataset_name": "file://" + str(corpus)}).json()
+    assert r["status"] == "connected" and r["buffered_chunks"] == 2 and r["sample_preview"] == "first document"
+    assert client.get("/v1/datasets/stream/status").json()["path"] == str(corpus)
+
+    assert client.post("/v1/finetune/adapter", json={"action": "attach", "path": str(tmp_path / "none")}).status_code == 409  # no model yet
+    client.post("/v1/models/load", json={"model": "triune-nano", "overrides": TINY})
+    assert client.post("/v1/finetune/adapter", json={"action": "attach", "path": str(tmp_path / "none")}).status_code == 404
+    from triune_b200.trainer.finetune import LoRAConfig, TriuneFineTuner
+
+    st = get_state()
+    ft = TriuneFineTuner(st.model, LoRAConfig(rank=2, alpha=4.0))
+    for p in ft.get_trainable_parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    x = torch.randint(0, 256, (1, 8))
+    ft.save_adapter(tmp_path / "ad")
+    ft.detach_lora()
+    with torch.no_grad():
+        y_base = st.model(x, force_depth=2)[0].clone()
+    ft2 = TriuneFineTuner(st.model, LoRAConfig.from_pretrained(tmp_path / "ad"))
+    ft2.load_adapter(tmp_path / "ad")  # what the saved adapter computes (rows a fused projection masks are not saved)
+    with torch.no_grad():
+        y_adapted = st.model(x, force_depth=2)[0].clone()
+    ft2.detach_lora()
+    assert not torch.allclose(y_adapted, y_base)
+    r = client.post("/v1/finetune/adapter", json={"action": "attach", "path": str(tmp_path / "ad")}).json()
+    assert r["action"] == "attached" and r["active_adapter"]["rank"] == 2
+    with torch.no_grad():
+        assert torch.allclose(st.model(x, force_depth=2)[0], y_adapted, atol=1e-5)
+    client.post("/v1/finetune/adapter", json={"action": "attach", "path": str(tmp_path / "ad")})  # re-attach: no nesting
+    with torch.no_grad():
+        assert torch.allclose(st.model(x, force_depth=2)[0], y_adapted, atol=1e-5)
+    assert client.post("/v1/finetune/adapter", json={"action": "detach"}).json()["action"] == "detached"
+    with torch.no_grad():
+        assert torch.allclose(st.model(x, force_depth=2)[0], y_base, atol=1e-6)

@@ -14,6 +14,7 @@ import queue as _queue
 import threading
 import time
 import uuid
+from pathlib import Path
 from typing import Any, Dict, List, Optional
 
 from fastapi import APIRouter, HTTPException, WebSocket, WebSocketDisconnect
@@ -395,6 +396,44 @@ async def finetune_adapters():
     from ..trainer.finetune import list_adapters
 
     return {"adapters": list_adapters()}
+
+
+@router.post("/v1/finetune/adapter")
+async def finetune_adapter(body: Dict[str, Any]):
+    """Attach a saved LoRA / QLoRA adapter to the live model (``action: attach``, ``path``; rank and alpha come from the
+    adapter's own ``adapter_config.json`` when it has one) or take the attached one off (``action: detach``). An adapter
+    that is already attached is detached first, so adapters never nest (``triune/api/routes.py:3950-4010``)."""
+    from ..trainer.finetune import LoRAConfig, TriuneFineTuner
+
+    st = get_state()
+    action = str(body.get("action", "attach")).lower()
+    with st.lock:
+        prev = getattr(st, "_finetuner", None)
+        if prev is not None:
+            prev.detach_lora()
+            st._finetuner = None
+            st.active_adapter = None
+        if action == "detach":
+            return {"status": "success", "action": "detached", "active_adapter": None}
+        if action != "attach":
+            raise HTTPException(400, f"unknown action {action!r} (attach or detach)")
+        if st.model is None:
+            raise HTTPException(409, "no model is loaded; POST /v1/models/load first")
+        model = st.model
+        path = Path(str(body.get("path") or "checkpoints/lora_adapter"))
+        if not (path.is_dir() and (path / "adapter_config.json").is_file()):
+            raise HTTPException(404, f"no adapter at {path} (a directory with adapter_config.json)")
+        try:
+            cfg = LoRAConfig.from_pretrained(path)
+            ft = TriuneFineTuner(model, cfg)
+            ft.load_adapter(path)
+        except Exception as e:
+            raise HTTPException(400, f"{type(e).__name__}: {e}")
+        st._finetuner = ft
+        st.active_adapter = {"name": path.name, "path": str(path), "rank": cfg.rank, "alpha": cfg.alpha,
+                             "trainable": ft.count_trainable_parameters()}
+        st.srsm.clear_all()  # cached recurrent states were computed without the adapter
+        return {"status": "success", "action": "attached", "active_adapter": st.active_adapter}
 
 
 @router.post("/v1/finetune/merge")

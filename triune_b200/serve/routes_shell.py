@@ -260,6 +260,89 @@ async def modules_create_plugin(body: Dict[str, Any]):
     return {"created": str(path), "plugins": _registry().list()}
 
 
+def _local_source(src: str) -> Optional[Path]:
+    """A module source this server can reach: a local directory or a ``file://`` URL. Remote URLs return None."""
+    if src.startswith("file://"):
+        src = src[len("file://"):]
+    if "://" in src or src.startswith("git@"):
+        return None
+    p = Path(src).expanduser()
+    return p if p.is_dir() else None
+
+
+_NO_NETWORK = "remote repositories need network access, which this server does not use; give a local directory or a file:// URL"
+
+
+@shell_router.post("/v1/modules/install")
+@shell_router.post("/v1/modules/clone")
+async def modules_install(body: Dict[str, Any]):
+    """Copy a module (a plugin directory with its signed manifest, or a local git repository, cloned with ``git``) into
+    the plugin directory and register what it holds. Nothing is loaded until ``/v1/modules/activate``."""
+    import shutil
+    import subprocess
+
+    src = str(body.get("url") or body.get("repo_url") or body.get("path") or body.get("source") or "")
+    root = _local_source(src)
+    if root is None:
+        raise HTTPException(400 if not src else 501, "a module source is required" if not src else _NO_NETWORK)
+    name = str(body.get("name") or root.name)
+    try:
+        dst = _inside(str(_SHELL["config"]["plugin_dir"]), name)
+    except ValueError as e:
+        raise _bad(e, 403)
+    if dst.exists():
+        raise HTTPException(409, f"module {name!r} is already installed")
+    dst.parent.mkdir(parents=True, exist_ok=True)
+    if (root / ".git").exists():
+        cmd = ["git", "clone", "--quiet", "--depth", "1"] + (["--branch", str(body["branch"])] if body.get("branch") else []) + [str(root), str(dst)]
+        r = await asyncio.to_thread(subprocess.run, cmd, capture_output=True, text=True, timeout=120)
+        if r.returncode != 0:
+            raise HTTPException(400, f"git clone failed: {r.stderr.strip()[:300]}")
+    else:
+        await asyncio.to_thread(shutil.copytree, root, dst)
+    found = _registry().discover(str(dst.parent))
+    return {"status": "installed", "id": name, "path": str(dst), "is_git": (dst / ".git").exists(),
+            "plugins_found": [p.name for p in found if Path(p.path).resolve().is_relative_to(dst.resolve())]}
+
+
+@shell_router.post("/v1/modules/pull")
+async def modules_pull(body: Dict[str, Any]):
+    """``git pull`` in an installed module that is a clone of a local repository."""
+    import subprocess
+
+    name = str(body.get("id") or body.get("module_id") or body.get("name") or "")
+    try:
+        dst = _inside(str(_SHELL["config"]["plugin_dir"]), name)
+    except ValueError as e:
+        raise _bad(e, 403)
+    if not name or not (dst / ".git").exists():
+        raise HTTPException(404, f"no git module {name!r} is installed")
+    url = await asyncio.to_thread(subprocess.run, ["git", "-C", str(dst), "config", "--get", "remote.origin.url"], capture_output=True, text=True)
+    if _local_source(url.stdout.strip()) is None:
+        raise HTTPException(501, _NO_NETWORK)
+    r = await asyncio.to_thread(subprocess.run, ["git", "-C", str(dst), "pull", "--quiet", "--ff-only"], capture_output=True, text=True, timeout=120)
+    if r.returncode != 0:
+        raise HTTPException(400, f"git pull failed: {r.stderr.strip()[:300]}")
+    head = await asyncio.to_thread(subprocess.run, ["git", "-C", str(dst), "rev-parse", "--short", "HEAD"], capture_output=True, text=True)
+    return {"status": "updated", "id": name, "head": head.stdout.strip()}
+
+
+@shell_router.post("/v1/modules/uninstall")
+async def modules_uninstall(body: Dict[str, Any]):
+    import shutil
+
+    name = str(body.get("id") or body.get("name") or "")
+    try:
+        dst = _inside(str(_SHELL["config"]["plugin_dir"]), name)
+    except ValueError as e:
+        raise _bad(e, 403)
+    if not name or not dst.is_dir():
+        raise HTTPException(404, f"module {name!r} is not installed")
+    await asyncio.to_thread(shutil.rmtree, dst)
+    _SHELL["registry"] = None  # forget what was discovered there; the next listing rescans
+    return {"status": "uninstalled", "id": name}
+
+
 @shell_router.get("/v1/modules/search")
 @shell_router.get("/v1/modules/updates")
 async def modules_remote():
@@ -547,9 +630,36 @@ async def datasets_select(body: Dict[str, Any]):
     return {"selected": name, "train_config": {"dataset_path": _SHELL["datasets"][name]["path"]}}
 
 
+@shell_router.post("/v1/datasets/stream/connect")
+async def datasets_stream_connect(body: Dict[str, Any]):
+    """Make a dataset the active training stream. A local file or directory (or a ``file://`` URL, or a hub name that
+    exists as a local path) is read and registered; anything that needs the network answers ``status: error``."""
+    from ..execution.studio import _read_local_texts
+
+    name = str(body.get("dataset_name") or body.get("url") or "").strip()
+    if not name:
+        return {"status": "error", "message": "Dataset identifier or URL cannot be empty."}
+    local = name[len("file://"):] if name.startswith("file://") else (str(body.get("local_path") or "") or name)
+    if "://" in local or not os.path.exists(local):
+        return {"status": "error", "message": f"Could not stream from '{name}': remote hubs and URLs need network access, which this "
+                                              f"server does not use (give a local path, a file:// URL or 'local_path')"}
+    docs = await asyncio.to_thread(_read_local_texts, local, 20)
+    if not docs:
+        return {"status": "error", "message": f"'{local}' holds no text"}
+    _SHELL["stream"] = {"is_streaming": True, "dataset_name": name, "dataset_type": "local", "path": local, "split": body.get("split", "train"),
+                        "text_column": body.get("text_column", "text"), "buffered_chunks": len(docs), "connected": time.time()}
+    _SHELL["selected_dataset"] = local
+    return {"status": "connected", "dataset_name": name, "buffered_chunks": len(docs), "sample_preview": docs[0][:200],
+            "train_config": {"dataset_path": local}}
+
+
 @shell_router.get("/v1/datasets/stream/status")
 async def datasets_stream_status():
-    return {"connected": False, "note": "streaming from remote hubs needs network access, which this server does not use"}
+    st = _SHELL.get("stream")
+    if st:
+        return dict(st)
+    return {"is_streaming": False, "connected": False,
+            "note": "no stream is connected; remote hubs need network access, which this server does not use"}
 
 
 # ---------------------------------------------------------------------------------------------------- engine, hardware

@@ -212,6 +212,7 @@ class TriuneFineTuner:
                 blocks = [i for i, t in enumerate(_QKVG) if t in cfg.target_modules or "qkv_proj" in cfg.target_modules and i < 3]
                 if blocks:
                     ad = FusedProjectionLoRA(mod, blocks, cfg.rank, cfg.alpha, cfg.dropout)
+                    ad.train(mod.training)  # an adapter on an eval-mode model must not drop activations
                     mod.qkvg_lora = ad
                     self.applied_adapters[f"{name}.qkvg" if name else "qkvg"] = ad
                 continue
@@ -228,6 +229,7 @@ class TriuneFineTuner:
                     and mod.weight.numel() > 0):
                 base = NVFP4Linear.from_linear(mod, hadamard=cfg.hadamard)
             ad = LoRALayer(base, cfg.rank, cfg.alpha, cfg.dropout, self._adapter_device)
+            ad.train(mod.training)
             if isinstance(parent, (nn.Sequential, nn.ModuleList)) and attr.isdigit():
                 parent[int(attr)] = ad
             else:
