@@ -3,6 +3,7 @@ export, staging, planning, session state, callbacks."""
 
 import json
 import os
+import sys
 
 import pytest
 import torch
@@ -833,3 +834,145 @@ def test_expert_parallel_reduction_runs_follow_the_received_counts():
     # segment order is expert-major: (e0, r0), (e0, r1), (e0, r2), (e1, r0), ...
     assert runs[:, 0].tolist() == [0, 256, 512, 768, 1024, 1280]
     assert runs[:, 1].tolist() == [0, 1, 1, 2, 4, 2]
+
+
+def test_installer_plan_run_and_scripts(tmp_path):
+    """The installer on fake machines: what it detects, the plan it makes (kernels only where they can be built, wheel
+    directory and offline flags, existing environment reused), how a run stops or carries on, and what it writes."""
+    from triune_b200 import installer as ins
+
+    def machine(smi=None, nvcc=True):
+        def run(argv, cwd=None, timeout=0):
+            if argv[0] == "nvidia-smi":
+                return (0, smi) if smi else (127, "not found")
+            if argv[0] == "nvcc":
+                return (0, "nvcc: NVIDIA (R) Cuda compiler driver\nCuda compilation tools, release 12.9, V12.9.86\n") if nvcc else (127, "")
+            raise AssertionError(argv)
+        return run
+
+    b200 = ins.probe_machine(machine("NVIDIA B200, 183359, 580.159, 10.0\nNVIDIA B200, 183359, 580.159, 10.0\n"), os_type="Linux", proc_version="Linux version 6.1")
+    assert len(b200.gpus) == 2 and b200.gpus[0]["memory_gb"] == 179.1 and b200.driver == "580.159" and b200.nvcc == "12.9"
+    assert b200.blackwell and b200.can_build_kernels and not b200.is_wsl and not b200.notes
+    h100 = ins.probe_machine(machine("NVIDIA H100, 81559, 550.54, 9.0\n"), os_type="Linux", proc_version="Linux ... microsoft-standard-WSL2")
+    assert h100.is_wsl and not h100.blackwell and not h100.can_build_kernels and "10.x" in h100.notes[0]
+    cpu = ins.probe_machine(machine(None, nvcc=False), os_type="Darwin")
+    assert not cpu.gpus and "no NVIDIA GPU" in cpu.notes[0]
+    no_nvcc = ins.probe_machine(machine("NVIDIA B200, 183359, 580.159, 10.0\n", nvcc=False), os_type="Linux", proc_version="")
+    assert no_nvcc.blackwell and not no_nvcc.can_build_kernels and "nvcc was not found" in no_nvcc.notes[0]
+
+    venv = tmp_path / "env"
+    names = lambda steps: [s.name for s in steps]
+    plan = ins.plan_install(b200, venv, base_python="/usr/bin/python3")
+    assert names(plan) == ["create-venv", "install-torch", "install-core", "install-serve", "install-extras", "build-kernels", "launcher", "verify"]
+    assert plan[0].argv == ["/usr/bin/python3", "-m", "venv", str(venv)] and plan[1].argv[0] == str(venv / "bin" / "python")
+    assert "--index-url" in plan[1].argv and plan[5].argv[-2:] == ["triune_b200", "native"] and plan[6].argv[-1] == "linux"
+    assert [s.optional for s in plan] == [False, False, False, True, True, False, True, False]
+    assert "build-kernels" not in names(ins.plan_install(h100, venv)) and "build-kernels" not in names(ins.plan_install(b200, venv, build=False))
+    off = ins.plan_install(b200, venv, find_links="/wheels", offline=True, extras=False, shortcuts=False)
+    assert names(off) == ["create-venv", "install-torch", "install-core", "install-serve", "build-kernels", "verify"]
+    assert off[1].argv[-4:] == ["--no-index", "--find-links", "/wheels", "torch"] and "--index-url" not in off[1].argv
+    bare = ins.plan_install(cpu, None, offline=True, shortcuts=True)
+    assert names(bare) == ["check-torch", "launcher", "verify"] and bare[1].argv[-1] == "macos"
+    (venv / "bin").mkdir(parents=True)
+    (venv / "bin" / "python").write_text("")
+    assert names(ins.plan_install(b200, venv))[0] == "check-venv"
+    win = ins.plan_install(ins.MachineProfile(os_type="Windows", python=(3, 12)), tmp_path / "w")
+    assert win[1].argv[0].endswith("Scripts/python.exe") and win[-2].argv[-1] == "windows"
+
+    calls, lines = [], []
+
+    def runner(fail):
+        def run(argv, cwd=None, timeout=0):
+            calls.append(argv)
+            step = next(s.name for s in plan if s.argv == argv)
+            return (1, "boom\nlast line") if step in fail else (0, "fine")
+        return run
+
+    plan = ins.plan_install(b200, tmp_path / "e2", base_python="py")
+    rec = ins.run_plan(plan, runner({"install-extras", "launcher"}), lines.append)
+    assert rec["ok"] and [r["status"] for r in rec["steps"]] == ["done", "done", "done", "done", "skipped", "done", "skipped", "done"]
+    assert any("warning: exit code 1" in l and "last line" in l for l in lines)
+    calls.clear()
+    rec = ins.run_plan(plan, runner({"install-core"}), lines.append)
+    assert not rec["ok"] and rec["steps"][-1] == {"step": "install-core", "status": "failed", "exit_code": 1, "output": "boom\nlast line"}
+    assert len(calls) == 3  # nothing ran after the failing required step
+    calls.clear()
+    rec = ins.run_plan(plan, runner(set()), lines.append, dry_run=True)
+    assert rec["ok"] and not calls and all(r["status"] == "planned" for r in rec["steps"])
+
+    s = ins.write_bootstrap_scripts(tmp_path / "dist")
+    sh, bat = open(s["sh"]).read(), open(s["bat"], newline="").read()
+    assert sh.startswith("#!/usr/bin/env sh") and "-m triune_b200 install --venv" in sh and os.access(s["sh"], os.X_OK)
+    assert "wsl.exe --status" in bat and "\r\n" in bat and "-m triune_b200 install" in bat
+    real = tmp_path / "venv_real"
+    real.mkdir()
+    (real / "pyvenv.cfg").write_text("home = /usr/bin\n")
+    plain = tmp_path / "not_a_venv"
+    plain.mkdir()
+    assert ins.uninstall(str(plain), str(tmp_path / "dist"), dry_run=True)["kept"] and plain.exists()
+    out = ins.uninstall(str(real), str(tmp_path / "dist"))
+    assert not real.exists() and not os.path.exists(s["sh"]) and len(out["removed"]) == 3
+
+
+def test_desktop_wsl_discovery_and_launch(monkeypatch):
+    """The launcher's WSL path: path translation, choice of the interpreter inside WSL (one that sees a GPU wins; one
+    that cannot import the package is skipped), the command line, and a session started through it on a fake Windows."""
+    from triune_b200 import desktop as d
+
+    assert d.to_wsl_path("C:\\Users\\me\\repo") == "/mnt/c/Users/me/repo"
+    assert d.to_wsl_path("\\\\wsl$\\Ubuntu\\home\\me\\repo") == "/home/me/repo"
+    assert d.to_wsl_path("\\\\wsl.localhost\\Ubuntu-24.04\\srv") == "/srv" and d.to_wsl_path("/opt/x") == "/opt/x"
+
+    info = {"/home/me/venvs/triune/bin/python": {"torch": "2.11", "cuda": False, "package": True},
+            "/home/me/.venv/bin/python": {"torch": None, "cuda": False, "package": True},
+            "/mnt/c/w/.venv/bin/python": {"torch": "2.11", "cuda": True, "package": False},
+            "/usr/bin/python3": {"torch": "2.11", "cuda": True, "package": True}}
+    seen = []
+
+    def run(argv, timeout=0):
+        seen.append(list(argv))
+        if argv[:2] == ["wsl.exe", "--status"]:
+            return 0, ""
+        if argv[:3] == ["wsl.exe", "-e", "sh"]:
+            return (0, "/home/me") if "HOME" in argv[-1] else (0, "/usr/bin/python3\n")
+        if argv[:3] == ["wsl.exe", "-e", "test"]:
+            return (0 if argv[-1] in info else 1), ""
+        if argv[:2] == ["wsl.exe", "-e"] and argv[2] in info:
+            return 0, "warning line\n" + json.dumps(info[argv[2]]) + "\n"
+        return 1, ""
+
+    monkeypatch.delenv("TRIUNE_WSL_PYTHON", raising=False)
+    got = d.find_wsl_python("C:\\w", run=run)
+    assert got == {"python": "/usr/bin/python3", "cuda": True, "torch": "2.11", "workspace": "/mnt/c/w"}
+    assert all(c[-1] == "/mnt/c/w" for c in seen if len(c) > 3 and c[2] in info)  # every probe was told where the package lives
+    info["/usr/bin/python3"]["cuda"] = False
+    assert d.find_wsl_python("C:\\w", run=run)["python"] == "/home/me/venvs/triune/bin/python"  # first usable one without a GPU
+    assert d.find_wsl_python("C:\\w", run=lambda a, t=0: (1, "")) is None  # no WSL
+    cmd = d.wsl_server_command(got, 8123, model="triune-nano", precision="fp8")
+    assert cmd == ["wsl.exe", "--cd", "/mnt/c/w", "-e", "/usr/bin/python3", "-m", "triune_b200", "serve", "--host", "127.0.0.1", "--port", "8123",
+                   "--model", "triune-nano", "--precision", "fp8"]
+
+    started = []
+
+    class FakeProc:
+        def poll(self):
+            return None
+
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+        def kill(self):
+            pass
+
+    monkeypatch.setattr(d, "port_in_use", lambda port, host="127.0.0.1": False)
+    monkeypatch.setattr(d, "wait_for_server", lambda *a, **k: True)
+    monkeypatch.setattr(d, "_local_cuda", lambda: False)
+    info["/usr/bin/python3"]["cuda"] = True
+    ses = d.start_session(8123, quiet=True, allow_wsl=True, run=run, popen=lambda cmd, **kw: started.append(cmd) or FakeProc(), platform="win32")
+    assert started[0][0] == "wsl.exe" and started[0][started[0].index("-e") + 1] == "/usr/bin/python3" and not ses.reused
+    started.clear()
+    d.start_session(8123, quiet=True, allow_wsl=True, run=run, popen=lambda cmd, **kw: started.append(cmd) or FakeProc(), platform="linux")
+    assert started[0][0] == sys.executable  # WSL is only considered on a Windows host

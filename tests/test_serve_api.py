@@ -320,3 +320,28 @@ def test_module_lifecycle_dataset_stream_and_adapter_endpoints(client, tmp_path)
     assert client.post("/v1/finetune/adapter", json={"action": "detach"}).json()["action"] == "detached"
     with torch.no_grad():
         assert torch.allclose(st.model(x, force_depth=2)[0], y_base, atol=1e-6)
+
+
+def test_studio_page_is_served_and_matches_the_api(client):
+    """The packaged single-page Studio: served at / with its script and stylesheet; every API path the script calls is a
+    route of this server, and every element id the script looks up exists in the page."""
+    import re
+    from pathlib import Path
+
+    import triune_b200
+
+    root = Path(triune_b200.__file__).parent / "studio"
+    page = client.get("/")
+    assert page.status_code == 200 and "Triune Studio" in page.text and page.headers["cache-control"].startswith("no-cache")
+    js = client.get("/static/app.js")
+    assert js.status_code == 200 and js.text == (root / "app.js").read_text()
+    assert client.get("/static/style.css").status_code == 200
+    assert "Triune Studio" in client.get("/some/client/side/route").text  # unknown paths fall back to the page
+    routes = {getattr(r, "path", "") for r in client.app.routes}
+    called = set(re.findall(r'"(/(?:v1|ws)/[A-Za-z0-9_/]+?)/?"', js.text))
+    assert len(called) >= 25
+    for path in called:
+        assert path in routes or any(r.startswith(path + "/{") for r in routes), path
+    ids = set(re.findall(r'\$\("#([A-Za-z0-9_-]+)"\)', js.text))  # ids completed at run time ("#node-" + id) are not literals
+    html_ids = set(re.findall(r'id="([A-Za-z0-9_-]+)"', page.text))
+    assert ids and ids <= html_ids, sorted(ids - html_ids)

@@ -3,8 +3,8 @@
 Parity with the sub-commands of ``triune/cli.py:39-1618`` that concern the ML core and serving: ``serve``, ``chat``,
 ``infer``, ``scan``, ``transmute``, ``finetune``, ``adapter {list,merge,export}``, ``checkpoint {list,export}``,
 ``export``, ``models``, ``train``, ``bench``, ``gpucheck``, ``plan-memory``, ``cache`` (NVFP4 disk cache), ``native``
-(build the extensions), ``profile``, ``tokenizer``, ``sandbox``. The desktop application commands (``studio``,
-installers) belong to the product shell and are not part of this framework.
+(build the extensions), ``profile``, ``tokenizer``, ``sandbox``; and of the product shell: ``desktop`` (launcher, also
+through WSL 2 on a Windows host), ``package`` (launcher bundles), ``install`` / ``uninstall`` (``installer.py``).
 """
 
 from __future__ import annotations
@@ -480,7 +480,26 @@ def cmd_desktop(a) -> int:
     from .desktop import launch_desktop_app
 
     launch_desktop_app(a.port, use_browser=not a.no_browser, host=a.host, model=a.model, static_dir=a.static_dir,
-                       precision=a.precision)
+                       precision=a.precision, allow_wsl=a.allow_wsl)
+    return 0
+
+
+def cmd_install(a) -> int:
+    from . import installer
+
+    if a.scripts:
+        _print(installer.write_bootstrap_scripts(Path(a.scripts)))
+        return 0
+    out = installer.install(a.venv, a.find_links, a.offline, not a.no_build, not a.no_shortcuts, not a.no_extras, a.dry_run)
+    if a.json:
+        _print(out)
+    return 0 if out["ok"] else 1
+
+
+def cmd_uninstall(a) -> int:
+    from . import installer
+
+    _print(installer.uninstall(a.venv, a.dist, a.dry_run))
     return 0
 
 
@@ -706,7 +725,26 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--port", type=int, default=8000)
     s.add_argument("--static-dir", default=None)
     s.add_argument("--no-browser", action="store_true", help="do not open a browser; print the address only")
+    s.add_argument("--allow-wsl", action="store_true", help="on a Windows host without a CUDA PyTorch, run the server inside WSL 2")
     s.set_defaults(fn=cmd_desktop)
+
+    s = sub.add_parser("install", help="set the framework up on this machine (virtual environment, dependencies, kernels, launcher)")
+    s.add_argument("--venv", default=None, help="virtual environment to create or reuse (default: the current interpreter)")
+    s.add_argument("--find-links", default=None, help="directory of wheels to install from")
+    s.add_argument("--offline", action="store_true", help="never contact a package index")
+    s.add_argument("--no-build", action="store_true", help="do not compile the CUDA extensions")
+    s.add_argument("--no-shortcuts", action="store_true", help="do not generate the launcher bundle")
+    s.add_argument("--no-extras", action="store_true", help="skip the optional packages (tokenizers, safetensors, pyarrow, transformers)")
+    s.add_argument("--dry-run", action="store_true", help="print the plan and change nothing")
+    s.add_argument("--json", action="store_true", help="print the record of the run as JSON")
+    s.add_argument("--scripts", default=None, help="only write install.sh / install.bat into this directory")
+    s.set_defaults(fn=cmd_install)
+
+    s = sub.add_parser("uninstall", help="remove the virtual environment and the generated launcher bundles")
+    s.add_argument("--venv", required=True)
+    s.add_argument("--dist", default=None)
+    s.add_argument("--dry-run", action="store_true")
+    s.set_defaults(fn=cmd_uninstall)
 
     s = sub.add_parser("package", help="generate launcher bundles (Linux AppDir, macOS .app, Windows .cmd)")
     s.add_argument("--target", default="all", help="linux, macos, windows or all")

@@ -3,7 +3,7 @@
 Parity (``triune/api/server.py:57-221``): ``/healthz`` that touches neither PyTorch nor the model; a middleware that
 lets loopback clients through and requires ``Authorization: Bearer $TRIUNE_API_TOKEN`` (at least 32 characters,
 constant-time comparison) from anyone else on ``/v1`` and ``/api`` paths; binding to a non-loopback interface refuses to
-start without that token and TLS certificate + key files; optional static single-page-app mount under ``/static``.
+start without that token and TLS certificate + key files; the single-page Studio (``triune_b200/studio``, or ``static_dir``) mounted under ``/static`` and served at ``/``.
 """
 
 from __future__ import annotations
@@ -54,7 +54,8 @@ def create_app(static_dir: Optional[str] = None):
     from .routes_shell import shell_router
 
     app.include_router(shell_router)
-    root = Path(static_dir) if static_dir else None
+    # the packaged single-page Studio (chat, training control, graph canvas, fine-tuning, system) unless another directory is given
+    root = Path(static_dir) if static_dir else Path(__file__).resolve().parent.parent / "studio"
     if root is not None and root.is_dir() and (root / "index.html").is_file():
         from fastapi.staticfiles import StaticFiles
 
