@@ -394,12 +394,14 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated case names: " + ", ".join(CASES))
     ap.add_argument("--impl", default="both", choices=["both", "ours", "reference"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--budget", type=float, default=0.0, help="seconds after which the remaining cases are skipped (0: no limit)")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         emit(error="bench_micro.py needs a GPU")
         return 1
     names = [n for n in (a.only.split(",") if a.only else CASES) if n]
-    impls = ["reference", "ours"] if a.impl == "both" else [a.impl]
+    impls = ["ours", "reference"] if a.impl == "both" else [a.impl]
+    t_start = time.time()
     pr = torch.cuda.get_device_properties(0)
     emit(device=pr.name, sms=pr.multi_processor_count, torch=torch.__version__, timing="CUDA events, median, L2 flushed between calls",
          iters=a.iters, started=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()))
@@ -409,6 +411,9 @@ def main():
         for n in names:
             if n not in CASES:
                 emit(error=f"unknown case {n!r}")
+                continue
+            if a.budget and time.time() - t_start > a.budget:
+                emit(case=n, impl=impl, skipped=f"the time budget of {a.budget:.0f} s was used up")
                 continue
             guarded(CASES[n].__doc__.split("\n")[0] if CASES[n].__doc__ else n, impl)(CASES[n])(impl, a)
     return 0
