@@ -8,8 +8,10 @@ Categories (the reference groups its suite the same way, `scripts/run_all_benchm
 
     A  headline training step (bench.py, ours and the reference arm)         1 GPU
     B  serving: prefill 4 x 16384, decode, FP8 / NVFP4 (bench_serving.py)    1 GPU
-    C  kernels one at a time (triune_b200.bench_kernels, all cases)          1 GPU
-    D  associative recall of the mixers, 100-step optimizer convergence       1 GPU (or CPU)
+    C  kernels one at a time (triune_b200.bench_kernels, all cases) and the
+       reference's published micro-benchmarks with both arms (bench_micro.py)  1 GPU
+    D  associative recall of the mixers, 100-step optimizer convergence,
+       confidence-exit calibration, QR residuals, exit latencies              1 GPU (or CPU)
     E  multi-GPU: data parallel scaling, expert / tensor / pipeline parallel  2+ GPUs, skipped when there are fewer
     F  layer-streamed training from host memory (bench_streaming.py)         1 GPU
 
@@ -56,6 +58,10 @@ def plan(gpus: int, quick: bool) -> List[Tuple[str, int, int, List[str]]]:
         ("D", 0, 900, [PY, "-m", "triune_b200.evals.mqar"]),
         ("D", 0, 900, [PY, "-m", "triune_b200.evals.convergence", "--family", "dense"]),
         ("D", 0, 900, [PY, "-m", "triune_b200.evals.convergence", "--family", "moe"]),
+        ("D", 0, 900, [PY, "-m", "triune_b200.evals.calm", "--train-steps", "60"]),
+        ("D", 0, 900, [PY, "-m", "triune_b200.evals.qr_residuals", "--train-steps", "30"]),
+        ("D", 1, 600, [PY, "-m", "triune_b200.evals.dynamic_exits", "--calm-tau", "0.2"]),
+        ("C", 1, 1500, [PY, os.path.join(ROOT, "bench_micro.py")]),
     ]
     for n in (2, 4, 8):
         p.append(("E", n, 900, torchrun(n, 29500 + n, "bench.py", "--gpus", str(n), "--steps", steps, "--warmup", warm)))

@@ -976,3 +976,62 @@ def test_desktop_wsl_discovery_and_launch(monkeypatch):
     started.clear()
     d.start_session(8123, quiet=True, allow_wsl=True, run=run, popen=lambda cmd, **kw: started.append(cmd) or FakeProc(), platform="linux")
     assert started[0][0] == sys.executable  # WSL is only considered on a Windows host
+
+
+def test_calm_calibration_pieces():
+    """Statistics of the confidence-exit calibration on constructed data: Wilson bound, AUROC with ties, calibration
+    error, the threshold choice, and the whole evaluation on a tiny model."""
+    from triune_b200.evals import calm
+
+    assert calm.wilson_lower(0, 0) == 0.0 and 0.83 < calm.wilson_lower(95, 100) < 0.95 and calm.wilson_lower(100, 100) < 1.0
+    s = torch.tensor([0.1, 0.2, 0.3, 0.4, 0.5, 0.6])
+    assert calm.auroc(s, torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.bool)) == 1.0
+    assert calm.auroc(s, torch.tensor([1, 1, 1, 0, 0, 0], dtype=torch.bool)) == 0.0
+    assert calm.auroc(torch.tensor([0.5, 0.5, 0.5, 0.5]), torch.tensor([1, 0, 1, 0], dtype=torch.bool)) == 0.5  # all tied
+    assert calm.auroc(s, torch.ones(6, dtype=torch.bool)) is None
+    conf = torch.cat([torch.full((100,), 0.95), torch.full((100,), 0.15)])
+    agree = torch.cat([torch.ones(95), torch.zeros(5), torch.ones(15), torch.zeros(85)]).bool()
+    assert calm.reliability(conf, agree)["ece"] < 1e-6  # confidence equals the observed agreement in both bins
+    assert calm.reliability(conf, ~agree)["ece"] > 0.7
+    # margins above 0.4 always agree, below they agree half of the time: the smallest qualifying threshold is 0.4
+    g = torch.Generator().manual_seed(0)
+    margin = torch.rand(4000, generator=g)
+    ok = (margin >= 0.4) | (torch.rand(4000, generator=g) < 0.5)
+    assert calm.calibrate(margin, ok, 0.99) == 0.4
+    assert calm.calibrate(margin, ok, 0.99, min_positions=10**6) is None
+    rows = calm.curve(margin, ok)
+    assert rows[0]["coverage"] > rows[-1]["coverage"] and rows[-1]["agreement"] == 1.0
+
+    torch.manual_seed(0)
+    model = TriuneTransformer.from_config(ModelConfig(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=1, head_dim=32, num_experts=2,
+                                                      router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=3))
+    cal = calm.synthetic_batches(64, 2, 4, 24, seed=1)
+    held = calm.synthetic_batches(64, 2, 4, 24, seed=2)
+    assert not torch.equal(cal[0], held[0]) and cal[0].shape == (4, 25)
+    res = calm.evaluate(model, calm.collect(model, cal), calm.collect(model, held), (0.5,), min_positions=1)
+    assert res["positions"] == {"calibration": 192, "held_out": 192} and set(res["exits"]) == {"reflex", "limbic"}
+    assert 0.0 <= res["exits"]["reflex"]["agreement_all_positions"] <= 1.0
+    assert calm.layers_saved(model, 1.0, 0.0) == 0.4 and calm.layers_saved(model, 0.0, 1.0) == 0.2
+    lat = calm.policy_latency(model, held[0][:, :-1], 0.3, iters=1)
+    assert lat["full_depth_ms"] > 0 and lat["where_tokens_left"]["total_tokens"] == 96
+
+
+def test_qr_residuals_and_dynamic_exit_evals():
+    from triune_b200.evals import dynamic_exits, qr_residuals
+
+    rows = qr_residuals.sweep(K=6, d=96, r=8, conds=(1e1, 1e3, 1e6))
+    assert rows[0]["fast_path"] == 6 and rows[0]["fast_path_max"]["orthogonality"] < 1e-5 and rows[0]["fast_path_max"]["projector_distance"] < 1e-4
+    assert rows[1]["all_max"]["reconstruction"] < 1e-5
+    assert rows[2]["fallbacks"] == 6 and rows[2]["all_max"]["orthogonality"] < 1e-5  # ill-conditioned slices go to Householder QR
+    deg = qr_residuals.degenerate_cases()
+    assert deg["caught"] == [True, True, True] and deg["finite"]
+    A = qr_residuals.conditioned(2, 40, 5, 100.0, torch.Generator().manual_seed(0))
+    sv = torch.linalg.svdvals(A)
+    assert torch.allclose(sv[:, 0] / sv[:, -1], torch.full((2,), 100.0, dtype=torch.float64), rtol=1e-6)
+
+    torch.manual_seed(0)
+    model = TriuneTransformer.from_config(ModelConfig(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=1, head_dim=32, num_experts=2,
+                                                      router_prefix_layers=1, reflex_exit_layer=2, limbic_exit_layer=3))
+    res = dynamic_exits.measure(model, torch.randint(0, 64, (3, 16)), iters=1, calm_tau=0.5)
+    assert set(res["exits"]) == {"reflex", "limbic", "cortex"} and sum(res["router"]["sequences_per_depth"]) == 3
+    assert res["calm"]["where_tokens_left"]["total_tokens"] == 48
