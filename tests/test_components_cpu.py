@@ -1035,3 +1035,85 @@ def test_qr_residuals_and_dynamic_exit_evals():
     res = dynamic_exits.measure(model, torch.randint(0, 64, (3, 16)), iters=1, calm_tau=0.5)
     assert set(res["exits"]) == {"reflex", "limbic", "cortex"} and sum(res["router"]["sequences_per_depth"]) == 3
     assert res["calm"]["where_tokens_left"]["total_tokens"] == 48
+
+
+def test_local_ollama_probe_and_chat_stream():
+    """A stand-in daemon on the loopback address: tag listing, streamed chat pieces, a daemon-side error; nothing else is contacted."""
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from triune_b200.runtime import model_scanner as ms
+
+    seen = {}
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            body = json.dumps({"models": [{"name": "gemma3:4b"}, {"name": "qwen3:8b"}, {"nope": 1}]}).encode() if self.path == "/api/tags" else b"{}"
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_POST(self):
+            req = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            seen["req"] = req
+            lines = ([{"error": "model not found"}] if req["model"] == "missing" else
+                     [{"message": {"content": "Hel"}}, {"message": {"content": "lo"}}, {"message": {"content": ""}, "done": True}, {"message": {"content": "late"}}])
+            body = "".join(json.dumps(l) + "\n" for l in lines).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    t = threading.Thread(target=srv.serve_forever, daemon=True)
+    t.start()
+    url = f"http://127.0.0.1:{srv.server_port}"
+    try:
+        assert ms.query_ollama_running_tags(url, timeout=2.0) == ["gemma3:4b", "qwen3:8b"]
+        msgs = [{"role": "user", "content": "hi"}]
+        assert "".join(ms.stream_ollama_chat("gemma3:4b", msgs, url, options={"temperature": 0}, timeout=5.0)) == "Hello"
+        assert seen["req"]["stream"] is True and seen["req"]["messages"] == msgs and seen["req"]["options"] == {"temperature": 0}
+        with pytest.raises(RuntimeError, match="model not found"):
+            list(ms.stream_ollama_chat("missing", msgs, url, timeout=5.0))
+    finally:
+        srv.shutdown()
+    assert ms.query_ollama_running_tags(url, timeout=0.3) == []  # the daemon is gone
+    assert ms.query_ollama_running_tags("http://example.com:11434") == []  # never leaves the machine
+    with pytest.raises(ValueError):
+        list(ms.stream_ollama_chat("m", [], "http://example.com:11434"))
+    with pytest.raises(ConnectionError):
+        list(ms.stream_ollama_chat("m", [], url, timeout=0.5))
+
+
+def test_cli_reference_command_names_doctor_and_agent(tmp_path, capsys):
+    """The command names of the reference's CLI resolve here (aliases), `doctor` reports a healthy CPU installation,
+    and `agent` runs a goal through one persona and through a team, keeping a lesson for the next run."""
+    from triune_b200 import cli
+
+    p = cli.build_parser()
+    for argv in (["studio", "--no-browser"], ["benchmark"], ["build-native", "--target", "linux"], ["info"], ["cache-nvfp4", "--help"]):
+        if "--help" in argv:
+            with pytest.raises(SystemExit):
+                p.parse_args(argv)
+            capsys.readouterr()
+            continue
+        assert callable(p.parse_args(argv).fn), argv
+    assert p.parse_args(["studio"]).fn is cli.cmd_desktop and p.parse_args(["info"]).fn is cli.cmd_doctor
+    assert cli.main(["doctor"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["status"] == "healthy" and rep["tiny_forward"] and rep["studio_page"] and rep["model_zoo"]["presets"] >= 10
+    store = tmp_path / "agent"
+    base = ["agent", "--device", "cpu", "--model", "triune-nano", "--max-tokens", "4", "--store-dir", str(store)]
+    assert cli.main(base + ["list the files"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["persona"] == "assistant" and isinstance(out["text"], str)
+    assert cli.main(base + ["--team", "architect,engineer", "--goal", "list the files", "--read-only"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert [o["agent"] for o in out] == ["architect", "engineer"]
+    mem = json.loads((store / "memory.json").read_text())
+    assert len(mem["lessons"]) == 2
+    assert cli.main(["agent", "--device", "cpu"]) == 2  # no goal

@@ -345,3 +345,27 @@ def test_studio_page_is_served_and_matches_the_api(client):
     ids = set(re.findall(r'\$\("#([A-Za-z0-9_-]+)"\)', js.text))  # ids completed at run time ("#node-" + id) are not literals
     html_ids = set(re.findall(r'id="([A-Za-z0-9_-]+)"', page.text))
     assert ids and ids <= html_ids, sorted(ids - html_ids)
+
+
+def test_chat_through_a_local_ollama_daemon(client, monkeypatch):
+    """``model: "ollama:<tag>"`` is answered by the daemon on the loopback address, with and without streaming; a daemon
+    that does not answer is a 502."""
+    from triune_b200.runtime import model_scanner as ms
+
+    calls = []
+
+    def fake(tag, msgs, base_url=ms.OLLAMA_URL, options=None, timeout=120.0):
+        calls.append((tag, msgs, options))
+        if tag == "down":
+            raise ConnectionError("no Ollama daemon answers")
+        yield from ("Hi", " there")
+
+    monkeypatch.setattr(ms, "stream_ollama_chat", fake)
+    body = {"model": "ollama:gemma3:4b", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 5, "temperature": 0.0}
+    r = client.post("/v1/chat/completions", json=body)  # no local model is loaded: not needed for this backend
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"] == "Hi there" and r.json()["model"] == "ollama:gemma3:4b"
+    assert calls[0][0] == "gemma3:4b" and calls[0][1] == [{"role": "user", "content": "hello"}] and calls[0][2]["num_predict"] == 5
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as s:
+        text = "".join(json.loads(l[6:])["choices"][0]["delta"].get("content", "") for l in s.iter_lines() if l.startswith("data: {"))
+    assert text == "Hi there"
+    assert client.post("/v1/chat/completions", json={**body, "model": "ollama:down"}).status_code == 502

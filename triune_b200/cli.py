@@ -347,6 +347,109 @@ def cmd_gpucheck(a) -> int:
     return 0
 
 
+def cmd_doctor(a) -> int:
+    """One report of everything an installation depends on; exit code 1 when something required is missing."""
+    import importlib.util
+    import platform
+
+    import torch
+
+    from . import _ext
+    from .models.zoo import CANONICAL_MODEL_SPECS
+
+    rep: Dict[str, Any] = {"python": platform.python_version(), "platform": platform.platform(), "torch": torch.__version__,
+                           "cuda_available": torch.cuda.is_available(), "cuda_runtime": torch.version.cuda}
+    problems: List[str] = []
+    if torch.cuda.is_available():
+        rep["gpus"] = []
+        for i in range(torch.cuda.device_count()):
+            pr = torch.cuda.get_device_properties(i)
+            rep["gpus"].append({"index": i, "name": pr.name, "memory_gib": round(pr.total_memory / 2**30, 2), "capability": f"{pr.major}.{pr.minor}",
+                                "sms": pr.multi_processor_count})
+            if pr.major != 10:
+                problems.append(f"GPU {i} ({pr.name}) is not compute capability 10.x: the sm_100a kernels cannot run on it")
+    rep["cuda_extension"] = {"built": _ext.ext_available()}
+    if torch.cuda.is_available() and not _ext.ext_available():
+        problems.append("the CUDA extension is not built: run `python -m triune_b200 native`")
+    try:
+        from .ops import _c_bridge
+
+        rep["native_host_library"] = _c_bridge.get_native_c_info()
+    except Exception as e:
+        rep["native_host_library"] = {"loaded": False, "error": f"{type(e).__name__}: {e}"}
+    rep["model_zoo"] = {"presets": len(CANONICAL_MODEL_SPECS)}
+    rep["optimizers"] = ["centroid_steer (subspace tier with triangular core)", "muon (Newton-Schulz)", "adamw"]
+    rep["server_extras"] = {m: importlib.util.find_spec(m) is not None for m in ("fastapi", "uvicorn", "pydantic")}
+    if not all(rep["server_extras"].values()):
+        problems.append("the HTTP server needs fastapi, uvicorn and pydantic")
+    rep["optional"] = {m: importlib.util.find_spec(m) is not None for m in ("tokenizers", "safetensors", "pyarrow", "transformers", "datasets")}
+    studio = Path(__file__).resolve().parent / "studio" / "index.html"
+    rep["studio_page"] = studio.is_file()
+    try:
+        from .runtime.model_scanner import query_ollama_running_tags
+
+        tags = sorted(query_ollama_running_tags())
+        rep["local_ollama"] = tags[:6] if tags else "not detected on 127.0.0.1:11434"
+    except Exception:
+        rep["local_ollama"] = "not probed"
+    ck = Path("checkpoints_full")
+    rep["checkpoints"] = sorted(p.name for p in ck.glob("*.pt"))[:8] if ck.is_dir() else []
+    try:  # a forward pass of a tiny model is the one end-to-end proof that the install computes
+        from .models.zoo import load_model
+
+        m = load_model("default", vocab_size=64, hidden_dim=32, num_layers=4, num_heads=1, head_dim=32, num_experts=2, router_prefix_layers=1,
+                       reflex_exit_layer=2, limbic_exit_layer=3)
+        y = m(torch.randint(0, 64, (1, 8)), force_depth=2)[0]
+        rep["tiny_forward"] = bool(torch.isfinite(y).all())
+    except Exception as e:
+        rep["tiny_forward"] = False
+        problems.append(f"a tiny forward pass failed: {type(e).__name__}: {e}")
+    rep["status"] = "healthy" if not problems else "problems"
+    rep["problems"] = problems
+    _print(rep)
+    return 0 if not problems else 1
+
+
+def cmd_agent(a) -> int:
+    """A goal through the agent loop (persona prompt, tool calls, persistent memory) on a locally loaded model."""
+    from .agents import Agent, AgentMemoryStore, MultiAgentOrchestrator, Persona, ToolRegistry, build_integrated_toolbelt
+
+    goal = a.goal or a.goal_pos
+    if not goal:
+        print("a goal is required (positional or --goal)", file=sys.stderr)
+        return 2
+    st = _load_for_inference(a)
+    tools = build_integrated_toolbelt()
+    if a.read_only:
+        ro = ToolRegistry()
+        for t in tools.tools.values():
+            if not any(w in t.name for w in ("write", "edit", "delete", "append")):
+                ro.register(t)
+        tools = ro
+    store = AgentMemoryStore(str(Path(a.store_dir) / "memory.json"))
+
+    def generate(prompt: str) -> str:
+        return st.generate(prompt, max_new_tokens=a.max_tokens, temperature=0.7, template=False)["text"]
+
+    def persona(spec: str) -> Persona:
+        name, sep, prompt = spec.partition("=")
+        return Persona(name.strip(), prompt.strip() if sep else f"You are the {name.strip()} of the team. Be brief and concrete.")
+
+    lessons = store.recall(goal, k=3)
+    hint = ("\nRelevant notes from earlier runs:\n" + "\n".join(f"- {text}" for _, text in lessons)) if lessons else ""
+    if a.team:
+        names = [n for n in a.team.split(",") if n.strip()]
+        orch = MultiAgentOrchestrator({n: Agent(generate, persona(n), tools, max_tool_rounds=a.max_steps) for n in names})
+        out: Any = orch.run(goal + hint, names)
+    else:
+        out = Agent(generate, persona(a.persona), tools, max_tool_rounds=a.max_steps).run(goal + hint)
+    last = out[-1] if isinstance(out, list) else out
+    store.add_lesson(f"goal: {goal} -> {str(last.get('text', ''))[:400]}", tags=["cli"])
+    store.save()
+    _print(out)
+    return 0
+
+
 def cmd_plan_memory(a) -> int:
     from .config import get_model_config
     from .runtime.memory_planner import MemoryPlanner
@@ -627,7 +730,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--auto_fit", "--auto-fit", dest="auto_fit", action="store_true")
     s.set_defaults(fn=cmd_train)
 
-    s = sub.add_parser("bench", help="run the headline benchmark or a kernel micro-benchmark")
+    s = sub.add_parser("bench", aliases=["benchmark"], help="run the headline benchmark or a kernel micro-benchmark")
     s.add_argument("--gpus", type=int, default=1)
     s.add_argument("--steps", type=int, default=10)
     s.add_argument("--warmup", type=int, default=3)
@@ -635,6 +738,19 @@ def build_parser() -> argparse.ArgumentParser:
     s.set_defaults(fn=cmd_bench)
 
     sub.add_parser("gpucheck", help="device, driver and kernel diagnostics").set_defaults(fn=cmd_gpucheck)
+    sub.add_parser("doctor", aliases=["info"], help="health of the whole installation: runtime, devices, kernels, zoo, server extras, local state").set_defaults(fn=cmd_doctor)
+
+    s = sub.add_parser("agent", help="run a goal through the tool-using agent loop on a local model")
+    model_args(s, default="triune-nano")
+    s.add_argument("goal_pos", nargs="?", default=None, help="the goal (or use --goal)")
+    s.add_argument("-g", "--goal", default=None)
+    s.add_argument("--persona", default="assistant", help="persona name; 'name=system prompt' defines one on the spot")
+    s.add_argument("--team", default=None, help="comma-separated personas that take the goal in turn, each seeing the previous answer")
+    s.add_argument("--max-steps", type=int, default=3, help="tool rounds per goal")
+    s.add_argument("--max-tokens", type=int, default=128)
+    s.add_argument("--read-only", action="store_true", help="leave out the tools that write files")
+    s.add_argument("--store-dir", default="checkpoints/agent_harness", help="persistent memory and skills")
+    s.set_defaults(fn=cmd_agent)
 
     s = sub.add_parser("plan-memory", help="estimate the memory budget of a run")
     s.add_argument("--model", default="triune-base")
@@ -647,7 +763,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--quantization", default=None)
     s.set_defaults(fn=cmd_plan_memory)
 
-    s = sub.add_parser("cache", help="NVFP4 disk cache of a Hugging Face checkpoint")
+    s = sub.add_parser("cache", aliases=["cache-nvfp4"], help="NVFP4 disk cache of a Hugging Face checkpoint")
     s.add_argument("action", choices=["build", "info"])
     s.add_argument("--source", default=None)
     s.add_argument("--cache-dir", required=True)
@@ -719,7 +835,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--key", default=None, help="signing key (default: TRIUNE_PLUGIN_KEY)")
     s.set_defaults(fn=cmd_plugin)
 
-    s = sub.add_parser("desktop", help="start (or reuse) the local server and open its page in the browser")
+    s = sub.add_parser("desktop", aliases=["studio"], help="start (or reuse) the local server and open its page in the browser")
     model_args(s, default=None)
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8000)
@@ -746,7 +862,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--dry-run", action="store_true")
     s.set_defaults(fn=cmd_uninstall)
 
-    s = sub.add_parser("package", help="generate launcher bundles (Linux AppDir, macOS .app, Windows .cmd)")
+    s = sub.add_parser("package", aliases=["build-native"], help="generate launcher bundles (Linux AppDir, macOS .app, Windows .cmd)")
     s.add_argument("--target", default="all", help="linux, macos, windows or all")
     s.add_argument("--out", default=None, help="output directory (default: dist/ in the source tree)")
     s.set_defaults(fn=cmd_package)

@@ -132,3 +132,61 @@ def scan_models(roots: Optional[Iterable[str]] = None, max_depth: int = 4, limit
     for e in found:
         by_kind[e["kind"]] = by_kind.get(e["kind"], 0) + 1
     return {"models": found, "counts": by_kind, "total_bytes": sum(int(e.get("size_bytes", 0)) for e in found)}
+
+
+# ---------------------------------------------------------------------------------------------------- a local Ollama daemon
+OLLAMA_URL = "http://127.0.0.1:11434"
+
+
+def _loopback(url: str) -> bool:
+    from urllib.parse import urlparse
+
+    host = (urlparse(url).hostname or "").lower()
+    return host in ("127.0.0.1", "localhost", "::1")
+
+
+def query_ollama_running_tags(base_url: str = OLLAMA_URL, timeout: float = 0.4) -> List[str]:
+    """Model tags a local Ollama daemon offers (``GET /api/tags``); an empty list when nothing answers on the loopback
+    address. Only loopback URLs are contacted (``triune/runtime/model_scanner.py:213-286`` of the reference)."""
+    import urllib.request
+
+    if not _loopback(base_url):
+        return []
+    try:
+        with urllib.request.urlopen(base_url.rstrip("/") + "/api/tags", timeout=timeout) as r:
+            data = json.loads(r.read().decode("utf-8", "replace"))
+    except (OSError, ValueError):
+        return []
+    return [str(m.get("name")) for m in data.get("models", []) if isinstance(m, dict) and m.get("name")]
+
+
+def stream_ollama_chat(model: str, messages: List[Dict[str, str]], base_url: str = OLLAMA_URL, options: Optional[Dict[str, Any]] = None,
+                       timeout: float = 120.0):
+    """Yield the text pieces of a chat answered by a local Ollama daemon (``POST /api/chat`` with ``stream: true``: one
+    JSON object per line). Raises ``ConnectionError`` when the daemon does not answer; refuses non-loopback URLs."""
+    import urllib.request
+
+    if not _loopback(base_url):
+        raise ValueError("only a daemon on the loopback address is contacted")
+    body = json.dumps({"model": model, "messages": messages, "stream": True, **({"options": options} if options else {})}).encode()
+    req = urllib.request.Request(base_url.rstrip("/") + "/api/chat", data=body, headers={"Content-Type": "application/json"}, method="POST")
+    try:
+        resp = urllib.request.urlopen(req, timeout=timeout)
+    except OSError as e:
+        raise ConnectionError(f"no Ollama daemon answers at {base_url}: {e}") from e
+    with resp:
+        for raw in resp:
+            line = raw.decode("utf-8", "replace").strip()
+            if not line:
+                continue
+            try:
+                obj = json.loads(line)
+            except ValueError:
+                continue
+            if obj.get("error"):
+                raise RuntimeError(str(obj["error"]))
+            piece = (obj.get("message") or {}).get("content")
+            if piece:
+                yield piece
+            if obj.get("done"):
+                break

@@ -94,9 +94,59 @@ def _completion(req_id: str, model_id: str, text: str, tele: Dict[str, Any], fin
 
 
 # ---------------------------------------------------------------------------------------------------- chat
+async def _ollama_completion(req: ChatRequest):
+    """``model: "ollama:<tag>"``: the request is answered by the Ollama daemon on this machine's loopback address (the
+    reference's Studio offers local Ollama models next to its own, ``triune/runtime/model_scanner.py:213-470``)."""
+    from ..runtime.model_scanner import stream_ollama_chat
+
+    tag = req.model.split(":", 1)[1]
+    req_id = req.request_id or f"chatcmpl-{uuid.uuid4().hex[:24]}"
+    msgs = [{"role": m.role, "content": m.content} for m in req.messages] or [{"role": "user", "content": req.prompt or ""}]
+    opts = {"temperature": req.temperature, "top_k": req.top_k, "num_predict": req.max_tokens, "repeat_penalty": req.repetition_penalty}
+    loop = asyncio.get_running_loop()
+    if not req.stream:
+        try:
+            text = await loop.run_in_executor(None, lambda: "".join(stream_ollama_chat(tag, msgs, options=opts)))
+        except ConnectionError as e:
+            raise HTTPException(502, str(e))
+        except Exception as e:
+            raise HTTPException(500, f"{type(e).__name__}: {e}")
+        return _completion(req_id, req.model, text, {"backend": "ollama"})
+    pieces: "_queue.Queue[Optional[Dict[str, Any]]]" = _queue.Queue()
+
+    def worker():
+        try:
+            for piece in stream_ollama_chat(tag, msgs, options=opts):
+                pieces.put({"delta": piece})
+        except Exception as e:
+            pieces.put({"error": f"{type(e).__name__}: {e}"})
+        finally:
+            pieces.put(None)
+
+    threading.Thread(target=worker, name=f"ollama-{req_id}", daemon=True).start()
+
+    async def sse():
+        head = {"id": req_id, "object": "chat.completion.chunk", "created": int(time.time()), "model": req.model}
+        yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
+        while True:
+            item = await loop.run_in_executor(None, pieces.get)
+            if item is None:
+                break
+            if "error" in item:
+                yield "data: " + json.dumps({**head, "error": item["error"]}) + "\n\n"
+            else:
+                yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {"content": item["delta"]}, "finish_reason": None}]}) + "\n\n"
+        yield "data: " + json.dumps({**head, "choices": [{"index": 0, "delta": {}, "finish_reason": "stop"}]}) + "\n\n"
+        yield "data: [DONE]\n\n"
+
+    return StreamingResponse(sse(), media_type="text/event-stream", headers={"Cache-Control": "no-cache", "X-Request-Id": req_id})
+
+
 @router.post("/v1/chat/completions")
 async def chat_completions(req: ChatRequest):
     st = get_state()
+    if req.model and req.model.startswith("ollama:"):
+        return await _ollama_completion(req)
     if st.model is None:
         raise HTTPException(409, "no model is loaded; POST /v1/models/load first")
     req_id = req.request_id or f"chatcmpl-{uuid.uuid4().hex[:24]}"
