@@ -1108,12 +1108,74 @@ def test_cli_reference_command_names_doctor_and_agent(tmp_path, capsys):
     assert rep["status"] == "healthy" and rep["tiny_forward"] and rep["studio_page"] and rep["model_zoo"]["presets"] >= 10
     store = tmp_path / "agent"
     base = ["agent", "--device", "cpu", "--model", "triune-nano", "--max-tokens", "4", "--store-dir", str(store)]
-    assert cli.main(base + ["list the files"]) == 0
+    assert cli.main(base + ["list the files", "--workspace", str(tmp_path)]) == 0
     out = json.loads(capsys.readouterr().out)
-    assert out["persona"] == "assistant" and isinstance(out["text"], str)
-    assert cli.main(base + ["--team", "architect,engineer", "--goal", "list the files", "--read-only"]) == 0
+    assert out["persona"] == "engineer" and isinstance(out["text"], str) and "read_file" in out["tools_offered"]  # "list the files": engineer by keyword
+    assert cli.main(base + ["--team", "architect,engineer", "--goal", "list the files", "--read-only", "--workspace", str(tmp_path)]) == 0
     out = json.loads(capsys.readouterr().out)
     assert [o["agent"] for o in out] == ["architect", "engineer"]
     mem = json.loads((store / "memory.json").read_text())
     assert len(mem["lessons"]) == 2
     assert cli.main(["agent", "--device", "cpu"]) == 2  # no goal
+
+
+def test_agent_harness_personas_tools_memory_and_skills(tmp_path):
+    """The harness with a scripted generator: persona choice, workspace confinement, read-only and shell switches, the
+    public-URL guard, tool statistics, lessons recalled by a later run, and a skill written from a successful run."""
+    from triune_b200.agents.harness import AgentHarness, choose_persona, resolve_persona, workspace_tools
+
+    assert choose_persona("why does the kernel hang with a traceback").name == "debugger"
+    assert choose_persona("make the decode loop faster, profile the latency").name == "optimizer"
+    assert choose_persona("hello").name == "assistant"
+    assert resolve_persona("sentinel").name == "sentinel" and resolve_persona("auto", "design the module layout").name == "architect"
+    custom = resolve_persona("poet=Answer in verse.")
+    assert custom.name == "poet" and custom.system_prompt == "Answer in verse."
+    assert resolve_persona("navigator").system_prompt.startswith("You are the navigator")
+
+    ws = tmp_path / "ws"
+    (ws / "src").mkdir(parents=True)
+    (ws / "src" / "a.py").write_text("def f():\n    return 41  # TODO fix\n")
+    (tmp_path / "secret.txt").write_text("outside")
+    tools = workspace_tools(str(ws), fetch=lambda url: "fetched " + url)
+    assert tools.call("list_dir", path=".") == ["src/"] and tools.call("read_file", path="src/a.py").startswith("def f")
+    assert tools.call("search", pattern="TODO")[0] == {"file": "src/a.py", "line": 2, "text": "    return 41  # TODO fix"}
+    for bad in ("../secret.txt", "/etc/passwd", "src/../../secret.txt"):
+        with pytest.raises(PermissionError):
+            tools.call("read_file", path=bad)
+    with pytest.raises(PermissionError):
+        tools.call("write_file", path="../evil.txt", content="x")
+    assert "edited" in tools.call("edit_file", path="src/a.py", old="41", new="42") and "42" in (ws / "src" / "a.py").read_text()
+    with pytest.raises(ValueError):
+        tools.call("edit_file", path="src/a.py", old="zzz", new="y")
+    with pytest.raises(PermissionError):
+        tools.call("http_get", url="http://127.0.0.1:8000/v1/models")
+    with pytest.raises(PermissionError):
+        tools.call("http_get", url="http://169.254.169.254/latest/meta-data")
+    assert tools.call("http_get", url="https://8.8.8.8/x") == "fetched https://8.8.8.8/x"
+    ro = workspace_tools(str(ws), read_only=True, allow_shell=True)
+    assert "write_file" not in ro.tools and "shell" not in ro.tools and "read_file" in ro.tools
+    sh = workspace_tools(str(ws), allow_shell=True)
+    assert sh.call("shell", command="ls src")["stdout"].strip() == "a.py"
+
+    script = ['I will look. <|tool_call|> {"tool": "search", "args": {"pattern": "TODO"}}', "The TODO is in src/a.py line 2."]
+    prompts = []
+
+    def generate(prompt):
+        prompts.append(prompt)
+        return script[min(len(prompts) - 1, len(script) - 1)] if len(prompts) <= 2 else "done"
+
+    h = AgentHarness(generate, str(tmp_path / "store"), workspace=str(ws))
+    out = h.run("debug the TODO bug: find where it fails")
+    assert out["persona"] == "debugger" and out["text"] == "The TODO is in src/a.py line 2."
+    assert out["tool_calls"][0]["result"][0]["file"] == "src/a.py" and "<|tool_return|>" in prompts[1]
+    assert out["new_skill"] and (tmp_path / "store" / "skills" / f"{out['new_skill']}.md").is_file()
+    assert h.memory.data["tool_stats"]["search"] == {"calls": 1, "failures": 0}
+    # a second harness on the same store starts from the lesson and the skill of the first run
+    prompts.clear()
+    h2 = AgentHarness(lambda p: (prompts.append(p), "ok")[1], str(tmp_path / "store"), workspace=str(ws))
+    h2.memory.set_preference("style", "terse")
+    out2 = h2.run("find the TODO in the code again")
+    assert "Notes from earlier runs" in prompts[0] and "## Skill: " in prompts[0] and "style = terse" in prompts[0]
+    assert out2["new_skill"] is None  # no tool was used this time
+    team = h2.run_team("review the code for risk", ["engineer", "sentinel"])
+    assert [t["agent"] for t in team] == ["engineer", "sentinel"] and team[1]["persona"] == "sentinel"

@@ -149,7 +149,7 @@ def test_shell_routes(client, tmp_path):
     assert client.post("/v1/engine/benchmarks", json={"case": "nope"}).status_code == 404
 
 
-def test_agents_and_turbo_mode(client):
+def test_agents_and_turbo_mode(client, tmp_path):
     """Agent endpoints drive the loaded model; turbo mode answers greedy requests through the graph decoder's step
     function (eager on CPU) with the same tokens as the sampling path at temperature 0."""
     assert client.post("/v1/agents/run", json={"message": "hi"}).status_code == 409
@@ -165,6 +165,15 @@ def test_agents_and_turbo_mode(client):
     assert [s["agent"] for s in team["steps"]] == ["planner", "worker"]
     st = client.get("/v1/agents/state").json()
     assert st["runs"] == 1 and st["memory_items"] == 1 and len(st["tools"]) > 0
+    # the harness form: persona by the goal's words, workspace tools without the writing ones, a lesson kept on disk
+    (tmp_path / "ws").mkdir()
+    h = client.post("/v1/agents/run", json={"goal": "review the code for security risk", "workspace": str(tmp_path / "ws"), "max_tokens": 3,
+                                            "store_dir": str(tmp_path / "store")}).json()
+    assert h["persona"] == "sentinel" and "read_file" in h["tools_offered"] and "write_file" not in h["tools_offered"] and "shell" not in h["tools_offered"]
+    assert (tmp_path / "store" / "memory.json").is_file()
+    t = client.post("/v1/agents/run", json={"goal": "plan it", "team": ["architect", "engineer"], "max_tokens": 3, "store_dir": str(tmp_path / "store"),
+                                            "workspace": str(tmp_path / "ws")}).json()
+    assert [x["agent"] for x in t["steps"]] == ["architect", "engineer"]
 
     # pure greedy decoding of the same prompt, token by token through the ordinary model call
     from triune_b200.inference import generate_tokens

@@ -411,42 +411,24 @@ def cmd_doctor(a) -> int:
 
 
 def cmd_agent(a) -> int:
-    """A goal through the agent loop (persona prompt, tool calls, persistent memory) on a locally loaded model."""
-    from .agents import Agent, AgentMemoryStore, MultiAgentOrchestrator, Persona, ToolRegistry, build_integrated_toolbelt
+    """A goal through the agent harness (persona, workspace tools, skills, persistent memory) on a locally loaded model."""
+    from .agents.harness import AgentHarness
 
     goal = a.goal or a.goal_pos
     if not goal:
         print("a goal is required (positional or --goal)", file=sys.stderr)
         return 2
     st = _load_for_inference(a)
-    tools = build_integrated_toolbelt()
-    if a.read_only:
-        ro = ToolRegistry()
-        for t in tools.tools.values():
-            if not any(w in t.name for w in ("write", "edit", "delete", "append")):
-                ro.register(t)
-        tools = ro
-    store = AgentMemoryStore(str(Path(a.store_dir) / "memory.json"))
 
     def generate(prompt: str) -> str:
         return st.generate(prompt, max_new_tokens=a.max_tokens, temperature=0.7, template=False)["text"]
 
-    def persona(spec: str) -> Persona:
-        name, sep, prompt = spec.partition("=")
-        return Persona(name.strip(), prompt.strip() if sep else f"You are the {name.strip()} of the team. Be brief and concrete.")
-
-    lessons = store.recall(goal, k=3)
-    hint = ("\nRelevant notes from earlier runs:\n" + "\n".join(f"- {text}" for _, text in lessons)) if lessons else ""
+    h = AgentHarness(generate, a.store_dir, workspace=a.workspace, persona=a.persona, read_only=a.read_only, allow_shell=a.allow_shell,
+                     auto_skill=not a.no_auto_skill, max_steps=a.max_steps)
     if a.team:
-        names = [n for n in a.team.split(",") if n.strip()]
-        orch = MultiAgentOrchestrator({n: Agent(generate, persona(n), tools, max_tool_rounds=a.max_steps) for n in names})
-        out: Any = orch.run(goal + hint, names)
+        _print(h.run_team(goal, [n.strip() for n in a.team.split(",") if n.strip()]))
     else:
-        out = Agent(generate, persona(a.persona), tools, max_tool_rounds=a.max_steps).run(goal + hint)
-    last = out[-1] if isinstance(out, list) else out
-    store.add_lesson(f"goal: {goal} -> {str(last.get('text', ''))[:400]}", tags=["cli"])
-    store.save()
-    _print(out)
+        _print(h.run(goal))
     return 0
 
 
@@ -744,7 +726,11 @@ def build_parser() -> argparse.ArgumentParser:
     model_args(s, default="triune-nano")
     s.add_argument("goal_pos", nargs="?", default=None, help="the goal (or use --goal)")
     s.add_argument("-g", "--goal", default=None)
-    s.add_argument("--persona", default="assistant", help="persona name; 'name=system prompt' defines one on the spot")
+    s.add_argument("--persona", default="auto", help="auto (by the goal), architect, engineer, researcher, debugger, optimizer, tutor, sentinel, "
+                   "or 'name=system prompt' for one defined on the spot")
+    s.add_argument("--workspace", default=".", help="directory the file tools are confined to")
+    s.add_argument("--allow-shell", action="store_true", help="offer a shell tool inside the workspace")
+    s.add_argument("--no-auto-skill", action="store_true", help="do not write successful tool sequences down as skills")
     s.add_argument("--team", default=None, help="comma-separated personas that take the goal in turn, each seeing the previous answer")
     s.add_argument("--max-steps", type=int, default=3, help="tool rounds per goal")
     s.add_argument("--max-tokens", type=int, default=128)

@@ -421,9 +421,30 @@ async def agents_persona(body: Dict[str, Any]):
 
 @shell_router.post("/v1/agents/run")
 async def agents_run(body: Dict[str, Any]):
+    """``{"message": ...}`` runs the session agent (its persona and in-memory notes). With ``"harness": true`` (or a
+    ``persona`` / ``team`` / ``workspace`` key) the goal goes through the agent harness instead: persona by name or by the
+    goal's words, file tools confined to ``workspace`` (read-only unless ``allow_write``), skills and lessons kept under
+    ``store_dir`` between runs. The shell tool is never offered over HTTP."""
+    goal = str(body.get("message") or body.get("goal") or "")
     try:
-        get_state().require_model()
-        out = await asyncio.to_thread(_agent(max_tokens=int(body.get("max_tokens", 256))).run, str(body.get("message", "")))
+        st = get_state()
+        st.require_model()
+        if body.get("harness") or any(k in body for k in ("persona", "team", "workspace")):
+            from ..agents.harness import AgentHarness
+
+            max_tokens = int(body.get("max_tokens", 256))
+
+            def generate(prompt: str) -> str:
+                return st.generate(prompt, max_new_tokens=max_tokens, temperature=float(body.get("temperature", 0.7)), template=False)["text"]
+
+            h = AgentHarness(generate, str(body.get("store_dir") or "checkpoints/agent_harness"), workspace=str(body.get("workspace") or "."),
+                             persona=str(body.get("persona") or "auto"), read_only=not bool(body.get("allow_write", False)), allow_shell=False,
+                             auto_skill=bool(body.get("auto_skill", True)), max_steps=int(body.get("max_steps", 3)))
+            team = body.get("team")
+            out = await asyncio.to_thread(h.run_team, goal, [str(t) for t in team]) if team else await asyncio.to_thread(h.run, goal)
+            out = {"steps": out} if team else out
+        else:
+            out = await asyncio.to_thread(_agent(max_tokens=int(body.get("max_tokens", 256))).run, goal)
     except RuntimeError as e:
         raise _bad(e, 409)
     _agents()["runs"] += 1
