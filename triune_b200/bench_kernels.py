@@ -367,7 +367,92 @@ def case_tp(a):
     dist.destroy_process_group()
 
 
-CASES = {"tp": case_tp, "dp": case_dp, "mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
+def case_small(a):
+    """The small bandwidth- or latency-bound kernels that have no case of their own: rotary embedding, add + RMSNorm,
+    the GLA decode step, the tier router, the heat map and tier-colour render, the steer update, the triangular AdamW on
+    the subspace cores, Newton-Schulz on a batch of square matrices, the LoRA linear, the small-M NVFP4 product and the
+    GGML block decoder. Each runs on its own; a failure is printed and the next one runs."""
+    from . import _ext, ops
+    from .ops import reference as ref
+
+    e = _ext.ext()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.bfloat16, generator=g)
+    f32 = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.float32, generator=g)
+    it = max(2, min(a.iters, 5))
+
+    def run(name, build):
+        try:
+            fn, nbytes, flops = build()
+            with torch.no_grad():
+                report(name, timeit(fn, it, 2), flops=flops, nbytes=nbytes)
+        except Exception as ex:  # keep going: every line of this case is independent
+            print(json.dumps({"case": name, "error": f"{type(ex).__name__}: {ex}"[:200]}), flush=True)
+
+    def rope():
+        x = bf(32, 2048, 6, 64)
+        cos, sin = ops.rope_tables(2048, 64, device=dev)
+        return (lambda: ops.apply_rope(x, cos, sin)), 2 * x.numel() * 2, 0.0
+
+    def add_norm():
+        x, r, w = bf(32768, 2048), bf(32768, 2048), torch.ones(2048, device=dev, dtype=torch.bfloat16)
+        return (lambda: ops.add_rmsnorm(x, r, w)), 4 * x.numel() * 2, 0.0
+
+    def decode():
+        q, k, v = bf(4, 1, 6, 64), bf(4, 1, 6, 64), bf(4, 1, 6, 64)
+        gd = -torch.rand(4, 1, 6, 64, device=dev, generator=g).to(torch.bfloat16) * 0.1
+        st = f32(4, 6, 64, 64)
+        return (lambda: ops.gla(q, k, v, gd, initial_state=st)), 2 * st.numel() * 4, 0.0
+
+    def tiers():
+        lg = f32(65536, 3)
+        return (lambda: ops.route_tiers(lg, 0.5)), lg.numel() * 4 + 65536 * 4, 0.0
+
+    def heat():
+        act = f32(8192 * 384)
+        return (lambda: ops.neuron_heatmap(act, 64)), act.numel() * 4, 0.0
+
+    def render():
+        act, t = f32(8192, 1536), torch.randint(0, 3, (8192,), device=dev, generator=g)
+        return (lambda: ops.tier_colour_render(act, t)), act.numel() * 8, 0.0
+
+    def steer():
+        P, G = f32(80, 257, 257), f32(80, 257, 257)
+        return (lambda: ops.triangular_steer_update(P, G, 0.9, 0.18)), 3 * P.numel() * 4, 0.0
+
+    def tri_adamw():
+        S, m, v = f32(80, 257, 257), torch.zeros(80, 257, 257, device=dev), torch.zeros(80, 257, 257, device=dev)
+        return (lambda: e.triangular_adamw(S, m, v, 0.9, 0.999, 1e-8, 3, True, None)), 6 * S.numel() * 4, 0.0
+
+    def ns():
+        G = bf(40, 384, 384)
+        return (lambda: ops.muon_ns(G, 5)), 0.0, 40 * 5 * 3 * 2.0 * 384**3
+
+    def lora():
+        x, w, A, B = bf(8192, 2048), bf(2048, 2048) * 0.02, bf(16, 2048) * 0.02, bf(2048, 16) * 0.02
+        return (lambda: ops.lora_linear(x, w, None, A, B, 2.0)), 0.0, 2.0 * 8192 * 2048 * (2048 + 32)
+
+    def gemv():
+        w = bf(4096, 4096) * 0.02
+        packed, scales, ts = ops.nvfp4_quantize(w)
+        x = bf(4, 4096)
+        return (lambda: e.nvfp4_gemv(x, packed, scales, ts)), packed.numel() + scales.numel(), 0.0
+
+    def ggml():
+        # Q8_0: blocks of 32 values = one fp16 scale + 32 int8; 64 Mi values decoded to bf16
+        n = 64 << 20
+        raw = torch.randint(0, 255, (n // 32 * 34,), device=dev, dtype=torch.uint8, generator=g)
+        return (lambda: e.ggml_dequant(raw, 8, n)), raw.numel() + n * 2, 0.0
+
+    for name, b in (("rotary embedding 32x2048x6x64", rope), ("add + RMSNorm 32768x2048", add_norm), ("GLA decode step B=4 H=6", decode),
+                    ("tier router 65536 rows", tiers), ("neuron heat map 3.1 M activations, 64 bins", heat), ("tier-colour render 8192x1536", render),
+                    ("steer update 80x257x257", steer), ("triangular AdamW 80x257x257", tri_adamw), ("Newton-Schulz 5 steps, 40x384x384", ns),
+                    ("LoRA linear 8192x2048x2048 r=16", lora), ("NVFP4 small-M product 4x4096x4096", gemv), ("GGML Q8_0 decode, 64 Mi values", ggml)):
+        run(name, b)
+
+
+CASES = {"small": case_small, "tp": case_tp, "dp": case_dp, "mlp": case_mlp, "moe_route": case_moe_route, "fp8": case_fp8, "nvfp4": case_nvfp4, "gemm": case_gemm, "wgrad": case_wgrad, "gla": case_gla, "gdn": case_gdn, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "ce": case_ce}
 
 
 def main():
