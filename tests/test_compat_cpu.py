@@ -1,0 +1,155 @@
+"""The reference's import paths served by this framework (``triune_b200.compat``)."""
+
+import importlib
+import sys
+
+import pytest
+import torch
+
+from triune_b200 import compat
+
+REFERENCE_EXPORTS = {
+    "optim": "AdamW8bit CentroidSteerOptimizer HAS_8BIT LowSpaceWeightProjector Muon QuantumUnitaryOptimizer UnitaryManifoldOptimizer build_optimizer zeropower_via_newtonschulz5",
+    "model": "CANONICAL_MODEL_SPECS MODEL_REGISTRY ModelSpec TriuneModel TriuneTransformer SelfSpeculativeGenerator TransformerBlock HybridAttention VectorisedGLA MoE_FFN "
+             "RoutingResult RMSNorm RotaryEmbedding apply_rotary rotate_half GumbelSoftmaxRouter FP4Linear FP8Linear build_model build_model_from_spec get_model_spec load_model "
+             "register_model WeightTiedExitProjection attach_early_exits generate_adaptive UniversalAdaptiveEmbedding JEVLatentPredictor JEVObjective JEVExitRouter "
+             "JEVRoutingResult TriuneLatentPredictor TriuneLatentObjective TriuneContinuousExitRouter ContinuousLatentExitRouter JointEmbeddingObjective LatentPredictor",
+    "runtime": "MemoryEstimate MemoryPlan MemoryPlanner DynamicResourceManager LiveVRAMMonitor AllotmentPlan HardwareProfile VRAMBudgetExceededError LayerStreamingEngine "
+               "StreamingConfig enable_layer_streaming apply_layer_streaming_if_requested PrecisionCapabilities ParameterStager StagingBuffer FP8StagingBuffer PythonSandbox "
+               "SandboxResult VRAMProfiler AutoOffloader CUDAGraphEngine NeuronScope ParallelEngine GLAPipelineBlock MoERoutingBlock",
+    "ops": "NativeTriuneEngine is_native_c_available get_native_c_info c_centroid_steer_update_f32 c_route_tiers_f32 c_compute_neuron_heatmap_f32 c_gla_recurrent_step_f32 "
+           "batched_qr cholesky_qr subspace_projection batched_subspace_projection triangular_steer_update gla muon_orthogonalize muon_ns norm rmsnorm rope swiglu gelu "
+           "cross_entropy chunked_cross_entropy FastChunkedCrossEntropyLoss lora_forward lora_linear upgrade route_tiers TIER_REFLEX TIER_LIMBIC TIER_CORTEX TIER_NAMES",
+    "agents": "Agent AgentHarness AgentMemoryStore AgentSkill BUILTIN_PERSONAS CognitiveState LearnedLesson MultiAgentOrchestrator PersonaProfile ProviderConfig "
+              "ProviderManager SkillLibrary StateController Tool ToolRegistry ToolStats UserPreference build_integrated_toolbelt",
+    "recipes": "bf16_autocast build_fp8_precision_context build_precision_context build_mxfp8_precision_context",
+    "trainer": "Engine TrainingEngine DistributedTrainingEngine DistributedContext setup_distributed cleanup_distributed is_distributed get_rank get_world_size "
+               "get_local_rank is_main_process all_reduce_tensor all_reduce_dict wrap_distributed_model Trainer NullLogger WandbLogger LoRAConfig LoRALayer TriuneFineTuner "
+               "list_adapters export_adapter merge_adapter_checkpoint",
+    "kernels": "is_triton_available get_kernel_backend get_triton_error is_turbo_mode_enabled set_turbo_mode get_kernel_telemetry fast_rmsnorm fast_fused_add_rmsnorm "
+               "FastRMSNorm fast_rope fast_swiglu fast_gelu FastSwiGLU FastGELU fast_cross_entropy chunked_cross_entropy_from_hidden FastChunkedCrossEntropyLoss fast_chunk_gla "
+               "fast_chunk_gated_deltanet fast_recurrent_gated_deltanet fast_zeropower_via_newtonschulz5 fast_lora_forward fast_lora_linear fast_qkv_lora_linear "
+               "fast_gate_up_lora_linear is_fp8_available fast_fp8_linear FastFP8Linear nvfp4_quantize nvfp4_dequantize nvfp4_linear fwht_16 NVFP4Linear",
+    "export": "export_gguf export_onnx export_safetensors export_model export_to_huggingface",
+    "api": "create_app run_server",
+    "callbacks": "Callback CallbackList TelemetryCallback EventEmitter global_emitter",
+    "configs": "build_config default_config validate_config",
+    "data": "AsyncDevicePrefetcher CyclingDataLoader DynamicTokenizer DynamicTokenizerOutput TokenStreamDataset TriuneTokenizer build_dataloader build_tokenizer load_tokenizer",
+    "plugins": "NodeRegistry NODE_REGISTRY global_registry node_registry get_node_executor list_registered_nodes register_node",
+    "execution": "DAGParser ExecutionEngine NodeExecutionError",
+    "modules": "ModuleManager",
+}
+
+
+@pytest.fixture()
+def triune():
+    compat.uninstall()
+    root = compat.install()
+    yield root
+    compat.uninstall()
+
+
+def test_every_exported_name_of_the_reference_resolves(triune):
+    cov = compat.coverage()
+    for pkg, names in REFERENCE_EXPORTS.items():
+        assert cov[pkg]["unresolved"] == {}, (pkg, cov[pkg]["unresolved"])
+        mod = importlib.import_module(f"triune.{pkg}")
+        for n in names.split():
+            assert getattr(mod, n) is not None or n in ("NODE_REGISTRY",), (pkg, n)
+    assert compat.install() is triune  # idempotent
+    with pytest.raises(AttributeError):
+        importlib.import_module("triune.model").no_such_name
+
+
+def test_a_script_written_against_the_reference_runs(triune, tmp_path):
+    """Imports by the reference's paths (package level and deep modules), builds the model, trains a step, exports."""
+    from triune.configs import build_config, default_config
+    from triune.export import export_model
+    from triune.kernels import fast_cross_entropy
+    from triune.model import TriuneModel, TriuneTransformer, apply_rotary, rotate_half
+    from triune.model.transformer import TriuneTransformer as Deep
+    from triune.optim import HAS_8BIT, AdamW8bit, CentroidSteerOptimizer
+    from triune.trainer import get_rank, get_world_size, is_distributed, is_main_process
+
+    import triune_b200.models.transformer as ours
+
+    assert Deep is TriuneTransformer is ours.TriuneTransformer and issubclass(TriuneModel, torch.nn.Module)
+    assert default_config() == build_config({}) and HAS_8BIT is True
+    assert (get_rank(), get_world_size(), is_distributed(), is_main_process()) == (0, 1, False, True)
+    x = torch.arange(8.0).view(1, 8)
+    assert rotate_half(x).tolist() == [[-4.0, -5.0, -6.0, -7.0, 0.0, 1.0, 2.0, 3.0]]
+    assert torch.allclose(apply_rotary(x, torch.ones(8), torch.zeros(8)), x)
+    torch.manual_seed(0)
+    model = TriuneTransformer(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=1, head_dim=32, num_experts=2, router_prefix_layers=1,
+                              reflex_exit_layer=2, limbic_exit_layer=3)
+    ids = torch.randint(0, 64, (2, 17))
+    opt = CentroidSteerOptimizer(model, lr=1e-3)
+    logits = model(ids[:, :-1], force_depth=2)[0]
+    loss = fast_cross_entropy(logits.reshape(-1, 64), ids[:, 1:].reshape(-1))
+    loss.backward()
+    opt.step()
+    assert torch.isfinite(loss)
+    out = export_model(model, str(tmp_path / "m.safetensors"), "safetensors")
+    assert (tmp_path / "m.safetensors").is_file() and str(out).endswith("m.safetensors")
+    # 8-bit AdamW: follows fp32 AdamW closely on a quadratic and keeps two bytes per parameter
+    w8, w32 = torch.nn.Parameter(torch.full((600,), 2.0)), torch.nn.Parameter(torch.full((600,), 2.0))
+    o8, o32 = AdamW8bit([w8], lr=0.05, weight_decay=0.0), torch.optim.AdamW([w32], lr=0.05, weight_decay=0.0)
+    for _ in range(30):
+        for w, o in ((w8, o8), (w32, o32)):
+            o.zero_grad()
+            (w * w).sum().backward()
+            o.step()
+    assert float((w8 - w32).abs().max()) < 0.05 and float(w8.abs().max()) < 1.2
+    assert o8.state_bytes() == 2 * 768 + 8 * 3  # 600 elements in 3 blocks of 256
+
+
+def test_graph_engine_registry_and_modules_under_reference_names(triune, tmp_path):
+    from triune.execution import DAGParser, ExecutionEngine, NodeExecutionError
+    from triune.execution.dag import ExecutionEngine as Deep
+    from triune.modules import ModuleManager
+    from triune.plugins import get_node_executor, global_registry, list_registered_nodes
+    from triune.agents import BUILTIN_PERSONAS, StateController
+
+    assert Deep is ExecutionEngine and "TriuneTransformer" in list_registered_nodes() and callable(get_node_executor("RMSNorm"))
+    assert "architect" in BUILTIN_PERSONAS and StateController().assess("why does it crash with a traceback")["persona"] == "debugger"
+    assert StateController(depth="auto").assess("hi")["depth"] == "reflex"
+    g = {"nodes": [{"id": "a", "type": "PythonSandbox", "params": {"code": "result = 'abc'"}}, {"id": "b", "type": "BPETokenizer"}],
+         "edges": [{"source": "a", "target": "b", "source_port": "result", "target_port": "text"}]}
+    assert DAGParser.parse(g)["execution_order"] == ["a", "b"] and DAGParser.from_json(g)["b"]["dependencies"] == ["a"]
+    with pytest.raises(NodeExecutionError):
+        DAGParser.parse({"nodes": [{"id": "a", "type": "X"}], "edges": [{"source": "a", "target": "zz"}]})
+    eng = ExecutionEngine()
+    events = []
+    eng.register_event_callback(events.append)
+    res = eng.execute_graph(g)
+    assert res["status"] == "success" and [e["event"] for e in events] == ["node_started", "node_finished"] * 2
+    assert eng.run(g)["b"]["status"] == "completed"
+    # a handler in the reference's convention: (node, context) -> dict, ports through context["port_data"]
+    def doubler(node, context):
+        context["port_data"].setdefault(node["id"], {})["doubled"] = 2 * context["current_inputs"]["value"]
+        return {"status": "completed", "note": "ok"}
+
+    eng.register_handler("Doubler", doubler)
+    out = eng.execute_node({"id": "d", "type": "Doubler"}, {"value": 21})
+    assert out["status"] == "success" and out["output"]["ports"]["doubled"] == 42
+    assert "Doubler" in global_registry
+    from triune_b200.plugins.registry import create_plugin
+
+    src = create_plugin(tmp_path / "src", "my_nodes")
+    mm = ModuleManager(str(tmp_path / "mods"))
+    assert mm.install_module({"path": str(src)})["status"] == "installed"
+    assert [m["name"] for m in mm.get_installed_modules()] == ["my_nodes"]
+    assert mm.install_module({"url": "https://github.com/a/b"})["status"] == "error"
+    assert mm.uninstall_module("my_nodes")["status"] == "uninstalled" and mm.uninstall_module("my_nodes")["status"] == "error"
+
+
+def test_a_real_package_of_that_name_is_not_shadowed():
+    compat.uninstall()
+    import types
+
+    sys.modules["triune"] = types.ModuleType("triune")
+    try:
+        with pytest.raises(RuntimeError):
+            compat.install()
+    finally:
+        del sys.modules["triune"]

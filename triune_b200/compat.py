@@ -1,0 +1,543 @@
+"""Import paths of the reference project, served by this framework.
+
+``triune_b200.compat.install()`` registers a package named ``triune`` whose sub-packages (``triune.model``,
+``triune.optim``, ``triune.kernels``, ``triune.runtime``, ``triune.trainer``, ``triune.data``, ``triune.export``,
+``triune.api``, ``triune.agents``, ``triune.plugins``, ``triune.execution`` ...) export, under the names of the
+reference's ``__init__`` files, the objects of this framework that do the same job. Scripts written against the
+reference then run with one extra line at the top::
+
+    import triune_b200.compat; triune_b200.compat.install()
+    from triune.model import TriuneTransformer
+    from triune.kernels import fast_chunk_gla, chunked_cross_entropy_from_hidden
+    from triune.optim import CentroidSteerOptimizer
+
+Nothing is copied: every name resolves, when first touched, to an object defined elsewhere in this package; the few
+names that have no object of their own here (aliases such as ``Engine``, ``MemoryPlan``, ``muon_orthogonalize``, small
+helpers such as ``rotate_half`` and ``is_main_process``, and the registry / engine classes that front
+``execution/studio.py``) are defined below. ``coverage()`` lists, per reference package, which names resolve. If the real
+``triune`` package is already imported, ``install`` refuses rather than shadow it.
+"""
+
+from __future__ import annotations
+
+import importlib
+import os
+import sys
+import types
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+# reference package -> [(module of this framework, names exported under the same name)], plus renames {ref name: "module:attr"}
+_SAME: Dict[str, List[Tuple[str, Tuple[str, ...]]]] = {
+    "optim": [("optim.centroid", ("CentroidSteerOptimizer",)), ("optim.manifold", ("LowSpaceWeightProjector", "QuantumUnitaryOptimizer", "UnitaryManifoldOptimizer")),
+              ("optim.muon", ("Muon", "zeropower_via_newtonschulz5")), ("optim.factory", ("build_optimizer",))],
+    "model": [("models.zoo", ("CANONICAL_MODEL_SPECS", "MODEL_REGISTRY", "ModelSpec", "build_model_from_spec", "get_model_spec", "load_model", "register_model")),
+              ("models.transformer", ("TriuneTransformer",)), ("models.speculative", ("SelfSpeculativeGenerator",)), ("models.block", ("TransformerBlock",)),
+              ("models.attention", ("HybridAttention", "VectorisedGLA")), ("models.moe", ("MoE_FFN", "RoutingResult")), ("models.norms", ("RMSNorm",)),
+              ("models.rotary", ("RotaryEmbedding",)), ("models.router", ("GumbelSoftmaxRouter",)), ("models.quant_linear", ("FP4Linear", "FP8Linear")),
+              ("models.factory", ("build_model",)), ("models.adapters", ("WeightTiedExitProjection", "attach_early_exits", "generate_adaptive")),
+              ("models.manifold_embedding", ("UniversalAdaptiveEmbedding",)),
+              ("models.jev", ("JEVLatentPredictor", "JEVObjective", "JEVExitRouter", "JEVRoutingResult", "TriuneLatentPredictor", "TriuneLatentObjective",
+                              "TriuneContinuousExitRouter", "ContinuousLatentExitRouter", "JointEmbeddingObjective", "LatentPredictor"))],
+    "runtime": [("runtime.memory_planner", ("MemoryEstimate", "MemoryPlanner")),
+                ("runtime.resource_manager", ("DynamicResourceManager", "LiveVRAMMonitor", "AllotmentPlan", "HardwareProfile", "VRAMBudgetExceededError")),
+                ("runtime.streaming", ("LayerStreamingEngine", "StreamingConfig", "enable_layer_streaming")), ("runtime.capabilities", ("PrecisionCapabilities",)),
+                ("runtime.staging", ("ParameterStager", "StagingBuffer", "FP8StagingBuffer")), ("runtime.sandbox", ("PythonSandbox", "SandboxResult")),
+                ("runtime.vram", ("VRAMProfiler", "AutoOffloader")), ("runtime.cuda_graph", ("CUDAGraphEngine",)), ("runtime.neuron_scope", ("NeuronScope",)),
+                ("runtime.parallel_engine", ("ParallelEngine", "GLAPipelineBlock", "MoERoutingBlock"))],
+    "ops": [("ops._c_bridge", ("NativeTriuneEngine", "get_native_c_info")),
+            ("optim.subspace", ("batched_qr", "cholesky_qr", "subspace_projection", "batched_subspace_projection")),
+            ("ops", ("triangular_steer_update", "gla", "muon_ns", "rmsnorm", "swiglu", "cross_entropy", "lora_linear", "route_tiers")),
+            ("runtime.neuron_scope", ("TIER_NAMES",)), ("kernels", ("FastChunkedCrossEntropyLoss",))],
+    "agents": [("agents", ("Agent", "MultiAgentOrchestrator", "Tool", "ToolRegistry", "build_integrated_toolbelt")), ("agents.harness", ("AgentHarness",)),
+               ("agents.extras", ("AgentMemoryStore", "ProviderManager", "SkillLibrary"))],
+    "recipes": [("recipes", ("bf16_autocast", "build_fp8_precision_context", "build_precision_context", "build_mxfp8_precision_context"))],
+    "trainer": [("trainer.engine", ("TrainingEngine",)), ("parallel.dist", ("DistributedContext", "setup_distributed", "cleanup_distributed", "all_reduce_tensor", "all_reduce_dict")),
+                ("trainer.trainer", ("Trainer",)), ("trainer.logger", ("NullLogger", "WandbLogger")),
+                ("trainer.finetune", ("LoRAConfig", "LoRALayer", "TriuneFineTuner", "list_adapters", "export_adapter", "merge_adapter_checkpoint"))],
+    "kernels": [("kernels", ())],  # every public name of kernels.py, see _names_of
+    "export": [("export.exporter", ("export_gguf", "export_onnx", "export_safetensors", "export_model")), ("export.hf_compat", ("export_to_huggingface",))],
+    "api": [("serve", ("create_app", "run_server"))],
+    "callbacks": [("callbacks.base", ("Callback", "CallbackList")), ("callbacks.telemetry", ("TelemetryCallback",)), ("callbacks.events", ("EventEmitter", "global_emitter"))],
+    "configs": [("config", ("build_config", "validate_config"))],
+    "data": [("data.dataloader", ("AsyncDevicePrefetcher", "CyclingDataLoader")), ("data.dynamic_tokenizer", ("DynamicTokenizer", "DynamicTokenizerOutput")),
+             ("data.dataset", ("TokenStreamDataset", "build_dataloader")), ("data.tokenizer", ("TriuneTokenizer", "build_tokenizer", "load_tokenizer"))],
+    "plugins": [("execution.dag", ("register_node",))],
+    "execution": [],
+    "modules": [],
+    "utils": [],
+}
+_RENAMED: Dict[str, Dict[str, str]] = {
+    "optim": {"AdamW8bit": "compat:AdamW8bit", "HAS_8BIT": "compat:HAS_8BIT"},
+    "model": {"TriuneModel": "compat:TriuneModel", "apply_rotary": "compat:apply_rotary", "rotate_half": "compat:rotate_half"},
+    "runtime": {"MemoryPlan": "runtime.memory_planner:MemoryEstimate", "apply_layer_streaming_if_requested": "compat:apply_layer_streaming_if_requested"},
+    "ops": {"is_native_c_available": "ops._c_bridge:is_available", "c_centroid_steer_update_f32": "ops._c_bridge:c_centroid_steer_update",
+            "c_route_tiers_f32": "ops._c_bridge:c_route_tiers", "c_compute_neuron_heatmap_f32": "ops._c_bridge:c_neuron_heatmap",
+            "c_gla_recurrent_step_f32": "ops._c_bridge:c_gla_recurrent_step", "muon_orthogonalize": "ops:muon_ns", "norm": "ops:rmsnorm", "rope": "ops:apply_rope",
+            "gelu": "ops:gelu_tanh", "chunked_cross_entropy": "kernels:chunked_cross_entropy_from_hidden", "lora_forward": "kernels:fast_lora_forward",
+            "upgrade": "models.universal:upgrade_model", "TIER_REFLEX": "compat:TIER_REFLEX", "TIER_LIMBIC": "compat:TIER_LIMBIC", "TIER_CORTEX": "compat:TIER_CORTEX"},
+    "agents": {"AgentSkill": "agents.extras:Skill", "BUILTIN_PERSONAS": "agents.harness:PERSONAS", "PersonaProfile": "agents.harness:PersonaSpec",
+               "ProviderConfig": "agents.extras:Provider", "StateController": "compat:StateController", "CognitiveState": "compat:CognitiveState",
+               "LearnedLesson": "compat:LearnedLesson", "ToolStats": "compat:ToolStats", "UserPreference": "compat:UserPreference"},
+    "trainer": {"Engine": "trainer.engine:TrainingEngine", "DistributedTrainingEngine": "compat:DistributedTrainingEngine", "is_distributed": "compat:is_distributed",
+                "get_rank": "compat:get_rank", "get_world_size": "compat:get_world_size", "get_local_rank": "compat:get_local_rank",
+                "is_main_process": "compat:is_main_process", "wrap_distributed_model": "compat:wrap_distributed_model"},
+    "configs": {"default_config": "compat:default_config"},
+    "plugins": {"NodeRegistry": "compat:NodeRegistry", "NODE_REGISTRY": "compat:global_registry", "global_registry": "compat:global_registry",
+                "node_registry": "compat:global_registry", "get_node_executor": "compat:get_node_executor", "list_registered_nodes": "compat:list_registered_nodes"},
+    "execution": {"DAGParser": "compat:DAGParser", "ExecutionEngine": "compat:ExecutionEngine", "NodeExecutionError": "execution.studio:StudioGraphError"},
+    "modules": {"ModuleManager": "compat:ModuleManager"},
+}
+# deeper import paths that scripts use directly: reference module -> module of this framework
+_MODULE_ALIASES = {
+    "model.transformer": "models.transformer", "model.moe": "models.moe", "model.attention": "models.attention", "model.router": "models.router",
+    "model.config": "config", "optim.centroid": "optim.centroid", "optim.muon": "optim.muon", "trainer.finetune": "trainer.finetune",
+    "trainer.checkpoint": "trainer.checkpoint", "trainer.engine": "trainer.engine", "runtime.streaming": "runtime.streaming", "runtime.sandbox": "runtime.sandbox",
+    "runtime.gguf_loader": "runtime.gguf_loader", "runtime.model_scanner": "runtime.model_scanner", "data.tokenizer": "data.tokenizer",
+    "data.dynamic_tokenizer": "data.dynamic_tokenizer", "data.dataset": "data.dataset", "data.dataloader": "data.dataloader", "export.exporter": "export.exporter",
+    "export.hf_compat": "export.hf_compat", "inference": "inference", "profiling": "profiling", "desktop": "desktop", "packaging": "packaging", "cli": "cli",
+    "api.server": "serve.server", "api.routes": "serve.routes", "api.srsm": "serve.srsm", "execution.dag": "compat", "kernels.fast_gla": "kernels",
+    "kernels.fast_cross_entropy": "kernels", "kernels.fast_rmsnorm": "kernels", "kernels.fast_rope": "kernels", "kernels.fast_swiglu": "kernels",
+    "kernels.fast_muon": "kernels", "kernels.fast_lora": "kernels", "kernels.fast_nvfp4": "kernels", "kernels.fast_fp8": "kernels",
+}
+
+_PKG = __name__.rsplit(".", 1)[0]
+
+
+def _resolve(target: str) -> Any:
+    mod, _, attr = target.partition(":")
+    m = sys.modules[__name__] if mod == "compat" else importlib.import_module(f"{_PKG}.{mod}" if mod else _PKG)
+    return getattr(m, attr) if attr else m
+
+
+def _names_of(pkg: str) -> Dict[str, str]:
+    out: Dict[str, str] = {}
+    for mod, names in _SAME.get(pkg, []):
+        if not names:  # the whole public surface of that module
+            names = tuple(getattr(importlib.import_module(f"{_PKG}.{mod}"), "__all__", ()))
+        for n in names:
+            out[n] = f"{mod}:{n}"
+    out.update(_RENAMED.get(pkg, {}))
+    return out
+
+
+class _Lazy(types.ModuleType):
+    """A module whose attributes are looked up in this framework when first touched."""
+
+    def __init__(self, name: str, table: Dict[str, str], doc: str):
+        super().__init__(name, doc)
+        self.__dict__["_table"] = table
+        self.__all__ = sorted(table)
+        self.__path__ = []  # a package: sub-modules may be imported from it
+
+    def __getattr__(self, name: str) -> Any:
+        table = self.__dict__["_table"]
+        if name not in table:
+            raise AttributeError(f"module {self.__name__!r} has no attribute {name!r}")
+        try:
+            val = _resolve(table[name])
+        except Exception as e:
+            raise AttributeError(f"{self.__name__}.{name} could not be resolved ({type(e).__name__}: {e})") from e
+        setattr(self, name, val)
+        return val
+
+    def __dir__(self):
+        return sorted(set(self.__dict__["_table"]) | set(super().__dir__()))
+
+
+def install(name: str = "triune", force: bool = False) -> types.ModuleType:
+    """Register the alias package in ``sys.modules`` and return it. Idempotent; refuses to shadow a real package of that
+    name that is already imported unless ``force``."""
+    cur = sys.modules.get(name)
+    if cur is not None and not isinstance(cur, _Lazy) and not force:
+        raise RuntimeError(f"a real package named {name!r} is already imported; not shadowing it")
+    if isinstance(cur, _Lazy):
+        return cur
+    root = _Lazy(name, {"__version__": "compat:__version__"}, f"{name}: import paths of the reference, served by {_PKG}")
+    sys.modules[name] = root
+    for pkg in _SAME:
+        sub = _Lazy(f"{name}.{pkg}", _names_of(pkg), f"{name}.{pkg} on {_PKG}")
+        sys.modules[f"{name}.{pkg}"] = sub
+        setattr(root, pkg, sub)
+    for ref_mod, ours in _MODULE_ALIASES.items():
+        full = f"{name}.{ref_mod}"
+        if full in sys.modules:
+            continue
+        target = sys.modules[__name__] if ours == "compat" else importlib.import_module(f"{_PKG}.{ours}")
+        sys.modules[full] = target
+        parent, _, leaf = full.rpartition(".")
+        if parent in sys.modules and isinstance(sys.modules[parent], _Lazy):
+            if leaf not in sys.modules[parent].__dict__["_table"]:  # a function of the same name wins over its module, as in the reference
+                sys.modules[parent].__dict__.setdefault(leaf, target)
+        elif parent == name:
+            setattr(root, leaf, target)
+    return root
+
+
+def uninstall(name: str = "triune") -> None:
+    """Remove the alias package again (a real package of that name is left alone)."""
+    if not isinstance(sys.modules.get(name), _Lazy):
+        return
+    for k in [k for k in sys.modules if k == name or k.startswith(name + ".")]:
+        del sys.modules[k]
+
+
+def coverage() -> Dict[str, Dict[str, Any]]:
+    """Per reference package: the names it exports that resolve here, and the ones that do not."""
+    rep: Dict[str, Dict[str, Any]] = {}
+    for pkg in _SAME:
+        ok, bad = [], {}
+        for n, target in _names_of(pkg).items():
+            try:
+                _resolve(target)
+                ok.append(n)
+            except Exception as e:
+                bad[n] = f"{type(e).__name__}: {e}"
+        rep[pkg] = {"resolved": sorted(ok), "unresolved": bad}
+    return rep
+
+
+__version__ = "1.0.0"
+TIER_REFLEX, TIER_LIMBIC, TIER_CORTEX = 0, 1, 2
+
+
+# ---------------------------------------------------------------------------------------------------- model helpers
+class TriuneModel(nn.Module):
+    """Base of model classes registered in the zoo: ``forward(input_ids, force_depth) -> (logits, aux)`` and a parameter
+    count (``triune/model/base.py:474-487``)."""
+
+    def forward(self, input_ids: torch.Tensor, force_depth: Optional[int] = None):  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def get_num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+
+def rotate_half(x: torch.Tensor) -> torch.Tensor:
+    """(x1, x2) -> (-x2, x1) over the two halves of the last dimension."""
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x * cos + rotate_half(x) * sin with tables that broadcast against x (half-split convention)."""
+    return x * cos + rotate_half(x) * sin
+
+
+def apply_layer_streaming_if_requested(model: nn.Module, device, config: Dict[str, Any], optimizer: Optional[Any] = None):
+    """Attach a layer-streaming engine when ``config["streaming"]`` is set (the reference's flat ``streaming_*`` keys)."""
+    if not config.get("streaming", False):
+        return None
+    from .runtime.streaming import StreamingConfig, enable_layer_streaming
+
+    cfg = StreamingConfig(enabled=True, chunk_size=int(config.get("streaming_chunk_size", 1)), pin_memory=config.get("streaming_pin_memory"),
+                          async_prefetch=bool(config.get("streaming_prefetch", True)), fp8_weights=bool(config.get("streaming_fp8_weights", False)),
+                          resident_gpu_layers=int(config.get("streaming_resident_gpu_layers", 0)), grad_clip=float(config.get("grad_clip", 1.0)),
+                          instant_optimizer=True, forward_snapshots=bool(config.get("streaming_capture_forward_snapshots", True)),
+                          activation_checkpointing=bool(config.get("streaming_activation_checkpointing", True)))
+    return enable_layer_streaming(model, device, cfg)
+
+
+def default_config() -> Dict[str, Any]:
+    from .config import build_config
+
+    return build_config({})
+
+
+# ---------------------------------------------------------------------------------------------------- optimizer
+HAS_8BIT = True  # 8-bit moments are part of this framework (``optim/adam8bit.py``); no external package is involved
+
+
+def AdamW8bit(params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01):
+    from .optim.adam8bit import AdamW8bit as _Impl
+
+    return _Impl(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+
+
+# ---------------------------------------------------------------------------------------------------- distributed helpers
+def is_distributed() -> bool:
+    import torch.distributed as dist
+
+    return dist.is_available() and dist.is_initialized()
+
+
+def get_rank() -> int:
+    import torch.distributed as dist
+
+    return dist.get_rank() if is_distributed() else int(os.environ.get("RANK", 0))
+
+
+def get_world_size() -> int:
+    import torch.distributed as dist
+
+    return dist.get_world_size() if is_distributed() else int(os.environ.get("WORLD_SIZE", 1))
+
+
+def get_local_rank() -> int:
+    return int(os.environ.get("LOCAL_RANK", 0))
+
+
+def is_main_process() -> bool:
+    return get_rank() == 0
+
+
+def wrap_distributed_model(model: nn.Module, device_ids: Optional[List[int]] = None, find_unused_parameters: bool = True):
+    """DistributedDataParallel around the model (the library baseline; this framework's own data parallelism is
+    ``parallel.data_parallel.ShardedDataParallel``, which the trainer uses when given a ``dp`` object)."""
+    if not is_distributed():
+        raise RuntimeError("Cannot wrap model in DDP when distributed mode is not initialized.")
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    return DDP(model, device_ids=device_ids, find_unused_parameters=find_unused_parameters, broadcast_buffers=False)
+
+
+def _training_engine_base():
+    from .trainer.engine import TrainingEngine
+
+    return TrainingEngine
+
+
+class DistributedTrainingEngine:
+    """``TrainingEngine`` whose step results also carry the loss and token count reduced over all ranks
+    (``global_loss``, ``global_lm_loss``, ``global_tokens``)."""
+
+    def __new__(cls, trainer):
+        base = _training_engine_base()
+
+        class _Engine(base):  # built on first use so that importing this module does not import the trainer
+            def step_once(self, *a, **k):
+                res = super().step_once(*a, **k)
+                if is_distributed() and isinstance(res, dict):
+                    from .parallel.dist import all_reduce_dict
+
+                    red = all_reduce_dict({"loss": float(res.get("loss", 0.0)), "lm_loss": float(res.get("lm", res.get("loss", 0.0))),
+                                           "tokens": float(res.get("tokens", 0))})
+                    res["global_loss"], res["global_lm_loss"], res["global_tokens"] = red["loss"], red["lm_loss"], int(red["tokens"])
+                return res
+
+        eng = _Engine(trainer)
+        eng.is_distributed = is_distributed()
+        return eng
+
+
+# ---------------------------------------------------------------------------------------------------- agents records
+class UserPreference(dict):
+    """One stored preference: ``{"key", "value", "updated"}``."""
+
+
+class LearnedLesson(dict):
+    """One stored lesson: ``{"text", "tags", "time"}``."""
+
+
+class ToolStats(dict):
+    """Per-tool counters: ``{"calls", "failures"}``."""
+
+
+class CognitiveState(dict):
+    """What the state controller reports: persona, depth tier, temperature."""
+
+
+class StateController:
+    """Chooses persona and depth for a goal (``triune/agents/personas.py``): persona by the goal's words, depth by its
+    length (short questions leave at the Reflex exit, long tasks use the full depth)."""
+
+    def __init__(self, persona: str = "auto", depth: str = "auto"):
+        self.persona, self.depth = persona, depth
+
+    def assess(self, goal: str) -> CognitiveState:
+        from .agents.harness import resolve_persona
+
+        p = resolve_persona(self.persona, goal)
+        words = len(goal.split())
+        depth = self.depth if self.depth != "auto" else ("reflex" if words < 8 else "limbic" if words < 40 else "cortex")
+        return CognitiveState(persona=p.name, system_prompt=p.system_prompt, temperature=p.temperature, depth=depth,
+                              force_depth={"reflex": 0, "limbic": 1, "cortex": 2}[depth])
+
+
+# ---------------------------------------------------------------------------------------------------- node registry, DAG engine
+class NodeRegistry:
+    """The node catalogue behind the canvas (``triune/plugins/registry.py:46-176``): built-in kinds come from
+    ``execution/studio.py``; ``register`` adds a kind with a handler ``(inputs, params, context) -> outputs``."""
+
+    def register_builtin_nodes(self) -> None:
+        from .execution import studio  # noqa: F401 - importing registers the built-in kinds
+
+    def register(self, name: str, handler: Callable, inputs: Optional[Dict[str, str]] = None, outputs: Optional[Dict[str, str]] = None,
+                 category: str = "Custom", parameters: Optional[Dict[str, Any]] = None, description: str = "") -> None:
+        from .execution.studio import studio_node
+
+        studio_node(name, category, inputs or {}, outputs or {}, parameters or {}, description)(handler)
+
+    def get(self, name: str):
+        from .execution.studio import STUDIO_NODES
+
+        return STUDIO_NODES.get(name)
+
+    def get_catalog(self) -> List[Dict[str, Any]]:
+        from .execution.studio import studio_catalog
+
+        return studio_catalog()
+
+    def __contains__(self, name: str) -> bool:
+        return self.get(name) is not None
+
+
+global_registry = NodeRegistry()
+
+
+def list_registered_nodes() -> List[str]:
+    return sorted(n["name"] for n in global_registry.get_catalog())
+
+
+def get_node_executor(name: str) -> Optional[Callable]:
+    spec = global_registry.get(name)
+    return None if spec is None else spec.fn
+
+
+class DAGParser:
+    """Validation and ordering of canvas graphs (``triune/execution/dag.py:39-216``)."""
+
+    @classmethod
+    def parse(cls, graph_json: Dict[str, Any]) -> Dict[str, Any]:
+        from .execution.studio import parse_studio_graph
+
+        g = parse_studio_graph(graph_json)
+        adj: Dict[str, List[str]] = {}
+        for e in g.edges:
+            adj.setdefault(e["source"], []).append(e["target"])
+        return {"execution_order": g.order, "node_map": g.nodes, "adj": adj}
+
+    @classmethod
+    def from_json(cls, graph_json: Dict[str, Any]) -> Dict[str, Any]:
+        from .execution.studio import parse_studio_graph
+
+        g = parse_studio_graph(graph_json)
+        deps: Dict[str, List[str]] = {n: [] for n in g.nodes}
+        for e in g.edges:
+            deps[e["target"]].append(e["source"])
+        return {n: {"id": n, "type": node.get("type"), "details": node.get("details"), "dependencies": deps[n]} for n, node in g.nodes.items()}
+
+
+class ExecutionEngine:
+    """Runs canvas graphs (``triune/execution/dag.py:271-3160``): ``execute_graph`` / ``run`` for whole graphs,
+    ``execute_node`` / ``execute_single_node`` for one node, event callbacks per node, extra handlers by name."""
+
+    def __init__(self):
+        self.event_callbacks: List[Callable[[Dict[str, Any]], None]] = []
+
+    def register_event_callback(self, cb) -> None:
+        if cb not in self.event_callbacks:
+            self.event_callbacks.append(cb)
+
+    def unregister_event_callback(self, cb) -> None:
+        if cb in self.event_callbacks:
+            self.event_callbacks.remove(cb)
+
+    def _emit(self, ev: Dict[str, Any]) -> None:
+        for cb in list(self.event_callbacks):
+            try:
+                cb(ev)
+            except Exception:
+                pass
+
+    def register_handler(self, node_type: str, handler: Callable) -> None:
+        """``handler(node, context) -> dict`` in the reference's convention: ``context["current_inputs"]`` holds the port
+        values; the returned dictionary's entries become the node's output ports."""
+        def adapted(inputs, params, ctx):
+            context = {"current_inputs": dict(inputs), "port_data": {}, **{k: v for k, v in ctx.items() if not k.startswith("_")}}
+            out = handler(dict(ctx.get("_node") or {}, params=params), context) or {}
+            if out.get("status") in ("failed", "error"):
+                from .execution.studio import NodeFailure
+
+                raise NodeFailure(str(out.get("error", "node reported failure")))
+            ports = dict(context["port_data"].get((ctx.get("_node") or {}).get("id"), {}))
+            return {**ports, "_info": {k: v for k, v in out.items() if k not in ports}}
+
+        global_registry.register(node_type, adapted, category="Custom")
+        from .execution.studio import STUDIO_NODES
+
+        STUDIO_NODES[node_type].dynamic_ports = True
+
+    def execute_graph(self, graph_json: Dict[str, Any], *, initial_context: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        from .execution.studio import StudioGraphRunner
+
+        return StudioGraphRunner(self._emit).run(graph_json, dict(initial_context or {}))
+
+    def run(self, graph_json: Dict[str, Any]) -> Dict[str, Any]:
+        return self.execute_graph(graph_json)["results"]
+
+    def execute_node(self, node_or_name, inputs: Optional[Dict[str, Any]] = None, context: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        from .execution.studio import run_studio_node
+
+        node = {"type": node_or_name, "title": node_or_name} if isinstance(node_or_name, str) else dict(node_or_name)
+        return run_studio_node(node, inputs, context)
+
+    def execute_single_node(self, node: Dict[str, Any], context: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        return self.execute_node(node, None, context)
+
+
+from .execution.studio import StudioGraphError as NodeExecutionError  # noqa: E402  (the error type graph validation raises)
+
+
+# ---------------------------------------------------------------------------------------------------- modules
+class ModuleManager:
+    """Life cycle of local modules (plugin directories with signed manifests) inside one directory: install from a local
+    directory, list, activate (verify and load), uninstall, scaffold. Remote catalogues are not contacted
+    (``triune/modules/manager.py:345-1757`` of the reference also clones from the network)."""
+
+    def __init__(self, directory: str = "plugins", key: Optional[str] = None):
+        from .plugins.registry import PluginRegistry
+
+        self.directory = directory
+        self.registry = PluginRegistry(key)
+        os.makedirs(directory, exist_ok=True)
+        self.registry.discover(directory)
+
+    def get_installed_modules(self) -> List[Dict[str, Any]]:
+        self.registry.discover(self.directory)
+        return self.registry.list()
+
+    def scan_workspace_plugins(self, path: Optional[str] = None) -> Dict[str, Any]:
+        found = self.registry.discover(path or self.directory)
+        return {"found": [p.name for p in found], "plugins": self.registry.list()}
+
+    def install_module(self, req: Dict[str, Any]) -> Dict[str, Any]:
+        import shutil
+        from pathlib import Path
+
+        src = Path(str(req.get("path") or req.get("url") or req.get("source") or "")).expanduser()
+        if "://" in str(src) or not src.is_dir():
+            return {"status": "error", "message": "only local module directories can be installed (no network access)"}
+        name = str(req.get("name") or src.name)
+        dst = (Path(self.directory) / name).resolve()
+        if Path(self.directory).resolve() not in dst.parents:
+            return {"status": "error", "message": "the module name escapes the module directory"}
+        if dst.exists():
+            return {"status": "error", "message": f"module {name!r} is already installed"}
+        shutil.copytree(src, dst)
+        self.registry.discover(self.directory)
+        return {"status": "installed", "id": name, "path": str(dst)}
+
+    def activate_module(self, name: str) -> Dict[str, Any]:
+        info = self.registry.load(name)
+        return {"status": "active", "id": info.name, "nodes": info.nodes}
+
+    def uninstall_module(self, module_id: str) -> Dict[str, Any]:
+        import shutil
+        from pathlib import Path
+
+        dst = (Path(self.directory) / module_id).resolve()
+        if Path(self.directory).resolve() not in dst.parents or not dst.is_dir():
+            return {"status": "error", "message": f"module {module_id!r} is not installed"}
+        shutil.rmtree(dst)
+        self.registry.plugins.pop(module_id, None)
+        return {"status": "uninstalled", "id": module_id}
+
+    def create_plugin_template(self, name: str) -> Dict[str, Any]:
+        from .plugins.registry import create_plugin
+
+        path = create_plugin(self.directory, name, self.registry.key)
+        self.registry.discover(self.directory)
+        return {"status": "created", "path": str(path)}

@@ -77,3 +77,49 @@ class BlockwiseMoments:
             raise ValueError("8-bit moment state has a different size")
         for k in ("m_q", "v_q", "m_scale", "v_scale"):
             getattr(self, k).copy_(sd[k].to(getattr(self, k).device))
+
+
+class AdamW8bit(torch.optim.Optimizer):
+    """AdamW whose two moments live in :class:`BlockwiseMoments` (2 bytes per parameter plus one scale per 256 elements).
+
+    A stand-alone optimizer with the constructor of ``torch.optim.AdamW`` (the reference re-exports
+    ``bitsandbytes.optim.AdamW8bit`` under this name when that package is installed, ``triune/optim/__init__.py``). The
+    update arithmetic is fp32 on decoded moments; decoupled weight decay; bias correction per parameter group step."""
+
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01):
+        if lr < 0 or eps < 0 or not (0 <= betas[0] < 1 and 0 <= betas[1] < 1):
+            raise ValueError("invalid AdamW8bit hyper-parameters")
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["moments"] = BlockwiseMoments(p.numel(), p.device)
+                st["step"] += 1
+                t = st["step"]
+                g = p.grad.detach().float().reshape(-1)
+                m, v = st["moments"].load(0, p.numel())
+                m.mul_(b1).add_(g, alpha=1 - b1)
+                v.mul_(b2).addcmul_(g, g, value=1 - b2)
+                st["moments"].store(0, p.numel(), m, v)
+                denom = (v / (1 - b2 ** t)).sqrt_().add_(group["eps"])
+                upd = (m / (1 - b1 ** t)).div_(denom).view_as(p)
+                if group["weight_decay"]:
+                    p.mul_(1 - group["lr"] * group["weight_decay"])
+                p.add_(upd.to(p.dtype), alpha=-group["lr"])
+        return loss
+
+    def state_bytes(self) -> int:
+        return sum(s["moments"].m_q.numel() + s["moments"].v_q.numel() + 4 * (s["moments"].m_scale.numel() + s["moments"].v_scale.numel())
+                   for s in self.state.values() if "moments" in s)
