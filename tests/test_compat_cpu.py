@@ -78,7 +78,8 @@ def test_a_script_written_against_the_reference_runs(triune, tmp_path):
     assert (get_rank(), get_world_size(), is_distributed(), is_main_process()) == (0, 1, False, True)
     x = torch.arange(8.0).view(1, 8)
     assert rotate_half(x).tolist() == [[-4.0, -5.0, -6.0, -7.0, 0.0, 1.0, 2.0, 3.0]]
-    assert torch.allclose(apply_rotary(x, torch.ones(8), torch.zeros(8)), x)
+    qr, kr = apply_rotary(x, 2 * x, torch.ones(8), torch.zeros(8))
+    assert torch.allclose(qr, x) and torch.allclose(kr, 2 * x)
     torch.manual_seed(0)
     model = TriuneTransformer(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=1, head_dim=32, num_experts=2, router_prefix_layers=1,
                               reflex_exit_layer=2, limbic_exit_layer=3)
@@ -133,6 +134,9 @@ def test_graph_engine_registry_and_modules_under_reference_names(triune, tmp_pat
     out = eng.execute_node({"id": "d", "type": "Doubler"}, {"value": 21})
     assert out["status"] == "success" and out["output"]["ports"]["doubled"] == 42
     assert "Doubler" in global_registry
+    from triune_b200.execution.studio import STUDIO_NODES
+
+    STUDIO_NODES.pop("Doubler")  # leave the process-wide catalogue as it was
     from triune_b200.plugins.registry import create_plugin
 
     src = create_plugin(tmp_path / "src", "my_nodes")
@@ -153,3 +157,56 @@ def test_a_real_package_of_that_name_is_not_shadowed():
             compat.install()
     finally:
         del sys.modules["triune"]
+
+
+def test_reference_signatures_of_operators_and_agents(triune, tmp_path):
+    """Where the two projects order or name arguments differently, the names under ``triune.*`` follow the reference."""
+    from triune.agents import AgentHarness, AgentMemoryStore, MultiAgentOrchestrator, SkillLibrary, build_integrated_toolbelt
+    from triune.ops import batched_qr, batched_subspace_projection, muon_orthogonalize, route_tiers, subspace_projection, triangular_steer_update
+    from triune.optim import zeropower_via_newtonschulz5
+    from triune.trainer import all_reduce_dict
+
+    from triune_b200 import ops
+
+    torch.manual_seed(0)
+    P, G = torch.randn(2, 6, 6), torch.randn(2, 6, 6)
+    want = ops.triangular_steer_update(P.clone(), G, 0.9, 0.25)  # this framework: (P, G, momentum, scale)
+    assert torch.allclose(triangular_steer_update(P.clone(), G, 0.25, 0.9), want)  # the reference: (P, G, scale, momentum)
+    assert torch.allclose(triangular_steer_update(P.clone(), G, steer_scale=0.25, momentum=0.9), want)
+    R = triangular_steer_update(torch.randn(2, 8, 4), torch.randn(2, 8, 4), 0.1, 0.9, retract_stiefel=True)
+    assert torch.allclose(R.transpose(1, 2) @ R, torch.eye(4).expand(2, 4, 4), atol=1e-3)
+    probs, tiers = route_tiers(torch.tensor([[4.0, 0.0, 0.0], [0.0, 0.0, 3.0]]), reflex_threshold=0.7)
+    assert torch.allclose(probs.sum(-1), torch.ones(2)) and tiers.tolist() == [0, 2]
+    A = torch.randn(3, 20, 4)
+    Q = batched_qr(A)
+    Q2, mask = batched_qr(A, return_fallback_mask=True)
+    Q3, info = batched_qr(A, return_diagnostics=True, out_dtype=torch.float64)
+    assert torch.allclose(Q, Q2) and mask.shape == (3,) and Q3.dtype == torch.float64 and "orth_err" in info
+    assert subspace_projection(torch.randn(16, 12), 4).shape[-1] == 4
+    Qb, path = batched_subspace_projection(torch.randn(2, 16, 12), 4)
+    assert Qb.shape[0] == 2 and isinstance(path, str) and len(batched_subspace_projection(torch.randn(2, 16, 12), 4, return_diagnostics=True)) == 3
+    Gm = torch.randn(8, 12)
+    assert torch.allclose(muon_orthogonalize(Gm, 5), zeropower_via_newtonschulz5(Gm, steps=5))
+    X, scratch = zeropower_via_newtonschulz5(Gm, 5, 1e-7, "buf", True)
+    assert scratch == "buf" and X.shape == Gm.shape
+    assert all_reduce_dict({"loss": 2.0, "tokens": 10}) == {"loss": 2.0, "tokens": 10.0}
+
+    ws = tmp_path / "ws"
+    ws.mkdir()
+    (ws / "a.txt").write_text("hello")
+    mem = AgentMemoryStore(tmp_path / "store")
+    tools = build_integrated_toolbelt(workspace=ws, memory=mem, allow_writes=False, subagent_runner=lambda task, persona: f"{persona}: {task}")
+    assert "write_file" not in tools.tools and tools.call("read_file", path="a.txt") == "hello"
+    assert tools.call("remember", text="the corpus lives in a.txt") == "noted" and "a.txt" in tools.call("recall", query="where is the corpus")[0]
+    assert tools.call("delegate", task="check", persona="sentinel") == "sentinel: check"
+    assert (tmp_path / "store" / "memory.json").is_file()
+    lib = SkillLibrary(tmp_path / "skills", extra_skill_dirs=[tmp_path / "none"])
+    assert lib.skills == {}
+    seen = []
+    h = AgentHarness(workspace=ws, store_dir=tmp_path / "store", completion_fn=lambda prompt: (seen.append(prompt), {"text": "done"})[1], allow_writes=False)
+    out = h.run("explain why the file exists")
+    assert out["text"] == "done" and out["persona"] == "researcher" and "write_file" not in out["tools_offered"]
+    orch = MultiAgentOrchestrator(h)
+    assert [o["agent"] for o in orch.execute("plan then review", ["architect", "sentinel"])] == ["architect", "sentinel"]
+    par = orch.execute_parallel("look at it", ["engineer", "tutor"], max_workers=2)
+    assert [o["agent"] for o in par] == ["engineer", "tutor"] and all(o["text"] == "done" for o in par)

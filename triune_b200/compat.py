@@ -32,7 +32,7 @@ import torch.nn as nn
 # reference package -> [(module of this framework, names exported under the same name)], plus renames {ref name: "module:attr"}
 _SAME: Dict[str, List[Tuple[str, Tuple[str, ...]]]] = {
     "optim": [("optim.centroid", ("CentroidSteerOptimizer",)), ("optim.manifold", ("LowSpaceWeightProjector", "QuantumUnitaryOptimizer", "UnitaryManifoldOptimizer")),
-              ("optim.muon", ("Muon", "zeropower_via_newtonschulz5")), ("optim.factory", ("build_optimizer",))],
+              ("optim.muon", ("Muon",)), ("optim.factory", ("build_optimizer",))],
     "model": [("models.zoo", ("CANONICAL_MODEL_SPECS", "MODEL_REGISTRY", "ModelSpec", "build_model_from_spec", "get_model_spec", "load_model", "register_model")),
               ("models.transformer", ("TriuneTransformer",)), ("models.speculative", ("SelfSpeculativeGenerator",)), ("models.block", ("TransformerBlock",)),
               ("models.attention", ("HybridAttention", "VectorisedGLA")), ("models.moe", ("MoE_FFN", "RoutingResult")), ("models.norms", ("RMSNorm",)),
@@ -48,15 +48,13 @@ _SAME: Dict[str, List[Tuple[str, Tuple[str, ...]]]] = {
                 ("runtime.vram", ("VRAMProfiler", "AutoOffloader")), ("runtime.cuda_graph", ("CUDAGraphEngine",)), ("runtime.neuron_scope", ("NeuronScope",)),
                 ("runtime.parallel_engine", ("ParallelEngine", "GLAPipelineBlock", "MoERoutingBlock"))],
     "ops": [("ops._c_bridge", ("NativeTriuneEngine", "get_native_c_info")),
-            ("optim.subspace", ("batched_qr", "cholesky_qr", "subspace_projection", "batched_subspace_projection")),
-            ("ops", ("triangular_steer_update", "gla", "muon_ns", "rmsnorm", "swiglu", "cross_entropy", "lora_linear", "route_tiers")),
+            ("ops", ("gla", "muon_ns", "rmsnorm", "swiglu", "cross_entropy", "lora_linear")),
             ("runtime.neuron_scope", ("TIER_NAMES",)), ("kernels", ("FastChunkedCrossEntropyLoss",))],
-    "agents": [("agents", ("Agent", "MultiAgentOrchestrator", "Tool", "ToolRegistry", "build_integrated_toolbelt")), ("agents.harness", ("AgentHarness",)),
-               ("agents.extras", ("AgentMemoryStore", "ProviderManager", "SkillLibrary"))],
+    "agents": [("agents", ("Agent", "Tool", "ToolRegistry")), ("agents.extras", ("ProviderManager",))],
     "recipes": [("recipes", ("bf16_autocast", "build_fp8_precision_context", "build_precision_context", "build_mxfp8_precision_context"))],
-    "trainer": [("trainer.engine", ("TrainingEngine",)), ("parallel.dist", ("DistributedContext", "setup_distributed", "cleanup_distributed", "all_reduce_tensor", "all_reduce_dict")),
+    "trainer": [("trainer.engine", ("TrainingEngine",)), ("parallel.dist", ("DistributedContext", "setup_distributed", "cleanup_distributed", "all_reduce_tensor")),
                 ("trainer.trainer", ("Trainer",)), ("trainer.logger", ("NullLogger", "WandbLogger")),
-                ("trainer.finetune", ("LoRAConfig", "LoRALayer", "TriuneFineTuner", "list_adapters", "export_adapter", "merge_adapter_checkpoint"))],
+                ("trainer.finetune", ("LoRAConfig", "LoRALayer", "TriuneFineTuner", "list_adapters", "export_adapter"))],
     "kernels": [("kernels", ())],  # every public name of kernels.py, see _names_of
     "export": [("export.exporter", ("export_gguf", "export_onnx", "export_safetensors", "export_model")), ("export.hf_compat", ("export_to_huggingface",))],
     "api": [("serve", ("create_app", "run_server"))],
@@ -70,18 +68,23 @@ _SAME: Dict[str, List[Tuple[str, Tuple[str, ...]]]] = {
     "utils": [],
 }
 _RENAMED: Dict[str, Dict[str, str]] = {
-    "optim": {"AdamW8bit": "compat:AdamW8bit", "HAS_8BIT": "compat:HAS_8BIT"},
+    "optim": {"AdamW8bit": "compat:AdamW8bit", "HAS_8BIT": "compat:HAS_8BIT", "zeropower_via_newtonschulz5": "compat:zeropower_via_newtonschulz5"},
     "model": {"TriuneModel": "compat:TriuneModel", "apply_rotary": "compat:apply_rotary", "rotate_half": "compat:rotate_half"},
     "runtime": {"MemoryPlan": "runtime.memory_planner:MemoryEstimate", "apply_layer_streaming_if_requested": "compat:apply_layer_streaming_if_requested"},
     "ops": {"is_native_c_available": "ops._c_bridge:is_available", "c_centroid_steer_update_f32": "ops._c_bridge:c_centroid_steer_update",
             "c_route_tiers_f32": "ops._c_bridge:c_route_tiers", "c_compute_neuron_heatmap_f32": "ops._c_bridge:c_neuron_heatmap",
-            "c_gla_recurrent_step_f32": "ops._c_bridge:c_gla_recurrent_step", "muon_orthogonalize": "ops:muon_ns", "norm": "ops:rmsnorm", "rope": "ops:apply_rope",
+            "c_gla_recurrent_step_f32": "ops._c_bridge:c_gla_recurrent_step", "muon_orthogonalize": "compat:muon_orthogonalize", "norm": "ops:rmsnorm", "rope": "ops:apply_rope",
+            "batched_qr": "compat:batched_qr", "cholesky_qr": "compat:cholesky_qr", "subspace_projection": "compat:subspace_projection",
+            "batched_subspace_projection": "compat:batched_subspace_projection", "triangular_steer_update": "compat:triangular_steer_update",
+            "route_tiers": "compat:route_tiers",
             "gelu": "ops:gelu_tanh", "chunked_cross_entropy": "kernels:chunked_cross_entropy_from_hidden", "lora_forward": "kernels:fast_lora_forward",
             "upgrade": "models.universal:upgrade_model", "TIER_REFLEX": "compat:TIER_REFLEX", "TIER_LIMBIC": "compat:TIER_LIMBIC", "TIER_CORTEX": "compat:TIER_CORTEX"},
-    "agents": {"AgentSkill": "agents.extras:Skill", "BUILTIN_PERSONAS": "agents.harness:PERSONAS", "PersonaProfile": "agents.harness:PersonaSpec",
+    "agents": {"AgentHarness": "compat:AgentHarness", "AgentMemoryStore": "compat:AgentMemoryStore", "SkillLibrary": "compat:SkillLibrary",
+               "MultiAgentOrchestrator": "compat:MultiAgentOrchestrator", "build_integrated_toolbelt": "compat:build_integrated_toolbelt",
+               "AgentSkill": "agents.extras:Skill", "BUILTIN_PERSONAS": "agents.harness:PERSONAS", "PersonaProfile": "agents.harness:PersonaSpec",
                "ProviderConfig": "agents.extras:Provider", "StateController": "compat:StateController", "CognitiveState": "compat:CognitiveState",
                "LearnedLesson": "compat:LearnedLesson", "ToolStats": "compat:ToolStats", "UserPreference": "compat:UserPreference"},
-    "trainer": {"Engine": "trainer.engine:TrainingEngine", "DistributedTrainingEngine": "compat:DistributedTrainingEngine", "is_distributed": "compat:is_distributed",
+    "trainer": {"all_reduce_dict": "compat:all_reduce_dict", "merge_adapter_checkpoint": "compat:merge_adapter_checkpoint", "Engine": "trainer.engine:TrainingEngine", "DistributedTrainingEngine": "compat:DistributedTrainingEngine", "is_distributed": "compat:is_distributed",
                 "get_rank": "compat:get_rank", "get_world_size": "compat:get_world_size", "get_local_rank": "compat:get_local_rank",
                 "is_main_process": "compat:is_main_process", "wrap_distributed_model": "compat:wrap_distributed_model"},
     "configs": {"default_config": "compat:default_config"},
@@ -221,9 +224,9 @@ def rotate_half(x: torch.Tensor) -> torch.Tensor:
     return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
 
 
-def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x * cos + rotate_half(x) * sin with tables that broadcast against x (half-split convention)."""
-    return x * cos + rotate_half(x) * sin
+def apply_rotary(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(q, k) -> (q cos + rotate_half(q) sin, k cos + rotate_half(k) sin) with tables that broadcast against them."""
+    return q * cos + rotate_half(q) * sin, k * cos + rotate_half(k) * sin
 
 
 def apply_layer_streaming_if_requested(model: nn.Module, device, config: Dict[str, Any], optimizer: Optional[Any] = None):
@@ -254,6 +257,181 @@ def AdamW8bit(params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, w
     from .optim.adam8bit import AdamW8bit as _Impl
 
     return _Impl(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+
+
+
+# ---------------------------------------------------------------------------------------------------- operator signatures
+def muon_orthogonalize(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    from . import ops
+
+    return ops.muon_ns(G, steps)
+
+
+def zeropower_via_newtonschulz5(G: torch.Tensor, steps: int = 5, eps: float = 1e-7, scratch_buffer: Any = None, return_scratch: bool = False):
+    from . import ops
+
+    X = ops.muon_ns(G, steps)
+    return (X, scratch_buffer) if return_scratch else X
+
+
+def triangular_steer_update(P: torch.Tensor, Grad_proj: torch.Tensor, steer_scale: float = 1.0, momentum: float = 0.9, retract_stiefel: bool = False) -> torch.Tensor:
+    """The reference's argument order (scale before momentum); optionally retracts the result onto orthonormal columns."""
+    from . import ops
+
+    out = ops.triangular_steer_update(P, Grad_proj, momentum, steer_scale)
+    if retract_stiefel:
+        from .optim.subspace import polar_stiefel_retraction
+
+        out = polar_stiefel_retraction(out)
+    return out
+
+
+def route_tiers(logits: torch.Tensor, reflex_threshold: float = 0.70) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (probabilities [B, 3], selected tier [B])."""
+    from . import ops
+
+    return torch.softmax(logits.float(), dim=-1), ops.route_tiers(logits.float(), reflex_threshold)
+
+
+def batched_qr(Y_mat: torch.Tensor, cond_threshold: float = 1e4, eps_shift: float = 1e-7, orth_tol: float = 1e-4, return_fallback_mask: bool = False,
+               return_diagnostics: bool = False, out_dtype: Optional[torch.dtype] = None):
+    from .optim.subspace import batched_qr as _qr
+
+    Q, info = _qr(Y_mat, cond_threshold, eps_shift, orth_tol, return_info=True)
+    if out_dtype is not None:
+        Q = Q.to(out_dtype)
+    if return_diagnostics:
+        return Q, info
+    if return_fallback_mask:
+        return Q, info["fallback_mask"]
+    return Q
+
+
+def cholesky_qr(Y_f: torch.Tensor, cond_threshold: float = 1e4, eps_shift: float = 1e-7, orth_tol: float = 1e-4) -> torch.Tensor:
+    return batched_qr(Y_f, cond_threshold, eps_shift, orth_tol)
+
+
+def subspace_projection(grad: torch.Tensor, rank: int, niter: int = 2, cond_threshold: float = 1e4, eps_shift: float = 1e-7, orth_tol: float = 1e-4) -> torch.Tensor:
+    from .optim.subspace import subspace_projection as _sp
+
+    return _sp(grad, rank, power_iters=max(0, int(niter) - 1))
+
+
+def batched_subspace_projection(grads: torch.Tensor, rank: int, niter: int = 2, cond_threshold: float = 1e4, eps_shift: float = 1e-7, orth_tol: float = 1e-4,
+                                return_diagnostics: bool = False):
+    """-> (bases [K, d, rank], name of the path taken) and, on request, per-call diagnostics."""
+    from .optim.subspace import batched_subspace_projection as _bsp
+    from .optim.subspace import flush_qr_telemetry, new_qr_telemetry  # noqa: F401
+
+    Q = _bsp(grads, rank, power_iters=max(0, int(niter) - 1))
+    path = "batched_scholqr2"
+    return (Q, path, []) if return_diagnostics else (Q, path)
+
+
+def all_reduce_dict(metrics: Dict[str, float], op: Any = None) -> Dict[str, float]:
+    """Average (the default) or sum of scalar metrics over the ranks."""
+    from .parallel.dist import all_reduce_dict as _ard
+
+    out = _ard({k: float(v) for k, v in metrics.items()})
+    if op is not None and "SUM" in str(op).upper():
+        out = {k: v * get_world_size() for k, v in out.items()}
+    return out
+
+
+def merge_adapter_checkpoint(adapter_path, checkpoint_path, output_path=None, tokenizer_path="triune_tokenizer.json"):
+    """Load the checkpoint's model, fold the adapter into its weights, write a checkpoint of the merged model; -> its path."""
+    from pathlib import Path
+
+    from .inference import load_checkpoint_model
+    from .trainer.checkpoint import save_checkpoint
+    from .trainer.finetune import merge_adapter_checkpoint as _merge
+
+    model = load_checkpoint_model(str(checkpoint_path))[0]
+    _merge(model, adapter_path)
+    out = Path(output_path) if output_path else Path(checkpoint_path).with_name(Path(checkpoint_path).stem + "_merged.pt")
+    save_checkpoint(str(out), model=model, step=0, config={})
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------- agents, reference signatures
+def AgentMemoryStore(store_dir="checkpoints/agent_harness"):
+    from pathlib import Path
+
+    from .agents.extras import AgentMemoryStore as _Impl
+
+    return _Impl(str(Path(store_dir) / "memory.json"))
+
+
+def SkillLibrary(store_dir="checkpoints/agent_harness/skills", extra_skill_dirs=None):
+    from pathlib import Path
+
+    from .agents.extras import SkillLibrary as _Impl
+
+    Path(store_dir).mkdir(parents=True, exist_ok=True)
+    lib = _Impl(str(store_dir))
+    for d in extra_skill_dirs or []:
+        if Path(d).is_dir():
+            lib.load_directory(str(d))
+    return lib
+
+
+def build_integrated_toolbelt(*, workspace=".", memory=None, skills=None, state_controller=None, subagent_runner=None, allow_shell: bool = False,
+                              allow_writes: bool = True, allow_local_http: bool = False):
+    """The workspace-confined tools (read-only unless ``allow_writes``; a shell only with ``allow_shell``); requests to
+    loopback or private addresses stay refused whatever ``allow_local_http`` says."""
+    from .agents import Tool
+    from .agents.harness import workspace_tools
+
+    reg = workspace_tools(str(workspace), read_only=not allow_writes, allow_shell=allow_shell)
+    if memory is not None:
+        reg.register(Tool("remember", "keep a note for later runs", lambda text: (memory.add_lesson(str(text)), memory.save(), "noted")[2], {"text": "str"}))
+        reg.register(Tool("recall", "notes of earlier runs that match a query", lambda query: [t for _, t in memory.recall(str(query))], {"query": "str"}))
+    if subagent_runner is not None:
+        reg.register(Tool("delegate", "hand a sub-task to another persona", lambda task, persona=None: subagent_runner(str(task), persona), {"task": "str", "persona": "str"}))
+    return reg
+
+
+class AgentHarness:
+    """The reference's keyword-only constructor over ``agents.harness.AgentHarness``. ``completion_fn(prompt=..., **kw)``
+    returns the text (or a dictionary with a ``text`` / ``content`` entry); without it ``model`` names a local model that
+    is loaded on first use."""
+
+    def __new__(cls, *, workspace=".", store_dir="checkpoints/agent_harness", model: Optional[str] = None, allow_shell: bool = False, allow_writes: bool = True,
+                allow_local_http: bool = False, completion_fn: Optional[Callable[..., Any]] = None, providers=None, depth: int = 0, persona: str = "auto",
+                max_steps: int = 3):
+        from .agents.harness import AgentHarness as _Impl
+
+        state: Dict[str, Any] = {}
+
+        def generate(prompt: str) -> str:
+            if completion_fn is not None:
+                out = completion_fn(prompt=prompt)
+                return out if isinstance(out, str) else str(out.get("text") or out.get("content") or "")
+            if "st" not in state:
+                from .serve.engine_state import EngineState
+
+                state["st"] = EngineState()
+                state["st"].load_model(model or "triune-nano")
+            return state["st"].generate(prompt, max_new_tokens=256, template=False)["text"]
+
+        return _Impl(generate, str(store_dir), workspace=str(workspace), persona=persona, read_only=not allow_writes, allow_shell=allow_shell, max_steps=max_steps)
+
+
+class MultiAgentOrchestrator:
+    """Specialists that take a goal in turn (``execute``) or side by side (``execute_parallel``) through one harness."""
+
+    def __init__(self, harness=None):
+        self.harness = harness
+
+    def execute(self, goal: str, personas: List[str]) -> List[Dict[str, Any]]:
+        return self.harness.run_team(goal, list(personas))
+
+    def execute_parallel(self, goal: str, personas: List[str], max_workers: int = 4) -> List[Dict[str, Any]]:
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=max(1, int(max_workers))) as ex:
+            outs = list(ex.map(lambda p: {"agent": p, **self.harness.run(goal, persona=p)}, personas))
+        return outs
 
 
 # ---------------------------------------------------------------------------------------------------- distributed helpers
@@ -343,8 +521,8 @@ class StateController:
     """Chooses persona and depth for a goal (``triune/agents/personas.py``): persona by the goal's words, depth by its
     length (short questions leave at the Reflex exit, long tasks use the full depth)."""
 
-    def __init__(self, persona: str = "auto", depth: str = "auto"):
-        self.persona, self.depth = persona, depth
+    def __init__(self, store_dir=None, persona: str = "auto", depth: str = "auto"):
+        self.store_dir, self.persona, self.depth = store_dir, persona, depth
 
     def assess(self, goal: str) -> CognitiveState:
         from .agents.harness import resolve_persona

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 import torch.nn as nn
 
@@ -11,8 +13,11 @@ from .. import ops
 class RotaryEmbedding(nn.Module):
     """Caches cos/sin [max_len, head_dim] (half-split layout); the cache doubles when a longer range is asked."""
 
-    def __init__(self, head_dim: int, max_seq_len: int = 8192, base: float = 10000.0):
+    def __init__(self, head_dim: Optional[int] = None, max_seq_len: int = 8192, base: float = 10000.0, dim: Optional[int] = None):
         super().__init__()
+        head_dim = head_dim if head_dim is not None else dim  # ``dim`` is the reference's name for this argument
+        if head_dim is None:
+            raise TypeError("RotaryEmbedding needs the head dimension")
         self.head_dim = head_dim
         self.base = base
         self.max_seq_len = max_seq_len

@@ -31,9 +31,12 @@ def _clone_cache(cache):
 
 
 class SelfSpeculativeGenerator:
-    def __init__(self, model, tokenizer=None, k_draft: int = 3, eos_token_id: Optional[int] = None,
-                 pad_token_id: Optional[int] = None, draft_depth: int = 0, verify_depth: int = 2):
+    def __init__(self, model, tokenizer=None, k_draft: int = 3, temperature: float = 0.0, pad_token_id: Optional[int] = None,
+                 eos_token_id: Optional[int] = None, draft_depth: int = 0, verify_depth: int = 2):
+        # positional order of the reference's constructor (``triune/model/speculative.py``); ``temperature`` is the default
+        # of ``generate`` when that call names none
         self.model = model
+        self.temperature = float(temperature)
         self.tokenizer = tokenizer
         self.k_draft = max(1, int(k_draft))
         self.draft_depth, self.verify_depth = draft_depth, verify_depth
@@ -58,7 +61,7 @@ class SelfSpeculativeGenerator:
         return F.softmax(lg / max(temperature, 1e-6), dim=-1)
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: float = 0.0, top_k: int = 0,
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: Optional[float] = None, top_k: int = 0,
                  generator: Optional[torch.Generator] = None) -> torch.Tensor:
         """input_ids [1, T]. Returns [1, T + n] with n <= max_new_tokens.
 
@@ -71,6 +74,7 @@ class SelfSpeculativeGenerator:
         was_training = model.training
         model.eval()
         dev = input_ids.device
+        temperature = self.temperature if temperature is None else float(temperature)
         greedy = temperature <= 0
         cache = model.init_cache(input_ids.shape[0])
         if input_ids.shape[1] > 1:

@@ -166,7 +166,12 @@ def find_layer_list(model: nn.Module, layers_attr: Optional[str] = None) -> nn.M
 
 
 class LayerStreamingEngine:
-    def __init__(self, model: nn.Module, device, config: Optional[StreamingConfig] = None, layers_attr: Optional[str] = None):
+    def __init__(self, model: nn.Module, device, config: Optional[StreamingConfig] = None, layers_attr: Optional[str] = None,
+                 optimizer=None, layers_path: Optional[str] = None):
+        # ``optimizer`` / ``layers_path``: keywords of the reference's constructor (``triune/runtime/streaming.py``). A tiered
+        # optimizer given here updates the streamed layers through ``step_parameters`` once the engine is attached.
+        layers_attr = layers_attr or layers_path
+        self._ctor_optimizer = optimizer
         self.model = model
         self.device = torch.device(device)
         self.cfg = config or StreamingConfig()
@@ -242,6 +247,12 @@ class LayerStreamingEngine:
         for b in self.model.buffers():
             b.data = b.data.to(self.device)
         self._attached = True
+        opt = self._ctor_optimizer
+        if opt is not None and hasattr(opt, "step_parameters") and getattr(self, "layer_optimizer", None) is None:
+            # the constructor was given a tiered optimizer: streamed layers are updated by the same kind, with its settings
+            kind = type(opt)
+            kw = {k: getattr(opt, k) for k in ("lr", "weight_decay") if isinstance(getattr(opt, k, None), (int, float))}
+            self.enable_tiered_optimizer(lambda module: kind(module, **kw))
         return self
 
     def detach(self):

@@ -34,7 +34,11 @@ class ConsoleLogger(NullLogger):
 
 class Trainer:
     def __init__(self, model: torch.nn.Module, config: Dict[str, Any], optimizer=None, train_loader: Optional[Iterable] = None,
-                 eval_loader: Optional[Iterable] = None, tokenizer=None, device=None, logger=None, dp=None):
+                 eval_loader: Optional[Iterable] = None, tokenizer=None, device=None, logger=None, dp=None,
+                 precision_context=None, sample_prompt: str = "The history of"):
+        # ``precision_context`` / ``sample_prompt``: keywords of the reference's constructor. Weights here are kept in their
+        # training dtype (bf16 on a GPU), so a context manager factory is only entered around evaluation passes.
+        self.precision_context, self.sample_prompt = precision_context, sample_prompt
         self.config = dict(config)
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         self.model = model
