@@ -210,3 +210,77 @@ def test_reference_signatures_of_operators_and_agents(triune, tmp_path):
     assert [o["agent"] for o in orch.execute("plan then review", ["architect", "sentinel"])] == ["architect", "sentinel"]
     par = orch.execute_parallel("look at it", ["engineer", "tutor"], max_workers=2)
     assert [o["agent"] for o in par] == ["engineer", "tutor"] and all(o["text"] == "done" for o in par)
+
+
+def test_method_names_of_the_reference_on_core_classes(triune):
+    """Methods that callers of the reference use on the engine, optimizer, layer and loader classes exist here and do the
+    same job (CPU: the graph engine captures nothing and falls back)."""
+    from triune.data import CyclingDataLoader
+    from triune.kernels import NVFP4Linear
+    from triune.model import FP4Linear, FP8Linear, MoE_FFN, RotaryEmbedding, SelfSpeculativeGenerator, TriuneTransformer
+    from triune.optim import CentroidSteerOptimizer
+    from triune.runtime import CUDAGraphEngine, LayerStreamingEngine, StreamingConfig
+    from triune.trainer import Trainer
+
+    torch.manual_seed(0)
+    model = TriuneTransformer(vocab_size=64, hidden_dim=32, num_layers=5, num_heads=1, head_dim=32, num_experts=2, router_prefix_layers=1,
+                              reflex_exit_layer=2, limbic_exit_layer=3)
+    opt = CentroidSteerOptimizer(model, lr=1e-3)
+    opt.param_groups[0]["lr"] = 5e-4  # what an outer PyTorch scheduler does
+    opt.sync_lr_from_param_groups()
+    assert opt.lr == 5e-4 and opt.muon_lr == pytest.approx(opt.initial_muon_lr * 0.5)
+    moe = MoE_FFN(32, 4, 2).eval()
+    x = torch.randn(2, 6, 32)
+    with torch.no_grad():
+        assert torch.allclose(moe.sparse_forward(x), moe(x, update_stats=False))
+    f4 = FP4Linear(32, 16)
+    q4 = f4.to_nvfp4_inference()
+    assert q4(torch.randn(3, 32)).shape == (3, 16)
+    with pytest.raises(ValueError):
+        FP4Linear(24, 8).to_nvfp4_inference()
+    f8 = FP8Linear(32, 16)
+    w0 = f8.weight.clone()
+    f8.reset_parameters()
+    assert not torch.equal(w0, f8.weight)
+    assert NVFP4Linear.empty_skeleton(32, 16).weight.shape == (16, 32)
+    assert RotaryEmbedding(dim=16).head_dim == 16 and RotaryEmbedding(16).head_dim == 16
+    gen = SelfSpeculativeGenerator(model, None, 2, 0.7)  # (model, tokenizer, k_draft, temperature): the reference's positional order
+    assert gen.temperature == 0.7 and gen.k_draft == 2
+    it = CyclingDataLoader([1, 2])
+    assert [it.next(), it.next(), it.next()] == [1, 2, 1]
+
+    tr = Trainer(model=model, optimizer=opt, train_loader=None, eval_loader=None, tokenizer=None, config={"vocab_size": 64, "lr": 1e-3},
+                 device="cpu", precision_context=None, logger=None, sample_prompt="Once")
+    assert tr.sample_prompt == "Once"
+    with tr.bf16_autocast():
+        pass
+    eng = LayerStreamingEngine(model, torch.device("cpu"), StreamingConfig(), optimizer=None, layers_path=None)
+    eng.attach()
+    try:
+        roots = eng.get_root_parameters()
+        inside = {id(p) for l in eng.layers for p in l.parameters()}
+        assert roots and all(id(p) not in inside for p in roots)
+        eng.set_optimizer(opt)
+        tr.engine.sync_streaming_engine()
+        eng.flush_d2h_transfers()
+        eng.zero_grad()
+        ids = torch.randint(0, 64, (2, 9))
+        model.forward_loss(ids[:, :-1], ids[:, 1:], force_depth=2).backward()
+        norm = eng.step_optimizer(None)
+        assert norm > 0
+        eng.cleanup_resident_layers()
+    finally:
+        eng.detach()
+
+    g = CUDAGraphEngine("cpu")
+    lin = torch.nn.Linear(4, 4)
+    sgd = torch.optim.SGD(lin.parameters(), lr=0.1)
+    xb, yb = torch.randn(2, 4), torch.randn(2, 4)
+    assert g.capture_training_step(lin, sgd, xb, yb) is False and g.capture_inference_step(lin, xb) is False and not g.can_replay(xb, yb)
+    assert g.step(xb, yb, sync=True, fallback_fn=lambda a, b: 1.5) == 1.5
+    assert float(g.step(xb, yb, fallback_fn=lambda a, b: 2.5)) == 2.5
+    assert torch.equal(g.inference_step(xb, fallback_fn=lambda a: a * 2), xb * 2)
+    with pytest.raises(RuntimeError):
+        g.step(xb, yb)
+    g.invalidate()
+    assert g.current_loss_item() == 0.0 and g.is_captured is False

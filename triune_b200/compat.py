@@ -471,33 +471,23 @@ def wrap_distributed_model(model: nn.Module, device_ids: Optional[List[int]] = N
     return DDP(model, device_ids=device_ids, find_unused_parameters=find_unused_parameters, broadcast_buffers=False)
 
 
-def _training_engine_base():
-    from .trainer.engine import TrainingEngine
-
-    return TrainingEngine
+from .trainer.engine import TrainingEngine as _TrainingEngine  # noqa: E402
 
 
-class DistributedTrainingEngine:
+class DistributedTrainingEngine(_TrainingEngine):
     """``TrainingEngine`` whose step results also carry the loss and token count reduced over all ranks
-    (``global_loss``, ``global_lm_loss``, ``global_tokens``)."""
+    (``global_loss``, ``global_lm_loss``, ``global_tokens``; ``triune/trainer/distributed.py:159-181``)."""
 
-    def __new__(cls, trainer):
-        base = _training_engine_base()
+    def __init__(self, trainer):
+        super().__init__(trainer)
+        self.is_distributed = is_distributed()
 
-        class _Engine(base):  # built on first use so that importing this module does not import the trainer
-            def step_once(self, *a, **k):
-                res = super().step_once(*a, **k)
-                if is_distributed() and isinstance(res, dict):
-                    from .parallel.dist import all_reduce_dict
-
-                    red = all_reduce_dict({"loss": float(res.get("loss", 0.0)), "lm_loss": float(res.get("lm", res.get("loss", 0.0))),
-                                           "tokens": float(res.get("tokens", 0))})
-                    res["global_loss"], res["global_lm_loss"], res["global_tokens"] = red["loss"], red["lm_loss"], int(red["tokens"])
-                return res
-
-        eng = _Engine(trainer)
-        eng.is_distributed = is_distributed()
-        return eng
+    def step_once(self, *a, **k):
+        res = super().step_once(*a, **k)
+        if self.is_distributed and isinstance(res, dict):
+            red = all_reduce_dict({"loss": float(res.get("loss", 0.0)), "lm_loss": float(res.get("lm", res.get("loss", 0.0))), "tokens": float(res.get("tokens", 0))})
+            res["global_loss"], res["global_lm_loss"], res["global_tokens"] = red["loss"], red["lm_loss"], int(red["tokens"])
+        return res
 
 
 # ---------------------------------------------------------------------------------------------------- agents records

@@ -27,6 +27,8 @@ class CyclingDataLoader:
             self._it = iter(self.loader)
             return next(self._it)
 
+    next = __next__
+
 
 class SyntheticTokenSource:
     """Endless (input, next-token label) batches of uniform-random ids; pinned when CUDA is present."""
@@ -93,4 +95,4 @@ class AsyncDevicePrefetcher:
         self._preload()
         return out
 
-    next_batch = __next__
+    next_batch = next = __next__

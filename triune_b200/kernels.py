@@ -227,6 +227,12 @@ class FastFP8Linear(nn.Module):
         nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
         self._q = None
 
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+        self._q = None
+
     def quantize(self):
         from .models.quant_linear import FP8Linear
 
@@ -285,6 +291,17 @@ class NVFP4Linear(nn.Module):
         self.impl = _Impl.from_linear(linear, hadamard=hadamard)
         self.in_features, self.out_features, self.hadamard, self.dtype = linear.in_features, linear.out_features, hadamard, linear.weight.dtype
         return self
+
+    @classmethod
+    def empty_skeleton(cls, in_features: int, out_features: int, bias: bool = False, hadamard: bool = False, device=None) -> "NVFP4Linear":
+        """A layer with packed storage of the right shape and no values yet, to be filled by a checkpoint loader."""
+        self = cls(in_features, out_features, bias=bias, hadamard=hadamard)
+        return self.to(device) if device is not None else self
+
+    @property
+    def weight(self) -> torch.Tensor:
+        """The de-quantised weight ``[out, in]`` (a copy; the storage stays packed)."""
+        return self.impl.dequantized()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.impl(x)

@@ -185,6 +185,11 @@ class MoE_FFN(nn.Module):
         cap = max(1, min(int(math.ceil(N / self.num_experts * self.capacity_multiplier)), N))
         return cap if cap < N else None
 
+    def sparse_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """The routed (top-k, grouped by expert) evaluation without touching the routing statistics: the reference's name
+        for it (``triune/model/moe.py:126``); here the forward pass always takes this form."""
+        return self.forward(x, update_stats=False)
+
     def forward(self, x: torch.Tensor, update_stats: bool = True) -> torch.Tensor:
         B, T, D = x.shape
         x2 = x.reshape(B * T, D)

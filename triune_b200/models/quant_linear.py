@@ -39,6 +39,12 @@ class FP8Linear(nn.Module):
         self._mx = None  # (version, E4M3 weight, blocked power-of-two scales per 1x32) for the block-scaled tensor-core GEMM
         self.mx = True   # inference on CUDA: MXFP8 (scales applied by the tensor core); False: fp32 128-block scales
 
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, std=0.02)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+        self._q = self._mx = None
+
     def quantized_mx(self):
         from ..ops import quant_cuda
 
@@ -193,6 +199,12 @@ class FP4Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
+
+    def to_nvfp4_inference(self) -> "NVFP4Linear":
+        """This layer as packed 4-bit inference storage (E2M1 values, one scale per 16 inputs)."""
+        if self.in_features % 16 != 0:
+            raise ValueError(f"NVFP4 packed format requires in_features % 16 == 0, got {self.in_features}")
+        return NVFP4Linear.from_linear(self)
 
     def forward(self, x):
         w = self.weight

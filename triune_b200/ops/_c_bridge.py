@@ -131,6 +131,10 @@ class NativeTriuneEngine:
             raise RuntimeError("triune_engine_create failed")
 
     @property
+    def is_ready(self) -> bool:
+        return bool(self._lib is not None and self._h)
+
+    @property
     def version(self) -> str:
         return self._lib.triune_engine_version().decode()
 

@@ -247,6 +247,14 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         return out
 
     # ------------------------------------------------------------------ learning rates
+    def sync_lr_from_param_groups(self) -> None:
+        """An outer PyTorch scheduler writes ``param_groups[0]["lr"]``; carry a change over to the tiers (Muon and expert
+        rates keep their ratios to the base rate)."""
+        if self.param_groups:
+            outer = self.param_groups[0].get("lr", self.lr)
+            if outer != self.lr:
+                self.set_lr(float(outer))
+
     def set_lr(self, lr: float, expert_lr: Optional[float] = None, muon_lr: Optional[float] = None):
         """Set the base LR; Muon and expert LRs keep their initial ratio to it unless given explicitly."""
         self._in_set_lr = True

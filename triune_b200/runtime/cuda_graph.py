@@ -22,7 +22,17 @@ from ..profiling import nvtx_range
 
 
 class CUDAGraphEngine:
-    def __init__(self, trainer=None, warmup_steps: int = 2):
+    def __init__(self, trainer=None, warmup_steps: int = 2, device=None):
+        if isinstance(trainer, (str, torch.device)):  # the reference's constructor takes the device first
+            trainer, device = None, trainer
+        self.device = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        # state of the generic capture below (one training or inference step of any model / optimizer pair)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.static_input: Optional[torch.Tensor] = None
+        self.static_target: Optional[torch.Tensor] = None
+        self.static_loss: Optional[torch.Tensor] = None
+        self.static_output: Any = None
+        self.is_captured = False
         self.trainer = trainer
         self.graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.outputs: Dict[Tuple, Any] = {}
@@ -38,6 +48,111 @@ class CUDAGraphEngine:
         # kept alive by a retained graph) remember the stream they were created on, and a capture that has to wait
         # for work on any other, uncaptured stream is invalid.
         self.stream = torch.cuda.Stream() if self.enabled else None
+
+    # ------------------------------------------------------------------ generic capture (any model / optimizer pair)
+    # The method names and arguments of the reference's engine (``triune/runtime/cuda_graph.py:31-230``). Capture needs a
+    # CUDA device; without one ``capture_*`` return False and ``step`` / ``inference_step`` run the fallback.
+    def invalidate(self) -> None:
+        self.graph = self.static_input = self.static_target = self.static_loss = self.static_output = None
+        self.is_captured = False
+
+    @staticmethod
+    def _same(a: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> bool:
+        return a is not None and b is not None and a.shape == b.shape and a.dtype == b.dtype and a.device == b.device
+
+    def can_replay(self, input_tokens: torch.Tensor, target_tokens: Optional[torch.Tensor] = None) -> bool:
+        if not self.is_captured or self.graph is None or not self._same(input_tokens, self.static_input):
+            return False
+        return target_tokens is None or self.static_target is None or self._same(target_tokens, self.static_target)
+
+    def _run_step(self, model, optimizer, loss_fn, step_fn):
+        if step_fn is not None:
+            return step_fn(model, optimizer, self.static_input, self.static_target)
+        optimizer.zero_grad(set_to_none=False)  # gradients keep their storage: the graph replays in place
+        out = model(self.static_input)
+        if loss_fn is not None:
+            loss = loss_fn(out, self.static_target)
+        else:
+            loss = (out[0] if isinstance(out, tuple) else out).sum()
+        loss.backward()
+        optimizer.step()
+        return loss
+
+    def capture_training_step(self, model, optimizer, sample_input: torch.Tensor, sample_target: torch.Tensor, loss_fn: Optional[Callable] = None,
+                              step_fn: Optional[Callable] = None, warmup_steps: int = 3) -> bool:
+        """Forward, backward and optimizer update of one batch shape in one graph; False (nothing captured) when that is
+        not possible here."""
+        if not torch.cuda.is_available() or self.device.type != "cuda":
+            return False
+        try:
+            for group in getattr(optimizer, "param_groups", []):
+                if "capturable" in group:
+                    group["capturable"] = True
+            self.static_input, self.static_target = sample_input.clone().to(self.device), sample_target.clone().to(self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):  # warm-up on the capture stream: lazily created optimizer state exists afterwards
+                for _ in range(max(1, int(warmup_steps))):
+                    self._run_step(model, optimizer, loss_fn, step_fn)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self.static_loss = self._run_step(model, optimizer, loss_fn, step_fn)
+            self.is_captured = True
+            return True
+        except Exception:
+            self.invalidate()
+            return False
+
+    def step(self, input_tokens: torch.Tensor, target_tokens: Optional[torch.Tensor] = None, sync: bool = False, fallback_fn: Optional[Callable] = None):
+        """Replay with a new batch; the loss stays on the device unless ``sync``. A batch of another shape goes to
+        ``fallback_fn(input, target)``."""
+        if not self.can_replay(input_tokens, target_tokens):
+            if fallback_fn is None:
+                raise RuntimeError("CUDA Graph cannot replay with mismatched tensor shapes without a fallback.")
+            res = fallback_fn(input_tokens, target_tokens)
+            if sync:
+                return float(res.item()) if isinstance(res, torch.Tensor) else float(res)
+            return res if isinstance(res, torch.Tensor) else torch.tensor(res, device=self.device)
+        self.static_input.copy_(input_tokens, non_blocking=True)
+        if self.static_target is not None and target_tokens is not None:
+            self.static_target.copy_(target_tokens, non_blocking=True)
+        self.graph.replay()
+        if sync:
+            return self.current_loss_item()
+        return self.static_loss
+
+    def current_loss_item(self) -> float:
+        return float(self.static_loss.item()) if self.static_loss is not None else 0.0
+
+    def capture_inference_step(self, model, sample_input: torch.Tensor, warmup_steps: int = 3) -> bool:
+        if not torch.cuda.is_available() or self.device.type != "cuda":
+            return False
+        try:
+            self.static_input = sample_input.clone().to(self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side), torch.no_grad():
+                for _ in range(max(1, int(warmup_steps))):
+                    model(self.static_input)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side), torch.no_grad():
+                self.static_output = model(self.static_input)
+            self.is_captured = True
+            return True
+        except Exception:
+            self.invalidate()
+            return False
+
+    def inference_step(self, input_tokens: torch.Tensor, fallback_fn: Optional[Callable] = None):
+        if not self.can_replay(input_tokens):
+            if fallback_fn is None:
+                raise RuntimeError("CUDA Graph cannot replay with mismatched tensor shapes without a fallback.")
+            return fallback_fn(input_tokens)
+        self.static_input.copy_(input_tokens, non_blocking=True)
+        self.graph.replay()
+        return self.static_output
 
     # ------------------------------------------------------------------ training
     def _body(self, x, y, n_valid):

@@ -226,6 +226,47 @@ class LayerStreamingEngine:
             for p in st.params:
                 p.grad = None
 
+    # ------------------------------------------------------------------ the reference's method names
+    # (``triune/runtime/streaming.py:442-450, 953-1078, 1209-1243``): the same operations under the names its callers use
+    def set_optimizer(self, optimizer) -> None:
+        """The optimizer that updates the root (non-streamed) parameters in ``step_optimizer``; a tiered optimizer also
+        becomes the kind that updates the streamed layers."""
+        self.optimizer = optimizer
+        self._ctor_optimizer = optimizer
+        if self._attached and optimizer is not None and hasattr(optimizer, "step_parameters") and self.layer_optimizer is None:
+            kind = type(optimizer)
+            kw = {k: getattr(optimizer, k) for k in ("lr", "weight_decay") if isinstance(getattr(optimizer, k, None), (int, float))}
+            self.enable_tiered_optimizer(lambda module: kind(module, **kw))
+
+    def get_root_parameters(self) -> List[nn.Parameter]:
+        """Parameters outside the streamed block stack (embeddings, router, heads): resident on the device."""
+        inside = {id(p) for layer in self.layers for p in layer.parameters()}
+        return [p for p in self.model.parameters() if id(p) not in inside]
+
+    def cleanup_resident_layers(self) -> None:
+        self.cleanup()
+
+    def flush_d2h_transfers(self) -> None:
+        """Wait until every gradient that is on its way to host memory has arrived."""
+        if self.cuda:
+            self.d2h_stream.synchronize()
+
+    def zero_grad(self) -> None:
+        self.model.zero_grad(set_to_none=True)
+        opt = getattr(self, "optimizer", None)
+        if opt is not None:
+            opt.zero_grad(set_to_none=True)
+        for st in self.stores.values():  # gradients of streamed layers accumulate in their host buffers
+            st.grad_sumsq = None
+            if getattr(st, "_has_grad", False):
+                st.host_grad.zero_()
+                st._has_grad = False
+
+    def step_optimizer(self, optimizer=None, **kw) -> float:
+        """Clip, update the root parameters with ``optimizer`` and the streamed layers with their own optimizer; -> the
+        global gradient norm."""
+        return self.step_streaming_optimizer(optimizer if optimizer is not None else getattr(self, "optimizer", None), **kw)
+
     # ------------------------------------------------------------------ attach / detach
     def attach(self):
         if self._attached:

@@ -48,6 +48,13 @@ class TrainingEngine:
         self._moe = _moe_layers(self.model)
         self.streaming_engine = getattr(trainer, "streaming_engine", None)
 
+    def sync_streaming_engine(self) -> None:
+        """Hand the optimizer and the clip norm to a layer-streaming engine attached to the model."""
+        eng = getattr(self.model, "_streaming_engine", None) or self.streaming_engine
+        if eng is not None and self.optimizer is not None:
+            eng.set_optimizer(self.optimizer)
+            eng.cfg.grad_clip = float(self.config.get("grad_clip", 1.0))
+
     # ------------------------------------------------------------------ helpers
     def _exploration(self) -> float:
         base = float(self.config.get("exploration", 0.2))

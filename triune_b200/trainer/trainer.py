@@ -69,6 +69,15 @@ class Trainer:
             self.graph_engine = CUDAGraphEngine(self)
 
     # ---- protocol used by TrainingEngine ------------------------------------------------------
+    def bf16_autocast(self):
+        """Context manager for evaluation passes on models kept in fp32 (``precision_context`` given to the constructor
+        wins)."""
+        if self.precision_context is not None:
+            return self.precision_context()
+        from ..recipes import bf16_autocast
+
+        return bf16_autocast(self.device.type)
+
     def next_batch(self):
         if self._pending is not None:
             b, self._pending = self._pending, None
