@@ -284,3 +284,59 @@ def test_method_names_of_the_reference_on_core_classes(triune):
         g.step(xb, yb)
     g.invalidate()
     assert g.current_loss_item() == 0.0 and g.is_captured is False
+
+
+def test_reference_method_names_on_agents_registry_and_modules(triune, tmp_path):
+    from triune.agents import AgentHarness, MultiAgentOrchestrator, PersonaProfile, ProviderManager, StateController, ToolStats, build_integrated_toolbelt
+    from triune.modules import ModuleManager
+    from triune.plugins import NodeRegistry
+
+    tools = build_integrated_toolbelt(workspace=tmp_path, allow_writes=True)
+    assert "read_file" in tools.names() and tools.get("clock").run().endswith("Z") and tools.get("nope") is None
+    ok = tools.execute("write_file", {"path": "a.txt", "content": "x"})
+    bad = tools.execute("read_file", {"path": "../outside"})
+    assert ok["ok"] and not bad["ok"] and "PermissionError" in bad["error"] and tools.stats["read_file"] == {"calls": 1, "failures": 1, "seconds": bad["seconds"]}
+    spec = {t["function"]["name"]: t for t in tools.to_openai_tools()}["read_file"]
+    assert spec["type"] == "function" and spec["function"]["parameters"]["properties"]["start"] == {"type": "integer"}
+    assert "- read_file(path, start, length)" in tools.format_prompt_catalog() and len(tools.list_tools()) == len(tools.names())
+    st = ToolStats(calls=4, failures=1, seconds=0.2)
+    assert st.success_rate == 0.75 and st.avg_latency_ms == pytest.approx(50.0) and st.calibrated_reliability == pytest.approx(4 / 6)
+    assert ToolStats().success_rate == 0.0 and ToolStats().calibrated_reliability == 0.5
+
+    sc = StateController(tmp_path)
+    sc.register_persona("poet", "Answer in verse.", 0.9, ("poem", "verse"))
+    assert sc.adapt_for_goal("a poem in verse, please")["persona"] == "poet" and sc.shift("sentinel")["persona"] == "sentinel"
+    assert sc.active_profile.name == "sentinel" and isinstance(sc.active_profile, PersonaProfile) and sc.active_profile.to_dict()["name"] == "sentinel"
+    sc2 = StateController()
+    assert sc2.adapt_after_tool("search", ok=False)["persona"] == "debugger"
+    assert sc.delete_persona("poet") and not sc.delete_persona("poet")
+
+    pm = ProviderManager(transport=lambda p, msgs, opt: f"{p.name}/{opt.get('model', p.model)}: {msgs[-1]['content']}")
+    pm.register_provider("local", "http://127.0.0.1:11434", "gemma3:4b")
+    pm.register_provider("cloud", "https://api.example.com", "big", api_key="")
+    assert pm.list_active_providers() == ["local"] and pm.pick_default_model() == "local:gemma3:4b" and pm.get_provider("LOCAL").model == "gemma3:4b"
+    assert pm.complete_chat([{"role": "user", "content": "hi"}]) == {"text": "local/gemma3:4b: hi", "provider": "local", "model": "gemma3:4b"}
+    with pytest.raises(KeyError):
+        pm.complete_chat([], model="nobody:x")
+
+    h = AgentHarness(workspace=tmp_path, store_dir=tmp_path / "store", completion_fn=lambda prompt: "fine")
+    assert h.run_goal("say something")["text"] == "fine"
+    orch = MultiAgentOrchestrator(h)
+    orch.add_agent("architect")
+    orch.add_agent("engineer")
+    orch.add_agent("architect")
+    assert [s["agent"] for s in orch.execute_pipeline("build it")] == ["architect", "engineer"]
+    team = orch.orchestrate_team("build it", parallel=True, max_workers=2)
+    assert team["team"] == ["architect", "engineer"] and team["final"] == "fine" and team["parallel"] is True
+
+    reg = NodeRegistry()
+    assert "TriuneTransformer" in reg.list_nodes() and reg.get_core_node_names() == reg.list_nodes()
+    assert [p["name"] for p in reg.get_schema("RouterZLoss")["inputs"]] == ["router_logits"] and reg.get_node("nope") is None
+
+    mm = ModuleManager(config_dir=str(tmp_path / "mods"))
+    assert mm.save_config({"directory": str(tmp_path / "mods"), "active": ["a"]}) == mm.get_config()
+    assert mm.inspect_directory(str(tmp_path))["files"] >= 1 and mm.inspect_directory(str(tmp_path / "zz"))["status"] == "error"
+    assert mm.search_marketplace("x")["results"] == [] and mm.check_updates()["updates"] == []
+    assert mm.clone_repository("https://github.com/a/b")["status"] == "error" and mm.git_pull("none")["status"] == "error"
+    assert "os_type" in mm.scan_hardware_and_software()
+    assert mm.create_custom_plugin_template("my_plug")["status"] == "created" and mm.discover_and_register_nodes("my_plug")["status"] == "active"

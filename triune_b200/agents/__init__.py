@@ -24,10 +24,14 @@ class Tool:
     fn: Callable[..., Any]
     parameters: Dict[str, str] = field(default_factory=dict)
 
+    def run(self, **args) -> Any:
+        return self.fn(**args)
+
 
 class ToolRegistry:
     def __init__(self):
         self.tools: Dict[str, Tool] = {}
+        self.stats: Dict[str, Dict[str, float]] = {}  # per tool: calls, failures, total seconds
 
     def register(self, tool: Tool) -> None:
         self.tools[tool.name] = tool
@@ -39,6 +43,39 @@ class ToolRegistry:
 
     def describe(self) -> List[Dict[str, Any]]:
         return [{"name": t.name, "description": t.description, "parameters": t.parameters} for t in self.tools.values()]
+
+    # ---- the same registry under the method names of the reference (``triune/agents/tools.py``)
+    def get(self, name: str) -> Optional[Tool]:
+        return self.tools.get(name)
+
+    def names(self) -> List[str]:
+        return sorted(self.tools)
+
+    def list_tools(self) -> List[Dict[str, Any]]:
+        return self.describe()
+
+    def execute(self, name: str, args: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        """Run a tool and report instead of raising: ``{"ok", "result" | "error", "seconds"}``; keeps per-tool statistics."""
+        t0 = time.time()
+        st = self.stats.setdefault(name, {"calls": 0, "failures": 0, "seconds": 0.0})
+        st["calls"] += 1
+        try:
+            out = {"ok": True, "result": self.call(name, **(args or {}))}
+        except Exception as e:
+            st["failures"] += 1
+            out = {"ok": False, "error": f"{type(e).__name__}: {e}"}
+        out["seconds"] = time.time() - t0
+        st["seconds"] += out["seconds"]
+        return out
+
+    def to_openai_tools(self) -> List[Dict[str, Any]]:
+        """The catalogue as ``tools`` of a chat-completions request (JSON-schema parameters)."""
+        kinds = {"str": "string", "int": "integer", "float": "number", "bool": "boolean"}
+        return [{"type": "function", "function": {"name": t.name, "description": t.description, "parameters": {
+            "type": "object", "properties": {k: {"type": kinds.get(v, "string")} for k, v in t.parameters.items()}}}} for t in self.tools.values()]
+
+    def format_prompt_catalog(self) -> str:
+        return "\n".join(f"- {t.name}({', '.join(t.parameters)}): {t.description}" for t in self.tools.values())
 
 
 _GROUP_NETS = (ipaddress.ip_network("224.0.0.0/4"), ipaddress.ip_network("ff00::/8"))  # group-addressed ranges
@@ -116,6 +153,9 @@ class Agent:
         tools = "\n".join(f"- {t['name']}: {t['description']}" for t in self.tools.describe())
         hist = "".join(f"{m['role'].capitalize()}: {m['content']}\n" for m in self.transcript[-8:])
         return f"System: {self.persona.system_prompt}\nTools:\n{tools}\n{hist}User: {user}\nAssistant:"
+
+    def run_task(self, task: str) -> Dict[str, Any]:
+        return self.run(task)
 
     def run(self, user: str) -> Dict[str, Any]:
         calls = []

@@ -101,6 +101,13 @@ class Skill:
     body: str
     path: Optional[str] = None
 
+    uses: int = 0
+    successes: int = 0
+
+    @property
+    def success_rate(self) -> float:
+        return self.successes / self.uses if self.uses else 0.0
+
     def matches(self, request: str) -> float:
         req = set(_tokens(request))
         hit = sum(1.0 for t in self.triggers if set(_tokens(t)) <= req)
@@ -174,6 +181,33 @@ class ProviderManager:
     def describe(self) -> List[Dict[str, Any]]:
         return [{"name": p.name, "base_url": p.base_url, "model": p.model, "key_hint": ("..." + p.api_key[-4:]) if p.api_key else ""}
                 for p in self.providers.values()]
+
+    # ---- method names of the reference's manager (``triune/agents/providers.py``)
+    def register_provider(self, name: str, base_url: str, model: str, api_key: str = "") -> Provider:
+        return self.save(name, base_url, model, api_key)
+
+    def get_provider(self, name: str) -> Optional[Provider]:
+        return self.providers.get(name.lower())
+
+    def list_active_providers(self) -> List[str]:
+        return sorted(n for n, p in self.providers.items() if p.api_key or p.base_url.startswith(("http://127.0.0.1", "http://localhost")))
+
+    def pick_default_model(self) -> Optional[str]:
+        act = self.list_active_providers()
+        return f"{act[0]}:{self.providers[act[0]].model}" if act else None
+
+    def complete_chat(self, messages: List[Dict[str, str]], model: Optional[str] = None, **options) -> Dict[str, Any]:
+        """``model`` is ``provider:model`` (or a provider name); -> ``{"text", "provider", "model"}``."""
+        spec = model or self.pick_default_model()
+        if spec is None:
+            raise RuntimeError("no provider is configured")
+        name, _, mdl = spec.partition(":")
+        p = self.providers.get(name.lower())
+        if p is None:
+            raise KeyError(f"unknown provider {name!r}")
+        if mdl:
+            options = {**options, "model": mdl}
+        return {"text": self.chat(name, messages, **options), "provider": p.name, "model": mdl or p.model}
 
     def chat(self, name: str, messages: List[Dict[str, str]], **options) -> str:
         p = self.providers.get(name.lower())

@@ -35,6 +35,9 @@ class PersonaSpec:
     temperature: float
     keywords: tuple  # words of a goal that point to this persona
 
+    def to_dict(self) -> Dict[str, Any]:
+        return {"name": self.name, "system_prompt": self.prompt, "temperature": self.temperature, "keywords": list(self.keywords)}
+
 
 PERSONAS: Dict[str, PersonaSpec] = {p.name: p for p in (
     PersonaSpec("architect", "You design systems. State the components, their interfaces and the trade-offs before any detail.", 0.5,
@@ -212,6 +215,9 @@ class AgentHarness:
         skill = self._synthesise_skill(goal, ok_calls) if self.auto_skill and ok_calls else None
         self.memory.save()
         return {**out, "seconds": time.time() - t0, "new_skill": skill, "tools_offered": sorted(self.tools.tools)}
+
+    def run_goal(self, goal: str, persona: Optional[str] = None) -> Dict[str, Any]:
+        return self.run(goal, persona)
 
     def _synthesise_skill(self, goal: str, calls: List[str]) -> Optional[str]:
         """Write the tool sequence that served this goal down as a skill (one file per distinct sequence)."""

@@ -391,16 +391,17 @@ def build_integrated_toolbelt(*, workspace=".", memory=None, skills=None, state_
     return reg
 
 
-class AgentHarness:
-    """The reference's keyword-only constructor over ``agents.harness.AgentHarness``. ``completion_fn(prompt=..., **kw)``
-    returns the text (or a dictionary with a ``text`` / ``content`` entry); without it ``model`` names a local model that
-    is loaded on first use."""
+from .agents.harness import AgentHarness as _HarnessImpl  # noqa: E402
 
-    def __new__(cls, *, workspace=".", store_dir="checkpoints/agent_harness", model: Optional[str] = None, allow_shell: bool = False, allow_writes: bool = True,
-                allow_local_http: bool = False, completion_fn: Optional[Callable[..., Any]] = None, providers=None, depth: int = 0, persona: str = "auto",
-                max_steps: int = 3):
-        from .agents.harness import AgentHarness as _Impl
 
+class AgentHarness(_HarnessImpl):
+    """The reference's keyword-only constructor over ``agents.harness.AgentHarness``. ``completion_fn(prompt=...)`` returns
+    the text (or a dictionary with a ``text`` / ``content`` entry); without it ``model`` names a local model that is loaded
+    on first use."""
+
+    def __init__(self, *, workspace=".", store_dir="checkpoints/agent_harness", model: Optional[str] = None, allow_shell: bool = False,
+                 allow_writes: bool = True, allow_local_http: bool = False, completion_fn: Optional[Callable[..., Any]] = None, providers=None,
+                 depth: int = 0, persona: str = "auto", max_steps: int = 3):
         state: Dict[str, Any] = {}
 
         def generate(prompt: str) -> str:
@@ -414,7 +415,9 @@ class AgentHarness:
                 state["st"].load_model(model or "triune-nano")
             return state["st"].generate(prompt, max_new_tokens=256, template=False)["text"]
 
-        return _Impl(generate, str(store_dir), workspace=str(workspace), persona=persona, read_only=not allow_writes, allow_shell=allow_shell, max_steps=max_steps)
+        super().__init__(generate, str(store_dir), workspace=str(workspace), persona=persona, read_only=not allow_writes, allow_shell=allow_shell,
+                         max_steps=max_steps)
+        self.providers, self.depth = providers, depth
 
 
 class MultiAgentOrchestrator:
@@ -422,6 +425,19 @@ class MultiAgentOrchestrator:
 
     def __init__(self, harness=None):
         self.harness = harness
+        self.team: List[str] = []
+
+    def add_agent(self, persona: str) -> None:
+        if persona not in self.team:
+            self.team.append(persona)
+
+    def execute_pipeline(self, goal: str, personas: Optional[List[str]] = None) -> List[Dict[str, Any]]:
+        return self.execute(goal, list(personas or self.team))
+
+    def orchestrate_team(self, goal: str, personas: Optional[List[str]] = None, parallel: bool = False, max_workers: int = 4) -> Dict[str, Any]:
+        names = list(personas or self.team)
+        steps = self.execute_parallel(goal, names, max_workers) if parallel else self.execute(goal, names)
+        return {"goal": goal, "team": names, "parallel": bool(parallel), "steps": steps, "final": steps[-1]["text"] if steps else ""}
 
     def execute(self, goal: str, personas: List[str]) -> List[Dict[str, Any]]:
         return self.harness.run_team(goal, list(personas))
@@ -500,7 +516,23 @@ class LearnedLesson(dict):
 
 
 class ToolStats(dict):
-    """Per-tool counters: ``{"calls", "failures"}``."""
+    """Per-tool counters: ``{"calls", "failures", "seconds"}`` with the derived figures the reference's record offers."""
+
+    @property
+    def success_rate(self) -> float:
+        c = float(self.get("calls", 0))
+        return (c - float(self.get("failures", 0))) / c if c else 0.0
+
+    @property
+    def avg_latency_ms(self) -> float:
+        c = float(self.get("calls", 0))
+        return 1e3 * float(self.get("seconds", 0.0)) / c if c else 0.0
+
+    @property
+    def calibrated_reliability(self) -> float:
+        """Success rate shrunk towards one half while there are few calls (one prior success and one prior failure)."""
+        c = float(self.get("calls", 0))
+        return (c - float(self.get("failures", 0)) + 1.0) / (c + 2.0)
 
 
 class CognitiveState(dict):
@@ -513,6 +545,37 @@ class StateController:
 
     def __init__(self, store_dir=None, persona: str = "auto", depth: str = "auto"):
         self.store_dir, self.persona, self.depth = store_dir, persona, depth
+
+    # ---- persona book-keeping under the reference's method names
+    def register_persona(self, name: str, system_prompt: str, temperature: float = 0.7, keywords=()) -> None:
+        from .agents.harness import PERSONAS, PersonaSpec
+
+        PERSONAS[name.lower()] = PersonaSpec(name.lower(), system_prompt, float(temperature), tuple(keywords))
+
+    def delete_persona(self, name: str) -> bool:
+        from .agents.harness import PERSONAS
+
+        return PERSONAS.pop(name.lower(), None) is not None
+
+    def shift(self, persona: str) -> CognitiveState:
+        """Switch to a persona by name and report the new state."""
+        self.persona = persona
+        return self.assess("")
+
+    def adapt_for_goal(self, goal: str) -> CognitiveState:
+        return self.assess(goal)
+
+    def adapt_after_tool(self, tool: str, ok: bool) -> CognitiveState:
+        """A failing tool call moves an automatic persona to the debugger for the rest of the goal."""
+        if not ok and self.persona in ("auto", ""):
+            self.persona = "debugger"
+        return self.assess("")
+
+    @property
+    def active_profile(self):
+        from .agents.harness import DEFAULT_PERSONA, PERSONAS
+
+        return PERSONAS.get(self.persona.lower(), DEFAULT_PERSONA)
 
     def assess(self, goal: str) -> CognitiveState:
         from .agents.harness import resolve_persona
@@ -547,6 +610,20 @@ class NodeRegistry:
         from .execution.studio import studio_catalog
 
         return studio_catalog()
+
+    def list_nodes(self) -> List[str]:
+        return sorted(n["name"] for n in self.get_catalog())
+
+    def get_core_node_names(self) -> List[str]:
+        """The built-in kinds (everything except ``Custom`` registrations)."""
+        return sorted(n["name"] for n in self.get_catalog() if n["category"] != "Custom")
+
+    def get_node(self, name: str) -> Optional[Dict[str, Any]]:
+        return next((n for n in self.get_catalog() if n["name"] == name), None)
+
+    def get_schema(self, name: str) -> Optional[Dict[str, Any]]:
+        n = self.get_node(name)
+        return None if n is None else {"inputs": n["typed_inputs"], "outputs": n["typed_outputs"], "parameters": n["parameters"]}
 
     def __contains__(self, name: str) -> bool:
         return self.get(name) is not None
@@ -655,10 +732,10 @@ class ModuleManager:
     directory, list, activate (verify and load), uninstall, scaffold. Remote catalogues are not contacted
     (``triune/modules/manager.py:345-1757`` of the reference also clones from the network)."""
 
-    def __init__(self, directory: str = "plugins", key: Optional[str] = None):
+    def __init__(self, directory: str = "plugins", key: Optional[str] = None, config_dir: Optional[str] = None):
         from .plugins.registry import PluginRegistry
 
-        self.directory = directory
+        self.directory = directory = str(config_dir or directory)
         self.registry = PluginRegistry(key)
         os.makedirs(directory, exist_ok=True)
         self.registry.discover(directory)
@@ -702,6 +779,80 @@ class ModuleManager:
         shutil.rmtree(dst)
         self.registry.plugins.pop(module_id, None)
         return {"status": "uninstalled", "id": module_id}
+
+    # ---- the rest of the reference manager's surface; what would need the network says so
+    def _config_path(self):
+        from pathlib import Path
+
+        return Path(self.directory) / "modules.json"
+
+    def get_config(self) -> Dict[str, Any]:
+        import json
+
+        p = self._config_path()
+        return json.loads(p.read_text()) if p.is_file() else {"directory": self.directory, "active": []}
+
+    def save_config(self, config: Dict[str, Any]) -> Dict[str, Any]:
+        import json
+
+        self._config_path().write_text(json.dumps(config, indent=1))
+        return config
+
+    def inspect_directory(self, path: str) -> Dict[str, Any]:
+        """What a directory holds, without importing anything from it."""
+        from pathlib import Path
+
+        d = Path(path)
+        if not d.is_dir():
+            return {"status": "error", "message": f"no such directory: {path}"}
+        files = [f for f in d.rglob("*") if f.is_file()]
+        return {"status": "ok", "path": str(d), "files": len(files), "python_files": sum(f.suffix == ".py" for f in files),
+                "has_manifest": (d / "plugin.json").is_file(), "is_git": (d / ".git").exists(),
+                "weights": sorted(f.name for f in files if f.suffix in (".safetensors", ".pt", ".gguf"))[:20]}
+
+    def discover_and_register_nodes(self, module_id: str) -> Dict[str, Any]:
+        return self.activate_module(module_id)
+
+    def create_custom_plugin_template(self, name: str) -> Dict[str, Any]:
+        return self.create_plugin_template(name)
+
+    def scan_hardware_and_software(self) -> Dict[str, Any]:
+        from .installer import probe_machine
+
+        return probe_machine().to_dict()
+
+    def search_marketplace(self, query: str = "") -> Dict[str, Any]:
+        return {"results": [], "note": "remote catalogues need network access, which this framework does not use"}
+
+    def check_updates(self) -> Dict[str, Any]:
+        return {"updates": [], "note": "remote catalogues need network access, which this framework does not use"}
+
+    def clone_repository(self, url: str, mod_type: str = "auto", branch: str = "main", name: Optional[str] = None) -> Dict[str, Any]:
+        """Clone a LOCAL git repository (a path or ``file://`` URL) into the module directory."""
+        import subprocess
+        from pathlib import Path
+
+        src = url[len("file://"):] if url.startswith("file://") else url
+        if "://" in src or src.startswith("git@") or not (Path(src) / ".git").exists():
+            return {"status": "error", "message": "only local git repositories can be cloned (no network access)"}
+        dst = (Path(self.directory) / (name or Path(src).name)).resolve()
+        if Path(self.directory).resolve() not in dst.parents or dst.exists():
+            return {"status": "error", "message": "the target exists already or escapes the module directory"}
+        r = subprocess.run(["git", "clone", "--quiet", "--depth", "1", src, str(dst)], capture_output=True, text=True, timeout=120)
+        if r.returncode != 0:
+            return {"status": "error", "message": r.stderr.strip()[:300]}
+        self.registry.discover(self.directory)
+        return {"status": "cloned", "id": dst.name, "path": str(dst)}
+
+    def git_pull(self, module_id: str) -> Dict[str, Any]:
+        import subprocess
+        from pathlib import Path
+
+        dst = (Path(self.directory) / module_id).resolve()
+        if Path(self.directory).resolve() not in dst.parents or not (dst / ".git").exists():
+            return {"status": "error", "message": f"no git module {module_id!r} is installed"}
+        r = subprocess.run(["git", "-C", str(dst), "pull", "--quiet", "--ff-only"], capture_output=True, text=True, timeout=120)
+        return {"status": "updated", "id": module_id} if r.returncode == 0 else {"status": "error", "message": r.stderr.strip()[:300]}
 
     def create_plugin_template(self, name: str) -> Dict[str, Any]:
         from .plugins.registry import create_plugin
