@@ -340,3 +340,32 @@ def test_reference_method_names_on_agents_registry_and_modules(triune, tmp_path)
     assert mm.clone_repository("https://github.com/a/b")["status"] == "error" and mm.git_pull("none")["status"] == "error"
     assert "os_type" in mm.scan_hardware_and_software()
     assert mm.create_custom_plugin_template("my_plug")["status"] == "created" and mm.discover_and_register_nodes("my_plug")["status"] == "active"
+
+
+def test_run_config_keys_and_exploration_schedule_follow_the_reference():
+    """Every key of the reference's default run config exists here (its 48 keys, read from its ``build_config``), and the
+    exploration schedule accepts the reference's names as well as a starting rate."""
+    from types import SimpleNamespace
+
+    from triune_b200.config import build_config
+    from triune_b200.trainer.engine import TrainingEngine
+
+    ref_keys = """vocab_size hidden_dim num_layers num_heads num_experts top_k router_prefix_layers reflex_exit_layer limbic_exit_layer target_depth_dist
+    depth_mode exploration exploration_steps use_fp4 use_fp8 batch_size seq_len grad_accum_steps total_steps lr min_lr warmup_steps betas weight_decay grad_clip
+    galore galore_rank galore_update_gap galore_lr galore_betas steer_scale use_triangular_core use_muon muon_lr muon_momentum log_every save_every eval_every
+    eval_batches checkpoint_dir shuffle_buffer dataset_name dataset_config num_workers""".split()
+    cfg = build_config({})
+    assert [k for k in ref_keys if k not in cfg] == [] and cfg["exploration"] == "linear" and cfg["dataset_config"] == "sample-10BT"
+
+    def rate(conf, step):
+        eng = SimpleNamespace(config=conf, step=step)
+        return TrainingEngine._exploration(eng)
+
+    lin = {"exploration": "linear", "exploration_steps": 100}
+    assert rate(lin, 0) == 1.0 and rate(lin, 25) == 0.75 and rate(lin, 100) == 0.0 and rate(lin, 500) == 0.0
+    cos = {"exploration": "cosine", "exploration_steps": 100}
+    assert rate(cos, 0) == 1.0 and rate(cos, 50) == pytest.approx(0.5) and rate(cos, 100) == 0.0
+    assert rate({"exploration": "none", "exploration_steps": 100}, 0) == 0.0 and rate({"exploration": "linear", "exploration_steps": 0}, 0) == 0.0
+    num = {"exploration": 0.2, "exploration_steps": 100}
+    assert rate(num, 0) == pytest.approx(0.2) and rate(num, 50) == pytest.approx(0.1) and rate(num, 100) == 0.0
+    assert rate({"exploration": 0.4, "exploration_steps": 100, "exploration_schedule": "cosine"}, 50) == pytest.approx(0.2)

@@ -244,7 +244,7 @@ class TrainConfig:
     checkpoint_dir: str = "checkpoints_full"
     grad_checkpoint: bool = True
     precision: str = "bf16"
-    exploration: float = 0.2
+    exploration: Any = "linear"  # schedule name ("linear", "cosine", "none") or a starting rate
     exploration_steps: int = 5000
     usage_ema_decay: float = DEPTH_USAGE_EMA
     bias_strength: float = DEPTH_BIAS_STRENGTH
@@ -357,7 +357,7 @@ _FLAT_DEFAULTS: Dict[str, Any] = {
     "bias_strength": DEPTH_BIAS_STRENGTH,
     "usage_ema_decay": DEPTH_USAGE_EMA,
     "depth_mode": "dynamic",
-    "exploration": 0.2,
+    "exploration": "linear",  # the reference's schedule name; a number is taken as a starting rate
     "exploration_steps": 5000,
     "exit_distill_coef": 0.2,
     "use_fp4": False,
@@ -394,6 +394,12 @@ _FLAT_DEFAULTS: Dict[str, Any] = {
     "cuda_graph": False,
     "layer_streaming": False,
     "seed": 0,
+    # data source keys of the reference's run config (``triune/configs/config.py:62-65``); with no network the dataset
+    # name is only a label unless ``dataset_path`` points at local files
+    "shuffle_buffer": 4096,
+    "dataset_name": "HuggingFaceFW/fineweb-edu",
+    "dataset_config": "sample-10BT",
+    "num_workers": 0,
 }
 
 

@@ -57,10 +57,22 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------ helpers
     def _exploration(self) -> float:
-        base = float(self.config.get("exploration", 0.2))
-        steps = max(1, int(self.config.get("exploration_steps", 5000)))
-        frac = min(1.0, self.step / steps)
-        if self.config.get("exploration_schedule", "linear") == "cosine":
+        """Probability of a random depth in the dynamic mode. ``exploration`` is either the reference's schedule name
+        (``"linear"`` / ``"cosine"`` / ``"none"``: from 1 down to 0 over ``exploration_steps``,
+        ``triune/trainer/engine.py:49-58``) or a number: the starting rate of a schedule named by ``exploration_schedule``."""
+        mode = self.config.get("exploration", "linear")
+        steps = int(self.config.get("exploration_steps", 5000))
+        if isinstance(mode, str):
+            if mode == "none" or steps <= 0:
+                return 0.0
+            base, sched = 1.0, mode
+        else:
+            base, sched = float(mode), str(self.config.get("exploration_schedule", "linear"))
+            steps = max(1, steps)
+        if self.step >= steps:
+            return 0.0
+        frac = self.step / steps
+        if sched == "cosine":
             return base * 0.5 * (1.0 + math.cos(math.pi * frac))
         return base * (1.0 - frac)
 
