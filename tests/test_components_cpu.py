@@ -1179,3 +1179,73 @@ def test_agent_harness_personas_tools_memory_and_skills(tmp_path):
     assert out2["new_skill"] is None  # no tool was used this time
     team = h2.run_team("review the code for risk", ["engineer", "sentinel"])
     assert [t["agent"] for t in team] == ["engineer", "sentinel"] and team[1]["persona"] == "sentinel"
+
+
+def test_staging_invariants_identity_restoration_and_backward_after_master_mutation():
+    """Parameters keep their identity through stage / release, the host master comes back unchanged, gradients flow
+    through staged weights, and a backward pass that runs after the layer was released and its host master overwritten
+    still differentiates the weights the forward pass used."""
+    from triune_b200.runtime.staging import ParameterStager
+
+    class Two(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin1, self.lin2 = nn.Linear(16, 16), nn.Linear(16, 16)
+
+        def forward(self, x):
+            return self.lin2(torch.relu(self.lin1(x)))
+
+    torch.manual_seed(42)
+    ref_layer, layer = Two(), Two()
+    layer.load_state_dict(ref_layer.state_dict())
+    ids = [id(p) for p in layer.parameters()]
+    before = [p.detach().clone() for p in layer.parameters()]
+    st = ParameterStager("cpu")
+    st.register_module(layer)
+    st.stage_layer(layer)
+    assert [id(p) for p in layer.parameters()] == ids
+    x_ref = torch.randn(4, 16, requires_grad=True)
+    x = x_ref.detach().clone().requires_grad_(True)
+    (ref_layer(x_ref) ** 2).sum().backward()
+    out = layer(x)
+    st.release_layer(layer)
+    assert [id(p) for p in layer.parameters()] == ids
+    assert all(torch.equal(a, b) for a, b in zip(before, layer.parameters()))
+    for b in st.buffers.values():  # something rewrites the host masters between this layer's forward and its backward
+        b.cpu_master.add_(torch.randn_like(b.cpu_master) * 10.0)
+    st.stage_layer(layer, is_backward=True)  # the backward pass re-stages the weights the forward pass saw
+    assert all(torch.equal(a, b) for a, b in zip(before, layer.parameters()))
+    (out ** 2).sum().backward()
+    st.release_layer(layer, clear_snapshot=True)
+    assert [id(p) for p in layer.parameters()] == ids
+    assert not any(torch.equal(a, b) for a, b in zip(before, layer.parameters()))  # the masters are the rewritten ones
+    assert st.get_memory_summary()["snapshot_bytes"] == 0
+    assert torch.allclose(x.grad, x_ref.grad, atol=1e-6)
+    for (n, p), (_, q) in zip(layer.named_parameters(), ref_layer.named_parameters()):
+        assert p.grad is not None and torch.allclose(p.grad, q.grad, atol=1e-6), n
+
+
+def test_profile_summaries_carry_their_commands_and_name_existing_files():
+    """Every measurement summary says what it ran on, gives at least one full command, and every repository file or
+    module a command names exists, so that each figure can be taken again from the committed tree."""
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    files = sorted((root / "profiles").glob("*.md"))
+    assert len(files) >= 10
+    for f in files:
+        text = f.read_text()
+        assert "B200" in text, f.name
+        assert "_work/" not in text, f.name
+        cmds = [ln.strip() for ln in text.splitlines() if re.match(r"\s*(python|ncu|nvcc)\s", ln)]
+        cmds += re.findall(r"`((?:python|ncu|nvcc) [^`]+)`", text)
+        assert cmds, f"{f.name}: no command line"
+        for c in cmds:
+            for script in re.findall(r"(?<![\w/.-])((?:[\w-]+/)*[\w-]+\.py)\b", c):
+                assert (root / script).exists(), f"{f.name}: {script}"
+            for mod in re.findall(r"-m (triune_b200[\w.]*)", c):
+                p = root / mod.replace(".", "/")
+                assert p.with_suffix(".py").exists() or (p / "__main__.py").exists() or (p / "__init__.py").exists(), f"{f.name}: {mod}"
+        cells = [c.strip().lower() for ln in text.splitlines() if ln.lstrip().startswith("|") for c in ln.split("|")]
+        assert not any(c in ("nan", "inf", "-inf") or re.fullmatch(r"-\d[\d.]*( ?[a-zµ/%]+)?", c) for c in cells), f.name
