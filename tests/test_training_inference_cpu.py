@@ -900,3 +900,42 @@ def test_streaming_fp8_weight_staging_and_bf16_gradient_staging():
     for p, (off, n, shape) in zip(st.params, st.slices):
         if p.dim() < 2:
             assert torch.equal(st.expand_fp8("cpu")[off : off + n].view(shape), st.host[off : off + n].view(shape))
+
+
+def test_streamed_model_keeps_dynamic_depth_forced_exits_all_exits_cached_decode_and_jev():
+    """With its layers streamed from the host, the model still chooses a depth per sequence, honours a forced depth, gives
+    all three exits at once, decodes step by step through the recurrent cache with the logits of the resident model, and
+    runs the JEV exit policy; afterwards no layer stays staged (tests/test_streaming_dynamic_depth.py:13-108)."""
+    from triune_b200.runtime.streaming import LayerStreamingEngine, StreamingConfig
+
+    ref, m = tiny(3).eval(), tiny(3).eval()
+    eng = LayerStreamingEngine(m, device="cpu", config=StreamingConfig(enabled=True, async_prefetch=True, pin_memory=False))
+    eng.attach()
+    x = torch.randint(0, 256, (2, 16))
+    with torch.no_grad():
+        logits, route = m(x)
+        assert logits.shape == (2, 16, 256) and route.shape == (2, 3)
+        assert m.last_depth_choice is not None and bool(torch.isin(m.last_depth_choice, torch.tensor([0, 1, 2])).all())
+        for depth in (0, 1, 2):
+            forced, froute = m(x, force_depth=depth)
+            assert forced.shape == (2, 16, 256) and froute.shape == (2, 3) and bool((m.last_depth_choice == depth).all())
+            assert torch.allclose(forced, ref(x, force_depth=depth)[0], atol=1e-5)
+        outs = m.forward_all_exits(x)
+        assert [tuple(o.shape) for o in outs] == [(2, 16, 256)] * 3 + [(2, 3)]
+        for o, r in zip(outs, ref.forward_all_exits(x)):
+            assert torch.allclose(o, r, atol=1e-5)
+        cache, rcache = m.init_cache(2), ref.init_cache(2)
+        for t in range(3):
+            tok = x[:, t : t + 1]
+            out, cache = m(tok, cache=cache, force_depth=2)
+            rout, rcache = ref(tok, cache=rcache, force_depth=2)
+            assert out.shape == (2, 1, 256) and torch.allclose(out, rout, atol=1e-5)
+        assert len(cache) == len(m.layers) and all(c is not None for c in cache)
+        m.enable_jev_routing(threshold=0.0)
+        jl, _ = m(x, exit_policy="jev")
+        assert jl.shape == (2, 16, 256) and bool(torch.isfinite(jl).all())
+    assert all(v == 0 for v in eng._staged.values())
+    assert sum(st.device_buf is not None for st in eng.stores.values()) <= 1  # at most the layer prefetched past an exit
+    eng.drop_prefetched()
+    assert all(st.device_buf is None for st in eng.stores.values())
+    eng.detach()

@@ -315,13 +315,14 @@ class LayerStreamingEngine:
                 return engine._unflatten(i, out)
             engine.stage(i, prefetch=i + 1)
             try:
-                return orig(x, *args, **kwargs)
+                out = orig(x, *args, **kwargs)
             except BaseException:
                 engine.release(i)
                 engine.drop_prefetched()
                 raise
-            else:
+            if not torch.is_grad_enabled():  # with a graph recorded and no recomputation, backward still reads these weights
                 engine.release(i)
+            return out
 
         layer.forward = forward
 
