@@ -106,6 +106,49 @@ _MODULE_ALIASES = {
     "kernels.fast_muon": "kernels", "kernels.fast_lora": "kernels", "kernels.fast_nvfp4": "kernels", "kernels.fast_fp8": "kernels",
 }
 
+# every other module path of the reference -> the modules of this framework its names are looked up in, in order ("compat":
+# this module). Looked up when a name is first touched, so importing one of these paths imports nothing heavy.
+_DEEP: Dict[str, Tuple[str, ...]] = {
+    "agents._storage": ("compat",), "agents.engine": ("compat", "agents", "agents.extras"), "agents.memory": ("compat", "agents.extras"),
+    "agents.personas": ("compat", "agents.harness"), "agents.providers": ("compat", "agents.extras"), "agents.skills": ("compat", "agents.extras"),
+    "agents.tools": ("compat", "agents", "agents.harness", "agents.extras"),
+    "callbacks.base": ("callbacks.base",), "callbacks.events": ("callbacks.events",), "callbacks.telemetry": ("callbacks.telemetry",),
+    "cli_ui": ("cli_ui",), "configs.config": ("compat", "config"), "execution.dag": ("compat", "execution.dag", "execution.studio", "execution.nodes"),
+    "kernels.dispatcher": ("kernels", "compat"), "kernels.fast_triangular": ("compat", "kernels"), "kernels.fast_muon": ("compat", "kernels"),
+    "kernels.fast_nvfp4": ("compat", "kernels"),
+    "model.adapters": ("models.adapters",), "model.base": ("models.zoo", "compat"), "model.block": ("models.block",),
+    "model.config": ("compat", "config"), "model.early_exit": ("models.adapters", "models.transformer"), "model.factory": ("models.factory", "models.zoo"),
+    "model.fp4": ("models.quant_linear", "kernels"), "model.fp8": ("models.quant_linear", "kernels"), "model.jev": ("models.jev",),
+    "model.manifold_embedding": ("models.manifold_embedding",), "model.norms": ("models.norms",), "model.rotary": ("compat", "models.rotary"),
+    "model.speculative": ("models.speculative",), "model.transmuter": ("models.transmuter",), "model.vectorised_gla": ("models.attention",),
+    "model.zoo": ("models.zoo",), "modules.manager": ("compat", "execution.studio"), "modules.github_client": ("compat",),
+    "modules.curated.custom_loss_nodes.custom_loss_nodes": ("compat", "execution.studio"),
+    "ops._c_bridge": ("compat", "ops._c_bridge"), "ops.centroid_steer": ("compat", "ops"), "ops.gla": ("compat", "ops", "kernels"), "ops.muon": ("compat", "ops"),
+    "ops.norm": ("compat", "ops"), "ops.router": ("compat", "ops"), "ops.swiglu": ("compat", "ops"),
+    "optim.factory": ("optim.factory",), "optim.manifold": ("optim.manifold",),
+    "plugins.node_schema": ("compat", "execution.studio", "execution.dag"), "plugins.registry": ("compat", "execution.dag", "plugins.registry"),
+    "recipes.bf16": ("recipes",), "recipes.fp8": ("recipes",), "recipes.mxfp8": ("recipes",), "recipes.nvfp4": ("recipes",),
+    "runtime.capabilities": ("runtime.capabilities",), "runtime.cuda_graph": ("runtime.cuda_graph",), "runtime.disk_streaming": ("runtime.disk_streaming", "compat"),
+    "runtime.memory_planner": ("compat", "runtime.memory_planner"), "runtime.neuron_scope": ("runtime.neuron_scope",),
+    "runtime.parallel_engine": ("runtime.parallel_engine",), "runtime.resource_manager": ("runtime.resource_manager",), "runtime.staging": ("runtime.staging",),
+    "runtime.vram": ("runtime.vram",), "trainer.callbacks": ("trainer.callbacks", "callbacks.base"), "trainer.distributed": ("compat", "parallel.dist"),
+    "trainer.evaluation": ("trainer.evaluation",), "trainer.logger": ("trainer.logger",), "trainer.scheduler": ("trainer.scheduler",),
+    "trainer.trainer": ("trainer.trainer",), "universal": ("compat", "models.universal"), "utils.device": ("compat", "utils"), "utils.seed": ("compat", "utils"),
+}
+# names of the reference's top-level package that are not simply a name of one of its sub-packages
+_ROOT: Dict[str, str] = {"__version__": "compat:__version__", "Model": "models.factory:build_model", "Config": "config:build_config",
+                         "CentroidSteer": "optim.centroid:CentroidSteerOptimizer", "UniversalDenseTransformer": "models.universal:UniversalDenseTransformer",
+                         "UniversalMoETransformer": "models.universal:UniversalMoETransformer", "TriuneUniversalEngine": "models.universal:TriuneUniversalEngine",
+                         "upgrade_model": "models.universal:upgrade_model", "upgrade": "models.universal:upgrade_model"}
+# names that modules aliased one-to-one (``_MODULE_ALIASES``) lack here but the reference's module has
+_ALIAS_FALLBACKS: Dict[str, Tuple[str, ...]] = {
+    "api.routes": ("compat", "serve.routes_shell", "serve.engine_state"), "api.server": ("compat",), "inference": ("compat",), "cli": ("compat",),
+    "packaging": ("compat",), "optim.centroid": ("compat", "optim.subspace"), "trainer.checkpoint": ("compat",), "runtime.model_scanner": ("compat",),
+    "runtime.gguf_loader": ("compat",), "model.attention": ("compat", "ops.reference"), "model.moe": ("compat",), "model.transformer": ("compat",),
+    "trainer.engine": ("compat",), "trainer.finetune": ("compat",), "runtime.streaming": ("compat", "runtime.staging"), "data.dynamic_tokenizer": ("compat",),
+    "model.router": ("compat",), "optim.muon": ("compat",), "desktop": ("compat",), "profiling": ("compat",),
+}
+
 _PKG = __name__.rsplit(".", 1)[0]
 
 
@@ -138,6 +181,11 @@ class _Lazy(types.ModuleType):
     def __getattr__(self, name: str) -> Any:
         table = self.__dict__["_table"]
         if name not in table:
+            for other in self.__dict__.get("_also", ()):  # the top-level package re-exports names of its sub-packages
+                if name in other.__dict__["_table"]:
+                    val = getattr(other, name)
+                    setattr(self, name, val)
+                    return val
             raise AttributeError(f"module {self.__name__!r} has no attribute {name!r}")
         try:
             val = _resolve(table[name])
@@ -150,6 +198,48 @@ class _Lazy(types.ModuleType):
         return sorted(set(self.__dict__["_table"]) | set(super().__dir__()))
 
 
+def _search(mods: Tuple[str, ...], name: str) -> Any:
+    """``name`` from the first of ``mods`` (modules of this framework; "compat" is this one) that has it."""
+    if name.startswith("__") and name.endswith("__"):
+        raise AttributeError(name)
+    for m in mods:
+        try:
+            mod = sys.modules[__name__] if m == "compat" else importlib.import_module(f"{_PKG}.{m}")
+        except ImportError:
+            continue
+        if name in vars(mod):
+            return vars(mod)[name]
+    raise AttributeError(name)
+
+
+class _Deep(types.ModuleType):
+    """A module path of the reference whose names are spread over one or more modules here."""
+
+    def __init__(self, name: str, mods: Tuple[str, ...]):
+        super().__init__(name, f"{name}: looked up in {', '.join(mods)} of {_PKG}")
+        self.__dict__["_mods"] = mods
+        self.__path__ = []
+
+    def __getattr__(self, name: str) -> Any:
+        try:
+            val = _search(self.__dict__["_mods"], name)
+        except AttributeError:
+            val, found = None, False
+            parent = self.__name__
+            while "." in parent and not found:  # a name the enclosing package exports lives in one of its modules
+                parent = parent.rpartition(".")[0]
+                pm = sys.modules.get(parent)
+                if isinstance(pm, _Lazy) and name in pm.__dict__["_table"]:
+                    val, found = getattr(pm, name), True
+            if not found:
+                raise AttributeError(f"module {self.__name__!r} has no attribute {name!r}") from None
+        setattr(self, name, val)
+        return val
+
+
+_PATCHED: List[types.ModuleType] = []  # modules of this framework that were given a fallback ``__getattr__`` by install()
+
+
 def install(name: str = "triune", force: bool = False) -> types.ModuleType:
     """Register the alias package in ``sys.modules`` and return it. Idempotent; refuses to shadow a real package of that
     name that is already imported unless ``force``."""
@@ -158,12 +248,15 @@ def install(name: str = "triune", force: bool = False) -> types.ModuleType:
         raise RuntimeError(f"a real package named {name!r} is already imported; not shadowing it")
     if isinstance(cur, _Lazy):
         return cur
-    root = _Lazy(name, {"__version__": "compat:__version__"}, f"{name}: import paths of the reference, served by {_PKG}")
+    root = _Lazy(name, dict(_ROOT), f"{name}: import paths of the reference, served by {_PKG}")
     sys.modules[name] = root
+    subs = []
     for pkg in _SAME:
         sub = _Lazy(f"{name}.{pkg}", _names_of(pkg), f"{name}.{pkg} on {_PKG}")
         sys.modules[f"{name}.{pkg}"] = sub
         setattr(root, pkg, sub)
+        subs.append(sub)
+    root.__dict__["_also"] = subs
     for ref_mod, ours in _MODULE_ALIASES.items():
         full = f"{name}.{ref_mod}"
         if full in sys.modules:
@@ -176,7 +269,37 @@ def install(name: str = "triune", force: bool = False) -> types.ModuleType:
                 sys.modules[parent].__dict__.setdefault(leaf, target)
         elif parent == name:
             setattr(root, leaf, target)
+        extra = _ALIAS_FALLBACKS.get(ref_mod)
+        if extra and ours != "compat" and "__getattr__" not in vars(target):
+            target.__getattr__ = (lambda mods, modname: lambda attr: _fallback(mods, modname, attr))(extra, target.__name__)
+            _PATCHED.append(target)
+    for ref_mod, mods in _DEEP.items():
+        full = f"{name}.{ref_mod}"
+        if full in sys.modules:
+            continue
+        parts = ref_mod.split(".")
+        for k in range(1, len(parts)):  # intermediate packages the reference has but nothing is imported from
+            mid = f"{name}.{'.'.join(parts[:k])}"
+            if mid not in sys.modules:
+                sys.modules[mid] = _Deep(mid, ())
+                setattr(sys.modules[mid.rpartition('.')[0]], parts[k - 1], sys.modules[mid])
+        mod = _Deep(full, mods)
+        sys.modules[full] = mod
+        parent, _, leaf = full.rpartition(".")
+        par = sys.modules[parent]
+        if isinstance(par, _Lazy):
+            if leaf not in par.__dict__["_table"]:
+                par.__dict__.setdefault(leaf, mod)
+        elif leaf not in vars(par):
+            setattr(par, leaf, mod)
     return root
+
+
+def _fallback(mods: Tuple[str, ...], modname: str, attr: str) -> Any:
+    try:
+        return _search(mods, attr)
+    except AttributeError:
+        raise AttributeError(f"module {modname!r} has no attribute {attr!r}") from None
 
 
 def uninstall(name: str = "triune") -> None:
@@ -185,6 +308,8 @@ def uninstall(name: str = "triune") -> None:
         return
     for k in [k for k in sys.modules if k == name or k.startswith(name + ".")]:
         del sys.modules[k]
+    while _PATCHED:
+        vars(_PATCHED.pop()).pop("__getattr__", None)
 
 
 def coverage() -> Dict[str, Dict[str, Any]]:

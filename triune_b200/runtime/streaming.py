@@ -38,6 +38,19 @@ class StreamingConfig:
     activation_checkpointing: bool = True
     forward_snapshots: bool = True
     grad_dtype: str = "fp32"  # "bf16": gradients leave the device (and return for the update) in bf16: half the traffic
+    layers_path: Optional[str] = None  # dotted path of the layer stack when discovery cannot decide
+    fp4_weights: bool = False  # accepted for configuration files of the reference; weights stage as FP8 or in full precision
+    capture_forward_snapshots: Optional[bool] = None  # the reference's name of ``forward_snapshots``
+
+    def __post_init__(self):
+        if self.capture_forward_snapshots is not None:
+            self.forward_snapshots = bool(self.capture_forward_snapshots)
+        self.capture_forward_snapshots = self.forward_snapshots
+
+
+class LayerDiscoveryError(ValueError, AttributeError):
+    """No single stack of layers could be named (a ``ValueError`` as in the reference; also an ``AttributeError``, which
+    is what a missing dotted path is)."""
 
 
 def _round_up(n: int, m: int) -> int:
@@ -149,20 +162,22 @@ def find_layer_list(model: nn.Module, layers_attr: Optional[str] = None) -> nn.M
     if layers_attr:
         found = walk(layers_attr)
         if found is None:
-            raise AttributeError(f"model has no layer list at '{layers_attr}'")
+            raise LayerDiscoveryError(f"Specified layers_path '{layers_attr}' does not name a non-empty layer list of the model")
         return found
     for path in _LAYER_PATHS:
         found = walk(path)
         if found is not None:
             return found
-    best = None
-    for m in model.modules():
-        if isinstance(m, nn.ModuleList) and len(m) > 1 and len({type(c) for c in m}) == 1:
-            if best is None or len(m) > len(best):
-                best = m
-    if best is None:
-        raise AttributeError("no stack of repeated layers found; pass layers_attr")
-    return best
+    stacks = [(n, m) for n, m in model.named_modules()
+              if isinstance(m, nn.ModuleList) and len(m) > 1 and len({type(c) for c in m}) == 1]
+    if not stacks:
+        raise LayerDiscoveryError("no stack of repeated layers found; pass layers_path")
+    longest = max(len(m) for _, m in stacks)
+    top = [(n, m) for n, m in stacks if len(m) == longest]
+    if len(top) > 1:
+        raise LayerDiscoveryError(f"Ambiguous layer discovery: {[n for n, _ in top]} all hold {longest} layers; "
+                                  "name the stack to stream with layers_path")
+    return top[0][1]
 
 
 class LayerStreamingEngine:
@@ -170,7 +185,7 @@ class LayerStreamingEngine:
                  optimizer=None, layers_path: Optional[str] = None):
         # ``optimizer`` / ``layers_path``: keywords of the reference's constructor (``triune/runtime/streaming.py``). A tiered
         # optimizer given here updates the streamed layers through ``step_parameters`` once the engine is attached.
-        layers_attr = layers_attr or layers_path
+        layers_attr = layers_attr or layers_path or (config.layers_path if config is not None else None)
         self._ctor_optimizer = optimizer
         self.model = model
         self.device = torch.device(device)
@@ -190,6 +205,17 @@ class LayerStreamingEngine:
         self.opt_state: Dict[int, Dict[str, torch.Tensor]] = {}
         self.step_count = 0
         self.layer_optimizer = None  # StreamedLayerOptimizer: tiered updates of the streamed layers
+
+    def _chunk_for_layer_idx(self, idx: int):
+        """(window number, first layer, last layer) of the staging window that holds layer ``idx``; windows are
+        ``chunk_size`` layers wide (``triune/runtime/streaming.py:215-220`` of the reference)."""
+        w = max(1, int(self.cfg.chunk_size))
+        c = idx // w
+        return c, c * w, min(len(self.layers), (c + 1) * w) - 1
+
+    def _resolve_layers(self) -> List[nn.Module]:
+        """The layer stack this engine streams (the reference's name of the discovery step)."""
+        return list(self.layers)
 
     def enable_tiered_optimizer(self, make_optimizer=None, state_dtype: torch.dtype = torch.float32, **optimizer_kwargs):
         """Update streamed layers with the tiered optimizer (AdamW / Muon / CentroidSteer through
@@ -371,6 +397,11 @@ class LayerStreamingEngine:
         self._staged[i] = self._staged.get(i, 0) + 1
         self.telemetry["peak_staged_layers"] = max(self.telemetry["peak_staged_layers"],
                                                    sum(1 for s in self.stores.values() if s.device_buf is not None))
+        c, lo, hi = self._chunk_for_layer_idx(i)
+        ahead = range(i + 1, hi + 1) if prefetch is None or prefetch >= i else range(lo, i)
+        for j in ahead:  # chunk_size > 1: the rest of this layer's window, in the direction of travel, comes with it
+            if j in self.stores:
+                self._start_copy(j)
         if self.cfg.async_prefetch and prefetch is not None and prefetch in self.stores:
             self._start_copy(prefetch)
 
