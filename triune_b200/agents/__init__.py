@@ -102,6 +102,41 @@ def is_safe_public_url(url: str, resolve: bool = True) -> bool:
         return False
 
 
+LOCAL_SERVICE_PORTS = frozenset({11434, *range(8000, 8021)})  # a local Ollama daemon and this framework's own servers
+
+
+def validate_http_url(url: str, *, allow_local_services: bool = False) -> str:
+    """The raising form of ``is_safe_public_url`` (``triune/agents/tools.py:23-62`` of the reference): returns the cleaned
+    URL, raises ``ValueError`` for anything that is not a plain http(s) URL with a resolvable host and ``PermissionError``
+    when an address it resolves to is not public. ``allow_local_services`` admits loopback on the ports of
+    ``LOCAL_SERVICE_PORTS`` only."""
+    clean = str(url or "").strip()
+    u = urlparse(clean)
+    if u.scheme.lower() not in ("http", "https"):
+        raise ValueError("Only http:// and https:// URLs are permitted.")
+    if u.username or u.password:
+        raise ValueError("URLs that carry user credentials are not permitted.")
+    if not u.hostname:
+        raise ValueError("URL is missing a valid hostname.")
+    port = u.port or (443 if u.scheme.lower() == "https" else 80)
+    try:
+        infos = socket.getaddrinfo(u.hostname, port, type=socket.SOCK_STREAM)
+    except socket.gaierror as e:
+        raise ValueError(f"Unable to resolve hostname '{u.hostname}': {e}") from e
+    if not infos:
+        raise ValueError(f"Hostname '{u.hostname}' resolved to no addresses.")
+    for info in infos:
+        a = ipaddress.ip_address(str(info[4][0]).split("%")[0])
+        if a.is_loopback:
+            if allow_local_services and port in LOCAL_SERVICE_PORTS:
+                continue
+            raise PermissionError(f"SSRF guard blocked loopback access to {u.hostname}:{port}.")
+        if (not a.is_global or a.is_private or a.is_link_local or a.is_reserved or a.is_unspecified or a.is_multicast
+                or any(a in n for n in _GROUP_NETS if n.version == a.version)):
+            raise PermissionError(f"SSRF guard blocked non-public IP {a} for host '{u.hostname}'.")
+    return clean
+
+
 def build_integrated_toolbelt() -> ToolRegistry:
     from ..runtime.sandbox import PythonSandbox
 

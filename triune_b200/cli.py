@@ -855,6 +855,9 @@ def build_parser() -> argparse.ArgumentParser:
     return p
 
 
+build_cli_parser = build_parser  # the reference's name (``triune/cli.py``)
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
     return int(args.fn(args) or 0)

@@ -21,6 +21,7 @@ helpers such as ``rotate_half`` and ``is_main_process``, and the registry / engi
 from __future__ import annotations
 
 import importlib
+import importlib.util
 import os
 import sys
 import types
@@ -209,7 +210,42 @@ def _search(mods: Tuple[str, ...], name: str) -> Any:
             continue
         if name in vars(mod):
             return vars(mod)[name]
+        if m == "compat" and name in _LAZY_VALUES:
+            return _LAZY_VALUES[name]()
     raise AttributeError(name)
+
+
+def _engine_state():
+    from .serve.engine_state import get_state
+
+    return get_state()
+
+
+def _attr(path: str) -> Callable[[], Any]:
+    return lambda: _resolve(path)
+
+
+# names of this module that are objects made (or imported) when first asked for
+_LAZY_VALUES: Dict[str, Callable[[], Any]] = {
+    "pytorch_state": _engine_state, "RealPyTorchEngineState": _attr("serve.engine_state:EngineState"),
+    "ChatCompletionRequest": _attr("serve.routes:ChatRequest"), "FineTuneRequest": _attr("serve.routes:FinetuneRequest"),
+    "ModelLoadRequest": _attr("serve.routes:LoadRequest"), "TrainingConfigRequest": _attr("serve.routes:TrainRequest"),
+    "HAS_FASTAPI": lambda: importlib.util.find_spec("fastapi") is not None,
+    "module_manager": lambda: _shared("module_manager", lambda: ModuleManager()),
+    "AgentSkill": _attr("agents.extras:Skill"), "BUILTIN_PERSONAS": _attr("agents.harness:PERSONAS"), "PersonaProfile": _attr("agents.harness:PersonaSpec"),
+    "ProviderConfig": _attr("agents.extras:Provider"), "IncrementalStreamingDecoder": _attr("inference:IncrementalStreamingDecoder"),
+    "atomic_write_text": _attr("agents.storage:atomic_write_text"), "atomic_write_json": _attr("agents.storage:atomic_write_json"),
+    "load_validated_json_dict": _attr("agents.storage:load_validated_json_dict"), "tokenize_terms": _attr("agents.storage:tokenize_terms"),
+    "compute_tfidf_cosine_scores": _attr("agents.storage:compute_tfidf_cosine_scores"),
+    "seed_everything": _attr("utils:seed_everything"), "device_diagnostic": _attr("utils:device_diagnostic"),
+}
+_SHARED: Dict[str, Any] = {}
+
+
+def _shared(key: str, make: Callable[[], Any]) -> Any:
+    if key not in _SHARED:
+        _SHARED[key] = make()
+    return _SHARED[key]
 
 
 class _Deep(types.ModuleType):

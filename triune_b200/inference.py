@@ -181,6 +181,99 @@ class StreamingDecoder:
         return delta
 
 
+class IncrementalStreamingDecoder:
+    """Detokeniser for streamed generation with the reference's interface (``triune/inference.py:714-745``): ``step``
+    returns (text so far, newly stable text); pieces that end inside a multi-byte character are held back; the window of
+    ids decoded together restarts at white space or after 16 ids so a long reply costs linear, not quadratic, time."""
+
+    def __init__(self, tokenizer, skip_special_tokens: bool = True):
+        self.tokenizer, self.skip_special_tokens = tokenizer, skip_special_tokens
+        self.token_cache: List[int] = []
+        self.print_len = 0
+        self.cumulative_text = ""
+
+    def _decode(self) -> str:
+        try:
+            return self.tokenizer.decode(self.token_cache, skip_special_tokens=self.skip_special_tokens)
+        except TypeError:  # tokenizers of this framework take ids only
+            return self.tokenizer.decode(self.token_cache)
+
+    def step(self, token_id: int) -> Tuple[str, str]:
+        self.token_cache.append(int(token_id))
+        text = self._decode()
+        if text.endswith("\ufffd"):
+            return self.cumulative_text, ""
+        delta = text[self.print_len:]
+        self.cumulative_text += delta
+        if text.endswith((" ", "\n")) or len(self.token_cache) >= 16:
+            self.token_cache, self.print_len = [], 0
+        else:
+            self.print_len = len(text)
+        return self.cumulative_text, delta
+
+    def flush(self) -> Tuple[str, str]:
+        delta = ""
+        if self.token_cache:
+            text = self._decode()
+            delta = text[self.print_len:]
+            self.cumulative_text += delta
+            self.token_cache, self.print_len = [], 0
+        return self.cumulative_text, delta
+
+
+def optimize_hf_model_for_inference(model: torch.nn.Module) -> torch.nn.Module:
+    """Route the RMSNorm modules of a Hugging Face model through this framework's fused kernel while no gradient is being
+    recorded and the module is in eval mode; training keeps the model's own forward. Gemma-family norms, whose weight is
+    an offset from one, are handled. Models under layer streaming are left alone (their weights move between calls).
+    Reference: ``triune/inference.py:31-110``."""
+    from . import ops
+
+    if getattr(model, "_streaming_engine", None) is not None or getattr(model, "_layer_streaming_active", False):
+        return model
+    for mod in model.modules():
+        name = type(mod).__name__.lower()
+        w = getattr(mod, "weight", None)
+        if getattr(mod, "_triune_rms_fused", False) or "rmsnorm" not in name or not isinstance(w, torch.Tensor):
+            continue
+        if w.dim() != 1 or w.numel() == 0 or w.device.type == "meta":
+            continue
+        eps = float(getattr(mod, "eps", getattr(mod, "variance_epsilon", 1e-6)))
+        offset = 1.0 if "gemma" in name else 0.0
+
+        def fused(x, _m=mod, _orig=mod.forward, _eps=eps, _off=offset):
+            if torch.is_grad_enabled() or _m.training:
+                return _orig(x)
+            wt = _m.weight if _off == 0.0 else (_off + _m.weight.float())
+            return ops.rmsnorm(x, wt.to(device=x.device, dtype=x.dtype), _eps)
+
+        mod.forward = fused
+        mod._triune_rms_fused = True
+    return model
+
+
+def release_cuda_graph_runner(model) -> None:
+    """Drop the captured decode graph (and its static cache) that a graphed decoder left on ``model``
+    (``triune/inference.py:304-317`` of the reference)."""
+    if model is None:
+        return
+    for attr in ("_triune_cg_runner", "_graphed_decoder"):
+        runner = getattr(model, attr, None)
+        if runner is None:
+            continue
+        for meth in ("release", "reset"):
+            fn = getattr(runner, meth, None)
+            if callable(fn):
+                try:
+                    fn()
+                except Exception:
+                    pass
+                break
+        try:
+            delattr(model, attr)
+        except AttributeError:
+            setattr(model, attr, None)
+
+
 def generate_response(model, tokenizer, prompt: str, max_new_tokens: int = 256, temperature: float = 0.7, top_k: int = 50,
                       repetition_penalty: float = 1.1, decode_depth: Optional[int] = 2, stop: Tuple[str, ...] = DEFAULT_STOPS,
                       stream_callback: Optional[Callable[[str], None]] = None, cancel_event: Optional[threading.Event] = None,

@@ -214,6 +214,16 @@ class TriuneUniversalEngine:
         return torch.cat(out, dim=1)
 
 
+def _is_silu(act) -> bool:
+    """True when a gated MLP's activation is SiLU (or unnamed, as in this framework's own blocks): only then is the MLP a
+    SwiGLU; GELU-gated MLPs (Gemma) keep their own forward."""
+    if act is None:
+        return True
+    if act is F.silu or isinstance(act, nn.SiLU):
+        return True
+    return type(act).__name__.lower() in ("silu", "siluactivation", "swish")
+
+
 def upgrade_model(model: nn.Module, lora_rank: int = 0, streaming_device=None, attach_optimizer: bool = False, lr: float = 1e-4):
     """Patch a third-party (e.g. Hugging Face) causal LM in place: RMSNorm modules call the fused kernel, SwiGLU
     MLPs call the fused activation, and optionally LoRA adapters / layer streaming / a tiered optimizer are attached.
@@ -221,11 +231,15 @@ def upgrade_model(model: nn.Module, lora_rank: int = 0, streaming_device=None, a
     patched = {"rmsnorm": 0, "swiglu": 0, "lora": 0}
     for mod in model.modules():
         name = mod.__class__.__name__.lower()
-        if "rmsnorm" in name and hasattr(mod, "weight") and not isinstance(mod, RMSNorm):
+        if "rmsnorm" in name and isinstance(getattr(mod, "weight", None), torch.Tensor) and mod.weight.dim() == 1 \
+                and not isinstance(mod, RMSNorm):
             eps = float(getattr(mod, "variance_epsilon", getattr(mod, "eps", 1e-6)))
-            mod.forward = (lambda m, e: (lambda x: ops.rmsnorm(x, m.weight, e)))(mod, eps)
+            if "gemma" in name:  # the Gemma family stores the scale as an offset from one
+                mod.forward = (lambda m, e: (lambda x: ops.rmsnorm(x, (1.0 + m.weight.float()).to(x.dtype), e)))(mod, eps)
+            else:
+                mod.forward = (lambda m, e: (lambda x: ops.rmsnorm(x, m.weight, e)))(mod, eps)
             patched["rmsnorm"] += 1
-        elif all(hasattr(mod, a) for a in ("gate_proj", "up_proj", "down_proj")):
+        elif all(hasattr(mod, a) for a in ("gate_proj", "up_proj", "down_proj")) and _is_silu(getattr(mod, "act_fn", None)):
             mod.forward = (lambda m: (lambda x: m.down_proj(ops.swiglu(m.gate_proj(x), m.up_proj(x)))))(mod)
             patched["swiglu"] += 1
     if lora_rank > 0:

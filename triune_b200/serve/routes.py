@@ -11,6 +11,7 @@ from __future__ import annotations
 import asyncio
 import json
 import queue as _queue
+import re
 import threading
 import time
 import uuid
@@ -27,6 +28,34 @@ router = APIRouter()
 
 
 # ---------------------------------------------------------------------------------------------------- schemas
+HAS_TRIUNE_MODULES = True  # the graph engine, node registry and module manager are part of this package
+
+# UTF-8 bytes that were read as Windows-1252 ("double decoding") turn up in scraped datasets and in the output of models
+# trained on them: a lead character from U+00C2..U+00F4 followed by one to three characters that Windows-1252 maps to
+# 0x80..0xBF. A run is repaired only when its bytes are valid UTF-8 again; typographic punctuation that results is
+# written in ASCII, as the reference does (``triune/api/routes.py:146-172``).
+_CP1252_TAIL = "\u0080-\u00bf\u0152\u0153\u0160\u0161\u0178\u017d\u017e\u0192\u02c6\u02dc\u2013\u2014\u2018-\u201e\u2020-\u2022\u2026\u2030\u2039\u203a\u20ac\u2122"
+_MOJIBAKE_RUN = re.compile(f"[\u00c2-\u00f4][{_CP1252_TAIL}]{{1,3}}")
+_ASCII_PUNCT = {"\u2018": "'", "\u2019": "'", "\u201c": '"', "\u201d": '"', "\u2013": "-", "\u2014": "--", "\u2026": "...", "\u00a0": " "}
+
+
+def _repair_run(m) -> str:
+    try:
+        fixed = m.group(0).encode("cp1252").decode("utf-8")
+    except (UnicodeEncodeError, UnicodeDecodeError):
+        return m.group(0)
+    return "".join(_ASCII_PUNCT.get(ch, ch) for ch in fixed)
+
+
+def sanitize_text(text: str) -> str:
+    """Repair double-decoded text and drop replacement characters; anything that is not a non-empty string gives ``""``."""
+    if not text or not isinstance(text, str):
+        return ""
+    text = _MOJIBAKE_RUN.sub(_repair_run, text)
+    text = text.replace("\u00e2\u20ac", '"')  # a closing quote whose last byte (0x9D) has no Windows-1252 character and was lost
+    return text.replace("\ufffd", "")
+
+
 class ChatMessage(BaseModel):
     role: str = "user"
     content: str = ""

@@ -9,6 +9,7 @@ start without that token and TLS certificate + key files; the single-page Studio
 from __future__ import annotations
 
 import hmac
+from contextlib import asynccontextmanager
 import ipaddress
 import os
 from pathlib import Path
@@ -26,13 +27,26 @@ def _is_loopback(host: Optional[str]) -> bool:
         return False
 
 
+@asynccontextmanager
+async def lifespan(app):
+    """Nothing to start (models load on request); on shutdown a training run that is still going is asked to stop and
+    joined, so that the process does not exit with the trainer half-way through a checkpoint."""
+    yield
+    from .engine_state import get_state
+
+    state = get_state()
+    if state.train_status.get("running"):
+        state.stop_training()
+
+
 def create_app(static_dir: Optional[str] = None):
     import fastapi
     from fastapi.responses import FileResponse, JSONResponse
 
     from .routes import router
 
-    app = fastapi.FastAPI(title="Triune B200 server", description="Serving, training control and telemetry API", version="1.0.0")
+    app = fastapi.FastAPI(title="Triune B200 server", description="Serving, training control and telemetry API", version="1.0.0",
+                          lifespan=lifespan)
 
     @app.get("/healthz", include_in_schema=False)
     async def healthz():
