@@ -123,7 +123,7 @@ _DEEP: Dict[str, Tuple[str, ...]] = {
     "model.manifold_embedding": ("models.manifold_embedding",), "model.norms": ("models.norms",), "model.rotary": ("compat", "models.rotary"),
     "model.speculative": ("models.speculative",), "model.transmuter": ("models.transmuter",), "model.vectorised_gla": ("models.attention",),
     "model.zoo": ("models.zoo",), "modules.manager": ("compat", "execution.studio"), "modules.github_client": ("compat",),
-    "modules.curated.custom_loss_nodes.custom_loss_nodes": ("compat", "execution.studio"),
+    "modules.curated.custom_loss_nodes.custom_loss_nodes": ("plugins.curated.custom_loss_nodes.custom_loss_nodes",),
     "ops._c_bridge": ("compat", "ops._c_bridge"), "ops.centroid_steer": ("compat", "ops"), "ops.gla": ("compat", "ops", "kernels"), "ops.muon": ("compat", "ops"),
     "ops.norm": ("compat", "ops"), "ops.router": ("compat", "ops"), "ops.swiglu": ("compat", "ops"),
     "optim.factory": ("optim.factory",), "optim.manifold": ("optim.manifold",),
@@ -487,6 +487,19 @@ def batched_subspace_projection(grads: torch.Tensor, rank: int, niter: int = 2, 
     Q = _bsp(grads, rank, power_iters=max(0, int(niter) - 1))
     path = "batched_scholqr2"
     return (Q, path, []) if return_diagnostics else (Q, path)
+
+
+def fast_subspace_projection(grad: torch.Tensor, rank: int, niter: int = 2, cond_threshold: float = 1e4, eps_shift: float = 1e-7,
+                            orth_tol: float = 1e-4) -> Tuple[torch.Tensor, str]:
+    """-> (orthonormal basis of the dominant subspace on the short side of ``grad``, "left" or "right")."""
+    m, n = grad.shape
+    return subspace_projection(grad, rank, niter, cond_threshold, eps_shift, orth_tol), ("left" if m <= n else "right")
+
+
+def polar_stiefel_retraction(P: torch.Tensor, eps: float = 1e-7) -> torch.Tensor:
+    """``P [.., d, r]`` with its columns made orthonormal again (Cholesky QR with its condition check and Householder
+    fall-back); the span is kept."""
+    return batched_qr(P.float(), eps_shift=eps).to(P.dtype)
 
 
 def all_reduce_dict(metrics: Dict[str, float], op: Any = None) -> Dict[str, float]:
@@ -913,7 +926,16 @@ class ModuleManager:
         import shutil
         from pathlib import Path
 
-        src = Path(str(req.get("path") or req.get("url") or req.get("source") or "")).expanduser()
+        origin = str(req.get("download_url") or req.get("path") or req.get("url") or req.get("source") or "")
+        if origin.startswith("builtin://") or (not origin and req.get("id")):  # a module that ships with the framework
+            from .plugins.curated import curated_path
+
+            try:
+                origin = str(curated_path(origin[len("builtin://"):] if origin else str(req["id"])))
+            except KeyError:
+                return {"status": "error", "message": f"no curated module named {origin or req.get('id')!r}"}
+            req = {**req, "name": req.get("name") or Path(origin).name}
+        src = Path(origin).expanduser()
         if "://" in str(src) or not src.is_dir():
             return {"status": "error", "message": "only local module directories can be installed (no network access)"}
         name = str(req.get("name") or src.name)
@@ -982,8 +1004,15 @@ class ModuleManager:
 
         return probe_machine().to_dict()
 
-    def search_marketplace(self, query: str = "") -> Dict[str, Any]:
-        return {"results": [], "note": "remote catalogues need network access, which this framework does not use"}
+    def search_marketplace(self, query: str = "", source: str = "all") -> Dict[str, Any]:
+        """The curated modules that match ``query`` (they install offline from ``builtin://<id>``); remote catalogues are
+        not contacted."""
+        from .plugins.curated import CURATED
+
+        q = (query or "").lower()
+        hits = [dict(c, source="curated") for c in CURATED if not q or q in (c["id"] + " " + c["name"] + " " + c["description"]).lower()]
+        return {"results": hits, "curated": hits, "github": [], "huggingface": [],
+                "note": "remote catalogues need network access, which this framework does not use"}
 
     def check_updates(self) -> Dict[str, Any]:
         return {"updates": [], "note": "remote catalogues need network access, which this framework does not use"}

@@ -13,8 +13,10 @@ benchmark "90.8M-class" shape (E=8, top-2, hidden 1536).
 
 from __future__ import annotations
 
+import contextlib
 import json
 import math
+import threading
 from dataclasses import asdict, dataclass, field, fields
 from typing import Any, Dict, Optional, Tuple
 
@@ -61,6 +63,39 @@ MUON_MOMENTUM = 0.95
 MUON_WEIGHT_DECAY = 0.01
 NS_COEFFS = (1.875, -1.25, 0.375)
 NS_STEPS = 3
+# defaults of the research training script of the reference (``triune/model/config.py``), under its names
+USE_GLA, USE_ROPE, ROUTER_NOISE_STD = True, True, 0.0
+GALORE, USE_TRIANGULAR_CORE, USE_8BIT_BASE, USE_MUON = True, True, False, True
+BATCH_SIZE, GRAD_ACCUM_STEPS, SEQ_LEN, TOTAL_STEPS = 8, 4, 256, 50_000
+LR, MIN_LR, WARMUP_STEPS, BETAS, WEIGHT_DECAY, GRAD_CLIP = 1e-4, 1e-6, 500, (0.9, 0.95), 0.05, 1.0
+GRAD_CHECKPOINT, SHUFFLE_BUFFER = True, 4096
+LOG_EVERY, SAVE_EVERY, EVAL_EVERY, EVAL_BATCHES, CHECKPOINT_DIR = 10, 1000, 200, 5, "checkpoints_full"
+
+_recompute_state = threading.local()
+
+
+@contextlib.contextmanager
+def checkpoint_fwd_ctx():
+    """Context of the first pass through an activation-checkpointed region (nothing to mark)."""
+    yield
+
+
+@contextlib.contextmanager
+def checkpoint_bwd_ctx():
+    """Context of the recomputation pass: ``is_checkpoint_recomputing()`` is true inside, per thread, so that code with
+    side effects (running statistics, counters) can skip them the second time. Usable as the second half of
+    ``torch.utils.checkpoint.checkpoint(..., context_fn=lambda: (checkpoint_fwd_ctx(), checkpoint_bwd_ctx()))``; the
+    blocks of this framework enter it around their own recomputation."""
+    old = getattr(_recompute_state, "on", False)
+    _recompute_state.on = True
+    try:
+        yield
+    finally:
+        _recompute_state.on = old
+
+
+def is_checkpoint_recomputing() -> bool:
+    return getattr(_recompute_state, "on", False)
 
 
 @dataclass

@@ -23,6 +23,7 @@ import math
 import os
 import time
 from dataclasses import dataclass, field
+from enum import Enum
 from pathlib import Path
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
@@ -33,7 +34,10 @@ MAX_SUBGRAPH_DEPTH = 8
 # port types of the catalogue (``triune/plugins/node_schema.py:14-26``)
 TENSOR, TEXT, STREAM, MODEL, OPT, LOSS, TUPLE, METRICS, FILE, ANY = (
     "tensor", "text", "dataset_stream", "model_handle", "optimizer_handle", "loss", "tensor_tuple", "metrics", "file", "any")
-_COMPATIBLE = {(LOSS, TENSOR), (TENSOR, LOSS), (METRICS, ANY), (TUPLE, TENSOR)}
+CONFIG = "config"
+# (source type, target type) pairs that may be wired although the types differ: a dataset stream yields text samples, a
+# loss is a scalar tensor and a metric, tensors feed losses and metrics, a tuple of tensors stands in for its first member
+_COMPATIBLE = {(STREAM, TEXT), (LOSS, TENSOR), (LOSS, METRICS), (TENSOR, LOSS), (TENSOR, METRICS), (TUPLE, TENSOR)}
 
 
 class StudioGraphError(ValueError):
@@ -71,6 +75,75 @@ def studio_node(name: str, category: str, inputs: Dict[str, str], outputs: Dict[
 
 def ports_compatible(a: str, b: str) -> bool:
     return a == b or ANY in (a, b) or (a, b) in _COMPATIBLE
+
+
+class PortType(str, Enum):
+    """Port types under the reference's enumeration names (``triune/plugins/node_schema.py``)."""
+
+    TEXT = TEXT
+    TENSOR = TENSOR
+    TENSOR_TUPLE = TUPLE
+    DATASET_STREAM = STREAM
+    MODEL_HANDLE = MODEL
+    OPTIMIZER_HANDLE = OPT
+    LOSS = LOSS
+    METRICS = METRICS
+    CONFIG = CONFIG
+    FILE = FILE
+    ANY = ANY
+
+
+class NodeExecutionType(str, Enum):
+    EXECUTION = "execution"  # runs tensor work
+    SPECIFICATION = "specification"  # only describes (hyper-parameters, blueprints, provider settings)
+
+
+def is_port_compatible(source_type: Any, target_type: Any) -> bool:
+    """``ports_compatible`` for enumeration members or strings in any case."""
+    a = str(getattr(source_type, "value", source_type)).lower()
+    b = str(getattr(target_type, "value", target_type)).lower()
+    return ports_compatible(a, b)
+
+
+@dataclass
+class Port:
+    name: str
+    type: str = ANY
+    description: str = ""
+    required: bool = True
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"name": self.name, "type": str(getattr(self.type, "value", self.type)), "description": self.description,
+                "required": self.required}
+
+
+@dataclass
+class NodeSchema:
+    """Declarative description of a node kind, as the canvas and validators exchange it."""
+
+    id: str
+    name: str
+    category: str
+    execution_type: str = NodeExecutionType.EXECUTION.value
+    inputs: List[Port] = field(default_factory=list)
+    outputs: List[Port] = field(default_factory=list)
+    config_params: Dict[str, Any] = field(default_factory=dict)
+    description: str = ""
+    requires_cuda: bool = False
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"id": self.id, "name": self.name, "category": self.category,
+                "execution_type": str(getattr(self.execution_type, "value", self.execution_type)),
+                "inputs": [p.to_dict() for p in self.inputs], "outputs": [p.to_dict() for p in self.outputs],
+                "config_params": dict(self.config_params), "description": self.description, "requires_cuda": self.requires_cuda}
+
+
+def node_schema(kind: str) -> NodeSchema:
+    """The ``NodeSchema`` of a catalogue entry."""
+    n = STUDIO_NODES[kind]
+    return NodeSchema(id=n.name, name=n.name, category=n.category,
+                      inputs=[Port(k, t) for k, t in n.inputs.items()], outputs=[Port(k, t, required=False) for k, t in n.outputs.items()],
+                      config_params=dict(n.parameters), description=n.description)
 
 
 def is_studio_graph(spec: Any) -> bool:

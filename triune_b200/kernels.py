@@ -171,6 +171,62 @@ def fast_zeropower_via_newtonschulz5(G: torch.Tensor, steps: int = 5, eps: float
     return (X, scratch_buffer) if return_scratch else X
 
 
+NS5_COEFFS = (1.875, -1.25, 0.375)  # quintic Newton-Schulz polynomial X <- aX + b(XX^T)X + c(XX^T)^2 X
+NVFP4_GROUP_SIZE = 16  # elements per E4M3 block scale
+HAS_TRITON = False  # no kernel of this framework goes through Triton; the name answers scripts that ask
+
+
+def compute_muon_update_scale(d_out: int, d_in: int, rms_target: Optional[float] = None) -> float:
+    """Scale of an orthogonalised update so that its per-element size does not depend on the matrix's aspect ratio:
+    sqrt(max(1, d_out / d_in)), times ``rms_target`` when one is given (``triune/kernels/fast_muon.py:8-12``)."""
+    aspect = max(1.0, float(d_out) / float(d_in)) ** 0.5
+    return aspect * float(rms_target) if rms_target is not None and rms_target > 0 else aspect
+
+
+def fast_zeropower_via_newtonschulz5_batched(G_batch: torch.Tensor, steps: int = 5, eps: float = 1e-7, scratch_buffer=None,
+                                             return_scratch: bool = False):
+    """``fast_zeropower_via_newtonschulz5`` for a stack ``[B, m, n]`` (one launch per Newton-Schulz step for the whole
+    stack on the GPU)."""
+    if G_batch.ndim != 3:
+        raise ValueError(f"Batched orthogonalization requires 3D tensor [B, M, N], got ndim={G_batch.ndim}")
+    X = ops.muon_ns(G_batch, steps)
+    return (X, scratch_buffer) if return_scratch else X
+
+
+def fast_triangular_adamw(R_batch: torch.Tensor, batch_mom: torch.Tensor, batch_var: torch.Tensor, batch_delta: torch.Tensor,
+                          step_vals: torch.Tensor, beta1: float, beta2: float, eps: float = 1e-8, mask_mode: str = "triu") -> torch.Tensor:
+    """Adam direction of a stack of small core matrices ``[N, DR, DR]``: moments updated in place, the bias-corrected
+    direction written to ``batch_delta``; ``mask_mode="triu"`` zeroes the direction below the diagonal, ``"full"`` keeps
+    it dense. ``step_vals`` holds one step count per matrix. Where all counts agree and the stack is fp32 on the GPU the
+    fused kernel of the optimizer runs; otherwise the same arithmetic in PyTorch
+    (``triune/kernels/fast_triangular.py:91-170`` of the reference)."""
+    if mask_mode not in ("triu", "full"):
+        raise ValueError(f"Unknown mask_mode={mask_mode!r}; expected 'triu' or 'full'")
+    N = R_batch.shape[0]
+    steps = step_vals.reshape(-1)
+    if steps.numel() == 1 and N > 1:
+        steps = steps.expand(N)
+    if (_ext.use_kernels(R_batch) and mask_mode == "full" and R_batch.dtype == torch.float32 and R_batch.is_contiguous()
+            and batch_mom.dtype == torch.float32 and batch_var.dtype == torch.float32 and batch_mom.is_contiguous()
+            and batch_var.is_contiguous() and N > 0 and bool((steps == steps[0]).all())):
+        # the kernel masks its INPUT when asked for a triangle (moments of the lower part stay zero); the reference keeps
+        # dense moments and masks the direction only, so only the dense mode maps onto it one to one
+        delta = _ext.ext().triangular_adamw(R_batch, batch_mom, batch_var, beta1, beta2, eps, int(steps[0]), False, None)
+        batch_delta.copy_(delta)
+        return batch_delta
+    R = R_batch.float()
+    batch_mom.lerp_(R, 1.0 - beta1)
+    batch_var.mul_(beta2).addcmul_(R, R, value=1.0 - beta2)
+    t = steps.to(torch.float32).view(N, 1, 1)
+    c1 = 1.0 - beta1 ** t
+    c2 = (1.0 - beta2 ** t).clamp_min(1e-7)
+    delta = (batch_mom / c1) / ((batch_var / c2).sqrt() + eps)
+    if mask_mode == "triu":
+        delta = delta.triu()
+    batch_delta.copy_(delta)
+    return batch_delta
+
+
 def fast_lora_forward(x: torch.Tensor, lora_A: torch.Tensor, lora_B: torch.Tensor, scaling: float = 2.0) -> torch.Tensor:
     """scaling * (x A^T) B^T with A [r, in], B [out, r]."""
     return ops.linear(ops.linear(x, lora_A), lora_B, alpha=float(scaling))

@@ -15,7 +15,7 @@ import torch.nn as nn
 import torch.utils.checkpoint
 
 from .. import ops
-from ..config import NUM_EXPERTS, TOP_K_EXPERTS
+from ..config import NUM_EXPERTS, TOP_K_EXPERTS, checkpoint_bwd_ctx
 from .attention import HybridAttention
 from .moe import MoE_FFN
 from .norms import RMSNorm
@@ -94,7 +94,10 @@ class TransformerBlock(nn.Module):
             def run(t):
                 first = calls["n"] == 0
                 calls["n"] += 1
-                return self._body(t, None, update_stats and first)
+                if first:
+                    return self._body(t, None, update_stats)
+                with checkpoint_bwd_ctx():  # user modules inside the block can ask is_checkpoint_recomputing()
+                    return self._body(t, None, False)
 
             x, new_cache = torch.utils.checkpoint.checkpoint(run, x, use_reentrant=False)
         else:

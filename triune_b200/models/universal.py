@@ -52,6 +52,56 @@ class SwiGLUFFN(nn.Module):
         return ops.swiglu_mlp(x, self.gate_up, self.down.weight)
 
 
+class DenseAttention(nn.Module):
+    """A stand-alone attention layer with the reference's constructor (``triune/universal.py:147-268``): grouped-query
+    softmax attention, or gated linear attention when ``use_gla``. ``forward(x, state) -> (out, new_state)`` where the
+    state is the key/value cache or the GLA recurrent state."""
+
+    def __init__(self, dim: int, num_heads: int, head_dim: Optional[int] = None, num_kv_heads: Optional[int] = None,
+                 use_gla: bool = False):
+        super().__init__()
+        self.dim, self.num_heads, self.use_gla = dim, num_heads, use_gla
+        self.head_dim = head_dim or dim // num_heads
+        self.num_kv_heads = num_kv_heads or num_heads
+        self.mixer = (VectorisedGLA(dim, num_heads, self.head_dim) if use_gla
+                      else SoftmaxAttention(dim, num_heads, self.head_dim, self.num_kv_heads))
+
+    def forward(self, x, state=None):
+        return self.mixer(x, cache=state)
+
+
+class DenseMLP(nn.Module):
+    """A stand-alone feed-forward layer (``triune/universal.py:270-315``): SwiGLU (two GEMMs, gate and up as one weight)
+    or GELU. ``hidden_dim`` defaults to four times ``dim``."""
+
+    def __init__(self, dim: int, hidden_dim: Optional[int] = None, act_type: str = "swiglu"):
+        super().__init__()
+        self.act_type = act_type.lower()
+        hidden = hidden_dim or 4 * dim
+        self.ffn = SwiGLUFFN(dim, hidden) if self.act_type == "swiglu" else DenseFFN(dim, hidden)
+
+    def forward(self, x):
+        return self.ffn(x)
+
+
+class DenseTransformerBlock(nn.Module):
+    """Pre-norm block of ``DenseAttention`` and ``DenseMLP`` (``triune/universal.py:317-345``); the residual add and the
+    second norm are one kernel. ``forward(x, state) -> (x, new_state)``."""
+
+    def __init__(self, dim: int, num_heads: int, hidden_dim: Optional[int] = None, num_kv_heads: Optional[int] = None,
+                 use_gla: bool = False):
+        super().__init__()
+        self.norm1 = RMSNorm(dim)
+        self.attn = DenseAttention(dim, num_heads, num_kv_heads=num_kv_heads, use_gla=use_gla)
+        self.norm2 = RMSNorm(dim)
+        self.mlp = DenseMLP(dim, hidden_dim=hidden_dim)
+
+    def forward(self, x, state=None):
+        a, new_state = self.attn(self.norm1(x), state=state)
+        n, x = self.norm2.forward_add(a, x)
+        return x + self.mlp(n), new_state
+
+
 class UniversalBlock(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int):
         super().__init__()

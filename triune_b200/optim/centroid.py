@@ -27,7 +27,7 @@ from __future__ import annotations
 
 import fnmatch
 import math
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Any, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -1000,3 +1000,36 @@ class CentroidSteerOptimizer(torch.optim.Optimizer):
         out["steer_state_bytes_per_param"] = sb / n_steer
         out["adamw_equivalent_bytes"] = out["tiers"]["steer"]["params"] * 8
         return out
+
+
+def profile_rank_sensitivity(model: torch.nn.Module, target_energy: float = 0.85, max_rank: int = 32, min_rank: int = 4) -> Dict[str, Any]:
+    """Offline: for every weight matrix of ``model`` the smallest rank whose leading singular values hold
+    ``target_energy`` of the squared Frobenius norm, clamped to [``min_rank``, ``max_rank``], with the energy that rank
+    captures and the parameter ratio of a rank-k factorisation; totals over the model. Guides the choice of the subspace
+    rank (``triune/optim/centroid.py:1542-1609`` of the reference; the method of the same name on the optimizer measures
+    the live gradients instead)."""
+    layers: Dict[str, Dict[str, Any]] = {}
+    full_bytes = low_bytes = 0
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() < 2:
+                continue
+            w = p.detach().float().reshape(p.shape[0], -1)
+            m, n = w.shape
+            d = min(m, n)
+            try:
+                e = torch.linalg.svdvals(w).square()
+                cum = torch.cumsum(e, 0) / e.sum().clamp_min(1e-12)
+                hit = torch.nonzero(cum >= target_energy)
+                k = int(hit[0]) + 1 if hit.numel() else min(max_rank, d)
+            except RuntimeError:  # the decomposition did not converge: fall back to a quarter of the small side
+                cum, k = torch.ones(d), min(max_rank, max(min_rank, d // 4))
+            k = max(1, min(d, max(min_rank, min(max_rank, k))))
+            layers[name] = {"shape": [m, n], "recommended_rank": k, "captured_energy": round(float(cum[k - 1]), 4),
+                            "compression_ratio": round(m * n / max(1, (m + n) * k), 2)}
+            full_bytes += m * n * p.element_size()
+            low_bytes += (m + n) * k * p.element_size()
+    return {"target_energy": target_energy, "max_rank": max_rank, "min_rank": min_rank, "num_profiled_matrices": len(layers),
+            "total_uncompressed_params": sum(v["shape"][0] * v["shape"][1] for v in layers.values()),
+            "total_low_rank_params": sum(sum(v["shape"]) * v["recommended_rank"] for v in layers.values()),
+            "overall_compression_ratio": round(full_bytes / max(1, low_bytes), 2), "layers": layers}

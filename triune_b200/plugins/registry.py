@@ -47,6 +47,17 @@ def sign_manifest(name: str, version: str, sha256: str, key: str) -> str:
     return hmac.new(key.encode(), f"{name}|{version}|{sha256}".encode(), hashlib.sha256).hexdigest()
 
 
+def _is_curated_copy(info: "PluginInfo") -> bool:
+    """True when the plugin's entry file is byte for byte the one of a module shipped in ``plugins/curated``."""
+    try:
+        from .curated import curated_path
+
+        shipped = curated_path(info.name) / info.entry
+        return shipped.is_file() and hmac.compare_digest(file_sha256(shipped), file_sha256(info.path / info.entry))
+    except (KeyError, OSError):
+        return False
+
+
 class PluginRegistry:
     def __init__(self, key: Optional[str] = None):
         self.key = key if key is not None else os.environ.get("TRIUNE_PLUGIN_KEY") or None
@@ -77,10 +88,18 @@ class PluginRegistry:
     def register_node(self, info: PluginInfo):
         from ..execution import dag
 
+        bare = _is_curated_copy(info)
+
         def reg(name, inputs, outputs, description="", optional=()):
             full = f"{info.name}.{name}"
             info.nodes.append(full)
-            return dag.register_node(full, inputs, outputs, description, optional)
+            deco = dag.register_node(full, inputs, outputs, description, optional)
+            if not bare:
+                return deco
+            # modules that ship with the framework also answer to the plain node name, which is what saved graphs use
+            info.nodes.append(name)
+            plain = dag.register_node(name, inputs, outputs, description, optional)
+            return lambda fn: plain(deco(fn))
 
         return reg
 

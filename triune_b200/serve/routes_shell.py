@@ -262,6 +262,13 @@ async def modules_create_plugin(body: Dict[str, Any]):
 
 def _local_source(src: str) -> Optional[Path]:
     """A module source this server can reach: a local directory or a ``file://`` URL. Remote URLs return None."""
+    if src.startswith("builtin://"):  # a module that ships with the framework
+        from ..plugins.curated import curated_path
+
+        try:
+            return curated_path(src[len("builtin://"):])
+        except KeyError:
+            return None
     if src.startswith("file://"):
         src = src[len("file://"):]
     if "://" in src or src.startswith("git@"):
@@ -281,7 +288,7 @@ async def modules_install(body: Dict[str, Any]):
     import shutil
     import subprocess
 
-    src = str(body.get("url") or body.get("repo_url") or body.get("path") or body.get("source") or "")
+    src = str(body.get("download_url") or body.get("url") or body.get("repo_url") or body.get("path") or body.get("source") or "")
     root = _local_source(src)
     if root is None:
         raise HTTPException(400 if not src else 501, "a module source is required" if not src else _NO_NETWORK)
@@ -344,6 +351,16 @@ async def modules_uninstall(body: Dict[str, Any]):
 
 
 @shell_router.get("/v1/modules/search")
+async def modules_search(q: str = "", source: str = "all"):
+    """The modules that ship with the framework (installable from ``builtin://<id>``) that match ``q``."""
+    from ..plugins.curated import CURATED
+
+    ql = q.lower()
+    hits = [dict(c, source="curated") for c in CURATED if not ql or ql in (c["id"] + " " + c["name"] + " " + c["description"]).lower()]
+    return {"results": hits, "curated": hits, "github": [], "huggingface": [],
+            "note": "remote module catalogues need network access, which this server does not use"}
+
+
 @shell_router.get("/v1/modules/updates")
 async def modules_remote():
     return {"results": [], "note": "remote module catalogues need network access, which this server does not use"}

@@ -68,6 +68,14 @@ def model_fingerprint(config: Dict[str, Any]) -> str:
     return _digest(_canon(config, _MODEL_SPEC))
 
 
+# the reference's names of the same things (``triune/trainer/checkpoint.py:29-76``)
+MODEL_FINGERPRINT_KEYS = {c: list(k) for c, k in _MODEL_SPEC}
+OPTIMIZER_FINGERPRINT_KEYS = {c: list(k) for c, k in _OPTIMIZER_SPEC}
+compute_model_fingerprint = model_fingerprint
+extract_canonical_semantics = canonical_semantics
+compute_checkpoint_fingerprint = fingerprint
+
+
 def safe_torch_load(path, map_location="cpu"):
     """``torch.load(..., weights_only=True)`` and nothing else: a checkpoint path can come from an API request, so a
     file that needs the unrestricted unpickler is refused (the error says which type it wanted). Types that are
