@@ -70,7 +70,12 @@ def cmd_chat(a) -> int:
                           decode_depth=a.depth, stream_callback=lambda s: (sys.stdout.write(s), sys.stdout.flush()),
                           speculative=a.speculative)
         t = out["telemetry"]
-        print(f"\n[{t.get('new_tokens', 0)} tokens, {t.get('decode_tok_s', 0):.1f} tok/s, first token {1e3 * t.get('ttft_s', 0):.0f} ms]")
+        print()
+        from .cli_ui import render_telemetry_bar
+
+        render_telemetry_bar(str(t.get("exit") or t.get("depth") or a.depth or "auto"), tok_sec=float(t.get("decode_tok_s", 0.0)),
+                             ttft_ms=1e3 * float(t.get("ttft_s", 0.0)), tokens=int(t.get("new_tokens", 0)),
+                             latency_ms=1e3 * float(t.get("total_s", 0.0) or 0.0))
     return 0
 
 
@@ -190,10 +195,14 @@ def cmd_export(a) -> int:
 def cmd_models(a) -> int:
     from .models.zoo import CANONICAL_MODEL_SPECS
 
-    print(f"{'preset':<16}{'parameters':>14}{'active':>14}  layers  dim   experts  tier")
+    from .cli_ui import render_table
+
+    rows = []
     for k, s in CANONICAL_MODEL_SPECS.items():
         total, active = s.compute_exact_params()
-        print(f"{k:<16}{total / 1e6:>13.1f}M{active / 1e6:>13.1f}M  {s.num_layers:>6}  {s.hidden_dim:>4}  {s.num_experts:>7}  {s.tier}")
+        rows.append([k, f"{total / 1e6:.1f}M", f"{active / 1e6:.1f}M", s.num_layers, s.hidden_dim, s.num_experts, s.tier])
+    render_table("Model presets", [("preset", "left", "bold cyan"), ("parameters", "right", ""), ("active", "right", ""), ("layers", "right", ""),
+                                   ("dim", "right", ""), ("experts", "right", ""), ("tier", "left", "dim")], rows)
     return 0
 
 
@@ -859,6 +868,13 @@ build_cli_parser = build_parser  # the reference's name (``triune/cli.py``)
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    from . import cli_ui
+
+    cli_ui.ensure_utf8_stdio()
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv in (["-h"], ["--help"], ["help"]):  # the grouped overview; each command's -h lists its options
+        cli_ui.render_help_overview()
+        return 0
     args = build_parser().parse_args(argv)
     return int(args.fn(args) or 0)
 

@@ -122,7 +122,7 @@ _DEEP: Dict[str, Tuple[str, ...]] = {
     "model.fp4": ("models.quant_linear", "kernels"), "model.fp8": ("models.quant_linear", "kernels"), "model.jev": ("models.jev",),
     "model.manifold_embedding": ("models.manifold_embedding",), "model.norms": ("models.norms",), "model.rotary": ("compat", "models.rotary"),
     "model.speculative": ("models.speculative",), "model.transmuter": ("models.transmuter",), "model.vectorised_gla": ("models.attention",),
-    "model.zoo": ("models.zoo",), "modules.manager": ("compat", "execution.studio"), "modules.github_client": ("compat",),
+    "model.zoo": ("models.zoo",), "modules.manager": ("compat", "execution.studio"), "modules.github_client": ("plugins.repo_search",),
     "modules.curated.custom_loss_nodes.custom_loss_nodes": ("plugins.curated.custom_loss_nodes.custom_loss_nodes",),
     "ops._c_bridge": ("compat", "ops._c_bridge"), "ops.centroid_steer": ("compat", "ops"), "ops.gla": ("compat", "ops", "kernels"), "ops.muon": ("compat", "ops"),
     "ops.norm": ("compat", "ops"), "ops.router": ("compat", "ops"), "ops.swiglu": ("compat", "ops"),

@@ -25,6 +25,12 @@ from .tokenizer import SPECIAL_TOKENS, load_tokenizer
 
 CURATED_NGRAMS = (" the", " and", " of", " to", " in", " that", " is", " for", "ing", "tion", "    ", "        ", "\n\n",
                   " return", " self", " import", "def ", "class ", "    return ", " = ", "():", "\n    ")
+# word beginnings and endings of English and of code identifiers, registered (after the n-grams above, so their ids do
+# not move) with and without the space that precedes a prefix or follows a suffix
+COMMON_PREFIXES = ("un", "re", "pre", "dis", "anti", "multi", "inter", "over", "under", "sub", "super", "trans", "non", "semi", "auto", "micro")
+COMMON_SUFFIXES = ("tion", "tions", "ing", "ment", "ments", "able", "ible", "ness", "less", "ful", "ally", "ized", "izes", "ity", "ous", "ive",
+                   "ed", "er", "est", "ly")
+CURATED_NGRAM_PATTERNS = list(CURATED_NGRAMS)  # the reference's name of the first table
 
 
 @dataclass
@@ -80,6 +86,12 @@ class DynamicTokenizer:
                           "registered_ngrams": 0}
         for g in CURATED_NGRAMS:
             self.register_ngram(g)
+        for pre in COMMON_PREFIXES:
+            self.register_ngram(" " + pre)
+            self.register_ngram(pre)
+        for suf in COMMON_SUFFIXES:
+            self.register_ngram(suf + " ")
+            self.register_ngram(suf)
 
     # ------------------------------------------------------------------ base tokenizer access
     def _base_ids(self, text: str) -> List[int]:

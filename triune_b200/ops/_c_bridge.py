@@ -30,6 +30,9 @@ class TriuneStepStats(Structure):
                 ("cuda_runtime_bound", c_int)]
 
 
+TriuneConfigStruct, TriuneStepStatsStruct = TriuneConfig, TriuneStepStats  # the reference's names of the two structures
+
+
 def load_library(path: Optional[str] = None):
     global _lib
     if _lib is not None:

@@ -122,3 +122,10 @@ def build_native_targets(target: str = "all", workspace: Path = WORKSPACE_ROOT, 
         if t in ("all", name):
             res[name] = fn(Path(workspace), base / name if base else None)
     return res
+
+
+# the reference's names of the same builders and of the icon (``triune/packaging.py:20-283``)
+TRIUNE_SVG_ICON = ICON_SVG
+build_linux_native = build_linux_bundle
+build_macos_native = build_macos_bundle
+build_windows_native = build_windows_bundle

@@ -16,6 +16,7 @@ keeps as many decoded layers resident as ``resident_budget_gb`` allows before it
 from __future__ import annotations
 
 import json
+import os
 import re
 import shutil
 import threading
@@ -315,3 +316,141 @@ class DiskNVFP4StreamingEngine:
             out = layer_module(hidden, **layer_kwargs)
             hidden = out[0] if isinstance(out, tuple) else out
         return hidden
+
+
+# ---------------------------------------------------------------------------------------------------- a whole model on top of a cache
+def resolve_hf_model_dir(model_id_or_dir, *, local_files_only: bool = False) -> Path:
+    """The local directory of a Hugging Face model: the argument when it is a directory, else the snapshot of that
+    repository id in the local hub cache. Nothing is downloaded (``triune/runtime/disk_streaming.py:50-78`` of the
+    reference falls through to a download; here a model that is not on disk is a ``FileNotFoundError``)."""
+    p = Path(model_id_or_dir).expanduser()
+    if p.is_dir():
+        return p
+    hub = Path(os.environ.get("HF_HUB_CACHE") or Path(os.environ.get("HF_HOME", Path.home() / ".cache" / "huggingface")) / "hub")
+    snaps = hub / ("models--" + str(model_id_or_dir).replace("/", "--")) / "snapshots"
+    if snaps.is_dir():
+        for snap in sorted(snaps.iterdir(), key=lambda d: d.stat().st_mtime, reverse=True):
+            if any(snap.glob("*.safetensors")) or (snap / "model.safetensors.index.json").is_file():
+                return snap
+    raise FileNotFoundError(f"{model_id_or_dir} is neither a local directory nor a snapshot in {hub} (downloads need network access)")
+
+
+class _RotateIn(nn.Module):
+    """A linear layer whose weight was quantised in the rotated basis: rotate the input the same way (the 16-point
+    Walsh-Hadamard transform of every group of 16 features is its own inverse up to the scale both sides carry)."""
+
+    def __init__(self, inner: nn.Linear):
+        super().__init__()
+        self.inner = inner
+
+    @property
+    def weight(self):
+        return self.inner.weight
+
+    @property
+    def bias(self):
+        return self.inner.bias
+
+    def forward(self, x):
+        from ..ops import reference as ref
+
+        return self.inner(ref.fwht16(x.float()).to(x.dtype))
+
+
+def load_disk_streamed_model(model_or_cache_dir, *, cache_dir=None, device=None, hadamard: bool = True, protect_sensitive: bool = True,
+                             quantize_lm_head: bool = False, activation_checkpointing: bool = True, async_prefetch: bool = True,
+                             pin_memory: bool = False, local_files_only: bool = False):
+    """-> (model, engine, cache directory). A Hugging Face causal LM whose decoder layers exist only as an NVFP4 cache on
+    disk: the model is created without storage, the root tensors (embeddings, final norm, head) are loaded to ``device``,
+    and every decoder layer gets its weights from the ``DiskNVFP4StreamingEngine`` for the duration of its forward pass
+    (decoded to bf16; the next layer is read in the background) and gives them back afterwards, so device memory holds
+    one or two layers at a time. Inference only: the layers' weights are not parameters that an optimizer could update
+    (``activation_checkpointing`` is accepted for the reference's signature). The cache is built first when the argument
+    is a model directory (``triune/runtime/disk_streaming.py:696-800`` of the reference)."""
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    dev = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    cand = Path(model_or_cache_dir).expanduser()
+    if (cand / "manifest.json").is_file():
+        cache = cand
+    else:
+        src = resolve_hf_model_dir(model_or_cache_dir, local_files_only=local_files_only)
+        cache = Path(cache_dir) if cache_dir is not None else default_nvfp4_cache_dir(src, hadamard)
+        build_nvfp4_disk_cache(src, cache, hadamard=hadamard, protect_sensitive=protect_sensitive, quantize_lm_head=quantize_lm_head)
+    engine = DiskNVFP4StreamingEngine(cache, dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
+                                      prefetch=1 if async_prefetch else 0, pin_memory=pin_memory and dev.type == "cuda")
+    man = engine.manifest
+    cfg = AutoConfig.from_pretrained(str(cache))
+    with torch.device("meta"):
+        try:
+            model = AutoModelForCausalLM.from_config(cfg, dtype=engine.dtype)
+        except TypeError:
+            model = AutoModelForCausalLM.from_config(cfg, torch_dtype=engine.dtype)
+    layers = model
+    for part in str(man["layer_prefix"]).split("."):
+        layers = getattr(layers, part)
+    layers = list(layers)
+    for lay in layers:  # the layers never hold storage of their own
+        lay.requires_grad_(False)
+    root = engine.root_state()
+    if man.get("tie_word_embeddings") and "lm_head.weight" not in root:
+        emb = next((v for k, v in root.items() if k.endswith("embed_tokens.weight") or k.endswith("wte.weight")), None)
+        if emb is not None:
+            root["lm_head.weight"] = emb
+    inside = tuple(f"{man['layer_prefix']}.{i}." for i in range(len(layers)))
+    missing = [k for k, v in model.state_dict().items() if v.is_meta and k not in root and not k.startswith(inside)]
+    model.load_state_dict(root, strict=False, assign=True)
+    for name, buf in list(model.named_buffers()):  # rotary tables and the like are computed, not stored: make them again
+        if buf.is_meta:
+            owner = model.get_submodule(name.rpartition(".")[0]) if "." in name else model
+            fresh = type(owner)(config=cfg) if "rotary" in type(owner).__name__.lower() else None
+            if fresh is None:
+                raise RuntimeError(f"buffer {name} has no stored value in the cache and cannot be recomputed")
+            owner.register_buffer(name.rpartition(".")[2], getattr(fresh, name.rpartition(".")[2]).to(dev), persistent=False)
+    if missing:
+        raise RuntimeError(f"the cache holds no value for: {missing[:5]}")
+    rotated = bool(man.get("hadamard"))
+
+    def wrap(i: int, layer: nn.Module):
+        inner_forward = layer.forward
+        qmods = list(man["quantized_modules"][i])
+
+        def forward(*args, **kwargs):
+            state = engine.layer_state(i)
+            held = []
+            for key, value in state.items():
+                owner_name, _, leaf = key.rpartition(".")
+                owner = layer.get_submodule(owner_name) if owner_name else layer
+                if isinstance(owner, _RotateIn):
+                    owner = owner.inner
+                held.append((owner, leaf, owner._parameters.get(leaf), leaf in owner._parameters))
+                if leaf in owner._parameters:
+                    owner._parameters[leaf] = nn.Parameter(value, requires_grad=False)
+                else:
+                    owner._buffers[leaf] = value
+            try:
+                return inner_forward(*args, **kwargs)
+            finally:
+                for owner, leaf, old, is_param in held:
+                    if is_param:
+                        owner._parameters[leaf] = old
+                if engine.budget <= 0:
+                    with engine._lock:
+                        engine._resident.pop(i, None)
+                        engine._resident_bytes = sum(s.get("__nbytes__", 0) for s in engine._resident.values())
+
+        if rotated:
+            for stem in qmods:
+                parent_name, _, leaf = stem.rpartition(".")
+                parent = layer.get_submodule(parent_name) if parent_name else layer
+                lin = getattr(parent, leaf)
+                if isinstance(lin, nn.Linear):
+                    setattr(parent, leaf, _RotateIn(lin))
+        layer.forward = forward
+
+    for i, lay in enumerate(layers):
+        wrap(i, lay)
+    model.eval()
+    model._disk_streaming_engine = engine
+    model._layer_streaming_active = True
+    return model, engine, cache

@@ -342,6 +342,55 @@ def tokenizer_vocab_from_gguf(meta: Dict[str, Any]) -> Dict[str, Any]:
             "chat_template": meta.get("tokenizer.chat_template")}
 
 
+def build_hf_tokenizer_from_gguf(meta: Dict[str, Any]):
+    """A ``PreTrainedTokenizerFast`` rebuilt from the vocabulary a GGUF file carries, token ids preserved: byte-pair
+    encoding when the file stores merges (SentencePiece-style pieces with the U+2581 space marker, or GPT-2 byte-level
+    pieces), a unigram model over the stored scores otherwise. Control tokens (type 3) and the usual chat markers become
+    special tokens; the chat template travels along (``triune/runtime/gguf_loader.py:544-620`` of the reference)."""
+    from tokenizers import AddedToken, Tokenizer, decoders, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    v = tokenizer_vocab_from_gguf(meta)
+    tokens = [str(t) for t in v["tokens"]]
+    if not tokens:
+        raise ValueError("GGUF metadata contains no tokenizer vocabulary.")
+    ids = {t: i for i, t in enumerate(tokens)}
+
+    def named(key: str, default_id: int, fallback: str) -> str:
+        i = meta.get(key)
+        i = default_id if i is None else int(i)
+        return tokens[i] if 0 <= i < len(tokens) else fallback
+
+    bos, eos = named("tokenizer.ggml.bos_token_id", 1, "<s>"), named("tokenizer.ggml.eos_token_id", 2, "</s>")
+    unk = named("tokenizer.ggml.unknown_token_id", 0, "<unk>")
+    pad_id = meta.get("tokenizer.ggml.padding_token_id")
+    pad = tokens[int(pad_id)] if pad_id is not None and 0 <= int(pad_id) < len(tokens) else eos
+    sentencepiece = any(t.startswith("\u2581") for t in tokens[:1000])
+    if v["merges"]:
+        pairs = [tuple(p) for p in (str(m).split(" ") for m in v["merges"]) if len(p) == 2 and p[0] in ids and p[1] in ids]
+        tk = Tokenizer(models.BPE(vocab=ids, merges=pairs, unk_token=unk, ignore_merges=True))
+        if sentencepiece:
+            tk.pre_tokenizer = pre_tokenizers.Metaspace(replacement="\u2581", prepend_scheme="never")
+            tk.decoder = decoders.Sequence([decoders.Replace("\u2581", " "), decoders.ByteFallback()])
+        else:
+            tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+            tk.decoder = decoders.ByteLevel()
+    else:
+        scores = list(v["scores"] or [])
+        table = [(t, float(scores[i]) if i < len(scores) else -10.0) for i, t in enumerate(tokens)]
+        tk = Tokenizer(models.Unigram(table, unk_id=ids.get(unk, 0)))
+        tk.pre_tokenizer = pre_tokenizers.Metaspace(replacement="\u2581", prepend_scheme="never")
+        tk.decoder = decoders.Metaspace(replacement="\u2581")
+    types = list(v["token_type"] or [])
+    special = [tokens[i] for i, tt in enumerate(types) if tt == 3 and i < len(tokens)]
+    special += [t for t in ("<start_of_turn>", "<end_of_turn>", "<|eot_id|>", "<|im_start|>", "<|im_end|>") if t in ids and t not in special]
+    tk.add_special_tokens([AddedToken(t, special=True, normalized=False) for t in special])
+    fast = PreTrainedTokenizerFast(tokenizer_object=tk, bos_token=bos, eos_token=eos, unk_token=unk, pad_token=pad)
+    if v["chat_template"]:
+        fast.chat_template = str(v["chat_template"])
+    return fast
+
+
 # ---------------------------------------------------------------------------------------------------- writing
 def quantize_ggml(w: torch.Tensor, ggml_type: int) -> bytes:
     """Encode a tensor as F32 / F16 / BF16 / Q8_0 / Q4_0 blocks."""

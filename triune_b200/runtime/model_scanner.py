@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import json
 import os
+import struct
 from pathlib import Path
 from typing import Any, Dict, Iterable, List, Optional
 
@@ -190,3 +191,170 @@ def stream_ollama_chat(model: str, messages: List[Dict[str, str]], base_url: str
                 yield piece
             if obj.get("done"):
                 break
+
+
+# ---------------------------------------------------------------------------------------------------- shapes of models on disk
+def resolve_ollama_host(base_url: Optional[str] = None) -> str:
+    """Base URL of the local Ollama daemon: the argument, else ``$OLLAMA_HOST``, else the default; a scheme is added when
+    missing and a trailing slash removed."""
+    host = (base_url or os.environ.get("OLLAMA_HOST") or OLLAMA_URL).strip()
+    if not host.startswith(("http://", "https://")):
+        host = "http://" + host
+    return host.rstrip("/")
+
+
+def parse_gguf_header(gguf_path, max_kv: int = 96) -> Optional[Dict[str, Any]]:
+    """Architecture figures of a GGUF file read from its header only (no tensor data): ``architecture``, ``name``,
+    ``num_layers``, ``hidden_dim``, ``num_heads``, ``num_kv_heads``, ``ffn_dim``, ``vocab_size``, ``context_length``,
+    ``quantization`` (the most common tensor type) and ``tensors``. None when the file is not GGUF or cannot be read.
+    ``max_kv`` is accepted for the reference's signature; the whole key/value table is read (token arrays skipped)."""
+    from .gguf_loader import hf_config_from_gguf, read_gguf_directory
+
+    try:
+        d = read_gguf_directory(gguf_path, load_tokenizer_arrays=False)
+    except (OSError, ValueError, struct.error):
+        return None
+    meta = d["metadata"]
+    cfg = hf_config_from_gguf(meta)
+    types: Dict[int, int] = {}
+    for t in d["tensors"].values():
+        if len(t["shape"]) >= 2:
+            types[t["type"]] = types.get(t["type"], 0) + 1
+    names = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 10: "Q2_K", 11: "Q3_K", 12: "Q4_K", 13: "Q5_K",
+             14: "Q6_K", 15: "Q8_K", 30: "BF16"}
+    top = max(types, key=types.get) if types else None
+    arch = cfg["architecture"]
+    has = lambda k: meta.get(f"{arch}.{k}") is not None  # noqa: E731
+    return {"architecture": arch, "name": meta.get("general.name"), "num_layers": cfg["num_hidden_layers"] if has("block_count") else None,
+            "hidden_dim": cfg["hidden_size"] if has("embedding_length") else None,
+            "num_heads": cfg["num_attention_heads"] if has("attention.head_count") else None, "num_kv_heads": cfg["num_key_value_heads"],
+            "ffn_dim": cfg["intermediate_size"] if has("feed_forward_length") else None, "vocab_size": cfg["vocab_size"],
+            "context_length": cfg["max_position_embeddings"], "quantization": names.get(top, None if top is None else f"type{top}"),
+            "tensors": len(d["tensors"])}
+
+
+def scan_pc_models(extra_paths: Optional[List[str]] = None, *, include_wsl: bool = True, max_depth: int = 4,
+                   installed_modules: Optional[List[Dict[str, Any]]] = None) -> Dict[str, Any]:
+    """``scan_models`` over the default places plus ``extra_paths``, in the report shape of the reference
+    (``triune/runtime/model_scanner.py:489-700``): every entry gets an ``id`` (``ollama:<tag>`` for Ollama models, else
+    ``<kind>:<path>``), GGUF entries their header figures, Ollama entries whether the daemon lists them. ``include_wsl``
+    adds the Linux homes visible from a Windows host (``\\\\wsl$``); ``installed_modules`` are listed as they are."""
+    import time
+
+    t0 = time.perf_counter()
+    roots = [str(r) for r in DEFAULT_ROOTS] + [str(p) for p in (extra_paths or [])]
+    if include_wsl and os.name == "nt":
+        roots += [str(h / ".ollama" / "models") for d in Path(r"\\wsl$").glob("*") for h in (d / "home").glob("*")]
+    rep = scan_models(roots, max_depth=max_depth)
+    live = {t.lower() for t in query_ollama_running_tags()}
+    models, seen = [], set()
+    for e in rep["models"]:
+        e = dict(e)
+        if e["kind"] == "ollama":
+            e["id"] = f"ollama:{e['name']}".lower()
+            e["live"] = e["name"].lower() in live
+        else:
+            e["id"] = f"{e['kind']}:{e['path']}"
+        if e["id"] in seen:
+            continue
+        seen.add(e["id"])
+        if e.get("format") == "GGUF" and Path(e["path"]).is_file():
+            head = parse_gguf_header(e["path"])
+            if head:
+                e.update({k: v for k, v in head.items() if v is not None and k not in e})
+        e.setdefault("name", Path(e["path"]).name)
+        models.append(e)
+    for m in installed_modules or []:
+        models.append({"kind": "module", "id": f"module:{m.get('id') or m.get('name')}", **m})
+    return {"models": models, "counts": rep["counts"], "total_bytes": rep["total_bytes"], "scanned_roots": roots,
+            "ollama_live_tags": sorted(live), "scan_time_ms": round((time.perf_counter() - t0) * 1e3, 2)}
+
+
+def inspect_model_spec_for_upgrade(raw_source: str, *, checkpoint_arch_fn=None, fallback_spec: Optional[Dict[str, Any]] = None):
+    """(layers, hidden size, heads, FFN size, vocabulary size, label) of whatever ``raw_source`` names: ``ollama:<tag>``,
+    a GGUF file, a ``.pt`` / ``.safetensors`` file, an NVFP4 cache or Hugging Face directory; None when it cannot be read.
+    Used to size a model before converting it (``triune/runtime/model_scanner.py:1069-1230`` of the reference, which
+    also asks the Hugging Face hub about repository ids; that needs the network and is left out here)."""
+    raw = str(raw_source or "").strip()
+    if not raw:
+        return None
+
+    def out(layers, hidden, heads, ffn, vocab, label):
+        hidden = int(hidden or 1024)
+        return (int(layers or 24), hidden, int(heads or max(1, hidden // 64)), int(ffn or 4 * hidden), int(vocab or 32000), label)
+
+    if raw.lower().startswith("ollama:"):
+        from .gguf_loader import resolve_ollama_gguf_blob
+
+        blob = resolve_ollama_gguf_blob(raw[len("ollama:"):])
+        if blob is None:
+            return None
+        head = parse_gguf_header(blob)
+        if not head:
+            return None
+        return out(head["num_layers"], head["hidden_dim"], head["num_heads"], head["ffn_dim"], head["vocab_size"],
+                   f"Ollama ({raw[len('ollama:'):]} · {head.get('quantization') or 'GGUF'})")
+    p = Path(raw).expanduser()
+    if p.is_file() and p.suffix.lower() == ".gguf":
+        head = parse_gguf_header(p)
+        if head and (head["num_layers"] or head["hidden_dim"]):
+            return out(head["num_layers"], head["hidden_dim"], head["num_heads"], head["ffn_dim"], head["vocab_size"],
+                       f"{str(head['architecture']).upper()} GGUF ({p.name})")
+        return None
+    if p.is_file() and p.suffix.lower() == ".safetensors":
+        from ..export.safetensors_io import read_header as read_safetensors_header
+
+        try:
+            shapes = {k: tuple(v["shape"]) for k, v in read_safetensors_header(p).items() if k != "__metadata__"}
+        except (OSError, ValueError, KeyError):
+            return None
+        return _spec_from_shapes(shapes, f"Saved SafeTensors ({p.name})", out)
+    if p.is_file() and p.suffix.lower() in (".pt", ".pth", ".bin", ".ckpt"):
+        import torch
+
+        try:
+            ck = torch.load(p, map_location="cpu", weights_only=True)
+        except Exception:
+            return None
+        if isinstance(ck, dict) and checkpoint_arch_fn is not None:
+            try:
+                _, arch = checkpoint_arch_fn(ck, fallback_spec or {})
+                cfg = ck.get("config") if isinstance(ck.get("config"), dict) else {}
+                return out(arch.get("num_layers"), arch.get("hidden_dim"), arch.get("num_heads"), cfg.get("ffn_dim"), arch.get("vocab_size"),
+                           f"Saved Checkpoint ({p.name})")
+            except Exception:
+                pass
+        sd = ck.get("model_state", ck.get("model", ck)) if isinstance(ck, dict) else {}
+        shapes = {k: tuple(v.shape) for k, v in sd.items() if hasattr(v, "shape")} if isinstance(sd, dict) else {}
+        return _spec_from_shapes(shapes, f"Saved Checkpoint ({p.name})", out) if shapes else None
+    if p.is_dir():
+        if (p / "manifest.json").is_file():
+            try:
+                m = json.loads((p / "manifest.json").read_text())
+                cfg = m.get("config") or {}
+                return out(m.get("num_layers") or cfg.get("num_hidden_layers"), cfg.get("hidden_size"), cfg.get("num_attention_heads"),
+                           cfg.get("intermediate_size"), cfg.get("vocab_size"), f"NVFP4 cache ({p.name})")
+            except (OSError, ValueError):
+                return None
+        info = _hf_dir_info(p)
+        if info:
+            try:
+                cfg = json.loads((p / "config.json").read_text())
+            except (OSError, ValueError):
+                cfg = {}
+            return out(info.get("num_hidden_layers") or info.get("num_layers"), info.get("hidden_size") or info.get("hidden_dim"),
+                       info.get("num_attention_heads"), cfg.get("intermediate_size") or cfg.get("ffn_dim"), info.get("vocab_size"),
+                       f"{str(info.get('model_type') or 'hf').upper()} ({p.name})")
+    return None
+
+
+def _spec_from_shapes(shapes: Dict[str, tuple], label: str, out):
+    """Sizes of a decoder from the names and shapes of its tensors: layers from the highest block index, vocabulary and
+    width from the embedding matrix, FFN size from the first gate / up / fc1 / expert weight."""
+    import re
+
+    idx = [int(m.group(1)) for k in shapes if (m := re.match(r"(?:model\.layers|transformer\.h|layers)\.(\d+)\.", k))]
+    emb = next((s for k, s in shapes.items() if "embed" in k and len(s) == 2), None)
+    vocab, hidden = (emb if emb else (32000, 384))
+    ffn = next((max(s) for k, s in shapes.items() if len(s) >= 2 and any(t in k for t in ("gate_proj", "up_proj", "fc1", "experts.0.0", ".w1"))), None)
+    return out(max(idx) + 1 if idx else 8, hidden, None, ffn, vocab, label)
