@@ -336,7 +336,8 @@ def test_reference_method_names_on_agents_registry_and_modules(triune, tmp_path)
     mm = ModuleManager(config_dir=str(tmp_path / "mods"))
     assert mm.save_config({"directory": str(tmp_path / "mods"), "active": ["a"]}) == mm.get_config()
     assert mm.inspect_directory(str(tmp_path))["files"] >= 1 and mm.inspect_directory(str(tmp_path / "zz"))["status"] == "error"
-    assert mm.search_marketplace("x")["results"] == [] and mm.check_updates()["updates"] == []
+    assert mm.search_marketplace("zzz")["results"] == [] and mm.check_updates()["updates"] == []
+    assert [r["download_url"] for r in mm.search_marketplace("loss")["results"]] == ["builtin://custom_loss_nodes"]
     assert mm.clone_repository("https://github.com/a/b")["status"] == "error" and mm.git_pull("none")["status"] == "error"
     assert "os_type" in mm.scan_hardware_and_software()
     assert mm.create_custom_plugin_template("my_plug")["status"] == "created" and mm.discover_and_register_nodes("my_plug")["status"] == "active"
@@ -369,3 +370,93 @@ def test_run_config_keys_and_exploration_schedule_follow_the_reference():
     num = {"exploration": 0.2, "exploration_steps": 100}
     assert rate(num, 0) == pytest.approx(0.2) and rate(num, 50) == pytest.approx(0.1) and rate(num, 100) == 0.0
     assert rate({"exploration": 0.4, "exploration_steps": 100, "exploration_schedule": "cosine"}, 50) == pytest.approx(0.2)
+
+
+def test_every_module_path_of_the_reference_imports_and_top_level_names_resolve():
+    """Deep import paths (``triune.runtime.staging``, ``triune.model.manifold_embedding``, ``triune.agents.tools`` ...) and
+    the names the reference's top-level package re-exports resolve, and uninstalling removes the fall-back lookups that
+    were attached to this framework's modules."""
+    import importlib
+
+    import triune_b200.compat as compat
+
+    compat.install()
+    try:
+        import triune
+
+        assert triune.Model is importlib.import_module("triune_b200.models.factory").build_model
+        assert triune.CentroidSteer is triune.CentroidSteerOptimizer and triune.TriuneTransformer is triune.model.TriuneTransformer
+        assert callable(triune.upgrade) and callable(triune.fast_rope) and triune.Trainer is triune.trainer.Trainer
+        for path, names in {
+            "triune.runtime.staging": ["ParameterStager", "FP8StagingBuffer"], "triune.model.manifold_embedding": ["UniversalAdaptiveEmbedding"],
+            "triune.agents.tools": ["validate_http_url", "ToolRegistry"], "triune.agents._storage": ["atomic_write_json", "compute_tfidf_cosine_scores"],
+            "triune.agents.personas": ["BUILTIN_PERSONAS", "PersonaProfile"], "triune.kernels.fast_muon": ["NS5_COEFFS", "compute_muon_update_scale"],
+            "triune.kernels.fast_triangular": ["fast_triangular_adamw"], "triune.model.config": ["checkpoint_bwd_ctx", "BATCH_SIZE", "HIDDEN_DIM"],
+            "triune.plugins.node_schema": ["PortType", "NodeSchema", "is_port_compatible"], "triune.trainer.checkpoint": ["compute_checkpoint_fingerprint"],
+            "triune.universal": ["DenseTransformerBlock", "UniversalDenseTransformer", "upgrade_model"], "triune.utils.seed": ["seed_everything"],
+            "triune.api.routes": ["ChatCompletionRequest", "pytorch_state", "sanitize_text", "router"], "triune.api.server": ["lifespan", "create_app"],
+            "triune.cli_ui": ["render_table", "route_badge_markup"], "triune.modules.github_client": ["RepoSearchClient"],
+            "triune.modules.curated.custom_loss_nodes.custom_loss_nodes": ["FocalCrossEntropyLoss", "anneal_temperature"],
+            "triune.runtime.model_scanner": ["parse_gguf_header", "scan_pc_models"], "triune.inference": ["IncrementalStreamingDecoder"],
+            "triune.optim.centroid": ["profile_rank_sensitivity", "fast_subspace_projection", "CentroidSteerOptimizer"],
+            "triune.ops.centroid_steer": ["polar_stiefel_retraction", "batched_qr"], "triune.packaging": ["build_linux_native", "TRIUNE_SVG_ICON"],
+        }.items():
+            mod = importlib.import_module(path)
+            for n in names:
+                assert getattr(mod, n) is not None, f"{path}.{n}"
+        with pytest.raises(AttributeError):
+            importlib.import_module("triune.runtime.staging").no_such_name
+        import triune_b200.serve.routes as routes
+
+        assert routes.ChatCompletionRequest is routes.ChatRequest  # the fall-back attached to the aliased module
+    finally:
+        compat.uninstall()
+    import triune_b200.serve.routes as routes
+
+    assert not hasattr(routes, "pytorch_state")
+
+
+def test_reference_helper_functions_compute_what_they_name():
+    import torch
+
+    from triune_b200.agents import validate_http_url
+    from triune_b200.agents.storage import atomic_write_json, compute_tfidf_cosine_scores, load_validated_json_dict, tokenize_terms
+    from triune_b200.kernels import compute_muon_update_scale, fast_triangular_adamw, fast_zeropower_via_newtonschulz5_batched
+    from triune_b200.optim.centroid import profile_rank_sensitivity
+    from triune_b200.serve.routes import sanitize_text
+
+    with pytest.raises(ValueError):
+        validate_http_url("ftp://example.com/x")
+    with pytest.raises(ValueError):
+        validate_http_url("http://user:pw@127.0.0.1/")
+    with pytest.raises(PermissionError):
+        validate_http_url("http://127.0.0.1:9/")
+    assert validate_http_url(" http://127.0.0.1:11434/api/tags ", allow_local_services=True) == "http://127.0.0.1:11434/api/tags"
+    with pytest.raises(PermissionError):
+        validate_http_url("http://10.1.2.3/")
+    assert "#oke" in tokenize_terms("the tokenizer") and "the" not in tokenize_terms("the tokenizer")
+    s = compute_tfidf_cosine_scores("gpu memory planner", ["plan memory of a gpu", "bake bread", ""])
+    assert s[0] > s[1] == 0.0 and s[2] == 0.0 and all(0.0 <= v <= 1.0 for v in s)
+    import tempfile
+    from pathlib import Path
+
+    d = Path(tempfile.mkdtemp())
+    atomic_write_json(d / "a" / "x.json", {"k": [1, 2]})
+    assert load_validated_json_dict(d / "a" / "x.json") == {"k": [1, 2]} and not list((d / "a").glob(".*tmp"))
+    (d / "bad.json").write_text("{not json")
+    assert load_validated_json_dict(d / "bad.json") == {} and load_validated_json_dict(d / "none.json") == {}
+    broken = "it’s “here” — café".encode("utf-8").decode("cp1252", errors="replace")
+    assert sanitize_text(broken) == 'it\'s "here" -- café' and sanitize_text("plain ‘x’ é") == "plain ‘x’ é" and sanitize_text(None) == ""
+    assert compute_muon_update_scale(64, 16) == 2.0 and compute_muon_update_scale(16, 64, 0.2) == pytest.approx(0.2)
+    X = fast_zeropower_via_newtonschulz5_batched(torch.randn(2, 8, 24), steps=8)
+    assert torch.allclose(X @ X.transpose(1, 2), torch.eye(8).expand(2, 8, 8), atol=1e-2)
+    with pytest.raises(ValueError):
+        fast_zeropower_via_newtonschulz5_batched(torch.randn(8, 24))
+    R, m, v, out = torch.randn(3, 5, 5), torch.zeros(3, 5, 5), torch.zeros(3, 5, 5), torch.empty(3, 5, 5)
+    fast_triangular_adamw(R, m, v, out, torch.tensor([1, 1, 1]), 0.9, 0.999, mask_mode="triu")
+    assert torch.allclose(out, torch.sign(R).triu(), atol=1e-3) and torch.allclose(m, 0.1 * R)  # first step of Adam: the sign of the gradient
+    lin = torch.nn.Linear(32, 16, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.outer(torch.randn(16), torch.randn(32)))  # rank one
+    rep = profile_rank_sensitivity(lin, target_energy=0.9, min_rank=1)
+    assert rep["layers"]["weight"]["recommended_rank"] == 1 and rep["layers"]["weight"]["captured_energy"] > 0.99

@@ -8,6 +8,7 @@ import sys
 import pytest
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from triune_b200.config import ModelConfig
 from triune_b200.models import TriuneTransformer
@@ -1249,3 +1250,175 @@ def test_profile_summaries_carry_their_commands_and_name_existing_files():
                 assert p.with_suffix(".py").exists() or (p / "__main__.py").exists() or (p / "__init__.py").exists(), f"{f.name}: {mod}"
         cells = [c.strip().lower() for ln in text.splitlines() if ln.lstrip().startswith("|") for c in ln.split("|")]
         assert not any(c in ("nan", "inf", "-inf") or re.fullmatch(r"-\d[\d.]*( ?[a-zµ/%]+)?", c) for c in cells), f.name
+
+
+def test_whole_model_streams_from_an_nvfp4_disk_cache(tmp_path):
+    """``load_disk_streamed_model`` builds the cache from a Hugging Face directory, creates the model without storage,
+    serves each decoder layer from disk for the duration of its forward pass and reproduces the resident model's logits to
+    NVFP4 accuracy, with and without the Hadamard rotation; afterwards no layer holds storage."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from triune_b200.runtime.disk_streaming import load_disk_streamed_model, resolve_hf_model_dir
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                      max_position_embeddings=64, tie_word_embeddings=False)
+    ref = LlamaForCausalLM(cfg).eval()
+    ref.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    assert resolve_hf_model_dir(tmp_path / "hf") == tmp_path / "hf"
+    with pytest.raises(FileNotFoundError):
+        resolve_hf_model_dir("nobody/not-on-this-disk")
+    x = torch.randint(0, 128, (2, 10))
+    with torch.no_grad():
+        want = ref(x).logits
+    for had in (False, True):
+        model, eng, cache = load_disk_streamed_model(tmp_path / "hf", cache_dir=tmp_path / f"cache{int(had)}", device="cpu", hadamard=had)
+        assert (cache / "manifest.json").is_file() and eng.manifest["hadamard"] is had
+        with torch.no_grad():
+            got = model(x).logits
+            again = model(x).logits
+        assert F.cosine_similarity(got.flatten().float(), want.flatten(), dim=0) > 0.97 and torch.equal(got, again)
+        assert eng.telemetry["layers_loaded"] == 6 and len(eng._resident) == 0
+        assert all(p.is_meta for lay in model.model.layers for p in lay.parameters())
+        model2, eng2, cache2 = load_disk_streamed_model(cache, device="cpu")  # a cache directory is accepted as it is
+        assert cache2 == cache
+        eng.close(), eng2.close()
+
+
+def test_model_scanner_reads_sizes_from_headers(tmp_path):
+    from triune_b200.export.safetensors_io import save_file
+    from triune_b200.runtime.gguf_loader import build_hf_tokenizer_from_gguf, write_gguf
+    from triune_b200.runtime.model_scanner import inspect_model_spec_for_upgrade, parse_gguf_header, resolve_ollama_host, scan_pc_models
+
+    meta = {"general.architecture": "llama", "general.name": "tiny", "llama.block_count": 2, "llama.embedding_length": 64,
+            "llama.attention.head_count": 4, "llama.feed_forward_length": 128, "llama.context_length": 512, "llama.vocab_size": 100}
+    write_gguf(tmp_path / "m.gguf", {"token_embd.weight": (torch.randn(100, 64), 0), "blk.0.attn_q.weight": (torch.randn(64, 64), 8),
+                                     "blk.1.attn_q.weight": (torch.randn(64, 64), 8)}, meta)
+    head = parse_gguf_header(tmp_path / "m.gguf")
+    assert (head["num_layers"], head["hidden_dim"], head["num_heads"], head["ffn_dim"], head["vocab_size"], head["quantization"]) == (2, 64, 4, 128, 100, "Q8_0")
+    assert inspect_model_spec_for_upgrade(str(tmp_path / "m.gguf")) == (2, 64, 4, 128, 100, "LLAMA GGUF (m.gguf)")
+    save_file({"model.embed_tokens.weight": torch.randn(50, 32), "model.layers.2.mlp.gate_proj.weight": torch.randn(96, 32)}, str(tmp_path / "x.safetensors"))
+    assert inspect_model_spec_for_upgrade(str(tmp_path / "x.safetensors"))[:5] == (3, 32, 1, 96, 50)
+    torch.save({"model_state": {"embed.weight": torch.randn(40, 16), "layers.1.ffn.w1": torch.randn(4, 16, 48)}}, tmp_path / "c.pt")
+    assert inspect_model_spec_for_upgrade(str(tmp_path / "c.pt"))[:5] == (2, 16, 1, 48, 40)
+    assert inspect_model_spec_for_upgrade(str(tmp_path / "c.pt"), checkpoint_arch_fn=lambda ck, fb: ("x", {"num_layers": 7, "hidden_dim": 128}))[:3] == (7, 128, 2)
+    assert inspect_model_spec_for_upgrade("") is None and inspect_model_spec_for_upgrade(str(tmp_path / "nothing")) is None
+    assert parse_gguf_header(tmp_path / "c.pt") is None
+    rep = scan_pc_models([str(tmp_path)], include_wsl=False, installed_modules=[{"id": "m1"}])
+    by_id = {m["id"].split(":")[0]: m for m in rep["models"]}
+    assert by_id["gguf"]["num_layers"] == 2 and "checkpoint" in by_id and by_id["module"]["id"] == "module:m1" and str(tmp_path) in rep["scanned_roots"]
+    assert resolve_ollama_host("localhost:11434/") == "http://localhost:11434"
+    toks = ["<unk>", "<s>", "</s>"] + ["▁" + w for w in ("hello", "world")] + list("helowrd") + ["▁"]
+    tk = build_hf_tokenizer_from_gguf({"tokenizer.ggml.tokens": toks, "tokenizer.ggml.scores": [0.0] * 3 + [-1.0] * 2 + [-5.0] * 8,
+                                       "tokenizer.ggml.token_type": [2, 3, 3] + [1] * 10, "tokenizer.ggml.bos_token_id": 1,
+                                       "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.unknown_token_id": 0, "tokenizer.chat_template": "{{ messages }}"})
+    ids = tk.encode("hello world")
+    assert tk.decode(ids) == "hello world" and max(ids) < len(toks) and tk.bos_token == "<s>" and tk.chat_template == "{{ messages }}"
+    with pytest.raises(ValueError):
+        build_hf_tokenizer_from_gguf({})
+
+
+def test_curated_modules_install_offline_and_register_plain_node_names(tmp_path):
+    from triune_b200.execution.dag import NODE_TYPES, execute_dag
+    from triune_b200.plugins.curated import CURATED, curated_path
+    from triune_b200.plugins.curated.custom_loss_nodes.custom_loss_nodes import CentroidBalanceLoss, FocalCrossEntropyLoss, anneal_temperature
+    from triune_b200.plugins.registry import PluginRegistry, file_sha256
+
+    import json
+    import shutil
+
+    man = json.loads((curated_path("custom-loss-nodes") / "plugin.json").read_text())
+    assert man["sha256"] == file_sha256(curated_path("custom_loss_nodes") / man["entry"])  # the shipped manifest matches the shipped file
+    assert {c["id"] for c in CURATED} == {"custom_loss_nodes", "code_assistant_lora"}
+    assert json.loads((curated_path("code_assistant_lora") / "adapter_config.json").read_text())["r"] == 16
+    shutil.copytree(curated_path("custom_loss_nodes"), tmp_path / "custom_loss_nodes")
+    reg = PluginRegistry(key="")
+    reg.discover(tmp_path)
+    try:
+        info = reg.load("custom_loss_nodes")
+        assert {"FocalCrossEntropyLoss", "custom_loss_nodes.FocalCrossEntropyLoss", "TemperatureAnnealer"} <= set(info.nodes)
+        out = execute_dag({"nodes": [{"id": "t", "type": "TemperatureAnnealer", "params": {"global_step": 2500}}], "edges": []})
+        assert out["outputs"]["t.temperature"] == pytest.approx(0.55)
+    finally:
+        for n in ("FocalCrossEntropyLoss", "CentroidBalanceLoss", "TemperatureAnnealer"):
+            NODE_TYPES.pop(n, None), NODE_TYPES.pop(f"custom_loss_nodes.{n}", None)
+    # an edited copy is an ordinary plugin: its nodes get the plugin's prefix only
+    (tmp_path / "other").mkdir()
+    shutil.copytree(curated_path("custom_loss_nodes"), tmp_path / "other" / "custom_loss_nodes")
+    entry = tmp_path / "other" / "custom_loss_nodes" / man["entry"]
+    entry.write_text(entry.read_text() + "\n# edited\n")
+    from triune_b200.plugins.registry import write_manifest
+
+    write_manifest(tmp_path / "other" / "custom_loss_nodes", key="")
+    reg2 = PluginRegistry(key="")
+    reg2.discover(tmp_path / "other")
+    try:
+        assert "FocalCrossEntropyLoss" not in reg2.load("custom_loss_nodes").nodes
+    finally:
+        for n in ("FocalCrossEntropyLoss", "CentroidBalanceLoss", "TemperatureAnnealer"):
+            NODE_TYPES.pop(f"custom_loss_nodes.{n}", None)
+    logits, tgt = torch.randn(2, 5, 7), torch.randint(0, 7, (2, 5))
+    assert torch.allclose(FocalCrossEntropyLoss(0.0)(logits, tgt), F.cross_entropy(logits.view(-1, 7), tgt.view(-1)))
+    assert FocalCrossEntropyLoss(2.0)(logits, tgt) < FocalCrossEntropyLoss(0.0)(logits, tgt)
+    assert float(CentroidBalanceLoss(1.0)(torch.full((6, 4), 0.25))) == 0.0 and float(CentroidBalanceLoss(1.0)(torch.eye(4)[[0, 0, 0]])) == pytest.approx(0.75)
+    assert anneal_temperature(0) == 1.0 and anneal_temperature(10 ** 6) == pytest.approx(0.1)
+
+
+def test_upgrade_model_keeps_gemma_and_llama_logits():
+    """Patching a third-party model must not change what it computes: Gemma stores its norm scale as an offset from one
+    and gates its MLP with GELU, Llama uses the plain scale and SiLU."""
+    from transformers import GemmaConfig, GemmaForCausalLM, LlamaConfig, LlamaForCausalLM
+
+    from triune_b200.inference import IncrementalStreamingDecoder, optimize_hf_model_for_inference
+    from triune_b200.models.universal import upgrade_model
+
+    torch.manual_seed(0)
+    for C, M, swiglu in ((GemmaConfig, GemmaForCausalLM, 0), (LlamaConfig, LlamaForCausalLM, 2)):
+        cfg = C(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=16,
+                max_position_embeddings=64)
+        m = M(cfg).eval()
+        with torch.no_grad():
+            for p in m.parameters():
+                p.add_(torch.randn_like(p) * 0.05)
+        x = torch.randint(0, 128, (2, 12))
+        with torch.no_grad():
+            want = m(x).logits
+            optimize_hf_model_for_inference(m)
+            assert torch.allclose(m(x).logits, want, atol=1e-5)
+            upgrade_model(m)
+            assert torch.allclose(m(x).logits, want, atol=1e-5)
+        assert m._triune_upgrade["rmsnorm"] == 5 and m._triune_upgrade["swiglu"] == swiglu
+
+    class Tk:
+        def decode(self, ids):
+            return bytes(ids).decode("utf-8", errors="replace")
+
+    dec = IncrementalStreamingDecoder(Tk())
+    pieces = [dec.step(b)[1] for b in "hé there".encode("utf-8")]
+    assert "".join(pieces) + dec.flush()[1] == "hé there" and "" in pieces and dec.cumulative_text == "hé there"
+
+
+def test_terminal_rendering_plain_and_rich(capsys, monkeypatch):
+    from triune_b200 import cli_ui
+
+    for rich in (cli_ui.HAS_RICH, False):
+        monkeypatch.setattr(cli_ui, "HAS_RICH", rich)
+        cli_ui.render_banner("TITLE", "sub", "badge")
+        cli_ui.render_kv_panel("card", [("key", 1), ("longer key", "v")], footer="foot")
+        cli_ui.render_table("tab", [("name", "left", "cyan"), ("n", "right", "")], [["a", 1], ["bbb", 22]], caption="cap")
+        cli_ui.render_notice("done", "success")
+        cli_ui.render_telemetry_bar("limbic", tok_sec=12.3, ttft_ms=4.5, tokens=7, latency_ms=99, vram_gb=1.5, load_s=0.2, extra="x")
+        cli_ui.render_rule("rule")
+        with cli_ui.status_spinner("working"):
+            pass
+        out = capsys.readouterr().out
+        for piece in ("TITLE", "badge", "sub", "card", "longer key", "foot", "tab", "bbb", "22", "cap", "done", "LIMBIC", "12.3 tok/s", "4.5ms", "1.50GB", "rule", "working"):
+            assert piece in out, (rich, piece)
+        assert "\x1b[" not in out and "[bold" not in out  # no colour codes or markup when stdout is not a terminal
+    assert cli_ui.route_badge_ansi("reflex") == "[REFLEX]" and "CORTEX" in cli_ui.route_badge_markup("cortex") and "OLLAMA" in cli_ui.route_badge_markup("ollama:x")
+    cli_ui.render_help_overview()
+    overview = capsys.readouterr().out
+    assert all(c in overview for c in ("train", "finetune", "serve", "doctor", "plugin"))
+    from triune_b200.cli import main
+
+    assert main([]) == 0 and "chat" in capsys.readouterr().out

@@ -265,7 +265,7 @@ def scan_pc_models(extra_paths: Optional[List[str]] = None, *, include_wsl: bool
         e.setdefault("name", Path(e["path"]).name)
         models.append(e)
     for m in installed_modules or []:
-        models.append({"kind": "module", "id": f"module:{m.get('id') or m.get('name')}", **m})
+        models.append({**m, "kind": "module", "id": f"module:{m.get('id') or m.get('name')}"})
     return {"models": models, "counts": rep["counts"], "total_bytes": rep["total_bytes"], "scanned_roots": roots,
             "ollama_live_tags": sorted(live), "scan_time_ms": round((time.perf_counter() - t0) * 1e3, 2)}
 
