@@ -85,7 +85,9 @@ def test_shell_routes(client, tmp_path):
 
     assert client.get("/v1/plugins").json() == {"plugins": []} or isinstance(client.get("/v1/plugins").json()["plugins"], list)
     assert client.post("/v1/modules/scan_local", json={"directory": str(tmp_path / "none")}).status_code == 404
-    assert client.get("/v1/modules/search").json()["results"] == []
+    found = client.get("/v1/modules/search").json()  # the modules that ship with the framework; remote catalogues are not asked
+    assert {r["download_url"] for r in found["results"]} == {"builtin://custom_loss_nodes", "builtin://code_assistant_lora"} and found["github"] == []
+    assert client.get("/v1/modules/search", params={"q": "zzz"}).json()["results"] == []
 
     cfg = client.post("/v1/system/config", json={"plugin_dir": str(tmp_path)}).json()["config"]
     assert cfg["plugin_dir"] == str(tmp_path)
@@ -210,7 +212,7 @@ def test_canvas_graphs_over_http(client, tmp_path):
     from triune_b200.serve.engine_state import get_state
 
     cat = client.get("/v1/nodes/catalog").json()["studio_nodes"]
-    assert len(cat) == 49 and {"TriuneTransformer", "TrainingStep", "Subgraph"} <= {n["name"] for n in cat}
+    assert len(cat) == 50 and {"TriuneTransformer", "TrainingStep", "Subgraph", "RerouteNode"} <= {n["name"] for n in cat}
     assert client.get("/v1/dag/queue").json() == {"active_run_id": None, "waiting": 0, "capacity": 1}
     corpus = tmp_path / "c.txt"
     corpus.write_text("a few words of text for the graph to read and tokenise\n")

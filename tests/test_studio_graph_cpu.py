@@ -238,3 +238,70 @@ def test_subgraphs_with_declared_sockets_and_the_depth_limit():
         nested = {"nodes": [{"id": "s", "type": "Subgraph", "subgraph": nested}], "edges": [], "inputs": [], "outputs": []}
     r = run_studio_graph({"nodes": nested["nodes"], "edges": []})
     assert r["status"] == "failed" and "depth" in r["error"]
+
+
+# (display title in the canvas' palette, category the canvas stores in ``type``, node kind)
+PALETTE = [
+    ('Hugging Face Streamer', 'Data', 'HuggingFaceStreamer'),
+    ('URL Dataset Streamer', 'Data', 'URLDatasetStreamer'),
+    ('Local File Reader', 'Data', 'LocalFileReader'),
+    ('BPE Tokenizer', 'Data', 'BPETokenizer'),
+    ('Cycling DataLoader', 'Data', 'CyclingDataLoader'),
+    ('Autograd Training Step', 'Evaluation', 'TrainingStep'),
+    ('Triune MoE Transformer', 'Model', 'TriuneTransformer'),
+    ('Vectorised GLA Attention', 'Model', 'VectorisedGLA'),
+    ('Hybrid GLA + RoPE Attention', 'Model', 'HybridAttention'),
+    ('Sparse MoE FFN Layer', 'Model', 'MoE_FFN'),
+    ('Hierarchical Depth Router', 'Model', 'DepthRouter'),
+    ('FP8 Scaled Linear', 'Model', 'FP8Linear'),
+    ('NVFP4 Microscaling Linear', 'Model', 'FP4Linear'),
+    ('Tensor Inspector', 'Analysis', 'TensorInspector'),
+    ('Token Batch Inspector', 'Analysis', 'TokenBatchInspector'),
+    ('Fast RMSNorm', 'Model', 'RMSNorm'),
+    ('LoRA Adapter Layer', 'Model', 'LoRAAdapter'),
+    ('CentroidSteer Optimizer', 'Optimizer', 'CentroidSteerOptimizer'),
+    ('Muon Matrix Optimizer', 'Optimizer', 'MuonOptimizer'),
+    ('AdamW Optimizer', 'Optimizer', 'AdamWOptimizer'),
+    ('Cosine LR Scheduler', 'Optimizer', 'CosineLRScheduler'),
+    ('Fast Cross-Entropy Loss', 'Loss', 'FastCrossEntropy'),
+    ('Joint Exit Loss', 'Loss', 'JointExitLoss'),
+    ('Router Stability Z-Loss', 'Loss', 'RouterZLoss'),
+    ('Fast RoPE Kernel', 'Model', 'FastRoPE'),
+    ('Fast RMSNorm Kernel', 'Model', 'FastRMSNorm'),
+    ('Autoregressive Generator', 'Model', 'AutoregressiveGenerator'),
+    ('BYOK Chat Router', 'Model', 'BYOKChatRouter'),
+    ('Gradient Accumulator', 'Runtime', 'GradientAccumulator'),
+    ('Checkpoint Manager', 'Runtime', 'CheckpointManager'),
+    ('Dynamic Resource Manager', 'Runtime', 'DynamicResourceManager'),
+    ('Layer Streaming Engine', 'Runtime', 'LayerStreamingEngine'),
+    ('VRAM Profiler', 'Runtime', 'VRAMProfiler'),
+    ('Restricted Python Runner', 'Runtime', 'PythonSandbox'),
+    ('WandB Telemetry Logger', 'Runtime', 'WandbLogger'),
+    ('Perplexity Evaluator', 'Evaluation', 'PerplexityEvaluator'),
+    ('LoRA Fine-Tuner Engine', 'Evaluation', 'LoRAFineTuner'),
+    ('SafeTensors Exporter', 'Export', 'SafeTensorsExport'),
+    ('GGUF Export (Configuration Only)', 'Export', 'GGUFExport'),
+    ('ONNX Graph Exporter', 'Export', 'ONNXExport'),
+    ('Reroute Node', 'Reroute', 'RerouteNode'),
+]
+
+
+def test_nodes_are_identified_by_their_palette_title_before_their_category(tmp_path):
+    """The canvas stores the palette title in ``title`` and only the broad category in ``type``; a saved graph must resolve
+    to the specific node kinds, and a reroute junction passes values through."""
+    from triune_b200.execution.studio import resolve_kind
+
+    for title, category, kind in PALETTE:
+        assert resolve_kind({"id": "n", "type": category, "title": title}) == kind, title
+    assert resolve_kind({"id": "n", "type": "Data", "title": "My own reader"}) == "Data"  # an unknown title falls back to the category
+    g = {"nodes": [{"id": "a", "type": "Data", "title": "Local File Reader", "details": f"file_path={_corpus(tmp_path)}"},
+                   {"id": "r", "type": "Reroute", "title": "Reroute Node"}, {"id": "b", "type": "Data", "title": "BPE Tokenizer"}],
+         "edges": [{"source": "a", "target": "r", "source_port": "text_sample", "target_port": "in"},
+                   {"source": "r", "target": "b", "source_port": "out", "target_port": "text"}]}
+    out = run_studio_graph(g)
+    assert out["status"] == "success" and all(r["status"] == "completed" for r in out["results"].values())
+    bad = {"nodes": [{"id": "s", "type": "Data", "title": "Hugging Face Streamer"}, {"id": "t", "type": "Evaluation", "title": "Autograd Training Step"}],
+           "edges": [{"source": "s", "target": "t", "source_port": "dataset_stream", "target_port": "dataset_stream"}]}
+    from triune_b200.execution.studio import parse_studio_graph
+
+    assert parse_studio_graph(bad).order == ["s", "t"]

@@ -180,11 +180,39 @@ _KEYWORDS: Tuple[Tuple[Tuple[str, ...], str], ...] = (
 _CATEGORIES = ("Data", "Model", "Optimizer", "Loss", "Runtime", "Evaluation", "Export")
 
 
+# display titles of the canvas' palette (lower case, letters and digits only) -> node kind; the canvas stores the title a
+# node was created with and the broad category in ``type``, so this table is what identifies most nodes of a saved graph
+_TITLES = {
+    "huggingfacestreamer": "HuggingFaceStreamer", "urldatasetstreamer": "URLDatasetStreamer", "localfilereader": "LocalFileReader",
+    "bpetokenizer": "BPETokenizer", "cyclingdataloader": "CyclingDataLoader", "autogradtrainingstep": "TrainingStep",
+    "triunemoetransformer": "TriuneTransformer", "triunemoettransformer": "TriuneTransformer", "vectorisedglaattention": "VectorisedGLA",
+    "hybridglaropeattention": "HybridAttention", "sparsemoeffnlayer": "MoE_FFN", "hierarchicaldepthrouter": "DepthRouter",
+    "fp8scaledlinear": "FP8Linear", "nvfp4microscalinglinear": "FP4Linear", "tensorinspector": "TensorInspector",
+    "tokenbatchinspector": "TokenBatchInspector", "fastrmsnorm": "RMSNorm", "loraadapterlayer": "LoRAAdapter",
+    "centroidsteeroptimizer": "CentroidSteerOptimizer", "muonmatrixoptimizer": "MuonOptimizer", "adamwoptimizer": "AdamWOptimizer",
+    "cosinelrscheduler": "CosineLRScheduler", "fastcrossentropyloss": "FastCrossEntropy", "jointexitloss": "JointExitLoss",
+    "routerstabilityzloss": "RouterZLoss", "fastropekernel": "FastRoPE", "fastrmsnormkernel": "FastRMSNorm",
+    "autoregressivegenerator": "AutoregressiveGenerator", "byokchatrouter": "BYOKChatRouter", "gradientaccumulator": "GradientAccumulator",
+    "checkpointmanager": "CheckpointManager", "dynamicresourcemanager": "DynamicResourceManager", "layerstreamingengine": "LayerStreamingEngine",
+    "vramprofiler": "VRAMProfiler", "restrictedpythonrunner": "PythonSandbox", "wandbtelemetrylogger": "WandbLogger",
+    "perplexityevaluator": "PerplexityEvaluator", "lorafinetunerengine": "LoRAFineTuner", "safetensorsexporter": "SafeTensorsExport",
+    "ggufexportconfigurationonly": "GGUFExport", "onnxgraphexporter": "ONNXExport", "reroutenode": "RerouteNode", "reroute": "RerouteNode",
+}
+
+
+def _squash(text: str) -> str:
+    return "".join(ch for ch in text.lower() if ch.isalnum())
+
+
 def resolve_kind(node: Dict[str, Any]) -> Optional[str]:
-    """The node kind: a title that names one wins over the broad category in ``type``; then ``type``; then keywords."""
+    """The node kind: a title that names one (its kind, or its display title in the palette) wins over the broad category
+    in ``type``; then ``type``; then keywords."""
     title, typ = str(node.get("title") or node.get("name") or ""), str(node.get("type") or "")
     if title in STUDIO_NODES and title not in _CATEGORIES:
         return title
+    by_title = _TITLES.get(_squash(title)) or next((k for k in STUDIO_NODES if k not in _CATEGORIES and _squash(k) == _squash(title)), None)
+    if by_title in STUDIO_NODES:
+        return by_title
     if typ in STUDIO_NODES:
         return typ
     if title in STUDIO_NODES:
@@ -1160,6 +1188,12 @@ def _byok(i, p, c):
     cfg = {"provider": str(p["provider"]), "model": str(p["model"]), "temperature": float(p["temperature"]), "max_tokens": int(p["max_tokens"]),
            "has_key": bool(c.get("provider_keys", {}).get(str(p["provider"]))), "prompt_chars": len(i.get("prompt") or "")}
     return {"provider_config": cfg, "_specification": True}
+
+
+@studio_node("RerouteNode", "Reroute", {"in": ANY}, {"out": ANY}, {"label": "reroute"},
+             "a junction that passes its input on unchanged (keeps long wires of the canvas tidy)")
+def _reroute(i, p, c):
+    return {"out": i.get("in", next(iter(i.values()), None))}
 
 
 # ---------------------------------------------------------------------------------------------------- training, evaluation
