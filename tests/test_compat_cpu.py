@@ -460,3 +460,70 @@ def test_reference_helper_functions_compute_what_they_name():
         lin.weight.copy_(torch.outer(torch.randn(16), torch.randn(32)))  # rank one
     rep = profile_rank_sensitivity(lin, target_energy=0.9, min_rank=1)
     assert rep["layers"]["weight"]["recommended_rank"] == 1 and rep["layers"]["weight"]["captured_energy"] > 0.99
+
+
+def test_reference_calling_forms_of_generation_checkpoints_and_cache(tmp_path):
+    """``generate_response`` with the reference's keyword-only arguments returns text (a dict with ``return_info``);
+    ``save_latest`` / ``load_checkpoint`` take a trainer; ``build_nvfp4_disk_cache`` returns the cache directory; layer
+    constructors take ``device`` / ``dtype``; attribute names of the reference read back."""
+    import torch
+
+    import triune_b200.compat as compat
+    from triune_b200.config import ModelConfig
+    from triune_b200.models import TriuneTransformer
+
+    cfg = dict(vocab_size=256, hidden_dim=64, num_layers=5, num_heads=2, head_dim=32, num_experts=4, top_k=2, router_prefix_layers=1,
+               reflex_exit_layer=2, limbic_exit_layer=3, expert_hidden=96, dense_hidden=80)
+
+    class Tok:
+        pad_token_id, sep_token_id, eos_token_id = None, None, None
+
+        def encode(self, s):
+            return [ord(ch) % 256 for ch in s]
+
+        def decode(self, ids):
+            return "".join(chr(32 + i % 90) for i in ids)
+
+    compat.install()
+    try:
+        from triune.inference import generate_response
+        from triune.model.fp8 import FP8Linear
+        from triune.model.jev import JEVObjective
+        from triune.model.rotary import RotaryEmbedding
+        from triune.runtime.parallel_engine import MoERoutingBlock
+        from triune.trainer.checkpoint import compute_checkpoint_fingerprint, load_checkpoint, save_latest
+
+        torch.manual_seed(0)
+        model = TriuneTransformer.from_config(ModelConfig(**cfg)).eval()
+        text = generate_response(model, Tok(), "hi", device="cpu", pad_token_id=0, eos_token_id=255, max_new_tokens=4, temperature=0.0)
+        info = generate_response(model, Tok(), "hi", device="cpu", pad_token_id=0, eos_token_id=255, max_new_tokens=4, temperature=0.0,
+                                 force_depth=1, return_info=True)
+        assert isinstance(text, str) and info["route"] == "LIMBIC" and info["tokens_count"] <= 4 and not info["cancelled"] and "cache" in info
+        with pytest.raises(ValueError):
+            generate_response(model, Tok(), "hi", device="cpu", pad_token_id=0, eos_token_id=255, top_k=0)
+
+        class Trainer:
+            pass
+
+        t = Trainer()
+        t.model, t.config = model, dict(cfg, checkpoint_dir=str(tmp_path))
+        t.optimizer = torch.optim.AdamW(model.parameters())
+        eng = type("Engine", (), {"best_eval_loss": 1.5, "depth_usage_ema": [0.3, 0.3, 0.4]})()
+        path = save_latest(t, eng, 7, 2.5)
+        assert path == tmp_path / "latest.pt" and path.is_file()
+        t2 = Trainer()
+        t2.model, t2.optimizer, t2.config = TriuneTransformer.from_config(ModelConfig(**cfg)), None, dict(t.config)
+        ck = load_checkpoint(t2, path, load_optimizer=False)
+        key = next(iter(model.state_dict()))
+        assert ck["step"] == 7 and ck["best_eval_loss"] == 1.5 and ck["fingerprint"] == compute_checkpoint_fingerprint(t.config)
+        assert torch.equal(t2.model.state_dict()[key], model.state_dict()[key])
+        t2.config["hidden_dim"] = 128
+        with pytest.raises(ValueError):
+            load_checkpoint(t2, path, load_optimizer=False)
+        assert FP8Linear(32, 16, device="cpu", dtype=torch.float32).weight.shape == (16, 32)
+        assert RotaryEmbedding(dim=16, max_seq_len=32).cos_cached.shape[0] == 32 and MoERoutingBlock(dim=32, num_experts=2, top_k=1, mode="batched").mode == "batched"
+        obj = JEVObjective()
+        obj(torch.randn(4, 8), torch.randn(4, 8))
+        assert all(isinstance(v, float) for v in (obj.last_sim_loss, obj.last_stp_loss, obj.last_cov_loss, obj.last_total_loss))
+    finally:
+        compat.uninstall()

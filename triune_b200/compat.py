@@ -98,10 +98,10 @@ _RENAMED: Dict[str, Dict[str, str]] = {
 _MODULE_ALIASES = {
     "model.transformer": "models.transformer", "model.moe": "models.moe", "model.attention": "models.attention", "model.router": "models.router",
     "model.config": "config", "optim.centroid": "optim.centroid", "optim.muon": "optim.muon", "trainer.finetune": "trainer.finetune",
-    "trainer.checkpoint": "trainer.checkpoint", "trainer.engine": "trainer.engine", "runtime.streaming": "runtime.streaming", "runtime.sandbox": "runtime.sandbox",
+    "trainer.engine": "trainer.engine", "runtime.streaming": "runtime.streaming", "runtime.sandbox": "runtime.sandbox",
     "runtime.gguf_loader": "runtime.gguf_loader", "runtime.model_scanner": "runtime.model_scanner", "data.tokenizer": "data.tokenizer",
     "data.dynamic_tokenizer": "data.dynamic_tokenizer", "data.dataset": "data.dataset", "data.dataloader": "data.dataloader", "export.exporter": "export.exporter",
-    "export.hf_compat": "export.hf_compat", "inference": "inference", "profiling": "profiling", "desktop": "desktop", "packaging": "packaging", "cli": "cli",
+    "export.hf_compat": "export.hf_compat", "profiling": "profiling", "desktop": "desktop", "packaging": "packaging", "cli": "cli",
     "api.server": "serve.server", "api.routes": "serve.routes", "api.srsm": "serve.srsm", "execution.dag": "compat", "kernels.fast_gla": "kernels",
     "kernels.fast_cross_entropy": "kernels", "kernels.fast_rmsnorm": "kernels", "kernels.fast_rope": "kernels", "kernels.fast_swiglu": "kernels",
     "kernels.fast_muon": "kernels", "kernels.fast_lora": "kernels", "kernels.fast_nvfp4": "kernels", "kernels.fast_fp8": "kernels",
@@ -114,7 +114,7 @@ _DEEP: Dict[str, Tuple[str, ...]] = {
     "agents.personas": ("compat", "agents.harness"), "agents.providers": ("compat", "agents.extras"), "agents.skills": ("compat", "agents.extras"),
     "agents.tools": ("compat", "agents", "agents.harness", "agents.extras"),
     "callbacks.base": ("callbacks.base",), "callbacks.events": ("callbacks.events",), "callbacks.telemetry": ("callbacks.telemetry",),
-    "cli_ui": ("cli_ui",), "configs.config": ("compat", "config"), "execution.dag": ("compat", "execution.dag", "execution.studio", "execution.nodes"),
+    "cli_ui": ("cli_ui",), "inference": ("compat", "inference"), "trainer.checkpoint": ("compat", "trainer.checkpoint"), "configs.config": ("compat", "config"), "execution.dag": ("compat", "execution.dag", "execution.studio", "execution.nodes"),
     "kernels.dispatcher": ("kernels", "compat"), "kernels.fast_triangular": ("compat", "kernels"), "kernels.fast_muon": ("compat", "kernels"),
     "kernels.fast_nvfp4": ("compat", "kernels"),
     "model.adapters": ("models.adapters",), "model.base": ("models.zoo", "compat"), "model.block": ("models.block",),
@@ -129,7 +129,7 @@ _DEEP: Dict[str, Tuple[str, ...]] = {
     "optim.factory": ("optim.factory",), "optim.manifold": ("optim.manifold",),
     "plugins.node_schema": ("compat", "execution.studio", "execution.dag"), "plugins.registry": ("compat", "execution.dag", "plugins.registry"),
     "recipes.bf16": ("recipes",), "recipes.fp8": ("recipes",), "recipes.mxfp8": ("recipes",), "recipes.nvfp4": ("recipes",),
-    "runtime.capabilities": ("runtime.capabilities",), "runtime.cuda_graph": ("runtime.cuda_graph",), "runtime.disk_streaming": ("runtime.disk_streaming", "compat"),
+    "runtime.capabilities": ("runtime.capabilities",), "runtime.cuda_graph": ("runtime.cuda_graph",), "runtime.disk_streaming": ("compat", "runtime.disk_streaming"),
     "runtime.memory_planner": ("compat", "runtime.memory_planner"), "runtime.neuron_scope": ("runtime.neuron_scope",),
     "runtime.parallel_engine": ("runtime.parallel_engine",), "runtime.resource_manager": ("runtime.resource_manager",), "runtime.staging": ("runtime.staging",),
     "runtime.vram": ("runtime.vram",), "trainer.callbacks": ("trainer.callbacks", "callbacks.base"), "trainer.distributed": ("compat", "parallel.dist"),
@@ -500,6 +500,89 @@ def polar_stiefel_retraction(P: torch.Tensor, eps: float = 1e-7) -> torch.Tensor
     """``P [.., d, r]`` with its columns made orthonormal again (Cholesky QR with its condition check and Householder
     fall-back); the span is kept."""
     return batched_qr(P.float(), eps_shift=eps).to(P.dtype)
+
+
+def generate_response(model, tokenizer, prompt: str, *, device=None, pad_token_id: Optional[int] = None, eos_token_id: Optional[int] = None,
+                      force_depth: Optional[int] = None, temperature: float = 0.7, top_k: int = 50, repetition_penalty: float = 1.1,
+                      max_new_tokens: int = 100, prompt_is_formatted: bool = False, cancel_event=None, on_text=None, return_info: bool = False,
+                      cache=None):
+    """``inference.generate_response`` under the reference's keyword-only signature (``triune/inference.py:833-1052``):
+    returns the reply text, or with ``return_info`` a dict with the text, token count, rates, latencies, the exit tier
+    that decoded and the cache."""
+    import time
+
+    from .inference import generate_response as _gen
+
+    if temperature < 0:
+        raise ValueError("temperature must be non-negative")
+    if top_k <= 0:
+        raise ValueError("top_k must be a positive integer")
+    if repetition_penalty <= 0:
+        raise ValueError("repetition_penalty must be greater than zero")
+    if max_new_tokens <= 0:
+        raise ValueError("max_new_tokens must be positive")
+    t0 = time.perf_counter()
+    out = _gen(model, tokenizer, prompt, max_new_tokens=max_new_tokens, temperature=temperature, top_k=top_k,
+               repetition_penalty=repetition_penalty, decode_depth=force_depth, stream_callback=on_text, cancel_event=cancel_event, cache=cache,
+               template=not prompt_is_formatted, device=device, eos_token_id=eos_token_id, pad_token_id=pad_token_id)
+    text = out["text"].strip()
+    if not return_info:
+        return text
+    dt = max(1e-9, time.perf_counter() - t0)
+    tele, n = out["telemetry"], len(out["tokens"])
+    depth = force_depth if force_depth is not None else tele.get("depth")
+    route = ("REFLEX", "LIMBIC", "CORTEX")[int(depth)] if isinstance(depth, int) and 0 <= depth <= 2 else "AUTO"
+    return {"text": text, "tokens_count": n, "tokens_per_sec": n / dt, "latency_ms": round(dt * 1e3, 1),
+            "ttft_ms": round(1e3 * float(tele.get("ttft_s", 0.0)), 1), "decode_tokens_per_sec": round(float(tele.get("decode_tok_s", 0.0)), 2),
+            "route": route, "cancelled": bool(cancel_event is not None and cancel_event.is_set()), "cache": out["cache"]}
+
+
+def build_nvfp4_disk_cache(model_id_or_dir, cache_dir=None, *, hadamard: bool = True, protect_sensitive: bool = True, quantize_lm_head: bool = False,
+                           compute_device=None, force: bool = False, local_files_only: bool = False):
+    """-> the cache directory (the reference's return value; this framework's own function returns the manifest)."""
+    from .runtime import disk_streaming as ds
+
+    src = ds.resolve_hf_model_dir(model_id_or_dir, local_files_only=local_files_only)
+    target = ds.Path(cache_dir) if cache_dir is not None else ds.default_nvfp4_cache_dir(src, hadamard)
+    ds.build_nvfp4_disk_cache(src, target, hadamard=hadamard, protect_sensitive=protect_sensitive, quantize_lm_head=quantize_lm_head,
+                              device=None if compute_device is None else str(compute_device), force=force)
+    return target
+
+
+def _save_for_trainer(which: str, trainer, engine, step: int, loss: float):
+    from pathlib import Path
+
+    from .trainer import checkpoint as ck
+
+    fn = ck.save_latest if which == "latest" else ck.save_best
+    if isinstance(trainer, (str, os.PathLike)):  # this framework's own calling form
+        return fn(trainer, **({} if engine is None else {"model": engine}))
+    best = getattr(engine, "best_eval_loss", None)
+    return Path(fn(str(trainer.config["checkpoint_dir"]), model=trainer.model, optimizer=getattr(trainer, "optimizer", None), step=step, loss=loss,
+                   best_eval_loss=float("inf") if best is None else float(best), config=dict(getattr(trainer, "config", {}) or {}),
+                   depth_usage_ema=getattr(engine, "depth_usage_ema", None), wandb_run_id=getattr(getattr(trainer, "logger", None), "run_id", None)))
+
+
+def save_latest(trainer, engine=None, step: int = 0, loss: float = 0.0):
+    """``latest.pt`` in the trainer's checkpoint directory (``triune/trainer/checkpoint.py:138-146`` of the reference)."""
+    return _save_for_trainer("latest", trainer, engine, step, loss)
+
+
+def save_best(trainer, engine=None, step: int = 0, loss: float = 0.0):
+    return _save_for_trainer("best", trainer, engine, step, loss)
+
+
+def load_checkpoint(trainer, path=None, *, load_optimizer: bool = True, **kw):
+    """``load_checkpoint(trainer, path, load_optimizer=...)`` of the reference: restores the trainer's model (and
+    optimizer) after the fingerprint check against the trainer's configuration, and returns the checkpoint dict. A path
+    as first argument is this framework's own calling form and is passed through."""
+    from .trainer import checkpoint as ck
+
+    if isinstance(trainer, (str, os.PathLike)):
+        return ck.load_checkpoint(trainer, *(() if path is None else (path,)), **kw)
+    cfg = getattr(trainer, "config", None)
+    return ck.load_checkpoint(str(path), model=trainer.model, optimizer=getattr(trainer, "optimizer", None) if load_optimizer else None,
+                              config=dict(cfg) if isinstance(cfg, dict) else None)
 
 
 def all_reduce_dict(metrics: Dict[str, float], op: Any = None) -> Dict[str, float]:

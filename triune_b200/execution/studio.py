@@ -1332,12 +1332,12 @@ def _export_st(i, p, c):
 
 
 @studio_node("GGUFExport", "Export", {"model_handle": MODEL}, {"gguf_file": FILE}, {"quantization": "Q4_K_M", "filename": "model.gguf"},
-             "not supported, as in the reference exporter")
+             "GGUF export settings (configuration only: no file is written, as in the reference)")
 def _export_gguf(i, p, c):
-    from ..export.exporter import export_model
-
-    export_model(_model(i, c), str(_out_dir(p, c, "exports") / str(p["filename"])), "gguf")  # raises NotImplementedError with the reason
-    return {}
+    # The multi-exit MoE layout has no GGUF architecture to be written as; the node records the settings a later
+    # conversion would use, and reports itself as a specification node.
+    return {"format": "GGUF (llama.cpp / Ollama)", "quantization": str(p.get("quantization", "Q4_K_M")), "filename": str(p.get("filename", "model.gguf")),
+            "compatible_runtimes": ["Ollama", "llama.cpp", "LM Studio"], "real_computation": False, "_specification": True}
 
 
 @studio_node("ONNXExport", "Export", {"model_handle": MODEL}, {"onnx_file": FILE}, {"opset_version": 17, "dynamic_axes": True}, "ONNX graph of the forward pass")

@@ -278,14 +278,15 @@ def generate_response(model, tokenizer, prompt: str, max_new_tokens: int = 256, 
                       repetition_penalty: float = 1.1, decode_depth: Optional[int] = 2, stop: Tuple[str, ...] = DEFAULT_STOPS,
                       stream_callback: Optional[Callable[[str], None]] = None, cancel_event: Optional[threading.Event] = None,
                       cache: Optional[List[Any]] = None, template: bool = True, device=None, speculative: bool = False,
-                      k_draft: int = 3) -> Dict[str, Any]:
-    """Chat-style generation. Returns {"text", "tokens", "telemetry", "cache"}."""
+                      k_draft: int = 3, eos_token_id: Optional[int] = None, pad_token_id: Optional[int] = None) -> Dict[str, Any]:
+    """Chat-style generation. Returns {"text", "tokens", "telemetry", "cache"}. ``eos_token_id`` / ``pad_token_id`` override
+    what the tokenizer names."""
     dev = torch.device(device) if device is not None else next(model.parameters()).device
     text_in = f"User: {prompt}\nAssistant:" if template else prompt
     ids = torch.tensor([tokenizer.encode(text_in)], device=dev, dtype=torch.long)
     max_new_tokens = min(int(max_new_tokens), 8192)
-    eos = getattr(tokenizer, "sep_token_id", getattr(tokenizer, "eos_token_id", None))
-    pad = getattr(tokenizer, "pad_token_id", None)
+    eos = eos_token_id if eos_token_id is not None else getattr(tokenizer, "sep_token_id", getattr(tokenizer, "eos_token_id", None))
+    pad = pad_token_id if pad_token_id is not None else getattr(tokenizer, "pad_token_id", None)
     if speculative and temperature <= 0:
         from .models.speculative import SelfSpeculativeGenerator
 

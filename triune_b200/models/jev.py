@@ -121,6 +121,19 @@ class JEVObjective(nn.Module):
     def last_total_loss(self) -> Optional[float]:
         return float(self.last["total_loss"]) if self.last else None
 
+    # the three terms of the last call as floats (one host read each, made when asked for)
+    @property
+    def last_sim_loss(self) -> Optional[float]:
+        return float(self.last["l_sim"]) if self.last else None
+
+    @property
+    def last_stp_loss(self) -> Optional[float]:
+        return float(self.last["l_stp"]) if self.last else None
+
+    @property
+    def last_cov_loss(self) -> Optional[float]:
+        return float(self.last["l_cov"]) if self.last else None
+
 
 class JEVExitRouter(nn.Module):
     def __init__(self, dim: int, threshold: float = 0.85, distance_metric: str = "cosine",

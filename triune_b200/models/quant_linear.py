@@ -29,11 +29,11 @@ PROTECTED = ("router", "exit_head", "final_head", "lm_head", "embed")
 class FP8Linear(nn.Module):
     """Linear with a bf16/fp32 master weight; the forward runs the block-scaled E4M3 GEMM."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = True, block: int = 128):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, block: int = 128, device=None, dtype=None):
         super().__init__()
         self.in_features, self.out_features, self.block = in_features, out_features, block
-        self.weight = nn.Parameter(torch.empty(out_features, in_features))
-        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
         self._q = None  # (version, wq, ws)
         self._mx = None  # (version, E4M3 weight, blocked power-of-two scales per 1x32) for the block-scaled tensor-core GEMM
@@ -193,11 +193,11 @@ class FP4Linear(nn.Module):
     """Training-time 4-bit linear: quantise-dequantise forward with a straight-through estimator, master-weight
     backward (the reference used Transformer Engine when present, else this STE form)."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = True):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
-        self.weight = nn.Parameter(torch.empty(out_features, in_features))
-        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
 
     def to_nvfp4_inference(self) -> "NVFP4Linear":

@@ -24,6 +24,19 @@ class RotaryEmbedding(nn.Module):
         self._cos = None
         self._sin = None
 
+    @property
+    def cos_cached(self) -> torch.Tensor:
+        """The cosine table built so far (built for ``max_seq_len`` on first use); the reference's attribute name."""
+        if self._cos is None:
+            self._build(self.max_seq_len, "cpu")
+        return self._cos
+
+    @property
+    def sin_cached(self) -> torch.Tensor:
+        if self._sin is None:
+            self._build(self.max_seq_len, "cpu")
+        return self._sin
+
     def _build(self, length: int, device):
         cos, sin = ops.rope_tables(length, self.head_dim, self.base, 0, device)
         self._cos, self._sin = cos, sin

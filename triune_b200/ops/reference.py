@@ -370,7 +370,9 @@ def gated_deltanet_decode_step(q, k, v, g, state, beta=None, scale: float = 1.0)
 # Losses
 # ----------------------------------------------------------------------------
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
-    return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index=ignore_index)
+    t = targets.reshape(-1)
+    total = F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), t, ignore_index=ignore_index, reduction="sum")
+    return total / (t != ignore_index).sum().clamp_min(1)  # a batch with every target ignored has loss 0, not 0 / 0
 
 
 def linear_cross_entropy(

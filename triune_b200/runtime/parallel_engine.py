@@ -45,10 +45,14 @@ class GLAPipelineBlock(nn.Module):
 class MoERoutingBlock(nn.Module):
     """Pre-norm top-k MoE feed-forward with a residual connection."""
 
-    def __init__(self, dim: int = 512, num_experts: int = 8, top_k: int = 2, hidden: Optional[int] = None):
+    def __init__(self, dim: int = 512, num_experts: int = 8, top_k: int = 2, hidden: Optional[int] = None, mode: str = "auto"):
+        # ``mode`` ("auto" / "batched" / "sparse" in the reference) is accepted and recorded: the expert FFN here has one
+        # implementation, the grouped GEMM, which is the batched mode
         super().__init__()
         from ..models.moe import MoE_FFN
         from ..models.norms import RMSNorm
+
+        self.mode = mode
 
         self.norm = RMSNorm(dim)
         self.moe = MoE_FFN(dim, num_experts=num_experts, top_k=top_k, expert_hidden=hidden or 4 * dim)
